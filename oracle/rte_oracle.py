@@ -1,0 +1,645 @@
+"""CPU oracle for the ``recursive_macro`` / ``dense_exact`` training step.
+
+TEST INFRASTRUCTURE ONLY.  This file restates, in plain single-process PyTorch
+(CPU, fp32, autograd), the algorithm of the reference "Recursive Training
+Engine" for the one path this repository accelerates.  Nothing in the product
+package imports it; only the test-suite, the smoke entry and the benchmark's
+CPU-baseline leg do, and there only as the checker / the timed baseline.
+
+Parity status: PINNED.  ``tests/golden/make_golden.py`` imports the reference
+package in the build container, runs it on seeded inputs and stores its
+outputs, losses, gradients and a 20-step loss curve; ``tests/test_oracle_golden.py``
+checks this restatement against those fixtures.
+
+Every function cites the reference file:line it follows (paths relative to the
+reference project's ``src/recursive_training_engine``).
+
+Parameters travel as a flat ``dict[str, Tensor]`` using the reference's own
+``state_dict`` names (``embed.weight``, ``prelude.0.attn.wqkv.weight``,
+``core.attn.wqkv`` ...), so a checkpoint of either side loads into the other.
+"""
+from __future__ import annotations
+
+import math
+from dataclasses import dataclass, field
+from typing import Any
+
+import torch
+import torch.nn.functional as F
+
+# --------------------------------------------------------------------------
+# configuration (field names = reference config.py:11-81 / 85-336 subset)
+# --------------------------------------------------------------------------
+
+
+@dataclass
+class ModelCfg:
+    vocab_size: int = 2048
+    d_model: int = 128
+    n_heads: int = 4
+    d_ff: int = 512
+    n_dense_layers: int = 4
+    n_prelude: int = 1
+    n_coda: int = 1
+    t_max: int = 4
+    depth_choices: tuple = (1, 2, 4)
+    attn_banks: int = 1
+    ffn_banks: int = 1
+    head_groups: int = 4
+    ffn_groups: int = 8
+    active_head_groups: int = 2
+    active_ffn_groups: int = 2
+    recipe_count: int = 5
+    macro_rank: int = 32
+    macro_update_scale: float = 0.05
+    router_hidden: int | None = None
+    topology: str = "recursive"
+
+    @property
+    def router_hidden_dim(self) -> int:  # routing.py:50
+        return self.router_hidden or max(32, self.d_model)
+
+
+@dataclass
+class TrainCfg:
+    mode: str = "recursive_macro"
+    lr: float = 1e-3
+    weight_decay: float = 0.1
+    batch_size: int = 8
+    seq_len: int = 64
+    seed: int = 0
+    fixed_recipe: int | None = None
+    fixed_depth: int | None = 4
+    audit_fixed_count_per_batch: int | None = None  # None + p=0 -> no audit
+    audit_mode: str = "gradient_corrected"
+    audit_residual_clip: float | None = None
+    lambda_depth: float = 1e-4
+    lambda_load: float = 1e-2
+    lambda_cover: float = 1e-2
+    lambda_kl: float = 1e-2
+    lambda_delta_dir: float = 2.0
+    lambda_delta_rms: float = 2.0
+    lambda_endpoint_normed: float = 1.0
+    lambda_endpoint_raw: float = 0.05
+    distill_temperature: float = 2.0
+    coverage_min: float = 0.01
+    coverage_beta: float = 0.98
+    disable_router_aux: bool = False
+    grad_clip_norm: float | None = None
+    betas: tuple = (0.9, 0.999)
+    eps: float = 1e-8
+
+
+# --------------------------------------------------------------------------
+# recipes (recipes.py:65-107)
+# --------------------------------------------------------------------------
+
+
+@dataclass(frozen=True)
+class Recipe:
+    recipe_id: int
+    attention_banks: tuple
+    ffn_banks: tuple
+    head_groups: tuple
+    ffn_groups: tuple
+
+
+def build_recipes(cfg: ModelCfg) -> list[Recipe]:
+    """recipes.py:65-100: recipe 0 is the dense fallback, the rest rotate
+    through head/ffn slots and banks."""
+    out = [
+        Recipe(0, tuple(range(cfg.attn_banks)), tuple(range(cfg.ffn_banks)),
+               tuple(range(cfg.head_groups)), tuple(range(cfg.ffn_groups)))
+    ]
+    head_slots = max(1, cfg.head_groups // cfg.active_head_groups)
+    ffn_slots = max(1, cfg.ffn_groups // cfg.active_ffn_groups)
+    for idx in range(cfg.recipe_count - 1):
+        head_slot, ffn_slot = idx % head_slots, idx % ffn_slots
+        attn_bank = (idx // head_slots) % cfg.attn_banks
+        ffn_bank = (idx // ffn_slots) % cfg.ffn_banks
+        hs, fs = head_slot * cfg.active_head_groups, ffn_slot * cfg.active_ffn_groups
+        out.append(Recipe(
+            idx + 1, (attn_bank,), (ffn_bank,),
+            tuple((hs + j) % cfg.head_groups for j in range(cfg.active_head_groups)),
+            tuple((fs + j) % cfg.ffn_groups for j in range(cfg.active_ffn_groups)),
+        ))
+    return out
+
+
+def recipe_head_cols(cfg: ModelCfg, r: Recipe) -> list[int]:
+    """layers.py:673-682: columns of the active heads, head-major."""
+    hpg, hd = cfg.n_heads // cfg.head_groups, cfg.d_model // cfg.n_heads
+    cols: list[int] = []
+    for g in r.head_groups:
+        for head in range(g * hpg, (g + 1) * hpg):
+            cols.extend(range(head * hd, (head + 1) * hd))
+    return cols
+
+
+def recipe_ffn_cols(cfg: ModelCfg, r: Recipe) -> list[int]:
+    """layers.py:744-749: hidden units of the active FFN slabs."""
+    slab = cfg.d_ff // cfg.ffn_groups
+    cols: list[int] = []
+    for g in r.ffn_groups:
+        cols.extend(range(g * slab, (g + 1) * slab))
+    return cols
+
+
+def active_touch_table(cfg: ModelCfg) -> torch.Tensor:
+    """recipes.py:102-107,139-145."""
+    d = cfg.d_model
+    vals = []
+    for r in build_recipes(cfg):
+        attn = len(r.attention_banks) * 4 * d * d * len(r.head_groups) / cfg.head_groups
+        ffn = len(r.ffn_banks) * 3 * d * cfg.d_ff * len(r.ffn_groups) / cfg.ffn_groups
+        vals.append(float(attn + ffn))
+    return torch.tensor(vals, dtype=torch.float32)
+
+
+# --------------------------------------------------------------------------
+# parameter inventory and the benchmark's seeded initialisation
+# --------------------------------------------------------------------------
+
+
+def _block_shapes(prefix: str, cfg: ModelCfg) -> list[tuple[str, tuple]]:
+    d, f = cfg.d_model, cfg.d_ff
+    return [
+        (f"{prefix}.norm1.weight", (d,)),
+        (f"{prefix}.attn.wqkv.weight", (3 * d, d)),
+        (f"{prefix}.attn.wo.weight", (d, d)),
+        (f"{prefix}.norm2.weight", (d,)),
+        (f"{prefix}.mlp.wug.weight", (2 * f, d)),
+        (f"{prefix}.mlp.wd.weight", (d, f)),
+    ]
+
+
+def param_shapes(cfg: ModelCfg) -> list[tuple[str, tuple]]:
+    """Names/shapes in the reference's ``named_parameters()`` order
+    (models.py:125-151; dense: models.py:78-93)."""
+    d, f, v = cfg.d_model, cfg.d_ff, cfg.vocab_size
+    if cfg.topology == "dense":
+        out = [("embed.weight", (v, d))]
+        for i in range(cfg.n_dense_layers):
+            out += _block_shapes(f"blocks.{i}", cfg)
+        return out + [("final_norm.weight", (d,))]
+    hid, r, k, t, m = cfg.router_hidden_dim, cfg.recipe_count, len(cfg.depth_choices), cfg.t_max, cfg.macro_rank
+    head_slots = max(1, cfg.head_groups // cfg.active_head_groups)
+    ffn_slots = max(1, cfg.ffn_groups // cfg.active_ffn_groups)
+    out = [("embed.weight", (v, d))]
+    for i in range(cfg.n_prelude):
+        out += _block_shapes(f"prelude.{i}", cfg)
+    out += [("router.pass_recipe_bias", (t, r)), ("router.pass_factor_bias", (t, hid))]
+    for name, o in (("recipe_mlp", r),):
+        out += [(f"router.{name}.0.weight", (hid, d)), (f"router.{name}.0.bias", (hid,)),
+                (f"router.{name}.2.weight", (o, hid)), (f"router.{name}.2.bias", (o,))]
+    out += [("router.factor_mlp.0.weight", (hid, d)), ("router.factor_mlp.0.bias", (hid,)),
+            ("router.factor_mlp.2.weight", (hid, hid)), ("router.factor_mlp.2.bias", (hid,))]
+    for name, o in (("attn_bank_head", cfg.attn_banks), ("ffn_bank_head", cfg.ffn_banks),
+                    ("head_slot_head", head_slots), ("ffn_slot_head", ffn_slots)):
+        out += [(f"router.{name}.weight", (o, hid)), (f"router.{name}.bias", (o,))]
+    out += [("router.depth_mlp.0.weight", (hid, d)), ("router.depth_mlp.0.bias", (hid,)),
+            ("router.depth_mlp.2.weight", (k, hid)), ("router.depth_mlp.2.bias", (k,))]
+    out += [("core.pass_gamma1", (t, d)), ("core.pass_beta1", (t, d)),
+            ("core.pass_gamma2", (t, d)), ("core.pass_beta2", (t, d)),
+            ("core.pass_attn_scale", (t,)), ("core.pass_mlp_scale", (t,)), ("core.alpha_inj", ()),
+            ("core.norm1.weight", (d,)), ("core.attn.wqkv", (cfg.attn_banks, d, 3 * d)),
+            ("core.attn.wo", (cfg.attn_banks, d, d)), ("core.norm2.weight", (d,)),
+            ("core.mlp.wug", (cfg.ffn_banks, d, 2 * f)), ("core.mlp.wd", (cfg.ffn_banks, f, d))]
+    out += [("macro.d_gain", (r, k, d)), ("macro.v", (r, k, 3 * d, m)),
+            ("macro.u", (r, k, m, d)), ("macro.bias", (r, k, d))]
+    for i in range(cfg.n_coda):
+        out += _block_shapes(f"coda.{i}", cfg)
+    out += [("final_norm.weight", (d,))]
+    return out
+
+
+def init_params(cfg: ModelCfg, seed: int = 0, std: float = 0.02) -> dict[str, torch.Tensor]:
+    """The benchmark's weight rule: every tensor with ndim >= 2 ~ N(0, std) drawn
+    from one seeded CPU generator in ``named_parameters()`` order; norm gains and
+    per-pass scales 1, ``alpha_inj`` 0.1 (layers.py:826-827), biases 0."""
+    gen = torch.Generator().manual_seed(seed)
+    params: dict[str, torch.Tensor] = {}
+    for name, shape in param_shapes(cfg):
+        if len(shape) >= 2:
+            params[name] = torch.randn(shape, generator=gen, dtype=torch.float32) * std
+        elif name.endswith("norm1.weight") or name.endswith("norm2.weight") or name.endswith("final_norm.weight") \
+                or name.endswith("pass_attn_scale") or name.endswith("pass_mlp_scale"):
+            params[name] = torch.ones(shape, dtype=torch.float32)
+        elif name == "core.alpha_inj":
+            params[name] = torch.tensor(0.1, dtype=torch.float32)
+        else:
+            params[name] = torch.zeros(shape, dtype=torch.float32)
+    return params
+
+
+def macro_update_scale_buffer(cfg: ModelCfg) -> torch.Tensor:
+    """macro.py:99-108: in the legacy shape ``update_scale`` is a buffer of ones."""
+    return torch.ones(cfg.recipe_count, len(cfg.depth_choices), cfg.d_model)
+
+
+# --------------------------------------------------------------------------
+# synthetic Zipf token stream (stands in for the reference's TinyStories stream)
+# --------------------------------------------------------------------------
+
+
+def zipf_tokens(n: int, vocab: int, seed: int = 0, s: float = 1.1) -> torch.Tensor:
+    ranks = torch.arange(1, vocab + 1, dtype=torch.float64)
+    probs = ranks.pow(-s)
+    probs = (probs / probs.sum()).float()
+    gen = torch.Generator().manual_seed(seed)
+    return torch.multinomial(probs, n, replacement=True, generator=gen)
+
+
+def batches(tokens: torch.Tensor, batch_size: int, seq_len: int):
+    """utils.py:84-99: windows of seq_len+1 with stride seq_len, wrap to 0."""
+    max_start = tokens.numel() - seq_len - 1
+    cursor = 0
+    while True:
+        xs, ys = [], []
+        for _ in range(batch_size):
+            if cursor > max_start:
+                cursor = 0
+            chunk = tokens[cursor: cursor + seq_len + 1]
+            xs.append(chunk[:-1])
+            ys.append(chunk[1:])
+            cursor += seq_len
+        yield torch.stack(xs), torch.stack(ys)
+
+
+# --------------------------------------------------------------------------
+# per-op restatements
+# --------------------------------------------------------------------------
+
+
+def rmsnorm(x: torch.Tensor, weight: torch.Tensor | None = None, eps: float = 1e-5) -> torch.Tensor:
+    """kernels/reference.py:9-17 (weight given) and macro.py:16-18 (no weight)."""
+    n = x * torch.rsqrt(x.float().pow(2).mean(dim=-1, keepdim=True) + eps).to(x.dtype)
+    return n if weight is None else n * weight
+
+
+def rope_tables(seq: int, head_dim: int, base: float = 10000.0) -> tuple[torch.Tensor, torch.Tensor]:
+    """layers.py:36-44: adjacent-pair layout, cos/sin repeated per pair."""
+    inv = 1.0 / (base ** (torch.arange(0, head_dim, 2).float() / head_dim))
+    fr = torch.outer(torch.arange(seq, dtype=torch.float32), inv)
+    emb = torch.repeat_interleave(fr, 2, dim=-1)
+    return emb.cos(), emb.sin()
+
+
+def rope_apply(x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor) -> torch.Tensor:
+    """kernels/reference.py:20-28 for one tensor [..., S, hd]."""
+    x1, x2 = x[..., ::2], x[..., 1::2]
+    rot = torch.stack((-x2, x1), dim=-1).flatten(-2)
+    return x * cos + rot * sin
+
+
+def causal_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor) -> torch.Tensor:
+    """kernels/reference.py:40-41: softmax(q k^T / sqrt(hd) + causal) v on [B,H,S,hd]."""
+    s = q.shape[-2]
+    scores = (q @ k.transpose(-1, -2)) / math.sqrt(q.shape[-1])
+    mask = torch.ones(s, s, dtype=torch.bool).tril()
+    scores = scores.masked_fill(~mask, float("-inf"))
+    return torch.softmax(scores, dim=-1) @ v
+
+
+def dense_attention(x: torch.Tensor, wqkv: torch.Tensor, wo: torch.Tensor, n_heads: int) -> torch.Tensor:
+    """layers.py:64-75: fused QKV (q|k|v, head-major), RoPE, causal attention, wo."""
+    b, s, d = x.shape
+    hd = d // n_heads
+    qkv = (x @ wqkv.t()).view(b, s, 3, n_heads, hd)
+    q, k, v = (t.transpose(1, 2) for t in qkv.unbind(dim=2))
+    cos, sin = rope_tables(s, hd)
+    y = causal_attention(rope_apply(q, cos, sin), rope_apply(k, cos, sin), v)
+    return y.transpose(1, 2).reshape(b, s, d) @ wo.t()
+
+
+def dense_swiglu(x: torch.Tensor, wug: torch.Tensor, wd: torch.Tensor) -> torch.Tensor:
+    """layers.py:85-87: rows [0,F) of wug are *up*, rows [F,2F) are *gate*."""
+    up, gate = (x @ wug.t()).chunk(2, dim=-1)
+    return (up * F.silu(gate)) @ wd.t()
+
+
+def dense_block(p: dict, prefix: str, x: torch.Tensor, n_heads: int) -> torch.Tensor:
+    """layers.py:646-656 (pre-norm block)."""
+    u = x + dense_attention(rmsnorm(x, p[f"{prefix}.norm1.weight"]), p[f"{prefix}.attn.wqkv.weight"],
+                            p[f"{prefix}.attn.wo.weight"], n_heads)
+    return u + dense_swiglu(rmsnorm(u, p[f"{prefix}.norm2.weight"]), p[f"{prefix}.mlp.wug.weight"],
+                            p[f"{prefix}.mlp.wd.weight"])
+
+
+def lm_loss_per_sample(logits: torch.Tensor, targets: torch.Tensor) -> torch.Tensor:
+    """models.py:73-75: per-token CE summed over the sequence."""
+    tok = F.cross_entropy(logits.flatten(0, -2), targets.flatten(), reduction="none")
+    return tok.view_as(targets).sum(dim=-1)
+
+
+def argmax_lowest(x: torch.Tensor) -> torch.Tensor:
+    """Index of the maximum along the last axis; ties go to the LOWEST index
+    (the rule this build fixes; torch CPU argmax also returns the first max)."""
+    mx = x.max(dim=-1, keepdim=True).values
+    idx = torch.arange(x.shape[-1]).expand_as(x)
+    return torch.where(x == mx, idx, torch.full_like(idx, x.shape[-1])).min(dim=-1).values
+
+
+def topk_lowest(x: torch.Tensor, k: int) -> tuple[torch.Tensor, torch.Tensor]:
+    """Top-k along the last axis, descending value, ties to the LOWEST index
+    (stable descending sort).  torch.topk's tie order is unspecified."""
+    order = torch.sort(-x.double(), dim=-1, stable=True).indices[..., :k]
+    return torch.gather(x, -1, order), order
+
+
+def router_forward(p: dict, cfg: ModelCfg, h0: torch.Tensor, fixed_recipe: int | None,
+                   fixed_depth: int | None) -> dict[str, torch.Tensor]:
+    """routing.py:88-188 (temperature 1).  Only the fields the macro step and
+    the audit replay consume are produced."""
+    pooled = h0.mean(dim=1)
+
+    def mlp(name: str) -> torch.Tensor:
+        hid = F.silu(pooled @ p[f"router.{name}.0.weight"].t() + p[f"router.{name}.0.bias"])
+        return hid @ p[f"router.{name}.2.weight"].t() + p[f"router.{name}.2.bias"]
+
+    recipe_logits = mlp("recipe_mlp")
+    depth_logits = mlp("depth_mlp")
+    logits_by_pass = recipe_logits.unsqueeze(1) + p["router.pass_recipe_bias"].unsqueeze(0)
+    recipe_probs = F.softmax(recipe_logits, dim=-1)
+    probs_by_pass = F.softmax(logits_by_pass, dim=-1)
+    depth_probs = F.softmax(depth_logits, dim=-1)
+    b = h0.shape[0]
+    if fixed_recipe is None:
+        recipe_id = argmax_lowest(recipe_probs)
+        recipe_id_by_pass = argmax_lowest(probs_by_pass)
+    else:
+        recipe_id = torch.full((b,), fixed_recipe, dtype=torch.long)
+        recipe_id_by_pass = torch.full((b, cfg.t_max), fixed_recipe, dtype=torch.long)
+    depth_values = torch.tensor(cfg.depth_choices, dtype=torch.long)
+    if fixed_depth is None:
+        depth_id = argmax_lowest(depth_probs)
+    else:
+        depth_id = torch.full((b,), list(cfg.depth_choices).index(fixed_depth), dtype=torch.long)
+    recipe_entropy = -(recipe_probs.clamp_min(1e-9).log() * recipe_probs).sum(-1)
+    depth_entropy = -(depth_probs.clamp_min(1e-9).log() * depth_probs).sum(-1)
+    return dict(
+        recipe_logits=recipe_logits, recipe_probs=recipe_probs, recipe_id=recipe_id,
+        recipe_id_by_pass=recipe_id_by_pass, depth_logits=depth_logits, depth_probs=depth_probs,
+        depth_id=depth_id, depth=depth_values[depth_id],
+        expected_depth=(depth_probs * depth_values.float()).sum(-1),
+        router_entropy=recipe_entropy + depth_entropy,
+    )
+
+
+def macro_phi(p: dict, cfg: ModelCfg, h: torch.Tensor, h0: torch.Tensor, recipe_ids: torch.Tensor,
+              stride_ids: torch.Tensor) -> torch.Tensor:
+    """macro.py:201-236, legacy shape (hidden == rank, no gate, no extra inputs):
+    h + s_cfg * scale * tanh(gain*h + silu([rmsnorm(h), mean_S rmsnorm(h), h0] @ v) @ u + bias)."""
+    gain = p["macro.d_gain"][recipe_ids, stride_ids]
+    v = p["macro.v"][recipe_ids, stride_ids]
+    u = p["macro.u"][recipe_ids, stride_ids]
+    bias = p["macro.bias"][recipe_ids, stride_ids]
+    scale = p.get("macro.update_scale", macro_update_scale_buffer(cfg))[recipe_ids, stride_ids]
+    normed = rmsnorm(h)
+    pooled = normed.mean(dim=1, keepdim=True).expand_as(normed)
+    z = torch.cat([normed, pooled, h0], dim=-1)
+    low = torch.bmm(F.silu(torch.bmm(z, v)), u)
+    update = gain.unsqueeze(1) * h + low + bias.unsqueeze(1)
+    return h + cfg.macro_update_scale * scale.unsqueeze(1) * torch.tanh(update)
+
+
+def stride_ids_for_depths(cfg: ModelCfg, depths: torch.Tensor) -> torch.Tensor:
+    """macro.py:144-146."""
+    dv = torch.tensor(cfg.depth_choices, dtype=torch.long)
+    return (depths.unsqueeze(-1) == dv.unsqueeze(0)).float().argmax(dim=-1)
+
+
+def banked_attention(p: dict, cfg: ModelCfg, x: torch.Tensor, r: Recipe) -> torch.Tensor:
+    """layers.py:702-728: per bank, x @ wqkv[bank][:, cols|cols+d|cols+2d] ([in,out]
+    layout), RoPE, causal attention over the active heads, y @ wo[bank][cols, :];
+    mean over banks."""
+    b, s, d = x.shape
+    hd = d // cfg.n_heads
+    cols = torch.tensor(recipe_head_cols(cfg, r), dtype=torch.long)
+    qkv_cols = torch.cat([cols, cols + d, cols + 2 * d])
+    ad = cols.numel()
+    cos, sin = rope_tables(s, hd)
+    out = x.new_zeros(b, s, d)
+    for bank in r.attention_banks:
+        qkv = x @ p["core.attn.wqkv"][bank][:, qkv_cols]
+        q, k, v = (t.view(b, s, ad // hd, hd).transpose(1, 2) for t in qkv.split(ad, dim=-1))
+        y = causal_attention(rope_apply(q, cos, sin), rope_apply(k, cos, sin), v)
+        out = out + y.transpose(1, 2).reshape(b, s, ad) @ p["core.attn.wo"][bank][cols, :]
+    return out / max(len(r.attention_banks), 1)
+
+
+def banked_swiglu(p: dict, cfg: ModelCfg, x: torch.Tensor, r: Recipe) -> torch.Tensor:
+    """layers.py:765-779."""
+    slabs = torch.tensor(recipe_ffn_cols(cfg, r), dtype=torch.long)
+    gate_cols = torch.cat([slabs, slabs + cfg.d_ff])
+    out = x.new_zeros(*x.shape)
+    for bank in r.ffn_banks:
+        up, gate = (x @ p["core.mlp.wug"][bank][:, gate_cols]).split(slabs.numel(), dim=-1)
+        out = out + (up * F.silu(gate)) @ p["core.mlp.wd"][bank][slabs, :]
+    return out / max(len(r.ffn_banks), 1)
+
+
+def core_step_group(p: dict, cfg: ModelCfg, h: torch.Tensor, h0: torch.Tensor, r: Recipe, t: int) -> torch.Tensor:
+    """layers.py:831-852 (no global corrector): the residual base is h + alpha*h0."""
+    ht = h + p["core.alpha_inj"] * h0
+    n1 = rmsnorm(ht, p["core.norm1.weight"]) * (1.0 + p["core.pass_gamma1"][t]) + p["core.pass_beta1"][t]
+    u = ht + p["core.pass_attn_scale"][t] * banked_attention(p, cfg, n1, r)
+    n2 = rmsnorm(u, p["core.norm2.weight"]) * (1.0 + p["core.pass_gamma2"][t]) + p["core.pass_beta2"][t]
+    return u + p["core.pass_mlp_scale"][t] * banked_swiglu(p, cfg, n2, r)
+
+
+def core_forward_step(p: dict, cfg: ModelCfg, h: torch.Tensor, h0: torch.Tensor, recipe_ids: torch.Tensor,
+                      active: torch.Tensor, t: int) -> torch.Tensor:
+    """layers.py:854-870: samples grouped by recipe, inactive ones pass through."""
+    recipes = build_recipes(cfg)
+    pieces = []
+    for i in range(h.shape[0]):
+        if bool(active[i]):
+            pieces.append(core_step_group(p, cfg, h[i:i + 1], h0[i:i + 1], recipes[int(recipe_ids[i])], t))
+        else:
+            pieces.append(h[i:i + 1])
+    return torch.cat(pieces, dim=0)
+
+
+def coda_logits(p: dict, cfg: ModelCfg, h: torch.Tensor) -> tuple[torch.Tensor, torch.Tensor]:
+    """models.py:185-192: coda blocks, final norm, tied-embedding logits."""
+    for i in range(cfg.n_coda):
+        h = dense_block(p, f"coda.{i}", h, cfg.n_heads)
+    hidden = rmsnorm(h, p["final_norm.weight"])
+    return hidden, hidden @ p["embed.weight"].t()
+
+
+def exact_from_h0(p: dict, cfg: ModelCfg, h0: torch.Tensor, targets: torch.Tensor, route: dict) -> dict:
+    """models.py:416-512 with reused router decisions: t_max banked passes using the
+    per-pass recipe ids, samples with depth <= t frozen."""
+    h = h0
+    for t in range(cfg.t_max):
+        h = core_forward_step(p, cfg, h, h0, route["recipe_id_by_pass"][:, t], route["depth"] > t, t)
+    hidden, logits = coda_logits(p, cfg, h)
+    return dict(recurrent_hidden=h, hidden=hidden, logits=logits,
+                loss_per_sample=lm_loss_per_sample(logits, targets))
+
+
+def forward_macro(p: dict, cfg: ModelCfg, tokens: torch.Tensor, targets: torch.Tensor,
+                  fixed_recipe: int | None = None, fixed_depth: int | None = None) -> dict:
+    """models.py:681-723 (full-vocabulary branch)."""
+    h0 = p["embed.weight"][tokens]
+    for i in range(cfg.n_prelude):
+        h0 = dense_block(p, f"prelude.{i}", h0, cfg.n_heads)
+    route = router_forward(p, cfg, h0, fixed_recipe, fixed_depth)
+    h = macro_phi(p, cfg, h0, h0, route["recipe_id"], stride_ids_for_depths(cfg, route["depth"]))
+    hidden, logits = coda_logits(p, cfg, h)
+    return dict(h0=h0, route=route, recurrent_hidden=h, hidden=hidden, logits=logits,
+                loss_per_sample=lm_loss_per_sample(logits, targets))
+
+
+def forward_dense(p: dict, cfg: ModelCfg, tokens: torch.Tensor, targets: torch.Tensor) -> dict:
+    """models.py:98-122."""
+    x = p["embed.weight"][tokens]
+    for i in range(cfg.n_dense_layers):
+        x = dense_block(p, f"blocks.{i}", x, cfg.n_heads)
+    hidden = rmsnorm(x, p["final_norm.weight"])
+    logits = hidden @ p["embed.weight"].t()
+    return dict(hidden=hidden, logits=logits, loss_per_sample=lm_loss_per_sample(logits, targets))
+
+
+def router_aux_losses(tr: TrainCfg, recipe_probs: torch.Tensor, expected_depth: torch.Tensor,
+                      usage_ema: torch.Tensor) -> dict[str, torch.Tensor]:
+    """metrics.py:97-112."""
+    if tr.disable_router_aux:  # training.py:510-512
+        z = recipe_probs.new_zeros(())
+        return dict(load=z, cover=z, depth=z)
+    r = recipe_probs.shape[-1]
+    load = r * recipe_probs.mean(dim=0).square().sum() - 1.0
+    cover = F.relu(tr.coverage_min - usage_ema).square().sum()
+    return dict(load=tr.lambda_load * load, cover=tr.lambda_cover * cover,
+                depth=tr.lambda_depth * expected_depth.float().mean())
+
+
+def _rms(x: torch.Tensor, dim) -> torch.Tensor:
+    return x.float().pow(2).mean(dim=dim).sqrt()
+
+
+def macro_distill_loss(tr: TrainCfg, hot_hidden, exact_hidden, hot_logits, exact_logits, h0) -> dict:
+    """macro.py:394-469, delta objective (h0 given); rms-trust term off."""
+    exact_hidden, exact_logits, h0 = exact_hidden.detach(), exact_logits.detach(), h0.detach()
+    dp, de = hot_hidden - h0, exact_hidden - h0
+    delta_dir = 1.0 - F.cosine_similarity(dp.flatten(1), de.flatten(1), dim=-1, eps=1e-8).mean()
+    delta_rms = (torch.log(_rms(dp, (1, 2)).clamp_min(1e-8)) - torch.log(_rms(de, (1, 2)).clamp_min(1e-8))).square().mean()
+    endpoint_normed = F.smooth_l1_loss(rmsnorm(hot_hidden), rmsnorm(exact_hidden))
+    endpoint_raw = F.smooth_l1_loss(hot_hidden, exact_hidden)
+    temp = max(float(tr.distill_temperature), 1e-6)
+    exact_logp = F.log_softmax(exact_logits / temp, dim=-1)
+    hot_logp = F.log_softmax(hot_logits / temp, dim=-1)
+    kl = F.kl_div(hot_logp, exact_logp.exp(), reduction="batchmean") * temp ** 2
+    return dict(kl=tr.lambda_kl * kl, delta_dir=tr.lambda_delta_dir * delta_dir,
+                delta_rms=tr.lambda_delta_rms * delta_rms,
+                endpoint_normed=tr.lambda_endpoint_normed * endpoint_normed,
+                endpoint_raw=tr.lambda_endpoint_raw * endpoint_raw)
+
+
+def audit_choice(n: int, k: int, seed: int) -> torch.Tensor:
+    """audit.py:99-116 fixed-count sampler: the first k entries of a seeded
+    permutation (CPU generator), inclusion probability k/n for every sample."""
+    gen = torch.Generator().manual_seed(seed)
+    return torch.randperm(n, generator=gen)[:k]
+
+
+def macro_step_loss(p: dict, cfg: ModelCfg, tr: TrainCfg, tokens: torch.Tensor, targets: torch.Tensor,
+                    step: int, usage_ema: torch.Tensor) -> tuple[torch.Tensor, dict]:
+    """training.py:1336-1392 + audit.py:245-387 (fixed-count sampler,
+    gradient_corrected mode, consistency term off)."""
+    hot = forward_macro(p, cfg, tokens, targets, tr.fixed_recipe, tr.fixed_depth)
+    corrected = hot["loss_per_sample"].clone()
+    aux: dict[str, torch.Tensor] = {}
+    info: dict[str, Any] = dict(hot=hot)
+    k = tr.audit_fixed_count_per_batch or 0
+    if k > 0:
+        b = tokens.shape[0]
+        chosen = audit_choice(b, min(k, b), tr.seed + 10_000 + step)
+        mask = torch.zeros(b, dtype=torch.bool)
+        mask[chosen] = True
+        p_inc = float(min(k, b)) / float(b)
+        route = {key: val[mask] for key, val in hot["route"].items()}
+        exact = exact_from_h0(p, cfg, hot["h0"][mask], targets[mask], route)
+        hot_subset = hot["loss_per_sample"][mask]
+        residual = exact["loss_per_sample"] - hot_subset
+        if tr.audit_residual_clip is not None:
+            residual = residual.clamp(-tr.audit_residual_clip, tr.audit_residual_clip)
+        if tr.audit_mode == "gradient_corrected":
+            corrected[mask] = hot_subset + residual / max(p_inc, 1e-12)
+        aux = macro_distill_loss(tr, hot["recurrent_hidden"][mask], exact["recurrent_hidden"],
+                                 hot["logits"][mask], exact["logits"], hot["h0"][mask])
+        info.update(exact=exact, mask=mask)
+    aux_router = router_aux_losses(tr, hot["route"]["recipe_probs"], hot["route"]["expected_depth"], usage_ema)
+    loss = corrected.mean() / float(targets.shape[1]) + sum(aux.values()) + sum(aux_router.values())
+    info.update(corrected=corrected, aux=aux, aux_router=aux_router)
+    return loss, info
+
+
+def dense_step_loss(p: dict, cfg: ModelCfg, tokens: torch.Tensor, targets: torch.Tensor) -> tuple[torch.Tensor, dict]:
+    """training.py:742-769."""
+    out = forward_dense(p, cfg, tokens, targets)
+    return out["loss_per_sample"].mean() / float(targets.shape[1]), dict(hot=out)
+
+
+def update_usage(usage_ema: torch.Tensor, recipe_ids: torch.Tensor, beta: float) -> torch.Tensor:
+    """recipes.py:119-123."""
+    counts = torch.bincount(recipe_ids.long().flatten(), minlength=usage_ema.numel()).float()
+    return usage_ema * beta + (counts / counts.sum().clamp_min(1.0)) * (1.0 - beta)
+
+
+def adamw_update(param: torch.Tensor, grad: torch.Tensor, m: torch.Tensor, v: torch.Tensor, step: int,
+                 lr: float, wd: float, betas=(0.9, 0.999), eps: float = 1e-8) -> None:
+    """torch.optim.AdamW single-tensor rule (training.py:341-354 builds it with
+    default betas/eps): decoupled decay, bias-corrected moments, in place."""
+    b1, b2 = betas
+    param.mul_(1.0 - lr * wd)
+    m.mul_(b1).add_(grad, alpha=1.0 - b1)
+    v.mul_(b2).addcmul_(grad, grad, value=1.0 - b2)
+    bc1, bc2 = 1.0 - b1 ** step, 1.0 - b2 ** step
+    denom = (v.sqrt() / math.sqrt(bc2)).add_(eps)
+    param.addcdiv_(m, denom, value=-lr / bc1)
+
+
+@dataclass
+class OracleTrainer:
+    """training.py:1336-1476 + 445-468 as a loop over ``step``.  Parameters that
+    received no gradient are skipped by the optimiser exactly as
+    ``torch.optim.AdamW`` skips ``grad is None`` (no decay, no step count)."""
+    cfg: ModelCfg
+    tr: TrainCfg
+    params: dict
+    global_step: int = 0
+    usage_ema: torch.Tensor | None = None
+    opt_state: dict = field(default_factory=dict)
+
+    def __post_init__(self) -> None:
+        if self.usage_ema is None:
+            self.usage_ema = torch.zeros(self.cfg.recipe_count)
+
+    def loss_and_grads(self, tokens: torch.Tensor, targets: torch.Tensor):
+        leaves = {k: v.detach().clone().requires_grad_(True) for k, v in self.params.items()}
+        if self.cfg.topology == "dense":
+            loss, info = dense_step_loss(leaves, self.cfg, tokens, targets)
+        else:
+            loss, info = macro_step_loss(leaves, self.cfg, self.tr, tokens, targets, self.global_step, self.usage_ema)
+        loss.backward()
+        grads = {k: v.grad for k, v in leaves.items() if v.grad is not None}
+        if self.tr.grad_clip_norm is not None:  # training.py:456-462, before the optimiser reads them
+            total = torch.sqrt(sum(g.float().pow(2).sum() for g in grads.values()))
+            coef = min(1.0, float(self.tr.grad_clip_norm / (total + 1e-6)))
+            grads = {k: g * coef for k, g in grads.items()}
+        return loss.detach(), grads, info
+
+    def train_step(self, tokens: torch.Tensor, targets: torch.Tensor) -> float:
+        loss, grads, info = self.loss_and_grads(tokens, targets)
+        for name, g in grads.items():
+            st = self.opt_state.setdefault(name, dict(step=0, m=torch.zeros_like(g), v=torch.zeros_like(g)))
+            st["step"] += 1
+            adamw_update(self.params[name], g, st["m"], st["v"], st["step"], self.tr.lr,
+                         self.tr.weight_decay, self.tr.betas, self.tr.eps)
+        if self.cfg.topology != "dense":
+            self.usage_ema = update_usage(self.usage_ema, info["hot"]["route"]["recipe_id"], self.tr.coverage_beta)
+        self.global_step += 1
+        return float(loss)

@@ -1,0 +1,204 @@
+"""Generate the golden fixtures in this folder from the REFERENCE implementation.
+
+Run in a container that has the reference checkout (it is imported, unmodified,
+from ``$RTE_REFERENCE_SRC``, default ``/root/reference/src``):
+
+    python tests/golden/make_golden.py
+
+The fixtures (`*.npz`, a few tens of KB) are what `tests/test_oracle_golden.py`
+pins the CPU oracle against; the GPU box has no reference checkout, so the
+fixtures are committed.  Inputs are not stored: tokens and weights are
+re-derived from seeds by `oracle/rte_oracle.py` (`zipf_tokens`, `init_params`),
+which this script also uses to load identical weights into the reference.
+"""
+from __future__ import annotations
+
+import os
+import sys
+import tempfile
+from dataclasses import asdict
+from pathlib import Path
+
+import numpy as np
+import torch
+
+HERE = Path(__file__).resolve().parent
+ROOT = HERE.parents[1]
+sys.path.insert(0, str(ROOT))
+sys.path.insert(0, os.environ.get("RTE_REFERENCE_SRC", "/root/reference/src"))
+
+from oracle import rte_oracle as O  # noqa: E402
+from recursive_training_engine import config as RC  # noqa: E402
+from recursive_training_engine.training import TrainEngine  # noqa: E402
+from recursive_training_engine.kernels import reference as RK  # noqa: E402
+
+GOLDEN_CASES = {
+    # BASELINE config 1 (the reference's CPU-runnable case), audit probability 0.
+    "c1_macro": dict(
+        model=dict(vocab_size=2048, d_model=128, n_heads=4, d_ff=512, n_dense_layers=4, n_prelude=1, n_coda=1,
+                   t_max=4, depth_choices=(1, 2, 4), attn_banks=1, ffn_banks=1, head_groups=4, ffn_groups=8,
+                   active_head_groups=2, active_ffn_groups=2, recipe_count=5, macro_rank=32),
+        train=dict(mode="recursive_macro", lr=1e-3, weight_decay=0.1, batch_size=8, seq_len=64, seed=0,
+                   fixed_depth=4, audit_fixed_count_per_batch=None),
+        steps=20,
+    ),
+    # small model with one audited sample per batch, gradient-corrected control variate + distillation terms
+    "small_audit": dict(
+        model=dict(vocab_size=96, d_model=32, n_heads=4, d_ff=64, n_dense_layers=3, n_prelude=1, n_coda=1,
+                   t_max=4, depth_choices=(1, 2, 4), attn_banks=2, ffn_banks=2, head_groups=4, ffn_groups=4,
+                   active_head_groups=2, active_ffn_groups=1, recipe_count=6, macro_rank=8),
+        train=dict(mode="recursive_macro", lr=2e-3, weight_decay=0.1, batch_size=4, seq_len=16, seed=3,
+                   fixed_depth=None, audit_fixed_count_per_batch=1, grad_clip_norm=1.0),
+        steps=6,
+    ),
+    # router decides depth and recipe (no fixed depth), no audit, aux losses on
+    "small_routed": dict(
+        model=dict(vocab_size=96, d_model=32, n_heads=4, d_ff=64, n_dense_layers=3, n_prelude=2, n_coda=1,
+                   t_max=4, depth_choices=(1, 2, 4), attn_banks=1, ffn_banks=1, head_groups=4, ffn_groups=4,
+                   active_head_groups=1, active_ffn_groups=2, recipe_count=4, macro_rank=8),
+        train=dict(mode="recursive_macro", lr=2e-3, weight_decay=0.05, batch_size=6, seq_len=12, seed=5,
+                   fixed_depth=None, audit_fixed_count_per_batch=None),
+        steps=6,
+    ),
+    "small_dense": dict(
+        model=dict(topology="dense", vocab_size=96, d_model=32, n_heads=4, d_ff=64, n_dense_layers=2, n_prelude=1,
+                   n_coda=1, t_max=4, depth_choices=(1, 2, 4), attn_banks=1, ffn_banks=1, head_groups=4,
+                   ffn_groups=4, active_head_groups=1, active_ffn_groups=1, recipe_count=4, macro_rank=8),
+        train=dict(mode="dense_exact", lr=2e-3, weight_decay=0.1, batch_size=4, seq_len=16, seed=7),
+        steps=6,
+    ),
+}
+
+
+def reference_experiment(case: dict, run_dir: str) -> RC.ExperimentConfig:
+    m = dict(case["model"])
+    m.setdefault("topology", "recursive")
+    m["depth_choices"] = list(m["depth_choices"])
+    t = dict(case["train"])
+    audited = t.get("audit_fixed_count_per_batch") is not None
+    p = (t["audit_fixed_count_per_batch"] / t["batch_size"]) if audited else 0.0
+    tr = RC.TrainingConfig(
+        mode=t["mode"], lr=t["lr"], weight_decay=t["weight_decay"], batch_size=t["batch_size"],
+        seq_len=t["seq_len"], seed=t["seed"], precision="fp32", fixed_depth=t.get("fixed_depth"),
+        audit_p_min=p, audit_p_max=p, audit_alpha=0.0, audit_beta=0.0, audit_gamma=0.0,
+        audit_fixed_count_per_batch=t.get("audit_fixed_count_per_batch"),
+        audit_mode="gradient_corrected" if audited else "metric_only",
+        audit_gradient_correction=audited, lambda_cons=0.0, grad_clip_norm=t.get("grad_clip_norm"),
+        fused_optimizer=False, foreach_optimizer=True, allow_tf32=False, log_every=10_000,
+    )
+    return RC.ExperimentConfig(model=RC.ModelConfig(**m), training=tr, run_name="golden", output_dir=run_dir)
+
+
+def oracle_cfgs(case: dict) -> tuple[O.ModelCfg, O.TrainCfg]:
+    return O.ModelCfg(**case["model"]), O.TrainCfg(**case["train"])
+
+
+def load_oracle_init_into_reference(engine: TrainEngine, cfg: O.ModelCfg, seed: int) -> None:
+    model = engine.recursive_model if engine.recursive_model is not None else engine.dense_model
+    init = O.init_params(cfg, seed=seed)
+    names = [n for n, _ in model.named_parameters() if not n.startswith("shortlist_head.")]
+    assert names == [n for n, _ in O.param_shapes(cfg)], "oracle parameter inventory differs from the reference's"
+    with torch.no_grad():
+        for name, param in model.named_parameters():
+            if name in init:
+                assert tuple(param.shape) == tuple(init[name].shape), name
+                param.copy_(init[name])
+
+
+def run_case(name: str, case: dict) -> dict[str, np.ndarray]:
+    cfg, tr = oracle_cfgs(case)
+    out: dict[str, np.ndarray] = {}
+    with tempfile.TemporaryDirectory() as tmp:
+        engine = TrainEngine(reference_experiment(case, tmp), device=torch.device("cpu"))
+        load_oracle_init_into_reference(engine, cfg, seed=tr.seed)
+        model = engine.recursive_model if engine.recursive_model is not None else engine.dense_model
+        stream = O.zipf_tokens(tr.batch_size * tr.seq_len * (case["steps"] + 2) + 1, cfg.vocab_size, seed=tr.seed)
+        it = O.batches(stream, tr.batch_size, tr.seq_len)
+        losses = []
+        for step in range(case["steps"]):
+            tokens, targets = next(it)
+            if step == 0:
+                # gradients of the first step, captured just before the optimizer consumes them
+                captured: dict[str, torch.Tensor] = {}
+                orig = engine.optimizer.step
+
+                def step_and_capture(*a, **k):
+                    for n, prm in model.named_parameters():
+                        if prm.grad is not None:
+                            captured[n] = prm.grad.detach().clone()
+                    return orig(*a, **k)
+
+                engine.optimizer.step = step_and_capture
+                res = engine.train_step((tokens, targets))
+                engine.optimizer.step = orig
+                for n, g in captured.items():
+                    out[f"grad_sumsq/{n}"] = np.float64(g.double().pow(2).sum().item())
+                    out[f"grad_head/{n}"] = g.flatten()[:16].numpy().copy()
+                out["grad_names"] = np.array(sorted(captured), dtype=object).astype(str)
+                hot = res.model_output
+                out["hot_loss_per_sample"] = hot.loss_per_sample.detach().numpy().copy()
+                if hot.meta.router is not None:
+                    out["recipe_id"] = hot.meta.router.recipe_id.numpy().copy()
+                    out["recipe_id_by_pass"] = hot.meta.router.recipe_id_by_pass.numpy().copy()
+                    out["depth"] = hot.meta.router.depth.numpy().copy()
+                    out["recipe_logits"] = hot.meta.router.recipe_logits.detach().numpy().copy()
+                    out["h0_head"] = hot.meta.h0.detach().flatten()[:32].numpy().copy()
+                    out["phi_head"] = hot.meta.recurrent_hidden.detach().flatten()[:32].numpy().copy()
+                out["logits_head"] = hot.logits.detach().flatten()[:32].numpy().copy()
+                if res.audit is not None and res.audit.exact is not None:
+                    out["audit_mask"] = res.audit.audit_mask.numpy().copy()
+                    out["exact_loss_per_sample"] = res.audit.exact.loss_per_sample.detach().numpy().copy()
+                    out["corrected_loss_per_sample"] = res.audit.corrected_loss_per_sample.detach().numpy().copy()
+                    for k_, v_ in res.audit.macro_aux.items():
+                        out[f"macro_aux/{k_}"] = np.float64(float(v_))
+            else:
+                res = engine.train_step((tokens, targets))
+            losses.append(float(res.loss.detach()))
+        out["losses"] = np.array(losses, dtype=np.float64)
+        final = {n: p_.detach() for n, p_ in model.named_parameters()}
+        out["final_param_sumsq"] = np.array(
+            [final[n].double().pow(2).sum().item() for n, _ in O.param_shapes(cfg)], dtype=np.float64)
+        engine.close()
+    print(f"{name}: losses {losses[0]:.6f} -> {losses[-1]:.6f}")
+    return out
+
+
+def per_op_vectors() -> dict[str, np.ndarray]:
+    """Outputs of the reference's stand-alone kernel definitions on seeded inputs."""
+    g = torch.Generator().manual_seed(11)
+    out: dict[str, np.ndarray] = {}
+    x = torch.randn(3, 5, 24, generator=g)
+    w = torch.randn(24, generator=g)
+    out["rmsnorm"] = RK.k_fused_rmsnorm(x, w)[0].numpy()
+    from recursive_training_engine.layers import RotaryEmbedding
+    q = torch.randn(2, 3, 7, 8, generator=g)
+    k = torch.randn(2, 3, 7, 8, generator=g)
+    v = torch.randn(2, 3, 7, 8, generator=g)
+    rq, rk = RotaryEmbedding(8)(q, k)
+    out["rope_q"], out["rope_k"] = rq.numpy(), rk.numpy()
+    out["attn"] = RK.k_flash_causal_dense(rq, rk, v).numpy()
+    logits = torch.randn(4, 6, 17, generator=g)
+    tg = torch.randint(0, 17, (4, 6), generator=g)
+    out["ce"] = RK.k_cross_entropy_unreduced(logits, tg).numpy()
+    out["ce_targets"] = tg.numpy()
+    # AdamW: three steps of torch.optim.AdamW on one tensor (the optimiser the reference builds)
+    p = torch.nn.Parameter(torch.randn(37, generator=g))
+    opt = torch.optim.AdamW([p], lr=1e-2, weight_decay=0.1)
+    grads = torch.randn(3, 37, generator=g)
+    for i in range(3):
+        p.grad = grads[i].clone()
+        opt.step()
+    out["adamw_p"] = p.detach().numpy().copy()
+    return out
+
+
+def main() -> None:
+    torch.set_num_threads(4)
+    for name, case in GOLDEN_CASES.items():
+        np.savez_compressed(HERE / f"{name}.npz", **run_case(name, case))
+    np.savez_compressed(HERE / "per_op.npz", **per_op_vectors())
+    print("written to", HERE)
+
+
+if __name__ == "__main__":
+    main()

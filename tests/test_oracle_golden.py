@@ -1,0 +1,100 @@
+"""Pins the CPU oracle (oracle/rte_oracle.py) against fixtures produced by the
+reference implementation itself (tests/golden/make_golden.py)."""
+from pathlib import Path
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import rte_oracle as O
+from tests.golden.make_golden import GOLDEN_CASES, oracle_cfgs
+
+GOLDEN = Path(__file__).resolve().parent / "golden"
+
+
+def _run(name):
+    case = GOLDEN_CASES[name]
+    cfg, tr = oracle_cfgs(case)
+    gold = np.load(GOLDEN / f"{name}.npz")
+    trainer = O.OracleTrainer(cfg, tr, O.init_params(cfg, seed=tr.seed))
+    stream = O.zipf_tokens(tr.batch_size * tr.seq_len * (case["steps"] + 2) + 1, cfg.vocab_size, seed=tr.seed)
+    it = O.batches(stream, tr.batch_size, tr.seq_len)
+    return case, cfg, tr, gold, trainer, it
+
+
+@pytest.mark.parametrize("name", list(GOLDEN_CASES))
+def test_first_step_matches_reference(name):
+    case, cfg, tr, gold, trainer, it = _run(name)
+    tokens, targets = next(it)
+    loss, grads, info = trainer.loss_and_grads(tokens, targets)
+    assert abs(float(loss) - gold["losses"][0]) <= 2e-5 * max(1.0, abs(gold["losses"][0]))
+    np.testing.assert_allclose(info["hot"]["loss_per_sample"].detach().numpy(), gold["hot_loss_per_sample"],
+                               rtol=2e-5, atol=2e-5)
+    np.testing.assert_allclose(info["hot"]["logits"].detach().flatten()[:32].numpy(), gold["logits_head"],
+                               rtol=1e-4, atol=2e-6)
+    if cfg.topology != "dense":
+        route = info["hot"]["route"]
+        assert np.array_equal(route["recipe_id"].numpy(), gold["recipe_id"])
+        assert np.array_equal(route["recipe_id_by_pass"].numpy(), gold["recipe_id_by_pass"])
+        assert np.array_equal(route["depth"].numpy(), gold["depth"])
+        np.testing.assert_allclose(route["recipe_logits"].detach().numpy(), gold["recipe_logits"], rtol=1e-4, atol=1e-6)
+        np.testing.assert_allclose(info["hot"]["h0"].detach().flatten()[:32].numpy(), gold["h0_head"], rtol=1e-4, atol=1e-6)
+        np.testing.assert_allclose(info["hot"]["recurrent_hidden"].detach().flatten()[:32].numpy(), gold["phi_head"],
+                                   rtol=1e-4, atol=1e-6)
+    if "audit_mask" in gold:
+        assert np.array_equal(info["mask"].numpy(), gold["audit_mask"])
+        np.testing.assert_allclose(info["exact"]["loss_per_sample"].detach().numpy(), gold["exact_loss_per_sample"],
+                                   rtol=2e-5, atol=2e-5)
+        np.testing.assert_allclose(info["corrected"].detach().numpy(), gold["corrected_loss_per_sample"],
+                                   rtol=2e-4, atol=2e-4)
+        for key, val in info["aux"].items():
+            assert abs(float(val) - float(gold[f"macro_aux/{key}"])) <= 1e-5 + 1e-4 * abs(float(gold[f"macro_aux/{key}"])), key
+    # exactly the parameters the reference gave a gradient to, with the same gradients
+    assert sorted(grads) == sorted(str(n) for n in gold["grad_names"])
+    for n, g in grads.items():
+        ref_sumsq = float(gold[f"grad_sumsq/{n}"])
+        assert abs(float(g.double().pow(2).sum()) - ref_sumsq) <= 1e-3 * ref_sumsq + 1e-12, n
+        np.testing.assert_allclose(g.flatten()[:16].numpy(), gold[f"grad_head/{n}"], rtol=2e-3, atol=2e-6, err_msg=n)
+
+
+@pytest.mark.parametrize("name", list(GOLDEN_CASES))
+def test_loss_curve_and_final_weights_match_reference(name):
+    case, cfg, tr, gold, trainer, it = _run(name)
+    losses = [trainer.train_step(*next(it)) for _ in range(case["steps"])]
+    np.testing.assert_allclose(np.array(losses), gold["losses"], rtol=2e-4, atol=2e-5)
+    sumsq = np.array([trainer.params[n].double().pow(2).sum().item() for n, _ in O.param_shapes(cfg)])
+    np.testing.assert_allclose(sumsq, gold["final_param_sumsq"], rtol=2e-4, atol=1e-9)
+
+
+def test_per_op_vectors():
+    gold = np.load(GOLDEN / "per_op.npz")
+    g = torch.Generator().manual_seed(11)
+    x = torch.randn(3, 5, 24, generator=g)
+    w = torch.randn(24, generator=g)
+    np.testing.assert_allclose(O.rmsnorm(x, w).numpy(), gold["rmsnorm"], rtol=1e-6, atol=1e-6)
+    q = torch.randn(2, 3, 7, 8, generator=g)
+    k = torch.randn(2, 3, 7, 8, generator=g)
+    v = torch.randn(2, 3, 7, 8, generator=g)
+    cos, sin = O.rope_tables(7, 8)
+    rq, rk = O.rope_apply(q, cos, sin), O.rope_apply(k, cos, sin)
+    np.testing.assert_allclose(rq.numpy(), gold["rope_q"], rtol=1e-6, atol=1e-6)
+    np.testing.assert_allclose(rk.numpy(), gold["rope_k"], rtol=1e-6, atol=1e-6)
+    np.testing.assert_allclose(O.causal_attention(rq, rk, v).numpy(), gold["attn"], rtol=1e-5, atol=1e-6)
+    logits = torch.randn(4, 6, 17, generator=g)
+    tg = torch.randint(0, 17, (4, 6), generator=g)
+    assert np.array_equal(tg.numpy(), gold["ce_targets"])
+    np.testing.assert_allclose(O.lm_loss_per_sample(logits, tg).numpy(), gold["ce"].sum(-1), rtol=1e-5, atol=1e-5)
+    p = torch.randn(37, generator=g)
+    m, vv = torch.zeros(37), torch.zeros(37)
+    grads = torch.randn(3, 37, generator=g)
+    for i in range(3):
+        O.adamw_update(p, grads[i], m, vv, i + 1, 1e-2, 0.1)
+    np.testing.assert_allclose(p.numpy(), gold["adamw_p"], rtol=1e-6, atol=1e-6)
+
+
+def test_lowest_index_tie_rule():
+    x = torch.tensor([[1.0, 3.0, 3.0, 2.0, 3.0, 0.0], [5.0, 5.0, 5.0, 5.0, 5.0, 5.0]])
+    assert O.argmax_lowest(x).tolist() == [1, 0]
+    vals, idx = O.topk_lowest(x, 4)
+    assert idx.tolist() == [[1, 2, 4, 3], [0, 1, 2, 3]]
+    assert vals.tolist() == [[3.0, 3.0, 3.0, 2.0], [5.0, 5.0, 5.0, 5.0]]
