@@ -1,0 +1,238 @@
+/*
+ * rte_b200.h -- C ABI of the B200 (sm_100a) kernels behind the Recursive
+ * Training Engine's `recursive_macro` / `dense_exact` training step.
+ *
+ * The reference project has no FFI: its seam is a Python operator table
+ * (src/recursive_training_engine/kernels/optimized.py:58-154, definitions in
+ * kernels/reference.py:9-157) plus inline `nn.Linear`/`@`/`bmm` calls in
+ * layers.py / macro.py / models.py and `torch.optim.AdamW`
+ * (training.py:341-354).  Each entry point below names the reference
+ * function(s) whose arithmetic it replaces.
+ *
+ * Conventions
+ *  - plain device pointers, sizes and strides; no framework types.
+ *  - every call is asynchronous on `stream` (a cudaStream_t passed as void*),
+ *    never synchronises, never allocates; scratch memory is passed in.
+ *  - return value: 0 = launched; <0 = argument error (see rte_status_string).
+ *  - `status` arguments point to one device int32 that a kernel sets non-zero
+ *    when a bounded wait ran out or an index was out of range; the host reads
+ *    it when it next synchronises.  May be NULL.
+ *  - bf16 = 16-bit brain float, row-major unless stated; "ld" = row stride in
+ *    elements.  TMA operands need 16-byte aligned bases and ld % 8 == 0.
+ */
+#ifndef RTE_B200_H_
+#define RTE_B200_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef void* rte_stream_t;
+
+enum {
+  RTE_OK = 0,
+  RTE_ERR_BAD_ARG = -1,
+  RTE_ERR_ALIGNMENT = -2,
+  RTE_ERR_TENSOR_MAP = -3,
+  RTE_ERR_LAUNCH = -4,
+  RTE_ERR_UNSUPPORTED = -5,
+  RTE_ERR_NO_DEVICE = -6
+};
+
+/* Name of the backend ("cuda_sm100a_ext") for the reference's
+ * backend_status() manifest block (kernels/optimized.py:27-43). */
+const char* rte_backend_name(void);
+const char* rte_status_string(int code);
+/* Number of SMs of the current device (grid sizing); <0 on error. */
+int rte_device_sm_count(void);
+
+/* ---------------------------------------------------------------- GEMM ---
+ * C[M,N] (+)= A[M,K] * B[N,K]^T on the tcgen05 tensor cores, bf16 inputs,
+ * fp32 accumulation in tensor memory, operands fetched by TMA.
+ * Replaces: nn.Linear of the fused QKV / wo / W_ug / W_d / tied logits
+ * (layers.py:66,75,86-87; models.py:185) and their autograd backward GEMMs.
+ *
+ * a_mn_major = 0: A is stored [M,K] (K contiguous);  1: stored [K,M] (M contiguous).
+ * b_mn_major = 0: B is stored [N,K] (K contiguous);  1: stored [K,N] (N contiguous).
+ * lda / ldb are the row strides of the STORED matrices.
+ */
+enum {
+  RTE_EPI_BF16 = 0,        /* C bf16 = acc                                                   */
+  RTE_EPI_F32 = 1,         /* C f32 = acc (+ R f32 when R != NULL; R may alias C).            */
+                           /* With splits > 1 partial s goes to C + s*split_stride (no R).    */
+  RTE_EPI_SWIGLU_FWD = 2,  /* B rows [n, n+128) = up, [b_pair_offset+n, ..) = gate (N = 2F):  */
+                           /* C2 bf16 [M,2F] = (up | gate), C bf16 [M,F] = up * silu(gate)    */
+  RTE_EPI_SWIGLU_BWD = 3   /* acc = dz [M,F]; R bf16 [M,2F] = saved (up | gate):              */
+                           /* C bf16 [M,2F] = (dz*silu(g) | dz*up*sig(g)*(1+g*(1-sig(g))))    */
+};
+
+typedef struct rte_gemm_args {
+  int32_t M, N, K;
+  const void* A; int32_t lda; int32_t a_mn_major;
+  const void* B; int32_t ldb; int32_t b_mn_major;
+  int32_t epilogue;
+  void* C; int32_t ldc;
+  const void* R; int32_t ldr;
+  void* C2; int32_t ldc2;
+  int32_t b_pair_offset;    /* F for the SwiGLU epilogues, else 0 */
+  int32_t splits;           /* >= 1; > 1 only with RTE_EPI_F32 (split along K) */
+  int64_t split_stride;     /* elements between partial results */
+  int32_t max_ctas;         /* 0 = one CTA per SM */
+  int32_t* status;
+} rte_gemm_args;
+
+int rte_gemm_bf16(const rte_gemm_args* args, rte_stream_t stream);
+
+/* out[i] = (accumulate ? out[i] : 0) + sum_s ws[s*split_stride + i], i < n (deterministic order). */
+int rte_reduce_splits(const float* ws, int32_t splits, int64_t split_stride, int64_t n, float* out,
+                      int32_t accumulate, rte_stream_t stream);
+
+/* ---------------------------------------------------- embedding (models.py:136,693) */
+int rte_embed_fwd(const int64_t* tokens, const float* table, float* out, int32_t n_tokens, int32_t d,
+                  int32_t vocab, int32_t* status, rte_stream_t stream);
+/* dtable[tokens[i], :] += dx[i, :]  (atomic fp32 adds) */
+int rte_embed_bwd(const int64_t* tokens, const float* dx, float* dtable, int32_t n_tokens, int32_t d,
+                  int32_t vocab, int32_t* status, rte_stream_t stream);
+
+/* ------------------------------------------------- RMSNorm (kernels/reference.py:9-17)
+ * y = x * rsqrt(mean(x^2) + eps) * w [* (1 + film_gamma) + film_beta]  (FiLM: layers.py:841-847)
+ * x f32 [rows,d]; y bf16 and/or f32 (either may be NULL); rstd f32 [rows] saved for backward.
+ * w may be NULL (macro.py:16-18).                                                       */
+int rte_rmsnorm_fwd(const float* x, const float* w, const float* film_gamma, const float* film_beta,
+                    void* y_bf16, float* y_f32, float* rstd, int32_t rows, int32_t d, float eps,
+                    rte_stream_t stream);
+/* dx = rmsnorm_backward(dy) + dres;  dy is bf16 (dy_bf16) or f32 (dy_f32), dres f32 or NULL.
+ * dx written as f32 (dx_f32) and/or bf16 (dx_bf16).  dw_partial f32 [grid_rows, d] receives
+ * per-CTA partial sums of dy * xhat (and dfilm_* likewise) -- reduce with rte_colsum_partials.
+ * Returns the number of partial rows written through *n_partials (host value).          */
+int rte_rmsnorm_bwd(const float* x, const float* w, const float* film_gamma, const float* rstd,
+                    const void* dy_bf16, const float* dy_f32, const float* dres,
+                    float* dx_f32, void* dx_bf16, float* dw_partial, float* dgamma_partial,
+                    float* dbeta_partial, int32_t rows, int32_t d, int32_t max_partials,
+                    int32_t* n_partials, rte_stream_t stream);
+/* out[c] = (accumulate ? out[c] : 0) + sum_r partial[r, c] */
+int rte_colsum_partials(const float* partial, int32_t n_rows, int32_t d, float* out, int32_t accumulate,
+                        rte_stream_t stream);
+
+/* --------------------- causal attention with RoPE (layers.py:36-50,64-75; reference.py:20-28,40-41)
+ * qkv bf16 [B*S, 3*d] with columns (q | k | v), head-major inside each; adjacent-pair rotary
+ * embedding (base 10000, positions 0..S-1) applied to q and k inside the kernel; softmax scale
+ * 1/sqrt(head_dim).  y bf16 [B*S, d]; lse f32 [B, H, S] saved for backward.
+ * n_heads may be fewer than d/head_dim when only the first `n_heads` heads of a packed buffer
+ * exist (banked attention, layers.py:702-728): row stride stays `ld_qkv`, section stride `sec`.  */
+int rte_attn_fwd(const void* qkv, int32_t ld_qkv, int32_t sec, void* y, int32_t ld_y, float* lse,
+                 int32_t B, int32_t S, int32_t n_heads, int32_t head_dim, rte_stream_t stream);
+int rte_attn_bwd(const void* qkv, int32_t ld_qkv, int32_t sec, const void* y, const void* dy, int32_t ld_y,
+                 const float* lse, void* dqkv, int32_t B, int32_t S, int32_t n_heads, int32_t head_dim,
+                 rte_stream_t stream);
+
+/* ------------- per-token cross entropy + its gradient (models.py:73-75; training.py:1381-1385)
+ * logits bf16 [rows, V] (ld = ldl).  loss_tok f32 [rows] = logsumexp - logit[target].
+ * If dlogits != NULL: dlogits bf16 [rows, V] = row_weight[row / S] * (softmax - onehot); may
+ * alias logits.                                                                          */
+int rte_ce_fwd_bwd(const void* logits, int32_t ldl, const int64_t* targets, const float* row_weight,
+                   int32_t S, float* loss_tok, void* dlogits, int32_t rows, int32_t V, int32_t* status,
+                   rte_stream_t stream);
+/* out[b] = sum_s in[b*S + s]  (per-sample loss sums, models.py:75) */
+int rte_segment_sum(const float* in, float* out, int32_t n_seg, int32_t seg_len, rte_stream_t stream);
+
+/* ---------------------------------------------- router (routing.py:88-188; metrics.py:97-112)
+ * One decision per sample from pooled = mean_S(h0).  Weights f32 in nn.Linear layout.
+ * out_f f32 [B, RTE_ROUTER_F_STRIDE] and out_i int32 [B, RTE_ROUTER_I_STRIDE] are laid out as the
+ * offsets below say.  argmax ties go to the LOWEST index.  fixed_recipe / fixed_depth_id < 0 = unset. */
+enum { RTE_ROUTER_MAX_R = 32, RTE_ROUTER_MAX_K = 8, RTE_ROUTER_MAX_T = 32 };
+typedef struct rte_router_weights {
+  const float *r_w0, *r_b0, *r_w2, *r_b2;   /* recipe_mlp */
+  const float *d_w0, *d_b0, *d_w2, *d_b2;   /* depth_mlp  */
+  const float* pass_recipe_bias;            /* [T, R] */
+} rte_router_weights;
+typedef struct rte_router_out {
+  float* pooled;         /* [B, d]   */
+  float* r_hidden_pre;   /* [B, hid] pre-activation of recipe_mlp.0 (saved for backward) */
+  float* d_hidden_pre;   /* [B, hid] */
+  float* recipe_logits;  /* [B, R]   */
+  float* recipe_probs;   /* [B, R]   */
+  float* depth_probs;    /* [B, K]   */
+  float* expected_depth; /* [B]      */
+  float* router_entropy; /* [B]      */
+  int32_t* recipe_id;         /* [B]    */
+  int32_t* recipe_id_by_pass; /* [B, T] */
+  int32_t* depth_id;          /* [B]    */
+  int32_t* depth;             /* [B]    */
+} rte_router_out;
+int rte_router_fwd(const float* h0, const rte_router_weights* w, const int32_t* depth_values,
+                   const rte_router_out* out, int32_t B, int32_t S, int32_t d, int32_t hid, int32_t R,
+                   int32_t K, int32_t T, int32_t fixed_recipe, int32_t fixed_depth_id, rte_stream_t stream);
+/* aux[0] = lambda_load * (R * sum_r mean_B(p_r)^2 - 1), aux[1] = lambda_depth * mean_B E[depth]
+ * (metrics.py:103-111).  Backward of both through the two MLPs: weight/bias grads (f32, overwritten)
+ * and dh0[b,s,:] += dpooled[b,:] / S.  scratch f32 >= RTE_ROUTER_MAX_R + B*(2*hid + R + K).      */
+typedef struct rte_router_grads {
+  float *r_w0, *r_b0, *r_w2, *r_b2, *d_w0, *d_b0, *d_w2, *d_b2;
+} rte_router_grads;
+int rte_router_aux_bwd(const rte_router_weights* w, const rte_router_out* fwd, const int32_t* depth_values,
+                       float lambda_load, float lambda_depth, float* aux, const rte_router_grads* grads,
+                       float* dh0, float* scratch, int32_t B, int32_t S, int32_t d, int32_t hid, int32_t R,
+                       int32_t K, rte_stream_t stream);
+
+/* ---------------------------------- top-k with ties to the lowest index (output.py:78; layers.py:602-627)
+ * scores f32 [rows, n]; idx int32 [rows, k] and vals f32 [rows, k] (either may be NULL), descending. */
+int rte_topk_lowest_index(const float* scores, int32_t ld, int32_t rows, int32_t n, int32_t k,
+                          int32_t* idx, float* vals, rte_stream_t stream);
+
+/* ------------------------------------------ macro operator Phi (macro.py:201-236, legacy shape)
+ * out = h + s_cfg * scale[r,k] * tanh(gain[r,k]*h + silu([rmsnorm(h), mean_S rmsnorm(h), h0] @ v[r,k]) @ u[r,k] + bias[r,k])
+ * with h == h0 (models.py:695).  Per-sample (recipe, stride) ids int32.  m = rank <= 64.
+ * Saved for backward: rstd [B*S], pooled [B*d + B*m] (mean_S rmsnorm(h), then its product with
+ * v[d:2d]), act [B*S, m] (pre-activation z @ v).                                             */
+typedef struct rte_phi_params {
+  const float *gain, *v, *u, *bias, *scale;   /* [R,K,d], [R,K,3d,m], [R,K,m,d], [R,K,d], [R,K,d] */
+} rte_phi_params;
+int rte_macro_phi_fwd(const float* h0, const rte_phi_params* p, const int32_t* recipe_id,
+                      const int32_t* stride_id, float s_cfg, float* out, float* rstd, float* pooled,
+                      float* act, int32_t B, int32_t S, int32_t d, int32_t m, int32_t K_strides,
+                      float eps, rte_stream_t stream);
+/* dh0 f32 [B*S,d] (overwritten), parameter grads f32 (zeroed then accumulated, full [R,K,...] tensors).
+ * scratch f32 >= B*S*d + B*S*m + 3*B*d + B*m*d + B*3*d*m.                                           */
+typedef struct rte_phi_grads { float *gain, *v, *u, *bias; } rte_phi_grads;
+int rte_macro_phi_bwd(const float* h0, const float* dout, const rte_phi_params* p, const int32_t* recipe_id,
+                      const int32_t* stride_id, float s_cfg, const float* rstd, const float* pooled,
+                      const float* act, float* dh0, const rte_phi_grads* g, float* scratch, int32_t B,
+                      int32_t S, int32_t d, int32_t m, int32_t R, int32_t K_strides, float eps,
+                      rte_stream_t stream);
+
+/* -------------------------------------------------- fp32 -> bf16 shadow copies of weights */
+int rte_cast_f32_bf16(const float* src, void* dst, int64_t n, rte_stream_t stream);
+int rte_add_f32(float* dst, const float* src, int64_t n, rte_stream_t stream);   /* dst += src */
+int rte_axpy_rows_f32(float* dst, const float* vec, float alpha, int32_t rows, int32_t seg, int32_t d,
+                      rte_stream_t stream);  /* dst[r,:] += alpha * vec[r / seg, :] */
+
+/* ------------------------------- fused multi-tensor AdamW (training.py:341-354,445-468)
+ * torch.optim.AdamW semantics per tensor: p *= 1 - lr*wd; m,v EMA; bias correction with the
+ * tensor's own step count; p -= lr/bc1 * m / (sqrt(v)/sqrt(bc2) + eps).  Tensors absent from the
+ * table are untouched (the reference skips grad-less parameters).  One launch for all tensors.
+ * table: device array of rte_adamw_tensor; lr_table f32 [n_groups] on device (LR schedule is written
+ * there by the host); step_count int32 [n_tensors] on device, incremented by the kernel.
+ * grad_scale: device f32 scalar multiplied into every gradient (clip coefficient / 1/world), or NULL.
+ * bf16_shadow (per tensor, may be NULL) receives the updated weights as bf16 for the next forward.   */
+typedef struct rte_adamw_tensor {
+  float* p; const float* g; float* m; float* v; void* bf16_shadow;
+  int64_t n; int32_t lr_group; int32_t step_slot;
+} rte_adamw_tensor;
+int rte_adamw_multi_tensor(const rte_adamw_tensor* table, int32_t n_tensors, int64_t total_chunks,
+                           const int32_t* chunk_tensor, const int32_t* chunk_index, const float* lr_table,
+                           int32_t* step_count, float beta1, float beta2, float eps, float weight_decay,
+                           const float* grad_scale, rte_stream_t stream);
+enum { RTE_ADAMW_CHUNK = 4096 };
+/* sumsq[0] = sum over all table tensors of g^2 (deterministic two-stage); clip_coef[0] =
+ * min(1, max_norm / (sqrt(sumsq) + 1e-6)) (torch.nn.utils.clip_grad_norm_, training.py:456-462).
+ * partial f32 >= total_chunks.                                                                       */
+int rte_grad_norm_multi_tensor(const rte_adamw_tensor* table, int64_t total_chunks, const int32_t* chunk_tensor,
+                               const int32_t* chunk_index, float* partial, float* sumsq, float max_norm,
+                               float* clip_coef, rte_stream_t stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* RTE_B200_H_ */

@@ -1,0 +1,128 @@
+"""ctypes binding of ``include/rte_b200.h`` (the C ABI of ``lib/librte_b200.so``).
+
+The library is the product's only compute path: if it is missing or a symbol is absent the import
+of this module's ``load()`` raises -- there is no CPU or PyTorch fallback.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from pathlib import Path
+
+LIB_PATH = Path(__file__).resolve().parent / "lib" / "librte_b200.so"
+
+c_i32, c_i64, c_f32, c_vp = C.c_int32, C.c_int64, C.c_float, C.c_void_p
+
+EPI_BF16, EPI_F32, EPI_SWIGLU_FWD, EPI_SWIGLU_BWD = 0, 1, 2, 3
+ROUTER_MAX_R, ROUTER_MAX_K, ROUTER_MAX_T = 32, 8, 32
+ADAMW_CHUNK = 4096
+
+
+class GemmArgs(C.Structure):
+    _fields_ = [
+        ("M", c_i32), ("N", c_i32), ("K", c_i32),
+        ("A", c_vp), ("lda", c_i32), ("a_mn_major", c_i32),
+        ("B", c_vp), ("ldb", c_i32), ("b_mn_major", c_i32),
+        ("epilogue", c_i32),
+        ("C", c_vp), ("ldc", c_i32),
+        ("R", c_vp), ("ldr", c_i32),
+        ("C2", c_vp), ("ldc2", c_i32),
+        ("b_pair_offset", c_i32),
+        ("splits", c_i32),
+        ("split_stride", c_i64),
+        ("max_ctas", c_i32),
+        ("status", c_vp),
+    ]
+
+
+class RouterWeights(C.Structure):
+    _fields_ = [(n, c_vp) for n in ("r_w0", "r_b0", "r_w2", "r_b2", "d_w0", "d_b0", "d_w2", "d_b2", "pass_recipe_bias")]
+
+
+class RouterOut(C.Structure):
+    _fields_ = [(n, c_vp) for n in ("pooled", "r_hidden_pre", "d_hidden_pre", "recipe_logits", "recipe_probs",
+                                    "depth_probs", "expected_depth", "router_entropy", "recipe_id",
+                                    "recipe_id_by_pass", "depth_id", "depth")]
+
+
+class RouterGrads(C.Structure):
+    _fields_ = [(n, c_vp) for n in ("r_w0", "r_b0", "r_w2", "r_b2", "d_w0", "d_b0", "d_w2", "d_b2")]
+
+
+class PhiParams(C.Structure):
+    _fields_ = [(n, c_vp) for n in ("gain", "v", "u", "bias", "scale")]
+
+
+class PhiGrads(C.Structure):
+    _fields_ = [(n, c_vp) for n in ("gain", "v", "u", "bias")]
+
+
+class AdamWTensor(C.Structure):
+    _fields_ = [("p", c_vp), ("g", c_vp), ("m", c_vp), ("v", c_vp), ("bf16_shadow", c_vp),
+                ("n", c_i64), ("lr_group", c_i32), ("step_slot", c_i32)]
+
+
+P = C.POINTER
+
+# name -> (restype, argtypes); mirrors include/rte_b200.h declaration by declaration
+PROTOTYPES = {
+    "rte_backend_name": (C.c_char_p, []),
+    "rte_status_string": (C.c_char_p, [C.c_int]),
+    "rte_device_sm_count": (C.c_int, []),
+    "rte_gemm_bf16": (C.c_int, [P(GemmArgs), c_vp]),
+    "rte_reduce_splits": (C.c_int, [c_vp, c_i32, c_i64, c_i64, c_vp, c_i32, c_vp]),
+    "rte_embed_fwd": (C.c_int, [c_vp, c_vp, c_vp, c_i32, c_i32, c_i32, c_vp, c_vp]),
+    "rte_embed_bwd": (C.c_int, [c_vp, c_vp, c_vp, c_i32, c_i32, c_i32, c_vp, c_vp]),
+    "rte_rmsnorm_fwd": (C.c_int, [c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, c_i32, c_i32, c_f32, c_vp]),
+    "rte_rmsnorm_bwd": (C.c_int, [c_vp] * 12 + [c_i32, c_i32, c_i32, P(c_i32), c_vp]),
+    "rte_colsum_partials": (C.c_int, [c_vp, c_i32, c_i32, c_vp, c_i32, c_vp]),
+    "rte_attn_fwd": (C.c_int, [c_vp, c_i32, c_i32, c_vp, c_i32, c_vp, c_i32, c_i32, c_i32, c_i32, c_vp]),
+    "rte_attn_bwd": (C.c_int, [c_vp, c_i32, c_i32, c_vp, c_vp, c_i32, c_vp, c_vp, c_i32, c_i32, c_i32, c_i32, c_vp]),
+    "rte_ce_fwd_bwd": (C.c_int, [c_vp, c_i32, c_vp, c_vp, c_i32, c_vp, c_vp, c_i32, c_i32, c_vp, c_vp]),
+    "rte_segment_sum": (C.c_int, [c_vp, c_vp, c_i32, c_i32, c_vp]),
+    "rte_router_fwd": (C.c_int, [c_vp, P(RouterWeights), c_vp, P(RouterOut)] + [c_i32] * 9 + [c_vp]),
+    "rte_router_aux_bwd": (C.c_int, [P(RouterWeights), P(RouterOut), c_vp, c_f32, c_f32, c_vp, P(RouterGrads), c_vp,
+                                     c_vp] + [c_i32] * 6 + [c_vp]),
+    "rte_topk_lowest_index": (C.c_int, [c_vp, c_i32, c_i32, c_i32, c_i32, c_vp, c_vp, c_vp]),
+    "rte_macro_phi_fwd": (C.c_int, [c_vp, P(PhiParams), c_vp, c_vp, c_f32, c_vp, c_vp, c_vp, c_vp] + [c_i32] * 5 +
+                          [c_f32, c_vp]),
+    "rte_macro_phi_bwd": (C.c_int, [c_vp, c_vp, P(PhiParams), c_vp, c_vp, c_f32, c_vp, c_vp, c_vp, c_vp, P(PhiGrads),
+                                    c_vp] + [c_i32] * 6 + [c_f32, c_vp]),
+    "rte_cast_f32_bf16": (C.c_int, [c_vp, c_vp, c_i64, c_vp]),
+    "rte_add_f32": (C.c_int, [c_vp, c_vp, c_i64, c_vp]),
+    "rte_axpy_rows_f32": (C.c_int, [c_vp, c_vp, c_f32, c_i32, c_i32, c_i32, c_vp]),
+    "rte_adamw_multi_tensor": (C.c_int, [c_vp, c_i32, c_i64, c_vp, c_vp, c_vp, c_vp, c_f32, c_f32, c_f32, c_f32,
+                                         c_vp, c_vp]),
+    "rte_grad_norm_multi_tensor": (C.c_int, [c_vp, c_i64, c_vp, c_vp, c_vp, c_vp, c_f32, c_vp, c_vp]),
+}
+
+_lib = None
+
+
+class RteError(RuntimeError):
+    pass
+
+
+def load() -> C.CDLL:
+    """dlopen the library and bind every declared symbol; raises if anything is missing."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    if not LIB_PATH.exists():
+        raise RteError(f"{LIB_PATH} is missing: build it with `python -m speedup_thingy_b200.build` "
+                       "(CUDA + the sm_100a kernels are required; there is no fallback path)")
+    lib = C.CDLL(str(LIB_PATH))
+    for name, (restype, argtypes) in PROTOTYPES.items():
+        try:
+            fn = getattr(lib, name)
+        except AttributeError as exc:
+            raise RteError(f"librte_b200.so does not export {name}") from exc
+        fn.restype = restype
+        fn.argtypes = argtypes
+    _lib = lib
+    return lib
+
+
+def check(code: int, what: str) -> None:
+    if code != 0:
+        msg = load().rte_status_string(code).decode()
+        raise RteError(f"{what} failed: {msg} (code {code})")

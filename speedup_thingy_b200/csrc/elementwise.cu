@@ -1,0 +1,614 @@
+// HBM-bound kernels of the training step: embedding gather/scatter, RMSNorm forward/backward
+// (with the recurrent core's FiLM), per-token cross entropy with its gradient, split-K reduction,
+// fp32->bf16 weight shadows, fused multi-tensor AdamW and the global gradient norm.
+// All loads/stores are 16-byte vectors along the contiguous axis; grids are sized from the data
+// (one warp or one CTA per row), which at the step's sizes is many waves of 148 SMs.
+
+#include "rte_common.cuh"
+
+namespace {
+
+using rte::block_max;
+using rte::block_sum;
+using rte::warp_sum;
+
+// ------------------------------------------------------------------ embedding
+__global__ void embed_fwd_kernel(const int64_t* __restrict__ tokens, const float* __restrict__ table,
+                                 float* __restrict__ out, int n_tokens, int d, int vocab, int* status) {
+  const int d4 = d >> 2;
+  const long long total = (long long)n_tokens * d4;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+    const int t = int(i / d4), c = int(i % d4);
+    long long tok = tokens[t];
+    if (tok < 0 || tok >= vocab) {
+      if (status) atomicExch(status, RTE_DEV_INDEX_OUT_OF_RANGE);
+      tok = 0;
+    }
+    reinterpret_cast<float4*>(out)[i] = reinterpret_cast<const float4*>(table)[tok * d4 + c];
+  }
+}
+
+__global__ void embed_bwd_kernel(const int64_t* __restrict__ tokens, const float* __restrict__ dx,
+                                 float* __restrict__ dtable, int n_tokens, int d, int vocab, int* status) {
+  const long long total = (long long)n_tokens * d;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+    const int t = int(i / d), c = int(i % d);
+    const long long tok = tokens[t];
+    if (tok < 0 || tok >= vocab) {
+      if (status) atomicExch(status, RTE_DEV_INDEX_OUT_OF_RANGE);
+      continue;
+    }
+    atomicAdd(dtable + tok * d + c, dx[i]);
+  }
+}
+
+// ------------------------------------------------------------------ RMSNorm
+// One warp per row, row held in registers (d <= 32 * 4 * RN_MAX_V4).
+constexpr int RN_MAX_V4 = 16;   // d up to 2048
+
+template <int NV>
+__global__ void __launch_bounds__(256)
+rmsnorm_fwd_kernel(const float* __restrict__ x, const float* __restrict__ w, const float* __restrict__ fg,
+                   const float* __restrict__ fb, __nv_bfloat16* __restrict__ y16, float* __restrict__ y32,
+                   float* __restrict__ rstd, int rows, int d, float eps) {
+  const int lane = threadIdx.x & 31;
+  const int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (row >= rows) return;
+  const int d4 = d >> 2;
+  const float4* xr = reinterpret_cast<const float4*>(x + (size_t)row * d);
+  float4 v[NV];
+  float ss = 0.f;
+#pragma unroll
+  for (int i = 0; i < NV; ++i) {
+    const int c = lane + 32 * i;
+    if (c < d4) {
+      v[i] = xr[c];
+      ss += v[i].x * v[i].x + v[i].y * v[i].y + v[i].z * v[i].z + v[i].w * v[i].w;
+    }
+  }
+  ss = warp_sum(ss);
+  const float r = rsqrtf(ss / (float)d + eps);
+  if (lane == 0 && rstd) rstd[row] = r;
+#pragma unroll
+  for (int i = 0; i < NV; ++i) {
+    const int c = lane + 32 * i;
+    if (c < d4) {
+      float4 o = make_float4(v[i].x * r, v[i].y * r, v[i].z * r, v[i].w * r);
+      if (w) {
+        const float4 ww = reinterpret_cast<const float4*>(w)[c];
+        o.x *= ww.x; o.y *= ww.y; o.z *= ww.z; o.w *= ww.w;
+      }
+      if (fg) {
+        const float4 g = reinterpret_cast<const float4*>(fg)[c], b = reinterpret_cast<const float4*>(fb)[c];
+        o.x = o.x * (1.f + g.x) + b.x; o.y = o.y * (1.f + g.y) + b.y;
+        o.z = o.z * (1.f + g.z) + b.z; o.w = o.w * (1.f + g.w) + b.w;
+      }
+      if (y32) reinterpret_cast<float4*>(y32 + (size_t)row * d)[c] = o;
+      if (y16) {
+        uint2 pk = make_uint2(rte::pack_bf16x2(o.x, o.y), rte::pack_bf16x2(o.z, o.w));
+        reinterpret_cast<uint2*>(y16 + (size_t)row * d)[c] = pk;
+      }
+    }
+  }
+}
+
+// Backward.  y = xhat * w * (1 + fg) + fb with xhat = x * rstd.
+//   g  = dy * (1 + fg) * w          (gradient wrt xhat)
+//   dx = rstd * (g - xhat * mean(g * xhat)) + dres
+//   dw += dy * (1 + fg) * xhat,  dfg += dy * xhat * w,  dfb += dy
+// Each CTA walks rows blockIdx.x, blockIdx.x + gridDim.x, ...; column-wise partial sums for the
+// parameter gradients are kept in registers per warp, combined through shared memory at the end
+// and written to row blockIdx.x of the partial buffers (deterministic, no atomics).
+template <int NV>
+__global__ void __launch_bounds__(256)
+rmsnorm_bwd_kernel(const float* __restrict__ x, const float* __restrict__ w, const float* __restrict__ fg,
+                   const float* __restrict__ rstd, const __nv_bfloat16* __restrict__ dy16,
+                   const float* __restrict__ dy32, const float* __restrict__ dres, float* __restrict__ dx32,
+                   __nv_bfloat16* __restrict__ dx16, float* __restrict__ dw_part, float* __restrict__ dg_part,
+                   float* __restrict__ db_part, int rows, int d) {
+  extern __shared__ float sm[];   // [3][warps][d] when parameter gradients are requested
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarp = blockDim.x >> 5;
+  const int d4 = d >> 2;
+  float4 aw[NV], ag[NV], ab[NV];
+#pragma unroll
+  for (int i = 0; i < NV; ++i) aw[i] = ag[i] = ab[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+  const bool want_w = dw_part != nullptr, want_f = dg_part != nullptr;
+
+  for (int row = blockIdx.x * nwarp + warp; row < rows; row += gridDim.x * nwarp) {
+    const float r = rstd[row];
+    const float4* xr = reinterpret_cast<const float4*>(x + (size_t)row * d);
+    float4 xh[NV], g[NV];
+    float dot = 0.f;
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+      const int c = lane + 32 * i;
+      if (c < d4) {
+        float4 xv = xr[c];
+        xh[i] = make_float4(xv.x * r, xv.y * r, xv.z * r, xv.w * r);
+        float4 dyv;
+        if (dy16) {
+          const uint2 pk = reinterpret_cast<const uint2*>(dy16 + (size_t)row * d)[c];
+          const float2 a = rte::unpack_bf16x2(pk.x), b = rte::unpack_bf16x2(pk.y);
+          dyv = make_float4(a.x, a.y, b.x, b.y);
+        } else {
+          dyv = reinterpret_cast<const float4*>(dy32 + (size_t)row * d)[c];
+        }
+        float4 ww = w ? reinterpret_cast<const float4*>(w)[c] : make_float4(1.f, 1.f, 1.f, 1.f);
+        float4 f1 = make_float4(1.f, 1.f, 1.f, 1.f);
+        if (fg) {
+          const float4 t = reinterpret_cast<const float4*>(fg)[c];
+          f1 = make_float4(1.f + t.x, 1.f + t.y, 1.f + t.z, 1.f + t.w);
+        }
+        if (want_w) {
+          aw[i].x += dyv.x * f1.x * xh[i].x; aw[i].y += dyv.y * f1.y * xh[i].y;
+          aw[i].z += dyv.z * f1.z * xh[i].z; aw[i].w += dyv.w * f1.w * xh[i].w;
+        }
+        if (want_f) {
+          ag[i].x += dyv.x * xh[i].x * ww.x; ag[i].y += dyv.y * xh[i].y * ww.y;
+          ag[i].z += dyv.z * xh[i].z * ww.z; ag[i].w += dyv.w * xh[i].w * ww.w;
+          ab[i].x += dyv.x; ab[i].y += dyv.y; ab[i].z += dyv.z; ab[i].w += dyv.w;
+        }
+        g[i] = make_float4(dyv.x * f1.x * ww.x, dyv.y * f1.y * ww.y, dyv.z * f1.z * ww.z, dyv.w * f1.w * ww.w);
+        dot += g[i].x * xh[i].x + g[i].y * xh[i].y + g[i].z * xh[i].z + g[i].w * xh[i].w;
+      }
+    }
+    dot = warp_sum(dot) / (float)d;
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+      const int c = lane + 32 * i;
+      if (c < d4) {
+        float4 o = make_float4(r * (g[i].x - xh[i].x * dot), r * (g[i].y - xh[i].y * dot),
+                               r * (g[i].z - xh[i].z * dot), r * (g[i].w - xh[i].w * dot));
+        if (dres) {
+          const float4 t = reinterpret_cast<const float4*>(dres + (size_t)row * d)[c];
+          o.x += t.x; o.y += t.y; o.z += t.z; o.w += t.w;
+        }
+        if (dx32) reinterpret_cast<float4*>(dx32 + (size_t)row * d)[c] = o;
+        if (dx16) {
+          uint2 pk = make_uint2(rte::pack_bf16x2(o.x, o.y), rte::pack_bf16x2(o.z, o.w));
+          reinterpret_cast<uint2*>(dx16 + (size_t)row * d)[c] = pk;
+        }
+      }
+    }
+  }
+  if (!want_w && !want_f) return;
+  // combine the warps' column sums
+  float* sw = sm;
+  float* sg = sm + (size_t)nwarp * d;
+  float* sb = sm + (size_t)2 * nwarp * d;
+#pragma unroll
+  for (int i = 0; i < NV; ++i) {
+    const int c = lane + 32 * i;
+    if (c < d4) {
+      if (want_w) reinterpret_cast<float4*>(sw + (size_t)warp * d)[c] = aw[i];
+      if (want_f) {
+        reinterpret_cast<float4*>(sg + (size_t)warp * d)[c] = ag[i];
+        reinterpret_cast<float4*>(sb + (size_t)warp * d)[c] = ab[i];
+      }
+    }
+  }
+  __syncthreads();
+  for (int c = threadIdx.x; c < d; c += blockDim.x) {
+    float tw = 0.f, tg = 0.f, tb = 0.f;
+    for (int k = 0; k < nwarp; ++k) {
+      if (want_w) tw += sw[(size_t)k * d + c];
+      if (want_f) { tg += sg[(size_t)k * d + c]; tb += sb[(size_t)k * d + c]; }
+    }
+    if (want_w) dw_part[(size_t)blockIdx.x * d + c] = tw;
+    if (want_f) { dg_part[(size_t)blockIdx.x * d + c] = tg; db_part[(size_t)blockIdx.x * d + c] = tb; }
+  }
+}
+
+__global__ void colsum_kernel(const float* __restrict__ part, int n_rows, int d, float* __restrict__ out, int accumulate) {
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= d) return;
+  float s = 0.f;
+  for (int r = 0; r < n_rows; ++r) s += part[(size_t)r * d + c];
+  out[c] = accumulate ? out[c] + s : s;
+}
+
+// ------------------------------------------------------------------ cross entropy
+// One CTA per token row; logits read twice from L2/HBM (max+sum pass, gradient pass).
+__global__ void __launch_bounds__(256)
+ce_kernel(const __nv_bfloat16* __restrict__ logits, int ldl, const int64_t* __restrict__ targets,
+          const float* __restrict__ row_weight, int S, float* __restrict__ loss_tok,
+          __nv_bfloat16* __restrict__ dlogits, int rows, int V, int* status) {
+  __shared__ float red[32];
+  const int row = blockIdx.x;
+  if (row >= rows) return;
+  const __nv_bfloat16* lr = logits + (size_t)row * ldl;
+  long long tgt = targets[row];
+  if (tgt < 0 || tgt >= V) {
+    if (status && threadIdx.x == 0) atomicExch(status, RTE_DEV_INDEX_OUT_OF_RANGE);
+    tgt = 0;
+  }
+  const int V8 = ((ldl % 8) == 0 && (reinterpret_cast<uintptr_t>(logits) & 15) == 0) ? (V >> 3) : 0;
+  float mx = -INFINITY;
+  for (int c = threadIdx.x; c < V8; c += blockDim.x) {
+    const uint4 pk = reinterpret_cast<const uint4*>(lr)[c];
+    const float2 a = rte::unpack_bf16x2(pk.x), b = rte::unpack_bf16x2(pk.y), cc = rte::unpack_bf16x2(pk.z), dd = rte::unpack_bf16x2(pk.w);
+    mx = fmaxf(mx, fmaxf(fmaxf(fmaxf(a.x, a.y), fmaxf(b.x, b.y)), fmaxf(fmaxf(cc.x, cc.y), fmaxf(dd.x, dd.y))));
+  }
+  for (int c = V8 * 8 + threadIdx.x; c < V; c += blockDim.x) mx = fmaxf(mx, __bfloat162float(lr[c]));
+  mx = block_max(mx, red);
+  float se = 0.f;
+  for (int c = threadIdx.x; c < V8; c += blockDim.x) {
+    const uint4 pk = reinterpret_cast<const uint4*>(lr)[c];
+    const float2 a = rte::unpack_bf16x2(pk.x), b = rte::unpack_bf16x2(pk.y), cc = rte::unpack_bf16x2(pk.z), dd = rte::unpack_bf16x2(pk.w);
+    se += __expf(a.x - mx) + __expf(a.y - mx) + __expf(b.x - mx) + __expf(b.y - mx) + __expf(cc.x - mx) +
+          __expf(cc.y - mx) + __expf(dd.x - mx) + __expf(dd.y - mx);
+  }
+  for (int c = V8 * 8 + threadIdx.x; c < V; c += blockDim.x) se += __expf(__bfloat162float(lr[c]) - mx);
+  se = block_sum(se, red);
+  const float lse = mx + __logf(se);
+  const float tl = __bfloat162float(lr[tgt]);
+  if (threadIdx.x == 0) loss_tok[row] = lse - tl;
+  if (dlogits == nullptr) return;
+  __syncthreads();   // every thread has read lr[tgt] before an aliasing dlogits row is overwritten
+  const float wgt = row_weight[row / S];
+  __nv_bfloat16* dr = dlogits + (size_t)row * ldl;
+  for (int c = threadIdx.x; c < V8; c += blockDim.x) {
+    const uint4 pk = reinterpret_cast<const uint4*>(lr)[c];
+    const float2 a = rte::unpack_bf16x2(pk.x), b = rte::unpack_bf16x2(pk.y), cc = rte::unpack_bf16x2(pk.z), dd = rte::unpack_bf16x2(pk.w);
+    float v[8] = {a.x, a.y, b.x, b.y, cc.x, cc.y, dd.x, dd.y};
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const float pr = __expf(v[j] - lse);
+      v[j] = wgt * (pr - ((c * 8 + j) == tgt ? 1.f : 0.f));
+    }
+    uint4 o;
+    o.x = rte::pack_bf16x2(v[0], v[1]); o.y = rte::pack_bf16x2(v[2], v[3]);
+    o.z = rte::pack_bf16x2(v[4], v[5]); o.w = rte::pack_bf16x2(v[6], v[7]);
+    reinterpret_cast<uint4*>(dr)[c] = o;
+  }
+  for (int c = V8 * 8 + threadIdx.x; c < V; c += blockDim.x) {
+    const float pr = __expf(__bfloat162float(lr[c]) - lse);
+    dr[c] = __float2bfloat16_rn(wgt * (pr - (c == tgt ? 1.f : 0.f)));
+  }
+}
+
+__global__ void segment_sum_kernel(const float* __restrict__ in, float* __restrict__ out, int n_seg, int seg_len) {
+  __shared__ float red[32];
+  const int seg = blockIdx.x;
+  if (seg >= n_seg) return;
+  float s = 0.f;
+  for (int i = threadIdx.x; i < seg_len; i += blockDim.x) s += in[(size_t)seg * seg_len + i];
+  s = block_sum(s, red);
+  if (threadIdx.x == 0) out[seg] = s;
+}
+
+// ------------------------------------------------------------------ small vector kernels
+__global__ void reduce_splits_kernel(const float* __restrict__ ws, int splits, long long stride, long long n4,
+                                     float* __restrict__ out, int accumulate) {
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n4; i += (long long)gridDim.x * blockDim.x) {
+    float4 acc = accumulate ? reinterpret_cast<float4*>(out)[i] : make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int s = 0; s < splits; ++s) {
+      const float4 t = reinterpret_cast<const float4*>(ws + (size_t)s * stride)[i];
+      acc.x += t.x; acc.y += t.y; acc.z += t.z; acc.w += t.w;
+    }
+    reinterpret_cast<float4*>(out)[i] = acc;
+  }
+}
+__global__ void reduce_splits_tail_kernel(const float* __restrict__ ws, int splits, long long stride, long long start,
+                                          long long n, float* __restrict__ out, int accumulate) {
+  const long long i = start + blockIdx.x * (long long)blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  float acc = accumulate ? out[i] : 0.f;
+  for (int s = 0; s < splits; ++s) acc += ws[(size_t)s * stride + i];
+  out[i] = acc;
+}
+
+__global__ void cast_kernel(const float* __restrict__ src, __nv_bfloat16* __restrict__ dst, long long n) {
+  const long long n4 = n >> 2;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n4; i += (long long)gridDim.x * blockDim.x) {
+    const float4 t = reinterpret_cast<const float4*>(src)[i];
+    reinterpret_cast<uint2*>(dst)[i] = make_uint2(rte::pack_bf16x2(t.x, t.y), rte::pack_bf16x2(t.z, t.w));
+  }
+  for (long long i = n4 * 4 + blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x)
+    dst[i] = __float2bfloat16_rn(src[i]);
+}
+__global__ void add_kernel(float* __restrict__ dst, const float* __restrict__ src, long long n) {
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) dst[i] += src[i];
+}
+__global__ void axpy_rows_kernel(float* __restrict__ dst, const float* __restrict__ vec, float alpha, int rows, int seg, int d) {
+  const long long total = (long long)rows * d;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+    const int r = int(i / d), c = int(i % d);
+    dst[i] += alpha * vec[(size_t)(r / seg) * d + c];
+  }
+}
+
+// ------------------------------------------------------------------ AdamW
+__global__ void __launch_bounds__(256)
+adamw_kernel(const rte_adamw_tensor* __restrict__ table, const int32_t* __restrict__ chunk_tensor,
+             const int32_t* __restrict__ chunk_index, const float* __restrict__ lr_table,
+             const int32_t* __restrict__ step_count, float beta1, float beta2, float eps, float wd,
+             const float* __restrict__ grad_scale) {
+  const int ti = chunk_tensor[blockIdx.x];
+  const rte_adamw_tensor t = table[ti];
+  const long long base = (long long)chunk_index[blockIdx.x] * RTE_ADAMW_CHUNK;
+  const float lr = lr_table[t.lr_group];
+  const float step = (float)(step_count[t.step_slot] + 1);   // incremented by adamw_step_kernel afterwards
+  const float bc1 = 1.f - powf(beta1, step), bc2 = 1.f - powf(beta2, step);
+  const float gs = grad_scale ? *grad_scale : 1.f;
+  const float step_size = lr / bc1, inv_sqrt_bc2 = rsqrtf(bc2), decay = 1.f - lr * wd;
+  __nv_bfloat16* shadow = reinterpret_cast<__nv_bfloat16*>(t.bf16_shadow);
+#pragma unroll 4
+  for (int j = threadIdx.x; j < RTE_ADAMW_CHUNK; j += blockDim.x) {
+    const long long i = base + j;
+    if (i >= t.n) break;
+    const float g = t.g[i] * gs;
+    float p = t.p[i] * decay;
+    const float m = beta1 * t.m[i] + (1.f - beta1) * g;
+    const float v = beta2 * t.v[i] + (1.f - beta2) * g * g;
+    p -= step_size * m / (sqrtf(v) * inv_sqrt_bc2 + eps);
+    t.p[i] = p; t.m[i] = m; t.v[i] = v;
+    if (shadow) shadow[i] = __float2bfloat16_rn(p);
+  }
+}
+__global__ void adamw_step_kernel(const rte_adamw_tensor* __restrict__ table, int n_tensors, int32_t* step_count) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < n_tensors) step_count[table[i].step_slot] += 1;
+}
+
+__global__ void __launch_bounds__(256)
+gradnorm_partial_kernel(const rte_adamw_tensor* __restrict__ table, const int32_t* __restrict__ chunk_tensor,
+                        const int32_t* __restrict__ chunk_index, float* __restrict__ partial) {
+  __shared__ float red[32];
+  const rte_adamw_tensor t = table[chunk_tensor[blockIdx.x]];
+  const long long base = (long long)chunk_index[blockIdx.x] * RTE_ADAMW_CHUNK;
+  float s = 0.f;
+  for (int j = threadIdx.x; j < RTE_ADAMW_CHUNK; j += blockDim.x) {
+    const long long i = base + j;
+    if (i < t.n) { const float g = t.g[i]; s += g * g; }
+  }
+  s = block_sum(s, red);
+  if (threadIdx.x == 0) partial[blockIdx.x] = s;
+}
+__global__ void gradnorm_final_kernel(const float* __restrict__ partial, long long n, float* sumsq, float max_norm, float* clip_coef) {
+  __shared__ float red[32];
+  float s = 0.f;
+  for (long long i = threadIdx.x; i < n; i += blockDim.x) s += partial[i];
+  s = block_sum(s, red);
+  if (threadIdx.x == 0) {
+    sumsq[0] = s;
+    if (clip_coef) clip_coef[0] = max_norm > 0.f ? fminf(1.f, max_norm / (sqrtf(s) + 1e-6f)) : 1.f;
+  }
+}
+
+// ------------------------------------------------------------------ top-k, ties to the lowest index
+// One warp per row.  k rounds of a warp arg-max over (value desc, index asc); a selected entry is
+// masked by remembering the previous winner's (value, index) and only admitting strictly "later"
+// candidates in that order, so no scratch copy of the row is needed.
+__global__ void __launch_bounds__(256)
+topk_kernel(const float* __restrict__ scores, int ld, int rows, int n, int k, int32_t* __restrict__ idx, float* __restrict__ vals) {
+  const int lane = threadIdx.x & 31;
+  const int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (row >= rows) return;
+  const float* sr = scores + (size_t)row * ld;
+  float pv = INFINITY; int pi = -1;      // previous winner; first round admits everything
+  for (int r = 0; r < k; ++r) {
+    float bv = -INFINITY; int bi = 0x7fffffff;
+    for (int c = lane; c < n; c += 32) {
+      const float v = sr[c];
+      const bool after_prev = (v < pv) || (v == pv && c > pi);
+      const bool better = (v > bv) || (v == bv && c < bi);
+      if (after_prev && better) { bv = v; bi = c; }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+      const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+      if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
+    }
+    if (lane == 0) {
+      if (idx) idx[(size_t)row * k + r] = bi;
+      if (vals) vals[(size_t)row * k + r] = bv;
+    }
+    pv = bv; pi = bi;
+  }
+}
+
+inline int grid_for(long long n, int block, int cap = 148 * 16) {
+  long long g = (n + block - 1) / block;
+  if (g > cap) g = cap;
+  if (g < 1) g = 1;
+  return (int)g;
+}
+
+}  // namespace
+
+#define ST(s) reinterpret_cast<cudaStream_t>(s)
+
+extern "C" const char* rte_backend_name(void) { return "cuda_sm100a_ext"; }
+
+extern "C" const char* rte_status_string(int code) {
+  switch (code) {
+    case RTE_OK: return "ok";
+    case RTE_ERR_BAD_ARG: return "bad argument";
+    case RTE_ERR_ALIGNMENT: return "pointer or stride not 16-byte aligned";
+    case RTE_ERR_TENSOR_MAP: return "tensor map creation failed";
+    case RTE_ERR_LAUNCH: return "kernel launch failed";
+    case RTE_ERR_UNSUPPORTED: return "unsupported size";
+    case RTE_ERR_NO_DEVICE: return "no CUDA device";
+    case RTE_DEV_WAIT_TIMEOUT_PRODUCER: return "device: TMA producer wait ran out";
+    case RTE_DEV_WAIT_TIMEOUT_MMA: return "device: MMA issuer wait ran out";
+    case RTE_DEV_WAIT_TIMEOUT_EPILOGUE: return "device: epilogue wait ran out";
+    case RTE_DEV_INDEX_OUT_OF_RANGE: return "device: index out of range";
+    default: return "unknown";
+  }
+}
+
+extern "C" int rte_embed_fwd(const int64_t* tokens, const float* table, float* out, int32_t n_tokens, int32_t d,
+                             int32_t vocab, int32_t* status, rte_stream_t stream) {
+  RTE_CHECK_ARG(tokens && table && out && n_tokens > 0 && d > 0 && d % 4 == 0);
+  embed_fwd_kernel<<<grid_for((long long)n_tokens * (d / 4), 256), 256, 0, ST(stream)>>>(tokens, table, out, n_tokens, d, vocab, status);
+  RTE_LAUNCH_CHECK();
+  return RTE_OK;
+}
+extern "C" int rte_embed_bwd(const int64_t* tokens, const float* dx, float* dtable, int32_t n_tokens, int32_t d,
+                             int32_t vocab, int32_t* status, rte_stream_t stream) {
+  RTE_CHECK_ARG(tokens && dx && dtable && n_tokens > 0 && d > 0);
+  embed_bwd_kernel<<<grid_for((long long)n_tokens * d, 256), 256, 0, ST(stream)>>>(tokens, dx, dtable, n_tokens, d, vocab, status);
+  RTE_LAUNCH_CHECK();
+  return RTE_OK;
+}
+
+extern "C" int rte_rmsnorm_fwd(const float* x, const float* w, const float* film_gamma, const float* film_beta,
+                               void* y_bf16, float* y_f32, float* rstd, int32_t rows, int32_t d, float eps,
+                               rte_stream_t stream) {
+  RTE_CHECK_ARG(x && rows > 0 && d > 0 && d % 4 == 0 && (y_bf16 || y_f32));
+  RTE_CHECK_ARG((film_gamma == nullptr) == (film_beta == nullptr));
+  if (d > 128 * RN_MAX_V4) return RTE_ERR_UNSUPPORTED;
+#define RTE_RN_FWD(NV)                                                                            \
+  rmsnorm_fwd_kernel<NV><<<rte::ceil_div(rows, 8), 256, 0, ST(stream)>>>(x, w, film_gamma, film_beta, \
+      reinterpret_cast<__nv_bfloat16*>(y_bf16), y_f32, rstd, rows, d, eps)
+  if (d <= 128) RTE_RN_FWD(1);
+  else if (d <= 256) RTE_RN_FWD(2);
+  else if (d <= 512) RTE_RN_FWD(4);
+  else if (d <= 1024) RTE_RN_FWD(8);
+  else RTE_RN_FWD(16);
+#undef RTE_RN_FWD
+  RTE_LAUNCH_CHECK();
+  return RTE_OK;
+}
+
+extern "C" int rte_rmsnorm_bwd(const float* x, const float* w, const float* film_gamma, const float* rstd,
+                               const void* dy_bf16, const float* dy_f32, const float* dres, float* dx_f32,
+                               void* dx_bf16, float* dw_partial, float* dgamma_partial, float* dbeta_partial,
+                               int32_t rows, int32_t d, int32_t max_partials, int32_t* n_partials,
+                               rte_stream_t stream) {
+  RTE_CHECK_ARG(x && rstd && rows > 0 && d > 0 && d % 4 == 0 && (dy_bf16 || dy_f32) && (dx_f32 || dx_bf16));
+  RTE_CHECK_ARG((dgamma_partial == nullptr) == (dbeta_partial == nullptr));
+  if (d > 128 * RN_MAX_V4) return RTE_ERR_UNSUPPORTED;
+  const bool grads = dw_partial || dgamma_partial;
+  int grid = rte::ceil_div(rows, 8);
+  const int cap = 148 * 2;
+  if (grid > cap) grid = cap;
+  if (grads) {
+    RTE_CHECK_ARG(max_partials >= 1);
+    if (grid > max_partials) grid = max_partials;
+  }
+  if (n_partials) *n_partials = grid;
+  const size_t smem = grads ? (size_t)3 * 8 * d * sizeof(float) : 0;
+#define RTE_RN_BWD(NV)                                                                                           \
+  do {                                                                                                           \
+    if (smem > 48 * 1024) {                                                                                      \
+      static bool set = false;                                                                                   \
+      if (!set) {                                                                                                \
+        if (cudaFuncSetAttribute(rmsnorm_bwd_kernel<NV>, cudaFuncAttributeMaxDynamicSharedMemorySize,            \
+                                 200 * 1024) != cudaSuccess)                                                     \
+          return RTE_ERR_LAUNCH;                                                                                 \
+        set = true;                                                                                              \
+      }                                                                                                          \
+    }                                                                                                            \
+    rmsnorm_bwd_kernel<NV><<<grid, 256, smem, ST(stream)>>>(x, w, film_gamma, rstd,                              \
+        reinterpret_cast<const __nv_bfloat16*>(dy_bf16), dy_f32, dres, dx_f32,                                   \
+        reinterpret_cast<__nv_bfloat16*>(dx_bf16), dw_partial, dgamma_partial, dbeta_partial, rows, d);          \
+  } while (0)
+  if (d <= 128) RTE_RN_BWD(1);
+  else if (d <= 256) RTE_RN_BWD(2);
+  else if (d <= 512) RTE_RN_BWD(4);
+  else if (d <= 1024) RTE_RN_BWD(8);
+  else RTE_RN_BWD(16);
+#undef RTE_RN_BWD
+  RTE_LAUNCH_CHECK();
+  return RTE_OK;
+}
+
+extern "C" int rte_colsum_partials(const float* partial, int32_t n_rows, int32_t d, float* out, int32_t accumulate,
+                                   rte_stream_t stream) {
+  RTE_CHECK_ARG(partial && out && n_rows > 0 && d > 0);
+  colsum_kernel<<<rte::ceil_div(d, 128), 128, 0, ST(stream)>>>(partial, n_rows, d, out, accumulate);
+  RTE_LAUNCH_CHECK();
+  return RTE_OK;
+}
+
+extern "C" int rte_ce_fwd_bwd(const void* logits, int32_t ldl, const int64_t* targets, const float* row_weight,
+                              int32_t S, float* loss_tok, void* dlogits, int32_t rows, int32_t V, int32_t* status,
+                              rte_stream_t stream) {
+  RTE_CHECK_ARG(logits && targets && loss_tok && rows > 0 && V > 0 && ldl >= V && S > 0);
+  RTE_CHECK_ARG(dlogits == nullptr || row_weight != nullptr);
+  ce_kernel<<<rows, 256, 0, ST(stream)>>>(reinterpret_cast<const __nv_bfloat16*>(logits), ldl, targets, row_weight, S,
+                                          loss_tok, reinterpret_cast<__nv_bfloat16*>(dlogits), rows, V, status);
+  RTE_LAUNCH_CHECK();
+  return RTE_OK;
+}
+
+extern "C" int rte_segment_sum(const float* in, float* out, int32_t n_seg, int32_t seg_len, rte_stream_t stream) {
+  RTE_CHECK_ARG(in && out && n_seg > 0 && seg_len > 0);
+  segment_sum_kernel<<<n_seg, 128, 0, ST(stream)>>>(in, out, n_seg, seg_len);
+  RTE_LAUNCH_CHECK();
+  return RTE_OK;
+}
+
+extern "C" int rte_reduce_splits(const float* ws, int32_t splits, int64_t split_stride, int64_t n, float* out,
+                                 int32_t accumulate, rte_stream_t stream) {
+  RTE_CHECK_ARG(ws && out && splits >= 1 && n > 0);
+  const bool vec = (split_stride % 4 == 0) && ((reinterpret_cast<uintptr_t>(ws) & 15) == 0) &&
+                   ((reinterpret_cast<uintptr_t>(out) & 15) == 0);
+  const long long n4 = vec ? (n >> 2) : 0;
+  if (n4 > 0) {
+    reduce_splits_kernel<<<grid_for(n4, 256), 256, 0, ST(stream)>>>(ws, splits, split_stride, n4, out, accumulate);
+    RTE_LAUNCH_CHECK();
+  }
+  const long long rest = n - n4 * 4;
+  if (rest > 0) {
+    reduce_splits_tail_kernel<<<(int)rte::ceil_div64(rest, 256), 256, 0, ST(stream)>>>(ws, splits, split_stride, n4 * 4, n, out, accumulate);
+    RTE_LAUNCH_CHECK();
+  }
+  return RTE_OK;
+}
+
+extern "C" int rte_cast_f32_bf16(const float* src, void* dst, int64_t n, rte_stream_t stream) {
+  RTE_CHECK_ARG(src && dst && n > 0);
+  if ((reinterpret_cast<uintptr_t>(src) & 15) || (reinterpret_cast<uintptr_t>(dst) & 7)) return RTE_ERR_ALIGNMENT;
+  cast_kernel<<<grid_for(n / 4 + 1, 256), 256, 0, ST(stream)>>>(src, reinterpret_cast<__nv_bfloat16*>(dst), n);
+  RTE_LAUNCH_CHECK();
+  return RTE_OK;
+}
+extern "C" int rte_add_f32(float* dst, const float* src, int64_t n, rte_stream_t stream) {
+  RTE_CHECK_ARG(src && dst && n > 0);
+  add_kernel<<<grid_for(n, 256), 256, 0, ST(stream)>>>(dst, src, n);
+  RTE_LAUNCH_CHECK();
+  return RTE_OK;
+}
+extern "C" int rte_axpy_rows_f32(float* dst, const float* vec, float alpha, int32_t rows, int32_t seg, int32_t d,
+                                 rte_stream_t stream) {
+  RTE_CHECK_ARG(dst && vec && rows > 0 && seg > 0 && d > 0);
+  axpy_rows_kernel<<<grid_for((long long)rows * d, 256), 256, 0, ST(stream)>>>(dst, vec, alpha, rows, seg, d);
+  RTE_LAUNCH_CHECK();
+  return RTE_OK;
+}
+
+extern "C" int rte_adamw_multi_tensor(const rte_adamw_tensor* table, int32_t n_tensors, int64_t total_chunks,
+                                      const int32_t* chunk_tensor, const int32_t* chunk_index, const float* lr_table,
+                                      int32_t* step_count, float beta1, float beta2, float eps, float weight_decay,
+                                      const float* grad_scale, rte_stream_t stream) {
+  RTE_CHECK_ARG(table && chunk_tensor && chunk_index && lr_table && step_count && n_tensors > 0 && total_chunks > 0);
+  adamw_kernel<<<(unsigned)total_chunks, 256, 0, ST(stream)>>>(table, chunk_tensor, chunk_index, lr_table, step_count,
+                                                               beta1, beta2, eps, weight_decay, grad_scale);
+  RTE_LAUNCH_CHECK();
+  adamw_step_kernel<<<rte::ceil_div(n_tensors, 128), 128, 0, ST(stream)>>>(table, n_tensors, step_count);
+  RTE_LAUNCH_CHECK();
+  return RTE_OK;
+}
+
+extern "C" int rte_grad_norm_multi_tensor(const rte_adamw_tensor* table, int64_t total_chunks, const int32_t* chunk_tensor,
+                                          const int32_t* chunk_index, float* partial, float* sumsq, float max_norm,
+                                          float* clip_coef, rte_stream_t stream) {
+  RTE_CHECK_ARG(table && chunk_tensor && chunk_index && partial && sumsq && total_chunks > 0);
+  gradnorm_partial_kernel<<<(unsigned)total_chunks, 256, 0, ST(stream)>>>(table, chunk_tensor, chunk_index, partial);
+  RTE_LAUNCH_CHECK();
+  gradnorm_final_kernel<<<1, 1024, 0, ST(stream)>>>(partial, total_chunks, sumsq, max_norm, clip_coef);
+  RTE_LAUNCH_CHECK();
+  return RTE_OK;
+}
+
+extern "C" int rte_topk_lowest_index(const float* scores, int32_t ld, int32_t rows, int32_t n, int32_t k,
+                                     int32_t* idx, float* vals, rte_stream_t stream) {
+  RTE_CHECK_ARG(scores && rows > 0 && n > 0 && k > 0 && k <= n && ld >= n && (idx || vals));
+  topk_kernel<<<rte::ceil_div(rows, 8), 256, 0, ST(stream)>>>(scores, ld, rows, n, k, idx, vals);
+  RTE_LAUNCH_CHECK();
+  return RTE_OK;
+}

@@ -1,0 +1,472 @@
+// The macro operator Phi of the recursive model, forward and backward, on device:
+//   out = h + s_cfg * scale * tanh(gain * h + silu(z @ v) @ u + bias),
+//   z   = [rmsnorm(h), mean_S rmsnorm(h), h0],  h == h0 on the hot path,
+// with gain / v / u / bias / scale selected PER SAMPLE by (recipe id, stride id).
+//
+// The per-sample low-rank weights are small (3d x m and m x d, m <= 64), so these are SIMT kernels
+// tiled through shared memory; the weight gather is pointer arithmetic, the concat `z` is never
+// materialised (three K-slices; the pooled slice collapses to one m-vector per sample).
+// Parameter gradients are produced per sample and then summed per (recipe, stride) key in sample
+// order, so results are bitwise reproducible and keys no sample used receive exact zeros.
+
+#include "rte_common.cuh"
+
+namespace {
+
+constexpr int TT = 32;        // tokens per CTA tile
+constexpr int NTHR = 256;
+constexpr int CH = 64;        // d-chunk staged in shared memory
+constexpr int MMAX = 64;      // largest supported macro rank
+
+struct PhiDims { int B, S, d, m, K; };
+
+__device__ __forceinline__ size_t key_of(const int32_t* rid, const int32_t* sid, int b, int K) {
+  return (size_t)rid[b] * K + sid[b];
+}
+
+// rstd per token, pooled = mean_S(rmsnorm(h0)) per sample, pa = pooled @ v[d:2d, :]
+__global__ void __launch_bounds__(NTHR)
+phi_prep_kernel(const float* __restrict__ h0, const float* __restrict__ v, const int32_t* __restrict__ rid,
+                const int32_t* __restrict__ sid, float* __restrict__ rstd, float* __restrict__ pooled,
+                float* __restrict__ pa, PhiDims D, float eps) {
+  extern __shared__ float sm[];            // rstd_s[S] then pooled_s[d]
+  float* rs = sm;
+  float* ps = sm + D.S;
+  const int b = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const float* hb = h0 + (size_t)b * D.S * D.d;
+  for (int s = warp; s < D.S; s += NTHR / 32) {
+    float ss = 0.f;
+    for (int c = lane; c < D.d; c += 32) { const float x = hb[(size_t)s * D.d + c]; ss += x * x; }
+    ss = rte::warp_sum(ss);
+    if (lane == 0) { const float r = rsqrtf(ss / (float)D.d + eps); rs[s] = r; rstd[(size_t)b * D.S + s] = r; }
+  }
+  __syncthreads();
+  for (int c = threadIdx.x; c < D.d; c += NTHR) {
+    float acc = 0.f;
+    for (int s = 0; s < D.S; ++s) acc += hb[(size_t)s * D.d + c] * rs[s];
+    acc /= (float)D.S;
+    ps[c] = acc;
+    pooled[(size_t)b * D.d + c] = acc;
+  }
+  __syncthreads();
+  const float* v2 = v + (key_of(rid, sid, b, D.K) * 3 * D.d + D.d) * D.m;
+  for (int j = warp; j < D.m; j += NTHR / 32) {
+    float acc = 0.f;
+    for (int c = lane; c < D.d; c += 32) acc += ps[c] * v2[(size_t)c * D.m + j];
+    acc = rte::warp_sum(acc);
+    if (lane == 0) pa[(size_t)b * D.m + j] = acc;
+  }
+}
+
+// act[tok, j] = pa[b, j] + sum_c h0[tok,c] * (rstd[tok] * v1[c,j] + v3[c,j])
+__global__ void __launch_bounds__(NTHR)
+phi_act_kernel(const float* __restrict__ h0, const float* __restrict__ rstd, const float* __restrict__ pa,
+               const float* __restrict__ v, const int32_t* __restrict__ rid, const int32_t* __restrict__ sid,
+               float* __restrict__ act, PhiDims D) {
+  __shared__ float sx[TT][CH + 1];
+  __shared__ float sv1[CH][MMAX];
+  __shared__ float sv3[CH][MMAX];
+  const int tiles = rte::ceil_div(D.S, TT);
+  const int b = blockIdx.x / tiles, tok0 = (blockIdx.x % tiles) * TT;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const float* vb = v + key_of(rid, sid, b, D.K) * 3 * D.d * D.m;
+  float acc[4][2], rs[4];
+#pragma unroll
+  for (int t = 0; t < 4; ++t) {
+    const int s = tok0 + warp * 4 + t;
+    rs[t] = (s < D.S) ? rstd[(size_t)b * D.S + s] : 0.f;
+#pragma unroll
+    for (int q = 0; q < 2; ++q) { const int j = lane + 32 * q; acc[t][q] = (j < D.m) ? pa[(size_t)b * D.m + j] : 0.f; }
+  }
+  for (int c0 = 0; c0 < D.d; c0 += CH) {
+    for (int i = threadIdx.x; i < TT * CH; i += NTHR) {
+      const int t = i / CH, c = i % CH, s = tok0 + t;
+      sx[t][c] = (s < D.S && c0 + c < D.d) ? h0[((size_t)b * D.S + s) * D.d + c0 + c] : 0.f;
+    }
+    for (int i = threadIdx.x; i < CH * D.m; i += NTHR) {
+      const int c = i / D.m, j = i % D.m;
+      const bool ok = c0 + c < D.d;
+      sv1[c][j] = ok ? vb[(size_t)(c0 + c) * D.m + j] : 0.f;
+      sv3[c][j] = ok ? vb[(size_t)(2 * D.d + c0 + c) * D.m + j] : 0.f;
+    }
+    __syncthreads();
+#pragma unroll 4
+    for (int c = 0; c < CH; ++c) {
+#pragma unroll
+      for (int q = 0; q < 2; ++q) {
+        const int j = lane + 32 * q;
+        if (j < D.m) {
+          const float w1 = sv1[c][j], w3 = sv3[c][j];
+#pragma unroll
+          for (int t = 0; t < 4; ++t) { const float x = sx[warp * 4 + t][c]; acc[t][q] += x * (rs[t] * w1 + w3); }
+        }
+      }
+    }
+    __syncthreads();
+  }
+#pragma unroll
+  for (int t = 0; t < 4; ++t) {
+    const int s = tok0 + warp * 4 + t;
+    if (s < D.S) {
+#pragma unroll
+      for (int q = 0; q < 2; ++q) { const int j = lane + 32 * q; if (j < D.m) act[((size_t)b * D.S + s) * D.m + j] = acc[t][q]; }
+    }
+  }
+}
+
+// MODE 0 (forward):  out = h + s_cfg*scale*tanh(gain*h + silu(act) @ u + bias)
+// MODE 1 (backward): dupd = dout*s_cfg*scale*(1 - tanh^2);  dh0 = dout + gain*dupd   (dupd -> scratch)
+template <int MODE>
+__global__ void __launch_bounds__(NTHR)
+phi_out_kernel(const float* __restrict__ h0, const float* __restrict__ act, const float* __restrict__ gain,
+               const float* __restrict__ u, const float* __restrict__ bias, const float* __restrict__ scale,
+               const int32_t* __restrict__ rid, const int32_t* __restrict__ sid, float s_cfg,
+               const float* __restrict__ dout, float* __restrict__ out, float* __restrict__ dupd, PhiDims D) {
+  __shared__ float ssa[TT][MMAX];
+  const int tiles = rte::ceil_div(D.S, TT);
+  const int b = blockIdx.x / tiles, tok0 = (blockIdx.x % tiles) * TT;
+  const size_t key = key_of(rid, sid, b, D.K);
+  for (int i = threadIdx.x; i < TT * D.m; i += NTHR) {
+    const int t = i / D.m, j = i % D.m, s = tok0 + t;
+    ssa[t][j] = (s < D.S) ? rte::silu_f(act[((size_t)b * D.S + s) * D.m + j]) : 0.f;
+  }
+  __syncthreads();
+  const float* ub = u + key * D.m * D.d;
+  for (int c = threadIdx.x; c < D.d; c += NTHR) {
+    float ur[MMAX];
+#pragma unroll
+    for (int j = 0; j < MMAX; ++j) ur[j] = (j < D.m) ? ub[(size_t)j * D.d + c] : 0.f;
+    const float g = gain[key * D.d + c], bs = bias[key * D.d + c], sc = s_cfg * scale[key * D.d + c];
+    for (int t = 0; t < TT; ++t) {
+      const int s = tok0 + t;
+      if (s >= D.S) break;
+      float low = 0.f;
+#pragma unroll
+      for (int j = 0; j < MMAX; ++j) low += ssa[t][j] * ur[j];
+      const size_t idx = ((size_t)b * D.S + s) * D.d + c;
+      const float h = h0[idx];
+      const float th = tanhf(g * h + low + bs);
+      if (MODE == 0) {
+        out[idx] = h + sc * th;
+      } else {
+        const float du = dout[idx] * sc * (1.f - th * th);
+        dupd[idx] = du;
+        out[idx] = dout[idx] + g * du;
+      }
+    }
+  }
+}
+
+// da[tok, j] = silu'(act[tok,j]) * sum_c dupd[tok,c] * u[j,c]
+__global__ void __launch_bounds__(NTHR)
+phi_da_kernel(const float* __restrict__ dupd, const float* __restrict__ act, const float* __restrict__ u,
+              const int32_t* __restrict__ rid, const int32_t* __restrict__ sid, float* __restrict__ da, PhiDims D) {
+  __shared__ float sd[TT][CH + 1];
+  __shared__ float su[MMAX][CH + 1];
+  const int tiles = rte::ceil_div(D.S, TT);
+  const int b = blockIdx.x / tiles, tok0 = (blockIdx.x % tiles) * TT;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const float* ub = u + key_of(rid, sid, b, D.K) * D.m * D.d;
+  float acc[4][2];
+#pragma unroll
+  for (int t = 0; t < 4; ++t) acc[t][0] = acc[t][1] = 0.f;
+  for (int c0 = 0; c0 < D.d; c0 += CH) {
+    for (int i = threadIdx.x; i < TT * CH; i += NTHR) {
+      const int t = i / CH, c = i % CH, s = tok0 + t;
+      sd[t][c] = (s < D.S && c0 + c < D.d) ? dupd[((size_t)b * D.S + s) * D.d + c0 + c] : 0.f;
+    }
+    for (int i = threadIdx.x; i < D.m * CH; i += NTHR) {
+      const int j = i / CH, c = i % CH;
+      su[j][c] = (c0 + c < D.d) ? ub[(size_t)j * D.d + c0 + c] : 0.f;
+    }
+    __syncthreads();
+#pragma unroll 4
+    for (int c = 0; c < CH; ++c) {
+#pragma unroll
+      for (int q = 0; q < 2; ++q) {
+        const int j = lane + 32 * q;
+        if (j < D.m) {
+          const float w = su[j][c];
+#pragma unroll
+          for (int t = 0; t < 4; ++t) acc[t][q] += sd[warp * 4 + t][c] * w;
+        }
+      }
+    }
+    __syncthreads();
+  }
+#pragma unroll
+  for (int t = 0; t < 4; ++t) {
+    const int s = tok0 + warp * 4 + t;
+    if (s < D.S) {
+#pragma unroll
+      for (int q = 0; q < 2; ++q) {
+        const int j = lane + 32 * q;
+        if (j < D.m) {
+          const size_t idx = ((size_t)b * D.S + s) * D.m + j;
+          const float a = act[idx], sg = rte::sigmoid_f(a);
+          da[idx] = acc[t][q] * sg * (1.f + a * (1.f - sg));
+        }
+      }
+    }
+  }
+}
+
+// Per-sample parameter gradients of u, gain, bias:  pu[b][j,c], pg[b][c], pb[b][c].
+__global__ void __launch_bounds__(NTHR)
+phi_pu_kernel(const float* __restrict__ h0, const float* __restrict__ act, const float* __restrict__ dupd,
+              float* __restrict__ pu, float* __restrict__ pg, float* __restrict__ pb, PhiDims D) {
+  extern __shared__ float ssa[];     // [S][m]
+  const int cblocks = rte::ceil_div(D.d, NTHR);
+  const int b = blockIdx.x / cblocks, c = (blockIdx.x % cblocks) * NTHR + threadIdx.x;
+  for (int i = threadIdx.x; i < D.S * D.m; i += NTHR) ssa[i] = rte::silu_f(act[(size_t)b * D.S * D.m + i]);
+  __syncthreads();
+  if (c >= D.d) return;
+  float au[MMAX];
+#pragma unroll
+  for (int j = 0; j < MMAX; ++j) au[j] = 0.f;
+  float ag = 0.f, ab = 0.f;
+  for (int s = 0; s < D.S; ++s) {
+    const size_t idx = ((size_t)b * D.S + s) * D.d + c;
+    const float du = dupd[idx];
+    ag += du * h0[idx];
+    ab += du;
+#pragma unroll
+    for (int j = 0; j < MMAX; ++j) if (j < D.m) au[j] += ssa[s * D.m + j] * du;
+  }
+  pg[(size_t)b * D.d + c] = ag;
+  pb[(size_t)b * D.d + c] = ab;
+#pragma unroll
+  for (int j = 0; j < MMAX; ++j) if (j < D.m) pu[((size_t)b * D.m + j) * D.d + c] = au[j];
+}
+
+// Per-sample gradient of v:  pv[b][c', j] for c' in [0, 3d):
+//   c' <  d  : sum_s h0[s,c]*rstd[s] * da[s,j]
+//   c' < 2d  : pooled[b,c] * sum_s da[s,j]
+//   else     : sum_s h0[s,c] * da[s,j]
+__global__ void __launch_bounds__(NTHR)
+phi_pv_kernel(const float* __restrict__ h0, const float* __restrict__ rstd, const float* __restrict__ pooled,
+              const float* __restrict__ da, float* __restrict__ pv, PhiDims D) {
+  extern __shared__ float sm[];      // sda[S][m], rs[S], sx[S][8]
+  float* sda = sm;
+  float* rs = sm + D.S * D.m;
+  float* sx = rs + D.S;
+  constexpr int ROWS = 8;
+  const int rblocks = rte::ceil_div(D.d, ROWS);
+  const int b = blockIdx.x / rblocks, c0 = (blockIdx.x % rblocks) * ROWS;
+  for (int i = threadIdx.x; i < D.S * D.m; i += NTHR) sda[i] = da[(size_t)b * D.S * D.m + i];
+  for (int i = threadIdx.x; i < D.S; i += NTHR) rs[i] = rstd[(size_t)b * D.S + i];
+  for (int i = threadIdx.x; i < D.S * ROWS; i += NTHR) {
+    const int s = i / ROWS, r = i % ROWS;
+    sx[i] = (c0 + r < D.d) ? h0[((size_t)b * D.S + s) * D.d + c0 + r] : 0.f;
+  }
+  __syncthreads();
+  float* pvb = pv + (size_t)b * 3 * D.d * D.m;
+  for (int o = threadIdx.x; o < ROWS * D.m; o += NTHR) {
+    const int r = o / D.m, j = o % D.m, c = c0 + r;
+    if (c >= D.d) continue;
+    float a1 = 0.f, a2 = 0.f, a3 = 0.f;
+    for (int s = 0; s < D.S; ++s) {
+      const float dv = sda[s * D.m + j], x = sx[s * ROWS + r];
+      a1 += x * rs[s] * dv;
+      a2 += dv;
+      a3 += x * dv;
+    }
+    pvb[(size_t)c * D.m + j] = a1;
+    pvb[(size_t)(D.d + c) * D.m + j] = pooled[(size_t)b * D.d + c] * a2;
+    pvb[(size_t)(2 * D.d + c) * D.m + j] = a3;
+  }
+}
+
+// sda[b, j] = sum_s da[b,s,j]  ->  dpool[b, c] = (1/S) * sum_j sda[b,j] * v2[c,j]
+__global__ void __launch_bounds__(NTHR)
+phi_dpool_kernel(const float* __restrict__ da, const float* __restrict__ v, const int32_t* __restrict__ rid,
+                 const int32_t* __restrict__ sid, float* __restrict__ dpool, PhiDims D) {
+  __shared__ float ssum[MMAX];
+  const int b = blockIdx.x;
+  for (int j = threadIdx.x; j < D.m; j += NTHR) {
+    float a = 0.f;
+    for (int s = 0; s < D.S; ++s) a += da[((size_t)b * D.S + s) * D.m + j];
+    ssum[j] = a;
+  }
+  __syncthreads();
+  const float* v2 = v + (key_of(rid, sid, b, D.K) * 3 * D.d + D.d) * D.m;
+  for (int c = threadIdx.x; c < D.d; c += NTHR) {
+    float a = 0.f;
+    for (int j = 0; j < D.m; ++j) a += ssum[j] * v2[(size_t)c * D.m + j];
+    dpool[(size_t)b * D.d + c] = a / (float)D.S;
+  }
+}
+
+// dh0[tok,:] += da @ v3^T + rmsnorm_backward(da @ v1^T + dpool[b,:])     (one warp per token)
+__global__ void __launch_bounds__(NTHR)
+phi_dz_kernel(const float* __restrict__ h0, const float* __restrict__ rstd, const float* __restrict__ da,
+              const float* __restrict__ dpool, const float* __restrict__ v, const int32_t* __restrict__ rid,
+              const int32_t* __restrict__ sid, float* __restrict__ dh0, PhiDims D) {
+  __shared__ float sv1[CH][MMAX + 1];
+  __shared__ float sv3[CH][MMAX + 1];
+  __shared__ float sda[TT][MMAX];
+  const int tiles = rte::ceil_div(D.S, TT);
+  const int b = blockIdx.x / tiles, tok0 = (blockIdx.x % tiles) * TT;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const float* vb = v + key_of(rid, sid, b, D.K) * 3 * D.d * D.m;
+  for (int i = threadIdx.x; i < TT * D.m; i += NTHR) {
+    const int t = i / D.m, j = i % D.m, s = tok0 + t;
+    sda[t][j] = (s < D.S) ? da[((size_t)b * D.S + s) * D.m + j] : 0.f;
+  }
+  // pass 1: dh0 += da @ v3^T and the row dot products <dn, xhat>; pass 2 recomputes dn per chunk
+  float dot[4] = {0.f, 0.f, 0.f, 0.f};
+  const int nchunks = rte::ceil_div(D.d, CH);
+  for (int ch = 0; ch < nchunks; ++ch) {
+    const int c0 = ch * CH;
+    __syncthreads();
+    for (int i = threadIdx.x; i < CH * D.m; i += NTHR) {
+      const int c = i / D.m, j = i % D.m;
+      const bool ok = c0 + c < D.d;
+      sv1[c][j] = ok ? vb[(size_t)(c0 + c) * D.m + j] : 0.f;
+      sv3[c][j] = ok ? vb[(size_t)(2 * D.d + c0 + c) * D.m + j] : 0.f;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int q = 0; q < 2; ++q) {
+      const int cl = lane + 32 * q, c = c0 + cl;
+#pragma unroll
+      for (int t = 0; t < 4; ++t) {
+        const int s = tok0 + warp * 4 + t;
+        float a1 = 0.f, a3 = 0.f;
+        for (int j = 0; j < D.m; ++j) { const float dv = sda[warp * 4 + t][j]; a1 += dv * sv1[cl][j]; a3 += dv * sv3[cl][j]; }
+        if (s < D.S && c < D.d) {
+          const size_t idx = ((size_t)b * D.S + s) * D.d + c;
+          const float dnv = a1 + dpool[(size_t)b * D.d + c];
+          dh0[idx] += a3;
+          dot[t] += dnv * h0[idx] * rstd[(size_t)b * D.S + s];
+        }
+      }
+    }
+  }
+#pragma unroll
+  for (int t = 0; t < 4; ++t) dot[t] = rte::warp_sum(dot[t]) / (float)D.d;
+  // second pass: recompute dn per chunk and finish dx = rstd * (dn - xhat * dot)
+  for (int ch = 0; ch < nchunks; ++ch) {
+    const int c0 = ch * CH;
+    __syncthreads();
+    for (int i = threadIdx.x; i < CH * D.m; i += NTHR) {
+      const int c = i / D.m, j = i % D.m;
+      sv1[c][j] = (c0 + c < D.d) ? vb[(size_t)(c0 + c) * D.m + j] : 0.f;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int q = 0; q < 2; ++q) {
+      const int cl = lane + 32 * q, c = c0 + cl;
+#pragma unroll
+      for (int t = 0; t < 4; ++t) {
+        const int s = tok0 + warp * 4 + t;
+        if (s < D.S && c < D.d) {
+          float a1 = 0.f;
+          for (int j = 0; j < D.m; ++j) a1 += sda[warp * 4 + t][j] * sv1[cl][j];
+          const size_t idx = ((size_t)b * D.S + s) * D.d + c;
+          const float r = rstd[(size_t)b * D.S + s];
+          const float dnv = a1 + dpool[(size_t)b * D.d + c];
+          dh0[idx] += r * (dnv - h0[idx] * r * dot[t]);
+        }
+      }
+    }
+  }
+}
+
+// out[key][e] = sum over samples b with key(b) == key, in sample order, of partial[b][e]
+__global__ void __launch_bounds__(NTHR)
+phi_reduce_keys_kernel(const float* __restrict__ partial, const int32_t* __restrict__ rid, const int32_t* __restrict__ sid,
+                       float* __restrict__ out, int B, int K, int n_keys, long long elems) {
+  const long long e = blockIdx.x * (long long)NTHR + threadIdx.x;
+  if (e >= elems) return;
+  for (int key = 0; key < n_keys; ++key) {
+    float acc = 0.f;
+    for (int b = 0; b < B; ++b)
+      if (rid[b] * K + sid[b] == key) acc += partial[(size_t)b * elems + e];
+    out[(size_t)key * elems + e] = acc;
+  }
+}
+
+}  // namespace
+
+#define ST(s) reinterpret_cast<cudaStream_t>(s)
+
+extern "C" int rte_macro_phi_fwd(const float* h0, const rte_phi_params* p, const int32_t* recipe_id,
+                                 const int32_t* stride_id, float s_cfg, float* out, float* rstd, float* pooled,
+                                 float* act, int32_t B, int32_t S, int32_t d, int32_t m, int32_t K_strides,
+                                 float eps, rte_stream_t stream) {
+  RTE_CHECK_ARG(h0 && p && p->gain && p->v && p->u && p->bias && p->scale && recipe_id && stride_id && out && rstd &&
+                pooled && act && B > 0 && S > 0 && d > 0 && m > 0 && K_strides > 0);
+  if (m > MMAX) return RTE_ERR_UNSUPPORTED;
+  PhiDims D{B, S, d, m, K_strides};
+  const int tiles = rte::ceil_div(S, TT);
+  // `act` doubles as the home of pa (B*m floats) is NOT safe; pa lives at the tail of `pooled`'s
+  // companion: callers give pooled >= B*d + B*m floats.
+  float* pa = pooled + (size_t)B * d;
+  phi_prep_kernel<<<B, NTHR, (size_t)(S + d) * sizeof(float), ST(stream)>>>(h0, p->v, recipe_id, stride_id, rstd, pooled, pa, D, eps);
+  RTE_LAUNCH_CHECK();
+  phi_act_kernel<<<B * tiles, NTHR, 0, ST(stream)>>>(h0, rstd, pa, p->v, recipe_id, stride_id, act, D);
+  RTE_LAUNCH_CHECK();
+  phi_out_kernel<0><<<B * tiles, NTHR, 0, ST(stream)>>>(h0, act, p->gain, p->u, p->bias, p->scale, recipe_id, stride_id,
+                                                        s_cfg, nullptr, out, nullptr, D);
+  RTE_LAUNCH_CHECK();
+  return RTE_OK;
+}
+
+extern "C" int rte_macro_phi_bwd(const float* h0, const float* dout, const rte_phi_params* p, const int32_t* recipe_id,
+                                 const int32_t* stride_id, float s_cfg, const float* rstd, const float* pooled,
+                                 const float* act, float* dh0, const rte_phi_grads* g, float* scratch, int32_t B,
+                                 int32_t S, int32_t d, int32_t m, int32_t R, int32_t K_strides, float eps,
+                                 rte_stream_t stream) {
+  (void)eps;
+  RTE_CHECK_ARG(h0 && dout && p && g && recipe_id && stride_id && rstd && pooled && act && dh0 && scratch && B > 0 &&
+                S > 0 && d > 0 && m > 0 && R > 0 && K_strides > 0);
+  RTE_CHECK_ARG(g->gain && g->v && g->u && g->bias);
+  if (m > MMAX) return RTE_ERR_UNSUPPORTED;
+  PhiDims D{B, S, d, m, K_strides};
+  const int tiles = rte::ceil_div(S, TT);
+  const size_t M = (size_t)B * S;
+  // scratch layout (floats): dupd[M*d] | da[M*m] | dpool[B*d] | pu[B*m*d] | pg[B*d] | pb[B*d] | pv[B*3d*m]
+  float* dupd = scratch;
+  float* da = dupd + M * d;
+  float* dpool = da + M * m;
+  float* pu = dpool + (size_t)B * d;
+  float* pg = pu + (size_t)B * m * d;
+  float* pb = pg + (size_t)B * d;
+  float* pv = pb + (size_t)B * d;
+  phi_out_kernel<1><<<B * tiles, NTHR, 0, ST(stream)>>>(h0, act, p->gain, p->u, p->bias, p->scale, recipe_id, stride_id,
+                                                        s_cfg, dout, dh0, dupd, D);
+  RTE_LAUNCH_CHECK();
+  phi_da_kernel<<<B * tiles, NTHR, 0, ST(stream)>>>(dupd, act, p->u, recipe_id, stride_id, da, D);
+  RTE_LAUNCH_CHECK();
+  phi_dpool_kernel<<<B, NTHR, 0, ST(stream)>>>(da, p->v, recipe_id, stride_id, dpool, D);
+  RTE_LAUNCH_CHECK();
+  phi_dz_kernel<<<B * tiles, NTHR, 0, ST(stream)>>>(h0, rstd, da, dpool, p->v, recipe_id, stride_id, dh0, D);
+  RTE_LAUNCH_CHECK();
+  const size_t smem_pu = (size_t)S * m * sizeof(float);
+  const size_t smem_pv = ((size_t)S * m + S + (size_t)S * 8) * sizeof(float);
+  if (smem_pu > 48 * 1024 || smem_pv > 48 * 1024) {
+    static bool set = false;
+    if (!set) {
+      if (cudaFuncSetAttribute(phi_pu_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024) != cudaSuccess ||
+          cudaFuncSetAttribute(phi_pv_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024) != cudaSuccess)
+        return RTE_ERR_LAUNCH;
+      set = true;
+    }
+  }
+  phi_pu_kernel<<<B * rte::ceil_div(d, NTHR), NTHR, smem_pu, ST(stream)>>>(h0, act, dupd, pu, pg, pb, D);
+  RTE_LAUNCH_CHECK();
+  phi_pv_kernel<<<B * rte::ceil_div(d, 8), NTHR, smem_pv, ST(stream)>>>(h0, rstd, pooled, da, pv, D);
+  RTE_LAUNCH_CHECK();
+  const int n_keys = R * K_strides;
+  const long long eu = (long long)m * d, ev = (long long)3 * d * m, ed = d;
+  phi_reduce_keys_kernel<<<(int)rte::ceil_div64(eu, NTHR), NTHR, 0, ST(stream)>>>(pu, recipe_id, stride_id, g->u, B, K_strides, n_keys, eu);
+  RTE_LAUNCH_CHECK();
+  phi_reduce_keys_kernel<<<(int)rte::ceil_div64(ev, NTHR), NTHR, 0, ST(stream)>>>(pv, recipe_id, stride_id, g->v, B, K_strides, n_keys, ev);
+  RTE_LAUNCH_CHECK();
+  phi_reduce_keys_kernel<<<(int)rte::ceil_div64(ed, NTHR), NTHR, 0, ST(stream)>>>(pg, recipe_id, stride_id, g->gain, B, K_strides, n_keys, ed);
+  RTE_LAUNCH_CHECK();
+  phi_reduce_keys_kernel<<<(int)rte::ceil_div64(ed, NTHR), NTHR, 0, ST(stream)>>>(pb, recipe_id, stride_id, g->bias, B, K_strides, n_keys, ed);
+  RTE_LAUNCH_CHECK();
+  return RTE_OK;
+}

@@ -1,0 +1,265 @@
+// Per-sample router of the recursive model and the backward pass of its auxiliary losses.
+// One decision per SAMPLE from pooled = mean over the sequence of h0: two small MLPs
+// (d -> hid -> R recipes, d -> hid -> K depths), softmaxes, arg-max ids with ties to the LOWEST
+// index, per-pass recipe ids (logits + per-pass bias), entropies, expected depth.
+// The matrices are tiny (hid x d floats, read once per sample from L2), so one CTA per sample.
+
+#include "rte_common.cuh"
+
+namespace {
+
+constexpr int NTHR = 256;
+
+__global__ void __launch_bounds__(NTHR)
+pool_kernel(const float* __restrict__ h0, float* __restrict__ pooled, int S, int d) {
+  const int b = blockIdx.y, c = blockIdx.x * NTHR + threadIdx.x;
+  if (c >= d) return;
+  float acc = 0.f;
+  for (int s = 0; s < S; ++s) acc += h0[((size_t)b * S + s) * d + c];
+  pooled[(size_t)b * d + c] = acc / (float)S;
+}
+
+// hidden_pre[j] = b0[j] + W0[j,:] . x ; logits[r] = b2[r] + W2[r,:] . silu(hidden_pre)
+__device__ void mlp_forward(const float* __restrict__ w0, const float* __restrict__ b0, const float* __restrict__ w2,
+                            const float* __restrict__ b2, const float* xs, float* hs, float* pre_out, float* logits,
+                            int d, int hid, int nout) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  for (int j = warp; j < hid; j += NTHR / 32) {
+    float acc = 0.f;
+    for (int c = lane; c < d; c += 32) acc += w0[(size_t)j * d + c] * xs[c];
+    acc = rte::warp_sum(acc);
+    if (lane == 0) { acc += b0[j]; pre_out[j] = acc; hs[j] = rte::silu_f(acc); }
+  }
+  __syncthreads();
+  for (int r = warp; r < nout; r += NTHR / 32) {
+    float acc = 0.f;
+    for (int j = lane; j < hid; j += 32) acc += w2[(size_t)r * hid + j] * hs[j];
+    acc = rte::warp_sum(acc);
+    if (lane == 0) logits[r] = acc + b2[r];
+  }
+  __syncthreads();
+}
+
+__device__ __forceinline__ int argmax_lowest(const float* v, int n) {
+  int best = 0;
+  for (int i = 1; i < n; ++i) if (v[i] > v[best]) best = i;   // strict '>' keeps the lowest index on ties
+  return best;
+}
+__device__ __forceinline__ void softmax_small(const float* logits, float* probs, int n) {
+  float mx = logits[0];
+  for (int i = 1; i < n; ++i) mx = fmaxf(mx, logits[i]);
+  float s = 0.f;
+  for (int i = 0; i < n; ++i) { probs[i] = expf(logits[i] - mx); s += probs[i]; }
+  const float inv = 1.f / s;
+  for (int i = 0; i < n; ++i) probs[i] *= inv;
+}
+
+__global__ void __launch_bounds__(NTHR)
+router_fwd_kernel(rte_router_weights w, const int32_t* __restrict__ depth_values, rte_router_out o, int d, int hid,
+                  int R, int K, int T, int fixed_recipe, int fixed_depth_id) {
+  extern __shared__ float sm[];   // xs[d], hs[hid]
+  __shared__ float rl[RTE_ROUTER_MAX_R], dl[RTE_ROUTER_MAX_K];
+  float* xs = sm;
+  float* hs = sm + d;
+  const int b = blockIdx.x;
+  for (int c = threadIdx.x; c < d; c += NTHR) xs[c] = o.pooled[(size_t)b * d + c];
+  __syncthreads();
+  mlp_forward(w.r_w0, w.r_b0, w.r_w2, w.r_b2, xs, hs, o.r_hidden_pre + (size_t)b * hid, rl, d, hid, R);
+  mlp_forward(w.d_w0, w.d_b0, w.d_w2, w.d_b2, xs, hs, o.d_hidden_pre + (size_t)b * hid, dl, d, hid, K);
+  if (threadIdx.x == 0) {
+    float rp[RTE_ROUTER_MAX_R], dp[RTE_ROUTER_MAX_K], tmp[RTE_ROUTER_MAX_R], tp[RTE_ROUTER_MAX_R];
+    softmax_small(rl, rp, R);
+    softmax_small(dl, dp, K);
+    float rent = 0.f, dent = 0.f, ed = 0.f;
+    for (int r = 0; r < R; ++r) {
+      o.recipe_logits[(size_t)b * R + r] = rl[r];
+      o.recipe_probs[(size_t)b * R + r] = rp[r];
+      rent -= logf(fmaxf(rp[r], 1e-9f)) * rp[r];
+    }
+    for (int k = 0; k < K; ++k) {
+      o.depth_probs[(size_t)b * K + k] = dp[k];
+      dent -= logf(fmaxf(dp[k], 1e-9f)) * dp[k];
+      ed += dp[k] * (float)depth_values[k];
+    }
+    o.expected_depth[b] = ed;
+    o.router_entropy[b] = rent + dent;
+    o.recipe_id[b] = fixed_recipe >= 0 ? fixed_recipe : argmax_lowest(rp, R);
+    for (int t = 0; t < T; ++t) {
+      int id = fixed_recipe;
+      if (fixed_recipe < 0) {
+        for (int r = 0; r < R; ++r) tmp[r] = rl[r] + w.pass_recipe_bias[t * R + r];
+        softmax_small(tmp, tp, R);
+        id = argmax_lowest(tp, R);
+      }
+      o.recipe_id_by_pass[(size_t)b * T + t] = id;
+    }
+    const int did = fixed_depth_id >= 0 ? fixed_depth_id : argmax_lowest(dp, K);
+    o.depth_id[b] = did;
+    o.depth[b] = depth_values[did];
+  }
+}
+
+// aux losses and the batch-mean of the recipe probabilities
+__global__ void __launch_bounds__(NTHR)
+aux_kernel(const float* __restrict__ recipe_probs, const float* __restrict__ expected_depth, float lambda_load,
+           float lambda_depth, float* __restrict__ aux, float* __restrict__ mean_prob, int B, int R) {
+  __shared__ float red[32];
+  __shared__ float mp[RTE_ROUTER_MAX_R];
+  for (int r = threadIdx.x; r < R; r += NTHR) {
+    float acc = 0.f;
+    for (int b = 0; b < B; ++b) acc += recipe_probs[(size_t)b * R + r];
+    acc /= (float)B;
+    mp[r] = acc;
+    mean_prob[r] = acc;
+  }
+  float ed = 0.f;
+  for (int b = threadIdx.x; b < B; b += NTHR) ed += expected_depth[b];
+  ed = rte::block_sum(ed, red);
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    float sq = 0.f;
+    for (int r = 0; r < R; ++r) sq += mp[r] * mp[r];
+    aux[0] = lambda_load * ((float)R * sq - 1.f);
+    aux[1] = lambda_depth * ed / (float)B;
+  }
+}
+
+// per-sample backward through softmax and both MLP heads; dh0 += dpooled / S
+__device__ void mlp_backward_sample(const float* __restrict__ w0, const float* __restrict__ w2, const float* dlog,
+                                    const float* __restrict__ pre, float* dpre_out, float* dhs, int d, int hid, int nout) {
+  for (int j = threadIdx.x; j < hid; j += NTHR) {
+    float acc = 0.f;
+    for (int r = 0; r < nout; ++r) acc += w2[(size_t)r * hid + j] * dlog[r];
+    const float a = pre[j], sg = rte::sigmoid_f(a);
+    const float v = acc * sg * (1.f + a * (1.f - sg));
+    dhs[j] = v;
+    dpre_out[j] = v;
+  }
+  __syncthreads();
+  (void)w0; (void)d;
+}
+
+__global__ void __launch_bounds__(NTHR)
+router_bwd_sample_kernel(rte_router_weights w, rte_router_out o, const int32_t* __restrict__ depth_values,
+                         const float* __restrict__ mean_prob, float lambda_load, float lambda_depth,
+                         float* __restrict__ dpre_r, float* __restrict__ dpre_d, float* __restrict__ dlog_r,
+                         float* __restrict__ dlog_d, float* __restrict__ dh0, int B, int S, int d, int hid, int R, int K) {
+  extern __shared__ float sm[];   // dhr[hid], dhd[hid]
+  __shared__ float dlr[RTE_ROUTER_MAX_R], dld[RTE_ROUTER_MAX_K];
+  float* dhr = sm;
+  float* dhd = sm + hid;
+  const int b = blockIdx.x;
+  if (threadIdx.x == 0) {
+    float dot = 0.f;
+    for (int r = 0; r < R; ++r) dot += o.recipe_probs[(size_t)b * R + r] * (lambda_load * (float)R * 2.f * mean_prob[r] / (float)B);
+    for (int r = 0; r < R; ++r) {
+      const float p = o.recipe_probs[(size_t)b * R + r];
+      const float v = p * (lambda_load * (float)R * 2.f * mean_prob[r] / (float)B - dot);
+      dlr[r] = v;
+      dlog_r[(size_t)b * R + r] = v;
+    }
+    float dotd = 0.f;
+    for (int k = 0; k < K; ++k) dotd += o.depth_probs[(size_t)b * K + k] * (lambda_depth * (float)depth_values[k] / (float)B);
+    for (int k = 0; k < K; ++k) {
+      const float p = o.depth_probs[(size_t)b * K + k];
+      const float v = p * (lambda_depth * (float)depth_values[k] / (float)B - dotd);
+      dld[k] = v;
+      dlog_d[(size_t)b * K + k] = v;
+    }
+  }
+  __syncthreads();
+  mlp_backward_sample(w.r_w0, w.r_w2, dlr, o.r_hidden_pre + (size_t)b * hid, dpre_r + (size_t)b * hid, dhr, d, hid, R);
+  mlp_backward_sample(w.d_w0, w.d_w2, dld, o.d_hidden_pre + (size_t)b * hid, dpre_d + (size_t)b * hid, dhd, d, hid, K);
+  for (int c = threadIdx.x; c < d; c += NTHR) {
+    float acc = 0.f;
+    for (int j = 0; j < hid; ++j) acc += w.r_w0[(size_t)j * d + c] * dhr[j] + w.d_w0[(size_t)j * d + c] * dhd[j];
+    acc /= (float)S;
+    for (int s = 0; s < S; ++s) dh0[((size_t)b * S + s) * d + c] += acc;
+  }
+}
+
+// dW0[j,c] = sum_b dpre[b,j] * pooled[b,c];  db0[j] = sum_b dpre[b,j]
+__global__ void __launch_bounds__(NTHR)
+router_dw0_kernel(const float* __restrict__ dpre, const float* __restrict__ pooled, float* __restrict__ dw0,
+                  float* __restrict__ db0, int B, int d, int hid) {
+  const long long i = blockIdx.x * (long long)NTHR + threadIdx.x;
+  if (i >= (long long)hid * d) return;
+  const int j = int(i / d), c = int(i % d);
+  float acc = 0.f, accb = 0.f;
+  for (int b = 0; b < B; ++b) {
+    const float v = dpre[(size_t)b * hid + j];
+    acc += v * pooled[(size_t)b * d + c];
+    accb += v;
+  }
+  dw0[i] = acc;
+  if (c == 0) db0[j] = accb;
+}
+// dW2[r,j] = sum_b dlog[b,r] * silu(pre[b,j]);  db2[r] = sum_b dlog[b,r]
+__global__ void __launch_bounds__(NTHR)
+router_dw2_kernel(const float* __restrict__ dlog, const float* __restrict__ pre, float* __restrict__ dw2,
+                  float* __restrict__ db2, int B, int hid, int nout) {
+  const int i = blockIdx.x * NTHR + threadIdx.x;
+  if (i >= nout * hid) return;
+  const int r = i / hid, j = i % hid;
+  float acc = 0.f, accb = 0.f;
+  for (int b = 0; b < B; ++b) {
+    const float v = dlog[(size_t)b * nout + r];
+    acc += v * rte::silu_f(pre[(size_t)b * hid + j]);
+    accb += v;
+  }
+  dw2[i] = acc;
+  if (j == 0) db2[r] = accb;
+}
+
+}  // namespace
+
+#define ST(s) reinterpret_cast<cudaStream_t>(s)
+
+extern "C" int rte_router_fwd(const float* h0, const rte_router_weights* w, const int32_t* depth_values,
+                              const rte_router_out* out, int32_t B, int32_t S, int32_t d, int32_t hid, int32_t R,
+                              int32_t K, int32_t T, int32_t fixed_recipe, int32_t fixed_depth_id, rte_stream_t stream) {
+  RTE_CHECK_ARG(h0 && w && depth_values && out && B > 0 && S > 0 && d > 0 && hid > 0);
+  RTE_CHECK_ARG(R > 0 && R <= RTE_ROUTER_MAX_R && K > 0 && K <= RTE_ROUTER_MAX_K && T > 0 && T <= RTE_ROUTER_MAX_T);
+  RTE_CHECK_ARG(fixed_recipe < R && fixed_depth_id < K);
+  RTE_CHECK_ARG(out->pooled && out->r_hidden_pre && out->d_hidden_pre && out->recipe_logits && out->recipe_probs &&
+                out->depth_probs && out->expected_depth && out->router_entropy && out->recipe_id &&
+                out->recipe_id_by_pass && out->depth_id && out->depth);
+  const size_t smem = (size_t)(d + hid) * sizeof(float);
+  if (smem > 48 * 1024) return RTE_ERR_UNSUPPORTED;
+  pool_kernel<<<dim3(rte::ceil_div(d, NTHR), B), NTHR, 0, ST(stream)>>>(h0, out->pooled, S, d);
+  RTE_LAUNCH_CHECK();
+  router_fwd_kernel<<<B, NTHR, smem, ST(stream)>>>(*w, depth_values, *out, d, hid, R, K, T, fixed_recipe, fixed_depth_id);
+  RTE_LAUNCH_CHECK();
+  return RTE_OK;
+}
+
+extern "C" int rte_router_aux_bwd(const rte_router_weights* w, const rte_router_out* fwd, const int32_t* depth_values,
+                                  float lambda_load, float lambda_depth, float* aux, const rte_router_grads* grads,
+                                  float* dh0, float* scratch, int32_t B, int32_t S, int32_t d, int32_t hid, int32_t R,
+                                  int32_t K, rte_stream_t stream) {
+  RTE_CHECK_ARG(w && fwd && depth_values && aux && grads && dh0 && scratch && B > 0 && S > 0 && d > 0 && hid > 0);
+  RTE_CHECK_ARG(R > 0 && R <= RTE_ROUTER_MAX_R && K > 0 && K <= RTE_ROUTER_MAX_K);
+  RTE_CHECK_ARG(grads->r_w0 && grads->r_b0 && grads->r_w2 && grads->r_b2 && grads->d_w0 && grads->d_b0 && grads->d_w2 && grads->d_b2);
+  float* mean_prob = scratch;                       // [RTE_ROUTER_MAX_R]
+  float* dpre_r = scratch + RTE_ROUTER_MAX_R;       // [B, hid]
+  float* dpre_d = dpre_r + (size_t)B * hid;         // [B, hid]
+  float* dlog_r = dpre_d + (size_t)B * hid;         // [B, R]
+  float* dlog_d = dlog_r + (size_t)B * R;           // [B, K]
+  aux_kernel<<<1, NTHR, 0, ST(stream)>>>(fwd->recipe_probs, fwd->expected_depth, lambda_load, lambda_depth, aux, mean_prob, B, R);
+  RTE_LAUNCH_CHECK();
+  const size_t smem = (size_t)2 * hid * sizeof(float);
+  if (smem > 48 * 1024) return RTE_ERR_UNSUPPORTED;
+  router_bwd_sample_kernel<<<B, NTHR, smem, ST(stream)>>>(*w, *fwd, depth_values, mean_prob, lambda_load, lambda_depth,
+                                                          dpre_r, dpre_d, dlog_r, dlog_d, dh0, B, S, d, hid, R, K);
+  RTE_LAUNCH_CHECK();
+  const int g0 = (int)rte::ceil_div64((long long)hid * d, NTHR);
+  router_dw0_kernel<<<g0, NTHR, 0, ST(stream)>>>(dpre_r, fwd->pooled, grads->r_w0, grads->r_b0, B, d, hid);
+  RTE_LAUNCH_CHECK();
+  router_dw0_kernel<<<g0, NTHR, 0, ST(stream)>>>(dpre_d, fwd->pooled, grads->d_w0, grads->d_b0, B, d, hid);
+  RTE_LAUNCH_CHECK();
+  router_dw2_kernel<<<rte::ceil_div(R * hid, NTHR), NTHR, 0, ST(stream)>>>(dlog_r, fwd->r_hidden_pre, grads->r_w2, grads->r_b2, B, hid, R);
+  RTE_LAUNCH_CHECK();
+  router_dw2_kernel<<<rte::ceil_div(K * hid, NTHR), NTHR, 0, ST(stream)>>>(dlog_d, fwd->d_hidden_pre, grads->d_w2, grads->d_b2, B, hid, K);
+  RTE_LAUNCH_CHECK();
+  return RTE_OK;
+}

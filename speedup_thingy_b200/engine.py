@@ -1,0 +1,417 @@
+"""Host side of the accelerated training step.
+
+``TrainEngine`` mirrors the reference's ``TrainEngine.train_step`` for the modes ``recursive_macro``
+(training.py:1336-1476 -> models.py:681-723) and ``dense_exact`` (training.py:742-769): same parameter
+names and shapes (a ``state_dict`` of either side loads into the other), same loss assembly, same
+AdamW semantics (parameters that receive no gradient are left untouched).  Everything numerical runs
+in hand-written sm_100a kernels behind the C ABI; the forward AND backward sequences are written out
+explicitly here (no autograd), all buffers are allocated once, and the whole step -- forward, backward,
+gradient norm, AdamW with bf16 shadow refresh -- is captured in one CUDA graph and replayed per step.
+
+PyTorch is used for device memory, streams and graph capture only.
+"""
+from __future__ import annotations
+
+import math
+from dataclasses import dataclass, field
+from typing import Any
+
+import torch
+
+from . import _abi as A
+from .config import ExperimentConfig, ModelConfig, TrainingConfig
+from .ops import AdamWPlan
+
+LR_GROUPS = ["embedding", "prelude", "core", "macro", "coda", "output", "router", "dense"]
+
+
+# --------------------------------------------------------------------------- parameters
+def _block_shapes(prefix: str, cfg: ModelConfig) -> list[tuple[str, tuple]]:
+    d, f = cfg.d_model, cfg.d_ff
+    return [(f"{prefix}.norm1.weight", (d,)), (f"{prefix}.attn.wqkv.weight", (3 * d, d)),
+            (f"{prefix}.attn.wo.weight", (d, d)), (f"{prefix}.norm2.weight", (d,)),
+            (f"{prefix}.mlp.wug.weight", (2 * f, d)), (f"{prefix}.mlp.wd.weight", (d, f))]
+
+
+def parameter_shapes(cfg: ModelConfig) -> list[tuple[str, tuple]]:
+    """Parameter names and shapes in the reference's registration order (models.py:78-93, 125-151)."""
+    d, f, v = cfg.d_model, cfg.d_ff, cfg.vocab_size
+    out: list[tuple[str, tuple]] = [("embed.weight", (v, d))]
+    if cfg.topology == "dense":
+        for i in range(cfg.n_dense_layers):
+            out += _block_shapes(f"blocks.{i}", cfg)
+        return out + [("final_norm.weight", (d,))]
+    hid, r, k, t, m = cfg.router_hidden_dim, cfg.recipe_count, len(cfg.depth_choices), cfg.t_max, cfg.macro_rank
+    head_slots = max(1, cfg.head_groups // cfg.active_head_groups)
+    ffn_slots = max(1, cfg.ffn_groups // cfg.active_ffn_groups)
+    for i in range(cfg.n_prelude):
+        out += _block_shapes(f"prelude.{i}", cfg)
+    out += [("router.pass_recipe_bias", (t, r)), ("router.pass_factor_bias", (t, hid))]
+
+    def mlp(name: str, n_in: int, n_mid: int, n_out: int):
+        return [(f"router.{name}.0.weight", (n_mid, n_in)), (f"router.{name}.0.bias", (n_mid,)),
+                (f"router.{name}.2.weight", (n_out, n_mid)), (f"router.{name}.2.bias", (n_out,))]
+
+    out += mlp("recipe_mlp", d, hid, r) + mlp("factor_mlp", d, hid, hid)
+    for name, o in (("attn_bank_head", cfg.attn_banks), ("ffn_bank_head", cfg.ffn_banks),
+                    ("head_slot_head", head_slots), ("ffn_slot_head", ffn_slots)):
+        out += [(f"router.{name}.weight", (o, hid)), (f"router.{name}.bias", (o,))]
+    out += mlp("depth_mlp", d, hid, k)
+    out += [("core.pass_gamma1", (t, d)), ("core.pass_beta1", (t, d)), ("core.pass_gamma2", (t, d)),
+            ("core.pass_beta2", (t, d)), ("core.pass_attn_scale", (t,)), ("core.pass_mlp_scale", (t,)),
+            ("core.alpha_inj", ()), ("core.norm1.weight", (d,)), ("core.attn.wqkv", (cfg.attn_banks, d, 3 * d)),
+            ("core.attn.wo", (cfg.attn_banks, d, d)), ("core.norm2.weight", (d,)),
+            ("core.mlp.wug", (cfg.ffn_banks, d, 2 * f)), ("core.mlp.wd", (cfg.ffn_banks, f, d))]
+    out += [("macro.d_gain", (r, k, d)), ("macro.v", (r, k, 3 * d, m)), ("macro.u", (r, k, m, d)),
+            ("macro.bias", (r, k, d))]
+    for i in range(cfg.n_coda):
+        out += _block_shapes(f"coda.{i}", cfg)
+    return out + [("final_norm.weight", (d,))]
+
+
+def init_parameters(cfg: ModelConfig, seed: int = 0, std: float = 0.02) -> dict[str, torch.Tensor]:
+    """Seeded benchmark initialisation: tensors with >= 2 dims ~ N(0, std) from one CPU generator in
+    registration order; norm gains and per-pass scales 1; the input-skip gain 0.1; biases 0."""
+    gen = torch.Generator().manual_seed(seed)
+    params: dict[str, torch.Tensor] = {}
+    for name, shape in parameter_shapes(cfg):
+        if len(shape) >= 2:
+            params[name] = torch.randn(shape, generator=gen, dtype=torch.float32) * std
+        elif name.endswith(("norm1.weight", "norm2.weight", "final_norm.weight", "pass_attn_scale", "pass_mlp_scale")):
+            params[name] = torch.ones(shape, dtype=torch.float32)
+        elif name == "core.alpha_inj":
+            params[name] = torch.tensor(0.1, dtype=torch.float32)
+        else:
+            params[name] = torch.zeros(shape, dtype=torch.float32)
+    return params
+
+
+def lr_group_of(name: str, topology: str) -> str:
+    if topology == "dense":
+        return "dense"
+    for prefix, group in (("embed.", "embedding"), ("prelude.", "prelude"), ("core.", "core"), ("macro.", "macro"),
+                          ("coda.", "coda"), ("final_norm.", "coda"), ("lm_head.", "output"), ("router.", "router")):
+        if name.startswith(prefix):
+            return group
+    raise KeyError(name)
+
+
+# --------------------------------------------------------------------------- results
+@dataclass
+class TrainStepResult:
+    loss: float
+    metrics: dict[str, Any] = field(default_factory=dict)
+
+
+class _Block:
+    """Saved activations of one pre-norm transformer block (layers.py:646-656)."""
+
+    def __init__(self, prefix: str, M: int, cfg: ModelConfig, B: int, S: int, device):
+        d, f = cfg.d_model, cfg.d_ff
+        bf, f32 = torch.bfloat16, torch.float32
+        e = lambda *shape, dtype=bf: torch.empty(*shape, dtype=dtype, device=device)  # noqa: E731
+        self.prefix = prefix
+        self.n1, self.n2, self.y = e(M, d), e(M, d), e(M, d)
+        self.qkv, self.ug, self.z = e(M, 3 * d), e(M, 2 * f), e(M, f)
+        self.u, self.out = e(M, d, dtype=f32), e(M, d, dtype=f32)
+        self.rstd1, self.rstd2 = e(M, dtype=f32), e(M, dtype=f32)
+        self.lse = e(B * cfg.n_heads * S, dtype=f32)
+        self.x_in: torch.Tensor | None = None
+
+
+class TrainEngine:
+    def __init__(self, config: ExperimentConfig, params: dict[str, torch.Tensor] | None = None, *,
+                 device: str | torch.device = "cuda:0", ops=None, use_cuda_graph: bool = True):
+        self.config = config
+        self.cfg, self.tr = config.model, config.training
+        self.device = torch.device(device)
+        if ops is None:
+            from .ops import CudaOps  # raises when CUDA or the library is missing: no fallback
+            ops = CudaOps(self.device)
+        self.ops = ops
+        self.use_cuda_graph = bool(use_cuda_graph) and self.device.type == "cuda"
+        cfg, tr = self.cfg, self.tr
+        self.B, self.S = tr.batch_size, tr.seq_len
+        self.M = self.B * self.S
+        self.dense = cfg.topology == "dense"
+        if self.dense != (tr.mode == "dense_exact"):
+            raise ValueError("mode dense_exact needs topology 'dense'; recursive_macro needs 'recursive'")
+        if tr.audit_fixed_count_per_batch:
+            raise NotImplementedError("exact-audit replay is not wired into this engine yet")
+        if cfg.d_model % 8 or cfg.d_ff % 64 or cfg.vocab_size % 8 or cfg.head_dim not in (8, 16, 32, 64, 128):
+            raise NotImplementedError("kernel size limits: d_model % 8 == 0, d_ff % 64 == 0, vocab % 8 == 0, "
+                                      "head_dim in {8,16,32,64,128}")
+        if self.S > 256:
+            raise NotImplementedError("seq_len <= 256")
+        dev, f32, bf = self.device, torch.float32, torch.bfloat16
+        init = params if params is not None else init_parameters(cfg, seed=tr.seed)
+        self.params = {n: init[n].detach().to(dev, f32).contiguous().clone() for n, _ in parameter_shapes(cfg)}
+        self.global_step = 0
+        self.tokens_seen = 0
+        self.usage_ema = torch.zeros(cfg.recipe_count, dtype=f32)
+
+        # ---- which parameters receive a gradient in this mode (everything else is never touched)
+        names = [n for n, _ in parameter_shapes(cfg)]
+        if self.dense:
+            self.trainable = names
+        else:
+            self.trainable = [n for n in names if n.startswith(("embed.", "prelude.", "macro.", "coda.", "final_norm."))]
+            if not tr.disable_router_aux:
+                self.trainable += [n for n in names if n.startswith(("router.recipe_mlp.", "router.depth_mlp."))]
+        self.grads = {n: torch.zeros_like(self.params[n]) for n in self.trainable}
+        self.exp_avg = {n: torch.zeros_like(self.params[n]) for n in self.trainable}
+        self.exp_avg_sq = {n: torch.zeros_like(self.params[n]) for n in self.trainable}
+
+        # ---- bf16 shadows of the GEMM weights (refreshed by the AdamW kernel)
+        self.shadow: dict[str, torch.Tensor] = {}
+        for n in names:
+            if n == "embed.weight" or n.endswith((".attn.wqkv.weight", ".attn.wo.weight", ".mlp.wug.weight", ".mlp.wd.weight")):
+                self.shadow[n] = torch.empty_like(self.params[n], dtype=bf)
+        entries = [dict(p=self.params[n], g=self.grads[n], m=self.exp_avg[n], v=self.exp_avg_sq[n],
+                        shadow=self.shadow.get(n), lr_group=LR_GROUPS.index(lr_group_of(n, cfg.topology)))
+                   for n in self.trainable]
+        self.plan = AdamWPlan(entries, len(LR_GROUPS), dev)
+        self._write_lr_table()
+
+        # ---- activations
+        M, d, V, B, S = self.M, cfg.d_model, cfg.vocab_size, self.B, self.S
+        e = lambda *shape, dtype=f32: torch.empty(*shape, dtype=dtype, device=dev)  # noqa: E731
+        self.tokens = torch.zeros(B, S, dtype=torch.int64, device=dev)
+        self.targets = torch.zeros(B, S, dtype=torch.int64, device=dev)
+        self.x0 = e(M, d)
+        if self.dense:
+            self.blocks = [_Block(f"blocks.{i}", M, cfg, B, S, dev) for i in range(cfg.n_dense_layers)]
+            self.prelude, self.coda = self.blocks, []
+        else:
+            self.prelude = [_Block(f"prelude.{i}", M, cfg, B, S, dev) for i in range(cfg.n_prelude)]
+            self.coda = [_Block(f"coda.{i}", M, cfg, B, S, dev) for i in range(cfg.n_coda)]
+            self.blocks = self.prelude + self.coda
+        self.hidden16, self.rstd_f = e(M, d, dtype=bf), e(M)
+        self.logits = e(M, V, dtype=bf)
+        self.loss_tok, self.loss_per_sample = e(M), e(B)
+        self.scalars = torch.zeros(8, dtype=f32, device=dev)   # [0]=sum loss, [1]=aux load, [2]=aux depth, [3]=sumsq, [4]=clip
+        self.row_weight = torch.full((B,), 1.0 / (B * S), dtype=f32, device=dev)
+        # backward temporaries
+        self.dug = e(M, 2 * cfg.d_ff, dtype=bf)
+        self.dn16, self.dy16, self.dx16 = e(M, d, dtype=bf), e(M, d, dtype=bf), e(M, d, dtype=bf)
+        self.dqkv = e(M, 3 * d, dtype=bf)
+        self.dxa, self.dxb, self.dxc = e(M, d), e(M, d), e(M, d)
+        self.partial = e(2 * 148, d)
+        self.gn_partial = e(self.plan.total_chunks)
+        max_ws = 0
+        for (mm, nn) in ((3 * d, d), (d, d), (2 * cfg.d_ff, d), (d, cfg.d_ff), (V, d)):
+            max_ws = max(max_ws, ops.pick_splits(mm, nn, M) * mm * nn)
+        ops.split_workspace(max_ws)
+        if not self.dense:
+            r, k, m, hid = cfg.recipe_count, len(cfg.depth_choices), cfg.macro_rank, cfg.router_hidden_dim
+            self.h_phi = e(M, d)
+            self.phi_rstd, self.phi_pooled, self.phi_act = e(M), e(B * d + B * m), e(M, m)
+            self.phi_scratch = e(ops.phi_bwd_scratch_floats(B, S, d, m))
+            self.macro_scale = torch.ones(r, k, d, dtype=f32, device=dev)   # `update_scale` buffer (macro.py:99-108)
+            self.depth_values = torch.tensor(list(cfg.depth_choices), dtype=torch.int32, device=dev)
+            i32 = torch.int32
+            self.route = dict(pooled=e(B, d), r_hidden_pre=e(B, hid), d_hidden_pre=e(B, hid), recipe_logits=e(B, r),
+                              recipe_probs=e(B, r), depth_probs=e(B, k), expected_depth=e(B), router_entropy=e(B),
+                              recipe_id=e(B, dtype=i32), recipe_id_by_pass=e(B, cfg.t_max, dtype=i32),
+                              depth_id=e(B, dtype=i32), depth=e(B, dtype=i32))
+            self.router_scratch = e(A.ROUTER_MAX_R + B * (2 * hid + r + k))
+        for n, sh in self.shadow.items():
+            ops.cast_bf16(self.params[n], sh)
+        self._graph = None
+        self._launches_per_step: int | None = None
+
+    # ------------------------------------------------------------------ small helpers
+    def _write_lr_table(self, scale: float = 1.0) -> None:
+        lrs = [self.tr.lr_for(g) * scale for g in LR_GROUPS]
+        self.plan.lr_table.copy_(torch.tensor(lrs, dtype=torch.float32))
+
+    def _router_weight_dict(self) -> dict[str, torch.Tensor]:
+        p = self.params
+        return dict(r_w0=p["router.recipe_mlp.0.weight"], r_b0=p["router.recipe_mlp.0.bias"],
+                    r_w2=p["router.recipe_mlp.2.weight"], r_b2=p["router.recipe_mlp.2.bias"],
+                    d_w0=p["router.depth_mlp.0.weight"], d_b0=p["router.depth_mlp.0.bias"],
+                    d_w2=p["router.depth_mlp.2.weight"], d_b2=p["router.depth_mlp.2.bias"],
+                    pass_recipe_bias=p["router.pass_recipe_bias"])
+
+    def _phi_param_dict(self) -> dict[str, torch.Tensor]:
+        p = self.params
+        return dict(gain=p["macro.d_gain"], v=p["macro.v"], u=p["macro.u"], bias=p["macro.bias"], scale=self.macro_scale)
+
+    # ------------------------------------------------------------------ one transformer block
+    def _block_fwd(self, blk: _Block, x_in: torch.Tensor) -> torch.Tensor:
+        o, cfg, p, sh, M = self.ops, self.cfg, self.params, self.shadow, self.M
+        d, f, pre = cfg.d_model, cfg.d_ff, blk.prefix
+        blk.x_in = x_in
+        o.rmsnorm_fwd(x_in, p[f"{pre}.norm1.weight"], blk.n1, blk.rstd1)
+        o.gemm(blk.n1, sh[f"{pre}.attn.wqkv.weight"], blk.qkv, M=M, N=3 * d, K=d)
+        o.attn_fwd(blk.qkv, blk.y, blk.lse, B=self.B, S=self.S, n_heads=cfg.n_heads, head_dim=cfg.head_dim)
+        o.gemm(blk.y, sh[f"{pre}.attn.wo.weight"], blk.u, M=M, N=d, K=d, epilogue=A.EPI_F32, residual=x_in)
+        o.rmsnorm_fwd(blk.u, p[f"{pre}.norm2.weight"], blk.n2, blk.rstd2)
+        o.gemm(blk.n2, sh[f"{pre}.mlp.wug.weight"], blk.z, M=M, N=2 * f, K=d, epilogue=A.EPI_SWIGLU_FWD, out2=blk.ug, pair=f)
+        o.gemm(blk.z, sh[f"{pre}.mlp.wd.weight"], blk.out, M=M, N=d, K=f, epilogue=A.EPI_F32, residual=blk.u)
+        return blk.out
+
+    def _block_bwd(self, blk: _Block, dout: torch.Tensor, dout16: torch.Tensor, dx: torch.Tensor,
+                   dx16: torch.Tensor | None, du: torch.Tensor) -> None:
+        """dout/dout16: gradient wrt the block output (f32 and its bf16 copy); writes dx (f32) and dx16."""
+        o, cfg, p, sh, g, M = self.ops, self.cfg, self.params, self.shadow, self.grads, self.M
+        d, f, pre = cfg.d_model, cfg.d_ff, blk.prefix
+        # --- MLP: x_out = u + wd(up * silu(gate)),  (up | gate) = wug(norm2(u))
+        o.gemm(dout16, sh[f"{pre}.mlp.wd.weight"], self.dug, M=M, N=f, K=d, b_mn=True, epilogue=A.EPI_SWIGLU_BWD,
+               residual=blk.ug, pair=f)
+        o.gemm_wgrad(dout16, blk.z, g[f"{pre}.mlp.wd.weight"], M=d, N=f, K=M)
+        o.gemm(self.dug, sh[f"{pre}.mlp.wug.weight"], self.dn16, M=M, N=d, K=2 * f, b_mn=True)
+        o.gemm_wgrad(self.dug, blk.n2, g[f"{pre}.mlp.wug.weight"], M=2 * f, N=d, K=M)
+        o.rmsnorm_bwd(blk.u, p[f"{pre}.norm2.weight"], blk.rstd2, self.dn16, dout, du, self.dy16,
+                      g[f"{pre}.norm2.weight"], self.partial)
+        du16 = self.dy16
+        # --- attention: u = x + wo(attn(rope(q), rope(k), v)),  (q | k | v) = wqkv(norm1(x))
+        o.gemm(du16, sh[f"{pre}.attn.wo.weight"], self.dn16, M=M, N=d, K=d, b_mn=True)
+        o.gemm_wgrad(du16, blk.y, g[f"{pre}.attn.wo.weight"], M=d, N=d, K=M)
+        o.attn_bwd(blk.qkv, blk.y, self.dn16, blk.lse, self.dqkv, B=self.B, S=self.S, n_heads=cfg.n_heads,
+                   head_dim=cfg.head_dim)
+        o.gemm(self.dqkv, sh[f"{pre}.attn.wqkv.weight"], self.dn16, M=M, N=d, K=3 * d, b_mn=True)
+        o.gemm_wgrad(self.dqkv, blk.n1, g[f"{pre}.attn.wqkv.weight"], M=3 * d, N=d, K=M)
+        o.rmsnorm_bwd(blk.x_in, p[f"{pre}.norm1.weight"], blk.rstd1, self.dn16, du, dx, dx16,
+                      g[f"{pre}.norm1.weight"], self.partial)
+
+    # ------------------------------------------------------------------ forward + backward
+    def _forward_backward(self) -> None:
+        o, cfg, p, sh, g, tr = self.ops, self.cfg, self.params, self.shadow, self.grads, self.tr
+        M, d, V, B, S = self.M, cfg.d_model, cfg.vocab_size, self.B, self.S
+        tokens, targets = self.tokens.view(-1), self.targets.view(-1)
+        # ---------------- forward
+        o.embed_fwd(tokens, p["embed.weight"], self.x0)
+        x = self.x0
+        for blk in self.prelude:
+            x = self._block_fwd(blk, x)
+        if not self.dense:
+            h0 = x
+            fixed_depth_id = None if tr.fixed_depth is None else list(cfg.depth_choices).index(tr.fixed_depth)
+            o.router_fwd(h0, self._router_weight_dict(), self.depth_values, self.route, B=B, S=S, d=d,
+                         hid=cfg.router_hidden_dim, R=cfg.recipe_count, K=len(cfg.depth_choices), T=cfg.t_max,
+                         fixed_recipe=tr.fixed_recipe, fixed_depth_id=fixed_depth_id)
+            o.macro_phi_fwd(h0, self._phi_param_dict(), self.route["recipe_id"], self.route["depth_id"],
+                            cfg.macro_update_scale, self.h_phi, self.phi_rstd, self.phi_pooled, self.phi_act,
+                            B=B, S=S, d=d, m=cfg.macro_rank, K=len(cfg.depth_choices))
+            x = self.h_phi
+            for blk in self.coda:
+                x = self._block_fwd(blk, x)
+        x_last = x
+        o.rmsnorm_fwd(x_last, p["final_norm.weight"], self.hidden16, self.rstd_f)
+        o.gemm(self.hidden16, sh["embed.weight"], self.logits, M=M, N=V, K=d)
+        o.ce_fwd_bwd(self.logits, targets, self.row_weight, S, self.loss_tok, self.logits)   # logits -> dlogits in place
+        o.segment_sum(self.loss_tok, self.loss_per_sample, B, S)
+        o.segment_sum(self.loss_per_sample, self.scalars[0:1], 1, B)
+        # ---------------- backward
+        dlogits = self.logits
+        o.gemm(dlogits, sh["embed.weight"], self.dn16, M=M, N=d, K=V, b_mn=True)
+        o.gemm_wgrad(dlogits, self.hidden16, g["embed.weight"], M=V, N=d, K=M)
+        o.rmsnorm_bwd(x_last, p["final_norm.weight"], self.rstd_f, self.dn16, None, self.dxa, self.dx16,
+                      g["final_norm.weight"], self.partial)
+        dcur, dalt = self.dxa, self.dxb
+        tail = self.coda if not self.dense else self.blocks
+        for i, blk in enumerate(reversed(tail)):
+            self._block_bwd(blk, dcur, self.dx16, dalt, self.dx16, self.dxc)
+            dcur, dalt = dalt, dcur
+        if not self.dense:
+            # Phi backward writes dh0 into `dalt`; the router's auxiliary losses add their share
+            o.macro_phi_bwd(self.prelude[-1].out if self.prelude else self.x0, dcur, self._phi_param_dict(),
+                            self.route["recipe_id"], self.route["depth_id"], cfg.macro_update_scale, self.phi_rstd,
+                            self.phi_pooled, self.phi_act, dalt,
+                            dict(gain=g["macro.d_gain"], v=g["macro.v"], u=g["macro.u"], bias=g["macro.bias"]),
+                            self.phi_scratch, B=B, S=S, d=d, m=cfg.macro_rank, R=cfg.recipe_count,
+                            K=len(cfg.depth_choices))
+            dcur, dalt = dalt, dcur
+            if not tr.disable_router_aux:
+                rg = dict(r_w0=g["router.recipe_mlp.0.weight"], r_b0=g["router.recipe_mlp.0.bias"],
+                          r_w2=g["router.recipe_mlp.2.weight"], r_b2=g["router.recipe_mlp.2.bias"],
+                          d_w0=g["router.depth_mlp.0.weight"], d_b0=g["router.depth_mlp.0.bias"],
+                          d_w2=g["router.depth_mlp.2.weight"], d_b2=g["router.depth_mlp.2.bias"])
+                o.router_aux_bwd(self._router_weight_dict(), self.route, self.depth_values, tr.lambda_load,
+                                 tr.lambda_depth, self.scalars[1:3], rg, dcur, self.router_scratch, B=B, S=S, d=d,
+                                 hid=cfg.router_hidden_dim, R=cfg.recipe_count, K=len(cfg.depth_choices))
+            o.cast_bf16(dcur, self.dx16)
+            for blk in reversed(self.prelude):
+                self._block_bwd(blk, dcur, self.dx16, dalt, self.dx16, self.dxc)
+                dcur, dalt = dalt, dcur
+        o.embed_bwd(tokens, dcur, g["embed.weight"])
+
+    def _optimizer_step(self) -> None:
+        o, tr = self.ops, self.tr
+        clip = None
+        if tr.grad_clip_norm is not None:
+            o.grad_norm(self.plan, self.gn_partial, self.scalars[3:4], float(tr.grad_clip_norm), self.scalars[4:5])
+            clip = self.scalars[4:5]
+        o.adamw(self.plan, 0.9, 0.999, 1e-8, tr.weight_decay, clip)
+
+    # ------------------------------------------------------------------ public API
+    def _load_batch(self, batch) -> None:
+        tokens, targets = batch
+        if tuple(tokens.shape) != (self.B, self.S) or tuple(targets.shape) != (self.B, self.S):
+            raise ValueError(f"batch must be [{self.B}, {self.S}] int64 token ids")
+        self.tokens.copy_(tokens, non_blocking=True)
+        self.targets.copy_(targets, non_blocking=True)
+
+    def _run_step_kernels(self, optimizer: bool) -> None:
+        if not self.use_cuda_graph or not optimizer:
+            self._forward_backward()
+            if optimizer:
+                self._optimizer_step()
+            return
+        if self._graph is None:
+            before = self.ops.launches
+            torch.cuda.synchronize(self.device)
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph):
+                self._forward_backward()
+                self._optimizer_step()
+            self._graph = graph
+            self._launches_per_step = self.ops.launches - before
+        self._graph.replay()
+
+    def loss_and_grads(self, batch) -> tuple[float, dict[str, torch.Tensor]]:
+        """Forward + backward without the optimiser (what the parity tests compare with the oracle)."""
+        self._load_batch(batch)
+        self._run_step_kernels(optimizer=False)
+        return self._assemble_loss(), self.grads
+
+    def _assemble_loss(self) -> float:
+        vals = self.scalars.detach().to("cpu")
+        if hasattr(self.ops, "check_status"):
+            self.ops.check_status()
+        loss = float(vals[0]) / (self.B * self.S)
+        if not self.dense and not self.tr.disable_router_aux:
+            cover = float(torch.relu(self.tr.coverage_min - self.usage_ema).square().sum()) * self.tr.lambda_cover
+            loss += float(vals[1]) + float(vals[2]) + cover
+        return loss
+
+    def train_step(self, batch) -> TrainStepResult:
+        """One optimiser step on a [B,S] int64 (tokens, targets) batch held on the host or the device."""
+        self._load_batch(batch)
+        self._run_step_kernels(optimizer=True)
+        loss = self._assemble_loss()
+        metrics: dict[str, Any] = {"mode": self.tr.mode, "loss": loss}
+        if not self.dense:
+            ids = self.route["recipe_id"].to("cpu").long()
+            counts = torch.bincount(ids, minlength=self.cfg.recipe_count).float()
+            self.usage_ema.mul_(self.tr.coverage_beta).add_(counts / counts.sum().clamp_min(1.0), alpha=1.0 - self.tr.coverage_beta)
+            metrics["unique_recipes_per_batch"] = int(ids.unique().numel())
+        self.global_step += 1
+        self.tokens_seen += self.B * self.S
+        metrics["tokens_seen"] = self.tokens_seen
+        return TrainStepResult(loss=loss, metrics=metrics)
+
+    # ------------------------------------------------------------------ state
+    def state_dict(self) -> dict[str, torch.Tensor]:
+        return {n: t.detach().clone() for n, t in self.params.items()}
+
+    def backend_status(self) -> dict[str, object]:
+        """Counterpart of kernels/optimized.py:27-43 for the run manifest."""
+        return {"mode": getattr(self.ops, "name", "unknown"), "strict_cuda": True, "require_flash": False,
+                "cuda_available": torch.cuda.is_available(), "triton_available": False,
+                "uses_reference_fallback": False}
+
+    @property
+    def kernel_launches_per_step(self) -> int | None:
+        return self._launches_per_step

@@ -1,0 +1,283 @@
+"""Tensor-level operator table over the C ABI (``include/rte_b200.h``).
+
+Every method takes preallocated ``torch`` CUDA tensors (used only as device memory), launches the
+corresponding sm_100a kernel on the current CUDA stream and returns nothing (outputs are arguments).
+This is the counterpart of the reference's ``kernels/optimized.py`` dispatch table: same operator
+granularity, but a missing library or a CPU tensor is a hard error, never a fallback.
+"""
+from __future__ import annotations
+
+import ctypes as C
+
+import torch
+
+from . import _abi as A
+
+
+def _ptr(t):
+    return None if t is None else C.c_void_p(t.data_ptr())
+
+
+def _require_cuda(*tensors) -> None:
+    for t in tensors:
+        if t is not None and not t.is_cuda:
+            raise A.RteError("strict_cuda: the rte_b200 kernels need CUDA tensors; CPU tensors are rejected "
+                             "(no reference fallback)")
+
+
+class CudaOps:
+    """Launches the hand-written kernels.  One instance per device."""
+
+    name = "cuda_sm100a_ext"
+
+    def __init__(self, device: torch.device | str = "cuda:0"):
+        if not torch.cuda.is_available():
+            raise A.RteError("CUDA is required: rte_b200 has no CPU path")
+        self.device = torch.device(device)
+        self.lib = A.load()
+        with torch.cuda.device(self.device):
+            self.sm_count = int(self.lib.rte_device_sm_count())
+        if self.sm_count <= 0:
+            raise A.RteError("could not query the SM count")
+        self.status = torch.zeros(1, dtype=torch.int32, device=self.device)
+        self.launches = 0          # kernels-entry calls issued (for bench accounting)
+        self._split_ws: torch.Tensor | None = None
+
+    # ------------------------------------------------------------------ helpers
+    @property
+    def stream(self):
+        return C.c_void_p(torch.cuda.current_stream(self.device).cuda_stream)
+
+    def check_status(self) -> None:
+        """Synchronises and raises if a kernel reported a device-side problem."""
+        code = int(self.status.item())
+        if code != 0:
+            self.status.zero_()
+            raise A.RteError(f"device status {code}: {self.lib.rte_status_string(code).decode()}")
+
+    def _call(self, name: str, *args) -> None:
+        self.launches += 1
+        A.check(getattr(self.lib, name)(*args), name)
+
+    def split_workspace(self, numel: int) -> torch.Tensor:
+        if self._split_ws is None or self._split_ws.numel() < numel:
+            self._split_ws = torch.empty(numel, dtype=torch.float32, device=self.device)
+        return self._split_ws
+
+    # ------------------------------------------------------------------ GEMM
+    def gemm(self, a, b, out, *, M: int, N: int, K: int, a_mn: bool = False, b_mn: bool = False,
+             epilogue: int = A.EPI_BF16, residual=None, out2=None, pair: int = 0, splits: int = 1,
+             split_stride: int = 0, lda: int | None = None, ldb: int | None = None, ldc: int | None = None,
+             ldr: int | None = None, ldc2: int | None = None) -> None:
+        """out[M,N] = a[M,K] @ b[N,K]^T with the stated epilogue (see rte_gemm_bf16)."""
+        _require_cuda(a, b, out, residual, out2)
+        args = A.GemmArgs()
+        args.M, args.N, args.K = M, N, K
+        args.A, args.lda, args.a_mn_major = a.data_ptr(), (lda if lda is not None else a.stride(0)), int(a_mn)
+        args.B, args.ldb, args.b_mn_major = b.data_ptr(), (ldb if ldb is not None else b.stride(0)), int(b_mn)
+        args.epilogue = epilogue
+        args.C, args.ldc = out.data_ptr(), (ldc if ldc is not None else out.stride(-2))
+        args.R = residual.data_ptr() if residual is not None else None
+        args.ldr = (ldr if ldr is not None else residual.stride(-2)) if residual is not None else 0
+        args.C2 = out2.data_ptr() if out2 is not None else None
+        args.ldc2 = (ldc2 if ldc2 is not None else out2.stride(-2)) if out2 is not None else 0
+        args.b_pair_offset = pair
+        args.splits, args.split_stride = splits, split_stride
+        args.max_ctas = 0
+        args.status = self.status.data_ptr()
+        self._call("rte_gemm_bf16", C.byref(args), self.stream)
+
+    def pick_splits(self, M: int, N: int, K: int) -> int:
+        """Split count for a reduction-heavy GEMM whose output has few tiles (weight gradients)."""
+        bn = 256 if N >= 192 else 128
+        tiles = -(-M // 128) * -(-N // bn)
+        kblocks = -(-K // 64)
+        want = max(1, min(self.sm_count // max(tiles, 1), kblocks // 8 if kblocks >= 16 else 1, 16))
+        while want > 1:
+            per = -(-kblocks // want)
+            if -(-kblocks // per) == want:
+                break
+            want -= 1
+        return max(want, 1)
+
+    def gemm_wgrad(self, a_t, b_t, out, *, M: int, N: int, K: int, accumulate: bool = False,
+                   lda: int | None = None, ldb: int | None = None) -> None:
+        """out f32 [M,N] (+)= a_t^T @ b_t where a_t is stored [K,M] and b_t is stored [K,N]
+        (both MN-major for the tensor core), split along K across SMs and reduced in fixed order."""
+        splits = self.pick_splits(M, N, K)
+        if splits == 1 and not accumulate:
+            self.gemm(a_t, b_t, out, M=M, N=N, K=K, a_mn=True, b_mn=True, epilogue=A.EPI_F32, lda=lda, ldb=ldb, ldc=N)
+            return
+        ws = self.split_workspace(splits * M * N)
+        self.gemm(a_t, b_t, ws, M=M, N=N, K=K, a_mn=True, b_mn=True, epilogue=A.EPI_F32, splits=splits,
+                  split_stride=M * N, lda=lda, ldb=ldb, ldc=N)
+        self.reduce_splits(ws, splits, M * N, M * N, out, accumulate)
+
+    def reduce_splits(self, ws, splits: int, stride: int, n: int, out, accumulate: bool) -> None:
+        self._call("rte_reduce_splits", _ptr(ws), splits, stride, n, _ptr(out), int(accumulate), self.stream)
+
+    # ------------------------------------------------------------------ embedding / norm / CE
+    def embed_fwd(self, tokens, table, out) -> None:
+        _require_cuda(tokens, table, out)
+        self._call("rte_embed_fwd", _ptr(tokens), _ptr(table), _ptr(out), tokens.numel(), table.shape[1],
+                   table.shape[0], _ptr(self.status), self.stream)
+
+    def embed_bwd(self, tokens, dx, dtable) -> None:
+        self._call("rte_embed_bwd", _ptr(tokens), _ptr(dx), _ptr(dtable), tokens.numel(), dtable.shape[1],
+                   dtable.shape[0], _ptr(self.status), self.stream)
+
+    def rmsnorm_fwd(self, x, w, y_bf16, rstd, *, y_f32=None, film_gamma=None, film_beta=None, eps: float = 1e-5,
+                    rows: int | None = None) -> None:
+        _require_cuda(x, w)
+        d = x.shape[-1]
+        rows = rows if rows is not None else x.numel() // d
+        self._call("rte_rmsnorm_fwd", _ptr(x), _ptr(w), _ptr(film_gamma), _ptr(film_beta), _ptr(y_bf16), _ptr(y_f32),
+                   _ptr(rstd), rows, d, eps, self.stream)
+
+    def rmsnorm_bwd(self, x, w, rstd, dy, dres, dx_f32, dx_bf16, dw_out, partial, *, film_gamma=None,
+                    dgamma_out=None, dbeta_out=None, partial_g=None, partial_b=None, accumulate_dw: bool = False,
+                    rows: int | None = None) -> None:
+        """dx = rmsnorm_backward(dy) + dres; dw_out (+)= column sums (two-stage, deterministic)."""
+        d = x.shape[-1]
+        rows = rows if rows is not None else x.numel() // d
+        n_part = C.c_int32(0)
+        dy16 = dy if dy.dtype == torch.bfloat16 else None
+        dy32 = dy if dy.dtype == torch.float32 else None
+        max_partials = partial.shape[0] if partial is not None else 0
+        self._call("rte_rmsnorm_bwd", _ptr(x), _ptr(w), _ptr(film_gamma), _ptr(rstd), _ptr(dy16), _ptr(dy32),
+                   _ptr(dres), _ptr(dx_f32), _ptr(dx_bf16), _ptr(partial if dw_out is not None else None),
+                   _ptr(partial_g), _ptr(partial_b), rows, d, max_partials, C.byref(n_part), self.stream)
+        if dw_out is not None:
+            self._call("rte_colsum_partials", _ptr(partial), n_part.value, d, _ptr(dw_out), int(accumulate_dw), self.stream)
+        if dgamma_out is not None:
+            self._call("rte_colsum_partials", _ptr(partial_g), n_part.value, d, _ptr(dgamma_out), int(accumulate_dw), self.stream)
+            self._call("rte_colsum_partials", _ptr(partial_b), n_part.value, d, _ptr(dbeta_out), int(accumulate_dw), self.stream)
+
+    def ce_fwd_bwd(self, logits, targets, row_weight, S: int, loss_tok, dlogits) -> None:
+        rows, V = logits.shape
+        self._call("rte_ce_fwd_bwd", _ptr(logits), logits.stride(0), _ptr(targets), _ptr(row_weight), S,
+                   _ptr(loss_tok), _ptr(dlogits), rows, V, _ptr(self.status), self.stream)
+
+    def segment_sum(self, src, out, n_seg: int, seg_len: int) -> None:
+        self._call("rte_segment_sum", _ptr(src), _ptr(out), n_seg, seg_len, self.stream)
+
+    # ------------------------------------------------------------------ attention
+    def attn_fwd(self, qkv, y, lse, *, B: int, S: int, n_heads: int, head_dim: int, sec: int | None = None) -> None:
+        sec = sec if sec is not None else n_heads * head_dim
+        self._call("rte_attn_fwd", _ptr(qkv), qkv.stride(0), sec, _ptr(y), y.stride(0), _ptr(lse), B, S, n_heads,
+                   head_dim, self.stream)
+
+    def attn_bwd(self, qkv, y, dy, lse, dqkv, *, B: int, S: int, n_heads: int, head_dim: int,
+                 sec: int | None = None) -> None:
+        sec = sec if sec is not None else n_heads * head_dim
+        self._call("rte_attn_bwd", _ptr(qkv), qkv.stride(0), sec, _ptr(y), _ptr(dy), y.stride(0), _ptr(lse),
+                   _ptr(dqkv), B, S, n_heads, head_dim, self.stream)
+
+    # ------------------------------------------------------------------ router
+    @staticmethod
+    def _router_weights(w: dict) -> A.RouterWeights:
+        s = A.RouterWeights()
+        for name in ("r_w0", "r_b0", "r_w2", "r_b2", "d_w0", "d_b0", "d_w2", "d_b2", "pass_recipe_bias"):
+            setattr(s, name, w[name].data_ptr())
+        return s
+
+    @staticmethod
+    def _router_out(o: dict) -> A.RouterOut:
+        s = A.RouterOut()
+        for name, _ in A.RouterOut._fields_:
+            setattr(s, name, o[name].data_ptr())
+        return s
+
+    def router_fwd(self, h0, w: dict, depth_values, out: dict, *, B, S, d, hid, R, K, T, fixed_recipe, fixed_depth_id):
+        sw, so = self._router_weights(w), self._router_out(out)
+        self._call("rte_router_fwd", _ptr(h0), C.byref(sw), _ptr(depth_values), C.byref(so), B, S, d, hid, R, K, T,
+                   -1 if fixed_recipe is None else fixed_recipe, -1 if fixed_depth_id is None else fixed_depth_id,
+                   self.stream)
+
+    def router_aux_bwd(self, w: dict, fwd: dict, depth_values, lambda_load, lambda_depth, aux, grads: dict, dh0,
+                       scratch, *, B, S, d, hid, R, K):
+        sw, so = self._router_weights(w), self._router_out(fwd)
+        sg = A.RouterGrads()
+        for name, _ in A.RouterGrads._fields_:
+            setattr(sg, name, grads[name].data_ptr())
+        self._call("rte_router_aux_bwd", C.byref(sw), C.byref(so), _ptr(depth_values), lambda_load, lambda_depth,
+                   _ptr(aux), C.byref(sg), _ptr(dh0), _ptr(scratch), B, S, d, hid, R, K, self.stream)
+
+    def topk_lowest_index(self, scores, k: int, idx, vals=None) -> None:
+        rows, n = scores.shape
+        self._call("rte_topk_lowest_index", _ptr(scores), scores.stride(0), rows, n, k, _ptr(idx), _ptr(vals), self.stream)
+
+    # ------------------------------------------------------------------ macro operator
+    @staticmethod
+    def _phi_params(p: dict) -> A.PhiParams:
+        s = A.PhiParams()
+        for name, _ in A.PhiParams._fields_:
+            setattr(s, name, p[name].data_ptr())
+        return s
+
+    def macro_phi_fwd(self, h0, p: dict, recipe_id, stride_id, s_cfg, out, rstd, pooled, act, *, B, S, d, m, K):
+        sp = self._phi_params(p)
+        self._call("rte_macro_phi_fwd", _ptr(h0), C.byref(sp), _ptr(recipe_id), _ptr(stride_id), s_cfg, _ptr(out),
+                   _ptr(rstd), _ptr(pooled), _ptr(act), B, S, d, m, K, 1e-5, self.stream)
+
+    def macro_phi_bwd(self, h0, dout, p: dict, recipe_id, stride_id, s_cfg, rstd, pooled, act, dh0, grads: dict,
+                      scratch, *, B, S, d, m, R, K):
+        sp = self._phi_params(p)
+        sg = A.PhiGrads()
+        for name, _ in A.PhiGrads._fields_:
+            setattr(sg, name, grads[name].data_ptr())
+        self._call("rte_macro_phi_bwd", _ptr(h0), _ptr(dout), C.byref(sp), _ptr(recipe_id), _ptr(stride_id), s_cfg,
+                   _ptr(rstd), _ptr(pooled), _ptr(act), _ptr(dh0), C.byref(sg), _ptr(scratch), B, S, d, m, R, K,
+                   1e-5, self.stream)
+
+    @staticmethod
+    def phi_bwd_scratch_floats(B, S, d, m) -> int:
+        return B * S * d + B * S * m + 3 * B * d + B * m * d + B * 3 * d * m
+
+    # ------------------------------------------------------------------ small vector ops
+    def cast_bf16(self, src, dst) -> None:
+        self._call("rte_cast_f32_bf16", _ptr(src), _ptr(dst), src.numel(), self.stream)
+
+    def add_(self, dst, src) -> None:
+        self._call("rte_add_f32", _ptr(dst), _ptr(src), dst.numel(), self.stream)
+
+    def axpy_rows(self, dst, vec, alpha: float, rows: int, seg: int, d: int) -> None:
+        self._call("rte_axpy_rows_f32", _ptr(dst), _ptr(vec), alpha, rows, seg, d, self.stream)
+
+    # ------------------------------------------------------------------ optimiser
+    def adamw(self, plan: "AdamWPlan", beta1, beta2, eps, weight_decay, grad_scale=None) -> None:
+        self._call("rte_adamw_multi_tensor", _ptr(plan.table), plan.n_tensors, plan.total_chunks,
+                   _ptr(plan.chunk_tensor), _ptr(plan.chunk_index), _ptr(plan.lr_table), _ptr(plan.step_count),
+                   beta1, beta2, eps, weight_decay, _ptr(grad_scale), self.stream)
+
+    def grad_norm(self, plan: "AdamWPlan", partial, sumsq, max_norm: float, clip_coef) -> None:
+        self._call("rte_grad_norm_multi_tensor", _ptr(plan.table), plan.total_chunks, _ptr(plan.chunk_tensor),
+                   _ptr(plan.chunk_index), _ptr(partial), _ptr(sumsq), max_norm, _ptr(clip_coef), self.stream)
+
+
+class AdamWPlan:
+    """Device-resident description of the tensors one fused AdamW launch updates."""
+
+    def __init__(self, entries: list[dict], lr_groups: int, device):
+        """entries: dicts with p, g, m, v (f32 tensors), shadow (bf16 tensor or None), lr_group (int)."""
+        n = len(entries)
+        table = (A.AdamWTensor * n)()
+        chunk_tensor: list[int] = []
+        chunk_index: list[int] = []
+        for i, e in enumerate(entries):
+            t = table[i]
+            t.p, t.g, t.m, t.v = e["p"].data_ptr(), e["g"].data_ptr(), e["m"].data_ptr(), e["v"].data_ptr()
+            t.bf16_shadow = e["shadow"].data_ptr() if e.get("shadow") is not None else None
+            t.n, t.lr_group, t.step_slot = e["p"].numel(), e["lr_group"], i
+            chunks = -(-e["p"].numel() // A.ADAMW_CHUNK)
+            chunk_tensor += [i] * chunks
+            chunk_index += list(range(chunks))
+        raw = bytes(table)
+        self.table = torch.frombuffer(bytearray(raw), dtype=torch.uint8).to(device)
+        self.n_tensors = n
+        self.total_chunks = len(chunk_tensor)
+        self.chunk_tensor = torch.tensor(chunk_tensor, dtype=torch.int32, device=device)
+        self.chunk_index = torch.tensor(chunk_index, dtype=torch.int32, device=device)
+        self.lr_table = torch.zeros(max(lr_groups, 1), dtype=torch.float32, device=device)
+        self.step_count = torch.zeros(n, dtype=torch.int32, device=device)
+        self.entries = entries

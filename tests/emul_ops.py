@@ -1,0 +1,361 @@
+"""TEST-ONLY stand-in for ``speedup_thingy_b200.ops.CudaOps``.
+
+Implements each operator of the C ABI with plain PyTorch on the CPU, following the contract written in
+``include/rte_b200.h`` (same argument meaning, same output dtypes, same saved tensors).  It exists so
+that the host-side step sequencing in ``engine.py`` -- the hand-written backward pass, buffer reuse,
+optimiser plan -- can be checked against the oracle on a machine without a GPU.  It is never imported
+by the package; the product path constructs ``CudaOps`` and fails without CUDA.
+"""
+from __future__ import annotations
+
+import math
+
+import torch
+import torch.nn.functional as F
+
+EPI_BF16, EPI_F32, EPI_SWIGLU_FWD, EPI_SWIGLU_BWD = 0, 1, 2, 3
+
+
+def _rope_tables(S, hd):
+    inv = 1.0 / (10000.0 ** (torch.arange(0, hd, 2).float() / hd))
+    fr = torch.outer(torch.arange(S, dtype=torch.float32), inv)
+    return fr.cos(), fr.sin()          # [S, hd/2]
+
+
+def _rope(x, cos, sin):               # x [B,H,S,hd] f32, adjacent pairs
+    a, b = x[..., ::2], x[..., 1::2]
+    return torch.stack((a * cos - b * sin, b * cos + a * sin), dim=-1).flatten(-2)
+
+
+def _unrope(g, cos, sin):
+    a, b = g[..., ::2], g[..., 1::2]
+    return torch.stack((a * cos + b * sin, -a * sin + b * cos), dim=-1).flatten(-2)
+
+
+class EmulOps:
+    name = "cpu_emulation_for_tests"
+
+    def __init__(self, device="cpu", sm_count=148):
+        self.device = torch.device(device)
+        self.sm_count = sm_count
+        self.launches = 0
+        self._ws = None
+
+    def check_status(self):
+        pass
+
+    def split_workspace(self, numel):
+        if self._ws is None or self._ws.numel() < numel:
+            self._ws = torch.empty(numel, dtype=torch.float32)
+        return self._ws
+
+    def pick_splits(self, M, N, K):
+        bn = 256 if N >= 192 else 128
+        tiles = -(-M // 128) * -(-N // bn)
+        kblocks = -(-K // 64)
+        want = max(1, min(self.sm_count // max(tiles, 1), kblocks // 8 if kblocks >= 16 else 1, 16))
+        while want > 1:
+            per = -(-kblocks // want)
+            if -(-kblocks // per) == want:
+                break
+            want -= 1
+        return max(want, 1)
+
+    # ---------------------------------------------------------------- GEMM
+    def gemm(self, a, b, out, *, M, N, K, a_mn=False, b_mn=False, epilogue=EPI_BF16, residual=None, out2=None,
+             pair=0, splits=1, split_stride=0, lda=None, ldb=None, ldc=None, ldr=None, ldc2=None):
+        self.launches += 1
+        A_ = (a.reshape(K, -1)[:, :M].t() if a_mn else a.reshape(-1, a.shape[-1])[:M, :K]).float()
+        B_ = (b.reshape(K, -1)[:, :N].t() if b_mn else b.reshape(-1, b.shape[-1])[:N, :K]).float()
+        acc = A_ @ B_.t()
+        if epilogue == EPI_BF16:
+            out.view(M, -1)[:, :N] = acc.to(torch.bfloat16)
+        elif epilogue == EPI_F32:
+            if splits > 1:
+                ws = out[: splits * split_stride].view(splits, split_stride)
+                ws.zero_()
+                ws[0, : M * N] = acc.flatten()          # emulation: whole sum in partial 0
+            else:
+                res = acc if residual is None else acc + residual.view(M, N)
+                out.view(-1)[: M * N] = res.flatten()
+        elif epilogue == EPI_SWIGLU_FWD:
+            f = pair
+            up = acc[:, :f].to(torch.bfloat16).float()
+            gate = acc[:, f:].to(torch.bfloat16).float()
+            out2[:, :f] = up.to(torch.bfloat16)
+            out2[:, f:] = gate.to(torch.bfloat16)
+            out[:, :f] = (up * F.silu(gate)).to(torch.bfloat16)
+        else:
+            f = pair
+            up, gate = residual[:, :f].float(), residual[:, f:].float()
+            sg = torch.sigmoid(gate)
+            out[:, :f] = (acc * gate * sg).to(torch.bfloat16)
+            out[:, f:] = (acc * up * sg * (1 + gate * (1 - sg))).to(torch.bfloat16)
+
+    def gemm_wgrad(self, a_t, b_t, out, *, M, N, K, accumulate=False, lda=None, ldb=None):
+        self.launches += 1
+        res = a_t.reshape(K, -1)[:, :M].float().t() @ b_t.reshape(K, -1)[:, :N].float()
+        if accumulate:
+            out.view(M, N).add_(res)
+        else:
+            out.view(M, N).copy_(res)
+
+    def reduce_splits(self, ws, splits, stride, n, out, accumulate):
+        res = ws[: splits * stride].view(splits, stride)[:, :n].sum(0)
+        out.view(-1)[:n] = res + (out.view(-1)[:n] if accumulate else 0)
+
+    # ---------------------------------------------------------------- embedding / norm / CE
+    def embed_fwd(self, tokens, table, out):
+        self.launches += 1
+        out.copy_(table[tokens.view(-1)])
+
+    def embed_bwd(self, tokens, dx, dtable):
+        self.launches += 1
+        dtable.index_add_(0, tokens.view(-1), dx)
+
+    def rmsnorm_fwd(self, x, w, y_bf16, rstd, *, y_f32=None, film_gamma=None, film_beta=None, eps=1e-5, rows=None):
+        self.launches += 1
+        d = x.shape[-1]
+        xr = x.reshape(-1, d)
+        r = torch.rsqrt(xr.pow(2).mean(-1, keepdim=True) + eps)
+        y = xr * r
+        if w is not None:
+            y = y * w
+        if film_gamma is not None:
+            y = y * (1 + film_gamma) + film_beta
+        if rstd is not None:
+            rstd.view(-1)[: xr.shape[0]] = r.view(-1)
+        if y_bf16 is not None:
+            y_bf16.view(-1, d).copy_(y.to(torch.bfloat16))
+        if y_f32 is not None:
+            y_f32.view(-1, d).copy_(y)
+
+    def rmsnorm_bwd(self, x, w, rstd, dy, dres, dx_f32, dx_bf16, dw_out, partial, *, film_gamma=None,
+                    dgamma_out=None, dbeta_out=None, partial_g=None, partial_b=None, accumulate_dw=False, rows=None):
+        self.launches += 1
+        d = x.shape[-1]
+        xr = x.reshape(-1, d)
+        r = rstd.view(-1)[: xr.shape[0]].unsqueeze(-1)
+        xh = xr * r
+        dyf = dy.reshape(-1, d).float()
+        ww = w if w is not None else torch.ones(d)
+        f1 = 1 + film_gamma if film_gamma is not None else torch.ones(d)
+        g = dyf * f1 * ww
+        dx = r * (g - xh * (g * xh).mean(-1, keepdim=True))
+        if dres is not None:
+            dx = dx + dres.reshape(-1, d)
+        if dw_out is not None:
+            val = (dyf * f1 * xh).sum(0)
+            dw_out.copy_(val + (dw_out if accumulate_dw else 0))
+        if dgamma_out is not None:
+            dgamma_out.copy_((dyf * xh * ww).sum(0) + (dgamma_out if accumulate_dw else 0))
+            dbeta_out.copy_(dyf.sum(0) + (dbeta_out if accumulate_dw else 0))
+        if dx_f32 is not None:
+            dx_f32.view(-1, d).copy_(dx)
+        if dx_bf16 is not None:
+            dx_bf16.view(-1, d).copy_(dx.to(torch.bfloat16))
+
+    def ce_fwd_bwd(self, logits, targets, row_weight, S, loss_tok, dlogits):
+        self.launches += 1
+        lf = logits.float()
+        lse = torch.logsumexp(lf, dim=-1)
+        tgt = targets.view(-1)
+        loss_tok.copy_(lse - lf.gather(1, tgt[:, None]).squeeze(1))
+        if dlogits is not None:
+            pr = torch.exp(lf - lse[:, None])
+            pr[torch.arange(pr.shape[0]), tgt] -= 1.0
+            wgt = row_weight.repeat_interleave(S)[:, None]
+            dlogits.copy_((pr * wgt).to(torch.bfloat16))
+
+    def segment_sum(self, src, out, n_seg, seg_len):
+        self.launches += 1
+        out.view(-1)[:n_seg] = src.view(-1)[: n_seg * seg_len].view(n_seg, seg_len).sum(-1)
+
+    # ---------------------------------------------------------------- attention
+    def _split_heads(self, qkv, B, S, H, hd, sec):
+        rows = qkv.reshape(B * S, -1).float()
+        pick = lambda off: rows[:, off: off + H * hd].view(B, S, H, hd).transpose(1, 2)  # noqa: E731
+        return pick(0), pick(sec), pick(2 * sec)
+
+    def attn_fwd(self, qkv, y, lse, *, B, S, n_heads, head_dim, sec=None):
+        self.launches += 1
+        sec = sec if sec is not None else n_heads * head_dim
+        q, k, v = self._split_heads(qkv, B, S, n_heads, head_dim, sec)
+        cos, sin = _rope_tables(S, head_dim)
+        q = _rope(q, cos, sin).to(torch.bfloat16).float()
+        k = _rope(k, cos, sin).to(torch.bfloat16).float()
+        sc = (q @ k.transpose(-1, -2)) / math.sqrt(head_dim)
+        sc = sc.masked_fill(~torch.ones(S, S, dtype=torch.bool).tril(), float("-inf"))
+        l = torch.logsumexp(sc, dim=-1)
+        out = torch.exp(sc - l[..., None]) @ v
+        y.view(B * S, -1)[:, : n_heads * head_dim] = out.transpose(1, 2).reshape(B * S, -1).to(torch.bfloat16)
+        lse.view(-1)[: B * n_heads * S] = l.reshape(-1)
+
+    def attn_bwd(self, qkv, y, dy, lse, dqkv, *, B, S, n_heads, head_dim, sec=None):
+        self.launches += 1
+        sec = sec if sec is not None else n_heads * head_dim
+        H, hd = n_heads, head_dim
+        q, k, v = self._split_heads(qkv, B, S, H, hd, sec)
+        cos, sin = _rope_tables(S, hd)
+        q = _rope(q, cos, sin).to(torch.bfloat16).float()
+        k = _rope(k, cos, sin).to(torch.bfloat16).float()
+        do = dy.reshape(B * S, -1)[:, : H * hd].float().view(B, S, H, hd).transpose(1, 2)
+        o = y.reshape(B * S, -1)[:, : H * hd].float().view(B, S, H, hd).transpose(1, 2)
+        scale = 1.0 / math.sqrt(hd)
+        sc = (q @ k.transpose(-1, -2)) * scale
+        mask = torch.ones(S, S, dtype=torch.bool).tril()
+        p = torch.exp(sc - lse.view(-1)[: B * H * S].view(B, H, S, 1)).masked_fill(~mask, 0.0)
+        dp = do @ v.transpose(-1, -2)
+        D = (do * o).sum(-1, keepdim=True)
+        ds = p * (dp - D)
+        dq = _unrope((ds @ k) * scale, cos, sin)
+        dk = _unrope((ds.transpose(-1, -2) @ q) * scale, cos, sin)
+        dv = p.transpose(-1, -2) @ do
+        rows = dqkv.view(B * S, -1)
+        flat = lambda t: t.transpose(1, 2).reshape(B * S, H * hd).to(torch.bfloat16)  # noqa: E731
+        rows[:, 0: H * hd] = flat(dq)
+        rows[:, sec: sec + H * hd] = flat(dk)
+        rows[:, 2 * sec: 2 * sec + H * hd] = flat(dv)
+
+    # ---------------------------------------------------------------- router
+    def router_fwd(self, h0, w, depth_values, out, *, B, S, d, hid, R, K, T, fixed_recipe, fixed_depth_id):
+        self.launches += 1
+        pooled = h0.view(B, S, d).mean(1)
+        out["pooled"].copy_(pooled)
+        rpre = pooled @ w["r_w0"].t() + w["r_b0"]
+        dpre = pooled @ w["d_w0"].t() + w["d_b0"]
+        out["r_hidden_pre"].copy_(rpre)
+        out["d_hidden_pre"].copy_(dpre)
+        rl = F.silu(rpre) @ w["r_w2"].t() + w["r_b2"]
+        dl = F.silu(dpre) @ w["d_w2"].t() + w["d_b2"]
+        rp, dp = torch.softmax(rl, -1), torch.softmax(dl, -1)
+        out["recipe_logits"].copy_(rl)
+        out["recipe_probs"].copy_(rp)
+        out["depth_probs"].copy_(dp)
+        dv = depth_values.float()
+        out["expected_depth"].copy_((dp * dv).sum(-1))
+        ent = lambda p: -(p.clamp_min(1e-9).log() * p).sum(-1)  # noqa: E731
+        out["router_entropy"].copy_(ent(rp) + ent(dp))
+
+        def amax(x):
+            mx = x.max(-1, keepdim=True).values
+            idx = torch.arange(x.shape[-1]).expand_as(x)
+            return torch.where(x == mx, idx, torch.full_like(idx, x.shape[-1])).min(-1).values
+
+        if fixed_recipe is None:
+            out["recipe_id"].copy_(amax(rp))
+            out["recipe_id_by_pass"].copy_(amax(torch.softmax(rl[:, None, :] + w["pass_recipe_bias"][None], -1)))
+        else:
+            out["recipe_id"].fill_(fixed_recipe)
+            out["recipe_id_by_pass"].fill_(fixed_recipe)
+        if fixed_depth_id is None:
+            out["depth_id"].copy_(amax(dp))
+        else:
+            out["depth_id"].fill_(fixed_depth_id)
+        out["depth"].copy_(depth_values[out["depth_id"].long()])
+
+    def router_aux_bwd(self, w, fwd, depth_values, lambda_load, lambda_depth, aux, grads, dh0, scratch, *, B, S, d, hid, R, K):
+        self.launches += 1
+        rp, dp = fwd["recipe_probs"], fwd["depth_probs"]
+        mean = rp.mean(0)
+        aux[0] = lambda_load * (R * mean.square().sum() - 1.0)
+        aux[1] = lambda_depth * fwd["expected_depth"].mean()
+        dprob_r = (lambda_load * R * 2.0 * mean / B).expand(B, R)
+        dprob_d = (lambda_depth * depth_values.float() / B).expand(B, K)
+        dlr = rp * (dprob_r - (rp * dprob_r).sum(-1, keepdim=True))
+        dld = dp * (dprob_d - (dp * dprob_d).sum(-1, keepdim=True))
+
+        def back(dlog, pre, w2):
+            sg = torch.sigmoid(pre)
+            return (dlog @ w2) * sg * (1 + pre * (1 - sg))
+
+        dpr = back(dlr, fwd["r_hidden_pre"], w["r_w2"])
+        dpd = back(dld, fwd["d_hidden_pre"], w["d_w2"])
+        grads["r_w2"].copy_(dlr.t() @ F.silu(fwd["r_hidden_pre"]))
+        grads["r_b2"].copy_(dlr.sum(0))
+        grads["d_w2"].copy_(dld.t() @ F.silu(fwd["d_hidden_pre"]))
+        grads["d_b2"].copy_(dld.sum(0))
+        grads["r_w0"].copy_(dpr.t() @ fwd["pooled"])
+        grads["r_b0"].copy_(dpr.sum(0))
+        grads["d_w0"].copy_(dpd.t() @ fwd["pooled"])
+        grads["d_b0"].copy_(dpd.sum(0))
+        dpooled = dpr @ w["r_w0"] + dpd @ w["d_w0"]
+        dh0.view(B, S, d).add_(dpooled[:, None, :] / S)
+
+    def topk_lowest_index(self, scores, k, idx, vals=None):
+        order = torch.sort(-scores.double(), dim=-1, stable=True).indices[:, :k]
+        if idx is not None:
+            idx.copy_(order)
+        if vals is not None:
+            vals.copy_(torch.gather(scores, -1, order))
+
+    # ---------------------------------------------------------------- macro operator (via autograd here)
+    def _phi(self, h0, p, rid, sid, s_cfg, B, S, d, m):
+        h = h0.view(B, S, d)
+        r, s = rid.long(), sid.long()
+        gain, v, u, bias, scale = (p[k][r, s] for k in ("gain", "v", "u", "bias", "scale"))
+        rstd = torch.rsqrt(h.pow(2).mean(-1, keepdim=True) + 1e-5)
+        normed = h * rstd
+        pooled = normed.mean(1, keepdim=True)
+        z = torch.cat([normed, pooled.expand_as(normed), h], -1)
+        act = torch.bmm(z, v)
+        low = torch.bmm(F.silu(act), u)
+        out = h + s_cfg * scale[:, None] * torch.tanh(gain[:, None] * h + low + bias[:, None])
+        return out, rstd, pooled, act
+
+    def macro_phi_fwd(self, h0, p, recipe_id, stride_id, s_cfg, out, rstd, pooled, act, *, B, S, d, m, K):
+        self.launches += 1
+        o, r, pl, a = self._phi(h0, p, recipe_id, stride_id, s_cfg, B, S, d, m)
+        out.view(B, S, d).copy_(o)
+        rstd.view(-1)[: B * S] = r.reshape(-1)
+        pooled.view(-1)[: B * d] = pl.reshape(-1)
+        act.view(B, S, m).copy_(a)
+
+    def macro_phi_bwd(self, h0, dout, p, recipe_id, stride_id, s_cfg, rstd, pooled, act, dh0, grads, scratch, *, B, S, d, m, R, K):
+        self.launches += 1
+        leaves = {k: p[k].detach().clone().requires_grad_(k != "scale") for k in p}
+        hh = h0.detach().clone().requires_grad_(True)
+        o, *_ = self._phi(hh, leaves, recipe_id, stride_id, s_cfg, B, S, d, m)
+        o.backward(dout.view(B, S, d))
+        dh0.view(B, S, d).copy_(hh.grad.view(B, S, d))
+        for k in ("gain", "v", "u", "bias"):
+            grads[k].copy_(leaves[k].grad if leaves[k].grad is not None else torch.zeros_like(grads[k]))
+
+    @staticmethod
+    def phi_bwd_scratch_floats(B, S, d, m):
+        return 8
+
+    # ---------------------------------------------------------------- small vector ops
+    def cast_bf16(self, src, dst):
+        self.launches += 1
+        dst.copy_(src.to(torch.bfloat16))
+
+    def add_(self, dst, src):
+        dst.add_(src)
+
+    def axpy_rows(self, dst, vec, alpha, rows, seg, d):
+        dst.view(rows, d).add_(vec.view(-1, d).repeat_interleave(seg, 0)[:rows] * alpha)
+
+    # ---------------------------------------------------------------- optimiser
+    def adamw(self, plan, beta1, beta2, eps, weight_decay, grad_scale=None):
+        self.launches += 1
+        gs = float(grad_scale) if grad_scale is not None else 1.0
+        for i, e in enumerate(plan.entries):
+            lr = float(plan.lr_table[e["lr_group"]])
+            step = int(plan.step_count[i]) + 1
+            g = e["g"] * gs
+            e["p"].mul_(1 - lr * weight_decay)
+            e["m"].mul_(beta1).add_(g, alpha=1 - beta1)
+            e["v"].mul_(beta2).addcmul_(g, g, value=1 - beta2)
+            bc1, bc2 = 1 - beta1 ** step, 1 - beta2 ** step
+            e["p"].addcdiv_(e["m"], e["v"].sqrt() / math.sqrt(bc2) + eps, value=-lr / bc1)
+            if e.get("shadow") is not None:
+                e["shadow"].copy_(e["p"].to(torch.bfloat16))
+            plan.step_count[i] = step
+
+    def grad_norm(self, plan, partial, sumsq, max_norm, clip_coef):
+        self.launches += 1
+        s = sum(float(e["g"].double().pow(2).sum()) for e in plan.entries)
+        sumsq[0] = s
+        if clip_coef is not None:
+            clip_coef[0] = min(1.0, max_norm / (math.sqrt(s) + 1e-6)) if max_norm > 0 else 1.0

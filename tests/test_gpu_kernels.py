@@ -1,0 +1,373 @@
+"""Per-kernel parity on a B200: every C-ABI entry point against the CPU oracle (or, for the plain
+GEMM, an fp32 matmul of the same bf16 inputs).  Tolerances: bf16 kernels max-abs 2e-2 relative to the
+output scale (BASELINE north_star), fp32 kernels 1e-4, indices bit-exact."""
+import math
+
+import numpy as np
+import pytest
+import torch
+import torch.nn.functional as F
+
+from oracle import rte_oracle as O
+
+pytestmark = pytest.mark.gpu
+
+DEV = "cuda:0"
+
+
+@pytest.fixture(scope="module")
+def ops():
+    from speedup_thingy_b200.ops import CudaOps
+    return CudaOps(DEV)
+
+
+def _close(got, ref, tol, what=""):
+    got, ref = got.detach().float().cpu(), ref.detach().float().cpu()
+    scale = max(ref.abs().max().item(), 1e-6)
+    err = (got - ref).abs().max().item()
+    assert err <= tol * scale, f"{what}: max-abs {err:.3e} vs scale {scale:.3e} (tol {tol})"
+
+
+def _bf(t):
+    return t.to(torch.bfloat16)
+
+
+# ------------------------------------------------------------------ GEMM
+@pytest.mark.parametrize("M,N,K", [(128, 128, 64), (256, 256, 128), (300, 200, 136), (1024, 1536, 512),
+                                   (8192, 512, 2048), (64, 96, 512)])
+@pytest.mark.parametrize("a_mn,b_mn", [(False, False), (False, True), (True, True), (True, False)])
+def test_gemm_bf16_all_majors(ops, M, N, K, a_mn, b_mn):
+    g = torch.Generator().manual_seed(M + N + K)
+    a = _bf(torch.randn(M, K, generator=g))
+    b = _bf(torch.randn(N, K, generator=g))
+    ref = a.float() @ b.float().t()
+    if (a_mn and M % 8) or (b_mn and N % 8):
+        pytest.skip("MN-major operands need a row stride that is a multiple of 8 elements")
+    a_dev = (a.t().contiguous() if a_mn else a).to(DEV)
+    b_dev = (b.t().contiguous() if b_mn else b).to(DEV)
+    out = torch.zeros(M, N, dtype=torch.bfloat16, device=DEV)
+    ops.gemm(a_dev, b_dev, out, M=M, N=N, K=K, a_mn=a_mn, b_mn=b_mn)
+    torch.cuda.synchronize()
+    ops.check_status()
+    _close(out, ref, 1e-2, f"gemm {M}x{N}x{K} a_mn={a_mn} b_mn={b_mn}")
+
+
+def test_gemm_f32_residual_and_alias(ops):
+    M, N, K = 512, 384, 256
+    g = torch.Generator().manual_seed(1)
+    a, b, r = _bf(torch.randn(M, K, generator=g)), _bf(torch.randn(N, K, generator=g)), torch.randn(M, N, generator=g)
+    ref = a.float() @ b.float().t() + r
+    out = r.clone().to(DEV)
+    ops.gemm(a.to(DEV), b.to(DEV), out, M=M, N=N, K=K, epilogue=1, residual=out)
+    torch.cuda.synchronize()
+    _close(out, ref, 2e-3, "gemm f32 + residual (aliased)")
+
+
+@pytest.mark.parametrize("Mo,No,Kred", [(1536, 512, 8192), (512, 512, 8192), (4096, 512, 4096), (96, 64, 1024), (200, 72, 520)])
+def test_gemm_wgrad_split_k(ops, Mo, No, Kred):
+    g = torch.Generator().manual_seed(Mo + No)
+    a_t, b_t = _bf(torch.randn(Kred, Mo, generator=g)), _bf(torch.randn(Kred, No, generator=g))
+    ref = a_t.float().t() @ b_t.float()
+    out = torch.full((Mo, No), 7.0, dtype=torch.float32, device=DEV)
+    ops.gemm_wgrad(a_t.to(DEV), b_t.to(DEV), out, M=Mo, N=No, K=Kred)
+    torch.cuda.synchronize()
+    ops.check_status()
+    _close(out, ref, 2e-3, f"wgrad {Mo}x{No} over {Kred}")
+    ops.gemm_wgrad(a_t.to(DEV), b_t.to(DEV), out, M=Mo, N=No, K=Kred, accumulate=True)
+    torch.cuda.synchronize()
+    _close(out, 2 * ref, 2e-3, "wgrad accumulate")
+
+
+@pytest.mark.parametrize("M,d,f", [(256, 128, 256), (512, 512, 2048), (100, 64, 64), (8192, 512, 2048)])
+def test_swiglu_epilogues(ops, M, d, f):
+    g = torch.Generator().manual_seed(f)
+    x, wug, wd = _bf(torch.randn(M, d, generator=g)), _bf(torch.randn(2 * f, d, generator=g) * 0.05), _bf(torch.randn(d, f, generator=g) * 0.05)
+    z = torch.zeros(M, f, dtype=torch.bfloat16, device=DEV)
+    ug = torch.zeros(M, 2 * f, dtype=torch.bfloat16, device=DEV)
+    ops.gemm(x.to(DEV), wug.to(DEV), z, M=M, N=2 * f, K=d, epilogue=2, out2=ug, pair=f)
+    torch.cuda.synchronize()
+    ops.check_status()
+    acc = x.float() @ wug.float().t()
+    up, gate = acc[:, :f], acc[:, f:]
+    _close(ug[:, :f], up, 1e-2, "saved up")
+    _close(ug[:, f:], gate, 1e-2, "saved gate")
+    _close(z, up * F.silu(gate), 1.5e-2, "z = up*silu(gate)")
+    # backward epilogue: dz = dout @ wd  (wd stored [d, f]),  (dup | dgate) from the saved (up | gate)
+    dout = _bf(torch.randn(M, d, generator=g))
+    dug = torch.zeros(M, 2 * f, dtype=torch.bfloat16, device=DEV)
+    ops.gemm(dout.to(DEV), wd.to(DEV), dug, M=M, N=f, K=d, b_mn=True, epilogue=3, residual=ug, pair=f)
+    torch.cuda.synchronize()
+    ops.check_status()
+    ups, gts = ug[:, :f].float().cpu(), ug[:, f:].float().cpu()
+    dz = dout.float() @ wd.float()
+    sg = torch.sigmoid(gts)
+    _close(dug[:, :f], dz * gts * sg, 1.5e-2, "d up")
+    _close(dug[:, f:], dz * ups * sg * (1 + gts * (1 - sg)), 1.5e-2, "d gate")
+
+
+# ------------------------------------------------------------------ norm / CE / embedding
+@pytest.mark.parametrize("rows,d", [(64, 128), (1000, 512), (333, 1024), (17, 64)])
+def test_rmsnorm_fwd_bwd(ops, rows, d):
+    g = torch.Generator().manual_seed(d)
+    x, w = torch.randn(rows, d, generator=g), torch.randn(d, generator=g)
+    fg, fb = torch.randn(d, generator=g) * 0.1, torch.randn(d, generator=g) * 0.1
+    dy, dres = torch.randn(rows, d, generator=g), torch.randn(rows, d, generator=g)
+    for film in (False, True):
+        xr, wr = x.clone().requires_grad_(True), w.clone().requires_grad_(True)
+        fgr, fbr = fg.clone().requires_grad_(True), fb.clone().requires_grad_(True)
+        y = O.rmsnorm(xr, wr)
+        if film:
+            y = y * (1 + fgr) + fbr
+        y.backward(dy)
+        y32 = torch.zeros(rows, d, device=DEV)
+        y16 = torch.zeros(rows, d, dtype=torch.bfloat16, device=DEV)
+        rstd = torch.zeros(rows, device=DEV)
+        kw = dict(film_gamma=fg.to(DEV), film_beta=fb.to(DEV)) if film else {}
+        ops.rmsnorm_fwd(x.to(DEV), w.to(DEV), y16, rstd, y_f32=y32, **kw)
+        _close(y32, y, 1e-5, "rmsnorm f32")
+        _close(y16, y, 1e-2, "rmsnorm bf16")
+        dx = torch.zeros(rows, d, device=DEV)
+        dx16 = torch.zeros(rows, d, dtype=torch.bfloat16, device=DEV)
+        dw, dgm, dbt = (torch.zeros(d, device=DEV) for _ in range(3))
+        part, pg, pb = (torch.zeros(296, d, device=DEV) for _ in range(3))
+        kwb = dict(film_gamma=fg.to(DEV), dgamma_out=dgm, dbeta_out=dbt, partial_g=pg, partial_b=pb) if film else {}
+        ops.rmsnorm_bwd(x.to(DEV), w.to(DEV), rstd, dy.to(DEV), dres.to(DEV), dx, dx16, dw, part, **kwb)
+        torch.cuda.synchronize()
+        _close(dx, xr.grad + dres, 1e-4, "rmsnorm dx")
+        _close(dx16, xr.grad + dres, 1e-2, "rmsnorm dx bf16")
+        _close(dw, wr.grad, 1e-4, "rmsnorm dw")
+        if film:
+            _close(dgm, fgr.grad, 1e-4, "film dgamma")
+            _close(dbt, fbr.grad, 1e-4, "film dbeta")
+
+
+@pytest.mark.parametrize("B,S,V", [(4, 16, 96), (8, 64, 2048), (3, 5, 1000)])
+def test_cross_entropy_fwd_bwd(ops, B, S, V):
+    g = torch.Generator().manual_seed(V)
+    logits = _bf(torch.randn(B * S, V, generator=g) * 3)
+    tg = torch.randint(0, V, (B, S), generator=g)
+    wgt = torch.rand(B, generator=g)
+    lr = logits.float().requires_grad_(True)
+    per = O.lm_loss_per_sample(lr.view(B, S, V), tg)
+    (per * wgt).sum().backward()
+    ld = logits.to(DEV).clone()
+    loss_tok = torch.zeros(B * S, device=DEV)
+    ops.ce_fwd_bwd(ld, tg.to(DEV).view(-1), wgt.to(DEV), S, loss_tok, ld)
+    per_dev = torch.zeros(B, device=DEV)
+    ops.segment_sum(loss_tok, per_dev, B, S)
+    torch.cuda.synchronize()
+    ops.check_status()
+    _close(per_dev, per, 1e-4, "per-sample CE")
+    _close(ld, lr.grad, 1e-2, "dlogits")
+
+
+def test_embedding_fwd_bwd(ops):
+    g = torch.Generator().manual_seed(5)
+    V, d, n = 300, 64, 1000
+    table, tok, dx = torch.randn(V, d, generator=g), torch.randint(0, V, (n,), generator=g), torch.randn(n, d, generator=g)
+    out = torch.zeros(n, d, device=DEV)
+    ops.embed_fwd(tok.to(DEV), table.to(DEV), out)
+    assert torch.equal(out.cpu(), table[tok])
+    dt = torch.zeros(V, d, device=DEV)
+    ops.embed_bwd(tok.to(DEV), dx.to(DEV), dt)
+    torch.cuda.synchronize()
+    _close(dt, torch.zeros(V, d).index_add_(0, tok, dx), 1e-5, "embedding grad")
+
+
+# ------------------------------------------------------------------ attention (+RoPE)
+@pytest.mark.parametrize("B,S,H,hd", [(2, 16, 4, 8), (3, 64, 4, 32), (2, 64, 8, 64), (1, 200, 2, 64), (2, 33, 2, 128), (2, 256, 2, 64)])
+def test_attention_fwd_bwd(ops, B, S, H, hd):
+    g = torch.Generator().manual_seed(S * H)
+    d = H * hd
+    qkv = _bf(torch.randn(B * S, 3 * d, generator=g))
+    dy = _bf(torch.randn(B * S, d, generator=g))
+    lr = qkv.float().requires_grad_(True)
+    q, k, v = (t.transpose(1, 2) for t in lr.view(B, S, 3, H, hd).unbind(2))
+    cos, sin = O.rope_tables(S, hd)
+    yref = O.causal_attention(O.rope_apply(q, cos, sin), O.rope_apply(k, cos, sin), v).transpose(1, 2).reshape(B * S, d)
+    yref.backward(dy.float())
+    y = torch.zeros(B * S, d, dtype=torch.bfloat16, device=DEV)
+    lse = torch.zeros(B * H * S, device=DEV)
+    dq = torch.zeros(B * S, 3 * d, dtype=torch.bfloat16, device=DEV)
+    qd = qkv.to(DEV)
+    ops.attn_fwd(qd, y, lse, B=B, S=S, n_heads=H, head_dim=hd)
+    ops.attn_bwd(qd, y, dy.to(DEV), lse, dq, B=B, S=S, n_heads=H, head_dim=hd)
+    torch.cuda.synchronize()
+    _close(y, yref, 2e-2, "attention out")
+    _close(dq, lr.grad, 2e-2, "attention dqkv")
+
+
+# ------------------------------------------------------------------ router / top-k
+def test_router_fwd_indices_and_aux_bwd(ops):
+    cfg = O.ModelCfg(vocab_size=64, d_model=64, n_heads=4, d_ff=64, recipe_count=5, head_groups=4, ffn_groups=4,
+                     active_head_groups=2, active_ffn_groups=2, macro_rank=8)
+    B, S, d, hid, R, K, T = 12, 8, 64, 64, 5, 3, 4
+    params = O.init_params(cfg, seed=2)
+    g = torch.Generator().manual_seed(9)
+    for n in list(params):
+        if n.startswith("router."):
+            params[n] = torch.randn(params[n].shape, generator=g) * 0.3
+    h0 = torch.randn(B, S, d, generator=g)
+    leaves = {n: v.clone().requires_grad_(True) for n, v in params.items()}
+    h0r = h0.clone().requires_grad_(True)
+    route = O.router_forward(leaves, cfg, h0r, None, None)
+    tr = O.TrainCfg()
+    aux = O.router_aux_losses(tr, route["recipe_probs"], route["expected_depth"], torch.zeros(R))
+    (aux["load"] + aux["depth"]).backward()
+    f32, i32 = torch.float32, torch.int32
+    e = lambda *s, dtype=f32: torch.zeros(*s, dtype=dtype, device=DEV)  # noqa: E731
+    w = dict(r_w0=params["router.recipe_mlp.0.weight"], r_b0=params["router.recipe_mlp.0.bias"],
+             r_w2=params["router.recipe_mlp.2.weight"], r_b2=params["router.recipe_mlp.2.bias"],
+             d_w0=params["router.depth_mlp.0.weight"], d_b0=params["router.depth_mlp.0.bias"],
+             d_w2=params["router.depth_mlp.2.weight"], d_b2=params["router.depth_mlp.2.bias"],
+             pass_recipe_bias=params["router.pass_recipe_bias"])
+    w = {k: v.to(DEV).contiguous() for k, v in w.items()}
+    out = dict(pooled=e(B, d), r_hidden_pre=e(B, hid), d_hidden_pre=e(B, hid), recipe_logits=e(B, R), recipe_probs=e(B, R),
+               depth_probs=e(B, K), expected_depth=e(B), router_entropy=e(B), recipe_id=e(B, dtype=i32),
+               recipe_id_by_pass=e(B, T, dtype=i32), depth_id=e(B, dtype=i32), depth=e(B, dtype=i32))
+    dv = torch.tensor(cfg.depth_choices, dtype=i32, device=DEV)
+    ops.router_fwd(h0.to(DEV), w, dv, out, B=B, S=S, d=d, hid=hid, R=R, K=K, T=T, fixed_recipe=None, fixed_depth_id=None)
+    torch.cuda.synchronize()
+    _close(out["recipe_logits"], route["recipe_logits"], 1e-4, "recipe logits")
+    _close(out["recipe_probs"], route["recipe_probs"], 1e-4, "recipe probs")
+    _close(out["expected_depth"], route["expected_depth"], 1e-4, "expected depth")
+    _close(out["router_entropy"], route["router_entropy"], 1e-4, "entropy")
+    # indices: bit-exact given the kernel's own logits (lowest index on ties)
+    rl = out["recipe_logits"].cpu()
+    assert torch.equal(out["recipe_id"].cpu().long(), O.argmax_lowest(torch.softmax(rl, -1)))
+    by_pass = O.argmax_lowest(torch.softmax(rl[:, None, :] + params["router.pass_recipe_bias"][None], -1))
+    assert torch.equal(out["recipe_id_by_pass"].cpu().long(), by_pass)
+    assert torch.equal(out["depth_id"].cpu().long(), O.argmax_lowest(out["depth_probs"].cpu()))
+    assert torch.equal(out["depth"].cpu().long(), torch.tensor(cfg.depth_choices)[out["depth_id"].cpu().long()])
+    grads = {k: e(*w[k].shape) for k in ("r_w0", "r_b0", "r_w2", "r_b2", "d_w0", "d_b0", "d_w2", "d_b2")}
+    dh0 = e(B * S, d)
+    auxd = e(2)
+    scratch = e(32 + B * (2 * hid + R + K))
+    ops.router_aux_bwd(w, out, dv, tr.lambda_load, tr.lambda_depth, auxd, grads, dh0, scratch, B=B, S=S, d=d, hid=hid, R=R, K=K)
+    torch.cuda.synchronize()
+    assert abs(float(auxd[0]) - float(aux["load"])) < 1e-6 and abs(float(auxd[1]) - float(aux["depth"])) < 1e-7
+    _close(dh0.view(B, S, d), h0r.grad, 1e-3, "router dh0")
+    names = dict(r_w0="router.recipe_mlp.0.weight", r_b0="router.recipe_mlp.0.bias", r_w2="router.recipe_mlp.2.weight",
+                 r_b2="router.recipe_mlp.2.bias", d_w0="router.depth_mlp.0.weight", d_b0="router.depth_mlp.0.bias",
+                 d_w2="router.depth_mlp.2.weight", d_b2="router.depth_mlp.2.bias")
+    for k, n in names.items():
+        _close(grads[k], leaves[n].grad, 1e-3, n)
+
+
+def test_router_fixed_ids(ops):
+    B, S, d, hid, R, K, T = 4, 4, 32, 32, 4, 3, 4
+    f32, i32 = torch.float32, torch.int32
+    e = lambda *s, dtype=f32: torch.zeros(*s, dtype=dtype, device=DEV)  # noqa: E731
+    w = dict(r_w0=e(hid, d), r_b0=e(hid), r_w2=e(R, hid), r_b2=e(R), d_w0=e(hid, d), d_b0=e(hid), d_w2=e(K, hid), d_b2=e(K),
+             pass_recipe_bias=e(T, R))
+    out = dict(pooled=e(B, d), r_hidden_pre=e(B, hid), d_hidden_pre=e(B, hid), recipe_logits=e(B, R), recipe_probs=e(B, R),
+               depth_probs=e(B, K), expected_depth=e(B), router_entropy=e(B), recipe_id=e(B, dtype=i32),
+               recipe_id_by_pass=e(B, T, dtype=i32), depth_id=e(B, dtype=i32), depth=e(B, dtype=i32))
+    dv = torch.tensor([1, 2, 4], dtype=i32, device=DEV)
+    ops.router_fwd(e(B * S, d), w, dv, out, B=B, S=S, d=d, hid=hid, R=R, K=K, T=T, fixed_recipe=2, fixed_depth_id=1)
+    torch.cuda.synchronize()
+    assert out["recipe_id"].tolist() == [2] * B and out["depth"].tolist() == [2] * B
+    assert out["recipe_id_by_pass"].flatten().tolist() == [2] * (B * T)
+    # all-equal logits: the tie goes to index 0
+    ops.router_fwd(e(B * S, d), w, dv, out, B=B, S=S, d=d, hid=hid, R=R, K=K, T=T, fixed_recipe=None, fixed_depth_id=None)
+    torch.cuda.synchronize()
+    assert out["recipe_id"].tolist() == [0] * B and out["depth_id"].tolist() == [0] * B
+
+
+@pytest.mark.parametrize("rows,n,k", [(7, 16, 4), (100, 2048, 256), (33, 100, 100), (5, 6, 2)])
+def test_topk_lowest_index_bit_exact(ops, rows, n, k):
+    g = torch.Generator().manual_seed(n)
+    scores = torch.randn(rows, n, generator=g)
+    scores[0] = 1.0                                          # all-equal row
+    scores[1, ::3] = scores[1, 0]                            # many ties
+    scores = (scores * 4).round() / 4                        # quantise -> constructed ties everywhere
+    vals, idx = O.topk_lowest(scores, k)
+    gi = torch.zeros(rows, k, dtype=torch.int32, device=DEV)
+    gv = torch.zeros(rows, k, device=DEV)
+    ops.topk_lowest_index(scores.to(DEV), k, gi, gv)
+    torch.cuda.synchronize()
+    assert torch.equal(gi.cpu().long(), idx)
+    assert torch.equal(gv.cpu(), vals)
+
+
+# ------------------------------------------------------------------ macro operator
+@pytest.mark.parametrize("B,S,d,m,R", [(4, 16, 64, 8, 5), (6, 64, 128, 32, 5), (3, 40, 512, 32, 5), (2, 8, 64, 48, 3)])
+def test_macro_phi_fwd_bwd(ops, B, S, d, m, R):
+    K = 3
+    cfg = O.ModelCfg(d_model=d, macro_rank=m, recipe_count=R, macro_update_scale=0.05)
+    g = torch.Generator().manual_seed(d + m)
+    p = {"macro.d_gain": torch.randn(R, K, d, generator=g) * 0.1, "macro.v": torch.randn(R, K, 3 * d, m, generator=g) * 0.05,
+         "macro.u": torch.randn(R, K, m, d, generator=g) * 0.3, "macro.bias": torch.randn(R, K, d, generator=g) * 0.1}
+    h0 = torch.randn(B, S, d, generator=g)
+    rid, sid = torch.randint(0, R, (B,), generator=g), torch.randint(0, K, (B,), generator=g)
+    rid[0] = rid[-1]
+    sid[0] = sid[-1]                                          # at least one key shared by two samples
+    dout = torch.randn(B, S, d, generator=g)
+    leaves = {k: v.clone().requires_grad_(True) for k, v in p.items()}
+    hr = h0.clone().requires_grad_(True)
+    ref = O.macro_phi(leaves, cfg, hr, hr, rid, sid)
+    ref.backward(dout)
+    e = lambda *s: torch.zeros(*s, device=DEV)  # noqa: E731
+    pd = dict(gain=p["macro.d_gain"].to(DEV), v=p["macro.v"].to(DEV), u=p["macro.u"].to(DEV), bias=p["macro.bias"].to(DEV),
+              scale=torch.ones(R, K, d, device=DEV))
+    out, rstd, pooled, act = e(B * S, d), e(B * S), e(B * d + B * m), e(B * S, m)
+    ri, si = rid.to(DEV, torch.int32), sid.to(DEV, torch.int32)
+    ops.macro_phi_fwd(h0.to(DEV).view(B * S, d), pd, ri, si, 0.05, out, rstd, pooled, act, B=B, S=S, d=d, m=m, K=K)
+    torch.cuda.synchronize()
+    _close(out.view(B, S, d), ref, 1e-4, "phi out")
+    dh0 = e(B * S, d)
+    gr = dict(gain=e(R, K, d), v=e(R, K, 3 * d, m), u=e(R, K, m, d), bias=e(R, K, d))
+    for t in gr.values():
+        t.fill_(3.0)                                          # must be overwritten, including unused keys
+    scratch = e(ops.phi_bwd_scratch_floats(B, S, d, m))
+    ops.macro_phi_bwd(h0.to(DEV).view(B * S, d), dout.to(DEV).view(B * S, d), pd, ri, si, 0.05, rstd, pooled, act, dh0, gr,
+                      scratch, B=B, S=S, d=d, m=m, R=R, K=K)
+    torch.cuda.synchronize()
+    _close(dh0.view(B, S, d), hr.grad, 2e-4, "phi dh0")
+    _close(gr["gain"], leaves["macro.d_gain"].grad, 2e-4, "phi dgain")
+    _close(gr["bias"], leaves["macro.bias"].grad, 2e-4, "phi dbias")
+    _close(gr["u"], leaves["macro.u"].grad, 2e-4, "phi du")
+    _close(gr["v"], leaves["macro.v"].grad, 2e-4, "phi dv")
+
+
+# ------------------------------------------------------------------ optimiser
+def test_adamw_multi_tensor_matches_oracle_and_skips_absent(ops):
+    from speedup_thingy_b200.ops import AdamWPlan
+    g = torch.Generator().manual_seed(3)
+    shapes = [(5000,), (37,), (128, 64), (4097,)]
+    ps = [torch.randn(s, generator=g) for s in shapes]
+    ref = [p.clone() for p in ps]
+    ms, vs = [torch.zeros_like(p) for p in ps], [torch.zeros_like(p) for p in ps]
+    dev = [dict(p=p.to(DEV), g=torch.zeros_like(p, device=DEV), m=torch.zeros_like(p, device=DEV),
+                v=torch.zeros_like(p, device=DEV), shadow=torch.zeros(p.shape, dtype=torch.bfloat16, device=DEV) if i == 2 else None,
+                lr_group=i % 2) for i, p in enumerate(ps)]
+    plan = AdamWPlan(dev, 2, DEV)
+    lrs = [1e-2, 3e-3]
+    plan.lr_table.copy_(torch.tensor(lrs))
+    coef = torch.tensor([0.5], device=DEV)
+    for step in range(1, 4):
+        grads = [torch.randn(s, generator=g) for s in shapes]
+        for e_, gr in zip(dev, grads):
+            e_["g"].copy_(gr)
+        ops.adamw(plan, 0.9, 0.999, 1e-8, 0.1, coef)
+        for i, gr in enumerate(grads):
+            O.adamw_update(ref[i], gr * 0.5, ms[i], vs[i], step, lrs[i % 2], 0.1)
+    torch.cuda.synchronize()
+    for i in range(len(ps)):
+        _close(dev[i]["p"], ref[i], 1e-5, f"adamw tensor {i}")
+    _close(dev[2]["shadow"], ref[2], 1e-2, "bf16 shadow")
+    assert plan.step_count.tolist() == [3, 3, 3, 3]
+    # global gradient norm + clip coefficient
+    partial = torch.zeros(plan.total_chunks, device=DEV)
+    sumsq, clip = torch.zeros(1, device=DEV), torch.zeros(1, device=DEV)
+    ops.grad_norm(plan, partial, sumsq, 1.0, clip)
+    torch.cuda.synchronize()
+    tot = sum(float(e_["g"].double().pow(2).sum()) for e_ in dev)
+    assert abs(float(sumsq) - tot) <= 1e-4 * tot
+    assert abs(float(clip) - min(1.0, 1.0 / (math.sqrt(tot) + 1e-6))) < 1e-5
+
+
+def test_cpu_tensors_are_rejected(ops):
+    with pytest.raises(RuntimeError, match="strict_cuda"):
+        ops.gemm(torch.zeros(128, 64, dtype=torch.bfloat16), torch.zeros(128, 64, dtype=torch.bfloat16),
+                 torch.zeros(128, 128, dtype=torch.bfloat16), M=128, N=128, K=64)

@@ -1,0 +1,108 @@
+"""Whole-step parity on a B200: the CUDA engine against the CPU oracle and the reference-generated
+golden loss curve.  Tolerances from the north star: gradients max-abs 2e-2 of their scale (bf16),
+training loss within 1 % relative over the run."""
+from pathlib import Path
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import rte_oracle as O
+from speedup_thingy_b200.config import ExperimentConfig, ModelConfig, TrainingConfig
+from speedup_thingy_b200.engine import TrainEngine, init_parameters, parameter_shapes
+from tests.golden.make_golden import GOLDEN_CASES
+from tests.test_engine_host import CASES
+
+pytestmark = pytest.mark.gpu
+GOLDEN = Path(__file__).resolve().parent / "golden"
+
+
+def _engine(model, train, **kw):
+    cfg = ExperimentConfig(ModelConfig(**model), TrainingConfig(**train))
+    params = init_parameters(cfg.model, seed=cfg.training.seed)
+    return cfg, params, TrainEngine(cfg, params, device="cuda:0", **kw)
+
+
+def _stream(cfg, steps):
+    tr = cfg.training
+    toks = O.zipf_tokens(tr.batch_size * tr.seq_len * (steps + 2) + 1, cfg.model.vocab_size, seed=tr.seed)
+    return O.batches(toks, tr.batch_size, tr.seq_len)
+
+
+@pytest.mark.parametrize("name", list(CASES))
+def test_first_step_loss_and_grads_match_oracle(name):
+    model, train = CASES[name]
+    cfg, params, eng = _engine(model, train, use_cuda_graph=False)
+    otr = O.TrainCfg(**{**train, "grad_clip_norm": None})
+    oracle = O.OracleTrainer(O.ModelCfg(**model), otr, {k: v.clone() for k, v in params.items()})
+    batch = next(_stream(cfg, 2))
+    ref_loss, ref_grads, info = oracle.loss_and_grads(*batch)
+    loss, grads = eng.loss_and_grads(batch)
+    assert abs(loss - float(ref_loss)) <= 1e-2 * abs(float(ref_loss))
+    assert sorted(grads) == sorted(ref_grads)
+    for n, g in grads.items():
+        err = (g.cpu() - ref_grads[n]).abs().max().item()
+        scale = ref_grads[n].abs().max().item()
+        assert err <= 2e-2 * max(scale, 1e-3) + 2e-4, (n, err, scale)
+    if not eng.dense:
+        assert torch.equal(eng.route["recipe_id"].cpu().long(), info["hot"]["route"]["recipe_id"])
+        assert torch.equal(eng.route["depth"].cpu().long(), info["hot"]["route"]["depth"])
+
+
+def test_c1_loss_curve_matches_reference_golden():
+    case = GOLDEN_CASES["c1_macro"]
+    train = {**case["train"], "audit_fixed_count_per_batch": None}
+    cfg, params, eng = _engine(case["model"], train)
+    gold = np.load(GOLDEN / "c1_macro.npz")["losses"]
+    it = _stream(cfg, case["steps"])
+    losses = np.array([eng.train_step(next(it)).loss for _ in range(case["steps"])])
+    rel = np.abs(losses - gold) / np.abs(gold)
+    assert rel.max() <= 1e-2, (rel.max(), losses, gold)
+    assert eng.backend_status()["mode"] == "cuda_sm100a_ext" and not eng.backend_status()["uses_reference_fallback"]
+    assert eng.kernel_launches_per_step and eng.kernel_launches_per_step > 20
+
+
+def test_200_step_training_loss_within_one_percent():
+    case = GOLDEN_CASES["c1_macro"]
+    train = {**case["train"], "audit_fixed_count_per_batch": None}
+    cfg, params, eng = _engine(case["model"], train)
+    oracle = O.OracleTrainer(O.ModelCfg(**case["model"]), O.TrainCfg(**train), {k: v.clone() for k, v in params.items()})
+    it = _stream(cfg, 200)
+    rels = []
+    for step in range(200):
+        batch = next(it)
+        a, b = eng.train_step(batch).loss, oracle.train_step(*batch)
+        rels.append(abs(a - b) / abs(b))
+    assert max(rels) <= 1e-2, max(rels)
+    untouched = [n for n, _ in parameter_shapes(cfg.model) if n not in eng.trainable]
+    for n in untouched:                      # grad-less parameters are never decayed or stepped
+        assert torch.equal(eng.params[n].cpu(), params[n]), n
+
+
+def test_graph_replay_equals_eager():
+    model, train = CASES["macro_routed_clip"]
+    cfg, params, eager = _engine(model, train, use_cuda_graph=False)
+    _, _, graphed = _engine(model, train, use_cuda_graph=True)
+    it = _stream(cfg, 5)
+    for _ in range(4):
+        batch = next(it)
+        a, b = eager.train_step(batch).loss, graphed.train_step(batch).loss
+        assert abs(a - b) <= 1e-4 * abs(a)
+
+
+def test_c3_shapes_one_step_finite_and_close():
+    """BASELINE configs[2] shapes without the audited sample: one step against the fp32 oracle."""
+    model = dict(vocab_size=2048, d_model=512, n_heads=8, d_ff=2048, n_prelude=1, n_coda=1, t_max=4, depth_choices=(1, 2, 4),
+                 attn_banks=1, ffn_banks=1, head_groups=8, ffn_groups=16, active_head_groups=2, active_ffn_groups=4,
+                 recipe_count=5, macro_rank=32)
+    train = dict(mode="recursive_macro", lr=1e-3, weight_decay=0.1, batch_size=16, seq_len=64, seed=0, fixed_depth=4)
+    cfg, params, eng = _engine(model, train, use_cuda_graph=False)
+    oracle = O.OracleTrainer(O.ModelCfg(**model), O.TrainCfg(**train), {k: v.clone() for k, v in params.items()})
+    batch = next(_stream(cfg, 2))
+    ref_loss, ref_grads, _ = oracle.loss_and_grads(*batch)
+    loss, grads = eng.loss_and_grads(batch)
+    assert abs(loss - float(ref_loss)) <= 1e-2 * abs(float(ref_loss))
+    for n, g in grads.items():
+        err = (g.cpu() - ref_grads[n]).abs().max().item()
+        scale = ref_grads[n].abs().max().item()
+        assert err <= 2e-2 * max(scale, 1e-3) + 2e-4, (n, err, scale)
