@@ -415,3 +415,43 @@ class TrainEngine:
     @property
     def kernel_launches_per_step(self) -> int | None:
         return self._launches_per_step
+
+    def gemm_roofline(self, repeats: int = 5) -> dict[str, Any]:
+        """Times every launch of the tcgen05 GEMM inside real (eager) forward+backward passes with a CUDA
+        event pair per launch on the launching stream, and relates the algorithmic 2*M*N*K FLOPs to it."""
+        records: list[tuple] = []
+        orig = self.ops.gemm
+        stream = torch.cuda.current_stream(self.device)
+
+        def timed(a, b, out, **kw):
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record(stream)
+            orig(a, b, out, **kw)
+            e1.record(stream)
+            records.append((kw["M"], kw["N"], kw["K"], kw.get("epilogue", 0), kw.get("splits", 1), e0, e1))
+
+        self.ops.gemm = timed
+        try:
+            self._forward_backward()          # untimed pass (instruction cache, tensor maps)
+            records.clear()
+            for _ in range(repeats):
+                self._forward_backward()
+        finally:
+            self.ops.gemm = orig
+        torch.cuda.synchronize(self.device)
+        per_shape: dict[str, list[float]] = {}
+        flops = ms = 0.0
+        for M, N, K, epi, splits, e0, e1 in records:
+            t = e0.elapsed_time(e1)
+            f = 2.0 * M * N * K
+            flops += f
+            ms += t
+            key = f"{M}x{N}x{K}/epi{epi}" + (f"/split{splits}" if splits > 1 else "")
+            acc = per_shape.setdefault(key, [0.0, 0.0, 0])
+            acc[0] += f
+            acc[1] += t
+            acc[2] += 1
+        table = {k: {"launches": v[2] // repeats, "us": 1e3 * v[1] / v[2], "tflops": v[0] / (v[1] * 1e-3) / 1e12}
+                 for k, v in per_shape.items()}
+        return {"tflops": flops / (ms * 1e-3) / 1e12, "launches": len(records) // repeats,
+                "gemm_ms_per_step": ms / repeats, "per_shape": table}

@@ -1,0 +1,45 @@
+"""The golden cases: model/training settings whose reference outputs are stored beside this file.
+Kept free of any import of the reference so that the fixtures can be consumed where it is absent."""
+from oracle import rte_oracle as O
+
+GOLDEN_CASES = {
+    # BASELINE config 1 (the reference's CPU-runnable case), audit probability 0.
+    "c1_macro": dict(
+        model=dict(vocab_size=2048, d_model=128, n_heads=4, d_ff=512, n_dense_layers=4, n_prelude=1, n_coda=1,
+                   t_max=4, depth_choices=(1, 2, 4), attn_banks=1, ffn_banks=1, head_groups=4, ffn_groups=8,
+                   active_head_groups=2, active_ffn_groups=2, recipe_count=5, macro_rank=32),
+        train=dict(mode="recursive_macro", lr=1e-3, weight_decay=0.1, batch_size=8, seq_len=64, seed=0,
+                   fixed_depth=4, audit_fixed_count_per_batch=None),
+        steps=20,
+    ),
+    # small model with one audited sample per batch, gradient-corrected control variate + distillation terms
+    "small_audit": dict(
+        model=dict(vocab_size=96, d_model=32, n_heads=4, d_ff=64, n_dense_layers=3, n_prelude=1, n_coda=1,
+                   t_max=4, depth_choices=(1, 2, 4), attn_banks=2, ffn_banks=2, head_groups=4, ffn_groups=4,
+                   active_head_groups=2, active_ffn_groups=1, recipe_count=6, macro_rank=8),
+        train=dict(mode="recursive_macro", lr=2e-3, weight_decay=0.1, batch_size=4, seq_len=16, seed=3,
+                   fixed_depth=None, audit_fixed_count_per_batch=1, grad_clip_norm=1.0),
+        steps=6,
+    ),
+    # router decides depth and recipe (no fixed depth), no audit, aux losses on
+    "small_routed": dict(
+        model=dict(vocab_size=96, d_model=32, n_heads=4, d_ff=64, n_dense_layers=3, n_prelude=2, n_coda=1,
+                   t_max=4, depth_choices=(1, 2, 4), attn_banks=1, ffn_banks=1, head_groups=4, ffn_groups=4,
+                   active_head_groups=1, active_ffn_groups=2, recipe_count=4, macro_rank=8),
+        train=dict(mode="recursive_macro", lr=2e-3, weight_decay=0.05, batch_size=6, seq_len=12, seed=5,
+                   fixed_depth=None, audit_fixed_count_per_batch=None),
+        steps=6,
+    ),
+    "small_dense": dict(
+        model=dict(topology="dense", vocab_size=96, d_model=32, n_heads=4, d_ff=64, n_dense_layers=2, n_prelude=1,
+                   n_coda=1, t_max=4, depth_choices=(1, 2, 4), attn_banks=1, ffn_banks=1, head_groups=4,
+                   ffn_groups=4, active_head_groups=1, active_ffn_groups=1, recipe_count=4, macro_rank=8),
+        train=dict(mode="dense_exact", lr=2e-3, weight_decay=0.1, batch_size=4, seq_len=16, seed=7),
+        steps=6,
+    ),
+}
+
+
+
+def oracle_cfgs(case: dict) -> tuple[O.ModelCfg, O.TrainCfg]:
+    return O.ModelCfg(**case["model"]), O.TrainCfg(**case["train"])

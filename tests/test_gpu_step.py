@@ -10,7 +10,7 @@ import torch
 from oracle import rte_oracle as O
 from speedup_thingy_b200.config import ExperimentConfig, ModelConfig, TrainingConfig
 from speedup_thingy_b200.engine import TrainEngine, init_parameters, parameter_shapes
-from tests.golden.make_golden import GOLDEN_CASES
+from tests.golden.cases import GOLDEN_CASES
 from tests.test_engine_host import CASES
 
 pytestmark = pytest.mark.gpu

@@ -7,7 +7,7 @@ import pytest
 import torch
 
 from oracle import rte_oracle as O
-from tests.golden.make_golden import GOLDEN_CASES, oracle_cfgs
+from tests.golden.cases import GOLDEN_CASES, oracle_cfgs
 
 GOLDEN = Path(__file__).resolve().parent / "golden"
 
