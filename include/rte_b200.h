@@ -38,7 +38,8 @@ enum {
   RTE_ERR_TENSOR_MAP = -3,
   RTE_ERR_LAUNCH = -4,
   RTE_ERR_UNSUPPORTED = -5,
-  RTE_ERR_NO_DEVICE = -6
+  RTE_ERR_NO_DEVICE = -6,
+  RTE_ERR_SCRATCH_CAPACITY = -7
 };
 
 /* Name of the backend ("cuda_sm100a_ext") for the reference's
@@ -231,6 +232,24 @@ enum { RTE_ADAMW_CHUNK = 4096 };
 int rte_grad_norm_multi_tensor(const rte_adamw_tensor* table, int64_t total_chunks, const int32_t* chunk_tensor,
                                const int32_t* chunk_index, float* partial, float* sumsq, float max_norm,
                                float* clip_coef, rte_stream_t stream);
+
+/* Global gradient norm and clip coefficient WITHOUT any caller-provided or allocated scratch.
+ * (No counterpart in the reference: it exists for embedders of this library, see below.)
+ * Same outputs as rte_grad_norm_multi_tensor.  The per-chunk partial sums live in a 256 KB array built into
+ * the library, so this is the variant for callers that own no spare device memory and must not create any:
+ * a clipping hook bound from another language into the reference's `_finish_step`, say, holds only the
+ * parameter and gradient pointers the framework gave it, while the framework's caching allocator owns the
+ * rest of the device -- a raw cudaMalloc there can fail outright, and it stalls the whole device.
+ * Limits and rules:
+ *  - total_chunks <= 65536 (268M gradient elements); larger tables return RTE_ERR_SCRATCH_CAPACITY.
+ *  - the first call on each device resolves the array's device address on the host; make that first call
+ *    with the right device current and outside any stream capture.
+ *  - every GPU that loads the library holds the array until the process exits.
+ *  - calls on the same device share the array: do not let two of them overlap on the GPU (issue them on
+ *    one stream, or order the streams), otherwise they race.  Nothing needs clearing between calls.       */
+int rte_grad_norm_multi_tensor_static(const rte_adamw_tensor* table, int64_t total_chunks,
+                                      const int32_t* chunk_tensor, const int32_t* chunk_index, float* sumsq,
+                                      float max_norm, float* clip_coef, rte_stream_t stream);
 
 #ifdef __cplusplus
 }

@@ -376,6 +376,30 @@ __global__ void gradnorm_final_kernel(const float* __restrict__ partial, long lo
   }
 }
 
+// ------------------------------------------------------------------ built-in scratch for the no-allocation gradient norm
+// Lives in the library image: every GPU that loads the library carries these 256 KB until the process ends.
+// In HOST code the name `g_gradnorm_scratch` is only a stand-in for the symbol, not a device address, so the
+// launcher below asks the runtime for the real address (once per device) and hands that to the kernels.
+constexpr long long GRADNORM_STATIC_MAX_CHUNKS = 65536;   // 65536 chunks x 4096 elements = 268M gradient elements
+static __device__ __align__(256) float g_gradnorm_scratch[GRADNORM_STATIC_MAX_CHUNKS];
+
+constexpr int MAX_DEVICES = 64;
+float* g_gradnorm_scratch_addr[MAX_DEVICES] = {nullptr};
+
+// Returns the device address of the scratch array on the CURRENT device (looked up on first use).
+int gradnorm_scratch_for_current_device(float** out) {
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= MAX_DEVICES) return RTE_ERR_NO_DEVICE;
+  if (g_gradnorm_scratch_addr[dev] == nullptr) {
+    float* ptr = nullptr;
+    if (cudaGetSymbolAddress(reinterpret_cast<void**>(&ptr), g_gradnorm_scratch) != cudaSuccess || ptr == nullptr)
+      return RTE_ERR_LAUNCH;
+    g_gradnorm_scratch_addr[dev] = ptr;
+  }
+  *out = g_gradnorm_scratch_addr[dev];
+  return RTE_OK;
+}
+
 // ------------------------------------------------------------------ top-k, ties to the lowest index
 // One warp per row.  k rounds of a warp arg-max over (value desc, index asc); a selected entry is
 // masked by remembering the previous winner's (value, index) and only admitting strictly "later"
@@ -431,6 +455,7 @@ extern "C" const char* rte_status_string(int code) {
     case RTE_ERR_LAUNCH: return "kernel launch failed";
     case RTE_ERR_UNSUPPORTED: return "unsupported size";
     case RTE_ERR_NO_DEVICE: return "no CUDA device";
+    case RTE_ERR_SCRATCH_CAPACITY: return "size exceeds the capacity of the library's built-in scratch array";
     case RTE_DEV_WAIT_TIMEOUT_PRODUCER: return "device: TMA producer wait ran out";
     case RTE_DEV_WAIT_TIMEOUT_MMA: return "device: MMA issuer wait ran out";
     case RTE_DEV_WAIT_TIMEOUT_EPILOGUE: return "device: epilogue wait ran out";
@@ -598,6 +623,26 @@ extern "C" int rte_grad_norm_multi_tensor(const rte_adamw_tensor* table, int64_t
                                           const int32_t* chunk_index, float* partial, float* sumsq, float max_norm,
                                           float* clip_coef, rte_stream_t stream) {
   RTE_CHECK_ARG(table && chunk_tensor && chunk_index && partial && sumsq && total_chunks > 0);
+  gradnorm_partial_kernel<<<(unsigned)total_chunks, 256, 0, ST(stream)>>>(table, chunk_tensor, chunk_index, partial);
+  RTE_LAUNCH_CHECK();
+  gradnorm_final_kernel<<<1, 1024, 0, ST(stream)>>>(partial, total_chunks, sumsq, max_norm, clip_coef);
+  RTE_LAUNCH_CHECK();
+  return RTE_OK;
+}
+
+// Same result as rte_grad_norm_multi_tensor, but the per-chunk partial sums go to the library's own
+// built-in array instead of a caller-supplied buffer: nothing is allocated here or by the caller.
+// The first call on a device looks up the array's device address (a host-side runtime query, not a launch).
+// Each call first overwrites every slot it later reads, so nothing has to be cleared between calls; but all
+// calls on one device share the one array, so two calls whose kernels overlap in time would corrupt each other.
+extern "C" int rte_grad_norm_multi_tensor_static(const rte_adamw_tensor* table, int64_t total_chunks,
+                                                 const int32_t* chunk_tensor, const int32_t* chunk_index, float* sumsq,
+                                                 float max_norm, float* clip_coef, rte_stream_t stream) {
+  RTE_CHECK_ARG(table && chunk_tensor && chunk_index && sumsq && total_chunks > 0);
+  if (total_chunks > GRADNORM_STATIC_MAX_CHUNKS) return RTE_ERR_SCRATCH_CAPACITY;
+  float* partial = nullptr;
+  const int rc = gradnorm_scratch_for_current_device(&partial);
+  if (rc != RTE_OK) return rc;
   gradnorm_partial_kernel<<<(unsigned)total_chunks, 256, 0, ST(stream)>>>(table, chunk_tensor, chunk_index, partial);
   RTE_LAUNCH_CHECK();
   gradnorm_final_kernel<<<1, 1024, 0, ST(stream)>>>(partial, total_chunks, sumsq, max_norm, clip_coef);

@@ -254,6 +254,12 @@ class CudaOps:
         self._call("rte_grad_norm_multi_tensor", _ptr(plan.table), plan.total_chunks, _ptr(plan.chunk_tensor),
                    _ptr(plan.chunk_index), _ptr(partial), _ptr(sumsq), max_norm, _ptr(clip_coef), self.stream)
 
+    def grad_norm_static(self, plan: "AdamWPlan", sumsq, max_norm: float, clip_coef) -> None:
+        """Gradient norm through the entry point that uses the library's built-in scratch array (no buffer
+        from the caller, no allocation).  Calls on one device must not overlap; see include/rte_b200.h."""
+        self._call("rte_grad_norm_multi_tensor_static", _ptr(plan.table), plan.total_chunks, _ptr(plan.chunk_tensor),
+                   _ptr(plan.chunk_index), _ptr(sumsq), max_norm, _ptr(clip_coef), self.stream)
+
 
 class AdamWPlan:
     """Device-resident description of the tensors one fused AdamW launch updates."""
