@@ -199,12 +199,26 @@ rmsnorm_bwd_kernel(const float* __restrict__ x, const float* __restrict__ w, con
   }
 }
 
-__global__ void colsum_kernel(const float* __restrict__ part, int n_rows, int d, float* __restrict__ out, int accumulate) {
-  const int c = blockIdx.x * blockDim.x + threadIdx.x;
-  if (c >= d) return;
+// 32 columns x 8 row-groups per CTA: eight partial sums per column, combined through shared memory in a
+// fixed order (deterministic).
+__global__ void __launch_bounds__(256)
+colsum_kernel(const float* __restrict__ part, int n_rows, int d, float* __restrict__ out, int accumulate) {
+  __shared__ float sm[8][33];
+  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+  const int c = blockIdx.x * 32 + tx;
   float s = 0.f;
-  for (int r = 0; r < n_rows; ++r) s += part[(size_t)r * d + c];
-  out[c] = accumulate ? out[c] + s : s;
+  if (c < d) {
+#pragma unroll 4
+    for (int r = ty; r < n_rows; r += 8) s += part[(size_t)r * d + c];
+  }
+  sm[ty][tx] = s;
+  __syncthreads();
+  if (ty == 0 && c < d) {
+    float t = 0.f;
+#pragma unroll
+    for (int k = 0; k < 8; ++k) t += sm[k][tx];
+    out[c] = accumulate ? out[c] + t : t;
+  }
 }
 
 // ------------------------------------------------------------------ cross entropy
@@ -544,7 +558,7 @@ extern "C" int rte_rmsnorm_bwd(const float* x, const float* w, const float* film
 extern "C" int rte_colsum_partials(const float* partial, int32_t n_rows, int32_t d, float* out, int32_t accumulate,
                                    rte_stream_t stream) {
   RTE_CHECK_ARG(partial && out && n_rows > 0 && d > 0);
-  colsum_kernel<<<rte::ceil_div(d, 128), 128, 0, ST(stream)>>>(partial, n_rows, d, out, accumulate);
+  colsum_kernel<<<rte::ceil_div(d, 32), 256, 0, ST(stream)>>>(partial, n_rows, d, out, accumulate);
   RTE_LAUNCH_CHECK();
   return RTE_OK;
 }

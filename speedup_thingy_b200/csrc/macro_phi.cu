@@ -373,18 +373,27 @@ phi_dz_kernel(const float* __restrict__ h0, const float* __restrict__ rstd, cons
   }
 }
 
-// out[key][e] = sum over samples b with key(b) == key, in sample order, of partial[b][e]
+// out[key][e] = sum over samples b with key(b) == key, in sample order, of partial[b][e]   (blockIdx.y = key)
 __global__ void __launch_bounds__(NTHR)
 phi_reduce_keys_kernel(const float* __restrict__ partial, const int32_t* __restrict__ rid, const int32_t* __restrict__ sid,
-                       float* __restrict__ out, int B, int K, int n_keys, long long elems) {
+                       float* __restrict__ out, int B, int K, long long elems) {
+  __shared__ int members[1024];
+  __shared__ int n_members;
+  const int key = blockIdx.y;
+  if (threadIdx.x == 0) {
+    int n = 0;
+    for (int b = 0; b < B && n < 1024; ++b)
+      if (rid[b] * K + sid[b] == key) members[n++] = b;
+    n_members = n;
+  }
+  __syncthreads();
   const long long e = blockIdx.x * (long long)NTHR + threadIdx.x;
   if (e >= elems) return;
-  for (int key = 0; key < n_keys; ++key) {
-    float acc = 0.f;
-    for (int b = 0; b < B; ++b)
-      if (rid[b] * K + sid[b] == key) acc += partial[(size_t)b * elems + e];
-    out[(size_t)key * elems + e] = acc;
-  }
+  float acc = 0.f;
+  const int n = n_members;
+#pragma unroll 4
+  for (int i = 0; i < n; ++i) acc += partial[(size_t)members[i] * elems + e];
+  out[(size_t)key * elems + e] = acc;
 }
 
 }  // namespace
@@ -422,7 +431,7 @@ extern "C" int rte_macro_phi_bwd(const float* h0, const float* dout, const rte_p
   RTE_CHECK_ARG(h0 && dout && p && g && recipe_id && stride_id && rstd && pooled && act && dh0 && scratch && B > 0 &&
                 S > 0 && d > 0 && m > 0 && R > 0 && K_strides > 0);
   RTE_CHECK_ARG(g->gain && g->v && g->u && g->bias);
-  if (m > MMAX) return RTE_ERR_UNSUPPORTED;
+  if (m > MMAX || B > 1024) return RTE_ERR_UNSUPPORTED;
   PhiDims D{B, S, d, m, K_strides};
   const int tiles = rte::ceil_div(S, TT);
   const size_t M = (size_t)B * S;
@@ -460,13 +469,13 @@ extern "C" int rte_macro_phi_bwd(const float* h0, const float* dout, const rte_p
   RTE_LAUNCH_CHECK();
   const int n_keys = R * K_strides;
   const long long eu = (long long)m * d, ev = (long long)3 * d * m, ed = d;
-  phi_reduce_keys_kernel<<<(int)rte::ceil_div64(eu, NTHR), NTHR, 0, ST(stream)>>>(pu, recipe_id, stride_id, g->u, B, K_strides, n_keys, eu);
+  phi_reduce_keys_kernel<<<dim3((unsigned)rte::ceil_div64(eu, NTHR), n_keys), NTHR, 0, ST(stream)>>>(pu, recipe_id, stride_id, g->u, B, K_strides, eu);
   RTE_LAUNCH_CHECK();
-  phi_reduce_keys_kernel<<<(int)rte::ceil_div64(ev, NTHR), NTHR, 0, ST(stream)>>>(pv, recipe_id, stride_id, g->v, B, K_strides, n_keys, ev);
+  phi_reduce_keys_kernel<<<dim3((unsigned)rte::ceil_div64(ev, NTHR), n_keys), NTHR, 0, ST(stream)>>>(pv, recipe_id, stride_id, g->v, B, K_strides, ev);
   RTE_LAUNCH_CHECK();
-  phi_reduce_keys_kernel<<<(int)rte::ceil_div64(ed, NTHR), NTHR, 0, ST(stream)>>>(pg, recipe_id, stride_id, g->gain, B, K_strides, n_keys, ed);
+  phi_reduce_keys_kernel<<<dim3((unsigned)rte::ceil_div64(ed, NTHR), n_keys), NTHR, 0, ST(stream)>>>(pg, recipe_id, stride_id, g->gain, B, K_strides, ed);
   RTE_LAUNCH_CHECK();
-  phi_reduce_keys_kernel<<<(int)rte::ceil_div64(ed, NTHR), NTHR, 0, ST(stream)>>>(pb, recipe_id, stride_id, g->bias, B, K_strides, n_keys, ed);
+  phi_reduce_keys_kernel<<<dim3((unsigned)rte::ceil_div64(ed, NTHR), n_keys), NTHR, 0, ST(stream)>>>(pb, recipe_id, stride_id, g->bias, B, K_strides, ed);
   RTE_LAUNCH_CHECK();
   return RTE_OK;
 }

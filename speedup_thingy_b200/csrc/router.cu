@@ -20,19 +20,37 @@ pool_kernel(const float* __restrict__ h0, float* __restrict__ pooled, int S, int
 }
 
 // hidden_pre[j] = b0[j] + W0[j,:] . x ; logits[r] = b2[r] + W2[r,:] . silu(hidden_pre)
+// Each warp owns four rows at a time and reads them as float4, so sixteen independent 16-byte loads are in
+// flight per lane before the first reduction (the matrices come from L2; latency, not bandwidth, is the cost).
 __device__ void mlp_forward(const float* __restrict__ w0, const float* __restrict__ b0, const float* __restrict__ w2,
                             const float* __restrict__ b2, const float* xs, float* hs, float* pre_out, float* logits,
                             int d, int hid, int nout) {
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  for (int j = warp; j < hid; j += NTHR / 32) {
-    float acc = 0.f;
-    for (int c = lane; c < d; c += 32) acc += w0[(size_t)j * d + c] * xs[c];
-    acc = rte::warp_sum(acc);
-    if (lane == 0) { acc += b0[j]; pre_out[j] = acc; hs[j] = rte::silu_f(acc); }
+  const int d4 = d >> 2;
+  const float4* xs4 = reinterpret_cast<const float4*>(xs);
+  for (int j0 = warp * 4; j0 < hid; j0 += (NTHR / 32) * 4) {
+    float acc[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll 4
+    for (int c = lane; c < d4; c += 32) {
+      const float4 x = xs4[c];
+#pragma unroll
+      for (int r = 0; r < 4; ++r) {
+        if (j0 + r < hid) {
+          const float4 w = reinterpret_cast<const float4*>(w0 + (size_t)(j0 + r) * d)[c];
+          acc[r] += w.x * x.x + w.y * x.y + w.z * x.z + w.w * x.w;
+        }
+      }
+    }
+#pragma unroll
+    for (int r = 0; r < 4; ++r) {
+      const float v = rte::warp_sum(acc[r]);
+      if (lane == 0 && j0 + r < hid) { const float t = v + b0[j0 + r]; pre_out[j0 + r] = t; hs[j0 + r] = rte::silu_f(t); }
+    }
   }
   __syncthreads();
   for (int r = warp; r < nout; r += NTHR / 32) {
     float acc = 0.f;
+#pragma unroll 4
     for (int j = lane; j < hid; j += 32) acc += w2[(size_t)r * hid + j] * hs[j];
     acc = rte::warp_sum(acc);
     if (lane == 0) logits[r] = acc + b2[r];
@@ -170,11 +188,49 @@ router_bwd_sample_kernel(rte_router_weights w, rte_router_out o, const int32_t* 
   __syncthreads();
   mlp_backward_sample(w.r_w0, w.r_w2, dlr, o.r_hidden_pre + (size_t)b * hid, dpre_r + (size_t)b * hid, dhr, d, hid, R);
   mlp_backward_sample(w.d_w0, w.d_w2, dld, o.d_hidden_pre + (size_t)b * hid, dpre_d + (size_t)b * hid, dhd, d, hid, K);
-  for (int c = threadIdx.x; c < d; c += NTHR) {
-    float acc = 0.f;
-    for (int j = 0; j < hid; ++j) acc += w.r_w0[(size_t)j * d + c] * dhr[j] + w.d_w0[(size_t)j * d + c] * dhd[j];
-    acc /= (float)S;
-    for (int s = 0; s < S; ++s) dh0[((size_t)b * S + s) * d + c] += acc;
+}
+
+// dh0[b,s,:] += (dpre_r[b,:] @ W0r + dpre_d[b,:] @ W0d) / S.  CTA = 4 samples x 128 columns; the two halves of
+// the block split the hidden dimension and are combined through shared memory.
+__global__ void __launch_bounds__(NTHR)
+router_dpooled_kernel(const float* __restrict__ w0r, const float* __restrict__ w0d, const float* __restrict__ dpre_r,
+                      const float* __restrict__ dpre_d, float* __restrict__ dh0, int B, int S, int d, int hid) {
+  extern __shared__ float sm[];            // sr[4][hid], sd[4][hid], comb[4][128]
+  float* sr = sm;
+  float* sd = sm + 4 * hid;
+  float* comb = sm + 8 * hid;
+  const int cblocks = rte::ceil_div(d, 128);
+  const int b0 = (blockIdx.x / cblocks) * 4, c = (blockIdx.x % cblocks) * 128 + (threadIdx.x & 127);
+  const int half = threadIdx.x >> 7;
+  for (int i = threadIdx.x; i < 4 * hid; i += NTHR) {
+    const int bb = b0 + i / hid;
+    sr[i] = bb < B ? dpre_r[(size_t)bb * hid + i % hid] : 0.f;
+    sd[i] = bb < B ? dpre_d[(size_t)bb * hid + i % hid] : 0.f;
+  }
+  __syncthreads();
+  float acc[4] = {0.f, 0.f, 0.f, 0.f};
+  if (c < d) {
+    const int jh = (hid + 1) / 2, j_lo = half * jh, j_hi = min(hid, j_lo + jh);
+#pragma unroll 8
+    for (int j = j_lo; j < j_hi; ++j) {
+      const float wr = w0r[(size_t)j * d + c], wd = w0d[(size_t)j * d + c];
+#pragma unroll
+      for (int q = 0; q < 4; ++q) acc[q] += wr * sr[q * hid + j] + wd * sd[q * hid + j];
+    }
+  }
+  if (half == 1) {
+#pragma unroll
+    for (int q = 0; q < 4; ++q) comb[q * 128 + (threadIdx.x & 127)] = acc[q];
+  }
+  __syncthreads();
+  if (half == 0 && c < d) {
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+      const int bb = b0 + q;
+      if (bb >= B) break;
+      const float v = (acc[q] + comb[q * 128 + threadIdx.x]) / (float)S;
+      for (int t = 0; t < S; ++t) dh0[((size_t)bb * S + t) * d + c] += v;
+    }
   }
 }
 
@@ -186,6 +242,7 @@ router_dw0_kernel(const float* __restrict__ dpre, const float* __restrict__ pool
   if (i >= (long long)hid * d) return;
   const int j = int(i / d), c = int(i % d);
   float acc = 0.f, accb = 0.f;
+#pragma unroll 8
   for (int b = 0; b < B; ++b) {
     const float v = dpre[(size_t)b * hid + j];
     acc += v * pooled[(size_t)b * d + c];
@@ -202,6 +259,7 @@ router_dw2_kernel(const float* __restrict__ dlog, const float* __restrict__ pre,
   if (i >= nout * hid) return;
   const int r = i / hid, j = i % hid;
   float acc = 0.f, accb = 0.f;
+#pragma unroll 8
   for (int b = 0; b < B; ++b) {
     const float v = dlog[(size_t)b * nout + r];
     acc += v * rte::silu_f(pre[(size_t)b * hid + j]);
@@ -251,6 +309,11 @@ extern "C" int rte_router_aux_bwd(const rte_router_weights* w, const rte_router_
   if (smem > 48 * 1024) return RTE_ERR_UNSUPPORTED;
   router_bwd_sample_kernel<<<B, NTHR, smem, ST(stream)>>>(*w, *fwd, depth_values, mean_prob, lambda_load, lambda_depth,
                                                           dpre_r, dpre_d, dlog_r, dlog_d, dh0, B, S, d, hid, R, K);
+  RTE_LAUNCH_CHECK();
+  const size_t smem_dp = (size_t)(8 * hid + 4 * 128) * sizeof(float);
+  if (smem_dp > 48 * 1024) return RTE_ERR_UNSUPPORTED;
+  router_dpooled_kernel<<<rte::ceil_div(B, 4) * rte::ceil_div(d, 128), NTHR, smem_dp, ST(stream)>>>(
+      w->r_w0, w->d_w0, dpre_r, dpre_d, dh0, B, S, d, hid);
   RTE_LAUNCH_CHECK();
   const int g0 = (int)rte::ceil_div64((long long)hid * d, NTHR);
   router_dw0_kernel<<<g0, NTHR, 0, ST(stream)>>>(dpre_r, fwd->pooled, grads->r_w0, grads->r_b0, B, d, hid);

@@ -121,7 +121,8 @@ class _Block:
 
 class TrainEngine:
     def __init__(self, config: ExperimentConfig, params: dict[str, torch.Tensor] | None = None, *,
-                 device: str | torch.device = "cuda:0", ops=None, use_cuda_graph: bool = True):
+                 device: str | torch.device = "cuda:0", ops=None, use_cuda_graph: bool = True,
+                 process_group=None, bucket_cap_mb: float = 25.0):
         self.config = config
         self.cfg, self.tr = config.model, config.training
         self.device = torch.device(device)
@@ -130,6 +131,12 @@ class TrainEngine:
             ops = CudaOps(self.device)
         self.ops = ops
         self.use_cuda_graph = bool(use_cuda_graph) and self.device.type == "cuda"
+        # data parallelism: one process per GPU, the batch in `training.batch_size` is this rank's shard
+        self.pg = process_group
+        self.world = 1
+        if process_group is not None:
+            import torch.distributed as dist
+            self.world = dist.get_world_size(process_group)
         cfg, tr = self.cfg, self.tr
         self.B, self.S = tr.batch_size, tr.seq_len
         self.M = self.B * self.S
@@ -158,7 +165,32 @@ class TrainEngine:
             self.trainable = [n for n in names if n.startswith(("embed.", "prelude.", "macro.", "coda.", "final_norm."))]
             if not tr.disable_router_aux:
                 self.trainable += [n for n in names if n.startswith(("router.recipe_mlp.", "router.depth_mlp."))]
-        self.grads = {n: torch.zeros_like(self.params[n]) for n in self.trainable}
+        # gradients live in one flat buffer, laid out in the order the backward pass completes them, so that
+        # data-parallel buckets are contiguous slices that can be all-reduced while backward continues
+        order = self._grad_completion_order()
+        assert sorted(order) == sorted(self.trainable)
+        offsets, total = {}, 0
+        for n in order:
+            offsets[n] = total
+            total += -(-self.params[n].numel() // 64) * 64          # 256-byte aligned slots
+        self.grad_flat = torch.zeros(max(total, 64), dtype=f32, device=dev)
+        self.grads = {n: self.grad_flat[offsets[n]: offsets[n] + self.params[n].numel()].view(self.params[n].shape)
+                      for n in self.trainable}
+        self._buckets: list[tuple[int, int]] = []                   # [start, end) element ranges of grad_flat
+        self._bucket_of: dict[str, int] = {}
+        self._bucket_pending: list[int] = []
+        self._bucket_size: list[int] = []
+        cap = max(int(bucket_cap_mb * 1024 * 1024 / 4), 1)
+        start = 0
+        for n in order:
+            end = offsets[n] + -(-self.params[n].numel() // 64) * 64
+            if self._buckets and end - self._buckets[-1][0] <= cap:
+                self._buckets[-1] = (self._buckets[-1][0], end)
+            else:
+                self._buckets.append((offsets[n], end))
+            self._bucket_of[n] = len(self._buckets) - 1
+        self._bucket_size = [sum(1 for n in order if self._bucket_of[n] == i) for i in range(len(self._buckets))]
+        self._comm_stream = torch.cuda.Stream(device=dev) if (self.world > 1 and dev.type == "cuda") else None
         self.exp_avg = {n: torch.zeros_like(self.params[n]) for n in self.trainable}
         self.exp_avg_sq = {n: torch.zeros_like(self.params[n]) for n in self.trainable}
 
@@ -190,7 +222,7 @@ class TrainEngine:
         self.logits = e(M, V, dtype=bf)
         self.loss_tok, self.loss_per_sample = e(M), e(B)
         self.scalars = torch.zeros(8, dtype=f32, device=dev)   # [0]=sum loss, [1]=aux load, [2]=aux depth, [3]=sumsq, [4]=clip
-        self.row_weight = torch.full((B,), 1.0 / (B * S), dtype=f32, device=dev)
+        self.row_weight = torch.full((B,), 1.0 / (B * S * self.world), dtype=f32, device=dev)
         # backward temporaries
         self.dug = e(M, 2 * cfg.d_ff, dtype=bf)
         self.dn16, self.dy16, self.dx16 = e(M, d, dtype=bf), e(M, d, dtype=bf), e(M, d, dtype=bf)
@@ -219,6 +251,56 @@ class TrainEngine:
             ops.cast_bf16(self.params[n], sh)
         self._graph = None
         self._launches_per_step: int | None = None
+
+    # ------------------------------------------------------------------ data-parallel gradient exchange
+    def _grad_completion_order(self) -> list[str]:
+        """Trainable parameter names in the order `_forward_backward` finishes their gradients."""
+        cfg = self.cfg
+
+        def block(prefix: str) -> list[str]:
+            return [f"{prefix}.mlp.wd.weight", f"{prefix}.mlp.wug.weight", f"{prefix}.norm2.weight",
+                    f"{prefix}.attn.wo.weight", f"{prefix}.attn.wqkv.weight", f"{prefix}.norm1.weight"]
+
+        order = ["final_norm.weight"]
+        if self.dense:
+            for i in reversed(range(cfg.n_dense_layers)):
+                order += block(f"blocks.{i}")
+        else:
+            for i in reversed(range(cfg.n_coda)):
+                order += block(f"coda.{i}")
+            order += ["macro.d_gain", "macro.v", "macro.u", "macro.bias"]
+            if not self.tr.disable_router_aux:
+                for mlp in ("recipe_mlp", "depth_mlp"):
+                    order += [f"router.{mlp}.0.weight", f"router.{mlp}.0.bias", f"router.{mlp}.2.weight", f"router.{mlp}.2.bias"]
+            for i in reversed(range(cfg.n_prelude)):
+                order += block(f"prelude.{i}")
+        return order + ["embed.weight"]
+
+    def _begin_backward(self) -> None:
+        self._bucket_pending = list(self._bucket_size)
+
+    def _grad_ready(self, *names: str) -> None:
+        """Marks gradients as final; a bucket whose last gradient arrived is summed across ranks on the
+        communication stream (NCCL over NVLink) while the compute stream carries on with backward."""
+        if self.world == 1:
+            return
+        import torch.distributed as dist
+        for n in names:
+            i = self._bucket_of[n]
+            self._bucket_pending[i] -= 1
+            if self._bucket_pending[i] == 0:
+                lo, hi = self._buckets[i]
+                view = self.grad_flat[lo:hi]
+                if self._comm_stream is None:
+                    dist.all_reduce(view, op=dist.ReduceOp.SUM, group=self.pg)
+                else:
+                    self._comm_stream.wait_stream(torch.cuda.current_stream(self.device))
+                    with torch.cuda.stream(self._comm_stream):
+                        dist.all_reduce(view, op=dist.ReduceOp.SUM, group=self.pg)
+
+    def _finish_backward(self) -> None:
+        if self._comm_stream is not None:
+            torch.cuda.current_stream(self.device).wait_stream(self._comm_stream)
 
     # ------------------------------------------------------------------ small helpers
     def _write_lr_table(self, scale: float = 1.0) -> None:
@@ -260,20 +342,26 @@ class TrainEngine:
         o.gemm(dout16, sh[f"{pre}.mlp.wd.weight"], self.dug, M=M, N=f, K=d, b_mn=True, epilogue=A.EPI_SWIGLU_BWD,
                residual=blk.ug, pair=f)
         o.gemm_wgrad(dout16, blk.z, g[f"{pre}.mlp.wd.weight"], M=d, N=f, K=M)
+        self._grad_ready(f"{pre}.mlp.wd.weight")
         o.gemm(self.dug, sh[f"{pre}.mlp.wug.weight"], self.dn16, M=M, N=d, K=2 * f, b_mn=True)
         o.gemm_wgrad(self.dug, blk.n2, g[f"{pre}.mlp.wug.weight"], M=2 * f, N=d, K=M)
+        self._grad_ready(f"{pre}.mlp.wug.weight")
         o.rmsnorm_bwd(blk.u, p[f"{pre}.norm2.weight"], blk.rstd2, self.dn16, dout, du, self.dy16,
                       g[f"{pre}.norm2.weight"], self.partial)
+        self._grad_ready(f"{pre}.norm2.weight")
         du16 = self.dy16
         # --- attention: u = x + wo(attn(rope(q), rope(k), v)),  (q | k | v) = wqkv(norm1(x))
         o.gemm(du16, sh[f"{pre}.attn.wo.weight"], self.dn16, M=M, N=d, K=d, b_mn=True)
         o.gemm_wgrad(du16, blk.y, g[f"{pre}.attn.wo.weight"], M=d, N=d, K=M)
+        self._grad_ready(f"{pre}.attn.wo.weight")
         o.attn_bwd(blk.qkv, blk.y, self.dn16, blk.lse, self.dqkv, B=self.B, S=self.S, n_heads=cfg.n_heads,
                    head_dim=cfg.head_dim)
         o.gemm(self.dqkv, sh[f"{pre}.attn.wqkv.weight"], self.dn16, M=M, N=d, K=3 * d, b_mn=True)
         o.gemm_wgrad(self.dqkv, blk.n1, g[f"{pre}.attn.wqkv.weight"], M=3 * d, N=d, K=M)
+        self._grad_ready(f"{pre}.attn.wqkv.weight")
         o.rmsnorm_bwd(blk.x_in, p[f"{pre}.norm1.weight"], blk.rstd1, self.dn16, du, dx, dx16,
                       g[f"{pre}.norm1.weight"], self.partial)
+        self._grad_ready(f"{pre}.norm1.weight")
 
     # ------------------------------------------------------------------ forward + backward
     def _forward_backward(self) -> None:
@@ -304,11 +392,13 @@ class TrainEngine:
         o.segment_sum(self.loss_tok, self.loss_per_sample, B, S)
         o.segment_sum(self.loss_per_sample, self.scalars[0:1], 1, B)
         # ---------------- backward
+        self._begin_backward()
         dlogits = self.logits
         o.gemm(dlogits, sh["embed.weight"], self.dn16, M=M, N=d, K=V, b_mn=True)
         o.gemm_wgrad(dlogits, self.hidden16, g["embed.weight"], M=V, N=d, K=M)
         o.rmsnorm_bwd(x_last, p["final_norm.weight"], self.rstd_f, self.dn16, None, self.dxa, self.dx16,
                       g["final_norm.weight"], self.partial)
+        self._grad_ready("final_norm.weight")
         dcur, dalt = self.dxa, self.dxb
         tail = self.coda if not self.dense else self.blocks
         for i, blk in enumerate(reversed(tail)):
@@ -322,20 +412,27 @@ class TrainEngine:
                             dict(gain=g["macro.d_gain"], v=g["macro.v"], u=g["macro.u"], bias=g["macro.bias"]),
                             self.phi_scratch, B=B, S=S, d=d, m=cfg.macro_rank, R=cfg.recipe_count,
                             K=len(cfg.depth_choices))
+            self._grad_ready("macro.d_gain", "macro.v", "macro.u", "macro.bias")
             dcur, dalt = dalt, dcur
             if not tr.disable_router_aux:
                 rg = dict(r_w0=g["router.recipe_mlp.0.weight"], r_b0=g["router.recipe_mlp.0.bias"],
                           r_w2=g["router.recipe_mlp.2.weight"], r_b2=g["router.recipe_mlp.2.bias"],
                           d_w0=g["router.depth_mlp.0.weight"], d_b0=g["router.depth_mlp.0.bias"],
                           d_w2=g["router.depth_mlp.2.weight"], d_b2=g["router.depth_mlp.2.bias"])
-                o.router_aux_bwd(self._router_weight_dict(), self.route, self.depth_values, tr.lambda_load,
-                                 tr.lambda_depth, self.scalars[1:3], rg, dcur, self.router_scratch, B=B, S=S, d=d,
-                                 hid=cfg.router_hidden_dim, R=cfg.recipe_count, K=len(cfg.depth_choices))
+                # under data parallelism each rank evaluates the auxiliary losses on its own shard and
+                # contributes 1/world of their gradient (the cross-entropy part is exactly the global mean)
+                o.router_aux_bwd(self._router_weight_dict(), self.route, self.depth_values, tr.lambda_load / self.world,
+                                 tr.lambda_depth / self.world, self.scalars[1:3], rg, dcur, self.router_scratch, B=B,
+                                 S=S, d=d, hid=cfg.router_hidden_dim, R=cfg.recipe_count, K=len(cfg.depth_choices))
+                self._grad_ready(*[f"router.{m}.{i}.{k}" for m in ("recipe_mlp", "depth_mlp") for i in (0, 2)
+                                   for k in ("weight", "bias")])
             o.cast_bf16(dcur, self.dx16)
             for blk in reversed(self.prelude):
                 self._block_bwd(blk, dcur, self.dx16, dalt, self.dx16, self.dxc)
                 dcur, dalt = dalt, dcur
         o.embed_bwd(tokens, dcur, g["embed.weight"])
+        self._grad_ready("embed.weight")
+        self._finish_backward()
 
     def _optimizer_step(self) -> None:
         o, tr = self.ops, self.tr
@@ -380,10 +477,10 @@ class TrainEngine:
         vals = self.scalars.detach().to("cpu")
         if hasattr(self.ops, "check_status"):
             self.ops.check_status()
-        loss = float(vals[0]) / (self.B * self.S)
+        loss = float(vals[0]) / (self.B * self.S)          # this rank's shard
         if not self.dense and not self.tr.disable_router_aux:
             cover = float(torch.relu(self.tr.coverage_min - self.usage_ema).square().sum()) * self.tr.lambda_cover
-            loss += float(vals[1]) + float(vals[2]) + cover
+            loss += (float(vals[1]) + float(vals[2])) * self.world + cover
         return loss
 
     def train_step(self, batch) -> TrainStepResult:

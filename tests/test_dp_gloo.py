@@ -1,0 +1,67 @@
+"""Data-parallel path on CPU: two gloo ranks, each with half of the global batch, must end up with the
+gradients (and, after the optimiser, the weights) of one process that saw the whole batch -- the reference's
+grad-accumulation parity (tests/test_training_fixes.py:53-75) carried over to ranks."""
+import os
+import socket
+
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+from speedup_thingy_b200.config import ExperimentConfig, ModelConfig, TrainingConfig
+from speedup_thingy_b200.engine import TrainEngine, init_parameters
+from tests.emul_ops import EmulOps
+
+MODEL = dict(vocab_size=96, d_model=64, n_heads=4, d_ff=128, n_prelude=1, n_coda=1, t_max=4, depth_choices=(1, 2, 4),
+             attn_banks=1, ffn_banks=1, head_groups=4, ffn_groups=4, active_head_groups=2, active_ffn_groups=2,
+             recipe_count=5, macro_rank=8)
+TRAIN = dict(mode="recursive_macro", lr=2e-3, weight_decay=0.1, seq_len=16, seed=3, fixed_depth=4,
+             disable_router_aux=True, grad_clip_norm=1.0)
+GLOBAL_B = 8
+
+
+def _batch():
+    g = torch.Generator().manual_seed(42)
+    toks = torch.randint(0, MODEL["vocab_size"], (GLOBAL_B, TRAIN["seq_len"] + 1), generator=g)
+    return toks[:, :-1].contiguous(), toks[:, 1:].contiguous()
+
+
+def _worker(rank, world, port, out_path):
+    os.environ["MASTER_ADDR"], os.environ["MASTER_PORT"] = "127.0.0.1", str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    torch.set_num_threads(1)
+    cfg = ExperimentConfig(ModelConfig(**MODEL), TrainingConfig(**{**TRAIN, "batch_size": GLOBAL_B // world}))
+    params = init_parameters(cfg.model, seed=3)
+    eng = TrainEngine(cfg, params, device="cpu", ops=EmulOps(), use_cuda_graph=False, process_group=dist.group.WORLD,
+                      bucket_cap_mb=0.05)   # tiny buckets: several exchanges per step
+    assert len(eng._buckets) > 3
+    x, y = _batch()
+    lo, hi = rank * (GLOBAL_B // world), (rank + 1) * (GLOBAL_B // world)
+    _, grads = eng.loss_and_grads((x[lo:hi], y[lo:hi]))
+    grads = {k: v.clone() for k, v in grads.items()}
+    eng.train_step((x[lo:hi], y[lo:hi]))
+    if rank == 0:
+        torch.save({"grads": grads, "params": {k: v.clone() for k, v in eng.params.items()}}, out_path)
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_two_ranks_equal_one_process_on_the_global_batch(tmp_path):
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    out = tmp_path / "rank0.pt"
+    mp.spawn(_worker, args=(2, port, str(out)), nprocs=2, join=True)
+    got = torch.load(out)
+    cfg = ExperimentConfig(ModelConfig(**MODEL), TrainingConfig(**{**TRAIN, "batch_size": GLOBAL_B}))
+    single = TrainEngine(cfg, init_parameters(cfg.model, seed=3), device="cpu", ops=EmulOps(), use_cuda_graph=False)
+    _, ref = single.loss_and_grads(_batch())
+    ref = {k: v.clone() for k, v in ref.items()}
+    single.train_step(_batch())
+    assert sorted(ref) == sorted(got["grads"])
+    for n in ref:
+        scale = max(ref[n].abs().max().item(), 1e-6)
+        assert (ref[n] - got["grads"][n]).abs().max().item() <= 2e-2 * scale + 1e-6, n
+    for n, p in single.params.items():
+        assert (p - got["params"][n]).abs().max().item() <= 2.1 * TRAIN["lr"], n
