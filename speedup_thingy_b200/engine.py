@@ -131,12 +131,22 @@ class TrainEngine:
             ops = CudaOps(self.device)
         self.ops = ops
         self.use_cuda_graph = bool(use_cuda_graph) and self.device.type == "cuda"
+        self._eager_steps_left = 0
+        self._dp_paused = False      # True while one rank runs local passes (profiling) that others do not join
         # data parallelism: one process per GPU, the batch in `training.batch_size` is this rank's shard
         self.pg = process_group
         self.world = 1
         if process_group is not None:
             import torch.distributed as dist
             self.world = dist.get_world_size(process_group)
+        if self.world > 1:
+            # NCCL sets up its channels lazily on the first collectives (allocations, host synchronisation),
+            # which must not happen inside stream capture: run the first steps launch by launch, and capture
+            # the collective-bearing graph only when RTE_DP_GRAPH=1 asks for it.
+            import os
+            self._eager_steps_left = 3
+            if os.environ.get("RTE_DP_GRAPH", "0") != "1":
+                self.use_cuda_graph = False
         cfg, tr = self.cfg, self.tr
         self.B, self.S = tr.batch_size, tr.seq_len
         self.M = self.B * self.S
@@ -282,7 +292,7 @@ class TrainEngine:
     def _grad_ready(self, *names: str) -> None:
         """Marks gradients as final; a bucket whose last gradient arrived is summed across ranks on the
         communication stream (NCCL over NVLink) while the compute stream carries on with backward."""
-        if self.world == 1:
+        if self.world == 1 or self._dp_paused:
             return
         import torch.distributed as dist
         for n in names:
@@ -451,7 +461,9 @@ class TrainEngine:
         self.targets.copy_(targets, non_blocking=True)
 
     def _run_step_kernels(self, optimizer: bool) -> None:
-        if not self.use_cuda_graph or not optimizer:
+        if not self.use_cuda_graph or not optimizer or self._eager_steps_left > 0:
+            if optimizer and self._eager_steps_left > 0:
+                self._eager_steps_left -= 1
             self._forward_backward()
             if optimizer:
                 self._optimizer_step()
@@ -528,6 +540,7 @@ class TrainEngine:
             records.append((kw["M"], kw["N"], kw["K"], kw.get("epilogue", 0), kw.get("splits", 1), e0, e1))
 
         self.ops.gemm = timed
+        self._dp_paused = True                # rank-local passes: no collective may be issued here
         try:
             self._forward_backward()          # untimed pass (instruction cache, tensor maps)
             records.clear()
@@ -535,6 +548,7 @@ class TrainEngine:
                 self._forward_backward()
         finally:
             self.ops.gemm = orig
+            self._dp_paused = False
         torch.cuda.synchronize(self.device)
         per_shape: dict[str, list[float]] = {}
         flops = ms = 0.0
