@@ -26,8 +26,9 @@ sys.path.insert(0, str(ROOT))
 C3_MODEL = dict(vocab_size=2048, d_model=512, n_heads=8, d_ff=2048, n_prelude=1, n_coda=1, t_max=4,
                 depth_choices=(1, 2, 4), attn_banks=1, ffn_banks=1, head_groups=8, ffn_groups=16,
                 active_head_groups=2, active_ffn_groups=4, recipe_count=5, macro_rank=32)
-C3_TRAIN = dict(mode="recursive_macro", lr=1e-3, weight_decay=0.1, batch_size=128, seq_len=64, seed=0, fixed_depth=4)
-WORKLOAD = "BASELINE configs[2]: recursive_macro depth 4, d512 H8 F2048 (16x128 slabs, 4 active) V2048, batch 128x64"
+C3_TRAIN = dict(mode="recursive_macro", lr=1e-3, weight_decay=0.1, batch_size=128, seq_len=64, seed=0, fixed_depth=4,
+                audit_fixed_count_per_batch=1)     # exact-audit control variate at probability 1/128
+WORKLOAD = "BASELINE configs[2]: recursive_macro depth 4, d512 H8 F2048 (16x128 slabs, 4 active) V2048, batch 128x64, audit 1/128"
 
 
 def step_flops_per_token(m: dict) -> float:
@@ -233,7 +234,7 @@ def main() -> None:
             "metric": "train_tokens_per_sec", "value": value, "unit": "tokens/s", "n_gpus": world, "steps": K,
             "warmup": W, "ms_per_step": ms_dev / K, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
             "dtype": "bf16", "data": "synthetic",
-            "config": {"workload": WORKLOAD, "audit": "no audited sample in this build (audit_fixed_count_per_batch unset)",
+            "config": {"workload": WORKLOAD, "audit": "1 audited sample per rank-batch (p = 1/128), gradient-corrected, with distillation terms",
                        "global_batch": B * world, "seq_len": S, "parallelism": f"dp{world}",
                        "l2": "per-step working set (~1 GB of activations) exceeds the 126 MB L2; no explicit flush",
                        "timing": "CUDA events around K graph replays, max over ranks"},

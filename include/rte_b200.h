@@ -206,6 +206,7 @@ int rte_macro_phi_bwd(const float* h0, const float* dout, const rte_phi_params* 
 /* -------------------------------------------------- fp32 -> bf16 shadow copies of weights */
 int rte_cast_f32_bf16(const float* src, void* dst, int64_t n, rte_stream_t stream);
 int rte_add_f32(float* dst, const float* src, int64_t n, rte_stream_t stream);   /* dst += src */
+int rte_fill_f32(float* dst, float value, int64_t n, rte_stream_t stream);        /* dst[:] = value */
 int rte_axpy_rows_f32(float* dst, const float* vec, float alpha, int32_t rows, int32_t seg, int32_t d,
                       rte_stream_t stream);  /* dst[r,:] += alpha * vec[r / seg, :] */
 
@@ -232,6 +233,51 @@ enum { RTE_ADAMW_CHUNK = 4096 };
 int rte_grad_norm_multi_tensor(const rte_adamw_tensor* table, int64_t total_chunks, const int32_t* chunk_tensor,
                                const int32_t* chunk_index, float* partial, float* sumsq, float max_norm,
                                float* clip_coef, rte_stream_t stream);
+
+/* ------------------------------------------------ exact-audit replay helpers (audit.py:245-387; models.py:605-679;
+ * layers.py:831-870).  The audited subset has a fixed size n (fixed-count sampler), chosen on the host.
+ * Per-sample recipe choices stay on the device: every kernel below looks the recipe of (pass, sample) up in
+ * `rid` and applies the recipe's column mask (already multiplied by 1/len(banks) when the bank takes part, 0 when
+ * not) from a table [R, cols], so tensor shapes never depend on the routing decision.                           */
+/* dst[i, :] = src[idx[i], :], rows of row_bytes bytes (multiple of 16, 16-byte aligned). */
+int rte_gather_rows(const void* src, const int32_t* idx, void* dst, int32_t n, int64_t row_bytes, rte_stream_t stream);
+/* dst[idx[i], :] += src[i, :] (f32; idx entries distinct). */
+int rte_scatter_add_rows_f32(float* dst, const int32_t* idx, const float* src, int32_t n, int64_t row_elems,
+                             rte_stream_t stream);
+/* rid_out[t, i] = recipe_id_by_pass[idx[i], t];  active_out[t, i] = depth[idx[i]] > t. */
+int rte_audit_route(const int32_t* recipe_id_by_pass, const int32_t* depth, const int32_t* idx, int32_t* rid_out,
+                    int32_t* active_out, int32_t n, int32_t T, rte_stream_t stream);
+/* out[r, c] = x[r, c] * table[rid[r / S], c]   (bf16 in/out; used for y and, in backward, for dy) */
+int rte_colmask_mul_bf16(const void* x, const int32_t* rid, const float* table, int32_t S, void* out, int32_t rows,
+                         int32_t cols, rte_stream_t stream);
+/* z[r, j] = up*silu(gate)*table[rid[r/S], j] from ug = (up | gate) [rows, 2F];  backward writes dug [rows, 2F]. */
+int rte_swiglu_masked_fwd(const void* ug, const int32_t* rid, const float* table, int32_t S, void* z, int32_t rows,
+                          int32_t F, rte_stream_t stream);
+int rte_swiglu_masked_bwd(const void* ug, const void* dz, const int32_t* rid, const float* table, int32_t S, void* dug,
+                          int32_t rows, int32_t F, rte_stream_t stream);
+/* out = base + (*scale) * branch  where `active` (per sample, may be NULL) holds, else out = passthrough.
+ * base/branch/passthrough/out f32 [n*S*d] (out may alias base).  layers.py:831-852,862-870.                      */
+int rte_scaled_residual_fwd(const float* base, const float* branch, const float* scale, const int32_t* active,
+                            const float* passthrough, float* out, int32_t n, int64_t sample_elems, rte_stream_t stream);
+/* Backward of the above for gradient dout: dbase (=) dout where active else 0 (may alias dout);
+ * dbranch_bf16 = scale*dout where active else 0 (NULL to skip); dbranch_f32_accum += scale*dout (NULL to skip);
+ * dpassthrough += dout where inactive (NULL if no mask); dscale_partial[blockIdx] = sum dout*branch over active
+ * samples (one f32 per CTA; *n_partials CTAs, host value).                                                     */
+int rte_scaled_residual_bwd(const float* dout, const float* branch, const float* scale, const int32_t* active,
+                            float* dbase, void* dbranch_bf16, float* dbranch_f32_accum, float* dpassthrough,
+                            float* dscale_partial, int32_t max_partials, int32_t* n_partials, int32_t n,
+                            int64_t sample_elems, rte_stream_t stream);
+/* Distillation terms of the audited samples (macro.py:394-469, delta objective) and their gradient wrt the hot
+ * endpoint.  hot/exact/h0 f32 [n, S, d].  terms f32 [n, 4] = per-sample (1 - cos, log-rms diff^2, sum smooth_l1 of
+ * normed rows, sum smooth_l1 raw); dhot f32 [n,S,d] = gradient of
+ *   l_dir*mean(1-cos) + l_rms*mean(diff^2) + l_normed*mean_elem(sl1 normed) + l_raw*mean_elem(sl1 raw).          */
+int rte_macro_distill(const float* hot, const float* exact, const float* h0, float l_dir, float l_rms, float l_normed,
+                      float l_raw, float* terms, float* dhot, int32_t n, int32_t S, int32_t d, rte_stream_t stream);
+/* KL(exact || hot) at temperature temp per token row; adds coef*(p_hot - p_exact) into the rows
+ * idx[i]*S + s of dlogits_hot (bf16).  hot/exact logits bf16 [n*S, V]; kl_rows f32 [n*S].                        */
+int rte_kl_distill(const void* hot_logits, const void* exact_logits, float temp, float coef, const int32_t* idx,
+                   int32_t S, void* dlogits_hot, int32_t ld_dlogits, float* kl_rows, int32_t rows, int32_t V,
+                   rte_stream_t stream);
 
 /* Global gradient norm and clip coefficient WITHOUT any caller-provided or allocated scratch.
  * (No counterpart in the reference: it exists for embedders of this library, see below.)

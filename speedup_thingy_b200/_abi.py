@@ -89,10 +89,21 @@ PROTOTYPES = {
                                     c_vp] + [c_i32] * 6 + [c_f32, c_vp]),
     "rte_cast_f32_bf16": (C.c_int, [c_vp, c_vp, c_i64, c_vp]),
     "rte_add_f32": (C.c_int, [c_vp, c_vp, c_i64, c_vp]),
+    "rte_fill_f32": (C.c_int, [c_vp, c_f32, c_i64, c_vp]),
     "rte_axpy_rows_f32": (C.c_int, [c_vp, c_vp, c_f32, c_i32, c_i32, c_i32, c_vp]),
     "rte_adamw_multi_tensor": (C.c_int, [c_vp, c_i32, c_i64, c_vp, c_vp, c_vp, c_vp, c_f32, c_f32, c_f32, c_f32,
                                          c_vp, c_vp]),
     "rte_grad_norm_multi_tensor": (C.c_int, [c_vp, c_i64, c_vp, c_vp, c_vp, c_vp, c_f32, c_vp, c_vp]),
+    "rte_gather_rows": (C.c_int, [c_vp, c_vp, c_vp, c_i32, c_i64, c_vp]),
+    "rte_scatter_add_rows_f32": (C.c_int, [c_vp, c_vp, c_vp, c_i32, c_i64, c_vp]),
+    "rte_audit_route": (C.c_int, [c_vp, c_vp, c_vp, c_vp, c_vp, c_i32, c_i32, c_vp]),
+    "rte_colmask_mul_bf16": (C.c_int, [c_vp, c_vp, c_vp, c_i32, c_vp, c_i32, c_i32, c_vp]),
+    "rte_swiglu_masked_fwd": (C.c_int, [c_vp, c_vp, c_vp, c_i32, c_vp, c_i32, c_i32, c_vp]),
+    "rte_swiglu_masked_bwd": (C.c_int, [c_vp, c_vp, c_vp, c_vp, c_i32, c_vp, c_i32, c_i32, c_vp]),
+    "rte_scaled_residual_fwd": (C.c_int, [c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, c_i32, c_i64, c_vp]),
+    "rte_scaled_residual_bwd": (C.c_int, [c_vp] * 9 + [c_i32, P(c_i32), c_i32, c_i64, c_vp]),
+    "rte_macro_distill": (C.c_int, [c_vp, c_vp, c_vp, c_f32, c_f32, c_f32, c_f32, c_vp, c_vp, c_i32, c_i32, c_i32, c_vp]),
+    "rte_kl_distill": (C.c_int, [c_vp, c_vp, c_f32, c_f32, c_vp, c_i32, c_vp, c_i32, c_vp, c_i32, c_i32, c_vp]),
     "rte_grad_norm_multi_tensor_static": (C.c_int, [c_vp, c_i64, c_vp, c_vp, c_vp, c_f32, c_vp, c_vp]),
 }
 

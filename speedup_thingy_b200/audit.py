@@ -1,0 +1,263 @@
+"""Exact-audit replay of the `recursive_macro` step, kept on the device.
+
+Reference: ``AuditEngine.correction`` (audit.py:245-387) with the fixed-count sampler (audit.py:99-116),
+``RecursiveModel.forward_exact_subset`` -> ``forward_exact_from_h0`` (models.py:605-679, 416-512),
+``BankedRecursiveCore.forward_step`` / ``step_group`` (layers.py:831-870), ``macro_distill_loss``
+(macro.py:394-469, delta objective) and the control variate ``hot + (exact - hot) / p``.
+
+The audited samples (k per batch, chosen on the host with the same seeded CPU permutation the reference
+draws) are replayed through the banked core for ``t_max`` passes.  A recipe selects heads / FFN slabs /
+banks; here every pass computes all columns of every bank and multiplies by the recipe's column mask looked
+up on the device from the router's per-pass choice, so tensor shapes never depend on routing and the replay
+is part of the step's CUDA graph.  The replay's gradients flow into the core, the coda, the tied embedding
+and -- through the cached h0 -- the prelude, exactly as under ``audit_mode: gradient_corrected``.
+"""
+from __future__ import annotations
+
+import torch
+
+from . import _abi as A
+
+
+def build_recipes(cfg) -> list[dict]:
+    """Static recipe templates (recipes.py:65-100): recipe 0 = dense fallback over all banks and groups."""
+    out = [dict(attn_banks=tuple(range(cfg.attn_banks)), ffn_banks=tuple(range(cfg.ffn_banks)),
+                head_groups=tuple(range(cfg.head_groups)), ffn_groups=tuple(range(cfg.ffn_groups)))]
+    head_slots = max(1, cfg.head_groups // cfg.active_head_groups)
+    ffn_slots = max(1, cfg.ffn_groups // cfg.active_ffn_groups)
+    for idx in range(cfg.recipe_count - 1):
+        hs = (idx % head_slots) * cfg.active_head_groups
+        fs = (idx % ffn_slots) * cfg.active_ffn_groups
+        out.append(dict(attn_banks=((idx // head_slots) % cfg.attn_banks,), ffn_banks=((idx // ffn_slots) % cfg.ffn_banks,),
+                        head_groups=tuple((hs + j) % cfg.head_groups for j in range(cfg.active_head_groups)),
+                        ffn_groups=tuple((fs + j) % cfg.ffn_groups for j in range(cfg.active_ffn_groups))))
+    return out
+
+
+def recipe_mask_tables(cfg, device) -> tuple[torch.Tensor, torch.Tensor]:
+    """head_tab [attn_banks, R, d] and ffn_tab [ffn_banks, R, F]: 1/len(banks of the recipe) on the columns the
+    recipe activates in a bank it uses, 0 elsewhere (layers.py:673-700,728,744-763,779)."""
+    d, f, hd = cfg.d_model, cfg.d_ff, cfg.d_model // cfg.n_heads
+    hpg, slab = cfg.n_heads // cfg.head_groups, cfg.d_ff // cfg.ffn_groups
+    recipes = build_recipes(cfg)
+    head = torch.zeros(cfg.attn_banks, len(recipes), d)
+    ffn = torch.zeros(cfg.ffn_banks, len(recipes), f)
+    for r, rec in enumerate(recipes):
+        for bank in rec["attn_banks"]:
+            for grp in rec["head_groups"]:
+                head[bank, r, grp * hpg * hd:(grp + 1) * hpg * hd] = 1.0 / len(rec["attn_banks"])
+        for bank in rec["ffn_banks"]:
+            for grp in rec["ffn_groups"]:
+                ffn[bank, r, grp * slab:(grp + 1) * slab] = 1.0 / len(rec["ffn_banks"])
+    return head.to(device), ffn.to(device)
+
+
+CORE_PARAMS = ["core.pass_gamma1", "core.pass_beta1", "core.pass_gamma2", "core.pass_beta2", "core.pass_attn_scale",
+               "core.pass_mlp_scale", "core.alpha_inj", "core.norm1.weight", "core.attn.wqkv", "core.attn.wo",
+               "core.norm2.weight", "core.mlp.wug", "core.mlp.wd"]
+CORE_SHADOWED = ["core.attn.wqkv", "core.attn.wo", "core.mlp.wug", "core.mlp.wd"]
+
+
+class AuditReplay:
+    """Buffers and launch sequences of the replay; owned by ``TrainEngine`` (``eng``)."""
+
+    def __init__(self, eng, k: int):
+        from .engine import _Block, _Temps
+
+        self.eng, self.k = eng, k
+        cfg, dev = eng.cfg, eng.device
+        self.n, self.S, self.T = k, eng.S, cfg.t_max
+        self.Ma = k * eng.S
+        n, S, T, Ma, d, f, V = self.n, self.S, self.T, self.Ma, cfg.d_model, cfg.d_ff, cfg.vocab_size
+        f32, bf, i32 = torch.float32, torch.bfloat16, torch.int32
+        e = lambda *shape, dtype=f32: torch.zeros(*shape, dtype=dtype, device=dev)  # noqa: E731
+        self.p_inc = float(k) / float(eng.B)                              # inclusion probability k/n (audit.py:116)
+        self.idx = e(n, dtype=i32)
+        self.head_tab, self.ffn_tab = recipe_mask_tables(cfg, dev)
+        self.rid, self.active = e(T, n, dtype=i32), e(T, n, dtype=i32)
+        self.h0a, self.targets_a = e(Ma, d), e(Ma, dtype=torch.int64)
+        self.h = [e(Ma, d) for _ in range(T + 1)]                          # h[0] = h0a copy, h[t+1] = after pass t
+        self.ht, self.u = [e(Ma, d) for _ in range(T)], [e(Ma, d) for _ in range(T)]
+        self.n1, self.n2 = [e(Ma, d, dtype=bf) for _ in range(T)], [e(Ma, d, dtype=bf) for _ in range(T)]
+        self.rstd1, self.rstd2 = [e(Ma) for _ in range(T)], [e(Ma) for _ in range(T)]
+        self.attn_acc, self.mlp_acc = [e(Ma, d) for _ in range(T)], [e(Ma, d) for _ in range(T)]
+        ab, fb, H = cfg.attn_banks, cfg.ffn_banks, cfg.n_heads
+        self.qkv = [[e(Ma, 3 * d, dtype=bf) for _ in range(ab)] for _ in range(T)]
+        self.y = [[e(Ma, d, dtype=bf) for _ in range(ab)] for _ in range(T)]
+        self.ym = [[e(Ma, d, dtype=bf) for _ in range(ab)] for _ in range(T)]
+        self.lse = [[e(n * H * S) for _ in range(ab)] for _ in range(T)]
+        self.ug = [[e(Ma, 2 * f, dtype=bf) for _ in range(fb)] for _ in range(T)]
+        self.zm = [[e(Ma, f, dtype=bf) for _ in range(fb)] for _ in range(T)]
+        self.coda = [_Block(f"coda.{i}@audit", Ma, cfg, n, S, dev) for i in range(cfg.n_coda)]
+        self.tmp = _Temps(Ma, cfg, dev)
+        self.hidden16, self.rstd_f = e(Ma, d, dtype=bf), e(Ma)
+        self.logits, self.hot_logits = e(Ma, V, dtype=bf), e(Ma, V, dtype=bf)
+        self.loss_tok, self.exact_loss = e(Ma), e(n)
+        self.hot_end = e(Ma, d)
+        self.terms, self.dhot_extra, self.kl_rows, self.kl_sum = e(n, 4), e(Ma, d), e(Ma), e(1)
+        self.row_weight_a = torch.full((n,), 1.0 / (eng.B * eng.S * eng.world) / self.p_inc, dtype=f32, device=dev)
+        # backward scratch
+        self.dn_f32, self.dh0_acc, self.dcur, self.dalt = e(Ma, d), e(Ma, d), e(Ma, d), e(Ma, d)
+        self.d16a, self.d16b = e(Ma, d, dtype=bf), e(Ma, d, dtype=bf)
+        self.dz16, self.dug16, self.dqkv16 = e(Ma, f, dtype=bf), e(Ma, 2 * f, dtype=bf), e(Ma, 3 * d, dtype=bf)
+        self.partial_g, self.partial_b = e(2 * 148, d), e(2 * 148, d)
+        self.P = 64
+        self.part_alpha, self.part_attn, self.part_mlp = e(T * self.P), e(T * self.P), e(T * self.P)
+
+    # ------------------------------------------------------------------ host side, once per step
+    def choose(self, step_seed: int) -> None:
+        """Fixed-count sampler: first k entries of a seeded CPU permutation (audit.py:99-116); writes the subset
+        indices and the control-variate weights of the hot rows."""
+        eng = self.eng
+        gen = torch.Generator().manual_seed(step_seed)
+        chosen = torch.sort(torch.randperm(eng.B, generator=gen)[: self.k]).values
+        self.idx.copy_(chosen.to(torch.int32))
+        w0 = 1.0 / (eng.B * eng.S * eng.world)
+        rw = torch.full((eng.B,), w0, dtype=torch.float32)
+        rw[chosen] = w0 * (1.0 - 1.0 / self.p_inc)                       # d corrected / d hot on audited samples
+        eng.row_weight.copy_(rw)
+        self.last_chosen = chosen
+
+    # ------------------------------------------------------------------ forward
+    def forward(self, h0: torch.Tensor, h_phi: torch.Tensor) -> None:
+        eng = self.eng
+        o, cfg, p, sh = eng.ops, eng.cfg, eng.params, eng.shadow
+        n, S, T, Ma, d, f, V = self.n, self.S, self.T, self.Ma, cfg.d_model, cfg.d_ff, cfg.vocab_size
+        o.gather_rows(h0, self.idx, self.h0a, n, S * d * 4)
+        o.gather_rows(h0, self.idx, self.h[0], n, S * d * 4)
+        o.gather_rows(eng.targets, self.idx, self.targets_a, n, S * 8)
+        o.gather_rows(h_phi, self.idx, self.hot_end, n, S * d * 4)
+        o.audit_route(eng.route["recipe_id_by_pass"], eng.route["depth"], self.idx, self.rid, self.active, n, T)
+        alpha = p["core.alpha_inj"].view(1)
+        for t in range(T):
+            rid = self.rid[t]
+            o.scaled_residual_fwd(self.h[t], self.h0a, alpha, None, None, self.ht[t], n, S * d)
+            o.rmsnorm_fwd(self.ht[t], p["core.norm1.weight"], self.n1[t], self.rstd1[t],
+                          film_gamma=p["core.pass_gamma1"][t], film_beta=p["core.pass_beta1"][t])
+            for bk in range(cfg.attn_banks):
+                o.gemm(self.n1[t], sh["core.attn.wqkv"][bk], self.qkv[t][bk], M=Ma, N=3 * d, K=d, b_mn=True)
+                o.attn_fwd(self.qkv[t][bk], self.y[t][bk], self.lse[t][bk], B=n, S=S, n_heads=cfg.n_heads, head_dim=cfg.head_dim)
+                o.colmask_mul(self.y[t][bk], rid, self.head_tab[bk], S, self.ym[t][bk], Ma, d)
+                o.gemm(self.ym[t][bk], sh["core.attn.wo"][bk], self.attn_acc[t], M=Ma, N=d, K=d, b_mn=True,
+                       epilogue=A.EPI_F32, residual=self.attn_acc[t] if bk > 0 else None)
+            o.scaled_residual_fwd(self.ht[t], self.attn_acc[t], p["core.pass_attn_scale"][t:t + 1], None, None, self.u[t], n, S * d)
+            o.rmsnorm_fwd(self.u[t], p["core.norm2.weight"], self.n2[t], self.rstd2[t],
+                          film_gamma=p["core.pass_gamma2"][t], film_beta=p["core.pass_beta2"][t])
+            for bk in range(cfg.ffn_banks):
+                o.gemm(self.n2[t], sh["core.mlp.wug"][bk], self.ug[t][bk], M=Ma, N=2 * f, K=d, b_mn=True)
+                o.swiglu_masked_fwd(self.ug[t][bk], rid, self.ffn_tab[bk], S, self.zm[t][bk], Ma, f)
+                o.gemm(self.zm[t][bk], sh["core.mlp.wd"][bk], self.mlp_acc[t], M=Ma, N=d, K=f, b_mn=True,
+                       epilogue=A.EPI_F32, residual=self.mlp_acc[t] if bk > 0 else None)
+            o.scaled_residual_fwd(self.u[t], self.mlp_acc[t], p["core.pass_mlp_scale"][t:t + 1], self.active[t], self.h[t],
+                                  self.h[t + 1], n, S * d)
+        x = self.h[T]
+        for blk in self.coda:
+            x = eng._block_fwd(blk, x)
+        self.x_last = x
+        o.rmsnorm_fwd(x, p["final_norm.weight"], self.hidden16, self.rstd_f)
+        o.gemm(self.hidden16, sh["embed.weight"], self.logits, M=Ma, N=V, K=d)
+        # distillation terms (hot side receives the gradient, the exact side is a constant: macro.py:413-415)
+        tr, w = eng.tr, 1.0 / eng.world
+        o.macro_distill(self.hot_end, self.h[T], self.h0a, tr.lambda_delta_dir * w, tr.lambda_delta_rms * w,
+                        tr.lambda_endpoint_normed * w, tr.lambda_endpoint_raw * w, self.terms, self.dhot_extra, n, S, d)
+        temp = max(float(tr.distill_temperature), 1e-6)
+        o.kl_distill(self.hot_logits, self.logits, temp, tr.lambda_kl * w * temp / n, self.idx, S, eng.logits, self.kl_rows, Ma, V)
+        o.segment_sum(self.kl_rows, self.kl_sum, 1, Ma)
+        o.ce_fwd_bwd(self.logits, self.targets_a, self.row_weight_a, S, self.loss_tok, self.logits)
+        o.segment_sum(self.loss_tok, self.exact_loss, n, S)
+
+    def save_hot_logits(self) -> None:
+        """Copies the audited rows of the hot logits before the cross-entropy kernel overwrites them."""
+        V = self.eng.cfg.vocab_size
+        self.eng.ops.gather_rows(self.eng.logits, self.idx, self.hot_logits, self.n, self.S * V * 2)
+
+    # ------------------------------------------------------------------ backward
+    def backward_head(self) -> torch.Tensor:
+        """Logits, final norm and coda of the replay (weight gradients are ADDED to the hot pass's).
+        Returns the gradient wrt the last recurrent state h[T]."""
+        eng = self.eng
+        o, cfg, p, sh, g = eng.ops, eng.cfg, eng.params, eng.shadow, eng.grads
+        Ma, d, V = self.Ma, cfg.d_model, cfg.vocab_size
+        t = self.tmp
+        o.gemm(self.logits, sh["embed.weight"], t.dn16, M=Ma, N=d, K=V, b_mn=True)
+        o.gemm_wgrad(self.logits, self.hidden16, g["embed.weight"], M=V, N=d, K=Ma, accumulate=True)
+        o.rmsnorm_bwd(self.x_last, p["final_norm.weight"], self.rstd_f, t.dn16, None, t.dxa, t.dx16,
+                      g["final_norm.weight"], t.partial, accumulate_dw=True)
+        dcur, dalt = t.dxa, t.dxb
+        for blk in reversed(self.coda):
+            eng._block_bwd(blk, dcur, t.dx16, dalt, t.dx16, t.dxc, tmp=t, accumulate=True, mark_ready=False)
+            dcur, dalt = dalt, dcur
+        return dcur
+
+    def backward_core(self, dh_last: torch.Tensor, dh0_hot: torch.Tensor) -> None:
+        """Backward through the t_max banked passes; adds the subset's h0 gradient into rows `idx` of dh0_hot."""
+        eng = self.eng
+        o, cfg, p, sh, g = eng.ops, eng.cfg, eng.params, eng.shadow, eng.grads
+        n, S, T, Ma, d, f, P = self.n, self.S, self.T, self.Ma, cfg.d_model, cfg.d_ff, self.P
+        alpha = p["core.alpha_inj"].view(1)
+        o.fill_(self.dh0_acc, 0.0)
+        dnext, dthis = dh_last, (self.dcur if dh_last is not self.dcur else self.dalt)
+        for t in reversed(range(T)):
+            rid, first = self.rid[t], t == T - 1
+            acc = not first
+            du, dht = self.tmp.dxc, self.tmp.dxb if dnext is not self.tmp.dxb else self.tmp.dxa
+            if du is dnext:
+                du = self.tmp.dxa if dht is not self.tmp.dxa else self.tmp.dxb
+            # out = active ? u + s_mlp * mlp : h_in
+            o.scaled_residual_bwd(dnext, self.mlp_acc[t], p["core.pass_mlp_scale"][t:t + 1], self.active[t], du,
+                                          self.d16a, None, None, self.part_mlp[t * P:(t + 1) * P], n, S * d)
+            for bk in range(cfg.ffn_banks):
+                o.gemm(self.d16a, sh["core.mlp.wd"][bk], self.dz16, M=Ma, N=f, K=d)
+                o.gemm_wgrad(self.zm[t][bk], self.d16a, g["core.mlp.wd"][bk], M=f, N=d, K=Ma, accumulate=acc)
+                o.swiglu_masked_bwd(self.ug[t][bk], self.dz16, rid, self.ffn_tab[bk], S, self.dug16, Ma, f)
+                o.gemm(self.dug16, sh["core.mlp.wug"][bk], self.dn_f32, M=Ma, N=d, K=2 * f, epilogue=A.EPI_F32,
+                       residual=self.dn_f32 if bk > 0 else None)
+                o.gemm_wgrad(self.n2[t], self.dug16, g["core.mlp.wug"][bk], M=d, N=2 * f, K=Ma, accumulate=acc)
+            o.rmsnorm_bwd(self.u[t], p["core.norm2.weight"], self.rstd2[t], self.dn_f32, du, du, None,
+                          g["core.norm2.weight"], self.tmp.partial, film_gamma=p["core.pass_gamma2"][t],
+                          dgamma_out=g["core.pass_gamma2"][t], dbeta_out=g["core.pass_beta2"][t],
+                          partial_g=self.partial_g, partial_b=self.partial_b, accumulate_dw=acc)
+            # u = ht + s_attn * attn
+            o.scaled_residual_bwd(du, self.attn_acc[t], p["core.pass_attn_scale"][t:t + 1], None, dht, self.d16a, None, None,
+                                  self.part_attn[t * P:(t + 1) * P], n, S * d)
+            for bk in range(cfg.attn_banks):
+                o.gemm(self.d16a, sh["core.attn.wo"][bk], self.d16b, M=Ma, N=d, K=d)
+                o.gemm_wgrad(self.ym[t][bk], self.d16a, g["core.attn.wo"][bk], M=d, N=d, K=Ma, accumulate=acc)
+                o.colmask_mul(self.d16b, rid, self.head_tab[bk], S, self.d16b, Ma, d)
+                o.attn_bwd(self.qkv[t][bk], self.y[t][bk], self.d16b, self.lse[t][bk], self.dqkv16, B=n, S=S,
+                           n_heads=cfg.n_heads, head_dim=cfg.head_dim)
+                o.gemm(self.dqkv16, sh["core.attn.wqkv"][bk], self.dn_f32, M=Ma, N=d, K=3 * d, epilogue=A.EPI_F32,
+                       residual=self.dn_f32 if bk > 0 else None)
+                o.gemm_wgrad(self.n1[t], self.dqkv16, g["core.attn.wqkv"][bk], M=d, N=3 * d, K=Ma, accumulate=acc)
+            o.rmsnorm_bwd(self.ht[t], p["core.norm1.weight"], self.rstd1[t], self.dn_f32, dht, dht, None,
+                          g["core.norm1.weight"], self.tmp.partial, film_gamma=p["core.pass_gamma1"][t],
+                          dgamma_out=g["core.pass_gamma1"][t], dbeta_out=g["core.pass_beta1"][t],
+                          partial_g=self.partial_g, partial_b=self.partial_b, accumulate_dw=acc)
+            # ht = h_in + alpha * h0
+            o.scaled_residual_bwd(dht, self.h0a, alpha, None, dthis, None, self.dh0_acc, None,
+                                  self.part_alpha[t * P:(t + 1) * P], n, S * d)
+            # samples that were frozen in this pass hand their gradient straight through
+            o.scaled_residual_bwd(dnext, dnext, alpha, self.active[t], None, None, None, dthis, None, n, S * d)
+            dnext, dthis = dthis, (self.dalt if dthis is self.dcur else self.dcur)
+        # scalar parameters: per-CTA partial sums -> gradients (fixed order)
+        # (slots of part_* beyond the CTAs actually launched stay at their initial zero)
+        o.segment_sum(self.part_mlp, g["core.pass_mlp_scale"], T, P)
+        o.segment_sum(self.part_attn, g["core.pass_attn_scale"], T, P)
+        o.segment_sum(self.part_alpha, g["core.alpha_inj"].view(1), 1, T * P)
+        o.scatter_add_rows(dh0_hot, self.idx, self.dh0_acc, n, S * d)
+        o.scatter_add_rows(dh0_hot, self.idx, dnext, n, S * d)
+
+    # ------------------------------------------------------------------ reporting
+    def loss_terms(self, hot_per_sample: torch.Tensor) -> dict[str, float]:
+        """Host-side assembly of the audited quantities for the reported loss (training.py:1381-1385)."""
+        tr, n, Ma, d = self.eng.tr, self.n, self.Ma, self.eng.cfg.d_model
+        terms = self.terms.to("cpu")
+        exact = self.exact_loss.to("cpu")
+        hot = hot_per_sample[self.last_chosen]
+        temp = max(float(tr.distill_temperature), 1e-6)
+        aux = dict(delta_dir=tr.lambda_delta_dir * float(terms[:, 0].mean()),
+                   delta_rms=tr.lambda_delta_rms * float(terms[:, 1].mean()),
+                   endpoint_normed=tr.lambda_endpoint_normed * float(terms[:, 2].sum()) / (Ma * d),
+                   endpoint_raw=tr.lambda_endpoint_raw * float(terms[:, 3].sum()) / (Ma * d),
+                   kl=tr.lambda_kl * float(self.kl_sum.to("cpu")) / n * temp * temp)
+        return dict(correction=float(((exact - hot) / self.p_inc).sum()), exact=exact, aux=aux)

@@ -1,0 +1,324 @@
+// Helpers of the exact-audit replay: the audited samples (a fixed, small count per batch) are run through the
+// banked recurrent core with the router's per-pass recipe choices applied as COLUMN MASKS read from tables, so
+// that no tensor shape depends on a routing decision and the replay can sit in the same CUDA graph as the hot
+// pass.  Everything here is small (n*S tokens, n = audited samples) and bandwidth-trivial; the point of these
+// kernels is to keep the whole step on the device without host branches.
+
+#include "rte_common.cuh"
+
+namespace {
+
+constexpr int NTHR = 256;
+
+inline int grid_for(long long n, int block, int cap = 148 * 8) {
+  long long g = (n + block - 1) / block;
+  if (g > cap) g = cap;
+  if (g < 1) g = 1;
+  return (int)g;
+}
+
+__global__ void gather_rows_kernel(const uint4* __restrict__ src, const int32_t* __restrict__ idx, uint4* __restrict__ dst,
+                                   int n, long long row16) {
+  const long long total = (long long)n * row16;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+    const int r = int(i / row16);
+    dst[i] = src[(long long)idx[r] * row16 + (i % row16)];
+  }
+}
+
+__global__ void scatter_add_rows_kernel(float* __restrict__ dst, const int32_t* __restrict__ idx, const float* __restrict__ src,
+                                        int n, long long row) {
+  const long long total = (long long)n * row;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+    const int r = int(i / row);
+    dst[(long long)idx[r] * row + (i % row)] += src[i];
+  }
+}
+
+__global__ void audit_route_kernel(const int32_t* __restrict__ by_pass, const int32_t* __restrict__ depth,
+                                   const int32_t* __restrict__ idx, int32_t* __restrict__ rid, int32_t* __restrict__ active,
+                                   int n, int T) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n * T) return;
+  const int t = i / n, s = i % n, b = idx[s];
+  rid[i] = by_pass[b * T + t];
+  active[i] = depth[b] > t ? 1 : 0;
+}
+
+__global__ void colmask_mul_kernel(const __nv_bfloat16* __restrict__ x, const int32_t* __restrict__ rid,
+                                   const float* __restrict__ table, int S, __nv_bfloat16* __restrict__ out, int rows, int cols) {
+  const long long total = (long long)rows * cols;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+    const int r = int(i / cols), c = int(i % cols);
+    out[i] = __float2bfloat16_rn(__bfloat162float(x[i]) * table[(size_t)rid[r / S] * cols + c]);
+  }
+}
+
+__global__ void swiglu_masked_fwd_kernel(const __nv_bfloat16* __restrict__ ug, const int32_t* __restrict__ rid,
+                                         const float* __restrict__ table, int S, __nv_bfloat16* __restrict__ z, int rows, int F) {
+  const long long total = (long long)rows * F;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+    const int r = int(i / F), j = int(i % F);
+    const float up = __bfloat162float(ug[(size_t)r * 2 * F + j]), g = __bfloat162float(ug[(size_t)r * 2 * F + F + j]);
+    z[i] = __float2bfloat16_rn(up * rte::silu_f(g) * table[(size_t)rid[r / S] * F + j]);
+  }
+}
+
+__global__ void swiglu_masked_bwd_kernel(const __nv_bfloat16* __restrict__ ug, const __nv_bfloat16* __restrict__ dz,
+                                         const int32_t* __restrict__ rid, const float* __restrict__ table, int S,
+                                         __nv_bfloat16* __restrict__ dug, int rows, int F) {
+  const long long total = (long long)rows * F;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+    const int r = int(i / F), j = int(i % F);
+    const float up = __bfloat162float(ug[(size_t)r * 2 * F + j]), g = __bfloat162float(ug[(size_t)r * 2 * F + F + j]);
+    const float d = __bfloat162float(dz[i]) * table[(size_t)rid[r / S] * F + j];
+    const float sg = rte::sigmoid_f(g);
+    dug[(size_t)r * 2 * F + j] = __float2bfloat16_rn(d * g * sg);
+    dug[(size_t)r * 2 * F + F + j] = __float2bfloat16_rn(d * up * sg * (1.f + g * (1.f - sg)));
+  }
+}
+
+__global__ void scaled_residual_fwd_kernel(const float* __restrict__ base, const float* __restrict__ branch,
+                                           const float* __restrict__ scale, const int32_t* __restrict__ active,
+                                           const float* __restrict__ pass, float* __restrict__ out, int n, long long se) {
+  const float s = *scale;
+  const long long total = (long long)n * se;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+    const bool on = active == nullptr || active[i / se] != 0;
+    out[i] = on ? base[i] + s * branch[i] : pass[i];
+  }
+}
+
+__global__ void __launch_bounds__(NTHR)
+scaled_residual_bwd_kernel(const float* __restrict__ dout, const float* __restrict__ branch, const float* __restrict__ scale,
+                           const int32_t* __restrict__ active, float* __restrict__ dbase, __nv_bfloat16* __restrict__ db16,
+                           float* __restrict__ db32, float* __restrict__ dpass, float* __restrict__ dscale_part, int n,
+                           long long se) {
+  __shared__ float red[32];
+  const float s = *scale;
+  const long long total = (long long)n * se;
+  float acc = 0.f;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+    const bool on = active == nullptr || active[i / se] != 0;
+    const float g = dout[i];
+    if (on) acc += g * branch[i];
+    if (dpass && !on) dpass[i] += g;
+    if (db16) db16[i] = __float2bfloat16_rn(on ? s * g : 0.f);
+    if (db32 && on) db32[i] += s * g;
+    if (dbase) dbase[i] = on ? g : 0.f;
+  }
+  acc = rte::block_sum(acc, red);
+  if (threadIdx.x == 0 && dscale_part) dscale_part[blockIdx.x] = acc;
+}
+
+__device__ __forceinline__ float smooth_l1(float x) { const float a = fabsf(x); return a < 1.f ? 0.5f * x * x : a - 0.5f; }
+__device__ __forceinline__ float clamp1(float x) { return fminf(1.f, fmaxf(-1.f, x)); }
+
+// One CTA per audited sample.  Phase A: whole-sample reductions for the direction / rms terms.
+// Phase B: one warp per row for the two smooth-L1 terms (the normed one goes back through the row's rmsnorm).
+__global__ void __launch_bounds__(NTHR)
+macro_distill_kernel(const float* __restrict__ hot, const float* __restrict__ exact, const float* __restrict__ h0,
+                     float l_dir, float l_rms, float l_normed, float l_raw, float* __restrict__ terms,
+                     float* __restrict__ dhot, int n, int S, int d) {
+  __shared__ float red[32];
+  __shared__ float row_sums[2][NTHR / 32];
+  const int i = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const long long N = (long long)S * d;
+  const float* hp = hot + (size_t)i * N;
+  const float* ep = exact + (size_t)i * N;
+  const float* zp = h0 + (size_t)i * N;
+  float* gp = dhot + (size_t)i * N;
+  float dot = 0.f, pp = 0.f, ee = 0.f;
+  for (long long k = threadIdx.x; k < N; k += NTHR) {
+    const float a = hp[k] - zp[k], b = ep[k] - zp[k];
+    dot += a * b; pp += a * a; ee += b * b;
+  }
+  dot = rte::block_sum(dot, red);
+  pp = rte::block_sum(pp, red);
+  ee = rte::block_sum(ee, red);
+  const float np = fmaxf(sqrtf(pp), 1e-8f), ne = fmaxf(sqrtf(ee), 1e-8f);
+  const float cosv = dot / (np * ne);
+  const float rp = fmaxf(sqrtf(pp / (float)N), 1e-8f), re = fmaxf(sqrtf(ee / (float)N), 1e-8f);
+  const float delta = logf(rp) - logf(re);
+  const float c_dir = -l_dir / (float)n, c_rms = l_rms / (float)n * 2.f * delta / ((float)N * rp * rp);
+  const float c_el = 1.f / ((float)n * (float)N);
+  float sl1n = 0.f, sl1r = 0.f;
+  for (int s = warp; s < S; s += NTHR / 32) {
+    const float* hr = hp + (size_t)s * d;
+    const float* er = ep + (size_t)s * d;
+    float sh = 0.f, se = 0.f;
+    for (int c = lane; c < d; c += 32) { sh += hr[c] * hr[c]; se += er[c] * er[c]; }
+    sh = rte::warp_sum(sh); se = rte::warp_sum(se);
+    const float rh = rsqrtf(sh / (float)d + 1e-5f), rx = rsqrtf(se / (float)d + 1e-5f);
+    float rowdot = 0.f;
+    for (int c = lane; c < d; c += 32) {
+      const float hn = hr[c] * rh, df = hn - er[c] * rx;
+      sl1n += smooth_l1(df);
+      rowdot += clamp1(df) * hn;
+    }
+    rowdot = rte::warp_sum(rowdot) / (float)d;
+    for (int c = lane; c < d; c += 32) {
+      const float hn = hr[c] * rh, df = hn - er[c] * rx, raw = hr[c] - er[c];
+      sl1r += smooth_l1(raw);
+      const float a = hr[c] - zp[(size_t)s * d + c], b = er[c] - zp[(size_t)s * d + c];
+      float g = l_normed * c_el * rh * (clamp1(df) - hn * rowdot);
+      g += l_raw * c_el * clamp1(raw);
+      g += c_dir * (b / (np * ne) - cosv * a / (np * np));
+      g += c_rms * a;
+      gp[(size_t)s * d + c] = g;
+    }
+  }
+  sl1n = rte::warp_sum(sl1n); sl1r = rte::warp_sum(sl1r);
+  if (lane == 0) { row_sums[0][warp] = sl1n; row_sums[1][warp] = sl1r; }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    float a = 0.f, b = 0.f;
+    for (int w = 0; w < NTHR / 32; ++w) { a += row_sums[0][w]; b += row_sums[1][w]; }
+    terms[i * 4 + 0] = 1.f - cosv;
+    terms[i * 4 + 1] = delta * delta;
+    terms[i * 4 + 2] = a;
+    terms[i * 4 + 3] = b;
+  }
+}
+
+// One CTA per token row of the audited subset.
+__global__ void __launch_bounds__(NTHR)
+kl_distill_kernel(const __nv_bfloat16* __restrict__ hot, const __nv_bfloat16* __restrict__ exact, float inv_temp, float coef,
+                  const int32_t* __restrict__ idx, int S, __nv_bfloat16* __restrict__ dlog, int ld, float* __restrict__ kl_rows,
+                  int V) {
+  __shared__ float red[32];
+  const int row = blockIdx.x;
+  const __nv_bfloat16* hr = hot + (size_t)row * V;
+  const __nv_bfloat16* er = exact + (size_t)row * V;
+  float mh = -INFINITY, me = -INFINITY;
+  for (int c = threadIdx.x; c < V; c += NTHR) {
+    mh = fmaxf(mh, __bfloat162float(hr[c]) * inv_temp);
+    me = fmaxf(me, __bfloat162float(er[c]) * inv_temp);
+  }
+  mh = rte::block_max(mh, red);
+  me = rte::block_max(me, red);
+  float sh = 0.f, se = 0.f;
+  for (int c = threadIdx.x; c < V; c += NTHR) {
+    sh += __expf(__bfloat162float(hr[c]) * inv_temp - mh);
+    se += __expf(__bfloat162float(er[c]) * inv_temp - me);
+  }
+  sh = rte::block_sum(sh, red);
+  se = rte::block_sum(se, red);
+  const float lh = mh + __logf(sh), le = me + __logf(se);
+  __nv_bfloat16* dr = dlog + ((size_t)idx[row / S] * S + (row % S)) * ld;
+  float kl = 0.f;
+  for (int c = threadIdx.x; c < V; c += NTHR) {
+    const float lph = __bfloat162float(hr[c]) * inv_temp - lh, lpe = __bfloat162float(er[c]) * inv_temp - le;
+    const float ph = __expf(lph), pe = __expf(lpe);
+    kl += pe * (lpe - lph);
+    dr[c] = __float2bfloat16_rn(__bfloat162float(dr[c]) + coef * (ph - pe));
+  }
+  kl = rte::block_sum(kl, red);
+  if (threadIdx.x == 0) kl_rows[row] = kl;
+}
+
+}  // namespace
+
+#define ST(s) reinterpret_cast<cudaStream_t>(s)
+
+extern "C" int rte_gather_rows(const void* src, const int32_t* idx, void* dst, int32_t n, int64_t row_bytes, rte_stream_t stream) {
+  RTE_CHECK_ARG(src && idx && dst && n > 0 && row_bytes > 0);
+  if ((row_bytes % 16) || (reinterpret_cast<uintptr_t>(src) & 15) || (reinterpret_cast<uintptr_t>(dst) & 15)) return RTE_ERR_ALIGNMENT;
+  const long long row16 = row_bytes / 16;
+  gather_rows_kernel<<<grid_for((long long)n * row16, NTHR), NTHR, 0, ST(stream)>>>(
+      reinterpret_cast<const uint4*>(src), idx, reinterpret_cast<uint4*>(dst), n, row16);
+  RTE_LAUNCH_CHECK();
+  return RTE_OK;
+}
+
+extern "C" int rte_scatter_add_rows_f32(float* dst, const int32_t* idx, const float* src, int32_t n, int64_t row_elems,
+                                        rte_stream_t stream) {
+  RTE_CHECK_ARG(dst && idx && src && n > 0 && row_elems > 0);
+  scatter_add_rows_kernel<<<grid_for((long long)n * row_elems, NTHR), NTHR, 0, ST(stream)>>>(dst, idx, src, n, row_elems);
+  RTE_LAUNCH_CHECK();
+  return RTE_OK;
+}
+
+extern "C" int rte_audit_route(const int32_t* recipe_id_by_pass, const int32_t* depth, const int32_t* idx, int32_t* rid_out,
+                               int32_t* active_out, int32_t n, int32_t T, rte_stream_t stream) {
+  RTE_CHECK_ARG(recipe_id_by_pass && depth && idx && rid_out && active_out && n > 0 && T > 0);
+  audit_route_kernel<<<rte::ceil_div(n * T, 128), 128, 0, ST(stream)>>>(recipe_id_by_pass, depth, idx, rid_out, active_out, n, T);
+  RTE_LAUNCH_CHECK();
+  return RTE_OK;
+}
+
+extern "C" int rte_colmask_mul_bf16(const void* x, const int32_t* rid, const float* table, int32_t S, void* out, int32_t rows,
+                                    int32_t cols, rte_stream_t stream) {
+  RTE_CHECK_ARG(x && rid && table && out && S > 0 && rows > 0 && cols > 0);
+  colmask_mul_kernel<<<grid_for((long long)rows * cols, NTHR), NTHR, 0, ST(stream)>>>(
+      reinterpret_cast<const __nv_bfloat16*>(x), rid, table, S, reinterpret_cast<__nv_bfloat16*>(out), rows, cols);
+  RTE_LAUNCH_CHECK();
+  return RTE_OK;
+}
+
+extern "C" int rte_swiglu_masked_fwd(const void* ug, const int32_t* rid, const float* table, int32_t S, void* z, int32_t rows,
+                                     int32_t F, rte_stream_t stream) {
+  RTE_CHECK_ARG(ug && rid && table && z && S > 0 && rows > 0 && F > 0);
+  swiglu_masked_fwd_kernel<<<grid_for((long long)rows * F, NTHR), NTHR, 0, ST(stream)>>>(
+      reinterpret_cast<const __nv_bfloat16*>(ug), rid, table, S, reinterpret_cast<__nv_bfloat16*>(z), rows, F);
+  RTE_LAUNCH_CHECK();
+  return RTE_OK;
+}
+
+extern "C" int rte_swiglu_masked_bwd(const void* ug, const void* dz, const int32_t* rid, const float* table, int32_t S,
+                                     void* dug, int32_t rows, int32_t F, rte_stream_t stream) {
+  RTE_CHECK_ARG(ug && dz && rid && table && dug && S > 0 && rows > 0 && F > 0);
+  swiglu_masked_bwd_kernel<<<grid_for((long long)rows * F, NTHR), NTHR, 0, ST(stream)>>>(
+      reinterpret_cast<const __nv_bfloat16*>(ug), reinterpret_cast<const __nv_bfloat16*>(dz), rid, table, S,
+      reinterpret_cast<__nv_bfloat16*>(dug), rows, F);
+  RTE_LAUNCH_CHECK();
+  return RTE_OK;
+}
+
+extern "C" int rte_scaled_residual_fwd(const float* base, const float* branch, const float* scale, const int32_t* active,
+                                       const float* passthrough, float* out, int32_t n, int64_t sample_elems,
+                                       rte_stream_t stream) {
+  RTE_CHECK_ARG(base && branch && scale && out && n > 0 && sample_elems > 0 && (active == nullptr || passthrough != nullptr));
+  scaled_residual_fwd_kernel<<<grid_for((long long)n * sample_elems, NTHR), NTHR, 0, ST(stream)>>>(base, branch, scale, active,
+                                                                                                 passthrough, out, n, sample_elems);
+  RTE_LAUNCH_CHECK();
+  return RTE_OK;
+}
+
+extern "C" int rte_scaled_residual_bwd(const float* dout, const float* branch, const float* scale, const int32_t* active,
+                                       float* dbase, void* dbranch_bf16, float* dbranch_f32_accum, float* dpassthrough,
+                                       float* dscale_partial, int32_t max_partials, int32_t* n_partials, int32_t n,
+                                       int64_t sample_elems, rte_stream_t stream) {
+  RTE_CHECK_ARG(dout && branch && scale && n > 0 && sample_elems > 0);
+  int grid = grid_for((long long)n * sample_elems, NTHR, 64);
+  if (dscale_partial) {
+    RTE_CHECK_ARG(max_partials >= 1);
+    if (grid > max_partials) grid = max_partials;
+  }
+  if (n_partials) *n_partials = grid;
+  scaled_residual_bwd_kernel<<<grid, NTHR, 0, ST(stream)>>>(dout, branch, scale, active, dbase,
+      reinterpret_cast<__nv_bfloat16*>(dbranch_bf16), dbranch_f32_accum, dpassthrough, dscale_partial, n, sample_elems);
+  RTE_LAUNCH_CHECK();
+  return RTE_OK;
+}
+
+extern "C" int rte_macro_distill(const float* hot, const float* exact, const float* h0, float l_dir, float l_rms,
+                                 float l_normed, float l_raw, float* terms, float* dhot, int32_t n, int32_t S, int32_t d,
+                                 rte_stream_t stream) {
+  RTE_CHECK_ARG(hot && exact && h0 && terms && dhot && n > 0 && S > 0 && d > 0);
+  macro_distill_kernel<<<n, NTHR, 0, ST(stream)>>>(hot, exact, h0, l_dir, l_rms, l_normed, l_raw, terms, dhot, n, S, d);
+  RTE_LAUNCH_CHECK();
+  return RTE_OK;
+}
+
+extern "C" int rte_kl_distill(const void* hot_logits, const void* exact_logits, float temp, float coef, const int32_t* idx,
+                              int32_t S, void* dlogits_hot, int32_t ld_dlogits, float* kl_rows, int32_t rows, int32_t V,
+                              rte_stream_t stream) {
+  RTE_CHECK_ARG(hot_logits && exact_logits && idx && dlogits_hot && kl_rows && temp > 0.f && S > 0 && rows > 0 && V > 0 &&
+                ld_dlogits >= V);
+  kl_distill_kernel<<<rows, NTHR, 0, ST(stream)>>>(reinterpret_cast<const __nv_bfloat16*>(hot_logits),
+      reinterpret_cast<const __nv_bfloat16*>(exact_logits), 1.f / temp, coef, idx, S,
+      reinterpret_cast<__nv_bfloat16*>(dlogits_hot), ld_dlogits, kl_rows, V);
+  RTE_LAUNCH_CHECK();
+  return RTE_OK;
+}

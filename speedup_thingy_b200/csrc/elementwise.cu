@@ -321,6 +321,9 @@ __global__ void cast_kernel(const float* __restrict__ src, __nv_bfloat16* __rest
   for (long long i = n4 * 4 + blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x)
     dst[i] = __float2bfloat16_rn(src[i]);
 }
+__global__ void fill_kernel(float* __restrict__ dst, float value, long long n) {
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) dst[i] = value;
+}
 __global__ void add_kernel(float* __restrict__ dst, const float* __restrict__ src, long long n) {
   for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) dst[i] += src[i];
 }
@@ -603,6 +606,12 @@ extern "C" int rte_cast_f32_bf16(const float* src, void* dst, int64_t n, rte_str
   RTE_CHECK_ARG(src && dst && n > 0);
   if ((reinterpret_cast<uintptr_t>(src) & 15) || (reinterpret_cast<uintptr_t>(dst) & 7)) return RTE_ERR_ALIGNMENT;
   cast_kernel<<<grid_for(n / 4 + 1, 256), 256, 0, ST(stream)>>>(src, reinterpret_cast<__nv_bfloat16*>(dst), n);
+  RTE_LAUNCH_CHECK();
+  return RTE_OK;
+}
+extern "C" int rte_fill_f32(float* dst, float value, int64_t n, rte_stream_t stream) {
+  RTE_CHECK_ARG(dst && n > 0);
+  fill_kernel<<<grid_for(n, 256), 256, 0, ST(stream)>>>(dst, value, n);
   RTE_LAUNCH_CHECK();
   return RTE_OK;
 }

@@ -111,12 +111,26 @@ class _Block:
         bf, f32 = torch.bfloat16, torch.float32
         e = lambda *shape, dtype=bf: torch.empty(*shape, dtype=dtype, device=device)  # noqa: E731
         self.prefix = prefix
+        self.M, self.B, self.S = M, B, S
         self.n1, self.n2, self.y = e(M, d), e(M, d), e(M, d)
         self.qkv, self.ug, self.z = e(M, 3 * d), e(M, 2 * f), e(M, f)
         self.u, self.out = e(M, d, dtype=f32), e(M, d, dtype=f32)
         self.rstd1, self.rstd2 = e(M, dtype=f32), e(M, dtype=f32)
         self.lse = e(B * cfg.n_heads * S, dtype=f32)
         self.x_in: torch.Tensor | None = None
+
+
+class _Temps:
+    """Scratch tensors of one block-backward pass over M tokens (reused by every block)."""
+
+    def __init__(self, M: int, cfg: ModelConfig, device):
+        d, f = cfg.d_model, cfg.d_ff
+        bf, f32 = torch.bfloat16, torch.float32
+        self.dug = torch.empty(M, 2 * f, dtype=bf, device=device)
+        self.dn16, self.dy16, self.dx16 = (torch.empty(M, d, dtype=bf, device=device) for _ in range(3))
+        self.dqkv = torch.empty(M, 3 * d, dtype=bf, device=device)
+        self.dxa, self.dxb, self.dxc = (torch.empty(M, d, dtype=f32, device=device) for _ in range(3))
+        self.partial = torch.empty(2 * 148, d, dtype=f32, device=device)
 
 
 class TrainEngine:
@@ -153,8 +167,14 @@ class TrainEngine:
         self.dense = cfg.topology == "dense"
         if self.dense != (tr.mode == "dense_exact"):
             raise ValueError("mode dense_exact needs topology 'dense'; recursive_macro needs 'recursive'")
-        if tr.audit_fixed_count_per_batch:
-            raise NotImplementedError("exact-audit replay is not wired into this engine yet")
+        self.audit_k = int(tr.audit_fixed_count_per_batch or 0)
+        if self.audit_k:
+            if self.dense:
+                raise ValueError("the exact audit belongs to the recursive model")
+            if tr.audit_mode != "gradient_corrected" or tr.audit_residual_clip is not None:
+                raise NotImplementedError("audit: only audit_mode='gradient_corrected' without residual clipping")
+            if self.S % 2:
+                raise NotImplementedError("audit: seq_len must be even")
         if cfg.d_model % 8 or cfg.d_ff % 64 or cfg.vocab_size % 8 or cfg.head_dim not in (8, 16, 32, 64, 128):
             raise NotImplementedError("kernel size limits: d_model % 8 == 0, d_ff % 64 == 0, vocab % 8 == 0, "
                                       "head_dim in {8,16,32,64,128}")
@@ -175,6 +195,9 @@ class TrainEngine:
             self.trainable = [n for n in names if n.startswith(("embed.", "prelude.", "macro.", "coda.", "final_norm."))]
             if not tr.disable_router_aux:
                 self.trainable += [n for n in names if n.startswith(("router.recipe_mlp.", "router.depth_mlp."))]
+            if self.audit_k:
+                from .audit import CORE_PARAMS
+                self.trainable += CORE_PARAMS
         # gradients live in one flat buffer, laid out in the order the backward pass completes them, so that
         # data-parallel buckets are contiguous slices that can be all-reduced while backward continues
         order = self._grad_completion_order()
@@ -209,6 +232,10 @@ class TrainEngine:
         for n in names:
             if n == "embed.weight" or n.endswith((".attn.wqkv.weight", ".attn.wo.weight", ".mlp.wug.weight", ".mlp.wd.weight")):
                 self.shadow[n] = torch.empty_like(self.params[n], dtype=bf)
+        if self.audit_k:
+            from .audit import CORE_SHADOWED
+            for n in CORE_SHADOWED:
+                self.shadow[n] = torch.empty_like(self.params[n], dtype=bf)
         entries = [dict(p=self.params[n], g=self.grads[n], m=self.exp_avg[n], v=self.exp_avg_sq[n],
                         shadow=self.shadow.get(n), lr_group=LR_GROUPS.index(lr_group_of(n, cfg.topology)))
                    for n in self.trainable]
@@ -234,11 +261,10 @@ class TrainEngine:
         self.scalars = torch.zeros(8, dtype=f32, device=dev)   # [0]=sum loss, [1]=aux load, [2]=aux depth, [3]=sumsq, [4]=clip
         self.row_weight = torch.full((B,), 1.0 / (B * S * self.world), dtype=f32, device=dev)
         # backward temporaries
-        self.dug = e(M, 2 * cfg.d_ff, dtype=bf)
-        self.dn16, self.dy16, self.dx16 = e(M, d, dtype=bf), e(M, d, dtype=bf), e(M, d, dtype=bf)
-        self.dqkv = e(M, 3 * d, dtype=bf)
-        self.dxa, self.dxb, self.dxc = e(M, d), e(M, d), e(M, d)
-        self.partial = e(2 * 148, d)
+        self.tmp = _Temps(M, cfg, dev)
+        t_ = self.tmp
+        self.dug, self.dn16, self.dy16, self.dx16, self.dqkv = t_.dug, t_.dn16, t_.dy16, t_.dx16, t_.dqkv
+        self.dxa, self.dxb, self.dxc, self.partial = t_.dxa, t_.dxb, t_.dxc, t_.partial
         self.gn_partial = e(self.plan.total_chunks)
         max_ws = 0
         for (mm, nn) in ((3 * d, d), (d, d), (2 * cfg.d_ff, d), (d, cfg.d_ff), (V, d)):
@@ -257,6 +283,10 @@ class TrainEngine:
                               recipe_id=e(B, dtype=i32), recipe_id_by_pass=e(B, cfg.t_max, dtype=i32),
                               depth_id=e(B, dtype=i32), depth=e(B, dtype=i32))
             self.router_scratch = e(A.ROUTER_MAX_R + B * (2 * hid + r + k))
+        self.audit = None
+        if self.audit_k:
+            from .audit import AuditReplay
+            self.audit = AuditReplay(self, self.audit_k)
         for n, sh in self.shadow.items():
             ops.cast_bf16(self.params[n], sh)
         self._graph = None
@@ -279,6 +309,9 @@ class TrainEngine:
             for i in reversed(range(cfg.n_coda)):
                 order += block(f"coda.{i}")
             order += ["macro.d_gain", "macro.v", "macro.u", "macro.bias"]
+            if self.audit_k:
+                from .audit import CORE_PARAMS
+                order += CORE_PARAMS
             if not self.tr.disable_router_aux:
                 for mlp in ("recipe_mlp", "depth_mlp"):
                     order += [f"router.{mlp}.0.weight", f"router.{mlp}.0.bias", f"router.{mlp}.2.weight", f"router.{mlp}.2.bias"]
@@ -331,12 +364,12 @@ class TrainEngine:
 
     # ------------------------------------------------------------------ one transformer block
     def _block_fwd(self, blk: _Block, x_in: torch.Tensor) -> torch.Tensor:
-        o, cfg, p, sh, M = self.ops, self.cfg, self.params, self.shadow, self.M
-        d, f, pre = cfg.d_model, cfg.d_ff, blk.prefix
+        o, cfg, p, sh, M = self.ops, self.cfg, self.params, self.shadow, blk.M
+        d, f, pre = cfg.d_model, cfg.d_ff, blk.prefix.split("@")[0]
         blk.x_in = x_in
         o.rmsnorm_fwd(x_in, p[f"{pre}.norm1.weight"], blk.n1, blk.rstd1)
         o.gemm(blk.n1, sh[f"{pre}.attn.wqkv.weight"], blk.qkv, M=M, N=3 * d, K=d)
-        o.attn_fwd(blk.qkv, blk.y, blk.lse, B=self.B, S=self.S, n_heads=cfg.n_heads, head_dim=cfg.head_dim)
+        o.attn_fwd(blk.qkv, blk.y, blk.lse, B=blk.B, S=blk.S, n_heads=cfg.n_heads, head_dim=cfg.head_dim)
         o.gemm(blk.y, sh[f"{pre}.attn.wo.weight"], blk.u, M=M, N=d, K=d, epilogue=A.EPI_F32, residual=x_in)
         o.rmsnorm_fwd(blk.u, p[f"{pre}.norm2.weight"], blk.n2, blk.rstd2)
         o.gemm(blk.n2, sh[f"{pre}.mlp.wug.weight"], blk.z, M=M, N=2 * f, K=d, epilogue=A.EPI_SWIGLU_FWD, out2=blk.ug, pair=f)
@@ -344,34 +377,38 @@ class TrainEngine:
         return blk.out
 
     def _block_bwd(self, blk: _Block, dout: torch.Tensor, dout16: torch.Tensor, dx: torch.Tensor,
-                   dx16: torch.Tensor | None, du: torch.Tensor) -> None:
-        """dout/dout16: gradient wrt the block output (f32 and its bf16 copy); writes dx (f32) and dx16."""
-        o, cfg, p, sh, g, M = self.ops, self.cfg, self.params, self.shadow, self.grads, self.M
-        d, f, pre = cfg.d_model, cfg.d_ff, blk.prefix
+                   dx16: torch.Tensor | None, du: torch.Tensor, tmp: "_Temps | None" = None,
+                   accumulate: bool = False, mark_ready: bool = True) -> None:
+        """dout/dout16: gradient wrt the block output (f32 and its bf16 copy); writes dx (f32) and dx16.
+        `accumulate` adds the weight gradients to what is already there (second pass over shared weights)."""
+        o, cfg, p, sh, g, M = self.ops, self.cfg, self.params, self.shadow, self.grads, blk.M
+        t = tmp if tmp is not None else self.tmp
+        d, f, pre = cfg.d_model, cfg.d_ff, blk.prefix.split("@")[0]
+        ready = self._grad_ready if mark_ready else (lambda *names: None)
         # --- MLP: x_out = u + wd(up * silu(gate)),  (up | gate) = wug(norm2(u))
-        o.gemm(dout16, sh[f"{pre}.mlp.wd.weight"], self.dug, M=M, N=f, K=d, b_mn=True, epilogue=A.EPI_SWIGLU_BWD,
+        o.gemm(dout16, sh[f"{pre}.mlp.wd.weight"], t.dug, M=M, N=f, K=d, b_mn=True, epilogue=A.EPI_SWIGLU_BWD,
                residual=blk.ug, pair=f)
-        o.gemm_wgrad(dout16, blk.z, g[f"{pre}.mlp.wd.weight"], M=d, N=f, K=M)
-        self._grad_ready(f"{pre}.mlp.wd.weight")
-        o.gemm(self.dug, sh[f"{pre}.mlp.wug.weight"], self.dn16, M=M, N=d, K=2 * f, b_mn=True)
-        o.gemm_wgrad(self.dug, blk.n2, g[f"{pre}.mlp.wug.weight"], M=2 * f, N=d, K=M)
-        self._grad_ready(f"{pre}.mlp.wug.weight")
-        o.rmsnorm_bwd(blk.u, p[f"{pre}.norm2.weight"], blk.rstd2, self.dn16, dout, du, self.dy16,
-                      g[f"{pre}.norm2.weight"], self.partial)
-        self._grad_ready(f"{pre}.norm2.weight")
-        du16 = self.dy16
+        o.gemm_wgrad(dout16, blk.z, g[f"{pre}.mlp.wd.weight"], M=d, N=f, K=M, accumulate=accumulate)
+        ready(f"{pre}.mlp.wd.weight")
+        o.gemm(t.dug, sh[f"{pre}.mlp.wug.weight"], t.dn16, M=M, N=d, K=2 * f, b_mn=True)
+        o.gemm_wgrad(t.dug, blk.n2, g[f"{pre}.mlp.wug.weight"], M=2 * f, N=d, K=M, accumulate=accumulate)
+        ready(f"{pre}.mlp.wug.weight")
+        o.rmsnorm_bwd(blk.u, p[f"{pre}.norm2.weight"], blk.rstd2, t.dn16, dout, du, t.dy16,
+                      g[f"{pre}.norm2.weight"], t.partial, accumulate_dw=accumulate)
+        ready(f"{pre}.norm2.weight")
+        du16 = t.dy16
         # --- attention: u = x + wo(attn(rope(q), rope(k), v)),  (q | k | v) = wqkv(norm1(x))
-        o.gemm(du16, sh[f"{pre}.attn.wo.weight"], self.dn16, M=M, N=d, K=d, b_mn=True)
-        o.gemm_wgrad(du16, blk.y, g[f"{pre}.attn.wo.weight"], M=d, N=d, K=M)
-        self._grad_ready(f"{pre}.attn.wo.weight")
-        o.attn_bwd(blk.qkv, blk.y, self.dn16, blk.lse, self.dqkv, B=self.B, S=self.S, n_heads=cfg.n_heads,
+        o.gemm(du16, sh[f"{pre}.attn.wo.weight"], t.dn16, M=M, N=d, K=d, b_mn=True)
+        o.gemm_wgrad(du16, blk.y, g[f"{pre}.attn.wo.weight"], M=d, N=d, K=M, accumulate=accumulate)
+        ready(f"{pre}.attn.wo.weight")
+        o.attn_bwd(blk.qkv, blk.y, t.dn16, blk.lse, t.dqkv, B=blk.B, S=blk.S, n_heads=cfg.n_heads,
                    head_dim=cfg.head_dim)
-        o.gemm(self.dqkv, sh[f"{pre}.attn.wqkv.weight"], self.dn16, M=M, N=d, K=3 * d, b_mn=True)
-        o.gemm_wgrad(self.dqkv, blk.n1, g[f"{pre}.attn.wqkv.weight"], M=3 * d, N=d, K=M)
-        self._grad_ready(f"{pre}.attn.wqkv.weight")
-        o.rmsnorm_bwd(blk.x_in, p[f"{pre}.norm1.weight"], blk.rstd1, self.dn16, du, dx, dx16,
-                      g[f"{pre}.norm1.weight"], self.partial)
-        self._grad_ready(f"{pre}.norm1.weight")
+        o.gemm(t.dqkv, sh[f"{pre}.attn.wqkv.weight"], t.dn16, M=M, N=d, K=3 * d, b_mn=True)
+        o.gemm_wgrad(t.dqkv, blk.n1, g[f"{pre}.attn.wqkv.weight"], M=3 * d, N=d, K=M, accumulate=accumulate)
+        ready(f"{pre}.attn.wqkv.weight")
+        o.rmsnorm_bwd(blk.x_in, p[f"{pre}.norm1.weight"], blk.rstd1, t.dn16, du, dx, dx16,
+                      g[f"{pre}.norm1.weight"], t.partial, accumulate_dw=accumulate)
+        ready(f"{pre}.norm1.weight")
 
     # ------------------------------------------------------------------ forward + backward
     def _forward_backward(self) -> None:
@@ -398,9 +435,14 @@ class TrainEngine:
         x_last = x
         o.rmsnorm_fwd(x_last, p["final_norm.weight"], self.hidden16, self.rstd_f)
         o.gemm(self.hidden16, sh["embed.weight"], self.logits, M=M, N=V, K=d)
+        if self.audit is not None:
+            self.audit.save_hot_logits()
         o.ce_fwd_bwd(self.logits, targets, self.row_weight, S, self.loss_tok, self.logits)   # logits -> dlogits in place
         o.segment_sum(self.loss_tok, self.loss_per_sample, B, S)
         o.segment_sum(self.loss_per_sample, self.scalars[0:1], 1, B)
+        if self.audit is not None:
+            # exact replay of the audited samples; also adds the KL-distillation gradient to their hot dlogits rows
+            self.audit.forward(self.prelude[-1].out if self.prelude else self.x0, self.h_phi)
         # ---------------- backward
         self._begin_backward()
         dlogits = self.logits
@@ -408,12 +450,24 @@ class TrainEngine:
         o.gemm_wgrad(dlogits, self.hidden16, g["embed.weight"], M=V, N=d, K=M)
         o.rmsnorm_bwd(x_last, p["final_norm.weight"], self.rstd_f, self.dn16, None, self.dxa, self.dx16,
                       g["final_norm.weight"], self.partial)
-        self._grad_ready("final_norm.weight")
+        audited = self.audit is not None
+        if not audited:
+            self._grad_ready("final_norm.weight")
         dcur, dalt = self.dxa, self.dxb
         tail = self.coda if not self.dense else self.blocks
         for i, blk in enumerate(reversed(tail)):
-            self._block_bwd(blk, dcur, self.dx16, dalt, self.dx16, self.dxc)
+            self._block_bwd(blk, dcur, self.dx16, dalt, self.dx16, self.dxc, mark_ready=not audited)
             dcur, dalt = dalt, dcur
+        if audited:
+            # distillation gradient on the hot endpoint of the audited samples, then the replay's own
+            # logits / final-norm / coda backward (their weight gradients add to the hot pass's)
+            o.scatter_add_rows(dcur, self.audit.idx, self.audit.dhot_extra, self.audit.n, S * d)
+            dh_exact = self.audit.backward_head()
+            self._grad_ready("final_norm.weight")
+            for blk in reversed(self.coda):
+                pre = blk.prefix
+                self._grad_ready(f"{pre}.mlp.wd.weight", f"{pre}.mlp.wug.weight", f"{pre}.norm2.weight",
+                                 f"{pre}.attn.wo.weight", f"{pre}.attn.wqkv.weight", f"{pre}.norm1.weight")
         if not self.dense:
             # Phi backward writes dh0 into `dalt`; the router's auxiliary losses add their share
             o.macro_phi_bwd(self.prelude[-1].out if self.prelude else self.x0, dcur, self._phi_param_dict(),
@@ -424,6 +478,10 @@ class TrainEngine:
                             K=len(cfg.depth_choices))
             self._grad_ready("macro.d_gain", "macro.v", "macro.u", "macro.bias")
             dcur, dalt = dalt, dcur
+            if audited:
+                from .audit import CORE_PARAMS
+                self.audit.backward_core(dh_exact, dcur)
+                self._grad_ready(*CORE_PARAMS)
             if not tr.disable_router_aux:
                 rg = dict(r_w0=g["router.recipe_mlp.0.weight"], r_b0=g["router.recipe_mlp.0.bias"],
                           r_w2=g["router.recipe_mlp.2.weight"], r_b2=g["router.recipe_mlp.2.bias"],
@@ -459,6 +517,8 @@ class TrainEngine:
             raise ValueError(f"batch must be [{self.B}, {self.S}] int64 token ids")
         self.tokens.copy_(tokens, non_blocking=True)
         self.targets.copy_(targets, non_blocking=True)
+        if self.audit is not None:
+            self.audit.choose(self.tr.seed + 10_000 + self.global_step)
 
     def _run_step_kernels(self, optimizer: bool) -> None:
         if not self.use_cuda_graph or not optimizer or self._eager_steps_left > 0:
@@ -490,6 +550,10 @@ class TrainEngine:
         if hasattr(self.ops, "check_status"):
             self.ops.check_status()
         loss = float(vals[0]) / (self.B * self.S)          # this rank's shard
+        if self.audit is not None:
+            terms = self.audit.loss_terms(self.loss_per_sample.detach().to("cpu"))
+            loss += terms["correction"] / (self.B * self.S) + sum(terms["aux"].values())
+            self.last_audit = terms
         if not self.dense and not self.tr.disable_router_aux:
             cover = float(torch.relu(self.tr.coverage_min - self.usage_ema).square().sum()) * self.tr.lambda_cover
             loss += (float(vals[1]) + float(vals[2])) * self.world + cover

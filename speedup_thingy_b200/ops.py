@@ -136,7 +136,7 @@ class CudaOps:
 
     def rmsnorm_bwd(self, x, w, rstd, dy, dres, dx_f32, dx_bf16, dw_out, partial, *, film_gamma=None,
                     dgamma_out=None, dbeta_out=None, partial_g=None, partial_b=None, accumulate_dw: bool = False,
-                    rows: int | None = None) -> None:
+                    accumulate_film: bool = False, rows: int | None = None) -> None:
         """dx = rmsnorm_backward(dy) + dres; dw_out (+)= column sums (two-stage, deterministic)."""
         d = x.shape[-1]
         rows = rows if rows is not None else x.numel() // d
@@ -150,8 +150,8 @@ class CudaOps:
         if dw_out is not None:
             self._call("rte_colsum_partials", _ptr(partial), n_part.value, d, _ptr(dw_out), int(accumulate_dw), self.stream)
         if dgamma_out is not None:
-            self._call("rte_colsum_partials", _ptr(partial_g), n_part.value, d, _ptr(dgamma_out), int(accumulate_dw), self.stream)
-            self._call("rte_colsum_partials", _ptr(partial_b), n_part.value, d, _ptr(dbeta_out), int(accumulate_dw), self.stream)
+            self._call("rte_colsum_partials", _ptr(partial_g), n_part.value, d, _ptr(dgamma_out), int(accumulate_film), self.stream)
+            self._call("rte_colsum_partials", _ptr(partial_b), n_part.value, d, _ptr(dbeta_out), int(accumulate_film), self.stream)
 
     def ce_fwd_bwd(self, logits, targets, row_weight, S: int, loss_tok, dlogits) -> None:
         rows, V = logits.shape
@@ -234,9 +234,53 @@ class CudaOps:
     def phi_bwd_scratch_floats(B, S, d, m) -> int:
         return B * S * d + B * S * m + 3 * B * d + B * m * d + B * 3 * d * m
 
+    # ------------------------------------------------------------------ exact-audit replay helpers
+    def gather_rows(self, src, idx, dst, n: int, row_bytes: int) -> None:
+        self._call("rte_gather_rows", _ptr(src), _ptr(idx), _ptr(dst), n, row_bytes, self.stream)
+
+    def scatter_add_rows(self, dst, idx, src, n: int, row_elems: int) -> None:
+        self._call("rte_scatter_add_rows_f32", _ptr(dst), _ptr(idx), _ptr(src), n, row_elems, self.stream)
+
+    def audit_route(self, by_pass, depth, idx, rid_out, active_out, n: int, T: int) -> None:
+        self._call("rte_audit_route", _ptr(by_pass), _ptr(depth), _ptr(idx), _ptr(rid_out), _ptr(active_out), n, T, self.stream)
+
+    def colmask_mul(self, x, rid, table, S: int, out, rows: int, cols: int) -> None:
+        self._call("rte_colmask_mul_bf16", _ptr(x), _ptr(rid), _ptr(table), S, _ptr(out), rows, cols, self.stream)
+
+    def swiglu_masked_fwd(self, ug, rid, table, S: int, z, rows: int, F: int) -> None:
+        self._call("rte_swiglu_masked_fwd", _ptr(ug), _ptr(rid), _ptr(table), S, _ptr(z), rows, F, self.stream)
+
+    def swiglu_masked_bwd(self, ug, dz, rid, table, S: int, dug, rows: int, F: int) -> None:
+        self._call("rte_swiglu_masked_bwd", _ptr(ug), _ptr(dz), _ptr(rid), _ptr(table), S, _ptr(dug), rows, F, self.stream)
+
+    def scaled_residual_fwd(self, base, branch, scale, active, passthrough, out, n: int, sample_elems: int) -> None:
+        self._call("rte_scaled_residual_fwd", _ptr(base), _ptr(branch), _ptr(scale), _ptr(active), _ptr(passthrough),
+                   _ptr(out), n, sample_elems, self.stream)
+
+    def scaled_residual_bwd(self, dout, branch, scale, active, dbase, dbranch_bf16, dbranch_f32_accum, dpassthrough,
+                            dscale_partial, n: int, sample_elems: int) -> int:
+        """Returns how many per-CTA partial sums of d(scale) were written to `dscale_partial`."""
+        n_part = C.c_int32(0)
+        cap = dscale_partial.numel() if dscale_partial is not None else 0
+        self._call("rte_scaled_residual_bwd", _ptr(dout), _ptr(branch), _ptr(scale), _ptr(active), _ptr(dbase),
+                   _ptr(dbranch_bf16), _ptr(dbranch_f32_accum), _ptr(dpassthrough), _ptr(dscale_partial), cap,
+                   C.byref(n_part), n, sample_elems, self.stream)
+        return n_part.value
+
+    def macro_distill(self, hot, exact, h0, l_dir, l_rms, l_normed, l_raw, terms, dhot, n: int, S: int, d: int) -> None:
+        self._call("rte_macro_distill", _ptr(hot), _ptr(exact), _ptr(h0), l_dir, l_rms, l_normed, l_raw, _ptr(terms),
+                   _ptr(dhot), n, S, d, self.stream)
+
+    def kl_distill(self, hot_logits, exact_logits, temp, coef, idx, S: int, dlogits_hot, kl_rows, rows: int, V: int) -> None:
+        self._call("rte_kl_distill", _ptr(hot_logits), _ptr(exact_logits), temp, coef, _ptr(idx), S, _ptr(dlogits_hot),
+                   dlogits_hot.stride(0), _ptr(kl_rows), rows, V, self.stream)
+
     # ------------------------------------------------------------------ small vector ops
     def cast_bf16(self, src, dst) -> None:
         self._call("rte_cast_f32_bf16", _ptr(src), _ptr(dst), src.numel(), self.stream)
+
+    def fill_(self, dst, value: float) -> None:
+        self._call("rte_fill_f32", _ptr(dst), value, dst.numel(), self.stream)
 
     def add_(self, dst, src) -> None:
         self._call("rte_add_f32", _ptr(dst), _ptr(src), dst.numel(), self.stream)

@@ -131,7 +131,8 @@ class EmulOps:
             y_f32.view(-1, d).copy_(y)
 
     def rmsnorm_bwd(self, x, w, rstd, dy, dres, dx_f32, dx_bf16, dw_out, partial, *, film_gamma=None,
-                    dgamma_out=None, dbeta_out=None, partial_g=None, partial_b=None, accumulate_dw=False, rows=None):
+                    dgamma_out=None, dbeta_out=None, partial_g=None, partial_b=None, accumulate_dw=False,
+                    accumulate_film=False, rows=None):
         self.launches += 1
         d = x.shape[-1]
         xr = x.reshape(-1, d)
@@ -148,8 +149,8 @@ class EmulOps:
             val = (dyf * f1 * xh).sum(0)
             dw_out.copy_(val + (dw_out if accumulate_dw else 0))
         if dgamma_out is not None:
-            dgamma_out.copy_((dyf * xh * ww).sum(0) + (dgamma_out if accumulate_dw else 0))
-            dbeta_out.copy_(dyf.sum(0) + (dbeta_out if accumulate_dw else 0))
+            dgamma_out.copy_((dyf * xh * ww).sum(0) + (dgamma_out if accumulate_film else 0))
+            dbeta_out.copy_(dyf.sum(0) + (dbeta_out if accumulate_film else 0))
         if dx_f32 is not None:
             dx_f32.view(-1, d).copy_(dx)
         if dx_bf16 is not None:
@@ -325,10 +326,101 @@ class EmulOps:
     def phi_bwd_scratch_floats(B, S, d, m):
         return 8
 
+    # ---------------------------------------------------------------- exact-audit replay helpers
+    def gather_rows(self, src, idx, dst, n, row_bytes):
+        self.launches += 1
+        per = row_bytes // src.element_size()
+        dst.view(-1)[: n * per].view(n, per).copy_(src.reshape(-1, per)[idx[:n].long()])
+
+    def scatter_add_rows(self, dst, idx, src, n, row_elems):
+        self.launches += 1
+        dst.view(-1, row_elems).index_add_(0, idx[:n].long(), src.view(-1)[: n * row_elems].view(n, row_elems))
+
+    def audit_route(self, by_pass, depth, idx, rid_out, active_out, n, T):
+        self.launches += 1
+        ii = idx[:n].long()
+        rid_out.view(T, n).copy_(by_pass.view(-1, T)[ii].t())
+        active_out.view(T, n).copy_((depth[ii][None, :] > torch.arange(T)[:, None]).int())
+
+    def colmask_mul(self, x, rid, table, S, out, rows, cols):
+        self.launches += 1
+        m = table.view(-1, cols)[rid.long()].repeat_interleave(S, 0)[:rows]
+        out.view(rows, cols).copy_((x.view(rows, cols).float() * m).to(torch.bfloat16))
+
+    def swiglu_masked_fwd(self, ug, rid, table, S, z, rows, F_):
+        self.launches += 1
+        m = table.view(-1, F_)[rid.long()].repeat_interleave(S, 0)[:rows]
+        u, g = ug.view(rows, 2 * F_)[:, :F_].float(), ug.view(rows, 2 * F_)[:, F_:].float()
+        z.view(rows, F_).copy_((u * F.silu(g) * m).to(torch.bfloat16))
+
+    def swiglu_masked_bwd(self, ug, dz, rid, table, S, dug, rows, F_):
+        self.launches += 1
+        m = table.view(-1, F_)[rid.long()].repeat_interleave(S, 0)[:rows]
+        u, g = ug.view(rows, 2 * F_)[:, :F_].float(), ug.view(rows, 2 * F_)[:, F_:].float()
+        d = dz.view(rows, F_).float() * m
+        sg = torch.sigmoid(g)
+        dug.view(rows, 2 * F_)[:, :F_] = (d * g * sg).to(torch.bfloat16)
+        dug.view(rows, 2 * F_)[:, F_:] = (d * u * sg * (1 + g * (1 - sg))).to(torch.bfloat16)
+
+    def scaled_residual_fwd(self, base, branch, scale, active, passthrough, out, n, sample_elems):
+        self.launches += 1
+        res = base.view(n, -1) + float(scale) * branch.view(n, -1)
+        if active is not None:
+            res = torch.where(active.view(n, 1) != 0, res, passthrough.view(n, -1))
+        out.view(n, -1).copy_(res)
+
+    def scaled_residual_bwd(self, dout, branch, scale, active, dbase, dbranch_bf16, dbranch_f32_accum, dpassthrough,
+                            dscale_partial, n, sample_elems):
+        self.launches += 1
+        on = torch.ones(n, 1, dtype=torch.bool) if active is None else (active.view(n, 1) != 0)
+        g = dout.view(n, -1).clone()
+        s = float(scale)
+        if dscale_partial is not None:
+            dscale_partial.zero_()
+            dscale_partial[0] = (torch.where(on, g, torch.zeros_like(g)) * branch.view(n, -1)).sum()
+        if dpassthrough is not None:
+            dpassthrough.view(n, -1).add_(torch.where(on, torch.zeros_like(g), g))
+        if dbranch_bf16 is not None:
+            dbranch_bf16.view(n, -1).copy_(torch.where(on, s * g, torch.zeros_like(g)).to(torch.bfloat16))
+        if dbranch_f32_accum is not None:
+            dbranch_f32_accum.view(n, -1).add_(torch.where(on, s * g, torch.zeros_like(g)))
+        if dbase is not None:
+            dbase.view(n, -1).copy_(torch.where(on, g, torch.zeros_like(g)))
+        return 1
+
+    def macro_distill(self, hot, exact, h0, l_dir, l_rms, l_normed, l_raw, terms, dhot, n, S, d):
+        self.launches += 1
+        h = hot.view(n, S, d).detach().clone().requires_grad_(True)
+        e, z = exact.view(n, S, d), h0.view(n, S, d)
+        dp, de = h - z, e - z
+        cos = F.cosine_similarity(dp.flatten(1), de.flatten(1), dim=-1, eps=1e-8)
+        rms = lambda x: x.pow(2).mean(dim=(1, 2)).sqrt().clamp_min(1e-8)  # noqa: E731
+        diff2 = (torch.log(rms(dp)) - torch.log(rms(de))).square()
+        nrm = lambda x: x * torch.rsqrt(x.pow(2).mean(-1, keepdim=True) + 1e-5)  # noqa: E731
+        sl_n = F.smooth_l1_loss(nrm(h), nrm(e), reduction="none").sum(dim=(1, 2))
+        sl_r = F.smooth_l1_loss(h, e, reduction="none").sum(dim=(1, 2))
+        total = l_dir * (1 - cos).mean() + l_rms * diff2.mean() + (l_normed * sl_n.sum() + l_raw * sl_r.sum()) / (n * S * d)
+        total.backward()
+        terms.view(n, 4).copy_(torch.stack([1 - cos, diff2, sl_n, sl_r], dim=1).detach())
+        dhot.view(n, S, d).copy_(h.grad)
+
+    def kl_distill(self, hot_logits, exact_logits, temp, coef, idx, S, dlogits_hot, kl_rows, rows, V):
+        self.launches += 1
+        lh = torch.log_softmax(hot_logits.view(rows, V).float() / temp, -1)
+        le = torch.log_softmax(exact_logits.view(rows, V).float() / temp, -1)
+        kl_rows.view(-1)[:rows] = (le.exp() * (le - lh)).sum(-1)
+        n = rows // S
+        tgt = (idx[:n].long()[:, None] * S + torch.arange(S)[None, :]).reshape(-1)
+        cur = dlogits_hot[tgt, :V].float()
+        dlogits_hot[tgt, :V] = (cur + coef * (lh.exp() - le.exp())).to(torch.bfloat16)
+
     # ---------------------------------------------------------------- small vector ops
     def cast_bf16(self, src, dst):
         self.launches += 1
         dst.copy_(src.to(torch.bfloat16))
+
+    def fill_(self, dst, value):
+        dst.fill_(value)
 
     def add_(self, dst, src):
         dst.add_(src)

@@ -21,6 +21,12 @@ CASES = {
              recipe_count=4, macro_rank=8),
         dict(mode="recursive_macro", lr=2e-3, weight_decay=0.05, batch_size=6, seq_len=12, seed=5, fixed_depth=None,
              grad_clip_norm=0.5)),
+    "macro_audit_two_banks": (
+        dict(vocab_size=96, d_model=64, n_heads=4, d_ff=128, n_prelude=1, n_coda=1, t_max=4, depth_choices=(1, 2, 4),
+             attn_banks=2, ffn_banks=2, head_groups=4, ffn_groups=4, active_head_groups=2, active_ffn_groups=1,
+             recipe_count=6, macro_rank=8),
+        dict(mode="recursive_macro", lr=2e-3, weight_decay=0.1, batch_size=4, seq_len=16, seed=3, fixed_depth=None,
+             audit_fixed_count_per_batch=2, grad_clip_norm=1.0)),
     "dense": (
         dict(topology="dense", vocab_size=96, d_model=64, n_heads=4, d_ff=128, n_dense_layers=2),
         dict(mode="dense_exact", lr=2e-3, weight_decay=0.1, batch_size=4, seq_len=16, seed=7)),

@@ -371,3 +371,104 @@ def test_cpu_tensors_are_rejected(ops):
     with pytest.raises(RuntimeError, match="strict_cuda"):
         ops.gemm(torch.zeros(128, 64, dtype=torch.bfloat16), torch.zeros(128, 64, dtype=torch.bfloat16),
                  torch.zeros(128, 128, dtype=torch.bfloat16), M=128, N=128, K=64)
+
+
+# ------------------------------------------------------------------ exact-audit helpers
+def test_audit_distillation_terms_and_gradients(ops):
+    n, S, d, V = 3, 16, 64, 200
+    g = torch.Generator().manual_seed(77)
+    h0 = torch.randn(n, S, d, generator=g)
+    hot = (h0 + 0.3 * torch.randn(n, S, d, generator=g)).requires_grad_(True)
+    exact = h0 + 0.3 * torch.randn(n, S, d, generator=g)
+    hot_logits = _bf(torch.randn(n * S, V, generator=g) * 2)
+    exact_logits = _bf(torch.randn(n * S, V, generator=g) * 2)
+    tr = O.TrainCfg()
+    hl = hot_logits.float().view(n, S, V).requires_grad_(True)
+    aux = O.macro_distill_loss(tr, hot, exact, hl, exact_logits.float().view(n, S, V), h0)
+    sum(aux.values()).backward()
+    terms, dhot = torch.zeros(n, 4, device=DEV), torch.zeros(n * S, d, device=DEV)
+    ops.macro_distill(hot.detach().to(DEV), exact.to(DEV), h0.to(DEV), tr.lambda_delta_dir, tr.lambda_delta_rms,
+                      tr.lambda_endpoint_normed, tr.lambda_endpoint_raw, terms, dhot, n, S, d)
+    B = 7
+    idx = torch.tensor([1, 4, 6], dtype=torch.int32, device=DEV)
+    dlog = torch.zeros(B * S, V, dtype=torch.bfloat16, device=DEV)
+    kl_rows = torch.zeros(n * S, device=DEV)
+    temp = tr.distill_temperature
+    ops.kl_distill(hot_logits.to(DEV), exact_logits.to(DEV), temp, tr.lambda_kl * temp / n, idx, S, dlog, kl_rows, n * S, V)
+    torch.cuda.synchronize()
+    _close(dhot.view(n, S, d), hot.grad, 1e-3, "distill d hot")
+    t = terms.cpu()
+    assert abs(tr.lambda_delta_dir * float(t[:, 0].mean()) - float(aux["delta_dir"])) < 1e-4
+    assert abs(tr.lambda_delta_rms * float(t[:, 1].mean()) - float(aux["delta_rms"])) < 1e-4
+    assert abs(tr.lambda_endpoint_normed * float(t[:, 2].sum()) / (n * S * d) - float(aux["endpoint_normed"])) < 1e-4
+    assert abs(tr.lambda_endpoint_raw * float(t[:, 3].sum()) / (n * S * d) - float(aux["endpoint_raw"])) < 1e-4
+    assert abs(tr.lambda_kl * float(kl_rows.sum()) / n * temp * temp - float(aux["kl"])) < 1e-3 * max(1.0, float(aux["kl"]))
+    rows = (idx.cpu().long()[:, None] * S + torch.arange(S)[None]).reshape(-1)
+    _close(dlog.cpu()[rows], hl.grad.view(n * S, V), 2e-2, "KL gradient rows")
+    others = torch.ones(B * S, dtype=torch.bool)
+    others[rows] = False
+    assert float(dlog.cpu()[others].abs().max()) == 0.0
+
+
+def test_audit_mask_and_residual_helpers(ops):
+    g = torch.Generator().manual_seed(5)
+    n, S, d, F_, R = 3, 8, 64, 128, 4
+    rows = n * S
+    rid = torch.tensor([2, 0, 3], dtype=torch.int32)
+    tab = (torch.rand(R, d, generator=g) > 0.5).float() * 0.5
+    x = _bf(torch.randn(rows, d, generator=g))
+    out = torch.zeros(rows, d, dtype=torch.bfloat16, device=DEV)
+    ops.colmask_mul(x.to(DEV), rid.to(DEV), tab.to(DEV), S, out, rows, d)
+    _close(out, x.float() * tab[rid.long()].repeat_interleave(S, 0), 1e-2, "colmask")
+    ftab = (torch.rand(R, F_, generator=g) > 0.5).float()
+    ug = _bf(torch.randn(rows, 2 * F_, generator=g))
+    z = torch.zeros(rows, F_, dtype=torch.bfloat16, device=DEV)
+    ops.swiglu_masked_fwd(ug.to(DEV), rid.to(DEV), ftab.to(DEV), S, z, rows, F_)
+    m = ftab[rid.long()].repeat_interleave(S, 0)
+    ugr = ug.float().requires_grad_(True)
+    zr = ugr[:, :F_] * F.silu(ugr[:, F_:]) * m
+    _close(z, zr, 1e-2, "masked swiglu")
+    dz = _bf(torch.randn(rows, F_, generator=g))
+    zr.backward(dz.float())
+    dug = torch.zeros(rows, 2 * F_, dtype=torch.bfloat16, device=DEV)
+    ops.swiglu_masked_bwd(ug.to(DEV), dz.to(DEV), rid.to(DEV), ftab.to(DEV), S, dug, rows, F_)
+    _close(dug, ugr.grad, 1e-2, "masked swiglu backward")
+    # gather / scatter-add / routing
+    Bn = 6
+    src = torch.randn(Bn, S * d, generator=g)
+    idx = torch.tensor([0, 3, 5], dtype=torch.int32, device=DEV)
+    dst = torch.zeros(n, S * d, device=DEV)
+    ops.gather_rows(src.to(DEV), idx, dst, n, S * d * 4)
+    assert torch.equal(dst.cpu(), src[idx.cpu().long()])
+    acc = src.clone().to(DEV)
+    ops.scatter_add_rows(acc, idx, dst, n, S * d)
+    ref = src.clone()
+    ref[idx.cpu().long()] *= 2
+    _close(acc, ref, 1e-6, "scatter add")
+    by_pass = torch.randint(0, R, (Bn, 4), generator=g, dtype=torch.int32)
+    depth = torch.tensor([1, 2, 4, 4, 1, 2], dtype=torch.int32)
+    ro, ao = torch.zeros(4, n, dtype=torch.int32, device=DEV), torch.zeros(4, n, dtype=torch.int32, device=DEV)
+    ops.audit_route(by_pass.to(DEV), depth.to(DEV), idx, ro, ao, n, 4)
+    ii = idx.cpu().long()
+    assert torch.equal(ro.cpu(), by_pass[ii].t().contiguous())
+    assert torch.equal(ao.cpu(), (depth[ii][None] > torch.arange(4)[:, None]).int())
+    # scaled residual forward / backward with a frozen sample
+    base, br, pas = (torch.randn(n, S * d, generator=g) for _ in range(3))
+    sc = torch.tensor([0.7])
+    act = torch.tensor([1, 0, 1], dtype=torch.int32)
+    o2 = torch.zeros(n, S * d, device=DEV)
+    ops.scaled_residual_fwd(base.to(DEV), br.to(DEV), sc.to(DEV), act.to(DEV), pas.to(DEV), o2, n, S * d)
+    on = act.view(n, 1) != 0
+    _close(o2, torch.where(on, base + 0.7 * br, pas), 1e-6, "scaled residual")
+    dout = torch.randn(n, S * d, generator=g)
+    dbase, db32, dpas = torch.zeros(n, S * d, device=DEV), torch.ones(n, S * d, device=DEV), torch.ones(n, S * d, device=DEV)
+    db16 = torch.zeros(n, S * d, dtype=torch.bfloat16, device=DEV)
+    part = torch.zeros(64, device=DEV)
+    ops.scaled_residual_bwd(dout.to(DEV), br.to(DEV), sc.to(DEV), act.to(DEV), dbase, db16, db32, dpas, part, n, S * d)
+    torch.cuda.synchronize()
+    zero = torch.zeros_like(dout)
+    _close(dbase, torch.where(on, dout, zero), 1e-6, "d base")
+    _close(db16, torch.where(on, 0.7 * dout, zero), 1e-2, "d branch bf16")
+    _close(db32, 1 + torch.where(on, 0.7 * dout, zero), 1e-6, "d branch f32 accumulate")
+    _close(dpas, 1 + torch.where(on, zero, dout), 1e-6, "d passthrough")
+    assert abs(float(part.sum()) - float((torch.where(on, dout, zero) * br).sum())) < 1e-2
