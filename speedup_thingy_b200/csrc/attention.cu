@@ -8,6 +8,7 @@
 // 2*sec + h*HD.  Rotary pairs are ADJACENT elements (2i, 2i+1), angle = pos * 10000^(-2i/HD).
 
 #include "rte_common.cuh"
+#include "attention_mma.cuh"
 
 namespace {
 
@@ -313,10 +314,31 @@ int launch_bwd(const void* qkv, int ld, int sec, const void* y, const void* dy, 
     }                                                                          \
   } while (0)
 
+// Tensor-core path for the head sizes the mma.sync tiles cover; everything else falls through to the
+// SIMT kernels above (tiny heads of the test configurations).  Needs 16-byte aligned rows for ldmatrix.
+#define RTE_ATT_MMA_DISPATCH(FN, ...)                                          \
+  do {                                                                         \
+    if (ld_qkv % 8 == 0 && sec % 8 == 0 && ld_y % 8 == 0) {                    \
+      const int smax = S <= 64 ? 64 : S <= 128 ? 128 : 256;                    \
+      switch (head_dim * 1000 + smax) {                                        \
+        case 32064: return FN<32, 64>(__VA_ARGS__);                            \
+        case 32128: return FN<32, 128>(__VA_ARGS__);                           \
+        case 32256: return FN<32, 256>(__VA_ARGS__);                           \
+        case 64064: return FN<64, 64>(__VA_ARGS__);                            \
+        case 64128: return FN<64, 128>(__VA_ARGS__);                           \
+        case 64256: return FN<64, 256>(__VA_ARGS__);                           \
+        case 128064: return FN<128, 64>(__VA_ARGS__);                          \
+        case 128128: return FN<128, 128>(__VA_ARGS__);                         \
+        default: break;                                                        \
+      }                                                                        \
+    }                                                                          \
+  } while (0)
+
 extern "C" int rte_attn_fwd(const void* qkv, int32_t ld_qkv, int32_t sec, void* y, int32_t ld_y, float* lse,
                             int32_t B, int32_t S, int32_t n_heads, int32_t head_dim, rte_stream_t stream) {
   RTE_CHECK_ARG(qkv && y && lse && B > 0 && S > 0 && S <= 256 && n_heads > 0 && ld_qkv % 2 == 0 && sec % 2 == 0);
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  RTE_ATT_MMA_DISPATCH(attn_mma::launch_fwd, qkv, ld_qkv, sec, y, ld_y, lse, B, S, n_heads, st);
   RTE_ATT_DISPATCH(launch_fwd, qkv, ld_qkv, sec, y, ld_y, lse, B, S, n_heads, st);
 }
 
@@ -326,5 +348,6 @@ extern "C" int rte_attn_bwd(const void* qkv, int32_t ld_qkv, int32_t sec, const 
   RTE_CHECK_ARG(qkv && y && dy && lse && dqkv && B > 0 && S > 0 && S <= 256 && n_heads > 0 && ld_qkv % 2 == 0 &&
                 sec % 2 == 0 && ld_y % 2 == 0);
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  RTE_ATT_MMA_DISPATCH(attn_mma::launch_bwd, qkv, ld_qkv, sec, y, dy, ld_y, lse, dqkv, B, S, n_heads, st);
   RTE_ATT_DISPATCH(launch_bwd, qkv, ld_qkv, sec, y, dy, ld_y, lse, dqkv, B, S, n_heads, st);
 }
