@@ -103,6 +103,20 @@ class AuditReplay:
         self.partial_g, self.partial_b = e(2 * 148, d), e(2 * 148, d)
         self.P = 64
         self.part_alpha, self.part_attn, self.part_mlp = e(T * self.P), e(T * self.P), e(T * self.P)
+        # The replay runs on its own stream beside the hot pass, so the gradients it contributes to parameters the
+        # hot pass also touches (final norm, coda, tied embedding) are written to a private mirror of those slices of
+        # the flat gradient buffer and added after the join; likewise it owns a split-K workspace.
+        names = ["final_norm.weight"] + [n for n in eng.grads if n.startswith("coda.")]
+        lo = min(eng._grad_offsets[nm] for nm in names)
+        hi = max(eng._grad_offsets[nm] + -(-eng.params[nm].numel() // 64) * 64 for nm in names)
+        self.shared_range = (lo, hi)
+        self.shared_flat = e(hi - lo)
+        self.g_shared = {nm: self.shared_flat[eng._grad_offsets[nm] - lo: eng._grad_offsets[nm] - lo + eng.params[nm].numel()]
+                         .view(eng.params[nm].shape) for nm in names}
+        self.g_embed = e(*eng.params["embed.weight"].shape)
+        self.g_shared["embed.weight"] = self.g_embed
+        big = max(V * d, 2 * f * d, 3 * d * d)
+        self.ws = e(big)
 
     # ------------------------------------------------------------------ host side, once per step
     def choose(self, step_seed: int) -> None:
@@ -119,7 +133,8 @@ class AuditReplay:
         self.last_chosen = chosen
 
     # ------------------------------------------------------------------ forward
-    def forward(self, h0: torch.Tensor, h_phi: torch.Tensor) -> None:
+    def forward_replay(self, h0: torch.Tensor, h_phi: torch.Tensor) -> None:
+        """Everything of the replay's forward that needs only h0, the macro output and the routing decisions."""
         eng = self.eng
         o, cfg, p, sh = eng.ops, eng.cfg, eng.params, eng.shadow
         n, S, T, Ma, d, f, V = self.n, self.S, self.T, self.Ma, cfg.d_model, cfg.d_ff, cfg.vocab_size
@@ -160,6 +175,12 @@ class AuditReplay:
         tr, w = eng.tr, 1.0 / eng.world
         o.macro_distill(self.hot_end, self.h[T], self.h0a, tr.lambda_delta_dir * w, tr.lambda_delta_rms * w,
                         tr.lambda_endpoint_normed * w, tr.lambda_endpoint_raw * w, self.terms, self.dhot_extra, n, S, d)
+
+    def forward_losses(self) -> None:
+        """Needs the hot pass's cross entropy to be done: KL term into the hot dlogits, then the replay's own CE."""
+        eng = self.eng
+        o, cfg, tr, w = eng.ops, eng.cfg, eng.tr, 1.0 / eng.world
+        n, S, Ma, V = self.n, self.S, self.Ma, cfg.vocab_size
         temp = max(float(tr.distill_temperature), 1e-6)
         o.kl_distill(self.hot_logits, self.logits, temp, tr.lambda_kl * w * temp / n, self.idx, S, eng.logits, self.kl_rows, Ma, V)
         o.segment_sum(self.kl_rows, self.kl_sum, 1, Ma)
@@ -180,17 +201,18 @@ class AuditReplay:
         Ma, d, V = self.Ma, cfg.d_model, cfg.vocab_size
         t = self.tmp
         o.gemm(self.logits, sh["embed.weight"], t.dn16, M=Ma, N=d, K=V, b_mn=True)
-        o.gemm_wgrad(self.logits, self.hidden16, g["embed.weight"], M=V, N=d, K=Ma, accumulate=True)
+        gs = self.g_shared
+        o.gemm_wgrad(self.logits, self.hidden16, gs["embed.weight"], M=V, N=d, K=Ma, ws=self.ws)
         o.rmsnorm_bwd(self.x_last, p["final_norm.weight"], self.rstd_f, t.dn16, None, t.dxa, t.dx16,
-                      g["final_norm.weight"], t.partial, accumulate_dw=True)
+                      gs["final_norm.weight"], t.partial)
         dcur, dalt = t.dxa, t.dxb
         for blk in reversed(self.coda):
-            eng._block_bwd(blk, dcur, t.dx16, dalt, t.dx16, t.dxc, tmp=t, accumulate=True, mark_ready=False)
+            eng._block_bwd(blk, dcur, t.dx16, dalt, t.dx16, t.dxc, tmp=t, mark_ready=False, grads=gs, ws=self.ws)
             dcur, dalt = dalt, dcur
         return dcur
 
-    def backward_core(self, dh_last: torch.Tensor, dh0_hot: torch.Tensor) -> None:
-        """Backward through the t_max banked passes; adds the subset's h0 gradient into rows `idx` of dh0_hot."""
+    def backward_core(self, dh_last: torch.Tensor) -> None:
+        """Backward through the t_max banked passes (the subset's h0 gradient is folded in by `merge`)."""
         eng = self.eng
         o, cfg, p, sh, g = eng.ops, eng.cfg, eng.params, eng.shadow, eng.grads
         n, S, T, Ma, d, f, P = self.n, self.S, self.T, self.Ma, cfg.d_model, cfg.d_ff, self.P
@@ -208,11 +230,11 @@ class AuditReplay:
                                           self.d16a, None, None, self.part_mlp[t * P:(t + 1) * P], n, S * d)
             for bk in range(cfg.ffn_banks):
                 o.gemm(self.d16a, sh["core.mlp.wd"][bk], self.dz16, M=Ma, N=f, K=d)
-                o.gemm_wgrad(self.zm[t][bk], self.d16a, g["core.mlp.wd"][bk], M=f, N=d, K=Ma, accumulate=acc)
+                o.gemm_wgrad(self.zm[t][bk], self.d16a, g["core.mlp.wd"][bk], M=f, N=d, K=Ma, accumulate=acc, ws=self.ws)
                 o.swiglu_masked_bwd(self.ug[t][bk], self.dz16, rid, self.ffn_tab[bk], S, self.dug16, Ma, f)
                 o.gemm(self.dug16, sh["core.mlp.wug"][bk], self.dn_f32, M=Ma, N=d, K=2 * f, epilogue=A.EPI_F32,
                        residual=self.dn_f32 if bk > 0 else None)
-                o.gemm_wgrad(self.n2[t], self.dug16, g["core.mlp.wug"][bk], M=d, N=2 * f, K=Ma, accumulate=acc)
+                o.gemm_wgrad(self.n2[t], self.dug16, g["core.mlp.wug"][bk], M=d, N=2 * f, K=Ma, accumulate=acc, ws=self.ws)
             o.rmsnorm_bwd(self.u[t], p["core.norm2.weight"], self.rstd2[t], self.dn_f32, du, du, None,
                           g["core.norm2.weight"], self.tmp.partial, film_gamma=p["core.pass_gamma2"][t],
                           dgamma_out=g["core.pass_gamma2"][t], dbeta_out=g["core.pass_beta2"][t],
@@ -222,13 +244,13 @@ class AuditReplay:
                                   self.part_attn[t * P:(t + 1) * P], n, S * d)
             for bk in range(cfg.attn_banks):
                 o.gemm(self.d16a, sh["core.attn.wo"][bk], self.d16b, M=Ma, N=d, K=d)
-                o.gemm_wgrad(self.ym[t][bk], self.d16a, g["core.attn.wo"][bk], M=d, N=d, K=Ma, accumulate=acc)
+                o.gemm_wgrad(self.ym[t][bk], self.d16a, g["core.attn.wo"][bk], M=d, N=d, K=Ma, accumulate=acc, ws=self.ws)
                 o.colmask_mul(self.d16b, rid, self.head_tab[bk], S, self.d16b, Ma, d)
                 o.attn_bwd(self.qkv[t][bk], self.y[t][bk], self.d16b, self.lse[t][bk], self.dqkv16, B=n, S=S,
                            n_heads=cfg.n_heads, head_dim=cfg.head_dim)
                 o.gemm(self.dqkv16, sh["core.attn.wqkv"][bk], self.dn_f32, M=Ma, N=d, K=3 * d, epilogue=A.EPI_F32,
                        residual=self.dn_f32 if bk > 0 else None)
-                o.gemm_wgrad(self.n1[t], self.dqkv16, g["core.attn.wqkv"][bk], M=d, N=3 * d, K=Ma, accumulate=acc)
+                o.gemm_wgrad(self.n1[t], self.dqkv16, g["core.attn.wqkv"][bk], M=d, N=3 * d, K=Ma, accumulate=acc, ws=self.ws)
             o.rmsnorm_bwd(self.ht[t], p["core.norm1.weight"], self.rstd1[t], self.dn_f32, dht, dht, None,
                           g["core.norm1.weight"], self.tmp.partial, film_gamma=p["core.pass_gamma1"][t],
                           dgamma_out=g["core.pass_gamma1"][t], dbeta_out=g["core.pass_beta1"][t],
@@ -244,8 +266,17 @@ class AuditReplay:
         o.segment_sum(self.part_mlp, g["core.pass_mlp_scale"], T, P)
         o.segment_sum(self.part_attn, g["core.pass_attn_scale"], T, P)
         o.segment_sum(self.part_alpha, g["core.alpha_inj"].view(1), 1, T * P)
+        self.dh_first = dnext
+
+    def merge(self, dh0_hot: torch.Tensor) -> None:
+        """After the join with the hot pass: adds the replay's share of the shared gradients and of d h0."""
+        eng = self.eng
+        o, n, S, d = eng.ops, self.n, self.S, eng.cfg.d_model
+        lo, hi = self.shared_range
+        o.add_(eng.grad_flat[lo:hi], self.shared_flat)
+        o.add_(eng.grads["embed.weight"], self.g_embed)
         o.scatter_add_rows(dh0_hot, self.idx, self.dh0_acc, n, S * d)
-        o.scatter_add_rows(dh0_hot, self.idx, dnext, n, S * d)
+        o.scatter_add_rows(dh0_hot, self.idx, self.dh_first, n, S * d)
 
     # ------------------------------------------------------------------ reporting
     def loss_terms(self, hot_per_sample: torch.Tensor) -> dict[str, float]:

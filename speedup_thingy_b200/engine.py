@@ -206,6 +206,7 @@ class TrainEngine:
         for n in order:
             offsets[n] = total
             total += -(-self.params[n].numel() // 64) * 64          # 256-byte aligned slots
+        self._grad_offsets = offsets
         self.grad_flat = torch.zeros(max(total, 64), dtype=f32, device=dev)
         self.grads = {n: self.grad_flat[offsets[n]: offsets[n] + self.params[n].numel()].view(self.params[n].shape)
                       for n in self.trainable}
@@ -284,6 +285,7 @@ class TrainEngine:
                               depth_id=e(B, dtype=i32), depth=e(B, dtype=i32))
             self.router_scratch = e(A.ROUTER_MAX_R + B * (2 * hid + r + k))
         self.audit = None
+        self._side_stream = torch.cuda.Stream(device=dev) if (self.audit_k and dev.type == "cuda") else None
         if self.audit_k:
             from .audit import AuditReplay
             self.audit = AuditReplay(self, self.audit_k)
@@ -345,6 +347,21 @@ class TrainEngine:
         if self._comm_stream is not None:
             torch.cuda.current_stream(self.device).wait_stream(self._comm_stream)
 
+    # ------------------------------------------------------------------ side stream of the audit replay
+    def _on_side(self):
+        import contextlib
+        if self._side_stream is None:
+            return contextlib.nullcontext()
+        return torch.cuda.stream(self._side_stream)
+
+    def _side_wait_main(self) -> None:
+        if self._side_stream is not None:
+            self._side_stream.wait_stream(torch.cuda.current_stream(self.device))
+
+    def _main_wait_side(self) -> None:
+        if self._side_stream is not None:
+            torch.cuda.current_stream(self.device).wait_stream(self._side_stream)
+
     # ------------------------------------------------------------------ small helpers
     def _write_lr_table(self, scale: float = 1.0) -> None:
         lrs = [self.tr.lr_for(g) * scale for g in LR_GROUPS]
@@ -378,20 +395,21 @@ class TrainEngine:
 
     def _block_bwd(self, blk: _Block, dout: torch.Tensor, dout16: torch.Tensor, dx: torch.Tensor,
                    dx16: torch.Tensor | None, du: torch.Tensor, tmp: "_Temps | None" = None,
-                   accumulate: bool = False, mark_ready: bool = True) -> None:
+                   accumulate: bool = False, mark_ready: bool = True, grads: dict | None = None, ws=None) -> None:
         """dout/dout16: gradient wrt the block output (f32 and its bf16 copy); writes dx (f32) and dx16.
         `accumulate` adds the weight gradients to what is already there (second pass over shared weights)."""
-        o, cfg, p, sh, g, M = self.ops, self.cfg, self.params, self.shadow, self.grads, blk.M
+        o, cfg, p, sh, M = self.ops, self.cfg, self.params, self.shadow, blk.M
+        g = grads if grads is not None else self.grads
         t = tmp if tmp is not None else self.tmp
         d, f, pre = cfg.d_model, cfg.d_ff, blk.prefix.split("@")[0]
         ready = self._grad_ready if mark_ready else (lambda *names: None)
         # --- MLP: x_out = u + wd(up * silu(gate)),  (up | gate) = wug(norm2(u))
         o.gemm(dout16, sh[f"{pre}.mlp.wd.weight"], t.dug, M=M, N=f, K=d, b_mn=True, epilogue=A.EPI_SWIGLU_BWD,
                residual=blk.ug, pair=f)
-        o.gemm_wgrad(dout16, blk.z, g[f"{pre}.mlp.wd.weight"], M=d, N=f, K=M, accumulate=accumulate)
+        o.gemm_wgrad(dout16, blk.z, g[f"{pre}.mlp.wd.weight"], M=d, N=f, K=M, accumulate=accumulate, ws=ws)
         ready(f"{pre}.mlp.wd.weight")
         o.gemm(t.dug, sh[f"{pre}.mlp.wug.weight"], t.dn16, M=M, N=d, K=2 * f, b_mn=True)
-        o.gemm_wgrad(t.dug, blk.n2, g[f"{pre}.mlp.wug.weight"], M=2 * f, N=d, K=M, accumulate=accumulate)
+        o.gemm_wgrad(t.dug, blk.n2, g[f"{pre}.mlp.wug.weight"], M=2 * f, N=d, K=M, accumulate=accumulate, ws=ws)
         ready(f"{pre}.mlp.wug.weight")
         o.rmsnorm_bwd(blk.u, p[f"{pre}.norm2.weight"], blk.rstd2, t.dn16, dout, du, t.dy16,
                       g[f"{pre}.norm2.weight"], t.partial, accumulate_dw=accumulate)
@@ -399,12 +417,12 @@ class TrainEngine:
         du16 = t.dy16
         # --- attention: u = x + wo(attn(rope(q), rope(k), v)),  (q | k | v) = wqkv(norm1(x))
         o.gemm(du16, sh[f"{pre}.attn.wo.weight"], t.dn16, M=M, N=d, K=d, b_mn=True)
-        o.gemm_wgrad(du16, blk.y, g[f"{pre}.attn.wo.weight"], M=d, N=d, K=M, accumulate=accumulate)
+        o.gemm_wgrad(du16, blk.y, g[f"{pre}.attn.wo.weight"], M=d, N=d, K=M, accumulate=accumulate, ws=ws)
         ready(f"{pre}.attn.wo.weight")
         o.attn_bwd(blk.qkv, blk.y, t.dn16, blk.lse, t.dqkv, B=blk.B, S=blk.S, n_heads=cfg.n_heads,
                    head_dim=cfg.head_dim)
         o.gemm(t.dqkv, sh[f"{pre}.attn.wqkv.weight"], t.dn16, M=M, N=d, K=3 * d, b_mn=True)
-        o.gemm_wgrad(t.dqkv, blk.n1, g[f"{pre}.attn.wqkv.weight"], M=3 * d, N=d, K=M, accumulate=accumulate)
+        o.gemm_wgrad(t.dqkv, blk.n1, g[f"{pre}.attn.wqkv.weight"], M=3 * d, N=d, K=M, accumulate=accumulate, ws=ws)
         ready(f"{pre}.attn.wqkv.weight")
         o.rmsnorm_bwd(blk.x_in, p[f"{pre}.norm1.weight"], blk.rstd1, t.dn16, du, dx, dx16,
                       g[f"{pre}.norm1.weight"], t.partial, accumulate_dw=accumulate)
@@ -430,6 +448,11 @@ class TrainEngine:
                             cfg.macro_update_scale, self.h_phi, self.phi_rstd, self.phi_pooled, self.phi_act,
                             B=B, S=S, d=d, m=cfg.macro_rank, K=len(cfg.depth_choices))
             x = self.h_phi
+            if self.audit is not None:
+                # exact replay of the audited samples, concurrent with the rest of the hot pass
+                self._side_wait_main()
+                with self._on_side():
+                    self.audit.forward_replay(h0, self.h_phi)
             for blk in self.coda:
                 x = self._block_fwd(blk, x)
         x_last = x
@@ -441,8 +464,15 @@ class TrainEngine:
         o.segment_sum(self.loss_tok, self.loss_per_sample, B, S)
         o.segment_sum(self.loss_per_sample, self.scalars[0:1], 1, B)
         if self.audit is not None:
-            # exact replay of the audited samples; also adds the KL-distillation gradient to their hot dlogits rows
-            self.audit.forward(self.prelude[-1].out if self.prelude else self.x0, self.h_phi)
+            # the replay (started on the side stream right after Phi) now adds the KL-distillation gradient to the
+            # audited rows of the hot dlogits; the hot backward may not read them before that
+            self._side_wait_main()
+            with self._on_side():
+                self.audit.forward_losses()
+            self._main_wait_side()
+            with self._on_side():
+                self.audit_dh_exact = self.audit.backward_head()
+                self.audit.backward_core(self.audit_dh_exact)
         # ---------------- backward
         self._begin_backward()
         dlogits = self.logits
@@ -462,12 +492,6 @@ class TrainEngine:
             # distillation gradient on the hot endpoint of the audited samples, then the replay's own
             # logits / final-norm / coda backward (their weight gradients add to the hot pass's)
             o.scatter_add_rows(dcur, self.audit.idx, self.audit.dhot_extra, self.audit.n, S * d)
-            dh_exact = self.audit.backward_head()
-            self._grad_ready("final_norm.weight")
-            for blk in reversed(self.coda):
-                pre = blk.prefix
-                self._grad_ready(f"{pre}.mlp.wd.weight", f"{pre}.mlp.wug.weight", f"{pre}.norm2.weight",
-                                 f"{pre}.attn.wo.weight", f"{pre}.attn.wqkv.weight", f"{pre}.norm1.weight")
         if not self.dense:
             # Phi backward writes dh0 into `dalt`; the router's auxiliary losses add their share
             o.macro_phi_bwd(self.prelude[-1].out if self.prelude else self.x0, dcur, self._phi_param_dict(),
@@ -480,7 +504,14 @@ class TrainEngine:
             dcur, dalt = dalt, dcur
             if audited:
                 from .audit import CORE_PARAMS
-                self.audit.backward_core(dh_exact, dcur)
+                # join: the replay's backward ran beside the hot backward; fold its results in
+                self._main_wait_side()
+                self.audit.merge(dcur)
+                self._grad_ready("final_norm.weight")
+                for blk in reversed(self.coda):
+                    pre = blk.prefix
+                    self._grad_ready(f"{pre}.mlp.wd.weight", f"{pre}.mlp.wug.weight", f"{pre}.norm2.weight",
+                                     f"{pre}.attn.wo.weight", f"{pre}.attn.wqkv.weight", f"{pre}.norm1.weight")
                 self._grad_ready(*CORE_PARAMS)
             if not tr.disable_router_aux:
                 rg = dict(r_w0=g["router.recipe_mlp.0.weight"], r_b0=g["router.recipe_mlp.0.bias"],

@@ -101,14 +101,17 @@ class CudaOps:
         return max(want, 1)
 
     def gemm_wgrad(self, a_t, b_t, out, *, M: int, N: int, K: int, accumulate: bool = False,
-                   lda: int | None = None, ldb: int | None = None) -> None:
+                   lda: int | None = None, ldb: int | None = None, ws=None) -> None:
         """out f32 [M,N] (+)= a_t^T @ b_t where a_t is stored [K,M] and b_t is stored [K,N]
         (both MN-major for the tensor core), split along K across SMs and reduced in fixed order."""
         splits = self.pick_splits(M, N, K)
         if splits == 1 and not accumulate:
             self.gemm(a_t, b_t, out, M=M, N=N, K=K, a_mn=True, b_mn=True, epilogue=A.EPI_F32, lda=lda, ldb=ldb, ldc=N)
             return
-        ws = self.split_workspace(splits * M * N)
+        if ws is None:
+            ws = self.split_workspace(splits * M * N)
+        elif ws.numel() < splits * M * N:
+            raise A.RteError("split-K workspace too small")
         self.gemm(a_t, b_t, ws, M=M, N=N, K=K, a_mn=True, b_mn=True, epilogue=A.EPI_F32, splits=splits,
                   split_stride=M * N, lda=lda, ldb=ldb, ldc=N)
         self.reduce_splits(ws, splits, M * N, M * N, out, accumulate)

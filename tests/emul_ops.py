@@ -92,7 +92,7 @@ class EmulOps:
             out[:, :f] = (acc * gate * sg).to(torch.bfloat16)
             out[:, f:] = (acc * up * sg * (1 + gate * (1 - sg))).to(torch.bfloat16)
 
-    def gemm_wgrad(self, a_t, b_t, out, *, M, N, K, accumulate=False, lda=None, ldb=None):
+    def gemm_wgrad(self, a_t, b_t, out, *, M, N, K, accumulate=False, lda=None, ldb=None, ws=None):
         self.launches += 1
         res = a_t.reshape(K, -1)[:, :M].float().t() @ b_t.reshape(K, -1)[:, :N].float()
         if accumulate:
