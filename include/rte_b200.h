@@ -122,12 +122,17 @@ int rte_colsum_partials(const float* partial, int32_t n_rows, int32_t d, float* 
  * embedding (base 10000, positions 0..S-1) applied to q and k inside the kernel; softmax scale
  * 1/sqrt(head_dim).  y bf16 [B*S, d]; lse f32 [B, H, S] saved for backward.
  * n_heads may be fewer than d/head_dim when only the first `n_heads` heads of a packed buffer
- * exist (banked attention, layers.py:702-728): row stride stays `ld_qkv`, section stride `sec`.  */
+ * exist (banked attention, layers.py:702-728): row stride stays `ld_qkv`, section stride `sec`.
+ * rope_table (optional, may be NULL): f32 [S, head_dim/2, 2] = (cos, sin) of pos * 10000^(-2i/head_dim) as
+ * written by rte_rope_table (the reference's cached buffers, layers.py:37-44); without it the kernels compute
+ * the angles themselves.                                                                                       */
+int rte_rope_table(float* out, int32_t S, int32_t head_dim, rte_stream_t stream);
 int rte_attn_fwd(const void* qkv, int32_t ld_qkv, int32_t sec, void* y, int32_t ld_y, float* lse,
-                 int32_t B, int32_t S, int32_t n_heads, int32_t head_dim, rte_stream_t stream);
-int rte_attn_bwd(const void* qkv, int32_t ld_qkv, int32_t sec, const void* y, const void* dy, int32_t ld_y,
-                 const float* lse, void* dqkv, int32_t B, int32_t S, int32_t n_heads, int32_t head_dim,
+                 const float* rope_table, int32_t B, int32_t S, int32_t n_heads, int32_t head_dim,
                  rte_stream_t stream);
+int rte_attn_bwd(const void* qkv, int32_t ld_qkv, int32_t sec, const void* y, const void* dy, int32_t ld_y,
+                 const float* lse, void* dqkv, const float* rope_table, int32_t B, int32_t S, int32_t n_heads,
+                 int32_t head_dim, rte_stream_t stream);
 
 /* ------------- per-token cross entropy + its gradient (models.py:73-75; training.py:1381-1385)
  * logits bf16 [rows, V] (ld = ldl).  loss_tok f32 [rows] = logsumexp - logit[target].
@@ -168,7 +173,7 @@ int rte_router_fwd(const float* h0, const rte_router_weights* w, const int32_t* 
                    int32_t K, int32_t T, int32_t fixed_recipe, int32_t fixed_depth_id, rte_stream_t stream);
 /* aux[0] = lambda_load * (R * sum_r mean_B(p_r)^2 - 1), aux[1] = lambda_depth * mean_B E[depth]
  * (metrics.py:103-111).  Backward of both through the two MLPs: weight/bias grads (f32, overwritten)
- * and dh0[b,s,:] += dpooled[b,:] / S.  scratch f32 >= RTE_ROUTER_MAX_R + B*(2*hid + R + K).      */
+ * and dh0[b,s,:] += dpooled[b,:] / S.  scratch f32 >= RTE_ROUTER_MAX_R + B*(2*hid + R + K + d).      */
 typedef struct rte_router_grads {
   float *r_w0, *r_b0, *r_w2, *r_b2, *d_w0, *d_b0, *d_w2, *d_b2;
 } rte_router_grads;

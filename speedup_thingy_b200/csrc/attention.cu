@@ -27,7 +27,8 @@ __device__ __forceinline__ float rope_inv_freq(int pair, int hd) {
 
 // Loads rows [0,S) of one head's slice into smem (bf16), optionally applying the rotary embedding.
 template <int HD, bool ROPE>
-__device__ __forceinline__ void load_head(const __nv_bfloat16* __restrict__ src, int ld, int S, __nv_bfloat16* dst) {
+__device__ __forceinline__ void load_head(const __nv_bfloat16* __restrict__ src, int ld, int S, __nv_bfloat16* dst,
+                                          const float* __restrict__ rope = nullptr) {
   constexpr int LDS = AttCfg<HD>::LDS;
   for (int idx = threadIdx.x; idx < S * (HD / 2); idx += blockDim.x) {
     const int s = idx / (HD / 2), pr = idx % (HD / 2);
@@ -35,7 +36,7 @@ __device__ __forceinline__ void load_head(const __nv_bfloat16* __restrict__ src,
     float2 v = __bfloat1622float2(in);
     if (ROPE) {
       float sn, cs;
-      sincosf((float)s * rope_inv_freq(pr, HD), &sn, &cs);
+      attn_mma::rope_cs(rope, s, pr, HD, cs, sn);
       v = make_float2(v.x * cs - v.y * sn, v.y * cs + v.x * sn);
     }
     *reinterpret_cast<__nv_bfloat162*>(dst + s * LDS + 2 * pr) = __floats2bfloat162_rn(v.x, v.y);
@@ -58,7 +59,7 @@ __device__ __forceinline__ float dot_rows(const __nv_bfloat16* a, const __nv_bfl
 template <int HD, int SMAX>
 __global__ void __launch_bounds__(ATT_THREADS)
 attn_fwd_kernel(const __nv_bfloat16* __restrict__ qkv, int ld, int sec, __nv_bfloat16* __restrict__ y, int ldy,
-                float* __restrict__ lse, int S, int H) {
+                float* __restrict__ lse, const float* __restrict__ rope, int S, int H) {
   constexpr int LDS = AttCfg<HD>::LDS, DPL = AttCfg<HD>::DPL, NT = SMAX / 32;
   extern __shared__ __align__(16) uint8_t smraw[];
   __nv_bfloat16* sq = reinterpret_cast<__nv_bfloat16*>(smraw);
@@ -66,8 +67,8 @@ attn_fwd_kernel(const __nv_bfloat16* __restrict__ qkv, int ld, int sec, __nv_bfl
   __nv_bfloat16* sv = sk + SMAX * LDS;
   const int b = blockIdx.x / H, h = blockIdx.x % H;
   const __nv_bfloat16* base = qkv + (size_t)b * S * ld + h * HD;
-  load_head<HD, true>(base, ld, S, sq);
-  load_head<HD, true>(base + sec, ld, S, sk);
+  load_head<HD, true>(base, ld, S, sq, rope);
+  load_head<HD, true>(base + sec, ld, S, sk, rope);
   load_head<HD, false>(base + 2 * sec, ld, S, sv);
   __syncthreads();
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -117,14 +118,15 @@ attn_fwd_kernel(const __nv_bfloat16* __restrict__ qkv, int ld, int sec, __nv_bfl
 
 // Inverse rotary embedding of a gradient vector held `DPL` consecutive dims per lane.
 template <int HD>
-__device__ __forceinline__ void unrope_inplace(float (&g)[AttCfg<HD>::DPL], int c0, int pos, int lane) {
+__device__ __forceinline__ void unrope_inplace(float (&g)[AttCfg<HD>::DPL], int c0, int pos, int lane,
+                                               const float* __restrict__ rope) {
   constexpr int DPL = AttCfg<HD>::DPL;
   if constexpr (DPL >= 2) {
     if (c0 < HD) {
 #pragma unroll
       for (int c = 0; c < DPL; c += 2) {
         float sn, cs;
-        sincosf((float)pos * rope_inv_freq((c0 + c) / 2, HD), &sn, &cs);
+        attn_mma::rope_cs(rope, pos, (c0 + c) / 2, HD, cs, sn);
         const float a = g[c], bq = g[c + 1];
         g[c] = a * cs + bq * sn;
         g[c + 1] = -a * sn + bq * cs;
@@ -134,7 +136,7 @@ __device__ __forceinline__ void unrope_inplace(float (&g)[AttCfg<HD>::DPL], int 
     const float other = __shfl_xor_sync(0xffffffffu, g[0], 1);
     if (c0 < HD) {
       float sn, cs;
-      sincosf((float)pos * rope_inv_freq(c0 / 2, HD), &sn, &cs);
+      attn_mma::rope_cs(rope, pos, c0 / 2, HD, cs, sn);
       g[0] = (c0 & 1) ? (-other * sn + g[0] * cs) : (g[0] * cs + other * sn);
     }
   }
@@ -145,7 +147,7 @@ template <int HD, int SMAX>
 __global__ void __launch_bounds__(ATT_THREADS)
 attn_bwd_kernel(const __nv_bfloat16* __restrict__ qkv, int ld, int sec, const __nv_bfloat16* __restrict__ y,
                 const __nv_bfloat16* __restrict__ dy, int ldy, const float* __restrict__ lse,
-                __nv_bfloat16* __restrict__ dqkv, int S, int H) {
+                __nv_bfloat16* __restrict__ dqkv, const float* __restrict__ rope, int S, int H) {
   constexpr int LDS = AttCfg<HD>::LDS, DPL = AttCfg<HD>::DPL, NT = SMAX / 32;
   extern __shared__ __align__(16) uint8_t smraw[];
   __nv_bfloat16* sq = reinterpret_cast<__nv_bfloat16*>(smraw);
@@ -156,8 +158,8 @@ attn_bwd_kernel(const __nv_bfloat16* __restrict__ qkv, int ld, int sec, const __
   float* sD = slse + SMAX;
   const int b = blockIdx.x / H, h = blockIdx.x % H;
   const __nv_bfloat16* base = qkv + (size_t)b * S * ld + h * HD;
-  load_head<HD, true>(base, ld, S, sq);
-  load_head<HD, true>(base + sec, ld, S, sk);
+  load_head<HD, true>(base, ld, S, sq, rope);
+  load_head<HD, true>(base + sec, ld, S, sk, rope);
   load_head<HD, false>(base + 2 * sec, ld, S, sv);
   load_head<HD, false>(dy + (size_t)b * S * ldy + h * HD, ldy, S, sdo);
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -206,7 +208,7 @@ attn_bwd_kernel(const __nv_bfloat16* __restrict__ qkv, int ld, int sec, const __
     }
 #pragma unroll
     for (int c = 0; c < DPL; ++c) acc[c] *= scale;
-    unrope_inplace<HD>(acc, c0, i, lane);
+    unrope_inplace<HD>(acc, c0, i, lane, rope);
     if (c0 < HD) {
 #pragma unroll
       for (int c = 0; c < DPL; ++c) dbase[(size_t)i * ld + c0 + c] = __float2bfloat16_rn(acc[c]);
@@ -249,7 +251,7 @@ attn_bwd_kernel(const __nv_bfloat16* __restrict__ qkv, int ld, int sec, const __
     }
 #pragma unroll
     for (int c = 0; c < DPL; ++c) ak[c] *= scale;
-    unrope_inplace<HD>(ak, c0, j, lane);
+    unrope_inplace<HD>(ak, c0, j, lane, rope);
     if (c0 < HD) {
 #pragma unroll
       for (int c = 0; c < DPL; ++c) {
@@ -261,7 +263,7 @@ attn_bwd_kernel(const __nv_bfloat16* __restrict__ qkv, int ld, int sec, const __
 }
 
 template <int HD, int SMAX>
-int launch_fwd(const void* qkv, int ld, int sec, void* y, int ldy, float* lse, int B, int S, int H, cudaStream_t st) {
+int launch_fwd(const void* qkv, int ld, int sec, void* y, int ldy, float* lse, const float* rope, int B, int S, int H, cudaStream_t st) {
   constexpr size_t smem = (size_t)3 * SMAX * AttCfg<HD>::LDS * 2;
   static bool set = false;
   if (!set && smem > 48 * 1024) {
@@ -270,13 +272,13 @@ int launch_fwd(const void* qkv, int ld, int sec, void* y, int ldy, float* lse, i
     set = true;
   }
   attn_fwd_kernel<HD, SMAX><<<B * H, ATT_THREADS, smem, st>>>(reinterpret_cast<const __nv_bfloat16*>(qkv), ld, sec,
-      reinterpret_cast<__nv_bfloat16*>(y), ldy, lse, S, H);
+      reinterpret_cast<__nv_bfloat16*>(y), ldy, lse, rope, S, H);
   RTE_LAUNCH_CHECK();
   return RTE_OK;
 }
 template <int HD, int SMAX>
 int launch_bwd(const void* qkv, int ld, int sec, const void* y, const void* dy, int ldy, const float* lse, void* dqkv,
-               int B, int S, int H, cudaStream_t st) {
+               const float* rope, int B, int S, int H, cudaStream_t st) {
   constexpr size_t smem = (size_t)4 * SMAX * AttCfg<HD>::LDS * 2 + (size_t)2 * SMAX * 4;
   static bool set = false;
   if (!set && smem > 48 * 1024) {
@@ -286,9 +288,18 @@ int launch_bwd(const void* qkv, int ld, int sec, const void* y, const void* dy, 
   }
   attn_bwd_kernel<HD, SMAX><<<B * H, ATT_THREADS, smem, st>>>(reinterpret_cast<const __nv_bfloat16*>(qkv), ld, sec,
       reinterpret_cast<const __nv_bfloat16*>(y), reinterpret_cast<const __nv_bfloat16*>(dy), ldy, lse,
-      reinterpret_cast<__nv_bfloat16*>(dqkv), S, H);
+      reinterpret_cast<__nv_bfloat16*>(dqkv), rope, S, H);
   RTE_LAUNCH_CHECK();
   return RTE_OK;
+}
+
+__global__ void rope_table_kernel(float* __restrict__ out, int S, int hd) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= S * (hd / 2)) return;
+  float sn, cs;
+  sincosf((float)(i / (hd / 2)) * rope_inv_freq(i % (hd / 2), hd), &sn, &cs);
+  out[2 * i] = cs;
+  out[2 * i + 1] = sn;
 }
 
 }  // namespace
@@ -334,20 +345,29 @@ int launch_bwd(const void* qkv, int ld, int sec, const void* y, const void* dy, 
     }                                                                          \
   } while (0)
 
+extern "C" int rte_rope_table(float* out, int32_t S, int32_t head_dim, rte_stream_t stream) {
+  RTE_CHECK_ARG(out && S > 0 && head_dim > 0 && head_dim % 2 == 0);
+  const int n = S * (head_dim / 2);
+  rope_table_kernel<<<rte::ceil_div(n, 256), 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(out, S, head_dim);
+  RTE_LAUNCH_CHECK();
+  return RTE_OK;
+}
+
 extern "C" int rte_attn_fwd(const void* qkv, int32_t ld_qkv, int32_t sec, void* y, int32_t ld_y, float* lse,
-                            int32_t B, int32_t S, int32_t n_heads, int32_t head_dim, rte_stream_t stream) {
+                            const float* rope_table, int32_t B, int32_t S, int32_t n_heads, int32_t head_dim,
+                            rte_stream_t stream) {
   RTE_CHECK_ARG(qkv && y && lse && B > 0 && S > 0 && S <= 256 && n_heads > 0 && ld_qkv % 2 == 0 && sec % 2 == 0);
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
-  RTE_ATT_MMA_DISPATCH(attn_mma::launch_fwd, qkv, ld_qkv, sec, y, ld_y, lse, B, S, n_heads, st);
-  RTE_ATT_DISPATCH(launch_fwd, qkv, ld_qkv, sec, y, ld_y, lse, B, S, n_heads, st);
+  RTE_ATT_MMA_DISPATCH(attn_mma::launch_fwd, qkv, ld_qkv, sec, y, ld_y, lse, rope_table, B, S, n_heads, st);
+  RTE_ATT_DISPATCH(launch_fwd, qkv, ld_qkv, sec, y, ld_y, lse, rope_table, B, S, n_heads, st);
 }
 
 extern "C" int rte_attn_bwd(const void* qkv, int32_t ld_qkv, int32_t sec, const void* y, const void* dy, int32_t ld_y,
-                            const float* lse, void* dqkv, int32_t B, int32_t S, int32_t n_heads, int32_t head_dim,
-                            rte_stream_t stream) {
+                            const float* lse, void* dqkv, const float* rope_table, int32_t B, int32_t S, int32_t n_heads,
+                            int32_t head_dim, rte_stream_t stream) {
   RTE_CHECK_ARG(qkv && y && dy && lse && dqkv && B > 0 && S > 0 && S <= 256 && n_heads > 0 && ld_qkv % 2 == 0 &&
                 sec % 2 == 0 && ld_y % 2 == 0);
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
-  RTE_ATT_MMA_DISPATCH(attn_mma::launch_bwd, qkv, ld_qkv, sec, y, dy, ld_y, lse, dqkv, B, S, n_heads, st);
-  RTE_ATT_DISPATCH(launch_bwd, qkv, ld_qkv, sec, y, dy, ld_y, lse, dqkv, B, S, n_heads, st);
+  RTE_ATT_MMA_DISPATCH(attn_mma::launch_bwd, qkv, ld_qkv, sec, y, dy, ld_y, lse, dqkv, rope_table, B, S, n_heads, st);
+  RTE_ATT_DISPATCH(launch_bwd, qkv, ld_qkv, sec, y, dy, ld_y, lse, dqkv, rope_table, B, S, n_heads, st);
 }

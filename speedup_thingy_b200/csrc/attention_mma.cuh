@@ -31,11 +31,20 @@ __device__ __forceinline__ void ldsm_x2_trans(uint32_t& b0, uint32_t& b1, const 
 __device__ __forceinline__ uint32_t ld32(const __nv_bfloat16* p) { return *reinterpret_cast<const uint32_t*>(p); }
 
 __device__ __forceinline__ float inv_freq(int pair, int hd) { return 1.0f / powf(10000.0f, (float)(2 * pair) / (float)hd); }
+// cos/sin of position `pos`, rotary pair `pair`: from the caller's table [S, hd/2, 2] when given, else computed.
+__device__ __forceinline__ void rope_cs(const float* __restrict__ table, int pos, int pair, int hd, float& cs, float& sn) {
+  if (table != nullptr) {
+    const float2 v = *reinterpret_cast<const float2*>(table + ((size_t)pos * (hd / 2) + pair) * 2);
+    cs = v.x; sn = v.y;
+  } else {
+    sincosf((float)pos * inv_freq(pair, hd), &sn, &cs);
+  }
+}
 
 // rows [0, n_rows) of one head -> smem (bf16, row stride HD + 8); rows in [n_rows, pad_rows) are zeroed.
 template <int HD, bool ROPE>
 __device__ __forceinline__ void load_rows(const __nv_bfloat16* __restrict__ src, int ld, int n_rows, int pad_rows,
-                                          __nv_bfloat16* dst) {
+                                          __nv_bfloat16* dst, const float* __restrict__ rope = nullptr) {
   constexpr int LDS = HD + 8;
   for (int idx = threadIdx.x; idx < pad_rows * (HD / 2); idx += blockDim.x) {
     const int s = idx / (HD / 2), pr = idx % (HD / 2);
@@ -44,7 +53,7 @@ __device__ __forceinline__ void load_rows(const __nv_bfloat16* __restrict__ src,
       v = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(src + (size_t)s * ld + 2 * pr));
       if (ROPE) {
         float sn, cs;
-        sincosf((float)s * inv_freq(pr, HD), &sn, &cs);
+        rope_cs(rope, s, pr, HD, cs, sn);
         v = make_float2(v.x * cs - v.y * sn, v.y * cs + v.x * sn);
       }
     }
@@ -83,7 +92,7 @@ __device__ __forceinline__ void rowrow_tile(float (&acc)[4], const uint32_t (&a)
 template <int HD, int SMAX>
 __global__ void __launch_bounds__(NTHR)
 fwd_kernel(const __nv_bfloat16* __restrict__ qkv, int ld, int sec, __nv_bfloat16* __restrict__ y, int ldy,
-           float* __restrict__ lse, int S, int H) {
+           float* __restrict__ lse, const float* __restrict__ rope, int S, int H) {
   constexpr int LDS = HD + 8, KT = SMAX / 8;
   extern __shared__ __align__(16) uint8_t smraw[];
   __nv_bfloat16* sq = reinterpret_cast<__nv_bfloat16*>(smraw);       // [QB][LDS]
@@ -102,13 +111,13 @@ fwd_kernel(const __nv_bfloat16* __restrict__ qkv, int ld, int sec, __nv_bfloat16
       if (s < S) {
         v = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(base + (size_t)s * ld + 2 * pr));
         float sn, cs;
-        sincosf((float)s * inv_freq(pr, HD), &sn, &cs);
+        rope_cs(rope, s, pr, HD, cs, sn);
         v = make_float2(v.x * cs - v.y * sn, v.y * cs + v.x * sn);
       }
       *reinterpret_cast<__nv_bfloat162*>(sq + r * LDS + 2 * pr) = __floats2bfloat162_rn(v.x, v.y);
     }
   }
-  load_rows<HD, true>(base + sec, ld, kv_rows, kv_pad, sk);
+  load_rows<HD, true>(base + sec, ld, kv_rows, kv_pad, sk, rope);
   load_rows<HD, false>(base + 2 * sec, ld, kv_rows, kv_pad, sv);
   __syncthreads();
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, g = lane >> 2, t = lane & 3;
@@ -185,9 +194,9 @@ fwd_kernel(const __nv_bfloat16* __restrict__ qkv, int ld, int sec, __nv_bfloat16
 }
 
 // ------------------------------------------------------------------ backward
-__device__ __forceinline__ void unrope_pair(float& a, float& b, int pos, int pair, int hd) {
+__device__ __forceinline__ void unrope_pair(float& a, float& b, int pos, int pair, int hd, const float* __restrict__ rope) {
   float sn, cs;
-  sincosf((float)pos * inv_freq(pair, hd), &sn, &cs);
+  rope_cs(rope, pos, pair, hd, cs, sn);
   const float x = a, y = b;
   a = x * cs + y * sn;
   b = -x * sn + y * cs;
@@ -197,7 +206,7 @@ template <int HD, int SMAX>
 __global__ void __launch_bounds__(NTHR)
 bwd_kernel(const __nv_bfloat16* __restrict__ qkv, int ld, int sec, const __nv_bfloat16* __restrict__ y,
            const __nv_bfloat16* __restrict__ dy, int ldy, const float* __restrict__ lse,
-           __nv_bfloat16* __restrict__ dqkv, int S, int H) {
+           __nv_bfloat16* __restrict__ dqkv, const float* __restrict__ rope, int S, int H) {
   constexpr int LDS = HD + 8;
   extern __shared__ __align__(16) uint8_t smraw[];
   __nv_bfloat16* sq = reinterpret_cast<__nv_bfloat16*>(smraw);
@@ -209,8 +218,8 @@ bwd_kernel(const __nv_bfloat16* __restrict__ qkv, int ld, int sec, const __nv_bf
   const int b = blockIdx.x / H, h = blockIdx.x % H, blk0 = blockIdx.y * QB;
   const int s_pad = min(SMAX, (S + 15) & ~15);
   const __nv_bfloat16* base = qkv + (size_t)b * S * ld + h * HD;
-  load_rows<HD, true>(base, ld, S, s_pad, sq);
-  load_rows<HD, true>(base + sec, ld, S, s_pad, sk);
+  load_rows<HD, true>(base, ld, S, s_pad, sq, rope);
+  load_rows<HD, true>(base + sec, ld, S, s_pad, sk, rope);
   load_rows<HD, false>(base + 2 * sec, ld, S, s_pad, sv);
   load_rows<HD, false>(dy + (size_t)b * S * ldy + h * HD, ldy, S, s_pad, sdo);
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, g = lane >> 2, t = lane & 3;
@@ -267,8 +276,8 @@ bwd_kernel(const __nv_bfloat16* __restrict__ qkv, int ld, int sec, const __nv_bf
     for (int nd = 0; nd < HD / 8; ++nd) {
       const int pair = nd * 4 + t;
       float a0 = dq[nd][0] * scale, a1 = dq[nd][1] * scale, b0 = dq[nd][2] * scale, b1 = dq[nd][3] * scale;
-      unrope_pair(a0, a1, row_a, pair, HD);
-      unrope_pair(b0, b1, row_b, pair, HD);
+      unrope_pair(a0, a1, min(row_a, S - 1), pair, HD, rope);
+      unrope_pair(b0, b1, min(row_b, S - 1), pair, HD, rope);
       if (row_a < S) *reinterpret_cast<__nv_bfloat162*>(dbase + (size_t)row_a * ld + nd * 8 + 2 * t) = __floats2bfloat162_rn(a0, a1);
       if (row_b < S) *reinterpret_cast<__nv_bfloat162*>(dbase + (size_t)row_b * ld + nd * 8 + 2 * t) = __floats2bfloat162_rn(b0, b1);
     }
@@ -321,8 +330,8 @@ bwd_kernel(const __nv_bfloat16* __restrict__ qkv, int ld, int sec, const __nv_bf
     for (int nd = 0; nd < HD / 8; ++nd) {
       const int pair = nd * 4 + t;
       float a0 = dk[nd][0] * scale, a1 = dk[nd][1] * scale, b0 = dk[nd][2] * scale, b1 = dk[nd][3] * scale;
-      unrope_pair(a0, a1, row_a, pair, HD);
-      unrope_pair(b0, b1, row_b, pair, HD);
+      unrope_pair(a0, a1, min(row_a, S - 1), pair, HD, rope);
+      unrope_pair(b0, b1, min(row_b, S - 1), pair, HD, rope);
       if (row_a < S) {
         *reinterpret_cast<__nv_bfloat162*>(dbase + (size_t)row_a * ld + sec + nd * 8 + 2 * t) = __floats2bfloat162_rn(a0, a1);
         *reinterpret_cast<__nv_bfloat162*>(dbase + (size_t)row_a * ld + 2 * sec + nd * 8 + 2 * t) = __floats2bfloat162_rn(dv[nd][0], dv[nd][1]);
@@ -336,7 +345,7 @@ bwd_kernel(const __nv_bfloat16* __restrict__ qkv, int ld, int sec, const __nv_bf
 }
 
 template <int HD, int SMAX>
-int launch_fwd(const void* qkv, int ld, int sec, void* y, int ldy, float* lse, int B, int S, int H, cudaStream_t st) {
+int launch_fwd(const void* qkv, int ld, int sec, void* y, int ldy, float* lse, const float* rope, int B, int S, int H, cudaStream_t st) {
   constexpr int smem = (QB + 2 * SMAX) * (HD + 8) * 2;
   static bool set = false;
   if (!set && smem > 48 * 1024) {
@@ -344,14 +353,14 @@ int launch_fwd(const void* qkv, int ld, int sec, void* y, int ldy, float* lse, i
     set = true;
   }
   fwd_kernel<HD, SMAX><<<dim3(B * H, rte::ceil_div(S, QB)), NTHR, smem, st>>>(
-      reinterpret_cast<const __nv_bfloat16*>(qkv), ld, sec, reinterpret_cast<__nv_bfloat16*>(y), ldy, lse, S, H);
+      reinterpret_cast<const __nv_bfloat16*>(qkv), ld, sec, reinterpret_cast<__nv_bfloat16*>(y), ldy, lse, rope, S, H);
   RTE_LAUNCH_CHECK();
   return RTE_OK;
 }
 
 template <int HD, int SMAX>
 int launch_bwd(const void* qkv, int ld, int sec, const void* y, const void* dy, int ldy, const float* lse, void* dqkv,
-               int B, int S, int H, cudaStream_t st) {
+               const float* rope, int B, int S, int H, cudaStream_t st) {
   constexpr int smem = 4 * SMAX * (HD + 8) * 2 + 2 * SMAX * 4;
   static bool set = false;
   if (!set && smem > 48 * 1024) {
@@ -360,7 +369,7 @@ int launch_bwd(const void* qkv, int ld, int sec, const void* y, const void* dy, 
   }
   bwd_kernel<HD, SMAX><<<dim3(B * H, rte::ceil_div(S, QB)), NTHR, smem, st>>>(
       reinterpret_cast<const __nv_bfloat16*>(qkv), ld, sec, reinterpret_cast<const __nv_bfloat16*>(y),
-      reinterpret_cast<const __nv_bfloat16*>(dy), ldy, lse, reinterpret_cast<__nv_bfloat16*>(dqkv), S, H);
+      reinterpret_cast<const __nv_bfloat16*>(dy), ldy, lse, reinterpret_cast<__nv_bfloat16*>(dqkv), rope, S, H);
   RTE_LAUNCH_CHECK();
   return RTE_OK;
 }

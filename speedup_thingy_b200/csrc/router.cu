@@ -19,45 +19,6 @@ pool_kernel(const float* __restrict__ h0, float* __restrict__ pooled, int S, int
   pooled[(size_t)b * d + c] = acc / (float)S;
 }
 
-// hidden_pre[j] = b0[j] + W0[j,:] . x ; logits[r] = b2[r] + W2[r,:] . silu(hidden_pre)
-// Each warp owns four rows at a time and reads them as float4, so sixteen independent 16-byte loads are in
-// flight per lane before the first reduction (the matrices come from L2; latency, not bandwidth, is the cost).
-__device__ void mlp_forward(const float* __restrict__ w0, const float* __restrict__ b0, const float* __restrict__ w2,
-                            const float* __restrict__ b2, const float* xs, float* hs, float* pre_out, float* logits,
-                            int d, int hid, int nout) {
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  const int d4 = d >> 2;
-  const float4* xs4 = reinterpret_cast<const float4*>(xs);
-  for (int j0 = warp * 4; j0 < hid; j0 += (NTHR / 32) * 4) {
-    float acc[4] = {0.f, 0.f, 0.f, 0.f};
-#pragma unroll 4
-    for (int c = lane; c < d4; c += 32) {
-      const float4 x = xs4[c];
-#pragma unroll
-      for (int r = 0; r < 4; ++r) {
-        if (j0 + r < hid) {
-          const float4 w = reinterpret_cast<const float4*>(w0 + (size_t)(j0 + r) * d)[c];
-          acc[r] += w.x * x.x + w.y * x.y + w.z * x.z + w.w * x.w;
-        }
-      }
-    }
-#pragma unroll
-    for (int r = 0; r < 4; ++r) {
-      const float v = rte::warp_sum(acc[r]);
-      if (lane == 0 && j0 + r < hid) { const float t = v + b0[j0 + r]; pre_out[j0 + r] = t; hs[j0 + r] = rte::silu_f(t); }
-    }
-  }
-  __syncthreads();
-  for (int r = warp; r < nout; r += NTHR / 32) {
-    float acc = 0.f;
-#pragma unroll 4
-    for (int j = lane; j < hid; j += 32) acc += w2[(size_t)r * hid + j] * hs[j];
-    acc = rte::warp_sum(acc);
-    if (lane == 0) logits[r] = acc + b2[r];
-  }
-  __syncthreads();
-}
-
 __device__ __forceinline__ int argmax_lowest(const float* v, int n) {
   int best = 0;
   for (int i = 1; i < n; ++i) if (v[i] > v[best]) best = i;   // strict '>' keeps the lowest index on ties
@@ -72,18 +33,70 @@ __device__ __forceinline__ void softmax_small(const float* logits, float* probs,
   for (int i = 0; i < n; ++i) probs[i] *= inv;
 }
 
+// Hidden layer of one router MLP for 16 samples x 32 hidden rows per CTA: every weight row is read once per
+// 16 samples (kept in registers as float4 chunks) and dotted with the samples' pooled vectors held in smem.
+constexpr int RH_SAMPLES = 16, RH_ROWS = 32;
+__global__ void __launch_bounds__(NTHR)
+router_hidden_kernel(const float* __restrict__ pooled, const float* __restrict__ w0a, const float* __restrict__ b0a,
+                     float* __restrict__ prea, const float* __restrict__ w0b, const float* __restrict__ b0b,
+                     float* __restrict__ preb, int B, int d, int hid) {
+  extern __shared__ float xs[];                 // [RH_SAMPLES][d]
+  const float* w0 = blockIdx.z == 0 ? w0a : w0b;
+  const float* b0 = blockIdx.z == 0 ? b0a : b0b;
+  float* pre = blockIdx.z == 0 ? prea : preb;
+  const int s0 = blockIdx.y * RH_SAMPLES, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  for (int i = threadIdx.x; i < RH_SAMPLES * d; i += NTHR) {
+    const int s = s0 + i / d;
+    xs[i] = s < B ? pooled[(size_t)s * d + i % d] : 0.f;
+  }
+  __syncthreads();
+  const int d4 = d >> 2;
+  for (int r = 0; r < RH_ROWS / (NTHR / 32); ++r) {
+    const int j = blockIdx.x * RH_ROWS + warp * (RH_ROWS / (NTHR / 32)) + r;
+    if (j >= hid) break;
+    float acc[RH_SAMPLES];
+#pragma unroll
+    for (int q = 0; q < RH_SAMPLES; ++q) acc[q] = 0.f;
+    for (int c = lane; c < d4; c += 32) {
+      const float4 w = reinterpret_cast<const float4*>(w0 + (size_t)j * d)[c];
+#pragma unroll
+      for (int q = 0; q < RH_SAMPLES; ++q) {
+        const float4 x = reinterpret_cast<const float4*>(xs + (size_t)q * d)[c];
+        acc[q] += w.x * x.x + w.y * x.y + w.z * x.z + w.w * x.w;
+      }
+    }
+#pragma unroll
+    for (int q = 0; q < RH_SAMPLES; ++q) {
+      const float v = rte::warp_sum(acc[q]);
+      if (lane == 0 && s0 + q < B) pre[(size_t)(s0 + q) * hid + j] = v + b0[j];
+    }
+  }
+}
+
+__device__ void head_logits(const float* __restrict__ pre, const float* __restrict__ w2, const float* __restrict__ b2,
+                            float* hs, float* logits, int hid, int nout) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  for (int j = threadIdx.x; j < hid; j += NTHR) hs[j] = rte::silu_f(pre[j]);
+  __syncthreads();
+  for (int r = warp; r < nout; r += NTHR / 32) {
+    float acc = 0.f;
+#pragma unroll 4
+    for (int j = lane; j < hid; j += 32) acc += w2[(size_t)r * hid + j] * hs[j];
+    acc = rte::warp_sum(acc);
+    if (lane == 0) logits[r] = acc + b2[r];
+  }
+  __syncthreads();
+}
+
 __global__ void __launch_bounds__(NTHR)
 router_fwd_kernel(rte_router_weights w, const int32_t* __restrict__ depth_values, rte_router_out o, int d, int hid,
                   int R, int K, int T, int fixed_recipe, int fixed_depth_id) {
-  extern __shared__ float sm[];   // xs[d], hs[hid]
+  extern __shared__ float sm[];   // hs[hid]
   __shared__ float rl[RTE_ROUTER_MAX_R], dl[RTE_ROUTER_MAX_K];
-  float* xs = sm;
-  float* hs = sm + d;
+  float* hs = sm;
   const int b = blockIdx.x;
-  for (int c = threadIdx.x; c < d; c += NTHR) xs[c] = o.pooled[(size_t)b * d + c];
-  __syncthreads();
-  mlp_forward(w.r_w0, w.r_b0, w.r_w2, w.r_b2, xs, hs, o.r_hidden_pre + (size_t)b * hid, rl, d, hid, R);
-  mlp_forward(w.d_w0, w.d_b0, w.d_w2, w.d_b2, xs, hs, o.d_hidden_pre + (size_t)b * hid, dl, d, hid, K);
+  head_logits(o.r_hidden_pre + (size_t)b * hid, w.r_w2, w.r_b2, hs, rl, hid, R);
+  head_logits(o.d_hidden_pre + (size_t)b * hid, w.d_w2, w.d_b2, hs, dl, hid, K);
   if (threadIdx.x == 0) {
     float rp[RTE_ROUTER_MAX_R], dp[RTE_ROUTER_MAX_K], tmp[RTE_ROUTER_MAX_R], tp[RTE_ROUTER_MAX_R];
     softmax_small(rl, rp, R);
@@ -190,11 +203,25 @@ router_bwd_sample_kernel(rte_router_weights w, rte_router_out o, const int32_t* 
   mlp_backward_sample(w.d_w0, w.d_w2, dld, o.d_hidden_pre + (size_t)b * hid, dpre_d + (size_t)b * hid, dhd, d, hid, K);
 }
 
-// dh0[b,s,:] += (dpre_r[b,:] @ W0r + dpre_d[b,:] @ W0d) / S.  CTA = 4 samples x 128 columns; the two halves of
-// the block split the hidden dimension and are combined through shared memory.
+// dst[r,:] += vec[r / seg,:]
+__global__ void bcast_add_kernel(float* __restrict__ dst, const float* __restrict__ vec, int rows, int seg, int d) {
+  const long long total = (long long)rows * (d >> 2);
+  const int d4 = d >> 2;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+    const int r = int(i / d4), c = int(i % d4);
+    float4 a = reinterpret_cast<float4*>(dst)[i];
+    const float4 v = reinterpret_cast<const float4*>(vec)[(size_t)(r / seg) * d4 + c];
+    a.x += v.x; a.y += v.y; a.z += v.z; a.w += v.w;
+    reinterpret_cast<float4*>(dst)[i] = a;
+  }
+}
+
+// dpooled[b,:] = (dpre_r[b,:] @ W0r + dpre_d[b,:] @ W0d) / S.  CTA = 4 samples x 128 columns; the two halves of
+// the block split the hidden dimension and are combined through shared memory.  (Broadcast over the sequence
+// into dh0 is a separate fully parallel kernel.)
 __global__ void __launch_bounds__(NTHR)
 router_dpooled_kernel(const float* __restrict__ w0r, const float* __restrict__ w0d, const float* __restrict__ dpre_r,
-                      const float* __restrict__ dpre_d, float* __restrict__ dh0, int B, int S, int d, int hid) {
+                      const float* __restrict__ dpre_d, float* __restrict__ dpooled, int B, int S, int d, int hid) {
   extern __shared__ float sm[];            // sr[4][hid], sd[4][hid], comb[4][128]
   float* sr = sm;
   float* sd = sm + 4 * hid;
@@ -228,8 +255,7 @@ router_dpooled_kernel(const float* __restrict__ w0r, const float* __restrict__ w
     for (int q = 0; q < 4; ++q) {
       const int bb = b0 + q;
       if (bb >= B) break;
-      const float v = (acc[q] + comb[q * 128 + threadIdx.x]) / (float)S;
-      for (int t = 0; t < S; ++t) dh0[((size_t)bb * S + t) * d + c] += v;
+      dpooled[(size_t)bb * d + c] = (acc[q] + comb[q * 128 + threadIdx.x]) / (float)S;
     }
   }
 }
@@ -251,22 +277,32 @@ router_dw0_kernel(const float* __restrict__ dpre, const float* __restrict__ pool
   dw0[i] = acc;
   if (c == 0) db0[j] = accb;
 }
-// dW2[r,j] = sum_b dlog[b,r] * silu(pre[b,j]);  db2[r] = sum_b dlog[b,r]
+// dW2[r,j] = sum_b dlog[b,r] * silu(pre[b,j]);  db2[r] = sum_b dlog[b,r].  32 outputs x 8 sample groups per CTA.
 __global__ void __launch_bounds__(NTHR)
 router_dw2_kernel(const float* __restrict__ dlog, const float* __restrict__ pre, float* __restrict__ dw2,
                   float* __restrict__ db2, int B, int hid, int nout) {
-  const int i = blockIdx.x * NTHR + threadIdx.x;
-  if (i >= nout * hid) return;
-  const int r = i / hid, j = i % hid;
+  __shared__ float sa[8][33], sb[8][33];
+  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+  const int i = blockIdx.x * 32 + tx;
   float acc = 0.f, accb = 0.f;
-#pragma unroll 8
-  for (int b = 0; b < B; ++b) {
-    const float v = dlog[(size_t)b * nout + r];
-    acc += v * rte::silu_f(pre[(size_t)b * hid + j]);
-    accb += v;
+  if (i < nout * hid) {
+    const int r = i / hid, j = i % hid;
+#pragma unroll 4
+    for (int b = ty; b < B; b += 8) {
+      const float v = dlog[(size_t)b * nout + r];
+      acc += v * rte::silu_f(pre[(size_t)b * hid + j]);
+      accb += v;
+    }
   }
-  dw2[i] = acc;
-  if (j == 0) db2[r] = accb;
+  sa[ty][tx] = acc; sb[ty][tx] = accb;
+  __syncthreads();
+  if (ty == 0 && i < nout * hid) {
+    float t = 0.f, u = 0.f;
+#pragma unroll
+    for (int k = 0; k < 8; ++k) { t += sa[k][tx]; u += sb[k][tx]; }
+    dw2[i] = t;
+    if (i % hid == 0) db2[i / hid] = u;
+  }
 }
 
 }  // namespace
@@ -282,9 +318,21 @@ extern "C" int rte_router_fwd(const float* h0, const rte_router_weights* w, cons
   RTE_CHECK_ARG(out->pooled && out->r_hidden_pre && out->d_hidden_pre && out->recipe_logits && out->recipe_probs &&
                 out->depth_probs && out->expected_depth && out->router_entropy && out->recipe_id &&
                 out->recipe_id_by_pass && out->depth_id && out->depth);
-  const size_t smem = (size_t)(d + hid) * sizeof(float);
-  if (smem > 48 * 1024) return RTE_ERR_UNSUPPORTED;
+  const size_t smem = (size_t)hid * sizeof(float);
+  const size_t smem_h = (size_t)RH_SAMPLES * d * sizeof(float);
+  if (smem > 48 * 1024 || d % 4 != 0) return RTE_ERR_UNSUPPORTED;
+  if (smem_h > 48 * 1024) {
+    static bool set = false;
+    if (!set) {
+      if (cudaFuncSetAttribute(router_hidden_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 128 * 1024) != cudaSuccess)
+        return RTE_ERR_LAUNCH;
+      set = true;
+    }
+  }
   pool_kernel<<<dim3(rte::ceil_div(d, NTHR), B), NTHR, 0, ST(stream)>>>(h0, out->pooled, S, d);
+  RTE_LAUNCH_CHECK();
+  router_hidden_kernel<<<dim3(rte::ceil_div(hid, RH_ROWS), rte::ceil_div(B, RH_SAMPLES), 2), NTHR, smem_h, ST(stream)>>>(
+      out->pooled, w->r_w0, w->r_b0, out->r_hidden_pre, w->d_w0, w->d_b0, out->d_hidden_pre, B, d, hid);
   RTE_LAUNCH_CHECK();
   router_fwd_kernel<<<B, NTHR, smem, ST(stream)>>>(*w, depth_values, *out, d, hid, R, K, T, fixed_recipe, fixed_depth_id);
   RTE_LAUNCH_CHECK();
@@ -303,6 +351,7 @@ extern "C" int rte_router_aux_bwd(const rte_router_weights* w, const rte_router_
   float* dpre_d = dpre_r + (size_t)B * hid;         // [B, hid]
   float* dlog_r = dpre_d + (size_t)B * hid;         // [B, R]
   float* dlog_d = dlog_r + (size_t)B * R;           // [B, K]
+  float* dpooled = dlog_d + (size_t)B * K;          // [B, d]
   aux_kernel<<<1, NTHR, 0, ST(stream)>>>(fwd->recipe_probs, fwd->expected_depth, lambda_load, lambda_depth, aux, mean_prob, B, R);
   RTE_LAUNCH_CHECK();
   const size_t smem = (size_t)2 * hid * sizeof(float);
@@ -313,16 +362,24 @@ extern "C" int rte_router_aux_bwd(const rte_router_weights* w, const rte_router_
   const size_t smem_dp = (size_t)(8 * hid + 4 * 128) * sizeof(float);
   if (smem_dp > 48 * 1024) return RTE_ERR_UNSUPPORTED;
   router_dpooled_kernel<<<rte::ceil_div(B, 4) * rte::ceil_div(d, 128), NTHR, smem_dp, ST(stream)>>>(
-      w->r_w0, w->d_w0, dpre_r, dpre_d, dh0, B, S, d, hid);
+      w->r_w0, w->d_w0, dpre_r, dpre_d, dpooled, B, S, d, hid);
   RTE_LAUNCH_CHECK();
+  if (d % 4 != 0) return RTE_ERR_UNSUPPORTED;
+  {
+    long long n4 = (long long)B * S * (d / 4);
+    int grid = (int)((n4 + NTHR - 1) / NTHR);
+    if (grid > 148 * 8) grid = 148 * 8;
+    bcast_add_kernel<<<grid, NTHR, 0, ST(stream)>>>(dh0, dpooled, B * S, S, d);
+    RTE_LAUNCH_CHECK();
+  }
   const int g0 = (int)rte::ceil_div64((long long)hid * d, NTHR);
   router_dw0_kernel<<<g0, NTHR, 0, ST(stream)>>>(dpre_r, fwd->pooled, grads->r_w0, grads->r_b0, B, d, hid);
   RTE_LAUNCH_CHECK();
   router_dw0_kernel<<<g0, NTHR, 0, ST(stream)>>>(dpre_d, fwd->pooled, grads->d_w0, grads->d_b0, B, d, hid);
   RTE_LAUNCH_CHECK();
-  router_dw2_kernel<<<rte::ceil_div(R * hid, NTHR), NTHR, 0, ST(stream)>>>(dlog_r, fwd->r_hidden_pre, grads->r_w2, grads->r_b2, B, hid, R);
+  router_dw2_kernel<<<rte::ceil_div(R * hid, 32), NTHR, 0, ST(stream)>>>(dlog_r, fwd->r_hidden_pre, grads->r_w2, grads->r_b2, B, hid, R);
   RTE_LAUNCH_CHECK();
-  router_dw2_kernel<<<rte::ceil_div(K * hid, NTHR), NTHR, 0, ST(stream)>>>(dlog_d, fwd->d_hidden_pre, grads->d_w2, grads->d_b2, B, hid, K);
+  router_dw2_kernel<<<rte::ceil_div(K * hid, 32), NTHR, 0, ST(stream)>>>(dlog_d, fwd->d_hidden_pre, grads->d_w2, grads->d_b2, B, hid, K);
   RTE_LAUNCH_CHECK();
   return RTE_OK;
 }

@@ -42,6 +42,7 @@ class CudaOps:
         self.status = torch.zeros(1, dtype=torch.int32, device=self.device)
         self.launches = 0          # kernels-entry calls issued (for bench accounting)
         self._split_ws: torch.Tensor | None = None
+        self._rope_tables: dict[tuple[int, int], torch.Tensor] = {}
 
     # ------------------------------------------------------------------ helpers
     @property
@@ -165,16 +166,25 @@ class CudaOps:
         self._call("rte_segment_sum", _ptr(src), _ptr(out), n_seg, seg_len, self.stream)
 
     # ------------------------------------------------------------------ attention
+    def rope_table(self, S: int, head_dim: int) -> torch.Tensor:
+        """(cos, sin) table [S, head_dim/2, 2] for the attention kernels, built once per (S, head_dim)."""
+        key = (S, head_dim)
+        if key not in self._rope_tables:
+            out = torch.empty(S, head_dim // 2, 2, dtype=torch.float32, device=self.device)
+            self._call("rte_rope_table", _ptr(out), S, head_dim, self.stream)
+            self._rope_tables[key] = out
+        return self._rope_tables[key]
+
     def attn_fwd(self, qkv, y, lse, *, B: int, S: int, n_heads: int, head_dim: int, sec: int | None = None) -> None:
         sec = sec if sec is not None else n_heads * head_dim
-        self._call("rte_attn_fwd", _ptr(qkv), qkv.stride(0), sec, _ptr(y), y.stride(0), _ptr(lse), B, S, n_heads,
-                   head_dim, self.stream)
+        self._call("rte_attn_fwd", _ptr(qkv), qkv.stride(0), sec, _ptr(y), y.stride(0), _ptr(lse),
+                   _ptr(self.rope_table(S, head_dim)), B, S, n_heads, head_dim, self.stream)
 
     def attn_bwd(self, qkv, y, dy, lse, dqkv, *, B: int, S: int, n_heads: int, head_dim: int,
                  sec: int | None = None) -> None:
         sec = sec if sec is not None else n_heads * head_dim
         self._call("rte_attn_bwd", _ptr(qkv), qkv.stride(0), sec, _ptr(y), _ptr(dy), y.stride(0), _ptr(lse),
-                   _ptr(dqkv), B, S, n_heads, head_dim, self.stream)
+                   _ptr(dqkv), _ptr(self.rope_table(S, head_dim)), B, S, n_heads, head_dim, self.stream)
 
     # ------------------------------------------------------------------ router
     @staticmethod
