@@ -35,6 +35,7 @@ struct KParams {
   int pair_off;
   int splits; long long split_stride;
   int num_m_blocks, num_n_blocks, kblocks_total, kblocks_per_split;
+  int tma_store;            // 1: outputs leave through shared-memory staging + TMA bulk stores
   int* status;
 };
 
@@ -75,6 +76,19 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map
       "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
       ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y), "r"(bar)
       : "memory");
+}
+__device__ __forceinline__ void tma_store_3d(const CUtensorMap* map, uint32_t src, int x, int y, int z) {
+  asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.bulk_group [%0, {%2, %3, %4}], [%1];"
+               ::"l"(reinterpret_cast<uint64_t>(map)), "r"(src), "r"(x), "r"(y), "r"(z)
+               : "memory");
+}
+__device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void bulk_wait_read() { asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory"); }
+__device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
+__device__ __forceinline__ void epi_barrier() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
+__device__ __forceinline__ void st_shared_v4(uint32_t addr, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
+  asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
 }
 __device__ __forceinline__ void prefetch_tmap(const CUtensorMap* map) {
   asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(map)) : "memory");
@@ -194,7 +208,9 @@ struct SmemLayout {
   static constexpr int B_BYTES = BN * BK * 2;    // 16/32 KB
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
   static constexpr int STAGES = (BN == 256) ? 4 : 6;
-  static constexpr int BAR_OFFSET = STAGES * STAGE_BYTES;
+  static constexpr int STAGING_OFFSET = STAGES * STAGE_BYTES;     // output staging ring for TMA stores
+  static constexpr int STAGING_BYTES = 32 * 1024;                 // 4 x [128 rows x 64 B] or 2 x [128 rows x 128 B]
+  static constexpr int BAR_OFFSET = STAGING_OFFSET + STAGING_BYTES;
   static constexpr int TOTAL = BAR_OFFSET + 256 + 1024;   // barriers + slack for 1024-byte alignment
 };
 
@@ -202,6 +218,7 @@ struct SmemLayout {
 template <int BN>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+                    const __grid_constant__ CUtensorMap tmap_c, const __grid_constant__ CUtensorMap tmap_c2,
                     const KParams p) {
   using L = SmemLayout<BN>;
   constexpr int STAGES = L::STAGES;
@@ -329,6 +346,130 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
     // ---------------- epilogue (warps 2..5) ----------------
     const int quad = warp & 3;               // TMEM lane quadrant this warp may read
     int acc = 0; uint32_t acc_phase = 0; bool ok = true;
+    if (p.tma_store) {
+      // Each 32-column slice of the accumulator becomes one "store job": the 128 epilogue threads write their rows
+      // into a swizzled staging buffer, one thread hands the buffer to the TMA (which clips rows/columns beyond
+      // M/N), and a small ring of buffers keeps several stores in flight.  One named barrier per job.
+      const uint32_t staging = smem_base + L::STAGING_OFFSET;
+      const bool issuer = (warp == 2 && lane == 0);
+      const int r = quad * 32 + lane;        // row of the tile this thread owns
+      uint32_t job = 0;
+      // 16-bit outputs: 64-byte rows, ring of 4;  32-bit outputs: 128-byte rows, ring of 2
+      auto emit16 = [&](const CUtensorMap* map, int x, int y, const float (&v)[32]) {
+        const uint32_t base = staging + (job & 3u) * 8192u + uint32_t(r) * 64u;
+        const uint32_t sw = (uint32_t(r) >> 1) & 3u;
+#pragma unroll
+        for (uint32_t c = 0; c < 4; ++c)
+          st_shared_v4(base + ((c ^ sw) << 4), rte::pack_bf16x2(v[8 * c], v[8 * c + 1]), rte::pack_bf16x2(v[8 * c + 2], v[8 * c + 3]),
+                       rte::pack_bf16x2(v[8 * c + 4], v[8 * c + 5]), rte::pack_bf16x2(v[8 * c + 6], v[8 * c + 7]));
+        fence_proxy_async();
+        if (issuer) bulk_wait_read<2>();
+        epi_barrier();
+        if (issuer) { tma_store_3d(map, staging + (job & 3u) * 8192u, x, y, 0); bulk_commit(); }
+        ++job;
+      };
+      auto emit32 = [&](const CUtensorMap* map, int x, int y, int z, const float (&v)[32]) {
+        const uint32_t base = staging + (job & 1u) * 16384u + uint32_t(r) * 128u;
+        const uint32_t sw = uint32_t(r) & 7u;
+#pragma unroll
+        for (uint32_t c = 0; c < 8; ++c)
+          st_shared_v4(base + ((c ^ sw) << 4), __float_as_uint(v[4 * c]), __float_as_uint(v[4 * c + 1]),
+                       __float_as_uint(v[4 * c + 2]), __float_as_uint(v[4 * c + 3]));
+        fence_proxy_async();
+        if (issuer) bulk_wait_read<0>();
+        epi_barrier();
+        if (issuer) { tma_store_3d(map, staging + (job & 1u) * 16384u, x, y, z); bulk_commit(); }
+        ++job;
+      };
+      for (int w = blockIdx.x; w < total_work && ok; w += gridDim.x) {
+        const int split = w / tiles, t = w % tiles;
+        const int m0 = (t % p.num_m_blocks) * BM, nblk = t / p.num_m_blocks, n0 = nblk * BN;
+        if (!mbar_wait(tfull_bar(acc), acc_phase)) {
+          if (p.status && lane == 0) atomicExch(p.status, RTE_DEV_WAIT_TIMEOUT_EPILOGUE);
+          ok = false; break;
+        }
+        tc_fence_after();
+        const int row = m0 + r;
+        const bool row_ok = row < p.M;
+        const uint32_t t_row = tmem_base + (uint32_t(quad * 32) << 16) + acc * BN;
+        uint32_t raw[32];
+        float v[32];
+        if (p.epilogue == RTE_EPI_BF16) {
+          for (int c = 0; c < BN / 32; ++c) {
+            const int col = n0 + c * 32;
+            if (col >= p.N) break;
+            tmem_ld32(t_row + c * 32, raw); tmem_ld_wait();
+#pragma unroll
+            for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(raw[j]);
+            emit16(&tmap_c, col, m0, v);
+          }
+        } else if (p.epilogue == RTE_EPI_F32) {
+          for (int c = 0; c < BN / 32; ++c) {
+            const int col = n0 + c * 32;
+            if (col >= p.N) break;
+            tmem_ld32(t_row + c * 32, raw); tmem_ld_wait();
+            if (p.R != nullptr) {
+              if (row_ok) load_f32x32(reinterpret_cast<const float*>(p.R) + size_t(row) * p.ldr + col, v, p.N - col);
+#pragma unroll
+              for (int j = 0; j < 32; ++j) v[j] = (row_ok ? v[j] : 0.f) + __uint_as_float(raw[j]);
+            } else {
+#pragma unroll
+              for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(raw[j]);
+            }
+            emit32(&tmap_c, col, m0, split, v);
+          }
+        } else if (p.epilogue == RTE_EPI_SWIGLU_FWD) {
+          const int j0 = nblk * (BN / 2);
+          uint32_t rawg[32];
+          for (int c = 0; c < BN / 64; ++c) {
+            const int col = j0 + c * 32;
+            if (col >= p.pair_off) break;
+            tmem_ld32(t_row + c * 32, raw);
+            tmem_ld32(t_row + BN / 2 + c * 32, rawg);
+            tmem_ld_wait();
+            float up[32], gt[32];
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+              up[j] = __bfloat162float(__float2bfloat16_rn(__uint_as_float(raw[j])));
+              gt[j] = __bfloat162float(__float2bfloat16_rn(__uint_as_float(rawg[j])));
+              v[j] = up[j] * rte::silu_f(gt[j]);
+            }
+            emit16(&tmap_c2, col, m0, up);
+            emit16(&tmap_c2, p.pair_off + col, m0, gt);
+            emit16(&tmap_c, col, m0, v);
+          }
+        } else {  // RTE_EPI_SWIGLU_BWD
+          const int F = p.pair_off;
+          for (int c = 0; c < BN / 32; ++c) {
+            const int col = n0 + c * 32;
+            if (col >= p.N) break;
+            tmem_ld32(t_row + c * 32, raw); tmem_ld_wait();
+            float up[32], gt[32], dg[32];
+            if (row_ok) {
+              const __nv_bfloat16* ug = reinterpret_cast<const __nv_bfloat16*>(p.R) + size_t(row) * p.ldr;
+              load_bf16x32(ug + col, up, p.N - col);
+              load_bf16x32(ug + F + col, gt, p.N - col);
+            }
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+              const float dz = __uint_as_float(raw[j]);
+              const float g_ = row_ok ? gt[j] : 0.f, u_ = row_ok ? up[j] : 0.f;
+              const float sg = rte::sigmoid_f(g_);
+              v[j] = dz * g_ * sg;
+              dg[j] = dz * u_ * sg * (1.f + g_ * (1.f - sg));
+            }
+            // tmap_c views columns [0, F) of the output, tmap_c2 columns [F, 2F): each clips at its own edge
+            emit16(&tmap_c, col, m0, v);
+            emit16(&tmap_c2, col, m0, dg);
+          }
+        }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(tempty_bar(acc));
+        if (++acc == 2) { acc = 0; acc_phase ^= 1u; }
+      }
+      if (issuer) bulk_wait_all();
+    } else
     for (int w = blockIdx.x; w < total_work && ok; w += gridDim.x) {
       const int split = w / tiles, t = w % tiles;
       const int m0 = (t % p.num_m_blocks) * BM, nblk = t / p.num_m_blocks, n0 = nblk * BN;
@@ -467,8 +608,27 @@ int make_tmap(CUtensorMap* map, const void* base, long long rows, long long cols
   return r == CUDA_SUCCESS ? RTE_OK : RTE_ERR_TENSOR_MAP;
 }
 
+// 3-D tensor map for the epilogue's bulk stores: [planes, rows, cols] with a 32-column x 128-row box and the swizzle
+// that matches the staging layout (64-byte rows for 16-bit outputs, 128-byte rows for 32-bit outputs).
+int make_store_tmap(CUtensorMap* map, const void* base, long long rows, long long cols, long long ld, long long planes,
+                    long long plane_stride, bool f32) {
+  EncodeTiledFn fn = get_encode_fn();
+  if (!fn) return RTE_ERR_TENSOR_MAP;
+  const unsigned long long es = f32 ? 4ull : 2ull;
+  cuuint64_t dims[3] = {static_cast<cuuint64_t>(cols), static_cast<cuuint64_t>(rows), static_cast<cuuint64_t>(planes)};
+  cuuint64_t strides[2] = {static_cast<cuuint64_t>(ld) * es, static_cast<cuuint64_t>(plane_stride) * es};
+  cuuint32_t box[3] = {32, 128, 1};
+  cuuint32_t estr[3] = {1, 1, 1};
+  CUresult r = fn(map, f32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(base),
+                  dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                  f32 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B, CU_TENSOR_MAP_L2_PROMOTION_NONE,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? RTE_OK : RTE_ERR_TENSOR_MAP;
+}
+
 template <int BN>
-int launch(const rte_gemm_args* a, const CUtensorMap& ta, const CUtensorMap& tb, KParams& kp, int sm_count, cudaStream_t st) {
+int launch(const rte_gemm_args* a, const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc,
+           const CUtensorMap& tc2, KParams& kp, int sm_count, cudaStream_t st) {
   using L = SmemLayout<BN>;
   static bool attr_set = false;
   if (!attr_set) {
@@ -479,7 +639,7 @@ int launch(const rte_gemm_args* a, const CUtensorMap& ta, const CUtensorMap& tb,
   const int total = kp.num_m_blocks * kp.num_n_blocks * kp.splits;
   int grid = a->max_ctas > 0 ? a->max_ctas : sm_count;
   if (grid > total) grid = total;
-  gemm_tcgen05_kernel<BN><<<grid, NUM_THREADS, L::TOTAL, st>>>(ta, tb, kp);
+  gemm_tcgen05_kernel<BN><<<grid, NUM_THREADS, L::TOTAL, st>>>(ta, tb, tc, tc2, kp);
   RTE_LAUNCH_CHECK();
   return RTE_OK;
 }
@@ -543,8 +703,34 @@ extern "C" int rte_gemm_bf16(const rte_gemm_args* a, rte_stream_t stream) {
   }
   if (rc != RTE_OK) return rc;
 
+  // Outputs through TMA bulk stores whenever their addresses and strides allow it (16-byte rules of the TMA);
+  // otherwise the epilogue writes with plain vector stores.
+  CUtensorMap tc = ta, tc2 = ta;
+  const bool out_f32 = a->epilogue == RTE_EPI_F32;
+  const long long es = out_f32 ? 4 : 2;
+  auto aligned = [&](const void* ptr, long long ld) { return ptr && (reinterpret_cast<uintptr_t>(ptr) & 15) == 0 && (ld * es) % 16 == 0; };
+  bool tma_ok = aligned(a->C, a->ldc) && a->M >= 1;
+  if (splits > 1) tma_ok = tma_ok && (a->split_stride * es) % 16 == 0;
+  if (swiglu_f) tma_ok = tma_ok && aligned(a->C2, a->ldc2) && (a->b_pair_offset % 32 == 0);
+  if (swiglu_b) tma_ok = tma_ok && (a->N % 8 == 0);
+  if (tma_ok) {
+    const long long plane = splits > 1 ? a->split_stride : (long long)a->M * a->ldc;
+    if (swiglu_f) {
+      rc = make_store_tmap(&tc, a->C, a->M, a->b_pair_offset, a->ldc, 1, (long long)a->M * a->ldc, false);
+      if (rc == RTE_OK) rc = make_store_tmap(&tc2, a->C2, a->M, 2LL * a->b_pair_offset, a->ldc2, 1, (long long)a->M * a->ldc2, false);
+    } else if (swiglu_b) {
+      rc = make_store_tmap(&tc, a->C, a->M, a->N, a->ldc, 1, (long long)a->M * a->ldc, false);
+      if (rc == RTE_OK)
+        rc = make_store_tmap(&tc2, reinterpret_cast<const __nv_bfloat16*>(a->C) + a->N, a->M, a->N, a->ldc, 1, (long long)a->M * a->ldc, false);
+    } else {
+      rc = make_store_tmap(&tc, a->C, a->M, a->N, a->ldc, splits, plane, out_f32);
+    }
+    if (rc != RTE_OK) tma_ok = false;     // e.g. a stride the encoder rejects: use the direct path
+  }
+  kp.tma_store = tma_ok ? 1 : 0;
+
   const int sms = rte_device_sm_count();
   if (sms <= 0) return RTE_ERR_NO_DEVICE;
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
-  return bn == 256 ? launch<256>(a, ta, tb, kp, sms, st) : launch<128>(a, ta, tb, kp, sms, st);
+  return bn == 256 ? launch<256>(a, ta, tb, tc, tc2, kp, sms, st) : launch<128>(a, ta, tb, tc, tc2, kp, sms, st);
 }
