@@ -173,7 +173,7 @@ int rte_router_fwd(const float* h0, const rte_router_weights* w, const int32_t* 
                    int32_t K, int32_t T, int32_t fixed_recipe, int32_t fixed_depth_id, rte_stream_t stream);
 /* aux[0] = lambda_load * (R * sum_r mean_B(p_r)^2 - 1), aux[1] = lambda_depth * mean_B E[depth]
  * (metrics.py:103-111).  Backward of both through the two MLPs: weight/bias grads (f32, overwritten)
- * and dh0[b,s,:] += dpooled[b,:] / S.  scratch f32 >= RTE_ROUTER_MAX_R + B*(2*hid + R + K + d).      */
+ * and dh0[b,s,:] += dpooled[b,:] / S.  scratch f32 (16-byte aligned) >= RTE_ROUTER_MAX_R + B*(2*hid + R + K + d) + 4.      */
 typedef struct rte_router_grads {
   float *r_w0, *r_b0, *r_w2, *r_b2, *d_w0, *d_b0, *d_w2, *d_b2;
 } rte_router_grads;

@@ -392,75 +392,83 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
         const int row = m0 + r;
         const bool row_ok = row < p.M;
         const uint32_t t_row = tmem_base + (uint32_t(quad * 32) << 16) + acc * BN;
-        uint32_t raw[32];
+        // TMEM reads queue behind the MMAs already issued for the next tile, so their latency is long: fetch four
+        // 32-column slices (128 columns) per wait instead of one.
+        uint32_t raw[4][32];
         float v[32];
-        if (p.epilogue == RTE_EPI_BF16) {
-          for (int c = 0; c < BN / 32; ++c) {
-            const int col = n0 + c * 32;
-            if (col >= p.N) break;
-            tmem_ld32(t_row + c * 32, raw); tmem_ld_wait();
+        if (p.epilogue == RTE_EPI_BF16 || p.epilogue == RTE_EPI_F32 || p.epilogue == RTE_EPI_SWIGLU_BWD) {
+          for (int cg = 0; cg < BN / 128; ++cg) {
+            if (n0 + cg * 128 >= p.N) break;
 #pragma unroll
-            for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(raw[j]);
-            emit16(&tmap_c, col, m0, v);
-          }
-        } else if (p.epilogue == RTE_EPI_F32) {
-          for (int c = 0; c < BN / 32; ++c) {
-            const int col = n0 + c * 32;
-            if (col >= p.N) break;
-            tmem_ld32(t_row + c * 32, raw); tmem_ld_wait();
-            if (p.R != nullptr) {
-              if (row_ok) load_f32x32(reinterpret_cast<const float*>(p.R) + size_t(row) * p.ldr + col, v, p.N - col);
-#pragma unroll
-              for (int j = 0; j < 32; ++j) v[j] = (row_ok ? v[j] : 0.f) + __uint_as_float(raw[j]);
-            } else {
-#pragma unroll
-              for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(raw[j]);
-            }
-            emit32(&tmap_c, col, m0, split, v);
-          }
-        } else if (p.epilogue == RTE_EPI_SWIGLU_FWD) {
-          const int j0 = nblk * (BN / 2);
-          uint32_t rawg[32];
-          for (int c = 0; c < BN / 64; ++c) {
-            const int col = j0 + c * 32;
-            if (col >= p.pair_off) break;
-            tmem_ld32(t_row + c * 32, raw);
-            tmem_ld32(t_row + BN / 2 + c * 32, rawg);
+            for (int q = 0; q < 4; ++q) tmem_ld32(t_row + cg * 128 + q * 32, raw[q]);
             tmem_ld_wait();
-            float up[32], gt[32];
 #pragma unroll
-            for (int j = 0; j < 32; ++j) {
-              up[j] = __bfloat162float(__float2bfloat16_rn(__uint_as_float(raw[j])));
-              gt[j] = __bfloat162float(__float2bfloat16_rn(__uint_as_float(rawg[j])));
-              v[j] = up[j] * rte::silu_f(gt[j]);
+            for (int q = 0; q < 4; ++q) {
+              const int col = n0 + cg * 128 + q * 32;
+              if (col < p.N) {
+                if (p.epilogue == RTE_EPI_BF16) {
+#pragma unroll
+                  for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(raw[q][j]);
+                  emit16(&tmap_c, col, m0, v);
+                } else if (p.epilogue == RTE_EPI_F32) {
+                  if (p.R != nullptr) {
+                    if (row_ok) load_f32x32(reinterpret_cast<const float*>(p.R) + size_t(row) * p.ldr + col, v, p.N - col);
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) v[j] = (row_ok ? v[j] : 0.f) + __uint_as_float(raw[q][j]);
+                  } else {
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(raw[q][j]);
+                  }
+                  emit32(&tmap_c, col, m0, split, v);
+                } else {
+                  const int F = p.pair_off;
+                  float up[32], gt[32], dg[32];
+                  if (row_ok) {
+                    const __nv_bfloat16* ug = reinterpret_cast<const __nv_bfloat16*>(p.R) + size_t(row) * p.ldr;
+                    load_bf16x32(ug + col, up, p.N - col);
+                    load_bf16x32(ug + F + col, gt, p.N - col);
+                  }
+#pragma unroll
+                  for (int j = 0; j < 32; ++j) {
+                    const float dz = __uint_as_float(raw[q][j]);
+                    const float g_ = row_ok ? gt[j] : 0.f, u_ = row_ok ? up[j] : 0.f;
+                    const float sg = rte::sigmoid_f(g_);
+                    v[j] = dz * g_ * sg;
+                    dg[j] = dz * u_ * sg * (1.f + g_ * (1.f - sg));
+                  }
+                  // tmap_c views columns [0, F) of the output, tmap_c2 columns [F, 2F): each clips at its own edge
+                  emit16(&tmap_c, col, m0, v);
+                  emit16(&tmap_c2, col, m0, dg);
+                }
+              }
             }
-            emit16(&tmap_c2, col, m0, up);
-            emit16(&tmap_c2, p.pair_off + col, m0, gt);
-            emit16(&tmap_c, col, m0, v);
           }
-        } else {  // RTE_EPI_SWIGLU_BWD
-          const int F = p.pair_off;
-          for (int c = 0; c < BN / 32; ++c) {
-            const int col = n0 + c * 32;
-            if (col >= p.N) break;
-            tmem_ld32(t_row + c * 32, raw); tmem_ld_wait();
-            float up[32], gt[32], dg[32];
-            if (row_ok) {
-              const __nv_bfloat16* ug = reinterpret_cast<const __nv_bfloat16*>(p.R) + size_t(row) * p.ldr;
-              load_bf16x32(ug + col, up, p.N - col);
-              load_bf16x32(ug + F + col, gt, p.N - col);
-            }
+        } else {  // RTE_EPI_SWIGLU_FWD: two (up, gate) slice pairs per wait
+          const int j0 = nblk * (BN / 2);
+          for (int cg = 0; cg < BN / 128; ++cg) {
+            if (j0 + cg * 64 >= p.pair_off) break;
 #pragma unroll
-            for (int j = 0; j < 32; ++j) {
-              const float dz = __uint_as_float(raw[j]);
-              const float g_ = row_ok ? gt[j] : 0.f, u_ = row_ok ? up[j] : 0.f;
-              const float sg = rte::sigmoid_f(g_);
-              v[j] = dz * g_ * sg;
-              dg[j] = dz * u_ * sg * (1.f + g_ * (1.f - sg));
+            for (int q = 0; q < 2; ++q) {
+              tmem_ld32(t_row + cg * 64 + q * 32, raw[2 * q]);
+              tmem_ld32(t_row + BN / 2 + cg * 64 + q * 32, raw[2 * q + 1]);
             }
-            // tmap_c views columns [0, F) of the output, tmap_c2 columns [F, 2F): each clips at its own edge
-            emit16(&tmap_c, col, m0, v);
-            emit16(&tmap_c2, col, m0, dg);
+            tmem_ld_wait();
+#pragma unroll
+            for (int q = 0; q < 2; ++q) {
+              const int col = j0 + cg * 64 + q * 32;
+              if (col < p.pair_off) {
+                float up[32], gt[32];
+#pragma unroll
+                for (int j = 0; j < 32; ++j) {
+                  up[j] = __bfloat162float(__float2bfloat16_rn(__uint_as_float(raw[2 * q][j])));
+                  gt[j] = __bfloat162float(__float2bfloat16_rn(__uint_as_float(raw[2 * q + 1][j])));
+                  v[j] = up[j] * rte::silu_f(gt[j]);
+                }
+                emit16(&tmap_c2, col, m0, up);
+                emit16(&tmap_c2, p.pair_off + col, m0, gt);
+                emit16(&tmap_c, col, m0, v);
+              }
+            }
           }
         }
         tc_fence_before();

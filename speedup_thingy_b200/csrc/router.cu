@@ -351,7 +351,8 @@ extern "C" int rte_router_aux_bwd(const rte_router_weights* w, const rte_router_
   float* dpre_d = dpre_r + (size_t)B * hid;         // [B, hid]
   float* dlog_r = dpre_d + (size_t)B * hid;         // [B, R]
   float* dlog_d = dlog_r + (size_t)B * R;           // [B, K]
-  float* dpooled = dlog_d + (size_t)B * K;          // [B, d]
+  float* dpooled = scratch + (((size_t)RTE_ROUTER_MAX_R + (size_t)B * (2 * hid + R + K) + 3) & ~(size_t)3);   // [B, d], 16-byte aligned
+  if (reinterpret_cast<uintptr_t>(scratch) & 15) return RTE_ERR_ALIGNMENT;
   aux_kernel<<<1, NTHR, 0, ST(stream)>>>(fwd->recipe_probs, fwd->expected_depth, lambda_load, lambda_depth, aux, mean_prob, B, R);
   RTE_LAUNCH_CHECK();
   const size_t smem = (size_t)2 * hid * sizeof(float);
