@@ -100,7 +100,7 @@ class AuditReplay:
         self.dn_f32, self.dh0_acc, self.dcur, self.dalt = e(Ma, d), e(Ma, d), e(Ma, d), e(Ma, d)
         self.d16a, self.d16b = e(Ma, d, dtype=bf), e(Ma, d, dtype=bf)
         self.dz16, self.dug16, self.dqkv16 = e(Ma, f, dtype=bf), e(Ma, 2 * f, dtype=bf), e(Ma, 3 * d, dtype=bf)
-        self.partial_g, self.partial_b = e(2 * 148, d), e(2 * 148, d)
+        self.partial_g, self.partial_b = e(8 * 148, d), e(8 * 148, d)
         self.P = 64
         self.part_alpha, self.part_attn, self.part_mlp = e(T * self.P), e(T * self.P), e(T * self.P)
         # The replay runs on its own stream beside the hot pass, so the gradients it contributes to parameters the

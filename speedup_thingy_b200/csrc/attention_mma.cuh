@@ -41,23 +41,49 @@ __device__ __forceinline__ void rope_cs(const float* __restrict__ table, int pos
   }
 }
 
-// rows [0, n_rows) of one head -> smem (bf16, row stride HD + 8); rows in [n_rows, pad_rows) are zeroed.
+// rows [row0, row0 + n_rows) of one head -> smem rows [0, pad_rows) (bf16, row stride HD + 8); rows past n_rows are
+// zeroed.  Each thread moves 8 consecutive dims (4 rotary pairs) with one 16-byte load; rotary positions are absolute
+// (row0 + r).  When `dsum` is given, also accumulates sum_c x[r,c] * other[r,c] per row into dsum[r] (used for
+// D = rowsum(dO * O) in backward): the HD/8 threads of a row are neighbouring lanes.
 template <int HD, bool ROPE>
 __device__ __forceinline__ void load_rows(const __nv_bfloat16* __restrict__ src, int ld, int n_rows, int pad_rows,
-                                          __nv_bfloat16* dst, const float* __restrict__ rope = nullptr) {
-  constexpr int LDS = HD + 8;
-  for (int idx = threadIdx.x; idx < pad_rows * (HD / 2); idx += blockDim.x) {
-    const int s = idx / (HD / 2), pr = idx % (HD / 2);
-    float2 v = make_float2(0.f, 0.f);
-    if (s < n_rows) {
-      v = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(src + (size_t)s * ld + 2 * pr));
+                                          __nv_bfloat16* dst, const float* __restrict__ rope = nullptr, int row0 = 0,
+                                          const __nv_bfloat16* __restrict__ other = nullptr, int ld_other = 0,
+                                          float* dsum = nullptr) {
+  constexpr int LDS = HD + 8, CPR = HD / 8;      // 16-byte chunks per row
+  for (int idx = threadIdx.x; idx < pad_rows * CPR; idx += blockDim.x) {
+    const int r = idx / CPR, ch = idx % CPR;
+    uint4 raw = make_uint4(0u, 0u, 0u, 0u);
+    float part = 0.f;
+    if (r < n_rows) {
+      raw = *reinterpret_cast<const uint4*>(src + (size_t)(row0 + r) * ld + 8 * ch);
       if (ROPE) {
-        float sn, cs;
-        rope_cs(rope, s, pr, HD, cs, sn);
-        v = make_float2(v.x * cs - v.y * sn, v.y * cs + v.x * sn);
+        uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          float cs, sn;
+          rope_cs(rope, row0 + r, 4 * ch + q, HD, cs, sn);
+          const float2 v = rte::unpack_bf16x2(w[q]);
+          w[q] = rte::pack_bf16x2(v.x * cs - v.y * sn, v.y * cs + v.x * sn);
+        }
+        raw = make_uint4(w[0], w[1], w[2], w[3]);
+      }
+      if (other != nullptr) {
+        const uint4 o = *reinterpret_cast<const uint4*>(other + (size_t)(row0 + r) * ld_other + 8 * ch);
+        const uint32_t a4[4] = {raw.x, raw.y, raw.z, raw.w}, b4[4] = {o.x, o.y, o.z, o.w};
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          const float2 x = rte::unpack_bf16x2(a4[q]), y = rte::unpack_bf16x2(b4[q]);
+          part += x.x * y.x + x.y * y.y;
+        }
       }
     }
-    *reinterpret_cast<__nv_bfloat162*>(dst + s * LDS + 2 * pr) = __floats2bfloat162_rn(v.x, v.y);
+    *reinterpret_cast<uint4*>(dst + r * LDS + 8 * ch) = raw;
+    if (dsum != nullptr) {
+#pragma unroll
+      for (int o = 1; o < CPR; o <<= 1) part += __shfl_xor_sync(0xffffffffu, part, o);
+      if (ch == 0) dsum[r] = part;
+    }
   }
 }
 
@@ -102,21 +128,7 @@ fwd_kernel(const __nv_bfloat16* __restrict__ qkv, int ld, int sec, __nv_bfloat16
   const int kv_rows = min(S, qb0 + QB);                               // causal: later keys are never read
   const int kv_pad = min(SMAX, (kv_rows + 15) & ~15);
   const __nv_bfloat16* base = qkv + (size_t)b * S * ld + h * HD;
-  {
-    // queries of this block: rope positions are absolute, so load through a shifted view
-    constexpr int HP = HD / 2;
-    for (int idx = threadIdx.x; idx < QB * HP; idx += blockDim.x) {
-      const int r = idx / HP, pr = idx % HP, s = qb0 + r;
-      float2 v = make_float2(0.f, 0.f);
-      if (s < S) {
-        v = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(base + (size_t)s * ld + 2 * pr));
-        float sn, cs;
-        rope_cs(rope, s, pr, HD, cs, sn);
-        v = make_float2(v.x * cs - v.y * sn, v.y * cs + v.x * sn);
-      }
-      *reinterpret_cast<__nv_bfloat162*>(sq + r * LDS + 2 * pr) = __floats2bfloat162_rn(v.x, v.y);
-    }
-  }
+  load_rows<HD, true>(base, ld, max(0, min(QB, S - qb0)), QB, sq, rope, qb0);
   load_rows<HD, true>(base + sec, ld, kv_rows, kv_pad, sk, rope);
   load_rows<HD, false>(base + 2 * sec, ld, kv_rows, kv_pad, sv);
   __syncthreads();
@@ -221,18 +233,10 @@ bwd_kernel(const __nv_bfloat16* __restrict__ qkv, int ld, int sec, const __nv_bf
   load_rows<HD, true>(base, ld, S, s_pad, sq, rope);
   load_rows<HD, true>(base + sec, ld, S, s_pad, sk, rope);
   load_rows<HD, false>(base + 2 * sec, ld, S, s_pad, sv);
-  load_rows<HD, false>(dy + (size_t)b * S * ldy + h * HD, ldy, S, s_pad, sdo);
+  load_rows<HD, false>(dy + (size_t)b * S * ldy + h * HD, ldy, S, s_pad, sdo, nullptr, 0,
+                       y + (size_t)b * S * ldy + h * HD, ldy, sD);
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, g = lane >> 2, t = lane & 3;
-  for (int i = warp; i < s_pad; i += NTHR / 32) {
-    float part = 0.f;
-    if (i < S) {
-      const __nv_bfloat16* a = dy + (size_t)(b * S + i) * ldy + h * HD;
-      const __nv_bfloat16* o = y + (size_t)(b * S + i) * ldy + h * HD;
-      for (int c = lane; c < HD; c += 32) part += __bfloat162float(a[c]) * __bfloat162float(o[c]);
-    }
-    part = rte::warp_sum(part);
-    if (lane == 0) { sD[i] = part; slse[i] = (i < S) ? lse[((size_t)b * H + h) * S + i] : 0.f; }
-  }
+  for (int i = threadIdx.x; i < s_pad; i += NTHR) slse[i] = (i < S) ? lse[((size_t)b * H + h) * S + i] : 0.f;
   __syncthreads();
   const float scale = rsqrtf((float)HD);
   const int r0 = blk0 + warp * 16;

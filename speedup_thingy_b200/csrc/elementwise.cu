@@ -525,7 +525,7 @@ extern "C" int rte_rmsnorm_bwd(const float* x, const float* w, const float* film
   if (d > 128 * RN_MAX_V4) return RTE_ERR_UNSUPPORTED;
   const bool grads = dw_partial || dgamma_partial;
   int grid = rte::ceil_div(rows, 8);
-  const int cap = 148 * 2;
+  const int cap = 148 * 8;      // enough CTAs in flight to cover HBM latency; each writes one partial row
   if (grid > cap) grid = cap;
   if (grads) {
     RTE_CHECK_ARG(max_partials >= 1);

@@ -130,7 +130,7 @@ class _Temps:
         self.dn16, self.dy16, self.dx16 = (torch.empty(M, d, dtype=bf, device=device) for _ in range(3))
         self.dqkv = torch.empty(M, 3 * d, dtype=bf, device=device)
         self.dxa, self.dxb, self.dxc = (torch.empty(M, d, dtype=f32, device=device) for _ in range(3))
-        self.partial = torch.empty(2 * 148, d, dtype=f32, device=device)
+        self.partial = torch.empty(8 * 148, d, dtype=f32, device=device)
 
 
 class TrainEngine:
@@ -621,6 +621,52 @@ class TrainEngine:
     @property
     def kernel_launches_per_step(self) -> int | None:
         return self._launches_per_step
+
+    def profile_step(self, repeats: int = 3) -> list[tuple[str, float]]:
+        """Device-side duration of every C-ABI call of one step, measured INSIDE a CUDA graph (event-record
+        nodes around each call), so that host launch latency does not leak into the numbers.  Returns
+        (entry point + shape tag, microseconds) in launch order, averaged over `repeats` replays."""
+        ops = self.ops
+        calls: list[tuple[str, Any, Any]] = []
+        orig_call, orig_gemm = ops._call, ops.gemm
+        tag = {"v": ""}
+
+        def timed_call(name, *args):
+            e0 = torch.cuda.Event(enable_timing=True, external=True)
+            e1 = torch.cuda.Event(enable_timing=True, external=True)
+            st = torch.cuda.current_stream(self.device)
+            e0.record(st)
+            orig_call(name, *args)
+            e1.record(st)
+            calls.append((name + tag["v"], e0, e1))
+
+        def tagged_gemm(a, b, out, **kw):
+            tag["v"] = f"[{kw['M']}x{kw['N']}x{kw['K']}/epi{kw.get('epilogue', 0)}" + (f"/split{kw['splits']}" if kw.get("splits", 1) > 1 else "") + "]"
+            try:
+                orig_gemm(a, b, out, **kw)
+            finally:
+                tag["v"] = ""
+
+        ops._call, ops.gemm = timed_call, tagged_gemm
+        self._dp_paused = True
+        try:
+            torch.cuda.synchronize(self.device)
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph):
+                self._forward_backward()
+                self._optimizer_step()
+        finally:
+            ops._call, ops.gemm = orig_call, orig_gemm
+            self._dp_paused = False
+        totals = [0.0] * len(calls)
+        graph.replay()
+        torch.cuda.synchronize(self.device)
+        for _ in range(repeats):
+            graph.replay()
+            torch.cuda.synchronize(self.device)
+            for i, (_, e0, e1) in enumerate(calls):
+                totals[i] += e0.elapsed_time(e1) * 1e3
+        return [(calls[i][0], totals[i] / repeats) for i in range(len(calls))]
 
     def gemm_roofline(self, repeats: int = 5) -> dict[str, Any]:
         """Times every launch of the tcgen05 GEMM inside real (eager) forward+backward passes with a CUDA
