@@ -239,6 +239,25 @@ int rte_grad_norm_multi_tensor(const rte_adamw_tensor* table, int64_t total_chun
                                const int32_t* chunk_index, float* partial, float* sumsq, float max_norm,
                                float* clip_coef, rte_stream_t stream);
 
+/* ------------------------------------------------ vocabulary shortlist (output.py:46-136, `recursive_macro_shortlist`)
+ * rte_shortlist_build: shortlist int32 [rows, K] = the first K distinct ids, in order of first appearance, of
+ *   [target | members of the TC top clusters (cluster c = ids c, c+C, ...; ceil(V/C) slots each, padded with id 0) |
+ *    hard negatives 0..HN-1 (mod V) | random_negs[row, 0..RN) | filler 0..K-1 (mod V) | (target + 0..2K-1) mod V]
+ *   (= ShortlistHead.build_shortlist + _dedupe_preserve_first; the target is always slot 0).
+ *   top_clusters int32 [rows, TC] (e.g. from rte_topk_lowest_index over the cluster-router logits);
+ *   dup_count int32 [rows] (optional) = candidates minus distinct candidates.  Indices are bit-exact.
+ * rte_shortlist_ce: logits[k] = hidden . W[shortlist[k]] (k_logits_shortlist, reference.py:141-143), cross entropy
+ *   against slot 0 -> loss_tok; logits_out bf16 [rows, K] optional; dlogits_dense bf16 [rows, V] (optional) receives
+ *   row_weight[row/S] * (softmax - onehot(0)) at the shortlisted ids and zero elsewhere.
+ * rte_random_tokens: counter-based pseudo-random ids in [0, vocab) from a device-resident seed.                 */
+int rte_shortlist_build(const int64_t* targets, const int32_t* top_clusters, const int32_t* random_negs,
+                        int32_t* shortlist, int32_t* dup_count, int32_t rows, int32_t V, int32_t C, int32_t TC,
+                        int32_t HN, int32_t RN, int32_t K, int32_t* status, rte_stream_t stream);
+int rte_shortlist_ce(const void* hidden, const void* W, const int32_t* shortlist, const float* row_weight, int32_t S,
+                     float* loss_tok, void* logits_out, void* dlogits_dense, int32_t rows, int32_t d, int32_t V,
+                     int32_t K, rte_stream_t stream);
+int rte_random_tokens(int32_t* out, int64_t n, int32_t vocab, const int64_t* seed, rte_stream_t stream);
+
 /* ------------------------------------------------ exact-audit replay helpers (audit.py:245-387; models.py:605-679;
  * layers.py:831-870).  The audited subset has a fixed size n (fixed-count sampler), chosen on the host.
  * Per-sample recipe choices stay on the device: every kernel below looks the recipe of (pass, sample) up in

@@ -54,10 +54,22 @@ class ModelCfg:
     macro_update_scale: float = 0.05
     router_hidden: int | None = None
     topology: str = "recursive"
+    shortlist_clusters: int = 64       # OutputConfig.num_clusters (sizes shortlist_head.cluster_router)
 
     @property
     def router_hidden_dim(self) -> int:  # routing.py:50
         return self.router_hidden or max(32, self.d_model)
+
+
+@dataclass
+class OutputCfg:
+    """config.py:340-346."""
+    mode: str = "full"
+    num_clusters: int = 64
+    shortlist_top_clusters: int = 2
+    shortlist_max_tokens: int = 128
+    hard_negatives: int = 32
+    random_negatives: int = 32
 
 
 @dataclass
@@ -209,7 +221,7 @@ def param_shapes(cfg: ModelCfg) -> list[tuple[str, tuple]]:
             ("macro.u", (r, k, m, d)), ("macro.bias", (r, k, d))]
     for i in range(cfg.n_coda):
         out += _block_shapes(f"coda.{i}", cfg)
-    out += [("final_norm.weight", (d,))]
+    out += [("final_norm.weight", (d,)), ("shortlist_head.cluster_router.weight", (cfg.shortlist_clusters, d))]
     return out
 
 
@@ -481,16 +493,73 @@ def exact_from_h0(p: dict, cfg: ModelCfg, h0: torch.Tensor, targets: torch.Tenso
 
 
 def forward_macro(p: dict, cfg: ModelCfg, tokens: torch.Tensor, targets: torch.Tensor,
-                  fixed_recipe: int | None = None, fixed_depth: int | None = None) -> dict:
-    """models.py:681-723 (full-vocabulary branch)."""
+                  fixed_recipe: int | None = None, fixed_depth: int | None = None, oc: OutputCfg | None = None,
+                  seed: int = 0, top_clusters: torch.Tensor | None = None) -> dict:
+    """models.py:681-723 (full-vocabulary branch, or the shortlist branch when `oc` is given)."""
     h0 = p["embed.weight"][tokens]
     for i in range(cfg.n_prelude):
         h0 = dense_block(p, f"prelude.{i}", h0, cfg.n_heads)
     route = router_forward(p, cfg, h0, fixed_recipe, fixed_depth)
     h = macro_phi(p, cfg, h0, h0, route["recipe_id"], stride_ids_for_depths(cfg, route["depth"]))
+    if oc is not None:
+        x = h
+        for i in range(cfg.n_coda):
+            x = dense_block(p, f"coda.{i}", x, cfg.n_heads)
+        hidden = rmsnorm(x, p["final_norm.weight"])
+        sl = shortlist_loss(p, cfg, oc, hidden, targets, seed, top_clusters)
+        return dict(h0=h0, route=route, recurrent_hidden=h, hidden=hidden, logits=sl["logits"], shortlist=sl,
+                    loss_per_sample=sl["loss_per_sample"])
     hidden, logits = coda_logits(p, cfg, h)
     return dict(h0=h0, route=route, recurrent_hidden=h, hidden=hidden, logits=logits,
                 loss_per_sample=lm_loss_per_sample(logits, targets))
+
+
+def shortlist_candidates(targets: torch.Tensor, top_clusters: torch.Tensor, random_negs: torch.Tensor, vocab: int,
+                         oc: OutputCfg) -> torch.Tensor:
+    """output.py:81-108: [target | members of the top clusters | hard | random | filler | target + 0..2K-1]."""
+    c, k = oc.num_clusters, oc.shortlist_max_tokens
+    mpc = (vocab + c - 1) // c
+    members = top_clusters.unsqueeze(-1) + torch.arange(mpc).view(1, 1, 1, -1) * c      # cluster c = ids c, c+C, ...
+    members = torch.where(members < vocab, members, torch.zeros_like(members)).flatten(start_dim=-2)
+    b, s = targets.shape
+    hard = (torch.arange(oc.hard_negatives) % vocab).view(1, 1, -1).expand(b, s, -1)
+    filler = (torch.arange(k) % vocab).view(1, 1, -1).expand(b, s, -1)
+    tfill = (targets.unsqueeze(-1) + torch.arange(2 * k).view(1, 1, -1)) % vocab
+    return torch.cat([targets.unsqueeze(-1), members, hard, random_negs, filler, tfill], dim=-1)
+
+
+def dedupe_preserve_first(cands: torch.Tensor, k: int) -> torch.Tensor:
+    """output.py:46-70: the k distinct ids with the smallest first position, in that order."""
+    flat = cands.reshape(-1, cands.shape[-1])
+    out = torch.empty(flat.shape[0], k, dtype=torch.long)
+    for r in range(flat.shape[0]):
+        seen: dict[int, None] = {}
+        for v in flat[r].tolist():
+            if v not in seen:
+                seen[v] = None
+                if len(seen) == k:
+                    break
+        out[r] = torch.tensor(list(seen), dtype=torch.long)
+    return out.view(*cands.shape[:-1], k)
+
+
+def shortlist_loss(p: dict, cfg: ModelCfg, oc: OutputCfg, hidden: torch.Tensor, targets: torch.Tensor, seed: int,
+                   top_clusters: torch.Tensor | None = None) -> dict:
+    """output.py:72-136: cluster router -> top clusters -> shortlist -> gathered-row logits -> CE vs slot 0.
+    `top_clusters` may be injected (tests that compare at identical routing)."""
+    b, s, _ = hidden.shape
+    cluster_logits = hidden @ p["shortlist_head.cluster_router.weight"].t()
+    if top_clusters is None:
+        top_clusters = topk_lowest(cluster_logits, min(oc.shortlist_top_clusters, oc.num_clusters))[1]
+    gen = torch.Generator().manual_seed(seed)
+    random_negs = torch.randint(0, cfg.vocab_size, (b, s, oc.random_negatives), generator=gen)
+    cands = shortlist_candidates(targets, top_clusters, random_negs, cfg.vocab_size, oc)
+    shortlist = dedupe_preserve_first(cands, oc.shortlist_max_tokens)
+    rows = p["embed.weight"][shortlist]
+    logits = (hidden.unsqueeze(-2) * rows).sum(dim=-1)
+    tok = F.cross_entropy(logits.flatten(0, -2), torch.zeros(b * s, dtype=torch.long), reduction="none").view(b, s)
+    return dict(loss_per_sample=tok.sum(-1), logits=logits, shortlist=shortlist, cluster_logits=cluster_logits,
+                top_clusters=top_clusters, random_negs=random_negs)
 
 
 def forward_dense(p: dict, cfg: ModelCfg, tokens: torch.Tensor, targets: torch.Tensor) -> dict:
@@ -529,9 +598,12 @@ def macro_distill_loss(tr: TrainCfg, hot_hidden, exact_hidden, hot_logits, exact
     endpoint_normed = F.smooth_l1_loss(rmsnorm(hot_hidden), rmsnorm(exact_hidden))
     endpoint_raw = F.smooth_l1_loss(hot_hidden, exact_hidden)
     temp = max(float(tr.distill_temperature), 1e-6)
-    exact_logp = F.log_softmax(exact_logits / temp, dim=-1)
-    hot_logp = F.log_softmax(hot_logits / temp, dim=-1)
-    kl = F.kl_div(hot_logp, exact_logp.exp(), reduction="batchmean") * temp ** 2
+    if hot_logits.shape == exact_logits.shape:
+        exact_logp = F.log_softmax(exact_logits / temp, dim=-1)
+        hot_logp = F.log_softmax(hot_logits / temp, dim=-1)
+        kl = F.kl_div(hot_logp, exact_logp.exp(), reduction="batchmean") * temp ** 2
+    else:       # shortlist logits [.., K] against exact full-vocabulary logits [.., V]: no KL term (macro.py:452)
+        kl = hot_hidden.new_zeros(())
     return dict(kl=tr.lambda_kl * kl, delta_dir=tr.lambda_delta_dir * delta_dir,
                 delta_rms=tr.lambda_delta_rms * delta_rms,
                 endpoint_normed=tr.lambda_endpoint_normed * endpoint_normed,
@@ -546,10 +618,13 @@ def audit_choice(n: int, k: int, seed: int) -> torch.Tensor:
 
 
 def macro_step_loss(p: dict, cfg: ModelCfg, tr: TrainCfg, tokens: torch.Tensor, targets: torch.Tensor,
-                    step: int, usage_ema: torch.Tensor) -> tuple[torch.Tensor, dict]:
+                    step: int, usage_ema: torch.Tensor, oc: OutputCfg | None = None,
+                    top_clusters: torch.Tensor | None = None) -> tuple[torch.Tensor, dict]:
     """training.py:1336-1392 + audit.py:245-387 (fixed-count sampler,
     gradient_corrected mode, consistency term off)."""
-    hot = forward_macro(p, cfg, tokens, targets, tr.fixed_recipe, tr.fixed_depth)
+    shortlist = tr.mode == "recursive_macro_shortlist"
+    hot = forward_macro(p, cfg, tokens, targets, tr.fixed_recipe, tr.fixed_depth, oc if shortlist else None,
+                        seed=tr.seed + step, top_clusters=top_clusters)      # training.py:1364
     corrected = hot["loss_per_sample"].clone()
     aux: dict[str, torch.Tensor] = {}
     info: dict[str, Any] = dict(hot=hot)
@@ -613,6 +688,8 @@ class OracleTrainer:
     global_step: int = 0
     usage_ema: torch.Tensor | None = None
     opt_state: dict = field(default_factory=dict)
+    oc: OutputCfg | None = None
+    top_clusters: torch.Tensor | None = None      # test hook: shortlist routing injected for the next step
 
     def __post_init__(self) -> None:
         if self.usage_ema is None:
@@ -623,7 +700,8 @@ class OracleTrainer:
         if self.cfg.topology == "dense":
             loss, info = dense_step_loss(leaves, self.cfg, tokens, targets)
         else:
-            loss, info = macro_step_loss(leaves, self.cfg, self.tr, tokens, targets, self.global_step, self.usage_ema)
+            loss, info = macro_step_loss(leaves, self.cfg, self.tr, tokens, targets, self.global_step, self.usage_ema,
+                                         self.oc, self.top_clusters)
         loss.backward()
         grads = {k: v.grad for k, v in leaves.items() if v.grad is not None}
         if self.tr.grad_clip_norm is not None:  # training.py:456-462, before the optimiser reads them

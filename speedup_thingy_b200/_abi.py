@@ -95,6 +95,9 @@ PROTOTYPES = {
     "rte_adamw_multi_tensor": (C.c_int, [c_vp, c_i32, c_i64, c_vp, c_vp, c_vp, c_vp, c_f32, c_f32, c_f32, c_f32,
                                          c_vp, c_vp]),
     "rte_grad_norm_multi_tensor": (C.c_int, [c_vp, c_i64, c_vp, c_vp, c_vp, c_vp, c_f32, c_vp, c_vp]),
+    "rte_shortlist_build": (C.c_int, [c_vp, c_vp, c_vp, c_vp, c_vp] + [c_i32] * 7 + [c_vp, c_vp]),
+    "rte_shortlist_ce": (C.c_int, [c_vp, c_vp, c_vp, c_vp, c_i32, c_vp, c_vp, c_vp, c_i32, c_i32, c_i32, c_i32, c_vp]),
+    "rte_random_tokens": (C.c_int, [c_vp, c_i64, c_i32, c_vp, c_vp]),
     "rte_gather_rows": (C.c_int, [c_vp, c_vp, c_vp, c_i32, c_i64, c_vp]),
     "rte_scatter_add_rows_f32": (C.c_int, [c_vp, c_vp, c_vp, c_i32, c_i64, c_vp]),
     "rte_audit_route": (C.c_int, [c_vp, c_vp, c_vp, c_vp, c_vp, c_i32, c_i32, c_vp]),

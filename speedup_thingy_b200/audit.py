@@ -182,8 +182,9 @@ class AuditReplay:
         o, cfg, tr, w = eng.ops, eng.cfg, eng.tr, 1.0 / eng.world
         n, S, Ma, V = self.n, self.S, self.Ma, cfg.vocab_size
         temp = max(float(tr.distill_temperature), 1e-6)
-        o.kl_distill(self.hot_logits, self.logits, temp, tr.lambda_kl * w * temp / n, self.idx, S, eng.logits, self.kl_rows, Ma, V)
-        o.segment_sum(self.kl_rows, self.kl_sum, 1, Ma)
+        if not eng.shortlist:      # the shortlist head keeps no full hot logits, so the KL term is absent (models.py:698-703)
+            o.kl_distill(self.hot_logits, self.logits, temp, tr.lambda_kl * w * temp / n, self.idx, S, eng.logits, self.kl_rows, Ma, V)
+            o.segment_sum(self.kl_rows, self.kl_sum, 1, Ma)
         o.ce_fwd_bwd(self.logits, self.targets_a, self.row_weight_a, S, self.loss_tok, self.logits)
         o.segment_sum(self.loss_tok, self.exact_loss, n, S)
 

@@ -107,8 +107,9 @@ class TrainingConfig:
     strict_cuda: bool = True
 
     def __post_init__(self) -> None:
-        if self.mode not in ("recursive_macro", "dense_exact"):
-            raise NotImplementedError(f"rte_b200 implements modes recursive_macro and dense_exact, not {self.mode!r}")
+        if self.mode not in ("recursive_macro", "recursive_macro_shortlist", "dense_exact"):
+            raise NotImplementedError("rte_b200 implements modes recursive_macro, recursive_macro_shortlist and "
+                                      f"dense_exact, not {self.mode!r}")
         if self.loss_normalization != "token_mean":
             raise NotImplementedError("only loss_normalization='token_mean'")
         if self.precision != "bf16":
@@ -124,9 +125,25 @@ class TrainingConfig:
 
 
 @dataclass
+class OutputConfig:
+    """Vocabulary-shortlist head settings (reference config.py:340-346)."""
+    mode: str = "full"
+    num_clusters: int = 64
+    shortlist_top_clusters: int = 2
+    shortlist_max_tokens: int = 128
+    hard_negatives: int = 32
+    random_negatives: int = 32
+
+    def __post_init__(self) -> None:
+        if self.mode not in ("full", "shortlist"):
+            raise ValueError("output.mode must be 'full' or 'shortlist'")
+
+
+@dataclass
 class ExperimentConfig:
     model: ModelConfig = field(default_factory=ModelConfig)
     training: TrainingConfig = field(default_factory=TrainingConfig)
+    output: OutputConfig = field(default_factory=OutputConfig)
 
 
 def _build(cls, data: dict[str, Any], path: str):
@@ -143,4 +160,5 @@ def load_config(path: str | Path) -> ExperimentConfig:
 
     raw = yaml.safe_load(Path(path).read_text()) or {}
     return ExperimentConfig(model=_build(ModelConfig, raw.get("model", {}), "model"),
-                            training=_build(TrainingConfig, raw.get("training", {}), "training"))
+                            training=_build(TrainingConfig, raw.get("training", {}), "training"),
+                            output=_build(OutputConfig, raw.get("output", {}), "output"))

@@ -33,8 +33,9 @@ def _block_shapes(prefix: str, cfg: ModelConfig) -> list[tuple[str, tuple]]:
             (f"{prefix}.mlp.wug.weight", (2 * f, d)), (f"{prefix}.mlp.wd.weight", (d, f))]
 
 
-def parameter_shapes(cfg: ModelConfig) -> list[tuple[str, tuple]]:
-    """Parameter names and shapes in the reference's registration order (models.py:78-93, 125-151)."""
+def parameter_shapes(cfg: ModelConfig, num_clusters: int = 64) -> list[tuple[str, tuple]]:
+    """Parameter names and shapes in the reference's registration order (models.py:78-93, 125-151);
+    `num_clusters` sizes the shortlist head's cluster router (output.py:29)."""
     d, f, v = cfg.d_model, cfg.d_ff, cfg.vocab_size
     out: list[tuple[str, tuple]] = [("embed.weight", (v, d))]
     if cfg.topology == "dense":
@@ -66,15 +67,15 @@ def parameter_shapes(cfg: ModelConfig) -> list[tuple[str, tuple]]:
             ("macro.bias", (r, k, d))]
     for i in range(cfg.n_coda):
         out += _block_shapes(f"coda.{i}", cfg)
-    return out + [("final_norm.weight", (d,))]
+    return out + [("final_norm.weight", (d,)), ("shortlist_head.cluster_router.weight", (num_clusters, d))]
 
 
-def init_parameters(cfg: ModelConfig, seed: int = 0, std: float = 0.02) -> dict[str, torch.Tensor]:
+def init_parameters(cfg: ModelConfig, seed: int = 0, std: float = 0.02, num_clusters: int = 64) -> dict[str, torch.Tensor]:
     """Seeded benchmark initialisation: tensors with >= 2 dims ~ N(0, std) from one CPU generator in
     registration order; norm gains and per-pass scales 1; the input-skip gain 0.1; biases 0."""
     gen = torch.Generator().manual_seed(seed)
     params: dict[str, torch.Tensor] = {}
-    for name, shape in parameter_shapes(cfg):
+    for name, shape in parameter_shapes(cfg, num_clusters):
         if len(shape) >= 2:
             params[name] = torch.randn(shape, generator=gen, dtype=torch.float32) * std
         elif name.endswith(("norm1.weight", "norm2.weight", "final_norm.weight", "pass_attn_scale", "pass_mlp_scale")):
@@ -90,7 +91,8 @@ def lr_group_of(name: str, topology: str) -> str:
     if topology == "dense":
         return "dense"
     for prefix, group in (("embed.", "embedding"), ("prelude.", "prelude"), ("core.", "core"), ("macro.", "macro"),
-                          ("coda.", "coda"), ("final_norm.", "coda"), ("lm_head.", "output"), ("router.", "router")):
+                          ("coda.", "coda"), ("final_norm.", "coda"), ("lm_head.", "output"), ("router.", "router"),
+                          ("shortlist_head.", "output")):
         if name.startswith(prefix):
             return group
     raise KeyError(name)
@@ -167,6 +169,9 @@ class TrainEngine:
         self.dense = cfg.topology == "dense"
         if self.dense != (tr.mode == "dense_exact"):
             raise ValueError("mode dense_exact needs topology 'dense'; recursive_macro needs 'recursive'")
+        self.oc = config.output
+        self.shortlist = tr.mode == "recursive_macro_shortlist"
+        self.n_clusters = self.oc.num_clusters
         self.audit_k = int(tr.audit_fixed_count_per_batch or 0)
         if self.audit_k:
             if self.dense:
@@ -181,14 +186,15 @@ class TrainEngine:
         if self.S > 256:
             raise NotImplementedError("seq_len <= 256")
         dev, f32, bf = self.device, torch.float32, torch.bfloat16
-        init = params if params is not None else init_parameters(cfg, seed=tr.seed)
-        self.params = {n: init[n].detach().to(dev, f32).contiguous().clone() for n, _ in parameter_shapes(cfg)}
+        init = params if params is not None else init_parameters(cfg, seed=tr.seed, num_clusters=self.n_clusters)
+        self._shapes = [(n, sh) for n, sh in parameter_shapes(cfg, self.n_clusters) if n in init]
+        self.params = {n: init[n].detach().to(dev, f32).contiguous().clone() for n, _ in self._shapes}
         self.global_step = 0
         self.tokens_seen = 0
         self.usage_ema = torch.zeros(cfg.recipe_count, dtype=f32)
 
         # ---- which parameters receive a gradient in this mode (everything else is never touched)
-        names = [n for n, _ in parameter_shapes(cfg)]
+        names = [n for n, _ in self._shapes]
         if self.dense:
             self.trainable = names
         else:
@@ -284,6 +290,18 @@ class TrainEngine:
                               recipe_id=e(B, dtype=i32), recipe_id_by_pass=e(B, cfg.t_max, dtype=i32),
                               depth_id=e(B, dtype=i32), depth=e(B, dtype=i32))
             self.router_scratch = e(A.ROUTER_MAX_R + B * (2 * hid + r + k + d) + 4)
+        if self.shortlist:
+            oc, i32 = self.oc, torch.int32
+            if "shortlist_head.cluster_router.weight" not in self.params:
+                raise ValueError("recursive_macro_shortlist needs shortlist_head.cluster_router.weight")
+            self.sl_tc = min(oc.shortlist_top_clusters, oc.num_clusters)
+            self.cluster_w16 = torch.empty(oc.num_clusters, d, dtype=bf, device=dev)
+            ops.cast_bf16(self.params["shortlist_head.cluster_router.weight"], self.cluster_w16)
+            self.cluster_logits = e(M, oc.num_clusters)
+            self.top_clusters = e(M, self.sl_tc, dtype=i32)
+            self.random_negs = torch.zeros(M, max(oc.random_negatives, 1), dtype=i32, device=dev)
+            self.shortlist_ids = e(M, oc.shortlist_max_tokens, dtype=i32)
+            self.shortlist_dups = e(M, dtype=i32)
         self.audit = None
         self._side_stream = torch.cuda.Stream(device=dev) if (self.audit_k and dev.type == "cuda") else None
         if self.audit_k:
@@ -459,10 +477,22 @@ class TrainEngine:
                 x = self._block_fwd(blk, x)
         x_last = x
         o.rmsnorm_fwd(x_last, p["final_norm.weight"], self.hidden16, self.rstd_f)
-        o.gemm(self.hidden16, sh["embed.weight"], self.logits, M=M, N=V, K=d)
-        if self.audit is not None:
-            self.audit.save_hot_logits()
-        o.ce_fwd_bwd(self.logits, targets, self.row_weight, S, self.loss_tok, self.logits)   # logits -> dlogits in place
+        if self.shortlist:
+            # cluster router -> top clusters -> shortlist -> gathered-row logits + CE (output.py:72-136); the gradient
+            # comes back as a dense, otherwise-zero [M, V] row block so that backward is the full-vocabulary one
+            oc = self.oc
+            o.gemm(self.hidden16, self.cluster_w16, self.cluster_logits, M=M, N=oc.num_clusters, K=d, epilogue=A.EPI_F32)
+            o.topk_lowest_index(self.cluster_logits, self.sl_tc, self.top_clusters)
+            o.shortlist_build(targets, self.top_clusters, self.random_negs, self.shortlist_ids, self.shortlist_dups,
+                              V=V, C=oc.num_clusters, TC=self.sl_tc, HN=oc.hard_negatives, RN=oc.random_negatives,
+                              K=oc.shortlist_max_tokens)
+            o.shortlist_ce(self.hidden16, sh["embed.weight"], self.shortlist_ids, self.row_weight, S, self.loss_tok, None,
+                           self.logits)
+        else:
+            o.gemm(self.hidden16, sh["embed.weight"], self.logits, M=M, N=V, K=d)
+            if self.audit is not None:
+                self.audit.save_hot_logits()
+            o.ce_fwd_bwd(self.logits, targets, self.row_weight, S, self.loss_tok, self.logits)   # logits -> dlogits in place
         o.segment_sum(self.loss_tok, self.loss_per_sample, B, S)
         o.segment_sum(self.loss_per_sample, self.scalars[0:1], 1, B)
         if self.audit is not None:
@@ -552,6 +582,11 @@ class TrainEngine:
         self.targets.copy_(targets, non_blocking=True)
         if self.audit is not None:
             self.audit.choose(self.tr.seed + 10_000 + self.global_step)
+        if self.shortlist and self.oc.random_negatives > 0:
+            # the reference draws them with a generator seeded by seed + step (output.py:86-94, training.py:1364)
+            gen = torch.Generator().manual_seed(self.tr.seed + self.global_step)
+            rn = torch.randint(0, self.cfg.vocab_size, (self.B, self.S, self.oc.random_negatives), generator=gen)
+            self.random_negs.copy_(rn.view(self.M, -1).to(torch.int32), non_blocking=True)
 
     def _run_step_kernels(self, optimizer: bool) -> None:
         if not self.use_cuda_graph or not optimizer or self._eager_steps_left > 0:

@@ -247,6 +247,19 @@ class CudaOps:
     def phi_bwd_scratch_floats(B, S, d, m) -> int:
         return B * S * d + B * S * m + 3 * B * d + B * m * d + B * 3 * d * m
 
+    # ------------------------------------------------------------------ vocabulary shortlist
+    def shortlist_build(self, targets, top_clusters, random_negs, shortlist, dup_count, *, V, C, TC, HN, RN, K) -> None:
+        self._call("rte_shortlist_build", _ptr(targets), _ptr(top_clusters), _ptr(random_negs), _ptr(shortlist),
+                   _ptr(dup_count), shortlist.shape[0], V, C, TC, HN, RN, K, _ptr(self.status), self.stream)
+
+    def shortlist_ce(self, hidden, W, shortlist, row_weight, S, loss_tok, logits_out, dlogits_dense) -> None:
+        rows, K = shortlist.shape
+        self._call("rte_shortlist_ce", _ptr(hidden), _ptr(W), _ptr(shortlist), _ptr(row_weight), S, _ptr(loss_tok),
+                   _ptr(logits_out), _ptr(dlogits_dense), rows, hidden.shape[-1], W.shape[0], K, self.stream)
+
+    def random_tokens(self, out, vocab: int, seed) -> None:
+        self._call("rte_random_tokens", _ptr(out), out.numel(), vocab, _ptr(seed), self.stream)
+
     # ------------------------------------------------------------------ exact-audit replay helpers
     def gather_rows(self, src, idx, dst, n: int, row_bytes: int) -> None:
         self._call("rte_gather_rows", _ptr(src), _ptr(idx), _ptr(dst), n, row_bytes, self.stream)

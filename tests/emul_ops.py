@@ -290,6 +290,37 @@ class EmulOps:
         if vals is not None:
             vals.copy_(torch.gather(scores, -1, order))
 
+    # ---------------------------------------------------------------- vocabulary shortlist
+    def shortlist_build(self, targets, top_clusters, random_negs, shortlist, dup_count, *, V, C, TC, HN, RN, K):
+        self.launches += 1
+        rows, mpc = shortlist.shape[0], -(-V // C)
+        tg = targets.view(-1).tolist()
+        for r in range(rows):
+            seq = [tg[r]]
+            for c in top_clusters[r].tolist():
+                seq += [(c + j * C) if c + j * C < V else 0 for j in range(mpc)]
+            seq += [p % V for p in range(HN)] + random_negs[r, :RN].tolist() + [p % V for p in range(K)]
+            seq += [(tg[r] + p) % V for p in range(2 * K)]
+            uniq = list(dict.fromkeys(seq))
+            shortlist[r] = torch.tensor(uniq[:K], dtype=shortlist.dtype)
+            if dup_count is not None:
+                dup_count[r] = len(seq) - len(uniq)
+
+    def shortlist_ce(self, hidden, W, shortlist, row_weight, S, loss_tok, logits_out, dlogits_dense):
+        self.launches += 1
+        rows, K = shortlist.shape
+        lg = torch.einsum("rd,rkd->rk", hidden.float(), W.float()[shortlist.long()]).to(torch.bfloat16).float()
+        lse = torch.logsumexp(lg, dim=-1)
+        loss_tok.copy_(lse - lg[:, 0])
+        if logits_out is not None:
+            logits_out.copy_(lg.to(torch.bfloat16))
+        if dlogits_dense is not None:
+            g = torch.exp(lg - lse[:, None])
+            g[:, 0] -= 1.0
+            g = g * row_weight.repeat_interleave(S)[:, None]
+            dlogits_dense.zero_()
+            dlogits_dense.scatter_(1, shortlist.long(), g.to(torch.bfloat16))
+
     # ---------------------------------------------------------------- macro operator (via autograd here)
     def _phi(self, h0, p, rid, sid, s_cfg, B, S, d, m):
         h = h0.view(B, S, d)

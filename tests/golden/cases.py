@@ -30,6 +30,17 @@ GOLDEN_CASES = {
                    fixed_depth=None, audit_fixed_count_per_batch=None),
         steps=6,
     ),
+    # vocabulary-shortlist head (recursive_macro_shortlist) with one audited sample per batch
+    "small_shortlist": dict(
+        model=dict(vocab_size=96, d_model=32, n_heads=4, d_ff=64, n_dense_layers=3, n_prelude=1, n_coda=1,
+                   t_max=4, depth_choices=(1, 2, 4), attn_banks=1, ffn_banks=1, head_groups=4, ffn_groups=4,
+                   active_head_groups=1, active_ffn_groups=2, recipe_count=4, macro_rank=8, shortlist_clusters=8),
+        train=dict(mode="recursive_macro_shortlist", lr=2e-3, weight_decay=0.05, batch_size=4, seq_len=12, seed=9,
+                   fixed_depth=None, audit_fixed_count_per_batch=1),
+        output=dict(mode="shortlist", num_clusters=8, shortlist_top_clusters=2, shortlist_max_tokens=16,
+                    hard_negatives=4, random_negatives=4),
+        steps=6,
+    ),
     "small_dense": dict(
         model=dict(topology="dense", vocab_size=96, d_model=32, n_heads=4, d_ff=64, n_dense_layers=2, n_prelude=1,
                    n_coda=1, t_max=4, depth_choices=(1, 2, 4), attn_banks=1, ffn_banks=1, head_groups=4,
@@ -43,3 +54,7 @@ GOLDEN_CASES = {
 
 def oracle_cfgs(case: dict) -> tuple[O.ModelCfg, O.TrainCfg]:
     return O.ModelCfg(**case["model"]), O.TrainCfg(**case["train"])
+
+
+def oracle_output_cfg(case: dict) -> "O.OutputCfg | None":
+    return O.OutputCfg(**case["output"]) if "output" in case else None

@@ -35,6 +35,7 @@ from recursive_training_engine.kernels import reference as RK  # noqa: E402
 
 def reference_experiment(case: dict, run_dir: str) -> RC.ExperimentConfig:
     m = dict(case["model"])
+    m.pop("shortlist_clusters", None)
     m.setdefault("topology", "recursive")
     m["depth_choices"] = list(m["depth_choices"])
     t = dict(case["train"])
@@ -49,13 +50,14 @@ def reference_experiment(case: dict, run_dir: str) -> RC.ExperimentConfig:
         audit_gradient_correction=audited, lambda_cons=0.0, grad_clip_norm=t.get("grad_clip_norm"),
         fused_optimizer=False, foreach_optimizer=True, allow_tf32=False, log_every=10_000,
     )
-    return RC.ExperimentConfig(model=RC.ModelConfig(**m), training=tr, run_name="golden", output_dir=run_dir)
+    out = RC.OutputConfig(**case["output"]) if "output" in case else RC.OutputConfig()
+    return RC.ExperimentConfig(model=RC.ModelConfig(**m), training=tr, output=out, run_name="golden", output_dir=run_dir)
 
 
 def load_oracle_init_into_reference(engine: TrainEngine, cfg: O.ModelCfg, seed: int) -> None:
     model = engine.recursive_model if engine.recursive_model is not None else engine.dense_model
     init = O.init_params(cfg, seed=seed)
-    names = [n for n, _ in model.named_parameters() if not n.startswith("shortlist_head.")]
+    names = [n for n, _ in model.named_parameters()]
     assert names == [n for n, _ in O.param_shapes(cfg)], "oracle parameter inventory differs from the reference's"
     with torch.no_grad():
         for name, param in model.named_parameters():
@@ -104,6 +106,8 @@ def run_case(name: str, case: dict) -> dict[str, np.ndarray]:
                     out["h0_head"] = hot.meta.h0.detach().flatten()[:32].numpy().copy()
                     out["phi_head"] = hot.meta.recurrent_hidden.detach().flatten()[:32].numpy().copy()
                 out["logits_head"] = hot.logits.detach().flatten()[:32].numpy().copy()
+                if hot.meta.shortlist is not None:
+                    out["shortlist"] = hot.meta.shortlist.shortlist.numpy().copy()
                 if res.audit is not None and res.audit.exact is not None:
                     out["audit_mask"] = res.audit.audit_mask.numpy().copy()
                     out["exact_loss_per_sample"] = res.audit.exact.loss_per_sample.detach().numpy().copy()

@@ -290,6 +290,53 @@ def test_topk_lowest_index_bit_exact(ops, rows, n, k):
     assert torch.equal(gv.cpu(), vals)
 
 
+# ------------------------------------------------------------------ vocabulary shortlist
+@pytest.mark.parametrize("B,S,V,C,TC,HN,RN,K", [(3, 7, 96, 8, 2, 4, 4, 16), (4, 33, 2048, 64, 2, 32, 32, 128),
+                                                (2, 5, 50, 7, 3, 60, 0, 50), (2, 9, 4096, 64, 1, 0, 8, 256)])
+def test_shortlist_build_bit_exact(ops, B, S, V, C, TC, HN, RN, K):
+    g = torch.Generator().manual_seed(V + K)
+    oc = O.OutputCfg(mode="shortlist", num_clusters=C, shortlist_top_clusters=TC, shortlist_max_tokens=K,
+                     hard_negatives=HN, random_negatives=RN)
+    targets = torch.randint(0, V, (B, S), generator=g)
+    targets[0, 0], targets[-1, -1] = 0, V - 1
+    top = torch.stack([torch.randperm(C, generator=g)[:TC] for _ in range(B * S)]).view(B, S, TC)
+    rnd = torch.randint(0, V, (B, S, RN), generator=g)
+    cands = O.shortlist_candidates(targets, top, rnd, V, oc)
+    want = O.dedupe_preserve_first(cands, K)
+    dups = torch.tensor([cands.shape[-1] - len(set(r.tolist())) for r in cands.view(B * S, -1)])
+    out = torch.full((B * S, K), -1, dtype=torch.int32, device=DEV)
+    dc = torch.zeros(B * S, dtype=torch.int32, device=DEV)
+    rnd_dev = rnd.view(B * S, RN).to(torch.int32).to(DEV) if RN else torch.zeros(1, dtype=torch.int32, device=DEV)
+    ops.shortlist_build(targets.to(DEV), top.view(B * S, TC).to(torch.int32).to(DEV), rnd_dev, out, dc,
+                        V=V, C=C, TC=TC, HN=HN, RN=RN, K=K)
+    ops.check_status()
+    assert torch.equal(out.cpu().long().view(B, S, K), want)
+    assert torch.equal(dc.cpu().long(), dups)
+    assert torch.equal(out[:, 0].cpu().long(), targets.view(-1))
+
+
+@pytest.mark.parametrize("rows,S,d,V,K", [(21, 7, 64, 96, 16), (256, 64, 512, 2048, 128)])
+def test_shortlist_ce_matches_reference_math(ops, rows, S, d, V, K):
+    g = torch.Generator().manual_seed(rows)
+    hidden = torch.randn(rows, d, generator=g).bfloat16()
+    W = (torch.randn(V, d, generator=g) * 0.2).bfloat16()
+    sl = torch.stack([torch.randperm(V, generator=g)[:K] for _ in range(rows)])
+    wgt = torch.rand(rows // S, generator=g) + 0.5
+    lg = torch.einsum("rd,rkd->rk", hidden.float(), W.float()[sl]).bfloat16().float().requires_grad_(True)
+    loss_tok = torch.nn.functional.cross_entropy(lg, torch.zeros(rows, dtype=torch.long), reduction="none")
+    (loss_tok.view(-1, S).sum(1) * wgt).sum().backward()
+    dense_ref = torch.zeros(rows, V).scatter_(1, sl, lg.grad)
+    out_loss = torch.zeros(rows, device=DEV)
+    out_lg = torch.zeros(rows, K, dtype=torch.bfloat16, device=DEV)
+    dense = torch.full((rows, V), 7.0, dtype=torch.bfloat16, device=DEV)
+    ops.shortlist_ce(hidden.to(DEV), W.to(DEV), sl.to(torch.int32).to(DEV), wgt.to(DEV), S, out_loss, out_lg, dense)
+    torch.cuda.synchronize()
+    assert (out_lg.cpu().float() - lg.detach()).abs().max() <= 0.02 * lg.detach().abs().max()
+    assert (out_loss.cpu() - loss_tok.detach()).abs().max() <= 2e-2
+    assert (dense.cpu().float() - dense_ref).abs().max() <= 1e-2 * dense_ref.abs().max() + 1e-3
+    assert (dense.cpu().float() != 0).sum(1).max() <= K
+
+
 # ------------------------------------------------------------------ macro operator
 @pytest.mark.parametrize("B,S,d,m,R", [(4, 16, 64, 8, 5), (6, 64, 128, 32, 5), (3, 40, 512, 32, 5), (2, 8, 64, 48, 3)])
 def test_macro_phi_fwd_bwd(ops, B, S, d, m, R):

@@ -8,18 +8,19 @@ import pytest
 import torch
 
 from oracle import rte_oracle as O
-from speedup_thingy_b200.config import ExperimentConfig, ModelConfig, TrainingConfig
+from speedup_thingy_b200.config import ExperimentConfig, ModelConfig, OutputConfig, TrainingConfig
 from speedup_thingy_b200.engine import TrainEngine, init_parameters, parameter_shapes
 from tests.golden.cases import GOLDEN_CASES
-from tests.test_engine_host import CASES
+from tests.test_engine_host import CASES, _oracle, _pair, _share_top_clusters
 
 pytestmark = pytest.mark.gpu
 GOLDEN = Path(__file__).resolve().parent / "golden"
 
 
-def _engine(model, train, **kw):
-    cfg = ExperimentConfig(ModelConfig(**model), TrainingConfig(**train))
-    params = init_parameters(cfg.model, seed=cfg.training.seed)
+def _engine(model, train, output=None, **kw):
+    model = {k: v for k, v in model.items() if k != "shortlist_clusters"}
+    cfg = ExperimentConfig(ModelConfig(**model), TrainingConfig(**train), OutputConfig(**(output or {})))
+    params = init_parameters(cfg.model, seed=cfg.training.seed, num_clusters=cfg.output.num_clusters)
     return cfg, params, TrainEngine(cfg, params, device="cuda:0", **kw)
 
 
@@ -31,13 +32,14 @@ def _stream(cfg, steps):
 
 @pytest.mark.parametrize("name", list(CASES))
 def test_first_step_loss_and_grads_match_oracle(name):
-    model, train = CASES[name]
-    cfg, params, eng = _engine(model, train, use_cuda_graph=False)
-    otr = O.TrainCfg(**{**train, "grad_clip_norm": None})
-    oracle = O.OracleTrainer(O.ModelCfg(**model), otr, {k: v.clone() for k, v in params.items()})
+    model, train, *rest = CASES[name]
+    cfg, params, eng = _engine(model, train, *rest, use_cuda_graph=False)
+    _, ocfg, _ = _pair(name)
+    oracle = _oracle(cfg, ocfg, O.TrainCfg(**{**train, "grad_clip_norm": None}), params)
     batch = next(_stream(cfg, 2))
-    ref_loss, ref_grads, info = oracle.loss_and_grads(*batch)
     loss, grads = eng.loss_and_grads(batch)
+    _share_top_clusters(eng, oracle)
+    ref_loss, ref_grads, info = oracle.loss_and_grads(*batch)
     assert abs(loss - float(ref_loss)) <= 1e-2 * abs(float(ref_loss))
     assert sorted(grads) == sorted(ref_grads)
     for n, g in grads.items():
@@ -77,6 +79,27 @@ def test_200_step_training_loss_within_one_percent():
     untouched = [n for n, _ in parameter_shapes(cfg.model) if n not in eng.trainable]
     for n in untouched:                      # grad-less parameters are never decayed or stepped
         assert torch.equal(eng.params[n].cpu(), params[n]), n
+
+
+def test_shortlist_loss_curve_matches_reference_golden():
+    """recursive_macro_shortlist with one audited sample per batch: the shortlist ids are bit-exact whenever the
+    top clusters agree, and the loss curve follows the reference's within 1 %."""
+    case = GOLDEN_CASES["small_shortlist"]
+    cfg, params, eng = _engine(case["model"], case["train"], case["output"])
+    gold = np.load(GOLDEN / "small_shortlist.npz")
+    it = _stream(cfg, case["steps"])
+    losses = []
+    for step in range(case["steps"]):
+        tokens, targets = next(it)
+        losses.append(eng.train_step((tokens, targets)).loss)
+        top = eng.top_clusters.view(eng.B, eng.S, -1).cpu().long()
+        gen = torch.Generator().manual_seed(cfg.training.seed + step)
+        rnd = torch.randint(0, cfg.model.vocab_size, (eng.B, eng.S, cfg.output.random_negatives), generator=gen)
+        want = O.dedupe_preserve_first(O.shortlist_candidates(targets, top, rnd, cfg.model.vocab_size,
+                                                              O.OutputCfg(**case["output"])), cfg.output.shortlist_max_tokens)
+        assert torch.equal(eng.shortlist_ids.view(eng.B, eng.S, -1).cpu().long(), want)
+    rel = np.abs(np.array(losses) - gold["losses"]) / np.abs(gold["losses"])
+    assert rel.max() <= 1e-2, (rel.max(), losses, gold["losses"])
 
 
 def test_graph_replay_equals_eager():

@@ -7,7 +7,7 @@ import pytest
 import torch
 
 from oracle import rte_oracle as O
-from tests.golden.cases import GOLDEN_CASES, oracle_cfgs
+from tests.golden.cases import GOLDEN_CASES, oracle_cfgs, oracle_output_cfg
 
 GOLDEN = Path(__file__).resolve().parent / "golden"
 
@@ -16,7 +16,7 @@ def _run(name):
     case = GOLDEN_CASES[name]
     cfg, tr = oracle_cfgs(case)
     gold = np.load(GOLDEN / f"{name}.npz")
-    trainer = O.OracleTrainer(cfg, tr, O.init_params(cfg, seed=tr.seed))
+    trainer = O.OracleTrainer(cfg, tr, O.init_params(cfg, seed=tr.seed), oc=oracle_output_cfg(case))
     stream = O.zipf_tokens(tr.batch_size * tr.seq_len * (case["steps"] + 2) + 1, cfg.vocab_size, seed=tr.seed)
     it = O.batches(stream, tr.batch_size, tr.seq_len)
     return case, cfg, tr, gold, trainer, it
@@ -41,6 +41,8 @@ def test_first_step_matches_reference(name):
         np.testing.assert_allclose(info["hot"]["h0"].detach().flatten()[:32].numpy(), gold["h0_head"], rtol=1e-4, atol=1e-6)
         np.testing.assert_allclose(info["hot"]["recurrent_hidden"].detach().flatten()[:32].numpy(), gold["phi_head"],
                                    rtol=1e-4, atol=1e-6)
+    if "shortlist" in gold:
+        assert np.array_equal(info["hot"]["shortlist"]["shortlist"].numpy(), gold["shortlist"])
     if "audit_mask" in gold:
         assert np.array_equal(info["mask"].numpy(), gold["audit_mask"])
         np.testing.assert_allclose(info["exact"]["loss_per_sample"].detach().numpy(), gold["exact_loss_per_sample"],
