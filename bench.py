@@ -221,7 +221,7 @@ def main() -> None:
         ms_dev, ms_e2e = float(t[0]), float(t[1])
     eng.ops.check_status()
 
-    # ---- roofline of the dominant kernel (the tcgen05 GEMM): per-launch CUDA-event timing in an eager step
+    # ---- roofline of the dominant kernel (the tcgen05 GEMM): CUDA-event nodes around every launch of a captured step
     roof = None
     if rank == 0 and not args.no_roofline:
         roof = eng.gemm_roofline(repeats=max(3, min(K, 10)))
@@ -251,6 +251,8 @@ def main() -> None:
             line["roofline"] = {"bound": "tensor", "achieved": roof["tflops"], "peak": peak, "unit": "TFLOP/s",
                                 "frac": roof["tflops"] / peak, "traffic": None, "of": which + " (sustained)",
                                 "kernel": "gemm_tcgen05_kernel", "launches_per_step": roof["launches"],
+                                "gemm_ms_per_step": roof["gemm_ms_per_step"],
+                                "timing": "event-record nodes around each launch inside a captured step",
                                 "per_shape": roof["per_shape"]}
         if world == 1 and not args.no_cpu_baseline:
             threads = os.cpu_count() or 1

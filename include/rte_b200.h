@@ -127,6 +127,11 @@ int rte_colsum_partials(const float* partial, int32_t n_rows, int32_t d, float* 
  * written by rte_rope_table (the reference's cached buffers, layers.py:37-44); without it the kernels compute
  * the angles themselves.                                                                                       */
 int rte_rope_table(float* out, int32_t S, int32_t head_dim, rte_stream_t stream);
+/* k_rope_apply (kernels/reference.py:20-28) as an operator of its own: out = x*cos + rotate_half(x)*sin over
+ * x [rows, S, head_dim] (rows = B*H), cos/sin f32 [S, head_dim]; f32 or bf16 data; adjoint != 0 applies the
+ * transposed rotation (the operator's backward).  out may alias x.                                              */
+int rte_rope_apply(const void* x, const float* cos_tab, const float* sin_tab, void* out, int64_t rows, int32_t S,
+                   int32_t head_dim, int32_t is_bf16, int32_t adjoint, rte_stream_t stream);
 int rte_attn_fwd(const void* qkv, int32_t ld_qkv, int32_t sec, void* y, int32_t ld_y, float* lse,
                  const float* rope_table, int32_t B, int32_t S, int32_t n_heads, int32_t head_dim,
                  rte_stream_t stream);
@@ -208,6 +213,13 @@ int rte_macro_phi_bwd(const float* h0, const float* dout, const rte_phi_params* 
                       int32_t S, int32_t d, int32_t m, int32_t R, int32_t K_strides, float eps,
                       rte_stream_t stream);
 
+/* -------------------------------------------------- SwiGLU as its own pass (layers.py:78-87), for callers that
+ * keep the W_ug GEMM's plain bf16 output: ug bf16 [rows, 2F] = (up | gate); z bf16 [rows, F] = up * silu(gate);
+ * backward: dug = (dz * gate*sigmoid(gate) | dz * up * d silu(gate)).  The same arithmetic exists as GEMM
+ * epilogues (RTE_EPI_SWIGLU_FWD/BWD); the step picks whichever is faster at its size.                         */
+int rte_swiglu_fwd(const void* ug, void* z, int64_t rows, int32_t F, rte_stream_t stream);
+int rte_swiglu_bwd(const void* ug, const void* dz, void* dug, int64_t rows, int32_t F, rte_stream_t stream);
+
 /* -------------------------------------------------- fp32 -> bf16 shadow copies of weights */
 int rte_cast_f32_bf16(const float* src, void* dst, int64_t n, rte_stream_t stream);
 int rte_add_f32(float* dst, const float* src, int64_t n, rte_stream_t stream);   /* dst += src */
@@ -257,6 +269,10 @@ int rte_shortlist_ce(const void* hidden, const void* W, const int32_t* shortlist
                      float* loss_tok, void* logits_out, void* dlogits_dense, int32_t rows, int32_t d, int32_t V,
                      int32_t K, rte_stream_t stream);
 int rte_random_tokens(int32_t* out, int64_t n, int32_t vocab, const int64_t* seed, rte_stream_t stream);
+/* dense bf16 [rows, V] = 0 except dense[r, ids[r, k]] = vals[r, k] (ids distinct per row): turns a gradient over
+ * shortlist slots (backward of k_logits_shortlist, reference.py:141-143) into rows the dense GEMMs can consume. */
+int rte_scatter_cols_bf16(const void* vals, const int32_t* ids, void* dense, int32_t rows, int32_t V, int32_t K,
+                          rte_stream_t stream);
 
 /* ------------------------------------------------ exact-audit replay helpers (audit.py:245-387; models.py:605-679;
  * layers.py:831-870).  The audited subset has a fixed size n (fixed-count sampler), chosen on the host.

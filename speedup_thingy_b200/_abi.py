@@ -76,6 +76,7 @@ PROTOTYPES = {
     "rte_rmsnorm_bwd": (C.c_int, [c_vp] * 12 + [c_i32, c_i32, c_i32, P(c_i32), c_vp]),
     "rte_colsum_partials": (C.c_int, [c_vp, c_i32, c_i32, c_vp, c_i32, c_vp]),
     "rte_rope_table": (C.c_int, [c_vp, c_i32, c_i32, c_vp]),
+    "rte_rope_apply": (C.c_int, [c_vp, c_vp, c_vp, c_vp, c_i64, c_i32, c_i32, c_i32, c_i32, c_vp]),
     "rte_attn_fwd": (C.c_int, [c_vp, c_i32, c_i32, c_vp, c_i32, c_vp, c_vp, c_i32, c_i32, c_i32, c_i32, c_vp]),
     "rte_attn_bwd": (C.c_int, [c_vp, c_i32, c_i32, c_vp, c_vp, c_i32, c_vp, c_vp, c_vp, c_i32, c_i32, c_i32, c_i32, c_vp]),
     "rte_ce_fwd_bwd": (C.c_int, [c_vp, c_i32, c_vp, c_vp, c_i32, c_vp, c_vp, c_i32, c_i32, c_vp, c_vp]),
@@ -88,6 +89,8 @@ PROTOTYPES = {
                           [c_f32, c_vp]),
     "rte_macro_phi_bwd": (C.c_int, [c_vp, c_vp, P(PhiParams), c_vp, c_vp, c_f32, c_vp, c_vp, c_vp, c_vp, P(PhiGrads),
                                     c_vp] + [c_i32] * 6 + [c_f32, c_vp]),
+    "rte_swiglu_fwd": (C.c_int, [c_vp, c_vp, c_i64, c_i32, c_vp]),
+    "rte_swiglu_bwd": (C.c_int, [c_vp, c_vp, c_vp, c_i64, c_i32, c_vp]),
     "rte_cast_f32_bf16": (C.c_int, [c_vp, c_vp, c_i64, c_vp]),
     "rte_add_f32": (C.c_int, [c_vp, c_vp, c_i64, c_vp]),
     "rte_fill_f32": (C.c_int, [c_vp, c_f32, c_i64, c_vp]),
@@ -98,6 +101,7 @@ PROTOTYPES = {
     "rte_shortlist_build": (C.c_int, [c_vp, c_vp, c_vp, c_vp, c_vp] + [c_i32] * 7 + [c_vp, c_vp]),
     "rte_shortlist_ce": (C.c_int, [c_vp, c_vp, c_vp, c_vp, c_i32, c_vp, c_vp, c_vp, c_i32, c_i32, c_i32, c_i32, c_vp]),
     "rte_random_tokens": (C.c_int, [c_vp, c_i64, c_i32, c_vp, c_vp]),
+    "rte_scatter_cols_bf16": (C.c_int, [c_vp, c_vp, c_vp, c_i32, c_i32, c_i32, c_vp]),
     "rte_gather_rows": (C.c_int, [c_vp, c_vp, c_vp, c_i32, c_i64, c_vp]),
     "rte_scatter_add_rows_f32": (C.c_int, [c_vp, c_vp, c_vp, c_i32, c_i64, c_vp]),
     "rte_audit_route": (C.c_int, [c_vp, c_vp, c_vp, c_vp, c_vp, c_i32, c_i32, c_vp]),

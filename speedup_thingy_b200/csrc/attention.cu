@@ -302,6 +302,27 @@ __global__ void rope_table_kernel(float* __restrict__ out, int S, int hd) {
   out[2 * i + 1] = sn;
 }
 
+// Stand-alone rotary application over [rows, S, hd] tensors (rows = B*H) with caller-supplied cos/sin [S, hd]
+// (the layout of the reference's cached buffers after repeat_interleave).  adjoint != 0 applies the transpose
+// of the rotation (the backward pass of the same operator).
+template <typename T>
+__global__ void rope_apply_kernel(const T* __restrict__ x, const float* __restrict__ cs, const float* __restrict__ sn,
+                                  T* __restrict__ out, long long pairs, int S, int hd, int adjoint) {
+  const int hp = hd / 2;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < pairs; i += (long long)gridDim.x * blockDim.x) {
+    const int pr = (int)(i % hp);
+    const int pos = (int)((i / hp) % S);
+    const float a = (float)x[2 * i], b = (float)x[2 * i + 1];
+    const float c0 = cs[pos * hd + 2 * pr], c1 = cs[pos * hd + 2 * pr + 1];
+    const float s0 = sn[pos * hd + 2 * pr], s1 = sn[pos * hd + 2 * pr + 1];
+    float o0, o1;
+    if (!adjoint) { o0 = a * c0 - b * s0; o1 = b * c1 + a * s1; }       // x*cos + rotate_half(x)*sin
+    else          { o0 = a * c0 + b * s1; o1 = b * c1 - a * s0; }
+    out[2 * i] = (T)o0;
+    out[2 * i + 1] = (T)o1;
+  }
+}
+
 }  // namespace
 
 #define RTE_ATT_DISPATCH(FN, ...)                                              \
@@ -349,6 +370,23 @@ extern "C" int rte_rope_table(float* out, int32_t S, int32_t head_dim, rte_strea
   RTE_CHECK_ARG(out && S > 0 && head_dim > 0 && head_dim % 2 == 0);
   const int n = S * (head_dim / 2);
   rope_table_kernel<<<rte::ceil_div(n, 256), 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(out, S, head_dim);
+  RTE_LAUNCH_CHECK();
+  return RTE_OK;
+}
+
+extern "C" int rte_rope_apply(const void* x, const float* cos_tab, const float* sin_tab, void* out, int64_t rows, int32_t S,
+                              int32_t head_dim, int32_t is_bf16, int32_t adjoint, rte_stream_t stream) {
+  RTE_CHECK_ARG(x && cos_tab && sin_tab && out && rows > 0 && S > 0 && head_dim > 0 && head_dim % 2 == 0);
+  const long long pairs = rows * (long long)S * (head_dim / 2);
+  long long g = (pairs + 255) / 256;
+  if (g > 148 * 16) g = 148 * 16;
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  if (is_bf16)
+    rope_apply_kernel<__nv_bfloat16><<<(int)g, 256, 0, st>>>(reinterpret_cast<const __nv_bfloat16*>(x), cos_tab, sin_tab,
+                                                            reinterpret_cast<__nv_bfloat16*>(out), pairs, S, head_dim, adjoint);
+  else
+    rope_apply_kernel<float><<<(int)g, 256, 0, st>>>(reinterpret_cast<const float*>(x), cos_tab, sin_tab,
+                                                    reinterpret_cast<float*>(out), pairs, S, head_dim, adjoint);
   RTE_LAUNCH_CHECK();
   return RTE_OK;
 }

@@ -132,6 +132,20 @@ shortlist_ce_kernel(const __nv_bfloat16* __restrict__ hidden, const __nv_bfloat1
   }
 }
 
+// dense[row, ids[row, k]] = vals[row, k], zero elsewhere (ids distinct within a row)
+__global__ void __launch_bounds__(128)
+scatter_cols_kernel(const __nv_bfloat16* __restrict__ vals, const int32_t* __restrict__ ids, __nv_bfloat16* __restrict__ dense,
+                    int V, int K) {
+  const int row = blockIdx.x;
+  uint4* dr = reinterpret_cast<uint4*>(dense + (size_t)row * V);
+  for (int i = threadIdx.x; i < V / 8; i += blockDim.x) dr[i] = make_uint4(0u, 0u, 0u, 0u);
+  __syncthreads();
+  for (int k = threadIdx.x; k < K; k += blockDim.x) {
+    const int id = ids[(size_t)row * K + k];
+    if (id >= 0 && id < V) dense[(size_t)row * V + id] = vals[(size_t)row * K + k];
+  }
+}
+
 // out[i] = hash(seed, i) mod vocab  (counter-based, reproducible; used when no host-drawn negatives are supplied)
 __global__ void random_tokens_kernel(int32_t* __restrict__ out, long long n, int vocab, const int64_t* __restrict__ seed) {
   const unsigned long long s = (unsigned long long)(*seed);
@@ -181,6 +195,16 @@ extern "C" int rte_shortlist_ce(const void* hidden, const void* W, const int32_t
   shortlist_ce_kernel<<<rows, 128, smem, ST(stream)>>>(reinterpret_cast<const __nv_bfloat16*>(hidden),
       reinterpret_cast<const __nv_bfloat16*>(W), shortlist, row_weight, S, loss_tok,
       reinterpret_cast<__nv_bfloat16*>(logits_out), reinterpret_cast<__nv_bfloat16*>(dlogits_dense), d, V, K);
+  RTE_LAUNCH_CHECK();
+  return RTE_OK;
+}
+
+extern "C" int rte_scatter_cols_bf16(const void* vals, const int32_t* ids, void* dense, int32_t rows, int32_t V, int32_t K,
+                                     rte_stream_t stream) {
+  RTE_CHECK_ARG(vals && ids && dense && rows > 0 && V > 0 && V % 8 == 0 && K > 0);
+  if (reinterpret_cast<uintptr_t>(dense) & 15) return RTE_ERR_ALIGNMENT;
+  scatter_cols_kernel<<<rows, 128, 0, ST(stream)>>>(reinterpret_cast<const __nv_bfloat16*>(vals), ids,
+                                                    reinterpret_cast<__nv_bfloat16*>(dense), V, K);
   RTE_LAUNCH_CHECK();
   return RTE_OK;
 }

@@ -129,6 +129,7 @@ class _Temps:
         d, f = cfg.d_model, cfg.d_ff
         bf, f32 = torch.bfloat16, torch.float32
         self.dug = torch.empty(M, 2 * f, dtype=bf, device=device)
+        self.dz16 = torch.empty(M, f, dtype=bf, device=device)
         self.dn16, self.dy16, self.dx16 = (torch.empty(M, d, dtype=bf, device=device) for _ in range(3))
         self.dqkv = torch.empty(M, 3 * d, dtype=bf, device=device)
         self.dxa, self.dxb, self.dxc = (torch.empty(M, d, dtype=f32, device=device) for _ in range(3))
@@ -138,7 +139,7 @@ class _Temps:
 class TrainEngine:
     def __init__(self, config: ExperimentConfig, params: dict[str, torch.Tensor] | None = None, *,
                  device: str | torch.device = "cuda:0", ops=None, use_cuda_graph: bool = True,
-                 process_group=None, bucket_cap_mb: float = 25.0):
+                 process_group=None, bucket_cap_mb: float = 25.0, swiglu_fuse_max_rows: int = 1024):
         self.config = config
         self.cfg, self.tr = config.model, config.training
         self.device = torch.device(device)
@@ -169,6 +170,7 @@ class TrainEngine:
         self.dense = cfg.topology == "dense"
         if self.dense != (tr.mode == "dense_exact"):
             raise ValueError("mode dense_exact needs topology 'dense'; recursive_macro needs 'recursive'")
+        self.swiglu_fuse_max_rows = swiglu_fuse_max_rows
         self.oc = config.output
         self.shortlist = tr.mode == "recursive_macro_shortlist"
         self.n_clusters = self.oc.num_clusters
@@ -409,7 +411,11 @@ class TrainEngine:
         o.attn_fwd(blk.qkv, blk.y, blk.lse, B=blk.B, S=blk.S, n_heads=cfg.n_heads, head_dim=cfg.head_dim)
         o.gemm(blk.y, sh[f"{pre}.attn.wo.weight"], blk.u, M=M, N=d, K=d, epilogue=A.EPI_F32, residual=x_in)
         o.rmsnorm_fwd(blk.u, p[f"{pre}.norm2.weight"], blk.n2, blk.rstd2)
-        o.gemm(blk.n2, sh[f"{pre}.mlp.wug.weight"], blk.z, M=M, N=2 * f, K=d, epilogue=A.EPI_SWIGLU_FWD, out2=blk.ug, pair=f)
+        if M <= self.swiglu_fuse_max_rows:
+            o.gemm(blk.n2, sh[f"{pre}.mlp.wug.weight"], blk.z, M=M, N=2 * f, K=d, epilogue=A.EPI_SWIGLU_FWD, out2=blk.ug, pair=f)
+        else:       # at large M the plain-store GEMM plus one vectorised pass beats the fused epilogue (measured)
+            o.gemm(blk.n2, sh[f"{pre}.mlp.wug.weight"], blk.ug, M=M, N=2 * f, K=d)
+            o.swiglu_fwd(blk.ug, blk.z, M, f)
         o.gemm(blk.z, sh[f"{pre}.mlp.wd.weight"], blk.out, M=M, N=d, K=f, epilogue=A.EPI_F32, residual=blk.u)
         return blk.out
 
@@ -424,8 +430,12 @@ class TrainEngine:
         d, f, pre = cfg.d_model, cfg.d_ff, blk.prefix.split("@")[0]
         ready = self._grad_ready if mark_ready else (lambda *names: None)
         # --- MLP: x_out = u + wd(up * silu(gate)),  (up | gate) = wug(norm2(u))
-        o.gemm(dout16, sh[f"{pre}.mlp.wd.weight"], t.dug, M=M, N=f, K=d, b_mn=True, epilogue=A.EPI_SWIGLU_BWD,
-               residual=blk.ug, pair=f)
+        if M <= self.swiglu_fuse_max_rows:
+            o.gemm(dout16, sh[f"{pre}.mlp.wd.weight"], t.dug, M=M, N=f, K=d, b_mn=True, epilogue=A.EPI_SWIGLU_BWD,
+                   residual=blk.ug, pair=f)
+        else:
+            o.gemm(dout16, sh[f"{pre}.mlp.wd.weight"], t.dz16, M=M, N=f, K=d, b_mn=True)
+            o.swiglu_bwd(blk.ug, t.dz16, t.dug, M, f)
         o.gemm_wgrad(dout16, blk.z, g[f"{pre}.mlp.wd.weight"], M=d, N=f, K=M, accumulate=accumulate, ws=ws)
         ready(f"{pre}.mlp.wd.weight")
         o.gemm(t.dug, sh[f"{pre}.mlp.wug.weight"], t.dn16, M=M, N=d, K=2 * f, b_mn=True)
@@ -704,43 +714,23 @@ class TrainEngine:
         return [(calls[i][0], totals[i] / repeats) for i in range(len(calls))]
 
     def gemm_roofline(self, repeats: int = 5) -> dict[str, Any]:
-        """Times every launch of the tcgen05 GEMM inside real (eager) forward+backward passes with a CUDA
-        event pair per launch on the launching stream, and relates the algorithmic 2*M*N*K FLOPs to it."""
-        records: list[tuple] = []
-        orig = self.ops.gemm
-        stream = torch.cuda.current_stream(self.device)
-
-        def timed(a, b, out, **kw):
-            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            e0.record(stream)
-            orig(a, b, out, **kw)
-            e1.record(stream)
-            records.append((kw["M"], kw["N"], kw["K"], kw.get("epilogue", 0), kw.get("splits", 1), e0, e1))
-
-        self.ops.gemm = timed
-        self._dp_paused = True                # rank-local passes: no collective may be issued here
-        try:
-            self._forward_backward()          # untimed pass (instruction cache, tensor maps)
-            records.clear()
-            for _ in range(repeats):
-                self._forward_backward()
-        finally:
-            self.ops.gemm = orig
-            self._dp_paused = False
-        torch.cuda.synchronize(self.device)
+        """Relates the algorithmic 2*M*N*K FLOPs of every tcgen05 GEMM launch of one step to its device
+        duration, taken from event-record nodes around each launch inside a captured step (`profile_step`),
+        i.e. under the same cache state and stream concurrency as the timed step and without host gaps."""
+        import re
         per_shape: dict[str, list[float]] = {}
-        flops = ms = 0.0
-        for M, N, K, epi, splits, e0, e1 in records:
-            t = e0.elapsed_time(e1)
-            f = 2.0 * M * N * K
-            flops += f
-            ms += t
-            key = f"{M}x{N}x{K}/epi{epi}" + (f"/split{splits}" if splits > 1 else "")
-            acc = per_shape.setdefault(key, [0.0, 0.0, 0])
+        flops = us = 0.0
+        n = 0
+        for name, t in self.profile_step(repeats):
+            m = re.match(r"rte_gemm_bf16\[(\d+)x(\d+)x(\d+)/(.*)\]", name)
+            if not m:
+                continue
+            f = 2.0 * int(m.group(1)) * int(m.group(2)) * int(m.group(3))
+            flops, us, n = flops + f, us + t, n + 1
+            acc = per_shape.setdefault(f"{m.group(1)}x{m.group(2)}x{m.group(3)}/{m.group(4)}", [0.0, 0.0, 0])
             acc[0] += f
             acc[1] += t
             acc[2] += 1
-        table = {k: {"launches": v[2] // repeats, "us": 1e3 * v[1] / v[2], "tflops": v[0] / (v[1] * 1e-3) / 1e12}
+        table = {k: {"launches": v[2], "us": v[1] / v[2], "tflops": v[0] / (v[1] * 1e-6) / 1e12}
                  for k, v in per_shape.items()}
-        return {"tflops": flops / (ms * 1e-3) / 1e12, "launches": len(records) // repeats,
-                "gemm_ms_per_step": ms / repeats, "per_shape": table}
+        return {"tflops": flops / (us * 1e-6) / 1e12, "launches": n, "gemm_ms_per_step": us * 1e-3, "per_shape": table}

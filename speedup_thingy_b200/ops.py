@@ -175,16 +175,33 @@ class CudaOps:
             self._rope_tables[key] = out
         return self._rope_tables[key]
 
-    def attn_fwd(self, qkv, y, lse, *, B: int, S: int, n_heads: int, head_dim: int, sec: int | None = None) -> None:
+    def identity_rope_table(self, S: int, head_dim: int) -> torch.Tensor:
+        """(cos, sin) = (1, 0): attention over q and k that already carry their positions (k_flash_causal_*)."""
+        key = (-S, head_dim)
+        if key not in self._rope_tables:
+            out = torch.zeros(S, head_dim // 2, 2, dtype=torch.float32, device=self.device)
+            out[..., 0] = 1.0
+            self._rope_tables[key] = out
+        return self._rope_tables[key]
+
+    def attn_fwd(self, qkv, y, lse, *, B: int, S: int, n_heads: int, head_dim: int, sec: int | None = None,
+                 rope=None) -> None:
         sec = sec if sec is not None else n_heads * head_dim
+        rope = rope if rope is not None else self.rope_table(S, head_dim)
         self._call("rte_attn_fwd", _ptr(qkv), qkv.stride(0), sec, _ptr(y), y.stride(0), _ptr(lse),
-                   _ptr(self.rope_table(S, head_dim)), B, S, n_heads, head_dim, self.stream)
+                   _ptr(rope), B, S, n_heads, head_dim, self.stream)
 
     def attn_bwd(self, qkv, y, dy, lse, dqkv, *, B: int, S: int, n_heads: int, head_dim: int,
-                 sec: int | None = None) -> None:
+                 sec: int | None = None, rope=None) -> None:
         sec = sec if sec is not None else n_heads * head_dim
+        rope = rope if rope is not None else self.rope_table(S, head_dim)
         self._call("rte_attn_bwd", _ptr(qkv), qkv.stride(0), sec, _ptr(y), _ptr(dy), y.stride(0), _ptr(lse),
-                   _ptr(dqkv), _ptr(self.rope_table(S, head_dim)), B, S, n_heads, head_dim, self.stream)
+                   _ptr(dqkv), _ptr(rope), B, S, n_heads, head_dim, self.stream)
+
+    def rope_apply(self, x, cos, sin, out, *, rows: int, S: int, head_dim: int, adjoint: bool = False) -> None:
+        _require_cuda(x, cos, sin, out)
+        self._call("rte_rope_apply", _ptr(x), _ptr(cos), _ptr(sin), _ptr(out), rows, S, head_dim,
+                   int(x.dtype == torch.bfloat16), int(adjoint), self.stream)
 
     # ------------------------------------------------------------------ router
     @staticmethod
@@ -257,6 +274,10 @@ class CudaOps:
         self._call("rte_shortlist_ce", _ptr(hidden), _ptr(W), _ptr(shortlist), _ptr(row_weight), S, _ptr(loss_tok),
                    _ptr(logits_out), _ptr(dlogits_dense), rows, hidden.shape[-1], W.shape[0], K, self.stream)
 
+    def scatter_cols(self, vals, ids, dense) -> None:
+        rows, K = ids.shape
+        self._call("rte_scatter_cols_bf16", _ptr(vals), _ptr(ids), _ptr(dense), rows, dense.shape[-1], K, self.stream)
+
     def random_tokens(self, out, vocab: int, seed) -> None:
         self._call("rte_random_tokens", _ptr(out), out.numel(), vocab, _ptr(seed), self.stream)
 
@@ -300,6 +321,12 @@ class CudaOps:
     def kl_distill(self, hot_logits, exact_logits, temp, coef, idx, S: int, dlogits_hot, kl_rows, rows: int, V: int) -> None:
         self._call("rte_kl_distill", _ptr(hot_logits), _ptr(exact_logits), temp, coef, _ptr(idx), S, _ptr(dlogits_hot),
                    dlogits_hot.stride(0), _ptr(kl_rows), rows, V, self.stream)
+
+    def swiglu_fwd(self, ug, z, rows: int, F: int) -> None:
+        self._call("rte_swiglu_fwd", _ptr(ug), _ptr(z), rows, F, self.stream)
+
+    def swiglu_bwd(self, ug, dz, dug, rows: int, F: int) -> None:
+        self._call("rte_swiglu_bwd", _ptr(ug), _ptr(dz), _ptr(dug), rows, F, self.stream)
 
     # ------------------------------------------------------------------ small vector ops
     def cast_bf16(self, src, dst) -> None:

@@ -290,6 +290,18 @@ class EmulOps:
         if vals is not None:
             vals.copy_(torch.gather(scores, -1, order))
 
+    def swiglu_fwd(self, ug, z, rows, F):
+        self.launches += 1
+        up, gate = ug[:rows, :F].float(), ug[:rows, F:].float()
+        z[:rows] = (up * torch.nn.functional.silu(gate)).to(torch.bfloat16)
+
+    def swiglu_bwd(self, ug, dz, dug, rows, F):
+        self.launches += 1
+        up, gate, d = ug[:rows, :F].float(), ug[:rows, F:].float(), dz[:rows].float()
+        sg = torch.sigmoid(gate)
+        dug[:rows, :F] = (d * gate * sg).to(torch.bfloat16)
+        dug[:rows, F:] = (d * up * sg * (1 + gate * (1 - sg))).to(torch.bfloat16)
+
     # ---------------------------------------------------------------- vocabulary shortlist
     def shortlist_build(self, targets, top_clusters, random_negs, shortlist, dup_count, *, V, C, TC, HN, RN, K):
         self.launches += 1

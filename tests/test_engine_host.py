@@ -76,7 +76,9 @@ def test_engine_sequence_matches_oracle(name):
     cfg, ocfg, otr = _pair(name)
     tr = cfg.training
     params = init_parameters(cfg.model, seed=tr.seed, num_clusters=cfg.output.num_clusters)
-    eng = TrainEngine(cfg, params, device="cpu", ops=EmulOps(), use_cuda_graph=False)
+    # the dense case also exercises the un-fused SwiGLU path (what large batches take)
+    eng = TrainEngine(cfg, params, device="cpu", ops=EmulOps(), use_cuda_graph=False,
+                      swiglu_fuse_max_rows=0 if name == "dense" else 1024)
     oracle = _oracle(cfg, ocfg, otr, params)
     stream = O.zipf_tokens(tr.batch_size * tr.seq_len * 6 + 1, cfg.model.vocab_size, seed=tr.seed)
     it = O.batches(stream, tr.batch_size, tr.seq_len)

@@ -290,6 +290,24 @@ def test_topk_lowest_index_bit_exact(ops, rows, n, k):
     assert torch.equal(gv.cpu(), vals)
 
 
+def test_swiglu_standalone_pass_matches_fused_epilogue_math(ops):
+    g = torch.Generator().manual_seed(12)
+    rows, F_ = 300, 192
+    ug = torch.randn(rows, 2 * F_, generator=g).bfloat16()
+    dz = torch.randn(rows, F_, generator=g).bfloat16()
+    up, gate = ug[:, :F_].float().requires_grad_(), ug[:, F_:].float().requires_grad_()
+    z_ref = up * torch.nn.functional.silu(gate)
+    (z_ref * dz.float()).sum().backward()
+    z = torch.empty(rows, F_, dtype=torch.bfloat16, device=DEV)
+    dug = torch.empty(rows, 2 * F_, dtype=torch.bfloat16, device=DEV)
+    ops.swiglu_fwd(ug.to(DEV), z, rows, F_)
+    ops.swiglu_bwd(ug.to(DEV), dz.to(DEV), dug, rows, F_)
+    torch.cuda.synchronize()
+    assert (z.cpu().float() - z_ref.detach()).abs().max() <= 1e-2 * z_ref.abs().max()
+    ref = torch.cat([up.grad, gate.grad], dim=1)
+    assert (dug.cpu().float() - ref).abs().max() <= 1e-2 * ref.abs().max()
+
+
 # ------------------------------------------------------------------ vocabulary shortlist
 @pytest.mark.parametrize("B,S,V,C,TC,HN,RN,K", [(3, 7, 96, 8, 2, 4, 4, 16), (4, 33, 2048, 64, 2, 32, 32, 128),
                                                 (2, 5, 50, 7, 3, 60, 0, 50), (2, 9, 4096, 64, 1, 0, 8, 256)])
