@@ -253,7 +253,9 @@ def main() -> None:
                                 "kernel": "gemm_tcgen05_kernel", "launches_per_step": roof["launches"],
                                 "gemm_ms_per_step": roof["gemm_ms_per_step"],
                                 "timing": "event-record nodes around each launch inside a captured step",
-                                "per_shape": roof["per_shape"]}
+                                "scope": "hot-pass launches (main stream); the audit replay's launches overlap them on a "
+                                         "side stream and are listed under side_stream",
+                                "per_shape": roof["per_shape"], "side_stream": roof.get("side_stream")}
         if world == 1 and not args.no_cpu_baseline:
             threads = os.cpu_count() or 1
             v, sample = cpu_port_tokens_per_sec(sample_batch=8, steps=3, threads=threads)

@@ -82,6 +82,17 @@ typedef struct rte_gemm_args {
   int64_t split_stride;     /* elements between partial results */
   int32_t max_ctas;         /* 0 = one CTA per SM */
   int32_t* status;
+  /* Grouped mode (cluster-pool FFN, cluster_pool_ffn.py:206-241): the rows of A/C are packed by group in blocks of
+   * 128 rows; tile_group int32 [M/128] (device) names each block's group (< 0: unused block, skipped).  B is the
+   * stack of all groups' matrices; group g's matrix starts b_group_stride rows further (rows of the stored B: its
+   * N rows when K-major, its K rows when MN-major).  M must be a multiple of 128.  NULL = ordinary GEMM.        */
+  const int32_t* tile_group;
+  int32_t n_groups;
+  int32_t b_group_stride;
+  /* Ragged split-K (per-group weight gradients over packed rows): split s reduces the 64-wide k-blocks
+   * [split_kblocks[s], split_kblocks[s+1]) (device int32 [splits+1]) into C + s*split_stride; an empty range gives
+   * zeros.  RTE_EPI_F32 only.  NULL = equal splits.                                                             */
+  const int32_t* split_kblocks;
 } rte_gemm_args;
 
 int rte_gemm_bf16(const rte_gemm_args* args, rte_stream_t stream);
@@ -273,6 +284,32 @@ int rte_random_tokens(int32_t* out, int64_t n, int32_t vocab, const int64_t* see
  * shortlist slots (backward of k_logits_shortlist, reference.py:141-143) into rows the dense GEMMs can consume. */
 int rte_scatter_cols_bf16(const void* vals, const int32_t* ids, void* dense, int32_t rows, int32_t V, int32_t K,
                           rte_stream_t stream);
+
+/* ------------------------------------------------ static cluster-pool sparse FFN (layers.py:188-220;
+ * kernels/cluster_pool_ffn.py:90-241).  The pooled SwiGLU itself runs as rte_gemm_bf16 in grouped mode.
+ * rte_cluster_route: assignments[t] = argmax_c q[t,:] . centers[c,:] with the lowest index on ties
+ *   (route_to_static_centers; q = x @ [up_a | gate_a] from a GEMM; the reference's L2 normalisation of q is a
+ *   positive per-token scale and cannot change the arg-max).  scores_out f32 [n, C] optional.
+ * rte_cluster_pack: stable counting sort of tokens by cluster (build_static_pack_gather_indices) into one packed
+ *   row order where cluster c owns rows [offsets[c], offsets[c] + counts[c]) and offsets are multiples of 128:
+ *   perm int32 [capacity] (packed row -> token, -1 = padding), pos int32 [n] (token -> packed row),
+ *   tile_group int32 [capacity/128] and kblocks int32 [C+1] for rte_gemm_bf16's grouped / ragged-split modes.
+ *   capacity_rows >= n rounded up to 128, plus 128 per cluster, always suffices; overflow sets *status (202).
+ * rte_gather_rows_convert: dst[i,:] = src[idx[i],:] converted f32<->bf16, zeros where idx[i] < 0.
+ * rte_csr_row_reduce_f32: dense[f,:] (+)= sum_k src[rows[k],:], k in [row_ptr[f], row_ptr[f+1]) in that order
+ *   (scatter_cluster_pool_grads as a gather: no atomics, reproducible).
+ * rte_transpose_f32: dst [cols, rows] (bf16 or f32, optionally +=) = src f32 [rows, cols]^T.                  */
+int rte_cluster_route(const float* q, int32_t ldq, const float* centers, int32_t* assignments, float* scores_out,
+                      int32_t n_tokens, int32_t width, int32_t n_clusters, rte_stream_t stream);
+int rte_cluster_pack(const int32_t* assignments, int32_t n_tokens, int32_t n_clusters, int32_t capacity_rows,
+                     int32_t* perm, int32_t* pos, int32_t* counts, int32_t* offsets, int32_t* tile_group,
+                     int32_t* kblocks, int32_t* status, rte_stream_t stream);
+int rte_gather_rows_convert(const void* src, int32_t src_bf16, const int32_t* idx, void* dst, int32_t dst_bf16,
+                            int64_t n_out, int32_t d, rte_stream_t stream);
+int rte_csr_row_reduce_f32(const float* src, const int32_t* row_ptr, const int32_t* rows, float* dense,
+                           int64_t n_dense_rows, int32_t d, int32_t accumulate, rte_stream_t stream);
+int rte_transpose_f32(const float* src, void* dst, int32_t rows, int32_t cols, int32_t dst_bf16, int32_t accumulate,
+                      rte_stream_t stream);
 
 /* ------------------------------------------------ exact-audit replay helpers (audit.py:245-387; models.py:605-679;
  * layers.py:831-870).  The audited subset has a fixed size n (fixed-count sampler), chosen on the host.

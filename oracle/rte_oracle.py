@@ -721,3 +721,53 @@ class OracleTrainer:
             self.usage_ema = update_usage(self.usage_ema, info["hot"]["route"]["recipe_id"], self.tr.coverage_beta)
         self.global_step += 1
         return float(loss)
+
+
+# ----------------------------------------------------------------------------- static cluster-pool sparse FFN
+def cluster_route(x: torch.Tensor, up_a: torch.Tensor, gate_a: torch.Tensor, centers: torch.Tensor) -> torch.Tensor:
+    """kernels/cluster_pool_ffn.py:127-139: arg-max over centres of the L2-normalised selector features
+    (lowest index on ties, the rule this build fixes)."""
+    feats = F.normalize(torch.cat([x @ up_a, x @ gate_a], dim=-1).float(), dim=-1)
+    return argmax_lowest(feats @ centers.float().t())
+
+
+def cluster_pack_indices(assignments: torch.Tensor, cluster_count: int):
+    """kernels/cluster_pool_ffn.py:162-188: per cluster the member tokens in ascending order, padded with token 0
+    to the largest cluster; flat_gather[token] = cluster * max_count + rank."""
+    counts = torch.bincount(assignments, minlength=cluster_count)
+    max_count = int(counts.max()) if counts.numel() else 0
+    pack_index = torch.zeros(cluster_count, max_count, dtype=torch.long)
+    flat_gather = torch.empty(assignments.shape[0], dtype=torch.long)
+    for c in range(cluster_count):
+        idx = torch.nonzero(assignments == c).flatten()
+        pack_index[c, : idx.numel()] = idx
+        flat_gather[idx] = c * max_count + torch.arange(idx.numel())
+    return pack_index, flat_gather, counts, max_count
+
+
+def cluster_pool_ffn(x: torch.Tensor, assignments: torch.Tensor, w_up: torch.Tensor, w_gate: torch.Tensor,
+                     w_down_rows: torch.Tensor, candidate_ids: torch.Tensor) -> torch.Tensor:
+    """kernels/cluster_pool_ffn.py:90-124,142-159: every token runs SwiGLU over its cluster's candidate neurons.
+    w_up / w_gate / w_down_rows are [d_ff, d_model] (row f = neuron f); differentiable."""
+    out = torch.zeros_like(x)
+    for c in range(candidate_ids.shape[0]):
+        idx = torch.nonzero(assignments == c).flatten()
+        if idx.numel() == 0:
+            continue
+        ids = candidate_ids[c]
+        xc = x[idx]
+        z = (xc @ w_up[ids].t()) * F.silu(xc @ w_gate[ids].t())
+        out = out.index_add(0, idx, z @ w_down_rows[ids])
+    return out
+
+
+def static_cluster_pool_swiglu(x: torch.Tensor, wug: torch.Tensor, wd: torch.Tensor, up_a: torch.Tensor,
+                               gate_a: torch.Tensor, centers: torch.Tensor, candidate_ids: torch.Tensor,
+                               assignments: torch.Tensor | None = None) -> tuple[torch.Tensor, torch.Tensor]:
+    """layers.py:188-220: route, then the pooled FFN with wug [2F, d] = (up rows | gate rows), wd [d, F]."""
+    flat = x.reshape(-1, x.shape[-1])
+    if assignments is None:
+        assignments = cluster_route(flat, up_a, gate_a, centers)
+    f = wd.shape[1]
+    out = cluster_pool_ffn(flat, assignments, wug[:f], wug[f:], wd.t(), candidate_ids)
+    return out.view(x.shape), assignments

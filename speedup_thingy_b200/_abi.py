@@ -31,6 +31,10 @@ class GemmArgs(C.Structure):
         ("split_stride", c_i64),
         ("max_ctas", c_i32),
         ("status", c_vp),
+        ("tile_group", c_vp),
+        ("n_groups", c_i32),
+        ("b_group_stride", c_i32),
+        ("split_kblocks", c_vp),
     ]
 
 
@@ -89,6 +93,11 @@ PROTOTYPES = {
                           [c_f32, c_vp]),
     "rte_macro_phi_bwd": (C.c_int, [c_vp, c_vp, P(PhiParams), c_vp, c_vp, c_f32, c_vp, c_vp, c_vp, c_vp, P(PhiGrads),
                                     c_vp] + [c_i32] * 6 + [c_f32, c_vp]),
+    "rte_cluster_route": (C.c_int, [c_vp, c_i32, c_vp, c_vp, c_vp, c_i32, c_i32, c_i32, c_vp]),
+    "rte_cluster_pack": (C.c_int, [c_vp, c_i32, c_i32, c_i32, c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, c_vp]),
+    "rte_gather_rows_convert": (C.c_int, [c_vp, c_i32, c_vp, c_vp, c_i32, c_i64, c_i32, c_vp]),
+    "rte_csr_row_reduce_f32": (C.c_int, [c_vp, c_vp, c_vp, c_vp, c_i64, c_i32, c_i32, c_vp]),
+    "rte_transpose_f32": (C.c_int, [c_vp, c_vp, c_i32, c_i32, c_i32, c_i32, c_vp]),
     "rte_swiglu_fwd": (C.c_int, [c_vp, c_vp, c_i64, c_i32, c_vp]),
     "rte_swiglu_bwd": (C.c_int, [c_vp, c_vp, c_vp, c_i64, c_i32, c_vp]),
     "rte_cast_f32_bf16": (C.c_int, [c_vp, c_vp, c_i64, c_vp]),

@@ -15,7 +15,7 @@ PKG = Path(__file__).resolve().parent
 ROOT = PKG.parent
 CSRC = PKG / "csrc"
 LIB = PKG / "lib" / "librte_b200.so"
-SOURCES = ["gemm_tcgen05.cu", "elementwise.cu", "attention.cu", "macro_phi.cu", "router.cu", "audit.cu", "shortlist.cu"]
+SOURCES = ["gemm_tcgen05.cu", "elementwise.cu", "attention.cu", "macro_phi.cu", "router.cu", "audit.cu", "shortlist.cu", "cluster_pool.cu"]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
     "-Xcompiler", "-fPIC",
@@ -32,7 +32,8 @@ def _nvcc() -> str:
 def needs_build() -> bool:
     if not LIB.exists():
         return True
-    newest = max(p.stat().st_mtime for p in [*CSRC.glob("*.cu"), *CSRC.glob("*.cuh"), ROOT / "include" / "rte_b200.h"])
+    newest = max(p.stat().st_mtime for p in [*CSRC.glob("*.cu"), *CSRC.glob("*.cuh"), ROOT / "include" / "rte_b200.h",
+                                             Path(__file__)])
     return newest > LIB.stat().st_mtime
 
 

@@ -36,6 +36,9 @@ struct KParams {
   int splits; long long split_stride;
   int num_m_blocks, num_n_blocks, kblocks_total, kblocks_per_split;
   int tma_store;            // 1: outputs leave through shared-memory staging + TMA bulk stores
+  const int* tile_group;    // grouped mode: group id of every 128-row block of A/C (< 0: block unused), else null
+  int b_group_stride;       // grouped mode: rows of the stacked B between consecutive groups
+  const int* split_kb;      // ragged split-K: k-block range [split_kb[s], split_kb[s+1]) of split s, else null
   int* status;
 };
 
@@ -264,8 +267,14 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
       for (int w = blockIdx.x; w < total_work && ok; w += gridDim.x) {
         const int split = w / tiles, t = w % tiles;
         const int m0 = (t % p.num_m_blocks) * BM, n0 = (t / p.num_m_blocks) * BN;
-        const int kb0 = split * p.kblocks_per_split;
-        const int kb1 = min(kb0 + p.kblocks_per_split, p.kblocks_total);
+        int boff = 0;
+        if (p.tile_group) {
+          const int g = p.tile_group[t % p.num_m_blocks];
+          if (g < 0) continue;
+          boff = g * p.b_group_stride;
+        }
+        const int kb0 = p.split_kb ? p.split_kb[split] : split * p.kblocks_per_split;
+        const int kb1 = p.split_kb ? p.split_kb[split + 1] : min(kb0 + p.kblocks_per_split, p.kblocks_total);
         for (int kb = kb0; kb < kb1; ++kb) {
           if (!mbar_wait(empty_bar(stage), phase ^ 1u)) {
             if (p.status) atomicExch(p.status, RTE_DEV_WAIT_TIMEOUT_PRODUCER);
@@ -283,7 +292,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
           if (!p.b_mn) {
             if (p.pair_off > 0 && p.epilogue == RTE_EPI_SWIGLU_FWD) {
               // first half of the tile = "up" rows, second half = the matching "gate" rows
-              const int nh = (t / p.num_m_blocks) * (BN / 2);
+              const int nh = boff + (t / p.num_m_blocks) * (BN / 2);
               if (BN == 256) {
                 tma_load_2d(sb, &tmap_b, full_bar(stage), k0, nh);
                 tma_load_2d(sb + 16384, &tmap_b, full_bar(stage), k0, p.pair_off + nh);
@@ -294,11 +303,11 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
               }
             } else {
 #pragma unroll
-              for (int j = 0; j < BN / 128; ++j) tma_load_2d(sb + j * 16384, &tmap_b, full_bar(stage), k0, n0 + 128 * j);
+              for (int j = 0; j < BN / 128; ++j) tma_load_2d(sb + j * 16384, &tmap_b, full_bar(stage), k0, boff + n0 + 128 * j);
             }
           } else {
 #pragma unroll
-            for (int j = 0; j < BN / 64; ++j) tma_load_2d(sb + j * 8192, &tmap_b, full_bar(stage), n0 + 64 * j, k0);
+            for (int j = 0; j < BN / 64; ++j) tma_load_2d(sb + j * 8192, &tmap_b, full_bar(stage), n0 + 64 * j, boff + k0);
           }
           if (++stage == STAGES) { stage = 0; phase ^= 1u; }
         }
@@ -314,8 +323,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
       int stage = 0; uint32_t phase = 0; int acc = 0; uint32_t acc_phase = 0; bool ok = true;
       for (int w = blockIdx.x; w < total_work && ok; w += gridDim.x) {
         const int split = w / tiles;
-        const int kb0 = split * p.kblocks_per_split;
-        const int kb1 = min(kb0 + p.kblocks_per_split, p.kblocks_total);
+        if (p.tile_group && p.tile_group[(w % tiles) % p.num_m_blocks] < 0) continue;
+        const int kb0 = p.split_kb ? p.split_kb[split] : split * p.kblocks_per_split;
+        const int kb1 = p.split_kb ? p.split_kb[split + 1] : min(kb0 + p.kblocks_per_split, p.kblocks_total);
         if (!mbar_wait(tempty_bar(acc), acc_phase ^ 1u)) {
           if (p.status) atomicExch(p.status, RTE_DEV_WAIT_TIMEOUT_MMA);
           ok = false; break;
@@ -384,6 +394,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
       for (int w = blockIdx.x; w < total_work && ok; w += gridDim.x) {
         const int split = w / tiles, t = w % tiles;
         const int m0 = (t % p.num_m_blocks) * BM, nblk = t / p.num_m_blocks, n0 = nblk * BN;
+        if (p.tile_group && p.tile_group[t % p.num_m_blocks] < 0) continue;
+        // a split with an empty k-range never touched its accumulator: its partial is all zeros
+        const bool empty_acc = p.split_kb && p.split_kb[split + 1] <= p.split_kb[split];
         if (!mbar_wait(tfull_bar(acc), acc_phase)) {
           if (p.status && lane == 0) atomicExch(p.status, RTE_DEV_WAIT_TIMEOUT_EPILOGUE);
           ok = false; break;
@@ -417,7 +430,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
                     for (int j = 0; j < 32; ++j) v[j] = (row_ok ? v[j] : 0.f) + __uint_as_float(raw[q][j]);
                   } else {
 #pragma unroll
-                    for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(raw[q][j]);
+                    for (int j = 0; j < 32; ++j) v[j] = empty_acc ? 0.f : __uint_as_float(raw[q][j]);
                   }
                   emit32(&tmap_c, col, m0, split, v);
                 } else {
@@ -481,6 +494,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
     for (int w = blockIdx.x; w < total_work && ok; w += gridDim.x) {
       const int split = w / tiles, t = w % tiles;
       const int m0 = (t % p.num_m_blocks) * BM, nblk = t / p.num_m_blocks, n0 = nblk * BN;
+      if (p.tile_group && p.tile_group[t % p.num_m_blocks] < 0) continue;
+      const bool empty_acc = p.split_kb && p.split_kb[split + 1] <= p.split_kb[split];
       if (!mbar_wait(tfull_bar(acc), acc_phase)) {
         if (p.status && lane == 0) atomicExch(p.status, RTE_DEV_WAIT_TIMEOUT_EPILOGUE);
         ok = false; break;
@@ -513,7 +528,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
               for (int j = 0; j < 32; ++j) v[j] += __uint_as_float(raw[j]);
             } else {
 #pragma unroll
-              for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(raw[j]);
+              for (int j = 0; j < 32; ++j) v[j] = empty_acc ? 0.f : __uint_as_float(raw[j]);
             }
             store_f32x32(Cf + size_t(row) * p.ldc + col, v, p.N - col);
           }
@@ -693,21 +708,33 @@ extern "C" int rte_gemm_bf16(const rte_gemm_args* a, rte_stream_t stream) {
   kp.num_n_blocks = rte::ceil_div(a->N, bn);
   kp.kblocks_total = rte::ceil_div(a->K, BK);
   kp.kblocks_per_split = rte::ceil_div(kp.kblocks_total, splits);
-  kp.splits = rte::ceil_div(kp.kblocks_total, kp.kblocks_per_split);   // drop empty trailing splits
   kp.status = a->status;
-  // a dropped split would leave its partial unwritten: the caller reduces `splits` partials, so insist
-  RTE_CHECK_ARG(kp.splits == splits);
+  kp.tile_group = a->tile_group;
+  kp.b_group_stride = a->b_group_stride;
+  kp.split_kb = a->split_kblocks;
+  if (a->tile_group) {
+    RTE_CHECK_ARG(a->n_groups >= 1 && a->b_group_stride > 0 && a->M % BM == 0);
+    RTE_CHECK_ARG(!a->b_mn_major || a->K % BK == 0);          // a ragged k-block would read the next group's rows
+  }
+  if (a->split_kblocks) {
+    RTE_CHECK_ARG(a->epilogue == RTE_EPI_F32 && a->R == nullptr && a->tile_group == nullptr);
+  } else {
+    kp.splits = rte::ceil_div(kp.kblocks_total, kp.kblocks_per_split);   // drop empty trailing splits
+    // a dropped split would leave its partial unwritten: the caller reduces `splits` partials, so insist
+    RTE_CHECK_ARG(kp.splits == splits);
+  }
 
   CUtensorMap ta, tb;
   int rc;
   if (!kp.a_mn) rc = make_tmap(&ta, a->A, a->M, a->K, a->lda, BK, BM);
   else rc = make_tmap(&ta, a->A, a->K, a->M, a->lda, 64, BK);
   if (rc != RTE_OK) return rc;
+  const long long b_groups = a->tile_group ? a->n_groups : 0;     // grouped mode: B is the stack of every group's matrix
   if (!kp.b_mn) {
     const int box_rows = (swiglu_f && bn == 128) ? 64 : 128;
-    rc = make_tmap(&tb, a->B, a->N, a->K, a->ldb, BK, box_rows);
+    rc = make_tmap(&tb, a->B, b_groups ? b_groups * a->b_group_stride : a->N, a->K, a->ldb, BK, box_rows);
   } else {
-    rc = make_tmap(&tb, a->B, a->K, a->N, a->ldb, 64, BK);
+    rc = make_tmap(&tb, a->B, b_groups ? b_groups * a->b_group_stride : a->K, a->N, a->ldb, 64, BK);
   }
   if (rc != RTE_OK) return rc;
 

@@ -23,7 +23,8 @@ enum : int {
   RTE_DEV_WAIT_TIMEOUT_PRODUCER = 101,
   RTE_DEV_WAIT_TIMEOUT_MMA = 102,
   RTE_DEV_WAIT_TIMEOUT_EPILOGUE = 103,
-  RTE_DEV_INDEX_OUT_OF_RANGE = 201
+  RTE_DEV_INDEX_OUT_OF_RANGE = 201,
+  RTE_DEV_CAPACITY_OVERFLOW = 202
 };
 
 namespace rte {

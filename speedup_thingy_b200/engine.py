@@ -670,7 +670,8 @@ class TrainEngine:
     def profile_step(self, repeats: int = 3) -> list[tuple[str, float]]:
         """Device-side duration of every C-ABI call of one step, measured INSIDE a CUDA graph (event-record
         nodes around each call), so that host launch latency does not leak into the numbers.  Returns
-        (entry point + shape tag, microseconds) in launch order, averaged over `repeats` replays."""
+        (entry point + shape tag, microseconds) in launch order, averaged over `repeats` replays; calls issued on
+        the audit replay's side stream carry the suffix "@side"."""
         ops = self.ops
         calls: list[tuple[str, Any, Any]] = []
         orig_call, orig_gemm = ops._call, ops.gemm
@@ -683,7 +684,7 @@ class TrainEngine:
             e0.record(st)
             orig_call(name, *args)
             e1.record(st)
-            calls.append((name + tag["v"], e0, e1))
+            calls.append((name + tag["v"] + ("" if st.cuda_stream == main_stream else "@side"), e0, e1))
 
         def tagged_gemm(a, b, out, **kw):
             tag["v"] = f"[{kw['M']}x{kw['N']}x{kw['K']}/epi{kw.get('epilogue', 0)}" + (f"/split{kw['splits']}" if kw.get("splits", 1) > 1 else "") + "]"
@@ -693,11 +694,13 @@ class TrainEngine:
                 tag["v"] = ""
 
         ops._call, ops.gemm = timed_call, tagged_gemm
+        main_stream = None
         self._dp_paused = True
         try:
             torch.cuda.synchronize(self.device)
             graph = torch.cuda.CUDAGraph()
             with torch.cuda.graph(graph):
+                main_stream = torch.cuda.current_stream(self.device).cuda_stream
                 self._forward_backward()
                 self._optimizer_step()
         finally:
@@ -716,21 +719,30 @@ class TrainEngine:
     def gemm_roofline(self, repeats: int = 5) -> dict[str, Any]:
         """Relates the algorithmic 2*M*N*K FLOPs of every tcgen05 GEMM launch of one step to its device
         duration, taken from event-record nodes around each launch inside a captured step (`profile_step`),
-        i.e. under the same cache state and stream concurrency as the timed step and without host gaps."""
+        i.e. under the same cache state and stream concurrency as the timed step and without host gaps.  The
+        headline figures cover the hot pass (main stream); the audit replay's small GEMMs, which run beside it on
+        a side stream, are reported under "side_stream"."""
         import re
-        per_shape: dict[str, list[float]] = {}
-        flops = us = 0.0
-        n = 0
+        acc = {"": [0.0, 0.0, 0, {}], "@side": [0.0, 0.0, 0, {}]}      # flops, us, launches, per shape
         for name, t in self.profile_step(repeats):
-            m = re.match(r"rte_gemm_bf16\[(\d+)x(\d+)x(\d+)/(.*)\]", name)
+            m = re.match(r"rte_gemm_bf16\[(\d+)x(\d+)x(\d+)/(.*)\](@side)?$", name)
             if not m:
                 continue
             f = 2.0 * int(m.group(1)) * int(m.group(2)) * int(m.group(3))
-            flops, us, n = flops + f, us + t, n + 1
-            acc = per_shape.setdefault(f"{m.group(1)}x{m.group(2)}x{m.group(3)}/{m.group(4)}", [0.0, 0.0, 0])
-            acc[0] += f
-            acc[1] += t
-            acc[2] += 1
-        table = {k: {"launches": v[2], "us": v[1] / v[2], "tflops": v[0] / (v[1] * 1e-6) / 1e12}
-                 for k, v in per_shape.items()}
-        return {"tflops": flops / (us * 1e-6) / 1e12, "launches": n, "gemm_ms_per_step": us * 1e-3, "per_shape": table}
+            a = acc[m.group(5) or ""]
+            a[0], a[1], a[2] = a[0] + f, a[1] + t, a[2] + 1
+            sh = a[3].setdefault(f"{m.group(1)}x{m.group(2)}x{m.group(3)}/{m.group(4)}", [0.0, 0.0, 0])
+            sh[0] += f
+            sh[1] += t
+            sh[2] += 1
+
+        def table(d):
+            return {k: {"launches": v[2], "us": v[1] / v[2], "tflops": v[0] / (v[1] * 1e-6) / 1e12} for k, v in d.items()}
+
+        hot, side = acc[""], acc["@side"]
+        out = {"tflops": hot[0] / (hot[1] * 1e-6) / 1e12, "launches": hot[2], "gemm_ms_per_step": hot[1] * 1e-3,
+               "per_shape": table(hot[3])}
+        if side[2]:
+            out["side_stream"] = {"tflops": side[0] / (side[1] * 1e-6) / 1e12, "launches": side[2],
+                                  "gemm_ms_per_step": side[1] * 1e-3, "per_shape": table(side[3])}
+        return out

@@ -69,8 +69,10 @@ class CudaOps:
     def gemm(self, a, b, out, *, M: int, N: int, K: int, a_mn: bool = False, b_mn: bool = False,
              epilogue: int = A.EPI_BF16, residual=None, out2=None, pair: int = 0, splits: int = 1,
              split_stride: int = 0, lda: int | None = None, ldb: int | None = None, ldc: int | None = None,
-             ldr: int | None = None, ldc2: int | None = None) -> None:
-        """out[M,N] = a[M,K] @ b[N,K]^T with the stated epilogue (see rte_gemm_bf16)."""
+             ldr: int | None = None, ldc2: int | None = None, tile_group=None, n_groups: int = 0,
+             b_group_stride: int = 0, split_kblocks=None) -> None:
+        """out[M,N] = a[M,K] @ b[N,K]^T with the stated epilogue (see rte_gemm_bf16).  `tile_group` switches on the
+        grouped mode (B = stack of per-group matrices), `split_kblocks` the ragged split-K."""
         _require_cuda(a, b, out, residual, out2)
         args = A.GemmArgs()
         args.M, args.N, args.K = M, N, K
@@ -86,6 +88,9 @@ class CudaOps:
         args.splits, args.split_stride = splits, split_stride
         args.max_ctas = 0
         args.status = self.status.data_ptr()
+        args.tile_group = tile_group.data_ptr() if tile_group is not None else None
+        args.n_groups, args.b_group_stride = n_groups, b_group_stride
+        args.split_kblocks = split_kblocks.data_ptr() if split_kblocks is not None else None
         self._call("rte_gemm_bf16", C.byref(args), self.stream)
 
     def pick_splits(self, M: int, N: int, K: int) -> int:
@@ -321,6 +326,30 @@ class CudaOps:
     def kl_distill(self, hot_logits, exact_logits, temp, coef, idx, S: int, dlogits_hot, kl_rows, rows: int, V: int) -> None:
         self._call("rte_kl_distill", _ptr(hot_logits), _ptr(exact_logits), temp, coef, _ptr(idx), S, _ptr(dlogits_hot),
                    dlogits_hot.stride(0), _ptr(kl_rows), rows, V, self.stream)
+
+    # ------------------------------------------------------------------ cluster-pool FFN helpers
+    def cluster_route(self, q, centers, assignments, scores=None) -> None:
+        n, W = q.shape
+        self._call("rte_cluster_route", _ptr(q), q.stride(0), _ptr(centers), _ptr(assignments), _ptr(scores), n, W,
+                   centers.shape[0], self.stream)
+
+    def cluster_pack(self, assignments, n_clusters: int, perm, pos, counts, offsets, tile_group, kblocks) -> None:
+        self._call("rte_cluster_pack", _ptr(assignments), assignments.numel(), n_clusters, perm.numel(), _ptr(perm),
+                   _ptr(pos), _ptr(counts), _ptr(offsets), _ptr(tile_group), _ptr(kblocks), _ptr(self.status), self.stream)
+
+    def gather_rows_convert(self, src, idx, dst) -> None:
+        _require_cuda(src, idx, dst)
+        self._call("rte_gather_rows_convert", _ptr(src), int(src.dtype == torch.bfloat16), _ptr(idx), _ptr(dst),
+                   int(dst.dtype == torch.bfloat16), idx.numel(), dst.shape[-1], self.stream)
+
+    def csr_row_reduce(self, src, row_ptr, rows, dense, accumulate: bool = False) -> None:
+        self._call("rte_csr_row_reduce_f32", _ptr(src), _ptr(row_ptr), _ptr(rows), _ptr(dense), dense.shape[0],
+                   dense.shape[1], int(accumulate), self.stream)
+
+    def transpose(self, src, dst, accumulate: bool = False) -> None:
+        rows, cols = src.shape
+        self._call("rte_transpose_f32", _ptr(src), _ptr(dst), rows, cols, int(dst.dtype == torch.bfloat16),
+                   int(accumulate), self.stream)
 
     def swiglu_fwd(self, ug, z, rows: int, F: int) -> None:
         self._call("rte_swiglu_fwd", _ptr(ug), _ptr(z), rows, F, self.stream)

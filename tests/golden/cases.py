@@ -58,3 +58,18 @@ def oracle_cfgs(case: dict) -> tuple[O.ModelCfg, O.TrainCfg]:
 
 def oracle_output_cfg(case: dict) -> "O.OutputCfg | None":
     return O.OutputCfg(**case["output"]) if "output" in case else None
+
+
+def cluster_pool_inputs(seed: int = 21, tokens=(5, 40), d=64, f=128, rank=8, clusters=4, pool=64):
+    """Seeded inputs of the static cluster-pool FFN golden case (shared by the generator and the tests)."""
+    import torch
+    g = torch.Generator().manual_seed(seed)
+    x = torch.randn(*tokens, d, generator=g)
+    wug = torch.randn(2 * f, d, generator=g) * 0.1
+    wd = torch.randn(d, f, generator=g) * 0.1
+    up_a = torch.randn(d, rank, generator=g) * 0.3
+    gate_a = torch.randn(d, rank, generator=g) * 0.3
+    centers = torch.nn.functional.normalize(torch.randn(clusters, 2 * rank, generator=g), dim=-1)
+    candidate_ids = torch.stack([torch.randperm(f, generator=g)[:pool] for _ in range(clusters)])
+    probe = torch.randn(*tokens, d, generator=g)
+    return dict(x=x, wug=wug, wd=wd, up_a=up_a, gate_a=gate_a, centers=centers, candidate_ids=candidate_ids, probe=probe)

@@ -155,11 +155,38 @@ def per_op_vectors() -> dict[str, np.ndarray]:
     return out
 
 
+def cluster_pool_vectors() -> dict[str, np.ndarray]:
+    """The reference's StaticClusterPoolSwiGLU (layers.py:119-220) on the seeded inputs of
+    tests/golden/cases.py::cluster_pool_inputs: routing, output, and gradients of sum(out * probe)."""
+    from recursive_training_engine.layers import DenseSwiGLU, StaticClusterPoolSwiGLU
+    from tests.golden.cases import cluster_pool_inputs
+    t = cluster_pool_inputs()
+    d, f = t["wd"].shape
+    from types import SimpleNamespace
+    dense = DenseSwiGLU(SimpleNamespace(d_model=d, d_ff=f))          # the constructor reads these two fields only
+    with torch.no_grad():
+        dense.wug.weight.copy_(t["wug"])
+        dense.wd.weight.copy_(t["wd"])
+    mod = StaticClusterPoolSwiGLU(dense, {"up_a": t["up_a"], "gate_a": t["gate_a"]},
+                                  {"centers": t["centers"], "candidate_ids": t["candidate_ids"]}, rank=t["up_a"].shape[1])
+    x = t["x"].clone().requires_grad_()
+    out = mod(x)
+    (out * t["probe"]).sum().backward()
+    from recursive_training_engine.kernels.cluster_pool_ffn import route_to_static_centers
+    assign = route_to_static_centers(t["x"].reshape(-1, d), t["up_a"], t["gate_a"], t["centers"])
+    return {"out": out.detach().numpy(), "assignments": assign.numpy(), "dx": x.grad.numpy(),
+            "dwug": mod.wug.weight.grad.numpy(), "dwd": mod.wd.weight.grad.numpy()}
+
+
 def main() -> None:
     torch.set_num_threads(4)
+    only = set(sys.argv[1:])                     # e.g. `make_golden.py cluster_pool` rewrites that file alone
     for name, case in GOLDEN_CASES.items():
-        np.savez_compressed(HERE / f"{name}.npz", **run_case(name, case))
-    np.savez_compressed(HERE / "per_op.npz", **per_op_vectors())
+        if not only or name in only:
+            np.savez_compressed(HERE / f"{name}.npz", **run_case(name, case))
+    for name, fn in (("per_op", per_op_vectors), ("cluster_pool", cluster_pool_vectors)):
+        if not only or name in only:
+            np.savez_compressed(HERE / f"{name}.npz", **fn())
     print("written to", HERE)
 
 

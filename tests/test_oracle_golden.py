@@ -100,3 +100,21 @@ def test_lowest_index_tie_rule():
     vals, idx = O.topk_lowest(x, 4)
     assert idx.tolist() == [[1, 2, 4, 3], [0, 1, 2, 3]]
     assert vals.tolist() == [[3.0, 3.0, 3.0, 2.0], [5.0, 5.0, 5.0, 5.0]]
+
+
+def test_cluster_pool_ffn_restatement_matches_reference_golden():
+    """Routing, output and every gradient of StaticClusterPoolSwiGLU (layers.py:188-220) on the seeded case."""
+    from tests.golden.cases import cluster_pool_inputs
+    gold = np.load(GOLDEN / "cluster_pool.npz")
+    t = cluster_pool_inputs()
+    x, wug, wd = (t[k].clone().requires_grad_() for k in ("x", "wug", "wd"))
+    out, assign = O.static_cluster_pool_swiglu(x, wug, wd, t["up_a"], t["gate_a"], t["centers"], t["candidate_ids"])
+    (out * t["probe"]).sum().backward()
+    assert np.array_equal(assign.numpy(), gold["assignments"])
+    np.testing.assert_allclose(out.detach().numpy(), gold["out"], rtol=1e-5, atol=1e-6)
+    for got, key in ((x.grad, "dx"), (wug.grad, "dwug"), (wd.grad, "dwd")):
+        np.testing.assert_allclose(got.numpy(), gold[key], rtol=1e-4, atol=1e-5)
+    # the packing restatement: ascending member order, rank-addressed gather (cluster_pool_ffn.py:162-188)
+    pack, flat, counts, mx = O.cluster_pack_indices(assign, 4)
+    assert int(counts.sum()) == assign.numel() and mx == int(counts.max())
+    assert torch.equal(pack.reshape(-1)[flat], torch.arange(assign.numel()))
