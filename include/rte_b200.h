@@ -311,6 +311,23 @@ int rte_csr_row_reduce_f32(const float* src, const int32_t* row_ptr, const int32
 int rte_transpose_f32(const float* src, void* dst, int32_t rows, int32_t cols, int32_t dst_bf16, int32_t accumulate,
                       rte_stream_t stream);
 
+/* ------------------------------------------------ SVD-factor sparse FFN, mask mode (layers.py:342-643;
+ * kernels/svd_sparse_ffn_triton.py:480-714).  The selector factors, the exact up/gate pre-activations of all F
+ * neurons and the down projection are rte_gemm_bf16 launches; this is the per-token selection between them.
+ * hats f32 [rows, 2F] = (x@up_a@up_b | x@gate_a@gate_b); ug bf16 [rows, 2F] = exact (up | gate); wd_norm f32 [F] =
+ * row norms of w_down.  Candidates = union of the top up_m / gate_m / product_m neurons under |up_hat|*wn,
+ * |silu(gate_hat)|*wn, |up_hat*silu(gate_hat)|*wn; selected = top top_k candidates under |up*silu(gate)|*wn
+ * (ties: lowest index).  z_masked bf16 [rows, F] = selected ? up*silu(gate) : 0; selected uint8 [rows, F] and
+ * cand_count int32 [rows] optional.  max(up_m, gate_m, product_m) >= top_k is required.
+ * rte_svd_ffn_swiglu_bwd: dug bf16 [rows, 2F] = SwiGLU backward of dz bf16 [rows, F] on selected neurons, else 0.
+ * rte_row_norm_f32: out[r] = ||w[r, :]||_2.                                                                    */
+int rte_svd_ffn_select(const float* hats, const void* ug, const float* wd_norm, void* z_masked, uint8_t* selected,
+                       int32_t* cand_count, int32_t rows, int32_t F, int32_t up_m, int32_t gate_m, int32_t product_m,
+                       int32_t top_k, rte_stream_t stream);
+int rte_svd_ffn_swiglu_bwd(const void* ug, const void* dz, const uint8_t* selected, void* dug, int64_t rows, int32_t F,
+                           rte_stream_t stream);
+int rte_row_norm_f32(const float* w, float* out, int32_t rows, int32_t d, rte_stream_t stream);
+
 /* ------------------------------------------------ exact-audit replay helpers (audit.py:245-387; models.py:605-679;
  * layers.py:831-870).  The audited subset has a fixed size n (fixed-count sampler), chosen on the host.
  * Per-sample recipe choices stay on the device: every kernel below looks the recipe of (pass, sample) up in

@@ -771,3 +771,47 @@ def static_cluster_pool_swiglu(x: torch.Tensor, wug: torch.Tensor, wd: torch.Ten
     f = wd.shape[1]
     out = cluster_pool_ffn(flat, assignments, wug[:f], wug[f:], wd.t(), candidate_ids)
     return out.view(x.shape), assignments
+
+
+# ----------------------------------------------------------------------------- SVD-factor sparse FFN (mask mode)
+def topk_membership(scores: torch.Tensor, k: int) -> torch.Tensor:
+    """Boolean mask of the k largest entries per row, lowest index first among equals."""
+    mask = torch.zeros_like(scores, dtype=torch.bool)
+    if k > 0:
+        mask.scatter_(-1, topk_lowest(scores, min(k, scores.shape[-1]))[1], True)
+    return mask
+
+
+def svd_ffn_hats(x, up_a, up_b, gate_a, gate_b):
+    """layers.py:585-588: low-rank estimates of the up and gate pre-activations."""
+    return (x @ up_a) @ up_b, (x @ gate_a) @ gate_b
+
+
+def svd_ffn_candidates(up_hat, gate_hat, wd_norm, up_m: int, gate_m: int, product_m: int) -> torch.Tensor:
+    """layers.py:589-592,473-489: union of the top-m neurons under the three selector scores."""
+    gact = F.silu(gate_hat)
+    cand = topk_membership(up_hat.abs() * wd_norm, up_m)
+    cand |= topk_membership(gact.abs() * wd_norm, gate_m)
+    cand |= topk_membership((up_hat * gact).abs() * wd_norm, product_m)
+    return cand
+
+
+def svd_ffn_select(z, cand, wd_norm, top_k: int) -> torch.Tensor:
+    """layers.py:617-621: the top_k candidates by |z| * ||w_down row||."""
+    return topk_membership((z.abs() * wd_norm).masked_fill(~cand, float("-inf")), top_k)
+
+
+def svd_sparse_ffn(x, w_up, w_gate, w_down, up_a, up_b, gate_a, gate_b, *, top_k: int, up_m: int, gate_m: int,
+                   product_m: int, selected: torch.Tensor | None = None):
+    """SVDFactorSparseFFN.forward in mask mode (layers.py:531-637): exact SwiGLU over the selected neurons only.
+    Differentiable in x and the three weight matrices; the selection carries no gradient.  Requires
+    max(up_m, gate_m, product_m) >= top_k (otherwise the reference's result depends on an unspecified order)."""
+    flat = x.reshape(-1, x.shape[-1])
+    wd_norm = w_down.detach().float().norm(dim=-1)
+    z = (flat @ w_up.t()) * F.silu(flat @ w_gate.t())
+    if selected is None:
+        up_hat, gate_hat = svd_ffn_hats(flat.detach(), up_a, up_b, gate_a, gate_b)
+        cand = svd_ffn_candidates(up_hat, gate_hat, wd_norm, up_m, gate_m, product_m)
+        selected = svd_ffn_select(z.detach(), cand, wd_norm, top_k)
+    out = (z * selected) @ w_down
+    return out.view(x.shape), selected

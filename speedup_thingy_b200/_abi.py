@@ -98,6 +98,9 @@ PROTOTYPES = {
     "rte_gather_rows_convert": (C.c_int, [c_vp, c_i32, c_vp, c_vp, c_i32, c_i64, c_i32, c_vp]),
     "rte_csr_row_reduce_f32": (C.c_int, [c_vp, c_vp, c_vp, c_vp, c_i64, c_i32, c_i32, c_vp]),
     "rte_transpose_f32": (C.c_int, [c_vp, c_vp, c_i32, c_i32, c_i32, c_i32, c_vp]),
+    "rte_svd_ffn_select": (C.c_int, [c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, c_i32, c_i32, c_i32, c_i32, c_i32, c_i32, c_vp]),
+    "rte_svd_ffn_swiglu_bwd": (C.c_int, [c_vp, c_vp, c_vp, c_vp, c_i64, c_i32, c_vp]),
+    "rte_row_norm_f32": (C.c_int, [c_vp, c_vp, c_i32, c_i32, c_vp]),
     "rte_swiglu_fwd": (C.c_int, [c_vp, c_vp, c_i64, c_i32, c_vp]),
     "rte_swiglu_bwd": (C.c_int, [c_vp, c_vp, c_vp, c_i64, c_i32, c_vp]),
     "rte_cast_f32_bf16": (C.c_int, [c_vp, c_vp, c_i64, c_vp]),

@@ -351,6 +351,19 @@ class CudaOps:
         self._call("rte_transpose_f32", _ptr(src), _ptr(dst), rows, cols, int(dst.dtype == torch.bfloat16),
                    int(accumulate), self.stream)
 
+    # ------------------------------------------------------------------ SVD-factor sparse FFN helpers
+    def svd_ffn_select(self, hats, ug, wd_norm, z_masked, selected, cand_count, *, up_m, gate_m, product_m, top_k) -> None:
+        rows, F = z_masked.shape
+        self._call("rte_svd_ffn_select", _ptr(hats), _ptr(ug), _ptr(wd_norm), _ptr(z_masked), _ptr(selected),
+                   _ptr(cand_count), rows, F, up_m, gate_m, product_m, top_k, self.stream)
+
+    def svd_ffn_swiglu_bwd(self, ug, dz, selected, dug) -> None:
+        rows, F = dz.shape
+        self._call("rte_svd_ffn_swiglu_bwd", _ptr(ug), _ptr(dz), _ptr(selected), _ptr(dug), rows, F, self.stream)
+
+    def row_norm(self, w, out) -> None:
+        self._call("rte_row_norm_f32", _ptr(w), _ptr(out), w.shape[0], w.shape[1], self.stream)
+
     def swiglu_fwd(self, ug, z, rows: int, F: int) -> None:
         self._call("rte_swiglu_fwd", _ptr(ug), _ptr(z), rows, F, self.stream)
 

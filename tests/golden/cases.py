@@ -73,3 +73,17 @@ def cluster_pool_inputs(seed: int = 21, tokens=(5, 40), d=64, f=128, rank=8, clu
     candidate_ids = torch.stack([torch.randperm(f, generator=g)[:pool] for _ in range(clusters)])
     probe = torch.randn(*tokens, d, generator=g)
     return dict(x=x, wug=wug, wd=wd, up_a=up_a, gate_a=gate_a, centers=centers, candidate_ids=candidate_ids, probe=probe)
+
+
+SVD_FFN = dict(d=32, f=64, rank=8, top_k=8, up_m=8, gate_m=8, product_m=8)
+
+
+def svd_ffn_inputs(seed: int = 31, tokens=(3, 11)):
+    """Seeded inputs of the SVD-factor sparse FFN golden case (factors drawn directly, no SVD refresh)."""
+    import torch
+    c = SVD_FFN
+    g = torch.Generator().manual_seed(seed)
+    r = lambda *s, scale: torch.randn(*s, generator=g) * scale  # noqa: E731
+    return dict(x=r(*tokens, c["d"], scale=1.0), w_up=r(c["f"], c["d"], scale=0.2), w_gate=r(c["f"], c["d"], scale=0.2),
+                w_down=r(c["f"], c["d"], scale=0.2), up_a=r(c["d"], c["rank"], scale=0.3), up_b=r(c["rank"], c["f"], scale=0.3),
+                gate_a=r(c["d"], c["rank"], scale=0.3), gate_b=r(c["rank"], c["f"], scale=0.3), probe=r(*tokens, c["d"], scale=1.0))

@@ -178,13 +178,33 @@ def cluster_pool_vectors() -> dict[str, np.ndarray]:
             "dwug": mod.wug.weight.grad.numpy(), "dwd": mod.wd.weight.grad.numpy()}
 
 
+def svd_ffn_vectors() -> dict[str, np.ndarray]:
+    """The reference's SVDFactorSparseFFN (layers.py:342-643, mask mode) on tests/golden/cases.py::svd_ffn_inputs."""
+    from recursive_training_engine.layers import SVDFactorSparseFFN
+    from tests.golden.cases import SVD_FFN, svd_ffn_inputs
+    c, t = SVD_FFN, svd_ffn_inputs()
+    mod = SVDFactorSparseFFN(c["d"], c["f"], rank=c["rank"], top_k=c["top_k"], up_m=c["up_m"], gate_m=c["gate_m"],
+                             product_m=c["product_m"], candidate_mode="mask", refresh_on_init=False)
+    with torch.no_grad():
+        for k in ("w_up", "w_gate", "w_down", "up_a", "up_b", "gate_a", "gate_b"):
+            getattr(mod, k).copy_(t[k])
+    x = t["x"].clone().requires_grad_()
+    out, aux = mod(x, return_aux=True)
+    (out * t["probe"]).sum().backward()
+    sel = torch.zeros(x.shape[0] * x.shape[1], c["f"], dtype=torch.bool).scatter_(-1, aux["selected_ids"], True)
+    return {"out": out.detach().numpy(), "selected": sel.numpy(), "avg_candidate_size": np.float64(aux["avg_candidate_size"]),
+            "dx": x.grad.numpy(), "dw_up": mod.w_up.grad.numpy(), "dw_gate": mod.w_gate.grad.numpy(),
+            "dw_down": mod.w_down.grad.numpy()}
+
+
 def main() -> None:
     torch.set_num_threads(4)
     only = set(sys.argv[1:])                     # e.g. `make_golden.py cluster_pool` rewrites that file alone
     for name, case in GOLDEN_CASES.items():
         if not only or name in only:
             np.savez_compressed(HERE / f"{name}.npz", **run_case(name, case))
-    for name, fn in (("per_op", per_op_vectors), ("cluster_pool", cluster_pool_vectors)):
+    for name, fn in (("per_op", per_op_vectors), ("cluster_pool", cluster_pool_vectors),
+                     ("svd_ffn", svd_ffn_vectors)):
         if not only or name in only:
             np.savez_compressed(HERE / f"{name}.npz", **fn())
     print("written to", HERE)

@@ -118,3 +118,23 @@ def test_cluster_pool_ffn_restatement_matches_reference_golden():
     pack, flat, counts, mx = O.cluster_pack_indices(assign, 4)
     assert int(counts.sum()) == assign.numel() and mx == int(counts.max())
     assert torch.equal(pack.reshape(-1)[flat], torch.arange(assign.numel()))
+
+
+def test_svd_sparse_ffn_restatement_matches_reference_golden():
+    """SVDFactorSparseFFN in mask mode (layers.py:531-637): selected neurons, candidate count, output, gradients."""
+    from tests.golden.cases import SVD_FFN as c, svd_ffn_inputs
+    gold = np.load(GOLDEN / "svd_ffn.npz")
+    t = svd_ffn_inputs()
+    leaves = {k: t[k].clone().requires_grad_() for k in ("x", "w_up", "w_gate", "w_down")}
+    kw = dict(top_k=c["top_k"], up_m=c["up_m"], gate_m=c["gate_m"], product_m=c["product_m"])
+    out, sel = O.svd_sparse_ffn(leaves["x"], leaves["w_up"], leaves["w_gate"], leaves["w_down"], t["up_a"], t["up_b"],
+                                t["gate_a"], t["gate_b"], **kw)
+    (out * t["probe"]).sum().backward()
+    assert np.array_equal(sel.numpy(), gold["selected"]) and (sel.sum(-1) == c["top_k"]).all()
+    flat = t["x"].reshape(-1, c["d"])
+    cand = O.svd_ffn_candidates(*O.svd_ffn_hats(flat, t["up_a"], t["up_b"], t["gate_a"], t["gate_b"]),
+                                t["w_down"].norm(dim=-1), c["up_m"], c["gate_m"], c["product_m"])
+    assert abs(float(cand.sum(-1).float().mean()) - float(gold["avg_candidate_size"])) < 1e-6
+    np.testing.assert_allclose(out.detach().numpy(), gold["out"], rtol=1e-5, atol=1e-6)
+    for k, name in (("x", "dx"), ("w_up", "dw_up"), ("w_gate", "dw_gate"), ("w_down", "dw_down")):
+        np.testing.assert_allclose(leaves[k].grad.numpy(), gold[name], rtol=1e-4, atol=1e-5)
