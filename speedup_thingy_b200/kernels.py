@@ -434,3 +434,79 @@ k_pack_by_recipe = _not_on_this_path("k_pack_by_recipe", "only the deferred-grou
 k_unpack_from_recipe = _not_on_this_path("k_unpack_from_recipe", "only the deferred-grouped exact mode calls it")
 k_sample_audit_mask = _not_on_this_path("k_sample_audit_mask", "the audited subset is drawn on the host "
                                                                 "(fixed-count sampler), see AuditReplay.choose")
+
+
+# --------------------------------------------------------------------------- packed SwiGLU FFN
+class _PackedSwiGLUFFN(torch.autograd.Function):
+    """(x @ wug^T -> (up | gate)) -> up * silu(gate) -> @ wdown_rows, saving (x, wug, wdown_rows, ug, z) in bf16
+    exactly as the reference's _TritonPackedSwiGLUFFN does (kernels/active_swiglu_triton.py:62-108)."""
+
+    @staticmethod
+    def forward(ctx, x, wug, wdown_rows):
+        ops = _ops_for(x)
+        N, d = x.shape
+        m = wug.shape[0] // 2
+        x16, wug16, wd16 = _bf16(x), _bf16(wug), _bf16(wdown_rows)
+        ug = torch.empty(N, 2 * m, dtype=torch.bfloat16, device=x.device)
+        z = torch.empty(N, m, dtype=torch.bfloat16, device=x.device)
+        y = torch.empty(N, d, dtype=torch.float32, device=x.device)
+        if m % 64 == 0 and N <= 1024:        # small batches: SwiGLU fused into the GEMM epilogue
+            ops.gemm(x16, wug16, z, M=N, N=2 * m, K=d, epilogue=A.EPI_SWIGLU_FWD, out2=ug, pair=m)
+        else:                                # large batches: plain-store GEMM + one vectorised pass is faster
+            ops.gemm(x16, wug16, ug, M=N, N=2 * m, K=d)
+            ops.swiglu_fwd(ug, z, N, m)
+        ops.gemm(z, wd16, y, M=N, N=d, K=m, b_mn=True, epilogue=A.EPI_F32)
+        ctx.save_for_backward(x16, wug16, wd16, ug, z)
+        ctx.dtypes = (x.dtype, wug.dtype, wdown_rows.dtype)
+        return y.to(x.dtype)
+
+    @staticmethod
+    def backward(ctx, dy):
+        x16, wug16, wd16, ug, z = ctx.saved_tensors
+        ops = _ops_for(x16)
+        N, d = x16.shape
+        m = wd16.shape[0]
+        dy16 = _bf16(dy)
+        dz = torch.empty(N, m, dtype=torch.bfloat16, device=x16.device)
+        dug = torch.empty(N, 2 * m, dtype=torch.bfloat16, device=x16.device)
+        ops.gemm(dy16, wd16, dz, M=N, N=m, K=d)
+        ops.swiglu_bwd(ug, dz, dug, N, m)
+        dx = torch.empty(N, d, dtype=torch.float32, device=x16.device)
+        ops.gemm(dug, wug16, dx, M=N, N=d, K=2 * m, b_mn=True, epilogue=A.EPI_F32)
+        dwug = torch.empty(2 * m, d, dtype=torch.float32, device=x16.device)
+        ops.gemm_wgrad(dug, x16, dwug, M=2 * m, N=d, K=N)
+        dwd = torch.empty(m, d, dtype=torch.float32, device=x16.device)
+        ops.gemm_wgrad(z, dy16, dwd, M=m, N=d, K=N)
+        xd, ud, dd = ctx.dtypes
+        return dx.to(xd), dwug.to(ud), dwd.to(dd)
+
+
+def packed_swiglu_ffn(x, wug, wdown_rows):
+    """Drop-in for ``triton_packed_swiglu_ffn`` (kernels/active_swiglu_triton.py:111-125; layers.py:90-116,284-339):
+    x [tokens, d], wug [2*active_m, d] = (up rows | gate rows), wdown_rows [active_m, d].  Same shape errors."""
+    _require_cuda_tensor(x, wug, wdown_rows)
+    if x.ndim != 2 or wug.ndim != 2 or wdown_rows.ndim != 2:
+        raise ValueError("expected x [N,D], wug [2M,D], wdown_rows [M,D]")
+    if wug.shape[0] % 2 != 0:
+        raise ValueError("wug first dimension must be 2M")
+    if wdown_rows.shape[0] != wug.shape[0] // 2:
+        raise ValueError("wdown_rows first dimension must match M")
+    _check_gemm_dims(x.shape[1], wdown_rows.shape[0])
+    return _PackedSwiGLUFFN.apply(x, wug, wdown_rows)
+
+
+triton_packed_swiglu_ffn = packed_swiglu_ffn          # the symbol layers.py:12-22 imports
+
+
+def active_union_swiglu(x, wug_weight, wd_weight, active_ids):
+    """ActiveUnionSwiGLU.forward (layers.py:267-282): SwiGLU over the sorted unique `active_ids` only.
+    wug_weight [2F, d], wd_weight [d, F]; the active rows are gathered by the C-ABI row gather."""
+    _require_cuda_tensor(x, wug_weight, wd_weight, active_ids)
+    ids = torch.unique(active_ids.reshape(-1).to(torch.int64), sorted=True)
+    f = wd_weight.shape[1]
+    rows = torch.cat([ids, ids + f]).to(torch.int32)
+    # index_select keeps autograd's scatter of the row gradients into the dense weights
+    wug_active = wug_weight.index_select(0, rows.long())
+    wd_rows = wd_weight.t().index_select(0, ids)
+    flat = x.reshape(-1, x.shape[-1])
+    return packed_swiglu_ffn(flat, wug_active, wd_rows).view(*x.shape[:-1], -1)

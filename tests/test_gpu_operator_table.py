@@ -182,3 +182,42 @@ def test_strict_cuda_and_status_contract():
         K.k_macro_phi()
     with pytest.raises(ValueError):
         K.k_fused_rmsnorm(torch.randn(2, 8, device=DEV), torch.ones(4, device=DEV))
+
+
+@pytest.mark.parametrize("N,d,m", [(50, 64, 64), (1500, 128, 192), (40, 64, 24)])
+def test_packed_swiglu_ffn_matches_reference_math_and_grads(N, d, m):
+    g = torch.Generator().manual_seed(N)
+    x, wug, wdr = torch.randn(N, d, generator=g), torch.randn(2 * m, d, generator=g) * 0.2, torch.randn(m, d, generator=g) * 0.2
+    L = [t.to(DEV).requires_grad_() for t in (x, wug, wdr)]
+    out = K.triton_packed_swiglu_ffn(*L)
+    R = [t.bfloat16().float().requires_grad_() for t in (x, wug, wdr)]
+    up, gate = (R[0] @ R[1].t()).chunk(2, dim=-1)
+    ref = (up * torch.nn.functional.silu(gate)) @ R[2]
+    _close(out, ref, 2e-2)
+    probe = torch.randn(N, d, generator=g)
+    (ref * probe).sum().backward()
+    (out * probe.to(DEV)).sum().backward()
+    for a, b in zip(L, R):
+        _close(a.grad, b.grad, 3e-2)
+    with pytest.raises(ValueError):
+        K.packed_swiglu_ffn(L[0], L[1][:-1], L[2])
+
+
+def test_active_union_swiglu_evaluates_only_the_active_rows():
+    g = torch.Generator().manual_seed(8)
+    d, F_ = 64, 256
+    x, wug, wd = torch.randn(3, 20, d, generator=g), torch.randn(2 * F_, d, generator=g) * 0.2, torch.randn(d, F_, generator=g) * 0.2
+    ids = torch.randperm(F_, generator=g)[:64].repeat(2)             # duplicates collapse (layers.py:262)
+    L = [t.to(DEV).requires_grad_() for t in (x, wug, wd)]
+    out = K.active_union_swiglu(L[0], L[1], L[2], ids.to(DEV))
+    R = [t.bfloat16().float().requires_grad_() for t in (x, wug, wd)]
+    u = torch.unique(ids)
+    ref = ((R[0] @ R[1][u].t()) * torch.nn.functional.silu(R[0] @ R[1][u + F_].t())) @ R[2].t()[u]
+    _close(out, ref, 2e-2)
+    ref.sum().backward()
+    out.sum().backward()
+    _close(L[1].grad, R[1].grad, 3e-2)
+    _close(L[2].grad, R[2].grad, 3e-2)
+    inactive = torch.ones(F_, dtype=torch.bool)
+    inactive[u] = False
+    assert (L[1].grad.cpu()[:F_][inactive] == 0).all()
