@@ -98,9 +98,16 @@ class AuditReplay:
         self.row_weight_a = torch.full((n,), 1.0 / (eng.B * eng.S * eng.world) / self.p_inc, dtype=f32, device=dev)
         # backward scratch
         self.dn_f32, self.dh0_acc, self.dcur, self.dalt = e(Ma, d), e(Ma, d), e(Ma, d), e(Ma, d)
-        self.d16a, self.d16b = e(Ma, d, dtype=bf), e(Ma, d, dtype=bf)
-        self.dz16, self.dug16, self.dqkv16 = e(Ma, f, dtype=bf), e(Ma, 2 * f, dtype=bf), e(Ma, 3 * d, dtype=bf)
-        self.partial_g, self.partial_b = e(8 * 148, d), e(8 * 148, d)
+        self.d16b = e(Ma, d, dtype=bf)
+        self.dz16 = e(Ma, f, dtype=bf)
+        # inputs of the weight-gradient launches are kept per pass: those launches run on their own stream and may
+        # trail the data-gradient chain, which therefore must not reuse what they still have to read
+        self.d16_mlp, self.d16_attn = [e(Ma, d, dtype=bf) for _ in range(T)], [e(Ma, d, dtype=bf) for _ in range(T)]
+        self.dug16, self.dqkv16 = [e(Ma, 2 * f, dtype=bf) for _ in range(T)], [e(Ma, 3 * d, dtype=bf) for _ in range(T)]
+        PR = 128
+        self.partials = [[(e(PR, d), e(PR, d), e(PR, d)) for _ in range(2)] for _ in range(T)]
+        self.coda_tmps = [_Temps(Ma, cfg, dev) for _ in range(cfg.n_coda)]
+        self.dx16_alt = e(Ma, d, dtype=bf)
         self.P = 64
         self.part_alpha, self.part_attn, self.part_mlp = e(T * self.P), e(T * self.P), e(T * self.P)
         # The replay runs on its own stream beside the hot pass, so the gradients it contributes to parameters the
@@ -133,15 +140,14 @@ class AuditReplay:
         self.last_chosen = chosen
 
     # ------------------------------------------------------------------ forward
-    def forward_replay(self, h0: torch.Tensor, h_phi: torch.Tensor) -> None:
-        """Everything of the replay's forward that needs only h0, the macro output and the routing decisions."""
+    def forward_replay(self, h0: torch.Tensor) -> None:
+        """Everything of the replay's forward that needs only h0 and the routing decisions."""
         eng = self.eng
         o, cfg, p, sh = eng.ops, eng.cfg, eng.params, eng.shadow
         n, S, T, Ma, d, f, V = self.n, self.S, self.T, self.Ma, cfg.d_model, cfg.d_ff, cfg.vocab_size
         o.gather_rows(h0, self.idx, self.h0a, n, S * d * 4)
         o.gather_rows(h0, self.idx, self.h[0], n, S * d * 4)
         o.gather_rows(eng.targets, self.idx, self.targets_a, n, S * 8)
-        o.gather_rows(h_phi, self.idx, self.hot_end, n, S * d * 4)
         o.audit_route(eng.route["recipe_id_by_pass"], eng.route["depth"], self.idx, self.rid, self.active, n, T)
         alpha = p["core.alpha_inj"].view(1)
         for t in range(T):
@@ -171,7 +177,14 @@ class AuditReplay:
         self.x_last = x
         o.rmsnorm_fwd(x, p["final_norm.weight"], self.hidden16, self.rstd_f)
         o.gemm(self.hidden16, sh["embed.weight"], self.logits, M=Ma, N=V, K=d)
-        # distillation terms (hot side receives the gradient, the exact side is a constant: macro.py:413-415)
+
+    def forward_distill(self, h_phi: torch.Tensor) -> None:
+        """Distillation terms between the macro output and the replay's endpoint (the hot side receives the
+        gradient, the exact side is a constant: macro.py:413-415).  Issued once the macro operator has run."""
+        eng = self.eng
+        o, cfg = eng.ops, eng.cfg
+        n, S, T, d = self.n, self.S, self.T, cfg.d_model
+        o.gather_rows(h_phi, self.idx, self.hot_end, n, S * d * 4)
         tr, w = eng.tr, 1.0 / eng.world
         o.macro_distill(self.hot_end, self.h[T], self.h0a, tr.lambda_delta_dir * w, tr.lambda_delta_rms * w,
                         tr.lambda_endpoint_normed * w, tr.lambda_endpoint_raw * w, self.terms, self.dhot_extra, n, S, d)
@@ -201,16 +214,26 @@ class AuditReplay:
         o, cfg, p, sh, g = eng.ops, eng.cfg, eng.params, eng.shadow, eng.grads
         Ma, d, V = self.Ma, cfg.d_model, cfg.vocab_size
         t = self.tmp
+        self._defer_param_grads(True)
         o.gemm(self.logits, sh["embed.weight"], t.dn16, M=Ma, N=d, K=V, b_mn=True)
         gs = self.g_shared
         o.gemm_wgrad(self.logits, self.hidden16, gs["embed.weight"], M=V, N=d, K=Ma, ws=self.ws)
         o.rmsnorm_bwd(self.x_last, p["final_norm.weight"], self.rstd_f, t.dn16, None, t.dxa, t.dx16,
                       gs["final_norm.weight"], t.partial)
         dcur, dalt = t.dxa, t.dxb
-        for blk in reversed(self.coda):
-            eng._block_bwd(blk, dcur, t.dx16, dalt, t.dx16, t.dxc, tmp=t, mark_ready=False, grads=gs, ws=self.ws)
+        in16, out16 = t.dx16, self.dx16_alt          # distinct: the deferred wd gradient still reads the block's input
+        for i, blk in enumerate(reversed(self.coda)):
+            eng._block_bwd(blk, dcur, in16, dalt, out16, t.dxc, tmp=self.coda_tmps[i], mark_ready=False, grads=gs, ws=self.ws)
             dcur, dalt = dalt, dcur
+            in16, out16 = out16, in16
+        self._defer_param_grads(False)
         return dcur
+
+    def _defer_param_grads(self, on: bool) -> None:
+        """Routes the replay's weight-gradient launches to the parameter-gradient stream (see CudaOps.param_stream)."""
+        eng = self.eng
+        if eng._param_stream is not None and hasattr(eng.ops, "param_stream"):
+            eng.ops.param_stream = eng._param_stream if on else None
 
     def backward_core(self, dh_last: torch.Tensor) -> None:
         """Backward through the t_max banked passes (the subset's h0 gradient is folded in by `merge`)."""
@@ -219,43 +242,52 @@ class AuditReplay:
         n, S, T, Ma, d, f, P = self.n, self.S, self.T, self.Ma, cfg.d_model, cfg.d_ff, self.P
         alpha = p["core.alpha_inj"].view(1)
         o.fill_(self.dh0_acc, 0.0)
+        # With several banks the per-bank buffers are reused inside a pass, so everything stays on the chain (after
+        # the head's deferred launches, which share the split-K workspace, have finished); the single-bank case (the
+        # usual one) defers its weight gradients.
+        defer = cfg.ffn_banks == 1 and cfg.attn_banks == 1
+        if not defer and eng._param_stream is not None:
+            torch.cuda.current_stream(eng.device).wait_stream(eng._param_stream)
+        self._defer_param_grads(defer)
         dnext, dthis = dh_last, (self.dcur if dh_last is not self.dcur else self.dalt)
         for t in reversed(range(T)):
             rid, first = self.rid[t], t == T - 1
             acc = not first
+            d16m, d16a, dug16, dqkv16 = self.d16_mlp[t], self.d16_attn[t], self.dug16[t], self.dqkv16[t]
+            (pw2, pg2, pb2), (pw1, pg1, pb1) = self.partials[t]
             du, dht = self.tmp.dxc, self.tmp.dxb if dnext is not self.tmp.dxb else self.tmp.dxa
             if du is dnext:
                 du = self.tmp.dxa if dht is not self.tmp.dxa else self.tmp.dxb
             # out = active ? u + s_mlp * mlp : h_in
             o.scaled_residual_bwd(dnext, self.mlp_acc[t], p["core.pass_mlp_scale"][t:t + 1], self.active[t], du,
-                                          self.d16a, None, None, self.part_mlp[t * P:(t + 1) * P], n, S * d)
+                                          d16m, None, None, self.part_mlp[t * P:(t + 1) * P], n, S * d)
             for bk in range(cfg.ffn_banks):
-                o.gemm(self.d16a, sh["core.mlp.wd"][bk], self.dz16, M=Ma, N=f, K=d)
-                o.gemm_wgrad(self.zm[t][bk], self.d16a, g["core.mlp.wd"][bk], M=f, N=d, K=Ma, accumulate=acc, ws=self.ws)
-                o.swiglu_masked_bwd(self.ug[t][bk], self.dz16, rid, self.ffn_tab[bk], S, self.dug16, Ma, f)
-                o.gemm(self.dug16, sh["core.mlp.wug"][bk], self.dn_f32, M=Ma, N=d, K=2 * f, epilogue=A.EPI_F32,
+                o.gemm(d16m, sh["core.mlp.wd"][bk], self.dz16, M=Ma, N=f, K=d)
+                o.gemm_wgrad(self.zm[t][bk], d16m, g["core.mlp.wd"][bk], M=f, N=d, K=Ma, accumulate=acc, ws=self.ws)
+                o.swiglu_masked_bwd(self.ug[t][bk], self.dz16, rid, self.ffn_tab[bk], S, dug16, Ma, f)
+                o.gemm(dug16, sh["core.mlp.wug"][bk], self.dn_f32, M=Ma, N=d, K=2 * f, epilogue=A.EPI_F32,
                        residual=self.dn_f32 if bk > 0 else None)
-                o.gemm_wgrad(self.n2[t], self.dug16, g["core.mlp.wug"][bk], M=d, N=2 * f, K=Ma, accumulate=acc, ws=self.ws)
+                o.gemm_wgrad(self.n2[t], dug16, g["core.mlp.wug"][bk], M=d, N=2 * f, K=Ma, accumulate=acc, ws=self.ws)
             o.rmsnorm_bwd(self.u[t], p["core.norm2.weight"], self.rstd2[t], self.dn_f32, du, du, None,
-                          g["core.norm2.weight"], self.tmp.partial, film_gamma=p["core.pass_gamma2"][t],
+                          g["core.norm2.weight"], pw2, film_gamma=p["core.pass_gamma2"][t],
                           dgamma_out=g["core.pass_gamma2"][t], dbeta_out=g["core.pass_beta2"][t],
-                          partial_g=self.partial_g, partial_b=self.partial_b, accumulate_dw=acc)
+                          partial_g=pg2, partial_b=pb2, accumulate_dw=acc)
             # u = ht + s_attn * attn
-            o.scaled_residual_bwd(du, self.attn_acc[t], p["core.pass_attn_scale"][t:t + 1], None, dht, self.d16a, None, None,
+            o.scaled_residual_bwd(du, self.attn_acc[t], p["core.pass_attn_scale"][t:t + 1], None, dht, d16a, None, None,
                                   self.part_attn[t * P:(t + 1) * P], n, S * d)
             for bk in range(cfg.attn_banks):
-                o.gemm(self.d16a, sh["core.attn.wo"][bk], self.d16b, M=Ma, N=d, K=d)
-                o.gemm_wgrad(self.ym[t][bk], self.d16a, g["core.attn.wo"][bk], M=d, N=d, K=Ma, accumulate=acc, ws=self.ws)
+                o.gemm(d16a, sh["core.attn.wo"][bk], self.d16b, M=Ma, N=d, K=d)
+                o.gemm_wgrad(self.ym[t][bk], d16a, g["core.attn.wo"][bk], M=d, N=d, K=Ma, accumulate=acc, ws=self.ws)
                 o.colmask_mul(self.d16b, rid, self.head_tab[bk], S, self.d16b, Ma, d)
-                o.attn_bwd(self.qkv[t][bk], self.y[t][bk], self.d16b, self.lse[t][bk], self.dqkv16, B=n, S=S,
+                o.attn_bwd(self.qkv[t][bk], self.y[t][bk], self.d16b, self.lse[t][bk], dqkv16, B=n, S=S,
                            n_heads=cfg.n_heads, head_dim=cfg.head_dim)
-                o.gemm(self.dqkv16, sh["core.attn.wqkv"][bk], self.dn_f32, M=Ma, N=d, K=3 * d, epilogue=A.EPI_F32,
+                o.gemm(dqkv16, sh["core.attn.wqkv"][bk], self.dn_f32, M=Ma, N=d, K=3 * d, epilogue=A.EPI_F32,
                        residual=self.dn_f32 if bk > 0 else None)
-                o.gemm_wgrad(self.n1[t], self.dqkv16, g["core.attn.wqkv"][bk], M=d, N=3 * d, K=Ma, accumulate=acc, ws=self.ws)
+                o.gemm_wgrad(self.n1[t], dqkv16, g["core.attn.wqkv"][bk], M=d, N=3 * d, K=Ma, accumulate=acc, ws=self.ws)
             o.rmsnorm_bwd(self.ht[t], p["core.norm1.weight"], self.rstd1[t], self.dn_f32, dht, dht, None,
-                          g["core.norm1.weight"], self.tmp.partial, film_gamma=p["core.pass_gamma1"][t],
+                          g["core.norm1.weight"], pw1, film_gamma=p["core.pass_gamma1"][t],
                           dgamma_out=g["core.pass_gamma1"][t], dbeta_out=g["core.pass_beta1"][t],
-                          partial_g=self.partial_g, partial_b=self.partial_b, accumulate_dw=acc)
+                          partial_g=pg1, partial_b=pb1, accumulate_dw=acc)
             # ht = h_in + alpha * h0
             o.scaled_residual_bwd(dht, self.h0a, alpha, None, dthis, None, self.dh0_acc, None,
                                   self.part_alpha[t * P:(t + 1) * P], n, S * d)
@@ -268,6 +300,9 @@ class AuditReplay:
         o.segment_sum(self.part_attn, g["core.pass_attn_scale"], T, P)
         o.segment_sum(self.part_alpha, g["core.alpha_inj"].view(1), 1, T * P)
         self.dh_first = dnext
+        self._defer_param_grads(False)
+        if eng._param_stream is not None:             # the replay's stream ends only when its weight gradients have
+            torch.cuda.current_stream(eng.device).wait_stream(eng._param_stream)
 
     def merge(self, dh0_hot: torch.Tensor) -> None:
         """After the join with the hot pass: adds the replay's share of the shared gradients and of d h0."""

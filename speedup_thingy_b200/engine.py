@@ -134,6 +134,7 @@ class _Temps:
         self.dqkv = torch.empty(M, 3 * d, dtype=bf, device=device)
         self.dxa, self.dxb, self.dxc = (torch.empty(M, d, dtype=f32, device=device) for _ in range(3))
         self.partial = torch.empty(8 * 148, d, dtype=f32, device=device)
+        self.partial2 = torch.empty(8 * 148, d, dtype=f32, device=device)      # second norm backward of a block
 
 
 class TrainEngine:
@@ -306,6 +307,7 @@ class TrainEngine:
             self.shortlist_dups = e(M, dtype=i32)
         self.audit = None
         self._side_stream = torch.cuda.Stream(device=dev) if (self.audit_k and dev.type == "cuda") else None
+        self._param_stream = torch.cuda.Stream(device=dev) if (self.audit_k and dev.type == "cuda") else None
         if self.audit_k:
             from .audit import AuditReplay
             self.audit = AuditReplay(self, self.audit_k)
@@ -455,7 +457,7 @@ class TrainEngine:
         o.gemm_wgrad(t.dqkv, blk.n1, g[f"{pre}.attn.wqkv.weight"], M=3 * d, N=d, K=M, accumulate=accumulate, ws=ws)
         ready(f"{pre}.attn.wqkv.weight")
         o.rmsnorm_bwd(blk.x_in, p[f"{pre}.norm1.weight"], blk.rstd1, t.dn16, du, dx, dx16,
-                      g[f"{pre}.norm1.weight"], t.partial, accumulate_dw=accumulate)
+                      g[f"{pre}.norm1.weight"], t.partial2, accumulate_dw=accumulate)
         ready(f"{pre}.norm1.weight")
 
     # ------------------------------------------------------------------ forward + backward
@@ -474,15 +476,20 @@ class TrainEngine:
             o.router_fwd(h0, self._router_weight_dict(), self.depth_values, self.route, B=B, S=S, d=d,
                          hid=cfg.router_hidden_dim, R=cfg.recipe_count, K=len(cfg.depth_choices), T=cfg.t_max,
                          fixed_recipe=tr.fixed_recipe, fixed_depth_id=fixed_depth_id)
+            if self.audit is not None:
+                # exact replay of the audited samples: needs only h0 and the routing, so it starts here and runs
+                # beside the macro operator and the rest of the hot pass
+                self._side_wait_main()
+                with self._on_side():
+                    self.audit.forward_replay(h0)
             o.macro_phi_fwd(h0, self._phi_param_dict(), self.route["recipe_id"], self.route["depth_id"],
                             cfg.macro_update_scale, self.h_phi, self.phi_rstd, self.phi_pooled, self.phi_act,
                             B=B, S=S, d=d, m=cfg.macro_rank, K=len(cfg.depth_choices))
             x = self.h_phi
             if self.audit is not None:
-                # exact replay of the audited samples, concurrent with the rest of the hot pass
                 self._side_wait_main()
                 with self._on_side():
-                    self.audit.forward_replay(h0, self.h_phi)
+                    self.audit.forward_distill(self.h_phi)
             for blk in self.coda:
                 x = self._block_fwd(blk, x)
         x_last = x

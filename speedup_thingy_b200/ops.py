@@ -42,6 +42,11 @@ class CudaOps:
         self.status = torch.zeros(1, dtype=torch.int32, device=self.device)
         self.launches = 0          # kernels-entry calls issued (for bench accounting)
         self._split_ws: torch.Tensor | None = None
+        self.gemm_max_ctas = 0     # 0 = one persistent CTA per SM; smaller values leave SMs to kernels of other streams
+        # When set, launches that only produce PARAMETER gradients (weight-gradient GEMMs with their split reduction,
+        # column-sum reductions of the norm backward) go to this stream, ordered after the work issued so far on the
+        # current one: a latency-bound backward chain then carries only the data-gradient launches.
+        self.param_stream: torch.cuda.Stream | None = None
         self._rope_tables: dict[tuple[int, int], torch.Tensor] = {}
 
     # ------------------------------------------------------------------ helpers
@@ -55,6 +60,14 @@ class CudaOps:
         if code != 0:
             self.status.zero_()
             raise A.RteError(f"device status {code}: {self.lib.rte_status_string(code).decode()}")
+
+    def _deferred(self):
+        import contextlib
+        ps = self.param_stream
+        if ps is None:
+            return contextlib.nullcontext()
+        ps.wait_stream(torch.cuda.current_stream(self.device))
+        return torch.cuda.stream(ps)
 
     def _call(self, name: str, *args) -> None:
         self.launches += 1
@@ -86,7 +99,7 @@ class CudaOps:
         args.ldc2 = (ldc2 if ldc2 is not None else out2.stride(-2)) if out2 is not None else 0
         args.b_pair_offset = pair
         args.splits, args.split_stride = splits, split_stride
-        args.max_ctas = 0
+        args.max_ctas = self.gemm_max_ctas
         args.status = self.status.data_ptr()
         args.tile_group = tile_group.data_ptr() if tile_group is not None else None
         args.n_groups, args.b_group_stride = n_groups, b_group_stride
@@ -111,16 +124,17 @@ class CudaOps:
         """out f32 [M,N] (+)= a_t^T @ b_t where a_t is stored [K,M] and b_t is stored [K,N]
         (both MN-major for the tensor core), split along K across SMs and reduced in fixed order."""
         splits = self.pick_splits(M, N, K)
-        if splits == 1 and not accumulate:
-            self.gemm(a_t, b_t, out, M=M, N=N, K=K, a_mn=True, b_mn=True, epilogue=A.EPI_F32, lda=lda, ldb=ldb, ldc=N)
-            return
-        if ws is None:
-            ws = self.split_workspace(splits * M * N)
-        elif ws.numel() < splits * M * N:
-            raise A.RteError("split-K workspace too small")
-        self.gemm(a_t, b_t, ws, M=M, N=N, K=K, a_mn=True, b_mn=True, epilogue=A.EPI_F32, splits=splits,
-                  split_stride=M * N, lda=lda, ldb=ldb, ldc=N)
-        self.reduce_splits(ws, splits, M * N, M * N, out, accumulate)
+        with self._deferred():
+            if splits == 1 and not accumulate:
+                self.gemm(a_t, b_t, out, M=M, N=N, K=K, a_mn=True, b_mn=True, epilogue=A.EPI_F32, lda=lda, ldb=ldb, ldc=N)
+                return
+            if ws is None:
+                ws = self.split_workspace(splits * M * N)
+            elif ws.numel() < splits * M * N:
+                raise A.RteError("split-K workspace too small")
+            self.gemm(a_t, b_t, ws, M=M, N=N, K=K, a_mn=True, b_mn=True, epilogue=A.EPI_F32, splits=splits,
+                      split_stride=M * N, lda=lda, ldb=ldb, ldc=N)
+            self.reduce_splits(ws, splits, M * N, M * N, out, accumulate)
 
     def reduce_splits(self, ws, splits: int, stride: int, n: int, out, accumulate: bool) -> None:
         self._call("rte_reduce_splits", _ptr(ws), splits, stride, n, _ptr(out), int(accumulate), self.stream)
@@ -156,11 +170,14 @@ class CudaOps:
         self._call("rte_rmsnorm_bwd", _ptr(x), _ptr(w), _ptr(film_gamma), _ptr(rstd), _ptr(dy16), _ptr(dy32),
                    _ptr(dres), _ptr(dx_f32), _ptr(dx_bf16), _ptr(partial if dw_out is not None else None),
                    _ptr(partial_g), _ptr(partial_b), rows, d, max_partials, C.byref(n_part), self.stream)
-        if dw_out is not None:
-            self._call("rte_colsum_partials", _ptr(partial), n_part.value, d, _ptr(dw_out), int(accumulate_dw), self.stream)
-        if dgamma_out is not None:
-            self._call("rte_colsum_partials", _ptr(partial_g), n_part.value, d, _ptr(dgamma_out), int(accumulate_film), self.stream)
-            self._call("rte_colsum_partials", _ptr(partial_b), n_part.value, d, _ptr(dbeta_out), int(accumulate_film), self.stream)
+        if dw_out is None and dgamma_out is None:
+            return
+        with self._deferred():
+            if dw_out is not None:
+                self._call("rte_colsum_partials", _ptr(partial), n_part.value, d, _ptr(dw_out), int(accumulate_dw), self.stream)
+            if dgamma_out is not None:
+                self._call("rte_colsum_partials", _ptr(partial_g), n_part.value, d, _ptr(dgamma_out), int(accumulate_film), self.stream)
+                self._call("rte_colsum_partials", _ptr(partial_b), n_part.value, d, _ptr(dbeta_out), int(accumulate_film), self.stream)
 
     def ce_fwd_bwd(self, logits, targets, row_weight, S: int, loss_tok, dlogits) -> None:
         rows, V = logits.shape
