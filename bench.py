@@ -138,6 +138,45 @@ def run_reference(args) -> None:
     print(json.dumps(line))
 
 
+def probe_gemm(iters: int, warmup: int) -> None:
+    """Stand-alone launches of the hot pass's GEMM shapes (one JSON line per shape): the small, fixed case the
+    `ncu --set full` capture of the tcgen05 kernel is taken on.  Operands rotate over sets larger than L2."""
+    import torch
+
+    from speedup_thingy_b200 import _abi as A
+    from speedup_thingy_b200.ops import CudaOps
+
+    ops, dev = CudaOps("cuda:0"), "cuda:0"
+    M, d, F, V = C3_TRAIN["batch_size"] * C3_TRAIN["seq_len"], C3_MODEL["d_model"], C3_MODEL["d_ff"], C3_MODEL["vocab_size"]
+    bf, f32 = torch.bfloat16, torch.float32
+    shapes = [  # name, M, N, K, a_mn, b_mn, epilogue, residual, splits
+        ("qkv", M, 3 * d, d, 0, 0, A.EPI_BF16, False, 1), ("wo+residual", M, d, d, 0, 0, A.EPI_F32, True, 1),
+        ("w_ug", M, 2 * F, d, 0, 0, A.EPI_BF16, False, 1), ("w_d+residual", M, d, F, 0, 0, A.EPI_F32, True, 1),
+        ("logits", M, V, d, 0, 0, A.EPI_BF16, False, 1), ("dz=dy.w_d", M, F, d, 0, 1, A.EPI_BF16, False, 1),
+        ("dn=dug.w_ug", M, d, 2 * F, 0, 1, A.EPI_BF16, False, 1), ("dw_ug", 2 * F, d, M, 1, 1, A.EPI_F32, False, 2),
+        ("dw_qkv", 3 * d, d, M, 1, 1, A.EPI_F32, False, 6)]
+    sets = 4
+    for name, m, n, k, a_mn, b_mn, epi, res, splits in shapes:
+        a = [torch.randn((k, m) if a_mn else (m, k), device=dev).to(bf) for _ in range(sets)]
+        b = [torch.randn((k, n) if b_mn else (n, k), device=dev).to(bf) for _ in range(sets)]
+        out = [torch.empty(splits * m * n, device=dev, dtype=f32 if epi == A.EPI_F32 else bf) for _ in range(sets)]
+        r = [torch.randn(m, n, device=dev) for _ in range(sets)] if res else [None] * sets
+        kw = dict(M=m, N=n, K=k, a_mn=bool(a_mn), b_mn=bool(b_mn), epilogue=epi, ldc=n)
+        if splits > 1:
+            kw.update(splits=splits, split_stride=m * n)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        for i in range(warmup):
+            ops.gemm(a[i % sets], b[i % sets], out[i % sets], residual=r[i % sets], **kw)
+        e0.record()
+        for i in range(iters):
+            ops.gemm(a[i % sets], b[i % sets], out[i % sets], residual=r[i % sets], **kw)
+        e1.record()
+        torch.cuda.synchronize()
+        us = e0.elapsed_time(e1) * 1e3 / iters
+        print(json.dumps({"gemm": name, "M": m, "N": n, "K": k, "splits": splits, "us": us, "tflops": 2.0 * m * n * k / us / 1e6}))
+    ops.check_status()
+
+
 def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -147,7 +186,13 @@ def main() -> None:
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--eager", action="store_true", help="launch kernels one by one instead of replaying the CUDA graph (profiling)")
     ap.add_argument("--no-roofline", action="store_true", help="skip the per-launch GEMM timing pass (profiling)")
+    ap.add_argument("--probe-gemm", action="store_true", help="time the hot pass's GEMM shapes stand-alone and exit (profiling)")
+    ap.add_argument("--probe-iters", type=int, default=20)
+    ap.add_argument("--probe-warmup", type=int, default=3)
     args = ap.parse_args()
+    if args.probe_gemm:
+        probe_gemm(args.probe_iters, args.probe_warmup)
+        return
     if args.impl == "reference":
         run_reference(args)
         return
