@@ -164,7 +164,7 @@ int rte_segment_sum(const float* in, float* out, int32_t n_seg, int32_t seg_len,
  * One decision per sample from pooled = mean_S(h0).  Weights f32 in nn.Linear layout.
  * out_f f32 [B, RTE_ROUTER_F_STRIDE] and out_i int32 [B, RTE_ROUTER_I_STRIDE] are laid out as the
  * offsets below say.  argmax ties go to the LOWEST index.  fixed_recipe / fixed_depth_id < 0 = unset. */
-enum { RTE_ROUTER_MAX_R = 32, RTE_ROUTER_MAX_K = 8, RTE_ROUTER_MAX_T = 32 };
+enum { RTE_ROUTER_MAX_R = 32, RTE_ROUTER_MAX_K = 8, RTE_ROUTER_MAX_T = 32, RTE_ROUTER_DPOOLED_PARTS = 4 };
 typedef struct rte_router_weights {
   const float *r_w0, *r_b0, *r_w2, *r_b2;   /* recipe_mlp */
   const float *d_w0, *d_b0, *d_w2, *d_b2;   /* depth_mlp  */
@@ -189,7 +189,7 @@ int rte_router_fwd(const float* h0, const rte_router_weights* w, const int32_t* 
                    int32_t K, int32_t T, int32_t fixed_recipe, int32_t fixed_depth_id, rte_stream_t stream);
 /* aux[0] = lambda_load * (R * sum_r mean_B(p_r)^2 - 1), aux[1] = lambda_depth * mean_B E[depth]
  * (metrics.py:103-111).  Backward of both through the two MLPs: weight/bias grads (f32, overwritten)
- * and dh0[b,s,:] += dpooled[b,:] / S.  scratch f32 (16-byte aligned) >= RTE_ROUTER_MAX_R + B*(2*hid + R + K + d) + 4.      */
+ * and dh0[b,s,:] += dpooled[b,:] / S.  scratch f32 (16-byte aligned) >= RTE_ROUTER_MAX_R + B*(2*hid + R + K + RTE_ROUTER_DPOOLED_PARTS*d) + 4.      */
 typedef struct rte_router_grads {
   float *r_w0, *r_b0, *r_w2, *r_b2, *d_w0, *d_b0, *d_w2, *d_b2;
 } rte_router_grads;

@@ -14,6 +14,7 @@ c_i32, c_i64, c_f32, c_vp = C.c_int32, C.c_int64, C.c_float, C.c_void_p
 
 EPI_BF16, EPI_F32, EPI_SWIGLU_FWD, EPI_SWIGLU_BWD = 0, 1, 2, 3
 ROUTER_MAX_R, ROUTER_MAX_K, ROUTER_MAX_T = 32, 8, 32
+ROUTER_DPOOLED_PARTS = 4
 ADAMW_CHUNK = 4096
 
 

@@ -124,6 +124,7 @@ class AuditReplay:
         self.g_shared["embed.weight"] = self.g_embed
         big = max(V * d, 2 * f * d, 3 * d * d)
         self.ws = e(big)
+        self.ws_chain = e(16 * Ma * d)          # split-K partials of the chain's own few-row GEMMs
 
     # ------------------------------------------------------------------ host side, once per step
     def choose(self, step_seed: int) -> None:
@@ -167,8 +168,8 @@ class AuditReplay:
             for bk in range(cfg.ffn_banks):
                 o.gemm(self.n2[t], sh["core.mlp.wug"][bk], self.ug[t][bk], M=Ma, N=2 * f, K=d, b_mn=True)
                 o.swiglu_masked_fwd(self.ug[t][bk], rid, self.ffn_tab[bk], S, self.zm[t][bk], Ma, f)
-                o.gemm(self.zm[t][bk], sh["core.mlp.wd"][bk], self.mlp_acc[t], M=Ma, N=d, K=f, b_mn=True,
-                       epilogue=A.EPI_F32, residual=self.mlp_acc[t] if bk > 0 else None)
+                o.gemm_f32_few_rows(self.zm[t][bk], sh["core.mlp.wd"][bk], self.mlp_acc[t], M=Ma, N=d, K=f, b_mn=True,
+                                    ws=self.ws_chain, accumulate=bk > 0)
             o.scaled_residual_fwd(self.u[t], self.mlp_acc[t], p["core.pass_mlp_scale"][t:t + 1], self.active[t], self.h[t],
                                   self.h[t + 1], n, S * d)
         x = self.h[T]
@@ -265,8 +266,8 @@ class AuditReplay:
                 o.gemm(d16m, sh["core.mlp.wd"][bk], self.dz16, M=Ma, N=f, K=d)
                 o.gemm_wgrad(self.zm[t][bk], d16m, g["core.mlp.wd"][bk], M=f, N=d, K=Ma, accumulate=acc, ws=self.ws)
                 o.swiglu_masked_bwd(self.ug[t][bk], self.dz16, rid, self.ffn_tab[bk], S, dug16, Ma, f)
-                o.gemm(dug16, sh["core.mlp.wug"][bk], self.dn_f32, M=Ma, N=d, K=2 * f, epilogue=A.EPI_F32,
-                       residual=self.dn_f32 if bk > 0 else None)
+                o.gemm_f32_few_rows(dug16, sh["core.mlp.wug"][bk], self.dn_f32, M=Ma, N=d, K=2 * f, b_mn=False,
+                                    ws=self.ws_chain, accumulate=bk > 0)
                 o.gemm_wgrad(self.n2[t], dug16, g["core.mlp.wug"][bk], M=d, N=2 * f, K=Ma, accumulate=acc, ws=self.ws)
             o.rmsnorm_bwd(self.u[t], p["core.norm2.weight"], self.rstd2[t], self.dn_f32, du, du, None,
                           g["core.norm2.weight"], pw2, film_gamma=p["core.pass_gamma2"][t],
@@ -281,8 +282,8 @@ class AuditReplay:
                 o.colmask_mul(self.d16b, rid, self.head_tab[bk], S, self.d16b, Ma, d)
                 o.attn_bwd(self.qkv[t][bk], self.y[t][bk], self.d16b, self.lse[t][bk], dqkv16, B=n, S=S,
                            n_heads=cfg.n_heads, head_dim=cfg.head_dim)
-                o.gemm(dqkv16, sh["core.attn.wqkv"][bk], self.dn_f32, M=Ma, N=d, K=3 * d, epilogue=A.EPI_F32,
-                       residual=self.dn_f32 if bk > 0 else None)
+                o.gemm_f32_few_rows(dqkv16, sh["core.attn.wqkv"][bk], self.dn_f32, M=Ma, N=d, K=3 * d, b_mn=False,
+                                    ws=self.ws_chain, accumulate=bk > 0)
                 o.gemm_wgrad(self.n1[t], dqkv16, g["core.attn.wqkv"][bk], M=d, N=3 * d, K=Ma, accumulate=acc, ws=self.ws)
             o.rmsnorm_bwd(self.ht[t], p["core.norm1.weight"], self.rstd1[t], self.dn_f32, dht, dht, None,
                           g["core.norm1.weight"], pw1, film_gamma=p["core.pass_gamma1"][t],

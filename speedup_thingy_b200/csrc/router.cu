@@ -203,22 +203,25 @@ router_bwd_sample_kernel(rte_router_weights w, rte_router_out o, const int32_t* 
   mlp_backward_sample(w.d_w0, w.d_w2, dld, o.d_hidden_pre + (size_t)b * hid, dpre_d + (size_t)b * hid, dhd, d, hid, K);
 }
 
-// dst[r,:] += vec[r / seg,:]
-__global__ void bcast_add_kernel(float* __restrict__ dst, const float* __restrict__ vec, int rows, int seg, int d) {
+// dst[r,:] += sum_p vec[p][r / seg,:]   (nparts partial vectors, part_stride floats apart, added in fixed order)
+__global__ void bcast_add_kernel(float* __restrict__ dst, const float* __restrict__ vec, int rows, int seg, int d, int nparts,
+                                 long long part_stride) {
   const long long total = (long long)rows * (d >> 2);
   const int d4 = d >> 2;
   for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
     const int r = int(i / d4), c = int(i % d4);
     float4 a = reinterpret_cast<float4*>(dst)[i];
-    const float4 v = reinterpret_cast<const float4*>(vec)[(size_t)(r / seg) * d4 + c];
-    a.x += v.x; a.y += v.y; a.z += v.z; a.w += v.w;
+    for (int p = 0; p < nparts; ++p) {
+      const float4 v = reinterpret_cast<const float4*>(vec + p * part_stride)[(size_t)(r / seg) * d4 + c];
+      a.x += v.x; a.y += v.y; a.z += v.z; a.w += v.w;
+    }
     reinterpret_cast<float4*>(dst)[i] = a;
   }
 }
 
-// dpooled[b,:] = (dpre_r[b,:] @ W0r + dpre_d[b,:] @ W0d) / S.  CTA = 4 samples x 128 columns; the two halves of
-// the block split the hidden dimension and are combined through shared memory.  (Broadcast over the sequence
-// into dh0 is a separate fully parallel kernel.)
+// dpooled[part][b,:] = (dpre_r[b, J] @ W0r[J,:] + dpre_d[b, J] @ W0d[J,:]) / S over the part's slice J of the hidden
+// dimension (blockIdx.y = part).  CTA = 4 samples x 128 columns; the two halves of the block split J again and are
+// combined through shared memory.  The broadcast kernel adds the parts in fixed order.
 __global__ void __launch_bounds__(NTHR)
 router_dpooled_kernel(const float* __restrict__ w0r, const float* __restrict__ w0d, const float* __restrict__ dpre_r,
                       const float* __restrict__ dpre_d, float* __restrict__ dpooled, int B, int S, int d, int hid) {
@@ -229,6 +232,9 @@ router_dpooled_kernel(const float* __restrict__ w0r, const float* __restrict__ w
   const int cblocks = rte::ceil_div(d, 128);
   const int b0 = (blockIdx.x / cblocks) * 4, c = (blockIdx.x % cblocks) * 128 + (threadIdx.x & 127);
   const int half = threadIdx.x >> 7;
+  const int part_len = (hid + (int)gridDim.y - 1) / (int)gridDim.y;
+  const int p_lo = blockIdx.y * part_len, p_hi = min(hid, p_lo + part_len);
+  dpooled += (size_t)blockIdx.y * B * d;
   for (int i = threadIdx.x; i < 4 * hid; i += NTHR) {
     const int bb = b0 + i / hid;
     sr[i] = bb < B ? dpre_r[(size_t)bb * hid + i % hid] : 0.f;
@@ -237,7 +243,7 @@ router_dpooled_kernel(const float* __restrict__ w0r, const float* __restrict__ w
   __syncthreads();
   float acc[4] = {0.f, 0.f, 0.f, 0.f};
   if (c < d) {
-    const int jh = (hid + 1) / 2, j_lo = half * jh, j_hi = min(hid, j_lo + jh);
+    const int jh = (p_hi - p_lo + 1) / 2, j_lo = p_lo + half * jh, j_hi = min(p_hi, j_lo + jh);
 #pragma unroll 8
     for (int j = j_lo; j < j_hi; ++j) {
       const float wr = w0r[(size_t)j * d + c], wd = w0d[(size_t)j * d + c];
@@ -362,7 +368,7 @@ extern "C" int rte_router_aux_bwd(const rte_router_weights* w, const rte_router_
   RTE_LAUNCH_CHECK();
   const size_t smem_dp = (size_t)(8 * hid + 4 * 128) * sizeof(float);
   if (smem_dp > 48 * 1024) return RTE_ERR_UNSUPPORTED;
-  router_dpooled_kernel<<<rte::ceil_div(B, 4) * rte::ceil_div(d, 128), NTHR, smem_dp, ST(stream)>>>(
+  router_dpooled_kernel<<<dim3(rte::ceil_div(B, 4) * rte::ceil_div(d, 128), RTE_ROUTER_DPOOLED_PARTS), NTHR, smem_dp, ST(stream)>>>(
       w->r_w0, w->d_w0, dpre_r, dpre_d, dpooled, B, S, d, hid);
   RTE_LAUNCH_CHECK();
   if (d % 4 != 0) return RTE_ERR_UNSUPPORTED;
@@ -370,7 +376,7 @@ extern "C" int rte_router_aux_bwd(const rte_router_weights* w, const rte_router_
     long long n4 = (long long)B * S * (d / 4);
     int grid = (int)((n4 + NTHR - 1) / NTHR);
     if (grid > 148 * 8) grid = 148 * 8;
-    bcast_add_kernel<<<grid, NTHR, 0, ST(stream)>>>(dh0, dpooled, B * S, S, d);
+    bcast_add_kernel<<<grid, NTHR, 0, ST(stream)>>>(dh0, dpooled, B * S, S, d, RTE_ROUTER_DPOOLED_PARTS, (long long)B * d);
     RTE_LAUNCH_CHECK();
   }
   const int g0 = (int)rte::ceil_div64((long long)hid * d, NTHR);

@@ -292,7 +292,7 @@ class TrainEngine:
                               recipe_probs=e(B, r), depth_probs=e(B, k), expected_depth=e(B), router_entropy=e(B),
                               recipe_id=e(B, dtype=i32), recipe_id_by_pass=e(B, cfg.t_max, dtype=i32),
                               depth_id=e(B, dtype=i32), depth=e(B, dtype=i32))
-            self.router_scratch = e(A.ROUTER_MAX_R + B * (2 * hid + r + k + d) + 4)
+            self.router_scratch = e(A.ROUTER_MAX_R + B * (2 * hid + r + k + A.ROUTER_DPOOLED_PARTS * d) + 4)
         if self.shortlist:
             oc, i32 = self.oc, torch.int32
             if "shortlist_head.cluster_router.weight" not in self.params:

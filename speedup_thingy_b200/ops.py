@@ -136,6 +136,20 @@ class CudaOps:
                       split_stride=M * N, lda=lda, ldb=ldb, ldc=N)
             self.reduce_splits(ws, splits, M * N, M * N, out, accumulate)
 
+    def gemm_f32_few_rows(self, a, b, out, *, M: int, N: int, K: int, b_mn: bool, ws, accumulate: bool = False) -> None:
+        """out f32 [M,N] (+)= a @ b^T for a GEMM with few rows and a long reduction (the audit replay's chain): one or
+        two output tiles would run their k-blocks one after another on one or two SMs, so the reduction is split
+        across up to 16 CTAs per tile and summed in fixed order."""
+        kb = -(-K // 64)
+        splits = 1
+        if M <= 256 and kb >= 16 and K % 64 == 0:
+            splits = max(s for s in range(1, 17) if kb % s == 0 and kb // s >= 2)
+        if splits == 1 or ws is None or ws.numel() < splits * M * N:
+            self.gemm(a, b, out, M=M, N=N, K=K, b_mn=b_mn, epilogue=A.EPI_F32, residual=out if accumulate else None)
+            return
+        self.gemm(a, b, ws, M=M, N=N, K=K, b_mn=b_mn, epilogue=A.EPI_F32, splits=splits, split_stride=M * N, ldc=N)
+        self.reduce_splits(ws, splits, M * N, M * N, out, accumulate)
+
     def reduce_splits(self, ws, splits: int, stride: int, n: int, out, accumulate: bool) -> None:
         self._call("rte_reduce_splits", _ptr(ws), splits, stride, n, _ptr(out), int(accumulate), self.stream)
 

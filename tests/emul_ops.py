@@ -100,6 +100,9 @@ class EmulOps:
         else:
             out.view(M, N).copy_(res)
 
+    def gemm_f32_few_rows(self, a, b, out, *, M, N, K, b_mn, ws, accumulate=False):
+        self.gemm(a, b, out, M=M, N=N, K=K, b_mn=b_mn, epilogue=EPI_F32, residual=out if accumulate else None)
+
     def reduce_splits(self, ws, splits, stride, n, out, accumulate):
         res = ws[: splits * stride].view(splits, stride)[:, :n].sum(0)
         out.view(-1)[:n] = res + (out.view(-1)[:n] if accumulate else 0)

@@ -242,7 +242,7 @@ def test_router_fwd_indices_and_aux_bwd(ops):
     grads = {k: e(*w[k].shape) for k in ("r_w0", "r_b0", "r_w2", "r_b2", "d_w0", "d_b0", "d_w2", "d_b2")}
     dh0 = e(B * S, d)
     auxd = e(2)
-    scratch = e(32 + B * (2 * hid + R + K + d) + 4)
+    scratch = e(32 + B * (2 * hid + R + K + 4 * d) + 4)
     ops.router_aux_bwd(w, out, dv, tr.lambda_load, tr.lambda_depth, auxd, grads, dh0, scratch, B=B, S=S, d=d, hid=hid, R=R, K=K)
     torch.cuda.synchronize()
     assert abs(float(auxd[0]) - float(aux["load"])) < 1e-6 and abs(float(auxd[1]) - float(aux["depth"])) < 1e-7
