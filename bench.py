@@ -202,6 +202,13 @@ def main() -> None:
     from speedup_thingy_b200.config import ExperimentConfig, ModelConfig, TrainingConfig
     from speedup_thingy_b200.engine import TrainEngine, init_parameters
 
+    # stdout carries exactly one JSON line: everything libraries print there (NCCL's version banner) goes to stderr
+    real_stdout = os.dup(1)
+    os.dup2(2, 1)
+
+    def _emit(text: str) -> None:
+        os.write(real_stdout, (text + "\n").encode())
+
     rank, world = int(os.environ.get("RANK", "0")), int(os.environ.get("WORLD_SIZE", "1"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
     if world != args.gpus:
@@ -235,6 +242,10 @@ def main() -> None:
     W, K = max(args.warmup, 3), args.steps
     for i in range(W):
         eng.train_step(host_batches[i % n_batches])
+    for i in range(8):          # data parallel: the first steps run eagerly (NCCL set-up); capture before timing
+        if not eng.use_cuda_graph or eng._graph is not None:
+            break
+        eng.train_step(host_batches[i % n_batches])
     torch.cuda.synchronize()
 
     def barrier():
@@ -247,12 +258,15 @@ def main() -> None:
     barrier()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     with ClockSampler(local) as clocks:
+        l0 = eng.ops.launches
         e0.record()
         for _ in range(K):
             eng._run_step_kernels(optimizer=True)
         e1.record()
         barrier()
         ms_dev = e0.elapsed_time(e1)
+        # C-ABI launches inside the timed region: counted directly when eager, per captured step when replayed
+        launches_timed = (eng.ops.launches - l0) or (eng.kernel_launches_per_step or 0) * K
         # ---- end to end through the public API with pinned host batches
         barrier()
         t0 = time.perf_counter()
@@ -285,7 +299,7 @@ def main() -> None:
                        "timing": "CUDA events around K graph replays, max over ranks"},
             "e2e": {"value": tokens * K / (ms_e2e / 1e3), "unit": "tokens/s", "h2d_bytes_per_step": 2 * B * S * 8,
                     "d2h_bytes_per_step": 8 * 4 + B * 4},
-            "gpu_launches": (eng.kernel_launches_per_step or 0) * K,
+            "gpu_launches": launches_timed,
             "clocks": clocks.summary(),
             "step_roofline": {"flops_per_token": step_flops_per_token(C3_MODEL),
                               "achieved_tflops": step_flops_per_token(C3_MODEL) * value / world / 1e12,
@@ -305,10 +319,15 @@ def main() -> None:
             threads = os.cpu_count() or 1
             v, sample = cpu_port_tokens_per_sec(sample_batch=8, steps=3, threads=threads)
             line["cpu_baseline"] = {"value": v, "unit": "tokens/s", "cores": threads, "kind": "port", "sample": sample}
-        print(json.dumps(line))
+        _emit(json.dumps(line))
+    eng.close()
     if dist is not None:
         dist.barrier()
-        dist.destroy_process_group()
+        torch.cuda.synchronize()
+        # NCCL's teardown after graph-captured collectives has hung on this pool: the result is out, leave at once
+        sys.stdout.flush()
+        sys.stderr.flush()
+        os._exit(0)
 
 
 if __name__ == "__main__":

@@ -65,6 +65,7 @@ class AuditReplay:
         from .engine import _Block, _Temps
 
         self.eng, self.k = eng, k
+        self._stage = None
         cfg, dev = eng.cfg, eng.device
         self.n, self.S, self.T = k, eng.S, cfg.t_max
         self.Ma = k * eng.S
@@ -133,11 +134,17 @@ class AuditReplay:
         eng = self.eng
         gen = torch.Generator().manual_seed(step_seed)
         chosen = torch.sort(torch.randperm(eng.B, generator=gen)[: self.k]).values
-        self.idx.copy_(chosen.to(torch.int32))
+        if self._stage is None:
+            pin = eng.device.type == "cuda"
+            self._stage = (torch.empty(self.k, dtype=torch.int32, pin_memory=pin),
+                           torch.empty(eng.B, dtype=torch.float32, pin_memory=pin))
+        h_idx, h_rw = self._stage
         w0 = 1.0 / (eng.B * eng.S * eng.world)
-        rw = torch.full((eng.B,), w0, dtype=torch.float32)
-        rw[chosen] = w0 * (1.0 - 1.0 / self.p_inc)                       # d corrected / d hot on audited samples
-        eng.row_weight.copy_(rw)
+        h_idx.copy_(chosen)
+        h_rw.fill_(w0)
+        h_rw[chosen] = w0 * (1.0 - 1.0 / self.p_inc)                     # d corrected / d hot on audited samples
+        self.idx.copy_(h_idx, non_blocking=True)
+        eng.row_weight.copy_(h_rw, non_blocking=True)
         self.last_chosen = chosen
 
     # ------------------------------------------------------------------ forward
@@ -316,16 +323,17 @@ class AuditReplay:
         o.scatter_add_rows(dh0_hot, self.idx, self.dh_first, n, S * d)
 
     # ------------------------------------------------------------------ reporting
-    def loss_terms(self, hot_per_sample: torch.Tensor) -> dict[str, float]:
-        """Host-side assembly of the audited quantities for the reported loss (training.py:1381-1385)."""
+    def loss_terms(self, hot_per_sample: torch.Tensor, host: dict) -> dict[str, float]:
+        """Host-side assembly of the audited quantities for the reported loss (training.py:1381-1385) from the
+        step's fetched results (`terms`, `exact_loss`, `kl_sum` already on the host)."""
         tr, n, Ma, d = self.eng.tr, self.n, self.Ma, self.eng.cfg.d_model
-        terms = self.terms.to("cpu")
-        exact = self.exact_loss.to("cpu")
+        terms = host["terms"]
+        exact = host["exact_loss"].clone()
         hot = hot_per_sample[self.last_chosen]
         temp = max(float(tr.distill_temperature), 1e-6)
         aux = dict(delta_dir=tr.lambda_delta_dir * float(terms[:, 0].mean()),
                    delta_rms=tr.lambda_delta_rms * float(terms[:, 1].mean()),
                    endpoint_normed=tr.lambda_endpoint_normed * float(terms[:, 2].sum()) / (Ma * d),
                    endpoint_raw=tr.lambda_endpoint_raw * float(terms[:, 3].sum()) / (Ma * d),
-                   kl=tr.lambda_kl * float(self.kl_sum.to("cpu")) / n * temp * temp)
+                   kl=tr.lambda_kl * float(host["kl_sum"]) / n * temp * temp)
         return dict(correction=float(((exact - hot) / self.p_inc).sum()), exact=exact, aux=aux)

@@ -160,10 +160,11 @@ class TrainEngine:
         if self.world > 1:
             # NCCL sets up its channels lazily on the first collectives (allocations, host synchronisation),
             # which must not happen inside stream capture: run the first steps launch by launch, and capture
-            # the collective-bearing graph only when RTE_DP_GRAPH=1 asks for it.
+            # the collective-bearing graph afterwards (RTE_DP_GRAPH=0 keeps every step eager).  A process that holds
+            # such a graph should call close() before it destroys the process group.
             import os
             self._eager_steps_left = 3
-            if os.environ.get("RTE_DP_GRAPH", "0") != "1":
+            if os.environ.get("RTE_DP_GRAPH", "1") == "0":
                 self.use_cuda_graph = False
         cfg, tr = self.cfg, self.tr
         self.B, self.S = tr.batch_size, tr.seq_len
@@ -316,6 +317,7 @@ class TrainEngine:
         if hasattr(ops, "rope_table"):
             ops.rope_table(S, cfg.head_dim)          # built once, before any stream capture
         self._graph = None
+        self._host: dict[str, torch.Tensor] | None = None
         self._launches_per_step: int | None = None
 
     # ------------------------------------------------------------------ data-parallel gradient exchange
@@ -368,7 +370,7 @@ class TrainEngine:
                         dist.all_reduce(view, op=dist.ReduceOp.SUM, group=self.pg)
 
     def _finish_backward(self) -> None:
-        if self._comm_stream is not None:
+        if self._comm_stream is not None and not self._dp_paused:
             torch.cuda.current_stream(self.device).wait_stream(self._comm_stream)
 
     # ------------------------------------------------------------------ side stream of the audit replay
@@ -624,19 +626,50 @@ class TrainEngine:
             self._launches_per_step = self.ops.launches - before
         self._graph.replay()
 
+    def close(self) -> None:
+        """Drops the captured step graph (which, under data parallelism, holds NCCL kernels) after the device has
+        drained, so that the process group can be torn down afterwards."""
+        if self.device.type == "cuda":
+            torch.cuda.synchronize(self.device)
+        self._graph = None
+        if self.device.type == "cuda":
+            torch.cuda.synchronize(self.device)
+
     def loss_and_grads(self, batch) -> tuple[float, dict[str, torch.Tensor]]:
         """Forward + backward without the optimiser (what the parity tests compare with the oracle)."""
         self._load_batch(batch)
         self._run_step_kernels(optimizer=False)
         return self._assemble_loss(), self.grads
 
+    def _fetch_results(self) -> dict[str, torch.Tensor]:
+        """One device-to-host round trip for everything the host reads after a step: the copies are queued into
+        pinned buffers behind the step's kernels and a single stream synchronisation waits for all of them."""
+        if self._host is None:
+            pin = self.device.type == "cuda"
+            mk = lambda t: torch.empty(t.shape, dtype=t.dtype, pin_memory=pin)  # noqa: E731
+            src = {"scalars": self.scalars, "loss_per_sample": self.loss_per_sample}
+            if hasattr(self.ops, "status"):
+                src["status"] = self.ops.status
+            if not self.dense:
+                src["recipe_id"] = self.route["recipe_id"]
+            if self.audit is not None:
+                src.update(terms=self.audit.terms, exact_loss=self.audit.exact_loss, kl_sum=self.audit.kl_sum)
+            self._host_src = src
+            self._host = {k: mk(v) for k, v in src.items()}
+        for k, v in self._host_src.items():
+            self._host[k].copy_(v, non_blocking=True)
+        if self.device.type == "cuda":
+            torch.cuda.current_stream(self.device).synchronize()
+        if "status" in self._host and int(self._host["status"][0]) != 0:
+            self.ops.check_status()                          # raises with the decoded device status
+        return self._host
+
     def _assemble_loss(self) -> float:
-        vals = self.scalars.detach().to("cpu")
-        if hasattr(self.ops, "check_status"):
-            self.ops.check_status()
+        host = self._fetch_results()
+        vals = host["scalars"]
         loss = float(vals[0]) / (self.B * self.S)          # this rank's shard
         if self.audit is not None:
-            terms = self.audit.loss_terms(self.loss_per_sample.detach().to("cpu"))
+            terms = self.audit.loss_terms(host["loss_per_sample"], host)
             loss += terms["correction"] / (self.B * self.S) + sum(terms["aux"].values())
             self.last_audit = terms
         if not self.dense and not self.tr.disable_router_aux:
@@ -651,7 +684,7 @@ class TrainEngine:
         loss = self._assemble_loss()
         metrics: dict[str, Any] = {"mode": self.tr.mode, "loss": loss}
         if not self.dense:
-            ids = self.route["recipe_id"].to("cpu").long()
+            ids = self._host["recipe_id"].long()
             counts = torch.bincount(ids, minlength=self.cfg.recipe_count).float()
             self.usage_ema.mul_(self.tr.coverage_beta).add_(counts / counts.sum().clamp_min(1.0), alpha=1.0 - self.tr.coverage_beta)
             metrics["unique_recipes_per_batch"] = int(ids.unique().numel())
