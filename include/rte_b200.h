@@ -96,6 +96,11 @@ typedef struct rte_gemm_args {
 } rte_gemm_args;
 
 int rte_gemm_bf16(const rte_gemm_args* args, rte_stream_t stream);
+/* The same product for FEW ROWS (the audited samples' replay, models.py:605-679: M = one or two samples): one
+ * 128-thread CTA per 64x64 output tile, cp.async + mma.sync, no tensor maps or TMEM set-up, so a dependent chain of
+ * such launches is not dominated by set-up time.  Subset of rte_gemm_args: A K-major, B either major, RTE_EPI_BF16
+ * or RTE_EPI_F32 (+R), equal split-K (fp32, no R), no grouping; K % 8 == 0 (and N % 8 == 0 when B is MN-major).   */
+int rte_gemm_bf16_small(const rte_gemm_args* args, rte_stream_t stream);
 
 /* out[i] = (accumulate ? out[i] : 0) + sum_s ws[s*split_stride + i], i < n (deterministic order). */
 int rte_reduce_splits(const float* ws, int32_t splits, int64_t split_stride, int64_t n, float* out,
@@ -119,6 +124,17 @@ int rte_rmsnorm_fwd(const float* x, const float* w, const float* film_gamma, con
  * dx written as f32 (dx_f32) and/or bf16 (dx_bf16).  dw_partial f32 [grid_rows, d] receives
  * per-CTA partial sums of dy * xhat (and dfilm_* likewise) -- reduce with rte_colsum_partials.
  * Returns the number of partial rows written through *n_partials (host value).          */
+/* Residual update(s) of the banked recurrent core fused in front of the norm (layers.py:831-870: "h + alpha*h0",
+ * "h + s*branch", frozen samples passed through), one launch instead of two or three:
+ *   x1 = (active == NULL || active[row / S]) ? base + *scale * branch : passthrough      -> x1_out (optional)
+ *   x  = add2 ? x1 + *scale2 * add2 : x1                                                  -> x_out
+ *   y  = rmsnorm(x) * w [* (1 + film_gamma) + film_beta]                                  -> y_bf16, rstd
+ * scale / scale2 are device scalars; active is per sample (S rows each).                                        */
+int rte_residual_rmsnorm_fwd(const float* base, const float* branch, const float* scale, const int32_t* active,
+                             const float* passthrough, int32_t S, const float* add2, const float* scale2,
+                             float* x1_out, float* x_out, const float* w, const float* film_gamma,
+                             const float* film_beta, void* y_bf16, float* rstd, int32_t rows, int32_t d, float eps,
+                             rte_stream_t stream);
 int rte_rmsnorm_bwd(const float* x, const float* w, const float* film_gamma, const float* rstd,
                     const void* dy_bf16, const float* dy_f32, const float* dres,
                     float* dx_f32, void* dx_bf16, float* dw_partial, float* dgamma_partial,

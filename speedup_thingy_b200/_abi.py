@@ -74,6 +74,7 @@ PROTOTYPES = {
     "rte_status_string": (C.c_char_p, [C.c_int]),
     "rte_device_sm_count": (C.c_int, []),
     "rte_gemm_bf16": (C.c_int, [P(GemmArgs), c_vp]),
+    "rte_gemm_bf16_small": (C.c_int, [P(GemmArgs), c_vp]),
     "rte_reduce_splits": (C.c_int, [c_vp, c_i32, c_i64, c_i64, c_vp, c_i32, c_vp]),
     "rte_embed_fwd": (C.c_int, [c_vp, c_vp, c_vp, c_i32, c_i32, c_i32, c_vp, c_vp]),
     "rte_embed_bwd": (C.c_int, [c_vp, c_vp, c_vp, c_i32, c_i32, c_i32, c_vp, c_vp]),
@@ -102,6 +103,8 @@ PROTOTYPES = {
     "rte_svd_ffn_select": (C.c_int, [c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, c_i32, c_i32, c_i32, c_i32, c_i32, c_i32, c_vp]),
     "rte_svd_ffn_swiglu_bwd": (C.c_int, [c_vp, c_vp, c_vp, c_vp, c_i64, c_i32, c_vp]),
     "rte_row_norm_f32": (C.c_int, [c_vp, c_vp, c_i32, c_i32, c_vp]),
+    "rte_residual_rmsnorm_fwd": (C.c_int, [c_vp, c_vp, c_vp, c_vp, c_vp, c_i32, c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, c_vp,
+                                           c_vp, c_i32, c_i32, C.c_float, c_vp]),
     "rte_swiglu_fwd": (C.c_int, [c_vp, c_vp, c_i64, c_i32, c_vp]),
     "rte_swiglu_bwd": (C.c_int, [c_vp, c_vp, c_vp, c_i64, c_i32, c_vp]),
     "rte_cast_f32_bf16": (C.c_int, [c_vp, c_vp, c_i64, c_vp]),

@@ -158,27 +158,36 @@ class AuditReplay:
         o.gather_rows(eng.targets, self.idx, self.targets_a, n, S * 8)
         o.audit_route(eng.route["recipe_id_by_pass"], eng.route["depth"], self.idx, self.rid, self.active, n, T)
         alpha = p["core.alpha_inj"].view(1)
+        # The residual updates ride in front of the norms (one launch each instead of two or three):
+        #   ht = h + alpha*h0 -> norm1;   u = ht + s_attn*attn -> norm2;
+        #   h' = active ? u + s_mlp*mlp : h, then ht' = h' + alpha*h0 -> next pass's norm1
+        film1 = lambda t: dict(film_gamma=p["core.pass_gamma1"][t], film_beta=p["core.pass_beta1"][t])  # noqa: E731
+        o.residual_rmsnorm_fwd(self.h[0], self.h0a, alpha, self.ht[0], p["core.norm1.weight"], self.n1[0], self.rstd1[0],
+                               S=S, **film1(0))
         for t in range(T):
             rid = self.rid[t]
-            o.scaled_residual_fwd(self.h[t], self.h0a, alpha, None, None, self.ht[t], n, S * d)
-            o.rmsnorm_fwd(self.ht[t], p["core.norm1.weight"], self.n1[t], self.rstd1[t],
-                          film_gamma=p["core.pass_gamma1"][t], film_beta=p["core.pass_beta1"][t])
             for bk in range(cfg.attn_banks):
                 o.gemm(self.n1[t], sh["core.attn.wqkv"][bk], self.qkv[t][bk], M=Ma, N=3 * d, K=d, b_mn=True)
                 o.attn_fwd(self.qkv[t][bk], self.y[t][bk], self.lse[t][bk], B=n, S=S, n_heads=cfg.n_heads, head_dim=cfg.head_dim)
                 o.colmask_mul(self.y[t][bk], rid, self.head_tab[bk], S, self.ym[t][bk], Ma, d)
                 o.gemm(self.ym[t][bk], sh["core.attn.wo"][bk], self.attn_acc[t], M=Ma, N=d, K=d, b_mn=True,
                        epilogue=A.EPI_F32, residual=self.attn_acc[t] if bk > 0 else None)
-            o.scaled_residual_fwd(self.ht[t], self.attn_acc[t], p["core.pass_attn_scale"][t:t + 1], None, None, self.u[t], n, S * d)
-            o.rmsnorm_fwd(self.u[t], p["core.norm2.weight"], self.n2[t], self.rstd2[t],
-                          film_gamma=p["core.pass_gamma2"][t], film_beta=p["core.pass_beta2"][t])
+            o.residual_rmsnorm_fwd(self.ht[t], self.attn_acc[t], p["core.pass_attn_scale"][t:t + 1], self.u[t],
+                                   p["core.norm2.weight"], self.n2[t], self.rstd2[t], S=S,
+                                   film_gamma=p["core.pass_gamma2"][t], film_beta=p["core.pass_beta2"][t])
             for bk in range(cfg.ffn_banks):
                 o.gemm(self.n2[t], sh["core.mlp.wug"][bk], self.ug[t][bk], M=Ma, N=2 * f, K=d, b_mn=True)
                 o.swiglu_masked_fwd(self.ug[t][bk], rid, self.ffn_tab[bk], S, self.zm[t][bk], Ma, f)
                 o.gemm_f32_few_rows(self.zm[t][bk], sh["core.mlp.wd"][bk], self.mlp_acc[t], M=Ma, N=d, K=f, b_mn=True,
                                     ws=self.ws_chain, accumulate=bk > 0)
-            o.scaled_residual_fwd(self.u[t], self.mlp_acc[t], p["core.pass_mlp_scale"][t:t + 1], self.active[t], self.h[t],
-                                  self.h[t + 1], n, S * d)
+            if t + 1 < T:
+                o.residual_rmsnorm_fwd(self.u[t], self.mlp_acc[t], p["core.pass_mlp_scale"][t:t + 1], self.ht[t + 1],
+                                       p["core.norm1.weight"], self.n1[t + 1], self.rstd1[t + 1], S=S,
+                                       active=self.active[t], passthrough=self.h[t], add2=self.h0a, scale2=alpha,
+                                       x1_out=self.h[t + 1], **film1(t + 1))
+            else:
+                o.scaled_residual_fwd(self.u[t], self.mlp_acc[t], p["core.pass_mlp_scale"][t:t + 1], self.active[t],
+                                      self.h[t], self.h[t + 1], n, S * d)
         x = self.h[T]
         for blk in self.coda:
             x = eng._block_fwd(blk, x)

@@ -92,6 +92,71 @@ rmsnorm_fwd_kernel(const float* __restrict__ x, const float* __restrict__ w, con
   }
 }
 
+// Residual update(s) fused in front of the norm (one warp per row):
+//   x1 = (active == NULL || active[row / S]) ? base + *scale * branch : passthrough      -> x1_out (optional)
+//   x  = add2 ? x1 + *scale2 * add2 : x1                                                  -> x_out
+//   y  = rmsnorm(x) * w [* (1 + fg) + fb]
+template <int NV>
+__global__ void __launch_bounds__(256)
+residual_rmsnorm_fwd_kernel(const float* __restrict__ base, const float* __restrict__ branch, const float* __restrict__ scale,
+                            const int32_t* __restrict__ active, const float* __restrict__ passthrough, int S,
+                            const float* __restrict__ add2, const float* __restrict__ scale2, float* __restrict__ x1_out,
+                            float* __restrict__ x_out, const float* __restrict__ w, const float* __restrict__ fg,
+                            const float* __restrict__ fb, __nv_bfloat16* __restrict__ y16, float* __restrict__ rstd, int rows, int d,
+                            float eps) {
+  const int lane = threadIdx.x & 31;
+  const int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (row >= rows) return;
+  const int d4 = d >> 2;
+  const size_t off = (size_t)row * d;
+  const bool on = active == nullptr || active[row / S] != 0;
+  const float s1 = *scale, s2 = add2 ? *scale2 : 0.f;
+  float4 v[NV];
+  float ss = 0.f;
+#pragma unroll
+  for (int i = 0; i < NV; ++i) {
+    const int c = lane + 32 * i;
+    if (c < d4) {
+      float4 x;
+      if (on) {
+        const float4 a = reinterpret_cast<const float4*>(base + off)[c], b = reinterpret_cast<const float4*>(branch + off)[c];
+        x = make_float4(a.x + s1 * b.x, a.y + s1 * b.y, a.z + s1 * b.z, a.w + s1 * b.w);
+      } else {
+        x = reinterpret_cast<const float4*>(passthrough + off)[c];
+      }
+      if (x1_out) reinterpret_cast<float4*>(x1_out + off)[c] = x;
+      if (add2) {
+        const float4 e = reinterpret_cast<const float4*>(add2 + off)[c];
+        x.x += s2 * e.x; x.y += s2 * e.y; x.z += s2 * e.z; x.w += s2 * e.w;
+      }
+      reinterpret_cast<float4*>(x_out + off)[c] = x;
+      v[i] = x;
+      ss += x.x * x.x + x.y * x.y + x.z * x.z + x.w * x.w;
+    }
+  }
+  ss = warp_sum(ss);
+  const float r = rsqrtf(ss / (float)d + eps);
+  if (lane == 0 && rstd) rstd[row] = r;
+#pragma unroll
+  for (int i = 0; i < NV; ++i) {
+    const int c = lane + 32 * i;
+    if (c < d4) {
+      float4 o = make_float4(v[i].x * r, v[i].y * r, v[i].z * r, v[i].w * r);
+      if (w) {
+        const float4 ww = reinterpret_cast<const float4*>(w)[c];
+        o.x *= ww.x; o.y *= ww.y; o.z *= ww.z; o.w *= ww.w;
+      }
+      if (fg) {
+        const float4 g = reinterpret_cast<const float4*>(fg)[c], b = reinterpret_cast<const float4*>(fb)[c];
+        o.x = o.x * (1.f + g.x) + b.x; o.y = o.y * (1.f + g.y) + b.y;
+        o.z = o.z * (1.f + g.z) + b.z; o.w = o.w * (1.f + g.w) + b.w;
+      }
+      uint2 pk = make_uint2(rte::pack_bf16x2(o.x, o.y), rte::pack_bf16x2(o.z, o.w));
+      reinterpret_cast<uint2*>(y16 + off)[c] = pk;
+    }
+  }
+}
+
 // Backward.  y = xhat * w * (1 + fg) + fb with xhat = x * rstd.
 //   g  = dy * (1 + fg) * w          (gradient wrt xhat)
 //   dx = rstd * (g - xhat * mean(g * xhat)) + dres
@@ -558,6 +623,28 @@ extern "C" int rte_rmsnorm_fwd(const float* x, const float* w, const float* film
   else if (d <= 1024) RTE_RN_FWD(8);
   else RTE_RN_FWD(16);
 #undef RTE_RN_FWD
+  RTE_LAUNCH_CHECK();
+  return RTE_OK;
+}
+
+extern "C" int rte_residual_rmsnorm_fwd(const float* base, const float* branch, const float* scale, const int32_t* active,
+                                        const float* passthrough, int32_t S, const float* add2, const float* scale2,
+                                        float* x1_out, float* x_out, const float* w, const float* film_gamma,
+                                        const float* film_beta, void* y_bf16, float* rstd, int32_t rows, int32_t d, float eps,
+                                        rte_stream_t stream) {
+  RTE_CHECK_ARG(base && branch && scale && x_out && y_bf16 && rows > 0 && d > 0 && d % 4 == 0 && S > 0);
+  RTE_CHECK_ARG((active == nullptr || passthrough != nullptr) && (add2 == nullptr || scale2 != nullptr));
+  RTE_CHECK_ARG((film_gamma == nullptr) == (film_beta == nullptr));
+  if (d > 128 * RN_MAX_V4) return RTE_ERR_UNSUPPORTED;
+#define RTE_RRN_FWD(NV)                                                                                              \
+  residual_rmsnorm_fwd_kernel<NV><<<rte::ceil_div(rows, 8), 256, 0, ST(stream)>>>(base, branch, scale, active, passthrough, \
+      S, add2, scale2, x1_out, x_out, w, film_gamma, film_beta, reinterpret_cast<__nv_bfloat16*>(y_bf16), rstd, rows, d, eps)
+  if (d <= 128) RTE_RRN_FWD(1);
+  else if (d <= 256) RTE_RRN_FWD(2);
+  else if (d <= 512) RTE_RRN_FWD(4);
+  else if (d <= 1024) RTE_RRN_FWD(8);
+  else RTE_RRN_FWD(16);
+#undef RTE_RRN_FWD
   RTE_LAUNCH_CHECK();
   return RTE_OK;
 }

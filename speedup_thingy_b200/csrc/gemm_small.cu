@@ -1,0 +1,183 @@
+// Few-row GEMM for the audit replay's launch chain: C[M,N] = A[M,K] * B^T with M of the order of one sample
+// (64..256 rows).  The persistent tcgen05 kernel spends most of such a launch on set-up (barriers, TMEM
+// allocation, tensor maps, TMA round trips) and covers N with a handful of CTAs; here every 64x64 output tile
+// is its own 128-thread CTA that streams its operands with cp.async (an 8-deep ring of k-tiles) and issues
+// mma.sync.m16n8k16, so a [64 x 1536 x 512] product is 24 CTAs of ~2 us instead of 6 CTAs of ~10 us.
+// bf16 in, fp32 accumulate; B either K-major ([N,K], nn.Linear layout) or MN-major ([K,N], the banked layout);
+// outputs bf16 or fp32 (+ fp32 residual), optional split along K into partial results (fp32, reduced by
+// rte_reduce_splits in fixed order).
+
+#include "rte_common.cuh"
+
+namespace {
+
+constexpr int BM = 64, BN = 64, BK = 64, LDS = BK + 8, THR = 128;
+constexpr int NST = 8;                                     // k-tiles in flight: the launch is latency-bound, not bandwidth-bound
+constexpr int SMEM_BYTES = NST * (BM + BN) * LDS * 2;
+
+__device__ __forceinline__ void cp_async16(void* smem, const void* gmem, bool valid) {
+  const uint32_t dst = static_cast<uint32_t>(__cvta_generic_to_shared(smem));
+  const int bytes = valid ? 16 : 0;                       // 0: the 16 bytes are zero-filled
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(gmem), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
+__device__ __forceinline__ void mma16816(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ void ldsm_x2_trans(uint32_t& b0, uint32_t& b1, const __nv_bfloat16* row_ptr) {
+  const uint32_t addr = static_cast<uint32_t>(__cvta_generic_to_shared(row_ptr));
+  asm volatile("ldmatrix.sync.aligned.m8n8.x2.trans.shared.b16 {%0,%1}, [%2];" : "=r"(b0), "=r"(b1) : "r"(addr));
+}
+__device__ __forceinline__ uint32_t ld32(const __nv_bfloat16* p) { return *reinterpret_cast<const uint32_t*>(p); }
+
+struct SmallParams {
+  const __nv_bfloat16* A; int lda;
+  const __nv_bfloat16* B; int ldb;
+  void* C; int ldc;
+  const float* R; int ldr;
+  int M, N, K;
+  int k_per_split; long long split_stride;
+};
+
+template <bool B_MN, bool OUT_F32>
+__global__ void __launch_bounds__(THR)
+gemm_small_kernel(const SmallParams p) {
+  extern __shared__ __align__(16) uint8_t smraw[];
+  __nv_bfloat16 (*sa)[BM * LDS] = reinterpret_cast<__nv_bfloat16 (*)[BM * LDS]>(smraw);
+  __nv_bfloat16 (*sb)[BN * LDS] = reinterpret_cast<__nv_bfloat16 (*)[BN * LDS]>(smraw + NST * BM * LDS * 2);   // K-major B: [n][k]; MN-major: [k][n]
+  const int n0 = blockIdx.x * BN, m0 = blockIdx.y * BM;
+  const int k_lo = blockIdx.z * p.k_per_split, k_hi = min(p.K, k_lo + p.k_per_split);
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, g = lane >> 2, t = lane & 3;
+
+  auto load_tile = [&](int buf, int k0) {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int chunk = threadIdx.x + i * THR, r = chunk >> 3, c = (chunk & 7) * 8;
+      // out-of-range chunks are zero-filled; their source address is clamped to the matrix base (never dereferenced)
+      const bool va = (m0 + r) < p.M && (k0 + c) < k_hi;
+      cp_async16(&sa[buf][r * LDS + c], va ? p.A + (size_t)(m0 + r) * p.lda + k0 + c : p.A, va);
+      if (!B_MN) {
+        const bool vb = (n0 + r) < p.N && (k0 + c) < k_hi;
+        cp_async16(&sb[buf][r * LDS + c], vb ? p.B + (size_t)(n0 + r) * p.ldb + k0 + c : p.B, vb);
+      } else {
+        const bool vb = (k0 + r) < k_hi && (n0 + c) < p.N;
+        cp_async16(&sb[buf][r * LDS + c], vb ? p.B + (size_t)(k0 + r) * p.ldb + n0 + c : p.B, vb);
+      }
+    }
+  };
+
+  float acc[BN / 8][4];
+#pragma unroll
+  for (int nt = 0; nt < BN / 8; ++nt) acc[nt][0] = acc[nt][1] = acc[nt][2] = acc[nt][3] = 0.f;
+
+  const int ktiles = (k_hi - k_lo + BK - 1) / BK;
+  // NST-deep ring: one commit group per k-tile slot (empty groups keep the counting uniform)
+#pragma unroll
+  for (int s_ = 0; s_ < NST - 1; ++s_) {
+    if (s_ < ktiles) load_tile(s_, k_lo + s_ * BK);
+    cp_async_commit();
+  }
+  for (int kt = 0; kt < ktiles; ++kt) {
+    const int buf = kt % NST;
+    cp_async_wait<NST - 2>();                   // tile kt has landed
+    __syncthreads();                            // ... for every thread, and everyone is done with tile kt-1
+    {
+      const int nx = kt + NST - 1;              // refill the slot tile kt-1 used
+      if (nx < ktiles) load_tile(nx % NST, k_lo + nx * BK);
+      cp_async_commit();
+    }
+    const __nv_bfloat16* a = sa[buf] + (warp * 16) * LDS;
+    const __nv_bfloat16* b = sb[buf];
+#pragma unroll
+    for (int ks = 0; ks < BK / 16; ++ks) {
+      uint32_t af[4];
+      af[0] = ld32(a + g * LDS + ks * 16 + 2 * t);
+      af[1] = ld32(a + (g + 8) * LDS + ks * 16 + 2 * t);
+      af[2] = ld32(a + g * LDS + ks * 16 + 8 + 2 * t);
+      af[3] = ld32(a + (g + 8) * LDS + ks * 16 + 8 + 2 * t);
+#pragma unroll
+      for (int nt = 0; nt < BN / 8; ++nt) {
+        uint32_t b0, b1;
+        if (!B_MN) {
+          b0 = ld32(b + (nt * 8 + g) * LDS + ks * 16 + 2 * t);
+          b1 = ld32(b + (nt * 8 + g) * LDS + ks * 16 + 8 + 2 * t);
+        } else {
+          ldsm_x2_trans(b0, b1, b + (ks * 16 + (lane & 15)) * LDS + nt * 8);
+        }
+        mma16816(acc[nt], af, b0, b1);
+      }
+    }
+  }
+  cp_async_wait<0>();
+
+  const int row_a = m0 + warp * 16 + g, row_b = row_a + 8;
+#pragma unroll
+  for (int nt = 0; nt < BN / 8; ++nt) {
+    const int col = n0 + nt * 8 + 2 * t;
+    if (col >= p.N) continue;
+    const bool two = col + 1 < p.N;
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      const int row = h ? row_b : row_a;
+      if (row >= p.M) continue;
+      float v0 = acc[nt][2 * h], v1 = acc[nt][2 * h + 1];
+      if (OUT_F32) {
+        float* out = reinterpret_cast<float*>(p.C) + (size_t)blockIdx.z * p.split_stride + (size_t)row * p.ldc + col;
+        if (p.R) { const float* r = p.R + (size_t)row * p.ldr + col; v0 += r[0]; if (two) v1 += r[1]; }
+        out[0] = v0;
+        if (two) out[1] = v1;
+      } else {
+        __nv_bfloat16* out = reinterpret_cast<__nv_bfloat16*>(p.C) + (size_t)row * p.ldc + col;
+        out[0] = __float2bfloat16_rn(v0);
+        if (two) out[1] = __float2bfloat16_rn(v1);
+      }
+    }
+  }
+}
+
+}  // namespace
+
+extern "C" int rte_gemm_bf16_small(const rte_gemm_args* a, rte_stream_t stream) {
+  RTE_CHECK_ARG(a != nullptr && a->A && a->B && a->C && a->M > 0 && a->N > 0 && a->K > 0);
+  RTE_CHECK_ARG(!a->a_mn_major && a->tile_group == nullptr && a->split_kblocks == nullptr);
+  RTE_CHECK_ARG(a->epilogue == RTE_EPI_BF16 || a->epilogue == RTE_EPI_F32);
+  const int splits = a->splits < 1 ? 1 : a->splits;
+  RTE_CHECK_ARG(splits == 1 || (a->epilogue == RTE_EPI_F32 && a->R == nullptr));
+  if ((reinterpret_cast<uintptr_t>(a->A) & 15) || (reinterpret_cast<uintptr_t>(a->B) & 15) || (a->lda % 8) || (a->ldb % 8) ||
+      (a->K % 8) || (a->b_mn_major && (a->N % 8)))
+    return RTE_ERR_ALIGNMENT;
+  SmallParams p;
+  p.A = reinterpret_cast<const __nv_bfloat16*>(a->A); p.lda = a->lda;
+  p.B = reinterpret_cast<const __nv_bfloat16*>(a->B); p.ldb = a->ldb;
+  p.C = a->C; p.ldc = a->ldc; p.R = reinterpret_cast<const float*>(a->R); p.ldr = a->ldr;
+  p.M = a->M; p.N = a->N; p.K = a->K;
+  const int ktiles = rte::ceil_div(a->K, BK);
+  p.k_per_split = rte::ceil_div(ktiles, splits) * BK;
+  RTE_CHECK_ARG(rte::ceil_div(a->K, p.k_per_split) == splits);      // every partial must be written
+  p.split_stride = a->split_stride;
+  dim3 grid(rte::ceil_div(a->N, BN), rte::ceil_div(a->M, BM), splits);
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  const bool f32 = a->epilogue == RTE_EPI_F32;
+  static bool attr_set = false;
+  if (!attr_set) {
+    if (cudaFuncSetAttribute(gemm_small_kernel<true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES) != cudaSuccess ||
+        cudaFuncSetAttribute(gemm_small_kernel<true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES) != cudaSuccess ||
+        cudaFuncSetAttribute(gemm_small_kernel<false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES) != cudaSuccess ||
+        cudaFuncSetAttribute(gemm_small_kernel<false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES) != cudaSuccess)
+      return RTE_ERR_LAUNCH;
+    attr_set = true;
+  }
+  if (a->b_mn_major) {
+    if (f32) gemm_small_kernel<true, true><<<grid, THR, SMEM_BYTES, st>>>(p); else gemm_small_kernel<true, false><<<grid, THR, SMEM_BYTES, st>>>(p);
+  } else {
+    if (f32) gemm_small_kernel<false, true><<<grid, THR, SMEM_BYTES, st>>>(p); else gemm_small_kernel<false, false><<<grid, THR, SMEM_BYTES, st>>>(p);
+  }
+  RTE_LAUNCH_CHECK();
+  return RTE_OK;
+}

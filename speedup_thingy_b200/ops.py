@@ -42,6 +42,7 @@ class CudaOps:
         self.status = torch.zeros(1, dtype=torch.int32, device=self.device)
         self.launches = 0          # kernels-entry calls issued (for bench accounting)
         self._split_ws: torch.Tensor | None = None
+        self.small_gemm_rows = 256  # products with at most this many rows go to the few-row kernel (0: never)
         self.gemm_max_ctas = 0     # 0 = one persistent CTA per SM; smaller values leave SMs to kernels of other streams
         # When set, launches that only produce PARAMETER gradients (weight-gradient GEMMs with their split reduction,
         # column-sum reductions of the norm backward) go to this stream, ordered after the work issued so far on the
@@ -104,7 +105,9 @@ class CudaOps:
         args.tile_group = tile_group.data_ptr() if tile_group is not None else None
         args.n_groups, args.b_group_stride = n_groups, b_group_stride
         args.split_kblocks = split_kblocks.data_ptr() if split_kblocks is not None else None
-        self._call("rte_gemm_bf16", C.byref(args), self.stream)
+        few_rows = (M <= self.small_gemm_rows and not a_mn and epilogue in (A.EPI_BF16, A.EPI_F32) and tile_group is None
+                    and split_kblocks is None and K % 8 == 0 and (not b_mn or N % 8 == 0))
+        self._call("rte_gemm_bf16_small" if few_rows else "rte_gemm_bf16", C.byref(args), self.stream)
 
     def pick_splits(self, M: int, N: int, K: int) -> int:
         """Split count for a reduction-heavy GEMM whose output has few tiles (weight gradients)."""
@@ -170,6 +173,14 @@ class CudaOps:
         rows = rows if rows is not None else x.numel() // d
         self._call("rte_rmsnorm_fwd", _ptr(x), _ptr(w), _ptr(film_gamma), _ptr(film_beta), _ptr(y_bf16), _ptr(y_f32),
                    _ptr(rstd), rows, d, eps, self.stream)
+
+    def residual_rmsnorm_fwd(self, base, branch, scale, x_out, w, y_bf16, rstd, *, S: int, active=None, passthrough=None,
+                             add2=None, scale2=None, x1_out=None, film_gamma=None, film_beta=None, eps: float = 1e-5) -> None:
+        """x1 = active ? base + scale*branch : passthrough; x = x1 (+ scale2*add2); y = rmsnorm(x)*w (FiLM)."""
+        d = base.shape[-1]
+        self._call("rte_residual_rmsnorm_fwd", _ptr(base), _ptr(branch), _ptr(scale), _ptr(active), _ptr(passthrough), S,
+                   _ptr(add2), _ptr(scale2), _ptr(x1_out), _ptr(x_out), _ptr(w), _ptr(film_gamma), _ptr(film_beta),
+                   _ptr(y_bf16), _ptr(rstd), base.numel() // d, d, eps, self.stream)
 
     def rmsnorm_bwd(self, x, w, rstd, dy, dres, dx_f32, dx_bf16, dw_out, partial, *, film_gamma=None,
                     dgamma_out=None, dbeta_out=None, partial_g=None, partial_b=None, accumulate_dw: bool = False,

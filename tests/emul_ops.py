@@ -133,6 +133,19 @@ class EmulOps:
         if y_f32 is not None:
             y_f32.view(-1, d).copy_(y)
 
+    def residual_rmsnorm_fwd(self, base, branch, scale, x_out, w, y_bf16, rstd, *, S, active=None, passthrough=None,
+                             add2=None, scale2=None, x1_out=None, film_gamma=None, film_beta=None, eps=1e-5):
+        d = base.shape[-1]
+        x1 = base.reshape(-1, d) + scale.reshape(()) * branch.reshape(-1, d)
+        if active is not None:
+            on = active.bool().repeat_interleave(S)[:, None]
+            x1 = torch.where(on, x1, passthrough.reshape(-1, d))
+        if x1_out is not None:
+            x1_out.copy_(x1.view_as(x1_out))
+        x = x1 if add2 is None else x1 + scale2.reshape(()) * add2.reshape(-1, d)
+        x_out.copy_(x.view_as(x_out))
+        self.rmsnorm_fwd(x_out, w, y_bf16, rstd, film_gamma=film_gamma, film_beta=film_beta, eps=eps)
+
     def rmsnorm_bwd(self, x, w, rstd, dy, dres, dx_f32, dx_bf16, dw_out, partial, *, film_gamma=None,
                     dgamma_out=None, dbeta_out=None, partial_g=None, partial_b=None, accumulate_dw=False,
                     accumulate_film=False, rows=None):

@@ -46,10 +46,47 @@ def test_gemm_bf16_all_majors(ops, M, N, K, a_mn, b_mn):
     a_dev = (a.t().contiguous() if a_mn else a).to(DEV)
     b_dev = (b.t().contiguous() if b_mn else b).to(DEV)
     out = torch.zeros(M, N, dtype=torch.bfloat16, device=DEV)
-    ops.gemm(a_dev, b_dev, out, M=M, N=N, K=K, a_mn=a_mn, b_mn=b_mn)
+    keep, ops.small_gemm_rows = ops.small_gemm_rows, 0          # this test is about the tcgen05 kernel at every size
+    try:
+        ops.gemm(a_dev, b_dev, out, M=M, N=N, K=K, a_mn=a_mn, b_mn=b_mn)
+    finally:
+        ops.small_gemm_rows = keep
     torch.cuda.synchronize()
     ops.check_status()
     _close(out, ref, 1e-2, f"gemm {M}x{N}x{K} a_mn={a_mn} b_mn={b_mn}")
+
+
+@pytest.mark.parametrize("M,N,K", [(64, 1536, 512), (64, 512, 4096), (70, 104, 136), (256, 2048, 512), (1, 8, 8), (130, 96, 72)])
+@pytest.mark.parametrize("b_mn", [False, True])
+@pytest.mark.parametrize("mode", ["bf16", "f32_residual", "f32_split"])
+def test_gemm_few_rows_kernel(ops, M, N, K, b_mn, mode):
+    """The cp.async + mma.sync kernel the replay's chain uses (rte_gemm_bf16_small), every epilogue and both B majors."""
+    g = torch.Generator().manual_seed(M * 7 + N + K)
+    a, b = _bf(torch.randn(M, K, generator=g)), _bf(torch.randn(N, K, generator=g))
+    ref = a.float() @ b.float().t()
+    b_dev = (b.t().contiguous() if b_mn else b).to(DEV)
+    assert M <= ops.small_gemm_rows
+    before = ops.launches
+    if mode == "bf16":
+        out = torch.zeros(M, N, dtype=torch.bfloat16, device=DEV)
+        ops.gemm(a.to(DEV), b_dev, out, M=M, N=N, K=K, b_mn=b_mn)
+        tol = 1e-2
+    elif mode == "f32_residual":
+        r = torch.randn(M, N, generator=g)
+        ref = ref + r
+        out = r.clone().to(DEV)
+        ops.gemm(a.to(DEV), b_dev, out, M=M, N=N, K=K, b_mn=b_mn, epilogue=1, residual=out)
+        tol = 2e-3
+    else:
+        out = torch.full((M, N), 3.0, device=DEV)
+        ws = torch.empty(16 * M * N, device=DEV)
+        ops.gemm_f32_few_rows(a.to(DEV), b_dev, out, M=M, N=N, K=K, b_mn=b_mn, ws=ws, accumulate=True)
+        ref = ref + 3.0
+        tol = 2e-3
+    torch.cuda.synchronize()
+    ops.check_status()
+    assert ops.launches > before
+    _close(out, ref, tol, f"few-row gemm {M}x{N}x{K} b_mn={b_mn} {mode}")
 
 
 def test_gemm_f32_residual_and_alias(ops):
@@ -288,6 +325,32 @@ def test_topk_lowest_index_bit_exact(ops, rows, n, k):
     torch.cuda.synchronize()
     assert torch.equal(gi.cpu().long(), idx)
     assert torch.equal(gv.cpu(), vals)
+
+
+@pytest.mark.parametrize("n,S,d,with_select,with_add2", [(3, 8, 64, False, False), (2, 16, 512, True, True), (5, 4, 128, True, False)])
+def test_residual_rmsnorm_fwd_matches_the_separate_steps(ops, n, S, d, with_select, with_add2):
+    g = torch.Generator().manual_seed(d + n)
+    rows = n * S
+    base, branch, pas, add2 = (torch.randn(rows, d, generator=g) for _ in range(4))
+    w, fg, fb = torch.randn(d, generator=g), torch.randn(d, generator=g) * 0.1, torch.randn(d, generator=g) * 0.1
+    s1, s2 = torch.tensor([0.7]), torch.tensor([0.1])
+    active = torch.tensor([i % 2 for i in range(n)], dtype=torch.int32)
+    x1 = base + 0.7 * branch
+    if with_select:
+        x1 = torch.where(active.bool().repeat_interleave(S)[:, None], x1, pas)
+    x = x1 + 0.1 * add2 if with_add2 else x1
+    y_ref = O.rmsnorm(x, w) * (1 + fg) + fb
+    dev = lambda t: t.to(DEV)  # noqa: E731
+    x1_out, x_out = torch.zeros(rows, d, device=DEV), torch.zeros(rows, d, device=DEV)
+    y16, rstd = torch.zeros(rows, d, dtype=torch.bfloat16, device=DEV), torch.zeros(rows, device=DEV)
+    ops.residual_rmsnorm_fwd(dev(base), dev(branch), dev(s1), x_out, dev(w), y16, rstd, S=S,
+                             active=dev(active) if with_select else None, passthrough=dev(pas) if with_select else None,
+                             add2=dev(add2) if with_add2 else None, scale2=dev(s2) if with_add2 else None, x1_out=x1_out,
+                             film_gamma=dev(fg), film_beta=dev(fb))
+    torch.cuda.synchronize()
+    assert (x1_out.cpu() - x1).abs().max() <= 1e-6 and (x_out.cpu() - x).abs().max() <= 1e-6
+    assert (y16.cpu().float() - y_ref).abs().max() <= 2e-2 * y_ref.abs().max()
+    assert (rstd.cpu() - torch.rsqrt(x.pow(2).mean(-1) + 1e-5)).abs().max() <= 1e-5
 
 
 def test_swiglu_standalone_pass_matches_fused_epilogue_math(ops):
