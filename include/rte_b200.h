@@ -239,6 +239,17 @@ int rte_macro_phi_bwd(const float* h0, const float* dout, const rte_phi_params* 
                       const float* act, float* dh0, const rte_phi_grads* g, float* scratch, int32_t B,
                       int32_t S, int32_t d, int32_t m, int32_t R, int32_t K_strides, float eps,
                       rte_stream_t stream);
+/* The same backward in two halves, so that a caller can put the parameter gradients on another stream: _data
+ * computes dh0 (what the rest of backward waits for) and leaves its intermediates in `scratch`; _params (ordered
+ * after _data, same `scratch`) reduces the per-sample parameter gradients per (recipe, stride) key.             */
+int rte_macro_phi_bwd_data(const float* h0, const float* dout, const rte_phi_params* p, const int32_t* recipe_id,
+                           const int32_t* stride_id, float s_cfg, const float* rstd, const float* act, float* dh0,
+                           float* scratch, int32_t B, int32_t S, int32_t d, int32_t m, int32_t K_strides,
+                           rte_stream_t stream);
+int rte_macro_phi_bwd_params(const float* h0, const int32_t* recipe_id, const int32_t* stride_id, const float* rstd,
+                             const float* pooled, const float* act, const rte_phi_grads* g, float* scratch,
+                             int32_t B, int32_t S, int32_t d, int32_t m, int32_t R, int32_t K_strides,
+                             rte_stream_t stream);
 
 /* -------------------------------------------------- SwiGLU as its own pass (layers.py:78-87), for callers that
  * keep the W_ug GEMM's plain bf16 output: ug bf16 [rows, 2F] = (up | gate); z bf16 [rows, F] = up * silu(gate);

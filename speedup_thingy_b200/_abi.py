@@ -95,6 +95,8 @@ PROTOTYPES = {
                           [c_f32, c_vp]),
     "rte_macro_phi_bwd": (C.c_int, [c_vp, c_vp, P(PhiParams), c_vp, c_vp, c_f32, c_vp, c_vp, c_vp, c_vp, P(PhiGrads),
                                     c_vp] + [c_i32] * 6 + [c_f32, c_vp]),
+    "rte_macro_phi_bwd_data": (C.c_int, [c_vp, c_vp, P(PhiParams), c_vp, c_vp, c_f32, c_vp, c_vp, c_vp, c_vp] + [c_i32] * 5 + [c_vp]),
+    "rte_macro_phi_bwd_params": (C.c_int, [c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, P(PhiGrads), c_vp] + [c_i32] * 6 + [c_vp]),
     "rte_cluster_route": (C.c_int, [c_vp, c_i32, c_vp, c_vp, c_vp, c_i32, c_i32, c_i32, c_vp]),
     "rte_cluster_pack": (C.c_int, [c_vp, c_i32, c_i32, c_i32, c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, c_vp]),
     "rte_gather_rows_convert": (C.c_int, [c_vp, c_i32, c_vp, c_vp, c_i32, c_i64, c_i32, c_vp]),

@@ -422,36 +422,58 @@ extern "C" int rte_macro_phi_fwd(const float* h0, const rte_phi_params* p, const
   return RTE_OK;
 }
 
-extern "C" int rte_macro_phi_bwd(const float* h0, const float* dout, const rte_phi_params* p, const int32_t* recipe_id,
-                                 const int32_t* stride_id, float s_cfg, const float* rstd, const float* pooled,
-                                 const float* act, float* dh0, const rte_phi_grads* g, float* scratch, int32_t B,
-                                 int32_t S, int32_t d, int32_t m, int32_t R, int32_t K_strides, float eps,
-                                 rte_stream_t stream) {
-  (void)eps;
-  RTE_CHECK_ARG(h0 && dout && p && g && recipe_id && stride_id && rstd && pooled && act && dh0 && scratch && B > 0 &&
-                S > 0 && d > 0 && m > 0 && R > 0 && K_strides > 0);
-  RTE_CHECK_ARG(g->gain && g->v && g->u && g->bias);
+namespace {
+struct PhiBwdScratch { float *dupd, *da, *dpool, *pu, *pg, *pb, *pv; };
+// scratch layout (floats): dupd[M*d] | da[M*m] | dpool[B*d] | pu[B*m*d] | pg[B*d] | pb[B*d] | pv[B*3d*m]
+inline PhiBwdScratch phi_scratch(float* scratch, int B, int S, int d, int m) {
+  const size_t M = (size_t)B * S;
+  PhiBwdScratch x;
+  x.dupd = scratch;
+  x.da = x.dupd + M * d;
+  x.dpool = x.da + M * m;
+  x.pu = x.dpool + (size_t)B * d;
+  x.pg = x.pu + (size_t)B * m * d;
+  x.pb = x.pg + (size_t)B * d;
+  x.pv = x.pb + (size_t)B * d;
+  return x;
+}
+}  // namespace
+
+// Data-gradient half: dh0 (the chain the rest of backward waits for); leaves dupd and da in `scratch`.
+extern "C" int rte_macro_phi_bwd_data(const float* h0, const float* dout, const rte_phi_params* p, const int32_t* recipe_id,
+                                      const int32_t* stride_id, float s_cfg, const float* rstd, const float* act, float* dh0,
+                                      float* scratch, int32_t B, int32_t S, int32_t d, int32_t m, int32_t K_strides,
+                                      rte_stream_t stream) {
+  RTE_CHECK_ARG(h0 && dout && p && recipe_id && stride_id && rstd && act && dh0 && scratch && B > 0 && S > 0 && d > 0 && m > 0 &&
+                K_strides > 0);
   if (m > MMAX || B > 1024) return RTE_ERR_UNSUPPORTED;
   PhiDims D{B, S, d, m, K_strides};
   const int tiles = rte::ceil_div(S, TT);
-  const size_t M = (size_t)B * S;
-  // scratch layout (floats): dupd[M*d] | da[M*m] | dpool[B*d] | pu[B*m*d] | pg[B*d] | pb[B*d] | pv[B*3d*m]
-  float* dupd = scratch;
-  float* da = dupd + M * d;
-  float* dpool = da + M * m;
-  float* pu = dpool + (size_t)B * d;
-  float* pg = pu + (size_t)B * m * d;
-  float* pb = pg + (size_t)B * d;
-  float* pv = pb + (size_t)B * d;
+  const PhiBwdScratch x = phi_scratch(scratch, B, S, d, m);
   phi_out_kernel<1><<<B * tiles, NTHR, 0, ST(stream)>>>(h0, act, p->gain, p->u, p->bias, p->scale, recipe_id, stride_id,
-                                                        s_cfg, dout, dh0, dupd, D);
+                                                        s_cfg, dout, dh0, x.dupd, D);
   RTE_LAUNCH_CHECK();
-  phi_da_kernel<<<B * tiles, NTHR, 0, ST(stream)>>>(dupd, act, p->u, recipe_id, stride_id, da, D);
+  phi_da_kernel<<<B * tiles, NTHR, 0, ST(stream)>>>(x.dupd, act, p->u, recipe_id, stride_id, x.da, D);
   RTE_LAUNCH_CHECK();
-  phi_dpool_kernel<<<B, NTHR, 0, ST(stream)>>>(da, p->v, recipe_id, stride_id, dpool, D);
+  phi_dpool_kernel<<<B, NTHR, 0, ST(stream)>>>(x.da, p->v, recipe_id, stride_id, x.dpool, D);
   RTE_LAUNCH_CHECK();
-  phi_dz_kernel<<<B * tiles, NTHR, 0, ST(stream)>>>(h0, rstd, da, dpool, p->v, recipe_id, stride_id, dh0, D);
+  phi_dz_kernel<<<B * tiles, NTHR, 0, ST(stream)>>>(h0, rstd, x.da, x.dpool, p->v, recipe_id, stride_id, dh0, D);
   RTE_LAUNCH_CHECK();
+  return RTE_OK;
+}
+
+// Parameter-gradient half: reads dupd and da left in `scratch` by rte_macro_phi_bwd_data (may run on another
+// stream, ordered after it); nothing downstream in backward depends on it.
+extern "C" int rte_macro_phi_bwd_params(const float* h0, const int32_t* recipe_id, const int32_t* stride_id, const float* rstd,
+                                        const float* pooled, const float* act, const rte_phi_grads* g, float* scratch,
+                                        int32_t B, int32_t S, int32_t d, int32_t m, int32_t R, int32_t K_strides,
+                                        rte_stream_t stream) {
+  RTE_CHECK_ARG(h0 && recipe_id && stride_id && rstd && pooled && act && g && scratch && B > 0 && S > 0 && d > 0 && m > 0 &&
+                R > 0 && K_strides > 0);
+  RTE_CHECK_ARG(g->gain && g->v && g->u && g->bias);
+  if (m > MMAX || B > 1024) return RTE_ERR_UNSUPPORTED;
+  PhiDims D{B, S, d, m, K_strides};
+  const PhiBwdScratch x = phi_scratch(scratch, B, S, d, m);
   const size_t smem_pu = (size_t)S * m * sizeof(float);
   const size_t smem_pv = ((size_t)S * m + S + (size_t)S * 8) * sizeof(float);
   if (smem_pu > 48 * 1024 || smem_pv > 48 * 1024) {
@@ -463,19 +485,32 @@ extern "C" int rte_macro_phi_bwd(const float* h0, const float* dout, const rte_p
       set = true;
     }
   }
-  phi_pu_kernel<<<B * rte::ceil_div(d, NTHR), NTHR, smem_pu, ST(stream)>>>(h0, act, dupd, pu, pg, pb, D);
+  phi_pu_kernel<<<B * rte::ceil_div(d, NTHR), NTHR, smem_pu, ST(stream)>>>(h0, act, x.dupd, x.pu, x.pg, x.pb, D);
   RTE_LAUNCH_CHECK();
-  phi_pv_kernel<<<B * rte::ceil_div(d, 8), NTHR, smem_pv, ST(stream)>>>(h0, rstd, pooled, da, pv, D);
+  phi_pv_kernel<<<B * rte::ceil_div(d, 8), NTHR, smem_pv, ST(stream)>>>(h0, rstd, pooled, x.da, x.pv, D);
   RTE_LAUNCH_CHECK();
   const int n_keys = R * K_strides;
   const long long eu = (long long)m * d, ev = (long long)3 * d * m, ed = d;
-  phi_reduce_keys_kernel<<<dim3((unsigned)rte::ceil_div64(eu, NTHR), n_keys), NTHR, 0, ST(stream)>>>(pu, recipe_id, stride_id, g->u, B, K_strides, eu);
+  phi_reduce_keys_kernel<<<dim3((unsigned)rte::ceil_div64(eu, NTHR), n_keys), NTHR, 0, ST(stream)>>>(x.pu, recipe_id, stride_id, g->u, B, K_strides, eu);
   RTE_LAUNCH_CHECK();
-  phi_reduce_keys_kernel<<<dim3((unsigned)rte::ceil_div64(ev, NTHR), n_keys), NTHR, 0, ST(stream)>>>(pv, recipe_id, stride_id, g->v, B, K_strides, ev);
+  phi_reduce_keys_kernel<<<dim3((unsigned)rte::ceil_div64(ev, NTHR), n_keys), NTHR, 0, ST(stream)>>>(x.pv, recipe_id, stride_id, g->v, B, K_strides, ev);
   RTE_LAUNCH_CHECK();
-  phi_reduce_keys_kernel<<<dim3((unsigned)rte::ceil_div64(ed, NTHR), n_keys), NTHR, 0, ST(stream)>>>(pg, recipe_id, stride_id, g->gain, B, K_strides, ed);
+  phi_reduce_keys_kernel<<<dim3((unsigned)rte::ceil_div64(ed, NTHR), n_keys), NTHR, 0, ST(stream)>>>(x.pg, recipe_id, stride_id, g->gain, B, K_strides, ed);
   RTE_LAUNCH_CHECK();
-  phi_reduce_keys_kernel<<<dim3((unsigned)rte::ceil_div64(ed, NTHR), n_keys), NTHR, 0, ST(stream)>>>(pb, recipe_id, stride_id, g->bias, B, K_strides, ed);
+  phi_reduce_keys_kernel<<<dim3((unsigned)rte::ceil_div64(ed, NTHR), n_keys), NTHR, 0, ST(stream)>>>(x.pb, recipe_id, stride_id, g->bias, B, K_strides, ed);
   RTE_LAUNCH_CHECK();
   return RTE_OK;
+}
+
+// Both halves on one stream.
+extern "C" int rte_macro_phi_bwd(const float* h0, const float* dout, const rte_phi_params* p, const int32_t* recipe_id,
+                                 const int32_t* stride_id, float s_cfg, const float* rstd, const float* pooled,
+                                 const float* act, float* dh0, const rte_phi_grads* g, float* scratch, int32_t B,
+                                 int32_t S, int32_t d, int32_t m, int32_t R, int32_t K_strides, float eps,
+                                 rte_stream_t stream) {
+  (void)eps;
+  RTE_CHECK_ARG(g != nullptr && R > 0);
+  const int rc = rte_macro_phi_bwd_data(h0, dout, p, recipe_id, stride_id, s_cfg, rstd, act, dh0, scratch, B, S, d, m, K_strides, stream);
+  if (rc != RTE_OK) return rc;
+  return rte_macro_phi_bwd_params(h0, recipe_id, stride_id, rstd, pooled, act, g, scratch, B, S, d, m, R, K_strides, stream);
 }

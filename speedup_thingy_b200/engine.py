@@ -313,7 +313,7 @@ class TrainEngine:
         self._side_stream = torch.cuda.Stream(device=dev, priority=-1) if (self.audit_k and dev.type == "cuda") else None
         if self._side_stream is not None and hasattr(ops, "gemm_max_ctas"):
             ops.gemm_max_ctas = max(ops.sm_count - 8, 1)
-        self._param_stream = torch.cuda.Stream(device=dev) if (self.audit_k and dev.type == "cuda") else None
+        self._param_stream = torch.cuda.Stream(device=dev) if (not self.dense and dev.type == "cuda") else None
         if self.audit_k:
             from .audit import AuditReplay
             self.audit = AuditReplay(self, self.audit_k)
@@ -542,8 +542,16 @@ class TrainEngine:
                 self.audit.forward_losses()
             self._main_wait_side()
             with self._on_side():
+                probes = getattr(self, "_join_probes", None)
+                if probes is not None:
+                    s0 = torch.cuda.Event(enable_timing=True, external=True)
+                    s0.record(torch.cuda.current_stream(self.device))
                 self.audit_dh_exact = self.audit.backward_head()
                 self.audit.backward_core(self.audit_dh_exact)
+                if probes is not None:
+                    s1 = torch.cuda.Event(enable_timing=True, external=True)
+                    s1.record(torch.cuda.current_stream(self.device))
+                    probes.append((s0, s1))
         # ---------------- backward
         self._begin_backward()
         dlogits = self.logits
@@ -565,13 +573,20 @@ class TrainEngine:
             o.scatter_add_rows(dcur, self.audit.idx, self.audit.dhot_extra, self.audit.n, S * d)
         if not self.dense:
             # Phi backward writes dh0 into `dalt`; the router's auxiliary losses add their share
-            o.macro_phi_bwd(self.prelude[-1].out if self.prelude else self.x0, dcur, self._phi_param_dict(),
-                            self.route["recipe_id"], self.route["depth_id"], cfg.macro_update_scale, self.phi_rstd,
-                            self.phi_pooled, self.phi_act, dalt,
-                            dict(gain=g["macro.d_gain"], v=g["macro.v"], u=g["macro.u"], bias=g["macro.bias"]),
-                            self.phi_scratch, B=B, S=S, d=d, m=cfg.macro_rank, R=cfg.recipe_count,
-                            K=len(cfg.depth_choices))
-            self._grad_ready("macro.d_gain", "macro.v", "macro.u", "macro.bias")
+            # (its parameter-gradient half goes to the parameter-gradient stream: backward only waits for dh0)
+            split = self._param_stream is not None and hasattr(o, "param_stream")
+            if split:
+                o.param_stream = self._param_stream
+            o.macro_phi_bwd_split(self.prelude[-1].out if self.prelude else self.x0, dcur, self._phi_param_dict(),
+                                  self.route["recipe_id"], self.route["depth_id"], cfg.macro_update_scale, self.phi_rstd,
+                                  self.phi_pooled, self.phi_act, dalt,
+                                  dict(gain=g["macro.d_gain"], v=g["macro.v"], u=g["macro.u"], bias=g["macro.bias"]),
+                                  self.phi_scratch, B=B, S=S, d=d, m=cfg.macro_rank, R=cfg.recipe_count,
+                                  K=len(cfg.depth_choices))
+            if split:
+                o.param_stream = None
+            else:
+                self._grad_ready("macro.d_gain", "macro.v", "macro.u", "macro.bias")
             dcur, dalt = dalt, dcur
             if audited:
                 from .audit import CORE_PARAMS
@@ -602,6 +617,9 @@ class TrainEngine:
                 dcur, dalt = dalt, dcur
         o.embed_bwd(tokens, dcur, g["embed.weight"])
         self._grad_ready("embed.weight")
+        if not self.dense and self._param_stream is not None and hasattr(o, "param_stream"):
+            torch.cuda.current_stream(self.device).wait_stream(self._param_stream)
+            self._grad_ready("macro.d_gain", "macro.v", "macro.u", "macro.bias")
         self._finish_backward()
 
     def _optimizer_step(self) -> None:

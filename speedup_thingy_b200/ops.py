@@ -307,6 +307,20 @@ class CudaOps:
                    _ptr(rstd), _ptr(pooled), _ptr(act), _ptr(dh0), C.byref(sg), _ptr(scratch), B, S, d, m, R, K,
                    1e-5, self.stream)
 
+    def macro_phi_bwd_split(self, h0, dout, p: dict, recipe_id, stride_id, s_cfg, rstd, pooled, act, dh0, grads: dict,
+                            scratch, *, B, S, d, m, R, K):
+        """The same backward with its parameter-gradient half on `param_stream` when one is set (nothing downstream
+        in backward reads those gradients); the data-gradient half stays on the current stream."""
+        sp = self._phi_params(p)
+        sg = A.PhiGrads()
+        for name, _ in A.PhiGrads._fields_:
+            setattr(sg, name, grads[name].data_ptr())
+        self._call("rte_macro_phi_bwd_data", _ptr(h0), _ptr(dout), C.byref(sp), _ptr(recipe_id), _ptr(stride_id), s_cfg,
+                   _ptr(rstd), _ptr(act), _ptr(dh0), _ptr(scratch), B, S, d, m, K, self.stream)
+        with self._deferred():
+            self._call("rte_macro_phi_bwd_params", _ptr(h0), _ptr(recipe_id), _ptr(stride_id), _ptr(rstd), _ptr(pooled),
+                       _ptr(act), C.byref(sg), _ptr(scratch), B, S, d, m, R, K, self.stream)
+
     @staticmethod
     def phi_bwd_scratch_floats(B, S, d, m) -> int:
         return B * S * d + B * S * m + 3 * B * d + B * m * d + B * 3 * d * m

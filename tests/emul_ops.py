@@ -371,6 +371,9 @@ class EmulOps:
         pooled.view(-1)[: B * d] = pl.reshape(-1)
         act.view(B, S, m).copy_(a)
 
+    def macro_phi_bwd_split(self, *args, **kw):
+        self.macro_phi_bwd(*args, **kw)
+
     def macro_phi_bwd(self, h0, dout, p, recipe_id, stride_id, s_cfg, rstd, pooled, act, dh0, grads, scratch, *, B, S, d, m, R, K):
         self.launches += 1
         leaves = {k: p[k].detach().clone().requires_grad_(k != "scale") for k in p}
