@@ -213,6 +213,12 @@ int rte_router_aux_bwd(const rte_router_weights* w, const rte_router_out* fwd, c
                        float lambda_load, float lambda_depth, float* aux, const rte_router_grads* grads,
                        float* dh0, float* scratch, int32_t B, int32_t S, int32_t d, int32_t hid, int32_t R,
                        int32_t K, rte_stream_t stream);
+/* The same backward in two halves (parameter gradients on another stream, ordered after _data, same `scratch`). */
+int rte_router_aux_bwd_data(const rte_router_weights* w, const rte_router_out* fwd, const int32_t* depth_values,
+                            float lambda_load, float lambda_depth, float* aux, float* dh0, float* scratch, int32_t B,
+                            int32_t S, int32_t d, int32_t hid, int32_t R, int32_t K, rte_stream_t stream);
+int rte_router_aux_bwd_params(const rte_router_out* fwd, const rte_router_grads* grads, float* scratch, int32_t B,
+                              int32_t d, int32_t hid, int32_t R, int32_t K, rte_stream_t stream);
 
 /* ---------------------------------- top-k with ties to the lowest index (output.py:78; layers.py:602-627)
  * scores f32 [rows, n]; idx int32 [rows, k] and vals f32 [rows, k] (either may be NULL), descending. */

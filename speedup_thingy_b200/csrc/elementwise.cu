@@ -264,24 +264,24 @@ rmsnorm_bwd_kernel(const float* __restrict__ x, const float* __restrict__ w, con
   }
 }
 
-// 32 columns x 8 row-groups per CTA: eight partial sums per column, combined through shared memory in a
+// 32 columns x 32 row-groups per CTA: thirty-two partial sums per column, combined through shared memory in a
 // fixed order (deterministic).
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(1024)
 colsum_kernel(const float* __restrict__ part, int n_rows, int d, float* __restrict__ out, int accumulate) {
-  __shared__ float sm[8][33];
+  __shared__ float sm[32][33];
   const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
   const int c = blockIdx.x * 32 + tx;
   float s = 0.f;
   if (c < d) {
 #pragma unroll 4
-    for (int r = ty; r < n_rows; r += 8) s += part[(size_t)r * d + c];
+    for (int r = ty; r < n_rows; r += 32) s += part[(size_t)r * d + c];
   }
   sm[ty][tx] = s;
   __syncthreads();
   if (ty == 0 && c < d) {
     float t = 0.f;
 #pragma unroll
-    for (int k = 0; k < 8; ++k) t += sm[k][tx];
+    for (int k = 0; k < 32; ++k) t += sm[k][tx];
     out[c] = accumulate ? out[c] + t : t;
   }
 }
@@ -659,14 +659,14 @@ extern "C" int rte_rmsnorm_bwd(const float* x, const float* w, const float* film
   if (d > 128 * RN_MAX_V4) return RTE_ERR_UNSUPPORTED;
   const bool grads = dw_partial || dgamma_partial;
   int grid = rte::ceil_div(rows, 8);
-  const int cap = 148 * 8;      // enough CTAs in flight to cover HBM latency; each writes one partial row
+  const int cap = 148 * 4;      // one wave of CTAs (each writes one partial row), enough rows in flight to cover HBM latency
   if (grid > cap) grid = cap;
   if (grads) {
     RTE_CHECK_ARG(max_partials >= 1);
     if (grid > max_partials) grid = max_partials;
   }
   if (n_partials) *n_partials = grid;
-  const size_t smem = grads ? (size_t)3 * 8 * d * sizeof(float) : 0;
+  const size_t smem = grads ? (size_t)(dgamma_partial ? 3 : 1) * 8 * d * sizeof(float) : 0;
 #define RTE_RN_BWD(NV)                                                                                           \
   do {                                                                                                           \
     if (smem > 48 * 1024) {                                                                                      \
@@ -695,7 +695,7 @@ extern "C" int rte_rmsnorm_bwd(const float* x, const float* w, const float* film
 extern "C" int rte_colsum_partials(const float* partial, int32_t n_rows, int32_t d, float* out, int32_t accumulate,
                                    rte_stream_t stream) {
   RTE_CHECK_ARG(partial && out && n_rows > 0 && d > 0);
-  colsum_kernel<<<rte::ceil_div(d, 32), 256, 0, ST(stream)>>>(partial, n_rows, d, out, accumulate);
+  colsum_kernel<<<rte::ceil_div(d, 32), 1024, 0, ST(stream)>>>(partial, n_rows, d, out, accumulate);
   RTE_LAUNCH_CHECK();
   return RTE_OK;
 }

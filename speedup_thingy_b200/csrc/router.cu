@@ -345,13 +345,13 @@ extern "C" int rte_router_fwd(const float* h0, const rte_router_weights* w, cons
   return RTE_OK;
 }
 
-extern "C" int rte_router_aux_bwd(const rte_router_weights* w, const rte_router_out* fwd, const int32_t* depth_values,
-                                  float lambda_load, float lambda_depth, float* aux, const rte_router_grads* grads,
-                                  float* dh0, float* scratch, int32_t B, int32_t S, int32_t d, int32_t hid, int32_t R,
-                                  int32_t K, rte_stream_t stream) {
-  RTE_CHECK_ARG(w && fwd && depth_values && aux && grads && dh0 && scratch && B > 0 && S > 0 && d > 0 && hid > 0);
+// Data-gradient half: the auxiliary losses, d(loss)/d(pre-activations) per sample (left in `scratch`), and
+// dh0[b,s,:] += dpooled[b,:] / S -- what the rest of backward waits for.
+extern "C" int rte_router_aux_bwd_data(const rte_router_weights* w, const rte_router_out* fwd, const int32_t* depth_values,
+                                       float lambda_load, float lambda_depth, float* aux, float* dh0, float* scratch, int32_t B,
+                                       int32_t S, int32_t d, int32_t hid, int32_t R, int32_t K, rte_stream_t stream) {
+  RTE_CHECK_ARG(w && fwd && depth_values && aux && dh0 && scratch && B > 0 && S > 0 && d > 0 && hid > 0);
   RTE_CHECK_ARG(R > 0 && R <= RTE_ROUTER_MAX_R && K > 0 && K <= RTE_ROUTER_MAX_K);
-  RTE_CHECK_ARG(grads->r_w0 && grads->r_b0 && grads->r_w2 && grads->r_b2 && grads->d_w0 && grads->d_b0 && grads->d_w2 && grads->d_b2);
   float* mean_prob = scratch;                       // [RTE_ROUTER_MAX_R]
   float* dpre_r = scratch + RTE_ROUTER_MAX_R;       // [B, hid]
   float* dpre_d = dpre_r + (size_t)B * hid;         // [B, hid]
@@ -379,6 +379,18 @@ extern "C" int rte_router_aux_bwd(const rte_router_weights* w, const rte_router_
     bcast_add_kernel<<<grid, NTHR, 0, ST(stream)>>>(dh0, dpooled, B * S, S, d, RTE_ROUTER_DPOOLED_PARTS, (long long)B * d);
     RTE_LAUNCH_CHECK();
   }
+  return RTE_OK;
+}
+
+// Parameter-gradient half of the auxiliary-loss backward: reads dpre / dlog left in `scratch` by the data half.
+extern "C" int rte_router_aux_bwd_params(const rte_router_out* fwd, const rte_router_grads* grads, float* scratch, int32_t B,
+                                         int32_t d, int32_t hid, int32_t R, int32_t K, rte_stream_t stream) {
+  RTE_CHECK_ARG(fwd && grads && scratch && B > 0 && d > 0 && hid > 0 && R > 0 && K > 0);
+  RTE_CHECK_ARG(grads->r_w0 && grads->r_b0 && grads->r_w2 && grads->r_b2 && grads->d_w0 && grads->d_b0 && grads->d_w2 && grads->d_b2);
+  float* dpre_r = scratch + RTE_ROUTER_MAX_R;
+  float* dpre_d = dpre_r + (size_t)B * hid;
+  float* dlog_r = dpre_d + (size_t)B * hid;
+  float* dlog_d = dlog_r + (size_t)B * R;
   const int g0 = (int)rte::ceil_div64((long long)hid * d, NTHR);
   router_dw0_kernel<<<g0, NTHR, 0, ST(stream)>>>(dpre_r, fwd->pooled, grads->r_w0, grads->r_b0, B, d, hid);
   RTE_LAUNCH_CHECK();
@@ -389,4 +401,15 @@ extern "C" int rte_router_aux_bwd(const rte_router_weights* w, const rte_router_
   router_dw2_kernel<<<rte::ceil_div(K * hid, 32), NTHR, 0, ST(stream)>>>(dlog_d, fwd->d_hidden_pre, grads->d_w2, grads->d_b2, B, hid, K);
   RTE_LAUNCH_CHECK();
   return RTE_OK;
+}
+
+// Both halves on one stream.
+extern "C" int rte_router_aux_bwd(const rte_router_weights* w, const rte_router_out* fwd, const int32_t* depth_values,
+                                  float lambda_load, float lambda_depth, float* aux, const rte_router_grads* grads,
+                                  float* dh0, float* scratch, int32_t B, int32_t S, int32_t d, int32_t hid, int32_t R,
+                                  int32_t K, rte_stream_t stream) {
+  RTE_CHECK_ARG(grads != nullptr);
+  const int rc = rte_router_aux_bwd_data(w, fwd, depth_values, lambda_load, lambda_depth, aux, dh0, scratch, B, S, d, hid, R, K, stream);
+  if (rc != RTE_OK) return rc;
+  return rte_router_aux_bwd_params(fwd, grads, scratch, B, d, hid, R, K, stream);
 }

@@ -421,6 +421,10 @@ class TrainEngine:
         return dict(gain=p["macro.d_gain"], v=p["macro.v"], u=p["macro.u"], bias=p["macro.bias"], scale=self.macro_scale)
 
     # ------------------------------------------------------------------ one transformer block
+    @staticmethod
+    def _router_grad_names() -> list[str]:
+        return [f"router.{m}.{i}.{k}" for m in ("recipe_mlp", "depth_mlp") for i in (0, 2) for k in ("weight", "bias")]
+
     def _fuse_swiglu(self, rows: int) -> bool:
         """SwiGLU inside the tcgen05 GEMM's epilogue only between the few-row kernel's range and the large-M range."""
         return getattr(self.ops, "small_gemm_rows", 0) < rows <= self.swiglu_fuse_max_rows
@@ -606,11 +610,15 @@ class TrainEngine:
                           d_w2=g["router.depth_mlp.2.weight"], d_b2=g["router.depth_mlp.2.bias"])
                 # under data parallelism each rank evaluates the auxiliary losses on its own shard and
                 # contributes 1/world of their gradient (the cross-entropy part is exactly the global mean)
-                o.router_aux_bwd(self._router_weight_dict(), self.route, self.depth_values, tr.lambda_load / self.world,
-                                 tr.lambda_depth / self.world, self.scalars[1:3], rg, dcur, self.router_scratch, B=B,
-                                 S=S, d=d, hid=cfg.router_hidden_dim, R=cfg.recipe_count, K=len(cfg.depth_choices))
-                self._grad_ready(*[f"router.{m}.{i}.{k}" for m in ("recipe_mlp", "depth_mlp") for i in (0, 2)
-                                   for k in ("weight", "bias")])
+                if split:
+                    o.param_stream = self._param_stream
+                o.router_aux_bwd_split(self._router_weight_dict(), self.route, self.depth_values, tr.lambda_load / self.world,
+                                       tr.lambda_depth / self.world, self.scalars[1:3], rg, dcur, self.router_scratch, B=B,
+                                       S=S, d=d, hid=cfg.router_hidden_dim, R=cfg.recipe_count, K=len(cfg.depth_choices))
+                if split:
+                    o.param_stream = None
+                else:
+                    self._grad_ready(*self._router_grad_names())
             o.cast_bf16(dcur, self.dx16)
             for blk in reversed(self.prelude):
                 self._block_bwd(blk, dcur, self.dx16, dalt, self.dx16, self.dxc)
@@ -620,6 +628,8 @@ class TrainEngine:
         if not self.dense and self._param_stream is not None and hasattr(o, "param_stream"):
             torch.cuda.current_stream(self.device).wait_stream(self._param_stream)
             self._grad_ready("macro.d_gain", "macro.v", "macro.u", "macro.bias")
+            if not self.tr.disable_router_aux:
+                self._grad_ready(*self._router_grad_names())
         self._finish_backward()
 
     def _optimizer_step(self) -> None:

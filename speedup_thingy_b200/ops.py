@@ -280,6 +280,18 @@ class CudaOps:
         self._call("rte_router_aux_bwd", C.byref(sw), C.byref(so), _ptr(depth_values), lambda_load, lambda_depth,
                    _ptr(aux), C.byref(sg), _ptr(dh0), _ptr(scratch), B, S, d, hid, R, K, self.stream)
 
+    def router_aux_bwd_split(self, w: dict, fwd: dict, depth_values, lambda_load, lambda_depth, aux, grads: dict, dh0,
+                             scratch, *, B, S, d, hid, R, K):
+        """The same backward with the weight gradients on `param_stream` when one is set."""
+        sw, so = self._router_weights(w), self._router_out(fwd)
+        sg = A.RouterGrads()
+        for name, _ in A.RouterGrads._fields_:
+            setattr(sg, name, grads[name].data_ptr())
+        self._call("rte_router_aux_bwd_data", C.byref(sw), C.byref(so), _ptr(depth_values), lambda_load, lambda_depth,
+                   _ptr(aux), _ptr(dh0), _ptr(scratch), B, S, d, hid, R, K, self.stream)
+        with self._deferred():
+            self._call("rte_router_aux_bwd_params", C.byref(so), C.byref(sg), _ptr(scratch), B, d, hid, R, K, self.stream)
+
     def topk_lowest_index(self, scores, k: int, idx, vals=None) -> None:
         rows, n = scores.shape
         self._call("rte_topk_lowest_index", _ptr(scores), scores.stride(0), rows, n, k, _ptr(idx), _ptr(vals), self.stream)

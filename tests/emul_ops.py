@@ -271,6 +271,9 @@ class EmulOps:
             out["depth_id"].fill_(fixed_depth_id)
         out["depth"].copy_(depth_values[out["depth_id"].long()])
 
+    def router_aux_bwd_split(self, *args, **kw):
+        self.router_aux_bwd(*args, **kw)
+
     def router_aux_bwd(self, w, fwd, depth_values, lambda_load, lambda_depth, aux, grads, dh0, scratch, *, B, S, d, hid, R, K):
         self.launches += 1
         rp, dp = fwd["recipe_probs"], fwd["depth_probs"]
