@@ -116,7 +116,7 @@ phi_act_kernel(const float* __restrict__ h0, const float* __restrict__ rstd, con
 
 // MODE 0 (forward):  out = h + s_cfg*scale*tanh(gain*h + silu(act) @ u + bias)
 // MODE 1 (backward): dupd = dout*s_cfg*scale*(1 - tanh^2);  dh0 = dout + gain*dupd   (dupd -> scratch)
-template <int MODE>
+template <int MODE, int MP>
 __global__ void __launch_bounds__(NTHR)
 phi_out_kernel(const float* __restrict__ h0, const float* __restrict__ act, const float* __restrict__ gain,
                const float* __restrict__ u, const float* __restrict__ bias, const float* __restrict__ scale,
@@ -126,23 +126,24 @@ phi_out_kernel(const float* __restrict__ h0, const float* __restrict__ act, cons
   const int tiles = rte::ceil_div(D.S, TT);
   const int b = blockIdx.x / tiles, tok0 = (blockIdx.x % tiles) * TT;
   const size_t key = key_of(rid, sid, b, D.K);
-  for (int i = threadIdx.x; i < TT * D.m; i += NTHR) {
-    const int t = i / D.m, j = i % D.m, s = tok0 + t;
-    ssa[t][j] = (s < D.S) ? rte::silu_f(act[((size_t)b * D.S + s) * D.m + j]) : 0.f;
+  for (int i = threadIdx.x; i < TT * MP; i += NTHR) {           // columns past the rank are zero (they meet ur[j] = 0)
+    const int t = i / MP, j = i % MP, s = tok0 + t;
+    ssa[t][j] = (s < D.S && j < D.m) ? rte::silu_f(act[((size_t)b * D.S + s) * D.m + j]) : 0.f;
   }
   __syncthreads();
   const float* ub = u + key * D.m * D.d;
   for (int c = threadIdx.x; c < D.d; c += NTHR) {
-    float ur[MMAX];
+    float ur[MP];                 // MP = macro rank rounded up to 32 or 64
 #pragma unroll
-    for (int j = 0; j < MMAX; ++j) ur[j] = (j < D.m) ? ub[(size_t)j * D.d + c] : 0.f;
+    for (int j = 0; j < MP; ++j) ur[j] = (j < D.m) ? ub[(size_t)j * D.d + c] : 0.f;
     const float g = gain[key * D.d + c], bs = bias[key * D.d + c], sc = s_cfg * scale[key * D.d + c];
-    for (int t = 0; t < TT; ++t) {
+    const int t_end = min(TT, D.S - tok0);
+#pragma unroll 4
+    for (int t = 0; t < t_end; ++t) {
       const int s = tok0 + t;
-      if (s >= D.S) break;
       float low = 0.f;
 #pragma unroll
-      for (int j = 0; j < MMAX; ++j) low += ssa[t][j] * ur[j];
+      for (int j = 0; j < MP; ++j) low += ssa[t][j] * ur[j];
       const size_t idx = ((size_t)b * D.S + s) * D.d + c;
       const float h = h0[idx];
       const float th = tanhf(g * h + low + bs);
@@ -326,18 +327,29 @@ phi_dz_kernel(const float* __restrict__ h0, const float* __restrict__ rstd, cons
       sv3[c][j] = ok ? vb[(size_t)(2 * D.d + c0 + c) * D.m + j] : 0.f;
     }
     __syncthreads();
+    float a1[4][2], a3[4][2];
+#pragma unroll
+    for (int t = 0; t < 4; ++t) a1[t][0] = a1[t][1] = a3[t][0] = a3[t][1] = 0.f;
+#pragma unroll 4
+    for (int j = 0; j < D.m; ++j) {
+      const float w1a = sv1[lane][j], w1b = sv1[lane + 32][j], w3a = sv3[lane][j], w3b = sv3[lane + 32][j];
+#pragma unroll
+      for (int t = 0; t < 4; ++t) {
+        const float dv = sda[warp * 4 + t][j];
+        a1[t][0] += dv * w1a; a1[t][1] += dv * w1b;
+        a3[t][0] += dv * w3a; a3[t][1] += dv * w3b;
+      }
+    }
 #pragma unroll
     for (int q = 0; q < 2; ++q) {
       const int cl = lane + 32 * q, c = c0 + cl;
 #pragma unroll
       for (int t = 0; t < 4; ++t) {
         const int s = tok0 + warp * 4 + t;
-        float a1 = 0.f, a3 = 0.f;
-        for (int j = 0; j < D.m; ++j) { const float dv = sda[warp * 4 + t][j]; a1 += dv * sv1[cl][j]; a3 += dv * sv3[cl][j]; }
         if (s < D.S && c < D.d) {
           const size_t idx = ((size_t)b * D.S + s) * D.d + c;
-          const float dnv = a1 + dpool[(size_t)b * D.d + c];
-          dh0[idx] += a3;
+          const float dnv = a1[t][q] + dpool[(size_t)b * D.d + c];
+          dh0[idx] += a3[t][q];
           dot[t] += dnv * h0[idx] * rstd[(size_t)b * D.S + s];
         }
       }
@@ -354,6 +366,18 @@ phi_dz_kernel(const float* __restrict__ h0, const float* __restrict__ rstd, cons
       sv1[c][j] = (c0 + c < D.d) ? vb[(size_t)(c0 + c) * D.m + j] : 0.f;
     }
     __syncthreads();
+    float a1[4][2];
+#pragma unroll
+    for (int t = 0; t < 4; ++t) a1[t][0] = a1[t][1] = 0.f;
+#pragma unroll 4
+    for (int j = 0; j < D.m; ++j) {
+      const float w1a = sv1[lane][j], w1b = sv1[lane + 32][j];
+#pragma unroll
+      for (int t = 0; t < 4; ++t) {
+        const float dv = sda[warp * 4 + t][j];
+        a1[t][0] += dv * w1a; a1[t][1] += dv * w1b;
+      }
+    }
 #pragma unroll
     for (int q = 0; q < 2; ++q) {
       const int cl = lane + 32 * q, c = c0 + cl;
@@ -361,11 +385,9 @@ phi_dz_kernel(const float* __restrict__ h0, const float* __restrict__ rstd, cons
       for (int t = 0; t < 4; ++t) {
         const int s = tok0 + warp * 4 + t;
         if (s < D.S && c < D.d) {
-          float a1 = 0.f;
-          for (int j = 0; j < D.m; ++j) a1 += sda[warp * 4 + t][j] * sv1[cl][j];
           const size_t idx = ((size_t)b * D.S + s) * D.d + c;
           const float r = rstd[(size_t)b * D.S + s];
-          const float dnv = a1 + dpool[(size_t)b * D.d + c];
+          const float dnv = a1[t][q] + dpool[(size_t)b * D.d + c];
           dh0[idx] += r * (dnv - h0[idx] * r * dot[t]);
         }
       }
@@ -416,8 +438,12 @@ extern "C" int rte_macro_phi_fwd(const float* h0, const rte_phi_params* p, const
   RTE_LAUNCH_CHECK();
   phi_act_kernel<<<B * tiles, NTHR, 0, ST(stream)>>>(h0, rstd, pa, p->v, recipe_id, stride_id, act, D);
   RTE_LAUNCH_CHECK();
-  phi_out_kernel<0><<<B * tiles, NTHR, 0, ST(stream)>>>(h0, act, p->gain, p->u, p->bias, p->scale, recipe_id, stride_id,
-                                                        s_cfg, nullptr, out, nullptr, D);
+  if (m <= 32)
+    phi_out_kernel<0, 32><<<B * tiles, NTHR, 0, ST(stream)>>>(h0, act, p->gain, p->u, p->bias, p->scale, recipe_id, stride_id,
+                                                              s_cfg, nullptr, out, nullptr, D);
+  else
+    phi_out_kernel<0, 64><<<B * tiles, NTHR, 0, ST(stream)>>>(h0, act, p->gain, p->u, p->bias, p->scale, recipe_id, stride_id,
+                                                              s_cfg, nullptr, out, nullptr, D);
   RTE_LAUNCH_CHECK();
   return RTE_OK;
 }
@@ -450,8 +476,12 @@ extern "C" int rte_macro_phi_bwd_data(const float* h0, const float* dout, const 
   PhiDims D{B, S, d, m, K_strides};
   const int tiles = rte::ceil_div(S, TT);
   const PhiBwdScratch x = phi_scratch(scratch, B, S, d, m);
-  phi_out_kernel<1><<<B * tiles, NTHR, 0, ST(stream)>>>(h0, act, p->gain, p->u, p->bias, p->scale, recipe_id, stride_id,
-                                                        s_cfg, dout, dh0, x.dupd, D);
+  if (m <= 32)
+    phi_out_kernel<1, 32><<<B * tiles, NTHR, 0, ST(stream)>>>(h0, act, p->gain, p->u, p->bias, p->scale, recipe_id, stride_id,
+                                                              s_cfg, dout, dh0, x.dupd, D);
+  else
+    phi_out_kernel<1, 64><<<B * tiles, NTHR, 0, ST(stream)>>>(h0, act, p->gain, p->u, p->bias, p->scale, recipe_id, stride_id,
+                                                              s_cfg, dout, dh0, x.dupd, D);
   RTE_LAUNCH_CHECK();
   phi_da_kernel<<<B * tiles, NTHR, 0, ST(stream)>>>(x.dupd, act, p->u, recipe_id, stride_id, x.da, D);
   RTE_LAUNCH_CHECK();
