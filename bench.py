@@ -297,8 +297,8 @@ def main() -> None:
                        "global_batch": B * world, "seq_len": S, "parallelism": f"dp{world}",
                        "l2": "per-step working set (~1 GB of activations) exceeds the 126 MB L2; no explicit flush",
                        "timing": "CUDA events around K graph replays, max over ranks"},
-            "e2e": {"value": tokens * K / (ms_e2e / 1e3), "unit": "tokens/s", "h2d_bytes_per_step": 2 * B * S * 8,
-                    "d2h_bytes_per_step": 8 * 4 + B * 4},
+            "e2e": {"value": tokens * K / (ms_e2e / 1e3), "unit": "tokens/s", "h2d_bytes_per_step": 2 * B * S * 8 + (4 + B * 4 if eng.audit is not None else 0),
+                    "d2h_bytes_per_step": eng._results.numel() * 4 + 4},
             "gpu_launches": launches_timed,
             "clocks": clocks.summary(),
             "step_roofline": {"flops_per_token": step_flops_per_token(C3_MODEL),

@@ -66,6 +66,7 @@ class AuditReplay:
 
         self.eng, self.k = eng, k
         self._stage = None
+        self._prepared = None
         cfg, dev = eng.cfg, eng.device
         self.n, self.S, self.T = k, eng.S, cfg.t_max
         self.Ma = k * eng.S
@@ -128,21 +129,33 @@ class AuditReplay:
         self.ws_chain = e(16 * Ma * d)          # split-K partials of the chain's own few-row GEMMs
 
     # ------------------------------------------------------------------ host side, once per step
-    def choose(self, step_seed: int) -> None:
-        """Fixed-count sampler: first k entries of a seeded CPU permutation (audit.py:99-116); writes the subset
-        indices and the control-variate weights of the hot rows."""
+    def prepare(self, step_seed: int) -> None:
+        """Host half of `choose` for a coming step: the seeded permutation and the control-variate weights, written to
+        a pinned staging pair (two pairs alternate, so the pair a queued copy may still read is never rewritten)."""
         eng = self.eng
-        gen = torch.Generator().manual_seed(step_seed)
-        chosen = torch.sort(torch.randperm(eng.B, generator=gen)[: self.k]).values
         if self._stage is None:
             pin = eng.device.type == "cuda"
-            self._stage = (torch.empty(self.k, dtype=torch.int32, pin_memory=pin),
-                           torch.empty(eng.B, dtype=torch.float32, pin_memory=pin))
-        h_idx, h_rw = self._stage
+            self._stage = [(torch.empty(self.k, dtype=torch.int32, pin_memory=pin),
+                            torch.empty(eng.B, dtype=torch.float32, pin_memory=pin)) for _ in range(2)]
+            self._stage_next = 0
+        gen = torch.Generator().manual_seed(step_seed)
+        chosen = torch.sort(torch.randperm(eng.B, generator=gen)[: self.k]).values
+        h_idx, h_rw = self._stage[self._stage_next]
         w0 = 1.0 / (eng.B * eng.S * eng.world)
         h_idx.copy_(chosen)
         h_rw.fill_(w0)
         h_rw[chosen] = w0 * (1.0 - 1.0 / self.p_inc)                     # d corrected / d hot on audited samples
+        self._prepared = (step_seed, chosen, h_idx, h_rw)
+        self._stage_next ^= 1
+
+    def choose(self, step_seed: int) -> None:
+        """Fixed-count sampler: first k entries of a seeded CPU permutation (audit.py:99-116); writes the subset
+        indices and the control-variate weights of the hot rows."""
+        eng = self.eng
+        if self._prepared is None or self._prepared[0] != step_seed:
+            self.prepare(step_seed)
+        _, chosen, h_idx, h_rw = self._prepared
+        self._prepared = None
         self.idx.copy_(h_idx, non_blocking=True)
         eng.row_weight.copy_(h_rw, non_blocking=True)
         self.last_chosen = chosen

@@ -268,8 +268,13 @@ class TrainEngine:
             self.blocks = self.prelude + self.coda
         self.hidden16, self.rstd_f = e(M, d, dtype=bf), e(M)
         self.logits = e(M, V, dtype=bf)
-        self.loss_tok, self.loss_per_sample = e(M), e(B)
-        self.scalars = torch.zeros(8, dtype=f32, device=dev)   # [0]=sum loss, [1]=aux load, [2]=aux depth, [3]=sumsq, [4]=clip
+        # Everything the host reads back after a step lives in ONE buffer, so that it is one device-to-host copy:
+        #   scalars[8] | loss_per_sample[B] | recipe_id[B] (int32) | audit terms[k,4] | audit exact_loss[k] | kl_sum[1]
+        k_a = self.audit_k or 0
+        self._results = torch.zeros(8 + 2 * B + 5 * k_a + 1, dtype=f32, device=dev)
+        self.loss_tok = e(M)
+        self.scalars = self._results[0:8]                      # [0]=sum loss, [1]=aux load, [2]=aux depth, [3]=sumsq, [4]=clip
+        self.loss_per_sample = self._results[8:8 + B]
         self.row_weight = torch.full((B,), 1.0 / (B * S * self.world), dtype=f32, device=dev)
         # backward temporaries
         self.tmp = _Temps(M, cfg, dev)
@@ -291,7 +296,7 @@ class TrainEngine:
             i32 = torch.int32
             self.route = dict(pooled=e(B, d), r_hidden_pre=e(B, hid), d_hidden_pre=e(B, hid), recipe_logits=e(B, r),
                               recipe_probs=e(B, r), depth_probs=e(B, k), expected_depth=e(B), router_entropy=e(B),
-                              recipe_id=e(B, dtype=i32), recipe_id_by_pass=e(B, cfg.t_max, dtype=i32),
+                              recipe_id=self._results[8 + B:8 + 2 * B].view(i32), recipe_id_by_pass=e(B, cfg.t_max, dtype=i32),
                               depth_id=e(B, dtype=i32), depth=e(B, dtype=i32))
             self.router_scratch = e(A.ROUTER_MAX_R + B * (2 * hid + r + k + A.ROUTER_DPOOLED_PARTS * d) + 4)
         if self.shortlist:
@@ -317,6 +322,10 @@ class TrainEngine:
         if self.audit_k:
             from .audit import AuditReplay
             self.audit = AuditReplay(self, self.audit_k)
+            r0, k_a = 8 + 2 * B, self.audit_k
+            self.audit.terms = self._results[r0:r0 + 4 * k_a].view(k_a, 4)
+            self.audit.exact_loss = self._results[r0 + 4 * k_a:r0 + 5 * k_a]
+            self.audit.kl_sum = self._results[r0 + 5 * k_a:r0 + 5 * k_a + 1]
         for n, sh in self.shadow.items():
             ops.cast_bf16(self.params[n], sh)
         if hasattr(ops, "rope_table"):
@@ -692,23 +701,24 @@ class TrainEngine:
     def _fetch_results(self) -> dict[str, torch.Tensor]:
         """One device-to-host round trip for everything the host reads after a step: the copies are queued into
         pinned buffers behind the step's kernels and a single stream synchronisation waits for all of them."""
+        B, k_a = self.B, self.audit_k or 0
         if self._host is None:
             pin = self.device.type == "cuda"
-            mk = lambda t: torch.empty(t.shape, dtype=t.dtype, pin_memory=pin)  # noqa: E731
-            src = {"scalars": self.scalars, "loss_per_sample": self.loss_per_sample}
-            if hasattr(self.ops, "status"):
-                src["status"] = self.ops.status
-            if not self.dense:
-                src["recipe_id"] = self.route["recipe_id"]
-            if self.audit is not None:
-                src.update(terms=self.audit.terms, exact_loss=self.audit.exact_loss, kl_sum=self.audit.kl_sum)
-            self._host_src = src
-            self._host = {k: mk(v) for k, v in src.items()}
-        for k, v in self._host_src.items():
-            self._host[k].copy_(v, non_blocking=True)
+            self._host_flat = torch.empty(self._results.shape, dtype=torch.float32, pin_memory=pin)
+            self._host_status = torch.zeros(1, dtype=torch.int32, pin_memory=pin)
+            h, r0 = self._host_flat, 8 + 2 * B
+            self._host = {"scalars": h[0:8], "loss_per_sample": h[8:8 + B], "recipe_id": h[8 + B:8 + 2 * B].view(torch.int32),
+                          "terms": h[r0:r0 + 4 * k_a].view(k_a, 4), "exact_loss": h[r0 + 4 * k_a:r0 + 5 * k_a],
+                          "kl_sum": h[r0 + 5 * k_a:r0 + 5 * k_a + 1]}
+        self._host_flat.copy_(self._results, non_blocking=True)
+        if hasattr(self.ops, "status"):
+            self._host_status.copy_(self.ops.status, non_blocking=True)
+        if self.audit is not None:
+            # host work for the NEXT step (the seeded permutation of its audited subset) while the device finishes this one
+            self.audit.prepare(self.tr.seed + 10_000 + self.global_step + 1)
         if self.device.type == "cuda":
             torch.cuda.current_stream(self.device).synchronize()
-        if "status" in self._host and int(self._host["status"][0]) != 0:
+        if int(self._host_status[0]) != 0:
             self.ops.check_status()                          # raises with the decoded device status
         return self._host
 
