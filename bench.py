@@ -312,8 +312,8 @@ def main() -> None:
                                 "kernel": "gemm_tcgen05_kernel", "launches_per_step": roof["launches"],
                                 "gemm_ms_per_step": roof["gemm_ms_per_step"],
                                 "timing": "event-record nodes around each launch inside a captured step",
-                                "scope": "hot-pass launches (main stream); the audit replay's launches overlap them on a "
-                                         "side stream and are listed under side_stream",
+                                "scope": "hot-pass launches (main stream + its weight-gradient stream); the audit replay's "
+                                         "few-row launches overlap them on their own streams and are listed under side_stream",
                                 "per_shape": roof["per_shape"], "side_stream": roof.get("side_stream")}
         if world == 1 and not args.no_cpu_baseline:
             threads = os.cpu_count() or 1

@@ -339,7 +339,9 @@ class AuditReplay:
         eng = self.eng
         o, n, S, d = eng.ops, self.n, self.S, eng.cfg.d_model
         lo, hi = self.shared_range
-        o.add_(eng.grad_flat[lo:hi], self.shared_flat)
+        import contextlib
+        with (o._deferred() if hasattr(o, "_deferred") else contextlib.nullcontext()):
+            o.add_(eng.grad_flat[lo:hi], self.shared_flat)
         o.add_(eng.grads["embed.weight"], self.g_embed)
         o.scatter_add_rows(dh0_hot, self.idx, self.dh0_acc, n, S * d)
         o.scatter_add_rows(dh0_hot, self.idx, self.dh_first, n, S * d)

@@ -278,9 +278,21 @@ class TrainEngine:
         self.row_weight = torch.full((B,), 1.0 / (B * S * self.world), dtype=f32, device=dev)
         # backward temporaries
         self.tmp = _Temps(M, cfg, dev)
+        # Weight-gradient launches of the hot pass run on their own stream beside the data-gradient chain (they fill the
+        # SMs that attention / norm / macro-operator kernels leave idle).  What they read must then outlive the chain's
+        # reuse of scratch: every block gets its own scratch set and its own bf16 input-gradient buffer.
+        self._hot_param_stream = torch.cuda.Stream(device=dev) if (dev.type == "cuda" and hasattr(ops, "param_stream")) else None
+        n_blocks = len(self.blocks) if self.dense else cfg.n_prelude + cfg.n_coda
+        if self._hot_param_stream is not None:
+            self.block_tmps = [self.tmp] + [_Temps(M, cfg, dev) for _ in range(n_blocks - 1)]
+            self.grad16 = [self.tmp.dx16] + [torch.empty(M, d, dtype=bf, device=dev) for _ in range(n_blocks + 1)]
+        else:
+            self.block_tmps = [self.tmp] * n_blocks
+            self.grad16 = [self.tmp.dx16] * (n_blocks + 2)
         t_ = self.tmp
         self.dug, self.dn16, self.dy16, self.dx16, self.dqkv = t_.dug, t_.dn16, t_.dy16, t_.dx16, t_.dqkv
         self.dxa, self.dxb, self.dxc, self.partial = t_.dxa, t_.dxb, t_.dxc, t_.partial
+        self.partial_final = torch.empty_like(self.partial)     # the final norm's column partials (its reduction is deferred too)
         self.gn_partial = e(self.plan.total_chunks)
         max_ws = 0
         for (mm, nn) in ((3 * d, d), (d, d), (2 * cfg.d_ff, d), (d, cfg.d_ff), (V, d)):
@@ -380,6 +392,8 @@ class TrainEngine:
                     dist.all_reduce(view, op=dist.ReduceOp.SUM, group=self.pg)
                 else:
                     self._comm_stream.wait_stream(torch.cuda.current_stream(self.device))
+                    if self._hot_param_stream is not None:       # weight gradients are produced there
+                        self._comm_stream.wait_stream(self._hot_param_stream)
                     with torch.cuda.stream(self._comm_stream):
                         dist.all_reduce(view, op=dist.ReduceOp.SUM, group=self.pg)
 
@@ -570,16 +584,26 @@ class TrainEngine:
         dlogits = self.logits
         o.gemm(dlogits, sh["embed.weight"], self.dn16, M=M, N=d, K=V, b_mn=True)
         o.gemm_wgrad(dlogits, self.hidden16, g["embed.weight"], M=V, N=d, K=M)
-        o.rmsnorm_bwd(x_last, p["final_norm.weight"], self.rstd_f, self.dn16, None, self.dxa, self.dx16,
-                      g["final_norm.weight"], self.partial)
+        hot = self._hot_param_stream
+
+        def defer(on: bool) -> None:        # weight-gradient launches of the hot pass -> their own stream
+            if hot is not None:
+                o.param_stream = hot if on else None
+
+        g16 = self.grad16
+        defer(True)
+        o.rmsnorm_bwd(x_last, p["final_norm.weight"], self.rstd_f, self.dn16, None, self.dxa, g16[0],
+                      g["final_norm.weight"], self.partial_final)
         audited = self.audit is not None
         if not audited:
             self._grad_ready("final_norm.weight")
         dcur, dalt = self.dxa, self.dxb
         tail = self.coda if not self.dense else self.blocks
         for i, blk in enumerate(reversed(tail)):
-            self._block_bwd(blk, dcur, self.dx16, dalt, self.dx16, self.dxc, mark_ready=not audited)
+            self._block_bwd(blk, dcur, g16[i], dalt, g16[i + 1], self.dxc, tmp=self.block_tmps[i], mark_ready=not audited)
             dcur, dalt = dalt, dcur
+        defer(False)
+        n_tail = len(tail)
         if audited:
             # distillation gradient on the hot endpoint of the audited samples, then the replay's own
             # logits / final-norm / coda backward (their weight gradients add to the hot pass's)
@@ -587,9 +611,9 @@ class TrainEngine:
         if not self.dense:
             # Phi backward writes dh0 into `dalt`; the router's auxiliary losses add their share
             # (its parameter-gradient half goes to the parameter-gradient stream: backward only waits for dh0)
-            split = self._param_stream is not None and hasattr(o, "param_stream")
+            split = hot is not None
             if split:
-                o.param_stream = self._param_stream
+                o.param_stream = hot
             o.macro_phi_bwd_split(self.prelude[-1].out if self.prelude else self.x0, dcur, self._phi_param_dict(),
                                   self.route["recipe_id"], self.route["depth_id"], cfg.macro_update_scale, self.phi_rstd,
                                   self.phi_pooled, self.phi_act, dalt,
@@ -605,7 +629,9 @@ class TrainEngine:
                 from .audit import CORE_PARAMS
                 # join: the replay's backward ran beside the hot backward; fold its results in
                 self._main_wait_side()
+                defer(True)                 # its add into the coda gradients follows the hot pass's own weight gradients
                 self.audit.merge(dcur)
+                defer(False)
                 self._grad_ready("final_norm.weight")
                 for blk in reversed(self.coda):
                     pre = blk.prefix
@@ -620,7 +646,7 @@ class TrainEngine:
                 # under data parallelism each rank evaluates the auxiliary losses on its own shard and
                 # contributes 1/world of their gradient (the cross-entropy part is exactly the global mean)
                 if split:
-                    o.param_stream = self._param_stream
+                    o.param_stream = hot
                 o.router_aux_bwd_split(self._router_weight_dict(), self.route, self.depth_values, tr.lambda_load / self.world,
                                        tr.lambda_depth / self.world, self.scalars[1:3], rg, dcur, self.router_scratch, B=B,
                                        S=S, d=d, hid=cfg.router_hidden_dim, R=cfg.recipe_count, K=len(cfg.depth_choices))
@@ -628,17 +654,20 @@ class TrainEngine:
                     o.param_stream = None
                 else:
                     self._grad_ready(*self._router_grad_names())
-            o.cast_bf16(dcur, self.dx16)
-            for blk in reversed(self.prelude):
-                self._block_bwd(blk, dcur, self.dx16, dalt, self.dx16, self.dxc)
+            o.cast_bf16(dcur, g16[n_tail])
+            defer(True)
+            for j, blk in enumerate(reversed(self.prelude)):
+                self._block_bwd(blk, dcur, g16[n_tail + j], dalt, g16[n_tail + j + 1], self.dxc, tmp=self.block_tmps[n_tail + j])
                 dcur, dalt = dalt, dcur
+            defer(False)
         o.embed_bwd(tokens, dcur, g["embed.weight"])
         self._grad_ready("embed.weight")
-        if not self.dense and self._param_stream is not None and hasattr(o, "param_stream"):
-            torch.cuda.current_stream(self.device).wait_stream(self._param_stream)
-            self._grad_ready("macro.d_gain", "macro.v", "macro.u", "macro.bias")
-            if not self.tr.disable_router_aux:
-                self._grad_ready(*self._router_grad_names())
+        if hot is not None:
+            torch.cuda.current_stream(self.device).wait_stream(hot)
+            if not self.dense:
+                self._grad_ready("macro.d_gain", "macro.v", "macro.u", "macro.bias")
+                if not self.tr.disable_router_aux:
+                    self._grad_ready(*self._router_grad_names())
         self._finish_backward()
 
     def _optimizer_step(self) -> None:
@@ -769,7 +798,7 @@ class TrainEngine:
         """Device-side duration of every C-ABI call of one step, measured INSIDE a CUDA graph (event-record
         nodes around each call), so that host launch latency does not leak into the numbers.  Returns
         (entry point + shape tag, microseconds) in launch order, averaged over `repeats` replays; calls issued on
-        the audit replay's side stream carry the suffix "@side"."""
+        the hot pass's weight-gradient stream carry the suffix "@wgrad", those of the audit replay's streams "@side"."""
         ops = self.ops
         calls: list[tuple[str, Any, Any]] = []
         orig_call, orig_gemm = ops._call, ops.gemm
@@ -782,7 +811,9 @@ class TrainEngine:
             e0.record(st)
             orig_call(name, *args)
             e1.record(st)
-            calls.append((name + tag["v"] + ("" if st.cuda_stream == main_stream else "@side"), e0, e1))
+            hot_ps = self._hot_param_stream.cuda_stream if self._hot_param_stream is not None else None
+            where = "" if st.cuda_stream == main_stream else ("@wgrad" if st.cuda_stream == hot_ps else "@side")
+            calls.append((name + tag["v"] + where, e0, e1))
 
         def tagged_gemm(a, b, out, **kw):
             tag["v"] = f"[{kw['M']}x{kw['N']}x{kw['K']}/epi{kw.get('epilogue', 0)}" + (f"/split{kw['splits']}" if kw.get("splits", 1) > 1 else "") + "]"
@@ -821,16 +852,16 @@ class TrainEngine:
         """Relates the algorithmic 2*M*N*K FLOPs of every tcgen05 GEMM launch of one step to its device
         duration, taken from event-record nodes around each launch inside a captured step (`profile_step`),
         i.e. under the same cache state and stream concurrency as the timed step and without host gaps.  The
-        headline figures cover the hot pass (main stream); the audit replay's small GEMMs, which run beside it on
-        a side stream, are reported under "side_stream"."""
+        headline figures cover the hot pass (main stream and its weight-gradient stream); the audit replay's
+        few-row GEMMs, which run beside it on their own streams, are reported under "side_stream"."""
         import re
         acc = {"": [0.0, 0.0, 0, {}], "@side": [0.0, 0.0, 0, {}]}      # flops, us, launches, per shape
         for name, t in self.profile_step(repeats):
-            m = re.match(r"rte_gemm_bf16\[(\d+)x(\d+)x(\d+)/(.*)\](@side)?$", name)
+            m = re.match(r"rte_gemm_bf16\[(\d+)x(\d+)x(\d+)/(.*)\](@side|@wgrad)?$", name)
             if not m:
                 continue
             f = 2.0 * int(m.group(1)) * int(m.group(2)) * int(m.group(3))
-            a = acc[m.group(5) or ""]
+            a = acc["@side" if m.group(5) == "@side" else ""]       # the hot pass = main stream + its weight-gradient stream
             a[0], a[1], a[2] = a[0] + f, a[1] + t, a[2] + 1
             sh = a[3].setdefault(f"{m.group(1)}x{m.group(2)}x{m.group(3)}/{m.group(4)}", [0.0, 0.0, 0])
             sh[0] += f
