@@ -244,8 +244,11 @@ bwd_kernel(const __nv_bfloat16* __restrict__ qkv, int ld, int sec, const __nv_bf
   __nv_bfloat16* dbase = dqkv + (size_t)b * S * ld + h * HD;
   const int row_a = r0 + g, row_b = r0 + g + 8;
 
+  // With few (sample, head) pairs the launch is split in two along z: one CTA per sweep, half the latency.
+  const int only = gridDim.z == 2 ? (int)blockIdx.z : -1;
+
   // ---- sweep 1: dQ of query rows r0 .. r0+15 over key blocks j <= r0/16
-  {
+  if (only != 1) {
     uint32_t qf[HD / 16][4], dof[HD / 16][4];
     load_a_frags<HD>(sq, r0, g, t, qf);
     load_a_frags<HD>(sdo, r0, g, t, dof);
@@ -288,7 +291,7 @@ bwd_kernel(const __nv_bfloat16* __restrict__ qkv, int ld, int sec, const __nv_bf
   }
 
   // ---- sweep 2: dK, dV of key rows r0 .. r0+15 over query blocks j >= r0/16
-  {
+  if (only != 0) {
     uint32_t kf[HD / 16][4], vf[HD / 16][4];
     load_a_frags<HD>(sk, r0, g, t, kf);
     load_a_frags<HD>(sv, r0, g, t, vf);
@@ -371,7 +374,8 @@ int launch_bwd(const void* qkv, int ld, int sec, const void* y, const void* dy, 
     if (cudaFuncSetAttribute(bwd_kernel<HD, SMAX>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess) return RTE_ERR_LAUNCH;
     set = true;
   }
-  bwd_kernel<HD, SMAX><<<dim3(B * H, rte::ceil_div(S, QB)), NTHR, smem, st>>>(
+  const int ctas = B * H * rte::ceil_div(S, QB);
+  bwd_kernel<HD, SMAX><<<dim3(B * H, rte::ceil_div(S, QB), ctas < 148 ? 2 : 1), NTHR, smem, st>>>(
       reinterpret_cast<const __nv_bfloat16*>(qkv), ld, sec, reinterpret_cast<const __nv_bfloat16*>(y),
       reinterpret_cast<const __nv_bfloat16*>(dy), ldy, lse, reinterpret_cast<__nv_bfloat16*>(dqkv), rope, S, H);
   RTE_LAUNCH_CHECK();

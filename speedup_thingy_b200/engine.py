@@ -856,8 +856,15 @@ class TrainEngine:
         few-row GEMMs, which run beside it on their own streams, are reported under "side_stream"."""
         import re
         acc = {"": [0.0, 0.0, 0, {}], "@side": [0.0, 0.0, 0, {}]}      # flops, us, launches, per shape
-        for name, t in self.profile_step(repeats):
-            m = re.match(r"rte_gemm_bf16\[(\d+)x(\d+)x(\d+)/(.*)\](@side|@wgrad)?$", name)
+        # the hot pass's weight-gradient GEMMs normally overlap its other kernels on their own stream, which would
+        # stretch every overlapping launch's event interval: for this measurement they run in line on the main stream
+        keep, self._hot_param_stream = self._hot_param_stream, None
+        try:
+            profile = self.profile_step(repeats)
+        finally:
+            self._hot_param_stream = keep
+        for name, t in profile:
+            m = re.match(r"rte_gemm_bf16(?:_small)?\[(\d+)x(\d+)x(\d+)/(.*)\](@side|@wgrad)?$", name)
             if not m:
                 continue
             f = 2.0 * int(m.group(1)) * int(m.group(2)) * int(m.group(3))
