@@ -105,6 +105,9 @@ class TrainingConfig:
     fixed_depth: int | None = None
     disable_router_aux: bool = False
     strict_cuda: bool = True
+    target_speedup_vs_dense: float | None = None
+    max_active_param_equiv_per_token: float | None = None
+    max_hotpath_flops_per_token: float | None = None
 
     def __post_init__(self) -> None:
         if self.mode not in ("recursive_macro", "recursive_macro_shortlist", "dense_exact"):
@@ -116,6 +119,9 @@ class TrainingConfig:
             raise NotImplementedError("the sm_100a path computes in bf16 with fp32 master weights (precision='bf16')")
         if self.audit_fixed_count_per_batch is not None and self.audit_fixed_count_per_batch > self.batch_size:
             raise ValueError("audit_fixed_count_per_batch must be <= batch_size")
+        for name in ("target_speedup_vs_dense", "max_active_param_equiv_per_token", "max_hotpath_flops_per_token"):
+            if getattr(self, name) is not None and getattr(self, name) <= 0:
+                raise ValueError(f"{name} must be positive")
 
     def lr_for(self, group: str) -> float:
         """Per-group learning rates (reference training.py:302-339)."""

@@ -98,6 +98,38 @@ def lr_group_of(name: str, topology: str) -> str:
     raise KeyError(name)
 
 
+# --------------------------------------------------------------------------- hot-path budget (host arithmetic)
+def dense_block_param_count(cfg: ModelConfig) -> int:
+    """metrics.py:12-14."""
+    d = cfg.d_model
+    return 4 * d * d + 3 * d * cfg.d_ff + 4 * d
+
+
+def dense_aligned_param_count(cfg: ModelConfig) -> int:
+    """Parameters of the dense model of the same width and depth (metrics.py:17-23,75-76; tied embeddings)."""
+    return cfg.vocab_size * cfg.d_model + cfg.n_dense_layers * dense_block_param_count(cfg) + cfg.d_model
+
+
+def hot_budget(cfg: ModelConfig, tr: TrainingConfig, shortlist_size: int | None) -> dict[str, float]:
+    """training.py:707-740 with metrics.py:69-94: parameter-equivalents and FLOPs one token touches on the hot path
+    (prelude + coda blocks, one macro operator, the output rows it scores); raises when a configured budget is exceeded."""
+    d = cfg.d_model
+    active = float((cfg.n_prelude + cfg.n_coda) * dense_block_param_count(cfg)
+                   + d + 3 * d * cfg.macro_rank + cfg.macro_rank * d + d
+                   + (cfg.vocab_size if shortlist_size is None else float(shortlist_size)) * d)
+    flops = 2.0 * active
+    limit = tr.max_active_param_equiv_per_token
+    if tr.target_speedup_vs_dense is not None:
+        target = dense_aligned_param_count(cfg) / tr.target_speedup_vs_dense
+        limit = target if limit is None else min(limit, target)
+    if limit is not None and active > limit:
+        raise RuntimeError(f"recursive hot path exceeds active parameter budget: {active:.1f} > {limit:.1f}")
+    if tr.max_hotpath_flops_per_token is not None and flops > tr.max_hotpath_flops_per_token:
+        raise RuntimeError(f"recursive hot path exceeds FLOPs/token budget: {flops:.1f} > {tr.max_hotpath_flops_per_token:.1f}")
+    return {"active_param_equiv_per_token": active, "hotpath_flops_per_token_est": flops,
+            "active_param_budget": limit if limit is not None else 0.0}
+
+
 # --------------------------------------------------------------------------- results
 @dataclass
 class TrainStepResult:
@@ -342,6 +374,8 @@ class TrainEngine:
             ops.cast_bf16(self.params[n], sh)
         if hasattr(ops, "rope_table"):
             ops.rope_table(S, cfg.head_dim)          # built once, before any stream capture
+        # the hot-path budget depends on the configuration only: checked once, before anything runs (training.py:1389-1392)
+        self._budget = {} if self.dense else hot_budget(cfg, tr, self.oc.shortlist_max_tokens if self.shortlist else None)
         self._graph = None
         self._host: dict[str, torch.Tensor] | None = None
         self._launches_per_step: int | None = None
@@ -775,6 +809,7 @@ class TrainEngine:
             counts = torch.bincount(ids, minlength=self.cfg.recipe_count).float()
             self.usage_ema.mul_(self.tr.coverage_beta).add_(counts / counts.sum().clamp_min(1.0), alpha=1.0 - self.tr.coverage_beta)
             metrics["unique_recipes_per_batch"] = int(ids.unique().numel())
+            metrics.update(self._budget)
         self.global_step += 1
         self.tokens_seen += self.B * self.S
         metrics["tokens_seen"] = self.tokens_seen

@@ -152,6 +152,12 @@ def per_op_vectors() -> dict[str, np.ndarray]:
         p.grad = grads[i].clone()
         opt.step()
     out["adamw_p"] = p.detach().numpy().copy()
+    # hot-path budget estimators (metrics.py:69-94) on BASELINE config 1
+    from recursive_training_engine import metrics as RM
+    mc = reference_experiment(GOLDEN_CASES["c1_macro"], tempfile.gettempdir()).model
+    out["budget"] = np.array([RM.estimate_hot_active_param_equiv_per_token(mc, shortlist_size=None, include_output=True),
+                              RM.estimate_hot_active_param_equiv_per_token(mc, shortlist_size=128, include_output=True),
+                              float(RM.dense_aligned_param_count(mc))], dtype=np.float64)
     return out
 
 

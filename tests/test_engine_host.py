@@ -111,3 +111,27 @@ def test_engine_sequence_matches_oracle(name):
     untouched = [n for n, _ in parameter_shapes(cfg.model, cfg.output.num_clusters) if n not in eng.trainable]
     for n in untouched:
         assert torch.equal(eng.params[n], params[n]), n
+
+
+def test_hot_budget_matches_reference_estimators_and_enforces_limits():
+    """training.py:707-740 / metrics.py:69-94, pinned to values the reference computed for BASELINE config 1."""
+    from pathlib import Path
+
+    from speedup_thingy_b200.engine import dense_aligned_param_count, hot_budget
+    from tests.golden.cases import GOLDEN_CASES
+    gold = np.load(Path(__file__).resolve().parent / "golden" / "per_op.npz")["budget"]
+    case = GOLDEN_CASES["c1_macro"]
+    model = ModelConfig(**{k: v for k, v in case["model"].items() if k != "shortlist_clusters"})
+    tr = TrainingConfig(**{**case["train"], "audit_fixed_count_per_batch": None})
+    assert hot_budget(model, tr, None)["active_param_equiv_per_token"] == gold[0]
+    assert hot_budget(model, tr, 128)["active_param_equiv_per_token"] == gold[1]
+    assert hot_budget(model, tr, None)["hotpath_flops_per_token_est"] == 2.0 * gold[0]
+    assert float(dense_aligned_param_count(model)) == gold[2]
+    with pytest.raises(RuntimeError, match="active parameter budget"):
+        hot_budget(model, TrainingConfig(**{**tr.__dict__, "max_active_param_equiv_per_token": gold[0] - 1}), None)
+    with pytest.raises(RuntimeError, match="FLOPs/token budget"):
+        hot_budget(model, TrainingConfig(**{**tr.__dict__, "max_hotpath_flops_per_token": gold[0]}), None)
+    with pytest.raises(RuntimeError, match="active parameter budget"):
+        hot_budget(model, TrainingConfig(**{**tr.__dict__, "target_speedup_vs_dense": 1e6}), None)
+    ok = hot_budget(model, TrainingConfig(**{**tr.__dict__, "target_speedup_vs_dense": 1.01}), None)
+    assert ok["active_param_budget"] == gold[2] / 1.01
