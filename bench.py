@@ -76,9 +76,14 @@ class ClockSampler:
             except subprocess.TimeoutExpired:
                 self.proc.kill()
 
+    def mark(self) -> None:
+        """Only samples taken from now on count (the sampler is started early so that nvidia-smi's start-up time does
+        not eat a short timed region)."""
+        self.first = len(self.rows)
+
     def summary(self) -> dict:
         sm, mx, reasons = [], 0.0, set()
-        for r in self.rows:
+        for r in self.rows[getattr(self, "first", 0):]:
             try:
                 sm.append(float(r[0]))
                 mx = max(mx, float(r[1]))
@@ -240,6 +245,7 @@ def main() -> None:
         host_batches.append((x, y))
 
     W, K = max(args.warmup, 3), args.steps
+    clocks = ClockSampler(local).__enter__()          # running before the timed region; see ClockSampler.mark
     for i in range(W):
         eng.train_step(host_batches[i % n_batches])
     for i in range(8):          # data parallel: the first steps run eagerly (NCCL set-up); capture before timing
@@ -257,7 +263,8 @@ def main() -> None:
     eng._load_batch(host_batches[0])
     barrier()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    with ClockSampler(local) as clocks:
+    clocks.mark()
+    try:
         l0 = eng.ops.launches
         e0.record()
         for _ in range(K):
@@ -274,10 +281,17 @@ def main() -> None:
             eng.train_step(host_batches[i % n_batches])
         torch.cuda.synchronize()
         ms_e2e = (time.perf_counter() - t0) * 1e3
-    if dist is not None:
-        t = torch.tensor([ms_dev, ms_e2e], device=dev)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        ms_dev, ms_e2e = float(t[0]), float(t[1])
+        if dist is not None:
+            t = torch.tensor([ms_dev, ms_e2e], device=dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms_dev, ms_e2e = float(t[0]), float(t[1])
+        # The two timed loops may be shorter than nvidia-smi's sampling period: keep the same step running (untimed)
+        # for about half a second so that a few clock samples under this load exist (same count on every rank).
+        for i in range(max(1, min(400, int(500.0 / max(ms_e2e / K, 0.1))))):
+            eng.train_step(host_batches[i % n_batches])
+        torch.cuda.synchronize()
+    finally:
+        clocks.__exit__(None, None, None)
     eng.ops.check_status()
 
     # ---- roofline of the dominant kernel (the tcgen05 GEMM): CUDA-event nodes around every launch of a captured step
