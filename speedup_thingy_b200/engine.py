@@ -256,6 +256,8 @@ class TrainEngine:
         self._bucket_of: dict[str, int] = {}
         self._bucket_pending: list[int] = []
         self._bucket_size: list[int] = []
+        import os as _os
+        bucket_cap_mb = float(_os.environ.get("RTE_BUCKET_MB", bucket_cap_mb))
         cap = max(int(bucket_cap_mb * 1024 * 1024 / 4), 1)
         start = 0
         for n in order:
@@ -656,8 +658,8 @@ class TrainEngine:
                                   K=len(cfg.depth_choices))
             if split:
                 o.param_stream = None
-            else:
-                self._grad_ready("macro.d_gain", "macro.v", "macro.u", "macro.bias")
+            # (the communication stream waits for the weight-gradient stream too, so marking here is safe)
+            self._grad_ready("macro.d_gain", "macro.v", "macro.u", "macro.bias")
             dcur, dalt = dalt, dcur
             if audited:
                 from .audit import CORE_PARAMS
@@ -686,8 +688,7 @@ class TrainEngine:
                                        S=S, d=d, hid=cfg.router_hidden_dim, R=cfg.recipe_count, K=len(cfg.depth_choices))
                 if split:
                     o.param_stream = None
-                else:
-                    self._grad_ready(*self._router_grad_names())
+                self._grad_ready(*self._router_grad_names())
             o.cast_bf16(dcur, g16[n_tail])
             defer(True)
             for j, blk in enumerate(reversed(self.prelude)):
@@ -698,10 +699,6 @@ class TrainEngine:
         self._grad_ready("embed.weight")
         if hot is not None:
             torch.cuda.current_stream(self.device).wait_stream(hot)
-            if not self.dense:
-                self._grad_ready("macro.d_gain", "macro.v", "macro.u", "macro.bias")
-                if not self.tr.disable_router_aux:
-                    self._grad_ready(*self._router_grad_names())
         self._finish_backward()
 
     def _optimizer_step(self) -> None:
