@@ -652,6 +652,21 @@ def macro_step_loss(p: dict, cfg: ModelCfg, tr: TrainCfg, tokens: torch.Tensor, 
     return loss, info
 
 
+def exact_step_loss(p: dict, cfg: ModelCfg, tr: TrainCfg, tokens: torch.Tensor, targets: torch.Tensor,
+                    usage_ema: torch.Tensor) -> tuple[torch.Tensor, dict]:
+    """training.py:771-797 (`recursive_exact`): prelude -> router -> t_max banked passes for every sample -> coda ->
+    cross entropy, plus the router's auxiliary losses (models.py:202-228, 416-512)."""
+    h0 = p["embed.weight"][tokens]
+    for i in range(cfg.n_prelude):
+        h0 = dense_block(p, f"prelude.{i}", h0, cfg.n_heads)
+    route = router_forward(p, cfg, h0, tr.fixed_recipe, tr.fixed_depth)
+    out = exact_from_h0(p, cfg, h0, targets, route)
+    aux_router = router_aux_losses(tr, route["recipe_probs"], route["expected_depth"], usage_ema)
+    loss = out["loss_per_sample"].mean() / float(targets.shape[1]) + sum(aux_router.values())
+    out.update(route=route, h0=h0)
+    return loss, dict(hot=out, aux_router=aux_router)
+
+
 def dense_step_loss(p: dict, cfg: ModelCfg, tokens: torch.Tensor, targets: torch.Tensor) -> tuple[torch.Tensor, dict]:
     """training.py:742-769."""
     out = forward_dense(p, cfg, tokens, targets)
@@ -699,6 +714,8 @@ class OracleTrainer:
         leaves = {k: v.detach().clone().requires_grad_(True) for k, v in self.params.items()}
         if self.cfg.topology == "dense":
             loss, info = dense_step_loss(leaves, self.cfg, tokens, targets)
+        elif self.tr.mode == "recursive_exact":
+            loss, info = exact_step_loss(leaves, self.cfg, self.tr, tokens, targets, self.usage_ema)
         else:
             loss, info = macro_step_loss(leaves, self.cfg, self.tr, tokens, targets, self.global_step, self.usage_ema,
                                          self.oc, self.top_clusters)

@@ -61,7 +61,9 @@ CORE_SHADOWED = ["core.attn.wqkv", "core.attn.wo", "core.mlp.wug", "core.mlp.wd"
 class AuditReplay:
     """Buffers and launch sequences of the replay; owned by ``TrainEngine`` (``eng``)."""
 
-    def __init__(self, eng, k: int):
+    def __init__(self, eng, k: int, direct_grads: bool = False):
+        """`direct_grads`: write the gradients of final norm / coda / embedding straight into the engine's buffers
+        (the `recursive_exact` mode, where no hot pass shares them) instead of a private mirror."""
         from .engine import _Block, _Temps
 
         self.eng, self.k = eng, k
@@ -124,7 +126,10 @@ class AuditReplay:
                          .view(eng.params[nm].shape) for nm in names}
         self.g_embed = e(*eng.params["embed.weight"].shape)
         self.g_shared["embed.weight"] = self.g_embed
-        big = max(V * d, 2 * f * d, 3 * d * d)
+        if direct_grads:
+            self.g_shared = eng.grads
+        big = max(eng.ops.pick_splits(mm, nn, Ma) * mm * nn
+                  for mm, nn in ((V, d), (2 * f, d), (d, 2 * f), (3 * d, d), (d, 3 * d), (d, d), (f, d), (d, f)))
         self.ws = e(big)
         self.ws_chain = e(16 * Ma * d)          # split-K partials of the chain's own few-row GEMMs
 

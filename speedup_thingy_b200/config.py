@@ -110,9 +110,9 @@ class TrainingConfig:
     max_hotpath_flops_per_token: float | None = None
 
     def __post_init__(self) -> None:
-        if self.mode not in ("recursive_macro", "recursive_macro_shortlist", "dense_exact"):
-            raise NotImplementedError("rte_b200 implements modes recursive_macro, recursive_macro_shortlist and "
-                                      f"dense_exact, not {self.mode!r}")
+        if self.mode not in ("recursive_macro", "recursive_macro_shortlist", "recursive_exact", "dense_exact"):
+            raise NotImplementedError("rte_b200 implements modes recursive_macro, recursive_macro_shortlist, "
+                                      f"recursive_exact and dense_exact, not {self.mode!r}")
         if self.loss_normalization != "token_mean":
             raise NotImplementedError("only loss_normalization='token_mean'")
         if self.precision != "bf16":

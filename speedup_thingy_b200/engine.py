@@ -208,7 +208,10 @@ class TrainEngine:
         self.oc = config.output
         self.shortlist = tr.mode == "recursive_macro_shortlist"
         self.n_clusters = self.oc.num_clusters
+        self.exact = tr.mode == "recursive_exact"       # every sample runs the banked recurrent core (training.py:771-797)
         self.audit_k = int(tr.audit_fixed_count_per_batch or 0)
+        if self.exact and (self.audit_k or self.dense):
+            raise ValueError("recursive_exact: recursive topology, no audit (the whole batch is exact)")
         if self.audit_k:
             if self.dense:
                 raise ValueError("the exact audit belongs to the recursive model")
@@ -234,10 +237,11 @@ class TrainEngine:
         if self.dense:
             self.trainable = names
         else:
-            self.trainable = [n for n in names if n.startswith(("embed.", "prelude.", "macro.", "coda.", "final_norm."))]
+            used = ("embed.", "prelude.", "coda.", "final_norm.") + (() if self.exact else ("macro.",))
+            self.trainable = [n for n in names if n.startswith(used)]
             if not tr.disable_router_aux:
                 self.trainable += [n for n in names if n.startswith(("router.recipe_mlp.", "router.depth_mlp."))]
-            if self.audit_k:
+            if self.audit_k or self.exact:
                 from .audit import CORE_PARAMS
                 self.trainable += CORE_PARAMS
         # gradients live in one flat buffer, laid out in the order the backward pass completes them, so that
@@ -277,7 +281,7 @@ class TrainEngine:
         for n in names:
             if n == "embed.weight" or n.endswith((".attn.wqkv.weight", ".attn.wo.weight", ".mlp.wug.weight", ".mlp.wd.weight")):
                 self.shadow[n] = torch.empty_like(self.params[n], dtype=bf)
-        if self.audit_k:
+        if self.audit_k or self.exact:
             from .audit import CORE_SHADOWED
             for n in CORE_SHADOWED:
                 self.shadow[n] = torch.empty_like(self.params[n], dtype=bf)
@@ -364,7 +368,12 @@ class TrainEngine:
         self._side_stream = torch.cuda.Stream(device=dev, priority=-1) if (self.audit_k and dev.type == "cuda") else None
         if self._side_stream is not None and hasattr(ops, "gemm_max_ctas"):
             ops.gemm_max_ctas = max(ops.sm_count - 8, 1)
-        self._param_stream = torch.cuda.Stream(device=dev) if (not self.dense and dev.type == "cuda") else None
+        self._param_stream = torch.cuda.Stream(device=dev) if (self.audit_k and dev.type == "cuda") else None
+        self.exact_core = None
+        if self.exact:
+            from .audit import AuditReplay
+            self.exact_core = AuditReplay(self, B, direct_grads=True)         # the replay machinery over the whole batch
+            self.exact_core.idx.copy_(torch.arange(B, dtype=torch.int32))
         if self.audit_k:
             from .audit import AuditReplay
             self.audit = AuditReplay(self, self.audit_k)
@@ -377,7 +386,7 @@ class TrainEngine:
         if hasattr(ops, "rope_table"):
             ops.rope_table(S, cfg.head_dim)          # built once, before any stream capture
         # the hot-path budget depends on the configuration only: checked once, before anything runs (training.py:1389-1392)
-        self._budget = {} if self.dense else hot_budget(cfg, tr, self.oc.shortlist_max_tokens if self.shortlist else None)
+        self._budget = {} if (self.dense or self.exact) else hot_budget(cfg, tr, self.oc.shortlist_max_tokens if self.shortlist else None)
         self._graph = None
         self._host: dict[str, torch.Tensor] | None = None
         self._launches_per_step: int | None = None
@@ -398,8 +407,9 @@ class TrainEngine:
         else:
             for i in reversed(range(cfg.n_coda)):
                 order += block(f"coda.{i}")
-            order += ["macro.d_gain", "macro.v", "macro.u", "macro.bias"]
-            if self.audit_k:
+            if not self.exact:
+                order += ["macro.d_gain", "macro.v", "macro.u", "macro.bias"]
+            if self.audit_k or self.exact:
                 from .audit import CORE_PARAMS
                 order += CORE_PARAMS
             if not self.tr.disable_router_aux:
@@ -546,7 +556,48 @@ class TrainEngine:
         ready(f"{pre}.norm1.weight")
 
     # ------------------------------------------------------------------ forward + backward
+    def _forward_backward_exact(self) -> None:
+        """`recursive_exact`: embed -> prelude -> router -> t_max banked passes for every sample -> coda -> logits ->
+        cross entropy (models.py:202-228, 416-512), then the same chain backwards; one stream."""
+        o, cfg, p, g, tr, a = self.ops, self.cfg, self.params, self.grads, self.tr, self.exact_core
+        M, d, B, S = self.M, cfg.d_model, self.B, self.S
+        tokens = self.tokens.view(-1)
+        o.embed_fwd(tokens, p["embed.weight"], self.x0)
+        x = self.x0
+        for blk in self.prelude:
+            x = self._block_fwd(blk, x)
+        h0 = x
+        fixed_depth_id = None if tr.fixed_depth is None else list(cfg.depth_choices).index(tr.fixed_depth)
+        o.router_fwd(h0, self._router_weight_dict(), self.depth_values, self.route, B=B, S=S, d=d,
+                     hid=cfg.router_hidden_dim, R=cfg.recipe_count, K=len(cfg.depth_choices), T=cfg.t_max,
+                     fixed_recipe=tr.fixed_recipe, fixed_depth_id=fixed_depth_id)
+        a.forward_replay(h0)
+        o.ce_fwd_bwd(a.logits, a.targets_a, a.row_weight_a, S, a.loss_tok, a.logits)
+        o.segment_sum(a.loss_tok, self.loss_per_sample, B, S)
+        o.segment_sum(self.loss_per_sample, self.scalars[0:1], 1, B)
+        # ---------------- backward
+        self._begin_backward()
+        a.backward_core(a.backward_head())
+        dcur, dalt = a.dh0_acc, self.dxb
+        o.add_(dcur, a.dh_first)                          # d h0 = through the alpha*h0 injections + through h[0]
+        if not tr.disable_router_aux:
+            rg = {f"{m_[0]}_{k_}": g[f"router.{m_}.{i_}.{w_}"] for m_ in ("recipe_mlp", "depth_mlp")
+                  for i_, w_, k_ in ((0, "weight", "w0"), (0, "bias", "b0"), (2, "weight", "w2"), (2, "bias", "b2"))}
+            o.router_aux_bwd(self._router_weight_dict(), self.route, self.depth_values, tr.lambda_load / self.world,
+                             tr.lambda_depth / self.world, self.scalars[1:3], rg, dcur, self.router_scratch, B=B, S=S,
+                             d=d, hid=cfg.router_hidden_dim, R=cfg.recipe_count, K=len(cfg.depth_choices))
+        g16 = self.grad16
+        o.cast_bf16(dcur, g16[0])
+        for j, blk in enumerate(reversed(self.prelude)):
+            self._block_bwd(blk, dcur, g16[j], dalt, g16[j + 1], self.dxc, tmp=self.block_tmps[j], mark_ready=False)
+            dcur, dalt = dalt, dcur
+        o.embed_bwd(tokens, dcur, g["embed.weight"])
+        self._grad_ready(*self.trainable)
+        self._finish_backward()
+
     def _forward_backward(self) -> None:
+        if self.exact:
+            return self._forward_backward_exact()
         o, cfg, p, sh, g, tr = self.ops, self.cfg, self.params, self.shadow, self.grads, self.tr
         M, d, V, B, S = self.M, cfg.d_model, cfg.vocab_size, self.B, self.S
         tokens, targets = self.tokens.view(-1), self.targets.view(-1)

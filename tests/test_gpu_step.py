@@ -102,6 +102,32 @@ def test_shortlist_loss_curve_matches_reference_golden():
     assert rel.max() <= 1e-2, (rel.max(), losses, gold["losses"])
 
 
+def test_recursive_exact_loss_curve_matches_reference_golden():
+    """`recursive_exact` (every sample through the banked recurrent core, two banks, router-chosen depth) against
+    the loss curve the reference produced."""
+    case = GOLDEN_CASES["small_exact"]
+    cfg, params, eng = _engine(case["model"], case["train"])
+    gold = np.load(GOLDEN / "small_exact.npz")["losses"]
+    it = _stream(cfg, case["steps"])
+    losses = np.array([eng.train_step(next(it)).loss for _ in range(case["steps"])])
+    rel = np.abs(losses - gold) / np.abs(gold)
+    assert rel.max() <= 1e-2, (rel.max(), losses, gold)
+    for n in ("macro.v", "macro.u"):                      # the macro operator is not on this path: untouched
+        assert torch.equal(eng.params[n].cpu(), params[n])
+
+
+def test_recursive_exact_at_c3_shapes_runs_and_learns():
+    model = dict(vocab_size=2048, d_model=512, n_heads=8, d_ff=2048, n_prelude=1, n_coda=1, t_max=4, depth_choices=(1, 2, 4),
+                 attn_banks=1, ffn_banks=1, head_groups=8, ffn_groups=16, active_head_groups=4, active_ffn_groups=4,
+                 recipe_count=5, macro_rank=32)
+    train = dict(mode="recursive_exact", lr=1e-3, weight_decay=0.1, batch_size=32, seq_len=64, seed=0, fixed_depth=4)
+    cfg, params, eng = _engine(model, train)
+    it = _stream(cfg, 6)
+    losses = [eng.train_step(next(it)).loss for _ in range(6)]
+    assert all(np.isfinite(losses)) and losses[-1] < losses[0]
+    eng.ops.check_status()
+
+
 def test_graph_replay_equals_eager():
     model, train = CASES["macro_routed_clip"]
     cfg, params, eager = _engine(model, train, use_cuda_graph=False)
