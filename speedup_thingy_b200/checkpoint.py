@@ -1,0 +1,106 @@
+"""Checkpoints in the reference's on-disk format (training.py:1656-1701): a ``torch.save`` payload with the model
+``state_dict`` under the reference's parameter names, a ``torch.optim.AdamW`` ``state_dict`` laid out like the
+reference's parameter groups (training.py:302-339: embedding, prelude, core, macro, coda + final norm, router), and
+the step counters -- so a run can move between the reference and this engine in either direction.
+"""
+from __future__ import annotations
+
+from pathlib import Path
+
+import torch
+
+from .engine import TrainEngine
+
+
+def optimizer_layout(engine: TrainEngine) -> list[tuple[str, list[str]]]:
+    """(group name, parameter names) in the order the reference builds its optimizer; parameters no group owns
+    (the shortlist head's cluster router) are left out exactly as there."""
+    names = list(engine.params)
+    if engine.dense:
+        return [("dense", names)]
+    pick = lambda *prefixes: [n for n in names if n.startswith(prefixes)]  # noqa: E731
+    groups = [("embedding", pick("embed.")), ("prelude", pick("prelude.")), ("core", pick("core.")),
+              ("macro", pick("macro.")), ("coda", pick("coda.") + pick("final_norm.")), ("router", pick("router."))]
+    return [(g, p) for g, p in groups if p]
+
+
+def optimizer_state_dict(engine: TrainEngine) -> dict:
+    """The AdamW state as ``torch.optim.AdamW(...).state_dict()`` would give it for the reference's groups: only
+    parameters that have taken a step carry state (``step``, ``exp_avg``, ``exp_avg_sq``)."""
+    tr = engine.tr
+    layout = optimizer_layout(engine)
+    cpu_params = {n: torch.nn.Parameter(torch.empty(0)) for _, ps in layout for n in ps}
+    groups = []
+    for gname, ps in layout:
+        lr = tr.lr_for(gname if gname != "dense" else "dense")
+        groups.append({"params": [cpu_params[n] for n in ps], "lr": lr, "base_lr": lr, "name": gname})
+    opt = torch.optim.AdamW(groups, weight_decay=tr.weight_decay, foreach=True)
+    steps = engine.plan.step_count.to("cpu")
+    slot = {n: i for i, n in enumerate(engine.trainable)}
+    for n, p in cpu_params.items():
+        if n in slot and int(steps[slot[n]]) > 0:
+            opt.state[p] = {"step": torch.tensor(float(steps[slot[n]])), "exp_avg": engine.exp_avg[n].detach().to("cpu").clone(),
+                            "exp_avg_sq": engine.exp_avg_sq[n].detach().to("cpu").clone()}
+    return opt.state_dict()
+
+
+def save_checkpoint(engine: TrainEngine, path: str | Path, *, data_cursor: int | None = None) -> None:
+    model = {n: t.detach().to("cpu").clone() for n, t in engine.params.items()}
+    if not engine.dense:
+        # the reference model's two persistent buffers (macro.py:99-122): the per-key update scale the macro kernels
+        # read, and the teacher statistic only the reference's distillation tooling writes
+        model["macro.update_scale"] = engine.macro_scale.detach().to("cpu").clone()
+        model["macro.teacher_delta_rms"] = engine.macro_teacher_delta_rms.clone()
+    payload = {"config": engine.config, "model": model,
+               "optimizer": optimizer_state_dict(engine), "global_step": engine.global_step,
+               "global_micro_step": engine.global_step, "tokens_seen": engine.tokens_seen, "audit": {},
+               "aligned_lm_phase": "aligned_lm", "data_cursor": data_cursor, "usage_ema": engine.usage_ema.clone(),
+               "torch_rng_state": torch.get_rng_state()}
+    p = Path(path)
+    p.parent.mkdir(parents=True, exist_ok=True)
+    torch.save(payload, p)
+
+
+def load_checkpoint(engine: TrainEngine, path: str | Path) -> int | None:
+    """Loads a checkpoint written by `save_checkpoint` or by the reference's ``TrainEngine.save_checkpoint``.
+    Returns the data cursor.  State of parameters this mode does not train is ignored, as is any buffer of the
+    reference model that is not a parameter here."""
+    payload = torch.load(path, map_location="cpu", weights_only=False)
+    model = payload.get("model") or {}
+    missing = [n for n in engine.params if n not in model]
+    if missing:
+        raise KeyError(f"checkpoint lacks parameters: {missing[:4]}{' ...' if len(missing) > 4 else ''}")
+    for n, t in engine.params.items():
+        if tuple(model[n].shape) != tuple(t.shape):
+            raise ValueError(f"{n}: checkpoint shape {tuple(model[n].shape)} != {tuple(t.shape)}")
+        t.copy_(model[n].to(t.dtype))
+    for n, sh in engine.shadow.items():
+        engine.ops.cast_bf16(engine.params[n], sh)
+    if not engine.dense:
+        if "macro.update_scale" in model:
+            engine.macro_scale.copy_(model["macro.update_scale"].to(engine.macro_scale.dtype))
+        if "macro.teacher_delta_rms" in model:
+            engine.macro_teacher_delta_rms.copy_(model["macro.teacher_delta_rms"])
+    opt = payload.get("optimizer")
+    steps = torch.zeros_like(engine.plan.step_count, device="cpu")
+    for n in engine.trainable:
+        engine.exp_avg[n].zero_()
+        engine.exp_avg_sq[n].zero_()
+    if opt is not None:
+        order = [n for _, ps in optimizer_layout(engine) for n in ps]
+        saved = [i for g in opt["param_groups"] for i in g["params"]]
+        if len(saved) == len(order):                     # same grouping: indices line up with our parameter order
+            slot = {n: i for i, n in enumerate(engine.trainable)}
+            for idx, n in zip(saved, order):
+                st = opt["state"].get(idx)
+                if st is not None and n in slot:
+                    engine.exp_avg[n].copy_(st["exp_avg"])
+                    engine.exp_avg_sq[n].copy_(st["exp_avg_sq"])
+                    steps[slot[n]] = int(float(st["step"]))
+        # a different grouping (e.g. a macro-only optimizer): weights load, the optimizer starts fresh (training.py:1683-1689)
+    engine.plan.step_count.copy_(steps)
+    engine.global_step = int(payload.get("global_step", 0))
+    engine.tokens_seen = int(payload.get("tokens_seen", 0))
+    if isinstance(payload.get("usage_ema"), torch.Tensor) and payload["usage_ema"].shape == engine.usage_ema.shape:
+        engine.usage_ema.copy_(payload["usage_ema"])
+    return payload.get("data_cursor")

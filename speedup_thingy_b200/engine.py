@@ -342,6 +342,7 @@ class TrainEngine:
             self.phi_rstd, self.phi_pooled, self.phi_act = e(M), e(B * d + B * m), e(M, m)
             self.phi_scratch = e(ops.phi_bwd_scratch_floats(B, S, d, m))
             self.macro_scale = torch.ones(r, k, d, dtype=f32, device=dev)   # `update_scale` buffer (macro.py:99-108)
+            self.macro_teacher_delta_rms = torch.zeros(r, k)               # carried through checkpoints only (macro.py:122)
             self.depth_values = torch.tensor(list(cfg.depth_choices), dtype=torch.int32, device=dev)
             i32 = torch.int32
             self.route = dict(pooled=e(B, d), r_hidden_pre=e(B, hid), d_hidden_pre=e(B, hid), recipe_logits=e(B, r),

@@ -1,0 +1,97 @@
+"""Checkpoints move between the reference and the engine in both directions (reference format:
+training.py:1656-1701).  Needs the reference sources, which exist only in the build container: skipped elsewhere."""
+import os
+import sys
+from pathlib import Path
+
+import pytest
+import torch
+
+REF_SRC = os.environ.get("RTE_REFERENCE_SRC", "/root/reference/src")
+pytestmark = pytest.mark.skipif(not Path(REF_SRC, "recursive_training_engine").is_dir(),
+                                reason="reference sources not present")
+
+from oracle import rte_oracle as O  # noqa: E402
+from speedup_thingy_b200.checkpoint import load_checkpoint, optimizer_layout, save_checkpoint  # noqa: E402
+from speedup_thingy_b200.config import ExperimentConfig, ModelConfig, TrainingConfig  # noqa: E402
+from speedup_thingy_b200.engine import TrainEngine, init_parameters  # noqa: E402
+from tests.emul_ops import EmulOps  # noqa: E402
+from tests.golden.cases import GOLDEN_CASES  # noqa: E402
+
+
+def _reference_engine(case, run_dir):
+    sys.path.insert(0, REF_SRC)
+    from tests.golden.make_golden import load_oracle_init_into_reference, reference_experiment
+    from recursive_training_engine.training import TrainEngine as RefEngine
+    from tests.golden.cases import oracle_cfgs
+    ref = RefEngine(reference_experiment(case, run_dir), device=torch.device("cpu"))
+    load_oracle_init_into_reference(ref, oracle_cfgs(case)[0], seed=case["train"]["seed"])
+    return ref
+
+
+def _engine(case):
+    model = {k: v for k, v in case["model"].items() if k != "shortlist_clusters"}
+    cfg = ExperimentConfig(ModelConfig(**model), TrainingConfig(**case["train"]))
+    params = init_parameters(cfg.model, seed=cfg.training.seed)
+    return cfg, TrainEngine(cfg, params, device="cpu", ops=EmulOps(), use_cuda_graph=False)
+
+
+def _batches(cfg, n):
+    tr = cfg.training
+    toks = O.zipf_tokens(tr.batch_size * tr.seq_len * (n + 1) + 1, cfg.model.vocab_size, seed=tr.seed)
+    it = O.batches(toks, tr.batch_size, tr.seq_len)
+    return [next(it) for _ in range(n)]
+
+
+def test_engine_checkpoint_loads_into_the_reference_and_training_continues(tmp_path):
+    case = GOLDEN_CASES["small_routed"]
+    cfg, eng = _engine(case)
+    batches = _batches(cfg, 3)
+    for b in batches[:2]:
+        eng.train_step(b)
+    save_checkpoint(eng, tmp_path / "engine.pt", data_cursor=17)
+    ref = _reference_engine(case, str(tmp_path))
+    assert ref.load_checkpoint(tmp_path / "engine.pt") == 17
+    assert ref.global_step == 2 and ref.tokens_seen == eng.tokens_seen
+    ref_params = dict(ref.recursive_model.named_parameters())
+    for n, t in eng.params.items():
+        assert torch.equal(ref_params[n].detach(), t), n
+    # optimizer: the reference's groups line up with the layout, and stepped parameters carry the engine's moments
+    layout = [n for _, ps in optimizer_layout(eng) for n in ps]
+    ref_order = [p for g in ref.optimizer.param_groups for p in g["params"]]
+    assert len(layout) == len(ref_order)
+    by_id = {id(p): n for n, p in ref_params.items()}
+    assert [by_id[id(p)] for p in ref_order] == layout
+    for p in ref_order:
+        n = by_id[id(p)]
+        if n in eng.trainable:
+            st = ref.optimizer.state[p]
+            assert float(st["step"]) == 2.0 and torch.equal(st["exp_avg"], eng.exp_avg[n]), n
+        else:
+            assert p not in ref.optimizer.state or not ref.optimizer.state[p]
+    # one more step on each side from the same state
+    a = eng.train_step(batches[2]).loss
+    b = float(ref.train_step(batches[2]).loss)
+    assert abs(a - b) <= 1e-2 * abs(b), (a, b)
+
+
+def test_reference_checkpoint_loads_into_the_engine(tmp_path):
+    case = GOLDEN_CASES["small_routed"]
+    cfg, eng = _engine(case)
+    ref = _reference_engine(case, str(tmp_path))
+    batches = _batches(cfg, 3)
+    for b in batches[:2]:
+        ref.train_step(b)
+    ref.save_checkpoint(tmp_path / "reference.pt", data_cursor=5)
+    assert load_checkpoint(eng, tmp_path / "reference.pt") == 5
+    assert eng.global_step == 2
+    for n, p in ref.recursive_model.named_parameters():
+        assert torch.equal(eng.params[n], p.detach()), n
+    stepped = {n for n, p in ref.recursive_model.named_parameters() if ref.optimizer.state.get(p)}
+    assert stepped == set(eng.trainable)
+    for n, p in ref.recursive_model.named_parameters():
+        if n in eng.trainable:
+            assert torch.equal(eng.exp_avg_sq[n], ref.optimizer.state[p]["exp_avg_sq"]), n
+    a = eng.train_step(batches[2]).loss
+    b = float(ref.train_step(batches[2]).loss)
+    assert abs(a - b) <= 1e-2 * abs(b), (a, b)

@@ -128,6 +128,26 @@ def test_recursive_exact_at_c3_shapes_runs_and_learns():
     eng.ops.check_status()
 
 
+def test_checkpoint_round_trip_resumes_the_same_run(tmp_path):
+    """Reference-format checkpoint (training.py:1656-1701) written by one engine and read by a fresh one: weights,
+    Adam moments and step counters carry over, so both continue with the same losses."""
+    from speedup_thingy_b200.checkpoint import load_checkpoint, save_checkpoint
+    model, train = CASES["macro_routed_clip"]
+    cfg, params, a = _engine(model, train)
+    it = _stream(cfg, 6)
+    batches = [next(it) for _ in range(5)]
+    for b in batches[:3]:
+        a.train_step(b)
+    save_checkpoint(a, tmp_path / "ck.pt", data_cursor=3)
+    _, _, b_eng = _engine(model, {**train, "seed": train["seed"] + 1})          # different initial weights
+    assert load_checkpoint(b_eng, tmp_path / "ck.pt") == 3 and b_eng.global_step == 3
+    for n in a.params:
+        assert torch.equal(a.params[n], b_eng.params[n]), n
+    for batch in batches[3:]:
+        la, lb = a.train_step(batch).loss, b_eng.train_step(batch).loss
+        assert abs(la - lb) <= 1e-4 * abs(la), (la, lb)
+
+
 def test_graph_replay_equals_eager():
     model, train = CASES["macro_routed_clip"]
     cfg, params, eager = _engine(model, train, use_cuda_graph=False)
