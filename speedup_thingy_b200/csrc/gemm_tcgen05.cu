@@ -3,8 +3,9 @@
 //   operands staged by TMA into 128B-swizzled shared memory, MMAs issued by one
 //   thread with tcgen05.mma (M=128, N=BN, K=16 per instruction).
 //
-// Roles per CTA (192 threads): warp 0 = TMA producer, warp 1 = TMEM owner + MMA
-// issuer, warps 2..5 = epilogue (each reads its 32-lane TMEM quadrant).  Two
+// Roles per CTA (320 threads): warp 0 = TMA producer, warp 1 = TMEM owner + MMA
+// issuer, warps 2..9 = two epilogue groups of four warps (each warp reads its 32-lane
+// TMEM quadrant; the groups split a tile's columns).  Two
 // accumulator buffers in TMEM let the epilogue of tile i overlap the main loop of
 // tile i+1.  Every wait is bounded: on expiry the role records a code in the
 // caller's status word and all roles drain to the common teardown, which frees TMEM.
@@ -22,7 +23,7 @@ namespace {
 constexpr int BM = 128;         // rows of C per tile (TMEM lanes)
 constexpr int BK = 64;          // bf16 elements per k-block (= one 128-byte swizzle row)
 constexpr int UMMA_K = 16;      // K per tcgen05.mma for 16-bit inputs
-constexpr int NUM_THREADS = 192;
+constexpr int NUM_THREADS = 320;   // warp 0 producer, warp 1 MMA issuer, warps 2..9 two epilogue groups of four
 constexpr uint32_t WAIT_LIMIT = 24u * 1000u * 1000u;   // polls (with back-off) before a wait gives up
 
 struct KParams {
@@ -89,7 +90,7 @@ __device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.comm
 template <int N>
 __device__ __forceinline__ void bulk_wait_read() { asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory"); }
 __device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
-__device__ __forceinline__ void epi_barrier() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
+__device__ __forceinline__ void epi_barrier(int group) { asm volatile("bar.sync %0, 128;" ::"r"(group + 1) : "memory"); }
 __device__ __forceinline__ void st_shared_v4(uint32_t addr, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
   asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
 }
@@ -243,7 +244,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
-    for (int b = 0; b < 2; ++b) { mbar_init(tfull_bar(b), 1); mbar_init(tempty_bar(b), 4); }
+    for (int b = 0; b < 2; ++b) { mbar_init(tfull_bar(b), 1); mbar_init(tempty_bar(b), 8); }
     fence_barrier_init();
     prefetch_tmap(&tmap_a);
     prefetch_tmap(&tmap_b);
@@ -353,42 +354,50 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
       }
     }
   } else {
-    // ---------------- epilogue (warps 2..5) ----------------
+    // ---------------- epilogue (warps 2..9: two groups of four warps) ----------------
+    // A warp may read the TMEM lane quadrant (warp % 4); each group of four consecutive warps covers all 128 rows.
+    // The groups split a tile's columns between them (BN=256: group 0 takes [0,128), group 1 [128,256)), so two
+    // 32-column slices are converted and staged at the same time.
     const int quad = warp & 3;               // TMEM lane quadrant this warp may read
+    const int grp = (warp - 2) >> 2;         // 0 or 1
     int acc = 0; uint32_t acc_phase = 0; bool ok = true;
     if (p.tma_store) {
-      // Each 32-column slice of the accumulator becomes one "store job": the 128 epilogue threads write their rows
-      // into a swizzled staging buffer, one thread hands the buffer to the TMA (which clips rows/columns beyond
-      // M/N), and a small ring of buffers keeps several stores in flight.  One named barrier per job.
-      const uint32_t staging = smem_base + L::STAGING_OFFSET;
-      const bool issuer = (warp == 2 && lane == 0);
+      // Each 32-column slice of the accumulator becomes one "store job": the group's 128 threads write their rows
+      // into a swizzled staging slot, one thread hands the slot to the TMA (which clips rows/columns beyond M/N).
+      // Per group: two 8 KB slots for 16-bit outputs, one 16 KB slot for 32-bit outputs.  Before a slot is
+      // rewritten the store that last used it must have finished reading it (barrier A), and all rows must be in
+      // place before the store is issued (barrier B).
+      const uint32_t staging = smem_base + L::STAGING_OFFSET + uint32_t(grp) * 16384u;
+      const bool issuer = (((warp - 2) & 3) == 0 && lane == 0);
       const int r = quad * 32 + lane;        // row of the tile this thread owns
       uint32_t job = 0;
-      // 16-bit outputs: 64-byte rows, ring of 4;  32-bit outputs: 128-byte rows, ring of 2
       auto emit16 = [&](const CUtensorMap* map, int x, int y, const float (&v)[32]) {
-        const uint32_t base = staging + (job & 3u) * 8192u + uint32_t(r) * 64u;
+        const uint32_t slot = staging + (job & 1u) * 8192u;
+        if (issuer) bulk_wait_read<1>();
+        epi_barrier(grp);
+        const uint32_t base = slot + uint32_t(r) * 64u;
         const uint32_t sw = (uint32_t(r) >> 1) & 3u;
 #pragma unroll
         for (uint32_t c = 0; c < 4; ++c)
           st_shared_v4(base + ((c ^ sw) << 4), rte::pack_bf16x2(v[8 * c], v[8 * c + 1]), rte::pack_bf16x2(v[8 * c + 2], v[8 * c + 3]),
                        rte::pack_bf16x2(v[8 * c + 4], v[8 * c + 5]), rte::pack_bf16x2(v[8 * c + 6], v[8 * c + 7]));
         fence_proxy_async();
-        if (issuer) bulk_wait_read<2>();
-        epi_barrier();
-        if (issuer) { tma_store_3d(map, staging + (job & 3u) * 8192u, x, y, 0); bulk_commit(); }
+        epi_barrier(grp);
+        if (issuer) { tma_store_3d(map, slot, x, y, 0); bulk_commit(); }
         ++job;
       };
       auto emit32 = [&](const CUtensorMap* map, int x, int y, int z, const float (&v)[32]) {
-        const uint32_t base = staging + (job & 1u) * 16384u + uint32_t(r) * 128u;
+        if (issuer) bulk_wait_read<0>();
+        epi_barrier(grp);
+        const uint32_t base = staging + uint32_t(r) * 128u;
         const uint32_t sw = uint32_t(r) & 7u;
 #pragma unroll
         for (uint32_t c = 0; c < 8; ++c)
           st_shared_v4(base + ((c ^ sw) << 4), __float_as_uint(v[4 * c]), __float_as_uint(v[4 * c + 1]),
                        __float_as_uint(v[4 * c + 2]), __float_as_uint(v[4 * c + 3]));
         fence_proxy_async();
-        if (issuer) bulk_wait_read<0>();
-        epi_barrier();
-        if (issuer) { tma_store_3d(map, staging + (job & 1u) * 16384u, x, y, z); bulk_commit(); }
+        epi_barrier(grp);
+        if (issuer) { tma_store_3d(map, staging, x, y, z); bulk_commit(); }
         ++job;
       };
       for (int w = blockIdx.x; w < total_work && ok; w += gridDim.x) {
@@ -405,19 +414,20 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
         const int row = m0 + r;
         const bool row_ok = row < p.M;
         const uint32_t t_row = tmem_base + (uint32_t(quad * 32) << 16) + acc * BN;
-        // TMEM reads queue behind the MMAs already issued for the next tile, so their latency is long: fetch four
-        // 32-column slices (128 columns) per wait instead of one.
-        uint32_t raw[4][32];
+        // two 32-column slices per TMEM wait
+        uint32_t raw[2][32];
         float v[32];
         if (p.epilogue == RTE_EPI_BF16 || p.epilogue == RTE_EPI_F32 || p.epilogue == RTE_EPI_SWIGLU_BWD) {
-          for (int cg = 0; cg < BN / 128; ++cg) {
-            if (n0 + cg * 128 >= p.N) break;
+          constexpr int HALF = BN / 2;                       // columns per group
+          for (int s2 = 0; s2 < HALF / 64; ++s2) {
+            const int cbase = grp * HALF + s2 * 64;          // column offset inside the tile
+            if (n0 + cbase >= p.N) break;
 #pragma unroll
-            for (int q = 0; q < 4; ++q) tmem_ld32(t_row + cg * 128 + q * 32, raw[q]);
+            for (int q = 0; q < 2; ++q) tmem_ld32(t_row + cbase + q * 32, raw[q]);
             tmem_ld_wait();
 #pragma unroll
-            for (int q = 0; q < 4; ++q) {
-              const int col = n0 + cg * 128 + q * 32;
+            for (int q = 0; q < 2; ++q) {
+              const int col = n0 + cbase + q * 32;
               if (col < p.N) {
                 if (p.epilogue == RTE_EPI_BF16) {
 #pragma unroll
@@ -456,32 +466,25 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
               }
             }
           }
-        } else {  // RTE_EPI_SWIGLU_FWD: two (up, gate) slice pairs per wait
+        } else {  // RTE_EPI_SWIGLU_FWD: the tile holds BN/2 (up, gate) column pairs; each group takes half of them
           const int j0 = nblk * (BN / 2);
-          for (int cg = 0; cg < BN / 128; ++cg) {
-            if (j0 + cg * 64 >= p.pair_off) break;
-#pragma unroll
-            for (int q = 0; q < 2; ++q) {
-              tmem_ld32(t_row + cg * 64 + q * 32, raw[2 * q]);
-              tmem_ld32(t_row + BN / 2 + cg * 64 + q * 32, raw[2 * q + 1]);
-            }
+          constexpr int PAIRS = BN / 64;                     // 32-column pairs per tile
+          for (int pq = grp * (PAIRS / 2); pq < (grp + 1) * (PAIRS / 2); ++pq) {
+            const int col = j0 + pq * 32;
+            if (col >= p.pair_off) break;
+            tmem_ld32(t_row + pq * 32, raw[0]);
+            tmem_ld32(t_row + BN / 2 + pq * 32, raw[1]);
             tmem_ld_wait();
+            float up[32], gt[32];
 #pragma unroll
-            for (int q = 0; q < 2; ++q) {
-              const int col = j0 + cg * 64 + q * 32;
-              if (col < p.pair_off) {
-                float up[32], gt[32];
-#pragma unroll
-                for (int j = 0; j < 32; ++j) {
-                  up[j] = __bfloat162float(__float2bfloat16_rn(__uint_as_float(raw[2 * q][j])));
-                  gt[j] = __bfloat162float(__float2bfloat16_rn(__uint_as_float(raw[2 * q + 1][j])));
-                  v[j] = up[j] * rte::silu_f(gt[j]);
-                }
-                emit16(&tmap_c2, col, m0, up);
-                emit16(&tmap_c2, p.pair_off + col, m0, gt);
-                emit16(&tmap_c, col, m0, v);
-              }
+            for (int j = 0; j < 32; ++j) {
+              up[j] = __bfloat162float(__float2bfloat16_rn(__uint_as_float(raw[0][j])));
+              gt[j] = __bfloat162float(__float2bfloat16_rn(__uint_as_float(raw[1][j])));
+              v[j] = up[j] * rte::silu_f(gt[j]);
             }
+            emit16(&tmap_c2, col, m0, up);
+            emit16(&tmap_c2, p.pair_off + col, m0, gt);
+            emit16(&tmap_c, col, m0, v);
           }
         }
         tc_fence_before();
@@ -507,7 +510,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
       uint32_t raw[32];
       float v[32];
       if (p.epilogue == RTE_EPI_BF16) {
-        for (int c = 0; c < BN / 32; ++c) {
+        for (int c = grp; c < BN / 32; c += 2) {           // the two groups take alternate 32-column slices
           tmem_ld32(t_row + c * 32, raw); tmem_ld_wait();
           const int col = n0 + c * 32;
           if (row_ok && col < p.N) {
@@ -518,7 +521,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
         }
       } else if (p.epilogue == RTE_EPI_F32) {
         float* Cf = reinterpret_cast<float*>(p.C) + size_t(split) * p.split_stride;
-        for (int c = 0; c < BN / 32; ++c) {
+        for (int c = grp; c < BN / 32; c += 2) {           // the two groups take alternate 32-column slices
           tmem_ld32(t_row + c * 32, raw); tmem_ld_wait();
           const int col = n0 + c * 32;
           if (row_ok && col < p.N) {
@@ -537,7 +540,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
         // tile columns [0, BN/2) = up_j, [BN/2, BN) = gate_j for hidden units j0 .. j0 + BN/2
         const int j0 = nblk * (BN / 2);
         uint32_t rawg[32];
-        for (int c = 0; c < BN / 64; ++c) {
+        for (int c = grp; c < BN / 64; c += 2) {
           tmem_ld32(t_row + c * 32, raw);
           tmem_ld32(t_row + BN / 2 + c * 32, rawg);
           tmem_ld_wait();
@@ -560,7 +563,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
         }
       } else {  // RTE_EPI_SWIGLU_BWD
         const int F = p.pair_off;
-        for (int c = 0; c < BN / 32; ++c) {
+        for (int c = grp; c < BN / 32; c += 2) {           // the two groups take alternate 32-column slices
           tmem_ld32(t_row + c * 32, raw); tmem_ld_wait();
           const int col = n0 + c * 32;
           if (row_ok && col < p.N) {
