@@ -1,7 +1,7 @@
 """Generate the golden fixtures in this folder from the REFERENCE implementation.
 
 Run in a container that has the reference checkout (it is imported, unmodified,
-from ``$RTE_REFERENCE_SRC``, default ``/root/reference/src``):
+from ``$RTE_REFERENCE_SRC``, default: the ``reference/src`` tree beside this repository):
 
     python tests/golden/make_golden.py
 
@@ -25,7 +25,7 @@ import torch
 HERE = Path(__file__).resolve().parent
 ROOT = HERE.parents[1]
 sys.path.insert(0, str(ROOT))
-sys.path.insert(0, os.environ.get("RTE_REFERENCE_SRC", "/root/reference/src"))
+sys.path.insert(0, os.environ.get("RTE_REFERENCE_SRC", str(ROOT.parent / "reference" / "src")))
 
 from oracle import rte_oracle as O  # noqa: E402
 from tests.golden.cases import GOLDEN_CASES, oracle_cfgs  # noqa: E402

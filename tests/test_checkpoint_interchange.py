@@ -7,7 +7,7 @@ from pathlib import Path
 import pytest
 import torch
 
-REF_SRC = os.environ.get("RTE_REFERENCE_SRC", "/root/reference/src")
+REF_SRC = os.environ.get("RTE_REFERENCE_SRC", str(Path(__file__).resolve().parents[2] / "reference" / "src"))
 pytestmark = pytest.mark.skipif(not Path(REF_SRC, "recursive_training_engine").is_dir(),
                                 reason="reference sources not present")
 
