@@ -325,7 +325,7 @@ def main() -> None:
                                 "frac": roof["tflops"] / peak,
                                 # DRAM bytes per launch (read + write), launch-weighted mean over the nine hot-pass shapes of the
                                 # ncu capture summarised in profiles/gemm_tcgen05_c3_shapes_ncu_full.md
-                                "traffic": 41.0e6, "traffic_unit": "bytes per launch (ncu dram__bytes_read+write, 9 shapes)",
+                                "traffic": 38.0e6, "traffic_unit": "bytes per launch (ncu dram__bytes_read+write, 9 shapes)",
                                 "of": which + " (sustained)",
                                 "kernel": "gemm_tcgen05_kernel", "launches_per_step": roof["launches"],
                                 "gemm_ms_per_step": roof["gemm_ms_per_step"],
