@@ -11,9 +11,9 @@
 
 namespace {
 
-constexpr int BM = 64, BN = 64, BK = 64, LDS = BK + 8, THR = 128;
+constexpr int BM = 64, BK = 64, LDS = BK + 8, THR = 128;       // BN (64 or 32) is a template parameter
 constexpr int NST = 8;                                     // k-tiles in flight: the launch is latency-bound, not bandwidth-bound
-constexpr int SMEM_BYTES = NST * (BM + BN) * LDS * 2;
+constexpr int SMEM_BYTES = NST * (BM + 64) * LDS * 2;        // sized for the wider tile
 
 __device__ __forceinline__ void cp_async16(void* smem, const void* gmem, bool valid) {
   const uint32_t dst = static_cast<uint32_t>(__cvta_generic_to_shared(smem));
@@ -45,29 +45,42 @@ struct SmallParams {
   int k_per_split; long long split_stride;
 };
 
-template <bool B_MN, bool OUT_F32>
+// The legacy mma.sync path peaks near 2 TFLOP/s per SM on this part, so a CTA's speed is set by how many MMAs it
+// issues per k-tile: narrow (BN = 32) tiles double the CTA count when the wide grid would leave most SMs idle.
+template <bool B_MN, bool OUT_F32, int BN>
 __global__ void __launch_bounds__(THR)
 gemm_small_kernel(const SmallParams p) {
+  constexpr int LDB = B_MN ? BN + 8 : LDS;       // row stride of the B tile ([k][n] rows are BN long, [n][k] rows BK long)
+  constexpr int B_ROWS = B_MN ? BK : BN;
   extern __shared__ __align__(16) uint8_t smraw[];
   __nv_bfloat16 (*sa)[BM * LDS] = reinterpret_cast<__nv_bfloat16 (*)[BM * LDS]>(smraw);
-  __nv_bfloat16 (*sb)[BN * LDS] = reinterpret_cast<__nv_bfloat16 (*)[BN * LDS]>(smraw + NST * BM * LDS * 2);   // K-major B: [n][k]; MN-major: [k][n]
+  __nv_bfloat16 (*sb)[B_ROWS * LDB] = reinterpret_cast<__nv_bfloat16 (*)[B_ROWS * LDB]>(smraw + NST * BM * LDS * 2);   // K-major B: [n][k]; MN-major: [k][n]
   const int n0 = blockIdx.x * BN, m0 = blockIdx.y * BM;
   const int k_lo = blockIdx.z * p.k_per_split, k_hi = min(p.K, k_lo + p.k_per_split);
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, g = lane >> 2, t = lane & 3;
 
   auto load_tile = [&](int buf, int k0) {
+    // out-of-range chunks are zero-filled; their source address is clamped to the matrix base (never dereferenced)
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
       const int chunk = threadIdx.x + i * THR, r = chunk >> 3, c = (chunk & 7) * 8;
-      // out-of-range chunks are zero-filled; their source address is clamped to the matrix base (never dereferenced)
       const bool va = (m0 + r) < p.M && (k0 + c) < k_hi;
       cp_async16(&sa[buf][r * LDS + c], va ? p.A + (size_t)(m0 + r) * p.lda + k0 + c : p.A, va);
-      if (!B_MN) {
+    }
+    if (!B_MN) {
+#pragma unroll
+      for (int i = 0; i < BN * 8 / THR; ++i) {            // BN rows of BK elements
+        const int chunk = threadIdx.x + i * THR, r = chunk >> 3, c = (chunk & 7) * 8;
         const bool vb = (n0 + r) < p.N && (k0 + c) < k_hi;
-        cp_async16(&sb[buf][r * LDS + c], vb ? p.B + (size_t)(n0 + r) * p.ldb + k0 + c : p.B, vb);
-      } else {
+        cp_async16(&sb[buf][r * LDB + c], vb ? p.B + (size_t)(n0 + r) * p.ldb + k0 + c : p.B, vb);
+      }
+    } else {
+      constexpr int CPR = BN / 8;                         // 16-byte chunks per k-row
+#pragma unroll
+      for (int i = 0; i < BK * CPR / THR; ++i) {          // BK rows of BN elements
+        const int chunk = threadIdx.x + i * THR, r = chunk / CPR, c = (chunk % CPR) * 8;
         const bool vb = (k0 + r) < k_hi && (n0 + c) < p.N;
-        cp_async16(&sb[buf][r * LDS + c], vb ? p.B + (size_t)(k0 + r) * p.ldb + n0 + c : p.B, vb);
+        cp_async16(&sb[buf][r * LDB + c], vb ? p.B + (size_t)(k0 + r) * p.ldb + n0 + c : p.B, vb);
       }
     }
   };
@@ -105,10 +118,10 @@ gemm_small_kernel(const SmallParams p) {
       for (int nt = 0; nt < BN / 8; ++nt) {
         uint32_t b0, b1;
         if (!B_MN) {
-          b0 = ld32(b + (nt * 8 + g) * LDS + ks * 16 + 2 * t);
-          b1 = ld32(b + (nt * 8 + g) * LDS + ks * 16 + 8 + 2 * t);
+          b0 = ld32(b + (nt * 8 + g) * LDB + ks * 16 + 2 * t);
+          b1 = ld32(b + (nt * 8 + g) * LDB + ks * 16 + 8 + 2 * t);
         } else {
-          ldsm_x2_trans(b0, b1, b + (ks * 16 + (lane & 15)) * LDS + nt * 8);
+          ldsm_x2_trans(b0, b1, b + (ks * 16 + (lane & 15)) * LDB + nt * 8);
         }
         mma16816(acc[nt], af, b0, b1);
       }
@@ -161,23 +174,30 @@ extern "C" int rte_gemm_bf16_small(const rte_gemm_args* a, rte_stream_t stream) 
   p.k_per_split = rte::ceil_div(ktiles, splits) * BK;
   RTE_CHECK_ARG(rte::ceil_div(a->K, p.k_per_split) == splits);      // every partial must be written
   p.split_stride = a->split_stride;
-  dim3 grid(rte::ceil_div(a->N, BN), rte::ceil_div(a->M, BM), splits);
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
   const bool f32 = a->epilogue == RTE_EPI_F32;
-  static bool attr_set = false;
-  if (!attr_set) {
-    if (cudaFuncSetAttribute(gemm_small_kernel<true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES) != cudaSuccess ||
-        cudaFuncSetAttribute(gemm_small_kernel<true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES) != cudaSuccess ||
-        cudaFuncSetAttribute(gemm_small_kernel<false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES) != cudaSuccess ||
-        cudaFuncSetAttribute(gemm_small_kernel<false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES) != cudaSuccess)
-      return RTE_ERR_LAUNCH;
-    attr_set = true;
-  }
+  const int wide_ctas = rte::ceil_div(a->N, 64) * rte::ceil_div(a->M, BM) * splits;
+  const bool narrow = wide_ctas < 74;                    // fewer CTAs than half the SMs: halve the tile width
+#define RTE_SMALL_LAUNCH(BMN, F32, BNV)                                                                               \
+  do {                                                                                                                \
+    static bool set_ = false;                                                                                         \
+    if (!set_) {                                                                                                      \
+      if (cudaFuncSetAttribute(gemm_small_kernel<BMN, F32, BNV>, cudaFuncAttributeMaxDynamicSharedMemorySize,         \
+                               SMEM_BYTES) != cudaSuccess)                                                            \
+        return RTE_ERR_LAUNCH;                                                                                        \
+      set_ = true;                                                                                                    \
+    }                                                                                                                 \
+    gemm_small_kernel<BMN, F32, BNV><<<dim3(rte::ceil_div(a->N, BNV), rte::ceil_div(a->M, BM), splits), THR,         \
+                                       SMEM_BYTES, st>>>(p);                                                          \
+  } while (0)
   if (a->b_mn_major) {
-    if (f32) gemm_small_kernel<true, true><<<grid, THR, SMEM_BYTES, st>>>(p); else gemm_small_kernel<true, false><<<grid, THR, SMEM_BYTES, st>>>(p);
+    if (f32) { if (narrow) RTE_SMALL_LAUNCH(true, true, 32); else RTE_SMALL_LAUNCH(true, true, 64); }
+    else     { if (narrow) RTE_SMALL_LAUNCH(true, false, 32); else RTE_SMALL_LAUNCH(true, false, 64); }
   } else {
-    if (f32) gemm_small_kernel<false, true><<<grid, THR, SMEM_BYTES, st>>>(p); else gemm_small_kernel<false, false><<<grid, THR, SMEM_BYTES, st>>>(p);
+    if (f32) { if (narrow) RTE_SMALL_LAUNCH(false, true, 32); else RTE_SMALL_LAUNCH(false, true, 64); }
+    else     { if (narrow) RTE_SMALL_LAUNCH(false, false, 32); else RTE_SMALL_LAUNCH(false, false, 64); }
   }
+#undef RTE_SMALL_LAUNCH
   RTE_LAUNCH_CHECK();
   return RTE_OK;
 }
