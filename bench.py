@@ -12,6 +12,7 @@ from __future__ import annotations
 
 import argparse
 import json
+import math
 import os
 import subprocess
 import sys
@@ -276,15 +277,23 @@ def main() -> None:
         launches_timed = (eng.ops.launches - l0) or (eng.kernel_launches_per_step or 0) * K
         # ---- end to end through the public API with pinned host batches
         barrier()
+        # (a) the pipelined loop (`train_steps`: two steps in flight; every step copies its batch in and its results
+        # out, and every step's loss is read on the host), (b) one synchronous `train_step` call per batch
+        t0 = time.perf_counter()
+        losses = [r.loss for r in eng.train_steps(host_batches[i % n_batches] for i in range(K))]
+        torch.cuda.synchronize()
+        ms_e2e = (time.perf_counter() - t0) * 1e3
+        assert len(losses) == K and all(math.isfinite(x) for x in losses)
+        barrier()
         t0 = time.perf_counter()
         for i in range(K):
             eng.train_step(host_batches[i % n_batches])
         torch.cuda.synchronize()
-        ms_e2e = (time.perf_counter() - t0) * 1e3
+        ms_e2e_sync = (time.perf_counter() - t0) * 1e3
         if dist is not None:
-            t = torch.tensor([ms_dev, ms_e2e], device=dev)
+            t = torch.tensor([ms_dev, ms_e2e, ms_e2e_sync], device=dev)
             dist.all_reduce(t, op=dist.ReduceOp.MAX)
-            ms_dev, ms_e2e = float(t[0]), float(t[1])
+            ms_dev, ms_e2e, ms_e2e_sync = float(t[0]), float(t[1]), float(t[2])
         # The two timed loops may be shorter than nvidia-smi's sampling period: keep the same step running (untimed)
         # for about half a second so that a few clock samples under this load exist (same count on every rank).
         for i in range(max(1, min(400, int(500.0 / max(ms_e2e / K, 0.1))))):
@@ -312,7 +321,9 @@ def main() -> None:
                        "l2": "per-step working set (~1 GB of activations) exceeds the 126 MB L2; no explicit flush",
                        "timing": "CUDA events around K graph replays, max over ranks"},
             "e2e": {"value": tokens * K / (ms_e2e / 1e3), "unit": "tokens/s", "h2d_bytes_per_step": 2 * B * S * 8 + (4 + B * 4 if eng.audit is not None else 0),
-                    "d2h_bytes_per_step": eng._results.numel() * 4 + 4},
+                    "d2h_bytes_per_step": eng._results.numel() * 4 + 4,
+                    "api": "TrainEngine.train_steps(batches): two steps in flight, each step's loss read on the host",
+                    "synchronous_train_step": tokens * K / (ms_e2e_sync / 1e3)},
             "gpu_launches": launches_timed,
             "clocks": clocks.summary(),
             "step_roofline": {"flops_per_token": step_flops_per_token(C3_MODEL),

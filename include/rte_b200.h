@@ -109,8 +109,9 @@ int rte_reduce_splits(const float* ws, int32_t splits, int64_t split_stride, int
 /* ---------------------------------------------------- embedding (models.py:136,693) */
 int rte_embed_fwd(const int64_t* tokens, const float* table, float* out, int32_t n_tokens, int32_t d,
                   int32_t vocab, int32_t* status, rte_stream_t stream);
-/* dtable[tokens[i], :] += dx[i, :]  (atomic fp32 adds) */
-int rte_embed_bwd(const int64_t* tokens, const float* dx, float* dtable, int32_t n_tokens, int32_t d,
+/* dtable[tokens[i], :] += dx[i, :].  Reproducible bit for bit: the addends meet in `accum` (scratch, vocab*d int64,
+ * any contents) as 64-bit fixed point (2^-40 resolution, order-free integer atomics) and are added to dtable once. */
+int rte_embed_bwd(const int64_t* tokens, const float* dx, float* dtable, int64_t* accum, int32_t n_tokens, int32_t d,
                   int32_t vocab, int32_t* status, rte_stream_t stream);
 
 /* ------------------------------------------------- RMSNorm (kernels/reference.py:9-17)

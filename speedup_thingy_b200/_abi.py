@@ -77,7 +77,7 @@ PROTOTYPES = {
     "rte_gemm_bf16_small": (C.c_int, [P(GemmArgs), c_vp]),
     "rte_reduce_splits": (C.c_int, [c_vp, c_i32, c_i64, c_i64, c_vp, c_i32, c_vp]),
     "rte_embed_fwd": (C.c_int, [c_vp, c_vp, c_vp, c_i32, c_i32, c_i32, c_vp, c_vp]),
-    "rte_embed_bwd": (C.c_int, [c_vp, c_vp, c_vp, c_i32, c_i32, c_i32, c_vp, c_vp]),
+    "rte_embed_bwd": (C.c_int, [c_vp, c_vp, c_vp, c_vp, c_i32, c_i32, c_i32, c_vp, c_vp]),
     "rte_rmsnorm_fwd": (C.c_int, [c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, c_i32, c_i32, c_f32, c_vp]),
     "rte_rmsnorm_bwd": (C.c_int, [c_vp] * 12 + [c_i32, c_i32, c_i32, P(c_i32), c_vp]),
     "rte_colsum_partials": (C.c_int, [c_vp, c_i32, c_i32, c_vp, c_i32, c_vp]),

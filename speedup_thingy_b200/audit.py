@@ -136,12 +136,13 @@ class AuditReplay:
     # ------------------------------------------------------------------ host side, once per step
     def prepare(self, step_seed: int) -> None:
         """Host half of `choose` for a coming step: the seeded permutation and the control-variate weights, written to
-        a pinned staging pair (two pairs alternate, so the pair a queued copy may still read is never rewritten)."""
+        a pinned staging pair.  Three pairs rotate: with up to two steps queued on the device, the pair written here for
+        step i+2 is the one step i-1 used, whose copy has completed by the time that step was collected."""
         eng = self.eng
         if self._stage is None:
             pin = eng.device.type == "cuda"
             self._stage = [(torch.empty(self.k, dtype=torch.int32, pin_memory=pin),
-                            torch.empty(eng.B, dtype=torch.float32, pin_memory=pin)) for _ in range(2)]
+                            torch.empty(eng.B, dtype=torch.float32, pin_memory=pin)) for _ in range(3)]
             self._stage_next = 0
         gen = torch.Generator().manual_seed(step_seed)
         chosen = torch.sort(torch.randperm(eng.B, generator=gen)[: self.k]).values
@@ -151,7 +152,7 @@ class AuditReplay:
         h_rw.fill_(w0)
         h_rw[chosen] = w0 * (1.0 - 1.0 / self.p_inc)                     # d corrected / d hot on audited samples
         self._prepared = (step_seed, chosen, h_idx, h_rw)
-        self._stage_next ^= 1
+        self._stage_next = (self._stage_next + 1) % 3
 
     def choose(self, step_seed: int) -> None:
         """Fixed-count sampler: first k entries of a seeded CPU permutation (audit.py:99-116); writes the subset
@@ -352,13 +353,13 @@ class AuditReplay:
         o.scatter_add_rows(dh0_hot, self.idx, self.dh_first, n, S * d)
 
     # ------------------------------------------------------------------ reporting
-    def loss_terms(self, hot_per_sample: torch.Tensor, host: dict) -> dict[str, float]:
+    def loss_terms(self, hot_per_sample: torch.Tensor, host: dict, chosen: torch.Tensor | None = None) -> dict[str, float]:
         """Host-side assembly of the audited quantities for the reported loss (training.py:1381-1385) from the
         step's fetched results (`terms`, `exact_loss`, `kl_sum` already on the host)."""
         tr, n, Ma, d = self.eng.tr, self.n, self.Ma, self.eng.cfg.d_model
         terms = host["terms"]
         exact = host["exact_loss"].clone()
-        hot = hot_per_sample[self.last_chosen]
+        hot = hot_per_sample[self.last_chosen if chosen is None else chosen]
         temp = max(float(tr.distill_temperature), 1e-6)
         aux = dict(delta_dir=tr.lambda_delta_dir * float(terms[:, 0].mean()),
                    delta_rms=tr.lambda_delta_rms * float(terms[:, 1].mean()),

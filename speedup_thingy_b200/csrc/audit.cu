@@ -4,7 +4,11 @@
 // pass.  Everything here is small (n*S tokens, n = audited samples) and bandwidth-trivial; the point of these
 // kernels is to keep the whole step on the device without host branches.
 
+#include <cooperative_groups.h>
+
 #include "rte_common.cuh"
+
+namespace cg = cooperative_groups;
 
 namespace {
 
@@ -114,28 +118,52 @@ scaled_residual_bwd_kernel(const float* __restrict__ dout, const float* __restri
 __device__ __forceinline__ float smooth_l1(float x) { const float a = fabsf(x); return a < 1.f ? 0.5f * x * x : a - 0.5f; }
 __device__ __forceinline__ float clamp1(float x) { return fminf(1.f, fmaxf(-1.f, x)); }
 
-// One CTA per audited sample.  Phase A: whole-sample reductions for the direction / rms terms.
-// Phase B: one warp per row for the two smooth-L1 terms (the normed one goes back through the row's rmsnorm).
-__global__ void __launch_bounds__(NTHR)
+// One thread-block cluster of DISTILL_CTAS CTAs per audited sample, one warp per token row.  Phase A: every warp
+// reduces its rows for the direction / rms terms; the CTAs' partial sums meet through distributed shared memory
+// (summed in rank order by every CTA, so all of them hold the same bits).  Phase B: the two smooth-L1 terms per row
+// (the normed one goes back through the row's rmsnorm) and the gradient with respect to the hot endpoint.
+constexpr int DISTILL_CTAS = 8;
+
+__global__ void __cluster_dims__(DISTILL_CTAS, 1, 1) __launch_bounds__(NTHR)
 macro_distill_kernel(const float* __restrict__ hot, const float* __restrict__ exact, const float* __restrict__ h0,
                      float l_dir, float l_rms, float l_normed, float l_raw, float* __restrict__ terms,
                      float* __restrict__ dhot, int n, int S, int d) {
-  __shared__ float red[32];
-  __shared__ float row_sums[2][NTHR / 32];
-  const int i = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  constexpr int NW = NTHR / 32;
+  __shared__ float wpart[NW][3];
+  __shared__ float cta_part[3];        // read by the other CTAs of the cluster
+  __shared__ float cta_sl1[2];         // read by rank 0
+  __shared__ float wsl1[NW][2];
+  cg::cluster_group cluster = cg::this_cluster();
+  const int rank = (int)cluster.block_rank();
+  const int i = blockIdx.x / DISTILL_CTAS, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int gw = rank * NW + warp, GW = DISTILL_CTAS * NW;
   const long long N = (long long)S * d;
   const float* hp = hot + (size_t)i * N;
   const float* ep = exact + (size_t)i * N;
   const float* zp = h0 + (size_t)i * N;
   float* gp = dhot + (size_t)i * N;
   float dot = 0.f, pp = 0.f, ee = 0.f;
-  for (long long k = threadIdx.x; k < N; k += NTHR) {
-    const float a = hp[k] - zp[k], b = ep[k] - zp[k];
-    dot += a * b; pp += a * a; ee += b * b;
+  for (int s = gw; s < S; s += GW) {
+    const size_t o = (size_t)s * d;
+    for (int c = lane; c < d; c += 32) {
+      const float z = zp[o + c], a = hp[o + c] - z, b = ep[o + c] - z;
+      dot += a * b; pp += a * a; ee += b * b;
+    }
   }
-  dot = rte::block_sum(dot, red);
-  pp = rte::block_sum(pp, red);
-  ee = rte::block_sum(ee, red);
+  dot = rte::warp_sum(dot); pp = rte::warp_sum(pp); ee = rte::warp_sum(ee);
+  if (lane == 0) { wpart[warp][0] = dot; wpart[warp][1] = pp; wpart[warp][2] = ee; }
+  __syncthreads();
+  if (threadIdx.x < 3) {
+    float t = 0.f;
+    for (int w = 0; w < NW; ++w) t += wpart[w][threadIdx.x];
+    cta_part[threadIdx.x] = t;
+  }
+  cluster.sync();
+  dot = pp = ee = 0.f;
+  for (int r = 0; r < DISTILL_CTAS; ++r) {
+    const float* rp_ = cluster.map_shared_rank(cta_part, r);
+    dot += rp_[0]; pp += rp_[1]; ee += rp_[2];
+  }
   const float np = fmaxf(sqrtf(pp), 1e-8f), ne = fmaxf(sqrtf(ee), 1e-8f);
   const float cosv = dot / (np * ne);
   const float rp = fmaxf(sqrtf(pp / (float)N), 1e-8f), re = fmaxf(sqrtf(ee / (float)N), 1e-8f);
@@ -143,7 +171,7 @@ macro_distill_kernel(const float* __restrict__ hot, const float* __restrict__ ex
   const float c_dir = -l_dir / (float)n, c_rms = l_rms / (float)n * 2.f * delta / ((float)N * rp * rp);
   const float c_el = 1.f / ((float)n * (float)N);
   float sl1n = 0.f, sl1r = 0.f;
-  for (int s = warp; s < S; s += NTHR / 32) {
+  for (int s = gw; s < S; s += GW) {
     const float* hr = hp + (size_t)s * d;
     const float* er = ep + (size_t)s * d;
     float sh = 0.f, se = 0.f;
@@ -169,16 +197,26 @@ macro_distill_kernel(const float* __restrict__ hot, const float* __restrict__ ex
     }
   }
   sl1n = rte::warp_sum(sl1n); sl1r = rte::warp_sum(sl1r);
-  if (lane == 0) { row_sums[0][warp] = sl1n; row_sums[1][warp] = sl1r; }
+  if (lane == 0) { wsl1[warp][0] = sl1n; wsl1[warp][1] = sl1r; }
   __syncthreads();
-  if (threadIdx.x == 0) {
+  if (threadIdx.x < 2) {
+    float t = 0.f;
+    for (int w = 0; w < NW; ++w) t += wsl1[w][threadIdx.x];
+    cta_sl1[threadIdx.x] = t;
+  }
+  cluster.sync();
+  if (rank == 0 && threadIdx.x == 0) {
     float a = 0.f, b = 0.f;
-    for (int w = 0; w < NTHR / 32; ++w) { a += row_sums[0][w]; b += row_sums[1][w]; }
+    for (int r = 0; r < DISTILL_CTAS; ++r) {
+      const float* q = cluster.map_shared_rank(cta_sl1, r);
+      a += q[0]; b += q[1];
+    }
     terms[i * 4 + 0] = 1.f - cosv;
     terms[i * 4 + 1] = delta * delta;
     terms[i * 4 + 2] = a;
     terms[i * 4 + 3] = b;
   }
+  cluster.sync();          // no CTA leaves while rank 0 may still read its shared memory
 }
 
 // One CTA per token row of the audited subset.
@@ -306,7 +344,7 @@ extern "C" int rte_macro_distill(const float* hot, const float* exact, const flo
                                  float l_normed, float l_raw, float* terms, float* dhot, int32_t n, int32_t S, int32_t d,
                                  rte_stream_t stream) {
   RTE_CHECK_ARG(hot && exact && h0 && terms && dhot && n > 0 && S > 0 && d > 0);
-  macro_distill_kernel<<<n, NTHR, 0, ST(stream)>>>(hot, exact, h0, l_dir, l_rms, l_normed, l_raw, terms, dhot, n, S, d);
+  macro_distill_kernel<<<n * DISTILL_CTAS, NTHR, 0, ST(stream)>>>(hot, exact, h0, l_dir, l_rms, l_normed, l_raw, terms, dhot, n, S, d);
   RTE_LAUNCH_CHECK();
   return RTE_OK;
 }

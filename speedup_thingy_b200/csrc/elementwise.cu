@@ -28,8 +28,14 @@ __global__ void embed_fwd_kernel(const int64_t* __restrict__ tokens, const float
   }
 }
 
-__global__ void embed_bwd_kernel(const int64_t* __restrict__ tokens, const float* __restrict__ dx,
-                                 float* __restrict__ dtable, int n_tokens, int d, int vocab, int* status) {
+// The scatter-add of token-row gradients into the table is ORDER-FREE: every addend is converted to 64-bit fixed
+// point (scale 2^40: resolution 9e-13, range +-8.4e6), integer atomics are associative, and the sum is converted
+// back once per table element, so repeated runs produce the same bits whatever order the adds land in.
+constexpr float EMBED_FX_SCALE = 1099511627776.f;          // 2^40
+
+__global__ void embed_bwd_accum_kernel(const int64_t* __restrict__ tokens, const float* __restrict__ dx,
+                                       unsigned long long* __restrict__ accum, float* __restrict__ dtable,
+                                       int n_tokens, int d, int vocab, int* status) {
   const long long total = (long long)n_tokens * d;
   for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
     const int t = int(i / d), c = int(i % d);
@@ -38,7 +44,16 @@ __global__ void embed_bwd_kernel(const int64_t* __restrict__ tokens, const float
       if (status) atomicExch(status, RTE_DEV_INDEX_OUT_OF_RANGE);
       continue;
     }
-    atomicAdd(dtable + tok * d + c, dx[i]);
+    const float x = dx[i];
+    if (!isfinite(x)) { dtable[tok * d + c] = x - x; continue; }      // NaN stays NaN through the final add
+    atomicAdd(accum + tok * d + c, (unsigned long long)__float2ll_rn(x * EMBED_FX_SCALE));
+  }
+}
+
+__global__ void embed_bwd_apply_kernel(const unsigned long long* __restrict__ accum, float* __restrict__ dtable, long long n) {
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
+    const long long q = (long long)accum[i];
+    if (q != 0) dtable[i] += __ll2float_rn(q) * (1.f / EMBED_FX_SCALE);
   }
 }
 
@@ -164,8 +179,9 @@ residual_rmsnorm_fwd_kernel(const float* __restrict__ base, const float* __restr
 // Each CTA walks rows blockIdx.x, blockIdx.x + gridDim.x, ...; column-wise partial sums for the
 // parameter gradients are kept in registers per warp, combined through shared memory at the end
 // and written to row blockIdx.x of the partial buffers (deterministic, no atomics).
-template <int NV>
-__global__ void __launch_bounds__(256)
+// FILM = false drops the FiLM accumulators (and a third of the registers) for the plain-norm launches.
+template <int NV, bool FILM>
+__global__ void __launch_bounds__(256, NV <= 4 ? (FILM ? 2 : 3) : 1)
 rmsnorm_bwd_kernel(const float* __restrict__ x, const float* __restrict__ w, const float* __restrict__ fg,
                    const float* __restrict__ rstd, const __nv_bfloat16* __restrict__ dy16,
                    const float* __restrict__ dy32, const float* __restrict__ dres, float* __restrict__ dx32,
@@ -174,10 +190,13 @@ rmsnorm_bwd_kernel(const float* __restrict__ x, const float* __restrict__ w, con
   extern __shared__ float sm[];   // [3][warps][d] when parameter gradients are requested
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarp = blockDim.x >> 5;
   const int d4 = d >> 2;
-  float4 aw[NV], ag[NV], ab[NV];
+  constexpr int NF = FILM ? NV : 1;
+  float4 aw[NV], ag[NF], ab[NF];
 #pragma unroll
-  for (int i = 0; i < NV; ++i) aw[i] = ag[i] = ab[i] = make_float4(0.f, 0.f, 0.f, 0.f);
-  const bool want_w = dw_part != nullptr, want_f = dg_part != nullptr;
+  for (int i = 0; i < NV; ++i) aw[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+  for (int i = 0; i < NF; ++i) ag[i] = ab[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+  const bool want_w = dw_part != nullptr, want_f = FILM && dg_part != nullptr;
 
   for (int row = blockIdx.x * nwarp + warp; row < rows; row += gridDim.x * nwarp) {
     const float r = rstd[row];
@@ -200,7 +219,7 @@ rmsnorm_bwd_kernel(const float* __restrict__ x, const float* __restrict__ w, con
         }
         float4 ww = w ? reinterpret_cast<const float4*>(w)[c] : make_float4(1.f, 1.f, 1.f, 1.f);
         float4 f1 = make_float4(1.f, 1.f, 1.f, 1.f);
-        if (fg) {
+        if (FILM && fg) {
           const float4 t = reinterpret_cast<const float4*>(fg)[c];
           f1 = make_float4(1.f + t.x, 1.f + t.y, 1.f + t.z, 1.f + t.w);
         }
@@ -208,10 +227,12 @@ rmsnorm_bwd_kernel(const float* __restrict__ x, const float* __restrict__ w, con
           aw[i].x += dyv.x * f1.x * xh[i].x; aw[i].y += dyv.y * f1.y * xh[i].y;
           aw[i].z += dyv.z * f1.z * xh[i].z; aw[i].w += dyv.w * f1.w * xh[i].w;
         }
-        if (want_f) {
-          ag[i].x += dyv.x * xh[i].x * ww.x; ag[i].y += dyv.y * xh[i].y * ww.y;
-          ag[i].z += dyv.z * xh[i].z * ww.z; ag[i].w += dyv.w * xh[i].w * ww.w;
-          ab[i].x += dyv.x; ab[i].y += dyv.y; ab[i].z += dyv.z; ab[i].w += dyv.w;
+        if constexpr (FILM) {
+          if (want_f) {
+            ag[i].x += dyv.x * xh[i].x * ww.x; ag[i].y += dyv.y * xh[i].y * ww.y;
+            ag[i].z += dyv.z * xh[i].z * ww.z; ag[i].w += dyv.w * xh[i].w * ww.w;
+            ab[i].x += dyv.x; ab[i].y += dyv.y; ab[i].z += dyv.z; ab[i].w += dyv.w;
+          }
         }
         g[i] = make_float4(dyv.x * f1.x * ww.x, dyv.y * f1.y * ww.y, dyv.z * f1.z * ww.z, dyv.w * f1.w * ww.w);
         dot += g[i].x * xh[i].x + g[i].y * xh[i].y + g[i].z * xh[i].z + g[i].w * xh[i].w;
@@ -246,9 +267,11 @@ rmsnorm_bwd_kernel(const float* __restrict__ x, const float* __restrict__ w, con
     const int c = lane + 32 * i;
     if (c < d4) {
       if (want_w) reinterpret_cast<float4*>(sw + (size_t)warp * d)[c] = aw[i];
-      if (want_f) {
-        reinterpret_cast<float4*>(sg + (size_t)warp * d)[c] = ag[i];
-        reinterpret_cast<float4*>(sb + (size_t)warp * d)[c] = ab[i];
+      if constexpr (FILM) {
+        if (want_f) {
+          reinterpret_cast<float4*>(sg + (size_t)warp * d)[c] = ag[i];
+          reinterpret_cast<float4*>(sb + (size_t)warp * d)[c] = ab[i];
+        }
       }
     }
   }
@@ -600,10 +623,14 @@ extern "C" int rte_embed_fwd(const int64_t* tokens, const float* table, float* o
   RTE_LAUNCH_CHECK();
   return RTE_OK;
 }
-extern "C" int rte_embed_bwd(const int64_t* tokens, const float* dx, float* dtable, int32_t n_tokens, int32_t d,
-                             int32_t vocab, int32_t* status, rte_stream_t stream) {
-  RTE_CHECK_ARG(tokens && dx && dtable && n_tokens > 0 && d > 0);
-  embed_bwd_kernel<<<grid_for((long long)n_tokens * d, 256), 256, 0, ST(stream)>>>(tokens, dx, dtable, n_tokens, d, vocab, status);
+extern "C" int rte_embed_bwd(const int64_t* tokens, const float* dx, float* dtable, int64_t* accum, int32_t n_tokens,
+                             int32_t d, int32_t vocab, int32_t* status, rte_stream_t stream) {
+  RTE_CHECK_ARG(tokens && dx && dtable && accum && n_tokens > 0 && d > 0 && vocab > 0);
+  const long long n = (long long)vocab * d;
+  if (cudaMemsetAsync(accum, 0, (size_t)n * sizeof(int64_t), ST(stream)) != cudaSuccess) return RTE_ERR_LAUNCH;
+  embed_bwd_accum_kernel<<<grid_for((long long)n_tokens * d, 256), 256, 0, ST(stream)>>>(
+      tokens, dx, reinterpret_cast<unsigned long long*>(accum), dtable, n_tokens, d, vocab, status);
+  embed_bwd_apply_kernel<<<grid_for(n, 256), 256, 0, ST(stream)>>>(reinterpret_cast<const unsigned long long*>(accum), dtable, n);
   RTE_LAUNCH_CHECK();
   return RTE_OK;
 }
@@ -659,7 +686,8 @@ extern "C" int rte_rmsnorm_bwd(const float* x, const float* w, const float* film
   if (d > 128 * RN_MAX_V4) return RTE_ERR_UNSUPPORTED;
   const bool grads = dw_partial || dgamma_partial;
   int grid = rte::ceil_div(rows, 8);
-  const int cap = 148 * 4;      // one wave of CTAs (each writes one partial row), enough rows in flight to cover HBM latency
+  // one wave of CTAs (each writes one partial row): three fit an SM without FiLM accumulators at d <= 512
+  const int cap = 148 * ((film_gamma || dgamma_partial || d > 512) ? 2 : 3);
   if (grid > cap) grid = cap;
   if (grads) {
     RTE_CHECK_ARG(max_partials >= 1);
@@ -669,16 +697,20 @@ extern "C" int rte_rmsnorm_bwd(const float* x, const float* w, const float* film
   const size_t smem = grads ? (size_t)(dgamma_partial ? 3 : 1) * 8 * d * sizeof(float) : 0;
 #define RTE_RN_BWD(NV)                                                                                           \
   do {                                                                                                           \
+    if (film_gamma || dgamma_partial) RTE_RN_BWD_F(NV, true); else RTE_RN_BWD_F(NV, false);                      \
+  } while (0)
+#define RTE_RN_BWD_F(NV, FILM)                                                                                   \
+  do {                                                                                                           \
     if (smem > 48 * 1024) {                                                                                      \
       static bool set = false;                                                                                   \
       if (!set) {                                                                                                \
-        if (cudaFuncSetAttribute(rmsnorm_bwd_kernel<NV>, cudaFuncAttributeMaxDynamicSharedMemorySize,            \
+        if (cudaFuncSetAttribute(rmsnorm_bwd_kernel<NV, FILM>, cudaFuncAttributeMaxDynamicSharedMemorySize,            \
                                  200 * 1024) != cudaSuccess)                                                     \
           return RTE_ERR_LAUNCH;                                                                                 \
         set = true;                                                                                              \
       }                                                                                                          \
     }                                                                                                            \
-    rmsnorm_bwd_kernel<NV><<<grid, 256, smem, ST(stream)>>>(x, w, film_gamma, rstd,                              \
+    rmsnorm_bwd_kernel<NV, FILM><<<grid, 256, smem, ST(stream)>>>(x, w, film_gamma, rstd,                              \
         reinterpret_cast<const __nv_bfloat16*>(dy_bf16), dy_f32, dres, dx_f32,                                   \
         reinterpret_cast<__nv_bfloat16*>(dx_bf16), dw_partial, dgamma_partial, dbeta_partial, rows, d);          \
   } while (0)
@@ -688,6 +720,7 @@ extern "C" int rte_rmsnorm_bwd(const float* x, const float* w, const float* film
   else if (d <= 1024) RTE_RN_BWD(8);
   else RTE_RN_BWD(16);
 #undef RTE_RN_BWD
+#undef RTE_RN_BWD_F
   RTE_LAUNCH_CHECK();
   return RTE_OK;
 }

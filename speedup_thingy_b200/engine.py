@@ -296,6 +296,7 @@ class TrainEngine:
         e = lambda *shape, dtype=f32: torch.empty(*shape, dtype=dtype, device=dev)  # noqa: E731
         self.tokens = torch.zeros(B, S, dtype=torch.int64, device=dev)
         self.targets = torch.zeros(B, S, dtype=torch.int64, device=dev)
+        self.embed_accum = torch.zeros(cfg.vocab_size * cfg.d_model, dtype=torch.int64, device=dev)   # embed_bwd scratch
         self.x0 = e(M, d)
         if self.dense:
             self.blocks = [_Block(f"blocks.{i}", M, cfg, B, S, dev) for i in range(cfg.n_dense_layers)]
@@ -389,7 +390,10 @@ class TrainEngine:
         # the hot-path budget depends on the configuration only: checked once, before anything runs (training.py:1389-1392)
         self._budget = {} if (self.dense or self.exact) else hot_budget(cfg, tr, self.oc.shortlist_max_tokens if self.shortlist else None)
         self._graph = None
-        self._host: dict[str, torch.Tensor] | None = None
+        self._host: dict[str, Any] | None = None           # results of the step collected last
+        self._host_slots = None
+        self._slot_next = 0
+        self._pending: list[dict[str, Any]] = []
         self._launches_per_step: int | None = None
 
     # ------------------------------------------------------------------ data-parallel gradient exchange
@@ -592,7 +596,7 @@ class TrainEngine:
         for j, blk in enumerate(reversed(self.prelude)):
             self._block_bwd(blk, dcur, g16[j], dalt, g16[j + 1], self.dxc, tmp=self.block_tmps[j], mark_ready=False)
             dcur, dalt = dalt, dcur
-        o.embed_bwd(tokens, dcur, g["embed.weight"])
+        o.embed_bwd(tokens, dcur, g["embed.weight"], self.embed_accum)
         self._grad_ready(*self.trainable)
         self._finish_backward()
 
@@ -747,7 +751,7 @@ class TrainEngine:
                 self._block_bwd(blk, dcur, g16[n_tail + j], dalt, g16[n_tail + j + 1], self.dxc, tmp=self.block_tmps[n_tail + j])
                 dcur, dalt = dalt, dcur
             defer(False)
-        o.embed_bwd(tokens, dcur, g["embed.weight"])
+        o.embed_bwd(tokens, dcur, g["embed.weight"], self.embed_accum)
         self._grad_ready("embed.weight")
         if hot is not None:
             torch.cuda.current_stream(self.device).wait_stream(hot)
@@ -810,36 +814,51 @@ class TrainEngine:
         self._run_step_kernels(optimizer=False)
         return self._assemble_loss(), self.grads
 
-    def _fetch_results(self) -> dict[str, torch.Tensor]:
-        """One device-to-host round trip for everything the host reads after a step: the copies are queued into
-        pinned buffers behind the step's kernels and a single stream synchronisation waits for all of them."""
-        B, k_a = self.B, self.audit_k or 0
-        if self._host is None:
-            pin = self.device.type == "cuda"
-            self._host_flat = torch.empty(self._results.shape, dtype=torch.float32, pin_memory=pin)
-            self._host_status = torch.zeros(1, dtype=torch.int32, pin_memory=pin)
-            h, r0 = self._host_flat, 8 + 2 * B
-            self._host = {"scalars": h[0:8], "loss_per_sample": h[8:8 + B], "recipe_id": h[8 + B:8 + 2 * B].view(torch.int32),
-                          "terms": h[r0:r0 + 4 * k_a].view(k_a, 4), "exact_loss": h[r0 + 4 * k_a:r0 + 5 * k_a],
-                          "kl_sum": h[r0 + 5 * k_a:r0 + 5 * k_a + 1]}
-        self._host_flat.copy_(self._results, non_blocking=True)
-        if hasattr(self.ops, "status"):
-            self._host_status.copy_(self.ops.status, non_blocking=True)
-        if self.audit is not None:
-            # host work for the NEXT step (the seeded permutation of its audited subset) while the device finishes this one
-            self.audit.prepare(self.tr.seed + 10_000 + self.global_step + 1)
-        if self.device.type == "cuda":
-            torch.cuda.current_stream(self.device).synchronize()
-        if int(self._host_status[0]) != 0:
-            self.ops.check_status()                          # raises with the decoded device status
-        return self._host
+    def _host_slot(self, i: int) -> dict[str, Any]:
+        """Pinned host buffers for the results of one in-flight step (two slots alternate)."""
+        if self._host_slots is None:
+            self._host_slots = [None, None]
+        if self._host_slots[i] is None:
+            B, k_a = self.B, self.audit_k or 0
+            cuda = self.device.type == "cuda"
+            h = torch.empty(self._results.shape, dtype=torch.float32, pin_memory=cuda)
+            r0 = 8 + 2 * B
+            self._host_slots[i] = {
+                "flat": h, "status": torch.zeros(1, dtype=torch.int32, pin_memory=cuda),
+                "event": torch.cuda.Event() if cuda else None,
+                "scalars": h[0:8], "loss_per_sample": h[8:8 + B], "recipe_id": h[8 + B:8 + 2 * B].view(torch.int32),
+                "terms": h[r0:r0 + 4 * k_a].view(k_a, 4), "exact_loss": h[r0 + 4 * k_a:r0 + 5 * k_a],
+                "kl_sum": h[r0 + 5 * k_a:r0 + 5 * k_a + 1]}
+        return self._host_slots[i]
 
-    def _assemble_loss(self) -> float:
-        host = self._fetch_results()
+    def _queue_fetch(self) -> dict[str, Any]:
+        """Queues, behind the step's kernels, the one device-to-host copy of everything the host reads after a step
+        (plus the status word) into the next pinned slot, and records the event `_wait_fetch` waits on."""
+        slot = self._host_slot(self._slot_next)
+        self._slot_next ^= 1
+        slot["flat"].copy_(self._results, non_blocking=True)
+        if hasattr(self.ops, "status"):
+            slot["status"].copy_(self.ops.status, non_blocking=True)
+        if slot["event"] is not None:
+            slot["event"].record(torch.cuda.current_stream(self.device))
+        slot["chosen"] = self.audit.last_chosen if self.audit is not None else None
+        return slot
+
+    def _wait_fetch(self, slot: dict[str, Any]) -> dict[str, Any]:
+        if slot["event"] is not None:
+            slot["event"].synchronize()
+        if int(slot["status"][0]) != 0:
+            self.ops.check_status()                          # raises with the decoded device status
+        self._host = slot
+        return slot
+
+    def _assemble_loss(self, host: dict[str, Any] | None = None) -> float:
+        if host is None:
+            host = self._wait_fetch(self._queue_fetch())
         vals = host["scalars"]
         loss = float(vals[0]) / (self.B * self.S)          # this rank's shard
         if self.audit is not None:
-            terms = self.audit.loss_terms(host["loss_per_sample"], host)
+            terms = self.audit.loss_terms(host["loss_per_sample"], host, host["chosen"])
             loss += terms["correction"] / (self.B * self.S) + sum(terms["aux"].values())
             self.last_audit = terms
         if not self.dense and not self.tr.disable_router_aux:
@@ -847,25 +866,62 @@ class TrainEngine:
             loss += (float(vals[1]) + float(vals[2])) * self.world + cover
         return loss
 
-    def train_step(self, batch) -> TrainStepResult:
-        """One optimiser step on a [B,S] int64 (tokens, targets) batch held on the host or the device."""
+    MAX_IN_FLIGHT = 2
+
+    def submit(self, batch) -> None:
+        """Queues one optimiser step on a [B,S] int64 (tokens, targets) batch and returns without waiting for the
+        device: the batch copy, the step's kernels (one graph replay) and the copy of its results into pinned host
+        memory are all stream-ordered.  At most `MAX_IN_FLIGHT` steps may be queued before `collect` is called;
+        a host batch must stay untouched until its step has been collected."""
+        if len(self._pending) >= self.MAX_IN_FLIGHT:
+            raise RuntimeError(f"{len(self._pending)} steps already in flight: call collect() first")
         self._load_batch(batch)
         self._run_step_kernels(optimizer=True)
-        loss = self._assemble_loss()
+        self._pending.append(self._queue_fetch())
+        self.global_step += 1
+        if self.audit is not None:
+            # host work for the NEXT step (the seeded permutation of its audited subset) while the device runs this one
+            self.audit.prepare(self.tr.seed + 10_000 + self.global_step)
+
+    def collect(self) -> TrainStepResult:
+        """Waits for the oldest queued step and returns its loss and metrics (steps complete in submission order)."""
+        if not self._pending:
+            raise RuntimeError("no step in flight")
+        host = self._wait_fetch(self._pending.pop(0))
+        loss = self._assemble_loss(host)
         metrics: dict[str, Any] = {"mode": self.tr.mode, "loss": loss}
         if not self.dense:
-            ids = self._host["recipe_id"].long()
+            ids = host["recipe_id"].long()
             counts = torch.bincount(ids, minlength=self.cfg.recipe_count).float()
             self.usage_ema.mul_(self.tr.coverage_beta).add_(counts / counts.sum().clamp_min(1.0), alpha=1.0 - self.tr.coverage_beta)
             metrics["unique_recipes_per_batch"] = int(ids.unique().numel())
             metrics.update(self._budget)
-        self.global_step += 1
         self.tokens_seen += self.B * self.S
         metrics["tokens_seen"] = self.tokens_seen
         return TrainStepResult(loss=loss, metrics=metrics)
 
+    def train_step(self, batch) -> TrainStepResult:
+        """One optimiser step on a [B,S] int64 (tokens, targets) batch held on the host or the device."""
+        if self._pending:
+            raise RuntimeError("steps are in flight: collect() them before a synchronous train_step")
+        self.submit(batch)
+        return self.collect()
+
+    def train_steps(self, batches):
+        """Pipelined loop over an iterable of batches: yields one TrainStepResult per batch, in order, keeping
+        `MAX_IN_FLIGHT` steps queued so that the host's work for a step (batch copy, launch, result read-back)
+        overlaps the device's work on the one before.  Same arithmetic as calling `train_step` per batch."""
+        for batch in batches:
+            if len(self._pending) >= self.MAX_IN_FLIGHT:
+                yield self.collect()
+            self.submit(batch)
+        while self._pending:
+            yield self.collect()
+
     # ------------------------------------------------------------------ state
     def state_dict(self) -> dict[str, torch.Tensor]:
+        if self._pending:
+            raise RuntimeError("steps are in flight: collect() them before reading the parameters")
         return {n: t.detach().clone() for n, t in self.params.items()}
 
     def backend_status(self) -> dict[str, object]:

@@ -162,8 +162,11 @@ class CudaOps:
         self._call("rte_embed_fwd", _ptr(tokens), _ptr(table), _ptr(out), tokens.numel(), table.shape[1],
                    table.shape[0], _ptr(self.status), self.stream)
 
-    def embed_bwd(self, tokens, dx, dtable) -> None:
-        self._call("rte_embed_bwd", _ptr(tokens), _ptr(dx), _ptr(dtable), tokens.numel(), dtable.shape[1],
+    def embed_bwd(self, tokens, dx, dtable, accum) -> None:
+        """`accum`: int64 scratch of dtable.numel() elements (fixed-point meeting place of the scatter-add)."""
+        if accum.dtype != torch.int64 or accum.numel() < dtable.numel():
+            raise ValueError("embed_bwd: accum must be int64 with at least dtable.numel() elements")
+        self._call("rte_embed_bwd", _ptr(tokens), _ptr(dx), _ptr(dtable), _ptr(accum), tokens.numel(), dtable.shape[1],
                    dtable.shape[0], _ptr(self.status), self.stream)
 
     def rmsnorm_fwd(self, x, w, y_bf16, rstd, *, y_f32=None, film_gamma=None, film_beta=None, eps: float = 1e-5,

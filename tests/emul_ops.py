@@ -112,7 +112,7 @@ class EmulOps:
         self.launches += 1
         out.copy_(table[tokens.view(-1)])
 
-    def embed_bwd(self, tokens, dx, dtable):
+    def embed_bwd(self, tokens, dx, dtable, accum=None):
         self.launches += 1
         dtable.index_add_(0, tokens.view(-1), dx)
 

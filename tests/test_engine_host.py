@@ -118,6 +118,33 @@ def test_engine_sequence_matches_oracle(name):
         assert torch.equal(eng.params[n], params[n]), n
 
 
+@pytest.mark.parametrize("name", ["macro_audit_two_banks", "macro_shortlist"])
+def test_pipelined_train_steps_equal_synchronous_steps(name):
+    """`train_steps` keeps two steps queued; losses, metrics and weights must be those of one `train_step` per batch
+    (per-step seeds, the audited subset of each step and the usage average all advance in submission order)."""
+    cfg, _, _ = _pair(name)
+    tr = cfg.training
+    params = init_parameters(cfg.model, seed=tr.seed, num_clusters=cfg.output.num_clusters)
+    stream = O.zipf_tokens(tr.batch_size * tr.seq_len * 5 + 1, cfg.model.vocab_size, seed=tr.seed)
+    batches = [b for _, b in zip(range(5), O.batches(stream, tr.batch_size, tr.seq_len))]
+    a = TrainEngine(cfg, {k: v.clone() for k, v in params.items()}, device="cpu", ops=EmulOps(), use_cuda_graph=False)
+    b = TrainEngine(cfg, {k: v.clone() for k, v in params.items()}, device="cpu", ops=EmulOps(), use_cuda_graph=False)
+    ra = [a.train_step(x) for x in batches]
+    rb = list(b.train_steps(iter(batches)))
+    assert [r.loss for r in ra] == [r.loss for r in rb]
+    assert ra[-1].metrics == rb[-1].metrics and a.global_step == b.global_step == 5
+    for n in a.params:
+        assert torch.equal(a.params[n], b.params[n]), n
+    b.submit(batches[0]); b.submit(batches[1])
+    with pytest.raises(RuntimeError, match="in flight"):
+        b.submit(batches[2])
+    with pytest.raises(RuntimeError, match="in flight"):
+        b.train_step(batches[2])
+    b.collect(); b.collect()
+    with pytest.raises(RuntimeError, match="no step in flight"):
+        b.collect()
+
+
 def test_hot_budget_matches_reference_estimators_and_enforces_limits():
     """training.py:707-740 / metrics.py:69-94, pinned to values the reference computed for BASELINE config 1."""
     from pathlib import Path

@@ -206,9 +206,16 @@ def test_embedding_fwd_bwd(ops):
     ops.embed_fwd(tok.to(DEV), table.to(DEV), out)
     assert torch.equal(out.cpu(), table[tok])
     dt = torch.zeros(V, d, device=DEV)
-    ops.embed_bwd(tok.to(DEV), dx.to(DEV), dt)
+    acc = torch.full((V * d,), 12345, dtype=torch.int64, device=DEV)      # scratch: any contents
+    ops.embed_bwd(tok.to(DEV), dx.to(DEV), dt, acc)
     torch.cuda.synchronize()
     _close(dt, torch.zeros(V, d).index_add_(0, tok, dx), 1e-5, "embedding grad")
+    # order-free accumulation: a second run is identical bit for bit, and accumulates onto what is there
+    dt2 = torch.zeros(V, d, device=DEV)
+    ops.embed_bwd(tok.to(DEV), dx.to(DEV), dt2, acc)
+    assert torch.equal(dt, dt2)
+    ops.embed_bwd(tok.to(DEV), dx.to(DEV), dt2, acc)
+    _close(dt2, 2 * torch.zeros(V, d).index_add_(0, tok, dx), 1e-5, "embedding grad accumulates")
 
 
 # ------------------------------------------------------------------ attention (+RoPE)

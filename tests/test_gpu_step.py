@@ -159,6 +159,21 @@ def test_graph_replay_equals_eager():
         assert abs(a - b) <= 1e-4 * abs(a)
 
 
+def test_pipelined_train_steps_equal_synchronous_steps():
+    """Two steps in flight (`train_steps`) against one `train_step` per batch, graph replays, pinned host batches:
+    identical losses and weights, with an audited sample per step."""
+    model, train = CASES["macro_audit_two_banks"]
+    cfg, params, a = _engine(model, train)
+    _, _, b = _engine(model, train)
+    batches = [tuple(t.pin_memory() for t in x) for _, x in zip(range(8), _stream(cfg, 9))]
+    ra = [a.train_step(x).loss for x in batches]
+    rb = [r.loss for r in b.train_steps(iter(batches))]
+    assert ra == rb
+    assert a.global_step == b.global_step == 8 and a.tokens_seen == b.tokens_seen
+    for n in a.params:
+        assert torch.equal(a.params[n], b.params[n]), n
+
+
 def test_c3_shapes_one_step_finite_and_close():
     """BASELINE configs[2] shapes without the audited sample: one step against the fp32 oracle."""
     model = dict(vocab_size=2048, d_model=512, n_heads=8, d_ff=2048, n_prelude=1, n_coda=1, t_max=4, depth_choices=(1, 2, 4),
