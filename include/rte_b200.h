@@ -406,6 +406,14 @@ int rte_macro_distill(const float* hot, const float* exact, const float* h0, flo
 int rte_kl_distill(const void* hot_logits, const void* exact_logits, float temp, float coef, const int32_t* idx,
                    int32_t S, void* dlogits_hot, int32_t ld_dlogits, float* kl_rows, int32_t rows, int32_t V,
                    rte_stream_t stream);
+/* The same term with the gradient kept apart: dgrad f32 [rows, V] = coef*(p_hot - p_exact), to be added to the hot
+ * dlogits by rte_add_rows_f32_to_bf16 once the hot pass's cross-entropy kernel has written them (the two then run
+ * on different streams; the sum and its single bf16 rounding are those of rte_kl_distill).                        */
+int rte_kl_distill_grad(const void* hot_logits, const void* exact_logits, float temp, float coef, float* dgrad,
+                        float* kl_rows, int32_t rows, int32_t V, rte_stream_t stream);
+/* dst[(idx[r / S] * S + r % S) * ld + c] = bf16(dst[...] + src[r * V + c]),  r < rows, c < V                      */
+int rte_add_rows_f32_to_bf16(void* dst_bf16, int32_t ld, const int32_t* idx, int32_t S, const float* src, int32_t rows,
+                             int32_t V, rte_stream_t stream);
 
 /* Global gradient norm and clip coefficient WITHOUT any caller-provided or allocated scratch.
  * (No counterpart in the reference: it exists for embedders of this library, see below.)

@@ -132,6 +132,8 @@ PROTOTYPES = {
     "rte_scaled_residual_bwd": (C.c_int, [c_vp] * 9 + [c_i32, P(c_i32), c_i32, c_i64, c_vp]),
     "rte_macro_distill": (C.c_int, [c_vp, c_vp, c_vp, c_f32, c_f32, c_f32, c_f32, c_vp, c_vp, c_i32, c_i32, c_i32, c_vp]),
     "rte_kl_distill": (C.c_int, [c_vp, c_vp, c_f32, c_f32, c_vp, c_i32, c_vp, c_i32, c_vp, c_i32, c_i32, c_vp]),
+    "rte_kl_distill_grad": (C.c_int, [c_vp, c_vp, c_f32, c_f32, c_vp, c_vp, c_i32, c_i32, c_vp]),
+    "rte_add_rows_f32_to_bf16": (C.c_int, [c_vp, c_i32, c_vp, c_i32, c_vp, c_i32, c_i32, c_vp]),
     "rte_grad_norm_multi_tensor_static": (C.c_int, [c_vp, c_i64, c_vp, c_vp, c_vp, c_f32, c_vp, c_vp]),
 }
 

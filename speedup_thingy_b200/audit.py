@@ -99,6 +99,7 @@ class AuditReplay:
         self.loss_tok, self.exact_loss = e(Ma), e(n)
         self.hot_end = e(Ma, d)
         self.terms, self.dhot_extra, self.kl_rows, self.kl_sum = e(n, 4), e(Ma, d), e(Ma), e(1)
+        self.dkl = e(Ma, V)
         self.row_weight_a = torch.full((n,), 1.0 / (eng.B * eng.S * eng.world) / self.p_inc, dtype=f32, device=dev)
         # backward scratch
         self.dn_f32, self.dh0_acc, self.dcur, self.dalt = e(Ma, d), e(Ma, d), e(Ma, d), e(Ma, d)
@@ -126,6 +127,27 @@ class AuditReplay:
                          .view(eng.params[nm].shape) for nm in names}
         self.g_embed = e(*eng.params["embed.weight"].shape)
         self.g_shared["embed.weight"] = self.g_embed
+        # The replay also carries the gradient of ITS h0 rows back through the prelude and the embedding on its own
+        # stream (few-row launches over copies of the hot pass's saved activations), so the hot backward never waits
+        # for the replay before its own prelude backward; the two shares meet just before the optimiser.
+        # (gather_rows moves 16-byte units: the per-sample rows of rstd / lse need S % 4 == 0.)
+        self.own_prelude = (not direct_grads) and len(eng.prelude) > 0 and S % 4 == 0
+        if self.own_prelude:
+            pnames = [nm for nm in eng.grads if nm.startswith("prelude.")]
+            plo = min(eng._grad_offsets[nm] for nm in pnames)
+            phi = max(eng._grad_offsets[nm] + -(-eng.params[nm].numel() // 64) * 64 for nm in pnames)
+            self.prelude_range = (plo, phi)
+            self.prelude_flat = e(phi - plo)
+            for nm in pnames:
+                o0 = eng._grad_offsets[nm] - plo
+                self.g_shared[nm] = self.prelude_flat[o0:o0 + eng.params[nm].numel()].view(eng.params[nm].shape)
+            self.prelude_a = [_Block(f"prelude.{i}@audit", Ma, cfg, n, S, dev) for i in range(len(eng.prelude))]
+            self.prelude_x_in = [e(Ma, d) for _ in eng.prelude]
+            self.prelude_tmps = [_Temps(Ma, cfg, dev) for _ in eng.prelude]
+            self.tokens_a = e(Ma, dtype=torch.int64)
+            self.dpre, self.dpre_u = e(Ma, d), e(Ma, d)
+            self.dpre16 = [e(Ma, d, dtype=bf) for _ in range(len(eng.prelude) + 1)]
+            self.embed_accum = torch.zeros(V * d, dtype=torch.int64, device=dev)
         if direct_grads:
             self.g_shared = eng.grads
         big = max(eng.ops.pick_splits(mm, nn, Ma) * mm * nn
@@ -167,27 +189,44 @@ class AuditReplay:
         self.last_chosen = chosen
 
     # ------------------------------------------------------------------ forward
-    def forward_replay(self, h0: torch.Tensor) -> None:
-        """Everything of the replay's forward that needs only h0 and the routing decisions."""
+    def forward_replay_head(self, h0: torch.Tensor) -> None:
+        """The part of the replay's forward that needs h0 but no routing decision yet: the gathers, the first norm and
+        the first pass's QKV product and attention (the recipe's column mask only enters after the attention), so it
+        can run beside the router."""
         eng = self.eng
         o, cfg, p, sh = eng.ops, eng.cfg, eng.params, eng.shadow
-        n, S, T, Ma, d, f, V = self.n, self.S, self.T, self.Ma, cfg.d_model, cfg.d_ff, cfg.vocab_size
+        n, S, Ma, d = self.n, self.S, self.Ma, cfg.d_model
         o.gather_rows(h0, self.idx, self.h0a, n, S * d * 4)
         o.gather_rows(h0, self.idx, self.h[0], n, S * d * 4)
         o.gather_rows(eng.targets, self.idx, self.targets_a, n, S * 8)
+        alpha = p["core.alpha_inj"].view(1)
+        o.residual_rmsnorm_fwd(self.h[0], self.h0a, alpha, self.ht[0], p["core.norm1.weight"], self.n1[0], self.rstd1[0],
+                               S=S, film_gamma=p["core.pass_gamma1"][0], film_beta=p["core.pass_beta1"][0])
+        for bk in range(cfg.attn_banks):
+            o.gemm(self.n1[0], sh["core.attn.wqkv"][bk], self.qkv[0][bk], M=Ma, N=3 * d, K=d, b_mn=True)
+            o.attn_fwd(self.qkv[0][bk], self.y[0][bk], self.lse[0][bk], B=n, S=S, n_heads=cfg.n_heads, head_dim=cfg.head_dim)
+
+    def forward_replay(self, h0: torch.Tensor, head_done: bool = False) -> None:
+        """Everything of the replay's forward that needs only h0 and the routing decisions (`head_done`: the caller
+        has already issued `forward_replay_head`)."""
+        eng = self.eng
+        o, cfg, p, sh = eng.ops, eng.cfg, eng.params, eng.shadow
+        n, S, T, Ma, d, f, V = self.n, self.S, self.T, self.Ma, cfg.d_model, cfg.d_ff, cfg.vocab_size
+        if not head_done:
+            self.forward_replay_head(h0)
         o.audit_route(eng.route["recipe_id_by_pass"], eng.route["depth"], self.idx, self.rid, self.active, n, T)
         alpha = p["core.alpha_inj"].view(1)
         # The residual updates ride in front of the norms (one launch each instead of two or three):
         #   ht = h + alpha*h0 -> norm1;   u = ht + s_attn*attn -> norm2;
         #   h' = active ? u + s_mlp*mlp : h, then ht' = h' + alpha*h0 -> next pass's norm1
         film1 = lambda t: dict(film_gamma=p["core.pass_gamma1"][t], film_beta=p["core.pass_beta1"][t])  # noqa: E731
-        o.residual_rmsnorm_fwd(self.h[0], self.h0a, alpha, self.ht[0], p["core.norm1.weight"], self.n1[0], self.rstd1[0],
-                               S=S, **film1(0))
         for t in range(T):
             rid = self.rid[t]
             for bk in range(cfg.attn_banks):
-                o.gemm(self.n1[t], sh["core.attn.wqkv"][bk], self.qkv[t][bk], M=Ma, N=3 * d, K=d, b_mn=True)
-                o.attn_fwd(self.qkv[t][bk], self.y[t][bk], self.lse[t][bk], B=n, S=S, n_heads=cfg.n_heads, head_dim=cfg.head_dim)
+                if t > 0:           # pass 0: issued by forward_replay_head
+                    o.gemm(self.n1[t], sh["core.attn.wqkv"][bk], self.qkv[t][bk], M=Ma, N=3 * d, K=d, b_mn=True)
+                    o.attn_fwd(self.qkv[t][bk], self.y[t][bk], self.lse[t][bk], B=n, S=S, n_heads=cfg.n_heads,
+                               head_dim=cfg.head_dim)
                 o.colmask_mul(self.y[t][bk], rid, self.head_tab[bk], S, self.ym[t][bk], Ma, d)
                 o.gemm(self.ym[t][bk], sh["core.attn.wo"][bk], self.attn_acc[t], M=Ma, N=d, K=d, b_mn=True,
                        epilogue=A.EPI_F32, residual=self.attn_acc[t] if bk > 0 else None)
@@ -225,15 +264,28 @@ class AuditReplay:
         o.macro_distill(self.hot_end, self.h[T], self.h0a, tr.lambda_delta_dir * w, tr.lambda_delta_rms * w,
                         tr.lambda_endpoint_normed * w, tr.lambda_endpoint_raw * w, self.terms, self.dhot_extra, n, S, d)
 
-    def forward_losses(self) -> None:
-        """Needs the hot pass's cross entropy to be done: KL term into the hot dlogits, then the replay's own CE."""
+    def forward_kl(self) -> None:
+        """KL-distillation term between the saved hot logits of the audited rows and the replay's logits; its gradient
+        goes to `self.dkl` (the hot pass adds it to its dlogits with `add_kl_grad` once its own cross-entropy kernel
+        has written them, so this launch can run beside that kernel)."""
         eng = self.eng
         o, cfg, tr, w = eng.ops, eng.cfg, eng.tr, 1.0 / eng.world
-        n, S, Ma, V = self.n, self.S, self.Ma, cfg.vocab_size
+        n, Ma, V = self.n, self.Ma, cfg.vocab_size
         temp = max(float(tr.distill_temperature), 1e-6)
         if not eng.shortlist:      # the shortlist head keeps no full hot logits, so the KL term is absent (models.py:698-703)
-            o.kl_distill(self.hot_logits, self.logits, temp, tr.lambda_kl * w * temp / n, self.idx, S, eng.logits, self.kl_rows, Ma, V)
+            o.kl_distill_grad(self.hot_logits, self.logits, temp, tr.lambda_kl * w * temp / n, self.dkl, self.kl_rows, Ma, V)
             o.segment_sum(self.kl_rows, self.kl_sum, 1, Ma)
+
+    def add_kl_grad(self) -> None:
+        """Hot-pass side of `forward_kl`: dlogits[audited rows] += dkl."""
+        eng = self.eng
+        if not eng.shortlist:
+            eng.ops.add_rows_to_bf16(eng.logits, self.idx, self.S, self.dkl, self.Ma, eng.cfg.vocab_size)
+
+    def forward_ce(self) -> None:
+        """The replay's own cross entropy (its logits become dlogits in place)."""
+        eng = self.eng
+        o, n, S = eng.ops, self.n, self.S
         o.ce_fwd_bwd(self.logits, self.targets_a, self.row_weight_a, S, self.loss_tok, self.logits)
         o.segment_sum(self.loss_tok, self.exact_loss, n, S)
 
@@ -340,17 +392,58 @@ class AuditReplay:
         if eng._param_stream is not None:             # the replay's stream ends only when its weight gradients have
             torch.cuda.current_stream(eng.device).wait_stream(eng._param_stream)
 
-    def merge(self, dh0_hot: torch.Tensor) -> None:
-        """After the join with the hot pass: adds the replay's share of the shared gradients and of d h0."""
+    def gather_prelude(self) -> None:
+        """Copies of what the hot pass's prelude saved for the audited samples (inputs of `backward_prelude`)."""
+        eng = self.eng
+        o, cfg, n, S = eng.ops, eng.cfg, self.n, self.S
+        d, f, H = cfg.d_model, cfg.d_ff, cfg.n_heads
+        o.gather_rows(eng.tokens, self.idx, self.tokens_a, n, S * 8)
+        for hot, mine, x_in in zip(eng.prelude, self.prelude_a, self.prelude_x_in):
+            o.gather_rows(hot.x_in, self.idx, x_in, n, S * d * 4)
+            mine.x_in = x_in
+            for name, row_bytes in (("n1", S * d * 2), ("n2", S * d * 2), ("y", S * d * 2), ("qkv", S * 3 * d * 2),
+                                    ("ug", S * 2 * f * 2), ("z", S * f * 2), ("u", S * d * 4), ("rstd1", S * 4),
+                                    ("rstd2", S * 4), ("lse", H * S * 4)):
+                o.gather_rows(getattr(hot, name), self.idx, getattr(mine, name), n, row_bytes)
+
+    def merge_shared(self) -> None:
+        """Adds the replay's share of the final-norm / coda gradients to the hot pass's (call once both are complete)."""
+        eng = self.eng
+        lo, hi = self.shared_range
+        eng.ops.add_(eng.grad_flat[lo:hi], self.shared_flat)
+
+    def backward_prelude(self) -> None:
+        """d h0 of the audited rows (through the alpha*h0 injections and through h[0]) back through the prelude blocks
+        and the embedding, into the replay's private mirrors of those gradients."""
         eng = self.eng
         o, n, S, d = eng.ops, self.n, self.S, eng.cfg.d_model
-        lo, hi = self.shared_range
-        import contextlib
-        with (o._deferred() if hasattr(o, "_deferred") else contextlib.nullcontext()):
-            o.add_(eng.grad_flat[lo:hi], self.shared_flat)
+        gs = self.g_shared
+        o.add_(self.dh0_acc, self.dh_first)
+        o.cast_bf16(self.dh0_acc, self.dpre16[0])
+        dcur, dalt = self.dh0_acc, self.dpre
+        self._defer_param_grads(True)
+        for j, blk in enumerate(reversed(self.prelude_a)):
+            eng._block_bwd(blk, dcur, self.dpre16[j], dalt, self.dpre16[j + 1], self.dpre_u, tmp=self.prelude_tmps[j],
+                           mark_ready=False, grads=gs, ws=self.ws)
+            dcur, dalt = dalt, dcur
+        self._defer_param_grads(False)
+        o.embed_bwd(self.tokens_a, dcur, self.g_embed, self.embed_accum)
+        if eng._param_stream is not None:
+            torch.cuda.current_stream(eng.device).wait_stream(eng._param_stream)
+
+    def merge_tail(self, dh0_hot: torch.Tensor | None) -> None:
+        """Last join with the hot pass.  With `own_prelude`: adds the replay's prelude and embedding gradients;
+        otherwise (`dh0_hot` given, before the hot prelude backward) adds the replay's d h0 rows and the embedding
+        share of its logits product."""
+        eng = self.eng
+        o, n, S, d = eng.ops, self.n, self.S, eng.cfg.d_model
         o.add_(eng.grads["embed.weight"], self.g_embed)
-        o.scatter_add_rows(dh0_hot, self.idx, self.dh0_acc, n, S * d)
-        o.scatter_add_rows(dh0_hot, self.idx, self.dh_first, n, S * d)
+        if self.own_prelude:
+            lo, hi = self.prelude_range
+            o.add_(eng.grad_flat[lo:hi], self.prelude_flat)
+        else:
+            o.scatter_add_rows(dh0_hot, self.idx, self.dh0_acc, n, S * d)
+            o.scatter_add_rows(dh0_hot, self.idx, self.dh_first, n, S * d)
 
     # ------------------------------------------------------------------ reporting
     def loss_terms(self, hot_per_sample: torch.Tensor, host: dict, chosen: torch.Tensor | None = None) -> dict[str, float]:

@@ -219,11 +219,13 @@ macro_distill_kernel(const float* __restrict__ hot, const float* __restrict__ ex
   cluster.sync();          // no CTA leaves while rank 0 may still read its shared memory
 }
 
-// One CTA per token row of the audited subset.
+// One CTA per token row of the audited subset.  SEPARATE: the gradient coef*(p_hot - p_exact) goes to the dense f32
+// buffer dsep [rows, V] (added to the hot dlogits later by add_rows_f32_to_bf16_kernel) instead of into dlog.
+template <bool SEPARATE>
 __global__ void __launch_bounds__(NTHR)
 kl_distill_kernel(const __nv_bfloat16* __restrict__ hot, const __nv_bfloat16* __restrict__ exact, float inv_temp, float coef,
-                  const int32_t* __restrict__ idx, int S, __nv_bfloat16* __restrict__ dlog, int ld, float* __restrict__ kl_rows,
-                  int V) {
+                  const int32_t* __restrict__ idx, int S, __nv_bfloat16* __restrict__ dlog, int ld, float* __restrict__ dsep,
+                  float* __restrict__ kl_rows, int V) {
   __shared__ float red[32];
   const int row = blockIdx.x;
   const __nv_bfloat16* hr = hot + (size_t)row * V;
@@ -243,16 +245,28 @@ kl_distill_kernel(const __nv_bfloat16* __restrict__ hot, const __nv_bfloat16* __
   sh = rte::block_sum(sh, red);
   se = rte::block_sum(se, red);
   const float lh = mh + __logf(sh), le = me + __logf(se);
-  __nv_bfloat16* dr = dlog + ((size_t)idx[row / S] * S + (row % S)) * ld;
+  __nv_bfloat16* dr = SEPARATE ? nullptr : dlog + ((size_t)idx[row / S] * S + (row % S)) * ld;
   float kl = 0.f;
   for (int c = threadIdx.x; c < V; c += NTHR) {
     const float lph = __bfloat162float(hr[c]) * inv_temp - lh, lpe = __bfloat162float(er[c]) * inv_temp - le;
     const float ph = __expf(lph), pe = __expf(lpe);
     kl += pe * (lpe - lph);
-    dr[c] = __float2bfloat16_rn(__bfloat162float(dr[c]) + coef * (ph - pe));
+    if (SEPARATE) dsep[(size_t)row * V + c] = coef * (ph - pe);
+    else dr[c] = __float2bfloat16_rn(__bfloat162float(dr[c]) + coef * (ph - pe));
   }
   kl = rte::block_sum(kl, red);
   if (threadIdx.x == 0) kl_rows[row] = kl;
+}
+
+// dst[(idx[row / S] * S + row % S) * ld + c] += src[row * V + c]   (bf16 destination, f32 addend, one rounding)
+__global__ void add_rows_f32_to_bf16_kernel(__nv_bfloat16* __restrict__ dst, int ld, const int32_t* __restrict__ idx, int S,
+                                            const float* __restrict__ src, int rows, int V) {
+  const long long total = (long long)rows * V;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+    const int row = int(i / V), c = int(i % V);
+    __nv_bfloat16* q = dst + ((size_t)idx[row / S] * S + (row % S)) * ld + c;
+    *q = __float2bfloat16_rn(__bfloat162float(*q) + src[i]);
+  }
 }
 
 }  // namespace
@@ -354,9 +368,27 @@ extern "C" int rte_kl_distill(const void* hot_logits, const void* exact_logits, 
                               rte_stream_t stream) {
   RTE_CHECK_ARG(hot_logits && exact_logits && idx && dlogits_hot && kl_rows && temp > 0.f && S > 0 && rows > 0 && V > 0 &&
                 ld_dlogits >= V);
-  kl_distill_kernel<<<rows, NTHR, 0, ST(stream)>>>(reinterpret_cast<const __nv_bfloat16*>(hot_logits),
+  kl_distill_kernel<false><<<rows, NTHR, 0, ST(stream)>>>(reinterpret_cast<const __nv_bfloat16*>(hot_logits),
       reinterpret_cast<const __nv_bfloat16*>(exact_logits), 1.f / temp, coef, idx, S,
-      reinterpret_cast<__nv_bfloat16*>(dlogits_hot), ld_dlogits, kl_rows, V);
+      reinterpret_cast<__nv_bfloat16*>(dlogits_hot), ld_dlogits, nullptr, kl_rows, V);
+  RTE_LAUNCH_CHECK();
+  return RTE_OK;
+}
+
+extern "C" int rte_kl_distill_grad(const void* hot_logits, const void* exact_logits, float temp, float coef, float* dgrad,
+                                   float* kl_rows, int32_t rows, int32_t V, rte_stream_t stream) {
+  RTE_CHECK_ARG(hot_logits && exact_logits && dgrad && kl_rows && temp > 0.f && rows > 0 && V > 0);
+  kl_distill_kernel<true><<<rows, NTHR, 0, ST(stream)>>>(reinterpret_cast<const __nv_bfloat16*>(hot_logits),
+      reinterpret_cast<const __nv_bfloat16*>(exact_logits), 1.f / temp, coef, nullptr, 1, nullptr, 0, dgrad, kl_rows, V);
+  RTE_LAUNCH_CHECK();
+  return RTE_OK;
+}
+
+extern "C" int rte_add_rows_f32_to_bf16(void* dst_bf16, int32_t ld, const int32_t* idx, int32_t S, const float* src,
+                                        int32_t rows, int32_t V, rte_stream_t stream) {
+  RTE_CHECK_ARG(dst_bf16 && idx && src && S > 0 && rows > 0 && V > 0 && ld >= V);
+  add_rows_f32_to_bf16_kernel<<<grid_for((long long)rows * V, NTHR), NTHR, 0, ST(stream)>>>(
+      reinterpret_cast<__nv_bfloat16*>(dst_bf16), ld, idx, S, src, rows, V);
   RTE_LAUNCH_CHECK();
   return RTE_OK;
 }

@@ -212,6 +212,87 @@ phi_da_kernel(const float* __restrict__ dupd, const float* __restrict__ act, con
   }
 }
 
+// ---- Tensor-core versions of the two data-gradient products (taken when d % 8 == 0): TF32 mma with the 3xTF32
+// error compensation, so results stay at fp32 accuracy.
+// Operand fragments of mma.m16n8k8 come straight from global memory: a quad of lanes reads 16 contiguous bytes of a
+// row and the two k-halves of a step complete the 32-byte sector, so no shared-memory staging (and no barrier) is
+// needed; the per-key weights stay in L1/L2.  Warp tile: 16 tokens; a CTA covers TT = 32 tokens of one sample.
+__device__ __forceinline__ uint32_t to_tf32(float x) {
+  uint32_t r;
+  asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(r) : "f"(x));
+  return r;
+}
+
+__device__ __forceinline__ void mma_tf32(float (&c)[4], const uint32_t (&a)[4], const uint32_t (&b)[2]) {
+  asm volatile("mma.sync.aligned.m16n8k8.row.col.f32.tf32.tf32.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+               : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+               : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b[0]), "r"(b[1]));
+}
+
+// fp32-accurate product from TF32 pieces: x = hi + lo with both representable in TF32, and
+// a*b ~= a_lo*b_hi + a_hi*b_lo + a_hi*b_hi (the dropped lo*lo term is below fp32 rounding).
+__device__ __forceinline__ void split_tf32(float x, uint32_t& hi, uint32_t& lo) {
+  hi = to_tf32(x);
+  lo = to_tf32(x - __uint_as_float(hi));
+}
+
+__device__ __forceinline__ void mma_3xtf32(float (&c)[4], const uint32_t (&ah)[4], const uint32_t (&al)[4],
+                                           const uint32_t (&bh)[2], const uint32_t (&bl)[2]) {
+  mma_tf32(c, al, bh);
+  mma_tf32(c, ah, bl);
+  mma_tf32(c, ah, bh);
+}
+
+// da[tok, j] = silu'(act[tok,j]) * sum_c dupd[tok,c] * u[j,c]:  M = tokens, N = rank, K = d.
+// Eight warps = 2 token tiles x 4 column groups; group ng owns rank columns [8ng, 8ng+8) and [8ng+32, 8ng+40).
+__global__ void __launch_bounds__(NTHR)
+phi_da_mma_kernel(const float* __restrict__ dupd, const float* __restrict__ act, const float* __restrict__ u,
+                  const int32_t* __restrict__ rid, const int32_t* __restrict__ sid, float* __restrict__ da, PhiDims D) {
+  const int tiles = rte::ceil_div(D.S, TT);
+  const int b = blockIdx.x / tiles, tok0 = (blockIdx.x % tiles) * TT;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, g = lane >> 2, t = lane & 3;
+  const int mt = warp & 1, ng = warp >> 1;
+  const int n_tiles = rte::ceil_div(D.m, 8);
+  if (ng >= n_tiles) return;                         // warp-uniform; the kernel has no barrier
+  const bool two = ng + 4 < n_tiles;
+  const float* ub = u + key_of(rid, sid, b, D.K) * D.m * D.d;
+  const int r0 = tok0 + mt * 16 + g, r1 = r0 + 8;
+  const bool ok0 = r0 < D.S, ok1 = r1 < D.S;
+  const float* a0p = dupd + ((size_t)b * D.S + (ok0 ? r0 : 0)) * D.d;
+  const float* a1p = dupd + ((size_t)b * D.S + (ok1 ? r1 : 0)) * D.d;
+  const int j0 = ng * 8 + g, j1 = j0 + 32;
+  const bool okb0 = j0 < D.m, okb1 = two && j1 < D.m;
+  const float* b0p = ub + (size_t)(okb0 ? j0 : 0) * D.d;
+  const float* b1p = ub + (size_t)(okb1 ? j1 : 0) * D.d;
+  float c0[4] = {0.f, 0.f, 0.f, 0.f}, c1[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll 4
+  for (int k0 = 0; k0 < D.d; k0 += 8) {
+    uint32_t a[4], al[4], f[2], fl[2];
+    split_tf32(ok0 ? a0p[k0 + t] : 0.f, a[0], al[0]);
+    split_tf32(ok1 ? a1p[k0 + t] : 0.f, a[1], al[1]);
+    split_tf32(ok0 ? a0p[k0 + t + 4] : 0.f, a[2], al[2]);
+    split_tf32(ok1 ? a1p[k0 + t + 4] : 0.f, a[3], al[3]);
+    split_tf32(okb0 ? b0p[k0 + t] : 0.f, f[0], fl[0]);
+    split_tf32(okb0 ? b0p[k0 + t + 4] : 0.f, f[1], fl[1]);
+    mma_3xtf32(c0, a, al, f, fl);
+    if (two) {
+      split_tf32(okb1 ? b1p[k0 + t] : 0.f, f[0], fl[0]);
+      split_tf32(okb1 ? b1p[k0 + t + 4] : 0.f, f[1], fl[1]);
+      mma_3xtf32(c1, a, al, f, fl);
+    }
+  }
+  auto put = [&](int row, int col, float x) {
+    if (row < D.S && col < D.m) {
+      const size_t idx = ((size_t)b * D.S + row) * D.m + col;
+      const float av = act[idx], sg = rte::sigmoid_f(av);
+      da[idx] = x * sg * (1.f + av * (1.f - sg));
+    }
+  };
+  const int col0 = ng * 8 + 2 * t;
+  put(r0, col0, c0[0]); put(r0, col0 + 1, c0[1]); put(r1, col0, c0[2]); put(r1, col0 + 1, c0[3]);
+  if (two) { put(r0, col0 + 32, c1[0]); put(r0, col0 + 33, c1[1]); put(r1, col0 + 32, c1[2]); put(r1, col0 + 33, c1[3]); }
+}
+
 // Per-sample parameter gradients of u, gain, bias:  pu[b][j,c], pg[b][c], pb[b][c].
 __global__ void __launch_bounds__(NTHR)
 phi_pu_kernel(const float* __restrict__ h0, const float* __restrict__ act, const float* __restrict__ dupd,
@@ -395,6 +476,112 @@ phi_dz_kernel(const float* __restrict__ h0, const float* __restrict__ rstd, cons
   }
 }
 
+// dh0[tok,:] += da @ v3^T + rmsnorm_backward(da @ v1^T + dpool[b,:]):  M = tokens, N = d, K = rank (tensor-core form).
+// Eight warps = 2 token tiles x 4 column groups (group cq owns the 8-column tiles cq, cq+4, cq+8, ...).  The whole
+// A operand (16 tokens x rank) lives in registers.  Pass 1 forms the row dot products <dn, xhat>; pass 2 recomputes
+// the tiny products and finishes with one read-modify-write of dh0.
+__global__ void __launch_bounds__(NTHR)
+phi_dz_mma_kernel(const float* __restrict__ h0, const float* __restrict__ rstd, const float* __restrict__ da,
+                  const float* __restrict__ dpool, const float* __restrict__ v, const int32_t* __restrict__ rid,
+                  const int32_t* __restrict__ sid, float* __restrict__ dh0, PhiDims D) {
+  constexpr int KS_MAX = MMAX / 8;
+  __shared__ float sdot[TT][4];
+  const int tiles = rte::ceil_div(D.S, TT);
+  const int b = blockIdx.x / tiles, tok0 = (blockIdx.x % tiles) * TT;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, g = lane >> 2, t = lane & 3;
+  const int mt = warp & 1, cq = warp >> 1;
+  const float* v1 = v + key_of(rid, sid, b, D.K) * 3 * D.d * D.m;
+  const float* v3 = v1 + (size_t)2 * D.d * D.m;
+  const int r0 = tok0 + mt * 16 + g, r1 = r0 + 8;
+  const bool ok0 = r0 < D.S, ok1 = r1 < D.S;
+  const size_t row0 = (size_t)b * D.S + (ok0 ? r0 : 0), row1 = (size_t)b * D.S + (ok1 ? r1 : 0);
+  const int ks_n = rte::ceil_div(D.m, 8);
+  uint32_t a[KS_MAX][4], al[KS_MAX][4];
+#pragma unroll
+  for (int ks = 0; ks < KS_MAX; ++ks) {
+    const int j = ks * 8 + t;
+    const bool in = ks < ks_n;
+    split_tf32((in && ok0 && j < D.m) ? da[row0 * D.m + j] : 0.f, a[ks][0], al[ks][0]);
+    split_tf32((in && ok1 && j < D.m) ? da[row1 * D.m + j] : 0.f, a[ks][1], al[ks][1]);
+    split_tf32((in && ok0 && j + 4 < D.m) ? da[row0 * D.m + j + 4] : 0.f, a[ks][2], al[ks][2]);
+    split_tf32((in && ok1 && j + 4 < D.m) ? da[row1 * D.m + j + 4] : 0.f, a[ks][3], al[ks][3]);
+  }
+  const float rs0 = ok0 ? rstd[row0] : 0.f, rs1 = ok1 ? rstd[row1] : 0.f;
+  const int n_tiles = D.d / 8;
+  const float* dpb = dpool + (size_t)b * D.d;
+  float dot0 = 0.f, dot1 = 0.f;
+  for (int nt = cq; nt < n_tiles; nt += 4) {
+    float c1[4] = {0.f, 0.f, 0.f, 0.f};
+    const float* w1 = v1 + (size_t)(nt * 8 + g) * D.m;
+#pragma unroll
+    for (int ks = 0; ks < KS_MAX; ++ks) {
+      if (ks < ks_n) {
+        const int k = ks * 8 + t;
+        uint32_t f[2], fl[2];
+        split_tf32(k < D.m ? w1[k] : 0.f, f[0], fl[0]);
+        split_tf32(k + 4 < D.m ? w1[k + 4] : 0.f, f[1], fl[1]);
+        mma_3xtf32(c1, a[ks], al[ks], f, fl);
+      }
+    }
+    const int col = nt * 8 + 2 * t;
+    const float2 dp = *reinterpret_cast<const float2*>(dpb + col);
+    if (ok0) {
+      const float2 hx = *reinterpret_cast<const float2*>(h0 + row0 * D.d + col);
+      dot0 += ((c1[0] + dp.x) * hx.x + (c1[1] + dp.y) * hx.y) * rs0;
+    }
+    if (ok1) {
+      const float2 hx = *reinterpret_cast<const float2*>(h0 + row1 * D.d + col);
+      dot1 += ((c1[2] + dp.x) * hx.x + (c1[3] + dp.y) * hx.y) * rs1;
+    }
+  }
+  dot0 += __shfl_xor_sync(0xffffffffu, dot0, 1); dot0 += __shfl_xor_sync(0xffffffffu, dot0, 2);
+  dot1 += __shfl_xor_sync(0xffffffffu, dot1, 1); dot1 += __shfl_xor_sync(0xffffffffu, dot1, 2);
+  if (t == 0) { sdot[mt * 16 + g][cq] = dot0; sdot[mt * 16 + g + 8][cq] = dot1; }
+  __syncthreads();
+  {
+    const float* q0 = sdot[mt * 16 + g];
+    const float* q1 = sdot[mt * 16 + g + 8];
+    dot0 = (q0[0] + q0[1] + q0[2] + q0[3]) / (float)D.d;
+    dot1 = (q1[0] + q1[1] + q1[2] + q1[3]) / (float)D.d;
+  }
+  for (int nt = cq; nt < n_tiles; nt += 4) {
+    float c1[4] = {0.f, 0.f, 0.f, 0.f}, c3[4] = {0.f, 0.f, 0.f, 0.f};
+    const float* w1 = v1 + (size_t)(nt * 8 + g) * D.m;
+    const float* w3 = v3 + (size_t)(nt * 8 + g) * D.m;
+#pragma unroll
+    for (int ks = 0; ks < KS_MAX; ++ks) {
+      if (ks < ks_n) {
+        const int k = ks * 8 + t;
+        uint32_t f[2], fl[2], h[2], hl[2];
+        split_tf32(k < D.m ? w1[k] : 0.f, f[0], fl[0]);
+        split_tf32(k + 4 < D.m ? w1[k + 4] : 0.f, f[1], fl[1]);
+        split_tf32(k < D.m ? w3[k] : 0.f, h[0], hl[0]);
+        split_tf32(k + 4 < D.m ? w3[k + 4] : 0.f, h[1], hl[1]);
+        mma_3xtf32(c1, a[ks], al[ks], f, fl);
+        mma_3xtf32(c3, a[ks], al[ks], h, hl);
+      }
+    }
+    const int col = nt * 8 + 2 * t;
+    const float2 dp = *reinterpret_cast<const float2*>(dpb + col);
+    if (ok0) {
+      const float2 hx = *reinterpret_cast<const float2*>(h0 + row0 * D.d + col);
+      float2* q = reinterpret_cast<float2*>(dh0 + row0 * D.d + col);
+      float2 o = *q;
+      o.x += c3[0] + rs0 * ((c1[0] + dp.x) - hx.x * rs0 * dot0);
+      o.y += c3[1] + rs0 * ((c1[1] + dp.y) - hx.y * rs0 * dot0);
+      *q = o;
+    }
+    if (ok1) {
+      const float2 hx = *reinterpret_cast<const float2*>(h0 + row1 * D.d + col);
+      float2* q = reinterpret_cast<float2*>(dh0 + row1 * D.d + col);
+      float2 o = *q;
+      o.x += c3[2] + rs1 * ((c1[2] + dp.x) - hx.x * rs1 * dot1);
+      o.y += c3[3] + rs1 * ((c1[3] + dp.y) - hx.y * rs1 * dot1);
+      *q = o;
+    }
+  }
+}
+
 // out[key][e] = sum over samples b with key(b) == key, in sample order, of partial[b][e]   (blockIdx.y = key)
 __global__ void __launch_bounds__(NTHR)
 phi_reduce_keys_kernel(const float* __restrict__ partial, const int32_t* __restrict__ rid, const int32_t* __restrict__ sid,
@@ -483,11 +670,14 @@ extern "C" int rte_macro_phi_bwd_data(const float* h0, const float* dout, const 
     phi_out_kernel<1, 64><<<B * tiles, NTHR, 0, ST(stream)>>>(h0, act, p->gain, p->u, p->bias, p->scale, recipe_id, stride_id,
                                                               s_cfg, dout, dh0, x.dupd, D);
   RTE_LAUNCH_CHECK();
-  phi_da_kernel<<<B * tiles, NTHR, 0, ST(stream)>>>(x.dupd, act, p->u, recipe_id, stride_id, x.da, D);
+  const bool mma = d % 8 == 0;          // tensor-core (TF32) products; odd widths keep the scalar kernels
+  if (mma) phi_da_mma_kernel<<<B * tiles, NTHR, 0, ST(stream)>>>(x.dupd, act, p->u, recipe_id, stride_id, x.da, D);
+  else phi_da_kernel<<<B * tiles, NTHR, 0, ST(stream)>>>(x.dupd, act, p->u, recipe_id, stride_id, x.da, D);
   RTE_LAUNCH_CHECK();
   phi_dpool_kernel<<<B, NTHR, 0, ST(stream)>>>(x.da, p->v, recipe_id, stride_id, x.dpool, D);
   RTE_LAUNCH_CHECK();
-  phi_dz_kernel<<<B * tiles, NTHR, 0, ST(stream)>>>(h0, rstd, x.da, x.dpool, p->v, recipe_id, stride_id, dh0, D);
+  if (mma) phi_dz_mma_kernel<<<B * tiles, NTHR, 0, ST(stream)>>>(h0, rstd, x.da, x.dpool, p->v, recipe_id, stride_id, dh0, D);
+  else phi_dz_kernel<<<B * tiles, NTHR, 0, ST(stream)>>>(h0, rstd, x.da, x.dpool, p->v, recipe_id, stride_id, dh0, D);
   RTE_LAUNCH_CHECK();
   return RTE_OK;
 }

@@ -12,6 +12,8 @@ PyTorch is used for device memory, streams and graph capture only.
 """
 from __future__ import annotations
 
+import os
+
 import math
 from dataclasses import dataclass, field
 from typing import Any
@@ -194,7 +196,6 @@ class TrainEngine:
             # which must not happen inside stream capture: run the first steps launch by launch, and capture
             # the collective-bearing graph afterwards (RTE_DP_GRAPH=0 keeps every step eager).  A process that holds
             # such a graph should call close() before it destroys the process group.
-            import os
             self._eager_steps_left = 3
             if os.environ.get("RTE_DP_GRAPH", "1") == "0":
                 self.use_cuda_graph = False
@@ -260,7 +261,7 @@ class TrainEngine:
         self._bucket_of: dict[str, int] = {}
         self._bucket_pending: list[int] = []
         self._bucket_size: list[int] = []
-        import os as _os
+        _os = os
         bucket_cap_mb = float(_os.environ.get("RTE_BUCKET_MB", bucket_cap_mb))
         cap = max(int(bucket_cap_mb * 1024 * 1024 / 4), 1)
         start = 0
@@ -321,6 +322,10 @@ class TrainEngine:
         # SMs that attention / norm / macro-operator kernels leave idle).  What they read must then outlive the chain's
         # reuse of scratch: every block gets its own scratch set and its own bf16 input-gradient buffer.
         self._hot_param_stream = torch.cuda.Stream(device=dev) if (dev.type == "cuda" and hasattr(ops, "param_stream")) else None
+        # The parameter-gradient halves of the macro operator and of the router (long SIMT kernels) get a stream of
+        # their own, so that the weight-gradient GEMMs keep following the data-gradient chain closely.
+        self._misc_param_stream = (torch.cuda.Stream(device=dev)
+                                   if (self._hot_param_stream is not None and not self.dense) else None)
         n_blocks = len(self.blocks) if self.dense else cfg.n_prelude + cfg.n_coda
         if self._hot_param_stream is not None:
             self.block_tmps = [self.tmp] + [_Temps(M, cfg, dev) for _ in range(n_blocks - 1)]
@@ -369,7 +374,7 @@ class TrainEngine:
         # hot-pass kernel to drain (measured: -2.5 % step time).
         self._side_stream = torch.cuda.Stream(device=dev, priority=-1) if (self.audit_k and dev.type == "cuda") else None
         if self._side_stream is not None and hasattr(ops, "gemm_max_ctas"):
-            ops.gemm_max_ctas = max(ops.sm_count - 8, 1)
+            ops.gemm_max_ctas = max(ops.sm_count - int(os.environ.get("RTE_SIDE_SMS", "8")), 1)
         self._param_stream = torch.cuda.Stream(device=dev) if (self.audit_k and dev.type == "cuda") else None
         self.exact_core = None
         if self.exact:
@@ -426,13 +431,17 @@ class TrainEngine:
 
     def _begin_backward(self) -> None:
         self._bucket_pending = list(self._bucket_size)
+        self._ready_events: list = []
 
-    def _grad_ready(self, *names: str) -> None:
+    def _grad_ready(self, *names: str, after=None) -> None:
         """Marks gradients as final; a bucket whose last gradient arrived is summed across ranks on the
-        communication stream (NCCL over NVLink) while the compute stream carries on with backward."""
+        communication stream (NCCL over NVLink) while the compute stream carries on with backward.
+        `after`: an event (recorded on another stream) that these gradients additionally depend on."""
         if self.world == 1 or self._dp_paused:
             return
         import torch.distributed as dist
+        if after is not None:
+            self._ready_events.append(after)      # every later bucket launch of this step waits for it too (cheap, monotone)
         for n in names:
             i = self._bucket_of[n]
             self._bucket_pending[i] -= 1
@@ -443,8 +452,12 @@ class TrainEngine:
                     dist.all_reduce(view, op=dist.ReduceOp.SUM, group=self.pg)
                 else:
                     self._comm_stream.wait_stream(torch.cuda.current_stream(self.device))
+                    for ev in self._ready_events:
+                        self._comm_stream.wait_event(ev)
                     if self._hot_param_stream is not None:       # weight gradients are produced there
                         self._comm_stream.wait_stream(self._hot_param_stream)
+                    if self._misc_param_stream is not None:
+                        self._comm_stream.wait_stream(self._misc_param_stream)
                     with torch.cuda.stream(self._comm_stream):
                         dist.all_reduce(view, op=dist.ReduceOp.SUM, group=self.pg)
 
@@ -463,7 +476,16 @@ class TrainEngine:
         if self._side_stream is not None:
             self._side_stream.wait_stream(torch.cuda.current_stream(self.device))
 
-    def _main_wait_side(self) -> None:
+    def _side_event(self):
+        """An event at the current end of the replay's stream (None without one: single-stream order then holds)."""
+        if self._side_stream is None:
+            return None
+        ev = torch.cuda.Event()
+        ev.record(self._side_stream)
+        return ev
+
+    def _main_wait_side(self, event=None) -> None:
+        """The hot pass waits for the replay's stream (or only for `event` recorded on it)."""
         if self._side_stream is None:
             return
         main = torch.cuda.current_stream(self.device)
@@ -471,7 +493,10 @@ class TrainEngine:
         if probes is not None:
             e0 = torch.cuda.Event(enable_timing=True, external=True)
             e0.record(main)
-        main.wait_stream(self._side_stream)
+        if event is not None:
+            main.wait_event(event)
+        else:
+            main.wait_stream(self._side_stream)
         if probes is not None:
             e1 = torch.cuda.Event(enable_timing=True, external=True)
             e1.record(main)
@@ -614,15 +639,30 @@ class TrainEngine:
         if not self.dense:
             h0 = x
             fixed_depth_id = None if tr.fixed_depth is None else list(cfg.depth_choices).index(tr.fixed_depth)
+            if self.audit is not None:
+                if self.audit.own_prelude:
+                    # copies of the prelude's saved activations for the audited samples (read by the replay's own
+                    # prelude backward, much later): on the replay's weight-gradient stream, idle during forward
+                    ps = self._param_stream
+                    if ps is not None:
+                        ps.wait_stream(torch.cuda.current_stream(self.device))
+                        with torch.cuda.stream(ps):
+                            self.audit.gather_prelude()
+                    else:
+                        self.audit.gather_prelude()
+                # the replay's first launches need h0 only: they run beside the router
+                self._side_wait_main()
+                with self._on_side():
+                    self.audit.forward_replay_head(h0)
             o.router_fwd(h0, self._router_weight_dict(), self.depth_values, self.route, B=B, S=S, d=d,
                          hid=cfg.router_hidden_dim, R=cfg.recipe_count, K=len(cfg.depth_choices), T=cfg.t_max,
                          fixed_recipe=tr.fixed_recipe, fixed_depth_id=fixed_depth_id)
             if self.audit is not None:
-                # exact replay of the audited samples: needs only h0 and the routing, so it starts here and runs
-                # beside the macro operator and the rest of the hot pass
+                # exact replay of the audited samples: needs only h0 and the routing, so it runs beside the macro
+                # operator and the rest of the hot pass
                 self._side_wait_main()
                 with self._on_side():
-                    self.audit.forward_replay(h0)
+                    self.audit.forward_replay(h0, head_done=True)
             o.macro_phi_fwd(h0, self._phi_param_dict(), self.route["recipe_id"], self.route["depth_id"],
                             cfg.macro_update_scale, self.h_phi, self.phi_rstd, self.phi_pooled, self.phi_act,
                             B=B, S=S, d=d, m=cfg.macro_rank, K=len(cfg.depth_choices))
@@ -650,21 +690,29 @@ class TrainEngine:
             o.gemm(self.hidden16, sh["embed.weight"], self.logits, M=M, N=V, K=d)
             if self.audit is not None:
                 self.audit.save_hot_logits()
+                # the replay's KL term needs the saved hot logits only: it runs beside the hot cross entropy
+                self._side_wait_main()
+                with self._on_side():
+                    self.audit.forward_kl()
+                    kl_done = self._side_event()
             o.ce_fwd_bwd(self.logits, targets, self.row_weight, S, self.loss_tok, self.logits)   # logits -> dlogits in place
         o.segment_sum(self.loss_tok, self.loss_per_sample, B, S)
         o.segment_sum(self.loss_per_sample, self.scalars[0:1], 1, B)
         if self.audit is not None:
-            # the replay (started on the side stream right after Phi) now adds the KL-distillation gradient to the
-            # audited rows of the hot dlogits; the hot backward may not read them before that
-            self._side_wait_main()
-            with self._on_side():
-                self.audit.forward_losses()
-            self._main_wait_side()
+            if self.shortlist:
+                self._side_wait_main()
+                with self._on_side():
+                    kl_done = self._side_event()
+            # join: the hot backward needs the distillation gradients (KL rows of dlogits, endpoint terms), not the
+            # replay's own cross entropy, which starts the replay's backward on its stream
+            self._main_wait_side(kl_done)
+            self.audit.add_kl_grad()
             with self._on_side():
                 probes = getattr(self, "_join_probes", None)
                 if probes is not None:
                     s0 = torch.cuda.Event(enable_timing=True, external=True)
                     s0.record(torch.cuda.current_stream(self.device))
+                self.audit.forward_ce()
                 self.audit_dh_exact = self.audit.backward_head()
                 self.audit.backward_core(self.audit_dh_exact)
                 if probes is not None:
@@ -696,6 +744,11 @@ class TrainEngine:
             dcur, dalt = dalt, dcur
         defer(False)
         n_tail = len(tail)
+        hot_w_done = None
+        if audited and self._side_stream is not None:
+            # the coda's weight gradients are queued: the replay adds its share to them once this point has passed
+            hot_w_done = torch.cuda.Event()
+            hot_w_done.record(hot if hot is not None else torch.cuda.current_stream(self.device))
         if audited:
             # distillation gradient on the hot endpoint of the audited samples, then the replay's own
             # logits / final-norm / coda backward (their weight gradients add to the hot pass's)
@@ -704,8 +757,9 @@ class TrainEngine:
             # Phi backward writes dh0 into `dalt`; the router's auxiliary losses add their share
             # (its parameter-gradient half goes to the parameter-gradient stream: backward only waits for dh0)
             split = hot is not None
+            misc = self._misc_param_stream if (split and self._misc_param_stream is not None) else hot
             if split:
-                o.param_stream = hot
+                o.param_stream = misc
             o.macro_phi_bwd_split(self.prelude[-1].out if self.prelude else self.x0, dcur, self._phi_param_dict(),
                                   self.route["recipe_id"], self.route["depth_id"], cfg.macro_update_scale, self.phi_rstd,
                                   self.phi_pooled, self.phi_act, dalt,
@@ -719,17 +773,26 @@ class TrainEngine:
             dcur, dalt = dalt, dcur
             if audited:
                 from .audit import CORE_PARAMS
-                # join: the replay's backward ran beside the hot backward; fold its results in
-                self._main_wait_side()
-                defer(True)                 # its add into the coda gradients follows the hot pass's own weight gradients
-                self.audit.merge(dcur)
-                defer(False)
-                self._grad_ready("final_norm.weight")
+                # The replay's backward ran beside the hot backward.  On ITS stream: once the hot pass's coda weight
+                # gradients are in place it adds its share of the shared gradients, then (own_prelude) carries its
+                # d h0 rows through the prelude itself.  The hot pass only waits where it needs a result.
+                with self._on_side():
+                    if hot_w_done is not None:
+                        self._side_stream.wait_event(hot_w_done)
+                    self.audit.merge_shared()
+                    core_done = self._side_event()
+                    if self.audit.own_prelude:
+                        self.audit.backward_prelude()
+                    side_done = self._side_event()
+                if not self.audit.own_prelude:
+                    self._main_wait_side(side_done)
+                    self.audit.merge_tail(dcur)
+                names = ["final_norm.weight"]
                 for blk in reversed(self.coda):
                     pre = blk.prefix
-                    self._grad_ready(f"{pre}.mlp.wd.weight", f"{pre}.mlp.wug.weight", f"{pre}.norm2.weight",
-                                     f"{pre}.attn.wo.weight", f"{pre}.attn.wqkv.weight", f"{pre}.norm1.weight")
-                self._grad_ready(*CORE_PARAMS)
+                    names += [f"{pre}.mlp.wd.weight", f"{pre}.mlp.wug.weight", f"{pre}.norm2.weight",
+                              f"{pre}.attn.wo.weight", f"{pre}.attn.wqkv.weight", f"{pre}.norm1.weight"]
+                self._grad_ready(*names, *CORE_PARAMS, after=core_done)
             if not tr.disable_router_aux:
                 rg = dict(r_w0=g["router.recipe_mlp.0.weight"], r_b0=g["router.recipe_mlp.0.bias"],
                           r_w2=g["router.recipe_mlp.2.weight"], r_b2=g["router.recipe_mlp.2.bias"],
@@ -738,7 +801,7 @@ class TrainEngine:
                 # under data parallelism each rank evaluates the auxiliary losses on its own shard and
                 # contributes 1/world of their gradient (the cross-entropy part is exactly the global mean)
                 if split:
-                    o.param_stream = hot
+                    o.param_stream = misc
                 o.router_aux_bwd_split(self._router_weight_dict(), self.route, self.depth_values, tr.lambda_load / self.world,
                                        tr.lambda_depth / self.world, self.scalars[1:3], rg, dcur, self.router_scratch, B=B,
                                        S=S, d=d, hid=cfg.router_hidden_dim, R=cfg.recipe_count, K=len(cfg.depth_choices))
@@ -747,14 +810,28 @@ class TrainEngine:
                 self._grad_ready(*self._router_grad_names())
             o.cast_bf16(dcur, g16[n_tail])
             defer(True)
+            late = audited and self.audit.own_prelude       # their other share arrives at the last join
             for j, blk in enumerate(reversed(self.prelude)):
-                self._block_bwd(blk, dcur, g16[n_tail + j], dalt, g16[n_tail + j + 1], self.dxc, tmp=self.block_tmps[n_tail + j])
+                self._block_bwd(blk, dcur, g16[n_tail + j], dalt, g16[n_tail + j + 1], self.dxc, tmp=self.block_tmps[n_tail + j],
+                                mark_ready=not late)
                 dcur, dalt = dalt, dcur
             defer(False)
         o.embed_bwd(tokens, dcur, g["embed.weight"], self.embed_accum)
+        if audited and self.audit.own_prelude:
+            # last join: the replay's prelude and embedding gradients meet the hot pass's
+            self._main_wait_side(side_done)
+            if hot is not None:
+                torch.cuda.current_stream(self.device).wait_stream(hot)
+            self.audit.merge_tail(None)
+            for blk in reversed(self.prelude):
+                pre = blk.prefix
+                self._grad_ready(f"{pre}.mlp.wd.weight", f"{pre}.mlp.wug.weight", f"{pre}.norm2.weight",
+                                 f"{pre}.attn.wo.weight", f"{pre}.attn.wqkv.weight", f"{pre}.norm1.weight")
         self._grad_ready("embed.weight")
         if hot is not None:
             torch.cuda.current_stream(self.device).wait_stream(hot)
+            if self._misc_param_stream is not None:
+                torch.cuda.current_stream(self.device).wait_stream(self._misc_param_stream)
         self._finish_backward()
 
     def _optimizer_step(self) -> None:
@@ -952,7 +1029,9 @@ class TrainEngine:
             orig_call(name, *args)
             e1.record(st)
             hot_ps = self._hot_param_stream.cuda_stream if self._hot_param_stream is not None else None
-            where = "" if st.cuda_stream == main_stream else ("@wgrad" if st.cuda_stream == hot_ps else "@side")
+            misc_ps = getattr(self, "_misc_param_stream", None)
+            where = "" if st.cuda_stream == main_stream else (
+                "@wgrad" if st.cuda_stream == hot_ps or (misc_ps is not None and st.cuda_stream == misc_ps.cuda_stream) else "@side")
             calls.append((name + tag["v"] + where, e0, e1))
 
         def tagged_gemm(a, b, out, **kw):

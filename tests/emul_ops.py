@@ -479,6 +479,19 @@ class EmulOps:
         cur = dlogits_hot[tgt, :V].float()
         dlogits_hot[tgt, :V] = (cur + coef * (lh.exp() - le.exp())).to(torch.bfloat16)
 
+    def kl_distill_grad(self, hot_logits, exact_logits, temp, coef, dgrad, kl_rows, rows, V):
+        self.launches += 1
+        lh = torch.log_softmax(hot_logits.view(rows, V).float() / temp, -1)
+        le = torch.log_softmax(exact_logits.view(rows, V).float() / temp, -1)
+        kl_rows.view(-1)[:rows] = (le.exp() * (le - lh)).sum(-1)
+        dgrad.view(rows, V).copy_(coef * (lh.exp() - le.exp()))
+
+    def add_rows_to_bf16(self, dst_bf16, idx, S, src_f32, rows, V):
+        self.launches += 1
+        n = rows // S
+        tgt = (idx[:n].long()[:, None] * S + torch.arange(S)[None, :]).reshape(-1)
+        dst_bf16[tgt, :V] = (dst_bf16[tgt, :V].float() + src_f32.view(rows, V)).to(torch.bfloat16)
+
     # ---------------------------------------------------------------- small vector ops
     def cast_bf16(self, src, dst):
         self.launches += 1

@@ -106,7 +106,7 @@ def test_engine_sequence_matches_oracle(name):
         r = eng.train_step(b)
         _share_top_clusters(eng, oracle)
         ol = oracle.train_step(*b)
-        assert abs(r.loss - ol) < 3e-2, (r.loss, ol)
+        assert abs(r.loss - ol) < max(3e-2, 2e-3 * abs(ol)), (r.loss, ol)       # bf16 products under Adam: 0.2 %
     # Adam normalises the step, so a bf16-level gradient perturbation on a near-zero gradient can flip a
     # whole +-lr step: bound the worst case by the optimiser's own step bound and the typical case tightly
     for n in eng.trainable:

@@ -543,6 +543,15 @@ def test_audit_distillation_terms_and_gradients(ops):
     others = torch.ones(B * S, dtype=torch.bool)
     others[rows] = False
     assert float(dlog.cpu()[others].abs().max()) == 0.0
+    # the two-launch form (gradient kept apart, added to the dlogits afterwards) gives the same bits
+    base = _bf(torch.randn(B * S, V, generator=g) * 0.01).to(DEV)
+    fused, split = base.clone(), base.clone()
+    ops.kl_distill(hot_logits.to(DEV), exact_logits.to(DEV), temp, tr.lambda_kl * temp / n, idx, S, fused, kl_rows, n * S, V)
+    dsep, kl2 = torch.zeros(n * S, V, device=DEV), torch.zeros(n * S, device=DEV)
+    ops.kl_distill_grad(hot_logits.to(DEV), exact_logits.to(DEV), temp, tr.lambda_kl * temp / n, dsep, kl2, n * S, V)
+    ops.add_rows_to_bf16(split, idx, S, dsep, n * S, V)
+    torch.cuda.synchronize()
+    assert torch.equal(fused, split) and torch.equal(kl_rows, kl2)
 
 
 def test_audit_mask_and_residual_helpers(ops):
