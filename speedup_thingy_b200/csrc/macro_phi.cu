@@ -243,7 +243,20 @@ __device__ __forceinline__ void mma_3xtf32(float (&c)[4], const uint32_t (&ah)[4
   mma_tf32(c, ah, bh);
 }
 
-// da[tok, j] = silu'(act[tok,j]) * sum_c dupd[tok,c] * u[j,c]:  M = tokens, N = rank, K = d.
+// Both kernels read their operands with 16-byte loads.  Inside a chunk of 32 reduction indices the mma's logical
+// k-slot (step s, slot t or t+4) is mapped to the physical index 8t+s or 8t+4+s: lane t then needs the eight
+// consecutive values [8t, 8t+8) of its rows -- two float4 -- and A and B use the same permutation, so the sum is
+// unchanged.
+struct Frag8 { float4 lo, hi; };     // physical indices 8t..8t+3 and 8t+4..8t+7 of one row
+__device__ __forceinline__ Frag8 load8(const float* p, bool ok) {
+  Frag8 f;
+  if (ok) { f.lo = *reinterpret_cast<const float4*>(p); f.hi = *reinterpret_cast<const float4*>(p + 4); }
+  else { f.lo = make_float4(0.f, 0.f, 0.f, 0.f); f.hi = f.lo; }
+  return f;
+}
+__device__ __forceinline__ float pick(const float4& v, int s) { return s == 0 ? v.x : s == 1 ? v.y : s == 2 ? v.z : v.w; }
+
+// da[tok, j] = silu'(act[tok,j]) * sum_c dupd[tok,c] * u[j,c]:  M = tokens, N = rank, K = d  (d % 32 == 0).
 // Eight warps = 2 token tiles x 4 column groups; group ng owns rank columns [8ng, 8ng+8) and [8ng+32, 8ng+40).
 __global__ void __launch_bounds__(NTHR)
 phi_da_mma_kernel(const float* __restrict__ dupd, const float* __restrict__ act, const float* __restrict__ u,
@@ -258,27 +271,34 @@ phi_da_mma_kernel(const float* __restrict__ dupd, const float* __restrict__ act,
   const float* ub = u + key_of(rid, sid, b, D.K) * D.m * D.d;
   const int r0 = tok0 + mt * 16 + g, r1 = r0 + 8;
   const bool ok0 = r0 < D.S, ok1 = r1 < D.S;
-  const float* a0p = dupd + ((size_t)b * D.S + (ok0 ? r0 : 0)) * D.d;
-  const float* a1p = dupd + ((size_t)b * D.S + (ok1 ? r1 : 0)) * D.d;
+  const float* a0p = dupd + ((size_t)b * D.S + (ok0 ? r0 : 0)) * D.d + 8 * t;
+  const float* a1p = dupd + ((size_t)b * D.S + (ok1 ? r1 : 0)) * D.d + 8 * t;
   const int j0 = ng * 8 + g, j1 = j0 + 32;
   const bool okb0 = j0 < D.m, okb1 = two && j1 < D.m;
-  const float* b0p = ub + (size_t)(okb0 ? j0 : 0) * D.d;
-  const float* b1p = ub + (size_t)(okb1 ? j1 : 0) * D.d;
+  const float* b0p = ub + (size_t)(okb0 ? j0 : 0) * D.d + 8 * t;
+  const float* b1p = ub + (size_t)(okb1 ? j1 : 0) * D.d + 8 * t;
   float c0[4] = {0.f, 0.f, 0.f, 0.f}, c1[4] = {0.f, 0.f, 0.f, 0.f};
-#pragma unroll 4
-  for (int k0 = 0; k0 < D.d; k0 += 8) {
-    uint32_t a[4], al[4], f[2], fl[2];
-    split_tf32(ok0 ? a0p[k0 + t] : 0.f, a[0], al[0]);
-    split_tf32(ok1 ? a1p[k0 + t] : 0.f, a[1], al[1]);
-    split_tf32(ok0 ? a0p[k0 + t + 4] : 0.f, a[2], al[2]);
-    split_tf32(ok1 ? a1p[k0 + t + 4] : 0.f, a[3], al[3]);
-    split_tf32(okb0 ? b0p[k0 + t] : 0.f, f[0], fl[0]);
-    split_tf32(okb0 ? b0p[k0 + t + 4] : 0.f, f[1], fl[1]);
-    mma_3xtf32(c0, a, al, f, fl);
-    if (two) {
-      split_tf32(okb1 ? b1p[k0 + t] : 0.f, f[0], fl[0]);
-      split_tf32(okb1 ? b1p[k0 + t + 4] : 0.f, f[1], fl[1]);
-      mma_3xtf32(c1, a, al, f, fl);
+#pragma unroll 2
+  for (int k0 = 0; k0 < D.d; k0 += 32) {
+    const Frag8 x0 = load8(a0p + k0, ok0), x1 = load8(a1p + k0, ok1);
+    const Frag8 w0 = load8(b0p + k0, okb0);
+    Frag8 w1;
+    if (two) w1 = load8(b1p + k0, okb1);
+#pragma unroll
+    for (int s = 0; s < 4; ++s) {
+      uint32_t a[4], al[4], f[2], fl[2];
+      split_tf32(pick(x0.lo, s), a[0], al[0]);
+      split_tf32(pick(x1.lo, s), a[1], al[1]);
+      split_tf32(pick(x0.hi, s), a[2], al[2]);
+      split_tf32(pick(x1.hi, s), a[3], al[3]);
+      split_tf32(pick(w0.lo, s), f[0], fl[0]);
+      split_tf32(pick(w0.hi, s), f[1], fl[1]);
+      mma_3xtf32(c0, a, al, f, fl);
+      if (two) {
+        split_tf32(pick(w1.lo, s), f[0], fl[0]);
+        split_tf32(pick(w1.hi, s), f[1], fl[1]);
+        mma_3xtf32(c1, a, al, f, fl);
+      }
     }
   }
   auto put = [&](int row, int col, float x) {
@@ -476,15 +496,18 @@ phi_dz_kernel(const float* __restrict__ h0, const float* __restrict__ rstd, cons
   }
 }
 
-// dh0[tok,:] += da @ v3^T + rmsnorm_backward(da @ v1^T + dpool[b,:]):  M = tokens, N = d, K = rank (tensor-core form).
-// Eight warps = 2 token tiles x 4 column groups (group cq owns the 8-column tiles cq, cq+4, cq+8, ...).  The whole
-// A operand (16 tokens x rank) lives in registers.  Pass 1 forms the row dot products <dn, xhat>; pass 2 recomputes
-// the tiny products and finishes with one read-modify-write of dh0.
-__global__ void __launch_bounds__(NTHR)
+// dh0[tok,:] += da @ v3^T + rmsnorm_backward(da @ v1^T + dpool[b,:]):  M = tokens, N = d, K = rank (tensor-core form;
+// d % 32 == 0, rank % 4 == 0).  Eight warps = 2 token tiles x 4 column groups; a group takes 32-column blocks
+// cq, cq+4, ...  The A operand (16 tokens x rank) lives in registers (KC chunks of 32 rank indices, permuted as
+// above).  Output columns are permuted too: mma tile j of a block holds, for lane t, the physical columns
+// 8t+2j and 8t+2j+1, so a lane owns the eight consecutive columns [8t, 8t+8) of its two rows and the epilogue moves
+// float4.  Pass 1 forms the row dot products <dn, xhat>; pass 2 recomputes the small products and finishes with one
+// read-modify-write of dh0.
+template <int KC>
+__global__ void __launch_bounds__(NTHR, KC == 1 ? 2 : 1)
 phi_dz_mma_kernel(const float* __restrict__ h0, const float* __restrict__ rstd, const float* __restrict__ da,
                   const float* __restrict__ dpool, const float* __restrict__ v, const int32_t* __restrict__ rid,
                   const int32_t* __restrict__ sid, float* __restrict__ dh0, PhiDims D) {
-  constexpr int KS_MAX = MMAX / 8;
   __shared__ float sdot[TT][4];
   const int tiles = rte::ceil_div(D.S, TT);
   const int b = blockIdx.x / tiles, tok0 = (blockIdx.x % tiles) * TT;
@@ -495,43 +518,77 @@ phi_dz_mma_kernel(const float* __restrict__ h0, const float* __restrict__ rstd, 
   const int r0 = tok0 + mt * 16 + g, r1 = r0 + 8;
   const bool ok0 = r0 < D.S, ok1 = r1 < D.S;
   const size_t row0 = (size_t)b * D.S + (ok0 ? r0 : 0), row1 = (size_t)b * D.S + (ok1 ? r1 : 0);
-  const int ks_n = rte::ceil_div(D.m, 8);
-  uint32_t a[KS_MAX][4], al[KS_MAX][4];
+  uint32_t ah[KC][4][4], al[KC][4][4];          // [chunk][k-step][fragment register]
 #pragma unroll
-  for (int ks = 0; ks < KS_MAX; ++ks) {
-    const int j = ks * 8 + t;
-    const bool in = ks < ks_n;
-    split_tf32((in && ok0 && j < D.m) ? da[row0 * D.m + j] : 0.f, a[ks][0], al[ks][0]);
-    split_tf32((in && ok1 && j < D.m) ? da[row1 * D.m + j] : 0.f, a[ks][1], al[ks][1]);
-    split_tf32((in && ok0 && j + 4 < D.m) ? da[row0 * D.m + j + 4] : 0.f, a[ks][2], al[ks][2]);
-    split_tf32((in && ok1 && j + 4 < D.m) ? da[row1 * D.m + j + 4] : 0.f, a[ks][3], al[ks][3]);
+  for (int ch = 0; ch < KC; ++ch) {
+    const int k = 32 * ch + 8 * t;
+    const bool in = k < D.m;                     // rank % 4 == 0 and 8-wide pieces: guard each half
+    const Frag8 x0 = load8(da + row0 * D.m + k, ok0 && in && k + 8 <= D.m);
+    const Frag8 x1 = load8(da + row1 * D.m + k, ok1 && in && k + 8 <= D.m);
+    Frag8 y0 = x0, y1 = x1;
+    if (in && k + 8 > D.m) {                     // only the first four of the eight exist
+      if (ok0) y0.lo = *reinterpret_cast<const float4*>(da + row0 * D.m + k);
+      if (ok1) y1.lo = *reinterpret_cast<const float4*>(da + row1 * D.m + k);
+    }
+#pragma unroll
+    for (int s = 0; s < 4; ++s) {
+      split_tf32(pick(y0.lo, s), ah[ch][s][0], al[ch][s][0]);
+      split_tf32(pick(y1.lo, s), ah[ch][s][1], al[ch][s][1]);
+      split_tf32(pick(y0.hi, s), ah[ch][s][2], al[ch][s][2]);
+      split_tf32(pick(y1.hi, s), ah[ch][s][3], al[ch][s][3]);
+    }
   }
   const float rs0 = ok0 ? rstd[row0] : 0.f, rs1 = ok1 ? rstd[row1] : 0.f;
-  const int n_tiles = D.d / 8;
+  const int n_blocks = D.d / 32;
   const float* dpb = dpool + (size_t)b * D.d;
-  float dot0 = 0.f, dot1 = 0.f;
-  for (int nt = cq; nt < n_tiles; nt += 4) {
-    float c1[4] = {0.f, 0.f, 0.f, 0.f};
-    const float* w1 = v1 + (size_t)(nt * 8 + g) * D.m;
+  // rows of v this lane loads for mma tile j of a 32-column block: physical column 8*(g>>1) + 2j + (g&1)
+  const int pc0 = 8 * (g >> 1) + (g & 1);
+
+  auto product = [&](const float* w, int cb, float (&c)[4][4]) {
 #pragma unroll
-    for (int ks = 0; ks < KS_MAX; ++ks) {
-      if (ks < ks_n) {
-        const int k = ks * 8 + t;
-        uint32_t f[2], fl[2];
-        split_tf32(k < D.m ? w1[k] : 0.f, f[0], fl[0]);
-        split_tf32(k + 4 < D.m ? w1[k + 4] : 0.f, f[1], fl[1]);
-        mma_3xtf32(c1, a[ks], al[ks], f, fl);
+    for (int j = 0; j < 4; ++j) {
+      c[j][0] = c[j][1] = c[j][2] = c[j][3] = 0.f;
+      const float* wr = w + (size_t)(cb + pc0 + 2 * j) * D.m;
+#pragma unroll
+      for (int ch = 0; ch < KC; ++ch) {
+        const int k = 32 * ch + 8 * t;
+        Frag8 f = load8(wr + k, k + 8 <= D.m);
+        if (k < D.m && k + 8 > D.m) f.lo = *reinterpret_cast<const float4*>(wr + k);
+#pragma unroll
+        for (int s = 0; s < 4; ++s) {
+          uint32_t fh[2], fl[2];
+          split_tf32(pick(f.lo, s), fh[0], fl[0]);
+          split_tf32(pick(f.hi, s), fh[1], fl[1]);
+          mma_3xtf32(c[j], ah[ch][s], al[ch][s], fh, fl);
+        }
       }
     }
-    const int col = nt * 8 + 2 * t;
-    const float2 dp = *reinterpret_cast<const float2*>(dpb + col);
+  };
+  // the lane's eight consecutive columns of row 0 / row 1 as two float4 each
+  auto row_vals = [](const float (&c)[4][4], int half, float4& lo, float4& hi) {
+    lo = make_float4(c[0][2 * half], c[0][2 * half + 1], c[1][2 * half], c[1][2 * half + 1]);
+    hi = make_float4(c[2][2 * half], c[2][2 * half + 1], c[3][2 * half], c[3][2 * half + 1]);
+  };
+  auto dot4 = [](const float4& a, const float4& p, const float4& x) {
+    return (a.x + p.x) * x.x + (a.y + p.y) * x.y + (a.z + p.z) * x.z + (a.w + p.w) * x.w;
+  };
+
+  float dot0 = 0.f, dot1 = 0.f;
+  for (int nb = cq; nb < n_blocks; nb += 4) {
+    const int cb = nb * 32, col = cb + 8 * t;
+    float c1[4][4];
+    product(v1, cb, c1);
+    const float4 dpa = *reinterpret_cast<const float4*>(dpb + col), dpc = *reinterpret_cast<const float4*>(dpb + col + 4);
+    float4 lo, hi;
     if (ok0) {
-      const float2 hx = *reinterpret_cast<const float2*>(h0 + row0 * D.d + col);
-      dot0 += ((c1[0] + dp.x) * hx.x + (c1[1] + dp.y) * hx.y) * rs0;
+      row_vals(c1, 0, lo, hi);
+      const float4 ha = *reinterpret_cast<const float4*>(h0 + row0 * D.d + col), hb = *reinterpret_cast<const float4*>(h0 + row0 * D.d + col + 4);
+      dot0 += (dot4(lo, dpa, ha) + dot4(hi, dpc, hb)) * rs0;
     }
     if (ok1) {
-      const float2 hx = *reinterpret_cast<const float2*>(h0 + row1 * D.d + col);
-      dot1 += ((c1[2] + dp.x) * hx.x + (c1[3] + dp.y) * hx.y) * rs1;
+      row_vals(c1, 1, lo, hi);
+      const float4 ha = *reinterpret_cast<const float4*>(h0 + row1 * D.d + col), hb = *reinterpret_cast<const float4*>(h0 + row1 * D.d + col + 4);
+      dot1 += (dot4(lo, dpa, ha) + dot4(hi, dpc, hb)) * rs1;
     }
   }
   dot0 += __shfl_xor_sync(0xffffffffu, dot0, 1); dot0 += __shfl_xor_sync(0xffffffffu, dot0, 2);
@@ -544,40 +601,33 @@ phi_dz_mma_kernel(const float* __restrict__ h0, const float* __restrict__ rstd, 
     dot0 = (q0[0] + q0[1] + q0[2] + q0[3]) / (float)D.d;
     dot1 = (q1[0] + q1[1] + q1[2] + q1[3]) / (float)D.d;
   }
-  for (int nt = cq; nt < n_tiles; nt += 4) {
-    float c1[4] = {0.f, 0.f, 0.f, 0.f}, c3[4] = {0.f, 0.f, 0.f, 0.f};
-    const float* w1 = v1 + (size_t)(nt * 8 + g) * D.m;
-    const float* w3 = v3 + (size_t)(nt * 8 + g) * D.m;
+  auto finish = [&](float4& o, const float4& a1v, const float4& a3v, const float4& dp, const float4& hx, float rs, float dot) {
+    o.x += a3v.x + rs * ((a1v.x + dp.x) - hx.x * rs * dot);
+    o.y += a3v.y + rs * ((a1v.y + dp.y) - hx.y * rs * dot);
+    o.z += a3v.z + rs * ((a1v.z + dp.z) - hx.z * rs * dot);
+    o.w += a3v.w + rs * ((a1v.w + dp.w) - hx.w * rs * dot);
+  };
+  for (int nb = cq; nb < n_blocks; nb += 4) {
+    const int cb = nb * 32, col = cb + 8 * t;
+    float c1[4][4], c3[4][4];
+    product(v1, cb, c1);
+    product(v3, cb, c3);
+    const float4 dpa = *reinterpret_cast<const float4*>(dpb + col), dpc = *reinterpret_cast<const float4*>(dpb + col + 4);
 #pragma unroll
-    for (int ks = 0; ks < KS_MAX; ++ks) {
-      if (ks < ks_n) {
-        const int k = ks * 8 + t;
-        uint32_t f[2], fl[2], h[2], hl[2];
-        split_tf32(k < D.m ? w1[k] : 0.f, f[0], fl[0]);
-        split_tf32(k + 4 < D.m ? w1[k + 4] : 0.f, f[1], fl[1]);
-        split_tf32(k < D.m ? w3[k] : 0.f, h[0], hl[0]);
-        split_tf32(k + 4 < D.m ? w3[k + 4] : 0.f, h[1], hl[1]);
-        mma_3xtf32(c1, a[ks], al[ks], f, fl);
-        mma_3xtf32(c3, a[ks], al[ks], h, hl);
-      }
-    }
-    const int col = nt * 8 + 2 * t;
-    const float2 dp = *reinterpret_cast<const float2*>(dpb + col);
-    if (ok0) {
-      const float2 hx = *reinterpret_cast<const float2*>(h0 + row0 * D.d + col);
-      float2* q = reinterpret_cast<float2*>(dh0 + row0 * D.d + col);
-      float2 o = *q;
-      o.x += c3[0] + rs0 * ((c1[0] + dp.x) - hx.x * rs0 * dot0);
-      o.y += c3[1] + rs0 * ((c1[1] + dp.y) - hx.y * rs0 * dot0);
-      *q = o;
-    }
-    if (ok1) {
-      const float2 hx = *reinterpret_cast<const float2*>(h0 + row1 * D.d + col);
-      float2* q = reinterpret_cast<float2*>(dh0 + row1 * D.d + col);
-      float2 o = *q;
-      o.x += c3[2] + rs1 * ((c1[2] + dp.x) - hx.x * rs1 * dot1);
-      o.y += c3[3] + rs1 * ((c1[3] + dp.y) - hx.y * rs1 * dot1);
-      *q = o;
+    for (int half = 0; half < 2; ++half) {
+      const bool ok = half ? ok1 : ok0;
+      if (!ok) continue;
+      const size_t row = half ? row1 : row0;
+      const float rs = half ? rs1 : rs0, dot = half ? dot1 : dot0;
+      float4 l1, h1, l3, h3;
+      row_vals(c1, half, l1, h1);
+      row_vals(c3, half, l3, h3);
+      const float4 ha = *reinterpret_cast<const float4*>(h0 + row * D.d + col), hb = *reinterpret_cast<const float4*>(h0 + row * D.d + col + 4);
+      float4* q = reinterpret_cast<float4*>(dh0 + row * D.d + col);
+      float4 oa = q[0], ob = q[1];
+      finish(oa, l1, l3, dpa, ha, rs, dot);
+      finish(ob, h1, h3, dpc, hb, rs, dot);
+      q[0] = oa; q[1] = ob;
     }
   }
 }
@@ -670,13 +720,16 @@ extern "C" int rte_macro_phi_bwd_data(const float* h0, const float* dout, const 
     phi_out_kernel<1, 64><<<B * tiles, NTHR, 0, ST(stream)>>>(h0, act, p->gain, p->u, p->bias, p->scale, recipe_id, stride_id,
                                                               s_cfg, dout, dh0, x.dupd, D);
   RTE_LAUNCH_CHECK();
-  const bool mma = d % 8 == 0;          // tensor-core (TF32) products; odd widths keep the scalar kernels
+  // tensor-core (3xTF32) products with 16-byte operand loads; other shapes keep the scalar kernels
+  const bool mma = d % 32 == 0 && m % 4 == 0 && ((reinterpret_cast<uintptr_t>(scratch) | reinterpret_cast<uintptr_t>(h0) |
+                   reinterpret_cast<uintptr_t>(dh0) | reinterpret_cast<uintptr_t>(p->u) | reinterpret_cast<uintptr_t>(p->v)) & 15) == 0;
   if (mma) phi_da_mma_kernel<<<B * tiles, NTHR, 0, ST(stream)>>>(x.dupd, act, p->u, recipe_id, stride_id, x.da, D);
   else phi_da_kernel<<<B * tiles, NTHR, 0, ST(stream)>>>(x.dupd, act, p->u, recipe_id, stride_id, x.da, D);
   RTE_LAUNCH_CHECK();
   phi_dpool_kernel<<<B, NTHR, 0, ST(stream)>>>(x.da, p->v, recipe_id, stride_id, x.dpool, D);
   RTE_LAUNCH_CHECK();
-  if (mma) phi_dz_mma_kernel<<<B * tiles, NTHR, 0, ST(stream)>>>(h0, rstd, x.da, x.dpool, p->v, recipe_id, stride_id, dh0, D);
+  if (mma && m <= 32) phi_dz_mma_kernel<1><<<B * tiles, NTHR, 0, ST(stream)>>>(h0, rstd, x.da, x.dpool, p->v, recipe_id, stride_id, dh0, D);
+  else if (mma) phi_dz_mma_kernel<2><<<B * tiles, NTHR, 0, ST(stream)>>>(h0, rstd, x.da, x.dpool, p->v, recipe_id, stride_id, dh0, D);
   else phi_dz_kernel<<<B * tiles, NTHR, 0, ST(stream)>>>(h0, rstd, x.da, x.dpool, p->v, recipe_id, stride_id, dh0, D);
   RTE_LAUNCH_CHECK();
   return RTE_OK;
