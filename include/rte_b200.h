@@ -218,6 +218,10 @@ int rte_router_aux_bwd(const rte_router_weights* w, const rte_router_out* fwd, c
 int rte_router_aux_bwd_data(const rte_router_weights* w, const rte_router_out* fwd, const int32_t* depth_values,
                             float lambda_load, float lambda_depth, float* aux, float* dh0, float* scratch, int32_t B,
                             int32_t S, int32_t d, int32_t hid, int32_t R, int32_t K, rte_stream_t stream);
+/* With dh0 == NULL the call above leaves out its last step; this performs it later (the rest needs no upstream
+ * gradient and can run right after the router's forward): dh0[b,s,:] += dpooled[b,:] / S, read from `scratch`.  */
+int rte_router_aux_add_dh0(float* dh0, const float* scratch, int32_t B, int32_t S, int32_t d, int32_t hid, int32_t R,
+                           int32_t K, rte_stream_t stream);
 int rte_router_aux_bwd_params(const rte_router_out* fwd, const rte_router_grads* grads, float* scratch, int32_t B,
                               int32_t d, int32_t hid, int32_t R, int32_t K, rte_stream_t stream);
 

@@ -88,6 +88,7 @@ PROTOTYPES = {
     "rte_ce_fwd_bwd": (C.c_int, [c_vp, c_i32, c_vp, c_vp, c_i32, c_vp, c_vp, c_i32, c_i32, c_vp, c_vp]),
     "rte_segment_sum": (C.c_int, [c_vp, c_vp, c_i32, c_i32, c_vp]),
     "rte_router_fwd": (C.c_int, [c_vp, P(RouterWeights), c_vp, P(RouterOut)] + [c_i32] * 9 + [c_vp]),
+    "rte_router_aux_add_dh0": (C.c_int, [c_vp, c_vp] + [c_i32] * 6 + [c_vp]),
     "rte_router_aux_bwd_data": (C.c_int, [P(RouterWeights), P(RouterOut), c_vp, c_f32, c_f32, c_vp, c_vp, c_vp] + [c_i32] * 6 + [c_vp]),
     "rte_router_aux_bwd_params": (C.c_int, [P(RouterOut), P(RouterGrads), c_vp] + [c_i32] * 5 + [c_vp]),
     "rte_router_aux_bwd": (C.c_int, [P(RouterWeights), P(RouterOut), c_vp, c_f32, c_f32, c_vp, P(RouterGrads), c_vp,

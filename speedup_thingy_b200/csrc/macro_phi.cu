@@ -327,13 +327,32 @@ phi_pu_kernel(const float* __restrict__ h0, const float* __restrict__ act, const
 #pragma unroll
   for (int j = 0; j < MMAX; ++j) au[j] = 0.f;
   float ag = 0.f, ab = 0.f;
-  for (int s = 0; s < D.S; ++s) {
-    const size_t idx = ((size_t)b * D.S + s) * D.d + c;
-    const float du = dupd[idx];
-    ag += du * h0[idx];
-    ab += du;
+  if (D.m % 4 == 0) {                 // four ranks per shared-memory read
+    const int m4 = D.m >> 2;
+#pragma unroll 2
+    for (int s = 0; s < D.S; ++s) {
+      const size_t idx = ((size_t)b * D.S + s) * D.d + c;
+      const float du = dupd[idx];
+      ag += du * h0[idx];
+      ab += du;
+      const float4* row = reinterpret_cast<const float4*>(ssa + s * D.m);
 #pragma unroll
-    for (int j = 0; j < MMAX; ++j) if (j < D.m) au[j] += ssa[s * D.m + j] * du;
+      for (int j4 = 0; j4 < MMAX / 4; ++j4) {
+        if (j4 < m4) {
+          const float4 sv = row[j4];
+          au[4 * j4] += sv.x * du; au[4 * j4 + 1] += sv.y * du; au[4 * j4 + 2] += sv.z * du; au[4 * j4 + 3] += sv.w * du;
+        }
+      }
+    }
+  } else {
+    for (int s = 0; s < D.S; ++s) {
+      const size_t idx = ((size_t)b * D.S + s) * D.d + c;
+      const float du = dupd[idx];
+      ag += du * h0[idx];
+      ab += du;
+#pragma unroll
+      for (int j = 0; j < MMAX; ++j) if (j < D.m) au[j] += ssa[s * D.m + j] * du;
+    }
   }
   pg[(size_t)b * D.d + c] = ag;
   pb[(size_t)b * D.d + c] = ab;
@@ -345,14 +364,16 @@ phi_pu_kernel(const float* __restrict__ h0, const float* __restrict__ act, const
 //   c' <  d  : sum_s h0[s,c]*rstd[s] * da[s,j]
 //   c' < 2d  : pooled[b,c] * sum_s da[s,j]
 //   else     : sum_s h0[s,c] * da[s,j]
+constexpr int PV_ROWS = 32;       // rows of v per CTA (one 128-byte line of h0 per token)
+
 __global__ void __launch_bounds__(NTHR)
 phi_pv_kernel(const float* __restrict__ h0, const float* __restrict__ rstd, const float* __restrict__ pooled,
               const float* __restrict__ da, float* __restrict__ pv, PhiDims D) {
-  extern __shared__ float sm[];      // sda[S][m], rs[S], sx[S][8]
+  extern __shared__ float sm[];      // sda[S][m], rs[S], sx[S][PV_ROWS]
   float* sda = sm;
   float* rs = sm + D.S * D.m;
   float* sx = rs + D.S;
-  constexpr int ROWS = 8;
+  constexpr int ROWS = PV_ROWS;
   const int rblocks = rte::ceil_div(D.d, ROWS);
   const int b = blockIdx.x / rblocks, c0 = (blockIdx.x % rblocks) * ROWS;
   for (int i = threadIdx.x; i < D.S * D.m; i += NTHR) sda[i] = da[(size_t)b * D.S * D.m + i];
@@ -748,7 +769,7 @@ extern "C" int rte_macro_phi_bwd_params(const float* h0, const int32_t* recipe_i
   PhiDims D{B, S, d, m, K_strides};
   const PhiBwdScratch x = phi_scratch(scratch, B, S, d, m);
   const size_t smem_pu = (size_t)S * m * sizeof(float);
-  const size_t smem_pv = ((size_t)S * m + S + (size_t)S * 8) * sizeof(float);
+  const size_t smem_pv = ((size_t)S * m + S + (size_t)S * PV_ROWS) * sizeof(float);
   if (smem_pu > 48 * 1024 || smem_pv > 48 * 1024) {
     static bool set = false;
     if (!set) {
@@ -760,7 +781,7 @@ extern "C" int rte_macro_phi_bwd_params(const float* h0, const int32_t* recipe_i
   }
   phi_pu_kernel<<<B * rte::ceil_div(d, NTHR), NTHR, smem_pu, ST(stream)>>>(h0, act, x.dupd, x.pu, x.pg, x.pb, D);
   RTE_LAUNCH_CHECK();
-  phi_pv_kernel<<<B * rte::ceil_div(d, 8), NTHR, smem_pv, ST(stream)>>>(h0, rstd, pooled, x.da, x.pv, D);
+  phi_pv_kernel<<<B * rte::ceil_div(d, PV_ROWS), NTHR, smem_pv, ST(stream)>>>(h0, rstd, pooled, x.da, x.pv, D);
   RTE_LAUNCH_CHECK();
   const int n_keys = R * K_strides;
   const long long eu = (long long)m * d, ev = (long long)3 * d * m, ed = d;

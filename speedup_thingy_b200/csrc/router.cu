@@ -346,11 +346,13 @@ extern "C" int rte_router_fwd(const float* h0, const rte_router_weights* w, cons
 }
 
 // Data-gradient half: the auxiliary losses, d(loss)/d(pre-activations) per sample (left in `scratch`), and
-// dh0[b,s,:] += dpooled[b,:] / S -- what the rest of backward waits for.
+// dh0[b,s,:] += dpooled[b,:] / S -- what the rest of backward waits for.  None of it depends on an upstream
+// gradient, so with dh0 == NULL everything but that last add can run as soon as the router's forward is done
+// (rte_router_aux_add_dh0 performs the add later, from `scratch`).
 extern "C" int rte_router_aux_bwd_data(const rte_router_weights* w, const rte_router_out* fwd, const int32_t* depth_values,
                                        float lambda_load, float lambda_depth, float* aux, float* dh0, float* scratch, int32_t B,
                                        int32_t S, int32_t d, int32_t hid, int32_t R, int32_t K, rte_stream_t stream) {
-  RTE_CHECK_ARG(w && fwd && depth_values && aux && dh0 && scratch && B > 0 && S > 0 && d > 0 && hid > 0);
+  RTE_CHECK_ARG(w && fwd && depth_values && aux && scratch && B > 0 && S > 0 && d > 0 && hid > 0);
   RTE_CHECK_ARG(R > 0 && R <= RTE_ROUTER_MAX_R && K > 0 && K <= RTE_ROUTER_MAX_K);
   float* mean_prob = scratch;                       // [RTE_ROUTER_MAX_R]
   float* dpre_r = scratch + RTE_ROUTER_MAX_R;       // [B, hid]
@@ -372,13 +374,28 @@ extern "C" int rte_router_aux_bwd_data(const rte_router_weights* w, const rte_ro
       w->r_w0, w->d_w0, dpre_r, dpre_d, dpooled, B, S, d, hid);
   RTE_LAUNCH_CHECK();
   if (d % 4 != 0) return RTE_ERR_UNSUPPORTED;
-  {
+  if (dh0) {
     long long n4 = (long long)B * S * (d / 4);
     int grid = (int)((n4 + NTHR - 1) / NTHR);
     if (grid > 148 * 8) grid = 148 * 8;
     bcast_add_kernel<<<grid, NTHR, 0, ST(stream)>>>(dh0, dpooled, B * S, S, d, RTE_ROUTER_DPOOLED_PARTS, (long long)B * d);
     RTE_LAUNCH_CHECK();
   }
+  return RTE_OK;
+}
+
+// dh0[b,s,:] += dpooled[b,:] / S from the `scratch` a call of rte_router_aux_bwd_data(dh0 = NULL) left behind.
+extern "C" int rte_router_aux_add_dh0(float* dh0, const float* scratch, int32_t B, int32_t S, int32_t d, int32_t hid, int32_t R,
+                                      int32_t K, rte_stream_t stream) {
+  RTE_CHECK_ARG(dh0 && scratch && B > 0 && S > 0 && d > 0 && hid > 0 && R > 0 && K > 0);
+  if (d % 4 != 0) return RTE_ERR_UNSUPPORTED;
+  if (reinterpret_cast<uintptr_t>(scratch) & 15) return RTE_ERR_ALIGNMENT;
+  const float* dpooled = scratch + (((size_t)RTE_ROUTER_MAX_R + (size_t)B * (2 * hid + R + K) + 3) & ~(size_t)3);
+  long long n4 = (long long)B * S * (d / 4);
+  int grid = (int)((n4 + NTHR - 1) / NTHR);
+  if (grid > 148 * 8) grid = 148 * 8;
+  bcast_add_kernel<<<grid, NTHR, 0, ST(stream)>>>(dh0, dpooled, B * S, S, d, RTE_ROUTER_DPOOLED_PARTS, (long long)B * d);
+  RTE_LAUNCH_CHECK();
   return RTE_OK;
 }
 

@@ -520,6 +520,13 @@ class TrainEngine:
         return dict(gain=p["macro.d_gain"], v=p["macro.v"], u=p["macro.u"], bias=p["macro.bias"], scale=self.macro_scale)
 
     # ------------------------------------------------------------------ one transformer block
+    def _router_grad_dict(self) -> dict[str, torch.Tensor]:
+        g = self.grads
+        return dict(r_w0=g["router.recipe_mlp.0.weight"], r_b0=g["router.recipe_mlp.0.bias"],
+                    r_w2=g["router.recipe_mlp.2.weight"], r_b2=g["router.recipe_mlp.2.bias"],
+                    d_w0=g["router.depth_mlp.0.weight"], d_b0=g["router.depth_mlp.0.bias"],
+                    d_w2=g["router.depth_mlp.2.weight"], d_b2=g["router.depth_mlp.2.bias"])
+
     @staticmethod
     def _router_grad_names() -> list[str]:
         return [f"router.{m}.{i}.{k}" for m in ("recipe_mlp", "depth_mlp") for i in (0, 2) for k in ("weight", "bias")]
@@ -657,6 +664,19 @@ class TrainEngine:
             o.router_fwd(h0, self._router_weight_dict(), self.depth_values, self.route, B=B, S=S, d=d,
                          hid=cfg.router_hidden_dim, R=cfg.recipe_count, K=len(cfg.depth_choices), T=cfg.t_max,
                          fixed_recipe=tr.fixed_recipe, fixed_depth_id=fixed_depth_id)
+            self._router_early = None
+            if not tr.disable_router_aux and self._misc_param_stream is not None and self._hot_param_stream is not None:
+                # The auxiliary losses' backward needs no upstream gradient: all of it except the add into d h0 runs
+                # here, on the parameter-gradient stream, beside the rest of the forward pass.
+                ms = self._misc_param_stream
+                ms.wait_stream(torch.cuda.current_stream(self.device))
+                with torch.cuda.stream(ms):
+                    o.router_aux_bwd_early(self._router_weight_dict(), self.route, self.depth_values, tr.lambda_load / self.world,
+                                           tr.lambda_depth / self.world, self.scalars[1:3], self._router_grad_dict(),
+                                           self.router_scratch, B=B, S=S, d=d, hid=cfg.router_hidden_dim,
+                                           R=cfg.recipe_count, K=len(cfg.depth_choices))
+                    self._router_early = torch.cuda.Event()
+                    self._router_early.record(ms)
             if self.audit is not None:
                 # exact replay of the audited samples: needs only h0 and the routing, so it runs beside the macro
                 # operator and the rest of the hot pass
@@ -794,19 +814,20 @@ class TrainEngine:
                               f"{pre}.attn.wo.weight", f"{pre}.attn.wqkv.weight", f"{pre}.norm1.weight"]
                 self._grad_ready(*names, *CORE_PARAMS, after=core_done)
             if not tr.disable_router_aux:
-                rg = dict(r_w0=g["router.recipe_mlp.0.weight"], r_b0=g["router.recipe_mlp.0.bias"],
-                          r_w2=g["router.recipe_mlp.2.weight"], r_b2=g["router.recipe_mlp.2.bias"],
-                          d_w0=g["router.depth_mlp.0.weight"], d_b0=g["router.depth_mlp.0.bias"],
-                          d_w2=g["router.depth_mlp.2.weight"], d_b2=g["router.depth_mlp.2.bias"])
                 # under data parallelism each rank evaluates the auxiliary losses on its own shard and
                 # contributes 1/world of their gradient (the cross-entropy part is exactly the global mean)
-                if split:
-                    o.param_stream = misc
-                o.router_aux_bwd_split(self._router_weight_dict(), self.route, self.depth_values, tr.lambda_load / self.world,
-                                       tr.lambda_depth / self.world, self.scalars[1:3], rg, dcur, self.router_scratch, B=B,
-                                       S=S, d=d, hid=cfg.router_hidden_dim, R=cfg.recipe_count, K=len(cfg.depth_choices))
-                if split:
-                    o.param_stream = None
+                dims = dict(B=B, S=S, d=d, hid=cfg.router_hidden_dim, R=cfg.recipe_count, K=len(cfg.depth_choices))
+                if self._router_early is not None:
+                    torch.cuda.current_stream(self.device).wait_event(self._router_early)
+                    o.router_aux_add_dh0(dcur, self.router_scratch, **dims)
+                else:
+                    if split:
+                        o.param_stream = misc
+                    o.router_aux_bwd_split(self._router_weight_dict(), self.route, self.depth_values, tr.lambda_load / self.world,
+                                           tr.lambda_depth / self.world, self.scalars[1:3], self._router_grad_dict(), dcur,
+                                           self.router_scratch, **dims)
+                    if split:
+                        o.param_stream = None
                 self._grad_ready(*self._router_grad_names())
             o.cast_bf16(dcur, g16[n_tail])
             defer(True)
@@ -869,6 +890,8 @@ class TrainEngine:
             before = self.ops.launches
             torch.cuda.synchronize(self.device)
             graph = torch.cuda.CUDAGraph()
+            # (capturing the hot pass on a raised-priority stream, so that its kernels are served before the
+            # weight-gradient streams, was measured: +3 % step time; all streams but the replay's keep the default)
             with torch.cuda.graph(graph):
                 self._forward_backward()
                 self._optimizer_step()

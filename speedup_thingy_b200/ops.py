@@ -295,6 +295,21 @@ class CudaOps:
         with self._deferred():
             self._call("rte_router_aux_bwd_params", C.byref(so), C.byref(sg), _ptr(scratch), B, d, hid, R, K, self.stream)
 
+    def router_aux_bwd_early(self, w: dict, fwd: dict, depth_values, lambda_load, lambda_depth, aux, grads: dict, scratch, *,
+                             B, S, d, hid, R, K):
+        """Everything of the auxiliary-loss backward except the add into dh0 (no upstream gradient is involved, so
+        this may run right after the router's forward); `router_aux_add_dh0` finishes it."""
+        sw, so = self._router_weights(w), self._router_out(fwd)
+        sg = A.RouterGrads()
+        for name, _ in A.RouterGrads._fields_:
+            setattr(sg, name, grads[name].data_ptr())
+        self._call("rte_router_aux_bwd_data", C.byref(sw), C.byref(so), _ptr(depth_values), lambda_load, lambda_depth,
+                   _ptr(aux), None, _ptr(scratch), B, S, d, hid, R, K, self.stream)
+        self._call("rte_router_aux_bwd_params", C.byref(so), C.byref(sg), _ptr(scratch), B, d, hid, R, K, self.stream)
+
+    def router_aux_add_dh0(self, dh0, scratch, *, B, S, d, hid, R, K) -> None:
+        self._call("rte_router_aux_add_dh0", _ptr(dh0), _ptr(scratch), B, S, d, hid, R, K, self.stream)
+
     def topk_lowest_index(self, scores, k: int, idx, vals=None) -> None:
         rows, n = scores.shape
         self._call("rte_topk_lowest_index", _ptr(scores), scores.stride(0), rows, n, k, _ptr(idx), _ptr(vals), self.stream)

@@ -300,7 +300,18 @@ class EmulOps:
         grads["d_w0"].copy_(dpd.t() @ fwd["pooled"])
         grads["d_b0"].copy_(dpd.sum(0))
         dpooled = dpr @ w["r_w0"] + dpd @ w["d_w0"]
-        dh0.view(B, S, d).add_(dpooled[:, None, :] / S)
+        if dh0 is None:
+            scratch.view(-1)[:B * d].copy_(dpooled.reshape(-1))
+        else:
+            dh0.view(B, S, d).add_(dpooled[:, None, :] / S)
+
+    def router_aux_bwd_early(self, w, fwd, depth_values, lambda_load, lambda_depth, aux, grads, scratch, *, B, S, d, hid, R, K):
+        self.router_aux_bwd(w, fwd, depth_values, lambda_load, lambda_depth, aux, grads, None, scratch, B=B, S=S, d=d,
+                            hid=hid, R=R, K=K)
+
+    def router_aux_add_dh0(self, dh0, scratch, *, B, S, d, hid, R, K):
+        self.launches += 1
+        dh0.view(B, S, d).add_(scratch.view(-1)[:B * d].view(B, 1, d) / S)
 
     def topk_lowest_index(self, scores, k, idx, vals=None):
         order = torch.sort(-scores.double(), dim=-1, stable=True).indices[:, :k]

@@ -296,6 +296,15 @@ def test_router_fwd_indices_and_aux_bwd(ops):
                  d_w2="router.depth_mlp.2.weight", d_b2="router.depth_mlp.2.bias")
     for k, n in names.items():
         _close(grads[k], leaves[n].grad, 1e-3, n)
+    # the two-part form (everything but the add into dh0 first, the add later) gives the same bits
+    grads2 = {k: e(*w[k].shape) for k in grads}
+    dh0b, aux2, scratch2 = e(B * S, d), e(2), e(32 + B * (2 * hid + R + K + 4 * d) + 4)
+    ops.router_aux_bwd_early(w, out, dv, tr.lambda_load, tr.lambda_depth, aux2, grads2, scratch2, B=B, S=S, d=d, hid=hid, R=R, K=K)
+    ops.router_aux_add_dh0(dh0b, scratch2, B=B, S=S, d=d, hid=hid, R=R, K=K)
+    torch.cuda.synchronize()
+    assert torch.equal(dh0, dh0b) and torch.equal(auxd, aux2)
+    for k in grads:
+        assert torch.equal(grads[k], grads2[k]), k
 
 
 def test_router_fixed_ids(ops):
