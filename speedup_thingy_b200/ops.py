@@ -7,6 +7,8 @@ granularity, but a missing library or a CPU tensor is a hard error, never a fall
 """
 from __future__ import annotations
 
+import os
+
 import ctypes as C
 
 import torch
@@ -43,6 +45,7 @@ class CudaOps:
         self.launches = 0          # kernels-entry calls issued (for bench accounting)
         self._split_ws: torch.Tensor | None = None
         self.small_gemm_rows = 256  # products with at most this many rows go to the few-row kernel (0: never)
+        self.few_rows_max_splits = int(os.environ.get("RTE_FEWROW_SPLITS", "4"))
         self.gemm_max_ctas = 0     # 0 = one persistent CTA per SM; smaller values leave SMs to kernels of other streams
         # When set, launches that only produce PARAMETER gradients (weight-gradient GEMMs with their split reduction,
         # column-sum reductions of the norm backward) go to this stream, ordered after the work issued so far on the
@@ -146,7 +149,7 @@ class CudaOps:
         kb = -(-K // 64)
         splits = 1
         if M <= 256 and kb >= 16 and K % 64 == 0:
-            splits = max(s for s in range(1, 17) if kb % s == 0 and kb // s >= 2)
+            splits = max(s for s in range(1, self.few_rows_max_splits + 1) if kb % s == 0 and kb // s >= 2)
         if splits == 1 or ws is None or ws.numel() < splits * M * N:
             self.gemm(a, b, out, M=M, N=N, K=K, b_mn=b_mn, epilogue=A.EPI_F32, residual=out if accumulate else None)
             return

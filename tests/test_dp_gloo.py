@@ -65,3 +65,43 @@ def test_two_ranks_equal_one_process_on_the_global_batch(tmp_path):
         assert (ref[n] - got["grads"][n]).abs().max().item() <= 2e-2 * scale + 1e-6, n
     for n, p in single.params.items():
         assert (p - got["params"][n]).abs().max().item() <= 2.1 * TRAIN["lr"], n
+
+
+AUDIT_TRAIN = dict(mode="recursive_macro", lr=2e-3, weight_decay=0.1, seq_len=16, seed=3, fixed_depth=None,
+                   audit_fixed_count_per_batch=1, grad_clip_norm=1.0)
+
+
+def _replicated_worker(rank, world, port, out_path):
+    os.environ["MASTER_ADDR"], os.environ["MASTER_PORT"] = "127.0.0.1", str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    torch.set_num_threads(1)
+    cfg = ExperimentConfig(ModelConfig(**MODEL), TrainingConfig(**{**AUDIT_TRAIN, "batch_size": 4}))
+    eng = TrainEngine(cfg, init_parameters(cfg.model, seed=3), device="cpu", ops=EmulOps(), use_cuda_graph=False,
+                      process_group=dist.group.WORLD, bucket_cap_mb=0.05)
+    x, y = _batch()
+    losses = [eng.train_step((x[:4], y[:4])).loss for _ in range(3)]
+    if rank == 0:
+        torch.save({"losses": losses, "params": {k: v.clone() for k, v in eng.params.items()}}, out_path)
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_two_ranks_with_the_same_shard_equal_one_process_with_audit(tmp_path):
+    """With an audited sample per rank (its gradients reach the buckets from the replay's side of the step, and the
+    prelude's only after the last join), two ranks that hold the SAME shard must reproduce the single-process run:
+    every gradient is g/2 + g/2."""
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    out = tmp_path / "rank0.pt"
+    mp.spawn(_replicated_worker, args=(2, port, str(out)), nprocs=2, join=True)
+    got = torch.load(out)
+    cfg = ExperimentConfig(ModelConfig(**MODEL), TrainingConfig(**{**AUDIT_TRAIN, "batch_size": 4}))
+    single = TrainEngine(cfg, init_parameters(cfg.model, seed=3), device="cpu", ops=EmulOps(), use_cuda_graph=False)
+    x, y = _batch()
+    losses = [single.train_step((x[:4], y[:4])).loss for _ in range(3)]
+    for a, b in zip(losses, got["losses"]):
+        assert abs(a - b) <= 2e-3 * abs(a), (losses, got["losses"])
+    for n, p in single.params.items():
+        assert (p - got["params"][n]).abs().max().item() <= 2.1 * AUDIT_TRAIN["lr"], n
+        assert (p - got["params"][n]).abs().mean().item() <= 0.05 * AUDIT_TRAIN["lr"], n
