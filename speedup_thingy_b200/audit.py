@@ -286,6 +286,9 @@ class AuditReplay:
         """The replay's own cross entropy (its logits become dlogits in place)."""
         eng = self.eng
         o, n, S = eng.ops, self.n, self.S
+        if self.own_prelude and eng._param_stream is not None:
+            # what `gather_prelude` queued on the weight-gradient stream during forward is read by this backward
+            torch.cuda.current_stream(eng.device).wait_stream(eng._param_stream)
         o.ce_fwd_bwd(self.logits, self.targets_a, self.row_weight_a, S, self.loss_tok, self.logits)
         o.segment_sum(self.loss_tok, self.exact_loss, n, S)
 
@@ -329,7 +332,8 @@ class AuditReplay:
         o, cfg, p, sh, g = eng.ops, eng.cfg, eng.params, eng.shadow, eng.grads
         n, S, T, Ma, d, f, P = self.n, self.S, self.T, self.Ma, cfg.d_model, cfg.d_ff, self.P
         alpha = p["core.alpha_inj"].view(1)
-        o.fill_(self.dh0_acc, 0.0)
+        if not self.own_prelude:          # (own_prelude: cleared during forward, off the chain, by `gather_prelude`)
+            o.fill_(self.dh0_acc, 0.0)
         # With several banks the per-bank buffers are reused inside a pass, so everything stays on the chain (after
         # the head's deferred launches, which share the split-K workspace, have finished); the single-bank case (the
         # usual one) defers its weight gradients.
@@ -382,21 +386,49 @@ class AuditReplay:
             # samples that were frozen in this pass hand their gradient straight through
             o.scaled_residual_bwd(dnext, dnext, alpha, self.active[t], None, None, None, dthis, None, n, S * d)
             dnext, dthis = dthis, (self.dalt if dthis is self.dcur else self.dcur)
-        # scalar parameters: per-CTA partial sums -> gradients (fixed order)
-        # (slots of part_* beyond the CTAs actually launched stay at their initial zero)
+        self.dh_first = dnext
+        self._defer_param_grads(False)
+        if not self.own_prelude:                      # (own_prelude: `finish_core` does this off the chain)
+            self._scalar_grads()
+            if eng._param_stream is not None:         # the replay's stream ends only when its weight gradients have
+                torch.cuda.current_stream(eng.device).wait_stream(eng._param_stream)
+
+    def _scalar_grads(self) -> None:
+        """Scalar parameters of the core: per-CTA partial sums -> gradients, in fixed order (slots of part_* beyond the
+        CTAs actually launched stay at their initial zero)."""
+        eng = self.eng
+        o, g, T, P = eng.ops, eng.grads, self.T, self.P
         o.segment_sum(self.part_mlp, g["core.pass_mlp_scale"], T, P)
         o.segment_sum(self.part_attn, g["core.pass_attn_scale"], T, P)
         o.segment_sum(self.part_alpha, g["core.alpha_inj"].view(1), 1, T * P)
-        self.dh_first = dnext
-        self._defer_param_grads(False)
-        if eng._param_stream is not None:             # the replay's stream ends only when its weight gradients have
-            torch.cuda.current_stream(eng.device).wait_stream(eng._param_stream)
+
+    def finish_core(self, hot_w_done):
+        """What completes the core / coda / final-norm gradients once the data-gradient chain has left the core: the
+        scalar-parameter sums and the add of the replay's share into the hot pass's coda gradients.  Neither feeds the
+        chain, so both go to the replay's weight-gradient stream (behind its weight-gradient GEMMs) and the chain
+        carries on with the prelude at once.  Returns the event that marks those gradients final."""
+        eng = self.eng
+        ps = eng._param_stream
+        if ps is None:
+            self._scalar_grads()
+            self.merge_shared()
+            return eng._side_event()
+        ps.wait_stream(torch.cuda.current_stream(eng.device))
+        if hot_w_done is not None:
+            ps.wait_event(hot_w_done)
+        with torch.cuda.stream(ps):
+            self._scalar_grads()
+            self.merge_shared()
+            ev = torch.cuda.Event()
+            ev.record(ps)
+        return ev
 
     def gather_prelude(self) -> None:
         """Copies of what the hot pass's prelude saved for the audited samples (inputs of `backward_prelude`)."""
         eng = self.eng
         o, cfg, n, S = eng.ops, eng.cfg, self.n, self.S
         d, f, H = cfg.d_model, cfg.d_ff, cfg.n_heads
+        o.fill_(self.dh0_acc, 0.0)          # accumulator of the core backward (`forward_ce` orders the chain behind this)
         o.gather_rows(eng.tokens, self.idx, self.tokens_a, n, S * 8)
         for hot, mine, x_in in zip(eng.prelude, self.prelude_a, self.prelude_x_in):
             o.gather_rows(hot.x_in, self.idx, x_in, n, S * d * 4)

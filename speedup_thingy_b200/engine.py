@@ -797,12 +797,14 @@ class TrainEngine:
                 # gradients are in place it adds its share of the shared gradients, then (own_prelude) carries its
                 # d h0 rows through the prelude itself.  The hot pass only waits where it needs a result.
                 with self._on_side():
-                    if hot_w_done is not None:
-                        self._side_stream.wait_event(hot_w_done)
-                    self.audit.merge_shared()
-                    core_done = self._side_event()
                     if self.audit.own_prelude:
+                        core_done = self.audit.finish_core(hot_w_done)
                         self.audit.backward_prelude()
+                    else:
+                        if hot_w_done is not None:
+                            self._side_stream.wait_event(hot_w_done)
+                        self.audit.merge_shared()
+                        core_done = self._side_event()
                     side_done = self._side_event()
                 if not self.audit.own_prelude:
                     self._main_wait_side(side_done)
