@@ -144,6 +144,10 @@ int rte_rmsnorm_bwd(const float* x, const float* w, const float* film_gamma, con
 /* out[c] = (accumulate ? out[c] : 0) + sum_r partial[r, c] */
 int rte_colsum_partials(const float* partial, int32_t n_rows, int32_t d, float* out, int32_t accumulate,
                         rte_stream_t stream);
+/* The same for up to three equally shaped partial buffers in ONE launch (norm weight + the two FiLM vectors):
+ * host arrays of `count` device pointers / flags.                                                                */
+int rte_colsum_partials3(const float* const* partials, float* const* outs, const int32_t* accumulate, int32_t count,
+                         int32_t n_rows, int32_t d, rte_stream_t stream);
 
 /* --------------------- causal attention with RoPE (layers.py:36-50,64-75; reference.py:20-28,40-41)
  * qkv bf16 [B*S, 3*d] with columns (q | k | v), head-major inside each; adjacent-pair rotary

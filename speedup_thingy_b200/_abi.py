@@ -80,6 +80,7 @@ PROTOTYPES = {
     "rte_embed_bwd": (C.c_int, [c_vp, c_vp, c_vp, c_vp, c_i32, c_i32, c_i32, c_vp, c_vp]),
     "rte_rmsnorm_fwd": (C.c_int, [c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, c_i32, c_i32, c_f32, c_vp]),
     "rte_rmsnorm_bwd": (C.c_int, [c_vp] * 12 + [c_i32, c_i32, c_i32, P(c_i32), c_vp]),
+    "rte_colsum_partials3": (C.c_int, [c_vp, c_vp, c_vp, c_i32, c_i32, c_i32, c_vp]),
     "rte_colsum_partials": (C.c_int, [c_vp, c_i32, c_i32, c_vp, c_i32, c_vp]),
     "rte_rope_table": (C.c_int, [c_vp, c_i32, c_i32, c_vp]),
     "rte_rope_apply": (C.c_int, [c_vp, c_vp, c_vp, c_vp, c_i64, c_i32, c_i32, c_i32, c_i32, c_vp]),

@@ -309,6 +309,31 @@ colsum_kernel(const float* __restrict__ part, int n_rows, int d, float* __restri
   }
 }
 
+// Up to three column sums of equally shaped partial buffers in one launch (blockIdx.y selects the buffer).
+struct ColsumJob { const float* part; float* out; int accumulate; };
+struct ColsumJobs { ColsumJob j[3]; };
+
+__global__ void __launch_bounds__(1024)
+colsum3_kernel(ColsumJobs jobs, int n_rows, int d) {
+  __shared__ float sm[32][33];
+  const ColsumJob job = jobs.j[blockIdx.y];
+  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+  const int c = blockIdx.x * 32 + tx;
+  float s = 0.f;
+  if (c < d) {
+#pragma unroll 4
+    for (int r = ty; r < n_rows; r += 32) s += job.part[(size_t)r * d + c];
+  }
+  sm[ty][tx] = s;
+  __syncthreads();
+  if (ty == 0 && c < d) {
+    float t = 0.f;
+#pragma unroll
+    for (int k = 0; k < 32; ++k) t += sm[k][tx];
+    job.out[c] = job.accumulate ? job.out[c] + t : t;
+  }
+}
+
 // ------------------------------------------------------------------ cross entropy
 // One CTA per token row; logits read twice from L2/HBM (max+sum pass, gradient pass).
 __global__ void __launch_bounds__(256)
@@ -729,6 +754,20 @@ extern "C" int rte_colsum_partials(const float* partial, int32_t n_rows, int32_t
                                    rte_stream_t stream) {
   RTE_CHECK_ARG(partial && out && n_rows > 0 && d > 0);
   colsum_kernel<<<rte::ceil_div(d, 32), 1024, 0, ST(stream)>>>(partial, n_rows, d, out, accumulate);
+  RTE_LAUNCH_CHECK();
+  return RTE_OK;
+}
+
+extern "C" int rte_colsum_partials3(const float* const* partials, float* const* outs, const int32_t* accumulate, int32_t count,
+                                    int32_t n_rows, int32_t d, rte_stream_t stream) {
+  RTE_CHECK_ARG(partials && outs && accumulate && count >= 1 && count <= 3 && n_rows > 0 && d > 0);
+  ColsumJobs jobs;
+  for (int i = 0; i < 3; ++i) {
+    const int k = i < count ? i : 0;
+    RTE_CHECK_ARG(partials[k] && outs[k]);
+    jobs.j[i] = ColsumJob{partials[k], outs[k], accumulate[k]};
+  }
+  colsum3_kernel<<<dim3(rte::ceil_div(d, 32), count), 1024, 0, ST(stream)>>>(jobs, n_rows, d);
   RTE_LAUNCH_CHECK();
   return RTE_OK;
 }

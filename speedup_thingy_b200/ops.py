@@ -131,8 +131,9 @@ class CudaOps:
         (both MN-major for the tensor core), split along K across SMs and reduced in fixed order."""
         splits = self.pick_splits(M, N, K)
         with self._deferred():
-            if splits == 1 and not accumulate:
-                self.gemm(a_t, b_t, out, M=M, N=N, K=K, a_mn=True, b_mn=True, epilogue=A.EPI_F32, lda=lda, ldb=ldb, ldc=N)
+            if splits == 1:         # accumulation rides in the epilogue (residual = the output itself)
+                self.gemm(a_t, b_t, out, M=M, N=N, K=K, a_mn=True, b_mn=True, epilogue=A.EPI_F32, lda=lda, ldb=ldb, ldc=N,
+                          residual=out if accumulate else None)
                 return
             if ws is None:
                 ws = self.split_workspace(splits * M * N)
@@ -203,12 +204,20 @@ class CudaOps:
                    _ptr(partial_g), _ptr(partial_b), rows, d, max_partials, C.byref(n_part), self.stream)
         if dw_out is None and dgamma_out is None:
             return
+        jobs = []
+        if dw_out is not None:
+            jobs.append((partial, dw_out, accumulate_dw))
+        if dgamma_out is not None:
+            jobs += [(partial_g, dgamma_out, accumulate_film), (partial_b, dbeta_out, accumulate_film)]
         with self._deferred():
-            if dw_out is not None:
-                self._call("rte_colsum_partials", _ptr(partial), n_part.value, d, _ptr(dw_out), int(accumulate_dw), self.stream)
-            if dgamma_out is not None:
-                self._call("rte_colsum_partials", _ptr(partial_g), n_part.value, d, _ptr(dgamma_out), int(accumulate_film), self.stream)
-                self._call("rte_colsum_partials", _ptr(partial_b), n_part.value, d, _ptr(dbeta_out), int(accumulate_film), self.stream)
+            if len(jobs) == 1:
+                self._call("rte_colsum_partials", _ptr(jobs[0][0]), n_part.value, d, _ptr(jobs[0][1]), int(jobs[0][2]), self.stream)
+            else:                   # norm weight and the two FiLM vectors: one launch
+                k = len(jobs)
+                parts = (C.c_void_p * k)(*[j[0].data_ptr() for j in jobs])
+                outs = (C.c_void_p * k)(*[j[1].data_ptr() for j in jobs])
+                acc = (C.c_int32 * k)(*[int(j[2]) for j in jobs])
+                self._call("rte_colsum_partials3", parts, outs, acc, k, n_part.value, d, self.stream)
 
     def ce_fwd_bwd(self, logits, targets, row_weight, S: int, loss_tok, dlogits) -> None:
         rows, V = logits.shape
