@@ -241,7 +241,14 @@ int rte_topk_lowest_index(const float* scores, int32_t ld, int32_t rows, int32_t
  * v[d:2d]), act [B*S, m] (pre-activation z @ v).                                             */
 typedef struct rte_phi_params {
   const float *gain, *v, *u, *bias, *scale;   /* [R,K,d], [R,K,3d,m], [R,K,m,d], [R,K,d], [R,K,d] */
+  const float* wt;                            /* optional: transposed v and u from rte_macro_phi_prepare (NULL: scalar kernels) */
+  int32_t n_keys;                             /* R*K, the row count behind wt's leading dimensions */
 } rte_phi_params;
+/* wt f32 [n_keys*(3d*m + m*d)] = v^T as [m][n_keys*3d] followed by u^T as [d][n_keys*m]; call once per optimiser
+ * step (after the parameters changed).  With it, d % 32 == 0 and rank % 4 == 0 the forward products and the
+ * first backward product run on tensor cores (TF32 with hi/lo split: fp32 accuracy).                            */
+int rte_macro_phi_prepare(const float* v, const float* u, float* wt, int32_t n_keys, int32_t d, int32_t m,
+                          rte_stream_t stream);
 int rte_macro_phi_fwd(const float* h0, const rte_phi_params* p, const int32_t* recipe_id,
                       const int32_t* stride_id, float s_cfg, float* out, float* rstd, float* pooled,
                       float* act, int32_t B, int32_t S, int32_t d, int32_t m, int32_t K_strides,

@@ -54,7 +54,7 @@ class RouterGrads(C.Structure):
 
 
 class PhiParams(C.Structure):
-    _fields_ = [(n, c_vp) for n in ("gain", "v", "u", "bias", "scale")]
+    _fields_ = [(n, c_vp) for n in ("gain", "v", "u", "bias", "scale", "wt")] + [("n_keys", C.c_int32)]
 
 
 class PhiGrads(C.Structure):
@@ -95,6 +95,7 @@ PROTOTYPES = {
     "rte_router_aux_bwd": (C.c_int, [P(RouterWeights), P(RouterOut), c_vp, c_f32, c_f32, c_vp, P(RouterGrads), c_vp,
                                      c_vp] + [c_i32] * 6 + [c_vp]),
     "rte_topk_lowest_index": (C.c_int, [c_vp, c_i32, c_i32, c_i32, c_i32, c_vp, c_vp, c_vp]),
+    "rte_macro_phi_prepare": (C.c_int, [c_vp, c_vp, c_vp, c_i32, c_i32, c_i32, c_vp]),
     "rte_macro_phi_fwd": (C.c_int, [c_vp, P(PhiParams), c_vp, c_vp, c_f32, c_vp, c_vp, c_vp, c_vp] + [c_i32] * 5 +
                           [c_f32, c_vp]),
     "rte_macro_phi_bwd": (C.c_int, [c_vp, c_vp, P(PhiParams), c_vp, c_vp, c_f32, c_vp, c_vp, c_vp, c_vp, P(PhiGrads),

@@ -313,6 +313,172 @@ phi_da_mma_kernel(const float* __restrict__ dupd, const float* __restrict__ act,
   if (two) { put(r0, col0 + 32, c1[0]); put(r0, col0 + 33, c1[1]); put(r1, col0 + 32, c1[2]); put(r1, col0 + 33, c1[3]); }
 }
 
+// ---- Forward products on tensor cores.  They need the reduction index contiguous per output column, i.e. the
+// TRANSPOSED parameters: wt = vt [m][keys*3d] (vt[j][key*3d + c] = v[key][c][j]) followed by
+// ut [d][keys*m] (ut[c][key*m + j] = u[key][j][c]), refreshed once per step by rte_macro_phi_prepare.
+
+// act[tok, j] = pa[b, j] + rstd[tok] * (h0 @ v1)[tok, j] + (h0 @ v3)[tok, j]:  M = tokens, N = rank, K = d (d % 32 == 0).
+// Same warp layout as phi_da_mma_kernel; two accumulators per rank tile (the v1 and v3 slices share the A fragments).
+__global__ void __launch_bounds__(NTHR)
+phi_act_mma_kernel(const float* __restrict__ h0, const float* __restrict__ rstd, const float* __restrict__ pa,
+                   const float* __restrict__ vt, long long vt_ld, const int32_t* __restrict__ rid,
+                   const int32_t* __restrict__ sid, float* __restrict__ act, PhiDims D) {
+  const int tiles = rte::ceil_div(D.S, TT);
+  const int b = blockIdx.x / tiles, tok0 = (blockIdx.x % tiles) * TT;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, g = lane >> 2, t = lane & 3;
+  const int mt = warp & 1, ng = warp >> 1;
+  const int n_tiles = rte::ceil_div(D.m, 8);
+  if (ng >= n_tiles) return;                         // warp-uniform; the kernel has no barrier
+  const bool two = ng + 4 < n_tiles;
+  const size_t koff = key_of(rid, sid, b, D.K) * 3 * D.d;
+  const int r0 = tok0 + mt * 16 + g, r1 = r0 + 8;
+  const bool ok0 = r0 < D.S, ok1 = r1 < D.S;
+  const float* a0p = h0 + ((size_t)b * D.S + (ok0 ? r0 : 0)) * D.d + 8 * t;
+  const float* a1p = h0 + ((size_t)b * D.S + (ok1 ? r1 : 0)) * D.d + 8 * t;
+  const int j0 = ng * 8 + g, j1 = j0 + 32;
+  const bool okb0 = j0 < D.m, okb1 = two && j1 < D.m;
+  const float* b0p = vt + (size_t)(okb0 ? j0 : 0) * vt_ld + koff + 8 * t;
+  const float* b1p = vt + (size_t)(okb1 ? j1 : 0) * vt_ld + koff + 8 * t;
+  float p1[2][4], p3[2][4];
+#pragma unroll
+  for (int q = 0; q < 2; ++q)
+#pragma unroll
+    for (int e = 0; e < 4; ++e) p1[q][e] = p3[q][e] = 0.f;
+#pragma unroll 2
+  for (int k0 = 0; k0 < D.d; k0 += 32) {
+    const Frag8 x0 = load8(a0p + k0, ok0), x1 = load8(a1p + k0, ok1);
+    const Frag8 w1 = load8(b0p + k0, okb0), w3 = load8(b0p + 2 * D.d + k0, okb0);
+    Frag8 y1, y3;
+    if (two) { y1 = load8(b1p + k0, okb1); y3 = load8(b1p + 2 * D.d + k0, okb1); }
+#pragma unroll
+    for (int s = 0; s < 4; ++s) {
+      uint32_t a[4], al[4], f[2], fl[2];
+      split_tf32(pick(x0.lo, s), a[0], al[0]);
+      split_tf32(pick(x1.lo, s), a[1], al[1]);
+      split_tf32(pick(x0.hi, s), a[2], al[2]);
+      split_tf32(pick(x1.hi, s), a[3], al[3]);
+      split_tf32(pick(w1.lo, s), f[0], fl[0]);
+      split_tf32(pick(w1.hi, s), f[1], fl[1]);
+      mma_3xtf32(p1[0], a, al, f, fl);
+      split_tf32(pick(w3.lo, s), f[0], fl[0]);
+      split_tf32(pick(w3.hi, s), f[1], fl[1]);
+      mma_3xtf32(p3[0], a, al, f, fl);
+      if (two) {
+        split_tf32(pick(y1.lo, s), f[0], fl[0]);
+        split_tf32(pick(y1.hi, s), f[1], fl[1]);
+        mma_3xtf32(p1[1], a, al, f, fl);
+        split_tf32(pick(y3.lo, s), f[0], fl[0]);
+        split_tf32(pick(y3.hi, s), f[1], fl[1]);
+        mma_3xtf32(p3[1], a, al, f, fl);
+      }
+    }
+  }
+  const float rs0 = ok0 ? rstd[(size_t)b * D.S + r0] : 0.f, rs1 = ok1 ? rstd[(size_t)b * D.S + r1] : 0.f;
+  auto put = [&](int row, int col, float rs, float a1v, float a3v) {
+    if (row < D.S && col < D.m) act[((size_t)b * D.S + row) * D.m + col] = pa[(size_t)b * D.m + col] + rs * a1v + a3v;
+  };
+#pragma unroll
+  for (int q = 0; q < 2; ++q) {
+    if (q == 1 && !two) break;
+    const int col0 = ng * 8 + 2 * t + 32 * q;
+    put(r0, col0, rs0, p1[q][0], p3[q][0]); put(r0, col0 + 1, rs0, p1[q][1], p3[q][1]);
+    put(r1, col0, rs1, p1[q][2], p3[q][2]); put(r1, col0 + 1, rs1, p1[q][3], p3[q][3]);
+  }
+}
+
+// MODE 0 (forward):  out = h + s_cfg*scale*tanh(gain*h + silu(act) @ u + bias)
+// MODE 1 (backward): dupd = dout*s_cfg*scale*(1 - tanh^2);  out (= dh0) = dout + gain*dupd
+// M = tokens, N = d, K = rank (d % 32 == 0, rank % 4 == 0); warp layout, operand permutations and float4 epilogue
+// as in phi_dz_mma_kernel; the A operand is silu(act) of the warp's 16 tokens, held in registers.
+template <int MODE, int KC>
+__global__ void __launch_bounds__(NTHR, KC == 1 ? 2 : 1)
+phi_out_mma_kernel(const float* __restrict__ h0, const float* __restrict__ act, const float* __restrict__ gain,
+                   const float* __restrict__ ut, long long ut_ld, const float* __restrict__ bias,
+                   const float* __restrict__ scale, const int32_t* __restrict__ rid, const int32_t* __restrict__ sid,
+                   float s_cfg, const float* __restrict__ dout, float* __restrict__ out, float* __restrict__ dupd, PhiDims D) {
+  const int tiles = rte::ceil_div(D.S, TT);
+  const int b = blockIdx.x / tiles, tok0 = (blockIdx.x % tiles) * TT;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, g = lane >> 2, t = lane & 3;
+  const int mt = warp & 1, cq = warp >> 1;
+  const size_t key = key_of(rid, sid, b, D.K);
+  const float* ub = ut + key * D.m;                 // row c of this key's u^T: ub + c * ut_ld
+  const int r0 = tok0 + mt * 16 + g, r1 = r0 + 8;
+  const bool ok0 = r0 < D.S, ok1 = r1 < D.S;
+  const size_t row0 = (size_t)b * D.S + (ok0 ? r0 : 0), row1 = (size_t)b * D.S + (ok1 ? r1 : 0);
+  uint32_t ah[KC][4][4], al[KC][4][4];
+#pragma unroll
+  for (int ch = 0; ch < KC; ++ch) {
+    const int k = 32 * ch + 8 * t;
+    Frag8 y0 = load8(act + row0 * D.m + k, ok0 && k + 8 <= D.m), y1 = load8(act + row1 * D.m + k, ok1 && k + 8 <= D.m);
+    if (k < D.m && k + 8 > D.m) {
+      if (ok0) y0.lo = *reinterpret_cast<const float4*>(act + row0 * D.m + k);
+      if (ok1) y1.lo = *reinterpret_cast<const float4*>(act + row1 * D.m + k);
+    }
+#pragma unroll
+    for (int s = 0; s < 4; ++s) {
+      const bool in_lo = k + s < D.m, in_hi = k + 4 + s < D.m;      // silu(0) = 0 anyway; keep padded slots exact zeros
+      split_tf32(in_lo ? rte::silu_f(pick(y0.lo, s)) : 0.f, ah[ch][s][0], al[ch][s][0]);
+      split_tf32(in_lo ? rte::silu_f(pick(y1.lo, s)) : 0.f, ah[ch][s][1], al[ch][s][1]);
+      split_tf32(in_hi ? rte::silu_f(pick(y0.hi, s)) : 0.f, ah[ch][s][2], al[ch][s][2]);
+      split_tf32(in_hi ? rte::silu_f(pick(y1.hi, s)) : 0.f, ah[ch][s][3], al[ch][s][3]);
+    }
+  }
+  const int n_blocks = D.d / 32;
+  const int pc0 = 8 * (g >> 1) + (g & 1);
+  const float* gk = gain + key * D.d;
+  const float* bk = bias + key * D.d;
+  const float* sk = scale + key * D.d;
+  for (int nb = cq; nb < n_blocks; nb += 4) {
+    const int cb = nb * 32, col = cb + 8 * t;
+    float c[4][4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      c[j][0] = c[j][1] = c[j][2] = c[j][3] = 0.f;
+      const float* wr = ub + (size_t)(cb + pc0 + 2 * j) * ut_ld;
+#pragma unroll
+      for (int ch = 0; ch < KC; ++ch) {
+        const int k = 32 * ch + 8 * t;
+        Frag8 f = load8(wr + k, k + 8 <= D.m);
+        if (k < D.m && k + 8 > D.m) f.lo = *reinterpret_cast<const float4*>(wr + k);
+#pragma unroll
+        for (int s = 0; s < 4; ++s) {
+          uint32_t fh[2], fl[2];
+          split_tf32(pick(f.lo, s), fh[0], fl[0]);
+          split_tf32(pick(f.hi, s), fh[1], fl[1]);
+          mma_3xtf32(c[j], ah[ch][s], al[ch][s], fh, fl);
+        }
+      }
+    }
+#pragma unroll
+    for (int half = 0; half < 2; ++half) {
+      if (!(half ? ok1 : ok0)) continue;
+      const size_t row = half ? row1 : row0;
+      const float low[8] = {c[0][2 * half], c[0][2 * half + 1], c[1][2 * half], c[1][2 * half + 1],
+                            c[2][2 * half], c[2][2 * half + 1], c[3][2 * half], c[3][2 * half + 1]};
+#pragma unroll
+      for (int q = 0; q < 2; ++q) {
+        const size_t idx = row * D.d + col + 4 * q;
+        const float4 h = *reinterpret_cast<const float4*>(h0 + idx);
+        const float4 gv = *reinterpret_cast<const float4*>(gk + col + 4 * q);
+        const float4 bv = *reinterpret_cast<const float4*>(bk + col + 4 * q);
+        float4 sc = *reinterpret_cast<const float4*>(sk + col + 4 * q);
+        sc.x *= s_cfg; sc.y *= s_cfg; sc.z *= s_cfg; sc.w *= s_cfg;
+        const float t0 = tanhf(gv.x * h.x + low[4 * q] + bv.x), t1 = tanhf(gv.y * h.y + low[4 * q + 1] + bv.y);
+        const float t2 = tanhf(gv.z * h.z + low[4 * q + 2] + bv.z), t3 = tanhf(gv.w * h.w + low[4 * q + 3] + bv.w);
+        if (MODE == 0) {
+          *reinterpret_cast<float4*>(out + idx) = make_float4(h.x + sc.x * t0, h.y + sc.y * t1, h.z + sc.z * t2, h.w + sc.w * t3);
+        } else {
+          const float4 dv = *reinterpret_cast<const float4*>(dout + idx);
+          const float4 du = make_float4(dv.x * sc.x * (1.f - t0 * t0), dv.y * sc.y * (1.f - t1 * t1),
+                                        dv.z * sc.z * (1.f - t2 * t2), dv.w * sc.w * (1.f - t3 * t3));
+          *reinterpret_cast<float4*>(dupd + idx) = du;
+          *reinterpret_cast<float4*>(out + idx) = make_float4(dv.x + gv.x * du.x, dv.y + gv.y * du.y, dv.z + gv.z * du.z, dv.w + gv.w * du.w);
+        }
+      }
+    }
+  }
+}
+
 // Per-sample parameter gradients of u, gain, bias:  pu[b][j,c], pg[b][c], pb[b][c].
 __global__ void __launch_bounds__(NTHR)
 phi_pu_kernel(const float* __restrict__ h0, const float* __restrict__ act, const float* __restrict__ dupd,
@@ -680,6 +846,26 @@ phi_reduce_keys_kernel(const float* __restrict__ partial, const int32_t* __restr
 
 #define ST(s) reinterpret_cast<cudaStream_t>(s)
 
+namespace {
+// The tensor-core forward / phi_out backward need the transposed parameters (p->wt, see rte_macro_phi_prepare),
+// d % 32 == 0, rank % 4 == 0 and 16-byte aligned buffers; otherwise the scalar kernels run.
+inline bool phi_tensor_path(const rte_phi_params* p, const void* a, const void* b, const void* c, int d, int m) {
+  return p->wt != nullptr && p->n_keys > 0 && d % 32 == 0 && m % 4 == 0 &&
+         ((reinterpret_cast<uintptr_t>(p->wt) | reinterpret_cast<uintptr_t>(a) | reinterpret_cast<uintptr_t>(b) |
+           reinterpret_cast<uintptr_t>(c) | reinterpret_cast<uintptr_t>(p->gain) | reinterpret_cast<uintptr_t>(p->bias) |
+           reinterpret_cast<uintptr_t>(p->scale)) & 15) == 0;
+}
+}  // namespace
+
+// wt (n_keys*(3d*m + m*d) floats) = [ v^T as [m][n_keys*3d] | u^T as [d][n_keys*m] ]: once per optimiser step.
+extern "C" int rte_macro_phi_prepare(const float* v, const float* u, float* wt, int32_t n_keys, int32_t d, int32_t m,
+                                     rte_stream_t stream) {
+  RTE_CHECK_ARG(v && u && wt && n_keys > 0 && d > 0 && m > 0);
+  int rc = rte_transpose_f32(v, wt, n_keys * 3 * d, m, 0, 0, stream);
+  if (rc != RTE_OK) return rc;
+  return rte_transpose_f32(u, wt + (size_t)m * n_keys * 3 * d, n_keys * m, d, 0, 0, stream);
+}
+
 extern "C" int rte_macro_phi_fwd(const float* h0, const rte_phi_params* p, const int32_t* recipe_id,
                                  const int32_t* stride_id, float s_cfg, float* out, float* rstd, float* pooled,
                                  float* act, int32_t B, int32_t S, int32_t d, int32_t m, int32_t K_strides,
@@ -694,6 +880,20 @@ extern "C" int rte_macro_phi_fwd(const float* h0, const rte_phi_params* p, const
   float* pa = pooled + (size_t)B * d;
   phi_prep_kernel<<<B, NTHR, (size_t)(S + d) * sizeof(float), ST(stream)>>>(h0, p->v, recipe_id, stride_id, rstd, pooled, pa, D, eps);
   RTE_LAUNCH_CHECK();
+  if (phi_tensor_path(p, h0, out, act, d, m)) {
+    const long long vt_ld = (long long)p->n_keys * 3 * d, ut_ld = (long long)p->n_keys * m;
+    const float* ut = p->wt + (size_t)m * vt_ld;
+    phi_act_mma_kernel<<<B * tiles, NTHR, 0, ST(stream)>>>(h0, rstd, pa, p->wt, vt_ld, recipe_id, stride_id, act, D);
+    RTE_LAUNCH_CHECK();
+    if (m <= 32)
+      phi_out_mma_kernel<0, 1><<<B * tiles, NTHR, 0, ST(stream)>>>(h0, act, p->gain, ut, ut_ld, p->bias, p->scale, recipe_id,
+                                                                   stride_id, s_cfg, nullptr, out, nullptr, D);
+    else
+      phi_out_mma_kernel<0, 2><<<B * tiles, NTHR, 0, ST(stream)>>>(h0, act, p->gain, ut, ut_ld, p->bias, p->scale, recipe_id,
+                                                                   stride_id, s_cfg, nullptr, out, nullptr, D);
+    RTE_LAUNCH_CHECK();
+    return RTE_OK;
+  }
   phi_act_kernel<<<B * tiles, NTHR, 0, ST(stream)>>>(h0, rstd, pa, p->v, recipe_id, stride_id, act, D);
   RTE_LAUNCH_CHECK();
   if (m <= 32)
@@ -734,7 +934,16 @@ extern "C" int rte_macro_phi_bwd_data(const float* h0, const float* dout, const 
   PhiDims D{B, S, d, m, K_strides};
   const int tiles = rte::ceil_div(S, TT);
   const PhiBwdScratch x = phi_scratch(scratch, B, S, d, m);
-  if (m <= 32)
+  if (phi_tensor_path(p, h0, dout, dh0, d, m) && (reinterpret_cast<uintptr_t>(scratch) & 15) == 0) {
+    const long long vt_ld = (long long)p->n_keys * 3 * d, ut_ld = (long long)p->n_keys * m;
+    const float* ut = p->wt + (size_t)m * vt_ld;
+    if (m <= 32)
+      phi_out_mma_kernel<1, 1><<<B * tiles, NTHR, 0, ST(stream)>>>(h0, act, p->gain, ut, ut_ld, p->bias, p->scale, recipe_id,
+                                                                   stride_id, s_cfg, dout, dh0, x.dupd, D);
+    else
+      phi_out_mma_kernel<1, 2><<<B * tiles, NTHR, 0, ST(stream)>>>(h0, act, p->gain, ut, ut_ld, p->bias, p->scale, recipe_id,
+                                                                   stride_id, s_cfg, dout, dh0, x.dupd, D);
+  } else if (m <= 32)
     phi_out_kernel<1, 32><<<B * tiles, NTHR, 0, ST(stream)>>>(h0, act, p->gain, p->u, p->bias, p->scale, recipe_id, stride_id,
                                                               s_cfg, dout, dh0, x.dupd, D);
   else

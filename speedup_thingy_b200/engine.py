@@ -347,6 +347,9 @@ class TrainEngine:
             self.h_phi = e(M, d)
             self.phi_rstd, self.phi_pooled, self.phi_act = e(M), e(B * d + B * m), e(M, m)
             self.phi_scratch = e(ops.phi_bwd_scratch_floats(B, S, d, m))
+            # transposed macro-operator weights for its tensor-core forward, refreshed every step (CudaOps only)
+            self.phi_wt = (e(cfg.recipe_count * len(cfg.depth_choices) * 4 * d * m)
+                           if hasattr(ops, "macro_phi_prepare") and dev.type == "cuda" else None)
             self.macro_scale = torch.ones(r, k, d, dtype=f32, device=dev)   # `update_scale` buffer (macro.py:99-108)
             self.macro_teacher_delta_rms = torch.zeros(r, k)               # carried through checkpoints only (macro.py:122)
             self.depth_values = torch.tensor(list(cfg.depth_choices), dtype=torch.int32, device=dev)
@@ -517,7 +520,8 @@ class TrainEngine:
 
     def _phi_param_dict(self) -> dict[str, torch.Tensor]:
         p = self.params
-        return dict(gain=p["macro.d_gain"], v=p["macro.v"], u=p["macro.u"], bias=p["macro.bias"], scale=self.macro_scale)
+        return dict(gain=p["macro.d_gain"], v=p["macro.v"], u=p["macro.u"], bias=p["macro.bias"], scale=self.macro_scale,
+                    wt=getattr(self, "phi_wt", None))
 
     # ------------------------------------------------------------------ one transformer block
     def _router_grad_dict(self) -> dict[str, torch.Tensor]:
@@ -683,6 +687,8 @@ class TrainEngine:
                 self._side_wait_main()
                 with self._on_side():
                     self.audit.forward_replay(h0, head_done=True)
+            if self.phi_wt is not None:
+                o.macro_phi_prepare(self._phi_param_dict())
             o.macro_phi_fwd(h0, self._phi_param_dict(), self.route["recipe_id"], self.route["depth_id"],
                             cfg.macro_update_scale, self.h_phi, self.phi_rstd, self.phi_pooled, self.phi_act,
                             B=B, S=S, d=d, m=cfg.macro_rank, K=len(cfg.depth_choices))
@@ -710,6 +716,12 @@ class TrainEngine:
             o.gemm(self.hidden16, sh["embed.weight"], self.logits, M=M, N=V, K=d)
             if self.audit is not None:
                 self.audit.save_hot_logits()
+                fwd_probe = getattr(self, "_fwd_probe", None)       # optional: (end of the replay's forward, hot logits ready)
+                if fwd_probe is not None and self._side_stream is not None:
+                    pe = (torch.cuda.Event(enable_timing=True, external=True), torch.cuda.Event(enable_timing=True, external=True))
+                    pe[0].record(self._side_stream)
+                    pe[1].record(torch.cuda.current_stream(self.device))
+                    fwd_probe.append(pe)
                 # the replay's KL term needs the saved hot logits only: it runs beside the hot cross entropy
                 self._side_wait_main()
                 with self._on_side():

@@ -330,9 +330,20 @@ class CudaOps:
     @staticmethod
     def _phi_params(p: dict) -> A.PhiParams:
         s = A.PhiParams()
-        for name, _ in A.PhiParams._fields_:
+        for name in ("gain", "v", "u", "bias", "scale"):
             setattr(s, name, p[name].data_ptr())
+        wt = p.get("wt")
+        s.wt = wt.data_ptr() if wt is not None else None
+        s.n_keys = p["gain"].shape[0] * p["gain"].shape[1] if wt is not None else 0
         return s
+
+    def macro_phi_prepare(self, p: dict) -> None:
+        """Refreshes p["wt"] (transposed v and u) for the tensor-core forward; call after the parameters changed."""
+        R, K, d = p["gain"].shape
+        m = p["u"].shape[2]
+        if p["wt"].numel() < R * K * (3 * d * m + m * d):
+            raise ValueError("macro_phi_prepare: wt too small")
+        self._call("rte_macro_phi_prepare", _ptr(p["v"]), _ptr(p["u"]), _ptr(p["wt"]), R * K, d, m, self.stream)
 
     def macro_phi_fwd(self, h0, p: dict, recipe_id, stride_id, s_cfg, out, rstd, pooled, act, *, B, S, d, m, K):
         sp = self._phi_params(p)

@@ -390,7 +390,7 @@ class EmulOps:
 
     def macro_phi_bwd(self, h0, dout, p, recipe_id, stride_id, s_cfg, rstd, pooled, act, dh0, grads, scratch, *, B, S, d, m, R, K):
         self.launches += 1
-        leaves = {k: p[k].detach().clone().requires_grad_(k != "scale") for k in p}
+        leaves = {k: p[k].detach().clone().requires_grad_(k != "scale") for k in p if k != "wt"}
         hh = h0.detach().clone().requires_grad_(True)
         o, *_ = self._phi(hh, leaves, recipe_id, stride_id, s_cfg, B, S, d, m)
         o.backward(dout.view(B, S, d))
@@ -489,6 +489,9 @@ class EmulOps:
         tgt = (idx[:n].long()[:, None] * S + torch.arange(S)[None, :]).reshape(-1)
         cur = dlogits_hot[tgt, :V].float()
         dlogits_hot[tgt, :V] = (cur + coef * (lh.exp() - le.exp())).to(torch.bfloat16)
+
+    def macro_phi_prepare(self, p):
+        pass
 
     def kl_distill_grad(self, hot_logits, exact_logits, temp, coef, dgrad, kl_rows, rows, V):
         self.launches += 1

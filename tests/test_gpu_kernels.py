@@ -435,8 +435,9 @@ def test_shortlist_ce_matches_reference_math(ops, rows, S, d, V, K):
 
 
 # ------------------------------------------------------------------ macro operator
+@pytest.mark.parametrize("tensor", [False, True])       # True: transposed weights prepared -> tensor-core forward
 @pytest.mark.parametrize("B,S,d,m,R", [(4, 16, 64, 8, 5), (6, 64, 128, 32, 5), (3, 40, 512, 32, 5), (2, 8, 64, 48, 3)])
-def test_macro_phi_fwd_bwd(ops, B, S, d, m, R):
+def test_macro_phi_fwd_bwd(ops, B, S, d, m, R, tensor):
     K = 3
     cfg = O.ModelCfg(d_model=d, macro_rank=m, recipe_count=R, macro_update_scale=0.05)
     g = torch.Generator().manual_seed(d + m)
@@ -456,6 +457,9 @@ def test_macro_phi_fwd_bwd(ops, B, S, d, m, R):
               scale=torch.ones(R, K, d, device=DEV))
     out, rstd, pooled, act = e(B * S, d), e(B * S), e(B * d + B * m), e(B * S, m)
     ri, si = rid.to(DEV, torch.int32), sid.to(DEV, torch.int32)
+    if tensor:
+        pd["wt"] = e(R * K * 4 * d * m)
+        ops.macro_phi_prepare(pd)
     ops.macro_phi_fwd(h0.to(DEV).view(B * S, d), pd, ri, si, 0.05, out, rstd, pooled, act, B=B, S=S, d=d, m=m, K=K)
     torch.cuda.synchronize()
     _close(out.view(B, S, d), ref, 1e-4, "phi out")
