@@ -405,10 +405,13 @@ int rte_scaled_residual_fwd(const float* base, const float* branch, const float*
 /* Backward of the above for gradient dout: dbase (=) dout where active else 0 (may alias dout);
  * dbranch_bf16 = scale*dout where active else 0 (NULL to skip); dbranch_f32_accum += scale*dout (NULL to skip);
  * dpassthrough += dout where inactive (NULL if no mask); dscale_partial[blockIdx] = sum dout*branch over active
- * samples (one f32 per CTA; *n_partials CTAs, host value).                                                     */
+ * samples (one f32 per CTA; *n_partials CTAs, host value).  frozen_active / frozen_src (both or neither): dbase
+ * additionally receives frozen_src where frozen_active[sample] == 0 -- the hand-through of samples that were
+ * frozen in the pass, folded into the pass's last launch.                                                      */
 int rte_scaled_residual_bwd(const float* dout, const float* branch, const float* scale, const int32_t* active,
                             float* dbase, void* dbranch_bf16, float* dbranch_f32_accum, float* dpassthrough,
-                            float* dscale_partial, int32_t max_partials, int32_t* n_partials, int32_t n,
+                            float* dscale_partial, int32_t max_partials, int32_t* n_partials,
+                            const int32_t* frozen_active, const float* frozen_src, int32_t n,
                             int64_t sample_elems, rte_stream_t stream);
 /* Distillation terms of the audited samples (macro.py:394-469, delta objective) and their gradient wrt the hot
  * endpoint.  hot/exact/h0 f32 [n, S, d].  terms f32 [n, 4] = per-sample (1 - cos, log-rms diff^2, sum smooth_l1 of

@@ -132,7 +132,7 @@ PROTOTYPES = {
     "rte_swiglu_masked_fwd": (C.c_int, [c_vp, c_vp, c_vp, c_i32, c_vp, c_i32, c_i32, c_vp]),
     "rte_swiglu_masked_bwd": (C.c_int, [c_vp, c_vp, c_vp, c_vp, c_i32, c_vp, c_i32, c_i32, c_vp]),
     "rte_scaled_residual_fwd": (C.c_int, [c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, c_i32, c_i64, c_vp]),
-    "rte_scaled_residual_bwd": (C.c_int, [c_vp] * 9 + [c_i32, P(c_i32), c_i32, c_i64, c_vp]),
+    "rte_scaled_residual_bwd": (C.c_int, [c_vp] * 9 + [c_i32, P(c_i32), c_vp, c_vp, c_i32, c_i64, c_vp]),
     "rte_macro_distill": (C.c_int, [c_vp, c_vp, c_vp, c_f32, c_f32, c_f32, c_f32, c_vp, c_vp, c_i32, c_i32, c_i32, c_vp]),
     "rte_kl_distill": (C.c_int, [c_vp, c_vp, c_f32, c_f32, c_vp, c_i32, c_vp, c_i32, c_vp, c_i32, c_i32, c_vp]),
     "rte_kl_distill_grad": (C.c_int, [c_vp, c_vp, c_f32, c_f32, c_vp, c_vp, c_i32, c_i32, c_vp]),

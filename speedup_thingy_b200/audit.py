@@ -381,10 +381,10 @@ class AuditReplay:
                           dgamma_out=g["core.pass_gamma1"][t], dbeta_out=g["core.pass_beta1"][t],
                           partial_g=pg1, partial_b=pb1, accumulate_dw=acc)
             # ht = h_in + alpha * h0
+            # (samples that were frozen in this pass hand their gradient `dnext` straight through: same launch)
             o.scaled_residual_bwd(dht, self.h0a, alpha, None, dthis, None, self.dh0_acc, None,
-                                  self.part_alpha[t * P:(t + 1) * P], n, S * d)
-            # samples that were frozen in this pass hand their gradient straight through
-            o.scaled_residual_bwd(dnext, dnext, alpha, self.active[t], None, None, None, dthis, None, n, S * d)
+                                  self.part_alpha[t * P:(t + 1) * P], n, S * d, frozen_active=self.active[t],
+                                  frozen_src=dnext)
             dnext, dthis = dthis, (self.dalt if dthis is self.dcur else self.dcur)
         self.dh_first = dnext
         self._defer_param_grads(False)

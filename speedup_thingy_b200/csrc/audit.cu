@@ -96,7 +96,8 @@ __global__ void scaled_residual_fwd_kernel(const float* __restrict__ base, const
 __global__ void __launch_bounds__(NTHR)
 scaled_residual_bwd_kernel(const float* __restrict__ dout, const float* __restrict__ branch, const float* __restrict__ scale,
                            const int32_t* __restrict__ active, float* __restrict__ dbase, __nv_bfloat16* __restrict__ db16,
-                           float* __restrict__ db32, float* __restrict__ dpass, float* __restrict__ dscale_part, int n,
+                           float* __restrict__ db32, float* __restrict__ dpass, float* __restrict__ dscale_part,
+                           const int32_t* __restrict__ frozen_active, const float* __restrict__ frozen_src, int n,
                            long long se) {
   __shared__ float red[32];
   const float s = *scale;
@@ -109,7 +110,11 @@ scaled_residual_bwd_kernel(const float* __restrict__ dout, const float* __restri
     if (dpass && !on) dpass[i] += g;
     if (db16) db16[i] = __float2bfloat16_rn(on ? s * g : 0.f);
     if (db32 && on) db32[i] += s * g;
-    if (dbase) dbase[i] = on ? g : 0.f;
+    if (dbase) {
+      float o = on ? g : 0.f;
+      if (frozen_src && frozen_active[i / se] == 0) o += frozen_src[i];     // samples frozen in this pass: hand-through
+      dbase[i] = o;
+    }
   }
   acc = rte::block_sum(acc, red);
   if (threadIdx.x == 0 && dscale_part) dscale_part[blockIdx.x] = acc;
@@ -339,9 +344,11 @@ extern "C" int rte_scaled_residual_fwd(const float* base, const float* branch, c
 
 extern "C" int rte_scaled_residual_bwd(const float* dout, const float* branch, const float* scale, const int32_t* active,
                                        float* dbase, void* dbranch_bf16, float* dbranch_f32_accum, float* dpassthrough,
-                                       float* dscale_partial, int32_t max_partials, int32_t* n_partials, int32_t n,
+                                       float* dscale_partial, int32_t max_partials, int32_t* n_partials,
+                                       const int32_t* frozen_active, const float* frozen_src, int32_t n,
                                        int64_t sample_elems, rte_stream_t stream) {
   RTE_CHECK_ARG(dout && branch && scale && n > 0 && sample_elems > 0);
+  RTE_CHECK_ARG((frozen_active == nullptr) == (frozen_src == nullptr) && (frozen_src == nullptr || dbase != nullptr));
   int grid = grid_for((long long)n * sample_elems, NTHR, 64);
   if (dscale_partial) {
     RTE_CHECK_ARG(max_partials >= 1);
@@ -349,7 +356,8 @@ extern "C" int rte_scaled_residual_bwd(const float* dout, const float* branch, c
   }
   if (n_partials) *n_partials = grid;
   scaled_residual_bwd_kernel<<<grid, NTHR, 0, ST(stream)>>>(dout, branch, scale, active, dbase,
-      reinterpret_cast<__nv_bfloat16*>(dbranch_bf16), dbranch_f32_accum, dpassthrough, dscale_partial, n, sample_elems);
+      reinterpret_cast<__nv_bfloat16*>(dbranch_bf16), dbranch_f32_accum, dpassthrough, dscale_partial, frozen_active,
+      frozen_src, n, sample_elems);
   RTE_LAUNCH_CHECK();
   return RTE_OK;
 }

@@ -419,13 +419,13 @@ class CudaOps:
                    _ptr(out), n, sample_elems, self.stream)
 
     def scaled_residual_bwd(self, dout, branch, scale, active, dbase, dbranch_bf16, dbranch_f32_accum, dpassthrough,
-                            dscale_partial, n: int, sample_elems: int) -> int:
+                            dscale_partial, n: int, sample_elems: int, frozen_active=None, frozen_src=None) -> int:
         """Returns how many per-CTA partial sums of d(scale) were written to `dscale_partial`."""
         n_part = C.c_int32(0)
         cap = dscale_partial.numel() if dscale_partial is not None else 0
         self._call("rte_scaled_residual_bwd", _ptr(dout), _ptr(branch), _ptr(scale), _ptr(active), _ptr(dbase),
                    _ptr(dbranch_bf16), _ptr(dbranch_f32_accum), _ptr(dpassthrough), _ptr(dscale_partial), cap,
-                   C.byref(n_part), n, sample_elems, self.stream)
+                   C.byref(n_part), _ptr(frozen_active), _ptr(frozen_src), n, sample_elems, self.stream)
         return n_part.value
 
     def macro_distill(self, hot, exact, h0, l_dir, l_rms, l_normed, l_raw, terms, dhot, n: int, S: int, d: int) -> None:

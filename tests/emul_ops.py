@@ -446,7 +446,7 @@ class EmulOps:
         out.view(n, -1).copy_(res)
 
     def scaled_residual_bwd(self, dout, branch, scale, active, dbase, dbranch_bf16, dbranch_f32_accum, dpassthrough,
-                            dscale_partial, n, sample_elems):
+                            dscale_partial, n, sample_elems, frozen_active=None, frozen_src=None):
         self.launches += 1
         on = torch.ones(n, 1, dtype=torch.bool) if active is None else (active.view(n, 1) != 0)
         g = dout.view(n, -1).clone()
@@ -461,7 +461,11 @@ class EmulOps:
         if dbranch_f32_accum is not None:
             dbranch_f32_accum.view(n, -1).add_(torch.where(on, s * g, torch.zeros_like(g)))
         if dbase is not None:
-            dbase.view(n, -1).copy_(torch.where(on, g, torch.zeros_like(g)))
+            base = torch.where(on, g, torch.zeros_like(g))
+            if frozen_src is not None:
+                frozen = frozen_active.view(n, 1) == 0
+                base = base + torch.where(frozen, frozen_src.view(n, -1), torch.zeros_like(g))
+            dbase.view(n, -1).copy_(base)
         return 1
 
     def macro_distill(self, hot, exact, h0, l_dir, l_rms, l_normed, l_raw, terms, dhot, n, S, d):

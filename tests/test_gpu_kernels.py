@@ -629,3 +629,10 @@ def test_audit_mask_and_residual_helpers(ops):
     _close(db32, 1 + torch.where(on, 0.7 * dout, zero), 1e-6, "d branch f32 accumulate")
     _close(dpas, 1 + torch.where(on, zero, dout), 1e-6, "d passthrough")
     assert abs(float(part.sum()) - float((torch.where(on, dout, zero) * br).sum())) < 1e-2
+    # hand-through of frozen samples folded into the launch: dbase = dout + (frozen ? src : 0)
+    src2 = torch.randn(n, S * d, generator=g)
+    dbase2 = torch.zeros(n, S * d, device=DEV)
+    ops.scaled_residual_bwd(dout.to(DEV), br.to(DEV), sc.to(DEV), None, dbase2, None, None, None, None, n, S * d,
+                            frozen_active=act.to(DEV), frozen_src=src2.to(DEV))
+    torch.cuda.synchronize()
+    _close(dbase2, dout + torch.where(on, zero, src2), 1e-6, "d base with hand-through")
