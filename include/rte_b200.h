@@ -167,6 +167,12 @@ int rte_rope_apply(const void* x, const float* cos_tab, const float* sin_tab, vo
 int rte_attn_fwd(const void* qkv, int32_t ld_qkv, int32_t sec, void* y, int32_t ld_y, float* lse,
                  const float* rope_table, int32_t B, int32_t S, int32_t n_heads, int32_t head_dim,
                  rte_stream_t stream);
+/* Forward with a second, column-masked copy of the output: y_masked[row, c] = y[row, c] * mask_table[mask_row[row / S]][c]
+ * (the banked core's recipe mask, layers.py:702-728; mask_table f32 [n_rows_of_table, n_heads*head_dim]).  One launch
+ * on the tensor-core path, otherwise rte_attn_fwd + rte_colmask_mul_bf16.  ld_y must equal n_heads*head_dim.     */
+int rte_attn_fwd_masked(const void* qkv, int32_t ld_qkv, int32_t sec, void* y, void* y_masked, int32_t ld_y, float* lse,
+                        const float* rope_table, const int32_t* mask_row, const float* mask_table, int32_t B, int32_t S,
+                        int32_t n_heads, int32_t head_dim, rte_stream_t stream);
 int rte_attn_bwd(const void* qkv, int32_t ld_qkv, int32_t sec, const void* y, const void* dy, int32_t ld_y,
                  const float* lse, void* dqkv, const float* rope_table, int32_t B, int32_t S, int32_t n_heads,
                  int32_t head_dim, rte_stream_t stream);

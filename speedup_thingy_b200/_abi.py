@@ -85,6 +85,7 @@ PROTOTYPES = {
     "rte_rope_table": (C.c_int, [c_vp, c_i32, c_i32, c_vp]),
     "rte_rope_apply": (C.c_int, [c_vp, c_vp, c_vp, c_vp, c_i64, c_i32, c_i32, c_i32, c_i32, c_vp]),
     "rte_attn_fwd": (C.c_int, [c_vp, c_i32, c_i32, c_vp, c_i32, c_vp, c_vp, c_i32, c_i32, c_i32, c_i32, c_vp]),
+    "rte_attn_fwd_masked": (C.c_int, [c_vp, c_i32, c_i32, c_vp, c_vp, c_i32, c_vp, c_vp, c_vp, c_vp, c_i32, c_i32, c_i32, c_i32, c_vp]),
     "rte_attn_bwd": (C.c_int, [c_vp, c_i32, c_i32, c_vp, c_vp, c_i32, c_vp, c_vp, c_vp, c_i32, c_i32, c_i32, c_i32, c_vp]),
     "rte_ce_fwd_bwd": (C.c_int, [c_vp, c_i32, c_vp, c_vp, c_i32, c_vp, c_vp, c_i32, c_i32, c_vp, c_vp]),
     "rte_segment_sum": (C.c_int, [c_vp, c_vp, c_i32, c_i32, c_vp]),

@@ -223,11 +223,12 @@ class AuditReplay:
         for t in range(T):
             rid = self.rid[t]
             for bk in range(cfg.attn_banks):
-                if t > 0:           # pass 0: issued by forward_replay_head
+                if t > 0:           # pass 0's attention was issued by forward_replay_head (before the routing was known)
                     o.gemm(self.n1[t], sh["core.attn.wqkv"][bk], self.qkv[t][bk], M=Ma, N=3 * d, K=d, b_mn=True)
-                    o.attn_fwd(self.qkv[t][bk], self.y[t][bk], self.lse[t][bk], B=n, S=S, n_heads=cfg.n_heads,
-                               head_dim=cfg.head_dim)
-                o.colmask_mul(self.y[t][bk], rid, self.head_tab[bk], S, self.ym[t][bk], Ma, d)
+                    o.attn_fwd_masked(self.qkv[t][bk], self.y[t][bk], self.ym[t][bk], self.lse[t][bk], rid, self.head_tab[bk],
+                                      B=n, S=S, n_heads=cfg.n_heads, head_dim=cfg.head_dim)
+                else:
+                    o.colmask_mul(self.y[t][bk], rid, self.head_tab[bk], S, self.ym[t][bk], Ma, d)
                 o.gemm(self.ym[t][bk], sh["core.attn.wo"][bk], self.attn_acc[t], M=Ma, N=d, K=d, b_mn=True,
                        epilogue=A.EPI_F32, residual=self.attn_acc[t] if bk > 0 else None)
             o.residual_rmsnorm_fwd(self.ht[t], self.attn_acc[t], p["core.pass_attn_scale"][t:t + 1], self.u[t],

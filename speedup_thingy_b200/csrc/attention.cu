@@ -400,6 +400,25 @@ extern "C" int rte_attn_fwd(const void* qkv, int32_t ld_qkv, int32_t sec, void* 
   RTE_ATT_DISPATCH(launch_fwd, qkv, ld_qkv, sec, y, ld_y, lse, rope_table, B, S, n_heads, st);
 }
 
+// Attention forward with a second, column-masked copy of the output (the banked core's recipe mask,
+// layers.py:702-728): ym[row, c] = y[row, c] * mask_table[mask_row[row / S]][c].  One launch on the tensor-core
+// path; otherwise the plain forward followed by rte_colmask_mul_bf16.  y and ym share the leading dimension.
+extern "C" int rte_attn_fwd_masked(const void* qkv, int32_t ld_qkv, int32_t sec, void* y, void* y_masked, int32_t ld_y,
+                                   float* lse, const float* rope_table, const int32_t* mask_row, const float* mask_table,
+                                   int32_t B, int32_t S, int32_t n_heads, int32_t head_dim, rte_stream_t stream) {
+  RTE_CHECK_ARG(qkv && y && y_masked && lse && mask_row && mask_table && B > 0 && S > 0 && S <= 256 && n_heads > 0 &&
+                ld_qkv % 2 == 0 && sec % 2 == 0);
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  if (ld_y == n_heads * head_dim && (reinterpret_cast<uintptr_t>(mask_table) & 7) == 0) {
+    RTE_ATT_MMA_DISPATCH(attn_mma::launch_fwd, qkv, ld_qkv, sec, y, ld_y, lse, rope_table, B, S, n_heads, st, y_masked, mask_row,
+                         mask_table);
+  }
+  const int rc = rte_attn_fwd(qkv, ld_qkv, sec, y, ld_y, lse, rope_table, B, S, n_heads, head_dim, stream);
+  if (rc != RTE_OK) return rc;
+  if (ld_y != n_heads * head_dim) return RTE_ERR_UNSUPPORTED;
+  return rte_colmask_mul_bf16(y, mask_row, mask_table, S, y_masked, B * S, n_heads * head_dim, stream);
+}
+
 extern "C" int rte_attn_bwd(const void* qkv, int32_t ld_qkv, int32_t sec, const void* y, const void* dy, int32_t ld_y,
                             const float* lse, void* dqkv, const float* rope_table, int32_t B, int32_t S, int32_t n_heads,
                             int32_t head_dim, rte_stream_t stream) {

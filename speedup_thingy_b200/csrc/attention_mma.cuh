@@ -118,7 +118,8 @@ __device__ __forceinline__ void rowrow_tile(float (&acc)[4], const uint32_t (&a)
 template <int HD, int SMAX>
 __global__ void __launch_bounds__(NTHR)
 fwd_kernel(const __nv_bfloat16* __restrict__ qkv, int ld, int sec, __nv_bfloat16* __restrict__ y, int ldy,
-           float* __restrict__ lse, const float* __restrict__ rope, int S, int H) {
+           float* __restrict__ lse, const float* __restrict__ rope, int S, int H,
+           __nv_bfloat16* __restrict__ ym, const int32_t* __restrict__ mask_row, const float* __restrict__ mask_tab) {
   constexpr int LDS = HD + 8, KT = SMAX / 8;
   extern __shared__ __align__(16) uint8_t smraw[];
   __nv_bfloat16* sq = reinterpret_cast<__nv_bfloat16*>(smraw);       // [QB][LDS]
@@ -189,18 +190,35 @@ fwd_kernel(const __nv_bfloat16* __restrict__ qkv, int ld, int sec, __nv_bfloat16
     }
   }
   const float i0 = 1.f / s0, i1 = 1.f / s1;
+  // optional second output: the same rows times a per-sample column mask (ym = bf16(y) * mask_tab[mask_row[b]][col],
+  // exactly what a separate pass over the stored y would give)
+  const float* mt = ym ? mask_tab + (size_t)mask_row[b] * (H * HD) + h * HD : nullptr;
   if (row_a < S) {
     __nv_bfloat16* yo = y + (size_t)(b * S + row_a) * ldy + h * HD;
 #pragma unroll
-    for (int nd = 0; nd < HD / 8; ++nd)
-      *reinterpret_cast<__nv_bfloat162*>(yo + nd * 8 + 2 * t) = __floats2bfloat162_rn(o[nd][0] * i0, o[nd][1] * i0);
+    for (int nd = 0; nd < HD / 8; ++nd) {
+      const __nv_bfloat162 v = __floats2bfloat162_rn(o[nd][0] * i0, o[nd][1] * i0);
+      *reinterpret_cast<__nv_bfloat162*>(yo + nd * 8 + 2 * t) = v;
+      if (ym) {
+        const float2 w = *reinterpret_cast<const float2*>(mt + nd * 8 + 2 * t);
+        *reinterpret_cast<__nv_bfloat162*>(ym + (size_t)(b * S + row_a) * ldy + h * HD + nd * 8 + 2 * t) =
+            __floats2bfloat162_rn(__low2float(v) * w.x, __high2float(v) * w.y);
+      }
+    }
     if (t == 0) lse[((size_t)b * H + h) * S + row_a] = m0 + __logf(s0);
   }
   if (row_b < S) {
     __nv_bfloat16* yo = y + (size_t)(b * S + row_b) * ldy + h * HD;
 #pragma unroll
-    for (int nd = 0; nd < HD / 8; ++nd)
-      *reinterpret_cast<__nv_bfloat162*>(yo + nd * 8 + 2 * t) = __floats2bfloat162_rn(o[nd][2] * i1, o[nd][3] * i1);
+    for (int nd = 0; nd < HD / 8; ++nd) {
+      const __nv_bfloat162 v = __floats2bfloat162_rn(o[nd][2] * i1, o[nd][3] * i1);
+      *reinterpret_cast<__nv_bfloat162*>(yo + nd * 8 + 2 * t) = v;
+      if (ym) {
+        const float2 w = *reinterpret_cast<const float2*>(mt + nd * 8 + 2 * t);
+        *reinterpret_cast<__nv_bfloat162*>(ym + (size_t)(b * S + row_b) * ldy + h * HD + nd * 8 + 2 * t) =
+            __floats2bfloat162_rn(__low2float(v) * w.x, __high2float(v) * w.y);
+      }
+    }
     if (t == 0) lse[((size_t)b * H + h) * S + row_b] = m1 + __logf(s1);
   }
 }
@@ -352,7 +370,8 @@ bwd_kernel(const __nv_bfloat16* __restrict__ qkv, int ld, int sec, const __nv_bf
 }
 
 template <int HD, int SMAX>
-int launch_fwd(const void* qkv, int ld, int sec, void* y, int ldy, float* lse, const float* rope, int B, int S, int H, cudaStream_t st) {
+int launch_fwd(const void* qkv, int ld, int sec, void* y, int ldy, float* lse, const float* rope, int B, int S, int H, cudaStream_t st,
+               void* ym = nullptr, const int32_t* mask_row = nullptr, const float* mask_tab = nullptr) {
   constexpr int smem = (QB + 2 * SMAX) * (HD + 8) * 2;
   static bool set = false;
   if (!set && smem > 48 * 1024) {
@@ -360,7 +379,8 @@ int launch_fwd(const void* qkv, int ld, int sec, void* y, int ldy, float* lse, c
     set = true;
   }
   fwd_kernel<HD, SMAX><<<dim3(B * H, rte::ceil_div(S, QB)), NTHR, smem, st>>>(
-      reinterpret_cast<const __nv_bfloat16*>(qkv), ld, sec, reinterpret_cast<__nv_bfloat16*>(y), ldy, lse, rope, S, H);
+      reinterpret_cast<const __nv_bfloat16*>(qkv), ld, sec, reinterpret_cast<__nv_bfloat16*>(y), ldy, lse, rope, S, H,
+      reinterpret_cast<__nv_bfloat16*>(ym), mask_row, mask_tab);
   RTE_LAUNCH_CHECK();
   return RTE_OK;
 }

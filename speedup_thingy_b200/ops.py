@@ -253,6 +253,14 @@ class CudaOps:
         self._call("rte_attn_fwd", _ptr(qkv), qkv.stride(0), sec, _ptr(y), y.stride(0), _ptr(lse),
                    _ptr(rope), B, S, n_heads, head_dim, self.stream)
 
+    def attn_fwd_masked(self, qkv, y, y_masked, lse, mask_row, mask_table, *, B: int, S: int, n_heads: int, head_dim: int,
+                        sec: int | None = None, rope=None) -> None:
+        """Attention forward plus y_masked = y * mask_table[mask_row[sample]] (one launch on the tensor-core path)."""
+        sec = sec if sec is not None else n_heads * head_dim
+        rope = rope if rope is not None else self.rope_table(S, head_dim)
+        self._call("rte_attn_fwd_masked", _ptr(qkv), qkv.stride(0), sec, _ptr(y), _ptr(y_masked), y.stride(0), _ptr(lse),
+                   _ptr(rope), _ptr(mask_row), _ptr(mask_table), B, S, n_heads, head_dim, self.stream)
+
     def attn_bwd(self, qkv, y, dy, lse, dqkv, *, B: int, S: int, n_heads: int, head_dim: int,
                  sec: int | None = None, rope=None) -> None:
         sec = sec if sec is not None else n_heads * head_dim

@@ -239,6 +239,16 @@ def test_attention_fwd_bwd(ops, B, S, H, hd):
     torch.cuda.synchronize()
     _close(y, yref, 2e-2, "attention out")
     _close(dq, lr.grad, 2e-2, "attention dqkv")
+    # forward with the column-masked second output == forward, then the mask as its own pass (same bits)
+    R = 3
+    tab = (torch.rand(R, d, generator=g) > 0.5).float().mul(0.5).to(DEV)
+    rows = torch.randint(0, R, (B,), generator=g).to(DEV, torch.int32)
+    y2, ym, lse2 = torch.zeros_like(y), torch.zeros_like(y), torch.zeros_like(lse)
+    ops.attn_fwd_masked(qd, y2, ym, lse2, rows, tab, B=B, S=S, n_heads=H, head_dim=hd)
+    ref_m = torch.zeros_like(y)
+    ops.colmask_mul(y, rows, tab, S, ref_m, B * S, d)
+    torch.cuda.synchronize()
+    assert torch.equal(y, y2) and torch.equal(lse, lse2) and torch.equal(ym, ref_m)
 
 
 # ------------------------------------------------------------------ router / top-k
