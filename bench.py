@@ -346,7 +346,7 @@ def main() -> None:
                                 "per_shape": roof["per_shape"], "side_stream": roof.get("side_stream")}
         if world == 1 and not args.no_cpu_baseline:
             threads = os.cpu_count() or 1
-            v, sample = cpu_port_tokens_per_sec(sample_batch=8, steps=3, threads=threads)
+            v, sample = cpu_port_tokens_per_sec(sample_batch=128, steps=32, threads=threads)     # the full step; ~12 s on 16 host cores
             line["cpu_baseline"] = {"value": v, "unit": "tokens/s", "cores": threads, "kind": "port", "sample": sample}
         _emit(json.dumps(line))
     eng.close()
