@@ -63,7 +63,7 @@ enum {
   RTE_EPI_BF16 = 0,        /* C bf16 = acc                                                   */
   RTE_EPI_F32 = 1,         /* C f32 = acc (+ R f32 when R != NULL; R may alias C).            */
                            /* With splits > 1 partial s goes to C + s*split_stride (no R).    */
-  RTE_EPI_SWIGLU_FWD = 2,  /* B rows [n, n+128) = up, [b_pair_offset+n, ..) = gate (N = 2F):  */
+  RTE_EPI_SWIGLU_FWD = 2,  /* B rows [0,F) = up, [F,2F) = gate, F = b_pair_offset (N = 2F): */
                            /* C2 bf16 [M,2F] = (up | gate), C bf16 [M,F] = up * silu(gate)    */
   RTE_EPI_SWIGLU_BWD = 3   /* acc = dz [M,F]; R bf16 [M,2F] = saved (up | gate):              */
                            /* C bf16 [M,2F] = (dz*silu(g) | dz*up*sig(g)*(1+g*(1-sig(g))))    */
@@ -93,9 +93,17 @@ typedef struct rte_gemm_args {
    * [split_kblocks[s], split_kblocks[s+1]) (device int32 [splits+1]) into C + s*split_stride; an empty range gives
    * zeros.  RTE_EPI_F32 only.  NULL = equal splits.                                                             */
   const int32_t* split_kblocks;
+  /* Tile shape (0 = chosen by the library).  tile_n: 128 or 256 columns per tile.  cta_pair: 1 = every tile is
+   * 128 rows on one CTA; otherwise a product with more than 128 rows (and neither grouping nor ragged splits) runs
+   * 256-row tiles on pairs of CTAs (tcgen05 cta_group::2), each CTA loading half of the tile's B operand.       */
+  int32_t tile_n;
+  int32_t cta_pair;
 } rte_gemm_args;
 
 int rte_gemm_bf16(const rte_gemm_args* args, rte_stream_t stream);
+/* The tile shape rte_gemm_bf16 would use for `args` (M, N, epilogue, grouping, tile hints and max_ctas are read) and
+ * how many tiles run at the same time: what a caller needs to choose a split count.  Any output may be NULL.  */
+int rte_gemm_tile_plan(const rte_gemm_args* args, int32_t* tile_m, int32_t* tile_n, int32_t* concurrent_tiles);
 /* The same product for FEW ROWS (the audited samples' replay, models.py:605-679: M = one or two samples): one
  * 128-thread CTA per 64x64 output tile, cp.async + mma.sync, no tensor maps or TMEM set-up, so a dependent chain of
  * such launches is not dominated by set-up time.  Subset of rte_gemm_args: A K-major, B either major, RTE_EPI_BF16
@@ -310,6 +318,31 @@ int rte_adamw_multi_tensor(const rte_adamw_tensor* table, int32_t n_tensors, int
                            int32_t* step_count, float beta1, float beta2, float eps, float weight_decay,
                            const float* grad_scale, rte_stream_t stream);
 enum { RTE_ADAMW_CHUNK = 4096 };
+/* The same update with the optional parts of the reference's `_finish_step` (training.py:445-468, 386-443):
+ *  skip: device int32; non-zero makes the launch a no-op (no parameter, moment, shadow or step-count change): the
+ *        step whose loss was not finite is dropped.  Written by rte_nonfinite_guard.
+ *  metric_out f32 [n_metric_groups][2]: sum of (grad_scale*g)^2 and of p^2 (before the update) per metric group,
+ *        metric_group int32 [n_tensors] (device) naming each table tensor's group; metric_partial f32
+ *        [total_chunks][2] is scratch.  All three NULL = no metrics.  Deterministic two-stage sums.          */
+typedef struct rte_adamw_extras {
+  const int32_t* skip;
+  float* metric_partial;
+  const int32_t* metric_group;
+  float* metric_out;
+  int32_t n_metric_groups;
+} rte_adamw_extras;
+int rte_adamw_multi_tensor_ex(const rte_adamw_tensor* table, int32_t n_tensors, int64_t total_chunks,
+                              const int32_t* chunk_tensor, const int32_t* chunk_index, const float* lr_table,
+                              int32_t* step_count, float beta1, float beta2, float eps, float weight_decay,
+                              const float* grad_scale, const rte_adamw_extras* extras, rte_stream_t stream);
+/* *skip = 1 if any of a[0..na), b[0..nb) or c[0..nc) is NaN or infinite, else 0 (`torch.isfinite(loss)`,
+ * training.py:448, applied to the pieces the loss is assembled from); *flag_out (optional f32) receives the same as
+ * 1.0 / 0.0.  Ranges with a zero count may be NULL.                                                          */
+int rte_nonfinite_guard(const float* a, int32_t na, const float* b, int32_t nb, const float* c, int32_t nc,
+                        int32_t* skip, float* flag_out, rte_stream_t stream);
+/* dst += src unless *skip != 0 (gradient accumulation over micro-batches, training.py:445-455: a micro-batch whose loss
+ * is not finite contributes nothing).                                                                         */
+int rte_add_f32_guarded(float* dst, const float* src, int64_t n, const int32_t* skip, rte_stream_t stream);
 /* sumsq[0] = sum over all table tensors of g^2 (deterministic two-stage); clip_coef[0] =
  * min(1, max_norm / (sqrt(sumsq) + 1e-6)) (torch.nn.utils.clip_grad_norm_, training.py:456-462).
  * partial f32 >= total_chunks.                                                                       */

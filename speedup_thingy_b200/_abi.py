@@ -36,6 +36,8 @@ class GemmArgs(C.Structure):
         ("n_groups", c_i32),
         ("b_group_stride", c_i32),
         ("split_kblocks", c_vp),
+        ("tile_n", c_i32),
+        ("cta_pair", c_i32),
     ]
 
 
@@ -66,6 +68,11 @@ class AdamWTensor(C.Structure):
                 ("n", c_i64), ("lr_group", c_i32), ("step_slot", c_i32)]
 
 
+class AdamWExtras(C.Structure):
+    _fields_ = [("skip", c_vp), ("metric_partial", c_vp), ("metric_group", c_vp), ("metric_out", c_vp),
+                ("n_metric_groups", c_i32)]
+
+
 P = C.POINTER
 
 # name -> (restype, argtypes); mirrors include/rte_b200.h declaration by declaration
@@ -75,6 +82,7 @@ PROTOTYPES = {
     "rte_device_sm_count": (C.c_int, []),
     "rte_gemm_bf16": (C.c_int, [P(GemmArgs), c_vp]),
     "rte_gemm_bf16_small": (C.c_int, [P(GemmArgs), c_vp]),
+    "rte_gemm_tile_plan": (C.c_int, [P(GemmArgs), P(c_i32), P(c_i32), P(c_i32)]),
     "rte_reduce_splits": (C.c_int, [c_vp, c_i32, c_i64, c_i64, c_vp, c_i32, c_vp]),
     "rte_embed_fwd": (C.c_int, [c_vp, c_vp, c_vp, c_i32, c_i32, c_i32, c_vp, c_vp]),
     "rte_embed_bwd": (C.c_int, [c_vp, c_vp, c_vp, c_vp, c_i32, c_i32, c_i32, c_vp, c_vp]),
@@ -121,6 +129,10 @@ PROTOTYPES = {
     "rte_axpy_rows_f32": (C.c_int, [c_vp, c_vp, c_f32, c_i32, c_i32, c_i32, c_vp]),
     "rte_adamw_multi_tensor": (C.c_int, [c_vp, c_i32, c_i64, c_vp, c_vp, c_vp, c_vp, c_f32, c_f32, c_f32, c_f32,
                                          c_vp, c_vp]),
+    "rte_adamw_multi_tensor_ex": (C.c_int, [c_vp, c_i32, c_i64, c_vp, c_vp, c_vp, c_vp, c_f32, c_f32, c_f32, c_f32,
+                                            c_vp, P(AdamWExtras), c_vp]),
+    "rte_nonfinite_guard": (C.c_int, [c_vp, c_i32, c_vp, c_i32, c_vp, c_i32, c_vp, c_vp, c_vp]),
+    "rte_add_f32_guarded": (C.c_int, [c_vp, c_vp, c_i64, c_vp, c_vp]),
     "rte_grad_norm_multi_tensor": (C.c_int, [c_vp, c_i64, c_vp, c_vp, c_vp, c_vp, c_f32, c_vp, c_vp]),
     "rte_shortlist_build": (C.c_int, [c_vp, c_vp, c_vp, c_vp, c_vp] + [c_i32] * 7 + [c_vp, c_vp]),
     "rte_shortlist_ce": (C.c_int, [c_vp, c_vp, c_vp, c_vp, c_i32, c_vp, c_vp, c_vp, c_i32, c_i32, c_i32, c_i32, c_vp]),

@@ -100,7 +100,7 @@ class AuditReplay:
         self.hot_end = e(Ma, d)
         self.terms, self.dhot_extra, self.kl_rows, self.kl_sum = e(n, 4), e(Ma, d), e(Ma), e(1)
         self.dkl = e(Ma, V)
-        self.row_weight_a = torch.full((n,), 1.0 / (eng.B * eng.S * eng.world) / self.p_inc, dtype=f32, device=dev)
+        self.row_weight_a = torch.full((n,), 1.0 / (eng.B * eng.S * eng.loss_div) / self.p_inc, dtype=f32, device=dev)
         # backward scratch
         self.dn_f32, self.dh0_acc, self.dcur, self.dalt = e(Ma, d), e(Ma, d), e(Ma, d), e(Ma, d)
         self.d16b = e(Ma, d, dtype=bf)
@@ -169,7 +169,7 @@ class AuditReplay:
         gen = torch.Generator().manual_seed(step_seed)
         chosen = torch.sort(torch.randperm(eng.B, generator=gen)[: self.k]).values
         h_idx, h_rw = self._stage[self._stage_next]
-        w0 = 1.0 / (eng.B * eng.S * eng.world)
+        w0 = 1.0 / (eng.B * eng.S * eng.loss_div)
         h_idx.copy_(chosen)
         h_rw.fill_(w0)
         h_rw[chosen] = w0 * (1.0 - 1.0 / self.p_inc)                     # d corrected / d hot on audited samples
@@ -261,7 +261,7 @@ class AuditReplay:
         o, cfg = eng.ops, eng.cfg
         n, S, T, d = self.n, self.S, self.T, cfg.d_model
         o.gather_rows(h_phi, self.idx, self.hot_end, n, S * d * 4)
-        tr, w = eng.tr, 1.0 / eng.world
+        tr, w = eng.tr, 1.0 / eng.loss_div
         o.macro_distill(self.hot_end, self.h[T], self.h0a, tr.lambda_delta_dir * w, tr.lambda_delta_rms * w,
                         tr.lambda_endpoint_normed * w, tr.lambda_endpoint_raw * w, self.terms, self.dhot_extra, n, S, d)
 
@@ -270,7 +270,7 @@ class AuditReplay:
         goes to `self.dkl` (the hot pass adds it to its dlogits with `add_kl_grad` once its own cross-entropy kernel
         has written them, so this launch can run beside that kernel)."""
         eng = self.eng
-        o, cfg, tr, w = eng.ops, eng.cfg, eng.tr, 1.0 / eng.world
+        o, cfg, tr, w = eng.ops, eng.cfg, eng.tr, 1.0 / eng.loss_div
         n, Ma, V = self.n, self.Ma, cfg.vocab_size
         temp = max(float(tr.distill_temperature), 1e-6)
         if not eng.shortlist:      # the shortlist head keeps no full hot logits, so the KL term is absent (models.py:698-703)

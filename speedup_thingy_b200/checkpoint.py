@@ -5,11 +5,15 @@ the step counters -- so a run can move between the reference and this engine in 
 """
 from __future__ import annotations
 
+import dataclasses
+import logging
 from pathlib import Path
 
 import torch
 
 from .engine import TrainEngine
+
+log = logging.getLogger(__name__)
 
 
 def optimizer_layout(engine: TrainEngine) -> list[tuple[str, list[str]]]:
@@ -45,15 +49,20 @@ def optimizer_state_dict(engine: TrainEngine) -> dict:
 
 
 def save_checkpoint(engine: TrainEngine, path: str | Path, *, data_cursor: int | None = None) -> None:
+    """Writes the reference's payload.  The configuration is stored as plain nested dicts (the reference's loader
+    never reads it back, training.py:1681-1701), so the file unpickles where this package is not importable."""
+    if engine._pending:
+        # global_step advances at submit, tokens_seen / usage_ema at collect: a snapshot in between is inconsistent
+        raise RuntimeError("steps are in flight: collect() them before saving a checkpoint")
     model = {n: t.detach().to("cpu").clone() for n, t in engine.params.items()}
     if not engine.dense:
         # the reference model's two persistent buffers (macro.py:99-122): the per-key update scale the macro kernels
         # read, and the teacher statistic only the reference's distillation tooling writes
         model["macro.update_scale"] = engine.macro_scale.detach().to("cpu").clone()
         model["macro.teacher_delta_rms"] = engine.macro_teacher_delta_rms.clone()
-    payload = {"config": engine.config, "model": model,
+    payload = {"config": dataclasses.asdict(engine.config), "model": model,
                "optimizer": optimizer_state_dict(engine), "global_step": engine.global_step,
-               "global_micro_step": engine.global_step, "tokens_seen": engine.tokens_seen, "audit": {},
+               "global_micro_step": engine._micro, "tokens_seen": engine.tokens_seen, "audit": {},
                "aligned_lm_phase": "aligned_lm", "data_cursor": data_cursor, "usage_ema": engine.usage_ema.clone(),
                "torch_rng_state": torch.get_rng_state()}
     p = Path(path)
@@ -76,6 +85,9 @@ def load_checkpoint(engine: TrainEngine, path: str | Path) -> int | None:
         t.copy_(model[n].to(t.dtype))
     for n, sh in engine.shadow.items():
         engine.ops.cast_bf16(engine.params[n], sh)
+    if engine.shortlist:
+        # the shortlist head's cluster router is in no optimiser group: its bf16 copy changes only here
+        engine.ops.cast_bf16(engine.params["shortlist_head.cluster_router.weight"], engine.cluster_w16)
     if not engine.dense:
         if "macro.update_scale" in model:
             engine.macro_scale.copy_(model["macro.update_scale"].to(engine.macro_scale.dtype))
@@ -97,10 +109,18 @@ def load_checkpoint(engine: TrainEngine, path: str | Path) -> int | None:
                     engine.exp_avg[n].copy_(st["exp_avg"])
                     engine.exp_avg_sq[n].copy_(st["exp_avg_sq"])
                     steps[slot[n]] = int(float(st["step"]))
-        # a different grouping (e.g. a macro-only optimizer): weights load, the optimizer starts fresh (training.py:1683-1689)
+        else:
+            # a different grouping (e.g. a macro-only optimizer, or a build with a separate output group): weights
+            # load, the optimizer starts fresh (training.py:1683-1689)
+            log.warning("checkpoint %s: optimizer state has %d parameter slots, this engine's layout %d; "
+                        "optimizer state discarded, moments and step counters start from zero", path, len(saved), len(order))
     engine.plan.step_count.copy_(steps)
     engine.global_step = int(payload.get("global_step", 0))
     engine.tokens_seen = int(payload.get("tokens_seen", 0))
+    engine._micro = int(payload.get("global_micro_step", engine.global_step * engine.accum))
+    engine._tokens_scheduled = engine.tokens_seen * engine.world        # the LR schedule resumes where it stopped
+    engine._write_lr_table(engine.tr.lr_scale(engine._tokens_scheduled))
+    engine._refresh_static_param_sq()
     if isinstance(payload.get("usage_ema"), torch.Tensor) and payload["usage_ema"].shape == engine.usage_ema.shape:
         engine.usage_ema.copy_(payload["usage_ema"])
     return payload.get("data_cursor")

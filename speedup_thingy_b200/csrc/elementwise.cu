@@ -440,6 +440,10 @@ __global__ void fill_kernel(float* __restrict__ dst, float value, long long n) {
 __global__ void add_kernel(float* __restrict__ dst, const float* __restrict__ src, long long n) {
   for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) dst[i] += src[i];
 }
+__global__ void add_guarded_kernel(float* __restrict__ dst, const float* __restrict__ src, long long n, const int32_t* __restrict__ skip) {
+  if (*skip != 0) return;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) dst[i] += src[i];
+}
 __global__ void axpy_rows_kernel(float* __restrict__ dst, const float* __restrict__ vec, float alpha, int rows, int seg, int d) {
   const long long total = (long long)rows * d;
   for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
@@ -449,11 +453,20 @@ __global__ void axpy_rows_kernel(float* __restrict__ dst, const float* __restric
 }
 
 // ------------------------------------------------------------------ AdamW
+// `skip` (optional device flag): non-zero turns the whole launch into a no-op -- parameters, moments, shadows and step
+// counters stay as they are (the reference drops a step whose loss is not finite, training.py:448-452).
+// `metric_partial` (optional, [chunks][2]): per-chunk sums of (grad_scale * g)^2 and of p^2 BEFORE the update, the
+// raw material of the per-group gradient / parameter norms (training.py:386-443); reduced by adamw_metric_kernel.
 __global__ void __launch_bounds__(256)
 adamw_kernel(const rte_adamw_tensor* __restrict__ table, const int32_t* __restrict__ chunk_tensor,
              const int32_t* __restrict__ chunk_index, const float* __restrict__ lr_table,
              const int32_t* __restrict__ step_count, float beta1, float beta2, float eps, float wd,
-             const float* __restrict__ grad_scale) {
+             const float* __restrict__ grad_scale, const int32_t* __restrict__ skip, float* __restrict__ metric_partial) {
+  __shared__ float red[32];
+  if (skip != nullptr && *skip != 0) {
+    if (metric_partial != nullptr && threadIdx.x == 0) { metric_partial[2 * blockIdx.x] = 0.f; metric_partial[2 * blockIdx.x + 1] = 0.f; }
+    return;
+  }
   const int ti = chunk_tensor[blockIdx.x];
   const rte_adamw_tensor t = table[ti];
   const long long base = (long long)chunk_index[blockIdx.x] * RTE_ADAMW_CHUNK;
@@ -463,22 +476,60 @@ adamw_kernel(const rte_adamw_tensor* __restrict__ table, const int32_t* __restri
   const float gs = grad_scale ? *grad_scale : 1.f;
   const float step_size = lr / bc1, inv_sqrt_bc2 = rsqrtf(bc2), decay = 1.f - lr * wd;
   __nv_bfloat16* shadow = reinterpret_cast<__nv_bfloat16*>(t.bf16_shadow);
+  float gsq = 0.f, psq = 0.f;
 #pragma unroll 4
   for (int j = threadIdx.x; j < RTE_ADAMW_CHUNK; j += blockDim.x) {
     const long long i = base + j;
     if (i >= t.n) break;
     const float g = t.g[i] * gs;
-    float p = t.p[i] * decay;
+    const float p0 = t.p[i];
+    gsq += g * g; psq += p0 * p0;
+    float p = p0 * decay;
     const float m = beta1 * t.m[i] + (1.f - beta1) * g;
     const float v = beta2 * t.v[i] + (1.f - beta2) * g * g;
     p -= step_size * m / (sqrtf(v) * inv_sqrt_bc2 + eps);
     t.p[i] = p; t.m[i] = m; t.v[i] = v;
     if (shadow) shadow[i] = __float2bfloat16_rn(p);
   }
+  if (metric_partial != nullptr) {       // uniform branch: every thread of the block takes part in the reductions
+    gsq = block_sum(gsq, red);
+    psq = block_sum(psq, red);
+    if (threadIdx.x == 0) { metric_partial[2 * blockIdx.x] = gsq; metric_partial[2 * blockIdx.x + 1] = psq; }
+  }
 }
-__global__ void adamw_step_kernel(const rte_adamw_tensor* __restrict__ table, int n_tensors, int32_t* step_count) {
+__global__ void adamw_step_kernel(const rte_adamw_tensor* __restrict__ table, int n_tensors, int32_t* step_count,
+                                  const int32_t* __restrict__ skip) {
+  if (skip != nullptr && *skip != 0) return;
   const int i = blockIdx.x * blockDim.x + threadIdx.x;
   if (i < n_tensors) step_count[table[i].step_slot] += 1;
+}
+// out[2*g] = sum of grad^2, out[2*g+1] = sum of param^2 over the chunks of the tensors of metric group g = blockIdx.x
+// (fixed summation order: reproducible).
+__global__ void __launch_bounds__(256)
+adamw_metric_kernel(const int32_t* __restrict__ chunk_tensor, const int32_t* __restrict__ metric_group, long long total_chunks,
+                    const float* __restrict__ partial, float* __restrict__ out) {
+  __shared__ float red[32];
+  float a = 0.f, b = 0.f;
+  for (long long c = threadIdx.x; c < total_chunks; c += blockDim.x)
+    if (metric_group[chunk_tensor[c]] == (int)blockIdx.x) { a += partial[2 * c]; b += partial[2 * c + 1]; }
+  a = block_sum(a, red);
+  b = block_sum(b, red);
+  if (threadIdx.x == 0) { out[2 * blockIdx.x] = a; out[2 * blockIdx.x + 1] = b; }
+}
+// skip = 1 (and flag_out = 1.0) when any of the listed values is not finite, else 0.
+__global__ void __launch_bounds__(256)
+nonfinite_guard_kernel(const float* __restrict__ a, int na, const float* __restrict__ b, int nb, const float* __restrict__ c, int nc,
+                       int32_t* skip, float* flag_out) {
+  __shared__ int bad;
+  if (threadIdx.x == 0) bad = 0;
+  __syncthreads();
+  int mine = 0;
+  for (int i = threadIdx.x; i < na; i += blockDim.x) mine |= !isfinite(a[i]);
+  for (int i = threadIdx.x; i < nb; i += blockDim.x) mine |= !isfinite(b[i]);
+  for (int i = threadIdx.x; i < nc; i += blockDim.x) mine |= !isfinite(c[i]);
+  if (mine) atomicOr(&bad, 1);
+  __syncthreads();
+  if (threadIdx.x == 0) { *skip = bad; if (flag_out) *flag_out = bad ? 1.f : 0.f; }
 }
 
 __global__ void __launch_bounds__(256)
@@ -516,7 +567,9 @@ static __device__ __align__(256) float g_gradnorm_scratch[GRADNORM_STATIC_MAX_CH
 constexpr int MAX_DEVICES = 64;
 float* g_gradnorm_scratch_addr[MAX_DEVICES] = {nullptr};
 
-// Returns the device address of the scratch array on the CURRENT device (looked up on first use).
+// Returns the device address of the scratch array on the CURRENT device (looked up on first use).  The cache is
+// written without a lock: two host threads that make the first call on a device at the same time both look the
+// address up and store the same value, which is harmless.
 int gradnorm_scratch_for_current_device(float** out) {
   int dev = -1;
   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= MAX_DEVICES) return RTE_ERR_NO_DEVICE;
@@ -853,15 +906,49 @@ extern "C" int rte_axpy_rows_f32(float* dst, const float* vec, float alpha, int3
   return RTE_OK;
 }
 
+extern "C" int rte_adamw_multi_tensor_ex(const rte_adamw_tensor* table, int32_t n_tensors, int64_t total_chunks,
+                                         const int32_t* chunk_tensor, const int32_t* chunk_index, const float* lr_table,
+                                         int32_t* step_count, float beta1, float beta2, float eps, float weight_decay,
+                                         const float* grad_scale, const rte_adamw_extras* ex, rte_stream_t stream) {
+  RTE_CHECK_ARG(table && chunk_tensor && chunk_index && lr_table && step_count && n_tensors > 0 && total_chunks > 0);
+  const int32_t* skip = ex ? ex->skip : nullptr;
+  float* mpart = nullptr;
+  if (ex && ex->metric_out) {
+    RTE_CHECK_ARG(ex->metric_partial && ex->metric_group && ex->n_metric_groups > 0);
+    mpart = ex->metric_partial;
+  }
+  adamw_kernel<<<(unsigned)total_chunks, 256, 0, ST(stream)>>>(table, chunk_tensor, chunk_index, lr_table, step_count,
+                                                               beta1, beta2, eps, weight_decay, grad_scale, skip, mpart);
+  RTE_LAUNCH_CHECK();
+  adamw_step_kernel<<<rte::ceil_div(n_tensors, 128), 128, 0, ST(stream)>>>(table, n_tensors, step_count, skip);
+  RTE_LAUNCH_CHECK();
+  if (mpart) {
+    adamw_metric_kernel<<<ex->n_metric_groups, 256, 0, ST(stream)>>>(chunk_tensor, ex->metric_group, total_chunks, mpart,
+                                                                     ex->metric_out);
+    RTE_LAUNCH_CHECK();
+  }
+  return RTE_OK;
+}
+
 extern "C" int rte_adamw_multi_tensor(const rte_adamw_tensor* table, int32_t n_tensors, int64_t total_chunks,
                                       const int32_t* chunk_tensor, const int32_t* chunk_index, const float* lr_table,
                                       int32_t* step_count, float beta1, float beta2, float eps, float weight_decay,
                                       const float* grad_scale, rte_stream_t stream) {
-  RTE_CHECK_ARG(table && chunk_tensor && chunk_index && lr_table && step_count && n_tensors > 0 && total_chunks > 0);
-  adamw_kernel<<<(unsigned)total_chunks, 256, 0, ST(stream)>>>(table, chunk_tensor, chunk_index, lr_table, step_count,
-                                                               beta1, beta2, eps, weight_decay, grad_scale);
+  return rte_adamw_multi_tensor_ex(table, n_tensors, total_chunks, chunk_tensor, chunk_index, lr_table, step_count, beta1,
+                                   beta2, eps, weight_decay, grad_scale, nullptr, stream);
+}
+
+extern "C" int rte_add_f32_guarded(float* dst, const float* src, int64_t n, const int32_t* skip, rte_stream_t stream) {
+  RTE_CHECK_ARG(dst && src && skip && n > 0);
+  add_guarded_kernel<<<grid_for(n, 256), 256, 0, ST(stream)>>>(dst, src, n, skip);
   RTE_LAUNCH_CHECK();
-  adamw_step_kernel<<<rte::ceil_div(n_tensors, 128), 128, 0, ST(stream)>>>(table, n_tensors, step_count);
+  return RTE_OK;
+}
+
+extern "C" int rte_nonfinite_guard(const float* a, int32_t na, const float* b, int32_t nb, const float* c, int32_t nc,
+                                   int32_t* skip, float* flag_out, rte_stream_t stream) {
+  RTE_CHECK_ARG(skip && na >= 0 && nb >= 0 && nc >= 0 && (a || na == 0) && (b || nb == 0) && (c || nc == 0));
+  nonfinite_guard_kernel<<<1, 256, 0, ST(stream)>>>(a, na, b, nb, c, nc, skip, flag_out);
   RTE_LAUNCH_CHECK();
   return RTE_OK;
 }

@@ -21,10 +21,21 @@ from typing import Any
 import torch
 
 from . import _abi as A
-from .config import ExperimentConfig, ModelConfig, TrainingConfig
+from .config import ExperimentConfig, ModelConfig, TrainingConfig, check_supported
 from .ops import AdamWPlan
 
 LR_GROUPS = ["embedding", "prelude", "core", "macro", "coda", "output", "router", "dense"]
+# groups whose gradient / parameter norms are reported (training.py:386-443): the optimizer's groups, with the core's
+# per-pass FiLM vectors and per-pass scales counted separately as well (they also belong to "core")
+METRIC_GROUPS = LR_GROUPS + ["pass_film", "pass_scale"]
+
+
+def metric_group_of(name: str, topology: str) -> int:
+    if name.startswith(("core.pass_gamma", "core.pass_beta")):
+        return METRIC_GROUPS.index("pass_film")
+    if name in ("core.pass_attn_scale", "core.pass_mlp_scale"):
+        return METRIC_GROUPS.index("pass_scale")
+    return METRIC_GROUPS.index(lr_group_of(name, topology))
 
 
 # --------------------------------------------------------------------------- parameters
@@ -174,7 +185,9 @@ class _Temps:
 class TrainEngine:
     def __init__(self, config: ExperimentConfig, params: dict[str, torch.Tensor] | None = None, *,
                  device: str | torch.device = "cuda:0", ops=None, use_cuda_graph: bool = True,
-                 process_group=None, bucket_cap_mb: float = 25.0, swiglu_fuse_max_rows: int = 1024):
+                 process_group=None, bucket_cap_mb: float = 25.0, swiglu_fuse_max_rows: int = 1024,
+                 grad_metrics: bool = True):
+        check_supported(config)          # NotImplementedError naming every configured value this path lacks
         self.config = config
         self.cfg, self.tr = config.model, config.training
         self.device = torch.device(device)
@@ -200,24 +213,28 @@ class TrainEngine:
             if os.environ.get("RTE_DP_GRAPH", "1") == "0":
                 self.use_cuda_graph = False
         cfg, tr = self.cfg, self.tr
+        # gradient accumulation (training.py:445-455): every micro-batch contributes 1/accum of its gradient, the
+        # optimiser runs on every accum-th call
+        self.accum = int(tr.grad_accum_steps)
+        self.loss_div = self.world * self.accum         # what every loss weight is divided by
+        self._micro = 0
+        self.grad_metrics = bool(grad_metrics)
         self.B, self.S = tr.batch_size, tr.seq_len
         self.M = self.B * self.S
         self.dense = cfg.topology == "dense"
         if self.dense != (tr.mode == "dense_exact"):
             raise ValueError("mode dense_exact needs topology 'dense'; recursive_macro needs 'recursive'")
-        self.swiglu_fuse_max_rows = swiglu_fuse_max_rows
+        self.swiglu_fuse_max_rows = int(os.environ.get("RTE_SWIGLU_FUSE_MAX_ROWS", swiglu_fuse_max_rows))
         self.oc = config.output
         self.shortlist = tr.mode == "recursive_macro_shortlist"
         self.n_clusters = self.oc.num_clusters
         self.exact = tr.mode == "recursive_exact"       # every sample runs the banked recurrent core (training.py:771-797)
-        self.audit_k = int(tr.audit_fixed_count_per_batch or 0)
+        self.audit_k = int(tr.audit_fixed_count_per_batch or 0) if tr.audits_enabled else 0
         if self.exact and (self.audit_k or self.dense):
             raise ValueError("recursive_exact: recursive topology, no audit (the whole batch is exact)")
         if self.audit_k:
             if self.dense:
                 raise ValueError("the exact audit belongs to the recursive model")
-            if tr.audit_mode != "gradient_corrected" or tr.audit_residual_clip is not None:
-                raise NotImplementedError("audit: only audit_mode='gradient_corrected' without residual clipping")
             if self.S % 2:
                 raise NotImplementedError("audit: seq_len must be even")
         if cfg.d_model % 8 or cfg.d_ff % 64 or cfg.vocab_size % 8 or cfg.head_dim not in (8, 16, 32, 64, 128):
@@ -287,10 +304,16 @@ class TrainEngine:
             for n in CORE_SHADOWED:
                 self.shadow[n] = torch.empty_like(self.params[n], dtype=bf)
         entries = [dict(p=self.params[n], g=self.grads[n], m=self.exp_avg[n], v=self.exp_avg_sq[n],
-                        shadow=self.shadow.get(n), lr_group=LR_GROUPS.index(lr_group_of(n, cfg.topology)))
+                        shadow=self.shadow.get(n), lr_group=LR_GROUPS.index(lr_group_of(n, cfg.topology)),
+                        metric_group=metric_group_of(n, cfg.topology))
                    for n in self.trainable]
-        self.plan = AdamWPlan(entries, len(LR_GROUPS), dev)
+        self.plan = AdamWPlan(entries, len(LR_GROUPS), dev, n_metric_groups=len(METRIC_GROUPS))
+        self._lr_stage = None                            # pinned staging of the per-step learning-rate table
+        self._tokens_scheduled = 0                       # tokens of the steps submitted so far (LR schedule, all ranks)
         self._write_lr_table()
+        self.skip_flag = torch.zeros(1, dtype=torch.int32, device=dev)      # set by the non-finite guard of a step
+        self.accum_flat = torch.zeros_like(self.grad_flat) if self.accum > 1 else None
+        self._refresh_static_param_sq()
 
         # ---- activations
         M, d, V, B, S = self.M, cfg.d_model, cfg.vocab_size, self.B, self.S
@@ -310,12 +333,16 @@ class TrainEngine:
         self.logits = e(M, V, dtype=bf)
         # Everything the host reads back after a step lives in ONE buffer, so that it is one device-to-host copy:
         #   scalars[8] | loss_per_sample[B] | recipe_id[B] (int32) | audit terms[k,4] | audit exact_loss[k] | kl_sum[1]
+        #   | per metric group (sum grad^2, sum param^2)
         k_a = self.audit_k or 0
-        self._results = torch.zeros(8 + 2 * B + 5 * k_a + 1, dtype=f32, device=dev)
+        n_mg = len(METRIC_GROUPS)
+        self._results = torch.zeros(8 + 2 * B + 5 * k_a + 1 + 2 * n_mg, dtype=f32, device=dev)
         self.loss_tok = e(M)
-        self.scalars = self._results[0:8]                      # [0]=sum loss, [1]=aux load, [2]=aux depth, [3]=sumsq, [4]=clip
+        # [0]=sum loss, [1]=aux load, [2]=aux depth, [3]=sumsq, [4]=clip, [5]=1.0 when the step was dropped (non-finite)
+        self.scalars = self._results[0:8]
         self.loss_per_sample = self._results[8:8 + B]
-        self.row_weight = torch.full((B,), 1.0 / (B * S * self.world), dtype=f32, device=dev)
+        self._metric_sums = self._results[8 + 2 * B + 5 * k_a + 1:].view(n_mg, 2)
+        self.row_weight = torch.full((B,), 1.0 / (B * S * self.loss_div), dtype=f32, device=dev)
         # backward temporaries
         self.tmp = _Temps(M, cfg, dev)
         # Weight-gradient launches of the hot pass run on their own stream beside the data-gradient chain (they fill the
@@ -397,7 +424,7 @@ class TrainEngine:
             ops.rope_table(S, cfg.head_dim)          # built once, before any stream capture
         # the hot-path budget depends on the configuration only: checked once, before anything runs (training.py:1389-1392)
         self._budget = {} if (self.dense or self.exact) else hot_budget(cfg, tr, self.oc.shortlist_max_tokens if self.shortlist else None)
-        self._graph = None
+        self._graphs: dict[str, Any] = {}                  # captured step graphs: "step" (with optimiser), "micro"
         self._host: dict[str, Any] | None = None           # results of the step collected last
         self._host_slots = None
         self._slot_next = 0
@@ -507,8 +534,28 @@ class TrainEngine:
 
     # ------------------------------------------------------------------ small helpers
     def _write_lr_table(self, scale: float = 1.0) -> None:
-        lrs = [self.tr.lr_for(g) * scale for g in LR_GROUPS]
-        self.plan.lr_table.copy_(torch.tensor(lrs, dtype=torch.float32))
+        """Per-group learning rates x the schedule's factor -> the device table the AdamW kernel reads.  Per step the
+        values go through pinned staging (three buffers in rotation, as many as steps can be in flight plus one), so the
+        copy is stream-ordered in front of the step that uses it."""
+        lrs = torch.tensor([self.tr.lr_for(g) * scale for g in LR_GROUPS], dtype=torch.float32)
+        self._lr_now = {g: float(v) for g, v in zip(LR_GROUPS, lrs)}
+        if self._lr_stage is None:
+            pin = self.device.type == "cuda"
+            self._lr_stage = [torch.empty(len(LR_GROUPS), dtype=torch.float32, pin_memory=pin) for _ in range(3)]
+            self._lr_stage_next = 0
+        h = self._lr_stage[self._lr_stage_next]
+        self._lr_stage_next = (self._lr_stage_next + 1) % 3
+        h.copy_(lrs)
+        self.plan.lr_table.copy_(h, non_blocking=True)
+
+    def _refresh_static_param_sq(self) -> None:
+        """Sum of squares, per metric group, of the parameters the optimiser never touches in this mode (they count
+        towards the reference's per-group parameter norms, training.py:386-443, and only change on a checkpoint load)."""
+        out = [0.0] * len(METRIC_GROUPS)
+        for n, p in self.params.items():
+            if n not in self.trainable and not n.startswith("shortlist_head."):
+                out[metric_group_of(n, self.cfg.topology)] += float(p.double().pow(2).sum())
+        self._static_param_sq = out
 
     def _router_weight_dict(self) -> dict[str, torch.Tensor]:
         p = self.params
@@ -624,8 +671,8 @@ class TrainEngine:
         if not tr.disable_router_aux:
             rg = {f"{m_[0]}_{k_}": g[f"router.{m_}.{i_}.{w_}"] for m_ in ("recipe_mlp", "depth_mlp")
                   for i_, w_, k_ in ((0, "weight", "w0"), (0, "bias", "b0"), (2, "weight", "w2"), (2, "bias", "b2"))}
-            o.router_aux_bwd(self._router_weight_dict(), self.route, self.depth_values, tr.lambda_load / self.world,
-                             tr.lambda_depth / self.world, self.scalars[1:3], rg, dcur, self.router_scratch, B=B, S=S,
+            o.router_aux_bwd(self._router_weight_dict(), self.route, self.depth_values, tr.lambda_load / self.loss_div,
+                             tr.lambda_depth / self.loss_div, self.scalars[1:3], rg, dcur, self.router_scratch, B=B, S=S,
                              d=d, hid=cfg.router_hidden_dim, R=cfg.recipe_count, K=len(cfg.depth_choices))
         g16 = self.grad16
         o.cast_bf16(dcur, g16[0])
@@ -675,8 +722,8 @@ class TrainEngine:
                 ms = self._misc_param_stream
                 ms.wait_stream(torch.cuda.current_stream(self.device))
                 with torch.cuda.stream(ms):
-                    o.router_aux_bwd_early(self._router_weight_dict(), self.route, self.depth_values, tr.lambda_load / self.world,
-                                           tr.lambda_depth / self.world, self.scalars[1:3], self._router_grad_dict(),
+                    o.router_aux_bwd_early(self._router_weight_dict(), self.route, self.depth_values, tr.lambda_load / self.loss_div,
+                                           tr.lambda_depth / self.loss_div, self.scalars[1:3], self._router_grad_dict(),
                                            self.router_scratch, B=B, S=S, d=d, hid=cfg.router_hidden_dim,
                                            R=cfg.recipe_count, K=len(cfg.depth_choices))
                     self._router_early = torch.cuda.Event()
@@ -837,8 +884,8 @@ class TrainEngine:
                 else:
                     if split:
                         o.param_stream = misc
-                    o.router_aux_bwd_split(self._router_weight_dict(), self.route, self.depth_values, tr.lambda_load / self.world,
-                                           tr.lambda_depth / self.world, self.scalars[1:3], self._router_grad_dict(), dcur,
+                    o.router_aux_bwd_split(self._router_weight_dict(), self.route, self.depth_values, tr.lambda_load / self.loss_div,
+                                           tr.lambda_depth / self.loss_div, self.scalars[1:3], self._router_grad_dict(), dcur,
                                            self.router_scratch, **dims)
                     if split:
                         o.param_stream = None
@@ -869,13 +916,38 @@ class TrainEngine:
                 torch.cuda.current_stream(self.device).wait_stream(self._misc_param_stream)
         self._finish_backward()
 
+    def _loss_guard(self) -> None:
+        """Device-side `torch.isfinite(loss)` (training.py:448): flags the step when any piece the loss is assembled from
+        -- summed token loss, auxiliary terms, per-sample losses, the audited terms -- or, with clipping, the
+        gradient's sum of squares is not finite.  (The reference checks the loss only; a non-finite gradient norm
+        under clipping would write NaN into every weight there, so dropping that step too is the stricter reading.)"""
+        B, k_a = self.B, self.audit_k or 0
+        r = self._results
+        audit_part = r[8 + 2 * B: 8 + 2 * B + 5 * k_a + 1] if k_a else None
+        self.ops.nonfinite_guard([r[0:4], r[8:8 + B], audit_part], self.skip_flag, self.scalars[5:6])
+
     def _optimizer_step(self) -> None:
         o, tr = self.ops, self.tr
         clip = None
         if tr.grad_clip_norm is not None:
             o.grad_norm(self.plan, self.gn_partial, self.scalars[3:4], float(tr.grad_clip_norm), self.scalars[4:5])
             clip = self.scalars[4:5]
-        o.adamw(self.plan, 0.9, 0.999, 1e-8, tr.weight_decay, clip)
+        self._loss_guard()
+        o.adamw(self.plan, 0.9, 0.999, 1e-8, tr.weight_decay, clip, skip=self.skip_flag,
+                metric_out=self._metric_sums if self.grad_metrics else None)
+
+    def _accumulate(self, last: bool) -> None:
+        """Gradient accumulation: a micro-batch's gradients join `accum_flat` (unless its loss was not finite); on the
+        cycle's last micro-batch the sum moves into the gradient buffer the optimiser reads."""
+        if self.accum == 1:
+            return
+        o = self.ops
+        if not last:
+            self._loss_guard()
+            o.add_guarded_(self.accum_flat, self.grad_flat, self.skip_flag)
+        else:
+            o.add_(self.grad_flat, self.accum_flat)
+            o.fill_(self.accum_flat, 0.0)
 
     # ------------------------------------------------------------------ public API
     def _load_batch(self, batch) -> None:
@@ -892,33 +964,47 @@ class TrainEngine:
             rn = torch.randint(0, self.cfg.vocab_size, (self.B, self.S, self.oc.random_negatives), generator=gen)
             self.random_negs.copy_(rn.view(self.M, -1).to(torch.int32), non_blocking=True)
 
-    def _run_step_kernels(self, optimizer: bool) -> None:
-        if not self.use_cuda_graph or not optimizer or self._eager_steps_left > 0:
-            if optimizer and self._eager_steps_left > 0:
-                self._eager_steps_left -= 1
+    def _run_step_kernels(self, optimizer: bool, accumulate: bool = False) -> None:
+        """`optimizer`: forward + backward + optimiser (the last micro-batch of an accumulation cycle, or every call
+        without accumulation); `accumulate`: forward + backward + add into the accumulation buffer; neither: forward +
+        backward only (`loss_and_grads`)."""
+        def body() -> None:
             self._forward_backward()
             if optimizer:
+                self._accumulate(last=True)
                 self._optimizer_step()
+            elif accumulate:
+                self._accumulate(last=False)
+
+        if not self.use_cuda_graph or not (optimizer or accumulate) or self._eager_steps_left > 0:
+            if optimizer and self._eager_steps_left > 0:
+                self._eager_steps_left -= 1
+            body()
             return
-        if self._graph is None:
+        key = "step" if optimizer else "micro"
+        if self._graphs.get(key) is None:
             before = self.ops.launches
             torch.cuda.synchronize(self.device)
             graph = torch.cuda.CUDAGraph()
             # (capturing the hot pass on a raised-priority stream, so that its kernels are served before the
             # weight-gradient streams, was measured: +3 % step time; all streams but the replay's keep the default)
             with torch.cuda.graph(graph):
-                self._forward_backward()
-                self._optimizer_step()
-            self._graph = graph
-            self._launches_per_step = self.ops.launches - before
-        self._graph.replay()
+                body()
+            self._graphs[key] = graph
+            if optimizer:
+                self._launches_per_step = self.ops.launches - before
+        self._graphs[key].replay()
+
+    @property
+    def _graph(self):
+        return self._graphs.get("step")
 
     def close(self) -> None:
         """Drops the captured step graph (which, under data parallelism, holds NCCL kernels) after the device has
         drained, so that the process group can be torn down afterwards."""
         if self.device.type == "cuda":
             torch.cuda.synchronize(self.device)
-        self._graph = None
+        self._graphs.clear()
         if self.device.type == "cuda":
             torch.cuda.synchronize(self.device)
 
@@ -942,7 +1028,8 @@ class TrainEngine:
                 "event": torch.cuda.Event() if cuda else None,
                 "scalars": h[0:8], "loss_per_sample": h[8:8 + B], "recipe_id": h[8 + B:8 + 2 * B].view(torch.int32),
                 "terms": h[r0:r0 + 4 * k_a].view(k_a, 4), "exact_loss": h[r0 + 4 * k_a:r0 + 5 * k_a],
-                "kl_sum": h[r0 + 5 * k_a:r0 + 5 * k_a + 1]}
+                "kl_sum": h[r0 + 5 * k_a:r0 + 5 * k_a + 1],
+                "metric_sums": h[r0 + 5 * k_a + 1:].view(len(METRIC_GROUPS), 2)}
         return self._host_slots[i]
 
     def _queue_fetch(self) -> dict[str, Any]:
@@ -977,25 +1064,58 @@ class TrainEngine:
             self.last_audit = terms
         if not self.dense and not self.tr.disable_router_aux:
             cover = float(torch.relu(self.tr.coverage_min - self.usage_ema).square().sum()) * self.tr.lambda_cover
-            loss += (float(vals[1]) + float(vals[2])) * self.world + cover
+            loss += (float(vals[1]) + float(vals[2])) * self.loss_div + cover
         return loss
 
     MAX_IN_FLIGHT = 2
 
     def submit(self, batch) -> None:
-        """Queues one optimiser step on a [B,S] int64 (tokens, targets) batch and returns without waiting for the
+        """Queues one training call on a [B,S] int64 (tokens, targets) batch and returns without waiting for the
         device: the batch copy, the step's kernels (one graph replay) and the copy of its results into pinned host
-        memory are all stream-ordered.  At most `MAX_IN_FLIGHT` steps may be queued before `collect` is called;
-        a host batch must stay untouched until its step has been collected."""
+        memory are all stream-ordered.  With `grad_accum_steps` = A the call is a micro-batch: the optimiser runs on
+        every A-th call.  At most `MAX_IN_FLIGHT` steps may be queued before `collect` is called; a host batch must
+        stay untouched until its step has been collected."""
         if len(self._pending) >= self.MAX_IN_FLIGHT:
             raise RuntimeError(f"{len(self._pending)} steps already in flight: call collect() first")
         self._load_batch(batch)
-        self._run_step_kernels(optimizer=True)
-        self._pending.append(self._queue_fetch())
-        self.global_step += 1
+        lr_scale = self.tr.lr_scale(self._tokens_scheduled)        # training.py:470-490, from the tokens seen so far
+        if self.tr.lr_schedule != "constant":
+            self._write_lr_table(lr_scale)
+        self._micro += 1
+        stepping = self._micro % self.accum == 0
+        self._run_step_kernels(optimizer=stepping, accumulate=not stepping)
+        slot = self._queue_fetch()
+        slot["stepping"], slot["lr"] = stepping, dict(self._lr_now)
+        self._pending.append(slot)
+        self._tokens_scheduled += self.B * self.S * self.world
+        if stepping:
+            self.global_step += 1
         if self.audit is not None:
             # host work for the NEXT step (the seeded permutation of its audited subset) while the device runs this one
             self.audit.prepare(self.tr.seed + 10_000 + self.global_step)
+
+    def _grad_metrics(self, host: dict[str, Any]) -> dict[str, float]:
+        """training.py:386-443 from the per-group sums the AdamW launch left in the results buffer: gradient norm (after
+        clipping) and lr * |g| / |p| per optimizer group, plus the core's per-pass FiLM / scale sub-groups."""
+        sums = host["metric_sums"]
+        gsq = [float(sums[i, 0]) for i in range(len(METRIC_GROUPS))]
+        psq = [float(sums[i, 1]) + self._static_param_sq[i] for i in range(len(METRIC_GROUPS))]
+        core, film, scale = (METRIC_GROUPS.index(x) for x in ("core", "pass_film", "pass_scale"))
+        out: dict[str, float] = {}
+        present = {lr_group_of(n, self.cfg.topology) for n in self.params if not n.startswith("shortlist_head.")}
+        for i, name in enumerate(LR_GROUPS):
+            if name not in present:
+                continue
+            g2, p2 = gsq[i], psq[i]
+            if i == core:                 # the sub-groups are part of the core group as well
+                g2, p2 = g2 + gsq[film] + gsq[scale], p2 + psq[film] + psq[scale]
+            out[f"grad_norm_{name}"] = g2 ** 0.5
+            out[f"update_ratio_{name}"] = host["lr"][name] * g2 ** 0.5 / max(p2 ** 0.5, 1e-12)
+        if not self.dense:
+            for i, name in ((film, "pass_film"), (scale, "pass_scale")):
+                out[f"grad_norm_{name}"] = gsq[i] ** 0.5
+                out[f"update_ratio_{name}"] = host["lr"]["core"] * gsq[i] ** 0.5 / max(psq[i] ** 0.5, 1e-12)
+        return out
 
     def collect(self) -> TrainStepResult:
         """Waits for the oldest queued step and returns its loss and metrics (steps complete in submission order)."""
@@ -1003,7 +1123,19 @@ class TrainEngine:
             raise RuntimeError("no step in flight")
         host = self._wait_fetch(self._pending.pop(0))
         loss = self._assemble_loss(host)
-        metrics: dict[str, Any] = {"mode": self.tr.mode, "loss": loss}
+        metrics: dict[str, Any] = {"mode": self.tr.mode, "loss": loss, "lr": host["lr"][LR_GROUPS[0] if not self.dense else "dense"]}
+        skipped = float(host["scalars"][5]) != 0.0
+        stepped = bool(host["stepping"]) and not skipped
+        metrics["did_optimizer_step"] = stepped
+        if skipped:
+            # training.py:448-452: a non-finite loss drops the step; weights, moments and step counters are untouched
+            # (the device flag made the AdamW launch a no-op).  Steps queued behind it were seeded with the
+            # speculative step number; from here on `global_step` again counts optimiser steps taken.
+            metrics["skipped_nonfinite_loss"] = 1.0
+            if host["stepping"]:
+                self.global_step -= 1
+        elif stepped and self.grad_metrics:
+            metrics.update(self._grad_metrics(host))
         if not self.dense:
             ids = host["recipe_id"].long()
             counts = torch.bincount(ids, minlength=self.cfg.recipe_count).float()

@@ -47,6 +47,10 @@ class CudaOps:
         self.small_gemm_rows = 256  # products with at most this many rows go to the few-row kernel (0: never)
         self.few_rows_max_splits = int(os.environ.get("RTE_FEWROW_SPLITS", "4"))
         self.gemm_max_ctas = 0     # 0 = one persistent CTA per SM; smaller values leave SMs to kernels of other streams
+        # tile hints passed to every tcgen05 GEMM (0 = the library's choice): RTE_GEMM_PAIR=0 keeps every tile on one
+        # CTA (no cta_group::2 pairs), RTE_GEMM_TILE_N forces 128 or 256 columns per tile
+        self.gemm_cta_pair = 1 if os.environ.get("RTE_GEMM_PAIR", "1") == "0" else 0
+        self.gemm_tile_n = int(os.environ.get("RTE_GEMM_TILE_N", "0"))
         # When set, launches that only produce PARAMETER gradients (weight-gradient GEMMs with their split reduction,
         # column-sum reductions of the norm backward) go to this stream, ordered after the work issued so far on the
         # current one: a latency-bound backward chain then carries only the data-gradient launches.
@@ -87,7 +91,7 @@ class CudaOps:
              epilogue: int = A.EPI_BF16, residual=None, out2=None, pair: int = 0, splits: int = 1,
              split_stride: int = 0, lda: int | None = None, ldb: int | None = None, ldc: int | None = None,
              ldr: int | None = None, ldc2: int | None = None, tile_group=None, n_groups: int = 0,
-             b_group_stride: int = 0, split_kblocks=None) -> None:
+             b_group_stride: int = 0, split_kblocks=None, tile_n: int | None = None, cta_pair: int | None = None) -> None:
         """out[M,N] = a[M,K] @ b[N,K]^T with the stated epilogue (see rte_gemm_bf16).  `tile_group` switches on the
         grouped mode (B = stack of per-group matrices), `split_kblocks` the ragged split-K."""
         _require_cuda(a, b, out, residual, out2)
@@ -108,16 +112,22 @@ class CudaOps:
         args.tile_group = tile_group.data_ptr() if tile_group is not None else None
         args.n_groups, args.b_group_stride = n_groups, b_group_stride
         args.split_kblocks = split_kblocks.data_ptr() if split_kblocks is not None else None
+        args.tile_n = self.gemm_tile_n if tile_n is None else tile_n
+        args.cta_pair = self.gemm_cta_pair if cta_pair is None else cta_pair
         few_rows = (M <= self.small_gemm_rows and not a_mn and epilogue in (A.EPI_BF16, A.EPI_F32) and tile_group is None
                     and split_kblocks is None and K % 8 == 0 and (not b_mn or N % 8 == 0))
         self._call("rte_gemm_bf16_small" if few_rows else "rte_gemm_bf16", C.byref(args), self.stream)
 
     def pick_splits(self, M: int, N: int, K: int) -> int:
         """Split count for a reduction-heavy GEMM whose output has few tiles (weight gradients)."""
-        bn = 256 if N >= 192 else 128
-        tiles = -(-M // 128) * -(-N // bn)
+        args = A.GemmArgs()
+        args.M, args.N, args.K, args.epilogue = M, N, K, A.EPI_F32
+        args.max_ctas, args.tile_n, args.cta_pair = self.gemm_max_ctas, self.gemm_tile_n, self.gemm_cta_pair
+        tm, tn, conc = C.c_int32(0), C.c_int32(0), C.c_int32(0)
+        A.check(self.lib.rte_gemm_tile_plan(C.byref(args), C.byref(tm), C.byref(tn), C.byref(conc)), "rte_gemm_tile_plan")
+        tiles = -(-M // tm.value) * -(-N // tn.value)
         kblocks = -(-K // 64)
-        want = max(1, min(self.sm_count // max(tiles, 1), kblocks // 8 if kblocks >= 16 else 1, 16))
+        want = max(1, min(conc.value // max(tiles, 1), kblocks // 8 if kblocks >= 16 else 1, 16))
         while want > 1:
             per = -(-kblocks // want)
             if -(-kblocks // per) == want:
@@ -509,10 +519,35 @@ class CudaOps:
         self._call("rte_axpy_rows_f32", _ptr(dst), _ptr(vec), alpha, rows, seg, d, self.stream)
 
     # ------------------------------------------------------------------ optimiser
-    def adamw(self, plan: "AdamWPlan", beta1, beta2, eps, weight_decay, grad_scale=None) -> None:
-        self._call("rte_adamw_multi_tensor", _ptr(plan.table), plan.n_tensors, plan.total_chunks,
+    def adamw(self, plan: "AdamWPlan", beta1, beta2, eps, weight_decay, grad_scale=None, *, skip=None,
+              metric_out=None) -> None:
+        """One fused AdamW launch over the plan's tensors.  `skip` (device int32): non-zero drops the update;
+        `metric_out` f32 [plan.n_metric_groups, 2]: per-group sums of grad^2 and param^2 (see rte_adamw_multi_tensor_ex)."""
+        if skip is None and metric_out is None:
+            self._call("rte_adamw_multi_tensor", _ptr(plan.table), plan.n_tensors, plan.total_chunks,
+                       _ptr(plan.chunk_tensor), _ptr(plan.chunk_index), _ptr(plan.lr_table), _ptr(plan.step_count),
+                       beta1, beta2, eps, weight_decay, _ptr(grad_scale), self.stream)
+            return
+        ex = A.AdamWExtras()
+        ex.skip = skip.data_ptr() if skip is not None else None
+        if metric_out is not None:
+            ex.metric_partial, ex.metric_group = plan.metric_partial.data_ptr(), plan.metric_group.data_ptr()
+            ex.metric_out, ex.n_metric_groups = metric_out.data_ptr(), plan.n_metric_groups
+        self._call("rte_adamw_multi_tensor_ex", _ptr(plan.table), plan.n_tensors, plan.total_chunks,
                    _ptr(plan.chunk_tensor), _ptr(plan.chunk_index), _ptr(plan.lr_table), _ptr(plan.step_count),
-                   beta1, beta2, eps, weight_decay, _ptr(grad_scale), self.stream)
+                   beta1, beta2, eps, weight_decay, _ptr(grad_scale), C.byref(ex), self.stream)
+
+    def nonfinite_guard(self, ranges, skip, flag_out=None) -> None:
+        """skip[0] = 1 when any element of the (up to three) f32 tensors in `ranges` is NaN or infinite, else 0."""
+        r = [t for t in ranges if t is not None and t.numel() > 0][:3]
+        r += [None] * (3 - len(r))
+        args = []
+        for t in r:
+            args += [_ptr(t), t.numel() if t is not None else 0]
+        self._call("rte_nonfinite_guard", *args, _ptr(skip), _ptr(flag_out), self.stream)
+
+    def add_guarded_(self, dst, src, skip) -> None:
+        self._call("rte_add_f32_guarded", _ptr(dst), _ptr(src), dst.numel(), _ptr(skip), self.stream)
 
     def grad_norm(self, plan: "AdamWPlan", partial, sumsq, max_norm: float, clip_coef) -> None:
         self._call("rte_grad_norm_multi_tensor", _ptr(plan.table), plan.total_chunks, _ptr(plan.chunk_tensor),
@@ -528,8 +563,9 @@ class CudaOps:
 class AdamWPlan:
     """Device-resident description of the tensors one fused AdamW launch updates."""
 
-    def __init__(self, entries: list[dict], lr_groups: int, device):
-        """entries: dicts with p, g, m, v (f32 tensors), shadow (bf16 tensor or None), lr_group (int)."""
+    def __init__(self, entries: list[dict], lr_groups: int, device, n_metric_groups: int = 0):
+        """entries: dicts with p, g, m, v (f32 tensors), shadow (bf16 tensor or None), lr_group (int) and, with
+        `n_metric_groups` > 0, metric_group (int): the group whose gradient / parameter norms the tensor counts towards."""
         n = len(entries)
         table = (A.AdamWTensor * n)()
         chunk_tensor: list[int] = []
@@ -551,3 +587,7 @@ class AdamWPlan:
         self.lr_table = torch.zeros(max(lr_groups, 1), dtype=torch.float32, device=device)
         self.step_count = torch.zeros(n, dtype=torch.int32, device=device)
         self.entries = entries
+        self.n_metric_groups = n_metric_groups
+        if n_metric_groups > 0:
+            self.metric_group = torch.tensor([e["metric_group"] for e in entries], dtype=torch.int32, device=device)
+            self.metric_partial = torch.zeros(self.total_chunks, 2, dtype=torch.float32, device=device)

@@ -529,9 +529,28 @@ class EmulOps:
         dst.view(rows, d).add_(vec.view(-1, d).repeat_interleave(seg, 0)[:rows] * alpha)
 
     # ---------------------------------------------------------------- optimiser
-    def adamw(self, plan, beta1, beta2, eps, weight_decay, grad_scale=None):
+    def nonfinite_guard(self, ranges, skip, flag_out=None):
+        bad = any(t is not None and t.numel() and not bool(torch.isfinite(t).all()) for t in ranges)
+        skip[0] = int(bad)
+        if flag_out is not None:
+            flag_out[0] = float(bad)
+
+    def add_guarded_(self, dst, src, skip):
+        if int(skip[0]) == 0:
+            dst.add_(src)
+
+    def adamw(self, plan, beta1, beta2, eps, weight_decay, grad_scale=None, *, skip=None, metric_out=None):
         self.launches += 1
+        if skip is not None and int(skip[0]) != 0:
+            if metric_out is not None:
+                metric_out.zero_()
+            return
         gs = float(grad_scale) if grad_scale is not None else 1.0
+        if metric_out is not None:
+            metric_out.zero_()
+            for e in plan.entries:
+                metric_out[e["metric_group"], 0] += float((e["g"] * gs).double().pow(2).sum())
+                metric_out[e["metric_group"], 1] += float(e["p"].double().pow(2).sum())
         for i, e in enumerate(plan.entries):
             lr = float(plan.lr_table[e["lr_group"]])
             step = int(plan.step_count[i]) + 1

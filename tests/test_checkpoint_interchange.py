@@ -13,7 +13,7 @@ pytestmark = pytest.mark.skipif(not Path(REF_SRC, "recursive_training_engine").i
 
 from oracle import rte_oracle as O  # noqa: E402
 from speedup_thingy_b200.checkpoint import load_checkpoint, optimizer_layout, save_checkpoint  # noqa: E402
-from speedup_thingy_b200.config import ExperimentConfig, ModelConfig, TrainingConfig  # noqa: E402
+from speedup_thingy_b200.config import ExperimentConfig, ModelConfig, OutputConfig, TrainingConfig  # noqa: E402
 from speedup_thingy_b200.engine import TrainEngine, init_parameters  # noqa: E402
 from tests.emul_ops import EmulOps  # noqa: E402
 from tests.golden.cases import GOLDEN_CASES  # noqa: E402
@@ -31,8 +31,8 @@ def _reference_engine(case, run_dir):
 
 def _engine(case):
     model = {k: v for k, v in case["model"].items() if k != "shortlist_clusters"}
-    cfg = ExperimentConfig(ModelConfig(**model), TrainingConfig(**case["train"]))
-    params = init_parameters(cfg.model, seed=cfg.training.seed)
+    cfg = ExperimentConfig(ModelConfig(**model), TrainingConfig(**case["train"]), OutputConfig(**case.get("output", {})))
+    params = init_parameters(cfg.model, seed=cfg.training.seed, num_clusters=cfg.output.num_clusters)
     return cfg, TrainEngine(cfg, params, device="cpu", ops=EmulOps(), use_cuda_graph=False)
 
 
@@ -95,3 +95,36 @@ def test_reference_checkpoint_loads_into_the_engine(tmp_path):
     a = eng.train_step(batches[2]).loss
     b = float(ref.train_step(batches[2]).loss)
     assert abs(a - b) <= 1e-2 * abs(b), (a, b)
+
+
+def test_reference_shortlist_checkpoint_refreshes_the_cluster_router(tmp_path):
+    """The shortlist head's cluster router is in no optimiser group, so its bf16 copy changes only on load: after a
+    reference checkpoint is loaded, the engine ranks clusters with the loaded weights."""
+    case = GOLDEN_CASES["small_shortlist"]
+    cfg, eng = _engine(case)
+    ref = _reference_engine(case, str(tmp_path))
+    router = ref.recursive_model.shortlist_head.cluster_router.weight
+    with torch.no_grad():
+        router.copy_(torch.randn(router.shape, generator=torch.Generator().manual_seed(123)) * 0.5)
+    ref.save_checkpoint(tmp_path / "reference.pt", data_cursor=0)
+    before = eng.cluster_w16.clone()
+    load_checkpoint(eng, tmp_path / "reference.pt")
+    assert torch.equal(eng.cluster_w16.float(), router.detach().to(torch.bfloat16).float())
+    assert not torch.equal(before, eng.cluster_w16)
+    eng.loss_and_grads(_batches(cfg, 1)[0])
+    scores = eng.hidden16.float() @ eng.cluster_w16.float().t()
+    want = O.topk_lowest(scores, eng.sl_tc)[1]
+    assert torch.equal(eng.top_clusters.long(), want)
+
+
+def test_checkpoint_payload_needs_no_package_and_refuses_steps_in_flight(tmp_path):
+    case = GOLDEN_CASES["small_routed"]
+    cfg, eng = _engine(case)
+    save_checkpoint(eng, tmp_path / "a.pt")
+    payload = torch.load(tmp_path / "a.pt", map_location="cpu", weights_only=False)
+    assert isinstance(payload["config"], dict) and payload["config"]["model"]["d_model"] == cfg.model.d_model
+    eng.submit(_batches(cfg, 1)[0])
+    with pytest.raises(RuntimeError, match="in flight"):
+        save_checkpoint(eng, tmp_path / "b.pt")
+    eng.collect()
+    save_checkpoint(eng, tmp_path / "b.pt")

@@ -525,6 +525,61 @@ def test_adamw_multi_tensor_matches_oracle_and_skips_absent(ops):
     assert abs(float(clip) - min(1.0, 1.0 / (math.sqrt(tot) + 1e-6))) < 1e-5
 
 
+def test_adamw_skip_flag_metric_sums_and_nonfinite_guard(ops):
+    """rte_adamw_multi_tensor_ex + rte_nonfinite_guard + rte_add_f32_guarded: a set flag makes the launch a no-op
+    (training.py:448-452); the per-group sums feed the gradient metrics (training.py:386-443)."""
+    from speedup_thingy_b200.ops import AdamWPlan
+    g = torch.Generator().manual_seed(5)
+    shapes = [(9000,), (130, 70), (4096,), (33,)]
+    groups = [0, 2, 0, 1]
+    ps = [torch.randn(s, generator=g) for s in shapes]
+    gs = [torch.randn(s, generator=g) for s in shapes]
+    dev = [dict(p=p.to(DEV), g=gr.to(DEV), m=torch.zeros_like(p, device=DEV), v=torch.zeros_like(p, device=DEV), shadow=None,
+                lr_group=0, metric_group=mg) for p, gr, mg in zip(ps, gs, groups)]
+    plan = AdamWPlan(dev, 1, DEV, n_metric_groups=3)
+    plan.lr_table.fill_(1e-2)
+    skip = torch.zeros(1, dtype=torch.int32, device=DEV)
+    flag = torch.zeros(1, device=DEV)
+    sums = torch.full((3, 2), -1.0, device=DEV)
+    coef = torch.tensor([0.5], device=DEV)
+    # guard: finite values -> 0, one NaN or inf in any range -> 1
+    a, b, c = torch.randn(7, device=DEV), torch.randn(300, device=DEV), torch.randn(5, device=DEV)
+    ops.nonfinite_guard([a, b, c], skip, flag)
+    assert int(skip) == 0 and float(flag) == 0.0
+    b[277] = float("inf")
+    ops.nonfinite_guard([a, b, c], skip, flag)
+    assert int(skip) == 1 and float(flag) == 1.0
+    b[277] = 0.0
+    c[4] = float("nan")
+    ops.nonfinite_guard([a, None, c], skip, flag)
+    assert int(skip) == 1
+    # flagged: nothing moves, sums are zero
+    ops.adamw(plan, 0.9, 0.999, 1e-8, 0.1, coef, skip=skip, metric_out=sums)
+    torch.cuda.synchronize()
+    for e_, p in zip(dev, ps):
+        assert torch.equal(e_["p"].cpu(), p) and float(e_["m"].abs().max()) == 0.0
+    assert plan.step_count.tolist() == [0, 0, 0, 0] and float(sums.abs().max()) == 0.0
+    dst = torch.ones(1000, device=DEV)
+    ops.add_guarded_(dst, torch.ones(1000, device=DEV), skip)
+    assert float(dst.sum()) == 1000.0
+    # not flagged: the ordinary update plus the sums of (0.5 g)^2 and p^2 (before the update) per metric group
+    c[4] = 0.0
+    ops.nonfinite_guard([a, b, c], skip, flag)
+    ops.add_guarded_(dst, torch.ones(1000, device=DEV), skip)
+    assert float(dst.sum()) == 2000.0
+    ops.adamw(plan, 0.9, 0.999, 1e-8, 0.1, coef, skip=skip, metric_out=sums)
+    torch.cuda.synchronize()
+    ref = [p.clone() for p in ps]
+    for i, gr in enumerate(gs):
+        O.adamw_update(ref[i], gr * 0.5, torch.zeros_like(gr), torch.zeros_like(gr), 1, 1e-2, 0.1)
+        _close(dev[i]["p"], ref[i], 1e-5, f"adamw_ex tensor {i}")
+    assert plan.step_count.tolist() == [1, 1, 1, 1]
+    for mg in range(3):
+        g2 = sum(float((gr * 0.5).double().pow(2).sum()) for gr, k in zip(gs, groups) if k == mg)
+        p2 = sum(float(p.double().pow(2).sum()) for p, k in zip(ps, groups) if k == mg)
+        assert abs(float(sums[mg, 0]) - g2) <= 1e-5 * g2 and abs(float(sums[mg, 1]) - p2) <= 1e-5 * p2
+
+
 def test_cpu_tensors_are_rejected(ops):
     with pytest.raises(RuntimeError, match="strict_cuda"):
         ops.gemm(torch.zeros(128, 64, dtype=torch.bfloat16), torch.zeros(128, 64, dtype=torch.bfloat16),
