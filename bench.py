@@ -315,6 +315,8 @@ def main() -> None:
     ap.add_argument("--probe-gemm", action="store_true", help="time the hot pass's GEMM shapes stand-alone and exit (profiling)")
     ap.add_argument("--probe-kernels", action="store_true",
                     help="time the memory-bound kernels of the step stand-alone against their algorithmic bytes and exit (profiling)")
+    ap.add_argument("--dp-timeline", action="store_true",
+                    help="data parallel: add the start / end of every gradient bucket's all-reduce inside a step (profiling)")
     ap.add_argument("--probe-iters", type=int, default=20)
     ap.add_argument("--probe-warmup", type=int, default=3)
     args = ap.parse_args()
@@ -436,6 +438,8 @@ def main() -> None:
         clocks.__exit__(None, None, None)
     eng.ops.check_status()
 
+    timeline = eng.dp_timeline() if (args.dp_timeline and world > 1) else None     # every rank takes part
+
     # ---- roofline of the dominant kernel (the tcgen05 GEMM): CUDA-event nodes around every launch of a captured step
     roof = None
     if rank == 0 and not args.no_roofline:
@@ -486,6 +490,8 @@ def main() -> None:
                                 "scope": "hot-pass launches (main stream + its weight-gradient stream); the audit replay's "
                                          "few-row launches overlap them on their own streams and are listed under side_stream",
                                 "per_shape": roof["per_shape"], "side_stream": roof.get("side_stream")}
+        if timeline is not None:
+            line["dp_timeline"] = timeline
         if world == 1 and not args.no_cpu_baseline:
             threads = os.cpu_count() or 1
             line["cpu_baseline"] = cpu_reference_tokens_per_sec(raw, steps=6, threads=threads, budget_s=40.0)
@@ -493,26 +499,12 @@ def main() -> None:
             line["gpu_torch_baseline"] = gpu_torch_tokens_per_sec(raw, dev, steps=10)
         _emit(json.dumps(line))
 
-    # ---- orderly teardown.  A communicator cannot be destroyed while CUDA graphs that captured its collectives are
-    # alive (NCCL keeps a reference per captured launch and its destroy waits for them): drain every stream, drop the
-    # graphs, collect garbage so their destructors run, synchronise again, then destroy the process group.  A watchdog
-    # ends the process if the teardown does not return (the result line is already out).
-    eng.close()
+    # ---- orderly teardown (graphs that captured collectives must be gone before the communicator is destroyed)
     if dist is not None:
-        import gc
-        barrier()
-        del eng
-        gc.collect()
-        torch.cuda.synchronize()
-        sys.stdout.flush()
-        sys.stderr.flush()
-        watchdog = threading.Timer(30.0, lambda: (sys.stderr.write("bench: process-group teardown did not return in 30 s\n"),
-                                                  os._exit(0)))
-        watchdog.daemon = True
-        watchdog.start()
-        dist.destroy_process_group()
-        watchdog.cancel()
-
+        from speedup_thingy_b200.engine import teardown_data_parallel
+        teardown_data_parallel(eng)
+    else:
+        eng.close()
 
 if __name__ == "__main__":
     main()

@@ -232,10 +232,16 @@ int rte_router_aux_bwd(const rte_router_weights* w, const rte_router_out* fwd, c
                        float lambda_load, float lambda_depth, float* aux, const rte_router_grads* grads,
                        float* dh0, float* scratch, int32_t B, int32_t S, int32_t d, int32_t hid, int32_t R,
                        int32_t K, rte_stream_t stream);
-/* The same backward in two halves (parameter gradients on another stream, ordered after _data, same `scratch`). */
+/* The same backward in two halves (parameter gradients on another stream, ordered after _data, same `scratch`).
+ * mean_prob_in (device f32 [R], may be NULL): the batch mean of the recipe probabilities to use instead of this
+ * call's own.  The load-balance loss squares a BATCH mean (metrics.py:103-105), so under data parallelism the
+ * global-batch step needs the mean over all shards: every rank writes scale * sum_b p with rte_router_mean_prob
+ * (scale = 1 / (B * world)), the ranks sum those R floats, and each passes the result here.                       */
+int rte_router_mean_prob(const float* recipe_probs, float* out, float scale, int32_t B, int32_t R, rte_stream_t stream);
 int rte_router_aux_bwd_data(const rte_router_weights* w, const rte_router_out* fwd, const int32_t* depth_values,
-                            float lambda_load, float lambda_depth, float* aux, float* dh0, float* scratch, int32_t B,
-                            int32_t S, int32_t d, int32_t hid, int32_t R, int32_t K, rte_stream_t stream);
+                            float lambda_load, float lambda_depth, float* aux, float* dh0, float* scratch,
+                            const float* mean_prob_in, int32_t B, int32_t S, int32_t d, int32_t hid, int32_t R,
+                            int32_t K, rte_stream_t stream);
 /* With dh0 == NULL the call above leaves out its last step; this performs it later (the rest needs no upstream
  * gradient and can run right after the router's forward): dh0[b,s,:] += dpooled[b,:] / S, read from `scratch`.  */
 int rte_router_aux_add_dh0(float* dh0, const float* scratch, int32_t B, int32_t S, int32_t d, int32_t hid, int32_t R,
@@ -415,6 +421,27 @@ int rte_svd_ffn_select(const float* hats, const void* ug, const float* wd_norm, 
 int rte_svd_ffn_swiglu_bwd(const void* ug, const void* dz, const uint8_t* selected, void* dug, int64_t rows, int32_t F,
                            rte_stream_t stream);
 int rte_row_norm_f32(const float* w, float* out, int32_t rows, int32_t d, rte_stream_t stream);
+
+/* ------------------------------------------------ offline cluster-pool codebook build (cli.py:3297-3389, 4703-4782)
+ * The step before the static cluster-pool FFN: cosine k-means over the selector features of a calibration window,
+ * per-cluster aggregation of the per-neuron pool scores, candidate lists by rte_topk_lowest_index.  All reductions
+ * run in a fixed order (reproducible).
+ * rte_normalize_rows_f32: out[r,:] = x[r,:] / max(||x[r,:]||, 1e-12)                      (F.normalize, cli.py:3308)
+ * rte_kmeans_update: centers_new[c,:] = normalise(mean of x_normed[t,:] over assignments[t] == c); a cluster without
+ *   members keeps centers_old[c,:] (normalised) (cli.py:3315-3322); counts int32 [C] optional; W <= 256.
+ *   One k-means round = rte_cluster_route (assignment, ties to the lowest centre) + this.
+ * rte_cluster_aggregate: out[c,:] = mean (use_max = 0) or max (1) of scores[t,:] over the members of c, zeros for an
+ *   empty cluster (cli.py:3326-3351).
+ * rte_cluster_pool_scores: out[t,j] = wd_norm[j] * (|up| + |silu(gate)| + |up*silu(gate)|) (mode 0 "sum"),
+ *   (|up| + |silu(gate)|) (1 "upgate") or |up*silu(gate)| (2 "product") of the low-rank estimates up_hat / gate_hat
+ *   f32 [n, F] (cli.py:3369-3385).                                                                               */
+int rte_normalize_rows_f32(const float* x, float* out, int32_t n, int32_t W, rte_stream_t stream);
+int rte_kmeans_update(const float* x_normed, const int32_t* assignments, const float* centers_old, float* centers_new,
+                      int32_t* counts, int32_t n, int32_t W, int32_t C, rte_stream_t stream);
+int rte_cluster_aggregate(const float* scores, const int32_t* assignments, float* out, int32_t n, int32_t F, int32_t C,
+                          int32_t use_max, rte_stream_t stream);
+int rte_cluster_pool_scores(const float* up_hat, const float* gate_hat, const float* wd_norm, float* out, int64_t n,
+                            int32_t F, int32_t mode, rte_stream_t stream);
 
 /* ------------------------------------------------ exact-audit replay helpers (audit.py:245-387; models.py:605-679;
  * layers.py:831-870).  The audited subset has a fixed size n (fixed-count sampler), chosen on the host.

@@ -729,6 +729,7 @@ class OracleTrainer:
 
     def train_step(self, tokens: torch.Tensor, targets: torch.Tensor) -> float:
         loss, grads, info = self.loss_and_grads(tokens, targets)
+        self.last_info = info            # what the step decided (routing, audited subset), for the parity tests
         for name, g in grads.items():
             st = self.opt_state.setdefault(name, dict(step=0, m=torch.zeros_like(g), v=torch.zeros_like(g)))
             st["step"] += 1
@@ -832,3 +833,87 @@ def svd_sparse_ffn(x, w_up, w_gate, w_down, up_a, up_b, gate_a, gate_b, *, top_k
         selected = svd_ffn_select(z.detach(), cand, wd_norm, top_k)
     out = (z * selected) @ w_down
     return out.view(x.shape), selected
+
+
+# ----------------------------------------------------------------------------- offline cluster-pool codebook build
+def svd_factor_cache(wug: torch.Tensor, max_rank: int) -> dict[str, torch.Tensor]:
+    """cli.py:3244-3261: truncated SVD factors of the up and gate halves of a fused W_ug [2F, d] (transposed to
+    [d, F]): `*_a` = U[:, :r] * S[:r] ([d, r]), `*_b` = Vh[:r, :] ([r, F])."""
+    up_w, gate_w = wug.detach().float().chunk(2, dim=0)
+    out: dict[str, torch.Tensor] = {}
+    for name, mat in (("up", up_w.t().contiguous()), ("gate", gate_w.t().contiguous())):
+        u, s, vh = torch.linalg.svd(mat, full_matrices=False)
+        r = min(max_rank, s.numel())
+        out[f"{name}_a"], out[f"{name}_b"] = u[:, :r] * s[:r], vh[:r, :]
+    return out
+
+
+def cluster_features_and_scores(normed: torch.Tensor, factors: dict, wd_norm: torch.Tensor, rank: int,
+                                score_mode: str) -> tuple[torch.Tensor, torch.Tensor]:
+    """cli.py:3357-3389: selector features [q_up | q_gate] and per-neuron pool scores of every token."""
+    flat = normed.reshape(-1, normed.shape[-1])
+    rank = min(max(1, int(rank)), factors["up_a"].shape[1], factors["gate_a"].shape[1])
+    q_up, q_gate = flat @ factors["up_a"][:, :rank], flat @ factors["gate_a"][:, :rank]
+    up_hat, gate_hat = q_up @ factors["up_b"][:rank, :], q_gate @ factors["gate_b"][:rank, :]
+    gact = F.silu(gate_hat)
+    up_s, gate_s, prod_s = up_hat.abs() * wd_norm, gact.abs() * wd_norm, (up_hat * gact).abs() * wd_norm
+    scores = {"sum": up_s + gate_s + prod_s, "upgate": up_s + gate_s, "product": prod_s}[score_mode]
+    return torch.cat([q_up, q_gate], dim=-1), scores
+
+
+def fit_cluster_centers(features: torch.Tensor, cluster_count: int, iters: int) -> tuple[torch.Tensor, torch.Tensor]:
+    """cli.py:3297-3323: cosine k-means -- rows L2-normalised, centres initialised from rows at evenly spaced
+    indices, `iters` rounds of (arg-max assignment, mean of members re-normalised; an empty cluster keeps its
+    centre).  Assignment ties go to the lowest centre index."""
+    n = features.shape[0]
+    cluster_count = min(max(1, int(cluster_count)), max(1, n))
+    x = F.normalize(features.float(), dim=-1)
+    if cluster_count == 1 or n == 1:
+        return torch.zeros(n, dtype=torch.long), F.normalize(x.mean(dim=0, keepdim=True), dim=-1)
+    init_idx = torch.linspace(0, n - 1, steps=cluster_count).round().long()
+    centers = x.index_select(0, init_idx).contiguous()
+    assignments = torch.zeros(n, dtype=torch.long)
+    for _ in range(max(1, int(iters))):
+        assignments = argmax_lowest(x @ centers.t())
+        new_centers = torch.zeros_like(centers)
+        counts = torch.bincount(assignments, minlength=cluster_count).to(new_centers.dtype)
+        new_centers.index_add_(0, assignments, x)
+        nonempty = counts > 0
+        new_centers[nonempty] = new_centers[nonempty] / counts[nonempty].unsqueeze(-1).clamp_min(1.0)
+        new_centers[~nonempty] = centers[~nonempty]
+        centers = F.normalize(new_centers, dim=-1)
+    return assignments, centers
+
+
+def aggregate_cluster_scores(scores: torch.Tensor, assignments: torch.Tensor, cluster_count: int, aggregation: str) -> torch.Tensor:
+    """cli.py:3326-3351: per-cluster mean or max of the members' scores (zeros for an empty cluster)."""
+    out = scores.new_zeros(cluster_count, scores.shape[-1])
+    for c in range(cluster_count):
+        mask = assignments == c
+        if bool(mask.any()):
+            out[c] = scores[mask].mean(dim=0) if aggregation == "mean" else scores[mask].amax(dim=0)
+    return out
+
+
+def build_cluster_pool_codebook(features: torch.Tensor, scores: torch.Tensor, cluster_count: int, candidate_m: int,
+                                aggregation: str, iters: int) -> dict[str, torch.Tensor]:
+    """cli.py:4741-4771 for one layer: centres from the calibration features, candidate ids = the `candidate_m` best
+    neurons of every cluster by aggregated score (ties to the lowest index)."""
+    assignments, centers = fit_cluster_centers(features, cluster_count, iters)
+    agg = aggregate_cluster_scores(scores.float(), assignments, centers.shape[0], aggregation)
+    ids = topk_lowest(agg, min(candidate_m, agg.shape[-1]))[1]
+    return dict(centers=centers, candidate_ids=ids, assignments=assignments, aggregate=agg)
+
+
+def active_union_ids(candidate_ids: torch.Tensor, hidden: int, cap: int | None = None) -> torch.Tensor:
+    """cli.py:4914-4941: sorted union of all clusters' candidates; above `cap`, the `cap` best by a
+    frequency-plus-rank score (rank weights 1 .. 1/M), ties to the lowest index."""
+    ids = candidate_ids.long()
+    full = torch.unique(ids.reshape(-1), sorted=True)
+    if cap is None or int(cap) <= 0 or full.numel() <= int(cap):
+        return full
+    cap = min(int(cap), hidden)
+    c, m = ids.shape
+    weight = torch.linspace(1.0, 1.0 / max(m, 1), steps=m).unsqueeze(0).expand(c, m).reshape(-1)
+    score = torch.zeros(hidden).index_add_(0, ids.reshape(-1), weight)
+    return torch.sort(topk_lowest(score.unsqueeze(0), cap)[1][0]).values

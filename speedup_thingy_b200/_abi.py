@@ -99,7 +99,8 @@ PROTOTYPES = {
     "rte_segment_sum": (C.c_int, [c_vp, c_vp, c_i32, c_i32, c_vp]),
     "rte_router_fwd": (C.c_int, [c_vp, P(RouterWeights), c_vp, P(RouterOut)] + [c_i32] * 9 + [c_vp]),
     "rte_router_aux_add_dh0": (C.c_int, [c_vp, c_vp] + [c_i32] * 6 + [c_vp]),
-    "rte_router_aux_bwd_data": (C.c_int, [P(RouterWeights), P(RouterOut), c_vp, c_f32, c_f32, c_vp, c_vp, c_vp] + [c_i32] * 6 + [c_vp]),
+    "rte_router_aux_bwd_data": (C.c_int, [P(RouterWeights), P(RouterOut), c_vp, c_f32, c_f32, c_vp, c_vp, c_vp, c_vp] + [c_i32] * 6 + [c_vp]),
+    "rte_router_mean_prob": (C.c_int, [c_vp, c_vp, c_f32, c_i32, c_i32, c_vp]),
     "rte_router_aux_bwd_params": (C.c_int, [P(RouterOut), P(RouterGrads), c_vp] + [c_i32] * 5 + [c_vp]),
     "rte_router_aux_bwd": (C.c_int, [P(RouterWeights), P(RouterOut), c_vp, c_f32, c_f32, c_vp, P(RouterGrads), c_vp,
                                      c_vp] + [c_i32] * 6 + [c_vp]),
@@ -150,6 +151,10 @@ PROTOTYPES = {
     "rte_kl_distill": (C.c_int, [c_vp, c_vp, c_f32, c_f32, c_vp, c_i32, c_vp, c_i32, c_vp, c_i32, c_i32, c_vp]),
     "rte_kl_distill_grad": (C.c_int, [c_vp, c_vp, c_f32, c_f32, c_vp, c_vp, c_i32, c_i32, c_vp]),
     "rte_add_rows_f32_to_bf16": (C.c_int, [c_vp, c_i32, c_vp, c_i32, c_vp, c_i32, c_i32, c_vp]),
+    "rte_normalize_rows_f32": (C.c_int, [c_vp, c_vp, c_i32, c_i32, c_vp]),
+    "rte_kmeans_update": (C.c_int, [c_vp, c_vp, c_vp, c_vp, c_vp, c_i32, c_i32, c_i32, c_vp]),
+    "rte_cluster_aggregate": (C.c_int, [c_vp, c_vp, c_vp, c_i32, c_i32, c_i32, c_i32, c_vp]),
+    "rte_cluster_pool_scores": (C.c_int, [c_vp, c_vp, c_vp, c_vp, c_i64, c_i32, c_i32, c_vp]),
     "rte_grad_norm_multi_tensor_static": (C.c_int, [c_vp, c_i64, c_vp, c_vp, c_vp, c_f32, c_vp, c_vp]),
 }
 

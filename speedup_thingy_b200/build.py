@@ -15,7 +15,7 @@ PKG = Path(__file__).resolve().parent
 ROOT = PKG.parent
 CSRC = PKG / "csrc"
 LIB = PKG / "lib" / "librte_b200.so"
-SOURCES = ["gemm_tcgen05.cu", "elementwise.cu", "attention.cu", "macro_phi.cu", "router.cu", "audit.cu", "shortlist.cu", "cluster_pool.cu", "svd_ffn.cu", "gemm_small.cu"]
+SOURCES = ["gemm_tcgen05.cu", "elementwise.cu", "attention.cu", "macro_phi.cu", "router.cu", "audit.cu", "shortlist.cu", "cluster_pool.cu", "svd_ffn.cu", "gemm_small.cu", "codebook.cu"]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
     "-Xcompiler", "-fPIC",

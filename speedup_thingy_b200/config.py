@@ -240,6 +240,9 @@ class TrainingConfig:
                 raise ValueError("audit_fixed_count_per_batch must be <= batch_size")
         if self.distill_temperature <= 0:
             raise ValueError("distill_temperature must be positive")
+        if self.audit_mode == "gradient_corrected" and not self.audit_gradient_correction and self.audit_p_max > 0:
+            raise ValueError("audit_mode='gradient_corrected' requires audit_gradient_correction=true "
+                             "when audits are enabled")             # config.py:255-263
         for name in ("target_speedup_vs_dense", "max_active_param_equiv_per_token", "max_hotpath_flops_per_token"):
             if getattr(self, name) is not None and getattr(self, name) <= 0:
                 raise ValueError(f"{name} must be positive")

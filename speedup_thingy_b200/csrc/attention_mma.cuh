@@ -87,6 +87,84 @@ __device__ __forceinline__ void load_rows(const __nv_bfloat16* __restrict__ src,
   }
 }
 
+// ---- asynchronous tile loads.  All tiles of a CTA are requested at once with cp.async (16-byte pieces straight into
+// shared memory, nothing held in registers), so a CTA has its whole working set in flight instead of one dependent
+// load per thread at a time; the rotary embedding is then applied in place by the thread that copied the piece.
+__device__ __forceinline__ void cp_async16(void* smem_dst, const void* gsrc) {
+  const uint32_t d = static_cast<uint32_t>(__cvta_generic_to_shared(smem_dst));
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(d), "l"(gsrc) : "memory");
+}
+__device__ __forceinline__ void cp_async_wait_all() {
+  asm volatile("cp.async.commit_group;\n\tcp.async.wait_group 0;" ::: "memory");
+}
+
+// rows [row0, row0 + n_rows) of one head -> smem rows [0, pad_rows) (row stride HD + 8), rows past n_rows zeroed.
+template <int HD>
+__device__ __forceinline__ void tile_async(const __nv_bfloat16* __restrict__ src, int ld, int n_rows, int pad_rows,
+                                           __nv_bfloat16* dst, int row0 = 0) {
+  constexpr int LDS = HD + 8, CPR = HD / 8;
+  for (int idx = threadIdx.x; idx < pad_rows * CPR; idx += blockDim.x) {
+    const int r = idx / CPR, ch = idx % CPR;
+    __nv_bfloat16* d = dst + r * LDS + 8 * ch;
+    if (r < n_rows) cp_async16(d, src + (size_t)(row0 + r) * ld + 8 * ch);
+    else *reinterpret_cast<uint4*>(d) = make_uint4(0u, 0u, 0u, 0u);
+  }
+}
+
+// Rotary embedding in place on a tile loaded by tile_async: every thread rotates exactly the pieces it copied (same
+// index mapping), so it only needs its own copies to have landed (cp_async_wait_all), not a CTA barrier.
+template <int HD>
+__device__ __forceinline__ void rotate_tile(__nv_bfloat16* tile, int n_rows, int pad_rows, const float* __restrict__ rope, int row0 = 0) {
+  constexpr int LDS = HD + 8, CPR = HD / 8;
+  for (int idx = threadIdx.x; idx < pad_rows * CPR; idx += blockDim.x) {
+    const int r = idx / CPR, ch = idx % CPR;
+    if (r >= n_rows) continue;
+    uint4* p = reinterpret_cast<uint4*>(tile + r * LDS + 8 * ch);
+    const uint4 raw = *p;
+    uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+    float cs[4], sn[4];
+    if (rope != nullptr) {            // (cos, sin) of 4 consecutive pairs = 32 contiguous bytes of the table
+      const float4* t4 = reinterpret_cast<const float4*>(rope + ((size_t)(row0 + r) * (HD / 2) + 4 * ch) * 2);
+      const float4 a = t4[0], b = t4[1];
+      cs[0] = a.x; sn[0] = a.y; cs[1] = a.z; sn[1] = a.w; cs[2] = b.x; sn[2] = b.y; cs[3] = b.z; sn[3] = b.w;
+    } else {
+#pragma unroll
+      for (int q = 0; q < 4; ++q) rope_cs(nullptr, row0 + r, 4 * ch + q, HD, cs[q], sn[q]);
+    }
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+      const float2 v = rte::unpack_bf16x2(w[q]);
+      w[q] = rte::pack_bf16x2(v.x * cs[q] - v.y * sn[q], v.y * cs[q] + v.x * sn[q]);
+    }
+    *p = make_uint4(w[0], w[1], w[2], w[3]);
+  }
+}
+
+// dsum[r] = sum_c tile[r, c] * other[row r of global `other`, c] (D = rowsum(dO * O) of backward): the HD/8 threads
+// of a row are neighbouring lanes.  `tile` pieces are the thread's own (loaded by tile_async with the same mapping).
+template <int HD>
+__device__ __forceinline__ void rowdot_tile(const __nv_bfloat16* tile, int n_rows, int pad_rows, const __nv_bfloat16* __restrict__ other,
+                                            int ld_other, float* dsum) {
+  constexpr int LDS = HD + 8, CPR = HD / 8;
+  for (int idx = threadIdx.x; idx < pad_rows * CPR; idx += blockDim.x) {
+    const int r = idx / CPR, ch = idx % CPR;
+    float part = 0.f;
+    if (r < n_rows) {
+      const uint4 a = *reinterpret_cast<const uint4*>(tile + r * LDS + 8 * ch);
+      const uint4 o = *reinterpret_cast<const uint4*>(other + (size_t)r * ld_other + 8 * ch);
+      const uint32_t a4[4] = {a.x, a.y, a.z, a.w}, b4[4] = {o.x, o.y, o.z, o.w};
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        const float2 x = rte::unpack_bf16x2(a4[q]), y = rte::unpack_bf16x2(b4[q]);
+        part += x.x * y.x + x.y * y.y;
+      }
+    }
+#pragma unroll
+    for (int o = 1; o < CPR; o <<= 1) part += __shfl_xor_sync(0xffffffffu, part, o);
+    if (ch == 0) dsum[r] = part;
+  }
+}
+
 // A fragments (16 rows starting at row0, all HD columns) of a row-major smem tile.
 template <int HD>
 __device__ __forceinline__ void load_a_frags(const __nv_bfloat16* tile, int row0, int g, int t, uint32_t (&f)[HD / 16][4]) {
@@ -116,7 +194,7 @@ __device__ __forceinline__ void rowrow_tile(float (&acc)[4], const uint32_t (&a)
 
 // ------------------------------------------------------------------ forward
 template <int HD, int SMAX>
-__global__ void __launch_bounds__(NTHR)
+__global__ void __launch_bounds__(NTHR, (SMAX <= 64 && HD <= 64) ? 6 : 1)
 fwd_kernel(const __nv_bfloat16* __restrict__ qkv, int ld, int sec, __nv_bfloat16* __restrict__ y, int ldy,
            float* __restrict__ lse, const float* __restrict__ rope, int S, int H,
            __nv_bfloat16* __restrict__ ym, const int32_t* __restrict__ mask_row, const float* __restrict__ mask_tab) {
@@ -129,9 +207,13 @@ fwd_kernel(const __nv_bfloat16* __restrict__ qkv, int ld, int sec, __nv_bfloat16
   const int kv_rows = min(S, qb0 + QB);                               // causal: later keys are never read
   const int kv_pad = min(SMAX, (kv_rows + 15) & ~15);
   const __nv_bfloat16* base = qkv + (size_t)b * S * ld + h * HD;
-  load_rows<HD, true>(base, ld, max(0, min(QB, S - qb0)), QB, sq, rope, qb0);
-  load_rows<HD, true>(base + sec, ld, kv_rows, kv_pad, sk, rope);
-  load_rows<HD, false>(base + 2 * sec, ld, kv_rows, kv_pad, sv);
+  const int q_rows = max(0, min(QB, S - qb0));
+  tile_async<HD>(base, ld, q_rows, QB, sq, qb0);
+  tile_async<HD>(base + sec, ld, kv_rows, kv_pad, sk);
+  tile_async<HD>(base + 2 * sec, ld, kv_rows, kv_pad, sv);
+  cp_async_wait_all();
+  rotate_tile<HD>(sq, q_rows, QB, rope, qb0);
+  rotate_tile<HD>(sk, kv_rows, kv_pad, rope);
   __syncthreads();
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, g = lane >> 2, t = lane & 3;
   const int r0 = warp * 16, q0 = qb0 + r0;
@@ -233,7 +315,7 @@ __device__ __forceinline__ void unrope_pair(float& a, float& b, int pos, int pai
 }
 
 template <int HD, int SMAX>
-__global__ void __launch_bounds__(NTHR)
+__global__ void __launch_bounds__(NTHR, (SMAX <= 64 && HD <= 64) ? 4 : 1)
 bwd_kernel(const __nv_bfloat16* __restrict__ qkv, int ld, int sec, const __nv_bfloat16* __restrict__ y,
            const __nv_bfloat16* __restrict__ dy, int ldy, const float* __restrict__ lse,
            __nv_bfloat16* __restrict__ dqkv, const float* __restrict__ rope, int S, int H) {
@@ -248,11 +330,14 @@ bwd_kernel(const __nv_bfloat16* __restrict__ qkv, int ld, int sec, const __nv_bf
   const int b = blockIdx.x / H, h = blockIdx.x % H, blk0 = blockIdx.y * QB;
   const int s_pad = min(SMAX, (S + 15) & ~15);
   const __nv_bfloat16* base = qkv + (size_t)b * S * ld + h * HD;
-  load_rows<HD, true>(base, ld, S, s_pad, sq, rope);
-  load_rows<HD, true>(base + sec, ld, S, s_pad, sk, rope);
-  load_rows<HD, false>(base + 2 * sec, ld, S, s_pad, sv);
-  load_rows<HD, false>(dy + (size_t)b * S * ldy + h * HD, ldy, S, s_pad, sdo, nullptr, 0,
-                       y + (size_t)b * S * ldy + h * HD, ldy, sD);
+  tile_async<HD>(base, ld, S, s_pad, sq);
+  tile_async<HD>(base + sec, ld, S, s_pad, sk);
+  tile_async<HD>(base + 2 * sec, ld, S, s_pad, sv);
+  tile_async<HD>(dy + (size_t)b * S * ldy + h * HD, ldy, S, s_pad, sdo);
+  cp_async_wait_all();
+  rotate_tile<HD>(sq, S, s_pad, rope);
+  rotate_tile<HD>(sk, S, s_pad, rope);
+  rowdot_tile<HD>(sdo, S, s_pad, y + (size_t)b * S * ldy + h * HD, ldy, sD);
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, g = lane >> 2, t = lane & 3;
   for (int i = threadIdx.x; i < s_pad; i += NTHR) slse[i] = (i < S) ? lse[((size_t)b * H + h) * S + i] : 0.f;
   __syncthreads();

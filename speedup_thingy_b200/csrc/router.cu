@@ -133,13 +133,18 @@ router_fwd_kernel(rte_router_weights w, const int32_t* __restrict__ depth_values
 // aux losses and the batch-mean of the recipe probabilities
 __global__ void __launch_bounds__(NTHR)
 aux_kernel(const float* __restrict__ recipe_probs, const float* __restrict__ expected_depth, float lambda_load,
-           float lambda_depth, float* __restrict__ aux, float* __restrict__ mean_prob, int B, int R) {
+           float lambda_depth, float* __restrict__ aux, float* __restrict__ mean_prob, const float* __restrict__ mean_given,
+           int B, int R) {
   __shared__ float red[32];
   __shared__ float mp[RTE_ROUTER_MAX_R];
   for (int r = threadIdx.x; r < R; r += NTHR) {
     float acc = 0.f;
-    for (int b = 0; b < B; ++b) acc += recipe_probs[(size_t)b * R + r];
-    acc /= (float)B;
+    if (mean_given != nullptr) {          // the batch mean over ALL data-parallel shards, reduced by the caller
+      acc = mean_given[r];
+    } else {
+      for (int b = 0; b < B; ++b) acc += recipe_probs[(size_t)b * R + r];
+      acc /= (float)B;
+    }
     mp[r] = acc;
     mean_prob[r] = acc;
   }
@@ -345,13 +350,32 @@ extern "C" int rte_router_fwd(const float* h0, const rte_router_weights* w, cons
   return RTE_OK;
 }
 
+// out[r] = scale * sum_b recipe_probs[b, r]: with scale = 1 / (B * world) the SUM of `out` over the data-parallel ranks is
+// the batch mean over the global batch, which rte_router_aux_bwd_data then takes as `mean_prob_in`.
+__global__ void __launch_bounds__(NTHR)
+mean_prob_kernel(const float* __restrict__ recipe_probs, float* __restrict__ out, float scale, int B, int R) {
+  for (int r = threadIdx.x; r < R; r += NTHR) {
+    float acc = 0.f;
+    for (int b = 0; b < B; ++b) acc += recipe_probs[(size_t)b * R + r];
+    out[r] = acc * scale;
+  }
+}
+
+extern "C" int rte_router_mean_prob(const float* recipe_probs, float* out, float scale, int32_t B, int32_t R, rte_stream_t stream) {
+  RTE_CHECK_ARG(recipe_probs && out && B > 0 && R > 0 && R <= RTE_ROUTER_MAX_R);
+  mean_prob_kernel<<<1, NTHR, 0, ST(stream)>>>(recipe_probs, out, scale, B, R);
+  RTE_LAUNCH_CHECK();
+  return RTE_OK;
+}
+
 // Data-gradient half: the auxiliary losses, d(loss)/d(pre-activations) per sample (left in `scratch`), and
 // dh0[b,s,:] += dpooled[b,:] / S -- what the rest of backward waits for.  None of it depends on an upstream
 // gradient, so with dh0 == NULL everything but that last add can run as soon as the router's forward is done
 // (rte_router_aux_add_dh0 performs the add later, from `scratch`).
 extern "C" int rte_router_aux_bwd_data(const rte_router_weights* w, const rte_router_out* fwd, const int32_t* depth_values,
-                                       float lambda_load, float lambda_depth, float* aux, float* dh0, float* scratch, int32_t B,
-                                       int32_t S, int32_t d, int32_t hid, int32_t R, int32_t K, rte_stream_t stream) {
+                                       float lambda_load, float lambda_depth, float* aux, float* dh0, float* scratch,
+                                       const float* mean_prob_in, int32_t B, int32_t S, int32_t d, int32_t hid, int32_t R,
+                                       int32_t K, rte_stream_t stream) {
   RTE_CHECK_ARG(w && fwd && depth_values && aux && scratch && B > 0 && S > 0 && d > 0 && hid > 0);
   RTE_CHECK_ARG(R > 0 && R <= RTE_ROUTER_MAX_R && K > 0 && K <= RTE_ROUTER_MAX_K);
   float* mean_prob = scratch;                       // [RTE_ROUTER_MAX_R]
@@ -361,7 +385,8 @@ extern "C" int rte_router_aux_bwd_data(const rte_router_weights* w, const rte_ro
   float* dlog_d = dlog_r + (size_t)B * R;           // [B, K]
   float* dpooled = scratch + (((size_t)RTE_ROUTER_MAX_R + (size_t)B * (2 * hid + R + K) + 3) & ~(size_t)3);   // [B, d], 16-byte aligned
   if (reinterpret_cast<uintptr_t>(scratch) & 15) return RTE_ERR_ALIGNMENT;
-  aux_kernel<<<1, NTHR, 0, ST(stream)>>>(fwd->recipe_probs, fwd->expected_depth, lambda_load, lambda_depth, aux, mean_prob, B, R);
+  aux_kernel<<<1, NTHR, 0, ST(stream)>>>(fwd->recipe_probs, fwd->expected_depth, lambda_load, lambda_depth, aux, mean_prob,
+                                         mean_prob_in, B, R);
   RTE_LAUNCH_CHECK();
   const size_t smem = (size_t)2 * hid * sizeof(float);
   if (smem > 48 * 1024) return RTE_ERR_UNSUPPORTED;
@@ -426,7 +451,8 @@ extern "C" int rte_router_aux_bwd(const rte_router_weights* w, const rte_router_
                                   float* dh0, float* scratch, int32_t B, int32_t S, int32_t d, int32_t hid, int32_t R,
                                   int32_t K, rte_stream_t stream) {
   RTE_CHECK_ARG(grads != nullptr);
-  const int rc = rte_router_aux_bwd_data(w, fwd, depth_values, lambda_load, lambda_depth, aux, dh0, scratch, B, S, d, hid, R, K, stream);
+  const int rc = rte_router_aux_bwd_data(w, fwd, depth_values, lambda_load, lambda_depth, aux, dh0, scratch, nullptr, B, S, d, hid, R, K,
+                                         stream);
   if (rc != RTE_OK) return rc;
   return rte_router_aux_bwd_params(fwd, grads, scratch, B, d, hid, R, K, stream);
 }

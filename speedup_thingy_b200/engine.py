@@ -143,6 +143,46 @@ def hot_budget(cfg: ModelConfig, tr: TrainingConfig, shortlist_size: int | None)
             "active_param_budget": limit if limit is not None else 0.0}
 
 
+# --------------------------------------------------------------------------- data-parallel teardown
+def teardown_data_parallel(engine: "TrainEngine | None", watchdog_s: float = 30.0) -> None:
+    """Ends a data-parallel run in the order NCCL needs.  A communicator keeps a reference for every collective that
+    was captured into a CUDA graph, and destroying it waits until those graphs are gone; destroying it while a step
+    graph (or work queued on the communication stream) still exists therefore blocks forever.  So: drain the device,
+    drop the engine's graphs, run the garbage collector so that the graph objects are really destroyed, drain again,
+    meet the other ranks in a last barrier, and only then destroy the process group.  Should the destroy still not
+    return within `watchdog_s` seconds, the process exits (everything a caller wants to keep must be written before
+    this call)."""
+    import gc
+    import sys
+    import threading
+
+    import torch.distributed as dist
+
+    if engine is not None:
+        engine.close()
+    gc.collect()
+    if torch.cuda.is_available():
+        torch.cuda.synchronize()
+    if not (dist.is_available() and dist.is_initialized()):
+        return
+    dist.barrier()
+    if torch.cuda.is_available():
+        torch.cuda.synchronize()
+    sys.stdout.flush()
+    sys.stderr.flush()
+
+    def give_up() -> None:
+        sys.stderr.write(f"teardown_data_parallel: destroy_process_group did not return in {watchdog_s:.0f} s; exiting\n")
+        sys.stderr.flush()
+        os._exit(0)
+
+    timer = threading.Timer(watchdog_s, give_up)
+    timer.daemon = True
+    timer.start()
+    dist.destroy_process_group()
+    timer.cancel()
+
+
 # --------------------------------------------------------------------------- results
 @dataclass
 class TrainStepResult:
@@ -185,7 +225,7 @@ class _Temps:
 class TrainEngine:
     def __init__(self, config: ExperimentConfig, params: dict[str, torch.Tensor] | None = None, *,
                  device: str | torch.device = "cuda:0", ops=None, use_cuda_graph: bool = True,
-                 process_group=None, bucket_cap_mb: float = 25.0, swiglu_fuse_max_rows: int = 1024,
+                 process_group=None, bucket_cap_mb: float | None = None, swiglu_fuse_max_rows: int = 1024,
                  grad_metrics: bool = True):
         check_supported(config)          # NotImplementedError naming every configured value this path lacks
         self.config = config
@@ -278,8 +318,11 @@ class TrainEngine:
         self._bucket_of: dict[str, int] = {}
         self._bucket_pending: list[int] = []
         self._bucket_size: list[int] = []
-        _os = os
-        bucket_cap_mb = float(_os.environ.get("RTE_BUCKET_MB", bucket_cap_mb))
+        # Bucket size: 25 MB (the usual data-parallel default) for large models, but never fewer than about eight
+        # buckets per step: the LAST bucket's exchange cannot hide behind backward, so it has to be a small share.
+        if bucket_cap_mb is None:
+            bucket_cap_mb = float(os.environ.get("RTE_BUCKET_MB", min(25.0, max(total * 4 / 2 ** 20 / 8.0, 1.0))))
+        self.bucket_cap_mb = float(bucket_cap_mb)
         cap = max(int(bucket_cap_mb * 1024 * 1024 / 4), 1)
         start = 0
         for n in order:
@@ -386,6 +429,7 @@ class TrainEngine:
                               recipe_id=self._results[8 + B:8 + 2 * B].view(i32), recipe_id_by_pass=e(B, cfg.t_max, dtype=i32),
                               depth_id=e(B, dtype=i32), depth=e(B, dtype=i32))
             self.router_scratch = e(A.ROUTER_MAX_R + B * (2 * hid + r + k + A.ROUTER_DPOOLED_PARTS * d) + 4)
+            self._mean_prob = torch.zeros(A.ROUTER_MAX_R, dtype=f32, device=dev)
         if self.shortlist:
             oc, i32 = self.oc, torch.int32
             if "shortlist_head.cluster_router.weight" not in self.params:
@@ -489,7 +533,26 @@ class TrainEngine:
                     if self._misc_param_stream is not None:
                         self._comm_stream.wait_stream(self._misc_param_stream)
                     with torch.cuda.stream(self._comm_stream):
+                        probes = getattr(self, "_dp_probes", None)       # optional: event pairs around every exchange
+                        if probes is not None:
+                            e0 = torch.cuda.Event(enable_timing=True, external=True)
+                            e0.record(self._comm_stream)
                         dist.all_reduce(view, op=dist.ReduceOp.SUM, group=self.pg)
+                        if probes is not None:
+                            e1 = torch.cuda.Event(enable_timing=True, external=True)
+                            e1.record(self._comm_stream)
+                            probes.append((f"bucket{i}", (hi - lo) * 4, e0, e1))
+
+    def _global_mean_prob(self):
+        """Under data parallelism: the recipe probabilities' mean over the GLOBAL batch (R floats summed across the
+        ranks on the current stream), which the load-balance loss squares (metrics.py:103-105); None on one rank."""
+        if self.world == 1 or self._dp_paused:
+            return None
+        import torch.distributed as dist
+        R = self.cfg.recipe_count
+        self.ops.router_mean_prob(self.route["recipe_probs"], self._mean_prob, 1.0 / (self.B * self.world), B=self.B, R=R)
+        dist.all_reduce(self._mean_prob, op=dist.ReduceOp.SUM, group=self.pg)
+        return self._mean_prob
 
     def _finish_backward(self) -> None:
         if self._comm_stream is not None and not self._dp_paused:
@@ -673,7 +736,8 @@ class TrainEngine:
                   for i_, w_, k_ in ((0, "weight", "w0"), (0, "bias", "b0"), (2, "weight", "w2"), (2, "bias", "b2"))}
             o.router_aux_bwd(self._router_weight_dict(), self.route, self.depth_values, tr.lambda_load / self.loss_div,
                              tr.lambda_depth / self.loss_div, self.scalars[1:3], rg, dcur, self.router_scratch, B=B, S=S,
-                             d=d, hid=cfg.router_hidden_dim, R=cfg.recipe_count, K=len(cfg.depth_choices))
+                             d=d, hid=cfg.router_hidden_dim, R=cfg.recipe_count, K=len(cfg.depth_choices),
+                             mean_prob=self._global_mean_prob())
         g16 = self.grad16
         o.cast_bf16(dcur, g16[0])
         for j, blk in enumerate(reversed(self.prelude)):
@@ -725,7 +789,7 @@ class TrainEngine:
                     o.router_aux_bwd_early(self._router_weight_dict(), self.route, self.depth_values, tr.lambda_load / self.loss_div,
                                            tr.lambda_depth / self.loss_div, self.scalars[1:3], self._router_grad_dict(),
                                            self.router_scratch, B=B, S=S, d=d, hid=cfg.router_hidden_dim,
-                                           R=cfg.recipe_count, K=len(cfg.depth_choices))
+                                           R=cfg.recipe_count, K=len(cfg.depth_choices), mean_prob=self._global_mean_prob())
                     self._router_early = torch.cuda.Event()
                     self._router_early.record(ms)
             if self.audit is not None:
@@ -875,8 +939,8 @@ class TrainEngine:
                               f"{pre}.attn.wo.weight", f"{pre}.attn.wqkv.weight", f"{pre}.norm1.weight"]
                 self._grad_ready(*names, *CORE_PARAMS, after=core_done)
             if not tr.disable_router_aux:
-                # under data parallelism each rank evaluates the auxiliary losses on its own shard and
-                # contributes 1/world of their gradient (the cross-entropy part is exactly the global mean)
+                # under data parallelism each rank contributes 1/world of the auxiliary losses' gradient on its own
+                # samples, with the load-balance term's batch mean taken over ALL shards (`_global_mean_prob`)
                 dims = dict(B=B, S=S, d=d, hid=cfg.router_hidden_dim, R=cfg.recipe_count, K=len(cfg.depth_choices))
                 if self._router_early is not None:
                     torch.cuda.current_stream(self.device).wait_event(self._router_early)
@@ -886,7 +950,7 @@ class TrainEngine:
                         o.param_stream = misc
                     o.router_aux_bwd_split(self._router_weight_dict(), self.route, self.depth_values, tr.lambda_load / self.loss_div,
                                            tr.lambda_depth / self.loss_div, self.scalars[1:3], self._router_grad_dict(), dcur,
-                                           self.router_scratch, **dims)
+                                           self.router_scratch, mean_prob=self._global_mean_prob(), **dims)
                     if split:
                         o.param_stream = None
                 self._grad_ready(*self._router_grad_names())
@@ -1000,8 +1064,8 @@ class TrainEngine:
         return self._graphs.get("step")
 
     def close(self) -> None:
-        """Drops the captured step graph (which, under data parallelism, holds NCCL kernels) after the device has
-        drained, so that the process group can be torn down afterwards."""
+        """Drops the captured step graphs (which, under data parallelism, hold NCCL kernels) after the device has
+        drained, so that the process group can be torn down afterwards (see `teardown_data_parallel`)."""
         if self.device.type == "cuda":
             torch.cuda.synchronize(self.device)
         self._graphs.clear()
@@ -1235,6 +1299,47 @@ class TrainEngine:
         first = calls[0][1]
         self.last_profile_starts = [first.elapsed_time(e0) * 1e3 for _, e0, _ in calls]
         return [(calls[i][0], totals[i] / repeats) for i in range(len(calls))]
+
+    def dp_timeline(self, repeats: int = 5) -> dict[str, Any]:
+        """Where the gradient exchange sits inside one data-parallel step: start / end of every bucket's all-reduce on the
+        communication stream, of backward and of the optimiser on the main stream, in microseconds from the start of the
+        step, from event-record nodes inside a captured step (averaged over `repeats` replays).  EVERY rank must call
+        this (the captured step contains the collectives)."""
+        self._dp_probes = []
+        marks: dict[str, Any] = {}
+        ev = lambda: torch.cuda.Event(enable_timing=True, external=True)       # noqa: E731
+        try:
+            torch.cuda.synchronize(self.device)
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph):
+                main = torch.cuda.current_stream(self.device)
+                marks["step_start"] = ev(); marks["step_start"].record(main)
+                self._forward_backward()
+                marks["backward_end"] = ev(); marks["backward_end"].record(main)
+                self._optimizer_step()
+                marks["step_end"] = ev(); marks["step_end"].record(main)
+            probes, self._dp_probes = self._dp_probes, None
+        finally:
+            self._dp_probes = None
+        acc: dict[str, list[float]] = {}
+        graph.replay()
+        torch.cuda.synchronize(self.device)
+        for _ in range(repeats):
+            graph.replay()
+            torch.cuda.synchronize(self.device)
+            t0 = marks["step_start"]
+            for k in ("backward_end", "step_end"):
+                acc.setdefault(k, []).append(t0.elapsed_time(marks[k]) * 1e3)
+            for name, nbytes, e0, e1 in probes:
+                acc.setdefault(name + ".start", []).append(t0.elapsed_time(e0) * 1e3)
+                acc.setdefault(name + ".end", []).append(t0.elapsed_time(e1) * 1e3)
+        del graph
+        mean = {k: sum(v) / len(v) for k, v in acc.items()}
+        buckets = [dict(name=name, mb=nbytes / 2 ** 20, start_us=mean[name + ".start"], end_us=mean[name + ".end"])
+                   for name, nbytes, _, _ in probes]
+        last_end = max((b["end_us"] for b in buckets), default=0.0)
+        return {"backward_end_us": mean["backward_end"], "step_end_us": mean["step_end"], "buckets": buckets,
+                "exchange_exposed_us": max(0.0, last_end - mean["backward_end"]), "bucket_cap_mb": self.bucket_cap_mb}
 
     def gemm_roofline(self, repeats: int = 5) -> dict[str, Any]:
         """Relates the algorithmic 2*M*N*K FLOPs of every tcgen05 GEMM launch of one step to its device

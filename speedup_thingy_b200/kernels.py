@@ -417,23 +417,114 @@ def k_metrics_reduce(values: dict) -> dict:
     return {k: float(v.detach().float().mean().cpu()) for k, v in values.items()}
 
 
-def _not_on_this_path(name: str, why: str):
-    def stub(*_args, **_kwargs):
-        raise NotImplementedError(f"{name} is not provided by rte_b200: {why}")
-    stub.__name__ = name
-    return stub
+def k_sample_audit_mask(p, seed: int):
+    """Bernoulli audit mask from a generator on p's device seeded with `seed` (reference.py:151-154): a host-side
+    sampling decision, kept as the reference draws it so that the same seed gives the same mask."""
+    gen = torch.Generator(device=p.device)
+    gen.manual_seed(seed)
+    return torch.bernoulli(p, generator=gen).bool()
 
 
-_FUSED = "the step computes it inside fused kernels; use speedup_thingy_b200.engine.TrainEngine"
-k_swiglu_dense = _not_on_this_path("k_swiglu_dense", _FUSED + " (SwiGLU runs as a GEMM epilogue)")
-k_swiglu_grouped = _not_on_this_path("k_swiglu_grouped", _FUSED + " (masked SwiGLU of the audit replay)")
-k_qkv_grouped = _not_on_this_path("k_qkv_grouped", _FUSED + " (column masks instead of weight gathers)")
-k_macro_phi = _not_on_this_path("k_macro_phi", "the model runs MacroOperators._apply_vectorized_bounded, which is "
-                                               "rte_macro_phi_fwd/bwd; the simplified form has no caller")
-k_pack_by_recipe = _not_on_this_path("k_pack_by_recipe", "only the deferred-grouped exact mode calls it")
-k_unpack_from_recipe = _not_on_this_path("k_unpack_from_recipe", "only the deferred-grouped exact mode calls it")
-k_sample_audit_mask = _not_on_this_path("k_sample_audit_mask", "the audited subset is drawn on the host "
-                                                                "(fixed-count sampler), see AuditReplay.choose")
+class PackedByRecipe:
+    """Result of `k_pack_by_recipe` (reference.py:81-88): same field names."""
+    __slots__ = ("packed", "permutation", "inverse_permutation", "keys", "offsets", "unique_keys")
+
+    def __init__(self, packed, permutation, inverse_permutation, keys, offsets, unique_keys):
+        self.packed, self.permutation, self.inverse_permutation = packed, permutation, inverse_permutation
+        self.keys, self.offsets, self.unique_keys = keys, offsets, unique_keys
+
+
+class _GatherRows(torch.autograd.Function):
+    """out[i] = src[index[i]] for a PERMUTATION `index` through the C-ABI row gather; the backward is the gather by
+    the inverse permutation (no atomics)."""
+
+    @staticmethod
+    def forward(ctx, src, index, inverse):
+        ops = _ops_for(src)
+        flat = src.detach().contiguous().view(src.shape[0], -1)
+        out = torch.empty_like(flat)
+        ops.gather_rows(flat, index.to(torch.int32), out, flat.shape[0], flat.shape[1] * flat.element_size())
+        ctx.save_for_backward(index, inverse)
+        return out.view(src.shape)
+
+    @staticmethod
+    def backward(ctx, d_out):
+        index, inverse = ctx.saved_tensors
+        ops = _ops_for(d_out)
+        flat = d_out.contiguous().view(d_out.shape[0], -1)
+        out = torch.empty_like(flat)
+        ops.gather_rows(flat, inverse.to(torch.int32), out, flat.shape[0], flat.shape[1] * flat.element_size())
+        return out.view(d_out.shape), None, None
+
+
+def _gather_ok(t: torch.Tensor) -> None:
+    if (t[0].numel() * t.element_size()) % 16:
+        raise ValueError("rte_b200 row gathers move 16-byte units: a row must be a multiple of 16 bytes")
+
+
+def k_pack_by_recipe(hidden, recipe_ids, depth_ids, audit_flags=None):
+    """Stable sort of the samples by (recipe, depth, audited) and the packed copy of `hidden` in that order
+    (reference.py:91-104).  The keys are sorted on the device by torch (index bookkeeping); the rows move through
+    rte_gather_rows."""
+    _require_cuda_tensor(hidden, recipe_ids, depth_ids, audit_flags)
+    audit = torch.zeros_like(recipe_ids) if audit_flags is None else audit_flags.long()
+    keys = recipe_ids.long() * 1_000_000 + depth_ids.long() * 10 + audit
+    sorted_keys, perm = torch.sort(keys, stable=True)
+    inverse = torch.empty_like(perm)
+    inverse[perm] = torch.arange(perm.numel(), device=perm.device)
+    unique, counts = torch.unique_consecutive(sorted_keys, return_counts=True)
+    offsets = torch.cat([counts.new_zeros(1), counts.cumsum(0)])
+    _gather_ok(hidden)
+    return PackedByRecipe(_GatherRows.apply(hidden, perm, inverse), perm, inverse, sorted_keys, offsets, unique)
+
+
+def k_unpack_from_recipe(packed, inverse_permutation):
+    """packed[inverse_permutation] (reference.py:107-108)."""
+    _require_cuda_tensor(packed, inverse_permutation)
+    _gather_ok(packed)
+    perm = torch.empty_like(inverse_permutation)
+    perm[inverse_permutation] = torch.arange(inverse_permutation.numel(), device=inverse_permutation.device)
+    return _GatherRows.apply(packed, inverse_permutation, perm)
+
+
+def k_qkv_grouped(x, wq, wk, wv, column_indices):
+    """x @ w[:, column_indices] for the three projections (reference.py:44-51); the gathered columns are multiplied by
+    the tcgen05 GEMM, autograd scatters their gradients back into the full weights."""
+    _require_cuda_tensor(x, wq, wk, wv, column_indices)
+    cols = column_indices.long()
+    return k_qkv_dense(x, wq.index_select(1, cols), wk.index_select(1, cols), wv.index_select(1, cols))
+
+
+def _swiglu_io(x, wu, wg, wd):
+    """(x @ wu) * silu(x @ wg) @ wd with [in, out] weights through the packed SwiGLU FFN (GEMM + SiLU-gate + GEMM)."""
+    wug = torch.cat([wu.t(), wg.t()], dim=0)            # [2M, d] = (up rows | gate rows)
+    flat = x.reshape(-1, x.shape[-1])
+    return packed_swiglu_ffn(flat, wug, wd).view(*x.shape[:-1], wd.shape[-1])
+
+
+def k_swiglu_dense(x, wu, wg, wd):
+    """reference.py:62-68."""
+    _require_cuda_tensor(x, wu, wg, wd)
+    return _swiglu_io(x, wu, wg, wd)
+
+
+def k_swiglu_grouped(x, wu, wg, wd, slab_indices):
+    """reference.py:71-78: SwiGLU over the hidden units `slab_indices` only."""
+    _require_cuda_tensor(x, wu, wg, wd, slab_indices)
+    idx = slab_indices.long()
+    return _swiglu_io(x, wu.index_select(1, idx), wg.index_select(1, idx), wd.index_select(0, idx))
+
+
+def k_macro_phi(h, h0, d_gain, v, u, bias, eps: float = 1e-5):
+    """The operator table's simplified macro operator (reference.py:111-124): h + d_gain*h + silu(z @ v) @ u + bias with
+    z = [rmsnorm(h) | mean_S rmsnorm(h) | h0].  (The model itself runs the bounded-residual form, rte_macro_phi_fwd.)
+    Norm and both products run in the sm_100a kernels; concatenation and the element-wise tail are tensor glue."""
+    _require_cuda_tensor(h, h0, d_gain, v, u, bias)
+    normed, _ = k_fused_rmsnorm(h, torch.ones(h.shape[-1], device=h.device, dtype=h.dtype), None, eps)
+    pooled = normed.mean(dim=1, keepdim=True).expand_as(normed)
+    z = torch.cat([normed, pooled, h0], dim=-1)
+    low = _MatmulIO.apply(torch.nn.functional.silu(_MatmulIO.apply(z, v)), u)
+    return h + d_gain * h + low + bias
 
 
 # --------------------------------------------------------------------------- packed SwiGLU FFN

@@ -305,28 +305,39 @@ class CudaOps:
                    self.stream)
 
     def router_aux_bwd(self, w: dict, fwd: dict, depth_values, lambda_load, lambda_depth, aux, grads: dict, dh0,
-                       scratch, *, B, S, d, hid, R, K):
+                       scratch, *, B, S, d, hid, R, K, mean_prob=None):
+        """`mean_prob` (device f32 [R], optional): the recipe probabilities' mean over the GLOBAL batch (all
+        data-parallel shards) to use instead of this batch's own (see rte_router_aux_bwd_data)."""
         sw, so = self._router_weights(w), self._router_out(fwd)
         sg = A.RouterGrads()
         for name, _ in A.RouterGrads._fields_:
             setattr(sg, name, grads[name].data_ptr())
-        self._call("rte_router_aux_bwd", C.byref(sw), C.byref(so), _ptr(depth_values), lambda_load, lambda_depth,
-                   _ptr(aux), C.byref(sg), _ptr(dh0), _ptr(scratch), B, S, d, hid, R, K, self.stream)
+        if mean_prob is None:
+            self._call("rte_router_aux_bwd", C.byref(sw), C.byref(so), _ptr(depth_values), lambda_load, lambda_depth,
+                       _ptr(aux), C.byref(sg), _ptr(dh0), _ptr(scratch), B, S, d, hid, R, K, self.stream)
+            return
+        self._call("rte_router_aux_bwd_data", C.byref(sw), C.byref(so), _ptr(depth_values), lambda_load, lambda_depth,
+                   _ptr(aux), _ptr(dh0), _ptr(scratch), _ptr(mean_prob), B, S, d, hid, R, K, self.stream)
+        self._call("rte_router_aux_bwd_params", C.byref(so), C.byref(sg), _ptr(scratch), B, d, hid, R, K, self.stream)
+
+    def router_mean_prob(self, recipe_probs, out, scale: float, *, B, R) -> None:
+        """out[r] = scale * sum_b recipe_probs[b, r] (this rank's share of the global batch mean)."""
+        self._call("rte_router_mean_prob", _ptr(recipe_probs), _ptr(out), scale, B, R, self.stream)
 
     def router_aux_bwd_split(self, w: dict, fwd: dict, depth_values, lambda_load, lambda_depth, aux, grads: dict, dh0,
-                             scratch, *, B, S, d, hid, R, K):
+                             scratch, *, B, S, d, hid, R, K, mean_prob=None):
         """The same backward with the weight gradients on `param_stream` when one is set."""
         sw, so = self._router_weights(w), self._router_out(fwd)
         sg = A.RouterGrads()
         for name, _ in A.RouterGrads._fields_:
             setattr(sg, name, grads[name].data_ptr())
         self._call("rte_router_aux_bwd_data", C.byref(sw), C.byref(so), _ptr(depth_values), lambda_load, lambda_depth,
-                   _ptr(aux), _ptr(dh0), _ptr(scratch), B, S, d, hid, R, K, self.stream)
+                   _ptr(aux), _ptr(dh0), _ptr(scratch), _ptr(mean_prob), B, S, d, hid, R, K, self.stream)
         with self._deferred():
             self._call("rte_router_aux_bwd_params", C.byref(so), C.byref(sg), _ptr(scratch), B, d, hid, R, K, self.stream)
 
     def router_aux_bwd_early(self, w: dict, fwd: dict, depth_values, lambda_load, lambda_depth, aux, grads: dict, scratch, *,
-                             B, S, d, hid, R, K):
+                             B, S, d, hid, R, K, mean_prob=None):
         """Everything of the auxiliary-loss backward except the add into dh0 (no upstream gradient is involved, so
         this may run right after the router's forward); `router_aux_add_dh0` finishes it."""
         sw, so = self._router_weights(w), self._router_out(fwd)
@@ -334,7 +345,7 @@ class CudaOps:
         for name, _ in A.RouterGrads._fields_:
             setattr(sg, name, grads[name].data_ptr())
         self._call("rte_router_aux_bwd_data", C.byref(sw), C.byref(so), _ptr(depth_values), lambda_load, lambda_depth,
-                   _ptr(aux), None, _ptr(scratch), B, S, d, hid, R, K, self.stream)
+                   _ptr(aux), None, _ptr(scratch), _ptr(mean_prob), B, S, d, hid, R, K, self.stream)
         self._call("rte_router_aux_bwd_params", C.byref(so), C.byref(sg), _ptr(scratch), B, d, hid, R, K, self.stream)
 
     def router_aux_add_dh0(self, dh0, scratch, *, B, S, d, hid, R, K) -> None:

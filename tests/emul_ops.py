@@ -274,10 +274,14 @@ class EmulOps:
     def router_aux_bwd_split(self, *args, **kw):
         self.router_aux_bwd(*args, **kw)
 
-    def router_aux_bwd(self, w, fwd, depth_values, lambda_load, lambda_depth, aux, grads, dh0, scratch, *, B, S, d, hid, R, K):
+    def router_mean_prob(self, recipe_probs, out, scale, *, B, R):
+        out[:R] = recipe_probs.sum(0) * scale
+
+    def router_aux_bwd(self, w, fwd, depth_values, lambda_load, lambda_depth, aux, grads, dh0, scratch, *, B, S, d, hid, R, K,
+                       mean_prob=None):
         self.launches += 1
         rp, dp = fwd["recipe_probs"], fwd["depth_probs"]
-        mean = rp.mean(0)
+        mean = rp.mean(0) if mean_prob is None else mean_prob[:R].clone()
         aux[0] = lambda_load * (R * mean.square().sum() - 1.0)
         aux[1] = lambda_depth * fwd["expected_depth"].mean()
         dprob_r = (lambda_load * R * 2.0 * mean / B).expand(B, R)
@@ -305,9 +309,10 @@ class EmulOps:
         else:
             dh0.view(B, S, d).add_(dpooled[:, None, :] / S)
 
-    def router_aux_bwd_early(self, w, fwd, depth_values, lambda_load, lambda_depth, aux, grads, scratch, *, B, S, d, hid, R, K):
+    def router_aux_bwd_early(self, w, fwd, depth_values, lambda_load, lambda_depth, aux, grads, scratch, *, B, S, d, hid, R, K,
+                             mean_prob=None):
         self.router_aux_bwd(w, fwd, depth_values, lambda_load, lambda_depth, aux, grads, None, scratch, B=B, S=S, d=d,
-                            hid=hid, R=R, K=K)
+                            hid=hid, R=R, K=K, mean_prob=mean_prob)
 
     def router_aux_add_dh0(self, dh0, scratch, *, B, S, d, hid, R, K):
         self.launches += 1

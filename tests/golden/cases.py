@@ -96,3 +96,21 @@ def svd_ffn_inputs(seed: int = 31, tokens=(3, 11)):
     return dict(x=r(*tokens, c["d"], scale=1.0), w_up=r(c["f"], c["d"], scale=0.2), w_gate=r(c["f"], c["d"], scale=0.2),
                 w_down=r(c["f"], c["d"], scale=0.2), up_a=r(c["d"], c["rank"], scale=0.3), up_b=r(c["rank"], c["f"], scale=0.3),
                 gate_a=r(c["d"], c["rank"], scale=0.3), gate_b=r(c["rank"], c["f"], scale=0.3), probe=r(*tokens, c["d"], scale=1.0))
+
+
+# offline cluster-pool codebook build (reference cli.py:3244-3389, 4741-4771): seeded inputs of one layer
+CODEBOOK = dict(d=64, f=256, rank=16, tokens=320, clusters=6, candidate_m=64, iters=5)
+
+
+def codebook_inputs() -> dict:
+    """Well-separated synthetic calibration data: tokens drawn around `clusters` prototype directions, so that the
+    k-means assignments do not hinge on near-ties."""
+    import torch
+    c = CODEBOOK
+    g = torch.Generator().manual_seed(77)
+    wug = torch.randn(2 * c["f"], c["d"], generator=g) * 0.3
+    wd = torch.randn(c["d"], c["f"], generator=g) * 0.3
+    protos = torch.randn(c["clusters"], c["d"], generator=g) * 2.0
+    which = torch.randint(0, c["clusters"], (c["tokens"],), generator=g)
+    normed = protos[which] + 0.25 * torch.randn(c["tokens"], c["d"], generator=g)
+    return dict(wug=wug, wd=wd, normed=normed)

@@ -203,6 +203,43 @@ def svd_ffn_vectors() -> dict[str, np.ndarray]:
             "dw_down": mod.w_down.grad.numpy()}
 
 
+def codebook_vectors() -> dict[str, np.ndarray]:
+    """The reference's offline codebook builders (cli.py: `_build_svd_factor_cache` 3244-3261 restated inline for one
+    weight pair, `_svd_cluster_features_and_scores` 3357-3389, `_fit_cluster_centers_from_features` 3297-3323,
+    `_aggregate_cluster_scores` 3326-3351, the top-M of 4756-4760, `_active_union_ids_from_codebook` 4914-4941) on
+    tests/golden/cases.py::codebook_inputs."""
+    from types import SimpleNamespace
+
+    from recursive_training_engine import cli as RCLI
+    from tests.golden.cases import CODEBOOK, codebook_inputs
+    c, t = CODEBOOK, codebook_inputs()
+    up_w, gate_w = t["wug"].chunk(2, dim=0)
+    factors = {}
+    for name, mat in (("up", up_w.t().contiguous()), ("gate", gate_w.t().contiguous())):
+        u, s, vh = torch.linalg.svd(mat, full_matrices=False)
+        factors[f"{name}_a"], factors[f"{name}_b"] = u[:, :c["rank"]] * s[:c["rank"]], vh[:c["rank"], :]
+    wd_lin = torch.nn.Linear(c["f"], c["d"], bias=False)
+    with torch.no_grad():
+        wd_lin.weight.copy_(t["wd"])
+    block = SimpleNamespace(mlp=SimpleNamespace(wd=wd_lin))
+    out = {}
+    for mode in ("sum", "upgate", "product"):
+        feats, scores = RCLI._svd_cluster_features_and_scores(block, t["normed"], factors, rank=c["rank"], score_mode=mode)
+        out[f"scores_{mode}"] = scores.numpy() if mode == "sum" else scores[:16].numpy()     # other modes: a 16-row sample
+    out["features"] = feats.numpy()
+    scores = torch.from_numpy(out["scores_sum"])
+    assign, centers = RCLI._fit_cluster_centers_from_features(feats, cluster_count=c["clusters"], iters=c["iters"])
+    out["assignments"], out["centers"] = assign.numpy(), centers.numpy()
+    for agg in ("mean", "max"):
+        a = RCLI._aggregate_cluster_scores(scores, assign, cluster_count=c["clusters"], aggregation=agg)
+        out[f"aggregate_{agg}"] = a.numpy()
+        out[f"candidate_ids_{agg}"] = torch.topk(a, k=c["candidate_m"], dim=-1).indices.numpy()
+    ids = torch.from_numpy(out["candidate_ids_mean"])
+    out["union_full"] = RCLI._active_union_ids_from_codebook(ids, hidden=c["f"]).numpy()
+    out["union_cap96"] = RCLI._active_union_ids_from_codebook(ids, hidden=c["f"], cap=96).numpy()
+    return out
+
+
 def main() -> None:
     torch.set_num_threads(4)
     only = set(sys.argv[1:])                     # e.g. `make_golden.py cluster_pool` rewrites that file alone
@@ -210,7 +247,7 @@ def main() -> None:
         if not only or name in only:
             np.savez_compressed(HERE / f"{name}.npz", **run_case(name, case))
     for name, fn in (("per_op", per_op_vectors), ("cluster_pool", cluster_pool_vectors),
-                     ("svd_ffn", svd_ffn_vectors)):
+                     ("svd_ffn", svd_ffn_vectors), ("codebook", codebook_vectors)):
         if not only or name in only:
             np.savez_compressed(HERE / f"{name}.npz", **fn())
     print("written to", HERE)

@@ -1,0 +1,148 @@
+"""The drop-in boundary against the real reference package: the operator table carries the reference's names and
+signatures (kernels/reference.py:9-157, kernels/optimized.py:12-154), and every configuration preset the reference
+ships parses into this package's schema (config.py:85-336, 406-449) -- either runnable or refused with a message
+naming the value.  Needs the reference package (a checkout beside the repository, $RTE_REFERENCE_SRC, or the
+in-tree install under baseline/_ref): skipped elsewhere."""
+import inspect
+import os
+import sys
+from pathlib import Path
+
+import pytest
+
+ROOT = Path(__file__).resolve().parents[1]
+
+
+def _reference_src():
+    for cand in (os.environ.get("RTE_REFERENCE_SRC"), str(ROOT.parent / "reference" / "src"), str(ROOT / "baseline" / "_ref")):
+        if cand and Path(cand, "recursive_training_engine", "kernels", "reference.py").exists():
+            return cand
+    return None
+
+
+REF_SRC = _reference_src()
+pytestmark = pytest.mark.skipif(REF_SRC is None, reason="reference package not present")
+if REF_SRC is not None and REF_SRC not in sys.path:
+    sys.path.insert(0, REF_SRC)
+
+
+def test_operator_table_has_the_reference_names_and_signatures():
+    from recursive_training_engine.kernels import optimized as ref_opt
+    from recursive_training_engine.kernels import reference as ref_ref
+    from speedup_thingy_b200 import kernels as mine
+
+    public = [n for n, f in vars(ref_opt).items() if inspect.isfunction(f) and not n.startswith("_") and f.__module__ == ref_opt.__name__]
+    assert {"k_fused_rmsnorm", "k_rope_apply", "k_flash_causal_dense", "k_flash_causal_grouped", "k_out_proj_grouped",
+            "k_logits_shortlist", "set_strict_cuda", "backend_status", "cuda_required"} <= set(public)
+    for name in public:
+        assert hasattr(mine, name), f"operator table lacks {name}"
+        # the reference's dispatch functions are (*args, **kwargs) wrappers: the signature lives in kernels/reference.py
+        want_fn = getattr(ref_ref, name, None) or getattr(ref_opt, name)
+        want, got = inspect.signature(want_fn), inspect.signature(getattr(mine, name))
+        w = [(p.name, p.kind, p.default if p.default is not inspect.Parameter.empty else None) for p in want.parameters.values()]
+        g = [(p.name, p.kind, p.default if p.default is not inspect.Parameter.empty else None) for p in got.parameters.values()]
+        assert w == g, (name, w, g)
+    # none of the table's operators is a stub
+    src = inspect.getsource(mine)
+    assert "NotImplementedError" not in src
+    assert set(mine.backend_status()) == set(ref_opt.backend_status())
+
+
+def test_every_reference_preset_parses_and_is_runnable_or_refused_by_value():
+    from recursive_training_engine.config import load_config as ref_load
+    from speedup_thingy_b200.config import check_supported, load_config, unsupported
+
+    presets = sorted((Path(REF_SRC).parent / "configs").glob("*.yaml"))
+    if not presets:
+        pytest.skip("the reference's configs/ directory is not beside the package (installed copy)")
+    runnable = []
+    for path in presets:
+        try:
+            ref = ref_load(path)
+        except ValueError as exc:             # a preset the reference itself refuses: refused here for the same reason
+            with pytest.raises(ValueError, match=str(exc)[:40]):
+                load_config(path)
+            continue
+        cfg = load_config(path)
+        # a file means here what it means there: every training / model / output field agrees with the reference's parse
+        for section in ("model", "training", "output"):
+            mine_s, ref_s = getattr(cfg, section), getattr(ref, section)
+            for f in ref_s.__dataclass_fields__:
+                a, b = getattr(mine_s, f), getattr(ref_s, f)
+                assert (list(a) if isinstance(a, tuple) else a) == b, (path.name, section, f, a, b)
+        problems = unsupported(cfg)
+        if problems:
+            for msg in problems:
+                section, rest = msg.split(".", 1)
+                key = rest.split("=", 1)[0]
+                assert section in ("model", "training", "output") and hasattr(getattr(cfg, section), key), msg
+                assert repr(getattr(getattr(cfg, section), key)) in msg, msg
+            with pytest.raises(NotImplementedError, match="does not implement"):
+                check_supported(cfg)
+            with pytest.raises(NotImplementedError):
+                load_config(path, check=True)
+        as_bf16 = load_config(path, precision="bf16")
+        if not unsupported(as_bf16):
+            runnable.append(path.name)
+    # the presets of the benchmarked pattern (fixed-count audit, constant or decaying LR, no consistency term) run
+    assert "medium_mac_real_clamped4_8_cheap_audit.yaml" in runnable, runnable
+    assert "medium_mac_real_hotpath.yaml" in runnable and "medium_mac_real_speed.yaml" in runnable, runnable
+    assert len(runnable) >= 4, runnable
+
+
+def test_unknown_keys_are_rejected_like_the_reference(tmp_path):
+    from speedup_thingy_b200.config import load_config
+    p = tmp_path / "bad.yaml"
+    p.write_text("model: {topology: recursive}\ntraining: {mode: recursive_macro, not_a_key: 1}\n")
+    with pytest.raises(ValueError, match="unknown config key"):
+        load_config(p)
+    p.write_text("allow_unknown_config_keys: true\nmodel: {topology: recursive}\ntraining: {mode: recursive_macro, not_a_key: 1}\n")
+    assert load_config(p).training.mode == "recursive_macro"
+
+
+@pytest.mark.gpu
+def test_table_bound_over_the_reference_runs_its_own_model_on_cuda():
+    """Assigns the operator table over `recursive_training_engine.kernels.optimized` and runs the reference's own
+    `RecursiveModel.forward_macro` (models.py:681-723) on CUDA through it, against the unpatched CPU result."""
+    import torch
+
+    from recursive_training_engine import config as RC
+    from recursive_training_engine.kernels import optimized as ref_opt
+    from recursive_training_engine.models import RecursiveModel
+    from speedup_thingy_b200 import kernels as mine
+
+    model_cfg = RC.ModelConfig(topology="recursive", vocab_size=256, d_model=128, n_heads=4, d_ff=256, n_dense_layers=2, n_prelude=1,
+                               n_coda=1, t_max=4, depth_choices=[1, 2, 4], attn_banks=1, ffn_banks=1, head_groups=4, ffn_groups=4,
+                               active_head_groups=2, active_ffn_groups=2, recipe_count=5, macro_rank=16)
+    torch.manual_seed(0)
+    model = RecursiveModel(model_cfg, RC.OutputConfig())
+    with torch.no_grad():
+        for prm in model.parameters():          # benchmark-style small weights: logits of order one
+            if prm.ndim >= 2:
+                prm.normal_(0.0, 0.05)
+    tokens = torch.randint(0, 256, (4, 32))
+    targets = torch.randint(0, 256, (4, 32))
+    with torch.no_grad():
+        want = model.forward_macro(tokens, targets, return_loss_per_sample=True, fixed_depth=4).loss_per_sample
+    names = ["k_fused_rmsnorm", "k_rope_apply", "k_flash_causal_dense", "k_flash_causal_grouped", "k_out_proj_grouped",
+             "k_logits_shortlist", "k_logits_full", "k_qkv_dense", "k_cross_entropy_unreduced"]
+    saved = {n: getattr(ref_opt, n) for n in names}
+    import recursive_training_engine.layers as ref_layers
+    import recursive_training_engine.output as ref_output
+    patched_modules = [ref_opt, ref_layers, ref_output]
+    saved_mod = [{n: getattr(m, n) for n in names if hasattr(m, n)} for m in patched_modules]
+    try:
+        for m in patched_modules:
+            for n in names:
+                if hasattr(m, n):
+                    setattr(m, n, getattr(mine, n))
+        cuda_model = model.to("cuda")
+        with torch.no_grad():
+            got = cuda_model.forward_macro(tokens.cuda(), targets.cuda(), return_loss_per_sample=True, fixed_depth=4).loss_per_sample.cpu()
+    finally:
+        for m, sv in zip(patched_modules, saved_mod):
+            for n, f in sv.items():
+                setattr(m, n, f)
+        for n, f in saved.items():
+            setattr(ref_opt, n, f)
+    assert torch.allclose(got, want, rtol=2e-2, atol=2e-2), (got, want)

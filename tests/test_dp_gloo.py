@@ -105,3 +105,56 @@ def test_two_ranks_with_the_same_shard_equal_one_process_with_audit(tmp_path):
     for n, p in single.params.items():
         assert (p - got["params"][n]).abs().max().item() <= 2.1 * AUDIT_TRAIN["lr"], n
         assert (p - got["params"][n]).abs().mean().item() <= 0.05 * AUDIT_TRAIN["lr"], n
+
+
+ROUTED_TRAIN = dict(mode="recursive_macro", lr=2e-3, weight_decay=0.1, seq_len=16, seed=3, fixed_depth=None,
+                    disable_router_aux=False, lambda_load=0.5, lambda_depth=0.05)
+
+
+def _routed_params():
+    """Benchmark initialisation with the recipe router's weights scaled up: the recipe probabilities differ clearly
+    from sample to sample, so the batch mean (and its square) is far from the uniform fixed point."""
+    params = init_parameters(ModelConfig(**MODEL), seed=3)
+    params["router.recipe_mlp.0.weight"] *= 40.0
+    params["router.recipe_mlp.2.weight"] *= 40.0
+    return params
+
+
+def _routed_worker(rank, world, port, out_path):
+    os.environ["MASTER_ADDR"], os.environ["MASTER_PORT"] = "127.0.0.1", str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    torch.set_num_threads(1)
+    cfg = ExperimentConfig(ModelConfig(**MODEL), TrainingConfig(**{**ROUTED_TRAIN, "batch_size": GLOBAL_B // world}))
+    eng = TrainEngine(cfg, _routed_params(), device="cpu", ops=EmulOps(), use_cuda_graph=False,
+                      process_group=dist.group.WORLD, bucket_cap_mb=0.05)
+    x, y = _batch()
+    lo, hi = rank * (GLOBAL_B // world), (rank + 1) * (GLOBAL_B // world)
+    loss, grads = eng.loss_and_grads((x[lo:hi], y[lo:hi]))
+    if rank == 0:
+        torch.save({"grads": {k: v.clone() for k, v in grads.items()}, "aux": eng.scalars[1:3].clone() * eng.loss_div}, out_path)
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_split_batch_with_router_aux_equals_the_global_batch(tmp_path):
+    """The load-balance loss squares a batch mean (metrics.py:103-105), so a shard-local mean would NOT reproduce the
+    global-batch gradient: the ranks exchange the R-float mean before the square.  Two ranks on a really split batch,
+    router-chosen recipes and depths, auxiliary losses on (weights raised so that they matter), against one process on
+    the whole batch."""
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    out = tmp_path / "rank0.pt"
+    mp.spawn(_routed_worker, args=(2, port, str(out)), nprocs=2, join=True)
+    got = torch.load(out)
+    cfg = ExperimentConfig(ModelConfig(**MODEL), TrainingConfig(**{**ROUTED_TRAIN, "batch_size": GLOBAL_B}))
+    single = TrainEngine(cfg, _routed_params(), device="cpu", ops=EmulOps(), use_cuda_graph=False)
+    _, ref = single.loss_and_grads(_batch())
+    assert float(single.scalars[1]) > 1e-3          # the term is active: the probabilities are far from uniform
+    assert abs(float(single.scalars[1]) - float(got["aux"][0])) <= 1e-5 * abs(float(single.scalars[1])) + 1e-8      # the load-balance loss itself
+    router = [n for n in ref if n.startswith("router.recipe_mlp")]
+    assert router
+    for n in ref:
+        scale = max(ref[n].abs().max().item(), 1e-6)
+        tol = 1e-4 if n in router else 2e-2          # the router only sees the auxiliary losses: exact up to fp32 order
+        assert (ref[n] - got["grads"][n]).abs().max().item() <= tol * scale + 1e-7, (n, scale)

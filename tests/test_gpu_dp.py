@@ -10,7 +10,7 @@ import torch.distributed as dist
 import torch.multiprocessing as mp
 
 from speedup_thingy_b200.config import ExperimentConfig, ModelConfig, TrainingConfig
-from speedup_thingy_b200.engine import TrainEngine, init_parameters
+from speedup_thingy_b200.engine import TrainEngine, init_parameters, teardown_data_parallel
 
 pytestmark = pytest.mark.gpu
 
@@ -43,10 +43,7 @@ def _worker(rank, world, port, out_path):
     captured = eng._graph is not None
     if rank == 0:
         torch.save({"losses": losses, "captured": captured, "params": {k: v.cpu() for k, v in eng.params.items()}}, out_path)
-    eng.close()
-    dist.barrier()
-    torch.cuda.synchronize()
-    os._exit(0)          # teardown of NCCL after graph-captured collectives is skipped (it has hung on some hosts)
+    teardown_data_parallel(eng)      # graphs first, then the process group
 
 
 def test_two_gpu_ranks_with_the_same_shard_equal_one_gpu(tmp_path):

@@ -178,8 +178,8 @@ def test_strict_cuda_and_status_contract():
     st = K.backend_status()
     assert st["mode"] == "cuda_sm100a_ext" and st["uses_reference_fallback"] is False and st["cuda_available"]
     K.cuda_required()
-    with pytest.raises(NotImplementedError):
-        K.k_macro_phi()
+    with pytest.raises(RuntimeError, match="strict_cuda"):
+        K.k_swiglu_dense(torch.randn(4, 8), torch.randn(8, 8), torch.randn(8, 8), torch.randn(8, 8))
     with pytest.raises(ValueError):
         K.k_fused_rmsnorm(torch.randn(2, 8, device=DEV), torch.ones(4, device=DEV))
 
@@ -221,3 +221,85 @@ def test_active_union_swiglu_evaluates_only_the_active_rows():
     inactive = torch.ones(F_, dtype=torch.bool)
     inactive[u] = False
     assert (L[1].grad.cpu()[:F_][inactive] == 0).all()
+
+
+def _ref_leaves(*ts):
+    return [t.bfloat16().float().requires_grad_() for t in ts]
+
+
+def test_swiglu_dense_and_grouped_match_reference_math_and_grads():
+    """k_swiglu_dense / k_swiglu_grouped (kernels/reference.py:62-78), weights stored [in, out]."""
+    g = torch.Generator().manual_seed(21)
+    x, wu, wg, wd = (torch.randn(3, 20, 64, generator=g), torch.randn(64, 128, generator=g) * 0.2,
+                     torch.randn(64, 128, generator=g) * 0.2, torch.randn(128, 64, generator=g) * 0.2)
+    slabs = torch.cat([torch.arange(32, 64), torch.arange(96, 128)])
+    for fn, extra, ref_fn in ((K.k_swiglu_dense, (), lambda X, U, G, D: (X @ U) * torch.nn.functional.silu(X @ G) @ D),
+                              (K.k_swiglu_grouped, (slabs,),
+                               lambda X, U, G, D: (X @ U[:, slabs]) * torch.nn.functional.silu(X @ G[:, slabs]) @ D[slabs, :])):
+        L = [t.to(DEV).requires_grad_() for t in (x, wu, wg, wd)]
+        out = fn(*L, *[e.to(DEV) for e in extra])
+        R = _ref_leaves(x, wu, wg, wd)
+        ref = ref_fn(*R)
+        _close(out, ref, 2e-2)
+        probe = torch.randn(ref.shape, generator=g)
+        (ref * probe).sum().backward()
+        (out * probe.to(DEV)).sum().backward()
+        for a, b in zip(L, R):
+            _close(a.grad, b.grad, 2.5e-2, 1e-4)
+
+
+def test_qkv_grouped_matches_reference_math_and_grads():
+    g = torch.Generator().manual_seed(22)
+    x = torch.randn(2, 16, 64, generator=g)
+    ws = [torch.randn(64, 64, generator=g) * 0.2 for _ in range(3)]
+    cols = torch.cat([torch.arange(16, 32), torch.arange(48, 64)])
+    L = [t.to(DEV).requires_grad_() for t in (x, *ws)]
+    outs = K.k_qkv_grouped(*L, cols.to(DEV))
+    R = _ref_leaves(x, *ws)
+    refs = [R[0] @ w[:, cols] for w in R[1:]]
+    probe = torch.randn(refs[0].shape, generator=g)
+    for o, r in zip(outs, refs):
+        _close(o, r, 2e-2)
+    sum((r * probe).sum() for r in refs).backward()
+    sum((o * probe.to(DEV)).sum() for o in outs).backward()
+    for a, b in zip(L, R):
+        _close(a.grad, b.grad, 2.5e-2, 1e-4)
+
+
+def test_macro_phi_simplified_form_matches_reference_math():
+    """k_macro_phi (kernels/reference.py:111-124)."""
+    g = torch.Generator().manual_seed(23)
+    B, S, d, m = 3, 16, 64, 16
+    h, h0 = torch.randn(B, S, d, generator=g), torch.randn(B, S, d, generator=g)
+    d_gain, bias = torch.randn(d, generator=g) * 0.1, torch.randn(d, generator=g) * 0.1
+    v, u = torch.randn(3 * d, m, generator=g) * 0.1, torch.randn(m, d, generator=g) * 0.1
+    out = K.k_macro_phi(*[t.to(DEV) for t in (h, h0, d_gain, v, u, bias)])
+    normed = h * torch.rsqrt(h.pow(2).mean(-1, keepdim=True) + 1e-5)
+    z = torch.cat([normed, normed.mean(1, keepdim=True).expand_as(normed), h0], dim=-1)
+    ref = h + d_gain * h + torch.nn.functional.silu(z @ v) @ u + bias
+    _close(out, ref, 2e-2)
+
+
+def test_pack_by_recipe_round_trip_and_grads():
+    """k_pack_by_recipe / k_unpack_from_recipe (kernels/reference.py:91-108): stable order by (recipe, depth, audited)."""
+    g = torch.Generator().manual_seed(24)
+    hidden = torch.randn(10, 6, 8, generator=g)
+    recipe = torch.tensor([2, 0, 1, 2, 0, 1, 1, 0, 2, 0])
+    depth = torch.tensor([1, 2, 1, 1, 2, 0, 1, 1, 0, 2])
+    hg = hidden.to(DEV).requires_grad_()
+    packed = K.k_pack_by_recipe(hg, recipe.to(DEV), depth.to(DEV))
+    keys = recipe * 1_000_000 + depth * 10
+    order = torch.sort(keys, stable=True).indices
+    assert torch.equal(packed.permutation.cpu(), order)
+    assert torch.equal(packed.packed.detach().cpu(), hidden[order])
+    assert torch.equal(packed.keys.cpu(), keys[order])
+    assert packed.offsets[-1].item() == 10 and packed.unique_keys.numel() == packed.offsets.numel() - 1
+    back = K.k_unpack_from_recipe(packed.packed, packed.inverse_permutation)
+    assert torch.equal(back.detach().cpu(), hidden)
+    probe = torch.randn(10, 6, 8, generator=g)
+    (packed.packed * probe.to(DEV)).sum().backward()
+    want = torch.empty_like(probe)
+    want[order] = probe
+    assert torch.equal(hg.grad.cpu(), want)
+    mask = K.k_sample_audit_mask(torch.full((64,), 0.25, device=DEV), 5)
+    assert mask.dtype == torch.bool and mask.shape == (64,)

@@ -138,3 +138,39 @@ def test_svd_sparse_ffn_restatement_matches_reference_golden():
     np.testing.assert_allclose(out.detach().numpy(), gold["out"], rtol=1e-5, atol=1e-6)
     for k, name in (("x", "dx"), ("w_up", "dw_up"), ("w_gate", "dw_gate"), ("w_down", "dw_down")):
         np.testing.assert_allclose(leaves[k].grad.numpy(), gold[name], rtol=1e-4, atol=1e-5)
+
+
+def test_codebook_build_restatement_matches_reference_golden():
+    """Offline cluster-pool codebook build (cli.py:3244-3389, 4741-4771, 4914-4941) against the reference's builders."""
+    from tests.golden.cases import CODEBOOK, codebook_inputs
+    gold = np.load(GOLDEN / "codebook.npz")
+    c, t = CODEBOOK, codebook_inputs()
+    factors = O.svd_factor_cache(t["wug"], c["rank"])
+    wd_norm = t["wd"].norm(dim=0)
+    for mode in ("sum", "upgate", "product"):
+        feats, scores = O.cluster_features_and_scores(t["normed"], factors, wd_norm, c["rank"], mode)
+        want = gold[f"scores_{mode}"]
+        np.testing.assert_allclose(scores[: want.shape[0]].numpy(), want, rtol=2e-3, atol=2e-2)    # SVD factors: LAPACK threading
+    np.testing.assert_allclose(feats.numpy(), gold["features"], rtol=2e-3, atol=1e-2)
+    feats, scores = torch.from_numpy(gold["features"]), torch.from_numpy(gold["scores_sum"])
+    assign, centers = O.fit_cluster_centers(feats, c["clusters"], c["iters"])
+    assert np.array_equal(assign.numpy(), gold["assignments"])
+    np.testing.assert_allclose(centers.numpy(), gold["centers"], rtol=1e-5, atol=1e-6)
+    for agg in ("mean", "max"):
+        a = O.aggregate_cluster_scores(scores, assign, c["clusters"], agg)
+        np.testing.assert_allclose(a.numpy(), gold[f"aggregate_{agg}"], rtol=1e-5, atol=1e-6)
+        book = O.build_cluster_pool_codebook(feats, scores, c["clusters"], c["candidate_m"], agg, c["iters"])
+        # the reference leaves the order of equal scores to torch.topk: compare as sets per cluster
+        for mine, ref in zip(book["candidate_ids"].numpy(), gold[f"candidate_ids_{agg}"]):
+            assert set(mine.tolist()) == set(ref.tolist())
+    ids = torch.from_numpy(gold["candidate_ids_mean"])
+    assert np.array_equal(O.active_union_ids(ids, c["f"]).numpy(), gold["union_full"])
+    # capped union: the reference leaves ties at the cap boundary to torch.topk; the restatement breaks them towards the
+    # lowest id, so the two selections may differ only in ids whose score equals the boundary score
+    mine, ref = set(O.active_union_ids(ids, c["f"], cap=96).tolist()), set(gold["union_cap96"].tolist())
+    assert len(mine) == len(ref) == 96
+    m = ids.shape[1]
+    weight = torch.linspace(1.0, 1.0 / m, steps=m).unsqueeze(0).expand(*ids.shape).reshape(-1)
+    score = torch.zeros(c["f"]).index_add_(0, ids.reshape(-1), weight)
+    boundary = min(float(score[i]) for i in ref)
+    assert all(abs(float(score[i]) - boundary) < 1e-6 for i in mine ^ ref), sorted(mine ^ ref)
