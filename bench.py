@@ -246,9 +246,11 @@ def run_reference(args, raw: dict) -> None:
 
 
 # --------------------------------------------------------------------------- stand-alone kernel probes (profiling)
-def probe_gemm(iters: int, warmup: int) -> None:
+def probe_gemm(iters: int, warmup: int, cublas: bool) -> None:
     """Stand-alone launches of the hot pass's GEMM shapes (one JSON line per shape): the small, fixed case the
-    `ncu --set full` capture of the tcgen05 kernel is taken on.  Operands rotate over sets larger than L2."""
+    `ncu --set full` capture of the tcgen05 kernel is taken on.  Operands rotate over sets larger than L2; each shape
+    is timed over a CUDA graph of `iters` launches, so host launch latency does not enter.  `cublas`: also time
+    torch.matmul (cuBLAS) on the plain bf16 shapes, the vendor library's figure for the same product."""
     import torch
 
     from speedup_thingy_b200 import _abi as A
@@ -261,11 +263,32 @@ def probe_gemm(iters: int, warmup: int) -> None:
     bf, f32 = torch.bfloat16, torch.float32
     shapes = [  # name, M, N, K, a_mn, b_mn, epilogue, residual, splits
         ("qkv", M, 3 * d, d, 0, 0, A.EPI_BF16, False, 1), ("wo+residual", M, d, d, 0, 0, A.EPI_F32, True, 1),
-        ("w_ug+swiglu", M, 2 * F, d, 0, 0, A.EPI_SWIGLU_FWD, False, 1), ("w_d+residual", M, d, F, 0, 0, A.EPI_F32, True, 1),
-        ("logits", M, V, d, 0, 0, A.EPI_BF16, False, 1), ("dz=dy.w_d+swiglu_bwd", M, F, d, 0, 1, A.EPI_SWIGLU_BWD, False, 1),
-        ("dn=dug.w_ug", M, d, 2 * F, 0, 1, A.EPI_BF16, False, 1), ("dw_ug", 2 * F, d, M, 1, 1, A.EPI_F32, False, 2),
-        ("dw_qkv", 3 * d, d, M, 1, 1, A.EPI_F32, False, 6)]
+        ("w_ug", M, 2 * F, d, 0, 0, A.EPI_BF16, False, 1), ("w_ug+swiglu", M, 2 * F, d, 0, 0, A.EPI_SWIGLU_FWD, False, 1),
+        ("w_d+residual", M, d, F, 0, 0, A.EPI_F32, True, 1), ("logits", M, V, d, 0, 0, A.EPI_BF16, False, 1),
+        ("dz=dy.w_d", M, F, d, 0, 1, A.EPI_BF16, False, 1), ("dz=dy.w_d+swiglu_bwd", M, F, d, 0, 1, A.EPI_SWIGLU_BWD, False, 1),
+        ("dn=dug.w_ug", M, d, 2 * F, 0, 1, A.EPI_BF16, False, 1), ("dn=dqkv.w_qkv", M, d, 3 * d, 0, 1, A.EPI_BF16, False, 1),
+        ("dy=du.w_o", M, d, d, 0, 1, A.EPI_BF16, False, 1), ("dw_ug", 2 * F, d, M, 1, 1, A.EPI_F32, False, 2),
+        ("dw_d", d, F, M, 1, 1, A.EPI_F32, False, 4), ("dw_qkv", 3 * d, d, M, 1, 1, A.EPI_F32, False, 6),
+        ("dw_o", d, d, M, 1, 1, A.EPI_F32, False, 16)]
     sets = 4
+
+    def timed(fn) -> float:
+        for i in range(max(warmup, 1)):
+            fn(i % sets)
+        torch.cuda.synchronize()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            for i in range(iters):
+                fn(i % sets)
+        g.replay()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        g.replay()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) * 1e3 / iters
+
     for name, m, n, k, a_mn, b_mn, epi, res, splits in shapes:
         a = [torch.randn((k, m) if a_mn else (m, k), device=dev).to(bf) for _ in range(sets)]
         b = [(torch.randn((k, n) if b_mn else (n, k), device=dev) * 0.02).to(bf) for _ in range(sets)]
@@ -286,16 +309,13 @@ def probe_gemm(iters: int, warmup: int) -> None:
                 extra = [dict(residual=torch.randn(m, n, device=dev)) for _ in range(sets)]
         if splits > 1:
             kw.update(splits=splits, split_stride=m * n)
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        for i in range(warmup):
-            ops.gemm(a[i % sets], b[i % sets], out[i % sets], **extra[i % sets], **kw)
-        e0.record()
-        for i in range(iters):
-            ops.gemm(a[i % sets], b[i % sets], out[i % sets], **extra[i % sets], **kw)
-        e1.record()
-        torch.cuda.synchronize()
-        us = e0.elapsed_time(e1) * 1e3 / iters
-        print(json.dumps({"gemm": name, "M": m, "N": n, "K": k, "splits": splits, "us": us, "tflops": 2.0 * m * n * k / us / 1e6}))
+        us = timed(lambda i: ops.gemm(a[i], b[i], out[i], **extra[i], **kw))
+        line = {"gemm": name, "M": m, "N": n, "K": k, "splits": splits, "us": round(us, 2), "tflops": round(2.0 * m * n * k / us / 1e6, 1)}
+        if cublas and epi == A.EPI_BF16 and not a_mn:
+            outs = [torch.empty(m, n, device=dev, dtype=bf) for _ in range(sets)]
+            usc = timed(lambda i: torch.matmul(a[i], b[i] if b_mn else b[i].t(), out=outs[i]))
+            line.update(cublas_us=round(usc, 2), cublas_tflops=round(2.0 * m * n * k / usc / 1e6, 1))
+        print(json.dumps(line), flush=True)
     ops.check_status()
 
 
@@ -317,11 +337,14 @@ def main() -> None:
                     help="time the memory-bound kernels of the step stand-alone against their algorithmic bytes and exit (profiling)")
     ap.add_argument("--dp-timeline", action="store_true",
                     help="data parallel: add the start / end of every gradient bucket's all-reduce inside a step (profiling)")
+    ap.add_argument("--step-timeline", metavar="FILE", default=None,
+                    help="write start and duration of every C-ABI call of one captured step, per stream, as JSON lines (profiling; 1 GPU)")
+    ap.add_argument("--probe-cublas", action="store_true", help="with --probe-gemm: also time torch.matmul (cuBLAS) on the same shapes")
     ap.add_argument("--probe-iters", type=int, default=20)
     ap.add_argument("--probe-warmup", type=int, default=3)
     args = ap.parse_args()
     if args.probe_gemm:
-        probe_gemm(args.probe_iters, args.probe_warmup)
+        probe_gemm(args.probe_iters, args.probe_warmup, args.probe_cublas)
         return
     if args.probe_kernels:
         from speedup_thingy_b200.kernel_probe import probe_kernels
@@ -439,6 +462,11 @@ def main() -> None:
     eng.ops.check_status()
 
     timeline = eng.dp_timeline() if (args.dp_timeline and world > 1) else None     # every rank takes part
+    if args.step_timeline and world == 1:
+        prof = eng.profile_step(repeats=3)
+        with open(args.step_timeline, "w") as fh:
+            for (name, us), start, where in zip(prof, eng.last_profile_starts, eng.last_profile_streams):
+                fh.write(json.dumps({"call": name.split("@")[0], "stream": where, "start_us": round(start, 1), "us": round(us, 2)}) + "\n")
 
     # ---- roofline of the dominant kernel (the tcgen05 GEMM): CUDA-event nodes around every launch of a captured step
     roof = None

@@ -373,6 +373,11 @@ int rte_shortlist_build(const int64_t* targets, const int32_t* top_clusters, con
 int rte_shortlist_ce(const void* hidden, const void* W, const int32_t* shortlist, const float* row_weight, int32_t S,
                      float* loss_tok, void* logits_out, void* dlogits_dense, int32_t rows, int32_t d, int32_t V,
                      int32_t K, rte_stream_t stream);
+/* rte_shortlist_ce with the dot products taken from FULL logits (bf16 [rows, V], e.g. hidden . W^T from rte_gemm_bf16):
+ * the same loss and the same dense gradient, written in place over the logits row.  While the vocabulary is small
+ * one GEMM over all V columns is cheaper than gathering K weight rows per token (2*d*V FLOP against K*d*2 bytes).  */
+int rte_shortlist_ce_from_logits(void* logits_inout, const int32_t* shortlist, const float* row_weight, int32_t S,
+                                 float* loss_tok, int32_t rows, int32_t V, int32_t K, rte_stream_t stream);
 int rte_random_tokens(int32_t* out, int64_t n, int32_t vocab, const int64_t* seed, rte_stream_t stream);
 /* dense bf16 [rows, V] = 0 except dense[r, ids[r, k]] = vals[r, k] (ids distinct per row): turns a gradient over
  * shortlist slots (backward of k_logits_shortlist, reference.py:141-143) into rows the dense GEMMs can consume. */
@@ -498,6 +503,40 @@ int rte_kl_distill_grad(const void* hot_logits, const void* exact_logits, float 
 /* dst[(idx[r / S] * S + r % S) * ld + c] = bf16(dst[...] + src[r * V + c]),  r < rows, c < V                      */
 int rte_add_rows_f32_to_bf16(void* dst_bf16, int32_t ld, const int32_t* idx, int32_t S, const float* src, int32_t rows,
                              int32_t V, rte_stream_t stream);
+
+/* ------------------------------------------------ gradient exchange over NVLink peer memory (data parallelism)
+ * Replaces the NCCL all-reduce a DistributedDataParallel wrapper of the reference would issue per gradient bucket
+ * (the reference has no multi-GPU path of its own; its gradient-accumulation parity, tests/test_training_fixes.py:53-75,
+ * is the arithmetic this reproduces across ranks).
+ * rte_peer_allreduce_sum_f32: in place, buf[q][offset .. offset+n) <- sum over ranks, on every rank, by ONE kernel per
+ * rank using plain peer loads / stores.  All ranks must launch it with the same (offset, n, slot); `buf[q]` / `flags[q]`
+ * are THIS process's mappings (CUDA IPC) of rank q's gradient buffer and flag array (uint32
+ * [RTE_COMM_MAX_SLOTS][2][RTE_COMM_MAX_RANKS], zero-initialised once); `epoch` and `done_count` are this rank's own
+ * uint32 [RTE_COMM_MAX_SLOTS], zero-initialised.  `slot` separates exchanges that may be in flight at the same time.
+ * Sums run in rank order, so every rank ends with bit-identical values.  Waits on peers are bounded; on expiry *status
+ * becomes 104 and the range is left unreduced.  n and offset are multiples of 4; max_ctas (0 = 64) bounds the grid. */
+enum { RTE_COMM_MAX_RANKS = 8, RTE_COMM_MAX_SLOTS = 64 };
+typedef struct rte_peer_comm {
+  float* buf[RTE_COMM_MAX_RANKS];
+  uint32_t* flags[RTE_COMM_MAX_RANKS];
+  uint32_t* epoch;
+  uint32_t* done_count;
+  int32_t world, rank;
+} rte_peer_comm;
+int rte_peer_allreduce_sum_f32(const rte_peer_comm* comm, int64_t offset, int64_t n, int32_t slot, int32_t max_ctas,
+                               int32_t* status, rte_stream_t stream);
+
+/* Device memory the other ranks of the node can map (what rte_peer_comm's pointers point into).
+ * rte_peer_alloc: zero-filled allocation on the current device plus its 64-byte inter-process handle (send the
+ *   handle to the peers by any host channel).  rte_peer_free releases it, after every peer has closed its mapping.
+ * rte_peer_open: maps a peer's allocation for kernels of the CURRENT device (`owner_device` = the owner's device
+ *   ordinal, or -1 to skip the can-access check; RTE_ERR_UNSUPPORTED when the two devices have no peer path).
+ *   rte_peer_close unmaps it. */
+enum { RTE_IPC_HANDLE_BYTES = 64 };
+int rte_peer_alloc(int64_t bytes, void** ptr, uint8_t* handle);
+int rte_peer_open(const uint8_t* handle, int32_t owner_device, void** ptr);
+int rte_peer_close(void* ptr);
+int rte_peer_free(void* ptr);
 
 /* Global gradient norm and clip coefficient WITHOUT any caller-provided or allocated scratch.
  * (No counterpart in the reference: it exists for embedders of this library, see below.)

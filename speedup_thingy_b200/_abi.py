@@ -68,6 +68,14 @@ class AdamWTensor(C.Structure):
                 ("n", c_i64), ("lr_group", c_i32), ("step_slot", c_i32)]
 
 
+COMM_MAX_RANKS, COMM_MAX_SLOTS, IPC_HANDLE_BYTES = 8, 64, 64
+
+
+class PeerComm(C.Structure):
+    _fields_ = [("buf", c_vp * COMM_MAX_RANKS), ("flags", c_vp * COMM_MAX_RANKS), ("epoch", c_vp), ("done_count", c_vp),
+                ("world", c_i32), ("rank", c_i32)]
+
+
 class AdamWExtras(C.Structure):
     _fields_ = [("skip", c_vp), ("metric_partial", c_vp), ("metric_group", c_vp), ("metric_out", c_vp),
                 ("n_metric_groups", c_i32)]
@@ -137,6 +145,7 @@ PROTOTYPES = {
     "rte_grad_norm_multi_tensor": (C.c_int, [c_vp, c_i64, c_vp, c_vp, c_vp, c_vp, c_f32, c_vp, c_vp]),
     "rte_shortlist_build": (C.c_int, [c_vp, c_vp, c_vp, c_vp, c_vp] + [c_i32] * 7 + [c_vp, c_vp]),
     "rte_shortlist_ce": (C.c_int, [c_vp, c_vp, c_vp, c_vp, c_i32, c_vp, c_vp, c_vp, c_i32, c_i32, c_i32, c_i32, c_vp]),
+    "rte_shortlist_ce_from_logits": (C.c_int, [c_vp, c_vp, c_vp, c_i32, c_vp, c_i32, c_i32, c_i32, c_vp]),
     "rte_random_tokens": (C.c_int, [c_vp, c_i64, c_i32, c_vp, c_vp]),
     "rte_scatter_cols_bf16": (C.c_int, [c_vp, c_vp, c_vp, c_i32, c_i32, c_i32, c_vp]),
     "rte_gather_rows": (C.c_int, [c_vp, c_vp, c_vp, c_i32, c_i64, c_vp]),
@@ -155,6 +164,11 @@ PROTOTYPES = {
     "rte_kmeans_update": (C.c_int, [c_vp, c_vp, c_vp, c_vp, c_vp, c_i32, c_i32, c_i32, c_vp]),
     "rte_cluster_aggregate": (C.c_int, [c_vp, c_vp, c_vp, c_i32, c_i32, c_i32, c_i32, c_vp]),
     "rte_cluster_pool_scores": (C.c_int, [c_vp, c_vp, c_vp, c_vp, c_i64, c_i32, c_i32, c_vp]),
+    "rte_peer_allreduce_sum_f32": (C.c_int, [P(PeerComm), c_i64, c_i64, c_i32, c_i32, c_vp, c_vp]),
+    "rte_peer_alloc": (C.c_int, [c_i64, P(c_vp), C.c_char_p]),
+    "rte_peer_open": (C.c_int, [C.c_char_p, c_i32, P(c_vp)]),
+    "rte_peer_close": (C.c_int, [c_vp]),
+    "rte_peer_free": (C.c_int, [c_vp]),
     "rte_grad_norm_multi_tensor_static": (C.c_int, [c_vp, c_i64, c_vp, c_vp, c_vp, c_f32, c_vp, c_vp]),
 }
 

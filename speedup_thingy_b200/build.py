@@ -6,6 +6,8 @@ nvcc cross-compiles without a GPU, so this also runs on a CPU-only build machine
 """
 from __future__ import annotations
 
+import os
+import shlex
 import shutil
 import subprocess
 import sys
@@ -15,7 +17,7 @@ PKG = Path(__file__).resolve().parent
 ROOT = PKG.parent
 CSRC = PKG / "csrc"
 LIB = PKG / "lib" / "librte_b200.so"
-SOURCES = ["gemm_tcgen05.cu", "elementwise.cu", "attention.cu", "macro_phi.cu", "router.cu", "audit.cu", "shortlist.cu", "cluster_pool.cu", "svd_ffn.cu", "gemm_small.cu", "codebook.cu"]
+SOURCES = ["gemm_tcgen05.cu", "elementwise.cu", "attention.cu", "macro_phi.cu", "router.cu", "audit.cu", "shortlist.cu", "cluster_pool.cu", "svd_ffn.cu", "gemm_small.cu", "codebook.cu", "allreduce.cu"]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
     "-Xcompiler", "-fPIC",
@@ -48,7 +50,9 @@ def build(force: bool = False, verbose: bool = False) -> Path:
         if not path.exists():
             continue
         obj = LIB.parent / (path.stem + ".o")
-        cmd = [_nvcc(), *NVCC_FLAGS, "-I", str(ROOT / "include"),
+        # RTE_NVCC_EXTRA: extra compiler flags, e.g. -DRTE_GEMM_DIAG (the GEMM's timing diagnostics: with it the
+        # environment variable RTE_GEMM_DIAG_FLAGS switches off stores / MMAs / loads inside the kernel)
+        cmd = [_nvcc(), *NVCC_FLAGS, *shlex.split(os.environ.get("RTE_NVCC_EXTRA", "")), "-I", str(ROOT / "include"),
                "-I", str(CSRC), "-c", str(path), "-o", str(obj)]
         if verbose:
             cmd.insert(1, "-Xptxas=-v")

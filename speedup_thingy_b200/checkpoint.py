@@ -54,6 +54,13 @@ def save_checkpoint(engine: TrainEngine, path: str | Path, *, data_cursor: int |
     if engine._pending:
         # global_step advances at submit, tokens_seen / usage_ema at collect: a snapshot in between is inconsistent
         raise RuntimeError("steps are in flight: collect() them before saving a checkpoint")
+    if engine.world > 1:
+        # data parallel: every rank holds the same weights and optimiser state after the all-reduced step, so one
+        # rank writes the file and the others wait for it (call this on every rank)
+        import torch.distributed as dist
+        if dist.get_rank(engine.pg) != 0:
+            dist.barrier(group=engine.pg)
+            return
     model = {n: t.detach().to("cpu").clone() for n, t in engine.params.items()}
     if not engine.dense:
         # the reference model's two persistent buffers (macro.py:99-122): the per-key update scale the macro kernels
@@ -68,6 +75,9 @@ def save_checkpoint(engine: TrainEngine, path: str | Path, *, data_cursor: int |
     p = Path(path)
     p.parent.mkdir(parents=True, exist_ok=True)
     torch.save(payload, p)
+    if engine.world > 1:
+        import torch.distributed as dist
+        dist.barrier(group=engine.pg)
 
 
 def load_checkpoint(engine: TrainEngine, path: str | Path) -> int | None:

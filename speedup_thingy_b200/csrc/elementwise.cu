@@ -688,6 +688,7 @@ extern "C" const char* rte_status_string(int code) {
     case RTE_DEV_WAIT_TIMEOUT_PRODUCER: return "device: TMA producer wait ran out";
     case RTE_DEV_WAIT_TIMEOUT_MMA: return "device: MMA issuer wait ran out";
     case RTE_DEV_WAIT_TIMEOUT_EPILOGUE: return "device: epilogue wait ran out";
+    case RTE_DEV_WAIT_TIMEOUT_PEER: return "device: wait for a data-parallel peer ran out";
     case RTE_DEV_INDEX_OUT_OF_RANGE: return "device: index out of range";
     case RTE_DEV_CAPACITY_OVERFLOW: return "device: packed rows exceed the caller's capacity";
     default: return "unknown";

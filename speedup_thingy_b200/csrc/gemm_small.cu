@@ -6,14 +6,22 @@
 // bf16 in, fp32 accumulate; B either K-major ([N,K], nn.Linear layout) or MN-major ([K,N], the banked layout);
 // outputs bf16 or fp32 (+ fp32 residual), optional split along K into partial results (fp32, reduced by
 // rte_reduce_splits in fixed order).
+//
+// The same kernel covers the replay's weight gradients dW[M,N] (+)= A^T B with A stored [K,M], B stored [K,N] and a
+// reduction of only K = rows-of-one-sample (64..256): an update of rank K whose cost is reading and writing dW.
+//
+// These launches run beside a hot pass whose persistent GEMM owns all the shared memory of every SM it sits on, so
+// what is left for them is a handful of SMs.  The ring of k-tiles is as deep as the reduction needs and no deeper
+// (2, 4 or 8 stages), so that short reductions leave room for several CTAs per SM.
 
 #include "rte_common.cuh"
 
 namespace {
 
 constexpr int BM = 64, BK = 64, LDS = BK + 8, THR = 128;       // BN (64 or 32) is a template parameter
-constexpr int NST = 8;                                     // k-tiles in flight: the launch is latency-bound, not bandwidth-bound
-constexpr int SMEM_BYTES = NST * (BM + 64) * LDS * 2;        // sized for the wider tile
+constexpr int smem_bytes(int nst, int bn, bool b_mn) {       // nst stages of an A tile and a B tile
+  return nst * (BM * LDS + (b_mn ? BK * (bn + 8) : bn * LDS)) * 2;
+}
 
 __device__ __forceinline__ void cp_async16(void* smem, const void* gmem, bool valid) {
   const uint32_t dst = static_cast<uint32_t>(__cvta_generic_to_shared(smem));
@@ -34,6 +42,11 @@ __device__ __forceinline__ void ldsm_x2_trans(uint32_t& b0, uint32_t& b1, const 
   const uint32_t addr = static_cast<uint32_t>(__cvta_generic_to_shared(row_ptr));
   asm volatile("ldmatrix.sync.aligned.m8n8.x2.trans.shared.b16 {%0,%1}, [%2];" : "=r"(b0), "=r"(b1) : "r"(addr));
 }
+__device__ __forceinline__ void ldsm_x4_trans(uint32_t (&a)[4], const __nv_bfloat16* row_ptr) {
+  const uint32_t addr = static_cast<uint32_t>(__cvta_generic_to_shared(row_ptr));
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(a[0]), "=r"(a[1]), "=r"(a[2]), "=r"(a[3]) : "r"(addr));
+}
 __device__ __forceinline__ uint32_t ld32(const __nv_bfloat16* p) { return *reinterpret_cast<const uint32_t*>(p); }
 
 struct SmallParams {
@@ -47,7 +60,9 @@ struct SmallParams {
 
 // The legacy mma.sync path peaks near 2 TFLOP/s per SM on this part, so a CTA's speed is set by how many MMAs it
 // issues per k-tile: narrow (BN = 32) tiles double the CTA count when the wide grid would leave most SMs idle.
-template <bool B_MN, bool OUT_F32, int BN>
+// A_MN: A is stored [K, M] (its tile sits in shared memory as [k][m] and the fragments come out of ldmatrix.trans).
+// NST: k-tiles in flight (a ring of NST stages, NST - 1 of them prefetched).
+template <bool A_MN, bool B_MN, bool OUT_F32, int BN, int NST>
 __global__ void __launch_bounds__(THR)
 gemm_small_kernel(const SmallParams p) {
   constexpr int LDB = B_MN ? BN + 8 : LDS;       // row stride of the B tile ([k][n] rows are BN long, [n][k] rows BK long)
@@ -55,6 +70,7 @@ gemm_small_kernel(const SmallParams p) {
   extern __shared__ __align__(16) uint8_t smraw[];
   __nv_bfloat16 (*sa)[BM * LDS] = reinterpret_cast<__nv_bfloat16 (*)[BM * LDS]>(smraw);
   __nv_bfloat16 (*sb)[B_ROWS * LDB] = reinterpret_cast<__nv_bfloat16 (*)[B_ROWS * LDB]>(smraw + NST * BM * LDS * 2);   // K-major B: [n][k]; MN-major: [k][n]
+  static_assert(BM == BK, "the A tile has the same footprint in either orientation");
   const int n0 = blockIdx.x * BN, m0 = blockIdx.y * BM;
   const int k_lo = blockIdx.z * p.k_per_split, k_hi = min(p.K, k_lo + p.k_per_split);
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, g = lane >> 2, t = lane & 3;
@@ -64,8 +80,13 @@ gemm_small_kernel(const SmallParams p) {
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
       const int chunk = threadIdx.x + i * THR, r = chunk >> 3, c = (chunk & 7) * 8;
-      const bool va = (m0 + r) < p.M && (k0 + c) < k_hi;
-      cp_async16(&sa[buf][r * LDS + c], va ? p.A + (size_t)(m0 + r) * p.lda + k0 + c : p.A, va);
+      if (!A_MN) {                                         // row r of the tile = output row, c = offset along k
+        const bool va = (m0 + r) < p.M && (k0 + c) < k_hi;
+        cp_async16(&sa[buf][r * LDS + c], va ? p.A + (size_t)(m0 + r) * p.lda + k0 + c : p.A, va);
+      } else {                                             // row r of the tile = k, c = offset along the output rows
+        const bool va = (k0 + r) < k_hi && (m0 + c) < p.M;
+        cp_async16(&sa[buf][r * LDS + c], va ? p.A + (size_t)(k0 + r) * p.lda + m0 + c : p.A, va);
+      }
     }
     if (!B_MN) {
 #pragma unroll
@@ -110,10 +131,16 @@ gemm_small_kernel(const SmallParams p) {
 #pragma unroll
     for (int ks = 0; ks < BK / 16; ++ks) {
       uint32_t af[4];
-      af[0] = ld32(a + g * LDS + ks * 16 + 2 * t);
-      af[1] = ld32(a + (g + 8) * LDS + ks * 16 + 2 * t);
-      af[2] = ld32(a + g * LDS + ks * 16 + 8 + 2 * t);
-      af[3] = ld32(a + (g + 8) * LDS + ks * 16 + 8 + 2 * t);
+      if (!A_MN) {
+        af[0] = ld32(a + g * LDS + ks * 16 + 2 * t);
+        af[1] = ld32(a + (g + 8) * LDS + ks * 16 + 2 * t);
+        af[2] = ld32(a + g * LDS + ks * 16 + 8 + 2 * t);
+        af[3] = ld32(a + (g + 8) * LDS + ks * 16 + 8 + 2 * t);
+      } else {
+        // four transposed 8x8 blocks of the [k][m] tile: (k lo, m lo), (k lo, m hi), (k hi, m lo), (k hi, m hi)
+        const int j = lane >> 3, i = lane & 7;
+        ldsm_x4_trans(af, sa[buf] + (ks * 16 + (j >> 1) * 8 + i) * LDS + warp * 16 + (j & 1) * 8);
+      }
 #pragma unroll
       for (int nt = 0; nt < BN / 8; ++nt) {
         uint32_t b0, b1;
@@ -158,12 +185,13 @@ gemm_small_kernel(const SmallParams p) {
 
 extern "C" int rte_gemm_bf16_small(const rte_gemm_args* a, rte_stream_t stream) {
   RTE_CHECK_ARG(a != nullptr && a->A && a->B && a->C && a->M > 0 && a->N > 0 && a->K > 0);
-  RTE_CHECK_ARG(!a->a_mn_major && a->tile_group == nullptr && a->split_kblocks == nullptr);
+  RTE_CHECK_ARG(a->tile_group == nullptr && a->split_kblocks == nullptr);
+  RTE_CHECK_ARG(!a->a_mn_major || (a->b_mn_major && a->epilogue == RTE_EPI_F32));      // A^T only for weight gradients
   RTE_CHECK_ARG(a->epilogue == RTE_EPI_BF16 || a->epilogue == RTE_EPI_F32);
   const int splits = a->splits < 1 ? 1 : a->splits;
   RTE_CHECK_ARG(splits == 1 || (a->epilogue == RTE_EPI_F32 && a->R == nullptr));
   if ((reinterpret_cast<uintptr_t>(a->A) & 15) || (reinterpret_cast<uintptr_t>(a->B) & 15) || (a->lda % 8) || (a->ldb % 8) ||
-      (a->K % 8) || (a->b_mn_major && (a->N % 8)))
+      (a->K % 8) || (a->b_mn_major && (a->N % 8)) || (a->a_mn_major && (a->M % 8)))
     return RTE_ERR_ALIGNMENT;
   SmallParams p;
   p.A = reinterpret_cast<const __nv_bfloat16*>(a->A); p.lda = a->lda;
@@ -178,25 +206,43 @@ extern "C" int rte_gemm_bf16_small(const rte_gemm_args* a, rte_stream_t stream) 
   const bool f32 = a->epilogue == RTE_EPI_F32;
   const int wide_ctas = rte::ceil_div(a->N, 64) * rte::ceil_div(a->M, BM) * splits;
   const bool narrow = wide_ctas < 74;                    // fewer CTAs than half the SMs: halve the tile width
-#define RTE_SMALL_LAUNCH(BMN, F32, BNV)                                                                               \
+  // k-tiles in flight: the whole reduction of a CTA up to eight tiles (one round trip to memory instead of several --
+  // the launch is latency-bound), but no more stages than the reduction has tiles
+  const int kt_cta = rte::ceil_div(p.k_per_split < a->K ? p.k_per_split : a->K, BK);
+  const int depth = kt_cta > 4 ? 8 : kt_cta > 2 ? 4 : 2;
+#define RTE_SMALL_LAUNCH(AMN, BMN, F32, BNV, NSTV)                                                                    \
   do {                                                                                                                \
+    constexpr int SM_ = smem_bytes(NSTV, BNV, BMN);                                                                   \
     static bool set_ = false;                                                                                         \
     if (!set_) {                                                                                                      \
-      if (cudaFuncSetAttribute(gemm_small_kernel<BMN, F32, BNV>, cudaFuncAttributeMaxDynamicSharedMemorySize,         \
-                               SMEM_BYTES) != cudaSuccess)                                                            \
+      if (cudaFuncSetAttribute(gemm_small_kernel<AMN, BMN, F32, BNV, NSTV>,                                           \
+                               cudaFuncAttributeMaxDynamicSharedMemorySize, SM_) != cudaSuccess)                      \
         return RTE_ERR_LAUNCH;                                                                                        \
       set_ = true;                                                                                                    \
     }                                                                                                                 \
-    gemm_small_kernel<BMN, F32, BNV><<<dim3(rte::ceil_div(a->N, BNV), rte::ceil_div(a->M, BM), splits), THR,         \
-                                       SMEM_BYTES, st>>>(p);                                                          \
+    gemm_small_kernel<AMN, BMN, F32, BNV, NSTV><<<dim3(rte::ceil_div(a->N, BNV), rte::ceil_div(a->M, BM), splits),   \
+                                                  THR, SM_, st>>>(p);                                                 \
   } while (0)
-  if (a->b_mn_major) {
-    if (f32) { if (narrow) RTE_SMALL_LAUNCH(true, true, 32); else RTE_SMALL_LAUNCH(true, true, 64); }
-    else     { if (narrow) RTE_SMALL_LAUNCH(true, false, 32); else RTE_SMALL_LAUNCH(true, false, 64); }
+#define RTE_SMALL_PICK(AMN, BMN, F32)                                                                                 \
+  do {                                                                                                                \
+    if (narrow) {                                                                                                     \
+      if (depth == 8) RTE_SMALL_LAUNCH(AMN, BMN, F32, 32, 8);                                                         \
+      else if (depth == 4) RTE_SMALL_LAUNCH(AMN, BMN, F32, 32, 4);                                                    \
+      else RTE_SMALL_LAUNCH(AMN, BMN, F32, 32, 2);                                                                    \
+    } else {                                                                                                          \
+      if (depth == 8) RTE_SMALL_LAUNCH(AMN, BMN, F32, 64, 8);                                                         \
+      else if (depth == 4) RTE_SMALL_LAUNCH(AMN, BMN, F32, 64, 4);                                                    \
+      else RTE_SMALL_LAUNCH(AMN, BMN, F32, 64, 2);                                                                    \
+    }                                                                                                                 \
+  } while (0)
+  if (a->a_mn_major) {
+    RTE_SMALL_PICK(true, true, true);                    // weight gradient: both operands [K, *], fp32 out
+  } else if (a->b_mn_major) {
+    if (f32) RTE_SMALL_PICK(false, true, true); else RTE_SMALL_PICK(false, true, false);
   } else {
-    if (f32) { if (narrow) RTE_SMALL_LAUNCH(false, true, 32); else RTE_SMALL_LAUNCH(false, true, 64); }
-    else     { if (narrow) RTE_SMALL_LAUNCH(false, false, 32); else RTE_SMALL_LAUNCH(false, false, 64); }
+    if (f32) RTE_SMALL_PICK(false, false, true); else RTE_SMALL_PICK(false, false, false);
   }
+#undef RTE_SMALL_PICK
 #undef RTE_SMALL_LAUNCH
   RTE_LAUNCH_CHECK();
   return RTE_OK;

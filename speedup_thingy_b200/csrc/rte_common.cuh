@@ -23,6 +23,7 @@ enum : int {
   RTE_DEV_WAIT_TIMEOUT_PRODUCER = 101,
   RTE_DEV_WAIT_TIMEOUT_MMA = 102,
   RTE_DEV_WAIT_TIMEOUT_EPILOGUE = 103,
+  RTE_DEV_WAIT_TIMEOUT_PEER = 104,
   RTE_DEV_INDEX_OUT_OF_RANGE = 201,
   RTE_DEV_CAPACITY_OVERFLOW = 202
 };

@@ -132,6 +132,36 @@ shortlist_ce_kernel(const __nv_bfloat16* __restrict__ hidden, const __nv_bfloat1
   }
 }
 
+// The same cross entropy when the FULL logits row already exists (one tcgen05 GEMM over the vocabulary costs less than
+// gathering K weight rows per token while the vocabulary is small): reads the K shortlisted logits of the row, then
+// overwrites the row in place with the dense gradient (zero outside the shortlist).  One CTA per token.
+__global__ void __launch_bounds__(128)
+shortlist_ce_logits_kernel(__nv_bfloat16* __restrict__ logits, const int32_t* __restrict__ shortlist,
+                           const float* __restrict__ row_weight, int S, float* __restrict__ loss_tok, int V, int K) {
+  extern __shared__ float lg[];          // [K]
+  __shared__ float red[32];
+  const int row = blockIdx.x;
+  __nv_bfloat16* lr = logits + (size_t)row * V;
+  for (int k = threadIdx.x; k < K; k += blockDim.x) lg[k] = __bfloat162float(lr[shortlist[(size_t)row * K + k]]);
+  __syncthreads();                        // every shortlisted logit has been read: the row may be overwritten
+  uint4* dr = reinterpret_cast<uint4*>(lr);
+  for (int i = threadIdx.x; i < V / 8; i += blockDim.x) dr[i] = make_uint4(0u, 0u, 0u, 0u);
+  float mx = -INFINITY;
+  for (int k = threadIdx.x; k < K; k += blockDim.x) mx = fmaxf(mx, lg[k]);
+  mx = rte::block_max(mx, red);
+  float se = 0.f;
+  for (int k = threadIdx.x; k < K; k += blockDim.x) se += __expf(lg[k] - mx);
+  se = rte::block_sum(se, red);           // (the reductions' barriers also order the zero fill before the scatter)
+  const float lse = mx + __logf(se);
+  if (threadIdx.x == 0) loss_tok[row] = lse - lg[0];
+  const float wgt = row_weight[row / S];
+  __syncthreads();
+  for (int k = threadIdx.x; k < K; k += blockDim.x) {
+    const float g = wgt * (__expf(lg[k] - lse) - (k == 0 ? 1.f : 0.f));
+    lr[shortlist[(size_t)row * K + k]] = __float2bfloat16_rn(g);
+  }
+}
+
 // dense[row, ids[row, k]] = vals[row, k], zero elsewhere (ids distinct within a row)
 __global__ void __launch_bounds__(128)
 scatter_cols_kernel(const __nv_bfloat16* __restrict__ vals, const int32_t* __restrict__ ids, __nv_bfloat16* __restrict__ dense,
@@ -195,6 +225,18 @@ extern "C" int rte_shortlist_ce(const void* hidden, const void* W, const int32_t
   shortlist_ce_kernel<<<rows, 128, smem, ST(stream)>>>(reinterpret_cast<const __nv_bfloat16*>(hidden),
       reinterpret_cast<const __nv_bfloat16*>(W), shortlist, row_weight, S, loss_tok,
       reinterpret_cast<__nv_bfloat16*>(logits_out), reinterpret_cast<__nv_bfloat16*>(dlogits_dense), d, V, K);
+  RTE_LAUNCH_CHECK();
+  return RTE_OK;
+}
+
+extern "C" int rte_shortlist_ce_from_logits(void* logits_inout, const int32_t* shortlist, const float* row_weight, int32_t S,
+                                           float* loss_tok, int32_t rows, int32_t V, int32_t K, rte_stream_t stream) {
+  RTE_CHECK_ARG(logits_inout && shortlist && row_weight && loss_tok && rows > 0 && S > 0 && V > 0 && V % 8 == 0 && K > 0);
+  if (reinterpret_cast<uintptr_t>(logits_inout) & 15) return RTE_ERR_ALIGNMENT;
+  const size_t smem = (size_t)K * sizeof(float);
+  if (smem > 48 * 1024) return RTE_ERR_UNSUPPORTED;
+  shortlist_ce_logits_kernel<<<rows, 128, smem, ST(stream)>>>(reinterpret_cast<__nv_bfloat16*>(logits_inout), shortlist, row_weight,
+                                                             S, loss_tok, V, K);
   RTE_LAUNCH_CHECK();
   return RTE_OK;
 }

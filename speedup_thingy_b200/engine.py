@@ -168,6 +168,12 @@ def teardown_data_parallel(engine: "TrainEngine | None", watchdog_s: float = 30.
     dist.barrier()
     if torch.cuda.is_available():
         torch.cuda.synchronize()
+    if engine is not None and getattr(engine, "_peer", None) is not None:
+        engine._peer.close()              # every rank is past its last exchange: unmap the peers' memory ...
+        dist.barrier()
+        engine._peer.flag_mem.free()      # ... and only then release what the peers had mapped
+        engine._grad_mem.free()           # (the engine's gradient views dangle from here on: it is closed)
+        engine._peer = engine._grad_mem = None
     sys.stdout.flush()
     sys.stderr.flush()
 
@@ -311,7 +317,18 @@ class TrainEngine:
             offsets[n] = total
             total += -(-self.params[n].numel() // 64) * 64          # 256-byte aligned slots
         self._grad_offsets = offsets
-        self.grad_flat = torch.zeros(max(total, 64), dtype=f32, device=dev)
+        # Gradient exchange: one kernel per rank over NVLink peer memory (peer_comm.PeerAllReduce) on GPUs, which
+        # needs the gradient buffer in memory the other ranks can map; RTE_DP_COMM=nccl keeps the library all-reduce
+        # (also what CPU / gloo process groups use).
+        self._peer = self._grad_mem = None
+        peer_comm = (self.world > 1 and dev.type == "cuda" and os.environ.get("RTE_DP_COMM", "peer") == "peer"
+                     and hasattr(ops, "lib"))
+        if peer_comm:
+            from .peer_comm import PeerMemory
+            self._grad_mem = PeerMemory(ops, max(total, 64) * 4)
+            self.grad_flat = self._grad_mem.tensor(f32)
+        else:
+            self.grad_flat = torch.zeros(max(total, 64), dtype=f32, device=dev)
         self.grads = {n: self.grad_flat[offsets[n]: offsets[n] + self.params[n].numel()].view(self.params[n].shape)
                       for n in self.trainable}
         self._buckets: list[tuple[int, int]] = []                   # [start, end) element ranges of grad_flat
@@ -334,6 +351,9 @@ class TrainEngine:
             self._bucket_of[n] = len(self._buckets) - 1
         self._bucket_size = [sum(1 for n in order if self._bucket_of[n] == i) for i in range(len(self._buckets))]
         self._comm_stream = torch.cuda.Stream(device=dev) if (self.world > 1 and dev.type == "cuda") else None
+        if peer_comm:
+            from .peer_comm import PeerAllReduce
+            self._peer = PeerAllReduce(ops, self._grad_mem, process_group)
         self.exp_avg = {n: torch.zeros_like(self.params[n]) for n in self.trainable}
         self.exp_avg_sq = {n: torch.zeros_like(self.params[n]) for n in self.trainable}
 
@@ -537,7 +557,10 @@ class TrainEngine:
                         if probes is not None:
                             e0 = torch.cuda.Event(enable_timing=True, external=True)
                             e0.record(self._comm_stream)
-                        dist.all_reduce(view, op=dist.ReduceOp.SUM, group=self.pg)
+                        if self._peer is not None:
+                            self._peer.all_reduce_(lo, hi, slot=i)
+                        else:
+                            dist.all_reduce(view, op=dist.ReduceOp.SUM, group=self.pg)
                         if probes is not None:
                             e1 = torch.cuda.Event(enable_timing=True, external=True)
                             e1.record(self._comm_stream)
@@ -707,7 +730,7 @@ class TrainEngine:
         ready(f"{pre}.norm1.weight")
 
     # ------------------------------------------------------------------ forward + backward
-    def _forward_backward_exact(self) -> None:
+    def _forward_backward_exact(self, forward_only: bool = False) -> None:
         """`recursive_exact`: embed -> prelude -> router -> t_max banked passes for every sample -> coda -> logits ->
         cross entropy (models.py:202-228, 416-512), then the same chain backwards; one stream."""
         o, cfg, p, g, tr, a = self.ops, self.cfg, self.params, self.grads, self.tr, self.exact_core
@@ -726,6 +749,8 @@ class TrainEngine:
         o.ce_fwd_bwd(a.logits, a.targets_a, a.row_weight_a, S, a.loss_tok, a.logits)
         o.segment_sum(a.loss_tok, self.loss_per_sample, B, S)
         o.segment_sum(self.loss_per_sample, self.scalars[0:1], 1, B)
+        if forward_only:
+            return
         # ---------------- backward
         self._begin_backward()
         a.backward_core(a.backward_head())
@@ -747,9 +772,10 @@ class TrainEngine:
         self._grad_ready(*self.trainable)
         self._finish_backward()
 
-    def _forward_backward(self) -> None:
+    def _forward_backward(self, forward_only: bool = False) -> None:
+        """`forward_only` (evaluation): stops after the per-sample losses; the caller switches the audit replay off."""
         if self.exact:
-            return self._forward_backward_exact()
+            return self._forward_backward_exact(forward_only)
         o, cfg, p, sh, g, tr = self.ops, self.cfg, self.params, self.shadow, self.grads, self.tr
         M, d, V, B, S = self.M, cfg.d_model, cfg.vocab_size, self.B, self.S
         tokens, targets = self.tokens.view(-1), self.targets.view(-1)
@@ -821,8 +847,14 @@ class TrainEngine:
             o.shortlist_build(targets, self.top_clusters, self.random_negs, self.shortlist_ids, self.shortlist_dups,
                               V=V, C=oc.num_clusters, TC=self.sl_tc, HN=oc.hard_negatives, RN=oc.random_negatives,
                               K=oc.shortlist_max_tokens)
-            o.shortlist_ce(self.hidden16, sh["embed.weight"], self.shortlist_ids, self.row_weight, S, self.loss_tok, None,
-                           self.logits)
+            if V <= 240 * oc.shortlist_max_tokens:
+                # small vocabulary: all V dot products as one tensor-core GEMM (2*d*V FLOP per token at ~1 PFLOP/s) cost
+                # less than gathering K weight rows per token from L2 (K*d*2 bytes at a few TB/s); same bf16 logits
+                o.gemm(self.hidden16, sh["embed.weight"], self.logits, M=M, N=V, K=d)
+                o.shortlist_ce_from_logits(self.logits, self.shortlist_ids, self.row_weight, S, self.loss_tok)
+            else:
+                o.shortlist_ce(self.hidden16, sh["embed.weight"], self.shortlist_ids, self.row_weight, S, self.loss_tok, None,
+                               self.logits)
         else:
             o.gemm(self.hidden16, sh["embed.weight"], self.logits, M=M, N=V, K=d)
             if self.audit is not None:
@@ -841,6 +873,8 @@ class TrainEngine:
             o.ce_fwd_bwd(self.logits, targets, self.row_weight, S, self.loss_tok, self.logits)   # logits -> dlogits in place
         o.segment_sum(self.loss_tok, self.loss_per_sample, B, S)
         o.segment_sum(self.loss_per_sample, self.scalars[0:1], 1, B)
+        if forward_only:
+            return
         if self.audit is not None:
             if self.shortlist:
                 self._side_wait_main()
@@ -1078,6 +1112,36 @@ class TrainEngine:
         self._run_step_kernels(optimizer=False)
         return self._assemble_loss(), self.grads
 
+    def evaluate(self, batches) -> dict[str, float]:
+        """Forward-only evaluation over an iterable of [B,S] (tokens, targets) batches, as `rte evaluate` does for one
+        batch (cli.py:193-319): the mode's own forward (the hot macro pass for `recursive_macro*`, the banked exact
+        passes for `recursive_exact`, the dense stack for `dense_exact`), no audit, no gradients, weights untouched.
+        Returns the mean per-sample loss (sum over a sample's tokens) and the mean negative log-likelihood per token."""
+        if self._pending:
+            raise RuntimeError("steps are in flight: collect() them before evaluating")
+        audit, self.audit = self.audit, None              # evaluation never replays audited samples
+        total, n = 0.0, 0
+        try:
+            for batch in batches:
+                tokens, targets = batch
+                if tuple(tokens.shape) != (self.B, self.S):
+                    raise ValueError(f"batch must be [{self.B}, {self.S}] int64 token ids")
+                self.tokens.copy_(tokens, non_blocking=True)
+                self.targets.copy_(targets, non_blocking=True)
+                if self.shortlist and self.oc.random_negatives > 0:
+                    gen = torch.Generator().manual_seed(self.tr.seed)       # `forward_macro(..., seed=0)` + config seed
+                    rn = torch.randint(0, self.cfg.vocab_size, (self.B, self.S, self.oc.random_negatives), generator=gen)
+                    self.random_negs.copy_(rn.view(self.M, -1).to(torch.int32), non_blocking=True)
+                self._forward_backward(forward_only=True)
+                total += float(self.loss_per_sample.sum())
+                n += self.B
+        finally:
+            self.audit = audit
+        if hasattr(self.ops, "check_status"):
+            self.ops.check_status()
+        mean = total / max(n, 1)
+        return {"mode": self.tr.mode, "eval_loss_per_sample": mean, "eval_nll_per_token": mean / self.S, "samples": n}
+
     def _host_slot(self, i: int) -> dict[str, Any]:
         """Pinned host buffers for the results of one in-flight step (two slots alternate)."""
         if self._host_slots is None:
@@ -1251,6 +1315,7 @@ class TrainEngine:
         the hot pass's weight-gradient stream carry the suffix "@wgrad", those of the audit replay's streams "@side"."""
         ops = self.ops
         calls: list[tuple[str, Any, Any]] = []
+        call_streams: list[int] = []
         orig_call, orig_gemm = ops._call, ops.gemm
         tag = {"v": ""}
 
@@ -1266,6 +1331,7 @@ class TrainEngine:
             where = "" if st.cuda_stream == main_stream else (
                 "@wgrad" if st.cuda_stream == hot_ps or (misc_ps is not None and st.cuda_stream == misc_ps.cuda_stream) else "@side")
             calls.append((name + tag["v"] + where, e0, e1))
+            call_streams.append(st.cuda_stream)
 
         def tagged_gemm(a, b, out, **kw):
             tag["v"] = f"[{kw['M']}x{kw['N']}x{kw['K']}/epi{kw.get('epilogue', 0)}" + (f"/split{kw['splits']}" if kw.get("splits", 1) > 1 else "") + "]"
@@ -1298,6 +1364,13 @@ class TrainEngine:
         # start of every call relative to the first one (last replay): the timeline across the streams
         first = calls[0][1]
         self.last_profile_starts = [first.elapsed_time(e0) * 1e3 for _, e0, _ in calls]
+        known = {main_stream: "main"}
+        for label, attr in (("hot_wgrad", "_hot_param_stream"), ("misc_wgrad", "_misc_param_stream"),
+                            ("replay", "_side_stream"), ("replay_wgrad", "_param_stream"), ("comm", "_comm_stream")):
+            st = getattr(self, attr, None)
+            if st is not None:
+                known.setdefault(st.cuda_stream, label)
+        self.last_profile_streams = [known.get(x, f"stream{x:#x}") for x in call_streams]
         return [(calls[i][0], totals[i] / repeats) for i in range(len(calls))]
 
     def dp_timeline(self, repeats: int = 5) -> dict[str, Any]:

@@ -45,6 +45,10 @@ class CudaOps:
         self.launches = 0          # kernels-entry calls issued (for bench accounting)
         self._split_ws: torch.Tensor | None = None
         self.small_gemm_rows = 256  # products with at most this many rows go to the few-row kernel (0: never)
+        # ... and so can weight gradients over that few rows (RTE_SMALL_WGRAD=1).  Off by default: inside the training
+        # step its hundreds of small CTAs on the replay's high-priority stream displace the hot pass (measured 2.04 ms
+        # per step against 1.72 ms with these products on the tcgen05 kernel's 32 tiles).
+        self.small_wgrad = os.environ.get("RTE_SMALL_WGRAD", "0") == "1"
         self.few_rows_max_splits = int(os.environ.get("RTE_FEWROW_SPLITS", "4"))
         self.gemm_max_ctas = 0     # 0 = one persistent CTA per SM; smaller values leave SMs to kernels of other streams
         # tile hints passed to every tcgen05 GEMM (0 = the library's choice): RTE_GEMM_PAIR=0 keeps every tile on one
@@ -114,8 +118,11 @@ class CudaOps:
         args.split_kblocks = split_kblocks.data_ptr() if split_kblocks is not None else None
         args.tile_n = self.gemm_tile_n if tile_n is None else tile_n
         args.cta_pair = self.gemm_cta_pair if cta_pair is None else cta_pair
-        few_rows = (M <= self.small_gemm_rows and not a_mn and epilogue in (A.EPI_BF16, A.EPI_F32) and tile_group is None
-                    and split_kblocks is None and K % 8 == 0 and (not b_mn or N % 8 == 0))
+        # few output rows, or (weight gradient of a few rows: A and B stored [K, *]) a reduction over few rows
+        few_rows = (epilogue in (A.EPI_BF16, A.EPI_F32) and tile_group is None and split_kblocks is None and K % 8 == 0
+                    and (not b_mn or N % 8 == 0)
+                    and ((not a_mn and M <= self.small_gemm_rows)
+                         or (a_mn and b_mn and self.small_wgrad and K <= self.small_gemm_rows and epilogue == A.EPI_F32 and M % 8 == 0 and splits == 1)))
         self._call("rte_gemm_bf16_small" if few_rows else "rte_gemm_bf16", C.byref(args), self.stream)
 
     def pick_splits(self, M: int, N: int, K: int) -> int:
@@ -416,6 +423,12 @@ class CudaOps:
         rows, K = shortlist.shape
         self._call("rte_shortlist_ce", _ptr(hidden), _ptr(W), _ptr(shortlist), _ptr(row_weight), S, _ptr(loss_tok),
                    _ptr(logits_out), _ptr(dlogits_dense), rows, hidden.shape[-1], W.shape[0], K, self.stream)
+
+    def shortlist_ce_from_logits(self, logits, shortlist, row_weight, S, loss_tok) -> None:
+        """Shortlist cross entropy read from full logits [rows, V]; the row becomes the dense gradient in place."""
+        rows, K = shortlist.shape
+        self._call("rte_shortlist_ce_from_logits", _ptr(logits), _ptr(shortlist), _ptr(row_weight), S, _ptr(loss_tok), rows,
+                   logits.shape[-1], K, self.stream)
 
     def scatter_cols(self, vals, ids, dense) -> None:
         rows, K = ids.shape

@@ -368,6 +368,17 @@ class EmulOps:
             dlogits_dense.zero_()
             dlogits_dense.scatter_(1, shortlist.long(), g.to(torch.bfloat16))
 
+    def shortlist_ce_from_logits(self, logits, shortlist, row_weight, S, loss_tok):
+        self.launches += 1
+        lg = torch.gather(logits.float(), 1, shortlist.long())
+        lse = torch.logsumexp(lg, dim=-1)
+        loss_tok.copy_(lse - lg[:, 0])
+        g = torch.exp(lg - lse[:, None])
+        g[:, 0] -= 1.0
+        g = g * row_weight.repeat_interleave(S)[:, None]
+        logits.zero_()
+        logits.scatter_(1, shortlist.long(), g.to(torch.bfloat16))
+
     # ---------------------------------------------------------------- macro operator (via autograd here)
     def _phi(self, h0, p, rid, sid, s_cfg, B, S, d, m):
         h = h0.view(B, S, d)

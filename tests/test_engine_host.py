@@ -167,3 +167,33 @@ def test_hot_budget_matches_reference_estimators_and_enforces_limits():
         hot_budget(model, TrainingConfig(**{**tr.__dict__, "target_speedup_vs_dense": 1e6}), None)
     ok = hot_budget(model, TrainingConfig(**{**tr.__dict__, "target_speedup_vs_dense": 1.01}), None)
     assert ok["active_param_budget"] == gold[2] / 1.01
+
+
+@pytest.mark.parametrize("name", ["macro_fixed_depth", "exact_two_banks", "dense", "macro_audit_two_banks"])
+def test_evaluate_is_forward_only_and_matches_the_oracle_forward(name):
+    """`TrainEngine.evaluate` (the counterpart of `rte evaluate`, cli.py:193-319): the mode's forward loss per sample,
+    nothing else touched."""
+    cfg, ocfg, otr = _pair(name)
+    tr = cfg.training
+    params = init_parameters(cfg.model, seed=tr.seed, num_clusters=cfg.output.num_clusters)
+    eng = TrainEngine(cfg, {k: v.clone() for k, v in params.items()}, device="cpu", ops=EmulOps(), use_cuda_graph=False)
+    stream = O.zipf_tokens(tr.batch_size * tr.seq_len * 3 + 1, cfg.model.vocab_size, seed=tr.seed)
+    batches = [b for _, b in zip(range(2), O.batches(stream, tr.batch_size, tr.seq_len))]
+    out = eng.evaluate(batches)
+    want = []
+    for tokens, targets in batches:
+        if cfg.model.topology == "dense":
+            want.append(O.forward_dense(params, ocfg, tokens, targets)["loss_per_sample"])
+        elif tr.mode == "recursive_exact":
+            _, info = O.exact_step_loss(params, ocfg, otr, tokens, targets, torch.zeros(ocfg.recipe_count))
+            want.append(info["hot"]["loss_per_sample"])
+        else:
+            want.append(O.forward_macro(params, ocfg, tokens, targets, tr.fixed_recipe, tr.fixed_depth)["loss_per_sample"])
+    ref = float(torch.cat(want).mean())
+    assert abs(out["eval_loss_per_sample"] - ref) <= 5e-3 * abs(ref), (out, ref)
+    assert out["eval_nll_per_token"] == pytest.approx(out["eval_loss_per_sample"] / tr.seq_len)
+    assert out["samples"] == 2 * tr.batch_size
+    for n in eng.params:                                   # weights, moments and counters untouched
+        assert torch.equal(eng.params[n], params[n]), n
+    assert eng.global_step == 0 and int(eng.plan.step_count.max()) == 0
+    assert (eng.audit is not None) == bool(tr.audit_fixed_count_per_batch)

@@ -31,14 +31,41 @@ def _batches():
     return out
 
 
-def _worker(rank, world, port, out_path):
+def _check_peer_allreduce(eng, rank, world):
+    """The exchange kernel on its own: ranges of several sizes and offsets of the shared gradient buffer, filled with
+    values every rank can reproduce, against the analytic sum; twice per range (the flags' epochs advance)."""
+    peer, flat = eng._peer, eng.grad_flat
+    n = flat.numel()
+    vals = [torch.randn(n, generator=torch.Generator().manual_seed(100 + q)) for q in range(world)]
+    want = sum(vals)
+    ranges = [(0, min(n, 4096)), (64, min(n, 64 + 1000 * 4)), (0, n - n % 4), (n // 2 - (n // 2) % 4, n - n % 4)]
+    for rep in range(2):
+        for slot, (lo, hi) in enumerate(ranges):
+            flat.copy_(vals[rank])
+            torch.cuda.synchronize()
+            dist.barrier()
+            peer.all_reduce_(lo, hi, slot)
+            torch.cuda.synchronize()
+            dist.barrier()
+            eng.ops.check_status()
+            got = flat.cpu()
+            assert torch.allclose(got[lo:hi], want[lo:hi], rtol=1e-6, atol=1e-6), (rep, lo, hi)
+            assert torch.equal(got[:lo], vals[rank][:lo]) and torch.equal(got[hi:], vals[rank][hi:])
+    flat.zero_()
+
+
+def _worker(rank, world, port, out_path, comm):
     os.environ["MASTER_ADDR"], os.environ["MASTER_PORT"] = "127.0.0.1", str(port)
     os.environ["NCCL_NVLS_ENABLE"] = "0"
+    os.environ["RTE_DP_COMM"] = comm
     torch.cuda.set_device(rank)
     dev = torch.device("cuda", rank)
     dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
     cfg = ExperimentConfig(ModelConfig(**MODEL), TrainingConfig(**TRAIN))
     eng = TrainEngine(cfg, init_parameters(cfg.model, seed=3), device=dev, process_group=dist.group.WORLD, bucket_cap_mb=0.25)
+    assert (eng._peer is not None) == (comm == "peer")
+    if eng._peer is not None:
+        _check_peer_allreduce(eng, rank, world)
     losses = [eng.train_step(b).loss for b in _batches()]
     captured = eng._graph is not None
     if rank == 0:
@@ -46,14 +73,16 @@ def _worker(rank, world, port, out_path):
     teardown_data_parallel(eng)      # graphs first, then the process group
 
 
-def test_two_gpu_ranks_with_the_same_shard_equal_one_gpu(tmp_path):
+@pytest.mark.parametrize("comm", ["peer", "nccl"])
+def test_two_gpu_ranks_with_the_same_shard_equal_one_gpu(tmp_path, comm):
+    """`comm`: the gradient exchange -- "peer" = one kernel per rank over NVLink peer memory, "nccl" = library all-reduce."""
     if torch.cuda.device_count() < 2:
         pytest.skip("needs two GPUs")
     with socket.socket() as s:
         s.bind(("127.0.0.1", 0))
         port = s.getsockname()[1]
     out = tmp_path / "rank0.pt"
-    ctx = mp.spawn(_worker, args=(2, port, str(out)), nprocs=2, join=False)
+    ctx = mp.spawn(_worker, args=(2, port, str(out), comm), nprocs=2, join=False)
     ctx.join(timeout=300)
     got = torch.load(out)
     assert got["captured"], "the data-parallel step graph was not captured"

@@ -115,6 +115,29 @@ def test_gemm_wgrad_split_k(ops, Mo, No, Kred):
     _close(out, 2 * ref, 2e-3, "wgrad accumulate")
 
 
+@pytest.mark.parametrize("Mo,No,Kred", [(2048, 512, 64), (512, 4096, 64), (1536, 512, 128), (512, 512, 256), (104, 72, 64), (8, 8, 8),
+                                        (200, 136, 200)])
+def test_gemm_wgrad_of_few_rows(ops, Mo, No, Kred):
+    """Weight gradient of one audited sample: a rank-Kred update (Kred = the sample's rows) through the few-row kernel's
+    transposed-A form, plain and accumulating."""
+    g = torch.Generator().manual_seed(Mo + No + Kred)
+    a_t, b_t = _bf(torch.randn(Kred, Mo, generator=g)), _bf(torch.randn(Kred, No, generator=g))
+    ref = a_t.float().t() @ b_t.float()
+    assert Kred <= ops.small_gemm_rows
+    out = torch.full((Mo, No), 7.0, dtype=torch.float32, device=DEV)
+    keep, ops.small_wgrad = ops.small_wgrad, True
+    try:
+        ops.gemm_wgrad(a_t.to(DEV), b_t.to(DEV), out, M=Mo, N=No, K=Kred)
+        torch.cuda.synchronize()
+        ops.check_status()
+        _close(out, ref, 2e-3, f"few-row wgrad {Mo}x{No} over {Kred}")
+        ops.gemm_wgrad(a_t.to(DEV), b_t.to(DEV), out, M=Mo, N=No, K=Kred, accumulate=True)
+        torch.cuda.synchronize()
+        _close(out, 2 * ref, 2e-3, "few-row wgrad accumulate")
+    finally:
+        ops.small_wgrad = keep
+
+
 @pytest.mark.parametrize("M,d,f", [(256, 128, 256), (512, 512, 2048), (100, 64, 64), (8192, 512, 2048)])
 def test_swiglu_epilogues(ops, M, d, f):
     g = torch.Generator().manual_seed(f)
@@ -445,6 +468,32 @@ def test_shortlist_ce_matches_reference_math(ops, rows, S, d, V, K):
 
 
 # ------------------------------------------------------------------ macro operator
+@pytest.mark.parametrize("rows,S,d,V,K", [(21, 7, 64, 96, 16), (256, 64, 512, 2048, 128)])
+def test_shortlist_ce_from_full_logits_equals_the_gathered_form(ops, rows, S, d, V, K):
+    """rte_shortlist_ce_from_logits (dot products taken from a full-vocabulary GEMM) against rte_shortlist_ce (K weight
+    rows gathered per token): same bf16 logits, so the loss and the dense gradient agree to rounding."""
+    g = torch.Generator().manual_seed(rows + K)
+    hidden = _bf(torch.randn(rows, d, generator=g)).to(DEV)
+    W = _bf(torch.randn(V, d, generator=g) * 0.1).to(DEV)
+    ids = torch.stack([torch.randperm(V, generator=g)[:K] for _ in range(rows)]).to(torch.int32).to(DEV)
+    rw = (torch.rand(-(-rows // S), generator=g) + 0.5).to(DEV)
+    loss_a, loss_b = torch.zeros(rows, device=DEV), torch.zeros(rows, device=DEV)
+    dense_a = torch.full((rows, V), 7.0, dtype=torch.bfloat16, device=DEV)
+    ops.shortlist_ce(hidden, W, ids, rw, S, loss_a, None, dense_a)
+    logits = torch.zeros(rows, V, dtype=torch.bfloat16, device=DEV)
+    keep, ops.small_gemm_rows = ops.small_gemm_rows, 0
+    try:
+        ops.gemm(hidden, W, logits, M=rows, N=V, K=d)
+    finally:
+        ops.small_gemm_rows = keep
+    ops.shortlist_ce_from_logits(logits, ids, rw, S, loss_b)
+    torch.cuda.synchronize()
+    ops.check_status()
+    _close(loss_b, loss_a, 1e-3, "loss from full logits")
+    assert (logits.float() - dense_a.float()).abs().max().item() <= 2e-2 * dense_a.float().abs().max().item()
+    assert int((logits != 0).sum(1).max()) <= K
+
+
 @pytest.mark.parametrize("tensor", [False, True])       # True: transposed weights prepared -> tensor-core forward
 @pytest.mark.parametrize("B,S,d,m,R", [(4, 16, 64, 8, 5), (6, 64, 128, 32, 5), (3, 40, 512, 32, 5), (2, 8, 64, 48, 3)])
 def test_macro_phi_fwd_bwd(ops, B, S, d, m, R, tensor):
