@@ -500,6 +500,15 @@ int rte_kl_distill(const void* hot_logits, const void* exact_logits, float temp,
  * on different streams; the sum and its single bf16 rounding are those of rte_kl_distill).                        */
 int rte_kl_distill_grad(const void* hot_logits, const void* exact_logits, float temp, float coef, float* dgrad,
                         float* kl_rows, int32_t rows, int32_t V, rte_stream_t stream);
+/* Residual clip of the control variate (audit.py:306-321): corrected = hot + clamp(exact - hot, -clip, clip) / p.
+ * For each audited sample j (hot row idx[j]) with |exact - hot| <= clip: f_hot = 1 - inv_p, f_exact = 1; otherwise
+ * f_hot = 1, f_exact = 0 -- the factors to apply (rte_scale_rows_bf16) to cross-entropy gradients that were written
+ * with the weights 1 (hot) and 1/p (exact).                                                                        */
+int rte_audit_clip(const float* hot_loss, const float* exact_loss, const int32_t* idx, int32_t n, float inv_p, float clip,
+                   float* f_hot, float* f_exact, rte_stream_t stream);
+/* x[row_of(r) * ld + c] = bf16(x[...] * scale[r / S]),  r < rows, c < V;  row_of(r) = idx ? idx[r / S] * S + r % S : r */
+int rte_scale_rows_bf16(void* x_bf16, int32_t ld, const int32_t* idx, int32_t S, const float* scale, int32_t rows, int32_t V,
+                        rte_stream_t stream);
 /* dst[(idx[r / S] * S + r % S) * ld + c] = bf16(dst[...] + src[r * V + c]),  r < rows, c < V                      */
 int rte_add_rows_f32_to_bf16(void* dst_bf16, int32_t ld, const int32_t* idx, int32_t S, const float* src, int32_t rows,
                              int32_t V, rte_stream_t stream);
@@ -509,15 +518,21 @@ int rte_add_rows_f32_to_bf16(void* dst_bf16, int32_t ld, const int32_t* idx, int
  * (the reference has no multi-GPU path of its own; its gradient-accumulation parity, tests/test_training_fixes.py:53-75,
  * is the arithmetic this reproduces across ranks).
  * rte_peer_allreduce_sum_f32: in place, buf[q][offset .. offset+n) <- sum over ranks, on every rank, by ONE kernel per
- * rank using plain peer loads / stores.  All ranks must launch it with the same (offset, n, slot); `buf[q]` / `flags[q]`
- * are THIS process's mappings (CUDA IPC) of rank q's gradient buffer and flag array (uint32
- * [RTE_COMM_MAX_SLOTS][2][RTE_COMM_MAX_RANKS], zero-initialised once); `epoch` and `done_count` are this rank's own
- * uint32 [RTE_COMM_MAX_SLOTS], zero-initialised.  `slot` separates exchanges that may be in flight at the same time.
- * Sums run in rank order, so every rank ends with bit-identical values.  Waits on peers are bounded; on expiry *status
- * becomes 104 and the range is left unreduced.  n and offset are multiples of 4; max_ctas (0 = 64) bounds the grid. */
+ * rank; everything that crosses the link is a plain peer store (each rank pushes its values of the other ranks' parts
+ * into their staging buffers, sums its own part locally in rank order, and stores the result into every buffer).  All
+ * ranks must launch it with the same (offset, n, slot).  `buf[q]` / `stage[q]` / `flags[q]` are THIS process's mappings
+ * (rte_peer_open) of rank q's gradient buffer, staging buffer (as large as the gradient buffer plus
+ * 4 * RTE_COMM_MAX_RANKS floats) and flag array (uint32 [RTE_COMM_MAX_SLOTS][2][RTE_COMM_MAX_RANKS], zero-initialised
+ * once); `epoch` (uint32 [RTE_COMM_MAX_SLOTS]) and `done_count` (uint32 [RTE_COMM_MAX_SLOTS][2]) are this rank's own,
+ * zero-initialised.  `slot` separates exchanges that may be in flight at the same time; such exchanges must also be
+ * at least 4 * RTE_COMM_MAX_RANKS floats apart in the buffer (a part's row in the staging buffer may overhang the range
+ * by that much).  Sums run in rank order, so every rank ends with bit-identical values.  Waits on peers are bounded; on
+ * expiry *status becomes 104 and the range is left unreduced.  n and offset are multiples of 4; max_ctas (0 = 64)
+ * bounds the grid. */
 enum { RTE_COMM_MAX_RANKS = 8, RTE_COMM_MAX_SLOTS = 64 };
 typedef struct rte_peer_comm {
   float* buf[RTE_COMM_MAX_RANKS];
+  float* stage[RTE_COMM_MAX_RANKS];
   uint32_t* flags[RTE_COMM_MAX_RANKS];
   uint32_t* epoch;
   uint32_t* done_count;

@@ -72,7 +72,8 @@ COMM_MAX_RANKS, COMM_MAX_SLOTS, IPC_HANDLE_BYTES = 8, 64, 64
 
 
 class PeerComm(C.Structure):
-    _fields_ = [("buf", c_vp * COMM_MAX_RANKS), ("flags", c_vp * COMM_MAX_RANKS), ("epoch", c_vp), ("done_count", c_vp),
+    _fields_ = [("buf", c_vp * COMM_MAX_RANKS), ("stage", c_vp * COMM_MAX_RANKS), ("flags", c_vp * COMM_MAX_RANKS),
+                ("epoch", c_vp), ("done_count", c_vp),
                 ("world", c_i32), ("rank", c_i32)]
 
 
@@ -159,6 +160,8 @@ PROTOTYPES = {
     "rte_macro_distill": (C.c_int, [c_vp, c_vp, c_vp, c_f32, c_f32, c_f32, c_f32, c_vp, c_vp, c_i32, c_i32, c_i32, c_vp]),
     "rte_kl_distill": (C.c_int, [c_vp, c_vp, c_f32, c_f32, c_vp, c_i32, c_vp, c_i32, c_vp, c_i32, c_i32, c_vp]),
     "rte_kl_distill_grad": (C.c_int, [c_vp, c_vp, c_f32, c_f32, c_vp, c_vp, c_i32, c_i32, c_vp]),
+    "rte_audit_clip": (C.c_int, [c_vp, c_vp, c_vp, c_i32, C.c_float, C.c_float, c_vp, c_vp, c_vp]),
+    "rte_scale_rows_bf16": (C.c_int, [c_vp, c_i32, c_vp, c_i32, c_vp, c_i32, c_i32, c_vp]),
     "rte_add_rows_f32_to_bf16": (C.c_int, [c_vp, c_i32, c_vp, c_i32, c_vp, c_i32, c_i32, c_vp]),
     "rte_normalize_rows_f32": (C.c_int, [c_vp, c_vp, c_i32, c_i32, c_vp]),
     "rte_kmeans_update": (C.c_int, [c_vp, c_vp, c_vp, c_vp, c_vp, c_i32, c_i32, c_i32, c_vp]),

@@ -76,6 +76,9 @@ class AuditReplay:
         f32, bf, i32 = torch.float32, torch.bfloat16, torch.int32
         e = lambda *shape, dtype=f32: torch.zeros(*shape, dtype=dtype, device=dev)  # noqa: E731
         self.p_inc = float(k) / float(eng.B)                              # inclusion probability k/n (audit.py:116)
+        self.grad = direct_grads or eng.tr.audit_mode == "gradient_corrected"      # does the replay carry gradients
+        self.clip = eng.tr.audit_residual_clip if (self.grad and not direct_grads) else None
+        self.f_hot, self.f_exact = e(n), e(n)                             # residual clip: per-sample gradient factors
         self.idx = e(n, dtype=i32)
         self.head_tab, self.ffn_tab = recipe_mask_tables(cfg, dev)
         self.rid, self.active = e(T, n, dtype=i32), e(T, n, dtype=i32)
@@ -172,7 +175,10 @@ class AuditReplay:
         w0 = 1.0 / (eng.B * eng.S * eng.loss_div)
         h_idx.copy_(chosen)
         h_rw.fill_(w0)
-        h_rw[chosen] = w0 * (1.0 - 1.0 / self.p_inc)                     # d corrected / d hot on audited samples
+        if self.grad and self.clip is None:
+            h_rw[chosen] = w0 * (1.0 - 1.0 / self.p_inc)                 # d corrected / d hot on audited samples
+        # (with a residual clip the factor depends on the losses: `clip_hot` applies it on the device;
+        #  without gradient correction the audited samples keep their plain weight)
         self._prepared = (step_seed, chosen, h_idx, h_rw)
         self._stage_next = (self._stage_next + 1) % 3
 
@@ -292,6 +298,21 @@ class AuditReplay:
             torch.cuda.current_stream(eng.device).wait_stream(eng._param_stream)
         o.ce_fwd_bwd(self.logits, self.targets_a, self.row_weight_a, S, self.loss_tok, self.logits)
         o.segment_sum(self.loss_tok, self.exact_loss, n, S)
+
+    def clip_exact(self) -> None:
+        """Residual clip (audit.py:306-321), replay side: decides per audited sample whether exact - hot lies inside the
+        clip and removes the replay's cross-entropy gradient (written with weight 1/p) where it does not."""
+        eng = self.eng
+        o = eng.ops
+        o.audit_clip(eng.loss_per_sample, self.exact_loss, self.idx, self.n, 1.0 / self.p_inc, float(self.clip),
+                     self.f_hot, self.f_exact)
+        o.scale_rows_bf16(self.logits, None, self.S, self.f_exact, self.Ma, eng.cfg.vocab_size)
+
+    def clip_hot(self) -> None:
+        """Hot side of `clip_exact`: the audited rows of the hot dlogits (written with weight 1) get 1 - 1/p inside the
+        clip and keep 1 outside."""
+        eng = self.eng
+        eng.ops.scale_rows_bf16(eng.logits, self.idx, self.S, self.f_hot, self.Ma, eng.cfg.vocab_size)
 
     def save_hot_logits(self) -> None:
         """Copies the audited rows of the hot logits before the cross-entropy kernel overwrites them."""
@@ -492,4 +513,9 @@ class AuditReplay:
                    endpoint_normed=tr.lambda_endpoint_normed * float(terms[:, 2].sum()) / (Ma * d),
                    endpoint_raw=tr.lambda_endpoint_raw * float(terms[:, 3].sum()) / (Ma * d),
                    kl=tr.lambda_kl * float(host["kl_sum"]) / n * temp * temp)
-        return dict(correction=float(((exact - hot) / self.p_inc).sum()), exact=exact, aux=aux)
+        residual = exact - hot
+        if self.clip is not None:
+            residual = residual.clamp(-float(self.clip), float(self.clip))
+        # the control variate is part of the loss only under gradient correction; its value is reported either way
+        corr = float((residual / self.p_inc).sum())
+        return dict(correction=corr if self.grad else 0.0, correction_metric=corr, exact=exact, aux=aux)

@@ -355,10 +355,8 @@ def unsupported(config: ExperimentConfig) -> list[str]:
         if t.audit_sampler != "fixed_count":
             no("training", "audit_sampler", "only the fixed-count sampler (audit_fixed_count_per_batch); "
                                             "audit_p_max=0 or audit_cap=0 switches audits off")
-        if t.audit_mode != "gradient_corrected":
-            no("training", "audit_mode", "only gradient_corrected")
-        if t.audit_residual_clip is not None:
-            no("training", "audit_residual_clip", "residual clipping is not implemented")
+        if t.audit_mode not in ("gradient_corrected", "metric_only", "distill_only"):
+            no("training", "audit_mode", "one of gradient_corrected, metric_only, distill_only")
         if t.audit_schedule_enabled:
             no("training", "audit_schedule_enabled", "the audit-count schedule is not implemented")
         if t.macro_rms_trust_region or t.macro_rms_clamp_early:

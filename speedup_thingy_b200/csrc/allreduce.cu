@@ -1,12 +1,19 @@
 // In-place sum of a gradient range across the data-parallel ranks of one node, over NVLink peer memory: ONE kernel
-// per rank does the whole exchange with plain peer loads and stores (no multimem, no library collective).
+// per rank does the whole exchange (no multimem, no library collective), and everything that crosses the link is a
+// plain peer STORE -- remote loads pay the link's round trip per request and reached less than half of the stores'
+// bandwidth when this exchange was built on them.
 //
-// Every rank holds device pointers to every rank's copy of the buffer (same layout everywhere) and to every rank's
-// flag array (CUDA IPC mappings made by the caller).  For a range of n floats, rank r owns the r-th of `world` equal
-// parts: it reads that part from all ranks, sums in rank order 0..world-1 (so every rank ends with bit-identical
-// values), and writes the sum back into every rank's buffer.  Two flag exchanges bracket the data phase:
-//   "ready": rank q's range is complete (its earlier kernels are ordered before this one by its stream);
-//   "done" : rank q has finished writing its part into everybody's buffer.
+// Every rank holds device pointers to every rank's gradient buffer, staging buffer (same size and layout) and flag
+// array (CUDA IPC mappings made by the caller).  A range of n floats is cut into `world` equal parts; part q belongs
+// to rank q.
+//   push   : rank r copies its own values of every foreign part q into rank q's staging buffer (row r of the part);
+//            the last of its blocks to finish tells every peer "pushed";
+//   reduce : once all peers have pushed, rank r sums its part in rank order 0..world-1 (its own values from its
+//            buffer, the others' from its staging buffer: local loads), so that every rank ends with bit-identical
+//            values, and stores the sum into every rank's buffer; the last block tells every peer "done" and waits
+//            for theirs (their parts have then landed here).
+// A rank leaves the kernel only after every peer's "done", i.e. after every peer has finished reading its staging
+// buffer and its gradient range, so the next exchange may overwrite both at once.
 // Flags carry an epoch that only grows, so nothing is ever reset; the epoch lives in device memory and is bumped by
 // the kernel itself, which keeps the launch replayable from a CUDA graph.  Every wait is bounded: when it runs out
 // the kernel records a code in the caller's status word and returns (the data is then not reduced).
@@ -21,9 +28,10 @@ constexpr uint32_t SPIN_LIMIT = 1u << 27;      // polls of a flag before a wait 
 
 struct Comm {
   float* buf[RTE_COMM_MAX_RANKS];
+  float* stage[RTE_COMM_MAX_RANKS];            // stage[q]: rank q's staging buffer (as large as buf, plus slack)
   uint32_t* flags[RTE_COMM_MAX_RANKS];         // flags[q]: rank q's array [slots][2][RTE_COMM_MAX_RANKS]
   uint32_t* epoch;                             // this rank's counters [slots]
-  uint32_t* done_count;                        // this rank's block counters [slots]
+  uint32_t* done_count;                        // this rank's block counters [slots][2]
   int world, rank;
 };
 
@@ -48,21 +56,51 @@ __device__ __forceinline__ bool wait_peers(const Comm& c, int slot, int phase, u
   }
   return true;
 }
+__device__ __forceinline__ void tell_peers(const Comm& c, int slot, int phase, uint32_t epoch) {
+  if (threadIdx.x < c.world && threadIdx.x != c.rank)
+    st_flag(c.flags[threadIdx.x] + ((size_t)slot * 2 + phase) * RTE_COMM_MAX_RANKS + c.rank, epoch);
+}
+// True in exactly one block of the grid: the last one to arrive (all threads of the block get the answer).
+__device__ __forceinline__ bool last_block(uint32_t* counter) {
+  __shared__ int last_s;
+  __threadfence_system();
+  __syncthreads();
+  if (threadIdx.x == 0) last_s = (atomicAdd(counter, 1u) == gridDim.x - 1) ? 1 : 0;
+  __syncthreads();
+  return last_s != 0;
+}
 
-// W > 0: the world size as a compile-time constant (the loads of all ranks and of U consecutive strides are issued
-// before the first add, which is what keeps enough bytes in flight for a link whose round trip is microseconds);
-// W == 0: any world size, one element at a time.
-template <int W, int U>
-__device__ __forceinline__ void reduce_part(const Comm& c, long long offset, long long lo, long long hi) {
+// dst[i] = src[i] for i in [0, cnt) float4, U independent 16-byte loads in flight per thread
+template <int U>
+__device__ __forceinline__ void copy_part(float4* __restrict__ dst, const float4* __restrict__ src, long long cnt) {
   const long long stride = (long long)gridDim.x * blockDim.x;
+  long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x;
+  for (; i + (U - 1) * stride < cnt; i += U * stride) {
+    float4 v[U];
+#pragma unroll
+    for (int u = 0; u < U; ++u) v[u] = src[i + u * stride];
+#pragma unroll
+    for (int u = 0; u < U; ++u) dst[i + u * stride] = v[u];
+  }
+  for (; i < cnt; i += stride) dst[i] = src[i];
+}
+
+// W > 0: the world size as a compile-time constant (all loads of U consecutive strides are issued before the first
+// add); W == 0: any world size, one element at a time.
+template <int W, int U>
+__device__ __forceinline__ void reduce_part(const Comm& c, long long offset, long long lo, long long hi, long long per) {
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  const float4* own = reinterpret_cast<const float4*>(c.buf[c.rank] + offset);
+  const float4* st = reinterpret_cast<const float4*>(c.stage[c.rank] + offset);       // row q at st + q * per
   long long i = lo + blockIdx.x * (long long)blockDim.x + threadIdx.x;
   if constexpr (W > 0) {
     for (; i + (U - 1) * stride < hi; i += U * stride) {
-      float4 v[U][W > 0 ? W : 1];
+      float4 v[U][W];
 #pragma unroll
       for (int u = 0; u < U; ++u)
 #pragma unroll
-        for (int q = 0; q < W; ++q) v[u][q] = reinterpret_cast<const float4*>(c.buf[q] + offset)[i + u * stride];
+        for (int q = 0; q < W; ++q)
+          v[u][q] = (q == c.rank) ? own[i + u * stride] : st[q * per + (i + u * stride - lo)];
 #pragma unroll
       for (int u = 0; u < U; ++u) {
         float4 acc = v[u][0];                               // rank order 0..W-1 on every rank: bit-identical sums
@@ -74,9 +112,9 @@ __device__ __forceinline__ void reduce_part(const Comm& c, long long offset, lon
     }
   }
   for (; i < hi; i += stride) {
-    float4 acc = reinterpret_cast<const float4*>(c.buf[0] + offset)[i];
+    float4 acc = (0 == c.rank) ? own[i] : st[i - lo];
     for (int q = 1; q < c.world; ++q) {
-      const float4 v = reinterpret_cast<const float4*>(c.buf[q] + offset)[i];
+      const float4 v = (q == c.rank) ? own[i] : st[q * per + (i - lo)];
       acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
     }
     for (int q = 0; q < c.world; ++q) reinterpret_cast<float4*>(c.buf[q] + offset)[i] = acc;
@@ -91,37 +129,35 @@ allreduce_sum_kernel(Comm c, long long offset, long long n, int slot, int* statu
   if (threadIdx.x == 0) { ok_s = 1; epoch_s = c.epoch[slot] + 1; }
   __syncthreads();
   const uint32_t epoch = epoch_s;
-  // ---- "ready": tell every peer that this rank's range is complete (one block does the telling) ...
-  if (blockIdx.x == 0 && threadIdx.x < c.world && threadIdx.x != c.rank) {
-    __threadfence_system();
-    st_flag(c.flags[threadIdx.x] + ((size_t)slot * 2 + 0) * RTE_COMM_MAX_RANKS + c.rank, epoch);
+  const long long n4 = n / 4;                                   // the caller keeps ranges multiples of 4 floats
+  const long long per = (n4 + c.world - 1) / c.world;           // float4 per part
+  // ---- push: this rank's values of every foreign part go into the owner's staging buffer (row = this rank)
+  for (int k = 1; k < c.world; ++k) {
+    const int q = (c.rank + k) % c.world;                       // every rank starts with another peer
+    const long long lo = (long long)q * per, hi = min(lo + per, n4);
+    if (hi > lo)
+      copy_part<U * 2>(reinterpret_cast<float4*>(c.stage[q] + offset) + (long long)c.rank * per,
+                       reinterpret_cast<const float4*>(c.buf[c.rank] + offset) + lo, hi - lo);
   }
-  // ... and every block waits (on this rank's own memory) until all peers have said the same
+  if (last_block(c.done_count + slot * 2 + 0)) tell_peers(c, slot, 0, epoch);
+  // ---- reduce: wait (on this rank's own memory) until every peer has pushed, then sum this rank's part
   if (threadIdx.x < 32 && !wait_peers(c, slot, 0, epoch)) ok_s = 0;
   __syncthreads();
   if (ok_s) {
-    // ---- this rank's part of the range: sum over ranks in fixed order, result to every rank
-    const long long n4 = n / 4;                                   // the caller keeps ranges multiples of 4 floats
-    const long long per = (n4 + c.world - 1) / c.world;
     const long long lo = (long long)c.rank * per, hi = min(lo + per, n4);
-    reduce_part<W, U>(c, offset, lo, hi);
+    reduce_part<W, U>(c, offset, lo, hi, per);
   }
-  // ---- "done": the last block of this rank to finish tells the peers, waits for theirs, and advances the epoch
-  __threadfence_system();
-  __syncthreads();
-  __shared__ int last_s;
-  if (threadIdx.x == 0) last_s = (atomicAdd(c.done_count + slot, 1u) == gridDim.x - 1) ? 1 : 0;
-  __syncthreads();
-  if (!last_s) {
+  // ---- done: the last block of this rank to finish tells the peers, waits for theirs, and advances the epoch
+  if (!last_block(c.done_count + slot * 2 + 1)) {
     if (!ok_s && threadIdx.x == 0 && status) atomicExch(status, RTE_DEV_WAIT_TIMEOUT_PEER);
     return;
   }
-  if (threadIdx.x < c.world && threadIdx.x != c.rank)
-    st_flag(c.flags[threadIdx.x] + ((size_t)slot * 2 + 1) * RTE_COMM_MAX_RANKS + c.rank, epoch);
+  tell_peers(c, slot, 1, epoch);
   if (threadIdx.x < 32 && !wait_peers(c, slot, 1, epoch)) ok_s = 0;
   __syncthreads();
   if (threadIdx.x == 0) {
-    c.done_count[slot] = 0;
+    c.done_count[slot * 2 + 0] = 0;
+    c.done_count[slot * 2 + 1] = 0;
     c.epoch[slot] = epoch;
     if (!ok_s && status) atomicExch(status, RTE_DEV_WAIT_TIMEOUT_PEER);
   }
@@ -187,9 +223,10 @@ extern "C" int rte_peer_allreduce_sum_f32(const rte_peer_comm* comm, int64_t off
   RTE_CHECK_ARG(comm->epoch != nullptr && comm->done_count != nullptr);
   Comm c;
   for (int q = 0; q < comm->world; ++q) {
-    RTE_CHECK_ARG(comm->buf[q] != nullptr && comm->flags[q] != nullptr);
-    if (reinterpret_cast<uintptr_t>(comm->buf[q]) & 15) return RTE_ERR_ALIGNMENT;
+    RTE_CHECK_ARG(comm->buf[q] != nullptr && comm->stage[q] != nullptr && comm->flags[q] != nullptr);
+    if ((reinterpret_cast<uintptr_t>(comm->buf[q]) | reinterpret_cast<uintptr_t>(comm->stage[q])) & 15) return RTE_ERR_ALIGNMENT;
     c.buf[q] = comm->buf[q];
+    c.stage[q] = comm->stage[q];
     c.flags[q] = comm->flags[q];
   }
   c.epoch = comm->epoch; c.done_count = comm->done_count; c.world = comm->world; c.rank = comm->rank;

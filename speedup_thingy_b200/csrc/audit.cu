@@ -274,9 +274,55 @@ __global__ void add_rows_f32_to_bf16_kernel(__nv_bfloat16* __restrict__ dst, int
   }
 }
 
+// Residual clip of the control variate (audit.py:306-321): corrected = hot + clamp(exact - hot, -c, c) / p.  Inside the
+// clip the derivative is (1 - 1/p) on the hot loss and 1/p on the exact loss; outside it is 1 and 0.  The two cross-entropy
+// launches have already written their gradients with the weights 1 (hot) and 1/p (exact), so the factors are
+//   f_hot = inside ? 1 - 1/p : 1,   f_exact = inside ? 1 : 0.
+__global__ void audit_clip_kernel(const float* __restrict__ hot_loss, const float* __restrict__ exact_loss,
+                                  const int32_t* __restrict__ idx, int n, float inv_p, float clip,
+                                  float* __restrict__ f_hot, float* __restrict__ f_exact) {
+  const int j = blockIdx.x * blockDim.x + threadIdx.x;
+  if (j >= n) return;
+  const float r = exact_loss[j] - hot_loss[idx[j]];
+  const bool inside = fabsf(r) <= clip;             // (a NaN residual counts as clipped: no gradient through it)
+  f_hot[j] = inside ? 1.f - inv_p : 1.f;
+  f_exact[j] = inside ? 1.f : 0.f;
+}
+
+// x[(row_of(r)) * ld + c] *= scale[r / S]  with row_of(r) = idx ? idx[r / S] * S + r % S : r   (bf16, one rounding)
+__global__ void scale_rows_bf16_kernel(__nv_bfloat16* __restrict__ x, int ld, const int32_t* __restrict__ idx, int S,
+                                       const float* __restrict__ scale, int rows, int V) {
+  const long long total = (long long)rows * V;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+    const int row = int(i / V), c = int(i % V);
+    const float f = scale[row / S];
+    if (f == 1.f) continue;
+    const size_t phys = idx ? (size_t)idx[row / S] * S + (row % S) : (size_t)row;
+    __nv_bfloat16* q = x + phys * ld + c;
+    *q = __float2bfloat16_rn(__bfloat162float(*q) * f);
+  }
+}
+
 }  // namespace
 
 #define ST(s) reinterpret_cast<cudaStream_t>(s)
+
+extern "C" int rte_audit_clip(const float* hot_loss, const float* exact_loss, const int32_t* idx, int32_t n, float inv_p,
+                              float clip, float* f_hot, float* f_exact, rte_stream_t stream) {
+  RTE_CHECK_ARG(hot_loss && exact_loss && idx && f_hot && f_exact && n > 0 && clip >= 0.f);
+  audit_clip_kernel<<<rte::ceil_div(n, 128), 128, 0, ST(stream)>>>(hot_loss, exact_loss, idx, n, inv_p, clip, f_hot, f_exact);
+  RTE_LAUNCH_CHECK();
+  return RTE_OK;
+}
+
+extern "C" int rte_scale_rows_bf16(void* x_bf16, int32_t ld, const int32_t* idx, int32_t S, const float* scale, int32_t rows,
+                                   int32_t V, rte_stream_t stream) {
+  RTE_CHECK_ARG(x_bf16 && scale && S > 0 && rows > 0 && V > 0 && ld >= V);
+  scale_rows_bf16_kernel<<<grid_for((long long)rows * V, NTHR), NTHR, 0, ST(stream)>>>(
+      reinterpret_cast<__nv_bfloat16*>(x_bf16), ld, idx, S, scale, rows, V);
+  RTE_LAUNCH_CHECK();
+  return RTE_OK;
+}
 
 extern "C" int rte_gather_rows(const void* src, const int32_t* idx, void* dst, int32_t n, int64_t row_bytes, rte_stream_t stream) {
   RTE_CHECK_ARG(src && idx && dst && n > 0 && row_bytes > 0);

@@ -172,6 +172,7 @@ def teardown_data_parallel(engine: "TrainEngine | None", watchdog_s: float = 30.
         engine._peer.close()              # every rank is past its last exchange: unmap the peers' memory ...
         dist.barrier()
         engine._peer.flag_mem.free()      # ... and only then release what the peers had mapped
+        engine._peer.stage_mem.free()
         engine._grad_mem.free()           # (the engine's gradient views dangle from here on: it is closed)
         engine._peer = engine._grad_mem = None
     sys.stdout.flush()
@@ -276,6 +277,9 @@ class TrainEngine:
         self.n_clusters = self.oc.num_clusters
         self.exact = tr.mode == "recursive_exact"       # every sample runs the banked recurrent core (training.py:771-797)
         self.audit_k = int(tr.audit_fixed_count_per_batch or 0) if tr.audits_enabled else 0
+        # audit_mode "metric_only" / "distill_only" run the exact subset without gradients (audit.py:295-298): the replay
+        # stops after its forward, the control variate leaves the loss, only the distillation terms reach the hot pass
+        self.audit_grad = bool(self.audit_k) and tr.audit_mode == "gradient_corrected"
         if self.exact and (self.audit_k or self.dense):
             raise ValueError("recursive_exact: recursive topology, no audit (the whole batch is exact)")
         if self.audit_k:
@@ -305,7 +309,7 @@ class TrainEngine:
             self.trainable = [n for n in names if n.startswith(used)]
             if not tr.disable_router_aux:
                 self.trainable += [n for n in names if n.startswith(("router.recipe_mlp.", "router.depth_mlp."))]
-            if self.audit_k or self.exact:
+            if self.audit_grad or self.exact:
                 from .audit import CORE_PARAMS
                 self.trainable += CORE_PARAMS
         # gradients live in one flat buffer, laid out in the order the backward pass completes them, so that
@@ -325,8 +329,9 @@ class TrainEngine:
                      and hasattr(ops, "lib"))
         if peer_comm:
             from .peer_comm import PeerMemory
-            self._grad_mem = PeerMemory(ops, max(total, 64) * 4)
-            self.grad_flat = self._grad_mem.tensor(f32)
+            # (128 more floats behind the gradients: the small vectors the step exchanges besides them)
+            self._grad_mem = PeerMemory(ops, (max(total, 64) + 128) * 4)
+            self.grad_flat = self._grad_mem.tensor(f32)[:max(total, 64)]
         else:
             self.grad_flat = torch.zeros(max(total, 64), dtype=f32, device=dev)
         self.grads = {n: self.grad_flat[offsets[n]: offsets[n] + self.params[n].numel()].view(self.params[n].shape)
@@ -335,10 +340,11 @@ class TrainEngine:
         self._bucket_of: dict[str, int] = {}
         self._bucket_pending: list[int] = []
         self._bucket_size: list[int] = []
-        # Bucket size: 25 MB (the usual data-parallel default) for large models, but never fewer than about eight
-        # buckets per step: the LAST bucket's exchange cannot hide behind backward, so it has to be a small share.
+        # Bucket size: 25 MB.  With an audited sample every bucket becomes complete only near the end of backward (the
+        # replay contributes late to all of them), so the exchange is mostly exposed and few large exchanges beat many
+        # small ones (2 ranks, c3: 25 MB 1.93 ms per step, 7 MB 2.16 ms, 2 MB 2.29 ms).  RTE_BUCKET_MB overrides.
         if bucket_cap_mb is None:
-            bucket_cap_mb = float(os.environ.get("RTE_BUCKET_MB", min(25.0, max(total * 4 / 2 ** 20 / 8.0, 1.0))))
+            bucket_cap_mb = float(os.environ.get("RTE_BUCKET_MB", 25.0))
         self.bucket_cap_mb = float(bucket_cap_mb)
         cap = max(int(bucket_cap_mb * 1024 * 1024 / 4), 1)
         start = 0
@@ -350,7 +356,10 @@ class TrainEngine:
                 self._buckets.append((offsets[n], end))
             self._bucket_of[n] = len(self._buckets) - 1
         self._bucket_size = [sum(1 for n in order if self._bucket_of[n] == i) for i in range(len(self._buckets))]
-        self._comm_stream = torch.cuda.Stream(device=dev) if (self.world > 1 and dev.type == "cuda") else None
+        # (high priority: an exchange is short, sits on the step's critical path once backward has finished, and all of
+        # its blocks must have run before it can tell the peers anything)
+        comm_prio = int(os.environ.get("RTE_COMM_PRIORITY", "-1"))
+        self._comm_stream = torch.cuda.Stream(device=dev, priority=comm_prio) if (self.world > 1 and dev.type == "cuda") else None
         if peer_comm:
             from .peer_comm import PeerAllReduce
             self._peer = PeerAllReduce(ops, self._grad_mem, process_group)
@@ -450,6 +459,9 @@ class TrainEngine:
                               depth_id=e(B, dtype=i32), depth=e(B, dtype=i32))
             self.router_scratch = e(A.ROUTER_MAX_R + B * (2 * hid + r + k + A.ROUTER_DPOOLED_PARTS * d) + 4)
             self._mean_prob = torch.zeros(A.ROUTER_MAX_R, dtype=f32, device=dev)
+            if self._grad_mem is not None:              # exchanged by the peer kernel: lives in the shared allocation
+                self._mean_prob_lo = self.grad_flat.numel() + 32         # (clear of the last bucket's staging overhang)
+                self._mean_prob = self._grad_mem.tensor(f32)[self._mean_prob_lo:self._mean_prob_lo + A.ROUTER_MAX_R]
         if self.shortlist:
             oc, i32 = self.oc, torch.int32
             if "shortlist_head.cluster_router.weight" not in self.params:
@@ -513,7 +525,7 @@ class TrainEngine:
                 order += block(f"coda.{i}")
             if not self.exact:
                 order += ["macro.d_gain", "macro.v", "macro.u", "macro.bias"]
-            if self.audit_k or self.exact:
+            if self.audit_grad or self.exact:
                 from .audit import CORE_PARAMS
                 order += CORE_PARAMS
             if not self.tr.disable_router_aux:
@@ -558,7 +570,7 @@ class TrainEngine:
                             e0 = torch.cuda.Event(enable_timing=True, external=True)
                             e0.record(self._comm_stream)
                         if self._peer is not None:
-                            self._peer.all_reduce_(lo, hi, slot=i)
+                            self._peer.all_reduce_(lo, hi, slot=i % (A.COMM_MAX_SLOTS - 1))     # the last slot: the router's vector
                         else:
                             dist.all_reduce(view, op=dist.ReduceOp.SUM, group=self.pg)
                         if probes is not None:
@@ -574,7 +586,10 @@ class TrainEngine:
         import torch.distributed as dist
         R = self.cfg.recipe_count
         self.ops.router_mean_prob(self.route["recipe_probs"], self._mean_prob, 1.0 / (self.B * self.world), B=self.B, R=R)
-        dist.all_reduce(self._mean_prob, op=dist.ReduceOp.SUM, group=self.pg)
+        if self._peer is not None:
+            self._peer.all_reduce_(self._mean_prob_lo, self._mean_prob_lo + A.ROUTER_MAX_R, slot=A.COMM_MAX_SLOTS - 1)
+        else:
+            dist.all_reduce(self._mean_prob, op=dist.ReduceOp.SUM, group=self.pg)
         return self._mean_prob
 
     def _finish_backward(self) -> None:
@@ -882,20 +897,36 @@ class TrainEngine:
                     kl_done = self._side_event()
             # join: the hot backward needs the distillation gradients (KL rows of dlogits, endpoint terms), not the
             # replay's own cross entropy, which starts the replay's backward on its stream
+            a = self.audit
             self._main_wait_side(kl_done)
-            self.audit.add_kl_grad()
+            clip = a.grad and a.clip is not None
+            if clip:
+                self._side_wait_main()            # the clip decision reads the hot pass's per-sample losses
+            else:
+                a.add_kl_grad()
+            clip_done = None
             with self._on_side():
                 probes = getattr(self, "_join_probes", None)
                 if probes is not None:
                     s0 = torch.cuda.Event(enable_timing=True, external=True)
                     s0.record(torch.cuda.current_stream(self.device))
-                self.audit.forward_ce()
-                self.audit_dh_exact = self.audit.backward_head()
-                self.audit.backward_core(self.audit_dh_exact)
+                a.forward_ce()
+                if clip:
+                    a.clip_exact()
+                    clip_done = self._side_event()
+                if a.grad:
+                    self.audit_dh_exact = a.backward_head()
+                    a.backward_core(self.audit_dh_exact)
                 if probes is not None:
                     s1 = torch.cuda.Event(enable_timing=True, external=True)
                     s1.record(torch.cuda.current_stream(self.device))
                     probes.append((s0, s1))
+            if clip:
+                # residual clip: both cross-entropy launches wrote unit-weight gradients; the audited rows of the hot
+                # dlogits get their factor now that the exact losses exist (then the KL rows, which it must not touch)
+                self._main_wait_side(clip_done)
+                a.clip_hot()
+                a.add_kl_grad()
         # ---------------- backward
         self._begin_backward()
         dlogits = self.logits
@@ -911,7 +942,7 @@ class TrainEngine:
         defer(True)
         o.rmsnorm_bwd(x_last, p["final_norm.weight"], self.rstd_f, self.dn16, None, self.dxa, g16[0],
                       g["final_norm.weight"], self.partial_final)
-        audited = self.audit is not None
+        audited = self.audit is not None and self.audit.grad       # the replay contributes gradients of its own
         if not audited:
             self._grad_ready("final_norm.weight")
         dcur, dalt = self.dxa, self.dxb
@@ -926,7 +957,7 @@ class TrainEngine:
             # the coda's weight gradients are queued: the replay adds its share to them once this point has passed
             hot_w_done = torch.cuda.Event()
             hot_w_done.record(hot if hot is not None else torch.cuda.current_stream(self.device))
-        if audited:
+        if self.audit is not None:
             # distillation gradient on the hot endpoint of the audited samples, then the replay's own
             # logits / final-norm / coda backward (their weight gradients add to the hot pass's)
             o.scatter_add_rows(dcur, self.audit.idx, self.audit.dhot_extra, self.audit.n, S * d)
@@ -1008,6 +1039,8 @@ class TrainEngine:
                 self._grad_ready(f"{pre}.mlp.wd.weight", f"{pre}.mlp.wug.weight", f"{pre}.norm2.weight",
                                  f"{pre}.attn.wo.weight", f"{pre}.attn.wqkv.weight", f"{pre}.norm1.weight")
         self._grad_ready("embed.weight")
+        if self.audit is not None and not audited:
+            self._main_wait_side(self._side_event())          # the replay's forward results are part of the step's results
         if hot is not None:
             torch.cuda.current_stream(self.device).wait_stream(hot)
             if self._misc_param_stream is not None:

@@ -486,6 +486,15 @@ class CudaOps:
         self._call("rte_add_rows_f32_to_bf16", _ptr(dst_bf16), dst_bf16.stride(0), _ptr(idx), S, _ptr(src_f32), rows, V,
                    self.stream)
 
+    def audit_clip(self, hot_loss, exact_loss, idx, n: int, inv_p: float, clip: float, f_hot, f_exact) -> None:
+        self._call("rte_audit_clip", _ptr(hot_loss), _ptr(exact_loss), _ptr(idx), n, float(inv_p), float(clip), _ptr(f_hot),
+                   _ptr(f_exact), self.stream)
+
+    def scale_rows_bf16(self, x_bf16, idx, S: int, scale, rows: int, V: int) -> None:
+        """x[rows of the samples idx (or the first rows // S samples), :V] *= scale[sample]."""
+        self._call("rte_scale_rows_bf16", _ptr(x_bf16), x_bf16.stride(0), _ptr(idx) if idx is not None else None, S, _ptr(scale),
+                   rows, V, self.stream)
+
     # ------------------------------------------------------------------ cluster-pool FFN helpers
     def cluster_route(self, q, centers, assignments, scores=None) -> None:
         n, W = q.shape

@@ -1,15 +1,16 @@
 """Gradient exchange of the data-parallel step over NVLink peer memory.
 
 One process per GPU on one node.  Every rank allocates its gradient buffer and a small flag array through the
-library (``rte_peer_alloc``: plain device allocations with an inter-process handle), sends the two 64-byte handles to
-the other ranks over the existing process group, and maps theirs with its own device current (``rte_peer_open``).
-From then on a bucket is summed across ranks by ONE kernel per rank (``rte_peer_allreduce_sum_f32``: plain peer loads
-and stores, sums in rank order, bounded waits) instead of a library collective.  The kernel takes no host-side state
+library (``rte_peer_alloc``: plain device allocations with an inter-process handle), plus a staging buffer of the
+same size, sends the 64-byte handles to the other ranks over the existing process group, and maps theirs with its own
+device current (``rte_peer_open``).  From then on a bucket is summed across ranks by ONE kernel per rank
+(``rte_peer_allreduce_sum_f32``: plain peer stores, sums in rank order, bounded waits) instead of a library collective.  The kernel takes no host-side state
 per call, so it can be captured into the step's CUDA graph.
 """
 from __future__ import annotations
 
 import ctypes as C
+import os
 
 import torch
 
@@ -61,22 +62,24 @@ class PeerAllReduce:
             raise ValueError(f"PeerAllReduce handles 2..{A.COMM_MAX_RANKS} ranks of one node")
         dev = ops.device
         self.flag_mem = PeerMemory(ops, A.COMM_MAX_SLOTS * 2 * A.COMM_MAX_RANKS * 4)
+        # where the peers push their values of this rank's parts (a part's row may overhang a range by 4 * ranks floats)
+        self.stage_mem = PeerMemory(ops, buffer_mem.nbytes + 4 * A.COMM_MAX_RANKS * 4)
         self.epoch = torch.zeros(A.COMM_MAX_SLOTS, dtype=torch.int32, device=dev)
-        self.done_count = torch.zeros(A.COMM_MAX_SLOTS, dtype=torch.int32, device=dev)
+        self.done_count = torch.zeros(A.COMM_MAX_SLOTS * 2, dtype=torch.int32, device=dev)
         torch.cuda.synchronize(dev)
-        mine = (buffer_mem.handle, self.flag_mem.handle, buffer_mem.nbytes, int(dev.index or 0))
+        mine = (buffer_mem.handle, self.stage_mem.handle, self.flag_mem.handle, buffer_mem.nbytes, int(dev.index or 0))
         gathered: list = [None] * self.world
         dist.all_gather_object(gathered, mine, group=process_group)
         self._mapped: list[int] = []               # peers' allocations mapped into this process
         comm = A.PeerComm()
         with torch.cuda.device(dev):               # the mappings must be opened with THIS rank's device current
-            for q, (buf_h, flag_h, nbytes, owner_dev) in enumerate(gathered):
+            for q, (buf_h, stage_h, flag_h, nbytes, owner_dev) in enumerate(gathered):
                 if nbytes != buffer_mem.nbytes:
                     raise ValueError("every rank's gradient buffer must have the same size")
                 if q == self.rank:
-                    comm.buf[q], comm.flags[q] = buffer_mem.ptr, self.flag_mem.ptr
+                    comm.buf[q], comm.stage[q], comm.flags[q] = buffer_mem.ptr, self.stage_mem.ptr, self.flag_mem.ptr
                     continue
-                for h, field in ((buf_h, comm.buf), (flag_h, comm.flags)):
+                for h, field in ((buf_h, comm.buf), (stage_h, comm.stage), (flag_h, comm.flags)):
                     p = A.c_vp()
                     A.check(ops.lib.rte_peer_open(h, owner_dev, C.byref(p)), "rte_peer_open")
                     self._mapped.append(int(p.value))
@@ -85,7 +88,7 @@ class PeerAllReduce:
         comm.world, comm.rank = self.world, self.rank
         self._comm = comm
         dist.barrier(group=process_group)          # everybody has mapped everybody before the first exchange
-        self.max_ctas = 64
+        self.max_ctas = int(os.environ.get("RTE_PEER_CTAS", "64"))      # CTAs of one exchange (the rest of the SMs keep computing)
 
     def all_reduce_(self, lo: int, hi: int, slot: int) -> None:
         """buffer[lo:hi] <- sum over ranks, in place, on the current stream.  Every rank must issue the same calls in

@@ -530,6 +530,21 @@ class EmulOps:
         tgt = (idx[:n].long()[:, None] * S + torch.arange(S)[None, :]).reshape(-1)
         dst_bf16[tgt, :V] = (dst_bf16[tgt, :V].float() + src_f32.view(rows, V)).to(torch.bfloat16)
 
+    def audit_clip(self, hot_loss, exact_loss, idx, n, inv_p, clip, f_hot, f_exact):
+        self.launches += 1
+        r = exact_loss[:n] - hot_loss[idx[:n].long()]
+        inside = r.abs() <= clip
+        f_hot[:n] = torch.where(inside, torch.full_like(r, 1.0 - inv_p), torch.ones_like(r))
+        f_exact[:n] = inside.float()
+
+    def scale_rows_bf16(self, x_bf16, idx, S, scale, rows, V):
+        self.launches += 1
+        n = rows // S
+        base = idx[:n].long() if idx is not None else torch.arange(n)
+        tgt = (base[:, None] * S + torch.arange(S)[None, :]).reshape(-1)
+        f = scale[:n].repeat_interleave(S)[:, None]
+        x_bf16[tgt, :V] = (x_bf16[tgt, :V].float() * f).to(torch.bfloat16)
+
     # ---------------------------------------------------------------- small vector ops
     def cast_bf16(self, src, dst):
         self.launches += 1

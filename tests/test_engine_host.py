@@ -27,6 +27,18 @@ CASES = {
              recipe_count=6, macro_rank=8),
         dict(mode="recursive_macro", lr=2e-3, weight_decay=0.1, batch_size=4, seq_len=16, seed=3, fixed_depth=None,
              audit_fixed_count_per_batch=2, grad_clip_norm=1.0)),
+    "macro_audit_residual_clip": (        # clip chosen so that some audited residuals fall inside and some outside
+        dict(vocab_size=96, d_model=64, n_heads=4, d_ff=128, n_prelude=1, n_coda=1, t_max=4, depth_choices=(1, 2, 4),
+             attn_banks=1, ffn_banks=1, head_groups=4, ffn_groups=4, active_head_groups=2, active_ffn_groups=2,
+             recipe_count=5, macro_rank=8),
+        dict(mode="recursive_macro", lr=2e-3, weight_decay=0.1, batch_size=6, seq_len=16, seed=13, fixed_depth=None,
+             audit_fixed_count_per_batch=4, audit_residual_clip=0.15, grad_clip_norm=1.0)),
+    "macro_audit_metric_only": (
+        dict(vocab_size=96, d_model=64, n_heads=4, d_ff=128, n_prelude=1, n_coda=1, t_max=4, depth_choices=(1, 2, 4),
+             attn_banks=1, ffn_banks=1, head_groups=4, ffn_groups=4, active_head_groups=2, active_ffn_groups=2,
+             recipe_count=5, macro_rank=8),
+        dict(mode="recursive_macro", lr=2e-3, weight_decay=0.1, batch_size=4, seq_len=16, seed=17, fixed_depth=None,
+             audit_fixed_count_per_batch=2, audit_mode="metric_only", audit_gradient_correction=False)),
     "macro_shortlist": (
         dict(vocab_size=96, d_model=64, n_heads=4, d_ff=128, n_prelude=1, n_coda=1, t_max=4, depth_choices=(1, 2, 4),
              attn_banks=1, ffn_banks=1, head_groups=4, ffn_groups=4, active_head_groups=2, active_ffn_groups=2,
@@ -51,7 +63,7 @@ def _pair(name):
     out = rest[0] if rest else {}
     cfg = ExperimentConfig(ModelConfig(**m), TrainingConfig(**t), OutputConfig(**out))
     ocfg = O.ModelCfg(**m, shortlist_clusters=cfg.output.num_clusters)
-    otr = O.TrainCfg(**{k: v for k, v in t.items()})
+    otr = O.TrainCfg(**{k: v for k, v in t.items() if k in O.TrainCfg.__dataclass_fields__})
     return cfg, ocfg, otr
 
 

@@ -750,3 +750,28 @@ def test_audit_mask_and_residual_helpers(ops):
                             frozen_active=act.to(DEV), frozen_src=src2.to(DEV))
     torch.cuda.synchronize()
     _close(dbase2, dout + torch.where(on, zero, src2), 1e-6, "d base with hand-through")
+
+
+def test_audit_residual_clip_factors_and_row_scaling(ops):
+    """rte_audit_clip / rte_scale_rows_bf16 against their definitions (audit.py:306-321): factors 1 - 1/p and 1 inside the
+    clip, 1 and 0 outside; rows scaled through the sample index or in place order; untouched rows stay bit-identical."""
+    from tests.emul_ops import EmulOps
+    g = torch.Generator().manual_seed(5)
+    B, n, S, V = 12, 5, 8, 72
+    hot, exact = torch.randn(B, generator=g) + 40, torch.randn(n, generator=g) + 40
+    idx = torch.tensor([1, 4, 6, 7, 11], dtype=torch.int32)
+    exact[2] = hot[6] + 0.01                         # well inside
+    f_hot, f_exact = torch.zeros(n, device=DEV), torch.zeros(n, device=DEV)
+    ops.audit_clip(hot.to(DEV), exact.to(DEV), idx.to(DEV), n, 1.0 / 0.25, 0.5, f_hot, f_exact)
+    r_hot, r_exact = torch.zeros(n), torch.zeros(n)
+    EmulOps().audit_clip(hot, exact, idx, n, 1.0 / 0.25, 0.5, r_hot, r_exact)
+    torch.cuda.synchronize()
+    assert torch.equal(f_hot.cpu(), r_hot) and torch.equal(f_exact.cpu(), r_exact)
+    assert r_exact[2] == 1.0 and r_hot[2] == -3.0 and set(r_exact.tolist()) == {0.0, 1.0}
+    x = _bf(torch.randn(B * S, V + 8, generator=g))
+    for use_idx in (True, False):
+        got, want = x.clone().to(DEV), x.clone()
+        ops.scale_rows_bf16(got, idx.to(DEV) if use_idx else None, S, f_hot, n * S, V)
+        EmulOps().scale_rows_bf16(want, idx if use_idx else None, S, r_hot, n * S, V)
+        torch.cuda.synchronize()
+        assert torch.equal(got.cpu(), want)

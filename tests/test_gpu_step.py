@@ -35,7 +35,8 @@ def test_first_step_loss_and_grads_match_oracle(name):
     model, train, *rest = CASES[name]
     cfg, params, eng = _engine(model, train, *rest, use_cuda_graph=False)
     _, ocfg, _ = _pair(name)
-    oracle = _oracle(cfg, ocfg, O.TrainCfg(**{**train, "grad_clip_norm": None}), params)
+    okeys = O.TrainCfg.__dataclass_fields__
+    oracle = _oracle(cfg, ocfg, O.TrainCfg(**{**{k: v for k, v in train.items() if k in okeys}, "grad_clip_norm": None}), params)
     batch = next(_stream(cfg, 2))
     loss, grads = eng.loss_and_grads(batch)
     _share_top_clusters(eng, oracle)
