@@ -340,6 +340,11 @@ class AuditReplay:
             dcur, dalt = dalt, dcur
             in16, out16 = out16, in16
         self._defer_param_grads(False)
+        # the head's weight gradients are queued: `merge_head` may add them to the hot pass's from here on
+        self.head_w_done = None
+        if eng._param_stream is not None and eng.device.type == "cuda":
+            self.head_w_done = torch.cuda.Event()
+            self.head_w_done.record(eng._param_stream)
         return dcur
 
     def _defer_param_grads(self, on: bool) -> None:
@@ -424,10 +429,28 @@ class AuditReplay:
         o.segment_sum(self.part_attn, g["core.pass_attn_scale"], T, P)
         o.segment_sum(self.part_alpha, g["core.alpha_inj"].view(1), 1, T * P)
 
-    def finish_core(self, hot_w_done):
-        """What completes the core / coda / final-norm gradients once the data-gradient chain has left the core: the
-        scalar-parameter sums and the add of the replay's share into the hot pass's coda gradients.  Neither feeds the
-        chain, so both go to the replay's weight-gradient stream (behind its weight-gradient GEMMs) and the chain
+    def merge_head(self, hot_w_done):
+        """Adds the replay's share of the final-norm / coda gradients to the hot pass's as soon as both exist -- the
+        replay's head backward is the first thing its backward does, the hot pass's coda backward the first thing of
+        its own -- on a stream of its own, so that these gradients are final (and their bucket can leave) while the
+        replay is still inside the core.  Returns the event that marks them final (None: single-stream order)."""
+        eng = self.eng
+        ms = getattr(eng, "_merge_stream", None)
+        if ms is None or self.head_w_done is None:
+            return None
+        ms.wait_event(self.head_w_done)
+        if hot_w_done is not None:
+            ms.wait_event(hot_w_done)
+        with torch.cuda.stream(ms):
+            self.merge_shared()
+            ev = torch.cuda.Event()
+            ev.record(ms)
+        return ev
+
+    def finish_core(self, head_done, hot_w_done=None):
+        """What completes the core gradients once the data-gradient chain has left the core: the scalar-parameter sums
+        (and, without a merge stream, the add of the replay's share into the hot pass's coda gradients).  Neither feeds
+        the chain, so both go to the replay's weight-gradient stream (behind its weight-gradient GEMMs) and the chain
         carries on with the prelude at once.  Returns the event that marks those gradients final."""
         eng = self.eng
         ps = eng._param_stream
@@ -436,11 +459,14 @@ class AuditReplay:
             self.merge_shared()
             return eng._side_event()
         ps.wait_stream(torch.cuda.current_stream(eng.device))
-        if hot_w_done is not None:
-            ps.wait_event(hot_w_done)
         with torch.cuda.stream(ps):
             self._scalar_grads()
-            self.merge_shared()
+            if head_done is None:
+                if hot_w_done is not None:
+                    ps.wait_event(hot_w_done)
+                self.merge_shared()
+            else:
+                ps.wait_event(head_done)        # whoever waits for the core's gradients has the head's as well
             ev = torch.cuda.Event()
             ev.record(ps)
         return ev

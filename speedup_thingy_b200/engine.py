@@ -348,9 +348,19 @@ class TrainEngine:
         self.bucket_cap_mb = float(bucket_cap_mb)
         cap = max(int(bucket_cap_mb * 1024 * 1024 / 4), 1)
         start = 0
+        # With an audited sample the gradients become final in three groups -- coda / final norm / macro operator once
+        # the replay's head backward has been merged, the recurrent core (and router) when the replay leaves the core,
+        # prelude and embedding at the last join -- so a bucket never straddles two of them.
+        def ready_group(name: str) -> int:
+            if not self.audit_grad:
+                return 0
+            return 1 if name.startswith(("core.", "router.")) else 2 if name.startswith(("prelude.", "embed.")) else 0
+
+        prev_group = None
         for n in order:
             end = offsets[n] + -(-self.params[n].numel() // 64) * 64
-            if self._buckets and end - self._buckets[-1][0] <= cap:
+            same_group, prev_group = ready_group(n) == prev_group, ready_group(n)
+            if self._buckets and same_group and end - self._buckets[-1][0] <= cap:
                 self._buckets[-1] = (self._buckets[-1][0], end)
             else:
                 self._buckets.append((offsets[n], end))
@@ -482,6 +492,7 @@ class TrainEngine:
         if self._side_stream is not None and hasattr(ops, "gemm_max_ctas"):
             ops.gemm_max_ctas = max(ops.sm_count - int(os.environ.get("RTE_SIDE_SMS", "8")), 1)
         self._param_stream = torch.cuda.Stream(device=dev) if (self.audit_k and dev.type == "cuda") else None
+        self._merge_stream = torch.cuda.Stream(device=dev) if (self.audit_k and dev.type == "cuda") else None
         self.exact_core = None
         if self.exact:
             from .audit import AuditReplay
@@ -984,9 +995,11 @@ class TrainEngine:
                 # The replay's backward ran beside the hot backward.  On ITS stream: once the hot pass's coda weight
                 # gradients are in place it adds its share of the shared gradients, then (own_prelude) carries its
                 # d h0 rows through the prelude itself.  The hot pass only waits where it needs a result.
+                head_done = None
                 with self._on_side():
                     if self.audit.own_prelude:
-                        core_done = self.audit.finish_core(hot_w_done)
+                        head_done = self.audit.merge_head(hot_w_done)
+                        core_done = self.audit.finish_core(head_done, hot_w_done)
                         self.audit.backward_prelude()
                     else:
                         if hot_w_done is not None:
@@ -1002,7 +1015,13 @@ class TrainEngine:
                     pre = blk.prefix
                     names += [f"{pre}.mlp.wd.weight", f"{pre}.mlp.wug.weight", f"{pre}.norm2.weight",
                               f"{pre}.attn.wo.weight", f"{pre}.attn.wqkv.weight", f"{pre}.norm1.weight"]
-                self._grad_ready(*names, *CORE_PARAMS, after=core_done)
+                if head_done is not None:
+                    # coda and final norm are final as soon as the replay's head backward has been merged: their bucket
+                    # leaves while the replay is still inside the core
+                    self._grad_ready(*names, after=head_done)
+                    self._grad_ready(*CORE_PARAMS, after=core_done)
+                else:
+                    self._grad_ready(*names, *CORE_PARAMS, after=core_done)
             if not tr.disable_router_aux:
                 # under data parallelism each rank contributes 1/world of the auxiliary losses' gradient on its own
                 # samples, with the load-balance term's batch mean taken over ALL shards (`_global_mean_prob`)
