@@ -281,6 +281,23 @@ int rte_macro_phi_bwd(const float* h0, const float* dout, const rte_phi_params* 
                       const float* act, float* dh0, const rte_phi_grads* g, float* scratch, int32_t B,
                       int32_t S, int32_t d, int32_t m, int32_t R, int32_t K_strides, float eps,
                       rte_stream_t stream);
+/* Phi applied to a state h that is NOT the injected h0 (macro.py:201-236 with h != h0; the second application inside
+ * MacroOperators.consistency_loss, macro.py:342-359): same buffers as above, `h` drives the norm, the pooled mean, the
+ * gain and the residual term, `h0` only the third slice of z.  Backward: dh is overwritten, dh0 is ACCUMULATED into
+ * (dh != dh0), parameter gradients as in rte_macro_phi_bwd (full tensors, overwritten).                            */
+int rte_macro_phi_fwd_hx(const float* h, const float* h0, const rte_phi_params* p, const int32_t* recipe_id,
+                         const int32_t* stride_id, float s_cfg, float* out, float* rstd, float* pooled,
+                         float* act, int32_t B, int32_t S, int32_t d, int32_t m, int32_t K_strides,
+                         float eps, rte_stream_t stream);
+int rte_macro_phi_bwd_hx(const float* h, const float* h0, const float* dout, const rte_phi_params* p,
+                         const int32_t* recipe_id, const int32_t* stride_id, float s_cfg, const float* rstd,
+                         const float* pooled, const float* act, float* dh, float* dh0, const rte_phi_grads* g,
+                         float* scratch, int32_t B, int32_t S, int32_t d, int32_t m, int32_t R, int32_t K_strides,
+                         rte_stream_t stream);
+/* Mean-squared-error pieces of the consistency term (F.mse_loss, macro.py:359): g = coef * (a - b) and
+ * sum_out (+)= sum (a - b)^2, summed in a fixed order.  `partial`: scratch of >= 1024 floats.                       */
+int rte_sqdiff_grad(const float* a, const float* b, int64_t n, float coef, float* g, float* partial, float* sum_out,
+                    int32_t accumulate, rte_stream_t stream);
 /* The same backward in two halves, so that a caller can put the parameter gradients on another stream: _data
  * computes dh0 (what the rest of backward waits for) and leaves its intermediates in `scratch`; _params (ordered
  * after _data, same `scratch`) reduces the per-sample parameter gradients per (recipe, stride) key.             */

@@ -93,6 +93,7 @@ class TrainCfg:
     lambda_delta_rms: float = 2.0
     lambda_endpoint_normed: float = 1.0
     lambda_endpoint_raw: float = 0.05
+    lambda_cons: float = 0.0                        # (the reference's default is 1e-3; the BASELINE workloads use 0)
     distill_temperature: float = 2.0
     coverage_min: float = 0.01
     coverage_beta: float = 0.98
@@ -415,6 +416,23 @@ def macro_phi(p: dict, cfg: ModelCfg, h: torch.Tensor, h0: torch.Tensor, recipe_
     return h + cfg.macro_update_scale * scale.unsqueeze(1) * torch.tanh(update)
 
 
+def macro_consistency_loss(p: dict, cfg: ModelCfg, h0: torch.Tensor, recipe_ids: torch.Tensor) -> torch.Tensor:
+    """macro.py:342-359 as audit.py:370-379 calls it (h = h0): for every stride k of the depth choices whose double 2k
+    is a depth choice too, mse( Phi_2k(h0, h0),  Phi_k(Phi_k(h0, h0), h0) ) over the pairs stacked along the batch."""
+    strides = list(cfg.depth_choices)
+    pairs = [(i, strides.index(s * 2)) for i, s in enumerate(strides) if s * 2 in strides]       # macro.py:126
+    if not pairs:
+        return h0.new_zeros(())
+    b = h0.shape[0]
+    h_rep = h0.unsqueeze(0).expand(len(pairs), *h0.shape).reshape(len(pairs) * b, *h0.shape[1:])
+    rid = recipe_ids.unsqueeze(0).expand(len(pairs), b).reshape(-1)
+    src = torch.tensor([a for a, _ in pairs]).unsqueeze(1).expand(len(pairs), b).reshape(-1)
+    dst = torch.tensor([c for _, c in pairs]).unsqueeze(1).expand(len(pairs), b).reshape(-1)
+    direct = macro_phi(p, cfg, h_rep, h_rep, rid, dst)
+    twice = macro_phi(p, cfg, macro_phi(p, cfg, h_rep, h_rep, rid, src), h_rep, rid, src)
+    return F.mse_loss(direct, twice)
+
+
 def stride_ids_for_depths(cfg: ModelCfg, depths: torch.Tensor) -> torch.Tensor:
     """macro.py:144-146."""
     dv = torch.tensor(cfg.depth_choices, dtype=torch.long)
@@ -621,7 +639,7 @@ def macro_step_loss(p: dict, cfg: ModelCfg, tr: TrainCfg, tokens: torch.Tensor, 
                     step: int, usage_ema: torch.Tensor, oc: OutputCfg | None = None,
                     top_clusters: torch.Tensor | None = None) -> tuple[torch.Tensor, dict]:
     """training.py:1336-1392 + audit.py:245-387 (fixed-count sampler,
-    gradient_corrected mode, consistency term off)."""
+    the three audit modes, residual clip, consistency term)."""
     shortlist = tr.mode == "recursive_macro_shortlist"
     hot = forward_macro(p, cfg, tokens, targets, tr.fixed_recipe, tr.fixed_depth, oc if shortlist else None,
                         seed=tr.seed + step, top_clusters=top_clusters)      # training.py:1364
@@ -646,6 +664,8 @@ def macro_step_loss(p: dict, cfg: ModelCfg, tr: TrainCfg, tokens: torch.Tensor, 
         aux = macro_distill_loss(tr, hot["recurrent_hidden"][mask], exact["recurrent_hidden"],
                                  hot["logits"][mask], exact["logits"], hot["h0"][mask])
         info.update(exact=exact, mask=mask)
+    if tr.lambda_cons != 0.0:       # audit.py:370-379: on every step of the macro modes, audited or not
+        aux = dict(aux, cons=tr.lambda_cons * macro_consistency_loss(p, cfg, hot["h0"], hot["route"]["recipe_id"]))
     aux_router = router_aux_losses(tr, hot["route"]["recipe_probs"], hot["route"]["expected_depth"], usage_ema)
     loss = corrected.mean() / float(targets.shape[1]) + sum(aux.values()) + sum(aux_router.values())
     info.update(corrected=corrected, aux=aux, aux_router=aux_router)

@@ -119,6 +119,11 @@ PROTOTYPES = {
                           [c_f32, c_vp]),
     "rte_macro_phi_bwd": (C.c_int, [c_vp, c_vp, P(PhiParams), c_vp, c_vp, c_f32, c_vp, c_vp, c_vp, c_vp, P(PhiGrads),
                                     c_vp] + [c_i32] * 6 + [c_f32, c_vp]),
+    "rte_macro_phi_fwd_hx": (C.c_int, [c_vp, c_vp, P(PhiParams), c_vp, c_vp, c_f32, c_vp, c_vp, c_vp, c_vp] + [c_i32] * 5 +
+                             [c_f32, c_vp]),
+    "rte_macro_phi_bwd_hx": (C.c_int, [c_vp, c_vp, c_vp, P(PhiParams), c_vp, c_vp, c_f32, c_vp, c_vp, c_vp, c_vp, c_vp,
+                                       P(PhiGrads), c_vp] + [c_i32] * 6 + [c_vp]),
+    "rte_sqdiff_grad": (C.c_int, [c_vp, c_vp, c_i64, c_f32, c_vp, c_vp, c_vp, c_i32, c_vp]),
     "rte_macro_phi_bwd_data": (C.c_int, [c_vp, c_vp, P(PhiParams), c_vp, c_vp, c_f32, c_vp, c_vp, c_vp, c_vp] + [c_i32] * 5 + [c_vp]),
     "rte_macro_phi_bwd_params": (C.c_int, [c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, P(PhiGrads), c_vp] + [c_i32] * 6 + [c_vp]),
     "rte_cluster_route": (C.c_int, [c_vp, c_i32, c_vp, c_vp, c_vp, c_i32, c_i32, c_i32, c_vp]),

@@ -361,9 +361,6 @@ def unsupported(config: ExperimentConfig) -> list[str]:
             no("training", "audit_schedule_enabled", "the audit-count schedule is not implemented")
         if t.macro_rms_trust_region or t.macro_rms_clamp_early:
             no("training", "macro_rms_trust_region", "the RMS trust region is not implemented")
-    if recursive and t.lambda_cons != 0:
-        # audit.py:370-379: the term is added on every step of the macro modes, audited or not
-        no("training", "lambda_cons", "the macro consistency term (macro.py:342-359) is not implemented; use 0")
     if t.fixed_recipe_schedule is not None:
         no("training", "fixed_recipe_schedule", "per-pass fixed recipes are not implemented")
     if t.coda_warmup_steps:

@@ -1,6 +1,7 @@
 // The macro operator Phi of the recursive model, forward and backward, on device:
 //   out = h + s_cfg * scale * tanh(gain * h + silu(z @ v) @ u + bias),
-//   z   = [rmsnorm(h), mean_S rmsnorm(h), h0],  h == h0 on the hot path,
+//   z   = [rmsnorm(h), mean_S rmsnorm(h), h0],  h == h0 on the hot path (the consistency term applies Phi to a state
+//   h != h0: the kernels that touch the h0 slice take it as a second pointer `hx`, equal to `h` on the hot path),
 // with gain / v / u / bias / scale selected PER SAMPLE by (recipe id, stride id).
 //
 // The per-sample low-rank weights are small (3d x m and m x d, m <= 64), so these are SIMT kernels
@@ -58,11 +59,11 @@ phi_prep_kernel(const float* __restrict__ h0, const float* __restrict__ v, const
   }
 }
 
-// act[tok, j] = pa[b, j] + sum_c h0[tok,c] * (rstd[tok] * v1[c,j] + v3[c,j])
+// act[tok, j] = pa[b, j] + sum_c (h0[tok,c] * rstd[tok] * v1[c,j] + hx[tok,c] * v3[c,j])      (hx == h0 on the hot path)
 __global__ void __launch_bounds__(NTHR)
-phi_act_kernel(const float* __restrict__ h0, const float* __restrict__ rstd, const float* __restrict__ pa,
-               const float* __restrict__ v, const int32_t* __restrict__ rid, const int32_t* __restrict__ sid,
-               float* __restrict__ act, PhiDims D) {
+phi_act_kernel(const float* __restrict__ h0, const float* __restrict__ hx, const float* __restrict__ rstd,
+               const float* __restrict__ pa, const float* __restrict__ v, const int32_t* __restrict__ rid,
+               const int32_t* __restrict__ sid, float* __restrict__ act, PhiDims D) {
   __shared__ float sx[TT][CH + 1];
   __shared__ float sv1[CH][MMAX];
   __shared__ float sv3[CH][MMAX];
@@ -70,6 +71,7 @@ phi_act_kernel(const float* __restrict__ h0, const float* __restrict__ rstd, con
   const int b = blockIdx.x / tiles, tok0 = (blockIdx.x % tiles) * TT;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const float* vb = v + key_of(rid, sid, b, D.K) * 3 * D.d * D.m;
+  const bool own3 = hx != h0;                        // kernel-uniform
   float acc[4][2], rs[4];
 #pragma unroll
   for (int t = 0; t < 4; ++t) {
@@ -98,7 +100,27 @@ phi_act_kernel(const float* __restrict__ h0, const float* __restrict__ rstd, con
         if (j < D.m) {
           const float w1 = sv1[c][j], w3 = sv3[c][j];
 #pragma unroll
-          for (int t = 0; t < 4; ++t) { const float x = sx[warp * 4 + t][c]; acc[t][q] += x * (rs[t] * w1 + w3); }
+          for (int t = 0; t < 4; ++t) { const float x = sx[warp * 4 + t][c]; acc[t][q] += own3 ? x * rs[t] * w1 : x * (rs[t] * w1 + w3); }
+        }
+      }
+    }
+    if (own3) {                                    // the v3 slice multiplies the injected state: second sweep over its tile
+      __syncthreads();
+      for (int i = threadIdx.x; i < TT * CH; i += NTHR) {
+        const int t = i / CH, c = i % CH, s = tok0 + t;
+        sx[t][c] = (s < D.S && c0 + c < D.d) ? hx[((size_t)b * D.S + s) * D.d + c0 + c] : 0.f;
+      }
+      __syncthreads();
+#pragma unroll 4
+      for (int c = 0; c < CH; ++c) {
+#pragma unroll
+        for (int q = 0; q < 2; ++q) {
+          const int j = lane + 32 * q;
+          if (j < D.m) {
+            const float w3 = sv3[c][j];
+#pragma unroll
+            for (int t = 0; t < 4; ++t) acc[t][q] += sx[warp * 4 + t][c] * w3;
+          }
         }
       }
     }
@@ -317,12 +339,13 @@ phi_da_mma_kernel(const float* __restrict__ dupd, const float* __restrict__ act,
 // TRANSPOSED parameters: wt = vt [m][keys*3d] (vt[j][key*3d + c] = v[key][c][j]) followed by
 // ut [d][keys*m] (ut[c][key*m + j] = u[key][j][c]), refreshed once per step by rte_macro_phi_prepare.
 
-// act[tok, j] = pa[b, j] + rstd[tok] * (h0 @ v1)[tok, j] + (h0 @ v3)[tok, j]:  M = tokens, N = rank, K = d (d % 32 == 0).
-// Same warp layout as phi_da_mma_kernel; two accumulators per rank tile (the v1 and v3 slices share the A fragments).
+// act[tok, j] = pa[b, j] + rstd[tok] * (h0 @ v1)[tok, j] + (hx @ v3)[tok, j]:  M = tokens, N = rank, K = d (d % 32 == 0).
+// Same warp layout as phi_da_mma_kernel; two accumulators per rank tile (with hx == h0, the hot path, the v1 and v3
+// slices share the A fragments; otherwise the v3 slice gets fragments of its own).
 __global__ void __launch_bounds__(NTHR)
-phi_act_mma_kernel(const float* __restrict__ h0, const float* __restrict__ rstd, const float* __restrict__ pa,
-                   const float* __restrict__ vt, long long vt_ld, const int32_t* __restrict__ rid,
-                   const int32_t* __restrict__ sid, float* __restrict__ act, PhiDims D) {
+phi_act_mma_kernel(const float* __restrict__ h0, const float* __restrict__ hx, const float* __restrict__ rstd,
+                   const float* __restrict__ pa, const float* __restrict__ vt, long long vt_ld,
+                   const int32_t* __restrict__ rid, const int32_t* __restrict__ sid, float* __restrict__ act, PhiDims D) {
   const int tiles = rte::ceil_div(D.S, TT);
   const int b = blockIdx.x / tiles, tok0 = (blockIdx.x % tiles) * TT;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, g = lane >> 2, t = lane & 3;
@@ -335,6 +358,9 @@ phi_act_mma_kernel(const float* __restrict__ h0, const float* __restrict__ rstd,
   const bool ok0 = r0 < D.S, ok1 = r1 < D.S;
   const float* a0p = h0 + ((size_t)b * D.S + (ok0 ? r0 : 0)) * D.d + 8 * t;
   const float* a1p = h0 + ((size_t)b * D.S + (ok1 ? r1 : 0)) * D.d + 8 * t;
+  const bool own3 = hx != h0;                        // kernel-uniform
+  const float* x0p = hx + ((size_t)b * D.S + (ok0 ? r0 : 0)) * D.d + 8 * t;
+  const float* x1p = hx + ((size_t)b * D.S + (ok1 ? r1 : 0)) * D.d + 8 * t;
   const int j0 = ng * 8 + g, j1 = j0 + 32;
   const bool okb0 = j0 < D.m, okb1 = two && j1 < D.m;
   const float* b0p = vt + (size_t)(okb0 ? j0 : 0) * vt_ld + koff + 8 * t;
@@ -347,29 +373,40 @@ phi_act_mma_kernel(const float* __restrict__ h0, const float* __restrict__ rstd,
 #pragma unroll 2
   for (int k0 = 0; k0 < D.d; k0 += 32) {
     const Frag8 x0 = load8(a0p + k0, ok0), x1 = load8(a1p + k0, ok1);
+    Frag8 z0 = x0, z1 = x1;                          // A operand of the v3 slice
+    if (own3) { z0 = load8(x0p + k0, ok0); z1 = load8(x1p + k0, ok1); }
     const Frag8 w1 = load8(b0p + k0, okb0), w3 = load8(b0p + 2 * D.d + k0, okb0);
     Frag8 y1, y3;
     if (two) { y1 = load8(b1p + k0, okb1); y3 = load8(b1p + 2 * D.d + k0, okb1); }
 #pragma unroll
     for (int s = 0; s < 4; ++s) {
-      uint32_t a[4], al[4], f[2], fl[2];
+      uint32_t a[4], al[4], c[4], cl[4], f[2], fl[2];
       split_tf32(pick(x0.lo, s), a[0], al[0]);
       split_tf32(pick(x1.lo, s), a[1], al[1]);
       split_tf32(pick(x0.hi, s), a[2], al[2]);
       split_tf32(pick(x1.hi, s), a[3], al[3]);
+      if (own3) {
+        split_tf32(pick(z0.lo, s), c[0], cl[0]);
+        split_tf32(pick(z1.lo, s), c[1], cl[1]);
+        split_tf32(pick(z0.hi, s), c[2], cl[2]);
+        split_tf32(pick(z1.hi, s), c[3], cl[3]);
+      } else {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) { c[e] = a[e]; cl[e] = al[e]; }
+      }
       split_tf32(pick(w1.lo, s), f[0], fl[0]);
       split_tf32(pick(w1.hi, s), f[1], fl[1]);
       mma_3xtf32(p1[0], a, al, f, fl);
       split_tf32(pick(w3.lo, s), f[0], fl[0]);
       split_tf32(pick(w3.hi, s), f[1], fl[1]);
-      mma_3xtf32(p3[0], a, al, f, fl);
+      mma_3xtf32(p3[0], c, cl, f, fl);
       if (two) {
         split_tf32(pick(y1.lo, s), f[0], fl[0]);
         split_tf32(pick(y1.hi, s), f[1], fl[1]);
         mma_3xtf32(p1[1], a, al, f, fl);
         split_tf32(pick(y3.lo, s), f[0], fl[0]);
         split_tf32(pick(y3.hi, s), f[1], fl[1]);
-        mma_3xtf32(p3[1], a, al, f, fl);
+        mma_3xtf32(p3[1], c, cl, f, fl);
       }
     }
   }
@@ -529,16 +566,17 @@ phi_pu_kernel(const float* __restrict__ h0, const float* __restrict__ act, const
 // Per-sample gradient of v:  pv[b][c', j] for c' in [0, 3d):
 //   c' <  d  : sum_s h0[s,c]*rstd[s] * da[s,j]
 //   c' < 2d  : pooled[b,c] * sum_s da[s,j]
-//   else     : sum_s h0[s,c] * da[s,j]
+//   else     : sum_s hx[s,c] * da[s,j]          (hx == h0 on the hot path)
 constexpr int PV_ROWS = 32;       // rows of v per CTA (one 128-byte line of h0 per token)
 
 __global__ void __launch_bounds__(NTHR)
-phi_pv_kernel(const float* __restrict__ h0, const float* __restrict__ rstd, const float* __restrict__ pooled,
-              const float* __restrict__ da, float* __restrict__ pv, PhiDims D) {
-  extern __shared__ float sm[];      // sda[S][m], rs[S], sx[S][PV_ROWS]
+phi_pv_kernel(const float* __restrict__ h0, const float* __restrict__ hx, const float* __restrict__ rstd,
+              const float* __restrict__ pooled, const float* __restrict__ da, float* __restrict__ pv, PhiDims D) {
+  extern __shared__ float sm[];      // sda[S][m], rs[S], sx[S][PV_ROWS], sx3[S][PV_ROWS]
   float* sda = sm;
   float* rs = sm + D.S * D.m;
   float* sx = rs + D.S;
+  float* sx3 = sx + D.S * PV_ROWS;
   constexpr int ROWS = PV_ROWS;
   const int rblocks = rte::ceil_div(D.d, ROWS);
   const int b = blockIdx.x / rblocks, c0 = (blockIdx.x % rblocks) * ROWS;
@@ -547,6 +585,7 @@ phi_pv_kernel(const float* __restrict__ h0, const float* __restrict__ rstd, cons
   for (int i = threadIdx.x; i < D.S * ROWS; i += NTHR) {
     const int s = i / ROWS, r = i % ROWS;
     sx[i] = (c0 + r < D.d) ? h0[((size_t)b * D.S + s) * D.d + c0 + r] : 0.f;
+    sx3[i] = (c0 + r < D.d) ? hx[((size_t)b * D.S + s) * D.d + c0 + r] : 0.f;
   }
   __syncthreads();
   float* pvb = pv + (size_t)b * 3 * D.d * D.m;
@@ -558,7 +597,7 @@ phi_pv_kernel(const float* __restrict__ h0, const float* __restrict__ rstd, cons
       const float dv = sda[s * D.m + j], x = sx[s * ROWS + r];
       a1 += x * rs[s] * dv;
       a2 += dv;
-      a3 += x * dv;
+      a3 += sx3[s * ROWS + r] * dv;
     }
     pvb[(size_t)c * D.m + j] = a1;
     pvb[(size_t)(D.d + c) * D.m + j] = pooled[(size_t)b * D.d + c] * a2;
@@ -586,11 +625,11 @@ phi_dpool_kernel(const float* __restrict__ da, const float* __restrict__ v, cons
   }
 }
 
-// dh0[tok,:] += da @ v3^T + rmsnorm_backward(da @ v1^T + dpool[b,:])     (one warp per token)
+// dhx[tok,:] += da @ v3^T;  dh0[tok,:] += rmsnorm_backward(da @ v1^T + dpool[b,:])     (one warp per token; dhx may be dh0)
 __global__ void __launch_bounds__(NTHR)
 phi_dz_kernel(const float* __restrict__ h0, const float* __restrict__ rstd, const float* __restrict__ da,
               const float* __restrict__ dpool, const float* __restrict__ v, const int32_t* __restrict__ rid,
-              const int32_t* __restrict__ sid, float* __restrict__ dh0, PhiDims D) {
+              const int32_t* __restrict__ sid, float* dh0, float* dhx, PhiDims D) {
   __shared__ float sv1[CH][MMAX + 1];
   __shared__ float sv3[CH][MMAX + 1];
   __shared__ float sda[TT][MMAX];
@@ -637,7 +676,7 @@ phi_dz_kernel(const float* __restrict__ h0, const float* __restrict__ rstd, cons
         if (s < D.S && c < D.d) {
           const size_t idx = ((size_t)b * D.S + s) * D.d + c;
           const float dnv = a1[t][q] + dpool[(size_t)b * D.d + c];
-          dh0[idx] += a3[t][q];
+          dhx[idx] += a3[t][q];
           dot[t] += dnv * h0[idx] * rstd[(size_t)b * D.S + s];
         }
       }
@@ -683,7 +722,8 @@ phi_dz_kernel(const float* __restrict__ h0, const float* __restrict__ rstd, cons
   }
 }
 
-// dh0[tok,:] += da @ v3^T + rmsnorm_backward(da @ v1^T + dpool[b,:]):  M = tokens, N = d, K = rank (tensor-core form;
+// dhx[tok,:] += da @ v3^T;  dh0[tok,:] += rmsnorm_backward(da @ v1^T + dpool[b,:])  (dhx may be dh0):  M = tokens, N = d,
+// K = rank (tensor-core form;
 // d % 32 == 0, rank % 4 == 0).  Eight warps = 2 token tiles x 4 column groups; a group takes 32-column blocks
 // cq, cq+4, ...  The A operand (16 tokens x rank) lives in registers (KC chunks of 32 rank indices, permuted as
 // above).  Output columns are permuted too: mma tile j of a block holds, for lane t, the physical columns
@@ -694,7 +734,7 @@ template <int KC>
 __global__ void __launch_bounds__(NTHR, KC == 1 ? 2 : 1)
 phi_dz_mma_kernel(const float* __restrict__ h0, const float* __restrict__ rstd, const float* __restrict__ da,
                   const float* __restrict__ dpool, const float* __restrict__ v, const int32_t* __restrict__ rid,
-                  const int32_t* __restrict__ sid, float* __restrict__ dh0, PhiDims D) {
+                  const int32_t* __restrict__ sid, float* dh0, float* dhx, PhiDims D) {
   __shared__ float sdot[TT][4];
   const int tiles = rte::ceil_div(D.S, TT);
   const int b = blockIdx.x / tiles, tok0 = (blockIdx.x % tiles) * TT;
@@ -788,12 +828,14 @@ phi_dz_mma_kernel(const float* __restrict__ h0, const float* __restrict__ rstd, 
     dot0 = (q0[0] + q0[1] + q0[2] + q0[3]) / (float)D.d;
     dot1 = (q1[0] + q1[1] + q1[2] + q1[3]) / (float)D.d;
   }
-  auto finish = [&](float4& o, const float4& a1v, const float4& a3v, const float4& dp, const float4& hx, float rs, float dot) {
-    o.x += a3v.x + rs * ((a1v.x + dp.x) - hx.x * rs * dot);
-    o.y += a3v.y + rs * ((a1v.y + dp.y) - hx.y * rs * dot);
-    o.z += a3v.z + rs * ((a1v.z + dp.z) - hx.z * rs * dot);
-    o.w += a3v.w + rs * ((a1v.w + dp.w) - hx.w * rs * dot);
+  const bool own3 = dhx != dh0;                      // kernel-uniform: the v3 slice's gradient has a buffer of its own
+  auto finish = [&](float4& o, const float4& a1v, const float4& a3v, const float4& dp, const float4& hv, float rs, float dot) {
+    o.x += a3v.x + rs * ((a1v.x + dp.x) - hv.x * rs * dot);
+    o.y += a3v.y + rs * ((a1v.y + dp.y) - hv.y * rs * dot);
+    o.z += a3v.z + rs * ((a1v.z + dp.z) - hv.z * rs * dot);
+    o.w += a3v.w + rs * ((a1v.w + dp.w) - hv.w * rs * dot);
   };
+  const float4 zero4 = make_float4(0.f, 0.f, 0.f, 0.f);
   for (int nb = cq; nb < n_blocks; nb += 4) {
     const int cb = nb * 32, col = cb + 8 * t;
     float c1[4][4], c3[4][4];
@@ -812,9 +854,16 @@ phi_dz_mma_kernel(const float* __restrict__ h0, const float* __restrict__ rstd, 
       const float4 ha = *reinterpret_cast<const float4*>(h0 + row * D.d + col), hb = *reinterpret_cast<const float4*>(h0 + row * D.d + col + 4);
       float4* q = reinterpret_cast<float4*>(dh0 + row * D.d + col);
       float4 oa = q[0], ob = q[1];
-      finish(oa, l1, l3, dpa, ha, rs, dot);
-      finish(ob, h1, h3, dpc, hb, rs, dot);
+      finish(oa, l1, own3 ? zero4 : l3, dpa, ha, rs, dot);
+      finish(ob, h1, own3 ? zero4 : h3, dpc, hb, rs, dot);
       q[0] = oa; q[1] = ob;
+      if (own3) {
+        float4* qx = reinterpret_cast<float4*>(dhx + row * D.d + col);
+        float4 xa = qx[0], xb = qx[1];
+        xa.x += l3.x; xa.y += l3.y; xa.z += l3.z; xa.w += l3.w;
+        xb.x += h3.x; xb.y += h3.y; xb.z += h3.z; xb.w += h3.w;
+        qx[0] = xa; qx[1] = xb;
+      }
     }
   }
 }
@@ -842,6 +891,30 @@ phi_reduce_keys_kernel(const float* __restrict__ partial, const int32_t* __restr
   out[(size_t)key * elems + e] = acc;
 }
 
+// Mean-squared-error pieces of the consistency term (macro.py:359): g[i] = coef * (a[i] - b[i]) and one partial sum of
+// (a[i] - b[i])^2 per block (fixed grid, grid-stride: the summation order does not depend on anything but n).
+constexpr int SQD_BLOCKS = 592;
+__global__ void __launch_bounds__(256)
+sqdiff_grad_kernel(const float* __restrict__ a, const float* __restrict__ b, long long n, float coef,
+                   float* __restrict__ g, float* __restrict__ partial) {
+  __shared__ float red[32];
+  float s = 0.f;
+  for (long long i = blockIdx.x * 256LL + threadIdx.x; i < n; i += (long long)gridDim.x * 256) {
+    const float dv = a[i] - b[i];
+    g[i] = coef * dv;
+    s += dv * dv;
+  }
+  s = rte::block_sum(s, red);
+  if (threadIdx.x == 0) partial[blockIdx.x] = s;
+}
+__global__ void sqdiff_final_kernel(const float* __restrict__ partial, int n, float* __restrict__ out, int accumulate) {
+  __shared__ float red[32];
+  float s = 0.f;
+  for (int i = threadIdx.x; i < n; i += blockDim.x) s += partial[i];
+  s = rte::block_sum(s, red);
+  if (threadIdx.x == 0) out[0] = accumulate ? out[0] + s : s;
+}
+
 }  // namespace
 
 #define ST(s) reinterpret_cast<cudaStream_t>(s)
@@ -866,11 +939,14 @@ extern "C" int rte_macro_phi_prepare(const float* v, const float* u, float* wt, 
   return rte_transpose_f32(u, wt + (size_t)m * n_keys * 3 * d, n_keys * m, d, 0, 0, stream);
 }
 
-extern "C" int rte_macro_phi_fwd(const float* h0, const rte_phi_params* p, const int32_t* recipe_id,
-                                 const int32_t* stride_id, float s_cfg, float* out, float* rstd, float* pooled,
-                                 float* act, int32_t B, int32_t S, int32_t d, int32_t m, int32_t K_strides,
-                                 float eps, rte_stream_t stream) {
-  RTE_CHECK_ARG(h0 && p && p->gain && p->v && p->u && p->bias && p->scale && recipe_id && stride_id && out && rstd &&
+namespace {
+// `h0`: the state Phi is applied to (norm, pooled mean, gain and residual terms); `hx`: the injected state of the third
+// slice of z (the same pointer on the hot path).
+int phi_fwd_impl(const float* h0, const float* hx, const rte_phi_params* p, const int32_t* recipe_id,
+                 const int32_t* stride_id, float s_cfg, float* out, float* rstd, float* pooled,
+                 float* act, int32_t B, int32_t S, int32_t d, int32_t m, int32_t K_strides,
+                 float eps, rte_stream_t stream) {
+  RTE_CHECK_ARG(h0 && hx && p && p->gain && p->v && p->u && p->bias && p->scale && recipe_id && stride_id && out && rstd &&
                 pooled && act && B > 0 && S > 0 && d > 0 && m > 0 && K_strides > 0);
   if (m > MMAX) return RTE_ERR_UNSUPPORTED;
   PhiDims D{B, S, d, m, K_strides};
@@ -880,10 +956,10 @@ extern "C" int rte_macro_phi_fwd(const float* h0, const rte_phi_params* p, const
   float* pa = pooled + (size_t)B * d;
   phi_prep_kernel<<<B, NTHR, (size_t)(S + d) * sizeof(float), ST(stream)>>>(h0, p->v, recipe_id, stride_id, rstd, pooled, pa, D, eps);
   RTE_LAUNCH_CHECK();
-  if (phi_tensor_path(p, h0, out, act, d, m)) {
+  if (phi_tensor_path(p, h0, out, act, d, m) && (reinterpret_cast<uintptr_t>(hx) & 15) == 0) {
     const long long vt_ld = (long long)p->n_keys * 3 * d, ut_ld = (long long)p->n_keys * m;
     const float* ut = p->wt + (size_t)m * vt_ld;
-    phi_act_mma_kernel<<<B * tiles, NTHR, 0, ST(stream)>>>(h0, rstd, pa, p->wt, vt_ld, recipe_id, stride_id, act, D);
+    phi_act_mma_kernel<<<B * tiles, NTHR, 0, ST(stream)>>>(h0, hx, rstd, pa, p->wt, vt_ld, recipe_id, stride_id, act, D);
     RTE_LAUNCH_CHECK();
     if (m <= 32)
       phi_out_mma_kernel<0, 1><<<B * tiles, NTHR, 0, ST(stream)>>>(h0, act, p->gain, ut, ut_ld, p->bias, p->scale, recipe_id,
@@ -894,7 +970,7 @@ extern "C" int rte_macro_phi_fwd(const float* h0, const rte_phi_params* p, const
     RTE_LAUNCH_CHECK();
     return RTE_OK;
   }
-  phi_act_kernel<<<B * tiles, NTHR, 0, ST(stream)>>>(h0, rstd, pa, p->v, recipe_id, stride_id, act, D);
+  phi_act_kernel<<<B * tiles, NTHR, 0, ST(stream)>>>(h0, hx, rstd, pa, p->v, recipe_id, stride_id, act, D);
   RTE_LAUNCH_CHECK();
   if (m <= 32)
     phi_out_kernel<0, 32><<<B * tiles, NTHR, 0, ST(stream)>>>(h0, act, p->gain, p->u, p->bias, p->scale, recipe_id, stride_id,
@@ -904,6 +980,21 @@ extern "C" int rte_macro_phi_fwd(const float* h0, const rte_phi_params* p, const
                                                               s_cfg, nullptr, out, nullptr, D);
   RTE_LAUNCH_CHECK();
   return RTE_OK;
+}
+}  // namespace
+
+extern "C" int rte_macro_phi_fwd(const float* h0, const rte_phi_params* p, const int32_t* recipe_id,
+                                 const int32_t* stride_id, float s_cfg, float* out, float* rstd, float* pooled,
+                                 float* act, int32_t B, int32_t S, int32_t d, int32_t m, int32_t K_strides,
+                                 float eps, rte_stream_t stream) {
+  return phi_fwd_impl(h0, h0, p, recipe_id, stride_id, s_cfg, out, rstd, pooled, act, B, S, d, m, K_strides, eps, stream);
+}
+
+extern "C" int rte_macro_phi_fwd_hx(const float* h, const float* h0, const rte_phi_params* p, const int32_t* recipe_id,
+                                    const int32_t* stride_id, float s_cfg, float* out, float* rstd, float* pooled,
+                                    float* act, int32_t B, int32_t S, int32_t d, int32_t m, int32_t K_strides,
+                                    float eps, rte_stream_t stream) {
+  return phi_fwd_impl(h, h0, p, recipe_id, stride_id, s_cfg, out, rstd, pooled, act, B, S, d, m, K_strides, eps, stream);
 }
 
 namespace {
@@ -923,12 +1014,14 @@ inline PhiBwdScratch phi_scratch(float* scratch, int B, int S, int d, int m) {
 }
 }  // namespace
 
-// Data-gradient half: dh0 (the chain the rest of backward waits for); leaves dupd and da in `scratch`.
-extern "C" int rte_macro_phi_bwd_data(const float* h0, const float* dout, const rte_phi_params* p, const int32_t* recipe_id,
-                                      const int32_t* stride_id, float s_cfg, const float* rstd, const float* act, float* dh0,
-                                      float* scratch, int32_t B, int32_t S, int32_t d, int32_t m, int32_t K_strides,
-                                      rte_stream_t stream) {
-  RTE_CHECK_ARG(h0 && dout && p && recipe_id && stride_id && rstd && act && dh0 && scratch && B > 0 && S > 0 && d > 0 && m > 0 &&
+namespace {
+// dh0 (overwritten): gradient wrt the state Phi was applied to; dhx (accumulated into; may be dh0): gradient wrt the
+// injected state of z's third slice.
+int phi_bwd_data_impl(const float* h0, const float* dout, const rte_phi_params* p, const int32_t* recipe_id,
+                      const int32_t* stride_id, float s_cfg, const float* rstd, const float* act, float* dh0, float* dhx,
+                      float* scratch, int32_t B, int32_t S, int32_t d, int32_t m, int32_t K_strides,
+                      rte_stream_t stream) {
+  RTE_CHECK_ARG(h0 && dhx && dout && p && recipe_id && stride_id && rstd && act && dh0 && scratch && B > 0 && S > 0 && d > 0 && m > 0 &&
                 K_strides > 0);
   if (m > MMAX || B > 1024) return RTE_ERR_UNSUPPORTED;
   PhiDims D{B, S, d, m, K_strides};
@@ -952,33 +1045,44 @@ extern "C" int rte_macro_phi_bwd_data(const float* h0, const float* dout, const 
   RTE_LAUNCH_CHECK();
   // tensor-core (3xTF32) products with 16-byte operand loads; other shapes keep the scalar kernels
   const bool mma = d % 32 == 0 && m % 4 == 0 && ((reinterpret_cast<uintptr_t>(scratch) | reinterpret_cast<uintptr_t>(h0) |
-                   reinterpret_cast<uintptr_t>(dh0) | reinterpret_cast<uintptr_t>(p->u) | reinterpret_cast<uintptr_t>(p->v)) & 15) == 0;
+                   reinterpret_cast<uintptr_t>(dh0) | reinterpret_cast<uintptr_t>(dhx) | reinterpret_cast<uintptr_t>(p->u) |
+                   reinterpret_cast<uintptr_t>(p->v)) & 15) == 0;
   if (mma) phi_da_mma_kernel<<<B * tiles, NTHR, 0, ST(stream)>>>(x.dupd, act, p->u, recipe_id, stride_id, x.da, D);
   else phi_da_kernel<<<B * tiles, NTHR, 0, ST(stream)>>>(x.dupd, act, p->u, recipe_id, stride_id, x.da, D);
   RTE_LAUNCH_CHECK();
   phi_dpool_kernel<<<B, NTHR, 0, ST(stream)>>>(x.da, p->v, recipe_id, stride_id, x.dpool, D);
   RTE_LAUNCH_CHECK();
-  if (mma && m <= 32) phi_dz_mma_kernel<1><<<B * tiles, NTHR, 0, ST(stream)>>>(h0, rstd, x.da, x.dpool, p->v, recipe_id, stride_id, dh0, D);
-  else if (mma) phi_dz_mma_kernel<2><<<B * tiles, NTHR, 0, ST(stream)>>>(h0, rstd, x.da, x.dpool, p->v, recipe_id, stride_id, dh0, D);
-  else phi_dz_kernel<<<B * tiles, NTHR, 0, ST(stream)>>>(h0, rstd, x.da, x.dpool, p->v, recipe_id, stride_id, dh0, D);
+  if (mma && m <= 32) phi_dz_mma_kernel<1><<<B * tiles, NTHR, 0, ST(stream)>>>(h0, rstd, x.da, x.dpool, p->v, recipe_id, stride_id, dh0, dhx, D);
+  else if (mma) phi_dz_mma_kernel<2><<<B * tiles, NTHR, 0, ST(stream)>>>(h0, rstd, x.da, x.dpool, p->v, recipe_id, stride_id, dh0, dhx, D);
+  else phi_dz_kernel<<<B * tiles, NTHR, 0, ST(stream)>>>(h0, rstd, x.da, x.dpool, p->v, recipe_id, stride_id, dh0, dhx, D);
   RTE_LAUNCH_CHECK();
   return RTE_OK;
+}
+}  // namespace
+
+// Data-gradient half: dh0 (the chain the rest of backward waits for); leaves dupd and da in `scratch`.
+extern "C" int rte_macro_phi_bwd_data(const float* h0, const float* dout, const rte_phi_params* p, const int32_t* recipe_id,
+                                      const int32_t* stride_id, float s_cfg, const float* rstd, const float* act, float* dh0,
+                                      float* scratch, int32_t B, int32_t S, int32_t d, int32_t m, int32_t K_strides,
+                                      rte_stream_t stream) {
+  return phi_bwd_data_impl(h0, dout, p, recipe_id, stride_id, s_cfg, rstd, act, dh0, dh0, scratch, B, S, d, m, K_strides, stream);
 }
 
 // Parameter-gradient half: reads dupd and da left in `scratch` by rte_macro_phi_bwd_data (may run on another
 // stream, ordered after it); nothing downstream in backward depends on it.
-extern "C" int rte_macro_phi_bwd_params(const float* h0, const int32_t* recipe_id, const int32_t* stride_id, const float* rstd,
-                                        const float* pooled, const float* act, const rte_phi_grads* g, float* scratch,
-                                        int32_t B, int32_t S, int32_t d, int32_t m, int32_t R, int32_t K_strides,
-                                        rte_stream_t stream) {
-  RTE_CHECK_ARG(h0 && recipe_id && stride_id && rstd && pooled && act && g && scratch && B > 0 && S > 0 && d > 0 && m > 0 &&
+namespace {
+int phi_bwd_params_impl(const float* h0, const float* hx, const int32_t* recipe_id, const int32_t* stride_id, const float* rstd,
+                        const float* pooled, const float* act, const rte_phi_grads* g, float* scratch,
+                        int32_t B, int32_t S, int32_t d, int32_t m, int32_t R, int32_t K_strides,
+                        rte_stream_t stream) {
+  RTE_CHECK_ARG(h0 && hx && recipe_id && stride_id && rstd && pooled && act && g && scratch && B > 0 && S > 0 && d > 0 && m > 0 &&
                 R > 0 && K_strides > 0);
   RTE_CHECK_ARG(g->gain && g->v && g->u && g->bias);
   if (m > MMAX || B > 1024) return RTE_ERR_UNSUPPORTED;
   PhiDims D{B, S, d, m, K_strides};
   const PhiBwdScratch x = phi_scratch(scratch, B, S, d, m);
   const size_t smem_pu = (size_t)S * m * sizeof(float);
-  const size_t smem_pv = ((size_t)S * m + S + (size_t)S * PV_ROWS) * sizeof(float);
+  const size_t smem_pv = ((size_t)S * m + S + 2 * (size_t)S * PV_ROWS) * sizeof(float);
   if (smem_pu > 48 * 1024 || smem_pv > 48 * 1024) {
     static bool set = false;
     if (!set) {
@@ -990,7 +1094,7 @@ extern "C" int rte_macro_phi_bwd_params(const float* h0, const int32_t* recipe_i
   }
   phi_pu_kernel<<<B * rte::ceil_div(d, NTHR), NTHR, smem_pu, ST(stream)>>>(h0, act, x.dupd, x.pu, x.pg, x.pb, D);
   RTE_LAUNCH_CHECK();
-  phi_pv_kernel<<<B * rte::ceil_div(d, PV_ROWS), NTHR, smem_pv, ST(stream)>>>(h0, rstd, pooled, x.da, x.pv, D);
+  phi_pv_kernel<<<B * rte::ceil_div(d, PV_ROWS), NTHR, smem_pv, ST(stream)>>>(h0, hx, rstd, pooled, x.da, x.pv, D);
   RTE_LAUNCH_CHECK();
   const int n_keys = R * K_strides;
   const long long eu = (long long)m * d, ev = (long long)3 * d * m, ed = d;
@@ -1004,6 +1108,27 @@ extern "C" int rte_macro_phi_bwd_params(const float* h0, const int32_t* recipe_i
   RTE_LAUNCH_CHECK();
   return RTE_OK;
 }
+}  // namespace
+
+extern "C" int rte_macro_phi_bwd_params(const float* h0, const int32_t* recipe_id, const int32_t* stride_id, const float* rstd,
+                                        const float* pooled, const float* act, const rte_phi_grads* g, float* scratch,
+                                        int32_t B, int32_t S, int32_t d, int32_t m, int32_t R, int32_t K_strides,
+                                        rte_stream_t stream) {
+  return phi_bwd_params_impl(h0, h0, recipe_id, stride_id, rstd, pooled, act, g, scratch, B, S, d, m, R, K_strides, stream);
+}
+
+// Phi applied to a state h that is not the injected h0 (macro.py:342-359, the consistency term's second application):
+// dh (overwritten) and dh0 (ACCUMULATED into) are separate; parameter gradients as in rte_macro_phi_bwd.
+extern "C" int rte_macro_phi_bwd_hx(const float* h, const float* h0, const float* dout, const rte_phi_params* p,
+                                    const int32_t* recipe_id, const int32_t* stride_id, float s_cfg, const float* rstd,
+                                    const float* pooled, const float* act, float* dh, float* dh0, const rte_phi_grads* g,
+                                    float* scratch, int32_t B, int32_t S, int32_t d, int32_t m, int32_t R, int32_t K_strides,
+                                    rte_stream_t stream) {
+  RTE_CHECK_ARG(g != nullptr && R > 0 && dh != dh0);
+  const int rc = phi_bwd_data_impl(h, dout, p, recipe_id, stride_id, s_cfg, rstd, act, dh, dh0, scratch, B, S, d, m, K_strides, stream);
+  if (rc != RTE_OK) return rc;
+  return phi_bwd_params_impl(h, h0, recipe_id, stride_id, rstd, pooled, act, g, scratch, B, S, d, m, R, K_strides, stream);
+}
 
 // Both halves on one stream.
 extern "C" int rte_macro_phi_bwd(const float* h0, const float* dout, const rte_phi_params* p, const int32_t* recipe_id,
@@ -1016,4 +1141,15 @@ extern "C" int rte_macro_phi_bwd(const float* h0, const float* dout, const rte_p
   const int rc = rte_macro_phi_bwd_data(h0, dout, p, recipe_id, stride_id, s_cfg, rstd, act, dh0, scratch, B, S, d, m, K_strides, stream);
   if (rc != RTE_OK) return rc;
   return rte_macro_phi_bwd_params(h0, recipe_id, stride_id, rstd, pooled, act, g, scratch, B, S, d, m, R, K_strides, stream);
+}
+
+// g = coef * (a - b);  sum_out (+)= sum (a - b)^2.  `partial`: >= 1024 floats of scratch.
+extern "C" int rte_sqdiff_grad(const float* a, const float* b, int64_t n, float coef, float* g, float* partial, float* sum_out,
+                               int32_t accumulate, rte_stream_t stream) {
+  RTE_CHECK_ARG(a && b && g && partial && sum_out && n > 0);
+  sqdiff_grad_kernel<<<SQD_BLOCKS, 256, 0, ST(stream)>>>(a, b, n, coef, g, partial);
+  RTE_LAUNCH_CHECK();
+  sqdiff_final_kernel<<<1, 1024, 0, ST(stream)>>>(partial, SQD_BLOCKS, sum_out, accumulate);
+  RTE_LAUNCH_CHECK();
+  return RTE_OK;
 }

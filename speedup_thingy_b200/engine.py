@@ -12,6 +12,7 @@ PyTorch is used for device memory, streams and graph capture only.
 """
 from __future__ import annotations
 
+import contextlib
 import os
 
 import math
@@ -459,6 +460,7 @@ class TrainEngine:
             # transposed macro-operator weights for its tensor-core forward, refreshed every step (CudaOps only)
             self.phi_wt = (e(cfg.recipe_count * len(cfg.depth_choices) * 4 * d * m)
                            if hasattr(ops, "macro_phi_prepare") and dev.type == "cuda" else None)
+            self._init_consistency(e)
             self.macro_scale = torch.ones(r, k, d, dtype=f32, device=dev)   # `update_scale` buffer (macro.py:99-108)
             self.macro_teacher_delta_rms = torch.zeros(r, k)               # carried through checkpoints only (macro.py:122)
             self.depth_values = torch.tensor(list(cfg.depth_choices), dtype=torch.int32, device=dev)
@@ -677,6 +679,88 @@ class TrainEngine:
                     d_w2=p["router.depth_mlp.2.weight"], d_b2=p["router.depth_mlp.2.bias"],
                     pass_recipe_bias=p["router.pass_recipe_bias"])
 
+    # ------------------------------------------------------------------ macro consistency term
+    def _init_consistency(self, e) -> None:
+        """Buffers of the consistency term lambda_cons * mse(Phi_2k(h0, h0), Phi_k(Phi_k(h0, h0), h0)) over the stride pairs
+        (k, 2k) of the depth choices (macro.py:126,342-359; added on every step of the macro modes, audit.py:370-379)."""
+        cfg, tr, dev = self.cfg, self.tr, self.device
+        strides = list(cfg.depth_choices)
+        self.cons_pairs = ([(i, strides.index(v * 2)) for i, v in enumerate(strides) if v * 2 in strides]
+                           if (tr.lambda_cons != 0.0 and not self.exact) else [])
+        self._cons_stream = None
+        if not self.cons_pairs:
+            return
+        B, M, d, m = self.B, self.M, cfg.d_model, cfg.macro_rank
+        i32 = torch.int32
+        self.cons_src = [torch.full((B,), a, dtype=i32, device=dev) for a, _ in self.cons_pairs]
+        self.cons_dst = [torch.full((B,), c, dtype=i32, device=dev) for _, c in self.cons_pairs]
+        self.cons_out = [e(M, d) for _ in range(3)]                       # direct, mid, twice
+        self.cons_saved = [(e(M), e(B * d + B * m), e(M, m)) for _ in range(3)]          # rstd, pooled(+pa), act of each
+        self.cons_g, self.cons_gneg = e(M, d), e(M, d)                    # coef * (direct - twice) and its negative
+        self.cons_dmid, self.cons_dh, self.cons_dh0 = e(M, d), e(M, d), e(M, d)
+        self.cons_scratch = e(self.ops.phi_bwd_scratch_floats(B, self.S, d, m))
+        self.cons_partial = e(1024)
+        # parameter gradients of the term: a mirror of the macro operator's slice of the flat gradient buffer (same
+        # relative offsets, so one add merges it) plus a scratch mirror each backward overwrites
+        names = ["macro.d_gain", "macro.v", "macro.u", "macro.bias"]
+        lo = min(self._grad_offsets[n] for n in names)
+        hi = max(self._grad_offsets[n] + -(-self.params[n].numel() // 64) * 64 for n in names)
+        self.cons_range = (lo, hi)
+        self.cons_pg_flat, self.cons_pg_tmp_flat = e(hi - lo), e(hi - lo)
+
+        def views(flat):
+            return {n.split(".")[1].replace("d_gain", "gain"): flat[self._grad_offsets[n] - lo: self._grad_offsets[n] - lo + self.params[n].numel()]
+                    .view(self.params[n].shape) for n in names}
+        self.cons_pg_tmp = views(self.cons_pg_tmp_flat)
+        if dev.type == "cuda":
+            self._cons_stream = torch.cuda.Stream(device=dev)
+
+    def _consistency_branch(self, h0: torch.Tensor):
+        """Forward and backward of the consistency term, on its own stream beside the rest of the step: needs h0, the
+        routed recipe ids and the prepared macro weights; leaves d h0 in `cons_dh0`, the parameter gradients in
+        `cons_pg_flat`, the summed squared difference in scalars[6].  Returns the event that marks them complete."""
+        o, cfg, tr = self.ops, self.cfg, self.tr
+        B, S, M, d, m = self.B, self.S, self.M, cfg.d_model, cfg.macro_rank
+        R, K, P = cfg.recipe_count, len(cfg.depth_choices), len(self.cons_pairs)
+        dims = dict(B=B, S=S, d=d, m=m, K=K)
+        pd, rid, s_cfg = self._phi_param_dict(), self.route["recipe_id"], cfg.macro_update_scale
+        coef = 2.0 * tr.lambda_cons / (P * M * d * self.loss_div)           # d(lambda * mse)/d direct, this rank's share
+        cs = self._cons_stream
+        if cs is not None:
+            cs.wait_stream(torch.cuda.current_stream(self.device))
+        ctx = torch.cuda.stream(cs) if cs is not None else contextlib.nullcontext()
+        with ctx:
+            o.fill_(self.cons_dh0, 0.0)
+            o.fill_(self.cons_pg_flat, 0.0)
+            direct, mid, twice = self.cons_out
+            (r_d, p_d, a_d), (r_m, p_m, a_m), (r_t, p_t, a_t) = self.cons_saved
+            for i in range(P):
+                src, dst = self.cons_src[i], self.cons_dst[i]
+                o.macro_phi_fwd(h0, pd, rid, dst, s_cfg, direct, r_d, p_d, a_d, **dims)
+                o.macro_phi_fwd(h0, pd, rid, src, s_cfg, mid, r_m, p_m, a_m, **dims)
+                o.macro_phi_fwd_hx(mid, h0, pd, rid, src, s_cfg, twice, r_t, p_t, a_t, **dims)
+                o.sqdiff_grad(direct, twice, coef, self.cons_g, self.cons_partial, self.scalars[6:7], accumulate=i > 0)
+                o.sqdiff_grad(twice, direct, coef, self.cons_gneg, self.cons_partial, self.scalars[7:8], accumulate=False)
+                # d twice = -g: through Phi_k(mid, h0) into mid and h0 ...
+                o.macro_phi_bwd_hx(mid, h0, self.cons_gneg, pd, rid, src, s_cfg, r_t, p_t, a_t, self.cons_dmid, self.cons_dh0,
+                                   self.cons_pg_tmp, self.cons_scratch, R=R, **dims)
+                o.add_(self.cons_pg_flat, self.cons_pg_tmp_flat)
+                # ... d mid through Phi_k(h0, h0) ...
+                o.macro_phi_bwd(h0, self.cons_dmid, pd, rid, src, s_cfg, r_m, p_m, a_m, self.cons_dh, self.cons_pg_tmp,
+                                self.cons_scratch, R=R, **dims)
+                o.add_(self.cons_dh0, self.cons_dh)
+                o.add_(self.cons_pg_flat, self.cons_pg_tmp_flat)
+                # ... and d direct = +g through Phi_2k(h0, h0)
+                o.macro_phi_bwd(h0, self.cons_g, pd, rid, dst, s_cfg, r_d, p_d, a_d, self.cons_dh, self.cons_pg_tmp,
+                                self.cons_scratch, R=R, **dims)
+                o.add_(self.cons_dh0, self.cons_dh)
+                o.add_(self.cons_pg_flat, self.cons_pg_tmp_flat)
+            done = None
+            if cs is not None:
+                done = torch.cuda.Event()
+                done.record(cs)
+        return done
+
     def _phi_param_dict(self) -> dict[str, torch.Tensor]:
         p = self.params
         return dict(gain=p["macro.d_gain"], v=p["macro.v"], u=p["macro.u"], bias=p["macro.bias"], scale=self.macro_scale,
@@ -852,6 +936,9 @@ class TrainEngine:
                     self.audit.forward_replay(h0, head_done=True)
             if self.phi_wt is not None:
                 o.macro_phi_prepare(self._phi_param_dict())
+            self._cons_done, self._cons_pending = None, False
+            if self.cons_pairs and not forward_only:
+                self._cons_done, self._cons_pending = self._consistency_branch(h0), True
             o.macro_phi_fwd(h0, self._phi_param_dict(), self.route["recipe_id"], self.route["depth_id"],
                             cfg.macro_update_scale, self.h_phi, self.phi_rstd, self.phi_pooled, self.phi_act,
                             B=B, S=S, d=d, m=cfg.macro_rank, K=len(cfg.depth_choices))
@@ -987,6 +1074,19 @@ class TrainEngine:
                                   K=len(cfg.depth_choices))
             if split:
                 o.param_stream = None
+            if getattr(self, "_cons_pending", False):
+                # the consistency term's share: d h0 on the chain, the parameter gradients behind the macro operator's own
+                clo, chi = self.cons_range
+                if self._cons_done is not None:
+                    torch.cuda.current_stream(self.device).wait_event(self._cons_done)
+                o.add_(dalt, self.cons_dh0)
+                if split:
+                    with torch.cuda.stream(misc):
+                        if self._cons_done is not None:
+                            misc.wait_event(self._cons_done)
+                        o.add_(self.grad_flat[clo:chi], self.cons_pg_flat)
+                else:
+                    o.add_(self.grad_flat[clo:chi], self.cons_pg_flat)
             # (the communication stream waits for the weight-gradient stream too, so marking here is safe)
             self._grad_ready("macro.d_gain", "macro.v", "macro.u", "macro.bias")
             dcur, dalt = dalt, dcur
@@ -1074,7 +1174,7 @@ class TrainEngine:
         B, k_a = self.B, self.audit_k or 0
         r = self._results
         audit_part = r[8 + 2 * B: 8 + 2 * B + 5 * k_a + 1] if k_a else None
-        self.ops.nonfinite_guard([r[0:4], r[8:8 + B], audit_part], self.skip_flag, self.scalars[5:6])
+        self.ops.nonfinite_guard([r[0:8], r[8:8 + B], audit_part], self.skip_flag, self.scalars[5:6])
 
     def _optimizer_step(self) -> None:
         o, tr = self.ops, self.tr
@@ -1242,6 +1342,10 @@ class TrainEngine:
             terms = self.audit.loss_terms(host["loss_per_sample"], host, host["chosen"])
             loss += terms["correction"] / (self.B * self.S) + sum(terms["aux"].values())
             self.last_audit = terms
+        if getattr(self, "cons_pairs", None):
+            cons = self.tr.lambda_cons * float(vals[6]) / (len(self.cons_pairs) * self.M * self.cfg.d_model)
+            loss += cons
+            self.last_consistency = cons
         if not self.dense and not self.tr.disable_router_aux:
             cover = float(torch.relu(self.tr.coverage_min - self.usage_ema).square().sum()) * self.tr.lambda_cover
             loss += (float(vals[1]) + float(vals[2])) * self.loss_div + cover

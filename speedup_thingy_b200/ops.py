@@ -396,6 +396,28 @@ class CudaOps:
                    _ptr(rstd), _ptr(pooled), _ptr(act), _ptr(dh0), C.byref(sg), _ptr(scratch), B, S, d, m, R, K,
                    1e-5, self.stream)
 
+    def macro_phi_fwd_hx(self, h, h0, p: dict, recipe_id, stride_id, s_cfg, out, rstd, pooled, act, *, B, S, d, m, K):
+        """Phi applied to a state `h` other than the injected `h0` (the consistency term's second application)."""
+        sp = self._phi_params(p)
+        self._call("rte_macro_phi_fwd_hx", _ptr(h), _ptr(h0), C.byref(sp), _ptr(recipe_id), _ptr(stride_id), s_cfg, _ptr(out),
+                   _ptr(rstd), _ptr(pooled), _ptr(act), B, S, d, m, K, 1e-5, self.stream)
+
+    def macro_phi_bwd_hx(self, h, h0, dout, p: dict, recipe_id, stride_id, s_cfg, rstd, pooled, act, dh, dh0, grads: dict,
+                         scratch, *, B, S, d, m, R, K):
+        """Backward of `macro_phi_fwd_hx`: `dh` overwritten, `dh0` accumulated into, parameter gradients overwritten."""
+        sp = self._phi_params(p)
+        sg = A.PhiGrads()
+        for name, _ in A.PhiGrads._fields_:
+            setattr(sg, name, grads[name].data_ptr())
+        self._call("rte_macro_phi_bwd_hx", _ptr(h), _ptr(h0), _ptr(dout), C.byref(sp), _ptr(recipe_id), _ptr(stride_id), s_cfg,
+                   _ptr(rstd), _ptr(pooled), _ptr(act), _ptr(dh), _ptr(dh0), C.byref(sg), _ptr(scratch), B, S, d, m, R, K,
+                   self.stream)
+
+    def sqdiff_grad(self, a, b, coef: float, g, partial, sum_out, accumulate: bool) -> None:
+        """g = coef * (a - b); sum_out (+)= sum (a - b)^2 (fixed order)."""
+        self._call("rte_sqdiff_grad", _ptr(a), _ptr(b), a.numel(), float(coef), _ptr(g), _ptr(partial), _ptr(sum_out),
+                   int(accumulate), self.stream)
+
     def macro_phi_bwd_split(self, h0, dout, p: dict, recipe_id, stride_id, s_cfg, rstd, pooled, act, dh0, grads: dict,
                             scratch, *, B, S, d, m, R, K):
         """The same backward with its parameter-gradient half on `param_stream` when one is set (nothing downstream

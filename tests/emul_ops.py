@@ -380,14 +380,15 @@ class EmulOps:
         logits.scatter_(1, shortlist.long(), g.to(torch.bfloat16))
 
     # ---------------------------------------------------------------- macro operator (via autograd here)
-    def _phi(self, h0, p, rid, sid, s_cfg, B, S, d, m):
+    def _phi(self, h0, p, rid, sid, s_cfg, B, S, d, m, hx=None):
         h = h0.view(B, S, d)
+        hx = h if hx is None else hx.view(B, S, d)
         r, s = rid.long(), sid.long()
         gain, v, u, bias, scale = (p[k][r, s] for k in ("gain", "v", "u", "bias", "scale"))
         rstd = torch.rsqrt(h.pow(2).mean(-1, keepdim=True) + 1e-5)
         normed = h * rstd
         pooled = normed.mean(1, keepdim=True)
-        z = torch.cat([normed, pooled.expand_as(normed), h], -1)
+        z = torch.cat([normed, pooled.expand_as(normed), hx], -1)
         act = torch.bmm(z, v)
         low = torch.bmm(F.silu(act), u)
         out = h + s_cfg * scale[:, None] * torch.tanh(gain[:, None] * h + low + bias[:, None])
@@ -403,6 +404,32 @@ class EmulOps:
 
     def macro_phi_bwd_split(self, *args, **kw):
         self.macro_phi_bwd(*args, **kw)
+
+    def sqdiff_grad(self, a, b, coef, g, partial, sum_out, accumulate):
+        self.launches += 1
+        dv = a.reshape(-1) - b.reshape(-1)
+        g.view(-1)[: dv.numel()] = coef * dv
+        sum_out[0] = (sum_out[0] if accumulate else 0.0) + dv.double().pow(2).sum().float()
+
+    def macro_phi_fwd_hx(self, h, h0, p, recipe_id, stride_id, s_cfg, out, rstd, pooled, act, *, B, S, d, m, K):
+        self.launches += 1
+        o, r, pl, a = self._phi(h, p, recipe_id, stride_id, s_cfg, B, S, d, m, hx=h0)
+        out.view(B, S, d).copy_(o)
+        rstd.view(-1)[: B * S] = r.reshape(-1)
+        pooled.view(-1)[: B * d] = pl.reshape(-1)
+        act.view(B, S, m).copy_(a)
+
+    def macro_phi_bwd_hx(self, h, h0, dout, p, recipe_id, stride_id, s_cfg, rstd, pooled, act, dh, dh0, grads, scratch, *,
+                         B, S, d, m, R, K):
+        self.launches += 1
+        leaves = {k: p[k].detach().clone().requires_grad_(k != "scale") for k in p if k != "wt"}
+        hh, hz = h.detach().clone().requires_grad_(True), h0.detach().clone().requires_grad_(True)
+        o, *_ = self._phi(hh, leaves, recipe_id, stride_id, s_cfg, B, S, d, m, hx=hz)
+        o.backward(dout.view(B, S, d))
+        dh.view(B, S, d).copy_(hh.grad.view(B, S, d))
+        dh0.view(B, S, d).add_(hz.grad.view(B, S, d))
+        for k in ("gain", "v", "u", "bias"):
+            grads[k].copy_(leaves[k].grad if leaves[k].grad is not None else torch.zeros_like(grads[k]))
 
     def macro_phi_bwd(self, h0, dout, p, recipe_id, stride_id, s_cfg, rstd, pooled, act, dh0, grads, scratch, *, B, S, d, m, R, K):
         self.launches += 1

@@ -41,6 +41,25 @@ GOLDEN_CASES = {
                     hard_negatives=4, random_negatives=4),
         steps=6,
     ),
+    # macro consistency term (lambda_cons) + residual clip of the control variate, two audited samples
+    "small_cons_clip": dict(
+        model=dict(vocab_size=96, d_model=32, n_heads=4, d_ff=64, n_dense_layers=3, n_prelude=1, n_coda=1,
+                   t_max=4, depth_choices=(1, 2, 4), attn_banks=1, ffn_banks=1, head_groups=4, ffn_groups=4,
+                   active_head_groups=2, active_ffn_groups=2, recipe_count=5, macro_rank=8),
+        train=dict(mode="recursive_macro", lr=2e-3, weight_decay=0.1, batch_size=6, seq_len=16, seed=23,
+                   fixed_depth=None, audit_fixed_count_per_batch=3, audit_residual_clip=0.1, lambda_cons=0.05,
+                   grad_clip_norm=1.0),
+        steps=6,
+    ),
+    # audit without gradient correction: the exact subset only feeds metrics and the distillation terms
+    "small_metric_only": dict(
+        model=dict(vocab_size=96, d_model=32, n_heads=4, d_ff=64, n_dense_layers=3, n_prelude=1, n_coda=1,
+                   t_max=4, depth_choices=(1, 2, 4), attn_banks=1, ffn_banks=1, head_groups=4, ffn_groups=4,
+                   active_head_groups=2, active_ffn_groups=2, recipe_count=5, macro_rank=8),
+        train=dict(mode="recursive_macro", lr=2e-3, weight_decay=0.1, batch_size=4, seq_len=16, seed=29,
+                   fixed_depth=None, audit_fixed_count_per_batch=1, audit_mode="metric_only"),
+        steps=6,
+    ),
     # recursive_exact: every sample runs the banked recurrent core (two banks, router-chosen depth)
     "small_exact": dict(
         model=dict(vocab_size=96, d_model=32, n_heads=4, d_ff=64, n_dense_layers=3, n_prelude=1, n_coda=1,
@@ -96,6 +115,21 @@ def svd_ffn_inputs(seed: int = 31, tokens=(3, 11)):
     return dict(x=r(*tokens, c["d"], scale=1.0), w_up=r(c["f"], c["d"], scale=0.2), w_gate=r(c["f"], c["d"], scale=0.2),
                 w_down=r(c["f"], c["d"], scale=0.2), up_a=r(c["d"], c["rank"], scale=0.3), up_b=r(c["rank"], c["f"], scale=0.3),
                 gate_a=r(c["d"], c["rank"], scale=0.3), gate_b=r(c["rank"], c["f"], scale=0.3), probe=r(*tokens, c["d"], scale=1.0))
+
+
+# macro consistency term (reference macro.py:342-359) with weights large enough for the term to matter
+MACRO_CONS = dict(d=32, rank=8, recipes=4, depth_choices=(1, 2, 4, 8), batch=5, seq=12, update_scale=0.05)
+
+
+def macro_cons_inputs() -> dict:
+    import torch
+    c = MACRO_CONS
+    g = torch.Generator().manual_seed(91)
+    R, K, d, m = c["recipes"], len(c["depth_choices"]), c["d"], c["rank"]
+    params = {"macro.d_gain": torch.randn(R, K, d, generator=g) * 0.3, "macro.v": torch.randn(R, K, 3 * d, m, generator=g) * 0.2,
+              "macro.u": torch.randn(R, K, m, d, generator=g) * 0.5, "macro.bias": torch.randn(R, K, d, generator=g) * 0.2}
+    return dict(params=params, h0=torch.randn(c["batch"], c["seq"], d, generator=g),
+                recipe_ids=torch.randint(0, R, (c["batch"],), generator=g))
 
 
 # offline cluster-pool codebook build (reference cli.py:3244-3389, 4741-4771): seeded inputs of one layer

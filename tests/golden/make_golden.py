@@ -46,8 +46,10 @@ def reference_experiment(case: dict, run_dir: str) -> RC.ExperimentConfig:
         seq_len=t["seq_len"], seed=t["seed"], precision="fp32", fixed_depth=t.get("fixed_depth"),
         audit_p_min=p, audit_p_max=p, audit_alpha=0.0, audit_beta=0.0, audit_gamma=0.0,
         audit_fixed_count_per_batch=t.get("audit_fixed_count_per_batch"),
-        audit_mode="gradient_corrected" if audited else "metric_only",
-        audit_gradient_correction=audited, lambda_cons=0.0, grad_clip_norm=t.get("grad_clip_norm"),
+        audit_mode=t.get("audit_mode", "gradient_corrected" if audited else "metric_only"),
+        audit_gradient_correction=audited and t.get("audit_mode", "gradient_corrected") == "gradient_corrected",
+        audit_residual_clip=t.get("audit_residual_clip"), lambda_cons=t.get("lambda_cons", 0.0),
+        grad_clip_norm=t.get("grad_clip_norm"),
         fused_optimizer=False, foreach_optimizer=True, allow_tf32=False, log_every=10_000,
     )
     out = RC.OutputConfig(**case["output"]) if "output" in case else RC.OutputConfig()
@@ -240,6 +242,31 @@ def codebook_vectors() -> dict[str, np.ndarray]:
     return out
 
 
+def macro_consistency_vectors() -> dict[str, np.ndarray]:
+    """MacroOperators.consistency_loss (macro.py:342-359) and its gradients on seeded inputs."""
+    from recursive_training_engine.macro import MacroOperators
+    from tests.golden.cases import MACRO_CONS, macro_cons_inputs
+    c, inp = MACRO_CONS, macro_cons_inputs()
+    mc = RC.ModelConfig(topology="recursive", vocab_size=96, d_model=c["d"], n_heads=4, d_ff=64, n_dense_layers=2, n_prelude=1,
+                        n_coda=1, attn_banks=1, ffn_banks=1, head_groups=4, ffn_groups=4, active_head_groups=2,
+                        active_ffn_groups=2, macro_rank=c["rank"], recipe_count=c["recipes"],
+                        depth_choices=list(c["depth_choices"]), t_max=max(c["depth_choices"]),
+                        macro_update_scale=c["update_scale"])
+    macro = MacroOperators(mc)
+    with torch.no_grad():
+        macro.d_gain.copy_(inp["params"]["macro.d_gain"])
+        macro.v.copy_(inp["params"]["macro.v"])
+        macro.u.copy_(inp["params"]["macro.u"])
+        macro.bias.copy_(inp["params"]["macro.bias"])
+    h0 = inp["h0"].clone().requires_grad_(True)
+    loss = macro.consistency_loss(h0, h0, inp["recipe_ids"])
+    loss.backward()
+    out = {"loss": np.float64(float(loss)), "dh0": h0.grad.numpy().copy()}
+    for name, prm in (("d_gain", macro.d_gain), ("v", macro.v), ("u", macro.u), ("bias", macro.bias)):
+        out[f"grad/{name}"] = prm.grad.numpy().copy()
+    return out
+
+
 def main() -> None:
     torch.set_num_threads(4)
     only = set(sys.argv[1:])                     # e.g. `make_golden.py cluster_pool` rewrites that file alone
@@ -247,7 +274,7 @@ def main() -> None:
         if not only or name in only:
             np.savez_compressed(HERE / f"{name}.npz", **run_case(name, case))
     for name, fn in (("per_op", per_op_vectors), ("cluster_pool", cluster_pool_vectors),
-                     ("svd_ffn", svd_ffn_vectors), ("codebook", codebook_vectors)):
+                     ("svd_ffn", svd_ffn_vectors), ("codebook", codebook_vectors), ("macro_cons", macro_consistency_vectors)):
         if not only or name in only:
             np.savez_compressed(HERE / f"{name}.npz", **fn())
     print("written to", HERE)

@@ -39,6 +39,12 @@ CASES = {
              recipe_count=5, macro_rank=8),
         dict(mode="recursive_macro", lr=2e-3, weight_decay=0.1, batch_size=4, seq_len=16, seed=17, fixed_depth=None,
              audit_fixed_count_per_batch=2, audit_mode="metric_only", audit_gradient_correction=False)),
+    "macro_consistency": (                 # lambda_cons with four depth choices: stride pairs (1,2), (2,4), (4,8)
+        dict(vocab_size=96, d_model=64, n_heads=4, d_ff=128, n_prelude=1, n_coda=1, t_max=8, depth_choices=(1, 2, 4, 8),
+             attn_banks=1, ffn_banks=1, head_groups=4, ffn_groups=4, active_head_groups=2, active_ffn_groups=2,
+             recipe_count=5, macro_rank=8),
+        dict(mode="recursive_macro", lr=2e-3, weight_decay=0.1, batch_size=4, seq_len=16, seed=19, fixed_depth=None,
+             audit_fixed_count_per_batch=1, lambda_cons=2000.0, grad_clip_norm=1.0)),
     "macro_shortlist": (
         dict(vocab_size=96, d_model=64, n_heads=4, d_ff=128, n_prelude=1, n_coda=1, t_max=4, depth_choices=(1, 2, 4),
              attn_banks=1, ffn_banks=1, head_groups=4, ffn_groups=4, active_head_groups=2, active_ffn_groups=2,
@@ -209,3 +215,40 @@ def test_evaluate_is_forward_only_and_matches_the_oracle_forward(name):
         assert torch.equal(eng.params[n], params[n]), n
     assert eng.global_step == 0 and int(eng.plan.step_count.max()) == 0
     assert (eng.audit is not None) == bool(tr.audit_fixed_count_per_batch)
+
+
+def _macro_scaled(params):
+    """Macro-operator weights far from their near-zero initialisation, so that the consistency term and its gradients
+    are of the same order as the rest of the loss."""
+    g = torch.Generator().manual_seed(123)
+    out = {k: v.clone() for k, v in params.items()}
+    out["macro.u"] = torch.randn(out["macro.u"].shape, generator=g) * 0.5
+    out["macro.v"] = torch.randn(out["macro.v"].shape, generator=g) * 0.2
+    out["macro.d_gain"] = torch.randn(out["macro.d_gain"].shape, generator=g) * 0.3
+    out["macro.bias"] = torch.randn(out["macro.bias"].shape, generator=g) * 0.2
+    return out
+
+
+def test_consistency_term_is_material_and_matches_the_oracle():
+    """lambda_cons * mse(Phi_2k(h0,h0), Phi_k(Phi_k(h0,h0),h0)) (macro.py:342-359): loss and every gradient against the
+    oracle with macro weights for which the term dominates the macro operator's gradients."""
+    cfg, ocfg, otr = _pair("macro_consistency")
+    tr = cfg.training
+    params = _macro_scaled(init_parameters(cfg.model, seed=tr.seed, num_clusters=cfg.output.num_clusters))
+    eng = TrainEngine(cfg, params, device="cpu", ops=EmulOps(), use_cuda_graph=False)
+    nc = {**otr.__dict__, "grad_clip_norm": None}
+    with_cons, without = _oracle(cfg, ocfg, O.TrainCfg(**nc), params), _oracle(cfg, ocfg, O.TrainCfg(**{**nc, "lambda_cons": 0.0}), params)
+    stream = O.zipf_tokens(tr.batch_size * tr.seq_len * 3 + 1, cfg.model.vocab_size, seed=tr.seed)
+    batch = next(O.batches(stream, tr.batch_size, tr.seq_len))
+    loss, grads = eng.loss_and_grads(batch)
+    ref_loss, ref_grads, info = with_cons.loss_and_grads(*batch)
+    base_loss, base_grads, _ = without.loss_and_grads(*batch)
+    assert float(info["aux"]["cons"]) > 0.01 * abs(float(base_loss))                 # the term matters
+    assert (ref_grads["macro.u"] - base_grads["macro.u"]).abs().max() > 0.5 * base_grads["macro.u"].abs().max()
+    assert (ref_grads["embed.weight"] - base_grads["embed.weight"]).abs().max() > 0.05 * base_grads["embed.weight"].abs().max()
+    assert abs(loss - float(ref_loss)) < 2e-2 * max(1.0, abs(float(ref_loss)))
+    assert abs(eng.last_consistency - float(info["aux"]["cons"])) <= 2e-2 * float(info["aux"]["cons"])
+    for n, g in grads.items():
+        err = (g - ref_grads[n]).abs().max().item()
+        scale = ref_grads[n].abs().max().item()
+        assert err <= 2e-2 * max(scale, 1e-3) + 2e-4, (n, err, scale)

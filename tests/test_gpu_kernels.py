@@ -537,6 +537,51 @@ def test_macro_phi_fwd_bwd(ops, B, S, d, m, R, tensor):
     _close(gr["v"], leaves["macro.v"].grad, 2e-4, "phi dv")
 
 
+@pytest.mark.parametrize("B,S,d,m,R,tensor", [(3, 16, 64, 8, 4, True), (2, 12, 40, 6, 3, False), (4, 64, 128, 32, 5, True),
+                                              (2, 32, 96, 48, 3, True)])
+def test_macro_phi_on_a_state_other_than_h0(ops, B, S, d, m, R, tensor):
+    """Phi(h, h0) with h != h0 (the second application inside the consistency term, macro.py:342-359): output, the two
+    separate data gradients (dh overwritten, dh0 accumulated into) and the parameter gradients against autograd."""
+    K = 3
+    cfg = O.ModelCfg(d_model=d, macro_rank=m, recipe_count=R, macro_update_scale=0.05)
+    g = torch.Generator().manual_seed(d + m + 1)
+    p = {"macro.d_gain": torch.randn(R, K, d, generator=g) * 0.1, "macro.v": torch.randn(R, K, 3 * d, m, generator=g) * 0.05,
+         "macro.u": torch.randn(R, K, m, d, generator=g) * 0.3, "macro.bias": torch.randn(R, K, d, generator=g) * 0.1}
+    h, h0 = torch.randn(B, S, d, generator=g), torch.randn(B, S, d, generator=g)
+    rid, sid = torch.randint(0, R, (B,), generator=g), torch.randint(0, K, (B,), generator=g)
+    rid[0], sid[0] = rid[-1], sid[-1]
+    dout, seed0 = torch.randn(B, S, d, generator=g), torch.randn(B, S, d, generator=g)
+    leaves = {k: v.clone().requires_grad_(True) for k, v in p.items()}
+    hr, h0r = h.clone().requires_grad_(True), h0.clone().requires_grad_(True)
+    ref = O.macro_phi(leaves, cfg, hr, h0r, rid, sid)
+    ref.backward(dout)
+    e = lambda *s: torch.zeros(*s, device=DEV)  # noqa: E731
+    pd = dict(gain=p["macro.d_gain"].to(DEV), v=p["macro.v"].to(DEV), u=p["macro.u"].to(DEV), bias=p["macro.bias"].to(DEV),
+              scale=torch.ones(R, K, d, device=DEV))
+    out, rstd, pooled, act = e(B * S, d), e(B * S), e(B * d + B * m), e(B * S, m)
+    ri, si = rid.to(DEV, torch.int32), sid.to(DEV, torch.int32)
+    if tensor:
+        pd["wt"] = e(R * K * 4 * d * m)
+        ops.macro_phi_prepare(pd)
+    hd, h0d = h.to(DEV).view(B * S, d), h0.to(DEV).view(B * S, d)
+    ops.macro_phi_fwd_hx(hd, h0d, pd, ri, si, 0.05, out, rstd, pooled, act, B=B, S=S, d=d, m=m, K=K)
+    torch.cuda.synchronize()
+    _close(out.view(B, S, d), ref, 1e-4, "phi(h, h0) out")
+    dh, dh0 = torch.full((B * S, d), 9.0, device=DEV), seed0.to(DEV).view(B * S, d).clone()
+    gr = dict(gain=e(R, K, d), v=e(R, K, 3 * d, m), u=e(R, K, m, d), bias=e(R, K, d))
+    scratch = e(ops.phi_bwd_scratch_floats(B, S, d, m))
+    ops.macro_phi_bwd_hx(hd, h0d, dout.to(DEV).view(B * S, d), pd, ri, si, 0.05, rstd, pooled, act, dh, dh0, gr, scratch,
+                         B=B, S=S, d=d, m=m, R=R, K=K)
+    torch.cuda.synchronize()
+    ops.check_status()
+    _close(dh.view(B, S, d), hr.grad, 2e-4, "phi(h, h0) dh")
+    _close(dh0.view(B, S, d), seed0 + h0r.grad, 2e-4, "phi(h, h0) dh0 (accumulated)")
+    _close(gr["gain"], leaves["macro.d_gain"].grad, 2e-4, "phi(h, h0) dgain")
+    _close(gr["bias"], leaves["macro.bias"].grad, 2e-4, "phi(h, h0) dbias")
+    _close(gr["u"], leaves["macro.u"].grad, 2e-4, "phi(h, h0) du")
+    _close(gr["v"], leaves["macro.v"].grad, 2e-4, "phi(h, h0) dv")
+
+
 # ------------------------------------------------------------------ optimiser
 def test_adamw_multi_tensor_matches_oracle_and_skips_absent(ops):
     from speedup_thingy_b200.ops import AdamWPlan

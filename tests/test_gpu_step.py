@@ -11,7 +11,7 @@ from oracle import rte_oracle as O
 from speedup_thingy_b200.config import ExperimentConfig, ModelConfig, OutputConfig, TrainingConfig
 from speedup_thingy_b200.engine import TrainEngine, init_parameters, parameter_shapes
 from tests.golden.cases import GOLDEN_CASES
-from tests.test_engine_host import CASES, _oracle, _pair, _share_top_clusters
+from tests.test_engine_host import CASES, _macro_scaled, _oracle, _pair, _share_top_clusters
 
 pytestmark = pytest.mark.gpu
 GOLDEN = Path(__file__).resolve().parent / "golden"
@@ -50,6 +50,38 @@ def test_first_step_loss_and_grads_match_oracle(name):
     if not eng.dense:
         assert torch.equal(eng.route["recipe_id"].cpu().long(), info["hot"]["route"]["recipe_id"])
         assert torch.equal(eng.route["depth"].cpu().long(), info["hot"]["route"]["depth"])
+
+
+def test_consistency_term_matches_oracle_with_material_macro_weights():
+    """lambda_cons * mse(Phi_2k(h0,h0), Phi_k(Phi_k(h0,h0),h0)) on the device (three stride pairs, its own stream, Phi on a
+    state other than h0): loss, the term itself and every gradient against the oracle, with macro weights for which the
+    term changes the macro operator's gradients by more than half; then graph replays equal the eager step."""
+    cfg, ocfg, otr = _pair("macro_consistency")
+    tr = cfg.training
+    params = _macro_scaled(init_parameters(cfg.model, seed=tr.seed, num_clusters=cfg.output.num_clusters))
+    eng = TrainEngine(cfg, params, device="cuda:0", use_cuda_graph=False)
+    nc = {**otr.__dict__, "grad_clip_norm": None}
+    with_cons = _oracle(cfg, ocfg, O.TrainCfg(**nc), params)
+    without = _oracle(cfg, ocfg, O.TrainCfg(**{**nc, "lambda_cons": 0.0}), params)
+    batch = next(_stream(cfg, 2))
+    loss, grads = eng.loss_and_grads(batch)
+    ref_loss, ref_grads, info = with_cons.loss_and_grads(*batch)
+    _, base_grads, _ = without.loss_and_grads(*batch)
+    assert (ref_grads["macro.u"] - base_grads["macro.u"]).abs().max() > 0.5 * base_grads["macro.u"].abs().max()
+    assert abs(loss - float(ref_loss)) <= 1e-2 * abs(float(ref_loss))
+    assert abs(eng.last_consistency - float(info["aux"]["cons"])) <= 2e-2 * float(info["aux"]["cons"])
+    for n, g in grads.items():
+        err = (g.cpu() - ref_grads[n]).abs().max().item()
+        scale = ref_grads[n].abs().max().item()
+        assert err <= 2e-2 * max(scale, 1e-3) + 2e-4, (n, err, scale)
+    # the captured step (the branch runs on its own stream inside the graph) follows the eager one
+    e1 = TrainEngine(cfg, params, device="cuda:0", use_cuda_graph=False)
+    e2 = TrainEngine(cfg, params, device="cuda:0", use_cuda_graph=True)
+    it1, it2 = _stream(cfg, 6), _stream(cfg, 6)
+    for _ in range(5):
+        a, b = e1.train_step(next(it1)).loss, e2.train_step(next(it2)).loss
+        assert abs(a - b) <= 1e-5 * abs(a), (a, b)
+    assert e2._graph is not None
 
 
 def test_c1_loss_curve_matches_reference_golden():

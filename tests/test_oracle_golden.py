@@ -174,3 +174,21 @@ def test_codebook_build_restatement_matches_reference_golden():
     score = torch.zeros(c["f"]).index_add_(0, ids.reshape(-1), weight)
     boundary = min(float(score[i]) for i in ref)
     assert all(abs(float(score[i]) - boundary) < 1e-6 for i in mine ^ ref), sorted(mine ^ ref)
+
+
+def test_macro_consistency_loss_matches_reference_golden():
+    """O.macro_consistency_loss against MacroOperators.consistency_loss (value, d h0, every parameter gradient)."""
+    from tests.golden.cases import MACRO_CONS, macro_cons_inputs
+    gold = np.load(GOLDEN / "macro_cons.npz")
+    c, inp = MACRO_CONS, macro_cons_inputs()
+    cfg = O.ModelCfg(d_model=c["d"], macro_rank=c["rank"], recipe_count=c["recipes"], depth_choices=c["depth_choices"],
+                     t_max=max(c["depth_choices"]), macro_update_scale=c["update_scale"])
+    leaves = {k: v.clone().requires_grad_(True) for k, v in inp["params"].items()}
+    h0 = inp["h0"].clone().requires_grad_(True)
+    loss = O.macro_consistency_loss(leaves, cfg, h0, inp["recipe_ids"])
+    loss.backward()
+    assert float(gold["loss"]) > 1e-4                      # the case is not a degenerate one
+    assert abs(float(loss) - float(gold["loss"])) <= 1e-5 * float(gold["loss"])
+    np.testing.assert_allclose(h0.grad.numpy(), gold["dh0"], rtol=1e-4, atol=1e-8)
+    for name in ("d_gain", "v", "u", "bias"):
+        np.testing.assert_allclose(leaves[f"macro.{name}"].grad.numpy(), gold[f"grad/{name}"], rtol=1e-4, atol=1e-8)
