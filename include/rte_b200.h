@@ -521,8 +521,36 @@ int rte_kl_distill_grad(const void* hot_logits, const void* exact_logits, float 
  * For each audited sample j (hot row idx[j]) with |exact - hot| <= clip: f_hot = 1 - inv_p, f_exact = 1; otherwise
  * f_hot = 1, f_exact = 0 -- the factors to apply (rte_scale_rows_bf16) to cross-entropy gradients that were written
  * with the weights 1 (hot) and 1/p (exact).                                                                        */
-int rte_audit_clip(const float* hot_loss, const float* exact_loss, const int32_t* idx, int32_t n, float inv_p, float clip,
-                   float* f_hot, float* f_exact, rte_stream_t stream);
+int rte_audit_clip(const float* hot_loss, const float* exact_loss, const int32_t* idx, int32_t n, float inv_p,
+                   const float* inv_p_slot /* per-sample 1/p, or NULL: inv_p for all */, float clip, float* f_hot,
+                   float* f_exact, rte_stream_t stream);
+/* Bernoulli audit sampler with adaptive probability and cap (AuditEngine.compute_audit_prob / sample_mask_with_prob /
+ * _update_audit_coverage, audit.py:62-132), on the device so that the audited subset can depend on this step's routing:
+ *   p_b = clamp(p_min + alpha * entropy_b * inv_r_plus_k + beta * recent[0] + gamma * deficit(recipe_b), p_min, p_max),
+ *   audited_b = u_b < p_b (u: the uniforms of torch.bernoulli, drawn by the host from the step's seed); with cap >= 0 and
+ *   more candidates than cap, the candidates at positions perm_table[candidates - cap - 1][0..cap) of the ascending
+ *   candidate list, inclusion probability p_b * cap / candidates.
+ * The replay has n_cap slots: idx[j] = idx_scatter[j] = j-th audited sample (ascending), valid[j] = 1, inv_p[j] = 1 / p_inc,
+ * dist_scale[j] = n_cap / audited, row_weight_a[j] = w0 / p_inc; unused slots: idx 0 (gathers stay in range),
+ * idx_scatter -1 (rte_scatter_add_rows_f32, rte_add_rows_f32_to_bf16 and rte_scale_rows_bf16 skip negative
+ * indices), weights 0.  row_weight[b] =
+ * w0 * (1 - 1/p_inc) on audited rows when weight_mode = 1, else w0.  ema[R] (audit-coverage average) is read, then
+ * updated.  stats = (candidates, audited, mean requested p, mean inclusion p).  More audited samples than n_cap set
+ * *status to 202.  B <= 1024, R <= 64.                                                                              */
+typedef struct rte_audit_sample_params {
+  float p_min, p_max, alpha, beta, gamma, coverage_min, coverage_beta, inv_r_plus_k, w0;
+  int32_t B, R, cap, n_cap, weight_mode;
+} rte_audit_sample_params;
+int rte_audit_sample_bernoulli(const float* entropy, const int32_t* recipe_id, const float* u, const int32_t* perm_table,
+                               float* ema, const float* recent, const rte_audit_sample_params* prm, int32_t* idx,
+                               int32_t* idx_scatter, float* valid, float* inv_p, float* dist_scale, float* row_weight, float* row_weight_a,
+                               float* stats, int32_t* status, rte_stream_t stream);
+/* x[j, 0..row_len) *= factor[j], j < n (fp32).                                                                      */
+int rte_scale_rows_f32(float* x, const float* factor, int32_t n, int64_t row_len, rte_stream_t stream);
+/* recent[0] = max(1 - mean over valid slots of cosine(hot_end_j, exact_end_j), 0) (audit.py:213-218; rows of row_len
+ * floats, F.cosine_similarity with eps 1e-8); unchanged when no slot is valid.  cos_scratch: n floats.              */
+int rte_audit_recent_residual(const float* hot_end, const float* exact_end, const float* valid, int32_t n, int64_t row_len,
+                              float* cos_scratch, float* recent, rte_stream_t stream);
 /* x[row_of(r) * ld + c] = bf16(x[...] * scale[r / S]),  r < rows, c < V;  row_of(r) = idx ? idx[r / S] * S + r % S : r */
 int rte_scale_rows_bf16(void* x_bf16, int32_t ld, const int32_t* idx, int32_t S, const float* scale, int32_t rows, int32_t V,
                         rte_stream_t stream);

@@ -85,6 +85,13 @@ class TrainCfg:
     audit_fixed_count_per_batch: int | None = None  # None + p=0 -> no audit
     audit_mode: str = "gradient_corrected"
     audit_residual_clip: float | None = None
+    audit_sampler: str = "fixed_count"              # or "bernoulli": adaptive probability, optional cap (audit.py:79-132)
+    audit_p_min: float = 0.0
+    audit_p_max: float = 0.0
+    audit_alpha: float = 0.08
+    audit_beta: float = 0.08
+    audit_gamma: float = 0.08
+    audit_cap: int | None = None
     lambda_depth: float = 1e-4
     lambda_load: float = 1e-2
     lambda_cover: float = 1e-2
@@ -635,9 +642,35 @@ def audit_choice(n: int, k: int, seed: int) -> torch.Tensor:
     return torch.randperm(n, generator=gen)[:k]
 
 
+def audit_probability(tr: TrainCfg, route: dict, recent_residual: float, audit_ema: torch.Tensor) -> torch.Tensor:
+    """audit.py:79-97: requested audit probability per sample from the router's entropy, the residual seen at the last
+    audit and how far the sample's recipe is below its audit-coverage floor."""
+    r_plus_k = route["recipe_logits"].shape[-1] + route["depth_logits"].shape[-1]
+    uncertainty = route["router_entropy"].detach() / r_plus_k
+    deficit = (tr.coverage_min - audit_ema[route["recipe_id"]]).clamp_min(0.0) / max(tr.coverage_min, 1e-12)
+    prob = tr.audit_p_min + tr.audit_alpha * uncertainty + tr.audit_beta * recent_residual + tr.audit_gamma * deficit
+    return prob.clamp(tr.audit_p_min, tr.audit_p_max)
+
+
+def audit_sample_bernoulli(prob: torch.Tensor, seed: int, cap: int | None) -> tuple[torch.Tensor, torch.Tensor]:
+    """audit.py:117-132: Bernoulli draws from a seeded CPU generator; more than `cap` hits are thinned to `cap` by a
+    seeded permutation of the hit list, and the inclusion probability becomes p * cap / hits."""
+    gen = torch.Generator().manual_seed(seed)
+    mask = torch.bernoulli(prob, generator=gen).bool()
+    inclusion = prob.clone()
+    if cap is not None and int(mask.sum()) > cap:
+        selected = mask.nonzero(as_tuple=False).flatten()
+        perm = torch.randperm(selected.numel(), generator=gen)
+        capped = torch.zeros_like(mask)
+        capped[selected[perm[:cap]]] = True
+        inclusion = prob * (float(cap) / float(selected.numel()))
+        mask = capped
+    return mask, inclusion
+
+
 def macro_step_loss(p: dict, cfg: ModelCfg, tr: TrainCfg, tokens: torch.Tensor, targets: torch.Tensor,
                     step: int, usage_ema: torch.Tensor, oc: OutputCfg | None = None,
-                    top_clusters: torch.Tensor | None = None) -> tuple[torch.Tensor, dict]:
+                    top_clusters: torch.Tensor | None = None, audit_state: dict | None = None) -> tuple[torch.Tensor, dict]:
     """training.py:1336-1392 + audit.py:245-387 (fixed-count sampler,
     the three audit modes, residual clip, consistency term)."""
     shortlist = tr.mode == "recursive_macro_shortlist"
@@ -647,12 +680,20 @@ def macro_step_loss(p: dict, cfg: ModelCfg, tr: TrainCfg, tokens: torch.Tensor, 
     aux: dict[str, torch.Tensor] = {}
     info: dict[str, Any] = dict(hot=hot)
     k = tr.audit_fixed_count_per_batch or 0
-    if k > 0:
-        b = tokens.shape[0]
+    b = tokens.shape[0]
+    mask = p_inc = None
+    if tr.audit_sampler == "bernoulli" and tr.audit_p_max > 0:
+        state = audit_state if audit_state is not None else {}
+        ema = state.setdefault("audit_ema", torch.zeros(cfg.recipe_count))
+        prob = audit_probability(tr, hot["route"], float(state.get("recent_residual", 0.0)), ema)
+        mask, p_inc = audit_sample_bernoulli(prob.detach().float(), tr.seed + 10_000 + step, tr.audit_cap)
+        info.update(audit_prob=prob)
+    elif k > 0:
         chosen = audit_choice(b, min(k, b), tr.seed + 10_000 + step)
         mask = torch.zeros(b, dtype=torch.bool)
         mask[chosen] = True
-        p_inc = float(min(k, b)) / float(b)
+        p_inc = torch.full((b,), float(min(k, b)) / float(b))
+    if mask is not None and bool(mask.any()):
         route = {key: val[mask] for key, val in hot["route"].items()}
         exact = exact_from_h0(p, cfg, hot["h0"][mask], targets[mask], route)
         hot_subset = hot["loss_per_sample"][mask]
@@ -660,10 +701,19 @@ def macro_step_loss(p: dict, cfg: ModelCfg, tr: TrainCfg, tokens: torch.Tensor, 
         if tr.audit_residual_clip is not None:
             residual = residual.clamp(-tr.audit_residual_clip, tr.audit_residual_clip)
         if tr.audit_mode == "gradient_corrected":
-            corrected[mask] = hot_subset + residual / max(p_inc, 1e-12)
+            corrected[mask] = hot_subset + residual / p_inc[mask].clamp_min(1e-12)
         aux = macro_distill_loss(tr, hot["recurrent_hidden"][mask], exact["recurrent_hidden"],
                                  hot["logits"][mask], exact["logits"], hot["h0"][mask])
-        info.update(exact=exact, mask=mask)
+        info.update(exact=exact)
+        if audit_state is not None:          # audit.py:213-218: the residual the next step's probabilities see
+            cos = F.cosine_similarity(hot["recurrent_hidden"][mask].detach().flatten(1),
+                                      exact["recurrent_hidden"].detach().flatten(1), dim=-1, eps=1e-8).mean()
+            audit_state["recent_residual"] = float((1.0 - cos).clamp_min(0))
+    if mask is not None:
+        info.update(mask=mask, p_inc=p_inc)
+        if audit_state is not None and "audit_ema" in audit_state:        # audit.py:70-77
+            counts = torch.bincount(hot["route"]["recipe_id"][mask].long(), minlength=cfg.recipe_count).float()
+            audit_state["audit_ema"].mul_(tr.coverage_beta).add_(counts / counts.sum().clamp_min(1.0), alpha=1.0 - tr.coverage_beta)
     if tr.lambda_cons != 0.0:       # audit.py:370-379: on every step of the macro modes, audited or not
         aux = dict(aux, cons=tr.lambda_cons * macro_consistency_loss(p, cfg, hot["h0"], hot["route"]["recipe_id"]))
     aux_router = router_aux_losses(tr, hot["route"]["recipe_probs"], hot["route"]["expected_depth"], usage_ema)
@@ -725,12 +775,16 @@ class OracleTrainer:
     opt_state: dict = field(default_factory=dict)
     oc: OutputCfg | None = None
     top_clusters: torch.Tensor | None = None      # test hook: shortlist routing injected for the next step
+    audit_state: dict = field(default_factory=dict)       # Bernoulli sampler: recent residual, audit-coverage average
 
     def __post_init__(self) -> None:
         if self.usage_ema is None:
             self.usage_ema = torch.zeros(self.cfg.recipe_count)
 
-    def loss_and_grads(self, tokens: torch.Tensor, targets: torch.Tensor):
+    def loss_and_grads(self, tokens: torch.Tensor, targets: torch.Tensor, commit: bool = False):
+        """`commit`: let the step advance the Bernoulli sampler's state (what `train_step` does); a bare call leaves it."""
+        import copy
+        state = self.audit_state if commit else copy.deepcopy(self.audit_state)
         leaves = {k: v.detach().clone().requires_grad_(True) for k, v in self.params.items()}
         if self.cfg.topology == "dense":
             loss, info = dense_step_loss(leaves, self.cfg, tokens, targets)
@@ -738,7 +792,7 @@ class OracleTrainer:
             loss, info = exact_step_loss(leaves, self.cfg, self.tr, tokens, targets, self.usage_ema)
         else:
             loss, info = macro_step_loss(leaves, self.cfg, self.tr, tokens, targets, self.global_step, self.usage_ema,
-                                         self.oc, self.top_clusters)
+                                         self.oc, self.top_clusters, audit_state=state)
         loss.backward()
         grads = {k: v.grad for k, v in leaves.items() if v.grad is not None}
         if self.tr.grad_clip_norm is not None:  # training.py:456-462, before the optimiser reads them
@@ -748,7 +802,7 @@ class OracleTrainer:
         return loss.detach(), grads, info
 
     def train_step(self, tokens: torch.Tensor, targets: torch.Tensor) -> float:
-        loss, grads, info = self.loss_and_grads(tokens, targets)
+        loss, grads, info = self.loss_and_grads(tokens, targets, commit=True)
         self.last_info = info            # what the step decided (routing, audited subset), for the parity tests
         for name, g in grads.items():
             st = self.opt_state.setdefault(name, dict(step=0, m=torch.zeros_like(g), v=torch.zeros_like(g)))

@@ -77,6 +77,12 @@ class PeerComm(C.Structure):
                 ("world", c_i32), ("rank", c_i32)]
 
 
+class AuditSampleParams(C.Structure):
+    _fields_ = [(n, C.c_float) for n in ("p_min", "p_max", "alpha", "beta", "gamma", "coverage_min", "coverage_beta",
+                                         "inv_r_plus_k", "w0")] + \
+               [(n, c_i32) for n in ("B", "R", "cap", "n_cap", "weight_mode")]
+
+
 class AdamWExtras(C.Structure):
     _fields_ = [("skip", c_vp), ("metric_partial", c_vp), ("metric_group", c_vp), ("metric_out", c_vp),
                 ("n_metric_groups", c_i32)]
@@ -165,7 +171,11 @@ PROTOTYPES = {
     "rte_macro_distill": (C.c_int, [c_vp, c_vp, c_vp, c_f32, c_f32, c_f32, c_f32, c_vp, c_vp, c_i32, c_i32, c_i32, c_vp]),
     "rte_kl_distill": (C.c_int, [c_vp, c_vp, c_f32, c_f32, c_vp, c_i32, c_vp, c_i32, c_vp, c_i32, c_i32, c_vp]),
     "rte_kl_distill_grad": (C.c_int, [c_vp, c_vp, c_f32, c_f32, c_vp, c_vp, c_i32, c_i32, c_vp]),
-    "rte_audit_clip": (C.c_int, [c_vp, c_vp, c_vp, c_i32, C.c_float, C.c_float, c_vp, c_vp, c_vp]),
+    "rte_audit_clip": (C.c_int, [c_vp, c_vp, c_vp, c_i32, C.c_float, c_vp, C.c_float, c_vp, c_vp, c_vp]),
+    "rte_audit_sample_bernoulli": (C.c_int, [c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, P(AuditSampleParams), c_vp, c_vp, c_vp, c_vp,
+                                             c_vp, c_vp, c_vp, c_vp, c_vp, c_vp]),
+    "rte_scale_rows_f32": (C.c_int, [c_vp, c_vp, c_i32, c_i64, c_vp]),
+    "rte_audit_recent_residual": (C.c_int, [c_vp, c_vp, c_vp, c_i32, c_i64, c_vp, c_vp, c_vp]),
     "rte_scale_rows_bf16": (C.c_int, [c_vp, c_i32, c_vp, c_i32, c_vp, c_i32, c_i32, c_vp]),
     "rte_add_rows_f32_to_bf16": (C.c_int, [c_vp, c_i32, c_vp, c_i32, c_vp, c_i32, c_i32, c_vp]),
     "rte_normalize_rows_f32": (C.c_int, [c_vp, c_vp, c_i32, c_i32, c_vp]),

@@ -76,6 +76,9 @@ class AuditReplay:
         f32, bf, i32 = torch.float32, torch.bfloat16, torch.int32
         e = lambda *shape, dtype=f32: torch.zeros(*shape, dtype=dtype, device=dev)  # noqa: E731
         self.p_inc = float(k) / float(eng.B)                              # inclusion probability k/n (audit.py:116)
+        # Bernoulli sampler (audit.py:79-132): the subset is drawn ON THE DEVICE from this step's routing; `k` is then
+        # the capacity of the replay's buffers, slots beyond the audited count carry weight 0
+        self.bernoulli = (not direct_grads) and getattr(eng, "audit_bernoulli", False)
         self.grad = direct_grads or eng.tr.audit_mode == "gradient_corrected"      # does the replay carry gradients
         self.clip = eng.tr.audit_residual_clip if (self.grad and not direct_grads) else None
         self.f_hot, self.f_exact = e(n), e(n)                             # residual clip: per-sample gradient factors
@@ -104,6 +107,16 @@ class AuditReplay:
         self.terms, self.dhot_extra, self.kl_rows, self.kl_sum = e(n, 4), e(Ma, d), e(Ma), e(1)
         self.dkl = e(Ma, V)
         self.row_weight_a = torch.full((n,), 1.0 / (eng.B * eng.S * eng.loss_div) / self.p_inc, dtype=f32, device=dev)
+        self.idx_scatter = self.idx                    # Bernoulli: a second index list with -1 on unused slots
+        if self.bernoulli:
+            tr, B = eng.tr, eng.B
+            self.cap = None if tr.audit_cap is None else int(tr.audit_cap)
+            self.idx_scatter = e(n, dtype=i32)
+            self.valid, self.dist_scale, self.cos = e(n), e(n), e(n)
+            self.u_dev = e(B)
+            self.perm_dev = e(max((B - self.cap) * self.cap, 1), dtype=i32) if (self.cap is not None and self.cap < B) else None
+            self.audit_ema = e(cfg.recipe_count)       # recipe_audit_ema (audit.py:62-77), starts at zero
+            self.recent = e(1)                         # recent_residual (audit.py:213-218)
         # backward scratch
         self.dn_f32, self.dh0_acc, self.dcur, self.dalt = e(Ma, d), e(Ma, d), e(Ma, d), e(Ma, d)
         self.d16b = e(Ma, d, dtype=bf)
@@ -164,6 +177,8 @@ class AuditReplay:
         a pinned staging pair.  Three pairs rotate: with up to two steps queued on the device, the pair written here for
         step i+2 is the one step i-1 used, whose copy has completed by the time that step was collected."""
         eng = self.eng
+        if self.bernoulli:
+            return self._prepare_bernoulli(step_seed)
         if self._stage is None:
             pin = eng.device.type == "cuda"
             self._stage = [(torch.empty(self.k, dtype=torch.int32, pin_memory=pin),
@@ -182,12 +197,59 @@ class AuditReplay:
         self._prepared = (step_seed, chosen, h_idx, h_rw)
         self._stage_next = (self._stage_next + 1) % 3
 
+    def _prepare_bernoulli(self, step_seed: int) -> None:
+        """Host half of the Bernoulli sampler: the uniforms `torch.bernoulli(p, generator)` compares p with (the same
+        CPU generator stream as `torch.rand`), and -- with a cap -- for every possible candidate count above the cap the
+        first `cap` entries of the permutation the reference would draw next from that generator (audit.py:117-131)."""
+        eng, B = self.eng, self.eng.B
+        if self._stage is None:
+            pin = eng.device.type == "cuda"
+            rows = max((B - self.cap) * self.cap, 1) if (self.cap is not None and self.cap < B) else 1
+            self._stage = [(torch.empty(B, dtype=torch.float32, pin_memory=pin),
+                            torch.zeros(rows, dtype=torch.int32, pin_memory=pin)) for _ in range(3)]
+            self._stage_next = 0
+        gen = torch.Generator().manual_seed(step_seed)
+        h_u, h_perm = self._stage[self._stage_next]
+        h_u.copy_(torch.rand(B, generator=gen))
+        if self.perm_dev is not None:
+            state = gen.get_state()
+            table = h_perm.view(B - self.cap, self.cap)
+            for count in range(self.cap + 1, B + 1):
+                g2 = torch.Generator()
+                g2.set_state(state)
+                table[count - self.cap - 1].copy_(torch.randperm(count, generator=g2)[: self.cap])
+        self._prepared = (step_seed, None, h_u, h_perm)
+        self._stage_next = (self._stage_next + 1) % 3
+
+    def sample(self) -> None:
+        """Device half of the Bernoulli sampler, after the router: audit probabilities, the subset, its per-sample
+        inclusion probabilities, the loss weights of the hot rows and of the replay, the coverage average."""
+        eng = self.eng
+        tr, cfg = eng.tr, eng.cfg
+        w0 = 1.0 / (eng.B * eng.S * eng.loss_div)
+        prm = dict(p_min=tr.audit_p_min, p_max=tr.audit_p_max, alpha=tr.audit_alpha, beta=tr.audit_beta, gamma=tr.audit_gamma,
+                   coverage_min=tr.coverage_min, coverage_beta=tr.coverage_beta,
+                   inv_r_plus_k=1.0 / (cfg.recipe_count + len(cfg.depth_choices)), w0=w0, B=eng.B, R=cfg.recipe_count,
+                   cap=-1 if self.cap is None else self.cap, n_cap=self.n,
+                   weight_mode=1 if (self.grad and self.clip is None) else 0)
+        eng.ops.audit_sample_bernoulli(eng.route["router_entropy"], eng.route["recipe_id"], self.u_dev, self.perm_dev,
+                                       self.audit_ema, self.recent, prm, self.idx, self.idx_scatter, self.valid, self.inv_p,
+                                       self.dist_scale, eng.row_weight, self.row_weight_a, self.stats)
+
     def choose(self, step_seed: int) -> None:
         """Fixed-count sampler: first k entries of a seeded CPU permutation (audit.py:99-116); writes the subset
         indices and the control-variate weights of the hot rows."""
         eng = self.eng
         if self._prepared is None or self._prepared[0] != step_seed:
             self.prepare(step_seed)
+        if self.bernoulli:
+            _, _, h_u, h_perm = self._prepared
+            self._prepared = None
+            self.u_dev.copy_(h_u, non_blocking=True)
+            if self.perm_dev is not None:
+                self.perm_dev.copy_(h_perm, non_blocking=True)
+            self.last_chosen = None
+            return
         _, chosen, h_idx, h_rw = self._prepared
         self._prepared = None
         self.idx.copy_(h_idx, non_blocking=True)
@@ -270,6 +332,10 @@ class AuditReplay:
         tr, w = eng.tr, 1.0 / eng.loss_div
         o.macro_distill(self.hot_end, self.h[T], self.h0a, tr.lambda_delta_dir * w, tr.lambda_delta_rms * w,
                         tr.lambda_endpoint_normed * w, tr.lambda_endpoint_raw * w, self.terms, self.dhot_extra, n, S, d)
+        if self.bernoulli:
+            # the kernel averaged over all n slots: n / audited on the audited samples' rows, 0 on the others
+            o.scale_rows_f32(self.dhot_extra, self.dist_scale, n, S * d)
+            o.audit_recent_residual(self.hot_end, self.h[T], self.valid, n, S * d, self.cos, self.recent)
 
     def forward_kl(self) -> None:
         """KL-distillation term between the saved hot logits of the audited rows and the replay's logits; its gradient
@@ -281,13 +347,16 @@ class AuditReplay:
         temp = max(float(tr.distill_temperature), 1e-6)
         if not eng.shortlist:      # the shortlist head keeps no full hot logits, so the KL term is absent (models.py:698-703)
             o.kl_distill_grad(self.hot_logits, self.logits, temp, tr.lambda_kl * w * temp / n, self.dkl, self.kl_rows, Ma, V)
+            if self.bernoulli:
+                o.scale_rows_f32(self.dkl, self.dist_scale, n, self.S * V)
+                o.scale_rows_f32(self.kl_rows, self.valid, n, self.S)
             o.segment_sum(self.kl_rows, self.kl_sum, 1, Ma)
 
     def add_kl_grad(self) -> None:
         """Hot-pass side of `forward_kl`: dlogits[audited rows] += dkl."""
         eng = self.eng
         if not eng.shortlist:
-            eng.ops.add_rows_to_bf16(eng.logits, self.idx, self.S, self.dkl, self.Ma, eng.cfg.vocab_size)
+            eng.ops.add_rows_to_bf16(eng.logits, self.idx_scatter, self.S, self.dkl, self.Ma, eng.cfg.vocab_size)
 
     def forward_ce(self) -> None:
         """The replay's own cross entropy (its logits become dlogits in place)."""
@@ -305,14 +374,14 @@ class AuditReplay:
         eng = self.eng
         o = eng.ops
         o.audit_clip(eng.loss_per_sample, self.exact_loss, self.idx, self.n, 1.0 / self.p_inc, float(self.clip),
-                     self.f_hot, self.f_exact)
+                     self.f_hot, self.f_exact, inv_p_slot=self.inv_p if self.bernoulli else None)
         o.scale_rows_bf16(self.logits, None, self.S, self.f_exact, self.Ma, eng.cfg.vocab_size)
 
     def clip_hot(self) -> None:
         """Hot side of `clip_exact`: the audited rows of the hot dlogits (written with weight 1) get 1 - 1/p inside the
         clip and keep 1 outside."""
         eng = self.eng
-        eng.ops.scale_rows_bf16(eng.logits, self.idx, self.S, self.f_hot, self.Ma, eng.cfg.vocab_size)
+        eng.ops.scale_rows_bf16(eng.logits, self.idx_scatter, self.S, self.f_hot, self.Ma, eng.cfg.vocab_size)
 
     def save_hot_logits(self) -> None:
         """Copies the audited rows of the hot logits before the cross-entropy kernel overwrites them."""
@@ -522,18 +591,20 @@ class AuditReplay:
             lo, hi = self.prelude_range
             o.add_(eng.grad_flat[lo:hi], self.prelude_flat)
         else:
-            o.scatter_add_rows(dh0_hot, self.idx, self.dh0_acc, n, S * d)
-            o.scatter_add_rows(dh0_hot, self.idx, self.dh_first, n, S * d)
+            o.scatter_add_rows(dh0_hot, self.idx_scatter, self.dh0_acc, n, S * d)
+            o.scatter_add_rows(dh0_hot, self.idx_scatter, self.dh_first, n, S * d)
 
     # ------------------------------------------------------------------ reporting
     def loss_terms(self, hot_per_sample: torch.Tensor, host: dict, chosen: torch.Tensor | None = None) -> dict[str, float]:
         """Host-side assembly of the audited quantities for the reported loss (training.py:1381-1385) from the
         step's fetched results (`terms`, `exact_loss`, `kl_sum` already on the host)."""
         tr, n, Ma, d = self.eng.tr, self.n, self.Ma, self.eng.cfg.d_model
+        temp = max(float(tr.distill_temperature), 1e-6)
+        if self.bernoulli:
+            return self._loss_terms_bernoulli(hot_per_sample, host, temp)
         terms = host["terms"]
         exact = host["exact_loss"].clone()
         hot = hot_per_sample[self.last_chosen if chosen is None else chosen]
-        temp = max(float(tr.distill_temperature), 1e-6)
         aux = dict(delta_dir=tr.lambda_delta_dir * float(terms[:, 0].mean()),
                    delta_rms=tr.lambda_delta_rms * float(terms[:, 1].mean()),
                    endpoint_normed=tr.lambda_endpoint_normed * float(terms[:, 2].sum()) / (Ma * d),
@@ -545,3 +616,27 @@ class AuditReplay:
         # the control variate is part of the loss only under gradient correction; its value is reported either way
         corr = float((residual / self.p_inc).sum())
         return dict(correction=corr if self.grad else 0.0, correction_metric=corr, exact=exact, aux=aux)
+
+    def _loss_terms_bernoulli(self, hot_per_sample: torch.Tensor, host: dict, temp: float) -> dict:
+        """`loss_terms` for the Bernoulli sampler: the audited samples, their count and inclusion probabilities come
+        back from the device with the step's results; every mean runs over the audited samples (none: all terms 0)."""
+        tr, S, d = self.eng.tr, self.S, self.eng.cfg.d_model
+        stats = host["audit_stats"]
+        a = min(int(round(float(stats[1]))), self.n)
+        chosen = host["audit_idx"][:a].long()
+        out = dict(chosen=chosen, candidates=int(round(float(stats[0]))), audited=a, p_requested=float(stats[2]),
+                   p_inclusion=float(stats[3]))
+        zero = dict(delta_dir=0.0, delta_rms=0.0, endpoint_normed=0.0, endpoint_raw=0.0, kl=0.0)
+        if a == 0:
+            return dict(correction=0.0, correction_metric=0.0, exact=host["exact_loss"][:0].clone(), aux=zero, **out)
+        terms, exact, inv_p = host["terms"][:a], host["exact_loss"][:a].clone(), host["audit_inv_p"][:a]
+        aux = dict(delta_dir=tr.lambda_delta_dir * float(terms[:, 0].mean()),
+                   delta_rms=tr.lambda_delta_rms * float(terms[:, 1].mean()),
+                   endpoint_normed=tr.lambda_endpoint_normed * float(terms[:, 2].sum()) / (a * S * d),
+                   endpoint_raw=tr.lambda_endpoint_raw * float(terms[:, 3].sum()) / (a * S * d),
+                   kl=tr.lambda_kl * float(host["kl_sum"]) / a * temp * temp)
+        residual = exact - hot_per_sample[chosen]
+        if self.clip is not None:
+            residual = residual.clamp(-float(self.clip), float(self.clip))
+        corr = float((residual * inv_p).sum())
+        return dict(correction=corr if self.grad else 0.0, correction_metric=corr, exact=exact, aux=aux, **out)

@@ -352,9 +352,6 @@ def unsupported(config: ExperimentConfig) -> list[str]:
         no("model", "tie_embeddings", "only tied input / output embeddings")
     recursive = t.mode in ("recursive_macro", "recursive_macro_shortlist")
     if recursive and t.audits_enabled:
-        if t.audit_sampler != "fixed_count":
-            no("training", "audit_sampler", "only the fixed-count sampler (audit_fixed_count_per_batch); "
-                                            "audit_p_max=0 or audit_cap=0 switches audits off")
         if t.audit_mode not in ("gradient_corrected", "metric_only", "distill_only"):
             no("training", "audit_mode", "one of gradient_corrected, metric_only, distill_only")
         if t.audit_schedule_enabled:

@@ -35,6 +35,7 @@ __global__ void scatter_add_rows_kernel(float* __restrict__ dst, const int32_t* 
   const long long total = (long long)n * row;
   for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
     const int r = int(i / row);
+    if (idx[r] < 0) continue;                       // unused slot of a capacity-padded subset
     dst[(long long)idx[r] * row + (i % row)] += src[i];
   }
 }
@@ -269,6 +270,7 @@ __global__ void add_rows_f32_to_bf16_kernel(__nv_bfloat16* __restrict__ dst, int
   const long long total = (long long)rows * V;
   for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
     const int row = int(i / V), c = int(i % V);
+    if (idx[row / S] < 0) continue;                 // unused slot of a capacity-padded subset
     __nv_bfloat16* q = dst + ((size_t)idx[row / S] * S + (row % S)) * ld + c;
     *q = __float2bfloat16_rn(__bfloat162float(*q) + src[i]);
   }
@@ -279,10 +281,11 @@ __global__ void add_rows_f32_to_bf16_kernel(__nv_bfloat16* __restrict__ dst, int
 // launches have already written their gradients with the weights 1 (hot) and 1/p (exact), so the factors are
 //   f_hot = inside ? 1 - 1/p : 1,   f_exact = inside ? 1 : 0.
 __global__ void audit_clip_kernel(const float* __restrict__ hot_loss, const float* __restrict__ exact_loss,
-                                  const int32_t* __restrict__ idx, int n, float inv_p, float clip,
-                                  float* __restrict__ f_hot, float* __restrict__ f_exact) {
+                                  const int32_t* __restrict__ idx, int n, float inv_p, const float* __restrict__ inv_p_slot,
+                                  float clip, float* __restrict__ f_hot, float* __restrict__ f_exact) {
   const int j = blockIdx.x * blockDim.x + threadIdx.x;
   if (j >= n) return;
+  if (inv_p_slot) inv_p = inv_p_slot[j];            // per-sample inclusion probabilities (Bernoulli sampler)
   const float r = exact_loss[j] - hot_loss[idx[j]];
   const bool inside = fabsf(r) <= clip;             // (a NaN residual counts as clipped: no gradient through it)
   f_hot[j] = inside ? 1.f - inv_p : 1.f;
@@ -296,11 +299,135 @@ __global__ void scale_rows_bf16_kernel(__nv_bfloat16* __restrict__ x, int ld, co
   for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
     const int row = int(i / V), c = int(i % V);
     const float f = scale[row / S];
-    if (f == 1.f) continue;
+    if (f == 1.f || (idx && idx[row / S] < 0)) continue;
     const size_t phys = idx ? (size_t)idx[row / S] * S + (row % S) : (size_t)row;
     __nv_bfloat16* q = x + phys * ld + c;
     *q = __float2bfloat16_rn(__bfloat162float(*q) * f);
   }
+}
+
+// ---- Bernoulli audit sampler with adaptive probability and cap (audit.py:79-132), one CTA of 1024 threads (B <= 1024)
+//   p_b   = clamp(p_min + alpha * entropy_b / (R + K) + beta * recent_residual + gamma * deficit(recipe_b), p_min, p_max)
+//           deficit(r) = max(coverage_min - ema[r], 0) / max(coverage_min, 1e-12)            (ema BEFORE this step's update)
+//   mask  = u_b < p_b                       (u: the uniforms torch.bernoulli would draw, staged by the host)
+//   cap   : more than `cap` candidates -> the candidates at positions perm[0..cap) of the ascending candidate list
+//           (perm: the row of `perm_table` for this candidate count), inclusion probability p_b * cap / candidates
+// Outputs for the replay's fixed-capacity slots (ascending sample order, unused slots point at sample 0 with weight 0):
+//   idx, valid (1/0), inv_p (1 / max(p_inc, 1e-12) or 0), dist_scale (n_cap / audited for valid slots: turns the replay's
+//   means over n_cap slots into means over the audited samples), the hot rows' loss weights and the replay's.
+// Then the coverage average of the audited recipes (audit.py:70-77): ema = beta_c * ema + (1 - beta_c) * counts / max(sum, 1).
+struct AuditSampleParams {
+  float p_min, p_max, alpha, beta, gamma, cov_min, cov_beta, inv_rk, w0;
+  int B, R, cap, n_cap, weight_mode;      // weight_mode 0: plain hot weights (no gradient correction, or residual clip:
+};                                        // the factor is applied later); 1: hot weight w0 * (1 - 1/p_inc) on audited rows
+
+__global__ void __launch_bounds__(1024)
+audit_sample_kernel(const float* __restrict__ entropy, const int32_t* __restrict__ recipe_id, const float* __restrict__ u,
+                    const int32_t* __restrict__ perm_table, float* __restrict__ ema, const float* __restrict__ recent,
+                    AuditSampleParams P, int32_t* __restrict__ idx, int32_t* __restrict__ idx_scatter,
+                    float* __restrict__ valid, float* __restrict__ inv_p,
+                    float* __restrict__ dist_scale, float* __restrict__ row_weight, float* __restrict__ row_weight_a,
+                    float* __restrict__ stats, int* __restrict__ status) {
+  __shared__ int scan[1024];
+  __shared__ int sel[1024];
+  __shared__ int chosen[1024];
+  __shared__ int rcount[64];
+  __shared__ float red[32];
+  const int b = threadIdx.x;
+  const bool in = b < P.B;
+  float p = 0.f;
+  int m = 0;
+  if (in) {
+    const int r = recipe_id[b];
+    const float deficit = fmaxf(P.cov_min - ema[r], 0.f) / fmaxf(P.cov_min, 1e-12f);
+    p = P.p_min + P.alpha * (entropy[b] * P.inv_rk) + P.beta * recent[0] + P.gamma * deficit;
+    p = fminf(fmaxf(p, P.p_min), P.p_max);
+    m = u[b] < p ? 1 : 0;
+  }
+  // inclusive scan of m over the block (ascending sample index)
+  auto block_scan = [&](int v) -> int {
+    scan[b] = v;
+    __syncthreads();
+    for (int off = 1; off < 1024; off <<= 1) {
+      const int add = b >= off ? scan[b - off] : 0;
+      __syncthreads();
+      scan[b] += add;
+      __syncthreads();
+    }
+    return scan[b];
+  };
+  int incl = block_scan(m);
+  const int candidates = scan[1023];
+  __syncthreads();
+  float p_inc = p;
+  int fin = m;
+  if (P.cap >= 0 && candidates > P.cap) {
+    if (m) sel[incl - 1] = b;
+    chosen[b] = 0;
+    __syncthreads();
+    const int32_t* perm = perm_table + (size_t)(candidates - P.cap - 1) * P.cap;
+    if (b < P.cap) chosen[sel[perm[b]]] = 1;
+    __syncthreads();
+    fin = chosen[b];
+    p_inc = p * ((float)P.cap / (float)candidates);
+    incl = block_scan(fin);
+  }
+  const int audited = scan[1023];
+  __syncthreads();
+  if (audited > P.n_cap && b == 0 && status) atomicExch(status, RTE_DEV_CAPACITY_OVERFLOW);
+  const float scale = audited > 0 ? (float)P.n_cap / (float)audited : 0.f;
+  if (in) {
+    const float ip = 1.f / fmaxf(p_inc, 1e-12f);
+    if (fin && incl - 1 < P.n_cap) {
+      const int j = incl - 1;
+      idx[j] = b; idx_scatter[j] = b; valid[j] = 1.f; inv_p[j] = ip; dist_scale[j] = scale; row_weight_a[j] = P.w0 * ip;
+    }
+    row_weight[b] = (fin && P.weight_mode == 1) ? P.w0 * (1.f - ip) : P.w0;
+  }
+  for (int j = min(audited, P.n_cap) + b; j < P.n_cap; j += 1024) {
+    idx[j] = 0; idx_scatter[j] = -1; valid[j] = 0.f; inv_p[j] = 0.f; dist_scale[j] = 0.f; row_weight_a[j] = 0.f;
+  }
+  // coverage average of the audited recipes
+  if (b < 64) rcount[b] = 0;
+  __syncthreads();
+  if (in && fin) atomicAdd(&rcount[recipe_id[b]], 1);
+  __syncthreads();
+  if (b < P.R) {
+    const float probs = (float)rcount[b] / fmaxf((float)audited, 1.f);
+    ema[b] = ema[b] * P.cov_beta + probs * (1.f - P.cov_beta);
+  }
+  // statistics: candidates, audited, mean requested p, mean inclusion p
+  float s_req = rte::block_sum(in ? p : 0.f, red);
+  float s_inc = rte::block_sum(in ? p_inc : 0.f, red);
+  if (b == 0) {
+    stats[0] = (float)candidates; stats[1] = (float)audited; stats[2] = s_req / (float)P.B; stats[3] = s_inc / (float)P.B;
+  }
+}
+
+// x[j, :] *= factor[j]  (fp32 rows of row_len elements)
+__global__ void scale_rows_f32_kernel(float* __restrict__ x, const float* __restrict__ factor, int n, long long row_len) {
+  const long long total = (long long)n * row_len;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x)
+    x[i] *= factor[i / row_len];
+}
+
+// cos[j] = <a_j, b_j> / (max(|a_j|, eps) * max(|b_j|, eps)) over rows of row_len elements (F.cosine_similarity, eps 1e-8);
+// then recent = max(1 - sum_j valid_j cos_j / sum_j valid_j, 0) when any slot is valid (audit.py:213-218), else unchanged.
+__global__ void __launch_bounds__(NTHR)
+rows_cosine_kernel(const float* __restrict__ a, const float* __restrict__ b, long long row_len, float* __restrict__ cos_out) {
+  __shared__ float red[32];
+  const float* x = a + (size_t)blockIdx.x * row_len;
+  const float* y = b + (size_t)blockIdx.x * row_len;
+  float sxy = 0.f, sxx = 0.f, syy = 0.f;
+  for (long long i = threadIdx.x; i < row_len; i += NTHR) { const float p = x[i], q = y[i]; sxy += p * q; sxx += p * p; syy += q * q; }
+  sxy = rte::block_sum(sxy, red); sxx = rte::block_sum(sxx, red); syy = rte::block_sum(syy, red);
+  if (threadIdx.x == 0) cos_out[blockIdx.x] = sxy / (fmaxf(sqrtf(sxx), 1e-8f) * fmaxf(sqrtf(syy), 1e-8f));
+}
+__global__ void audit_recent_kernel(const float* __restrict__ cos_in, const float* __restrict__ valid, int n, float* __restrict__ recent) {
+  if (threadIdx.x != 0 || blockIdx.x != 0) return;
+  float s = 0.f, c = 0.f;
+  for (int j = 0; j < n; ++j) { s += valid[j] * cos_in[j]; c += valid[j]; }
+  if (c > 0.f) recent[0] = fmaxf(1.f - s / c, 0.f);
 }
 
 }  // namespace
@@ -308,9 +435,10 @@ __global__ void scale_rows_bf16_kernel(__nv_bfloat16* __restrict__ x, int ld, co
 #define ST(s) reinterpret_cast<cudaStream_t>(s)
 
 extern "C" int rte_audit_clip(const float* hot_loss, const float* exact_loss, const int32_t* idx, int32_t n, float inv_p,
-                              float clip, float* f_hot, float* f_exact, rte_stream_t stream) {
+                              const float* inv_p_slot, float clip, float* f_hot, float* f_exact, rte_stream_t stream) {
   RTE_CHECK_ARG(hot_loss && exact_loss && idx && f_hot && f_exact && n > 0 && clip >= 0.f);
-  audit_clip_kernel<<<rte::ceil_div(n, 128), 128, 0, ST(stream)>>>(hot_loss, exact_loss, idx, n, inv_p, clip, f_hot, f_exact);
+  audit_clip_kernel<<<rte::ceil_div(n, 128), 128, 0, ST(stream)>>>(hot_loss, exact_loss, idx, n, inv_p, inv_p_slot, clip, f_hot,
+                                                                   f_exact);
   RTE_LAUNCH_CHECK();
   return RTE_OK;
 }
@@ -443,6 +571,40 @@ extern "C" int rte_add_rows_f32_to_bf16(void* dst_bf16, int32_t ld, const int32_
   RTE_CHECK_ARG(dst_bf16 && idx && src && S > 0 && rows > 0 && V > 0 && ld >= V);
   add_rows_f32_to_bf16_kernel<<<grid_for((long long)rows * V, NTHR), NTHR, 0, ST(stream)>>>(
       reinterpret_cast<__nv_bfloat16*>(dst_bf16), ld, idx, S, src, rows, V);
+  RTE_LAUNCH_CHECK();
+  return RTE_OK;
+}
+
+extern "C" int rte_audit_sample_bernoulli(const float* entropy, const int32_t* recipe_id, const float* u, const int32_t* perm_table,
+                                          float* ema, const float* recent, const rte_audit_sample_params* prm, int32_t* idx,
+                                          int32_t* idx_scatter, float* valid, float* inv_p, float* dist_scale, float* row_weight, float* row_weight_a,
+                                          float* stats, int32_t* status, rte_stream_t stream) {
+  RTE_CHECK_ARG(entropy && recipe_id && u && ema && recent && prm && idx && idx_scatter && valid && inv_p && dist_scale && row_weight &&
+                row_weight_a && stats);
+  RTE_CHECK_ARG(prm->B > 0 && prm->B <= 1024 && prm->R > 0 && prm->R <= 64 && prm->n_cap > 0 && (prm->cap < 0 || perm_table));
+  AuditSampleParams P;
+  P.p_min = prm->p_min; P.p_max = prm->p_max; P.alpha = prm->alpha; P.beta = prm->beta; P.gamma = prm->gamma;
+  P.cov_min = prm->coverage_min; P.cov_beta = prm->coverage_beta; P.inv_rk = prm->inv_r_plus_k; P.w0 = prm->w0;
+  P.B = prm->B; P.R = prm->R; P.cap = prm->cap; P.n_cap = prm->n_cap; P.weight_mode = prm->weight_mode;
+  audit_sample_kernel<<<1, 1024, 0, ST(stream)>>>(entropy, recipe_id, u, perm_table, ema, recent, P, idx, idx_scatter, valid, inv_p,
+                                                  dist_scale, row_weight, row_weight_a, stats, status);
+  RTE_LAUNCH_CHECK();
+  return RTE_OK;
+}
+
+extern "C" int rte_scale_rows_f32(float* x, const float* factor, int32_t n, int64_t row_len, rte_stream_t stream) {
+  RTE_CHECK_ARG(x && factor && n > 0 && row_len > 0);
+  scale_rows_f32_kernel<<<grid_for((long long)n * row_len, NTHR), NTHR, 0, ST(stream)>>>(x, factor, n, row_len);
+  RTE_LAUNCH_CHECK();
+  return RTE_OK;
+}
+
+extern "C" int rte_audit_recent_residual(const float* hot_end, const float* exact_end, const float* valid, int32_t n,
+                                         int64_t row_len, float* cos_scratch, float* recent, rte_stream_t stream) {
+  RTE_CHECK_ARG(hot_end && exact_end && valid && cos_scratch && recent && n > 0 && row_len > 0);
+  rows_cosine_kernel<<<n, NTHR, 0, ST(stream)>>>(hot_end, exact_end, row_len, cos_scratch);
+  RTE_LAUNCH_CHECK();
+  audit_recent_kernel<<<1, 32, 0, ST(stream)>>>(cos_scratch, valid, n, recent);
   RTE_LAUNCH_CHECK();
   return RTE_OK;
 }

@@ -278,6 +278,15 @@ class TrainEngine:
         self.n_clusters = self.oc.num_clusters
         self.exact = tr.mode == "recursive_exact"       # every sample runs the banked recurrent core (training.py:771-797)
         self.audit_k = int(tr.audit_fixed_count_per_batch or 0) if tr.audits_enabled else 0
+        # Bernoulli sampler (audit.py:79-132): the audited count varies per step, so the replay gets a fixed capacity --
+        # the cap when one is set, otherwise the count B * p_max can reach plus six standard deviations (beyond it the
+        # step raises through the status word rather than audit a different subset than the one drawn)
+        self.audit_bernoulli = (not self.dense and tr.mode != "recursive_exact" and tr.audits_enabled
+                                and tr.audit_fixed_count_per_batch is None)
+        if self.audit_bernoulli:
+            pm = min(max(float(tr.audit_p_max), 0.0), 1.0)
+            bound = int(math.ceil(self.B * pm + 6.0 * math.sqrt(self.B * pm * (1.0 - pm)) + 1.0))
+            self.audit_k = min(self.B, bound if tr.audit_cap is None else int(tr.audit_cap))
         # audit_mode "metric_only" / "distill_only" run the exact subset without gradients (audit.py:295-298): the replay
         # stops after its forward, the control variate leaves the loss, only the distillation terms reach the hot pass
         self.audit_grad = bool(self.audit_k) and tr.audit_mode == "gradient_corrected"
@@ -419,12 +428,14 @@ class TrainEngine:
         #   | per metric group (sum grad^2, sum param^2)
         k_a = self.audit_k or 0
         n_mg = len(METRIC_GROUPS)
-        self._results = torch.zeros(8 + 2 * B + 5 * k_a + 1 + 2 * n_mg, dtype=f32, device=dev)
+        # (Bernoulli sampler: + audited sample ids[k] (int32) | 1 / inclusion probability[k] | sampler statistics[4])
+        self._audit_extra = (2 * k_a + 4) if self.audit_bernoulli else 0
+        self._results = torch.zeros(8 + 2 * B + 5 * k_a + 1 + self._audit_extra + 2 * n_mg, dtype=f32, device=dev)
         self.loss_tok = e(M)
         # [0]=sum loss, [1]=aux load, [2]=aux depth, [3]=sumsq, [4]=clip, [5]=1.0 when the step was dropped (non-finite)
         self.scalars = self._results[0:8]
         self.loss_per_sample = self._results[8:8 + B]
-        self._metric_sums = self._results[8 + 2 * B + 5 * k_a + 1:].view(n_mg, 2)
+        self._metric_sums = self._results[8 + 2 * B + 5 * k_a + 1 + self._audit_extra:].view(n_mg, 2)
         self.row_weight = torch.full((B,), 1.0 / (B * S * self.loss_div), dtype=f32, device=dev)
         # backward temporaries
         self.tmp = _Temps(M, cfg, dev)
@@ -507,6 +518,11 @@ class TrainEngine:
             self.audit.terms = self._results[r0:r0 + 4 * k_a].view(k_a, 4)
             self.audit.exact_loss = self._results[r0 + 4 * k_a:r0 + 5 * k_a]
             self.audit.kl_sum = self._results[r0 + 5 * k_a:r0 + 5 * k_a + 1]
+            if self.audit_bernoulli:
+                x0 = r0 + 5 * k_a + 1
+                self.audit.idx = self._results[x0:x0 + k_a].view(torch.int32)
+                self.audit.inv_p = self._results[x0 + k_a:x0 + 2 * k_a]
+                self.audit.stats = self._results[x0 + 2 * k_a:x0 + 2 * k_a + 4]
         for n, sh in self.shadow.items():
             ops.cast_bf16(self.params[n], sh)
         if hasattr(ops, "rope_table"):
@@ -897,7 +913,7 @@ class TrainEngine:
         if not self.dense:
             h0 = x
             fixed_depth_id = None if tr.fixed_depth is None else list(cfg.depth_choices).index(tr.fixed_depth)
-            if self.audit is not None:
+            if self.audit is not None and not self.audit.bernoulli:
                 if self.audit.own_prelude:
                     # copies of the prelude's saved activations for the audited samples (read by the replay's own
                     # prelude backward, much later): on the replay's weight-gradient stream, idle during forward
@@ -928,6 +944,20 @@ class TrainEngine:
                                            R=cfg.recipe_count, K=len(cfg.depth_choices), mean_prob=self._global_mean_prob())
                     self._router_early = torch.cuda.Event()
                     self._router_early.record(ms)
+            if self.audit is not None and self.audit.bernoulli and not forward_only:
+                # the subset is drawn from this step's routing (entropy, recipes): sampler first, then what the
+                # fixed-count path had started before the router
+                self.audit.sample()
+                ps = self._param_stream
+                if self.audit.own_prelude and ps is not None:
+                    ps.wait_stream(torch.cuda.current_stream(self.device))
+                    with torch.cuda.stream(ps):
+                        self.audit.gather_prelude()
+                elif self.audit.own_prelude:
+                    self.audit.gather_prelude()
+                self._side_wait_main()
+                with self._on_side():
+                    self.audit.forward_replay_head(h0)
             if self.audit is not None:
                 # exact replay of the audited samples: needs only h0 and the routing, so it runs beside the macro
                 # operator and the rest of the hot pass
@@ -1058,7 +1088,7 @@ class TrainEngine:
         if self.audit is not None:
             # distillation gradient on the hot endpoint of the audited samples, then the replay's own
             # logits / final-norm / coda backward (their weight gradients add to the hot pass's)
-            o.scatter_add_rows(dcur, self.audit.idx, self.audit.dhot_extra, self.audit.n, S * d)
+            o.scatter_add_rows(dcur, self.audit.idx_scatter, self.audit.dhot_extra, self.audit.n, S * d)
         if not self.dense:
             # Phi backward writes dh0 into `dalt`; the router's auxiliary losses add their share
             # (its parameter-gradient half goes to the parameter-gradient stream: backward only waits for dh0)
@@ -1173,7 +1203,7 @@ class TrainEngine:
         under clipping would write NaN into every weight there, so dropping that step too is the stricter reading.)"""
         B, k_a = self.B, self.audit_k or 0
         r = self._results
-        audit_part = r[8 + 2 * B: 8 + 2 * B + 5 * k_a + 1] if k_a else None
+        audit_part = r[8 + 2 * B: 8 + 2 * B + 5 * k_a + 1] if k_a else None       # (terms of unused slots are finite too)
         self.ops.nonfinite_guard([r[0:8], r[8:8 + B], audit_part], self.skip_flag, self.scalars[5:6])
 
     def _optimizer_step(self) -> None:
@@ -1259,10 +1289,18 @@ class TrainEngine:
             torch.cuda.synchronize(self.device)
 
     def loss_and_grads(self, batch) -> tuple[float, dict[str, torch.Tensor]]:
-        """Forward + backward without the optimiser (what the parity tests compare with the oracle)."""
+        """Forward + backward without the optimiser (what the parity tests compare with the oracle).  The Bernoulli
+        sampler's running state (coverage average, last residual) is put back afterwards: only a training step
+        advances it."""
+        a = self.audit if (self.audit is not None and self.audit.bernoulli) else None
+        keep = (a.audit_ema.clone(), a.recent.clone()) if a is not None else None
         self._load_batch(batch)
         self._run_step_kernels(optimizer=False)
-        return self._assemble_loss(), self.grads
+        out = self._assemble_loss(), self.grads
+        if a is not None:
+            a.audit_ema.copy_(keep[0])
+            a.recent.copy_(keep[1])
+        return out
 
     def evaluate(self, batches) -> dict[str, float]:
         """Forward-only evaluation over an iterable of [B,S] (tokens, targets) batches, as `rte evaluate` does for one
@@ -1309,7 +1347,11 @@ class TrainEngine:
                 "scalars": h[0:8], "loss_per_sample": h[8:8 + B], "recipe_id": h[8 + B:8 + 2 * B].view(torch.int32),
                 "terms": h[r0:r0 + 4 * k_a].view(k_a, 4), "exact_loss": h[r0 + 4 * k_a:r0 + 5 * k_a],
                 "kl_sum": h[r0 + 5 * k_a:r0 + 5 * k_a + 1],
-                "metric_sums": h[r0 + 5 * k_a + 1:].view(len(METRIC_GROUPS), 2)}
+                "metric_sums": h[r0 + 5 * k_a + 1 + self._audit_extra:].view(len(METRIC_GROUPS), 2)}
+            if self._audit_extra:
+                x0 = r0 + 5 * k_a + 1
+                self._host_slots[i].update(audit_idx=h[x0:x0 + k_a].view(torch.int32), audit_inv_p=h[x0 + k_a:x0 + 2 * k_a],
+                                           audit_stats=h[x0 + 2 * k_a:x0 + 2 * k_a + 4])
         return self._host_slots[i]
 
     def _queue_fetch(self) -> dict[str, Any]:
@@ -1420,6 +1462,25 @@ class TrainEngine:
                 self.global_step -= 1
         elif stepped and self.grad_metrics:
             metrics.update(self._grad_metrics(host))
+        if self.audit is not None:
+            # audit.py:274-299, training.py:1405-1470: what the audit did this step
+            la, B, S = self.last_audit, self.B, self.S
+            audited = la.get("audited", self.audit.n)
+            metrics.update(audit_count=float(audited), audit_rate=audited / B,
+                           audit_sampler_fixed_count=0.0 if self.audit.bernoulli else 1.0,
+                           audit_is_gradient_corrected=1.0 if self.audit.grad else 0.0,
+                           audit_inclusion_prob=la.get("p_inclusion", self.audit.p_inc),
+                           audit_requested_probability=la.get("p_requested", self.audit.p_inc),
+                           audit_candidate_count=float(la.get("candidates", audited)),
+                           macro_distill_loss=sum(la["aux"].values()),
+                           hot_lm_loss=float(host["scalars"][0]) / (B * S),
+                           corrected_lm_loss=(float(host["scalars"][0]) + la["correction"]) / (B * S),
+                           corrected_metric_loss=(float(host["scalars"][0]) + la["correction_metric"]) / (B * S))
+            metrics.update({f"macro_{k}_loss": v for k, v in la["aux"].items()})
+            if audited:
+                metrics["exact_eval_nll"] = float(la["exact"].mean()) / S
+        if getattr(self, "cons_pairs", None):
+            metrics["macro_consistency_loss"] = self.last_consistency
         if not self.dense:
             ids = host["recipe_id"].long()
             counts = torch.bincount(ids, minlength=self.cfg.recipe_count).float()

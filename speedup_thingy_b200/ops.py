@@ -508,9 +508,27 @@ class CudaOps:
         self._call("rte_add_rows_f32_to_bf16", _ptr(dst_bf16), dst_bf16.stride(0), _ptr(idx), S, _ptr(src_f32), rows, V,
                    self.stream)
 
-    def audit_clip(self, hot_loss, exact_loss, idx, n: int, inv_p: float, clip: float, f_hot, f_exact) -> None:
-        self._call("rte_audit_clip", _ptr(hot_loss), _ptr(exact_loss), _ptr(idx), n, float(inv_p), float(clip), _ptr(f_hot),
-                   _ptr(f_exact), self.stream)
+    def audit_clip(self, hot_loss, exact_loss, idx, n: int, inv_p: float, clip: float, f_hot, f_exact, inv_p_slot=None) -> None:
+        self._call("rte_audit_clip", _ptr(hot_loss), _ptr(exact_loss), _ptr(idx), n, float(inv_p),
+                   _ptr(inv_p_slot) if inv_p_slot is not None else None, float(clip), _ptr(f_hot), _ptr(f_exact), self.stream)
+
+    def audit_sample_bernoulli(self, entropy, recipe_id, u, perm_table, ema, recent, prm: dict, idx, idx_scatter, valid, inv_p,
+                               dist_scale, row_weight, row_weight_a, stats) -> None:
+        """audit.py:62-132 on the device; `prm`: the fields of rte_audit_sample_params."""
+        sp = A.AuditSampleParams()
+        for k, v in prm.items():
+            setattr(sp, k, v)
+        self._call("rte_audit_sample_bernoulli", _ptr(entropy), _ptr(recipe_id), _ptr(u),
+                   _ptr(perm_table) if perm_table is not None else None, _ptr(ema), _ptr(recent), C.byref(sp), _ptr(idx),
+                   _ptr(idx_scatter), _ptr(valid), _ptr(inv_p), _ptr(dist_scale), _ptr(row_weight), _ptr(row_weight_a), _ptr(stats),
+                   C.c_void_p(self.status.data_ptr()), self.stream)
+
+    def scale_rows_f32(self, x, factor, n: int, row_len: int) -> None:
+        self._call("rte_scale_rows_f32", _ptr(x), _ptr(factor), n, row_len, self.stream)
+
+    def audit_recent_residual(self, hot_end, exact_end, valid, n: int, row_len: int, cos_scratch, recent) -> None:
+        self._call("rte_audit_recent_residual", _ptr(hot_end), _ptr(exact_end), _ptr(valid), n, row_len, _ptr(cos_scratch),
+                   _ptr(recent), self.stream)
 
     def scale_rows_bf16(self, x_bf16, idx, S: int, scale, rows: int, V: int) -> None:
         """x[rows of the samples idx (or the first rows // S samples), :V] *= scale[sample]."""

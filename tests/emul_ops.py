@@ -453,7 +453,8 @@ class EmulOps:
 
     def scatter_add_rows(self, dst, idx, src, n, row_elems):
         self.launches += 1
-        dst.view(-1, row_elems).index_add_(0, idx[:n].long(), src.view(-1)[: n * row_elems].view(n, row_elems))
+        keep = idx[:n] >= 0
+        dst.view(-1, row_elems).index_add_(0, idx[:n][keep].long(), src.view(-1)[: n * row_elems].view(n, row_elems)[keep])
 
     def audit_route(self, by_pass, depth, idx, rid_out, active_out, n, T):
         self.launches += 1
@@ -554,22 +555,73 @@ class EmulOps:
     def add_rows_to_bf16(self, dst_bf16, idx, S, src_f32, rows, V):
         self.launches += 1
         n = rows // S
-        tgt = (idx[:n].long()[:, None] * S + torch.arange(S)[None, :]).reshape(-1)
-        dst_bf16[tgt, :V] = (dst_bf16[tgt, :V].float() + src_f32.view(rows, V)).to(torch.bfloat16)
+        keep = (idx[:n] >= 0).repeat_interleave(S)
+        tgt = (idx[:n].long()[:, None] * S + torch.arange(S)[None, :]).reshape(-1)[keep]
+        dst_bf16[tgt, :V] = (dst_bf16[tgt, :V].float() + src_f32.view(rows, V)[keep]).to(torch.bfloat16)
 
-    def audit_clip(self, hot_loss, exact_loss, idx, n, inv_p, clip, f_hot, f_exact):
+    def audit_clip(self, hot_loss, exact_loss, idx, n, inv_p, clip, f_hot, f_exact, inv_p_slot=None):
         self.launches += 1
         r = exact_loss[:n] - hot_loss[idx[:n].long()]
         inside = r.abs() <= clip
-        f_hot[:n] = torch.where(inside, torch.full_like(r, 1.0 - inv_p), torch.ones_like(r))
+        ip = inv_p_slot[:n] if inv_p_slot is not None else torch.full_like(r, inv_p)
+        f_hot[:n] = torch.where(inside, 1.0 - ip, torch.ones_like(r))
         f_exact[:n] = inside.float()
+
+    def audit_sample_bernoulli(self, entropy, recipe_id, u, perm_table, ema, recent, prm, idx, idx_scatter, valid, inv_p,
+                               dist_scale, row_weight, row_weight_a, stats):
+        self.launches += 1
+        B, R, cap, n_cap = prm["B"], prm["R"], prm["cap"], prm["n_cap"]
+        rid = recipe_id[:B].long()
+        deficit = (prm["coverage_min"] - ema[rid]).clamp_min(0.0) / max(prm["coverage_min"], 1e-12)
+        p = prm["p_min"] + prm["alpha"] * (entropy[:B] * prm["inv_r_plus_k"]) + prm["beta"] * recent[0] + prm["gamma"] * deficit
+        p = p.clamp(prm["p_min"], prm["p_max"])
+        mask = u[:B] < p
+        cand = int(mask.sum())
+        p_inc = p.clone()
+        if cap >= 0 and cand > cap:
+            sel = mask.nonzero().flatten()
+            perm = perm_table.view(-1, cap)[cand - cap - 1].long()
+            mask = torch.zeros_like(mask)
+            mask[sel[perm]] = True
+            p_inc = p * (float(cap) / float(cand))
+        chosen = mask.nonzero().flatten()
+        a = int(chosen.numel())
+        if a > n_cap:
+            if not hasattr(self, "status"):
+                raise RuntimeError("device status 202: more audited samples than the replay's capacity")
+            self.status[0] = 202
+            chosen, a = chosen[:n_cap], n_cap
+        ip = 1.0 / p_inc.clamp_min(1e-12)
+        idx.zero_(); idx_scatter.fill_(-1); valid.zero_(); inv_p.zero_(); dist_scale.zero_(); row_weight_a.zero_()
+        idx[:a] = chosen.int(); idx_scatter[:a] = chosen.int(); valid[:a] = 1.0; inv_p[:a] = ip[chosen]
+        dist_scale[:a] = float(n_cap) / max(a, 1)
+        row_weight_a[:a] = prm["w0"] * ip[chosen]
+        row_weight[:B] = prm["w0"]
+        if prm["weight_mode"] == 1:
+            row_weight[chosen] = prm["w0"] * (1.0 - ip[chosen])
+        counts = torch.bincount(rid[mask], minlength=R).float()
+        ema[:R] = ema[:R] * prm["coverage_beta"] + counts / max(float(mask.sum()), 1.0) * (1.0 - prm["coverage_beta"])
+        stats[0], stats[1], stats[2], stats[3] = float(cand), float(mask.sum()), float(p.mean()), float(p_inc.mean())
+
+    def scale_rows_f32(self, x, factor, n, row_len):
+        self.launches += 1
+        x.view(-1)[: n * row_len].view(n, row_len).mul_(factor[:n, None])
+
+    def audit_recent_residual(self, hot_end, exact_end, valid, n, row_len, cos_scratch, recent):
+        self.launches += 1
+        a, b = hot_end.view(-1)[: n * row_len].view(n, row_len), exact_end.view(-1)[: n * row_len].view(n, row_len)
+        cos = F.cosine_similarity(a, b, dim=-1, eps=1e-8)
+        cos_scratch[:n] = cos
+        if float(valid[:n].sum()) > 0:
+            recent[0] = (1.0 - (valid[:n] * cos).sum() / valid[:n].sum()).clamp_min(0.0)
 
     def scale_rows_bf16(self, x_bf16, idx, S, scale, rows, V):
         self.launches += 1
         n = rows // S
         base = idx[:n].long() if idx is not None else torch.arange(n)
-        tgt = (base[:, None] * S + torch.arange(S)[None, :]).reshape(-1)
-        f = scale[:n].repeat_interleave(S)[:, None]
+        keep = (base >= 0).repeat_interleave(S)
+        tgt = (base[:, None] * S + torch.arange(S)[None, :]).reshape(-1)[keep]
+        f = scale[:n].repeat_interleave(S)[keep][:, None]
         x_bf16[tgt, :V] = (x_bf16[tgt, :V].float() * f).to(torch.bfloat16)
 
     # ---------------------------------------------------------------- small vector ops

@@ -39,12 +39,16 @@ def reference_experiment(case: dict, run_dir: str) -> RC.ExperimentConfig:
     m.setdefault("topology", "recursive")
     m["depth_choices"] = list(m["depth_choices"])
     t = dict(case["train"])
-    audited = t.get("audit_fixed_count_per_batch") is not None
-    p = (t["audit_fixed_count_per_batch"] / t["batch_size"]) if audited else 0.0
+    bernoulli = t.get("audit_sampler") == "bernoulli"
+    audited = t.get("audit_fixed_count_per_batch") is not None or bernoulli
+    p = (t["audit_fixed_count_per_batch"] / t["batch_size"]) if (audited and not bernoulli) else 0.0
+    sampler = (dict(audit_sampler="bernoulli", audit_p_min=t["audit_p_min"], audit_p_max=t["audit_p_max"],
+                    audit_alpha=t.get("audit_alpha", 0.08), audit_beta=t.get("audit_beta", 0.08),
+                    audit_gamma=t.get("audit_gamma", 0.08), audit_cap=t.get("audit_cap"))
+               if bernoulli else dict(audit_p_min=p, audit_p_max=p, audit_alpha=0.0, audit_beta=0.0, audit_gamma=0.0))
     tr = RC.TrainingConfig(
         mode=t["mode"], lr=t["lr"], weight_decay=t["weight_decay"], batch_size=t["batch_size"],
-        seq_len=t["seq_len"], seed=t["seed"], precision="fp32", fixed_depth=t.get("fixed_depth"),
-        audit_p_min=p, audit_p_max=p, audit_alpha=0.0, audit_beta=0.0, audit_gamma=0.0,
+        seq_len=t["seq_len"], seed=t["seed"], precision="fp32", fixed_depth=t.get("fixed_depth"), **sampler,
         audit_fixed_count_per_batch=t.get("audit_fixed_count_per_batch"),
         audit_mode=t.get("audit_mode", "gradient_corrected" if audited else "metric_only"),
         audit_gradient_correction=audited and t.get("audit_mode", "gradient_corrected") == "gradient_corrected",
@@ -119,6 +123,9 @@ def run_case(name: str, case: dict) -> dict[str, np.ndarray]:
             else:
                 res = engine.train_step((tokens, targets))
             losses.append(float(res.loss.detach()))
+            if case["train"].get("audit_sampler") == "bernoulli":
+                out[f"audit_mask_step{step}"] = res.audit.audit_mask.numpy().copy()
+                out[f"audit_p_step{step}"] = res.audit.p_audit.detach().numpy().copy()
         out["losses"] = np.array(losses, dtype=np.float64)
         final = {n: p_.detach() for n, p_ in model.named_parameters()}
         out["final_param_sumsq"] = np.array(

@@ -820,3 +820,60 @@ def test_audit_residual_clip_factors_and_row_scaling(ops):
         EmulOps().scale_rows_bf16(want, idx if use_idx else None, S, r_hot, n * S, V)
         torch.cuda.synchronize()
         assert torch.equal(got.cpu(), want)
+
+
+@pytest.mark.parametrize("B,R,cap,n_cap,p_lo,p_hi,mode", [(128, 5, 6, 6, 0.05, 0.25, 1), (128, 5, None, 40, 0.05, 0.25, 1),
+                                                         (64, 8, 3, 3, 0.3, 0.9, 0), (8, 5, None, 8, 0.0, 1.0, 1),
+                                                         (32, 4, 40, 32, 0.1, 0.4, 1)])
+def test_bernoulli_audit_sampler_matches_its_definition(ops, B, R, cap, n_cap, p_lo, p_hi, mode):
+    """rte_audit_sample_bernoulli against the emulation (audit.py:62-132): probabilities with all three adaptive terms,
+    the cap's thinning through the staged permutation table, per-slot outputs in ascending order with unused slots
+    marked, both loss-weight vectors, the coverage average, the statistics; plus the two small kernels beside it."""
+    from tests.emul_ops import EmulOps
+    g = torch.Generator().manual_seed(B + R + n_cap)
+    for trial in range(4):
+        entropy = torch.rand(B, generator=g) * 2.5
+        rid = torch.randint(0, R, (B,), generator=g).int()
+        u = torch.rand(B, generator=g)
+        ema0 = torch.rand(R, generator=g) * 0.02
+        recent = torch.rand(1, generator=g) * 0.3
+        perm = None
+        if cap is not None and cap < B:
+            perm = torch.stack([torch.randperm(c, generator=g)[:cap] for c in range(cap + 1, B + 1)]).int().reshape(-1)
+        prm = dict(p_min=p_lo, p_max=p_hi, alpha=0.4, beta=0.5, gamma=0.3, coverage_min=0.01, coverage_beta=0.98,
+                   inv_r_plus_k=1.0 / (R + 3), w0=1.0 / (B * 16), B=B, R=R, cap=-1 if cap is None else cap, n_cap=n_cap,
+                   weight_mode=mode)
+
+        def run(o, dev):
+            t = lambda x: x.clone().to(dev)  # noqa: E731
+            z = lambda n_, dt=torch.float32: torch.full((n_,), 7, dtype=dt, device=dev)  # noqa: E731
+            out = dict(ema=t(ema0), idx=z(n_cap, torch.int32), idx_scatter=z(n_cap, torch.int32), valid=z(n_cap), inv_p=z(n_cap),
+                       dist=z(n_cap), rw=z(B), rwa=z(n_cap), stats=z(4))
+            o.audit_sample_bernoulli(t(entropy), t(rid), t(u), t(perm) if perm is not None else None, out["ema"], t(recent), prm,
+                                     out["idx"], out["idx_scatter"], out["valid"], out["inv_p"], out["dist"], out["rw"],
+                                     out["rwa"], out["stats"])
+            return {k: v.cpu() for k, v in out.items()}
+
+        got, emu = run(ops, DEV), EmulOps()
+        emu.status = torch.zeros(1, dtype=torch.int32)
+        want = run(emu, "cpu")
+        torch.cuda.synchronize()
+        ops.check_status()
+        for k in ("idx", "idx_scatter", "valid"):
+            assert torch.equal(got[k], want[k]), (k, trial, got[k], want[k])
+        assert torch.equal(got["stats"][:2], want["stats"][:2]), (got["stats"], want["stats"])
+        for k in ("inv_p", "dist", "rw", "rwa", "ema", "stats"):
+            assert torch.allclose(got[k], want[k], rtol=1e-5, atol=1e-7), (k, trial, got[k], want[k])
+    x = torch.randn(6, 200, generator=g)
+    f = torch.tensor([1.0, 0.0, 2.5, 1.0, 0.0, 3.0])
+    xd = x.clone().to(DEV)
+    ops.scale_rows_f32(xd, f.to(DEV), 6, 200)
+    assert torch.allclose(xd.cpu(), x * f[:, None])
+    a, b_ = torch.randn(6, 300, generator=g), torch.randn(6, 300, generator=g)
+    valid = torch.tensor([1.0, 1.0, 0.0, 1.0, 0.0, 0.0])
+    rec, cosd = torch.full((1,), 0.5, device=DEV), torch.zeros(6, device=DEV)
+    ops.audit_recent_residual(a.to(DEV), b_.to(DEV), valid.to(DEV), 6, 300, cosd, rec)
+    cos = torch.nn.functional.cosine_similarity(a, b_, dim=-1, eps=1e-8)
+    assert torch.allclose(rec.cpu(), (1 - (cos * valid).sum() / valid.sum()).clamp_min(0).view(1), atol=1e-5)
+    ops.audit_recent_residual(a.to(DEV), b_.to(DEV), torch.zeros(6, device=DEV), 6, 300, cosd, rec)      # nobody audited: unchanged
+    assert torch.allclose(rec.cpu(), (1 - (cos * valid).sum() / valid.sum()).clamp_min(0).view(1), atol=1e-5)

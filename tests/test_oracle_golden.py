@@ -65,7 +65,9 @@ def test_loss_curve_and_final_weights_match_reference(name):
     losses = [trainer.train_step(*next(it)) for _ in range(case["steps"])]
     np.testing.assert_allclose(np.array(losses), gold["losses"], rtol=2e-4, atol=2e-5)
     sumsq = np.array([trainer.params[n].double().pow(2).sum().item() for n, _ in O.param_shapes(cfg)])
-    np.testing.assert_allclose(sumsq, gold["final_param_sumsq"], rtol=2e-4, atol=1e-9)
+    # (small_bernoulli: parameters that start at zero move by +-lr per Adam step on gradients of 1e-9, whose sign is
+    #  rounding noise between two fp32 implementations; their sums of squares are ~1e-5 and compared absolutely)
+    np.testing.assert_allclose(sumsq, gold["final_param_sumsq"], rtol=2e-4, atol=1e-6 if name == "small_bernoulli" else 1e-9)
 
 
 def test_per_op_vectors():
@@ -192,3 +194,18 @@ def test_macro_consistency_loss_matches_reference_golden():
     np.testing.assert_allclose(h0.grad.numpy(), gold["dh0"], rtol=1e-4, atol=1e-8)
     for name in ("d_gain", "v", "u", "bias"):
         np.testing.assert_allclose(leaves[f"macro.{name}"].grad.numpy(), gold[f"grad/{name}"], rtol=1e-4, atol=1e-8)
+
+
+def test_bernoulli_sampler_follows_the_reference_step_by_step():
+    """audit.py:79-132 over five optimiser steps: per step the audited mask and the inclusion probabilities (which
+    carry the entropy, last-residual and coverage-deficit terms and the cap's rescaling) equal the reference's."""
+    case, cfg, tr, gold, trainer, it = _run("small_bernoulli")
+    capped = 0
+    for step in range(case["steps"]):
+        trainer.train_step(*next(it))
+        info = trainer.last_info
+        assert np.array_equal(info["mask"].numpy(), gold[f"audit_mask_step{step}"]), step
+        np.testing.assert_allclose(info["p_inc"].numpy(), gold[f"audit_p_step{step}"], rtol=2e-4, atol=1e-6, err_msg=str(step))
+        capped += int(not np.allclose(info["p_inc"].numpy(), info["audit_prob"].detach().numpy()))
+    assert capped >= 1                      # the cap engaged on some steps and not on others
+    assert capped < case["steps"]
