@@ -508,9 +508,11 @@ def main() -> None:
                                 "frac": roof["tflops"] / peak,
                                 "frac_of_sustained": roof["tflops"] / peaks["bf16_tflops_sustained"],
                                 "peak_sustained": peaks["bf16_tflops_sustained"],
-                                # DRAM bytes per launch (read + write), launch-weighted mean over the hot-pass shapes of the
-                                # ncu capture summarised in profiles/gemm_tcgen05_c3_shapes_ncu_full.md
-                                "traffic": 38.0e6, "traffic_unit": "bytes per launch (ncu dram__bytes_read+write, c3 shapes)",
+                                # DRAM bytes per launch (read + write), mean over the hot-pass shapes of the ncu capture
+                                # summarised in profiles/gemm_tcgen05_c3_shapes_ncu_full.md (cold operand reads; outputs that
+                                # fit the L2 do not reach DRAM inside the launch); only meaningful for workload c3
+                                "traffic": 41.0e6 if args.config == "c3" else None,
+                                "traffic_unit": "bytes per launch (ncu dram__bytes_read+write, c3 shapes)",
                                 "of": which + " (burst)",
                                 "kernel": "gemm_tcgen05_kernel", "launches_per_step": roof["launches"],
                                 "gemm_ms_per_step": roof["gemm_ms_per_step"],

@@ -230,7 +230,7 @@ class AuditReplay:
         prm = dict(p_min=tr.audit_p_min, p_max=tr.audit_p_max, alpha=tr.audit_alpha, beta=tr.audit_beta, gamma=tr.audit_gamma,
                    coverage_min=tr.coverage_min, coverage_beta=tr.coverage_beta,
                    inv_r_plus_k=1.0 / (cfg.recipe_count + len(cfg.depth_choices)), w0=w0, B=eng.B, R=cfg.recipe_count,
-                   cap=-1 if self.cap is None else self.cap, n_cap=self.n,
+                   cap=-1 if (self.cap is None or self.cap >= eng.B) else self.cap, n_cap=self.n,      # (a cap of B or more never engages)
                    weight_mode=1 if (self.grad and self.clip is None) else 0)
         eng.ops.audit_sample_bernoulli(eng.route["router_entropy"], eng.route["recipe_id"], self.u_dev, self.perm_dev,
                                        self.audit_ema, self.recent, prm, self.idx, self.idx_scatter, self.valid, self.inv_p,

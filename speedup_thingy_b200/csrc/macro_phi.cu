@@ -342,6 +342,7 @@ phi_da_mma_kernel(const float* __restrict__ dupd, const float* __restrict__ act,
 // act[tok, j] = pa[b, j] + rstd[tok] * (h0 @ v1)[tok, j] + (hx @ v3)[tok, j]:  M = tokens, N = rank, K = d (d % 32 == 0).
 // Same warp layout as phi_da_mma_kernel; two accumulators per rank tile (with hx == h0, the hot path, the v1 and v3
 // slices share the A fragments; otherwise the v3 slice gets fragments of its own).
+template <bool OWN3>
 __global__ void __launch_bounds__(NTHR)
 phi_act_mma_kernel(const float* __restrict__ h0, const float* __restrict__ hx, const float* __restrict__ rstd,
                    const float* __restrict__ pa, const float* __restrict__ vt, long long vt_ld,
@@ -358,7 +359,7 @@ phi_act_mma_kernel(const float* __restrict__ h0, const float* __restrict__ hx, c
   const bool ok0 = r0 < D.S, ok1 = r1 < D.S;
   const float* a0p = h0 + ((size_t)b * D.S + (ok0 ? r0 : 0)) * D.d + 8 * t;
   const float* a1p = h0 + ((size_t)b * D.S + (ok1 ? r1 : 0)) * D.d + 8 * t;
-  const bool own3 = hx != h0;                        // kernel-uniform
+  // OWN3: hx is a different tensor than h0 (a compile-time switch: the hot path keeps its register footprint)
   const float* x0p = hx + ((size_t)b * D.S + (ok0 ? r0 : 0)) * D.d + 8 * t;
   const float* x1p = hx + ((size_t)b * D.S + (ok1 ? r1 : 0)) * D.d + 8 * t;
   const int j0 = ng * 8 + g, j1 = j0 + 32;
@@ -374,7 +375,7 @@ phi_act_mma_kernel(const float* __restrict__ h0, const float* __restrict__ hx, c
   for (int k0 = 0; k0 < D.d; k0 += 32) {
     const Frag8 x0 = load8(a0p + k0, ok0), x1 = load8(a1p + k0, ok1);
     Frag8 z0 = x0, z1 = x1;                          // A operand of the v3 slice
-    if (own3) { z0 = load8(x0p + k0, ok0); z1 = load8(x1p + k0, ok1); }
+    if constexpr (OWN3) { z0 = load8(x0p + k0, ok0); z1 = load8(x1p + k0, ok1); }
     const Frag8 w1 = load8(b0p + k0, okb0), w3 = load8(b0p + 2 * D.d + k0, okb0);
     Frag8 y1, y3;
     if (two) { y1 = load8(b1p + k0, okb1); y3 = load8(b1p + 2 * D.d + k0, okb1); }
@@ -385,7 +386,7 @@ phi_act_mma_kernel(const float* __restrict__ h0, const float* __restrict__ hx, c
       split_tf32(pick(x1.lo, s), a[1], al[1]);
       split_tf32(pick(x0.hi, s), a[2], al[2]);
       split_tf32(pick(x1.hi, s), a[3], al[3]);
-      if (own3) {
+      if constexpr (OWN3) {
         split_tf32(pick(z0.lo, s), c[0], cl[0]);
         split_tf32(pick(z1.lo, s), c[1], cl[1]);
         split_tf32(pick(z0.hi, s), c[2], cl[2]);
@@ -959,7 +960,8 @@ int phi_fwd_impl(const float* h0, const float* hx, const rte_phi_params* p, cons
   if (phi_tensor_path(p, h0, out, act, d, m) && (reinterpret_cast<uintptr_t>(hx) & 15) == 0) {
     const long long vt_ld = (long long)p->n_keys * 3 * d, ut_ld = (long long)p->n_keys * m;
     const float* ut = p->wt + (size_t)m * vt_ld;
-    phi_act_mma_kernel<<<B * tiles, NTHR, 0, ST(stream)>>>(h0, hx, rstd, pa, p->wt, vt_ld, recipe_id, stride_id, act, D);
+    if (hx != h0) phi_act_mma_kernel<true><<<B * tiles, NTHR, 0, ST(stream)>>>(h0, hx, rstd, pa, p->wt, vt_ld, recipe_id, stride_id, act, D);
+    else phi_act_mma_kernel<false><<<B * tiles, NTHR, 0, ST(stream)>>>(h0, hx, rstd, pa, p->wt, vt_ld, recipe_id, stride_id, act, D);
     RTE_LAUNCH_CHECK();
     if (m <= 32)
       phi_out_mma_kernel<0, 1><<<B * tiles, NTHR, 0, ST(stream)>>>(h0, act, p->gain, ut, ut_ld, p->bias, p->scale, recipe_id,

@@ -841,7 +841,7 @@ def test_bernoulli_audit_sampler_matches_its_definition(ops, B, R, cap, n_cap, p
         if cap is not None and cap < B:
             perm = torch.stack([torch.randperm(c, generator=g)[:cap] for c in range(cap + 1, B + 1)]).int().reshape(-1)
         prm = dict(p_min=p_lo, p_max=p_hi, alpha=0.4, beta=0.5, gamma=0.3, coverage_min=0.01, coverage_beta=0.98,
-                   inv_r_plus_k=1.0 / (R + 3), w0=1.0 / (B * 16), B=B, R=R, cap=-1 if cap is None else cap, n_cap=n_cap,
+                   inv_r_plus_k=1.0 / (R + 3), w0=1.0 / (B * 16), B=B, R=R, cap=-1 if (cap is None or cap >= B) else cap, n_cap=n_cap,
                    weight_mode=mode)
 
         def run(o, dev):
