@@ -16,31 +16,37 @@ pytestmark = pytest.mark.gpu
 DEV = "cuda:0"
 
 
-def _plan(shapes, gen):
+def _plan(shapes, gen, dev=DEV):
     from speedup_thingy_b200.ops import AdamWPlan
 
     entries = []
     for i, s in enumerate(shapes):
-        p = torch.randn(s, generator=gen).to(DEV)
+        p = torch.randn(s, generator=gen).to(dev)
         entries.append(dict(p=p, g=torch.zeros_like(p), m=torch.zeros_like(p), v=torch.zeros_like(p), shadow=None, lr_group=0))
-    return AdamWPlan(entries, 1, DEV), entries
+    return AdamWPlan(entries, 1, dev), entries
 
 
-def test_static_scratch_grad_norm_matches_the_regular_entry_point_twice_in_a_row():
+@pytest.mark.parametrize("dev", ["cuda:0", "cuda:1"])
+def test_static_scratch_grad_norm_matches_the_regular_entry_point_twice_in_a_row(dev):
+    """`cuda:1` (skipped on a single-GPU machine): the array's device address is looked up per device, with that device
+    current -- each GPU that loads the library carries its own copy of the array."""
     from speedup_thingy_b200.ops import CudaOps
 
-    ops = CudaOps(DEV)
+    if int(dev.split(":")[1]) >= torch.cuda.device_count():
+        pytest.skip("needs a second GPU")
+    ops = CudaOps(dev)
     gen = torch.Generator().manual_seed(1234)
-    plan, entries = _plan([(70_001,), (513, 129), (4096,), (3,)], gen)
-    partial = torch.zeros(plan.total_chunks, device=DEV)
+    plan, entries = _plan([(70_001,), (513, 129), (4096,), (3,)], gen, dev)
+    partial = torch.zeros(plan.total_chunks, device=dev)
     for call, scale in enumerate((1.0, 0.01)):
         for e in entries:
-            e["g"].copy_((torch.randn(e["g"].shape, generator=gen) * scale).to(DEV))
-        ref_sumsq, ref_clip = torch.zeros(1, device=DEV), torch.zeros(1, device=DEV)
-        got_sumsq, got_clip = torch.full((1,), -1.0, device=DEV), torch.full((1,), -1.0, device=DEV)
-        ops.grad_norm(plan, partial, ref_sumsq, 1.0, ref_clip)
-        ops.grad_norm_static(plan, got_sumsq, 1.0, got_clip)
-        torch.cuda.synchronize()
+            e["g"].copy_((torch.randn(e["g"].shape, generator=gen) * scale).to(dev))
+        ref_sumsq, ref_clip = torch.zeros(1, device=dev), torch.zeros(1, device=dev)
+        got_sumsq, got_clip = torch.full((1,), -1.0, device=dev), torch.full((1,), -1.0, device=dev)
+        with torch.cuda.device(dev):
+            ops.grad_norm(plan, partial, ref_sumsq, 1.0, ref_clip)
+            ops.grad_norm_static(plan, got_sumsq, 1.0, got_clip)
+        torch.cuda.synchronize(dev)
         host = sum(float(e["g"].double().pow(2).sum()) for e in entries)
         assert abs(float(ref_sumsq) - host) <= 1e-4 * host, call
         assert abs(float(got_sumsq) - float(ref_sumsq)) <= 1e-6 * float(ref_sumsq), call
