@@ -199,7 +199,7 @@ int rte_segment_sum(const float* in, float* out, int32_t n_seg, int32_t seg_len,
  * One decision per sample from pooled = mean_S(h0).  Weights f32 in nn.Linear layout.
  * out_f f32 [B, RTE_ROUTER_F_STRIDE] and out_i int32 [B, RTE_ROUTER_I_STRIDE] are laid out as the
  * offsets below say.  argmax ties go to the LOWEST index.  fixed_recipe / fixed_depth_id < 0 = unset. */
-enum { RTE_ROUTER_MAX_R = 32, RTE_ROUTER_MAX_K = 8, RTE_ROUTER_MAX_T = 32, RTE_ROUTER_DPOOLED_PARTS = 4 };
+enum { RTE_ROUTER_MAX_R = 32, RTE_ROUTER_MAX_K = 8, RTE_ROUTER_MAX_T = 128, RTE_ROUTER_DPOOLED_PARTS = 4 };
 typedef struct rte_router_weights {
   const float *r_w0, *r_b0, *r_w2, *r_b2;   /* recipe_mlp */
   const float *d_w0, *d_b0, *d_w2, *d_b2;   /* depth_mlp  */
@@ -353,6 +353,11 @@ typedef struct rte_adamw_extras {
   const int32_t* metric_group;
   float* metric_out;
   int32_t n_metric_groups;
+  /* tensors that may receive NO gradient in a step (the recurrent core when the Bernoulli sampler audited nobody):
+   * while *absent_flag != 0 the tensors with absent_mask[i] != 0 are left untouched -- no decay, no moment update, no
+   * step count -- as torch.optim.AdamW skips `grad is None`.  Both NULL = every tensor has a gradient.           */
+  const int32_t* absent_flag;
+  const uint8_t* absent_mask;   /* [n_tensors], device */
 } rte_adamw_extras;
 int rte_adamw_multi_tensor_ex(const rte_adamw_tensor* table, int32_t n_tensors, int64_t total_chunks,
                               const int32_t* chunk_tensor, const int32_t* chunk_index, const float* lr_table,
@@ -543,8 +548,10 @@ typedef struct rte_audit_sample_params {
 } rte_audit_sample_params;
 int rte_audit_sample_bernoulli(const float* entropy, const int32_t* recipe_id, const float* u, const int32_t* perm_table,
                                float* ema, const float* recent, const rte_audit_sample_params* prm, int32_t* idx,
-                               int32_t* idx_scatter, float* valid, float* inv_p, float* dist_scale, float* row_weight, float* row_weight_a,
-                               float* stats, int32_t* status, rte_stream_t stream);
+                               int32_t* idx_scatter, float* valid, float* inv_p, float* dist_scale, float* row_weight,
+                               float* row_weight_a, float* stats,
+                               int32_t* none_audited /* optional: 1 when nobody was audited, else 0 */, int32_t* status,
+                               rte_stream_t stream);
 /* x[j, 0..row_len) *= factor[j], j < n (fp32).                                                                      */
 int rte_scale_rows_f32(float* x, const float* factor, int32_t n, int64_t row_len, rte_stream_t stream);
 /* recent[0] = max(1 - mean over valid slots of cosine(hot_end_j, exact_end_j), 0) (audit.py:213-218; rows of row_len

@@ -13,7 +13,7 @@ LIB_PATH = Path(__file__).resolve().parent / "lib" / "librte_b200.so"
 c_i32, c_i64, c_f32, c_vp = C.c_int32, C.c_int64, C.c_float, C.c_void_p
 
 EPI_BF16, EPI_F32, EPI_SWIGLU_FWD, EPI_SWIGLU_BWD = 0, 1, 2, 3
-ROUTER_MAX_R, ROUTER_MAX_K, ROUTER_MAX_T = 32, 8, 32
+ROUTER_MAX_R, ROUTER_MAX_K, ROUTER_MAX_T = 32, 8, 128
 ROUTER_DPOOLED_PARTS = 4
 ADAMW_CHUNK = 4096
 
@@ -85,7 +85,7 @@ class AuditSampleParams(C.Structure):
 
 class AdamWExtras(C.Structure):
     _fields_ = [("skip", c_vp), ("metric_partial", c_vp), ("metric_group", c_vp), ("metric_out", c_vp),
-                ("n_metric_groups", c_i32)]
+                ("n_metric_groups", c_i32), ("absent_flag", c_vp), ("absent_mask", c_vp)]
 
 
 P = C.POINTER
@@ -173,7 +173,7 @@ PROTOTYPES = {
     "rte_kl_distill_grad": (C.c_int, [c_vp, c_vp, c_f32, c_f32, c_vp, c_vp, c_i32, c_i32, c_vp]),
     "rte_audit_clip": (C.c_int, [c_vp, c_vp, c_vp, c_i32, C.c_float, c_vp, C.c_float, c_vp, c_vp, c_vp]),
     "rte_audit_sample_bernoulli": (C.c_int, [c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, P(AuditSampleParams), c_vp, c_vp, c_vp, c_vp,
-                                             c_vp, c_vp, c_vp, c_vp, c_vp, c_vp]),
+                                             c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, c_vp]),
     "rte_scale_rows_f32": (C.c_int, [c_vp, c_vp, c_i32, c_i64, c_vp]),
     "rte_audit_recent_residual": (C.c_int, [c_vp, c_vp, c_vp, c_i32, c_i64, c_vp, c_vp, c_vp]),
     "rte_scale_rows_bf16": (C.c_int, [c_vp, c_i32, c_vp, c_i32, c_vp, c_i32, c_i32, c_vp]),

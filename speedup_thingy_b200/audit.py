@@ -234,7 +234,10 @@ class AuditReplay:
                    weight_mode=1 if (self.grad and self.clip is None) else 0)
         eng.ops.audit_sample_bernoulli(eng.route["router_entropy"], eng.route["recipe_id"], self.u_dev, self.perm_dev,
                                        self.audit_ema, self.recent, prm, self.idx, self.idx_scatter, self.valid, self.inv_p,
-                                       self.dist_scale, eng.row_weight, self.row_weight_a, self.stats)
+                                       self.dist_scale, eng.row_weight, self.row_weight_a, self.stats,
+                                       none_audited=eng._none_audited)
+        if eng._core_absent is not None:
+            eng._core_absent.mul_(eng._none_audited)      # stays 1 only while nobody has been audited in this cycle
 
     def choose(self, step_seed: int) -> None:
         """Fixed-count sampler: first k entries of a seeded CPU permutation (audit.py:99-116); writes the subset

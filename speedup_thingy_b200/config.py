@@ -336,6 +336,27 @@ def unsupported(config: ExperimentConfig) -> list[str]:
 
     if t.mode not in SUPPORTED_MODES:
         no("training", "mode", "implemented modes are " + ", ".join(SUPPORTED_MODES))
+    # kernel size limits (what TrainEngine would otherwise refuse at construction)
+    head_dim = m.d_model // max(m.n_heads, 1)
+    if m.d_model % 8:
+        no("model", "d_model", "kernel limit: a multiple of 8")
+    if head_dim not in (8, 16, 32, 64, 128):
+        no("model", "n_heads", f"kernel limit: head_dim = d_model / n_heads in {{8, 16, 32, 64, 128}}, not {head_dim}")
+    if m.d_ff % 64:
+        no("model", "d_ff", "kernel limit: a multiple of 64")
+    if m.vocab_size % 8:
+        no("model", "vocab_size", "kernel limit: a multiple of 8")
+    if t.seq_len > 256:
+        no("training", "seq_len", "kernel limit: at most 256")
+    if m.topology == "recursive":
+        if m.recipe_count > 32:
+            no("model", "recipe_count", "kernel limit: at most 32")
+        if len(m.depth_choices) > 8:
+            no("model", "depth_choices", "kernel limit: at most 8 depth choices")
+        if m.t_max > 128:
+            no("model", "t_max", "kernel limit: at most 128 passes")
+        if m.macro_rank > 64:
+            no("model", "macro_rank", "kernel limit: at most 64")
     if t.precision != "bf16":
         no("training", "precision", "the kernels compute in bf16 with fp32 master weights and accumulation; "
                                     "pass precision='bf16' to load_config to run this configuration that way")

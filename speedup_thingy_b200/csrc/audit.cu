@@ -327,7 +327,7 @@ audit_sample_kernel(const float* __restrict__ entropy, const int32_t* __restrict
                     AuditSampleParams P, int32_t* __restrict__ idx, int32_t* __restrict__ idx_scatter,
                     float* __restrict__ valid, float* __restrict__ inv_p,
                     float* __restrict__ dist_scale, float* __restrict__ row_weight, float* __restrict__ row_weight_a,
-                    float* __restrict__ stats, int* __restrict__ status) {
+                    float* __restrict__ stats, int32_t* __restrict__ none_audited, int* __restrict__ status) {
   __shared__ int scan[1024];
   __shared__ int sel[1024];
   __shared__ int chosen[1024];
@@ -401,6 +401,7 @@ audit_sample_kernel(const float* __restrict__ entropy, const int32_t* __restrict
   float s_inc = rte::block_sum(in ? p_inc : 0.f, red);
   if (b == 0) {
     stats[0] = (float)candidates; stats[1] = (float)audited; stats[2] = s_req / (float)P.B; stats[3] = s_inc / (float)P.B;
+    if (none_audited) none_audited[0] = audited == 0 ? 1 : 0;
   }
 }
 
@@ -578,7 +579,7 @@ extern "C" int rte_add_rows_f32_to_bf16(void* dst_bf16, int32_t ld, const int32_
 extern "C" int rte_audit_sample_bernoulli(const float* entropy, const int32_t* recipe_id, const float* u, const int32_t* perm_table,
                                           float* ema, const float* recent, const rte_audit_sample_params* prm, int32_t* idx,
                                           int32_t* idx_scatter, float* valid, float* inv_p, float* dist_scale, float* row_weight, float* row_weight_a,
-                                          float* stats, int32_t* status, rte_stream_t stream) {
+                                          float* stats, int32_t* none_audited, int32_t* status, rte_stream_t stream) {
   RTE_CHECK_ARG(entropy && recipe_id && u && ema && recent && prm && idx && idx_scatter && valid && inv_p && dist_scale && row_weight &&
                 row_weight_a && stats);
   RTE_CHECK_ARG(prm->B > 0 && prm->B <= 1024 && prm->R > 0 && prm->R <= 64 && prm->n_cap > 0 && (prm->cap < 0 || perm_table));
@@ -587,7 +588,7 @@ extern "C" int rte_audit_sample_bernoulli(const float* entropy, const int32_t* r
   P.cov_min = prm->coverage_min; P.cov_beta = prm->coverage_beta; P.inv_rk = prm->inv_r_plus_k; P.w0 = prm->w0;
   P.B = prm->B; P.R = prm->R; P.cap = prm->cap; P.n_cap = prm->n_cap; P.weight_mode = prm->weight_mode;
   audit_sample_kernel<<<1, 1024, 0, ST(stream)>>>(entropy, recipe_id, u, perm_table, ema, recent, P, idx, idx_scatter, valid, inv_p,
-                                                  dist_scale, row_weight, row_weight_a, stats, status);
+                                                  dist_scale, row_weight, row_weight_a, stats, none_audited, status);
   RTE_LAUNCH_CHECK();
   return RTE_OK;
 }

@@ -461,13 +461,16 @@ __global__ void __launch_bounds__(256)
 adamw_kernel(const rte_adamw_tensor* __restrict__ table, const int32_t* __restrict__ chunk_tensor,
              const int32_t* __restrict__ chunk_index, const float* __restrict__ lr_table,
              const int32_t* __restrict__ step_count, float beta1, float beta2, float eps, float wd,
-             const float* __restrict__ grad_scale, const int32_t* __restrict__ skip, float* __restrict__ metric_partial) {
+             const float* __restrict__ grad_scale, const int32_t* __restrict__ skip, float* __restrict__ metric_partial,
+             const int32_t* __restrict__ absent_flag, const uint8_t* __restrict__ absent_mask) {
   __shared__ float red[32];
-  if (skip != nullptr && *skip != 0) {
+  const int ti = chunk_tensor[blockIdx.x];
+  // dropped step, or a tensor that received no gradient in this step (torch.optim.AdamW skips `grad is None`: no decay,
+  // no moment update, no step count)
+  if ((skip != nullptr && *skip != 0) || (absent_flag != nullptr && *absent_flag != 0 && absent_mask[ti] != 0)) {
     if (metric_partial != nullptr && threadIdx.x == 0) { metric_partial[2 * blockIdx.x] = 0.f; metric_partial[2 * blockIdx.x + 1] = 0.f; }
     return;
   }
-  const int ti = chunk_tensor[blockIdx.x];
   const rte_adamw_tensor t = table[ti];
   const long long base = (long long)chunk_index[blockIdx.x] * RTE_ADAMW_CHUNK;
   const float lr = lr_table[t.lr_group];
@@ -498,10 +501,11 @@ adamw_kernel(const rte_adamw_tensor* __restrict__ table, const int32_t* __restri
   }
 }
 __global__ void adamw_step_kernel(const rte_adamw_tensor* __restrict__ table, int n_tensors, int32_t* step_count,
-                                  const int32_t* __restrict__ skip) {
+                                  const int32_t* __restrict__ skip, const int32_t* __restrict__ absent_flag,
+                                  const uint8_t* __restrict__ absent_mask) {
   if (skip != nullptr && *skip != 0) return;
   const int i = blockIdx.x * blockDim.x + threadIdx.x;
-  if (i < n_tensors) step_count[table[i].step_slot] += 1;
+  if (i < n_tensors && !(absent_flag != nullptr && *absent_flag != 0 && absent_mask[i] != 0)) step_count[table[i].step_slot] += 1;
 }
 // out[2*g] = sum of grad^2, out[2*g+1] = sum of param^2 over the chunks of the tensors of metric group g = blockIdx.x
 // (fixed summation order: reproducible).
@@ -913,15 +917,20 @@ extern "C" int rte_adamw_multi_tensor_ex(const rte_adamw_tensor* table, int32_t 
                                          const float* grad_scale, const rte_adamw_extras* ex, rte_stream_t stream) {
   RTE_CHECK_ARG(table && chunk_tensor && chunk_index && lr_table && step_count && n_tensors > 0 && total_chunks > 0);
   const int32_t* skip = ex ? ex->skip : nullptr;
+  const int32_t* absent_flag = ex ? ex->absent_flag : nullptr;
+  const uint8_t* absent_mask = ex ? ex->absent_mask : nullptr;
+  RTE_CHECK_ARG((absent_flag == nullptr) == (absent_mask == nullptr));
   float* mpart = nullptr;
   if (ex && ex->metric_out) {
     RTE_CHECK_ARG(ex->metric_partial && ex->metric_group && ex->n_metric_groups > 0);
     mpart = ex->metric_partial;
   }
   adamw_kernel<<<(unsigned)total_chunks, 256, 0, ST(stream)>>>(table, chunk_tensor, chunk_index, lr_table, step_count,
-                                                               beta1, beta2, eps, weight_decay, grad_scale, skip, mpart);
+                                                               beta1, beta2, eps, weight_decay, grad_scale, skip, mpart,
+                                                               absent_flag, absent_mask);
   RTE_LAUNCH_CHECK();
-  adamw_step_kernel<<<rte::ceil_div(n_tensors, 128), 128, 0, ST(stream)>>>(table, n_tensors, step_count, skip);
+  adamw_step_kernel<<<rte::ceil_div(n_tensors, 128), 128, 0, ST(stream)>>>(table, n_tensors, step_count, skip, absent_flag,
+                                                                           absent_mask);
   RTE_LAUNCH_CHECK();
   if (mpart) {
     adamw_metric_kernel<<<ex->n_metric_groups, 256, 0, ST(stream)>>>(chunk_tensor, ex->metric_group, total_chunks, mpart,

@@ -400,6 +400,15 @@ class TrainEngine:
                         metric_group=metric_group_of(n, cfg.topology))
                    for n in self.trainable]
         self.plan = AdamWPlan(entries, len(LR_GROUPS), dev, n_metric_groups=len(METRIC_GROUPS))
+        # Bernoulli sampler: on a step that audited nobody the recurrent core receives no gradient, and the reference's
+        # optimiser then leaves it alone (`grad is None`: no decay, no moments, no step count).  `_core_absent` stays 1
+        # while no micro-batch of the current accumulation cycle has audited anybody.
+        self._core_absent = self._none_audited = self._absent_mask = None
+        if self.audit_bernoulli and self.audit_grad:
+            from .audit import CORE_PARAMS
+            self._core_absent = torch.ones(1, dtype=torch.int32, device=dev)
+            self._none_audited = torch.zeros(1, dtype=torch.int32, device=dev)
+            self._absent_mask = torch.tensor([1 if n in CORE_PARAMS else 0 for n in self.trainable], dtype=torch.uint8, device=dev)
         self._lr_stage = None                            # pinned staging of the per-step learning-rate table
         self._tokens_scheduled = 0                       # tokens of the steps submitted so far (LR schedule, all ranks)
         self._write_lr_table()
@@ -1214,7 +1223,10 @@ class TrainEngine:
             clip = self.scalars[4:5]
         self._loss_guard()
         o.adamw(self.plan, 0.9, 0.999, 1e-8, tr.weight_decay, clip, skip=self.skip_flag,
-                metric_out=self._metric_sums if self.grad_metrics else None)
+                metric_out=self._metric_sums if self.grad_metrics else None,
+                absent_flag=self._core_absent, absent_mask=self._absent_mask)
+        if self._core_absent is not None:
+            self._core_absent.fill_(1)
 
     def _accumulate(self, last: bool) -> None:
         """Gradient accumulation: a micro-batch's gradients join `accum_flat` (unless its loss was not finite); on the
@@ -1300,6 +1312,8 @@ class TrainEngine:
         if a is not None:
             a.audit_ema.copy_(keep[0])
             a.recent.copy_(keep[1])
+            if self._core_absent is not None:
+                self._core_absent.fill_(1)
         return out
 
     def evaluate(self, batches) -> dict[str, float]:

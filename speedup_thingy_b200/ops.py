@@ -513,7 +513,7 @@ class CudaOps:
                    _ptr(inv_p_slot) if inv_p_slot is not None else None, float(clip), _ptr(f_hot), _ptr(f_exact), self.stream)
 
     def audit_sample_bernoulli(self, entropy, recipe_id, u, perm_table, ema, recent, prm: dict, idx, idx_scatter, valid, inv_p,
-                               dist_scale, row_weight, row_weight_a, stats) -> None:
+                               dist_scale, row_weight, row_weight_a, stats, none_audited=None) -> None:
         """audit.py:62-132 on the device; `prm`: the fields of rte_audit_sample_params."""
         sp = A.AuditSampleParams()
         for k, v in prm.items():
@@ -521,7 +521,7 @@ class CudaOps:
         self._call("rte_audit_sample_bernoulli", _ptr(entropy), _ptr(recipe_id), _ptr(u),
                    _ptr(perm_table) if perm_table is not None else None, _ptr(ema), _ptr(recent), C.byref(sp), _ptr(idx),
                    _ptr(idx_scatter), _ptr(valid), _ptr(inv_p), _ptr(dist_scale), _ptr(row_weight), _ptr(row_weight_a), _ptr(stats),
-                   C.c_void_p(self.status.data_ptr()), self.stream)
+                   _ptr(none_audited) if none_audited is not None else None, C.c_void_p(self.status.data_ptr()), self.stream)
 
     def scale_rows_f32(self, x, factor, n: int, row_len: int) -> None:
         self._call("rte_scale_rows_f32", _ptr(x), _ptr(factor), n, row_len, self.stream)
@@ -593,16 +593,19 @@ class CudaOps:
 
     # ------------------------------------------------------------------ optimiser
     def adamw(self, plan: "AdamWPlan", beta1, beta2, eps, weight_decay, grad_scale=None, *, skip=None,
-              metric_out=None) -> None:
+              metric_out=None, absent_flag=None, absent_mask=None) -> None:
         """One fused AdamW launch over the plan's tensors.  `skip` (device int32): non-zero drops the update;
-        `metric_out` f32 [plan.n_metric_groups, 2]: per-group sums of grad^2 and param^2 (see rte_adamw_multi_tensor_ex)."""
-        if skip is None and metric_out is None:
+        `metric_out` f32 [plan.n_metric_groups, 2]: per-group sums of grad^2 and param^2 (see rte_adamw_multi_tensor_ex);
+        `absent_flag` (device int32) + `absent_mask` (device uint8 per plan tensor): tensors without a gradient this step."""
+        if skip is None and metric_out is None and absent_flag is None:
             self._call("rte_adamw_multi_tensor", _ptr(plan.table), plan.n_tensors, plan.total_chunks,
                        _ptr(plan.chunk_tensor), _ptr(plan.chunk_index), _ptr(plan.lr_table), _ptr(plan.step_count),
                        beta1, beta2, eps, weight_decay, _ptr(grad_scale), self.stream)
             return
         ex = A.AdamWExtras()
         ex.skip = skip.data_ptr() if skip is not None else None
+        if absent_flag is not None:
+            ex.absent_flag, ex.absent_mask = absent_flag.data_ptr(), absent_mask.data_ptr()
         if metric_out is not None:
             ex.metric_partial, ex.metric_group = plan.metric_partial.data_ptr(), plan.metric_group.data_ptr()
             ex.metric_out, ex.n_metric_groups = metric_out.data_ptr(), plan.n_metric_groups

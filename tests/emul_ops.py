@@ -568,7 +568,7 @@ class EmulOps:
         f_exact[:n] = inside.float()
 
     def audit_sample_bernoulli(self, entropy, recipe_id, u, perm_table, ema, recent, prm, idx, idx_scatter, valid, inv_p,
-                               dist_scale, row_weight, row_weight_a, stats):
+                               dist_scale, row_weight, row_weight_a, stats, none_audited=None):
         self.launches += 1
         B, R, cap, n_cap = prm["B"], prm["R"], prm["cap"], prm["n_cap"]
         rid = recipe_id[:B].long()
@@ -602,6 +602,8 @@ class EmulOps:
         counts = torch.bincount(rid[mask], minlength=R).float()
         ema[:R] = ema[:R] * prm["coverage_beta"] + counts / max(float(mask.sum()), 1.0) * (1.0 - prm["coverage_beta"])
         stats[0], stats[1], stats[2], stats[3] = float(cand), float(mask.sum()), float(p.mean()), float(p_inc.mean())
+        if none_audited is not None:
+            none_audited[0] = int(a == 0)
 
     def scale_rows_f32(self, x, factor, n, row_len):
         self.launches += 1
@@ -649,7 +651,8 @@ class EmulOps:
         if int(skip[0]) == 0:
             dst.add_(src)
 
-    def adamw(self, plan, beta1, beta2, eps, weight_decay, grad_scale=None, *, skip=None, metric_out=None):
+    def adamw(self, plan, beta1, beta2, eps, weight_decay, grad_scale=None, *, skip=None, metric_out=None, absent_flag=None,
+              absent_mask=None):
         self.launches += 1
         if skip is not None and int(skip[0]) != 0:
             if metric_out is not None:
@@ -658,10 +661,14 @@ class EmulOps:
         gs = float(grad_scale) if grad_scale is not None else 1.0
         if metric_out is not None:
             metric_out.zero_()
-            for e in plan.entries:
+            for i, e in enumerate(plan.entries):
+                if absent_flag is not None and int(absent_flag[0]) and int(absent_mask[i]):
+                    continue
                 metric_out[e["metric_group"], 0] += float((e["g"] * gs).double().pow(2).sum())
                 metric_out[e["metric_group"], 1] += float(e["p"].double().pow(2).sum())
         for i, e in enumerate(plan.entries):
+            if absent_flag is not None and int(absent_flag[0]) and int(absent_mask[i]):
+                continue                      # no gradient this step: torch.optim.AdamW leaves the tensor alone
             lr = float(plan.lr_table[e["lr_group"]])
             step = int(plan.step_count[i]) + 1
             g = e["g"] * gs

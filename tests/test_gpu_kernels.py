@@ -877,3 +877,31 @@ def test_bernoulli_audit_sampler_matches_its_definition(ops, B, R, cap, n_cap, p
     assert torch.allclose(rec.cpu(), (1 - (cos * valid).sum() / valid.sum()).clamp_min(0).view(1), atol=1e-5)
     ops.audit_recent_residual(a.to(DEV), b_.to(DEV), torch.zeros(6, device=DEV), 6, 300, cosd, rec)      # nobody audited: unchanged
     assert torch.allclose(rec.cpu(), (1 - (cos * valid).sum() / valid.sum()).clamp_min(0).view(1), atol=1e-5)
+
+
+def test_adamw_leaves_tensors_without_a_gradient_alone(ops):
+    """absent_flag + absent_mask of rte_adamw_multi_tensor_ex: while the flag is set the masked tensors keep their
+    weights, moments and step counts (torch.optim.AdamW skips `grad is None`) and leave the metric sums; the other
+    tensors step as usual; with the flag clear everything steps."""
+    from speedup_thingy_b200.ops import AdamWPlan
+    g = torch.Generator().manual_seed(9)
+    shapes = [(3000,), (64, 65), (5000,)]
+    ps = [torch.randn(s_, generator=g) for s_ in shapes]
+    dev = [dict(p=p.clone().to(DEV), g=torch.randn(p.shape, generator=g).to(DEV), m=torch.zeros_like(p, device=DEV),
+                v=torch.zeros_like(p, device=DEV), shadow=None, lr_group=0, metric_group=i % 2) for i, p in enumerate(ps)]
+    plan = AdamWPlan(dev, 1, DEV, n_metric_groups=2)
+    plan.lr_table.fill_(1e-2)
+    mask = torch.tensor([0, 1, 0], dtype=torch.uint8, device=DEV)
+    flag = torch.ones(1, dtype=torch.int32, device=DEV)
+    sums = torch.zeros(2, 2, device=DEV)
+    ops.adamw(plan, 0.9, 0.999, 1e-8, 0.1, None, metric_out=sums, absent_flag=flag, absent_mask=mask)
+    torch.cuda.synchronize()
+    assert torch.equal(dev[1]["p"].cpu(), ps[1]) and not dev[1]["m"].any() and not dev[1]["v"].any()
+    assert not torch.equal(dev[0]["p"].cpu(), ps[0]) and not torch.equal(dev[2]["p"].cpu(), ps[2])
+    assert plan.step_count.cpu().tolist() == [1, 0, 1]
+    assert float(sums[1, 0]) == 0.0 and float(sums[0, 0]) > 0.0            # group 1 holds only the masked tensor
+    flag.zero_()
+    ops.adamw(plan, 0.9, 0.999, 1e-8, 0.1, None, metric_out=sums, absent_flag=flag, absent_mask=mask)
+    torch.cuda.synchronize()
+    assert not torch.equal(dev[1]["p"].cpu(), ps[1]) and plan.step_count.cpu().tolist() == [2, 1, 2]
+    assert float(sums[1, 0]) > 0.0
