@@ -552,6 +552,10 @@ int rte_audit_sample_bernoulli(const float* entropy, const int32_t* recipe_id, c
                                float* row_weight_a, float* stats,
                                int32_t* none_audited /* optional: 1 when nobody was audited, else 0 */, int32_t* status,
                                rte_stream_t stream);
+/* Per audited sample j the sums behind macro_alignment_metrics (macro.py:499-546): with a = macro endpoint, b = exact
+ * endpoint, z = h0 (rows of row_len floats): out[j][0..8) = (a.b, a.a, b.b, |a-b|^2, |a-z|^2, |b-z|^2, (a-z).(b-z), 0). */
+int rte_audit_alignment_sums(const float* hot_end, const float* exact_end, const float* h0, int32_t n, int64_t row_len,
+                             float* out, rte_stream_t stream);
 /* x[j, 0..row_len) *= factor[j], j < n (fp32).                                                                      */
 int rte_scale_rows_f32(float* x, const float* factor, int32_t n, int64_t row_len, rte_stream_t stream);
 /* recent[0] = max(1 - mean over valid slots of cosine(hot_end_j, exact_end_j), 0) (audit.py:213-218; rows of row_len

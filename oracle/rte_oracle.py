@@ -635,6 +635,21 @@ def macro_distill_loss(tr: TrainCfg, hot_hidden, exact_hidden, hot_logits, exact
                 endpoint_raw=tr.lambda_endpoint_raw * endpoint_raw)
 
 
+def macro_alignment_metrics(hot_hidden: torch.Tensor, exact_hidden: torch.Tensor, h0: torch.Tensor) -> dict:
+    """macro.py:499-546 without the logits' KL: cosine / mse / norms of the macro and the exact endpoint and of their
+    deltas against h0, each per-sample quantity averaged over the audited samples."""
+    hot_hidden, exact_hidden, h0 = hot_hidden.detach(), exact_hidden.detach(), h0.detach()
+    out = dict(hidden_cosine_exact_macro=F.cosine_similarity(hot_hidden.flatten(1), exact_hidden.flatten(1), dim=-1, eps=1e-8).mean(),
+               hidden_mse_exact_macro=(hot_hidden - exact_hidden).square().mean())
+    macro_norm, exact_norm = _rms(hot_hidden, (1, 2)).mean(), _rms(exact_hidden, (1, 2)).mean()
+    dp, de = hot_hidden - h0, exact_hidden - h0
+    pred_rms, exact_rms = _rms(dp, (1, 2)).mean(), _rms(de, (1, 2)).mean()
+    out.update(macro_norm=macro_norm, exact_norm=exact_norm, macro_exact_norm_ratio=macro_norm / exact_norm.clamp_min(1e-8),
+               delta_cosine_exact_macro=F.cosine_similarity(dp.flatten(1), de.flatten(1), dim=-1, eps=1e-8).mean(),
+               delta_rms_exact=exact_rms, delta_rms_pred=pred_rms, delta_rms_ratio=pred_rms / exact_rms.clamp_min(1e-8))
+    return {k: float(v) for k, v in out.items()}
+
+
 def audit_choice(n: int, k: int, seed: int) -> torch.Tensor:
     """audit.py:99-116 fixed-count sampler: the first k entries of a seeded
     permutation (CPU generator), inclusion probability k/n for every sample."""
@@ -704,7 +719,8 @@ def macro_step_loss(p: dict, cfg: ModelCfg, tr: TrainCfg, tokens: torch.Tensor, 
             corrected[mask] = hot_subset + residual / p_inc[mask].clamp_min(1e-12)
         aux = macro_distill_loss(tr, hot["recurrent_hidden"][mask], exact["recurrent_hidden"],
                                  hot["logits"][mask], exact["logits"], hot["h0"][mask])
-        info.update(exact=exact)
+        info.update(exact=exact, alignment=macro_alignment_metrics(hot["recurrent_hidden"][mask], exact["recurrent_hidden"],
+                                                                   hot["h0"][mask]))
         if audit_state is not None:          # audit.py:213-218: the residual the next step's probabilities see
             cos = F.cosine_similarity(hot["recurrent_hidden"][mask].detach().flatten(1),
                                       exact["recurrent_hidden"].detach().flatten(1), dim=-1, eps=1e-8).mean()

@@ -175,6 +175,7 @@ PROTOTYPES = {
     "rte_audit_sample_bernoulli": (C.c_int, [c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, P(AuditSampleParams), c_vp, c_vp, c_vp, c_vp,
                                              c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, c_vp]),
     "rte_scale_rows_f32": (C.c_int, [c_vp, c_vp, c_i32, c_i64, c_vp]),
+    "rte_audit_alignment_sums": (C.c_int, [c_vp, c_vp, c_vp, c_i32, c_i64, c_vp, c_vp]),
     "rte_audit_recent_residual": (C.c_int, [c_vp, c_vp, c_vp, c_i32, c_i64, c_vp, c_vp, c_vp]),
     "rte_scale_rows_bf16": (C.c_int, [c_vp, c_i32, c_vp, c_i32, c_vp, c_i32, c_i32, c_vp]),
     "rte_add_rows_f32_to_bf16": (C.c_int, [c_vp, c_i32, c_vp, c_i32, c_vp, c_i32, c_i32, c_vp]),

@@ -82,6 +82,7 @@ class AuditReplay:
         self.grad = direct_grads or eng.tr.audit_mode == "gradient_corrected"      # does the replay carry gradients
         self.clip = eng.tr.audit_residual_clip if (self.grad and not direct_grads) else None
         self.f_hot, self.f_exact = e(n), e(n)                             # residual clip: per-sample gradient factors
+        self.align = e(n, 8)                                              # alignment sums (the engine points it at the results)
         self.idx = e(n, dtype=i32)
         self.head_tab, self.ffn_tab = recipe_mask_tables(cfg, dev)
         self.rid, self.active = e(T, n, dtype=i32), e(T, n, dtype=i32)
@@ -335,6 +336,7 @@ class AuditReplay:
         tr, w = eng.tr, 1.0 / eng.loss_div
         o.macro_distill(self.hot_end, self.h[T], self.h0a, tr.lambda_delta_dir * w, tr.lambda_delta_rms * w,
                         tr.lambda_endpoint_normed * w, tr.lambda_endpoint_raw * w, self.terms, self.dhot_extra, n, S, d)
+        o.audit_alignment_sums(self.hot_end, self.h[T], self.h0a, n, S * d, self.align)
         if self.bernoulli:
             # the kernel averaged over all n slots: n / audited on the audited samples' rows, 0 on the others
             o.scale_rows_f32(self.dhot_extra, self.dist_scale, n, S * d)
@@ -618,7 +620,28 @@ class AuditReplay:
             residual = residual.clamp(-float(self.clip), float(self.clip))
         # the control variate is part of the loss only under gradient correction; its value is reported either way
         corr = float((residual / self.p_inc).sum())
-        return dict(correction=corr if self.grad else 0.0, correction_metric=corr, exact=exact, aux=aux)
+        align = self.alignment_metrics(host["align"], float(hot.mean()) / self.S, float(exact.mean()) / self.S)
+        return dict(correction=corr if self.grad else 0.0, correction_metric=corr, exact=exact, aux=aux, alignment=align)
+
+    def alignment_metrics(self, sums: torch.Tensor, hot_nll: float | None = None, exact_nll: float | None = None) -> dict:
+        """macro_alignment_metrics (macro.py:499-546) from the per-sample sums of `rte_audit_alignment_sums`
+        (`sums`: the audited samples' rows only); the logits' KL at temperature 1 is not part of it."""
+        L = float(self.S * self.eng.cfg.d_model)
+        s = sums.double()
+        ab, aa, bb, dd, pp, ee, pe = (s[:, k] for k in range(7))
+        eps = 1e-8
+        cos = (ab / (aa.sqrt().clamp_min(eps) * bb.sqrt().clamp_min(eps))).mean()
+        dcos = (pe / (pp.sqrt().clamp_min(eps) * ee.sqrt().clamp_min(eps))).mean()
+        macro_norm, exact_norm = (aa / L).sqrt().mean(), (bb / L).sqrt().mean()
+        pred_rms, exact_rms = (pp / L).sqrt().mean(), (ee / L).sqrt().mean()
+        out = dict(hidden_cosine_exact_macro=float(cos), hidden_mse_exact_macro=float(dd.sum() / (L * s.shape[0])),
+                   macro_norm=float(macro_norm), exact_norm=float(exact_norm),
+                   macro_exact_norm_ratio=float(macro_norm / exact_norm.clamp_min(1e-8)),
+                   delta_cosine_exact_macro=float(dcos), delta_rms_exact=float(exact_rms), delta_rms_pred=float(pred_rms),
+                   delta_rms_ratio=float(pred_rms / exact_rms.clamp_min(1e-8)))
+        if hot_nll is not None and exact_nll is not None:
+            out["hot_exact_nll_gap"] = hot_nll - exact_nll
+        return out
 
     def _loss_terms_bernoulli(self, hot_per_sample: torch.Tensor, host: dict, temp: float) -> dict:
         """`loss_terms` for the Bernoulli sampler: the audited samples, their count and inclusion probabilities come
@@ -642,4 +665,5 @@ class AuditReplay:
         if self.clip is not None:
             residual = residual.clamp(-float(self.clip), float(self.clip))
         corr = float((residual * inv_p).sum())
-        return dict(correction=corr if self.grad else 0.0, correction_metric=corr, exact=exact, aux=aux, **out)
+        align = self.alignment_metrics(host["align"][:a], float(hot_per_sample[chosen].mean()) / S, float(exact.mean()) / S)
+        return dict(correction=corr if self.grad else 0.0, correction_metric=corr, exact=exact, aux=aux, alignment=align, **out)

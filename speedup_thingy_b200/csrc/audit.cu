@@ -431,6 +431,28 @@ __global__ void audit_recent_kernel(const float* __restrict__ cos_in, const floa
   if (c > 0.f) recent[0] = fmaxf(1.f - s / c, 0.f);
 }
 
+// Sums behind macro_alignment_metrics (macro.py:499-546) for one audited sample per CTA: with a = macro endpoint,
+// b = exact endpoint, z = h0 (rows of row_len floats): out[j] = (a.b, a.a, b.b, |a-b|^2, |a-z|^2, |b-z|^2, (a-z).(b-z), 0).
+__global__ void __launch_bounds__(NTHR)
+alignment_sums_kernel(const float* __restrict__ a, const float* __restrict__ b, const float* __restrict__ z, long long row_len,
+                      float* __restrict__ out) {
+  __shared__ float red[32];
+  const float* x = a + (size_t)blockIdx.x * row_len;
+  const float* y = b + (size_t)blockIdx.x * row_len;
+  const float* w = z + (size_t)blockIdx.x * row_len;
+  float s[7] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+  for (long long i = threadIdx.x; i < row_len; i += NTHR) {
+    const float p = x[i], q = y[i], r = w[i], dp = p - r, dq = q - r, df = p - q;
+    s[0] += p * q; s[1] += p * p; s[2] += q * q; s[3] += df * df; s[4] += dp * dp; s[5] += dq * dq; s[6] += dp * dq;
+  }
+#pragma unroll
+  for (int k = 0; k < 7; ++k) {
+    const float t = rte::block_sum(s[k], red);
+    if (threadIdx.x == 0) out[(size_t)blockIdx.x * 8 + k] = t;
+  }
+  if (threadIdx.x == 0) out[(size_t)blockIdx.x * 8 + 7] = 0.f;
+}
+
 }  // namespace
 
 #define ST(s) reinterpret_cast<cudaStream_t>(s)
@@ -606,6 +628,14 @@ extern "C" int rte_audit_recent_residual(const float* hot_end, const float* exac
   rows_cosine_kernel<<<n, NTHR, 0, ST(stream)>>>(hot_end, exact_end, row_len, cos_scratch);
   RTE_LAUNCH_CHECK();
   audit_recent_kernel<<<1, 32, 0, ST(stream)>>>(cos_scratch, valid, n, recent);
+  RTE_LAUNCH_CHECK();
+  return RTE_OK;
+}
+
+extern "C" int rte_audit_alignment_sums(const float* hot_end, const float* exact_end, const float* h0, int32_t n, int64_t row_len,
+                                        float* out, rte_stream_t stream) {
+  RTE_CHECK_ARG(hot_end && exact_end && h0 && out && n > 0 && row_len > 0);
+  alignment_sums_kernel<<<n, NTHR, 0, ST(stream)>>>(hot_end, exact_end, h0, row_len, out);
   RTE_LAUNCH_CHECK();
   return RTE_OK;
 }

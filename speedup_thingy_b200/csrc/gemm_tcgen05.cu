@@ -42,7 +42,6 @@ constexpr int EPI_WARPS = 8;
 constexpr int SLOT_BYTES = 4096;       // one epilogue staging slot: 32 rows x 128 bytes
 constexpr int MAX_DYN_SMEM = 232448;   // 227 KB of dynamic shared memory per CTA
 constexpr uint32_t WAIT_LIMIT = 24u * 1000u * 1000u;   // polls (with back-off) before a wait gives up
-constexpr uint64_t WAIT_LIMIT_NS = 2000ull * 1000ull * 1000ull;   // ... or nanoseconds of the global timer
 
 #ifdef RTE_GEMM_DIAG
 constexpr bool DIAG = true;    // timing diagnostics: RTE_GEMM_DIAG_FLAGS bit 0 = no stores, 1 = no MMAs, 2 = no loads
@@ -118,48 +117,14 @@ __device__ __forceinline__ bool mbar_test(uint32_t bar, uint32_t parity) {
   }
   return ok != 0;
 }
-__device__ __forceinline__ uint64_t global_timer_ns() {
-  uint64_t t;
-  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-  return t;
-}
-template <int CTAS>
-__device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
-  uint32_t ok;
-  if (CTAS == 1) {
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-        "selp.u32 %0, 1, 0, p;\n\t}"
-        : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
-  } else {
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\t"
-        "selp.u32 %0, 1, 0, p;\n\t}"
-        : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
-  }
-  return ok != 0;
-}
 // Bounded wait: returns false when the limit ran out.
 template <int CTAS>
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
-#ifdef RTE_V_TRYWAIT
-  // try_wait suspends the thread in hardware for a bounded time instead of spinning on shared memory; the total
-  // wait is bounded by the global timer
-  if (mbar_try<CTAS>(bar, parity)) return true;
-  const uint64_t t0 = global_timer_ns();
-  for (;;) {
-    if (mbar_try<CTAS>(bar, parity)) return true;
-    if (global_timer_ns() - t0 > WAIT_LIMIT_NS) return false;
-  }
-#else
   for (uint32_t i = 0; i < WAIT_LIMIT; ++i) {
     if (mbar_test<CTAS>(bar, parity)) return true;
     if (i > 128) __nanosleep(i > 4096 ? 128 : 32);
   }
   return false;
-#endif
 }
 __device__ __forceinline__ void fence_barrier_init() { asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory"); }
 __device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
@@ -503,9 +468,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
             *err_flag = 1;
             ok = false; break;
           }
-#ifndef RTE_V_NOFENCE
           tc_fence_after();
-#endif
           const uint32_t sa = smem_base + stage * L::STAGE_BYTES, sb = sa + L::A_BYTES;
           const uint64_t adesc = make_smem_desc(sa, p.a_mn != 0), bdesc = make_smem_desc(sb, p.b_mn != 0);
           if (!(DIAG && (p.diag & 2)))
@@ -551,15 +514,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
     };
 
     auto epi_wait = [&](uint32_t bar, uint32_t parity) -> bool {
-#ifdef RTE_V_LANE0
-      // one lane waits, the warp follows: 8 polling threads per CTA instead of 256
-      uint32_t done = 1;
-      if (lane == 0) done = mbar_wait<CTAS>(bar, parity) ? 1u : 0u;
-      done = __shfl_sync(0xffffffffu, done, 0);
-      return done != 0;
-#else
       return mbar_wait<CTAS>(bar, parity);
-#endif
     };
     for (int w = unit; w < total_work && ok; w += n_units) {
       const int split = w / tiles, t = w % tiles;

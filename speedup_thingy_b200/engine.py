@@ -438,7 +438,8 @@ class TrainEngine:
         k_a = self.audit_k or 0
         n_mg = len(METRIC_GROUPS)
         # (Bernoulli sampler: + audited sample ids[k] (int32) | 1 / inclusion probability[k] | sampler statistics[4])
-        self._audit_extra = (2 * k_a + 4) if self.audit_bernoulli else 0
+        #  every audit: + alignment sums[k,8] (macro.py:499-546)
+        self._audit_extra = 8 * k_a + ((2 * k_a + 4) if self.audit_bernoulli else 0)
         self._results = torch.zeros(8 + 2 * B + 5 * k_a + 1 + self._audit_extra + 2 * n_mg, dtype=f32, device=dev)
         self.loss_tok = e(M)
         # [0]=sum loss, [1]=aux load, [2]=aux depth, [3]=sumsq, [4]=clip, [5]=1.0 when the step was dropped (non-finite)
@@ -527,8 +528,9 @@ class TrainEngine:
             self.audit.terms = self._results[r0:r0 + 4 * k_a].view(k_a, 4)
             self.audit.exact_loss = self._results[r0 + 4 * k_a:r0 + 5 * k_a]
             self.audit.kl_sum = self._results[r0 + 5 * k_a:r0 + 5 * k_a + 1]
+            self.audit.align = self._results[r0 + 5 * k_a + 1:r0 + 13 * k_a + 1].view(k_a, 8)
             if self.audit_bernoulli:
-                x0 = r0 + 5 * k_a + 1
+                x0 = r0 + 13 * k_a + 1
                 self.audit.idx = self._results[x0:x0 + k_a].view(torch.int32)
                 self.audit.inv_p = self._results[x0 + k_a:x0 + 2 * k_a]
                 self.audit.stats = self._results[x0 + 2 * k_a:x0 + 2 * k_a + 4]
@@ -1362,8 +1364,10 @@ class TrainEngine:
                 "terms": h[r0:r0 + 4 * k_a].view(k_a, 4), "exact_loss": h[r0 + 4 * k_a:r0 + 5 * k_a],
                 "kl_sum": h[r0 + 5 * k_a:r0 + 5 * k_a + 1],
                 "metric_sums": h[r0 + 5 * k_a + 1 + self._audit_extra:].view(len(METRIC_GROUPS), 2)}
-            if self._audit_extra:
-                x0 = r0 + 5 * k_a + 1
+            if k_a:
+                self._host_slots[i]["align"] = h[r0 + 5 * k_a + 1:r0 + 13 * k_a + 1].view(k_a, 8)
+            if self.audit_bernoulli:
+                x0 = r0 + 13 * k_a + 1
                 self._host_slots[i].update(audit_idx=h[x0:x0 + k_a].view(torch.int32), audit_inv_p=h[x0 + k_a:x0 + 2 * k_a],
                                            audit_stats=h[x0 + 2 * k_a:x0 + 2 * k_a + 4])
         return self._host_slots[i]
@@ -1491,6 +1495,7 @@ class TrainEngine:
                            corrected_lm_loss=(float(host["scalars"][0]) + la["correction"]) / (B * S),
                            corrected_metric_loss=(float(host["scalars"][0]) + la["correction_metric"]) / (B * S))
             metrics.update({f"macro_{k}_loss": v for k, v in la["aux"].items()})
+            metrics.update(la.get("alignment", {}))
             if audited:
                 metrics["exact_eval_nll"] = float(la["exact"].mean()) / S
         if getattr(self, "cons_pairs", None):

@@ -523,6 +523,9 @@ class CudaOps:
                    _ptr(idx_scatter), _ptr(valid), _ptr(inv_p), _ptr(dist_scale), _ptr(row_weight), _ptr(row_weight_a), _ptr(stats),
                    _ptr(none_audited) if none_audited is not None else None, C.c_void_p(self.status.data_ptr()), self.stream)
 
+    def audit_alignment_sums(self, hot_end, exact_end, h0, n: int, row_len: int, out) -> None:
+        self._call("rte_audit_alignment_sums", _ptr(hot_end), _ptr(exact_end), _ptr(h0), n, row_len, _ptr(out), self.stream)
+
     def scale_rows_f32(self, x, factor, n: int, row_len: int) -> None:
         self._call("rte_scale_rows_f32", _ptr(x), _ptr(factor), n, row_len, self.stream)
 

@@ -605,6 +605,15 @@ class EmulOps:
         if none_audited is not None:
             none_audited[0] = int(a == 0)
 
+    def audit_alignment_sums(self, hot_end, exact_end, h0, n, row_len, out):
+        self.launches += 1
+        a, b, z = (t.reshape(-1)[: n * row_len].view(n, row_len).double() for t in (hot_end, exact_end, h0))
+        o = out.view(-1)[: n * 8].view(n, 8)
+        cols = [(a * b), (a * a), (b * b), (a - b) ** 2, (a - z) ** 2, (b - z) ** 2, (a - z) * (b - z)]
+        for k, c in enumerate(cols):
+            o[:, k] = c.sum(-1).float()
+        o[:, 7] = 0.0
+
     def scale_rows_f32(self, x, factor, n, row_len):
         self.launches += 1
         x.view(-1)[: n * row_len].view(n, row_len).mul_(factor[:n, None])

@@ -120,6 +120,11 @@ def run_case(name: str, case: dict) -> dict[str, np.ndarray]:
                     out["corrected_loss_per_sample"] = res.audit.corrected_loss_per_sample.detach().numpy().copy()
                     for k_, v_ in res.audit.macro_aux.items():
                         out[f"macro_aux/{k_}"] = np.float64(float(v_))
+                    for k_ in ("hidden_cosine_exact_macro", "hidden_mse_exact_macro", "macro_norm", "exact_norm",
+                               "macro_exact_norm_ratio", "delta_cosine_exact_macro", "delta_rms_exact", "delta_rms_pred",
+                               "delta_rms_ratio"):
+                        if k_ in res.audit.metrics:
+                            out[f"audit_metric/{k_}"] = np.float64(float(res.audit.metrics[k_]))
             else:
                 res = engine.train_step((tokens, targets))
             losses.append(float(res.loss.detach()))

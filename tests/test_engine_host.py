@@ -114,6 +114,15 @@ def _drop_absent_core(eng, grads):
     return {n: g for n, g in grads.items() if n not in CORE_PARAMS}
 
 
+def _check_alignment(eng, info):
+    """macro_alignment_metrics of the audited samples (macro.py:499-546) against the oracle's."""
+    if eng.audit is None or "alignment" not in info:
+        return
+    got = eng.last_audit["alignment"]
+    for key, ref in info["alignment"].items():
+        assert abs(got[key] - ref) <= 2e-2 * max(abs(ref), 5e-2), (key, got[key], ref)      # (cosines near 0: absolute 1e-3)
+
+
 def _share_top_clusters(eng, *oracles):
     """The cluster ranking is a discrete decision on near-tied bf16 scores: the oracle replays the engine's."""
     if eng.shortlist:
@@ -146,9 +155,10 @@ def test_engine_sequence_matches_oracle(name):
     oracle_nc = _oracle(cfg, ocfg, otr_noclip, params)
     loss, grads = eng.loss_and_grads(batch)
     _share_top_clusters(eng, oracle_nc)
-    ref_loss, ref_grads, _ = oracle_nc.loss_and_grads(*batch)
+    ref_loss, ref_grads, ref_info = oracle_nc.loss_and_grads(*batch)
     assert abs(loss - float(ref_loss)) < 2e-2
     grads = _drop_absent_core(eng, grads)
+    _check_alignment(eng, ref_info)
     assert sorted(grads) == sorted(ref_grads)
     for n, g in grads.items():
         err = (g - ref_grads[n]).abs().max().item()

@@ -905,3 +905,17 @@ def test_adamw_leaves_tensors_without_a_gradient_alone(ops):
     torch.cuda.synchronize()
     assert not torch.equal(dev[1]["p"].cpu(), ps[1]) and plan.step_count.cpu().tolist() == [2, 1, 2]
     assert float(sums[1, 0]) > 0.0
+
+
+def test_alignment_sums_match_their_definition(ops):
+    """rte_audit_alignment_sums (the seven per-sample sums behind macro_alignment_metrics, macro.py:499-546)."""
+    from tests.emul_ops import EmulOps
+    g = torch.Generator().manual_seed(4)
+    n, L = 5, 64 * 96
+    a, b, z = (torch.randn(n, L, generator=g) for _ in range(3))
+    got = torch.full((n, 8), 9.0, device=DEV)
+    ops.audit_alignment_sums(a.to(DEV), b.to(DEV), z.to(DEV), n, L, got)
+    want = torch.zeros(n, 8)
+    EmulOps().audit_alignment_sums(a, b, z, n, L, want)
+    torch.cuda.synchronize()
+    assert torch.allclose(got.cpu(), want, rtol=1e-4, atol=1e-2)

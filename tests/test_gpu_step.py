@@ -11,7 +11,7 @@ from oracle import rte_oracle as O
 from speedup_thingy_b200.config import ExperimentConfig, ModelConfig, OutputConfig, TrainingConfig
 from speedup_thingy_b200.engine import TrainEngine, init_parameters, parameter_shapes
 from tests.golden.cases import GOLDEN_CASES
-from tests.test_engine_host import CASES, _drop_absent_core, _macro_scaled, _oracle, _pair, _share_top_clusters
+from tests.test_engine_host import CASES, _check_alignment, _drop_absent_core, _macro_scaled, _oracle, _pair, _share_top_clusters
 
 pytestmark = pytest.mark.gpu
 GOLDEN = Path(__file__).resolve().parent / "golden"
@@ -43,6 +43,7 @@ def test_first_step_loss_and_grads_match_oracle(name):
     ref_loss, ref_grads, info = oracle.loss_and_grads(*batch)
     assert abs(loss - float(ref_loss)) <= 1e-2 * abs(float(ref_loss))
     grads = _drop_absent_core(eng, grads)
+    _check_alignment(eng, info)
     assert sorted(grads) == sorted(ref_grads)
     for n, g in grads.items():
         err = (g.cpu() - ref_grads[n]).abs().max().item()

@@ -51,6 +51,10 @@ def test_first_step_matches_reference(name):
                                    rtol=2e-4, atol=2e-4)
         for key, val in info["aux"].items():
             assert abs(float(val) - float(gold[f"macro_aux/{key}"])) <= 1e-5 + 1e-4 * abs(float(gold[f"macro_aux/{key}"])), key
+        for key, val in info.get("alignment", {}).items():          # macro_alignment_metrics (macro.py:499-546)
+            if f"audit_metric/{key}" in gold:
+                ref = float(gold[f"audit_metric/{key}"])
+                assert abs(val - ref) <= 1e-6 + 2e-4 * abs(ref), (key, val, ref)
     # exactly the parameters the reference gave a gradient to, with the same gradients
     assert sorted(grads) == sorted(str(n) for n in gold["grad_names"])
     for n, g in grads.items():
