@@ -181,7 +181,7 @@ residual_rmsnorm_fwd_kernel(const float* __restrict__ base, const float* __restr
 // and written to row blockIdx.x of the partial buffers (deterministic, no atomics).
 // FILM = false drops the FiLM accumulators (and a third of the registers) for the plain-norm launches.
 template <int NV, bool FILM>
-__global__ void __launch_bounds__(256, NV <= 4 ? (FILM ? 2 : 3) : 1)
+__global__ void __launch_bounds__(256, NV <= 4 ? 2 : 1)
 rmsnorm_bwd_kernel(const float* __restrict__ x, const float* __restrict__ w, const float* __restrict__ fg,
                    const float* __restrict__ rstd, const __nv_bfloat16* __restrict__ dy16,
                    const float* __restrict__ dy32, const float* __restrict__ dres, float* __restrict__ dx32,
@@ -198,7 +198,83 @@ rmsnorm_bwd_kernel(const float* __restrict__ x, const float* __restrict__ w, con
   for (int i = 0; i < NF; ++i) ag[i] = ab[i] = make_float4(0.f, 0.f, 0.f, 0.f);
   const bool want_w = dw_part != nullptr, want_f = FILM && dg_part != nullptr;
 
-  for (int row = blockIdx.x * nwarp + warp; row < rows; row += gridDim.x * nwarp) {
+  int row = blockIdx.x * nwarp + warp;
+  const int stride = gridDim.x * nwarp;
+  if constexpr (!FILM && NV <= 4) {
+    // Two rows per trip with all loads of both rows issued before the first use: a warp that walks its rows one at a
+    // time keeps too few bytes in flight to cover the memory latency (the plain-norm launches of the hot pass).
+    for (; row + stride < rows; row += 2 * stride) {
+      const int rw[2] = {row, row + stride};
+      float rr[2];
+      float4 xh[2][NV], g[2][NV], dyv[2][NV];
+#pragma unroll
+      for (int u = 0; u < 2; ++u) {
+        rr[u] = rstd[rw[u]];
+        const float4* xr = reinterpret_cast<const float4*>(x + (size_t)rw[u] * d);
+#pragma unroll
+        for (int i = 0; i < NV; ++i) {
+          const int c = lane + 32 * i;
+          if (c < d4) {
+            xh[u][i] = xr[c];
+            if (dy16) {
+              const uint2 pk = reinterpret_cast<const uint2*>(dy16 + (size_t)rw[u] * d)[c];
+              const float2 a = rte::unpack_bf16x2(pk.x), b = rte::unpack_bf16x2(pk.y);
+              dyv[u][i] = make_float4(a.x, a.y, b.x, b.y);
+            } else {
+              dyv[u][i] = reinterpret_cast<const float4*>(dy32 + (size_t)rw[u] * d)[c];
+            }
+          }
+        }
+      }
+      float dot[2] = {0.f, 0.f};
+#pragma unroll
+      for (int i = 0; i < NV; ++i) {
+        const int c = lane + 32 * i;
+        if (c < d4) {
+          const float4 ww = w ? reinterpret_cast<const float4*>(w)[c] : make_float4(1.f, 1.f, 1.f, 1.f);
+#pragma unroll
+          for (int u = 0; u < 2; ++u) {
+            const float r = rr[u];
+            const float4 xv = xh[u][i], dv = dyv[u][i];
+            const float4 h = make_float4(xv.x * r, xv.y * r, xv.z * r, xv.w * r);
+            xh[u][i] = h;
+            if (want_w) { aw[i].x += dv.x * h.x; aw[i].y += dv.y * h.y; aw[i].z += dv.z * h.z; aw[i].w += dv.w * h.w; }
+            g[u][i] = make_float4(dv.x * ww.x, dv.y * ww.y, dv.z * ww.z, dv.w * ww.w);
+            dot[u] += g[u][i].x * h.x + g[u][i].y * h.y + g[u][i].z * h.z + g[u][i].w * h.w;
+          }
+        }
+      }
+      dot[0] = warp_sum(dot[0]) / (float)d;
+      dot[1] = warp_sum(dot[1]) / (float)d;
+      if (dres) {                                    // the residual gradient of both rows, loads first
+#pragma unroll
+        for (int u = 0; u < 2; ++u)
+#pragma unroll
+          for (int i = 0; i < NV; ++i) {
+            const int c = lane + 32 * i;
+            if (c < d4) dyv[u][i] = reinterpret_cast<const float4*>(dres + (size_t)rw[u] * d)[c];
+          }
+      }
+#pragma unroll
+      for (int u = 0; u < 2; ++u)
+#pragma unroll
+        for (int i = 0; i < NV; ++i) {
+          const int c = lane + 32 * i;
+          if (c < d4) {
+            const float r = rr[u], dt = dot[u];
+            float4 o = make_float4(r * (g[u][i].x - xh[u][i].x * dt), r * (g[u][i].y - xh[u][i].y * dt),
+                                   r * (g[u][i].z - xh[u][i].z * dt), r * (g[u][i].w - xh[u][i].w * dt));
+            if (dres) { const float4 t = dyv[u][i]; o.x += t.x; o.y += t.y; o.z += t.z; o.w += t.w; }
+            if (dx32) reinterpret_cast<float4*>(dx32 + (size_t)rw[u] * d)[c] = o;
+            if (dx16) {
+              uint2 pk = make_uint2(rte::pack_bf16x2(o.x, o.y), rte::pack_bf16x2(o.z, o.w));
+              reinterpret_cast<uint2*>(dx16 + (size_t)rw[u] * d)[c] = pk;
+            }
+          }
+        }
+    }
+  }
+  for (; row < rows; row += stride) {
     const float r = rstd[row];
     const float4* xr = reinterpret_cast<const float4*>(x + (size_t)row * d);
     float4 xh[NV], g[NV];
