@@ -98,6 +98,13 @@ typedef struct rte_gemm_args {
    * 256-row tiles on pairs of CTAs (tcgen05 cta_group::2), each CTA loading half of the tile's B operand.       */
   int32_t tile_n;
   int32_t cta_pair;
+  /* rte_gemm_bf16_small with splits > 1 only: reduce the partial results inside the launch.  The CTA that finishes
+   * last for an output tile (a counter per tile in split_counters: device int32, at least 1024, zero before the first
+   * use; the kernel leaves them zero) sums the tile's `splits` partials from C in split order and writes
+   * split_out[M,N] (row stride N; += when split_accumulate != 0).  NULL = the caller reduces (rte_reduce_splits).   */
+  int32_t* split_counters;
+  float* split_out;
+  int32_t split_accumulate;
 } rte_gemm_args;
 
 int rte_gemm_bf16(const rte_gemm_args* args, rte_stream_t stream);

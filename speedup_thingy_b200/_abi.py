@@ -38,6 +38,9 @@ class GemmArgs(C.Structure):
         ("split_kblocks", c_vp),
         ("tile_n", c_i32),
         ("cta_pair", c_i32),
+        ("split_counters", c_vp),
+        ("split_out", c_vp),
+        ("split_accumulate", c_i32),
     ]
 
 

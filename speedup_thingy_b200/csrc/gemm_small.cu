@@ -56,6 +56,7 @@ struct SmallParams {
   const float* R; int ldr;
   int M, N, K;
   int k_per_split; long long split_stride;
+  int* counters; float* red_out; int red_accumulate;      // in-launch reduction of the split partials (or counters == NULL)
 };
 
 // The legacy mma.sync path peaks near 2 TFLOP/s per SM on this part, so a CTA's speed is set by how many MMAs it
@@ -179,6 +180,29 @@ gemm_small_kernel(const SmallParams p) {
       }
     }
   }
+  if (OUT_F32 && p.counters != nullptr && gridDim.z > 1) {
+    // The last CTA to finish this output tile sums the tile's partials in split order (a fixed order: the result does
+    // not depend on which CTA comes last) and writes the final values; the counter is left at zero for the next launch.
+    __shared__ int last_s;
+    __threadfence();
+    __syncthreads();
+    const int tile = blockIdx.y * gridDim.x + blockIdx.x;
+    if (threadIdx.x == 0) last_s = (atomicAdd(p.counters + tile, 1) == (int)gridDim.z - 1) ? 1 : 0;
+    __syncthreads();
+    if (last_s) {
+      __threadfence();
+      const float* ws = reinterpret_cast<const float*>(p.C);
+      for (int e = threadIdx.x; e < BM * BN; e += THR) {
+        const int r = m0 + e / BN, c = n0 + e % BN;
+        if (r >= p.M || c >= p.N) continue;
+        const size_t o = (size_t)r * p.ldc + c;
+        float acc = p.red_accumulate ? p.red_out[(size_t)r * p.N + c] : 0.f;
+        for (int s_ = 0; s_ < (int)gridDim.z; ++s_) acc += ws[(size_t)s_ * p.split_stride + o];
+        p.red_out[(size_t)r * p.N + c] = acc;
+      }
+      if (threadIdx.x == 0) p.counters[tile] = 0;
+    }
+  }
 }
 
 }  // namespace
@@ -202,6 +226,10 @@ extern "C" int rte_gemm_bf16_small(const rte_gemm_args* a, rte_stream_t stream) 
   p.k_per_split = rte::ceil_div(ktiles, splits) * BK;
   RTE_CHECK_ARG(rte::ceil_div(a->K, p.k_per_split) == splits);      // every partial must be written
   p.split_stride = a->split_stride;
+  p.counters = splits > 1 ? a->split_counters : nullptr;
+  p.red_out = a->split_out;
+  p.red_accumulate = a->split_accumulate;
+  RTE_CHECK_ARG(p.counters == nullptr || (p.red_out != nullptr && rte::ceil_div(a->N, 32) * rte::ceil_div(a->M, BM) <= 1024));
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
   const bool f32 = a->epilogue == RTE_EPI_F32;
   const int wide_ctas = rte::ceil_div(a->N, 64) * rte::ceil_div(a->M, BM) * splits;

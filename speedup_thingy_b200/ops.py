@@ -49,6 +49,12 @@ class CudaOps:
         # step its hundreds of small CTAs on the replay's high-priority stream displace the hot pass (measured 2.04 ms
         # per step against 1.72 ms with these products on the tcgen05 kernel's 32 tiles).
         self.small_wgrad = os.environ.get("RTE_SMALL_WGRAD", "0") == "1"
+        # RTE_SMALL_FUSED_REDUCE=1: split-K partials of a few-row product summed inside the launch by each tile's last
+        # CTA (one launch less on the replay's chain per product).  Off by default: measured on one machine, the step
+        # takes 1.774 ms with it against 1.754 ms with the separate reduction launch (the serial tail of the last CTA
+        # costs more than the launch it saves).
+        self.small_fused_reduce = os.environ.get("RTE_SMALL_FUSED_REDUCE", "0") == "1"
+        self._split_counters = torch.zeros(1024, dtype=torch.int32, device=self.device)      # per-tile arrival counters
         self.few_rows_max_splits = int(os.environ.get("RTE_FEWROW_SPLITS", "4"))
         self.gemm_max_ctas = 0     # 0 = one persistent CTA per SM; smaller values leave SMs to kernels of other streams
         # tile hints passed to every tcgen05 GEMM (0 = the library's choice): RTE_GEMM_PAIR=0 keeps every tile on one
@@ -95,7 +101,8 @@ class CudaOps:
              epilogue: int = A.EPI_BF16, residual=None, out2=None, pair: int = 0, splits: int = 1,
              split_stride: int = 0, lda: int | None = None, ldb: int | None = None, ldc: int | None = None,
              ldr: int | None = None, ldc2: int | None = None, tile_group=None, n_groups: int = 0,
-             b_group_stride: int = 0, split_kblocks=None, tile_n: int | None = None, cta_pair: int | None = None) -> None:
+             b_group_stride: int = 0, split_kblocks=None, tile_n: int | None = None, cta_pair: int | None = None,
+             split_reduce=None) -> None:
         """out[M,N] = a[M,K] @ b[N,K]^T with the stated epilogue (see rte_gemm_bf16).  `tile_group` switches on the
         grouped mode (B = stack of per-group matrices), `split_kblocks` the ragged split-K."""
         _require_cuda(a, b, out, residual, out2)
@@ -118,6 +125,9 @@ class CudaOps:
         args.split_kblocks = split_kblocks.data_ptr() if split_kblocks is not None else None
         args.tile_n = self.gemm_tile_n if tile_n is None else tile_n
         args.cta_pair = self.gemm_cta_pair if cta_pair is None else cta_pair
+        if split_reduce is not None:          # (counters, final output, accumulate): the few-row kernel reduces its splits itself
+            args.split_counters, args.split_out = split_reduce[0].data_ptr(), split_reduce[1].data_ptr()
+            args.split_accumulate = int(split_reduce[2])
         # few output rows, or (weight gradient of a few rows: A and B stored [K, *]) a reduction over few rows
         few_rows = (epilogue in (A.EPI_BF16, A.EPI_F32) and tile_group is None and split_kblocks is None and K % 8 == 0
                     and (not b_mn or N % 8 == 0)
@@ -170,6 +180,11 @@ class CudaOps:
             splits = max(s for s in range(1, self.few_rows_max_splits + 1) if kb % s == 0 and kb // s >= 2)
         if splits == 1 or ws is None or ws.numel() < splits * M * N:
             self.gemm(a, b, out, M=M, N=N, K=K, b_mn=b_mn, epilogue=A.EPI_F32, residual=out if accumulate else None)
+            return
+        if self.small_fused_reduce and M <= self.small_gemm_rows and -(-N // 32) * -(-M // 64) <= 1024 and out.is_contiguous():
+            # one launch: the last CTA of every output tile sums the tile's partials (fixed order)
+            self.gemm(a, b, ws, M=M, N=N, K=K, b_mn=b_mn, epilogue=A.EPI_F32, splits=splits, split_stride=M * N, ldc=N,
+                      split_reduce=(self._split_counters, out, accumulate))
             return
         self.gemm(a, b, ws, M=M, N=N, K=K, b_mn=b_mn, epilogue=A.EPI_F32, splits=splits, split_stride=M * N, ldc=N)
         self.reduce_splits(ws, splits, M * N, M * N, out, accumulate)

@@ -83,6 +83,18 @@ def test_gemm_few_rows_kernel(ops, M, N, K, b_mn, mode):
         ops.gemm_f32_few_rows(a.to(DEV), b_dev, out, M=M, N=N, K=K, b_mn=b_mn, ws=ws, accumulate=True)
         ref = ref + 3.0
         tol = 2e-3
+        # the in-launch reduction (each tile's last CTA sums the partials) against the separate reduction launch, and a
+        # second fused call: the arrival counters must be back at zero
+        keep, ops.small_fused_reduce = ops.small_fused_reduce, True
+        try:
+            fused, again = torch.full((M, N), 3.0, device=DEV), torch.full((M, N), 3.0, device=DEV)
+            ops.gemm_f32_few_rows(a.to(DEV), b_dev, fused, M=M, N=N, K=K, b_mn=b_mn, ws=ws, accumulate=True)
+            ops.gemm_f32_few_rows(a.to(DEV), b_dev, again, M=M, N=N, K=K, b_mn=b_mn, ws=ws, accumulate=True)
+        finally:
+            ops.small_fused_reduce = keep
+        torch.cuda.synchronize()
+        assert torch.equal(out, fused) and torch.equal(out, again)
+        assert not bool(ops._split_counters.any())
     torch.cuda.synchronize()
     ops.check_status()
     assert ops.launches > before
