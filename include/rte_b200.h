@@ -526,7 +526,8 @@ int rte_kl_distill(const void* hot_logits, const void* exact_logits, float temp,
                    rte_stream_t stream);
 /* The same term with the gradient kept apart: dgrad f32 [rows, V] = coef*(p_hot - p_exact), to be added to the hot
  * dlogits by rte_add_rows_f32_to_bf16 once the hot pass's cross-entropy kernel has written them (the two then run
- * on different streams; the sum and its single bf16 rounding are those of rte_kl_distill).                        */
+ * on different streams; the sum and its single bf16 rounding are those of rte_kl_distill).  dgrad may be NULL: only
+ * kl_rows is written (the temperature-1 KL that macro_alignment_metrics reports, macro.py:538-543).               */
 int rte_kl_distill_grad(const void* hot_logits, const void* exact_logits, float temp, float coef, float* dgrad,
                         float* kl_rows, int32_t rows, int32_t V, rte_stream_t stream);
 /* Residual clip of the control variate (audit.py:306-321): corrected = hot + clamp(exact - hot, -clip, clip) / p.
@@ -560,7 +561,8 @@ int rte_audit_sample_bernoulli(const float* entropy, const int32_t* recipe_id, c
                                int32_t* none_audited /* optional: 1 when nobody was audited, else 0 */, int32_t* status,
                                rte_stream_t stream);
 /* Per audited sample j the sums behind macro_alignment_metrics (macro.py:499-546): with a = macro endpoint, b = exact
- * endpoint, z = h0 (rows of row_len floats): out[j][0..8) = (a.b, a.a, b.b, |a-b|^2, |a-z|^2, |b-z|^2, (a-z).(b-z), 0). */
+ * endpoint, z = h0 (rows of row_len floats): out[j][0..7) = (a.b, a.a, b.b, |a-b|^2, |a-z|^2, |b-z|^2, (a-z).(b-z));
+ * out[j][7] is left as it is (the caller's: the engine keeps the summed temperature-1 logit KL in out[0][7]).       */
 int rte_audit_alignment_sums(const float* hot_end, const float* exact_end, const float* h0, int32_t n, int64_t row_len,
                              float* out, rte_stream_t stream);
 /* x[j, 0..row_len) *= factor[j], j < n (fp32).                                                                      */

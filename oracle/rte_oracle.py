@@ -635,9 +635,11 @@ def macro_distill_loss(tr: TrainCfg, hot_hidden, exact_hidden, hot_logits, exact
                 endpoint_raw=tr.lambda_endpoint_raw * endpoint_raw)
 
 
-def macro_alignment_metrics(hot_hidden: torch.Tensor, exact_hidden: torch.Tensor, h0: torch.Tensor) -> dict:
-    """macro.py:499-546 without the logits' KL: cosine / mse / norms of the macro and the exact endpoint and of their
-    deltas against h0, each per-sample quantity averaged over the audited samples."""
+def macro_alignment_metrics(hot_hidden: torch.Tensor, exact_hidden: torch.Tensor, h0: torch.Tensor,
+                            hot_logits: torch.Tensor | None = None, exact_logits: torch.Tensor | None = None) -> dict:
+    """macro.py:499-546 with audit.py:207-243: cosine / mse / norms of the macro and the exact endpoint and of their
+    deltas against h0, each per-sample quantity averaged over the audited samples, and the KL(exact || hot) of the
+    audited rows' logits at temperature 1 (metrics.py:119-124), averaged over rows."""
     hot_hidden, exact_hidden, h0 = hot_hidden.detach(), exact_hidden.detach(), h0.detach()
     out = dict(hidden_cosine_exact_macro=F.cosine_similarity(hot_hidden.flatten(1), exact_hidden.flatten(1), dim=-1, eps=1e-8).mean(),
                hidden_mse_exact_macro=(hot_hidden - exact_hidden).square().mean())
@@ -647,6 +649,10 @@ def macro_alignment_metrics(hot_hidden: torch.Tensor, exact_hidden: torch.Tensor
     out.update(macro_norm=macro_norm, exact_norm=exact_norm, macro_exact_norm_ratio=macro_norm / exact_norm.clamp_min(1e-8),
                delta_cosine_exact_macro=F.cosine_similarity(dp.flatten(1), de.flatten(1), dim=-1, eps=1e-8).mean(),
                delta_rms_exact=exact_rms, delta_rms_pred=pred_rms, delta_rms_ratio=pred_rms / exact_rms.clamp_min(1e-8))
+    out.update(hidden_cosine=out["hidden_cosine_exact_macro"], hidden_residual_l2=out["hidden_mse_exact_macro"].sqrt())
+    if hot_logits is not None and exact_logits is not None and hot_logits.shape == exact_logits.shape:
+        le, lh = F.log_softmax(exact_logits.detach(), dim=-1), F.log_softmax(hot_logits.detach(), dim=-1)
+        out["logit_kl_exact_macro"] = out["logit_kl"] = (le.exp() * (le - lh)).sum(dim=-1).mean()
     return {k: float(v) for k, v in out.items()}
 
 
@@ -713,14 +719,18 @@ def macro_step_loss(p: dict, cfg: ModelCfg, tr: TrainCfg, tokens: torch.Tensor, 
         exact = exact_from_h0(p, cfg, hot["h0"][mask], targets[mask], route)
         hot_subset = hot["loss_per_sample"][mask]
         residual = exact["loss_per_sample"] - hot_subset
+        raw = residual.detach().float()                   # audit.py:306-310,363: reported before the clip
+        info["residual"] = dict(audit_residual_mean=float(raw.mean()), audit_residual_std=float(raw.std(unbiased=False)),
+                                audit_residual_var=float(raw.var(unbiased=False)), loss_residual=float(raw.mean()))
         if tr.audit_residual_clip is not None:
             residual = residual.clamp(-tr.audit_residual_clip, tr.audit_residual_clip)
+        info["residual"]["clipped_loss_residual"] = float(residual.detach().mean())
         if tr.audit_mode == "gradient_corrected":
             corrected[mask] = hot_subset + residual / p_inc[mask].clamp_min(1e-12)
         aux = macro_distill_loss(tr, hot["recurrent_hidden"][mask], exact["recurrent_hidden"],
                                  hot["logits"][mask], exact["logits"], hot["h0"][mask])
         info.update(exact=exact, alignment=macro_alignment_metrics(hot["recurrent_hidden"][mask], exact["recurrent_hidden"],
-                                                                   hot["h0"][mask]))
+                                                                   hot["h0"][mask], hot["logits"][mask], exact["logits"]))
         if audit_state is not None:          # audit.py:213-218: the residual the next step's probabilities see
             cos = F.cosine_similarity(hot["recurrent_hidden"][mask].detach().flatten(1),
                                       exact["recurrent_hidden"].detach().flatten(1), dim=-1, eps=1e-8).mean()

@@ -81,6 +81,8 @@ class AuditReplay:
         self.bernoulli = (not direct_grads) and getattr(eng, "audit_bernoulli", False)
         self.grad = direct_grads or eng.tr.audit_mode == "gradient_corrected"      # does the replay carry gradients
         self.clip = eng.tr.audit_residual_clip if (self.grad and not direct_grads) else None
+        # (the reported control variate is clipped in every audit mode, audit.py:311-318; `clip` is the device side)
+        self.clip_reported = None if direct_grads else eng.tr.audit_residual_clip
         self.f_hot, self.f_exact = e(n), e(n)                             # residual clip: per-sample gradient factors
         self.align = e(n, 8)                                              # alignment sums (the engine points it at the results)
         self.idx = e(n, dtype=i32)
@@ -106,6 +108,7 @@ class AuditReplay:
         self.loss_tok, self.exact_loss = e(Ma), e(n)
         self.hot_end = e(Ma, d)
         self.terms, self.dhot_extra, self.kl_rows, self.kl_sum = e(n, 4), e(Ma, d), e(Ma), e(1)
+        self.kl1_rows = e(Ma)
         self.dkl = e(Ma, V)
         self.row_weight_a = torch.full((n,), 1.0 / (eng.B * eng.S * eng.loss_div) / self.p_inc, dtype=f32, device=dev)
         self.idx_scatter = self.idx                    # Bernoulli: a second index list with -1 on unused slots
@@ -356,6 +359,13 @@ class AuditReplay:
                 o.scale_rows_f32(self.dkl, self.dist_scale, n, self.S * V)
                 o.scale_rows_f32(self.kl_rows, self.valid, n, self.S)
             o.segment_sum(self.kl_rows, self.kl_sum, 1, Ma)
+            if temp != 1.0:
+                # logit_kl_exact_macro (macro.py:538-543, metrics.py:119-124): the same KL at temperature 1, no
+                # gradient; its sum over the audited rows rides in the free eighth column of the alignment sums
+                o.kl_distill_grad(self.hot_logits, self.logits, 1.0, 0.0, None, self.kl1_rows, Ma, V)
+                if self.bernoulli:
+                    o.scale_rows_f32(self.kl1_rows, self.valid, n, self.S)
+                o.segment_sum(self.kl1_rows, self.align.view(-1)[7:8], 1, Ma)
 
     def add_kl_grad(self) -> None:
         """Hot-pass side of `forward_kl`: dlogits[audited rows] += dkl."""
@@ -616,16 +626,39 @@ class AuditReplay:
                    endpoint_raw=tr.lambda_endpoint_raw * float(terms[:, 3].sum()) / (Ma * d),
                    kl=tr.lambda_kl * float(host["kl_sum"]) / n * temp * temp)
         residual = exact - hot
-        if self.clip is not None:
-            residual = residual.clamp(-float(self.clip), float(self.clip))
+        res = self.residual_metrics(residual)
+        if self.clip_reported is not None:
+            residual = residual.clamp(-float(self.clip_reported), float(self.clip_reported))
+        res["clipped_loss_residual"] = float(residual.mean())
         # the control variate is part of the loss only under gradient correction; its value is reported either way
         corr = float((residual / self.p_inc).sum())
-        align = self.alignment_metrics(host["align"], float(hot.mean()) / self.S, float(exact.mean()) / self.S)
-        return dict(correction=corr if self.grad else 0.0, correction_metric=corr, exact=exact, aux=aux, alignment=align)
+        align = self.alignment_metrics(host["align"], float(hot.mean()) / self.S, float(exact.mean()) / self.S,
+                                       kl1=self._kl1_total(host, temp))
+        return dict(correction=corr if self.grad else 0.0, correction_metric=corr, exact=exact, aux=aux, alignment=align,
+                    residual=res)
 
-    def alignment_metrics(self, sums: torch.Tensor, hot_nll: float | None = None, exact_nll: float | None = None) -> dict:
-        """macro_alignment_metrics (macro.py:499-546) from the per-sample sums of `rte_audit_alignment_sums`
-        (`sums`: the audited samples' rows only); the logits' KL at temperature 1 is not part of it."""
+    @staticmethod
+    def residual_metrics(residual: torch.Tensor) -> dict[str, float]:
+        """audit.py:306-310,363: mean / std / variance (population) of exact - hot over the audited samples, before
+        any clip."""
+        r = residual.double()
+        var = float(r.var(unbiased=False)) if r.numel() else 0.0
+        return dict(audit_residual_mean=float(r.mean()), audit_residual_std=var ** 0.5, audit_residual_var=var,
+                    loss_residual=float(r.mean()))
+
+    def _kl1_total(self, host: dict, temp: float) -> float | None:
+        """Sum over the audited rows of KL(exact || hot) at temperature 1 (None with the shortlist head, which keeps no
+        full hot logits): the eighth column of the first alignment row, or the distillation's own sum when that already
+        runs at temperature 1."""
+        if self.eng.shortlist:
+            return None
+        return float(host["kl_sum"]) if temp == 1.0 else float(host["align"][0, 7])
+
+    def alignment_metrics(self, sums: torch.Tensor, hot_nll: float | None = None, exact_nll: float | None = None,
+                          kl1: float | None = None) -> dict:
+        """macro_alignment_metrics and compute_residual_metrics (macro.py:499-546, audit.py:207-243) from the
+        per-sample sums of `rte_audit_alignment_sums` (`sums`: the audited samples' rows only) and the summed
+        temperature-1 KL of the audited rows' logits (`kl1`)."""
         L = float(self.S * self.eng.cfg.d_model)
         s = sums.double()
         ab, aa, bb, dd, pp, ee, pe = (s[:, k] for k in range(7))
@@ -639,6 +672,9 @@ class AuditReplay:
                    macro_exact_norm_ratio=float(macro_norm / exact_norm.clamp_min(1e-8)),
                    delta_cosine_exact_macro=float(dcos), delta_rms_exact=float(exact_rms), delta_rms_pred=float(pred_rms),
                    delta_rms_ratio=float(pred_rms / exact_rms.clamp_min(1e-8)))
+        out.update(hidden_cosine=out["hidden_cosine_exact_macro"], hidden_residual_l2=out["hidden_mse_exact_macro"] ** 0.5)
+        if kl1 is not None:
+            out["logit_kl_exact_macro"] = out["logit_kl"] = kl1 / (s.shape[0] * self.S)
         if hot_nll is not None and exact_nll is not None:
             out["hot_exact_nll_gap"] = hot_nll - exact_nll
         return out
@@ -662,8 +698,12 @@ class AuditReplay:
                    endpoint_raw=tr.lambda_endpoint_raw * float(terms[:, 3].sum()) / (a * S * d),
                    kl=tr.lambda_kl * float(host["kl_sum"]) / a * temp * temp)
         residual = exact - hot_per_sample[chosen]
-        if self.clip is not None:
-            residual = residual.clamp(-float(self.clip), float(self.clip))
+        res = self.residual_metrics(residual)
+        if self.clip_reported is not None:
+            residual = residual.clamp(-float(self.clip_reported), float(self.clip_reported))
+        res["clipped_loss_residual"] = float(residual.mean())
         corr = float((residual * inv_p).sum())
-        align = self.alignment_metrics(host["align"][:a], float(hot_per_sample[chosen].mean()) / S, float(exact.mean()) / S)
-        return dict(correction=corr if self.grad else 0.0, correction_metric=corr, exact=exact, aux=aux, alignment=align, **out)
+        align = self.alignment_metrics(host["align"][:a], float(hot_per_sample[chosen].mean()) / S, float(exact.mean()) / S,
+                                       kl1=self._kl1_total(host, temp))
+        return dict(correction=corr if self.grad else 0.0, correction_metric=corr, exact=exact, aux=aux, alignment=align,
+                    residual=res, **out)

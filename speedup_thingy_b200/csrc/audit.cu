@@ -257,7 +257,7 @@ kl_distill_kernel(const __nv_bfloat16* __restrict__ hot, const __nv_bfloat16* __
     const float lph = __bfloat162float(hr[c]) * inv_temp - lh, lpe = __bfloat162float(er[c]) * inv_temp - le;
     const float ph = __expf(lph), pe = __expf(lpe);
     kl += pe * (lpe - lph);
-    if (SEPARATE) dsep[(size_t)row * V + c] = coef * (ph - pe);
+    if (SEPARATE) { if (dsep) dsep[(size_t)row * V + c] = coef * (ph - pe); }
     else dr[c] = __float2bfloat16_rn(__bfloat162float(dr[c]) + coef * (ph - pe));
   }
   kl = rte::block_sum(kl, red);
@@ -432,7 +432,7 @@ __global__ void audit_recent_kernel(const float* __restrict__ cos_in, const floa
 }
 
 // Sums behind macro_alignment_metrics (macro.py:499-546) for one audited sample per CTA: with a = macro endpoint,
-// b = exact endpoint, z = h0 (rows of row_len floats): out[j] = (a.b, a.a, b.b, |a-b|^2, |a-z|^2, |b-z|^2, (a-z).(b-z), 0).
+// b = exact endpoint, z = h0 (rows of row_len floats): out[j] = (a.b, a.a, b.b, |a-b|^2, |a-z|^2, |b-z|^2, (a-z).(b-z), untouched).
 __global__ void __launch_bounds__(NTHR)
 alignment_sums_kernel(const float* __restrict__ a, const float* __restrict__ b, const float* __restrict__ z, long long row_len,
                       float* __restrict__ out) {
@@ -450,7 +450,6 @@ alignment_sums_kernel(const float* __restrict__ a, const float* __restrict__ b, 
     const float t = rte::block_sum(s[k], red);
     if (threadIdx.x == 0) out[(size_t)blockIdx.x * 8 + k] = t;
   }
-  if (threadIdx.x == 0) out[(size_t)blockIdx.x * 8 + 7] = 0.f;
 }
 
 }  // namespace
@@ -582,7 +581,7 @@ extern "C" int rte_kl_distill(const void* hot_logits, const void* exact_logits, 
 
 extern "C" int rte_kl_distill_grad(const void* hot_logits, const void* exact_logits, float temp, float coef, float* dgrad,
                                    float* kl_rows, int32_t rows, int32_t V, rte_stream_t stream) {
-  RTE_CHECK_ARG(hot_logits && exact_logits && dgrad && kl_rows && temp > 0.f && rows > 0 && V > 0);
+  RTE_CHECK_ARG(hot_logits && exact_logits && kl_rows && temp > 0.f && rows > 0 && V > 0);
   kl_distill_kernel<true><<<rows, NTHR, 0, ST(stream)>>>(reinterpret_cast<const __nv_bfloat16*>(hot_logits),
       reinterpret_cast<const __nv_bfloat16*>(exact_logits), 1.f / temp, coef, nullptr, 1, nullptr, 0, dgrad, kl_rows, V);
   RTE_LAUNCH_CHECK();

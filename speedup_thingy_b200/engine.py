@@ -1496,6 +1496,7 @@ class TrainEngine:
                            corrected_metric_loss=(float(host["scalars"][0]) + la["correction_metric"]) / (B * S))
             metrics.update({f"macro_{k}_loss": v for k, v in la["aux"].items()})
             metrics.update(la.get("alignment", {}))
+            metrics.update(la.get("residual", {}))
             if audited:
                 metrics["exact_eval_nll"] = float(la["exact"].mean()) / S
         if getattr(self, "cons_pairs", None):

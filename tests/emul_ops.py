@@ -550,7 +550,8 @@ class EmulOps:
         lh = torch.log_softmax(hot_logits.view(rows, V).float() / temp, -1)
         le = torch.log_softmax(exact_logits.view(rows, V).float() / temp, -1)
         kl_rows.view(-1)[:rows] = (le.exp() * (le - lh)).sum(-1)
-        dgrad.view(rows, V).copy_(coef * (lh.exp() - le.exp()))
+        if dgrad is not None:
+            dgrad.view(rows, V).copy_(coef * (lh.exp() - le.exp()))
 
     def add_rows_to_bf16(self, dst_bf16, idx, S, src_f32, rows, V):
         self.launches += 1
@@ -611,8 +612,7 @@ class EmulOps:
         o = out.view(-1)[: n * 8].view(n, 8)
         cols = [(a * b), (a * a), (b * b), (a - b) ** 2, (a - z) ** 2, (b - z) ** 2, (a - z) * (b - z)]
         for k, c in enumerate(cols):
-            o[:, k] = c.sum(-1).float()
-        o[:, 7] = 0.0
+            o[:, k] = c.sum(-1).float()             # (column 7 is the caller's)
 
     def scale_rows_f32(self, x, factor, n, row_len):
         self.launches += 1

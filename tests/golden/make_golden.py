@@ -122,7 +122,9 @@ def run_case(name: str, case: dict) -> dict[str, np.ndarray]:
                         out[f"macro_aux/{k_}"] = np.float64(float(v_))
                     for k_ in ("hidden_cosine_exact_macro", "hidden_mse_exact_macro", "macro_norm", "exact_norm",
                                "macro_exact_norm_ratio", "delta_cosine_exact_macro", "delta_rms_exact", "delta_rms_pred",
-                               "delta_rms_ratio"):
+                               "delta_rms_ratio", "hidden_cosine", "hidden_residual_l2", "logit_kl", "logit_kl_exact_macro",
+                               "audit_residual_mean", "audit_residual_std", "audit_residual_var", "loss_residual",
+                               "clipped_loss_residual"):
                         if k_ in res.audit.metrics:
                             out[f"audit_metric/{k_}"] = np.float64(float(res.audit.metrics[k_]))
             else:

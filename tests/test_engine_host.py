@@ -118,9 +118,16 @@ def _check_alignment(eng, info):
     """macro_alignment_metrics of the audited samples (macro.py:499-546) against the oracle's."""
     if eng.audit is None or "alignment" not in info:
         return
-    got = eng.last_audit["alignment"]
-    for key, ref in info["alignment"].items():
-        assert abs(got[key] - ref) <= 2e-2 * max(abs(ref), 5e-2), (key, got[key], ref)      # (cosines near 0: absolute 1e-3)
+    got = dict(eng.last_audit["alignment"], **eng.last_audit["residual"])
+    for key, ref in dict(info["alignment"], **info["residual"]).items():
+        if key.startswith("logit_kl"):
+            # the engine's logits are bf16: their rounding noise is a sizeable share of a KL of 1e-3 between two
+            # nearly equal distributions (the kernel itself is checked to 1e-3 on given logits)
+            assert abs(got[key] - ref) <= 0.25 * abs(ref) + 1e-4, (key, got[key], ref)
+        elif key.startswith("audit_residual_") or key.endswith("loss_residual"):
+            assert abs(got[key] - ref) <= 2e-2 * max(abs(ref), 1.0), (key, got[key], ref)   # differences of summed losses
+        else:
+            assert abs(got[key] - ref) <= 2e-2 * max(abs(ref), 5e-2), (key, got[key], ref)  # (cosines near 0: absolute 1e-3)
 
 
 def _share_top_clusters(eng, *oracles):

@@ -736,6 +736,12 @@ def test_audit_distillation_terms_and_gradients(ops):
     ops.add_rows_to_bf16(split, idx, S, dsep, n * S, V)
     torch.cuda.synchronize()
     assert torch.equal(fused, split) and torch.equal(kl_rows, kl2)
+    # without a gradient buffer only the rows' KL is written: at temperature 1 the metric of macro.py:538-543
+    kl1 = torch.zeros(n * S, device=DEV)
+    ops.kl_distill_grad(hot_logits.to(DEV), exact_logits.to(DEV), 1.0, 0.0, None, kl1, n * S, V)
+    torch.cuda.synchronize()
+    le, lh = torch.log_softmax(exact_logits.float(), -1), torch.log_softmax(hot_logits.float(), -1)
+    _close(kl1, (le.exp() * (le - lh)).sum(-1), 1e-3, "KL rows at temperature 1")
 
 
 def test_audit_mask_and_residual_helpers(ops):
@@ -927,7 +933,8 @@ def test_alignment_sums_match_their_definition(ops):
     a, b, z = (torch.randn(n, L, generator=g) for _ in range(3))
     got = torch.full((n, 8), 9.0, device=DEV)
     ops.audit_alignment_sums(a.to(DEV), b.to(DEV), z.to(DEV), n, L, got)
-    want = torch.zeros(n, 8)
+    want = torch.full((n, 8), 9.0)                                 # column 7 stays the caller's
     EmulOps().audit_alignment_sums(a, b, z, n, L, want)
     torch.cuda.synchronize()
     assert torch.allclose(got.cpu(), want, rtol=1e-4, atol=1e-2)
+    assert torch.equal(got[:, 7].cpu(), torch.full((n,), 9.0))

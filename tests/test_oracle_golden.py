@@ -51,7 +51,9 @@ def test_first_step_matches_reference(name):
                                    rtol=2e-4, atol=2e-4)
         for key, val in info["aux"].items():
             assert abs(float(val) - float(gold[f"macro_aux/{key}"])) <= 1e-5 + 1e-4 * abs(float(gold[f"macro_aux/{key}"])), key
-        for key, val in info.get("alignment", {}).items():          # macro_alignment_metrics (macro.py:499-546)
+        reported = dict(info.get("alignment", {}), **info.get("residual", {}))
+        assert "audit_metric/logit_kl_exact_macro" not in gold or "logit_kl_exact_macro" in reported
+        for key, val in reported.items():          # macro_alignment_metrics, residual statistics (macro.py:499-546, audit.py:306-310)
             if f"audit_metric/{key}" in gold:
                 ref = float(gold[f"audit_metric/{key}"])
                 assert abs(val - ref) <= 1e-6 + 2e-4 * abs(ref), (key, val, ref)
