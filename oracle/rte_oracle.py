@@ -92,6 +92,18 @@ class TrainCfg:
     audit_beta: float = 0.08
     audit_gamma: float = 0.08
     audit_cap: int | None = None
+    audit_schedule_enabled: bool = False            # the fixed count halves / doubles from step to step (audit.py:137-185)
+    audit_schedule_min_count: int | None = None
+    audit_schedule_nll_gap_threshold: float = 0.05
+    audit_schedule_hidden_cosine_threshold: float = 0.98
+    audit_schedule_residual_var_threshold: float = 1.0
+    audit_schedule_delta_rms_ratio_min: float = 0.9
+    audit_schedule_delta_rms_ratio_max: float = 1.1
+    audit_schedule_hidden_mse_threshold: float = 1.0
+    audit_schedule_macro_norm_threshold: float | None = None
+    audit_schedule_macro_norm_threshold_mult: float = 2.0
+    audit_schedule_require_negative_mse_slope: bool = True
+    audit_schedule_require_negative_norm_slope: bool = True
     lambda_depth: float = 1e-4
     lambda_load: float = 1e-2
     lambda_cover: float = 1e-2
@@ -656,6 +668,37 @@ def macro_alignment_metrics(hot_hidden: torch.Tensor, exact_hidden: torch.Tensor
     return {k: float(v) for k, v in out.items()}
 
 
+def audit_schedule_next_count(tr: TrainCfg, current: int, metrics: dict, batch_size: int, state: dict) -> int:
+    """audit.py:137-185: after a step that audited somebody, the fixed count halves (not below the minimum) when the
+    macro endpoint tracked the exact one -- small loss residual, cosine, delta-RMS ratio, mse, norm, residual variance
+    within their thresholds, mse and norm not rising since the last audited step -- and doubles (up to the batch)
+    otherwise.  `state` keeps the last mse and norm.  A missing metric counts as failing its test."""
+    if not tr.audit_schedule_enabled or current <= 0:
+        return current
+    inf = float("inf")
+    min_count = tr.audit_schedule_min_count if tr.audit_schedule_min_count is not None else max(1, batch_size // 128)
+    hidden_cos = float(metrics.get("hidden_cosine_exact_macro", 0.0))
+    residual_var = float(metrics.get("audit_residual_var", inf))
+    loss_gap = abs(float(metrics.get("hot_exact_nll_gap", metrics.get("loss_residual", inf))))
+    ratio = float(metrics.get("delta_rms_ratio", inf))
+    mse, macro_norm = float(metrics.get("hidden_mse_exact_macro", inf)), float(metrics.get("macro_norm", inf))
+    norm_limit = tr.audit_schedule_macro_norm_threshold
+    if norm_limit is None:
+        norm_limit = tr.audit_schedule_macro_norm_threshold_mult * float(metrics.get("exact_norm", 0.0))
+    mse_slope = 0.0 if state.get("last_hidden_mse") is None else mse - state["last_hidden_mse"]
+    norm_slope = 0.0 if state.get("last_macro_norm") is None else macro_norm - state["last_macro_norm"]
+    good = (loss_gap <= tr.audit_schedule_nll_gap_threshold
+            and hidden_cos >= tr.audit_schedule_hidden_cosine_threshold
+            and tr.audit_schedule_delta_rms_ratio_min <= ratio <= tr.audit_schedule_delta_rms_ratio_max
+            and mse <= tr.audit_schedule_hidden_mse_threshold
+            and macro_norm <= norm_limit
+            and (not tr.audit_schedule_require_negative_mse_slope or mse_slope <= 0)
+            and (not tr.audit_schedule_require_negative_norm_slope or norm_slope <= 0)
+            and residual_var <= tr.audit_schedule_residual_var_threshold)
+    state["last_hidden_mse"], state["last_macro_norm"] = mse, macro_norm
+    return max(min_count, current // 2) if good else min(batch_size, max(current, current * 2))
+
+
 def audit_choice(n: int, k: int, seed: int) -> torch.Tensor:
     """audit.py:99-116 fixed-count sampler: the first k entries of a seeded
     permutation (CPU generator), inclusion probability k/n for every sample."""
@@ -701,6 +744,8 @@ def macro_step_loss(p: dict, cfg: ModelCfg, tr: TrainCfg, tokens: torch.Tensor, 
     aux: dict[str, torch.Tensor] = {}
     info: dict[str, Any] = dict(hot=hot)
     k = tr.audit_fixed_count_per_batch or 0
+    if tr.audit_schedule_enabled and audit_state is not None:
+        k = int(audit_state.get("fixed_count", k))           # audit.py:182-183: the schedule rewrites the count
     b = tokens.shape[0]
     mask = p_inc = None
     if tr.audit_sampler == "bernoulli" and tr.audit_p_max > 0:
@@ -731,6 +776,11 @@ def macro_step_loss(p: dict, cfg: ModelCfg, tr: TrainCfg, tokens: torch.Tensor, 
                                  hot["logits"][mask], exact["logits"], hot["h0"][mask])
         info.update(exact=exact, alignment=macro_alignment_metrics(hot["recurrent_hidden"][mask], exact["recurrent_hidden"],
                                                                    hot["h0"][mask], hot["logits"][mask], exact["logits"]))
+        info["audit_count"] = int(mask.sum())
+        if tr.audit_schedule_enabled and tr.audit_sampler != "bernoulli" and audit_state is not None:      # audit.py:365
+            audit_state["fixed_count"] = audit_schedule_next_count(tr, k, dict(info["alignment"], **info["residual"]), b,
+                                                                    audit_state)
+            info["audit_schedule_next_count"] = audit_state["fixed_count"]
         if audit_state is not None:          # audit.py:213-218: the residual the next step's probabilities see
             cos = F.cosine_similarity(hot["recurrent_hidden"][mask].detach().flatten(1),
                                       exact["recurrent_hidden"].detach().flatten(1), dim=-1, eps=1e-8).mean()

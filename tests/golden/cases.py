@@ -70,6 +70,20 @@ GOLDEN_CASES = {
                    audit_p_max=0.7, audit_alpha=0.5, audit_beta=2.0, audit_gamma=0.3, audit_cap=3, grad_clip_norm=1.0),
         steps=5,        # (at step 6 a near-tied router decision of one sample flips between two fp32 implementations)
     ),
+    # fixed-count sampler with the count schedule: the count halves after a step whose macro endpoint tracked the exact
+    # one and doubles otherwise (thresholds chosen so that both happen within the case)
+    "small_schedule": dict(
+        model=dict(vocab_size=96, d_model=32, n_heads=4, d_ff=64, n_dense_layers=3, n_prelude=1, n_coda=1,
+                   t_max=4, depth_choices=(1, 2, 4), attn_banks=1, ffn_banks=1, head_groups=4, ffn_groups=4,
+                   active_head_groups=2, active_ffn_groups=2, recipe_count=5, macro_rank=8),
+        train=dict(mode="recursive_macro", lr=2e-3, weight_decay=0.1, batch_size=8, seq_len=16, seed=37,
+                   fixed_depth=None, audit_fixed_count_per_batch=2, grad_clip_norm=1.0, audit_schedule_enabled=True,
+                   audit_schedule_min_count=1, audit_schedule_nll_gap_threshold=0.335,
+                   audit_schedule_hidden_cosine_threshold=0.9, audit_schedule_residual_var_threshold=1.0,
+                   audit_schedule_delta_rms_ratio_min=0.0, audit_schedule_delta_rms_ratio_max=10.0,
+                   audit_schedule_require_negative_mse_slope=False, audit_schedule_require_negative_norm_slope=False),
+        steps=8,
+    ),
     # recursive_exact: every sample runs the banked recurrent core (two banks, router-chosen depth)
     "small_exact": dict(
         model=dict(vocab_size=96, d_model=32, n_heads=4, d_ff=64, n_dense_layers=3, n_prelude=1, n_coda=1,

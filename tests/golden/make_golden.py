@@ -54,6 +54,7 @@ def reference_experiment(case: dict, run_dir: str) -> RC.ExperimentConfig:
         audit_gradient_correction=audited and t.get("audit_mode", "gradient_corrected") == "gradient_corrected",
         audit_residual_clip=t.get("audit_residual_clip"), lambda_cons=t.get("lambda_cons", 0.0),
         grad_clip_norm=t.get("grad_clip_norm"),
+        **{k_: v_ for k_, v_ in t.items() if k_.startswith("audit_schedule_")},
         fused_optimizer=False, foreach_optimizer=True, allow_tf32=False, log_every=10_000,
     )
     out = RC.OutputConfig(**case["output"]) if "output" in case else RC.OutputConfig()
@@ -130,6 +131,12 @@ def run_case(name: str, case: dict) -> dict[str, np.ndarray]:
             else:
                 res = engine.train_step((tokens, targets))
             losses.append(float(res.loss.detach()))
+            if case["train"].get("audit_schedule_enabled"):
+                out[f"audit_mask_step{step}"] = res.audit.audit_mask.numpy().copy()
+                out[f"audit_next_count_step{step}"] = np.int64(int(res.audit.metrics["audit_schedule_next_count"]))
+                for k_ in ("hidden_cosine_exact_macro", "hidden_mse_exact_macro", "loss_residual", "audit_residual_var",
+                           "delta_rms_ratio", "macro_norm", "exact_norm"):
+                    out[f"audit_metric_step{step}/{k_}"] = np.float64(float(res.audit.metrics[k_]))
             if case["train"].get("audit_sampler") == "bernoulli":
                 out[f"audit_mask_step{step}"] = res.audit.audit_mask.numpy().copy()
                 out[f"audit_p_step{step}"] = res.audit.p_audit.detach().numpy().copy()

@@ -215,3 +215,49 @@ def test_bernoulli_sampler_follows_the_reference_step_by_step():
         capped += int(not np.allclose(info["p_inc"].numpy(), info["audit_prob"].detach().numpy()))
     assert capped >= 1                      # the cap engaged on some steps and not on others
     assert capped < case["steps"]
+
+
+def test_fixed_count_schedule_follows_the_reference_step_by_step():
+    """audit.py:137-185 over eight optimiser steps: the audited subset of every step (whose size the schedule set after
+    the step before), the count it chose next, and the metrics it decided on equal the reference's; the count goes
+    down and up within the case."""
+    case, cfg, tr, gold, trainer, it = _run("small_schedule")
+    counts = []
+    for step in range(case["steps"]):
+        trainer.train_step(*next(it))
+        info = trainer.last_info
+        assert np.array_equal(info["mask"].numpy(), gold[f"audit_mask_step{step}"]), step
+        assert info["audit_schedule_next_count"] == int(gold[f"audit_next_count_step{step}"]), step
+        seen = dict(info["alignment"], **info["residual"])
+        for key in ("hidden_cosine_exact_macro", "hidden_mse_exact_macro", "loss_residual", "audit_residual_var",
+                    "delta_rms_ratio", "macro_norm", "exact_norm"):
+            ref = float(gold[f"audit_metric_step{step}/{key}"])
+            assert abs(seen[key] - ref) <= 1e-5 + 2e-3 * abs(ref), (step, key, seen[key], ref)
+        counts.append(info["audit_count"])
+    assert counts == [2, 4, 2, 1, 2, 4, 8, 8]
+
+
+def test_fixed_count_schedule_decisions():
+    """The decision rule alone (audit.py:137-185): every threshold can veto a reduction, a rising mse or norm vetoes it
+    when the slope tests are on, the count never leaves [minimum, batch]."""
+    tr = O.TrainCfg(batch_size=8, audit_fixed_count_per_batch=4, audit_schedule_enabled=True, audit_schedule_min_count=1)
+    good = dict(hidden_cosine_exact_macro=0.99, loss_residual=0.01, delta_rms_ratio=1.0, hidden_mse_exact_macro=0.1,
+                macro_norm=1.0, exact_norm=1.0, audit_residual_var=0.0)
+    nxt = lambda cur=4, state=None, **over: O.audit_schedule_next_count(tr, cur, dict(good, **over), 8, {} if state is None else state)  # noqa: E731
+    assert nxt() == 2 and nxt(cur=1) == 1 and nxt(cur=8) == 4
+    for veto in (dict(hidden_mse_exact_macro=10.0), dict(macro_norm=5.0), dict(hidden_cosine_exact_macro=0.9),
+                 dict(loss_residual=-0.2), dict(delta_rms_ratio=1.5), dict(delta_rms_ratio=0.5), dict(audit_residual_var=2.0)):
+        assert nxt(**veto) == 8, veto
+    assert nxt(cur=8, hidden_mse_exact_macro=10.0) == 8                       # capped at the batch
+    state = {}
+    assert nxt(state=state) == 2 and state["last_hidden_mse"] == 0.1
+    assert nxt(state=state, hidden_mse_exact_macro=0.2) == 8                  # mse rose since the last audited step
+    assert nxt(state=state, hidden_mse_exact_macro=0.15) == 2                 # ... and fell again
+    assert nxt(state=state, macro_norm=1.2) == 8                              # norm rose
+    missing = {k: v for k, v in good.items() if k != "audit_residual_var"}
+    assert O.audit_schedule_next_count(tr, 4, missing, 8, {}) == 8            # a missing metric fails its test
+    off = O.TrainCfg(batch_size=8, audit_fixed_count_per_batch=4)
+    assert O.audit_schedule_next_count(off, 4, good, 8, {}) == 4
+    default_min = O.TrainCfg(batch_size=512, audit_fixed_count_per_batch=8, audit_schedule_enabled=True)
+    assert O.audit_schedule_next_count(default_min, 8, good, 512, {}) == 4    # minimum defaults to batch // 128
+    assert O.audit_schedule_next_count(default_min, 4, good, 512, {}) == 4
