@@ -14,9 +14,42 @@ and -- through the cached h0 -- the prelude, exactly as under ``audit_mode: grad
 """
 from __future__ import annotations
 
+import math
+
 import torch
 
 from . import _abi as A
+
+
+def next_fixed_count(tr, current: int, metrics: dict, batch_size: int, state: dict) -> int:
+    """The fixed-count schedule's decision (audit.py:137-185) from the metrics of a step that audited somebody: halve
+    the count (not below `audit_schedule_min_count`, default batch // 128) when the loss residual, the endpoints'
+    cosine, mse, delta-RMS ratio and norm and the residual variance all pass their thresholds and -- where asked --
+    mse and norm did not rise since the last such step (`state`); double it, up to the batch, otherwise.  A metric
+    that is missing fails its test."""
+    if not tr.audit_schedule_enabled or current <= 0:
+        return current
+    get = lambda key, default: float(metrics.get(key, default))            # noqa: E731
+    floor = tr.audit_schedule_min_count if tr.audit_schedule_min_count is not None else max(1, batch_size // 128)
+    # (the reference looks the loss gap up in the audit's own metrics, where only `loss_residual` exists at that point:
+    #  the mean of exact - hot over the audited samples' summed token losses, before any clip)
+    gap = abs(get("loss_residual", math.inf))
+    mse, norm = get("hidden_mse_exact_macro", math.inf), get("macro_norm", math.inf)
+    limit = tr.audit_schedule_macro_norm_threshold
+    if limit is None:
+        limit = tr.audit_schedule_macro_norm_threshold_mult * get("exact_norm", 0.0)
+    rising_mse = state.get("mse") is not None and mse - state["mse"] > 0
+    rising_norm = state.get("norm") is not None and norm - state["norm"] > 0
+    state["mse"], state["norm"] = mse, norm
+    ratio = get("delta_rms_ratio", math.inf)
+    tracked = (gap <= tr.audit_schedule_nll_gap_threshold
+               and get("hidden_cosine_exact_macro", 0.0) >= tr.audit_schedule_hidden_cosine_threshold
+               and tr.audit_schedule_delta_rms_ratio_min <= ratio <= tr.audit_schedule_delta_rms_ratio_max
+               and mse <= tr.audit_schedule_hidden_mse_threshold and norm <= limit
+               and get("audit_residual_var", math.inf) <= tr.audit_schedule_residual_var_threshold
+               and not (tr.audit_schedule_require_negative_mse_slope and rising_mse)
+               and not (tr.audit_schedule_require_negative_norm_slope and rising_norm))
+    return max(floor, current // 2) if tracked else min(batch_size, current * 2)
 
 
 def build_recipes(cfg) -> list[dict]:
@@ -79,6 +112,10 @@ class AuditReplay:
         # Bernoulli sampler (audit.py:79-132): the subset is drawn ON THE DEVICE from this step's routing; `k` is then
         # the capacity of the replay's buffers, slots beyond the audited count carry weight 0
         self.bernoulli = (not direct_grads) and getattr(eng, "audit_bernoulli", False)
+        # Fixed-count schedule (audit.py:137-185): the host draws the subset as for a fixed count, but the count changes
+        # between steps; `k` is again a capacity, and the host stages what the Bernoulli kernel writes on the device
+        self.scheduled = (not direct_grads) and getattr(eng, "audit_scheduled", False)
+        self.padded = self.bernoulli or self.scheduled       # slots beyond the step's audited count carry weight 0
         self.grad = direct_grads or eng.tr.audit_mode == "gradient_corrected"      # does the replay carry gradients
         self.clip = eng.tr.audit_residual_clip if (self.grad and not direct_grads) else None
         # (the reported control variate is clipped in every audit mode, audit.py:311-318; `clip` is the device side)
@@ -111,7 +148,14 @@ class AuditReplay:
         self.kl1_rows = e(Ma)
         self.dkl = e(Ma, V)
         self.row_weight_a = torch.full((n,), 1.0 / (eng.B * eng.S * eng.loss_div) / self.p_inc, dtype=f32, device=dev)
-        self.idx_scatter = self.idx                    # Bernoulli: a second index list with -1 on unused slots
+        self.idx_scatter = self.idx                    # padded subsets: a second index list with -1 on unused slots
+        if self.scheduled:
+            # one staging copy fills: idx_scatter | valid | dist_scale | the replay's loss weights
+            self.sched_pack = e(4 * n)
+            self.idx_scatter = self.sched_pack[0:n].view(i32)
+            self.valid, self.dist_scale, self.row_weight_a = (self.sched_pack[j * n:(j + 1) * n] for j in (1, 2, 3))
+            self.count = int(eng.audit_count0)         # this step's count; `update_schedule` sets the next one
+            self.schedule_state: dict = {}             # mse and norm of the last audited step (the slope tests)
         if self.bernoulli:
             tr, B = eng.tr, eng.B
             self.cap = None if tr.audit_cap is None else int(tr.audit_cap)
@@ -183,6 +227,8 @@ class AuditReplay:
         eng = self.eng
         if self.bernoulli:
             return self._prepare_bernoulli(step_seed)
+        if self.scheduled:
+            return self._prepare_scheduled(step_seed)
         if self._stage is None:
             pin = eng.device.type == "cuda"
             self._stage = [(torch.empty(self.k, dtype=torch.int32, pin_memory=pin),
@@ -225,6 +271,51 @@ class AuditReplay:
         self._prepared = (step_seed, None, h_u, h_perm)
         self._stage_next = (self._stage_next + 1) % 3
 
+    def _prepare_scheduled(self, step_seed: int) -> None:
+        """Count schedule: the subset is the fixed-count sampler's (audit.py:99-116) for the current count; the host
+        writes what `rte_audit_sample_bernoulli` writes on the device for a drawn subset -- slot lists padded to the
+        capacity, per-slot 1/p, the rescaling of the distillation means, both sets of loss weights, the statistics."""
+        eng, n, B = self.eng, self.n, self.eng.B
+        k = min(self.count, B)
+        if k > n:
+            raise RuntimeError(f"the audit schedule asks for {k} audited samples, the replay was built for {n} "
+                               "(TrainEngine(audit_capacity=...))")
+        if self._stage is None:
+            pin = eng.device.type == "cuda"
+            self._stage = [(torch.zeros(2 * n + 4, dtype=torch.float32, pin_memory=pin),
+                            torch.zeros(4 * n, dtype=torch.float32, pin_memory=pin),
+                            torch.zeros(B, dtype=torch.float32, pin_memory=pin),
+                            torch.zeros(1, dtype=torch.int32, pin_memory=pin)) for _ in range(3)]
+            self._stage_next = 0
+        h_blk, h_pack, h_rw, h_none = self._stage[self._stage_next]
+        gen = torch.Generator().manual_seed(step_seed)
+        chosen = torch.sort(torch.randperm(B, generator=gen)[:k]).values.to(torch.int32)
+        p = float(k) / float(B)
+        ip = 1.0 / max(p, 1e-12)
+        w0 = 1.0 / (B * eng.S * eng.loss_div)
+        idx, inv_p, stats = h_blk[0:n].view(torch.int32), h_blk[n:2 * n], h_blk[2 * n:]
+        idx_scatter, valid, dist_scale, rw_a = h_pack[0:n].view(torch.int32), h_pack[n:2 * n], h_pack[2 * n:3 * n], h_pack[3 * n:]
+        idx.zero_(); idx_scatter.fill_(-1)                                                       # noqa: E702
+        for t in (inv_p, valid, dist_scale, rw_a):
+            t.zero_()
+        idx[:k], idx_scatter[:k] = chosen, chosen
+        inv_p[:k], valid[:k], rw_a[:k] = ip, 1.0, w0 * ip
+        if k:
+            dist_scale[:k] = float(n) / float(k)
+        stats.copy_(torch.tensor([float(k), float(k), p, p]))
+        h_rw.fill_(w0)
+        if k and self.grad and self.clip is None:
+            h_rw[chosen.long()] = w0 * (1.0 - ip)              # d corrected / d hot on audited samples
+        h_none.fill_(0 if k else 1)
+        self.p_inc = max(p, 1e-12)
+        self._prepared = (step_seed, chosen.long(), h_blk, h_pack, h_rw, h_none)
+        self._stage_next = (self._stage_next + 1) % 3
+
+    def update_schedule(self, metrics: dict) -> int:
+        """audit.py:137-185, called with the metrics of a step that audited somebody: sets the next step's count."""
+        self.count = next_fixed_count(self.eng.tr, self.count, metrics, self.eng.B, self.schedule_state)
+        return self.count
+
     def sample(self) -> None:
         """Device half of the Bernoulli sampler, after the router: audit probabilities, the subset, its per-sample
         inclusion probabilities, the loss weights of the hot rows and of the replay, the coverage average."""
@@ -256,6 +347,16 @@ class AuditReplay:
             if self.perm_dev is not None:
                 self.perm_dev.copy_(h_perm, non_blocking=True)
             self.last_chosen = None
+            return
+        if self.scheduled:
+            _, chosen, h_blk, h_pack, h_rw, h_none = self._prepared
+            self._prepared = None
+            self.sampler_block.copy_(h_blk, non_blocking=True)
+            self.sched_pack.copy_(h_pack, non_blocking=True)
+            eng.row_weight.copy_(h_rw, non_blocking=True)
+            if eng._none_audited is not None:
+                eng._none_audited.copy_(h_none, non_blocking=True)
+            self.last_chosen = chosen
             return
         _, chosen, h_idx, h_rw = self._prepared
         self._prepared = None
@@ -340,9 +441,10 @@ class AuditReplay:
         o.macro_distill(self.hot_end, self.h[T], self.h0a, tr.lambda_delta_dir * w, tr.lambda_delta_rms * w,
                         tr.lambda_endpoint_normed * w, tr.lambda_endpoint_raw * w, self.terms, self.dhot_extra, n, S, d)
         o.audit_alignment_sums(self.hot_end, self.h[T], self.h0a, n, S * d, self.align)
-        if self.bernoulli:
+        if self.padded:
             # the kernel averaged over all n slots: n / audited on the audited samples' rows, 0 on the others
             o.scale_rows_f32(self.dhot_extra, self.dist_scale, n, S * d)
+        if self.bernoulli:
             o.audit_recent_residual(self.hot_end, self.h[T], self.valid, n, S * d, self.cos, self.recent)
 
     def forward_kl(self) -> None:
@@ -355,7 +457,7 @@ class AuditReplay:
         temp = max(float(tr.distill_temperature), 1e-6)
         if not eng.shortlist:      # the shortlist head keeps no full hot logits, so the KL term is absent (models.py:698-703)
             o.kl_distill_grad(self.hot_logits, self.logits, temp, tr.lambda_kl * w * temp / n, self.dkl, self.kl_rows, Ma, V)
-            if self.bernoulli:
+            if self.padded:
                 o.scale_rows_f32(self.dkl, self.dist_scale, n, self.S * V)
                 o.scale_rows_f32(self.kl_rows, self.valid, n, self.S)
             o.segment_sum(self.kl_rows, self.kl_sum, 1, Ma)
@@ -363,7 +465,7 @@ class AuditReplay:
                 # logit_kl_exact_macro (macro.py:538-543, metrics.py:119-124): the same KL at temperature 1, no
                 # gradient; its sum over the audited rows rides in the free eighth column of the alignment sums
                 o.kl_distill_grad(self.hot_logits, self.logits, 1.0, 0.0, None, self.kl1_rows, Ma, V)
-                if self.bernoulli:
+                if self.padded:
                     o.scale_rows_f32(self.kl1_rows, self.valid, n, self.S)
                 o.segment_sum(self.kl1_rows, self.align.view(-1)[7:8], 1, Ma)
 
@@ -389,7 +491,7 @@ class AuditReplay:
         eng = self.eng
         o = eng.ops
         o.audit_clip(eng.loss_per_sample, self.exact_loss, self.idx, self.n, 1.0 / self.p_inc, float(self.clip),
-                     self.f_hot, self.f_exact, inv_p_slot=self.inv_p if self.bernoulli else None)
+                     self.f_hot, self.f_exact, inv_p_slot=self.inv_p if self.padded else None)
         o.scale_rows_bf16(self.logits, None, self.S, self.f_exact, self.Ma, eng.cfg.vocab_size)
 
     def clip_hot(self) -> None:
@@ -615,8 +717,8 @@ class AuditReplay:
         step's fetched results (`terms`, `exact_loss`, `kl_sum` already on the host)."""
         tr, n, Ma, d = self.eng.tr, self.n, self.Ma, self.eng.cfg.d_model
         temp = max(float(tr.distill_temperature), 1e-6)
-        if self.bernoulli:
-            return self._loss_terms_bernoulli(hot_per_sample, host, temp)
+        if self.padded:
+            return self._loss_terms_padded(hot_per_sample, host, temp)
         terms = host["terms"]
         exact = host["exact_loss"].clone()
         hot = hot_per_sample[self.last_chosen if chosen is None else chosen]
@@ -679,9 +781,9 @@ class AuditReplay:
             out["hot_exact_nll_gap"] = hot_nll - exact_nll
         return out
 
-    def _loss_terms_bernoulli(self, hot_per_sample: torch.Tensor, host: dict, temp: float) -> dict:
-        """`loss_terms` for the Bernoulli sampler: the audited samples, their count and inclusion probabilities come
-        back from the device with the step's results; every mean runs over the audited samples (none: all terms 0)."""
+    def _loss_terms_padded(self, hot_per_sample: torch.Tensor, host: dict, temp: float) -> dict:
+        """`loss_terms` for the Bernoulli sampler and the count schedule: the audited samples, their count and inclusion
+        probabilities come back with the step's results; every mean runs over the audited samples (none: all terms 0)."""
         tr, S, d = self.eng.tr, self.S, self.eng.cfg.d_model
         stats = host["audit_stats"]
         a = min(int(round(float(stats[1]))), self.n)

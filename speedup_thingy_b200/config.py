@@ -375,8 +375,6 @@ def unsupported(config: ExperimentConfig) -> list[str]:
     if recursive and t.audits_enabled:
         if t.audit_mode not in ("gradient_corrected", "metric_only", "distill_only"):
             no("training", "audit_mode", "one of gradient_corrected, metric_only, distill_only")
-        if t.audit_schedule_enabled:
-            no("training", "audit_schedule_enabled", "the audit-count schedule is not implemented")
         if t.macro_rms_trust_region or t.macro_rms_clamp_early:
             no("training", "macro_rms_trust_region", "the RMS trust region is not implemented")
     if t.fixed_recipe_schedule is not None:

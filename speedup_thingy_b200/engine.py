@@ -234,7 +234,7 @@ class TrainEngine:
     def __init__(self, config: ExperimentConfig, params: dict[str, torch.Tensor] | None = None, *,
                  device: str | torch.device = "cuda:0", ops=None, use_cuda_graph: bool = True,
                  process_group=None, bucket_cap_mb: float | None = None, swiglu_fuse_max_rows: int = 1024,
-                 grad_metrics: bool = True):
+                 grad_metrics: bool = True, audit_capacity: int | None = None):
         check_supported(config)          # NotImplementedError naming every configured value this path lacks
         self.config = config
         self.cfg, self.tr = config.model, config.training
@@ -287,6 +287,16 @@ class TrainEngine:
             pm = min(max(float(tr.audit_p_max), 0.0), 1.0)
             bound = int(math.ceil(self.B * pm + 6.0 * math.sqrt(self.B * pm * (1.0 - pm)) + 1.0))
             self.audit_k = min(self.B, bound if tr.audit_cap is None else int(tr.audit_cap))
+        # Fixed-count schedule (audit.py:137-185): the count halves or doubles between steps, up to the whole batch; the
+        # replay's buffers get the capacity `audit_capacity` (default: the batch), slots beyond the step's count idle
+        self.audit_scheduled = (not self.dense and tr.mode != "recursive_exact" and bool(self.audit_k)
+                                and not self.audit_bernoulli and tr.audit_schedule_enabled)
+        if self.audit_scheduled:
+            self.audit_count0 = min(self.audit_k, self.B)
+            self.audit_k = self.B if audit_capacity is None else int(audit_capacity)
+            if not self.audit_count0 <= self.audit_k <= self.B:
+                raise ValueError(f"audit_capacity must lie between the initial audit count {self.audit_count0} and the batch size")
+        self.audit_padded = self.audit_bernoulli or self.audit_scheduled
         # audit_mode "metric_only" / "distill_only" run the exact subset without gradients (audit.py:295-298): the replay
         # stops after its forward, the control variate leaves the loss, only the distillation terms reach the hot pass
         self.audit_grad = bool(self.audit_k) and tr.audit_mode == "gradient_corrected"
@@ -404,7 +414,7 @@ class TrainEngine:
         # optimiser then leaves it alone (`grad is None`: no decay, no moments, no step count).  `_core_absent` stays 1
         # while no micro-batch of the current accumulation cycle has audited anybody.
         self._core_absent = self._none_audited = self._absent_mask = None
-        if self.audit_bernoulli and self.audit_grad:
+        if self.audit_padded and self.audit_grad:
             from .audit import CORE_PARAMS
             self._core_absent = torch.ones(1, dtype=torch.int32, device=dev)
             self._none_audited = torch.zeros(1, dtype=torch.int32, device=dev)
@@ -437,9 +447,9 @@ class TrainEngine:
         #   | per metric group (sum grad^2, sum param^2)
         k_a = self.audit_k or 0
         n_mg = len(METRIC_GROUPS)
-        # (Bernoulli sampler: + audited sample ids[k] (int32) | 1 / inclusion probability[k] | sampler statistics[4])
-        #  every audit: + alignment sums[k,8] (macro.py:499-546)
-        self._audit_extra = 8 * k_a + ((2 * k_a + 4) if self.audit_bernoulli else 0)
+        # (Bernoulli sampler, scheduled count: + audited sample ids[k] (int32) | 1 / inclusion probability[k] | sampler
+        #  statistics[4];  every audit: + alignment sums[k,8] (macro.py:499-546)
+        self._audit_extra = 8 * k_a + ((2 * k_a + 4) if self.audit_padded else 0)
         self._results = torch.zeros(8 + 2 * B + 5 * k_a + 1 + self._audit_extra + 2 * n_mg, dtype=f32, device=dev)
         self.loss_tok = e(M)
         # [0]=sum loss, [1]=aux load, [2]=aux depth, [3]=sumsq, [4]=clip, [5]=1.0 when the step was dropped (non-finite)
@@ -529,8 +539,9 @@ class TrainEngine:
             self.audit.exact_loss = self._results[r0 + 4 * k_a:r0 + 5 * k_a]
             self.audit.kl_sum = self._results[r0 + 5 * k_a:r0 + 5 * k_a + 1]
             self.audit.align = self._results[r0 + 5 * k_a + 1:r0 + 13 * k_a + 1].view(k_a, 8)
-            if self.audit_bernoulli:
+            if self.audit_padded:
                 x0 = r0 + 13 * k_a + 1
+                self.audit.sampler_block = self._results[x0:x0 + 2 * k_a + 4]       # the three views below, contiguous
                 self.audit.idx = self._results[x0:x0 + k_a].view(torch.int32)
                 self.audit.inv_p = self._results[x0 + k_a:x0 + 2 * k_a]
                 self.audit.stats = self._results[x0 + 2 * k_a:x0 + 2 * k_a + 4]
@@ -939,6 +950,8 @@ class TrainEngine:
                 self._side_wait_main()
                 with self._on_side():
                     self.audit.forward_replay_head(h0)
+                if self.audit.scheduled and self._core_absent is not None:
+                    self._core_absent.mul_(self._none_audited)      # (a schedule whose minimum is 0 can stop auditing)
             o.router_fwd(h0, self._router_weight_dict(), self.depth_values, self.route, B=B, S=S, d=d,
                          hid=cfg.router_hidden_dim, R=cfg.recipe_count, K=len(cfg.depth_choices), T=cfg.t_max,
                          fixed_recipe=tr.fixed_recipe, fixed_depth_id=fixed_depth_id)
@@ -1366,7 +1379,7 @@ class TrainEngine:
                 "metric_sums": h[r0 + 5 * k_a + 1 + self._audit_extra:].view(len(METRIC_GROUPS), 2)}
             if k_a:
                 self._host_slots[i]["align"] = h[r0 + 5 * k_a + 1:r0 + 13 * k_a + 1].view(k_a, 8)
-            if self.audit_bernoulli:
+            if self.audit_padded:
                 x0 = r0 + 13 * k_a + 1
                 self._host_slots[i].update(audit_idx=h[x0:x0 + k_a].view(torch.int32), audit_inv_p=h[x0 + k_a:x0 + 2 * k_a],
                                            audit_stats=h[x0 + 2 * k_a:x0 + 2 * k_a + 4])
@@ -1413,13 +1426,18 @@ class TrainEngine:
 
     MAX_IN_FLIGHT = 2
 
+    @property
+    def _max_in_flight(self) -> int:
+        """The count schedule decides a step's audited count from the metrics of the step before: one step at a time."""
+        return 1 if self.audit_scheduled else self.MAX_IN_FLIGHT
+
     def submit(self, batch) -> None:
         """Queues one training call on a [B,S] int64 (tokens, targets) batch and returns without waiting for the
         device: the batch copy, the step's kernels (one graph replay) and the copy of its results into pinned host
         memory are all stream-ordered.  With `grad_accum_steps` = A the call is a micro-batch: the optimiser runs on
         every A-th call.  At most `MAX_IN_FLIGHT` steps may be queued before `collect` is called; a host batch must
         stay untouched until its step has been collected."""
-        if len(self._pending) >= self.MAX_IN_FLIGHT:
+        if len(self._pending) >= self._max_in_flight:
             raise RuntimeError(f"{len(self._pending)} steps already in flight: call collect() first")
         self._load_batch(batch)
         lr_scale = self.tr.lr_scale(self._tokens_scheduled)        # training.py:470-490, from the tokens seen so far
@@ -1434,8 +1452,9 @@ class TrainEngine:
         self._tokens_scheduled += self.B * self.S * self.world
         if stepping:
             self.global_step += 1
-        if self.audit is not None:
+        if self.audit is not None and not self.audit.scheduled:
             # host work for the NEXT step (the seeded permutation of its audited subset) while the device runs this one
+            # (under the count schedule the next step's count is only known once this step has been collected)
             self.audit.prepare(self.tr.seed + 10_000 + self.global_step)
 
     def _grad_metrics(self, host: dict[str, Any]) -> dict[str, float]:
@@ -1497,6 +1516,11 @@ class TrainEngine:
             metrics.update({f"macro_{k}_loss": v for k, v in la["aux"].items()})
             metrics.update(la.get("alignment", {}))
             metrics.update(la.get("residual", {}))
+            if self.audit.scheduled:
+                metrics["audit_fixed_count"] = float(self.audit.count)
+                if audited:
+                    self.audit.update_schedule(metrics)                  # audit.py:365: decides the next step's count
+                metrics["audit_schedule_next_count"] = float(self.audit.count)
             if audited:
                 metrics["exact_eval_nll"] = float(la["exact"].mean()) / S
         if getattr(self, "cons_pairs", None):
@@ -1523,7 +1547,7 @@ class TrainEngine:
         `MAX_IN_FLIGHT` steps queued so that the host's work for a step (batch copy, launch, result read-back)
         overlaps the device's work on the one before.  Same arithmetic as calling `train_step` per batch."""
         for batch in batches:
-            if len(self._pending) >= self.MAX_IN_FLIGHT:
+            if len(self._pending) >= self._max_in_flight:
                 yield self.collect()
             self.submit(batch)
         while self._pending:

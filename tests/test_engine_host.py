@@ -62,6 +62,15 @@ CASES = {
              # (the log-ratio term of a near-zero macro delta turns Adam's first +-lr steps on noise-level gradients into
              #  per-cent loss differences between a bf16 and an fp32 run; the other cases carry these terms)
              lambda_delta_rms=0.0, lambda_delta_dir=0.0)),
+    "macro_scheduled": (                   # fixed count 2 of 8 under the count schedule (capacity: the batch)
+        dict(vocab_size=96, d_model=64, n_heads=4, d_ff=128, n_prelude=1, n_coda=1, t_max=4, depth_choices=(1, 2, 4),
+             attn_banks=1, ffn_banks=1, head_groups=4, ffn_groups=4, active_head_groups=2, active_ffn_groups=2,
+             recipe_count=5, macro_rank=8),
+        dict(mode="recursive_macro", lr=2e-3, weight_decay=0.1, batch_size=8, seq_len=16, seed=41, fixed_depth=None,
+             audit_fixed_count_per_batch=2, grad_clip_norm=1.0, audit_schedule_enabled=True, audit_schedule_min_count=1,
+             audit_schedule_nll_gap_threshold=0.3, audit_schedule_hidden_cosine_threshold=0.9,
+             audit_schedule_delta_rms_ratio_min=0.0, audit_schedule_delta_rms_ratio_max=10.0,
+             audit_schedule_require_negative_mse_slope=False, audit_schedule_require_negative_norm_slope=False)),
     "preset_small": (                      # the dimensions and settings of the reference's configs/small.yaml
         dict(vocab_size=512, d_model=32, n_heads=4, d_ff=128, n_prelude=1, n_coda=1, t_max=64,
              depth_choices=(1, 2, 4, 8, 16, 32, 64), attn_banks=2, ffn_banks=1, head_groups=4, ffn_groups=16,
@@ -309,3 +318,42 @@ def test_consistency_term_is_material_and_matches_the_oracle():
         err = (g - ref_grads[n]).abs().max().item()
         scale = ref_grads[n].abs().max().item()
         assert err <= 2e-2 * max(scale, 1e-3) + 2e-4, (n, err, scale)
+
+
+def test_count_schedule_follows_the_reference_trajectory():
+    """audit.py:137-185 through the engine: on the golden case the reference ran (count 2 -> 4 -> 2 -> 1 -> 2 -> 4 -> 8
+    -> 8 of a batch of 8) every step audits the reference's subset, decides the reference's next count and reports its
+    loss; two steps can never be in flight, since a step's count depends on the metrics of the step before."""
+    from pathlib import Path
+
+    from tests.golden.cases import GOLDEN_CASES
+    case = GOLDEN_CASES["small_schedule"]
+    gold = np.load(Path(__file__).resolve().parent / "golden" / "small_schedule.npz")
+    cfg = ExperimentConfig(ModelConfig(**case["model"]), TrainingConfig(**case["train"]), OutputConfig())
+    tr = cfg.training
+    params = init_parameters(cfg.model, seed=tr.seed)
+    eng = TrainEngine(cfg, params, device="cpu", ops=EmulOps(), use_cuda_graph=False)
+    assert eng.audit.n == tr.batch_size and eng.audit.scheduled
+    stream = O.zipf_tokens(tr.batch_size * tr.seq_len * (case["steps"] + 2) + 1, cfg.model.vocab_size, seed=tr.seed)
+    it = O.batches(stream, tr.batch_size, tr.seq_len)
+    counts = []
+    for step, r in enumerate(eng.train_steps(next(it) for _ in range(case["steps"]))):
+        mask = torch.zeros(tr.batch_size, dtype=torch.bool)
+        mask[eng.last_audit["chosen"]] = True
+        assert np.array_equal(mask.numpy(), gold[f"audit_mask_step{step}"]), step
+        assert r.metrics["audit_schedule_next_count"] == float(gold[f"audit_next_count_step{step}"]), step
+        assert r.metrics["audit_count"] == r.metrics["audit_fixed_count"] == float(gold[f"audit_mask_step{step}"].sum())
+        assert abs(r.loss - float(gold["losses"][step])) <= 2e-2 * abs(float(gold["losses"][step])), step
+        for key in ("hidden_cosine_exact_macro", "loss_residual", "audit_residual_var", "macro_norm", "exact_norm"):
+            ref = float(gold[f"audit_metric_step{step}/{key}"])
+            assert abs(r.metrics[key] - ref) <= 5e-2 * max(abs(ref), 0.05), (step, key, r.metrics[key], ref)
+        counts.append(int(r.metrics["audit_count"]))
+    assert counts == [2, 4, 2, 1, 2, 4, 8, 8]
+    eng.submit(next(it))
+    with pytest.raises(RuntimeError, match="in flight"):
+        eng.submit(next(it))
+    eng.collect()
+    small = TrainEngine(cfg, params, device="cpu", ops=EmulOps(), use_cuda_graph=False, audit_capacity=2)
+    small.train_step(next(it))                   # 2 of capacity 2; the schedule then asks for 4
+    with pytest.raises(RuntimeError, match="audit_capacity"):
+        small.train_step(next(it))

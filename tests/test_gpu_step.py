@@ -137,6 +137,30 @@ def test_shortlist_loss_curve_matches_reference_golden():
     assert rel.max() <= 1e-2, (rel.max(), losses, gold["losses"])
 
 
+def test_count_schedule_follows_the_reference_trajectory_through_graph_replays():
+    """Fixed-count schedule (audit.py:137-185) on the golden case the reference ran: the audited count goes 2, 4, 2, 1,
+    2, 4, 8, 8 inside a replay built for the whole batch; the captured step graph serves every count (the host only
+    restages slot lists and weights), each step audits the reference's subset and reports its loss within 1 %."""
+    case = GOLDEN_CASES["small_schedule"]
+    cfg, params, eng = _engine(case["model"], case["train"])
+    gold = np.load(GOLDEN / "small_schedule.npz")
+    it = _stream(cfg, case["steps"])
+    counts, losses = [], []
+    for step, r in enumerate(eng.train_steps(next(it) for _ in range(case["steps"]))):
+        mask = torch.zeros(eng.B, dtype=torch.bool)
+        mask[eng.last_audit["chosen"]] = True
+        assert np.array_equal(mask.numpy(), gold[f"audit_mask_step{step}"]), step
+        assert r.metrics["audit_schedule_next_count"] == float(gold[f"audit_next_count_step{step}"]), step
+        for key in ("hidden_cosine_exact_macro", "loss_residual", "audit_residual_var", "macro_norm", "exact_norm"):
+            ref = float(gold[f"audit_metric_step{step}/{key}"])
+            assert abs(r.metrics[key] - ref) <= 5e-2 * max(abs(ref), 0.05), (step, key, r.metrics[key], ref)
+        counts.append(int(r.metrics["audit_count"]))
+        losses.append(r.loss)
+    assert counts == [2, 4, 2, 1, 2, 4, 8, 8] and eng._graph is not None
+    rel = np.abs(np.array(losses) - gold["losses"]) / np.abs(gold["losses"])
+    assert rel.max() <= 1e-2, (rel.max(), losses, gold["losses"])
+
+
 def test_recursive_exact_loss_curve_matches_reference_golden():
     """`recursive_exact` (every sample through the banked recurrent core, two banks, router-chosen depth) against
     the loss curve the reference produced."""
