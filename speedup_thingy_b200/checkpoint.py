@@ -48,6 +48,47 @@ def optimizer_state_dict(engine: TrainEngine) -> dict:
     return opt.state_dict()
 
 
+def audit_state_dict(engine: TrainEngine) -> dict:
+    """The audit sampler's running state under the reference's keys (audit.py:38-48): the last residual and the
+    audit-coverage average of the Bernoulli sampler, mse / norm of the last audited step for the count schedule --
+    plus `fixed_count`, the schedule's current count (the reference keeps that in its live configuration only)."""
+    a = engine.audit
+    if a is None:
+        return {}
+    last = getattr(engine, "last_audit", None) or {}
+    out: dict = {"last_sample_mode": "bernoulli" if a.bernoulli else "fixed_count",
+                 "last_candidate_count": int(last.get("candidates", last.get("audited", a.n if not a.padded else 0))),
+                 "last_capped_fraction": 0.0, "recent_residual": 0.0, "recipe_audit_ema": None,
+                 "last_hidden_mse": None, "last_macro_norm": None}
+    if a.bernoulli:
+        cand, aud = int(last.get("candidates", 0)), int(last.get("audited", 0))
+        out.update(recent_residual=float(a.recent.detach().cpu()), recipe_audit_ema=a.audit_ema.detach().to("cpu").clone(),
+                   last_capped_fraction=float(cand - aud) / max(cand, 1))
+    if a.scheduled:
+        out.update(last_hidden_mse=a.schedule_state.get("mse"), last_macro_norm=a.schedule_state.get("norm"),
+                   fixed_count=int(a.count))
+    return out
+
+
+def load_audit_state(engine: TrainEngine, state: dict) -> None:
+    """Counterpart of `audit_state_dict` (audit.py:50-60); keys a checkpoint lacks leave the fresh state."""
+    a = engine.audit
+    if a is None or not state:
+        return
+    if a.bernoulli:
+        a.recent.fill_(float(state.get("recent_residual", 0.0)))
+        ema = state.get("recipe_audit_ema")
+        if isinstance(ema, torch.Tensor) and ema.numel() == a.audit_ema.numel():
+            a.audit_ema.copy_(ema.to(a.audit_ema.dtype))
+        else:
+            a.audit_ema.zero_()
+    if a.scheduled:
+        a.schedule_state = {"mse": state.get("last_hidden_mse"), "norm": state.get("last_macro_norm")}
+        if state.get("fixed_count") is not None:
+            a.count = int(state["fixed_count"])
+    a._prepared = None                      # whatever was staged for the next step belonged to the old state
+
+
 def save_checkpoint(engine: TrainEngine, path: str | Path, *, data_cursor: int | None = None) -> None:
     """Writes the reference's payload.  The configuration is stored as plain nested dicts (the reference's loader
     never reads it back, training.py:1681-1701), so the file unpickles where this package is not importable."""
@@ -69,7 +110,7 @@ def save_checkpoint(engine: TrainEngine, path: str | Path, *, data_cursor: int |
         model["macro.teacher_delta_rms"] = engine.macro_teacher_delta_rms.clone()
     payload = {"config": dataclasses.asdict(engine.config), "model": model,
                "optimizer": optimizer_state_dict(engine), "global_step": engine.global_step,
-               "global_micro_step": engine._micro, "tokens_seen": engine.tokens_seen, "audit": {},
+               "global_micro_step": engine._micro, "tokens_seen": engine.tokens_seen, "audit": audit_state_dict(engine),
                "aligned_lm_phase": "aligned_lm", "data_cursor": data_cursor, "usage_ema": engine.usage_ema.clone(),
                "torch_rng_state": torch.get_rng_state()}
     p = Path(path)
@@ -133,4 +174,5 @@ def load_checkpoint(engine: TrainEngine, path: str | Path) -> int | None:
     engine._refresh_static_param_sq()
     if isinstance(payload.get("usage_ema"), torch.Tensor) and payload["usage_ema"].shape == engine.usage_ema.shape:
         engine.usage_ema.copy_(payload["usage_ema"])
+    load_audit_state(engine, payload.get("audit") or {})
     return payload.get("data_cursor")

@@ -4,6 +4,7 @@ import os
 import sys
 from pathlib import Path
 
+import numpy as np
 import pytest
 import torch
 
@@ -128,3 +129,34 @@ def test_checkpoint_payload_needs_no_package_and_refuses_steps_in_flight(tmp_pat
         save_checkpoint(eng, tmp_path / "b.pt")
     eng.collect()
     save_checkpoint(eng, tmp_path / "b.pt")
+
+
+@pytest.mark.parametrize("name", ["small_bernoulli", "small_schedule"])
+def test_audit_sampler_state_survives_a_checkpoint(tmp_path, name):
+    """The Bernoulli sampler's last residual and audit-coverage average, and the count schedule's count and slope
+    memory, are part of the checkpoint (audit.py:38-60): a resumed engine audits the same samples and reports the same
+    losses as the one that kept running, and the reference reads the state under its own keys."""
+    case = GOLDEN_CASES[name]
+    cfg, eng = _engine(case)
+    batches = _batches(cfg, 5)
+    for b in batches[:3]:
+        eng.train_step(b)
+    save_checkpoint(eng, tmp_path / "mid.pt")
+    _, resumed = _engine(case)
+    load_checkpoint(resumed, tmp_path / "mid.pt")
+    for b in batches[3:]:
+        x, y = eng.train_step(b), resumed.train_step(b)
+        assert x.loss == y.loss and x.metrics["audit_count"] == y.metrics["audit_count"]
+        assert torch.equal(eng.last_audit["chosen"], resumed.last_audit["chosen"])
+    state = torch.load(tmp_path / "mid.pt", weights_only=False)["audit"]
+    ref = _reference_engine(case, str(tmp_path))
+    ref.load_checkpoint(tmp_path / "mid.pt")
+    if name == "small_bernoulli":
+        assert state["last_sample_mode"] == "bernoulli" and state["recent_residual"] > 0
+        assert ref.audit_engine.recent_residual == state["recent_residual"]
+        assert torch.equal(ref.audit_engine.recipe_audit_ema, state["recipe_audit_ema"])
+        assert float(state["recipe_audit_ema"].sum()) > 0
+    else:
+        assert state["fixed_count"] == int(np.load(Path(__file__).parent / "golden" / f"{name}.npz")["audit_next_count_step2"])
+        assert ref.audit_engine.last_hidden_mse == state["last_hidden_mse"] > 0
+        assert ref.audit_engine.last_macro_norm == state["last_macro_norm"] > 0
