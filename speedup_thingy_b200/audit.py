@@ -128,16 +128,29 @@ class AuditReplay:
         self.h0a, self.targets_a = e(Ma, d), e(Ma, dtype=torch.int64)
         self.h = [e(Ma, d) for _ in range(T + 1)]                          # h[0] = h0a copy, h[t+1] = after pass t
         self.ht, self.u = [e(Ma, d) for _ in range(T)], [e(Ma, d) for _ in range(T)]
-        self.n1, self.n2 = [e(Ma, d, dtype=bf) for _ in range(T)], [e(Ma, d, dtype=bf) for _ in range(T)]
+        # With one attention and one FFN bank, what the weight-gradient products of the T passes read is laid out pass
+        # after pass in one tensor each, so that a weight's gradient is ONE product over T * Ma rows after the last
+        # pass instead of T products that each rewrite the whole fp32 gradient (RTE_REPLAY_FUSED_WGRAD=0: per pass).
+        import os
+        self.fused_wgrad = (cfg.attn_banks == 1 and cfg.ffn_banks == 1 and os.environ.get("RTE_REPLAY_FUSED_WGRAD", "1") != "0")
+        self._stacked: dict[str, torch.Tensor] = {}
+
+        def per_pass(name: str, cols: int) -> list[torch.Tensor]:
+            if not self.fused_wgrad:
+                return [e(Ma, cols, dtype=bf) for _ in range(T)]
+            self._stacked[name] = e(T * Ma, cols, dtype=bf)
+            return [self._stacked[name][t * Ma:(t + 1) * Ma] for t in range(T)]
+
+        self.n1, self.n2 = per_pass("n1", d), per_pass("n2", d)
         self.rstd1, self.rstd2 = [e(Ma) for _ in range(T)], [e(Ma) for _ in range(T)]
         self.attn_acc, self.mlp_acc = [e(Ma, d) for _ in range(T)], [e(Ma, d) for _ in range(T)]
         ab, fb, H = cfg.attn_banks, cfg.ffn_banks, cfg.n_heads
         self.qkv = [[e(Ma, 3 * d, dtype=bf) for _ in range(ab)] for _ in range(T)]
         self.y = [[e(Ma, d, dtype=bf) for _ in range(ab)] for _ in range(T)]
-        self.ym = [[e(Ma, d, dtype=bf) for _ in range(ab)] for _ in range(T)]
+        self.ym = [[x] for x in per_pass("ym", d)] if self.fused_wgrad else [[e(Ma, d, dtype=bf) for _ in range(ab)] for _ in range(T)]
         self.lse = [[e(n * H * S) for _ in range(ab)] for _ in range(T)]
         self.ug = [[e(Ma, 2 * f, dtype=bf) for _ in range(fb)] for _ in range(T)]
-        self.zm = [[e(Ma, f, dtype=bf) for _ in range(fb)] for _ in range(T)]
+        self.zm = [[x] for x in per_pass("zm", f)] if self.fused_wgrad else [[e(Ma, f, dtype=bf) for _ in range(fb)] for _ in range(T)]
         self.coda = [_Block(f"coda.{i}@audit", Ma, cfg, n, S, dev) for i in range(cfg.n_coda)]
         self.tmp = _Temps(Ma, cfg, dev)
         self.hidden16, self.rstd_f = e(Ma, d, dtype=bf), e(Ma)
@@ -171,8 +184,8 @@ class AuditReplay:
         self.dz16 = e(Ma, f, dtype=bf)
         # inputs of the weight-gradient launches are kept per pass: those launches run on their own stream and may
         # trail the data-gradient chain, which therefore must not reuse what they still have to read
-        self.d16_mlp, self.d16_attn = [e(Ma, d, dtype=bf) for _ in range(T)], [e(Ma, d, dtype=bf) for _ in range(T)]
-        self.dug16, self.dqkv16 = [e(Ma, 2 * f, dtype=bf) for _ in range(T)], [e(Ma, 3 * d, dtype=bf) for _ in range(T)]
+        self.d16_mlp, self.d16_attn = per_pass("d16_mlp", d), per_pass("d16_attn", d)
+        self.dug16, self.dqkv16 = per_pass("dug16", 2 * f), per_pass("dqkv16", 3 * d)
         PR = 128
         self.partials = [[(e(PR, d), e(PR, d), e(PR, d)) for _ in range(2)] for _ in range(T)]
         self.coda_tmps = [_Temps(Ma, cfg, dev) for _ in range(cfg.n_coda)]
@@ -216,6 +229,8 @@ class AuditReplay:
             self.g_shared = eng.grads
         big = max(eng.ops.pick_splits(mm, nn, Ma) * mm * nn
                   for mm, nn in ((V, d), (2 * f, d), (d, 2 * f), (3 * d, d), (d, 3 * d), (d, d), (f, d), (d, f)))
+        if self.fused_wgrad:
+            big = max(big, max(eng.ops.pick_splits(mm, nn, T * Ma) * mm * nn for mm, nn in ((f, d), (d, 2 * f), (d, d), (d, 3 * d))))
         self.ws = e(big)
         self.ws_chain = e(16 * Ma * d)          # split-K partials of the chain's own few-row GEMMs
 
@@ -551,6 +566,7 @@ class AuditReplay:
         # the head's deferred launches, which share the split-K workspace, have finished); the single-bank case (the
         # usual one) defers its weight gradients.
         defer = cfg.ffn_banks == 1 and cfg.attn_banks == 1
+        fused = self.fused_wgrad            # the four weight-gradient products once, over all passes, after the loop
         if not defer and eng._param_stream is not None:
             torch.cuda.current_stream(eng.device).wait_stream(eng._param_stream)
         self._defer_param_grads(defer)
@@ -568,11 +584,13 @@ class AuditReplay:
                                           d16m, None, None, self.part_mlp[t * P:(t + 1) * P], n, S * d)
             for bk in range(cfg.ffn_banks):
                 o.gemm(d16m, sh["core.mlp.wd"][bk], self.dz16, M=Ma, N=f, K=d)
-                o.gemm_wgrad(self.zm[t][bk], d16m, g["core.mlp.wd"][bk], M=f, N=d, K=Ma, accumulate=acc, ws=self.ws)
+                if not fused:
+                    o.gemm_wgrad(self.zm[t][bk], d16m, g["core.mlp.wd"][bk], M=f, N=d, K=Ma, accumulate=acc, ws=self.ws)
                 o.swiglu_masked_bwd(self.ug[t][bk], self.dz16, rid, self.ffn_tab[bk], S, dug16, Ma, f)
                 o.gemm_f32_few_rows(dug16, sh["core.mlp.wug"][bk], self.dn_f32, M=Ma, N=d, K=2 * f, b_mn=False,
                                     ws=self.ws_chain, accumulate=bk > 0)
-                o.gemm_wgrad(self.n2[t], dug16, g["core.mlp.wug"][bk], M=d, N=2 * f, K=Ma, accumulate=acc, ws=self.ws)
+                if not fused:
+                    o.gemm_wgrad(self.n2[t], dug16, g["core.mlp.wug"][bk], M=d, N=2 * f, K=Ma, accumulate=acc, ws=self.ws)
             o.rmsnorm_bwd(self.u[t], p["core.norm2.weight"], self.rstd2[t], self.dn_f32, du, du, None,
                           g["core.norm2.weight"], pw2, film_gamma=p["core.pass_gamma2"][t],
                           dgamma_out=g["core.pass_gamma2"][t], dbeta_out=g["core.pass_beta2"][t],
@@ -582,13 +600,15 @@ class AuditReplay:
                                   self.part_attn[t * P:(t + 1) * P], n, S * d)
             for bk in range(cfg.attn_banks):
                 o.gemm(d16a, sh["core.attn.wo"][bk], self.d16b, M=Ma, N=d, K=d)
-                o.gemm_wgrad(self.ym[t][bk], d16a, g["core.attn.wo"][bk], M=d, N=d, K=Ma, accumulate=acc, ws=self.ws)
+                if not fused:
+                    o.gemm_wgrad(self.ym[t][bk], d16a, g["core.attn.wo"][bk], M=d, N=d, K=Ma, accumulate=acc, ws=self.ws)
                 o.colmask_mul(self.d16b, rid, self.head_tab[bk], S, self.d16b, Ma, d)
                 o.attn_bwd(self.qkv[t][bk], self.y[t][bk], self.d16b, self.lse[t][bk], dqkv16, B=n, S=S,
                            n_heads=cfg.n_heads, head_dim=cfg.head_dim)
                 o.gemm_f32_few_rows(dqkv16, sh["core.attn.wqkv"][bk], self.dn_f32, M=Ma, N=d, K=3 * d, b_mn=False,
                                     ws=self.ws_chain, accumulate=bk > 0)
-                o.gemm_wgrad(self.n1[t], dqkv16, g["core.attn.wqkv"][bk], M=d, N=3 * d, K=Ma, accumulate=acc, ws=self.ws)
+                if not fused:
+                    o.gemm_wgrad(self.n1[t], dqkv16, g["core.attn.wqkv"][bk], M=d, N=3 * d, K=Ma, accumulate=acc, ws=self.ws)
             o.rmsnorm_bwd(self.ht[t], p["core.norm1.weight"], self.rstd1[t], self.dn_f32, dht, dht, None,
                           g["core.norm1.weight"], pw1, film_gamma=p["core.pass_gamma1"][t],
                           dgamma_out=g["core.pass_gamma1"][t], dbeta_out=g["core.pass_beta1"][t],
@@ -600,6 +620,12 @@ class AuditReplay:
                                   frozen_src=dnext)
             dnext, dthis = dthis, (self.dalt if dthis is self.dcur else self.dcur)
         self.dh_first = dnext
+        if fused:
+            st, K = self._stacked, T * Ma
+            o.gemm_wgrad(st["zm"], st["d16_mlp"], g["core.mlp.wd"][0], M=f, N=d, K=K, ws=self.ws)
+            o.gemm_wgrad(st["n2"], st["dug16"], g["core.mlp.wug"][0], M=d, N=2 * f, K=K, ws=self.ws)
+            o.gemm_wgrad(st["ym"], st["d16_attn"], g["core.attn.wo"][0], M=d, N=d, K=K, ws=self.ws)
+            o.gemm_wgrad(st["n1"], st["dqkv16"], g["core.attn.wqkv"][0], M=d, N=3 * d, K=K, ws=self.ws)
         self._defer_param_grads(False)
         if not self.own_prelude:                      # (own_prelude: `finish_core` does this off the chain)
             self._scalar_grads()

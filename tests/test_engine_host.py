@@ -93,6 +93,11 @@ CASES = {
              attn_banks=2, ffn_banks=2, head_groups=4, ffn_groups=4, active_head_groups=2, active_ffn_groups=1,
              recipe_count=6, macro_rank=8),
         dict(mode="recursive_exact", lr=2e-3, weight_decay=0.1, batch_size=4, seq_len=16, seed=21, fixed_depth=None)),
+    "exact_one_bank": (                    # one bank each: the passes' weight-gradient products run as one
+        dict(vocab_size=96, d_model=64, n_heads=4, d_ff=128, n_prelude=1, n_coda=1, t_max=4, depth_choices=(1, 2, 4),
+             attn_banks=1, ffn_banks=1, head_groups=4, ffn_groups=4, active_head_groups=2, active_ffn_groups=2,
+             recipe_count=5, macro_rank=8),
+        dict(mode="recursive_exact", lr=2e-3, weight_decay=0.1, batch_size=4, seq_len=16, seed=27, fixed_depth=None)),
     "dense": (
         dict(topology="dense", vocab_size=96, d_model=64, n_heads=4, d_ff=128, n_dense_layers=2),
         dict(mode="dense_exact", lr=2e-3, weight_decay=0.1, batch_size=4, seq_len=16, seed=7)),
