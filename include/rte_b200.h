@@ -527,9 +527,10 @@ int rte_kl_distill(const void* hot_logits, const void* exact_logits, float temp,
 /* The same term with the gradient kept apart: dgrad f32 [rows, V] = coef*(p_hot - p_exact), to be added to the hot
  * dlogits by rte_add_rows_f32_to_bf16 once the hot pass's cross-entropy kernel has written them (the two then run
  * on different streams; the sum and its single bf16 rounding are those of rte_kl_distill).  dgrad may be NULL: only
- * kl_rows is written (the temperature-1 KL that macro_alignment_metrics reports, macro.py:538-543).               */
+ * the rows' KL is written.  kl1_rows (optional, f32 [rows]): the same divergence at temperature 1, the quantity
+ * macro_alignment_metrics reports (macro.py:538-543), computed in the same pass over the rows.                      */
 int rte_kl_distill_grad(const void* hot_logits, const void* exact_logits, float temp, float coef, float* dgrad,
-                        float* kl_rows, int32_t rows, int32_t V, rte_stream_t stream);
+                        float* kl_rows, float* kl1_rows, int32_t rows, int32_t V, rte_stream_t stream);
 /* Residual clip of the control variate (audit.py:306-321): corrected = hot + clamp(exact - hot, -clip, clip) / p.
  * For each audited sample j (hot row idx[j]) with |exact - hot| <= clip: f_hot = 1 - inv_p, f_exact = 1; otherwise
  * f_hot = 1, f_exact = 0 -- the factors to apply (rte_scale_rows_bf16) to cross-entropy gradients that were written

@@ -173,7 +173,7 @@ PROTOTYPES = {
     "rte_scaled_residual_bwd": (C.c_int, [c_vp] * 9 + [c_i32, P(c_i32), c_vp, c_vp, c_i32, c_i64, c_vp]),
     "rte_macro_distill": (C.c_int, [c_vp, c_vp, c_vp, c_f32, c_f32, c_f32, c_f32, c_vp, c_vp, c_i32, c_i32, c_i32, c_vp]),
     "rte_kl_distill": (C.c_int, [c_vp, c_vp, c_f32, c_f32, c_vp, c_i32, c_vp, c_i32, c_vp, c_i32, c_i32, c_vp]),
-    "rte_kl_distill_grad": (C.c_int, [c_vp, c_vp, c_f32, c_f32, c_vp, c_vp, c_i32, c_i32, c_vp]),
+    "rte_kl_distill_grad": (C.c_int, [c_vp, c_vp, c_f32, c_f32, c_vp, c_vp, c_vp, c_i32, c_i32, c_vp]),
     "rte_audit_clip": (C.c_int, [c_vp, c_vp, c_vp, c_i32, C.c_float, c_vp, C.c_float, c_vp, c_vp, c_vp]),
     "rte_audit_sample_bernoulli": (C.c_int, [c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, P(AuditSampleParams), c_vp, c_vp, c_vp, c_vp,
                                              c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, c_vp]),

@@ -102,6 +102,7 @@ class AuditReplay:
         self.eng, self.k = eng, k
         self._stage = None
         self._prepared = None
+        self._prelude_copied = None
         cfg, dev = eng.cfg, eng.device
         self.n, self.S, self.T = k, eng.S, cfg.t_max
         self.Ma = k * eng.S
@@ -455,12 +456,9 @@ class AuditReplay:
         tr, w = eng.tr, 1.0 / eng.loss_div
         o.macro_distill(self.hot_end, self.h[T], self.h0a, tr.lambda_delta_dir * w, tr.lambda_delta_rms * w,
                         tr.lambda_endpoint_normed * w, tr.lambda_endpoint_raw * w, self.terms, self.dhot_extra, n, S, d)
-        o.audit_alignment_sums(self.hot_end, self.h[T], self.h0a, n, S * d, self.align)
         if self.padded:
             # the kernel averaged over all n slots: n / audited on the audited samples' rows, 0 on the others
             o.scale_rows_f32(self.dhot_extra, self.dist_scale, n, S * d)
-        if self.bernoulli:
-            o.audit_recent_residual(self.hot_end, self.h[T], self.valid, n, S * d, self.cos, self.recent)
 
     def forward_kl(self) -> None:
         """KL-distillation term between the saved hot logits of the audited rows and the replay's logits; its gradient
@@ -471,17 +469,41 @@ class AuditReplay:
         n, Ma, V = self.n, self.Ma, cfg.vocab_size
         temp = max(float(tr.distill_temperature), 1e-6)
         if not eng.shortlist:      # the shortlist head keeps no full hot logits, so the KL term is absent (models.py:698-703)
-            o.kl_distill_grad(self.hot_logits, self.logits, temp, tr.lambda_kl * w * temp / n, self.dkl, self.kl_rows, Ma, V)
+            # (the temperature-1 KL of logit_kl_exact_macro, macro.py:538-543 / metrics.py:119-124, is a by-product of the
+            #  same launch: the replay's logits are overwritten by its cross entropy right afterwards)
+            o.kl_distill_grad(self.hot_logits, self.logits, temp, tr.lambda_kl * w * temp / n, self.dkl, self.kl_rows, Ma, V,
+                              kl1_rows=self.kl1_rows if temp != 1.0 else None)
             if self.padded:
                 o.scale_rows_f32(self.dkl, self.dist_scale, n, self.S * V)
-                o.scale_rows_f32(self.kl_rows, self.valid, n, self.S)
+
+    def report(self) -> None:
+        """Everything of the replay's forward that the step only REPORTS (or that the next step's sampler reads): the
+        alignment sums, the summed KL rows, the temperature-1 KL, the sampler's last residual.  The hot pass waits
+        for none of it, so it is issued after the event the hot pass waits on, and -- when the replay goes on with a
+        backward pass -- on the replay's weight-gradient stream (idle until that backward's first weight gradient, and
+        joined before the optimiser), so that it delays neither the hot pass nor the replay's own chain."""
+        import contextlib
+        eng = self.eng
+        o, cfg, tr = eng.ops, eng.cfg, eng.tr
+        n, S, T, Ma, d, V = self.n, self.S, self.T, self.Ma, cfg.d_model, cfg.vocab_size
+        ps = eng._param_stream if self.grad else None
+        ctx = contextlib.nullcontext()
+        if ps is not None:
+            ps.wait_stream(torch.cuda.current_stream(eng.device))
+            ctx = torch.cuda.stream(ps)
+        with ctx:
+            o.audit_alignment_sums(self.hot_end, self.h[T], self.h0a, n, S * d, self.align)
+            if self.bernoulli:
+                o.audit_recent_residual(self.hot_end, self.h[T], self.valid, n, S * d, self.cos, self.recent)
+            if eng.shortlist:
+                return
+            if self.padded:
+                o.scale_rows_f32(self.kl_rows, self.valid, n, S)
             o.segment_sum(self.kl_rows, self.kl_sum, 1, Ma)
-            if temp != 1.0:
-                # logit_kl_exact_macro (macro.py:538-543, metrics.py:119-124): the same KL at temperature 1, no
-                # gradient; its sum over the audited rows rides in the free eighth column of the alignment sums
-                o.kl_distill_grad(self.hot_logits, self.logits, 1.0, 0.0, None, self.kl1_rows, Ma, V)
+            if max(float(tr.distill_temperature), 1e-6) != 1.0:
+                # the temperature-1 KL's sum over the audited rows rides in the free eighth column of the alignment sums
                 if self.padded:
-                    o.scale_rows_f32(self.kl1_rows, self.valid, n, self.S)
+                    o.scale_rows_f32(self.kl1_rows, self.valid, n, S)
                 o.segment_sum(self.kl1_rows, self.align.view(-1)[7:8], 1, Ma)
 
     def add_kl_grad(self) -> None:
@@ -496,7 +518,11 @@ class AuditReplay:
         o, n, S = eng.ops, self.n, self.S
         if self.own_prelude and eng._param_stream is not None:
             # what `gather_prelude` queued on the weight-gradient stream during forward is read by this backward
-            torch.cuda.current_stream(eng.device).wait_stream(eng._param_stream)
+            # (its event, not the whole stream: `report` may still be running there)
+            if self._prelude_copied is not None:
+                torch.cuda.current_stream(eng.device).wait_event(self._prelude_copied)
+            else:
+                torch.cuda.current_stream(eng.device).wait_stream(eng._param_stream)
         o.ce_fwd_bwd(self.logits, self.targets_a, self.row_weight_a, S, self.loss_tok, self.logits)
         o.segment_sum(self.loss_tok, self.exact_loss, n, S)
 
@@ -697,6 +723,10 @@ class AuditReplay:
                                     ("ug", S * 2 * f * 2), ("z", S * f * 2), ("u", S * d * 4), ("rstd1", S * 4),
                                     ("rstd2", S * 4), ("lse", H * S * 4)):
                 o.gather_rows(getattr(hot, name), self.idx, getattr(mine, name), n, row_bytes)
+        self._prelude_copied = None
+        if eng.device.type == "cuda":
+            self._prelude_copied = torch.cuda.Event()
+            self._prelude_copied.record(torch.cuda.current_stream(eng.device))
 
     def merge_shared(self) -> None:
         """Adds the replay's share of the final-norm / coda gradients to the hot pass's (call once both are complete)."""

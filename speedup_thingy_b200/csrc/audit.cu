@@ -231,7 +231,7 @@ template <bool SEPARATE>
 __global__ void __launch_bounds__(NTHR)
 kl_distill_kernel(const __nv_bfloat16* __restrict__ hot, const __nv_bfloat16* __restrict__ exact, float inv_temp, float coef,
                   const int32_t* __restrict__ idx, int S, __nv_bfloat16* __restrict__ dlog, int ld, float* __restrict__ dsep,
-                  float* __restrict__ kl_rows, int V) {
+                  float* __restrict__ kl_rows, float* __restrict__ kl1_rows, int V) {
   __shared__ float red[32];
   const int row = blockIdx.x;
   const __nv_bfloat16* hr = hot + (size_t)row * V;
@@ -243,25 +243,44 @@ kl_distill_kernel(const __nv_bfloat16* __restrict__ hot, const __nv_bfloat16* __
   }
   mh = rte::block_max(mh, red);
   me = rte::block_max(me, red);
-  float sh = 0.f, se = 0.f;
+  // (kl1_rows: the same divergence at temperature 1 as a by-product; max(x) = max(x / T) * T for T > 0)
+  const float mh1 = mh / inv_temp, me1 = me / inv_temp;
+  float sh = 0.f, se = 0.f, sh1 = 0.f, se1 = 0.f;
   for (int c = threadIdx.x; c < V; c += NTHR) {
-    sh += __expf(__bfloat162float(hr[c]) * inv_temp - mh);
-    se += __expf(__bfloat162float(er[c]) * inv_temp - me);
+    const float xh = __bfloat162float(hr[c]), xe = __bfloat162float(er[c]);
+    sh += __expf(xh * inv_temp - mh);
+    se += __expf(xe * inv_temp - me);
+    if (kl1_rows) { sh1 += __expf(xh - mh1); se1 += __expf(xe - me1); }
   }
   sh = rte::block_sum(sh, red);
   se = rte::block_sum(se, red);
   const float lh = mh + __logf(sh), le = me + __logf(se);
+  float lh1 = 0.f, le1 = 0.f;
+  if (kl1_rows) {
+    sh1 = rte::block_sum(sh1, red);
+    se1 = rte::block_sum(se1, red);
+    lh1 = mh1 + __logf(sh1);
+    le1 = me1 + __logf(se1);
+  }
   __nv_bfloat16* dr = SEPARATE ? nullptr : dlog + ((size_t)idx[row / S] * S + (row % S)) * ld;
-  float kl = 0.f;
+  float kl = 0.f, kl1 = 0.f;
   for (int c = threadIdx.x; c < V; c += NTHR) {
     const float lph = __bfloat162float(hr[c]) * inv_temp - lh, lpe = __bfloat162float(er[c]) * inv_temp - le;
     const float ph = __expf(lph), pe = __expf(lpe);
     kl += pe * (lpe - lph);
+    if (kl1_rows) {
+      const float a = __bfloat162float(hr[c]) - lh1, b = __bfloat162float(er[c]) - le1;
+      kl1 += __expf(b) * (b - a);
+    }
     if (SEPARATE) { if (dsep) dsep[(size_t)row * V + c] = coef * (ph - pe); }
     else dr[c] = __float2bfloat16_rn(__bfloat162float(dr[c]) + coef * (ph - pe));
   }
   kl = rte::block_sum(kl, red);
   if (threadIdx.x == 0) kl_rows[row] = kl;
+  if (kl1_rows) {
+    kl1 = rte::block_sum(kl1, red);
+    if (threadIdx.x == 0) kl1_rows[row] = kl1;
+  }
 }
 
 // dst[(idx[row / S] * S + row % S) * ld + c] += src[row * V + c]   (bf16 destination, f32 addend, one rounding)
@@ -574,16 +593,16 @@ extern "C" int rte_kl_distill(const void* hot_logits, const void* exact_logits, 
                 ld_dlogits >= V);
   kl_distill_kernel<false><<<rows, NTHR, 0, ST(stream)>>>(reinterpret_cast<const __nv_bfloat16*>(hot_logits),
       reinterpret_cast<const __nv_bfloat16*>(exact_logits), 1.f / temp, coef, idx, S,
-      reinterpret_cast<__nv_bfloat16*>(dlogits_hot), ld_dlogits, nullptr, kl_rows, V);
+      reinterpret_cast<__nv_bfloat16*>(dlogits_hot), ld_dlogits, nullptr, kl_rows, nullptr, V);
   RTE_LAUNCH_CHECK();
   return RTE_OK;
 }
 
 extern "C" int rte_kl_distill_grad(const void* hot_logits, const void* exact_logits, float temp, float coef, float* dgrad,
-                                   float* kl_rows, int32_t rows, int32_t V, rte_stream_t stream) {
+                                   float* kl_rows, float* kl1_rows, int32_t rows, int32_t V, rte_stream_t stream) {
   RTE_CHECK_ARG(hot_logits && exact_logits && kl_rows && temp > 0.f && rows > 0 && V > 0);
   kl_distill_kernel<true><<<rows, NTHR, 0, ST(stream)>>>(reinterpret_cast<const __nv_bfloat16*>(hot_logits),
-      reinterpret_cast<const __nv_bfloat16*>(exact_logits), 1.f / temp, coef, nullptr, 1, nullptr, 0, dgrad, kl_rows, V);
+      reinterpret_cast<const __nv_bfloat16*>(exact_logits), 1.f / temp, coef, nullptr, 1, nullptr, 0, dgrad, kl_rows, kl1_rows, V);
   RTE_LAUNCH_CHECK();
   return RTE_OK;
 }

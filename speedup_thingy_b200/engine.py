@@ -1037,6 +1037,7 @@ class TrainEngine:
                 with self._on_side():
                     self.audit.forward_kl()
                     kl_done = self._side_event()
+                    self.audit.report()
             o.ce_fwd_bwd(self.logits, targets, self.row_weight, S, self.loss_tok, self.logits)   # logits -> dlogits in place
         o.segment_sum(self.loss_tok, self.loss_per_sample, B, S)
         o.segment_sum(self.loss_per_sample, self.scalars[0:1], 1, B)
@@ -1047,6 +1048,7 @@ class TrainEngine:
                 self._side_wait_main()
                 with self._on_side():
                     kl_done = self._side_event()
+                    self.audit.report()
             # join: the hot backward needs the distillation gradients (KL rows of dlogits, endpoint terms), not the
             # replay's own cross entropy, which starts the replay's backward on its stream
             a = self.audit

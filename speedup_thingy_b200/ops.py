@@ -515,9 +515,9 @@ class CudaOps:
         self._call("rte_kl_distill", _ptr(hot_logits), _ptr(exact_logits), temp, coef, _ptr(idx), S, _ptr(dlogits_hot),
                    dlogits_hot.stride(0), _ptr(kl_rows), rows, V, self.stream)
 
-    def kl_distill_grad(self, hot_logits, exact_logits, temp, coef, dgrad, kl_rows, rows: int, V: int) -> None:
+    def kl_distill_grad(self, hot_logits, exact_logits, temp, coef, dgrad, kl_rows, rows: int, V: int, kl1_rows=None) -> None:
         self._call("rte_kl_distill_grad", _ptr(hot_logits), _ptr(exact_logits), temp, coef, _ptr(dgrad), _ptr(kl_rows),
-                   rows, V, self.stream)
+                   _ptr(kl1_rows), rows, V, self.stream)
 
     def add_rows_to_bf16(self, dst_bf16, idx, S: int, src_f32, rows: int, V: int) -> None:
         self._call("rte_add_rows_f32_to_bf16", _ptr(dst_bf16), dst_bf16.stride(0), _ptr(idx), S, _ptr(src_f32), rows, V,

@@ -545,13 +545,17 @@ class EmulOps:
     def macro_phi_prepare(self, p):
         pass
 
-    def kl_distill_grad(self, hot_logits, exact_logits, temp, coef, dgrad, kl_rows, rows, V):
+    def kl_distill_grad(self, hot_logits, exact_logits, temp, coef, dgrad, kl_rows, rows, V, kl1_rows=None):
         self.launches += 1
         lh = torch.log_softmax(hot_logits.view(rows, V).float() / temp, -1)
         le = torch.log_softmax(exact_logits.view(rows, V).float() / temp, -1)
         kl_rows.view(-1)[:rows] = (le.exp() * (le - lh)).sum(-1)
         if dgrad is not None:
             dgrad.view(rows, V).copy_(coef * (lh.exp() - le.exp()))
+        if kl1_rows is not None:
+            lh1 = torch.log_softmax(hot_logits.view(rows, V).float(), -1)
+            le1 = torch.log_softmax(exact_logits.view(rows, V).float(), -1)
+            kl1_rows.view(-1)[:rows] = (le1.exp() * (le1 - lh1)).sum(-1)
 
     def add_rows_to_bf16(self, dst_bf16, idx, S, src_f32, rows, V):
         self.launches += 1

@@ -732,16 +732,19 @@ def test_audit_distillation_terms_and_gradients(ops):
     fused, split = base.clone(), base.clone()
     ops.kl_distill(hot_logits.to(DEV), exact_logits.to(DEV), temp, tr.lambda_kl * temp / n, idx, S, fused, kl_rows, n * S, V)
     dsep, kl2 = torch.zeros(n * S, V, device=DEV), torch.zeros(n * S, device=DEV)
-    ops.kl_distill_grad(hot_logits.to(DEV), exact_logits.to(DEV), temp, tr.lambda_kl * temp / n, dsep, kl2, n * S, V)
+    kl1_side = torch.zeros(n * S, device=DEV)
+    ops.kl_distill_grad(hot_logits.to(DEV), exact_logits.to(DEV), temp, tr.lambda_kl * temp / n, dsep, kl2, n * S, V,
+                        kl1_rows=kl1_side)
     ops.add_rows_to_bf16(split, idx, S, dsep, n * S, V)
     torch.cuda.synchronize()
     assert torch.equal(fused, split) and torch.equal(kl_rows, kl2)
-    # without a gradient buffer only the rows' KL is written: at temperature 1 the metric of macro.py:538-543
+    # the temperature-1 KL of macro.py:538-543: as a by-product of that launch, and alone without a gradient buffer
     kl1 = torch.zeros(n * S, device=DEV)
     ops.kl_distill_grad(hot_logits.to(DEV), exact_logits.to(DEV), 1.0, 0.0, None, kl1, n * S, V)
     torch.cuda.synchronize()
     le, lh = torch.log_softmax(exact_logits.float(), -1), torch.log_softmax(hot_logits.float(), -1)
     _close(kl1, (le.exp() * (le - lh)).sum(-1), 1e-3, "KL rows at temperature 1")
+    _close(kl1_side, (le.exp() * (le - lh)).sum(-1), 1e-3, "KL rows at temperature 1, by-product")
 
 
 def test_audit_mask_and_residual_helpers(ops):
