@@ -103,6 +103,7 @@ class AuditReplay:
         self._stage = None
         self._prepared = None
         self._prelude_copied = None
+        self._core_fwd_done = self.distill_done = None
         cfg, dev = eng.cfg, eng.device
         self.n, self.S, self.T = k, eng.S, cfg.t_max
         self.Ma = k * eng.S
@@ -440,6 +441,10 @@ class AuditReplay:
                 o.scaled_residual_fwd(self.u[t], self.mlp_acc[t], p["core.pass_mlp_scale"][t:t + 1], self.active[t],
                                       self.h[t], self.h[t + 1], n, S * d)
         x = self.h[T]
+        self._core_fwd_done = None                  # the exact endpoint h[T] exists: the distillation terms can start
+        if eng._side_stream is not None:
+            self._core_fwd_done = torch.cuda.Event()
+            self._core_fwd_done.record(torch.cuda.current_stream(eng.device))
         for blk in self.coda:
             x = eng._block_fwd(blk, x)
         self.x_last = x
@@ -448,17 +453,34 @@ class AuditReplay:
 
     def forward_distill(self, h_phi: torch.Tensor) -> None:
         """Distillation terms between the macro output and the replay's endpoint (the hot side receives the
-        gradient, the exact side is a constant: macro.py:413-415).  Issued once the macro operator has run."""
+        gradient, the exact side is a constant: macro.py:413-415).  Issued by the hot pass once the macro operator has
+        run.  The terms need the replay's endpoint h[T] but not its coda or logits, and the hot pass needs their
+        gradient only when its backward reaches the macro operator (`distill_done`): they run on the replay's
+        weight-gradient stream, idle during forward, beside the replay's coda instead of in front of its KL term."""
         eng = self.eng
         o, cfg = eng.ops, eng.cfg
         n, S, T, d = self.n, self.S, self.T, cfg.d_model
-        o.gather_rows(h_phi, self.idx, self.hot_end, n, S * d * 4)
         tr, w = eng.tr, 1.0 / eng.loss_div
-        o.macro_distill(self.hot_end, self.h[T], self.h0a, tr.lambda_delta_dir * w, tr.lambda_delta_rms * w,
-                        tr.lambda_endpoint_normed * w, tr.lambda_endpoint_raw * w, self.terms, self.dhot_extra, n, S, d)
-        if self.padded:
-            # the kernel averaged over all n slots: n / audited on the audited samples' rows, 0 on the others
-            o.scale_rows_f32(self.dhot_extra, self.dist_scale, n, S * d)
+        ps, main = eng._param_stream, None
+        self.distill_done = None
+        if ps is not None and self._core_fwd_done is not None:
+            main = torch.cuda.current_stream(eng.device)
+            ps.wait_stream(main)                        # h_phi
+            ps.wait_event(self._core_fwd_done)          # h[T], h0a, idx
+            ctx = torch.cuda.stream(ps)
+        else:
+            eng._side_wait_main()
+            ctx = eng._on_side()
+        with ctx:
+            o.gather_rows(h_phi, self.idx, self.hot_end, n, S * d * 4)
+            o.macro_distill(self.hot_end, self.h[T], self.h0a, tr.lambda_delta_dir * w, tr.lambda_delta_rms * w,
+                            tr.lambda_endpoint_normed * w, tr.lambda_endpoint_raw * w, self.terms, self.dhot_extra, n, S, d)
+            if self.padded:
+                # the kernel averaged over all n slots: n / audited on the audited samples' rows, 0 on the others
+                o.scale_rows_f32(self.dhot_extra, self.dist_scale, n, S * d)
+            if main is not None:
+                self.distill_done = torch.cuda.Event()
+                self.distill_done.record(ps)
 
     def forward_kl(self) -> None:
         """KL-distillation term between the saved hot logits of the audited rows and the replay's logits; its gradient
@@ -491,6 +513,8 @@ class AuditReplay:
         if ps is not None:
             ps.wait_stream(torch.cuda.current_stream(eng.device))
             ctx = torch.cuda.stream(ps)
+        elif self.distill_done is not None:
+            torch.cuda.current_stream(eng.device).wait_event(self.distill_done)     # hot_end is written there
         with ctx:
             o.audit_alignment_sums(self.hot_end, self.h[T], self.h0a, n, S * d, self.align)
             if self.bernoulli:

@@ -998,9 +998,7 @@ class TrainEngine:
                             B=B, S=S, d=d, m=cfg.macro_rank, K=len(cfg.depth_choices))
             x = self.h_phi
             if self.audit is not None:
-                self._side_wait_main()
-                with self._on_side():
-                    self.audit.forward_distill(self.h_phi)
+                self.audit.forward_distill(self.h_phi)           # (picks its stream itself)
             for blk in self.coda:
                 x = self._block_fwd(blk, x)
         x_last = x
@@ -1114,6 +1112,8 @@ class TrainEngine:
         if self.audit is not None:
             # distillation gradient on the hot endpoint of the audited samples, then the replay's own
             # logits / final-norm / coda backward (their weight gradients add to the hot pass's)
+            if self.audit.distill_done is not None:
+                torch.cuda.current_stream(self.device).wait_event(self.audit.distill_done)
             o.scatter_add_rows(dcur, self.audit.idx_scatter, self.audit.dhot_extra, self.audit.n, S * d)
         if not self.dense:
             # Phi backward writes dh0 into `dalt`; the router's auxiliary losses add their share
