@@ -191,6 +191,13 @@ int rte_attn_fwd_masked(const void* qkv, int32_t ld_qkv, int32_t sec, void* y, v
 int rte_attn_bwd(const void* qkv, int32_t ld_qkv, int32_t sec, const void* y, const void* dy, int32_t ld_y,
                  const float* lse, void* dqkv, const float* rope_table, int32_t B, int32_t S, int32_t n_heads,
                  int32_t head_dim, rte_stream_t stream);
+/* The same backward for an upstream gradient dy * mask_table[mask_row[sample]] (the mask of rte_attn_fwd_masked on the
+ * way back, layers.py:702-728).  One launch on the tensor-core path, dy untouched; otherwise dy is masked in place
+ * (rte_colmask_mul_bf16) and rte_attn_bwd follows.  ld_y must equal n_heads*head_dim.                              */
+int rte_attn_bwd_masked(const void* qkv, int32_t ld_qkv, int32_t sec, const void* y, void* dy, int32_t ld_y,
+                        const float* lse, void* dqkv, const float* rope_table, const int32_t* mask_row,
+                        const float* mask_table, int32_t B, int32_t S, int32_t n_heads, int32_t head_dim,
+                        rte_stream_t stream);
 
 /* ------------- per-token cross entropy + its gradient (models.py:73-75; training.py:1381-1385)
  * logits bf16 [rows, V] (ld = ldl).  loss_tok f32 [rows] = logsumexp - logit[target].

@@ -113,6 +113,8 @@ PROTOTYPES = {
     "rte_attn_fwd": (C.c_int, [c_vp, c_i32, c_i32, c_vp, c_i32, c_vp, c_vp, c_i32, c_i32, c_i32, c_i32, c_vp]),
     "rte_attn_fwd_masked": (C.c_int, [c_vp, c_i32, c_i32, c_vp, c_vp, c_i32, c_vp, c_vp, c_vp, c_vp, c_i32, c_i32, c_i32, c_i32, c_vp]),
     "rte_attn_bwd": (C.c_int, [c_vp, c_i32, c_i32, c_vp, c_vp, c_i32, c_vp, c_vp, c_vp, c_i32, c_i32, c_i32, c_i32, c_vp]),
+    "rte_attn_bwd_masked": (C.c_int, [c_vp, c_i32, c_i32, c_vp, c_vp, c_i32, c_vp, c_vp, c_vp, c_vp, c_vp, c_i32, c_i32, c_i32,
+                                      c_i32, c_vp]),
     "rte_ce_fwd_bwd": (C.c_int, [c_vp, c_i32, c_vp, c_vp, c_i32, c_vp, c_vp, c_i32, c_i32, c_vp, c_vp]),
     "rte_segment_sum": (C.c_int, [c_vp, c_vp, c_i32, c_i32, c_vp]),
     "rte_router_fwd": (C.c_int, [c_vp, P(RouterWeights), c_vp, P(RouterOut)] + [c_i32] * 9 + [c_vp]),

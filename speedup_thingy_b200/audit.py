@@ -128,7 +128,7 @@ class AuditReplay:
         self.head_tab, self.ffn_tab = recipe_mask_tables(cfg, dev)
         self.rid, self.active = e(T, n, dtype=i32), e(T, n, dtype=i32)
         self.h0a, self.targets_a = e(Ma, d), e(Ma, dtype=torch.int64)
-        self.h = [e(Ma, d) for _ in range(T + 1)]                          # h[0] = h0a copy, h[t+1] = after pass t
+        self.h = [self.h0a] + [e(Ma, d) for _ in range(T)]                 # h[0] = the gathered h0 rows, h[t+1] = after pass t
         self.ht, self.u = [e(Ma, d) for _ in range(T)], [e(Ma, d) for _ in range(T)]
         # With one attention and one FFN bank, what the weight-gradient products of the T passes read is laid out pass
         # after pass in one tensor each, so that a weight's gradient is ONE product over T * Ma rows after the last
@@ -390,8 +390,8 @@ class AuditReplay:
         o, cfg, p, sh = eng.ops, eng.cfg, eng.params, eng.shadow
         n, S, Ma, d = self.n, self.S, self.Ma, cfg.d_model
         o.gather_rows(h0, self.idx, self.h0a, n, S * d * 4)
-        o.gather_rows(h0, self.idx, self.h[0], n, S * d * 4)
-        o.gather_rows(eng.targets, self.idx, self.targets_a, n, S * 8)
+        if not self.own_prelude:             # (own_prelude: `gather_prelude` copies the targets too, off this chain)
+            o.gather_rows(eng.targets, self.idx, self.targets_a, n, S * 8)
         alpha = p["core.alpha_inj"].view(1)
         o.residual_rmsnorm_fwd(self.h[0], self.h0a, alpha, self.ht[0], p["core.norm1.weight"], self.n1[0], self.rstd1[0],
                                S=S, film_gamma=p["core.pass_gamma1"][0], film_beta=p["core.pass_beta1"][0])
@@ -548,7 +548,14 @@ class AuditReplay:
             else:
                 torch.cuda.current_stream(eng.device).wait_stream(eng._param_stream)
         o.ce_fwd_bwd(self.logits, self.targets_a, self.row_weight_a, S, self.loss_tok, self.logits)
-        o.segment_sum(self.loss_tok, self.exact_loss, n, S)
+        ps = eng._param_stream
+        if self.grad and self.clip is None and ps is not None:
+            # the per-sample sums are only reported (a residual clip would read them): off the backward's chain
+            ps.wait_stream(torch.cuda.current_stream(eng.device))
+            with torch.cuda.stream(ps):
+                o.segment_sum(self.loss_tok, self.exact_loss, n, S)
+        else:
+            o.segment_sum(self.loss_tok, self.exact_loss, n, S)
 
     def clip_exact(self) -> None:
         """Residual clip (audit.py:306-321), replay side: decides per audited sample whether exact - hot lies inside the
@@ -652,9 +659,8 @@ class AuditReplay:
                 o.gemm(d16a, sh["core.attn.wo"][bk], self.d16b, M=Ma, N=d, K=d)
                 if not fused:
                     o.gemm_wgrad(self.ym[t][bk], d16a, g["core.attn.wo"][bk], M=d, N=d, K=Ma, accumulate=acc, ws=self.ws)
-                o.colmask_mul(self.d16b, rid, self.head_tab[bk], S, self.d16b, Ma, d)
-                o.attn_bwd(self.qkv[t][bk], self.y[t][bk], self.d16b, self.lse[t][bk], dqkv16, B=n, S=S,
-                           n_heads=cfg.n_heads, head_dim=cfg.head_dim)
+                o.attn_bwd_masked(self.qkv[t][bk], self.y[t][bk], self.d16b, self.lse[t][bk], dqkv16, rid, self.head_tab[bk],
+                                  B=n, S=S, n_heads=cfg.n_heads, head_dim=cfg.head_dim)
                 o.gemm_f32_few_rows(dqkv16, sh["core.attn.wqkv"][bk], self.dn_f32, M=Ma, N=d, K=3 * d, b_mn=False,
                                     ws=self.ws_chain, accumulate=bk > 0)
                 if not fused:
@@ -740,6 +746,7 @@ class AuditReplay:
         d, f, H = cfg.d_model, cfg.d_ff, cfg.n_heads
         o.fill_(self.dh0_acc, 0.0)          # accumulator of the core backward (`forward_ce` orders the chain behind this)
         o.gather_rows(eng.tokens, self.idx, self.tokens_a, n, S * 8)
+        o.gather_rows(eng.targets, self.idx, self.targets_a, n, S * 8)      # read by `forward_ce`
         for hot, mine, x_in in zip(eng.prelude, self.prelude_a, self.prelude_x_in):
             o.gather_rows(hot.x_in, self.idx, x_in, n, S * d * 4)
             mine.x_in = x_in

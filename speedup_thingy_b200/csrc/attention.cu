@@ -419,6 +419,28 @@ extern "C" int rte_attn_fwd_masked(const void* qkv, int32_t ld_qkv, int32_t sec,
   return rte_colmask_mul_bf16(y, mask_row, mask_table, S, y_masked, B * S, n_heads * head_dim, stream);
 }
 
+// Attention backward whose upstream gradient is dy times the per-sample column mask of rte_attn_fwd_masked (the banked
+// core applies the recipe mask to the attention output before the output projection).  One launch on the tensor-core
+// path (the mask is applied to the dy tile in shared memory, dy itself is left alone); otherwise dy is masked IN PLACE
+// by rte_colmask_mul_bf16 and the plain backward follows.
+extern "C" int rte_attn_bwd_masked(const void* qkv, int32_t ld_qkv, int32_t sec, const void* y, void* dy, int32_t ld_y,
+                                   const float* lse, void* dqkv, const float* rope_table, const int32_t* mask_row,
+                                   const float* mask_table, int32_t B, int32_t S, int32_t n_heads, int32_t head_dim,
+                                   rte_stream_t stream) {
+  RTE_CHECK_ARG(qkv && y && dy && lse && dqkv && mask_row && mask_table && B > 0 && S > 0 && S <= 256 && n_heads > 0 &&
+                ld_qkv % 2 == 0 && sec % 2 == 0 && ld_y % 2 == 0);
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  if (ld_y == n_heads * head_dim) {
+    RTE_ATT_MMA_DISPATCH(attn_mma::launch_bwd, qkv, ld_qkv, sec, y, dy, ld_y, lse, dqkv, rope_table, B, S, n_heads, st, mask_row,
+                         mask_table);
+  } else {
+    return RTE_ERR_UNSUPPORTED;
+  }
+  const int rc = rte_colmask_mul_bf16(dy, mask_row, mask_table, S, dy, B * S, n_heads * head_dim, stream);
+  if (rc != RTE_OK) return rc;
+  return rte_attn_bwd(qkv, ld_qkv, sec, y, dy, ld_y, lse, dqkv, rope_table, B, S, n_heads, head_dim, stream);
+}
+
 extern "C" int rte_attn_bwd(const void* qkv, int32_t ld_qkv, int32_t sec, const void* y, const void* dy, int32_t ld_y,
                             const float* lse, void* dqkv, const float* rope_table, int32_t B, int32_t S, int32_t n_heads,
                             int32_t head_dim, rte_stream_t stream) {

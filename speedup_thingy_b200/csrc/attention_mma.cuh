@@ -314,11 +314,33 @@ __device__ __forceinline__ void unrope_pair(float& a, float& b, int pos, int pai
   b = -x * sn + y * cs;
 }
 
-template <int HD, int SMAX>
+// tile[r][c] *= mask[c] on the pieces this thread copied itself (the mapping of tile_async), one bf16 rounding
+template <int HD>
+__device__ __forceinline__ void colscale_tile(__nv_bfloat16* tile, int n_rows, int pad_rows, const float* __restrict__ mask) {
+  constexpr int LDS = HD + 8, CPR = HD / 8;
+  for (int idx = threadIdx.x; idx < pad_rows * CPR; idx += blockDim.x) {
+    const int r = idx / CPR, ch = idx % CPR;
+    if (r >= n_rows) continue;
+    uint4* p = reinterpret_cast<uint4*>(tile + r * LDS + 8 * ch);
+    const uint4 raw = *p;
+    uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+      const float2 v = rte::unpack_bf16x2(w[q]);
+      w[q] = rte::pack_bf16x2(v.x * mask[8 * ch + 2 * q], v.y * mask[8 * ch + 2 * q + 1]);
+    }
+    *p = make_uint4(w[0], w[1], w[2], w[3]);
+  }
+}
+
+// MASKED: the upstream gradient is dy[row, c] * mask_tab[mask_row[sample]][c] (the banked core's recipe mask on the
+// attention output, layers.py:702-728); the mask is applied to the dy tile in shared memory.
+template <int HD, int SMAX, bool MASKED>
 __global__ void __launch_bounds__(NTHR, (SMAX <= 64 && HD <= 64) ? 4 : 1)
 bwd_kernel(const __nv_bfloat16* __restrict__ qkv, int ld, int sec, const __nv_bfloat16* __restrict__ y,
            const __nv_bfloat16* __restrict__ dy, int ldy, const float* __restrict__ lse,
-           __nv_bfloat16* __restrict__ dqkv, const float* __restrict__ rope, int S, int H) {
+           __nv_bfloat16* __restrict__ dqkv, const float* __restrict__ rope, int S, int H,
+           const int32_t* __restrict__ mask_row, const float* __restrict__ mask_tab) {
   constexpr int LDS = HD + 8;
   extern __shared__ __align__(16) uint8_t smraw[];
   __nv_bfloat16* sq = reinterpret_cast<__nv_bfloat16*>(smraw);
@@ -337,6 +359,7 @@ bwd_kernel(const __nv_bfloat16* __restrict__ qkv, int ld, int sec, const __nv_bf
   cp_async_wait_all();
   rotate_tile<HD>(sq, S, s_pad, rope);
   rotate_tile<HD>(sk, S, s_pad, rope);
+  if (MASKED) colscale_tile<HD>(sdo, S, s_pad, mask_tab + (size_t)mask_row[b] * (H * HD) + h * HD);
   rowdot_tile<HD>(sdo, S, s_pad, y + (size_t)b * S * ldy + h * HD, ldy, sD);
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, g = lane >> 2, t = lane & 3;
   for (int i = threadIdx.x; i < s_pad; i += NTHR) slse[i] = (i < S) ? lse[((size_t)b * H + h) * S + i] : 0.f;
@@ -472,17 +495,26 @@ int launch_fwd(const void* qkv, int ld, int sec, void* y, int ldy, float* lse, c
 
 template <int HD, int SMAX>
 int launch_bwd(const void* qkv, int ld, int sec, const void* y, const void* dy, int ldy, const float* lse, void* dqkv,
-               const float* rope, int B, int S, int H, cudaStream_t st) {
+               const float* rope, int B, int S, int H, cudaStream_t st, const int32_t* mask_row = nullptr,
+               const float* mask_tab = nullptr) {
   constexpr int smem = 4 * SMAX * (HD + 8) * 2 + 2 * SMAX * 4;
   static bool set = false;
   if (!set && smem > 48 * 1024) {
-    if (cudaFuncSetAttribute(bwd_kernel<HD, SMAX>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess) return RTE_ERR_LAUNCH;
+    if (cudaFuncSetAttribute(bwd_kernel<HD, SMAX, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess ||
+        cudaFuncSetAttribute(bwd_kernel<HD, SMAX, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess)
+      return RTE_ERR_LAUNCH;
     set = true;
   }
   const int ctas = B * H * rte::ceil_div(S, QB);
-  bwd_kernel<HD, SMAX><<<dim3(B * H, rte::ceil_div(S, QB), ctas < 148 ? 2 : 1), NTHR, smem, st>>>(
-      reinterpret_cast<const __nv_bfloat16*>(qkv), ld, sec, reinterpret_cast<const __nv_bfloat16*>(y),
-      reinterpret_cast<const __nv_bfloat16*>(dy), ldy, lse, reinterpret_cast<__nv_bfloat16*>(dqkv), rope, S, H);
+  const dim3 grid(B * H, rte::ceil_div(S, QB), ctas < 148 ? 2 : 1);
+  const auto* q16 = reinterpret_cast<const __nv_bfloat16*>(qkv);
+  const auto* y16 = reinterpret_cast<const __nv_bfloat16*>(y);
+  const auto* dy16 = reinterpret_cast<const __nv_bfloat16*>(dy);
+  auto* dq16 = reinterpret_cast<__nv_bfloat16*>(dqkv);
+  if (mask_row != nullptr)
+    bwd_kernel<HD, SMAX, true><<<grid, NTHR, smem, st>>>(q16, ld, sec, y16, dy16, ldy, lse, dq16, rope, S, H, mask_row, mask_tab);
+  else
+    bwd_kernel<HD, SMAX, false><<<grid, NTHR, smem, st>>>(q16, ld, sec, y16, dy16, ldy, lse, dq16, rope, S, H, nullptr, nullptr);
   RTE_LAUNCH_CHECK();
   return RTE_OK;
 }

@@ -300,6 +300,14 @@ class CudaOps:
         self._call("rte_attn_bwd", _ptr(qkv), qkv.stride(0), sec, _ptr(y), _ptr(dy), y.stride(0), _ptr(lse),
                    _ptr(dqkv), _ptr(rope), B, S, n_heads, head_dim, self.stream)
 
+    def attn_bwd_masked(self, qkv, y, dy, lse, dqkv, mask_row, mask_table, *, B: int, S: int, n_heads: int, head_dim: int,
+                        sec: int | None = None, rope=None) -> None:
+        """Attention backward for the upstream gradient dy * mask_table[mask_row[sample]] (dy may be masked in place)."""
+        sec = sec if sec is not None else n_heads * head_dim
+        rope = rope if rope is not None else self.rope_table(S, head_dim)
+        self._call("rte_attn_bwd_masked", _ptr(qkv), qkv.stride(0), sec, _ptr(y), _ptr(dy), y.stride(0), _ptr(lse),
+                   _ptr(dqkv), _ptr(rope), _ptr(mask_row), _ptr(mask_table), B, S, n_heads, head_dim, self.stream)
+
     def rope_apply(self, x, cos, sin, out, *, rows: int, S: int, head_dim: int, adjoint: bool = False) -> None:
         _require_cuda(x, cos, sin, out)
         self._call("rte_rope_apply", _ptr(x), _ptr(cos), _ptr(sin), _ptr(out), rows, S, head_dim,

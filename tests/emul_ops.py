@@ -538,6 +538,10 @@ class EmulOps:
         cur = dlogits_hot[tgt, :V].float()
         dlogits_hot[tgt, :V] = (cur + coef * (lh.exp() - le.exp())).to(torch.bfloat16)
 
+    def attn_bwd_masked(self, qkv, y, dy, lse, dqkv, mask_row, mask_table, *, B, S, n_heads, head_dim, sec=None, rope=None):
+        self.colmask_mul(dy, mask_row, mask_table, S, dy, B * S, n_heads * head_dim)
+        self.attn_bwd(qkv, y, dy, lse, dqkv, B=B, S=S, n_heads=n_heads, head_dim=head_dim, sec=sec)
+
     def attn_fwd_masked(self, qkv, y, y_masked, lse, mask_row, mask_table, *, B, S, n_heads, head_dim, sec=None, rope=None):
         self.attn_fwd(qkv, y, lse, B=B, S=S, n_heads=n_heads, head_dim=head_dim, sec=sec)
         self.colmask_mul(y, mask_row, mask_table, S, y_masked, B * S, n_heads * head_dim)

@@ -284,6 +284,18 @@ def test_attention_fwd_bwd(ops, B, S, H, hd):
     ops.colmask_mul(y, rows, tab, S, ref_m, B * S, d)
     torch.cuda.synchronize()
     assert torch.equal(y, y2) and torch.equal(lse, lse2) and torch.equal(ym, ref_m)
+    # backward on a masked upstream gradient == the mask as its own pass, then the plain backward (same bits), with
+    # dy left alone on the tensor-core path
+    dyd = dy.to(DEV)
+    dy_m, dq_ref, dq_m = torch.zeros_like(dyd), torch.zeros_like(dq), torch.zeros_like(dq)
+    ops.colmask_mul(dyd, rows, tab, S, dy_m, B * S, d)
+    ops.attn_bwd(qd, y, dy_m, lse, dq_ref, B=B, S=S, n_heads=H, head_dim=hd)
+    keep = dyd.clone()
+    ops.attn_bwd_masked(qd, y, dyd, lse, dq_m, rows, tab, B=B, S=S, n_heads=H, head_dim=hd)
+    torch.cuda.synchronize()
+    assert torch.equal(dq_m, dq_ref)
+    if hd in (32, 64, 128):
+        assert torch.equal(dyd, keep)
 
 
 # ------------------------------------------------------------------ router / top-k
