@@ -339,6 +339,8 @@ def main() -> None:
                     help="data parallel: add the start / end of every gradient bucket's all-reduce inside a step (profiling)")
     ap.add_argument("--step-timeline", metavar="FILE", default=None,
                     help="write start and duration of every C-ABI call of one captured step, per stream, as JSON lines (profiling; 1 GPU)")
+    ap.add_argument("--join-waits", action="store_true",
+                    help="also report how long the hot pass idles where it waits for the audit replay (event nodes at those waits only)")
     ap.add_argument("--probe-cublas", action="store_true", help="with --probe-gemm: also time torch.matmul (cuBLAS) on the same shapes")
     ap.add_argument("--probe-iters", type=int, default=20)
     ap.add_argument("--probe-warmup", type=int, default=3)
@@ -468,6 +470,8 @@ def main() -> None:
             for (name, us), start, where in zip(prof, eng.last_profile_starts, eng.last_profile_streams):
                 fh.write(json.dumps({"call": name.split("@")[0], "stream": where, "start_us": round(start, 1), "us": round(us, 2)}) + "\n")
 
+    join_waits = eng.join_waits() if (args.join_waits and world == 1) else None
+
     # ---- roofline of the dominant kernel (the tcgen05 GEMM): CUDA-event nodes around every launch of a captured step
     roof = None
     if rank == 0 and not args.no_roofline:
@@ -522,6 +526,8 @@ def main() -> None:
                                 "per_shape": roof["per_shape"], "side_stream": roof.get("side_stream")}
         if timeline is not None:
             line["dp_timeline"] = timeline
+        if join_waits is not None:
+            line["replay_join_waits"] = join_waits
         if world == 1 and not args.no_cpu_baseline:
             threads = os.cpu_count() or 1
             line["cpu_baseline"] = cpu_reference_tokens_per_sec(raw, steps=6, threads=threads, budget_s=40.0)

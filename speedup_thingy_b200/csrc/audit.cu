@@ -452,7 +452,7 @@ __global__ void audit_recent_kernel(const float* __restrict__ cos_in, const floa
 
 // Sums behind macro_alignment_metrics (macro.py:499-546) for one audited sample per CTA: with a = macro endpoint,
 // b = exact endpoint, z = h0 (rows of row_len floats): out[j] = (a.b, a.a, b.b, |a-b|^2, |a-z|^2, |b-z|^2, (a-z).(b-z), untouched).
-__global__ void __launch_bounds__(NTHR)
+__global__ void __launch_bounds__(1024)
 alignment_sums_kernel(const float* __restrict__ a, const float* __restrict__ b, const float* __restrict__ z, long long row_len,
                       float* __restrict__ out) {
   __shared__ float red[32];
@@ -460,9 +460,23 @@ alignment_sums_kernel(const float* __restrict__ a, const float* __restrict__ b, 
   const float* y = b + (size_t)blockIdx.x * row_len;
   const float* w = z + (size_t)blockIdx.x * row_len;
   float s[7] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-  for (long long i = threadIdx.x; i < row_len; i += NTHR) {
-    const float p = x[i], q = y[i], r = w[i], dp = p - r, dq = q - r, df = p - q;
+  auto take = [&](float p, float q, float r) {
+    const float dp = p - r, dq = q - r, df = p - q;
     s[0] += p * q; s[1] += p * p; s[2] += q * q; s[3] += df * df; s[4] += dp * dp; s[5] += dq * dq; s[6] += dp * dq;
+  };
+  // one CTA per sample (a handful of samples, tens of thousands of elements each): 1024 threads, 16-byte loads
+  const bool vec = (row_len % 4 == 0) && (((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(y) |
+                                            reinterpret_cast<uintptr_t>(w)) & 15) == 0);
+  if (vec) {
+    const float4* x4 = reinterpret_cast<const float4*>(x);
+    const float4* y4 = reinterpret_cast<const float4*>(y);
+    const float4* w4 = reinterpret_cast<const float4*>(w);
+    for (long long i = threadIdx.x; i < row_len / 4; i += blockDim.x) {
+      const float4 p = x4[i], q = y4[i], r = w4[i];
+      take(p.x, q.x, r.x); take(p.y, q.y, r.y); take(p.z, q.z, r.z); take(p.w, q.w, r.w);
+    }
+  } else {
+    for (long long i = threadIdx.x; i < row_len; i += blockDim.x) take(x[i], y[i], w[i]);
   }
 #pragma unroll
   for (int k = 0; k < 7; ++k) {
@@ -653,7 +667,7 @@ extern "C" int rte_audit_recent_residual(const float* hot_end, const float* exac
 extern "C" int rte_audit_alignment_sums(const float* hot_end, const float* exact_end, const float* h0, int32_t n, int64_t row_len,
                                         float* out, rte_stream_t stream) {
   RTE_CHECK_ARG(hot_end && exact_end && h0 && out && n > 0 && row_len > 0);
-  alignment_sums_kernel<<<n, NTHR, 0, ST(stream)>>>(hot_end, exact_end, h0, row_len, out);
+  alignment_sums_kernel<<<n, 1024, 0, ST(stream)>>>(hot_end, exact_end, h0, row_len, out);
   RTE_LAUNCH_CHECK();
   return RTE_OK;
 }

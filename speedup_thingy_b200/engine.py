@@ -682,7 +682,7 @@ class TrainEngine:
         if probes is not None:
             e1 = torch.cuda.Event(enable_timing=True, external=True)
             e1.record(main)
-            probes.append((e0, e1))
+            probes.append(("wait", e0, e1))
 
     # ------------------------------------------------------------------ small helpers
     def _write_lr_table(self, scale: float = 1.0) -> None:
@@ -1072,7 +1072,7 @@ class TrainEngine:
                 if probes is not None:
                     s1 = torch.cuda.Event(enable_timing=True, external=True)
                     s1.record(torch.cuda.current_stream(self.device))
-                    probes.append((s0, s1))
+                    probes.append(("replay_backward", s0, s1))
             if clip:
                 # residual clip: both cross-entropy launches wrote unit-weight gradients; the audited rows of the hot
                 # dlogits get their factor now that the exact losses exist (then the KL rows, which it must not touch)
@@ -1676,6 +1676,42 @@ class TrainEngine:
         last_end = max((b["end_us"] for b in buckets), default=0.0)
         return {"backward_end_us": mean["backward_end"], "step_end_us": mean["step_end"], "buckets": buckets,
                 "exchange_exposed_us": max(0.0, last_end - mean["backward_end"]), "bucket_cap_mb": self.bucket_cap_mb}
+
+    def join_waits(self, repeats: int = 20) -> dict[str, Any]:
+        """How long the hot pass idles at each point where it waits for the audit replay's stream, in microseconds, from
+        event-record nodes placed only around those waits inside a captured step (averaged over `repeats` replays of the
+        batch loaded last), with the length of that step.  A few nodes on one stream: unlike `profile_step`, this does
+        not stretch the replay's long chain of launches."""
+        if self._side_stream is None:
+            return {"waits_us": [], "step_us": None}
+        self._join_probes = []
+        ev = lambda: torch.cuda.Event(enable_timing=True, external=True)       # noqa: E731
+        try:
+            torch.cuda.synchronize(self.device)
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph):
+                main = torch.cuda.current_stream(self.device)
+                start = ev(); start.record(main)                                # noqa: E702
+                self._forward_backward()
+                self._optimizer_step()
+                end = ev(); end.record(main)                                    # noqa: E702
+            probes = self._join_probes
+        finally:
+            self._join_probes = None
+        graph.replay()
+        torch.cuda.synchronize(self.device)
+        spans, begins, step = [0.0] * len(probes), [0.0] * len(probes), 0.0
+        for _ in range(repeats):
+            graph.replay()
+            torch.cuda.synchronize(self.device)
+            step += start.elapsed_time(end) * 1e3 / repeats
+            for i, (_, e0, e1) in enumerate(probes):
+                spans[i] += e0.elapsed_time(e1) * 1e3 / repeats
+                begins[i] += start.elapsed_time(e0) * 1e3 / repeats
+        del graph
+        pick = lambda kind, vals: [round(v, 1) for (k, _, _), v in zip(probes, vals) if k == kind]      # noqa: E731
+        return {"waits_us": pick("wait", spans), "at_us": pick("wait", begins), "step_us": round(step, 1),
+                "replay_backward_us": pick("replay_backward", spans), "replay_backward_at_us": pick("replay_backward", begins)}
 
     def gemm_roofline(self, repeats: int = 5) -> dict[str, Any]:
         """Relates the algorithmic 2*M*N*K FLOPs of every tcgen05 GEMM launch of one step to its device

@@ -940,11 +940,12 @@ def test_adamw_leaves_tensors_without_a_gradient_alone(ops):
     assert float(sums[1, 0]) > 0.0
 
 
-def test_alignment_sums_match_their_definition(ops):
+@pytest.mark.parametrize("L", [64 * 96, 1001])          # 16-byte loads | scalar loads (length not a multiple of 4)
+def test_alignment_sums_match_their_definition(ops, L):
     """rte_audit_alignment_sums (the seven per-sample sums behind macro_alignment_metrics, macro.py:499-546)."""
     from tests.emul_ops import EmulOps
     g = torch.Generator().manual_seed(4)
-    n, L = 5, 64 * 96
+    n = 5
     a, b, z = (torch.randn(n, L, generator=g) for _ in range(3))
     got = torch.full((n, 8), 9.0, device=DEV)
     ops.audit_alignment_sums(a.to(DEV), b.to(DEV), z.to(DEV), n, L, got)
