@@ -156,6 +156,22 @@ int rte_rmsnorm_bwd(const float* x, const float* w, const float* film_gamma, con
                     float* dx_f32, void* dx_bf16, float* dw_partial, float* dgamma_partial,
                     float* dbeta_partial, int32_t rows, int32_t d, int32_t max_partials,
                     int32_t* n_partials, rte_stream_t stream);
+/* The two launches above fed with the split-K partials of a few-row product instead of its reduced result (the audit
+ * replay's chain: one dependent launch less per product).  `branch` / `dy_f32` then point at `*_splits` partials of
+ * rows*d floats each, `*_split_stride` floats apart (a multiple of 4), which the kernel sums in split order -- the
+ * bits rte_reduce_splits would have produced.  branch_out (optional) receives the summed branch.  With one split
+ * they are the launches above.                                                                                     */
+int rte_residual_rmsnorm_fwd_splits(const float* base, const float* branch, int32_t branch_splits,
+                                    int64_t branch_split_stride, float* branch_out, const float* scale,
+                                    const int32_t* active, const float* passthrough, int32_t S, const float* add2,
+                                    const float* scale2, float* x1_out, float* x_out, const float* w,
+                                    const float* film_gamma, const float* film_beta, void* y_bf16, float* rstd,
+                                    int32_t rows, int32_t d, float eps, rte_stream_t stream);
+int rte_rmsnorm_bwd_splits(const float* x, const float* w, const float* film_gamma, const float* rstd,
+                           const void* dy_bf16, const float* dy_f32, int32_t dy_splits, int64_t dy_split_stride,
+                           const float* dres, float* dx_f32, void* dx_bf16, float* dw_partial, float* dgamma_partial,
+                           float* dbeta_partial, int32_t rows, int32_t d, int32_t max_partials, int32_t* n_partials,
+                           rte_stream_t stream);
 /* out[c] = (accumulate ? out[c] : 0) + sum_r partial[r, c] */
 int rte_colsum_partials(const float* partial, int32_t n_rows, int32_t d, float* out, int32_t accumulate,
                         rte_stream_t stream);

@@ -106,6 +106,9 @@ PROTOTYPES = {
     "rte_embed_bwd": (C.c_int, [c_vp, c_vp, c_vp, c_vp, c_i32, c_i32, c_i32, c_vp, c_vp]),
     "rte_rmsnorm_fwd": (C.c_int, [c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, c_i32, c_i32, c_f32, c_vp]),
     "rte_rmsnorm_bwd": (C.c_int, [c_vp] * 12 + [c_i32, c_i32, c_i32, P(c_i32), c_vp]),
+    "rte_rmsnorm_bwd_splits": (C.c_int, [c_vp] * 6 + [c_i32, c_i64] + [c_vp] * 6 + [c_i32, c_i32, c_i32, P(c_i32), c_vp]),
+    "rte_residual_rmsnorm_fwd_splits": (C.c_int, [c_vp, c_vp, c_i32, c_i64, c_vp, c_vp, c_vp, c_vp, c_i32, c_vp, c_vp, c_vp, c_vp,
+                                                  c_vp, c_vp, c_vp, c_vp, c_vp, c_i32, c_i32, C.c_float, c_vp]),
     "rte_colsum_partials3": (C.c_int, [c_vp, c_vp, c_vp, c_i32, c_i32, c_i32, c_vp]),
     "rte_colsum_partials": (C.c_int, [c_vp, c_i32, c_i32, c_vp, c_i32, c_vp]),
     "rte_rope_table": (C.c_int, [c_vp, c_i32, c_i32, c_vp]),

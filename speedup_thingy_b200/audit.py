@@ -136,6 +136,9 @@ class AuditReplay:
         import os
         self.fused_wgrad = (cfg.attn_banks == 1 and cfg.ffn_banks == 1 and os.environ.get("RTE_REPLAY_FUSED_WGRAD", "1") != "0")
         self._stacked: dict[str, torch.Tensor] = {}
+        # the norm launches behind the core's split-K few-row products sum the partials themselves (one dependent
+        # launch less per product; RTE_REPLAY_SPLIT_FEED=0: a separate reduction launch)
+        self.split_feed = os.environ.get("RTE_REPLAY_SPLIT_FEED", "1") != "0"
 
         def per_pass(name: str, cols: int) -> list[torch.Tensor]:
             if not self.fused_wgrad:
@@ -430,13 +433,19 @@ class AuditReplay:
             for bk in range(cfg.ffn_banks):
                 o.gemm(self.n2[t], sh["core.mlp.wug"][bk], self.ug[t][bk], M=Ma, N=2 * f, K=d, b_mn=True)
                 o.swiglu_masked_fwd(self.ug[t][bk], rid, self.ffn_tab[bk], S, self.zm[t][bk], Ma, f)
-                o.gemm_f32_few_rows(self.zm[t][bk], sh["core.mlp.wd"][bk], self.mlp_acc[t], M=Ma, N=d, K=f, b_mn=True,
-                                    ws=self.ws_chain, accumulate=bk > 0)
+                # (one bank, another pass to come: the split-K partials go straight into the norm launch below, which
+                #  sums them in split order and keeps the sum in mlp_acc for the backward pass)
+                sp = o.gemm_f32_few_rows(self.zm[t][bk], sh["core.mlp.wd"][bk], self.mlp_acc[t], M=Ma, N=d, K=f, b_mn=True,
+                                         ws=self.ws_chain, accumulate=bk > 0,
+                                         reduce=not (self.split_feed and cfg.ffn_banks == 1 and t + 1 < T))
             if t + 1 < T:
-                o.residual_rmsnorm_fwd(self.u[t], self.mlp_acc[t], p["core.pass_mlp_scale"][t:t + 1], self.ht[t + 1],
+                split = sp[0] > 1
+                o.residual_rmsnorm_fwd(self.u[t], self.ws_chain if split else self.mlp_acc[t],
+                                       p["core.pass_mlp_scale"][t:t + 1], self.ht[t + 1],
                                        p["core.norm1.weight"], self.n1[t + 1], self.rstd1[t + 1], S=S,
                                        active=self.active[t], passthrough=self.h[t], add2=self.h0a, scale2=alpha,
-                                       x1_out=self.h[t + 1], **film1(t + 1))
+                                       x1_out=self.h[t + 1], branch_splits=sp, branch_out=self.mlp_acc[t] if split else None,
+                                       **film1(t + 1))
             else:
                 o.scaled_residual_fwd(self.u[t], self.mlp_acc[t], p["core.pass_mlp_scale"][t:t + 1], self.active[t],
                                       self.h[t], self.h[t + 1], n, S * d)
@@ -644,14 +653,15 @@ class AuditReplay:
                 if not fused:
                     o.gemm_wgrad(self.zm[t][bk], d16m, g["core.mlp.wd"][bk], M=f, N=d, K=Ma, accumulate=acc, ws=self.ws)
                 o.swiglu_masked_bwd(self.ug[t][bk], self.dz16, rid, self.ffn_tab[bk], S, dug16, Ma, f)
-                o.gemm_f32_few_rows(dug16, sh["core.mlp.wug"][bk], self.dn_f32, M=Ma, N=d, K=2 * f, b_mn=False,
-                                    ws=self.ws_chain, accumulate=bk > 0)
+                sp2 = o.gemm_f32_few_rows(dug16, sh["core.mlp.wug"][bk], self.dn_f32, M=Ma, N=d, K=2 * f, b_mn=False,
+                                          ws=self.ws_chain, accumulate=bk > 0, reduce=cfg.ffn_banks > 1 or not self.split_feed)
                 if not fused:
                     o.gemm_wgrad(self.n2[t], dug16, g["core.mlp.wug"][bk], M=d, N=2 * f, K=Ma, accumulate=acc, ws=self.ws)
-            o.rmsnorm_bwd(self.u[t], p["core.norm2.weight"], self.rstd2[t], self.dn_f32, du, du, None,
-                          g["core.norm2.weight"], pw2, film_gamma=p["core.pass_gamma2"][t],
+            # (one bank: the norm backward sums the product's split-K partials itself, in split order)
+            o.rmsnorm_bwd(self.u[t], p["core.norm2.weight"], self.rstd2[t], self.ws_chain if sp2[0] > 1 else self.dn_f32,
+                          du, du, None, g["core.norm2.weight"], pw2, film_gamma=p["core.pass_gamma2"][t],
                           dgamma_out=g["core.pass_gamma2"][t], dbeta_out=g["core.pass_beta2"][t],
-                          partial_g=pg2, partial_b=pb2, accumulate_dw=acc)
+                          partial_g=pg2, partial_b=pb2, accumulate_dw=acc, dy_splits=sp2)
             # u = ht + s_attn * attn
             o.scaled_residual_bwd(du, self.attn_acc[t], p["core.pass_attn_scale"][t:t + 1], None, dht, d16a, None, None,
                                   self.part_attn[t * P:(t + 1) * P], n, S * d)
@@ -661,14 +671,14 @@ class AuditReplay:
                     o.gemm_wgrad(self.ym[t][bk], d16a, g["core.attn.wo"][bk], M=d, N=d, K=Ma, accumulate=acc, ws=self.ws)
                 o.attn_bwd_masked(self.qkv[t][bk], self.y[t][bk], self.d16b, self.lse[t][bk], dqkv16, rid, self.head_tab[bk],
                                   B=n, S=S, n_heads=cfg.n_heads, head_dim=cfg.head_dim)
-                o.gemm_f32_few_rows(dqkv16, sh["core.attn.wqkv"][bk], self.dn_f32, M=Ma, N=d, K=3 * d, b_mn=False,
-                                    ws=self.ws_chain, accumulate=bk > 0)
+                sp1 = o.gemm_f32_few_rows(dqkv16, sh["core.attn.wqkv"][bk], self.dn_f32, M=Ma, N=d, K=3 * d, b_mn=False,
+                                          ws=self.ws_chain, accumulate=bk > 0, reduce=cfg.attn_banks > 1 or not self.split_feed)
                 if not fused:
                     o.gemm_wgrad(self.n1[t], dqkv16, g["core.attn.wqkv"][bk], M=d, N=3 * d, K=Ma, accumulate=acc, ws=self.ws)
-            o.rmsnorm_bwd(self.ht[t], p["core.norm1.weight"], self.rstd1[t], self.dn_f32, dht, dht, None,
-                          g["core.norm1.weight"], pw1, film_gamma=p["core.pass_gamma1"][t],
+            o.rmsnorm_bwd(self.ht[t], p["core.norm1.weight"], self.rstd1[t], self.ws_chain if sp1[0] > 1 else self.dn_f32,
+                          dht, dht, None, g["core.norm1.weight"], pw1, film_gamma=p["core.pass_gamma1"][t],
                           dgamma_out=g["core.pass_gamma1"][t], dbeta_out=g["core.pass_beta1"][t],
-                          partial_g=pg1, partial_b=pb1, accumulate_dw=acc)
+                          partial_g=pg1, partial_b=pb1, accumulate_dw=acc, dy_splits=sp1)
             # ht = h_in + alpha * h0
             # (samples that were frozen in this pass hand their gradient `dnext` straight through: same launch)
             o.scaled_residual_bwd(dht, self.h0a, alpha, None, dthis, None, self.dh0_acc, None,

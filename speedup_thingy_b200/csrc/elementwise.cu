@@ -118,7 +118,9 @@ residual_rmsnorm_fwd_kernel(const float* __restrict__ base, const float* __restr
                             const float* __restrict__ add2, const float* __restrict__ scale2, float* __restrict__ x1_out,
                             float* __restrict__ x_out, const float* __restrict__ w, const float* __restrict__ fg,
                             const float* __restrict__ fb, __nv_bfloat16* __restrict__ y16, float* __restrict__ rstd, int rows, int d,
-                            float eps) {
+                            float eps, int branch_splits, long long branch_stride, float* __restrict__ branch_out) {
+  // branch_splits > 1: `branch` holds that many split-K partials of the branch, branch_stride floats apart; they are
+  // summed here in split order (what rte_reduce_splits would have produced) and the sum is kept in branch_out.
   const int lane = threadIdx.x & 31;
   const int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   if (row >= rows) return;
@@ -133,8 +135,17 @@ residual_rmsnorm_fwd_kernel(const float* __restrict__ base, const float* __restr
     const int c = lane + 32 * i;
     if (c < d4) {
       float4 x;
+      float4 b = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (on || branch_out) {
+        b = reinterpret_cast<const float4*>(branch + off)[c];
+        for (int s = 1; s < branch_splits; ++s) {
+          const float4 t = reinterpret_cast<const float4*>(branch + (size_t)s * branch_stride + off)[c];
+          b.x += t.x; b.y += t.y; b.z += t.z; b.w += t.w;
+        }
+        if (branch_out) reinterpret_cast<float4*>(branch_out + off)[c] = b;
+      }
       if (on) {
-        const float4 a = reinterpret_cast<const float4*>(base + off)[c], b = reinterpret_cast<const float4*>(branch + off)[c];
+        const float4 a = reinterpret_cast<const float4*>(base + off)[c];
         x = make_float4(a.x + s1 * b.x, a.y + s1 * b.y, a.z + s1 * b.z, a.w + s1 * b.w);
       } else {
         x = reinterpret_cast<const float4*>(passthrough + off)[c];
@@ -186,7 +197,8 @@ rmsnorm_bwd_kernel(const float* __restrict__ x, const float* __restrict__ w, con
                    const float* __restrict__ rstd, const __nv_bfloat16* __restrict__ dy16,
                    const float* __restrict__ dy32, const float* __restrict__ dres, float* __restrict__ dx32,
                    __nv_bfloat16* __restrict__ dx16, float* __restrict__ dw_part, float* __restrict__ dg_part,
-                   float* __restrict__ db_part, int rows, int d) {
+                   float* __restrict__ db_part, int rows, int d, int dy_splits, long long dy_stride) {
+  // dy_splits > 1: dy32 holds that many split-K partials of dy, dy_stride floats apart, summed here in split order
   extern __shared__ float sm[];   // [3][warps][d] when parameter gradients are requested
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarp = blockDim.x >> 5;
   const int d4 = d >> 2;
@@ -203,7 +215,7 @@ rmsnorm_bwd_kernel(const float* __restrict__ x, const float* __restrict__ w, con
   if constexpr (!FILM && NV <= 4) {
     // Two rows per trip with all loads of both rows issued before the first use: a warp that walks its rows one at a
     // time keeps too few bytes in flight to cover the memory latency (the plain-norm launches of the hot pass).
-    for (; row + stride < rows; row += 2 * stride) {
+    for (; dy_splits <= 1 && row + stride < rows; row += 2 * stride) {
       const int rw[2] = {row, row + stride};
       float rr[2];
       float4 xh[2][NV], g[2][NV], dyv[2][NV];
@@ -292,6 +304,10 @@ rmsnorm_bwd_kernel(const float* __restrict__ x, const float* __restrict__ w, con
           dyv = make_float4(a.x, a.y, b.x, b.y);
         } else {
           dyv = reinterpret_cast<const float4*>(dy32 + (size_t)row * d)[c];
+          for (int s = 1; s < dy_splits; ++s) {
+            const float4 t = reinterpret_cast<const float4*>(dy32 + (size_t)s * dy_stride + (size_t)row * d)[c];
+            dyv.x += t.x; dyv.y += t.y; dyv.z += t.z; dyv.w += t.w;
+          }
         }
         float4 ww = w ? reinterpret_cast<const float4*>(w)[c] : make_float4(1.f, 1.f, 1.f, 1.f);
         float4 f1 = make_float4(1.f, 1.f, 1.f, 1.f);
@@ -818,13 +834,25 @@ extern "C" int rte_residual_rmsnorm_fwd(const float* base, const float* branch, 
                                         float* x1_out, float* x_out, const float* w, const float* film_gamma,
                                         const float* film_beta, void* y_bf16, float* rstd, int32_t rows, int32_t d, float eps,
                                         rte_stream_t stream) {
+  return rte_residual_rmsnorm_fwd_splits(base, branch, 1, 0, nullptr, scale, active, passthrough, S, add2, scale2, x1_out, x_out,
+                                         w, film_gamma, film_beta, y_bf16, rstd, rows, d, eps, stream);
+}
+
+extern "C" int rte_residual_rmsnorm_fwd_splits(const float* base, const float* branch, int32_t branch_splits,
+                                               int64_t branch_split_stride, float* branch_out, const float* scale,
+                                               const int32_t* active, const float* passthrough, int32_t S, const float* add2,
+                                               const float* scale2, float* x1_out, float* x_out, const float* w,
+                                               const float* film_gamma, const float* film_beta, void* y_bf16, float* rstd,
+                                               int32_t rows, int32_t d, float eps, rte_stream_t stream) {
   RTE_CHECK_ARG(base && branch && scale && x_out && y_bf16 && rows > 0 && d > 0 && d % 4 == 0 && S > 0);
+  RTE_CHECK_ARG(branch_splits >= 1 && (branch_splits == 1 || (branch_split_stride % 4 == 0 && branch_split_stride >= (int64_t)rows * d)));
   RTE_CHECK_ARG((active == nullptr || passthrough != nullptr) && (add2 == nullptr || scale2 != nullptr));
   RTE_CHECK_ARG((film_gamma == nullptr) == (film_beta == nullptr));
   if (d > 128 * RN_MAX_V4) return RTE_ERR_UNSUPPORTED;
 #define RTE_RRN_FWD(NV)                                                                                              \
   residual_rmsnorm_fwd_kernel<NV><<<rte::ceil_div(rows, 8), 256, 0, ST(stream)>>>(base, branch, scale, active, passthrough, \
-      S, add2, scale2, x1_out, x_out, w, film_gamma, film_beta, reinterpret_cast<__nv_bfloat16*>(y_bf16), rstd, rows, d, eps)
+      S, add2, scale2, x1_out, x_out, w, film_gamma, film_beta, reinterpret_cast<__nv_bfloat16*>(y_bf16), rstd, rows, d, eps, \
+      branch_splits, (long long)branch_split_stride, branch_out)
   if (d <= 128) RTE_RRN_FWD(1);
   else if (d <= 256) RTE_RRN_FWD(2);
   else if (d <= 512) RTE_RRN_FWD(4);
@@ -840,7 +868,18 @@ extern "C" int rte_rmsnorm_bwd(const float* x, const float* w, const float* film
                                void* dx_bf16, float* dw_partial, float* dgamma_partial, float* dbeta_partial,
                                int32_t rows, int32_t d, int32_t max_partials, int32_t* n_partials,
                                rte_stream_t stream) {
+  return rte_rmsnorm_bwd_splits(x, w, film_gamma, rstd, dy_bf16, dy_f32, 1, 0, dres, dx_f32, dx_bf16, dw_partial, dgamma_partial,
+                                dbeta_partial, rows, d, max_partials, n_partials, stream);
+}
+
+extern "C" int rte_rmsnorm_bwd_splits(const float* x, const float* w, const float* film_gamma, const float* rstd,
+                                      const void* dy_bf16, const float* dy_f32, int32_t dy_splits, int64_t dy_split_stride,
+                                      const float* dres, float* dx_f32, void* dx_bf16, float* dw_partial,
+                                      float* dgamma_partial, float* dbeta_partial, int32_t rows, int32_t d,
+                                      int32_t max_partials, int32_t* n_partials, rte_stream_t stream) {
   RTE_CHECK_ARG(x && rstd && rows > 0 && d > 0 && d % 4 == 0 && (dy_bf16 || dy_f32) && (dx_f32 || dx_bf16));
+  RTE_CHECK_ARG(dy_splits >= 1 && (dy_splits == 1 || (dy_f32 && !dy_bf16 && dy_split_stride % 4 == 0 &&
+                                                      dy_split_stride >= (int64_t)rows * d)));
   RTE_CHECK_ARG((dgamma_partial == nullptr) == (dbeta_partial == nullptr));
   if (d > 128 * RN_MAX_V4) return RTE_ERR_UNSUPPORTED;
   const bool grads = dw_partial || dgamma_partial;
@@ -871,7 +910,8 @@ extern "C" int rte_rmsnorm_bwd(const float* x, const float* w, const float* film
     }                                                                                                            \
     rmsnorm_bwd_kernel<NV, FILM><<<grid, 256, smem, ST(stream)>>>(x, w, film_gamma, rstd,                              \
         reinterpret_cast<const __nv_bfloat16*>(dy_bf16), dy_f32, dres, dx_f32,                                   \
-        reinterpret_cast<__nv_bfloat16*>(dx_bf16), dw_partial, dgamma_partial, dbeta_partial, rows, d);          \
+        reinterpret_cast<__nv_bfloat16*>(dx_bf16), dw_partial, dgamma_partial, dbeta_partial, rows, d,           \
+        dy_splits, (long long)dy_split_stride);                                                                  \
   } while (0)
   if (d <= 128) RTE_RN_BWD(1);
   else if (d <= 256) RTE_RN_BWD(2);

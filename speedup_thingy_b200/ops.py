@@ -170,24 +170,30 @@ class CudaOps:
                       split_stride=M * N, lda=lda, ldb=ldb, ldc=N)
             self.reduce_splits(ws, splits, M * N, M * N, out, accumulate)
 
-    def gemm_f32_few_rows(self, a, b, out, *, M: int, N: int, K: int, b_mn: bool, ws, accumulate: bool = False) -> None:
+    def gemm_f32_few_rows(self, a, b, out, *, M: int, N: int, K: int, b_mn: bool, ws, accumulate: bool = False,
+                          reduce: bool = True) -> tuple[int, int]:
         """out f32 [M,N] (+)= a @ b^T for a GEMM with few rows and a long reduction (the audit replay's chain): one or
         two output tiles would run their k-blocks one after another on one or two SMs, so the reduction is split
-        across up to 16 CTAs per tile and summed in fixed order."""
+        across up to 16 CTAs per tile and summed in fixed order.  `reduce=False` leaves the partials in `ws` for a
+        consumer that sums them itself; returns (splits, stride between partials) -- (1, 0) when `out` holds the result."""
         kb = -(-K // 64)
         splits = 1
         if M <= 256 and kb >= 16 and K % 64 == 0:
             splits = max(s for s in range(1, self.few_rows_max_splits + 1) if kb % s == 0 and kb // s >= 2)
         if splits == 1 or ws is None or ws.numel() < splits * M * N:
             self.gemm(a, b, out, M=M, N=N, K=K, b_mn=b_mn, epilogue=A.EPI_F32, residual=out if accumulate else None)
-            return
+            return (1, 0)
+        if not reduce and not accumulate and (M * N) % 4 == 0:
+            self.gemm(a, b, ws, M=M, N=N, K=K, b_mn=b_mn, epilogue=A.EPI_F32, splits=splits, split_stride=M * N, ldc=N)
+            return (splits, M * N)
         if self.small_fused_reduce and M <= self.small_gemm_rows and -(-N // 32) * -(-M // 64) <= 1024 and out.is_contiguous():
             # one launch: the last CTA of every output tile sums the tile's partials (fixed order)
             self.gemm(a, b, ws, M=M, N=N, K=K, b_mn=b_mn, epilogue=A.EPI_F32, splits=splits, split_stride=M * N, ldc=N,
                       split_reduce=(self._split_counters, out, accumulate))
-            return
+            return (1, 0)
         self.gemm(a, b, ws, M=M, N=N, K=K, b_mn=b_mn, epilogue=A.EPI_F32, splits=splits, split_stride=M * N, ldc=N)
         self.reduce_splits(ws, splits, M * N, M * N, out, accumulate)
+        return (1, 0)
 
     def reduce_splits(self, ws, splits: int, stride: int, n: int, out, accumulate: bool) -> None:
         self._call("rte_reduce_splits", _ptr(ws), splits, stride, n, _ptr(out), int(accumulate), self.stream)
@@ -214,24 +220,29 @@ class CudaOps:
                    _ptr(rstd), rows, d, eps, self.stream)
 
     def residual_rmsnorm_fwd(self, base, branch, scale, x_out, w, y_bf16, rstd, *, S: int, active=None, passthrough=None,
-                             add2=None, scale2=None, x1_out=None, film_gamma=None, film_beta=None, eps: float = 1e-5) -> None:
-        """x1 = active ? base + scale*branch : passthrough; x = x1 (+ scale2*add2); y = rmsnorm(x)*w (FiLM)."""
+                             add2=None, scale2=None, x1_out=None, film_gamma=None, film_beta=None, eps: float = 1e-5,
+                             branch_splits: tuple[int, int] = (1, 0), branch_out=None) -> None:
+        """x1 = active ? base + scale*branch : passthrough; x = x1 (+ scale2*add2); y = rmsnorm(x)*w (FiLM).
+        `branch_splits` = (count, stride): `branch` holds split-K partials, summed in the launch (sum kept in `branch_out`)."""
         d = base.shape[-1]
-        self._call("rte_residual_rmsnorm_fwd", _ptr(base), _ptr(branch), _ptr(scale), _ptr(active), _ptr(passthrough), S,
-                   _ptr(add2), _ptr(scale2), _ptr(x1_out), _ptr(x_out), _ptr(w), _ptr(film_gamma), _ptr(film_beta),
-                   _ptr(y_bf16), _ptr(rstd), base.numel() // d, d, eps, self.stream)
+        self._call("rte_residual_rmsnorm_fwd_splits", _ptr(base), _ptr(branch), branch_splits[0], branch_splits[1],
+                   _ptr(branch_out), _ptr(scale), _ptr(active), _ptr(passthrough), S, _ptr(add2), _ptr(scale2), _ptr(x1_out),
+                   _ptr(x_out), _ptr(w), _ptr(film_gamma), _ptr(film_beta), _ptr(y_bf16), _ptr(rstd), base.numel() // d, d,
+                   eps, self.stream)
 
     def rmsnorm_bwd(self, x, w, rstd, dy, dres, dx_f32, dx_bf16, dw_out, partial, *, film_gamma=None,
                     dgamma_out=None, dbeta_out=None, partial_g=None, partial_b=None, accumulate_dw: bool = False,
-                    accumulate_film: bool = False, rows: int | None = None) -> None:
-        """dx = rmsnorm_backward(dy) + dres; dw_out (+)= column sums (two-stage, deterministic)."""
+                    accumulate_film: bool = False, rows: int | None = None, dy_splits: tuple[int, int] = (1, 0)) -> None:
+        """dx = rmsnorm_backward(dy) + dres; dw_out (+)= column sums (two-stage, deterministic).
+        `dy_splits` = (count, stride): `dy` (fp32) holds split-K partials of the gradient, summed in the launch."""
         d = x.shape[-1]
         rows = rows if rows is not None else x.numel() // d
         n_part = C.c_int32(0)
         dy16 = dy if dy.dtype == torch.bfloat16 else None
         dy32 = dy if dy.dtype == torch.float32 else None
         max_partials = partial.shape[0] if partial is not None else 0
-        self._call("rte_rmsnorm_bwd", _ptr(x), _ptr(w), _ptr(film_gamma), _ptr(rstd), _ptr(dy16), _ptr(dy32),
+        self._call("rte_rmsnorm_bwd_splits", _ptr(x), _ptr(w), _ptr(film_gamma), _ptr(rstd), _ptr(dy16), _ptr(dy32),
+                   dy_splits[0], dy_splits[1],
                    _ptr(dres), _ptr(dx_f32), _ptr(dx_bf16), _ptr(partial if dw_out is not None else None),
                    _ptr(partial_g), _ptr(partial_b), rows, d, max_partials, C.byref(n_part), self.stream)
         if dw_out is None and dgamma_out is None:

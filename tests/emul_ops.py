@@ -100,8 +100,18 @@ class EmulOps:
         else:
             out.view(M, N).copy_(res)
 
-    def gemm_f32_few_rows(self, a, b, out, *, M, N, K, b_mn, ws, accumulate=False):
+    def gemm_f32_few_rows(self, a, b, out, *, M, N, K, b_mn, ws, accumulate=False, reduce=True):
+        if not reduce and not accumulate and ws is not None and ws.numel() >= 2 * M * N and K >= 2 and (M * N) % 4 == 0:
+            # two partials over the halves of the reduction, left for the consumer to sum (as the split-K launch does)
+            self.launches += 1
+            A_ = a.reshape(-1, a.shape[-1])[:M, :K].float()
+            B_ = (b.reshape(K, -1)[:, :N].t() if b_mn else b.reshape(-1, b.shape[-1])[:N, :K]).float()
+            h = K // 2
+            ws.view(-1)[: M * N] = (A_[:, :h] @ B_[:, :h].t()).flatten()
+            ws.view(-1)[M * N: 2 * M * N] = (A_[:, h:] @ B_[:, h:].t()).flatten()
+            return (2, M * N)
         self.gemm(a, b, out, M=M, N=N, K=K, b_mn=b_mn, epilogue=EPI_F32, residual=out if accumulate else None)
+        return (1, 0)
 
     def reduce_splits(self, ws, splits, stride, n, out, accumulate):
         res = ws[: splits * stride].view(splits, stride)[:, :n].sum(0)
@@ -134,8 +144,17 @@ class EmulOps:
             y_f32.view(-1, d).copy_(y)
 
     def residual_rmsnorm_fwd(self, base, branch, scale, x_out, w, y_bf16, rstd, *, S, active=None, passthrough=None,
-                             add2=None, scale2=None, x1_out=None, film_gamma=None, film_beta=None, eps=1e-5):
+                             add2=None, scale2=None, x1_out=None, film_gamma=None, film_beta=None, eps=1e-5,
+                             branch_splits=(1, 0), branch_out=None):
         d = base.shape[-1]
+        if branch_splits[0] > 1:
+            n = base.numel()
+            parts = branch.view(-1)[: branch_splits[0] * branch_splits[1]].view(branch_splits[0], branch_splits[1])[:, :n]
+            branch = parts[0].clone()
+            for s in range(1, branch_splits[0]):
+                branch = branch + parts[s]
+            if branch_out is not None:
+                branch_out.view(-1)[:n] = branch
         x1 = base.reshape(-1, d) + scale.reshape(()) * branch.reshape(-1, d)
         if active is not None:
             on = active.bool().repeat_interleave(S)[:, None]
@@ -148,9 +167,15 @@ class EmulOps:
 
     def rmsnorm_bwd(self, x, w, rstd, dy, dres, dx_f32, dx_bf16, dw_out, partial, *, film_gamma=None,
                     dgamma_out=None, dbeta_out=None, partial_g=None, partial_b=None, accumulate_dw=False,
-                    accumulate_film=False, rows=None):
+                    accumulate_film=False, rows=None, dy_splits=(1, 0)):
         self.launches += 1
         d = x.shape[-1]
+        if dy_splits[0] > 1:
+            n = x.numel()
+            parts = dy.view(-1)[: dy_splits[0] * dy_splits[1]].view(dy_splits[0], dy_splits[1])[:, :n]
+            dy = parts[0].clone()
+            for s in range(1, dy_splits[0]):
+                dy = dy + parts[s]
         xr = x.reshape(-1, d)
         r = rstd.view(-1)[: xr.shape[0]].unsqueeze(-1)
         xh = xr * r

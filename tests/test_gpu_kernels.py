@@ -426,6 +426,53 @@ def test_residual_rmsnorm_fwd_matches_the_separate_steps(ops, n, S, d, with_sele
     assert (rstd.cpu() - torch.rsqrt(x.pow(2).mean(-1) + 1e-5)).abs().max() <= 1e-5
 
 
+@pytest.mark.parametrize("n,S,d,splits,film", [(1, 64, 512, 4, True), (3, 16, 128, 3, True), (2, 8, 64, 2, False)])
+def test_norm_launches_fed_with_split_partials_equal_reduce_then_launch(ops, n, S, d, splits, film):
+    """rte_residual_rmsnorm_fwd_splits / rte_rmsnorm_bwd_splits: a branch (or dy) handed over as split-K partials gives
+    the bits of rte_reduce_splits followed by the plain launch, and the summed branch comes back in branch_out."""
+    g = torch.Generator().manual_seed(11 * d + splits)
+    rows = n * S
+    stride = rows * d + 64                                           # partials need not be packed
+    dev = lambda t: t.to(DEV)  # noqa: E731
+    parts = dev(torch.randn(splits, stride, generator=g))
+    base, pas, add2 = (dev(torch.randn(rows, d, generator=g)) for _ in range(3))
+    w, fg, fb = (dev(torch.randn(d, generator=g) * 0.3) for _ in range(3))
+    s1, s2 = dev(torch.tensor([0.7])), dev(torch.tensor([0.1]))
+    active = dev(torch.tensor([i % 2 for i in range(n)], dtype=torch.int32))
+    summed = torch.zeros(rows, d, device=DEV)
+    ops.reduce_splits(parts, splits, stride, rows * d, summed, False)
+    outs = []
+    for fused in (False, True):
+        x1, x = torch.zeros(rows, d, device=DEV), torch.zeros(rows, d, device=DEV)
+        y16, rstd = torch.zeros(rows, d, dtype=torch.bfloat16, device=DEV), torch.zeros(rows, device=DEV)
+        kept = torch.full((rows, d), 7.0, device=DEV)
+        ops.residual_rmsnorm_fwd(base, parts if fused else summed, s1, x, w, y16, rstd, S=S, active=active, passthrough=pas,
+                                 add2=add2, scale2=s2, x1_out=x1, film_gamma=fg if film else None, film_beta=fb if film else None,
+                                 branch_splits=(splits, stride) if fused else (1, 0), branch_out=kept if fused else None)
+        outs.append((x1, x, y16, rstd, kept))
+    torch.cuda.synchronize()
+    for a, b in zip(outs[0][:4], outs[1][:4]):
+        assert torch.equal(a, b)
+    assert torch.equal(outs[1][4], summed)                          # every row's sum is kept, frozen samples' too
+    # backward
+    xin, dres = dev(torch.randn(rows, d, generator=g)), dev(torch.randn(rows, d, generator=g))
+    rstd = dev(torch.rand(rows, generator=g) + 0.5)
+    res = []
+    for fused in (False, True):
+        dx, dx16 = torch.zeros(rows, d, device=DEV), torch.zeros(rows, d, dtype=torch.bfloat16, device=DEV)
+        dw, dg_, db_ = (torch.zeros(d, device=DEV) for _ in range(3))
+        pw, pg, pb = (torch.zeros(128, d, device=DEV) for _ in range(3))
+        ops.rmsnorm_bwd(xin, w, rstd, parts if fused else summed, dres, dx, dx16, dw, pw, film_gamma=fg if film else None,
+                        dgamma_out=dg_ if film else None, dbeta_out=db_ if film else None, partial_g=pg if film else None,
+                        partial_b=pb if film else None, dy_splits=(splits, stride) if fused else (1, 0))
+        res.append((dx, dx16, dw, dg_, db_))
+    torch.cuda.synchronize()
+    for a, b in zip(res[0], res[1]):
+        assert torch.equal(a, b)
+    with pytest.raises(Exception):
+        ops.rmsnorm_bwd(xin, w, rstd, parts, dres, res[0][0], None, None, None, dy_splits=(splits, rows * d - 4))   # overlapping partials
+
+
 def test_swiglu_standalone_pass_matches_fused_epilogue_math(ops):
     g = torch.Generator().manual_seed(12)
     rows, F_ = 300, 192
