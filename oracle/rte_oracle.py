@@ -81,6 +81,7 @@ class TrainCfg:
     seq_len: int = 64
     seed: int = 0
     fixed_recipe: int | None = None
+    fixed_recipe_schedule: tuple | None = None      # recursive_exact: pass t runs recipe schedule[t] for every sample
     fixed_depth: int | None = 4
     audit_fixed_count_per_batch: int | None = None  # None + p=0 -> no audit
     audit_mode: str = "gradient_corrected"
@@ -518,12 +519,20 @@ def coda_logits(p: dict, cfg: ModelCfg, h: torch.Tensor) -> tuple[torch.Tensor, 
     return hidden, hidden @ p["embed.weight"].t()
 
 
-def exact_from_h0(p: dict, cfg: ModelCfg, h0: torch.Tensor, targets: torch.Tensor, route: dict) -> dict:
+def exact_from_h0(p: dict, cfg: ModelCfg, h0: torch.Tensor, targets: torch.Tensor, route: dict,
+                  schedule: tuple | None = None) -> dict:
     """models.py:416-512 with reused router decisions: t_max banked passes using the
-    per-pass recipe ids, samples with depth <= t frozen."""
+    per-pass recipe ids, samples with depth <= t frozen.  `schedule` (models.py:230-247, 449-451): pass t runs recipe
+    schedule[t] for every sample instead."""
+    if schedule is not None:
+        if len(schedule) < cfg.t_max:
+            raise ValueError(f"fixed_recipe_schedule length {len(schedule)} is shorter than t_max={cfg.t_max}")
+        if any(not 0 <= int(r) < cfg.recipe_count for r in schedule):
+            raise ValueError("fixed_recipe_schedule recipe outside the recipe bank")
     h = h0
     for t in range(cfg.t_max):
-        h = core_forward_step(p, cfg, h, h0, route["recipe_id_by_pass"][:, t], route["depth"] > t, t)
+        rid = route["recipe_id_by_pass"][:, t] if schedule is None else torch.full_like(route["recipe_id"], int(schedule[t]))
+        h = core_forward_step(p, cfg, h, h0, rid, route["depth"] > t, t)
     hidden, logits = coda_logits(p, cfg, h)
     return dict(recurrent_hidden=h, hidden=hidden, logits=logits,
                 loss_per_sample=lm_loss_per_sample(logits, targets))
@@ -806,10 +815,12 @@ def exact_step_loss(p: dict, cfg: ModelCfg, tr: TrainCfg, tokens: torch.Tensor, 
     for i in range(cfg.n_prelude):
         h0 = dense_block(p, f"prelude.{i}", h0, cfg.n_heads)
     route = router_forward(p, cfg, h0, tr.fixed_recipe, tr.fixed_depth)
-    out = exact_from_h0(p, cfg, h0, targets, route)
+    out = exact_from_h0(p, cfg, h0, targets, route, tr.fixed_recipe_schedule)
     aux_router = router_aux_losses(tr, route["recipe_probs"], route["expected_depth"], usage_ema)
     loss = out["loss_per_sample"].mean() / float(targets.shape[1]) + sum(aux_router.values())
     out.update(route=route, h0=h0)
+    if tr.fixed_recipe_schedule is not None:      # models.py:480-497: what the usage average then counts
+        out["usage_ids"] = torch.tensor([int(r) for r in tr.fixed_recipe_schedule[:cfg.t_max]]).expand(h0.shape[0], -1)
     return loss, dict(hot=out, aux_router=aux_router)
 
 
@@ -886,7 +897,8 @@ class OracleTrainer:
             adamw_update(self.params[name], g, st["m"], st["v"], st["step"], self.tr.lr,
                          self.tr.weight_decay, self.tr.betas, self.tr.eps)
         if self.cfg.topology != "dense":
-            self.usage_ema = update_usage(self.usage_ema, info["hot"]["route"]["recipe_id"], self.tr.coverage_beta)
+            ids = info["hot"].get("usage_ids", info["hot"]["route"]["recipe_id"])
+            self.usage_ema = update_usage(self.usage_ema, ids, self.tr.coverage_beta)
         self.global_step += 1
         return float(loss)
 

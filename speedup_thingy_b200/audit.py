@@ -104,6 +104,7 @@ class AuditReplay:
         self._prepared = None
         self._prelude_copied = None
         self._core_fwd_done = self.distill_done = None
+        self.fixed_rid = None                        # [T, n] int32 when `recursive_exact` runs a fixed recipe schedule
         cfg, dev = eng.cfg, eng.device
         self.n, self.S, self.T = k, eng.S, cfg.t_max
         self.Ma = k * eng.S
@@ -411,6 +412,8 @@ class AuditReplay:
         if not head_done:
             self.forward_replay_head(h0)
         o.audit_route(eng.route["recipe_id_by_pass"], eng.route["depth"], self.idx, self.rid, self.active, n, T)
+        if self.fixed_rid is not None:               # a fixed per-pass recipe schedule overrides the routed recipes
+            self.rid.copy_(self.fixed_rid)
         alpha = p["core.alpha_inj"].view(1)
         # The residual updates ride in front of the norms (one launch each instead of two or three):
         #   ht = h + alpha*h0 -> norm1;   u = ht + s_attn*attn -> norm2;

@@ -377,8 +377,8 @@ def unsupported(config: ExperimentConfig) -> list[str]:
             no("training", "audit_mode", "one of gradient_corrected, metric_only, distill_only")
         if t.macro_rms_trust_region or t.macro_rms_clamp_early:
             no("training", "macro_rms_trust_region", "the RMS trust region is not implemented")
-    if t.fixed_recipe_schedule is not None:
-        no("training", "fixed_recipe_schedule", "per-pass fixed recipes are not implemented")
+    if t.fixed_recipe_schedule is not None and t.mode != "recursive_exact":
+        no("training", "fixed_recipe_schedule", "per-pass fixed recipes are implemented for mode recursive_exact only")
     if t.coda_warmup_steps:
         no("training", "coda_warmup_steps", "coda warm-up is not implemented")
     if t.debug_force_full_output and t.mode == "recursive_macro_shortlist":

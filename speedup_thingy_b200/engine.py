@@ -531,6 +531,16 @@ class TrainEngine:
             from .audit import AuditReplay
             self.exact_core = AuditReplay(self, B, direct_grads=True)         # the replay machinery over the whole batch
             self.exact_core.idx.copy_(torch.arange(B, dtype=torch.int32))
+            if tr.fixed_recipe_schedule is not None:
+                # models.py:230-247, 449-451: pass t runs recipe schedule[t] for every sample, whatever the router chose
+                sched = [int(r) for r in tr.fixed_recipe_schedule]
+                if len(sched) < cfg.t_max:
+                    raise ValueError(f"fixed_recipe_schedule length {len(sched)} is shorter than t_max={cfg.t_max}")
+                if any(not 0 <= r < cfg.recipe_count for r in sched):
+                    raise ValueError(f"fixed_recipe_schedule recipe outside [0, {cfg.recipe_count})")
+                self.exact_schedule = sched[:cfg.t_max]
+                self.exact_core.fixed_rid = (torch.tensor(self.exact_schedule, dtype=torch.int32).view(-1, 1)
+                                             .expand(cfg.t_max, B).contiguous().to(dev))
         if self.audit_k:
             from .audit import AuditReplay
             self.audit = AuditReplay(self, self.audit_k)
@@ -1529,6 +1539,8 @@ class TrainEngine:
             metrics["macro_consistency_loss"] = self.last_consistency
         if not self.dense:
             ids = host["recipe_id"].long()
+            if getattr(self, "exact_schedule", None) is not None:        # the schedule is what ran (models.py:480-497)
+                ids = torch.tensor(self.exact_schedule, dtype=torch.long).repeat(self.B)
             counts = torch.bincount(ids, minlength=self.cfg.recipe_count).float()
             self.usage_ema.mul_(self.tr.coverage_beta).add_(counts / counts.sum().clamp_min(1.0), alpha=1.0 - self.tr.coverage_beta)
             metrics["unique_recipes_per_batch"] = int(ids.unique().numel())

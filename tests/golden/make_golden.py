@@ -54,6 +54,7 @@ def reference_experiment(case: dict, run_dir: str) -> RC.ExperimentConfig:
         audit_gradient_correction=audited and t.get("audit_mode", "gradient_corrected") == "gradient_corrected",
         audit_residual_clip=t.get("audit_residual_clip"), lambda_cons=t.get("lambda_cons", 0.0),
         grad_clip_norm=t.get("grad_clip_norm"),
+        fixed_recipe_schedule=list(t["fixed_recipe_schedule"]) if t.get("fixed_recipe_schedule") is not None else None,
         **{k_: v_ for k_, v_ in t.items() if k_.startswith("audit_schedule_")},
         fused_optimizer=False, foreach_optimizer=True, allow_tf32=False, log_every=10_000,
     )

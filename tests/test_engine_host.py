@@ -362,3 +362,48 @@ def test_count_schedule_follows_the_reference_trajectory():
     small.train_step(next(it))                   # 2 of capacity 2; the schedule then asks for 4
     with pytest.raises(RuntimeError, match="audit_capacity"):
         small.train_step(next(it))
+
+
+def test_recursive_exact_with_a_fixed_recipe_schedule_follows_the_reference():
+    """`fixed_recipe_schedule` in mode recursive_exact (models.py:230-247, 449-451): every sample runs recipe
+    schedule[t] in pass t.  First-step gradients against the oracle, the loss curve against the golden the reference
+    produced, the usage average counts the schedule; a schedule shorter than t_max or outside the bank is refused."""
+    from pathlib import Path
+
+    from tests.golden.cases import GOLDEN_CASES
+    case = GOLDEN_CASES["small_exact_schedule"]
+    gold = np.load(Path(__file__).resolve().parent / "golden" / "small_exact_schedule.npz")
+    cfg = ExperimentConfig(ModelConfig(**case["model"]), TrainingConfig(**case["train"]), OutputConfig())
+    tr = cfg.training
+    params = init_parameters(cfg.model, seed=tr.seed)
+    eng = TrainEngine(cfg, params, device="cpu", ops=EmulOps(), use_cuda_graph=False)
+    oracle = O.OracleTrainer(O.ModelCfg(**case["model"]), O.TrainCfg(**case["train"]), {k: v.clone() for k, v in params.items()})
+    stream = O.zipf_tokens(tr.batch_size * tr.seq_len * (case["steps"] + 2) + 1, cfg.model.vocab_size, seed=tr.seed)
+    batches = [b for _, b in zip(range(case["steps"]), O.batches(stream, tr.batch_size, tr.seq_len))]
+    loss, grads = eng.loss_and_grads(batches[0])
+    ref_loss, ref_grads, _ = oracle.loss_and_grads(*batches[0])
+    assert abs(loss - float(ref_loss)) < 2e-2 and sorted(grads) == sorted(ref_grads)
+    for n, g in grads.items():
+        err, scale = (g - ref_grads[n]).abs().max().item(), ref_grads[n].abs().max().item()
+        assert err <= 2e-2 * max(scale, 1e-3) + 2e-4, (n, err, scale)
+    # the routed recipes would have given other gradients: the schedule is what ran
+    free = O.OracleTrainer(O.ModelCfg(**case["model"]), O.TrainCfg(**{**case["train"], "fixed_recipe_schedule": None}),
+                           {k: v.clone() for k, v in params.items()})
+    _, free_grads, _ = free.loss_and_grads(*batches[0])
+    name = "core.mlp.wug"
+    assert (free_grads[name] - ref_grads[name]).abs().max() > 0.2 * ref_grads[name].abs().max()
+    losses = [eng.train_step(b).loss for b in batches]
+    for b in batches:
+        oracle.train_step(*b)
+    rel = np.abs(np.array(losses) - gold["losses"]) / np.abs(gold["losses"])
+    assert rel.max() <= 1e-2, (rel.max(), losses, gold["losses"])
+    assert torch.allclose(eng.usage_ema, oracle.usage_ema, atol=1e-6)
+    assert float(eng.usage_ema[4]) == 0.0 and float(eng.usage_ema[[0, 1, 2, 3]].min()) > 0.0      # recipe 4 never ran
+    for bad in ((1, 2, 3), (1, 2, 3, 9)):
+        with pytest.raises(ValueError, match="fixed_recipe_schedule"):
+            TrainEngine(ExperimentConfig(ModelConfig(**case["model"]), TrainingConfig(**{**case["train"], "fixed_recipe_schedule": bad}),
+                                         OutputConfig()), params, device="cpu", ops=EmulOps(), use_cuda_graph=False)
+    with pytest.raises(NotImplementedError, match="fixed_recipe_schedule"):
+        TrainEngine(ExperimentConfig(ModelConfig(**case["model"]),
+                                     TrainingConfig(**{**case["train"], "mode": "recursive_macro"}), OutputConfig()),
+                    params, device="cpu", ops=EmulOps(), use_cuda_graph=False)
