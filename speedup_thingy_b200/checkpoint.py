@@ -106,7 +106,8 @@ def save_checkpoint(engine: TrainEngine, path: str | Path, *, data_cursor: int |
     if not engine.dense:
         # the reference model's two persistent buffers (macro.py:99-122): the per-key update scale the macro kernels
         # read, and the teacher statistic only the reference's distillation tooling writes
-        model["macro.update_scale"] = engine.macro_scale.detach().to("cpu").clone()
+        if "macro.update_scale" not in model:          # (a trainable parameter in the operator's variants, macro.py:99-108)
+            model["macro.update_scale"] = engine.macro_scale.detach().to("cpu").clone()
         model["macro.teacher_delta_rms"] = engine.macro_teacher_delta_rms.clone()
     payload = {"config": dataclasses.asdict(engine.config), "model": model,
                "optimizer": optimizer_state_dict(engine), "global_step": engine.global_step,

@@ -367,7 +367,10 @@ def unsupported(config: ExperimentConfig) -> list[str]:
                       ("macro_hidden_mult", 1), ("macro_use_gated_update", False), ("macro_include_delta_to_h0", False),
                       ("macro_use_delta_to_h0", False), ("macro_use_depth_embedding", False),
                       ("macro_use_recipe_embedding", False), ("macro_decomposition", "direct")):
-        if m.topology == "recursive" and getattr(m, key) != want:
+        # (mode recursive_exact never evaluates the macro operator: its variants then only add parameters the step
+        #  carries untouched -- no influence on the arithmetic)
+        inert = key.startswith("macro_") and t.mode == "recursive_exact"
+        if m.topology == "recursive" and getattr(m, key) != want and not inert:
             no("model", key, f"only {want!r} (the 3d -> rank -> d bounded-residual macro operator, macro.py:201-236)")
     if m.topology == "dense" and not m.tie_embeddings:
         no("model", "tie_embeddings", "only tied input / output embeddings")

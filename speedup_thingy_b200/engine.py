@@ -47,6 +47,44 @@ def _block_shapes(prefix: str, cfg: ModelConfig) -> list[tuple[str, tuple]]:
             (f"{prefix}.mlp.wug.weight", (2 * f, d)), (f"{prefix}.mlp.wd.weight", (d, f))]
 
 
+def macro_param_shapes(cfg) -> list[tuple[str, tuple]]:
+    """Parameters of ``MacroOperators`` in registration order for every variant the reference builds (macro.py:42-124):
+    the bounded-residual operator with its optional hidden layer, gate, delta-to-h0 / depth-embedding inputs and
+    trainable update scale, and the v2 delta-radius operator.  Only the plain bounded-residual form is ever
+    EVALUATED by this code; the others are carried (checkpoints, parameter counts) by modes that do not call the
+    macro operator."""
+    r, k, d, m = cfg.recipe_count, len(cfg.depth_choices), cfg.d_model, cfg.macro_rank
+    g = lambda name, default: getattr(cfg, name, default)      # noqa: E731
+    delta = g("macro_include_delta_to_h0", False)
+    depth_emb, hidden = g("macro_use_depth_embedding", False), max(m, m * g("macro_hidden_mult", 1))
+    out: list[tuple[str, tuple]] = []
+    if g("macro_type", "bounded_residual") == "v2_delta_radius":
+        n_in = 3 * d + (d if (delta or g("macro_use_delta_to_h0", False)) else 0) + (d if depth_emb else 0)
+        if depth_emb:
+            out.append(("macro.depth_embed", (k, d)))
+        if g("macro_use_recipe_embedding", False):
+            n_in += d
+            out.append(("macro.recipe_embed", (r, d)))
+        return out + [("macro.v", (r, k, n_in, hidden)), ("macro.v2", (r, k, hidden, m)), ("macro.u", (r, k, m, d)),
+                      ("macro.bias", (r, k, d)), ("macro.rho_base_raw", (r, k)), ("macro.rho_head", (r, k, d, 1))]
+    n_in = 3 * d + (d if delta else 0) + (d if depth_emb else 0)
+    gated = g("macro_use_gated_update", False)
+    legacy = (g("macro_hidden_mult", 1) == 1 and not gated and not delta and not depth_emb
+              and g("macro_update_scale_init", 1.0) == 1.0)          # then `update_scale` is a buffer, not a parameter
+    if depth_emb:
+        out.append(("macro.depth_embed", (k, d)))
+    out += [("macro.d_gain", (r, k, d)), ("macro.v", (r, k, n_in, hidden))]
+    if hidden != m:
+        out.append(("macro.v2", (r, k, hidden, m)))
+    out.append(("macro.u", (r, k, m, d)))
+    if not legacy:
+        out.append(("macro.update_scale", (r, k, d)))
+    out.append(("macro.bias", (r, k, d)))
+    if gated:
+        out += [("macro.gate_v", (r, k, n_in, m)), ("macro.gate_u", (r, k, m, d)), ("macro.gate_bias", (r, k, d))]
+    return out
+
+
 def parameter_shapes(cfg: ModelConfig, num_clusters: int = 64) -> list[tuple[str, tuple]]:
     """Parameter names and shapes in the reference's registration order (models.py:78-93, 125-151);
     `num_clusters` sizes the shortlist head's cluster router (output.py:29)."""
@@ -77,8 +115,7 @@ def parameter_shapes(cfg: ModelConfig, num_clusters: int = 64) -> list[tuple[str
             ("core.alpha_inj", ()), ("core.norm1.weight", (d,)), ("core.attn.wqkv", (cfg.attn_banks, d, 3 * d)),
             ("core.attn.wo", (cfg.attn_banks, d, d)), ("core.norm2.weight", (d,)),
             ("core.mlp.wug", (cfg.ffn_banks, d, 2 * f)), ("core.mlp.wd", (cfg.ffn_banks, f, d))]
-    out += [("macro.d_gain", (r, k, d)), ("macro.v", (r, k, 3 * d, m)), ("macro.u", (r, k, m, d)),
-            ("macro.bias", (r, k, d))]
+    out += macro_param_shapes(cfg)
     for i in range(cfg.n_coda):
         out += _block_shapes(f"coda.{i}", cfg)
     return out + [("final_norm.weight", (d,)), ("shortlist_head.cluster_router.weight", (num_clusters, d))]

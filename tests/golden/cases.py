@@ -102,6 +102,18 @@ GOLDEN_CASES = {
                    fixed_depth=None, audit_fixed_count_per_batch=None, fixed_recipe_schedule=(1, 3, 0, 2)),
         steps=6,
     ),
+    # recursive_exact on a model whose macro operator is a variant (hidden layer, gate, delta-to-h0 and depth-embedding
+    # inputs, trainable update scale): the step never evaluates it, its parameters ride along untouched
+    "small_exact_variant": dict(
+        model=dict(vocab_size=96, d_model=32, n_heads=4, d_ff=64, n_dense_layers=3, n_prelude=1, n_coda=1,
+                   t_max=4, depth_choices=(1, 2, 4), attn_banks=1, ffn_banks=1, head_groups=4, ffn_groups=4,
+                   active_head_groups=2, active_ffn_groups=2, recipe_count=5, macro_rank=8, macro_hidden_mult=2,
+                   macro_use_gated_update=True, macro_include_delta_to_h0=True, macro_use_depth_embedding=True,
+                   macro_update_scale_init=0.1),
+        train=dict(mode="recursive_exact", lr=2e-3, weight_decay=0.05, batch_size=4, seq_len=12, seed=47,
+                   fixed_depth=None, audit_fixed_count_per_batch=None),
+        steps=4,
+    ),
     "small_dense": dict(
         model=dict(topology="dense", vocab_size=96, d_model=32, n_heads=4, d_ff=64, n_dense_layers=2, n_prelude=1,
                    n_coda=1, t_max=4, depth_choices=(1, 2, 4), attn_banks=1, ffn_banks=1, head_groups=4,

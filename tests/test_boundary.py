@@ -87,7 +87,10 @@ def test_every_reference_preset_parses_and_is_runnable_or_refused_by_value():
     # the presets of the benchmarked pattern (fixed-count audit, constant or decaying LR, no consistency term) run
     assert "medium_mac_real_clamped4_8_cheap_audit.yaml" in runnable, runnable
     assert "medium_mac_real_hotpath.yaml" in runnable and "medium_mac_real_speed.yaml" in runnable, runnable
-    assert len(runnable) >= 4, runnable
+    # mode recursive_exact with a per-pass recipe schedule on a model whose (never evaluated) macro operator is a variant
+    for depth in (4, 8, 16):
+        assert f"proof_filter_depth{depth}_exact_teacher.yaml" in runnable, runnable
+    assert len(runnable) >= 14, runnable
 
 
 def test_unknown_keys_are_rejected_like_the_reference(tmp_path):

@@ -160,3 +160,30 @@ def test_audit_sampler_state_survives_a_checkpoint(tmp_path, name):
         assert state["fixed_count"] == int(np.load(Path(__file__).parent / "golden" / f"{name}.npz")["audit_next_count_step2"])
         assert ref.audit_engine.last_hidden_mse == state["last_hidden_mse"] > 0
         assert ref.audit_engine.last_macro_norm == state["last_macro_norm"] > 0
+
+
+def test_variant_macro_operator_checkpoints_move_both_ways(tmp_path):
+    """recursive_exact on a model with a variant macro operator (extra, untouched parameters; `update_scale` a
+    parameter instead of a buffer): the engine's checkpoint loads into the reference's model strictly, the
+    reference's into the engine, and both continue with the same loss."""
+    case = GOLDEN_CASES["small_exact_variant"]
+    cfg, eng = _engine(case)
+    batches = _batches(cfg, 3)
+    for b in batches[:2]:
+        eng.train_step(b)
+    save_checkpoint(eng, tmp_path / "engine.pt")
+    ref = _reference_engine(case, str(tmp_path))
+    ref.load_checkpoint(tmp_path / "engine.pt")
+    ref_params = dict(ref.recursive_model.named_parameters())
+    assert sorted(ref_params) == sorted(eng.params)
+    for n, t in eng.params.items():
+        assert torch.equal(ref_params[n].detach(), t), n
+    a = eng.train_step(batches[2]).loss
+    b = float(ref.train_step(batches[2]).loss)
+    assert abs(a - b) <= 1e-2 * abs(b), (a, b)
+    ref.save_checkpoint(tmp_path / "reference.pt")
+    _, back = _engine(case)
+    load_checkpoint(back, tmp_path / "reference.pt")
+    for n, p in ref.recursive_model.named_parameters():
+        assert torch.equal(back.params[n], p.detach()), n
+    assert back.global_step == 3

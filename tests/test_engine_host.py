@@ -407,3 +407,35 @@ def test_recursive_exact_with_a_fixed_recipe_schedule_follows_the_reference():
         TrainEngine(ExperimentConfig(ModelConfig(**case["model"]),
                                      TrainingConfig(**{**case["train"], "mode": "recursive_macro"}), OutputConfig()),
                     params, device="cpu", ops=EmulOps(), use_cuda_graph=False)
+
+
+def test_recursive_exact_carries_a_variant_macro_operator_untouched():
+    """Mode recursive_exact never evaluates the macro operator, so a model whose operator is one of the reference's
+    variants (hidden layer, gate, extra inputs, trainable update scale: macro.py:42-124) trains like any other: the
+    reference's parameter names and shapes, its loss curve, and every macro parameter exactly as initialised."""
+    from pathlib import Path
+
+    from speedup_thingy_b200.config import unsupported
+    from tests.golden.cases import GOLDEN_CASES
+    case = GOLDEN_CASES["small_exact_variant"]
+    gold = np.load(Path(__file__).resolve().parent / "golden" / "small_exact_variant.npz")
+    cfg = ExperimentConfig(ModelConfig(**case["model"]), TrainingConfig(**case["train"]), OutputConfig())
+    assert not [m for m in unsupported(cfg) if "precision" not in m]
+    macro_mode = ExperimentConfig(ModelConfig(**case["model"]), TrainingConfig(**{**case["train"], "mode": "recursive_macro"}),
+                                  OutputConfig())
+    assert any("macro_hidden_mult" in m for m in unsupported(macro_mode))          # still refused where it would be evaluated
+    tr = cfg.training
+    assert parameter_shapes(cfg.model, cfg.output.num_clusters) == O.param_shapes(O.ModelCfg(**case["model"]))
+    names = [n for n, _ in parameter_shapes(cfg.model)]
+    for extra in ("macro.depth_embed", "macro.v2", "macro.update_scale", "macro.gate_v", "macro.gate_u", "macro.gate_bias"):
+        assert extra in names
+    params = init_parameters(cfg.model, seed=tr.seed)
+    eng = TrainEngine(cfg, {k: v.clone() for k, v in params.items()}, device="cpu", ops=EmulOps(), use_cuda_graph=False)
+    assert not any(n.startswith("macro.") for n in eng.trainable)
+    stream = O.zipf_tokens(tr.batch_size * tr.seq_len * (case["steps"] + 2) + 1, cfg.model.vocab_size, seed=tr.seed)
+    losses = [eng.train_step(b).loss for _, b in zip(range(case["steps"]), O.batches(stream, tr.batch_size, tr.seq_len))]
+    rel = np.abs(np.array(losses) - gold["losses"]) / np.abs(gold["losses"])
+    assert rel.max() <= 1e-2, (rel.max(), losses, gold["losses"])
+    for n in names:
+        if n.startswith("macro."):
+            assert torch.equal(eng.params[n], params[n]), n
