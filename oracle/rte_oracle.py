@@ -872,6 +872,59 @@ def exact_step_loss(p: dict, cfg: ModelCfg, tr: TrainCfg, tokens: torch.Tensor, 
     return loss, dict(hot=out, aux_router=aux_router)
 
 
+def deferred_schedule(cfg: ModelCfg, tr: TrainCfg) -> list[int]:
+    """models.py:551-566: one recipe per micro-pass of the grouped block -- `fixed_recipe` (default 1) repeated
+    `fixed_depth` (default t_max) times, or the first entries of `fixed_recipe_schedule`, its last one repeated."""
+    depth = max(1, min(int(tr.fixed_depth or cfg.t_max), cfg.t_max))
+    if tr.fixed_recipe_schedule is None:
+        schedule = [int(tr.fixed_recipe if tr.fixed_recipe is not None else 1)] * depth
+    else:
+        schedule = [int(r) for r in tr.fixed_recipe_schedule[:depth]] or [int(tr.fixed_recipe if tr.fixed_recipe is not None else 1)]
+        schedule += [schedule[-1]] * (depth - len(schedule))
+    for r in schedule:
+        if not 0 <= r < cfg.recipe_count:
+            raise ValueError(f"deferred grouped recipe {r} is outside [0, {cfg.recipe_count})")
+    return schedule
+
+
+def deferred_grouped_block(p: dict, cfg: ModelCfg, h: torch.Tensor, h0: torch.Tensor, schedule: list[int],
+                           active: torch.Tensor) -> torch.Tensor:
+    """layers.py:872-912 (no global corrector): ONE block whose attention and MLP halves each sum the branches of all
+    scheduled recipes, every branch reading the same normed input under its own pass's FiLM and scale."""
+    recipes = build_recipes(cfg)
+    ht = h + p["core.alpha_inj"] * h0
+    n1 = rmsnorm(ht, p["core.norm1.weight"])
+    u = ht
+    for t, rid in enumerate(schedule):
+        i = min(t, cfg.t_max - 1)
+        u = u + p["core.pass_attn_scale"][i] * banked_attention(p, cfg, n1 * (1.0 + p["core.pass_gamma1"][i]) + p["core.pass_beta1"][i],
+                                                                recipes[rid])
+    n2 = rmsnorm(u, p["core.norm2.weight"])
+    out = u
+    for t, rid in enumerate(schedule):
+        i = min(t, cfg.t_max - 1)
+        out = out + p["core.pass_mlp_scale"][i] * banked_swiglu(p, cfg, n2 * (1.0 + p["core.pass_gamma2"][i]) + p["core.pass_beta2"][i],
+                                                                recipes[rid])
+    return torch.where(active.view(-1, 1, 1), out, h)
+
+
+def deferred_step_loss(p: dict, cfg: ModelCfg, tr: TrainCfg, tokens: torch.Tensor, targets: torch.Tensor,
+                       usage_ema: torch.Tensor) -> tuple[torch.Tensor, dict]:
+    """training.py:823-877 (`recursive_deferred_grouped_exact`), models.py:538-603."""
+    h0 = p["embed.weight"][tokens]
+    for i in range(cfg.n_prelude):
+        h0 = dense_block(p, f"prelude.{i}", h0, cfg.n_heads)
+    route = router_forward(p, cfg, h0, tr.fixed_recipe, tr.fixed_depth)
+    schedule = deferred_schedule(cfg, tr)
+    h = deferred_grouped_block(p, cfg, h0, h0, schedule, route["depth"] > 0)
+    hidden, logits = coda_logits(p, cfg, h)
+    out = dict(recurrent_hidden=h, hidden=hidden, logits=logits, loss_per_sample=lm_loss_per_sample(logits, targets),
+               route=route, h0=h0, usage_ids=torch.tensor(schedule).expand(h0.shape[0], -1))
+    aux_router = router_aux_losses(tr, route["recipe_probs"], route["expected_depth"], usage_ema)
+    loss = out["loss_per_sample"].mean() / float(targets.shape[1]) + sum(aux_router.values())
+    return loss, dict(hot=out, aux_router=aux_router)
+
+
 def dense_step_loss(p: dict, cfg: ModelCfg, tokens: torch.Tensor, targets: torch.Tensor) -> tuple[torch.Tensor, dict]:
     """training.py:742-769."""
     out = forward_dense(p, cfg, tokens, targets)
@@ -925,6 +978,8 @@ class OracleTrainer:
             loss, info = dense_step_loss(leaves, self.cfg, tokens, targets)
         elif self.tr.mode == "recursive_exact":
             loss, info = exact_step_loss(leaves, self.cfg, self.tr, tokens, targets, self.usage_ema)
+        elif self.tr.mode == "recursive_deferred_grouped_exact":
+            loss, info = deferred_step_loss(leaves, self.cfg, self.tr, tokens, targets, self.usage_ema)
         else:
             loss, info = macro_step_loss(leaves, self.cfg, self.tr, tokens, targets, self.global_step, self.usage_ema,
                                          self.oc, self.top_clusters, audit_state=state)

@@ -114,6 +114,15 @@ GOLDEN_CASES = {
                    fixed_depth=None, audit_fixed_count_per_batch=None),
         steps=4,
     ),
+    # recursive_deferred_grouped_exact: ONE grouped block (three scheduled recipes summed per half) instead of passes
+    "small_deferred": dict(
+        model=dict(vocab_size=96, d_model=32, n_heads=4, d_ff=64, n_dense_layers=3, n_prelude=1, n_coda=1,
+                   t_max=4, depth_choices=(1, 2, 4), attn_banks=1, ffn_banks=1, head_groups=4, ffn_groups=4,
+                   active_head_groups=2, active_ffn_groups=2, recipe_count=5, macro_rank=8),
+        train=dict(mode="recursive_deferred_grouped_exact", lr=2e-3, weight_decay=0.05, batch_size=4, seq_len=12, seed=53,
+                   fixed_depth=None, audit_fixed_count_per_batch=None, fixed_recipe_schedule=(1, 3, 2)),
+        steps=6,
+    ),
     "small_dense": dict(
         model=dict(topology="dense", vocab_size=96, d_model=32, n_heads=4, d_ff=64, n_dense_layers=2, n_prelude=1,
                    n_coda=1, t_max=4, depth_choices=(1, 2, 4), attn_banks=1, ffn_banks=1, head_groups=4,
