@@ -105,6 +105,7 @@ class AuditReplay:
         self._prelude_copied = None
         self._core_fwd_done = self.distill_done = None
         self.fixed_rid = None                        # [T, n] int32 when `recursive_exact` runs a fixed recipe schedule
+        self.deferred_depth = 0                      # branches of the grouped block (recursive_deferred_grouped_exact)
         cfg, dev = eng.cfg, eng.device
         self.n, self.S, self.T = k, eng.S, cfg.t_max
         self.Ma = k * eng.S
@@ -700,6 +701,107 @@ class AuditReplay:
             self._scalar_grads()
             if eng._param_stream is not None:         # the replay's stream ends only when its weight gradients have
                 torch.cuda.current_stream(eng.device).wait_stream(eng._param_stream)
+
+    # ------------------------------------------------------------------ the grouped block (recursive_deferred_grouped_exact)
+    def forward_deferred(self, h0: torch.Tensor) -> None:
+        """`BankedRecursiveCore.deferred_grouped_block` (layers.py:872-912) over the whole batch, then coda and logits:
+        ONE block whose attention half and MLP half each sum the branches of the `deferred_depth` scheduled recipes;
+        every branch reads the same normed input under its own pass's FiLM and enters with its own pass's scale.
+        Pass t's buffers hold branch t (one bank each; `fixed_rid` holds the schedule)."""
+        eng = self.eng
+        o, cfg, p, sh = eng.ops, eng.cfg, eng.params, eng.shadow
+        n, S, T, Ma, d, f, V, D = self.n, self.S, self.T, self.Ma, cfg.d_model, cfg.d_ff, cfg.vocab_size, self.deferred_depth
+        o.gather_rows(h0, self.idx, self.h0a, n, S * d * 4)
+        o.gather_rows(eng.targets, self.idx, self.targets_a, n, S * 8)
+        self.rid.copy_(self.fixed_rid)
+        alpha = p["core.alpha_inj"].view(1)
+        film = lambda k, t: dict(film_gamma=p[f"core.pass_gamma{k}"][t], film_beta=p[f"core.pass_beta{k}"][t])      # noqa: E731
+        ht, u, out = self.ht[0], self.u[0], self.h[T]
+        # ht = h0 + alpha * h0 (the block starts from h = h0), normed once per branch under that branch's FiLM
+        o.residual_rmsnorm_fwd(self.h0a, self.h0a, alpha, ht, p["core.norm1.weight"], self.n1[0], self.rstd1[0], S=S, **film(1, 0))
+        for t in range(D):
+            if t:
+                o.rmsnorm_fwd(ht, p["core.norm1.weight"], self.n1[t], self.rstd1[t], **film(1, t))
+            o.gemm(self.n1[t], sh["core.attn.wqkv"][0], self.qkv[t][0], M=Ma, N=3 * d, K=d, b_mn=True)
+            o.attn_fwd_masked(self.qkv[t][0], self.y[t][0], self.ym[t][0], self.lse[t][0], self.rid[t], self.head_tab[0],
+                              B=n, S=S, n_heads=cfg.n_heads, head_dim=cfg.head_dim)
+            o.gemm(self.ym[t][0], sh["core.attn.wo"][0], self.attn_acc[t], M=Ma, N=d, K=d, b_mn=True, epilogue=A.EPI_F32)
+            o.scaled_residual_fwd(ht if t == 0 else u, self.attn_acc[t], p["core.pass_attn_scale"][t:t + 1], None, None, u,
+                                  n, S * d)                                   # u = ht + sum_t s_attn[t] * attn_t
+        for t in range(D):
+            o.rmsnorm_fwd(u, p["core.norm2.weight"], self.n2[t], self.rstd2[t], **film(2, t))
+            o.gemm(self.n2[t], sh["core.mlp.wug"][0], self.ug[t][0], M=Ma, N=2 * f, K=d, b_mn=True)
+            o.swiglu_masked_fwd(self.ug[t][0], self.rid[t], self.ffn_tab[0], S, self.zm[t][0], Ma, f)
+            o.gemm_f32_few_rows(self.zm[t][0], sh["core.mlp.wd"][0], self.mlp_acc[t], M=Ma, N=d, K=f, b_mn=True,
+                                ws=self.ws_chain)
+            o.scaled_residual_fwd(u if t == 0 else out, self.mlp_acc[t], p["core.pass_mlp_scale"][t:t + 1], None, None, out,
+                                  n, S * d)                                   # out = u + sum_t s_mlp[t] * mlp_t
+        x = out
+        for blk in self.coda:
+            x = eng._block_fwd(blk, x)
+        self.x_last = x
+        o.rmsnorm_fwd(x, p["final_norm.weight"], self.hidden16, self.rstd_f)
+        o.gemm(self.hidden16, sh["embed.weight"], self.logits, M=Ma, N=V, K=d)
+
+    def backward_deferred(self, dh_last: torch.Tensor) -> None:
+        """Backward of `forward_deferred` from the gradient wrt the block's output: every MLP branch sends its share
+        through norm2 into d u, every attention branch through norm1 into d ht; leaves `dh_first` (the part of d h0
+        through h) and `dh0_acc` (the part through alpha * h0) like `backward_core`."""
+        eng = self.eng
+        o, cfg, p, sh, g = eng.ops, eng.cfg, eng.params, eng.shadow, eng.grads
+        n, S, T, Ma, d, f, P, D = self.n, self.S, self.T, self.Ma, cfg.d_model, cfg.d_ff, self.P, self.deferred_depth
+        alpha = p["core.alpha_inj"].view(1)
+        fused = self.fused_wgrad
+        self._defer_param_grads(True)
+        du, dht = [b for b in (self.dcur, self.dalt, self.tmp.dxa, self.tmp.dxb) if b is not dh_last][:2]
+        for t in range(D):
+            d16m, dug16, acc = self.d16_mlp[t], self.dug16[t], t > 0
+            (pw2, pg2, pb2), _ = self.partials[t]
+            o.scaled_residual_bwd(dh_last, self.mlp_acc[t], p["core.pass_mlp_scale"][t:t + 1], None, None, d16m, None, None,
+                                  self.part_mlp[t * P:(t + 1) * P], n, S * d)
+            o.gemm(d16m, sh["core.mlp.wd"][0], self.dz16, M=Ma, N=f, K=d)
+            if not fused:
+                o.gemm_wgrad(self.zm[t][0], d16m, g["core.mlp.wd"][0], M=f, N=d, K=Ma, accumulate=acc, ws=self.ws)
+            o.swiglu_masked_bwd(self.ug[t][0], self.dz16, self.rid[t], self.ffn_tab[0], S, dug16, Ma, f)
+            o.gemm_f32_few_rows(dug16, sh["core.mlp.wug"][0], self.dn_f32, M=Ma, N=d, K=2 * f, b_mn=False, ws=self.ws_chain)
+            if not fused:
+                o.gemm_wgrad(self.n2[t], dug16, g["core.mlp.wug"][0], M=d, N=2 * f, K=Ma, accumulate=acc, ws=self.ws)
+            # d u = d out + sum_t norm2-backward of branch t (the running sum rides in as the residual gradient)
+            o.rmsnorm_bwd(self.u[0], p["core.norm2.weight"], self.rstd2[t], self.dn_f32, dh_last if t == 0 else du, du, None,
+                          g["core.norm2.weight"], pw2, film_gamma=p["core.pass_gamma2"][t],
+                          dgamma_out=g["core.pass_gamma2"][t], dbeta_out=g["core.pass_beta2"][t],
+                          partial_g=pg2, partial_b=pb2, accumulate_dw=acc)
+        for t in range(D):
+            d16a, dqkv16, acc = self.d16_attn[t], self.dqkv16[t], t > 0
+            _, (pw1, pg1, pb1) = self.partials[t]
+            o.scaled_residual_bwd(du, self.attn_acc[t], p["core.pass_attn_scale"][t:t + 1], None, None, d16a, None, None,
+                                  self.part_attn[t * P:(t + 1) * P], n, S * d)
+            o.gemm(d16a, sh["core.attn.wo"][0], self.d16b, M=Ma, N=d, K=d)
+            if not fused:
+                o.gemm_wgrad(self.ym[t][0], d16a, g["core.attn.wo"][0], M=d, N=d, K=Ma, accumulate=acc, ws=self.ws)
+            o.attn_bwd_masked(self.qkv[t][0], self.y[t][0], self.d16b, self.lse[t][0], dqkv16, self.rid[t], self.head_tab[0],
+                              B=n, S=S, n_heads=cfg.n_heads, head_dim=cfg.head_dim)
+            o.gemm_f32_few_rows(dqkv16, sh["core.attn.wqkv"][0], self.dn_f32, M=Ma, N=d, K=3 * d, b_mn=False, ws=self.ws_chain)
+            if not fused:
+                o.gemm_wgrad(self.n1[t], dqkv16, g["core.attn.wqkv"][0], M=d, N=3 * d, K=Ma, accumulate=acc, ws=self.ws)
+            o.rmsnorm_bwd(self.ht[0], p["core.norm1.weight"], self.rstd1[t], self.dn_f32, du if t == 0 else dht, dht, None,
+                          g["core.norm1.weight"], pw1, film_gamma=p["core.pass_gamma1"][t],
+                          dgamma_out=g["core.pass_gamma1"][t], dbeta_out=g["core.pass_beta1"][t],
+                          partial_g=pg1, partial_b=pb1, accumulate_dw=acc)
+        # ht = h + alpha * h0 with h = h0: d h (-> dh_first) and alpha * d ht (-> dh0_acc), d alpha from the partial sums
+        o.fill_(self.dh0_acc, 0.0)
+        o.scaled_residual_bwd(dht, self.h0a, alpha, None, du, None, self.dh0_acc, None, self.part_alpha[0:P], n, S * d)
+        self.dh_first = du
+        if fused:
+            st, K = self._stacked, D * Ma
+            o.gemm_wgrad(st["zm"], st["d16_mlp"], g["core.mlp.wd"][0], M=f, N=d, K=K, ws=self.ws)
+            o.gemm_wgrad(st["n2"], st["dug16"], g["core.mlp.wug"][0], M=d, N=2 * f, K=K, ws=self.ws)
+            o.gemm_wgrad(st["ym"], st["d16_attn"], g["core.attn.wo"][0], M=d, N=d, K=K, ws=self.ws)
+            o.gemm_wgrad(st["n1"], st["dqkv16"], g["core.attn.wqkv"][0], M=d, N=3 * d, K=K, ws=self.ws)
+        self._defer_param_grads(False)
+        self._scalar_grads()
+        if eng._param_stream is not None:
+            torch.cuda.current_stream(eng.device).wait_stream(eng._param_stream)
 
     def _scalar_grads(self) -> None:
         """Scalar parameters of the core: per-CTA partial sums -> gradients, in fixed order (slots of part_* beyond the

@@ -13,7 +13,9 @@ from dataclasses import dataclass, field, fields
 from pathlib import Path
 from typing import Any
 
-SUPPORTED_MODES = ("recursive_macro", "recursive_macro_shortlist", "recursive_exact", "dense_exact")
+SUPPORTED_MODES = ("recursive_macro", "recursive_macro_shortlist", "recursive_exact", "recursive_deferred_grouped_exact",
+                   "dense_exact")
+EXACT_MODES = ("recursive_exact", "recursive_deferred_grouped_exact")        # modes that never evaluate the macro operator
 REFERENCE_MODES = ("dense_exact", "recursive_exact", "recursive_deferred_grouped_exact", "recursive_exact_route_em",
                    "recursive_exact_factorized_soft", "recursive_exact_dense_hidden_distill", "recursive_sandwich_supernet",
                    "recursive_macro", "recursive_macro_shortlist", "recursive_macro_distill_only",
@@ -369,7 +371,7 @@ def unsupported(config: ExperimentConfig) -> list[str]:
                       ("macro_use_recipe_embedding", False), ("macro_decomposition", "direct")):
         # (mode recursive_exact never evaluates the macro operator: its variants then only add parameters the step
         #  carries untouched -- no influence on the arithmetic)
-        inert = key.startswith("macro_") and t.mode == "recursive_exact"
+        inert = key.startswith("macro_") and t.mode in EXACT_MODES
         if m.topology == "recursive" and getattr(m, key) != want and not inert:
             no("model", key, f"only {want!r} (the 3d -> rank -> d bounded-residual macro operator, macro.py:201-236)")
     if m.topology == "dense" and not m.tie_embeddings:
@@ -380,8 +382,10 @@ def unsupported(config: ExperimentConfig) -> list[str]:
             no("training", "audit_mode", "one of gradient_corrected, metric_only, distill_only")
         if t.macro_rms_trust_region or t.macro_rms_clamp_early:
             no("training", "macro_rms_trust_region", "the RMS trust region is not implemented")
-    if t.fixed_recipe_schedule is not None and t.mode != "recursive_exact":
-        no("training", "fixed_recipe_schedule", "per-pass fixed recipes are implemented for mode recursive_exact only")
+    if t.fixed_recipe_schedule is not None and t.mode not in EXACT_MODES:
+        no("training", "fixed_recipe_schedule", "per-pass fixed recipes are implemented for the exact modes only")
+    if t.mode == "recursive_deferred_grouped_exact" and (m.attn_banks != 1 or m.ffn_banks != 1):
+        no("model", "attn_banks" if m.attn_banks != 1 else "ffn_banks", "the grouped block is implemented for one bank each")
     if t.coda_warmup_steps:
         no("training", "coda_warmup_steps", "coda warm-up is not implemented")
     if t.debug_force_full_output and t.mode == "recursive_macro_shortlist":

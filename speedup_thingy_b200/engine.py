@@ -313,12 +313,15 @@ class TrainEngine:
         self.oc = config.output
         self.shortlist = tr.mode == "recursive_macro_shortlist"
         self.n_clusters = self.oc.num_clusters
-        self.exact = tr.mode == "recursive_exact"       # every sample runs the banked recurrent core (training.py:771-797)
+        # every sample runs the banked recurrent core (training.py:771-797), as t_max passes or -- `deferred` -- as one
+        # grouped block that sums the scheduled recipes (training.py:823-877)
+        self.deferred = tr.mode == "recursive_deferred_grouped_exact"
+        self.exact = tr.mode == "recursive_exact" or self.deferred
         self.audit_k = int(tr.audit_fixed_count_per_batch or 0) if tr.audits_enabled else 0
         # Bernoulli sampler (audit.py:79-132): the audited count varies per step, so the replay gets a fixed capacity --
         # the cap when one is set, otherwise the count B * p_max can reach plus six standard deviations (beyond it the
         # step raises through the status word rather than audit a different subset than the one drawn)
-        self.audit_bernoulli = (not self.dense and tr.mode != "recursive_exact" and tr.audits_enabled
+        self.audit_bernoulli = (not self.dense and not self.exact and tr.audits_enabled
                                 and tr.audit_fixed_count_per_batch is None)
         if self.audit_bernoulli:
             pm = min(max(float(tr.audit_p_max), 0.0), 1.0)
@@ -326,7 +329,7 @@ class TrainEngine:
             self.audit_k = min(self.B, bound if tr.audit_cap is None else int(tr.audit_cap))
         # Fixed-count schedule (audit.py:137-185): the count halves or doubles between steps, up to the whole batch; the
         # replay's buffers get the capacity `audit_capacity` (default: the batch), slots beyond the step's count idle
-        self.audit_scheduled = (not self.dense and tr.mode != "recursive_exact" and bool(self.audit_k)
+        self.audit_scheduled = (not self.dense and not self.exact and bool(self.audit_k)
                                 and not self.audit_bernoulli and tr.audit_schedule_enabled)
         if self.audit_scheduled:
             self.audit_count0 = min(self.audit_k, self.B)
@@ -568,7 +571,22 @@ class TrainEngine:
             from .audit import AuditReplay
             self.exact_core = AuditReplay(self, B, direct_grads=True)         # the replay machinery over the whole batch
             self.exact_core.idx.copy_(torch.arange(B, dtype=torch.int32))
-            if tr.fixed_recipe_schedule is not None:
+            if self.deferred:
+                # models.py:551-566: one recipe per branch of the grouped block -- `fixed_recipe` (default 1) repeated
+                # `fixed_depth` (default t_max) times, or the head of `fixed_recipe_schedule` with its last entry repeated
+                depth = max(1, min(int(tr.fixed_depth or cfg.t_max), cfg.t_max))
+                first = int(tr.fixed_recipe if tr.fixed_recipe is not None else 1)
+                sched = [int(r) for r in (tr.fixed_recipe_schedule or [])][:depth] or [first]
+                if tr.fixed_recipe_schedule is None:
+                    sched = [first] * depth
+                sched += [sched[-1]] * (depth - len(sched))
+                if any(not 0 <= r < cfg.recipe_count for r in sched):
+                    raise ValueError(f"deferred grouped recipe outside [0, {cfg.recipe_count})")
+                self.exact_schedule = sched
+                self.exact_core.deferred_depth = depth
+                self.exact_core.fixed_rid = (torch.tensor(sched + [0] * (cfg.t_max - depth), dtype=torch.int32).view(-1, 1)
+                                             .expand(cfg.t_max, B).contiguous().to(dev))
+            elif tr.fixed_recipe_schedule is not None:
                 # models.py:230-247, 449-451: pass t runs recipe schedule[t] for every sample, whatever the router chose
                 sched = [int(r) for r in tr.fixed_recipe_schedule]
                 if len(sched) < cfg.t_max:
@@ -940,7 +958,10 @@ class TrainEngine:
         o.router_fwd(h0, self._router_weight_dict(), self.depth_values, self.route, B=B, S=S, d=d,
                      hid=cfg.router_hidden_dim, R=cfg.recipe_count, K=len(cfg.depth_choices), T=cfg.t_max,
                      fixed_recipe=tr.fixed_recipe, fixed_depth_id=fixed_depth_id)
-        a.forward_replay(h0)
+        if self.deferred:
+            a.forward_deferred(h0)
+        else:
+            a.forward_replay(h0)
         o.ce_fwd_bwd(a.logits, a.targets_a, a.row_weight_a, S, a.loss_tok, a.logits)
         o.segment_sum(a.loss_tok, self.loss_per_sample, B, S)
         o.segment_sum(self.loss_per_sample, self.scalars[0:1], 1, B)
@@ -948,7 +969,10 @@ class TrainEngine:
             return
         # ---------------- backward
         self._begin_backward()
-        a.backward_core(a.backward_head())
+        if self.deferred:
+            a.backward_deferred(a.backward_head())
+        else:
+            a.backward_core(a.backward_head())
         dcur, dalt = a.dh0_acc, self.dxb
         o.add_(dcur, a.dh_first)                          # d h0 = through the alpha*h0 injections + through h[0]
         if not tr.disable_router_aux:

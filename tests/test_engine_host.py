@@ -439,3 +439,42 @@ def test_recursive_exact_carries_a_variant_macro_operator_untouched():
     for n in names:
         if n.startswith("macro."):
             assert torch.equal(eng.params[n], params[n]), n
+
+
+@pytest.mark.parametrize("fused", ["1", "0"])
+def test_deferred_grouped_exact_mode_follows_the_reference(fused, monkeypatch):
+    """`recursive_deferred_grouped_exact` (training.py:823-877, layers.py:872-912): one grouped block that sums the
+    scheduled recipes' branches.  First-step loss and every gradient against the oracle, the loss curve against the
+    golden the reference produced, the usage average counts the schedule; with the branches' weight gradients as one
+    product over all branches and as one product per branch."""
+    from pathlib import Path
+
+    from tests.golden.cases import GOLDEN_CASES
+    monkeypatch.setenv("RTE_REPLAY_FUSED_WGRAD", fused)
+    case = GOLDEN_CASES["small_deferred"]
+    gold = np.load(Path(__file__).resolve().parent / "golden" / "small_deferred.npz")
+    cfg = ExperimentConfig(ModelConfig(**case["model"]), TrainingConfig(**case["train"]), OutputConfig())
+    tr = cfg.training
+    params = init_parameters(cfg.model, seed=tr.seed)
+    eng = TrainEngine(cfg, {k: v.clone() for k, v in params.items()}, device="cpu", ops=EmulOps(), use_cuda_graph=False)
+    assert eng.exact_schedule == [1, 3, 2, 2] and eng.exact_core.fused_wgrad == (fused == "1")
+    oracle = O.OracleTrainer(O.ModelCfg(**case["model"]), O.TrainCfg(**case["train"]), {k: v.clone() for k, v in params.items()})
+    stream = O.zipf_tokens(tr.batch_size * tr.seq_len * (case["steps"] + 2) + 1, cfg.model.vocab_size, seed=tr.seed)
+    batches = [b for _, b in zip(range(case["steps"]), O.batches(stream, tr.batch_size, tr.seq_len))]
+    loss, grads = eng.loss_and_grads(batches[0])
+    ref_loss, ref_grads, _ = oracle.loss_and_grads(*batches[0])
+    assert abs(loss - float(ref_loss)) < 2e-2 and sorted(grads) == sorted(ref_grads)
+    for n, g in grads.items():
+        err, scale = (g - ref_grads[n]).abs().max().item(), ref_grads[n].abs().max().item()
+        assert err <= 2e-2 * max(scale, 1e-3) + 2e-4, (n, err, scale)
+    losses = [eng.train_step(b).loss for b in batches]
+    for b in batches:
+        oracle.train_step(*b)
+    rel = np.abs(np.array(losses) - gold["losses"]) / np.abs(gold["losses"])
+    assert rel.max() <= 1e-2, (rel.max(), losses, gold["losses"])
+    assert torch.allclose(eng.usage_ema, oracle.usage_ema, atol=1e-6)
+    for n in eng.trainable:
+        assert (eng.params[n] - oracle.params[n]).abs().max().item() <= 2.1 * tr.lr * len(batches), n
+    two_banks = ExperimentConfig(ModelConfig(**{**case["model"], "ffn_banks": 2}), TrainingConfig(**case["train"]), OutputConfig())
+    with pytest.raises(NotImplementedError, match="ffn_banks"):
+        TrainEngine(two_banks, params, device="cpu", ops=EmulOps(), use_cuda_graph=False)
