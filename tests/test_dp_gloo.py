@@ -71,35 +71,55 @@ AUDIT_TRAIN = dict(mode="recursive_macro", lr=2e-3, weight_decay=0.1, seq_len=16
                    audit_fixed_count_per_batch=1, grad_clip_norm=1.0)
 
 
-def _replicated_worker(rank, world, port, out_path):
+SAMPLERS = {
+    "fixed_count": {},
+    # subset drawn on the device from the step's routing; capacity-padded replay
+    "bernoulli": dict(audit_fixed_count_per_batch=None, audit_sampler="bernoulli", audit_p_min=0.3, audit_p_max=0.8,
+                      audit_alpha=0.5, audit_beta=1.0, audit_gamma=0.3, audit_cap=2),
+    # fixed count under the count schedule (each rank decides from its own shard's metrics: equal shards, equal counts)
+    "scheduled": dict(audit_fixed_count_per_batch=2, audit_schedule_enabled=True, audit_schedule_min_count=1,
+                      audit_schedule_nll_gap_threshold=0.3, audit_schedule_hidden_cosine_threshold=0.9,
+                      audit_schedule_delta_rms_ratio_min=0.0, audit_schedule_delta_rms_ratio_max=10.0,
+                      audit_schedule_require_negative_mse_slope=False, audit_schedule_require_negative_norm_slope=False),
+}
+
+
+def _replicated_worker(rank, world, port, out_path, sampler="fixed_count"):
     os.environ["MASTER_ADDR"], os.environ["MASTER_PORT"] = "127.0.0.1", str(port)
     dist.init_process_group("gloo", rank=rank, world_size=world)
     torch.set_num_threads(1)
-    cfg = ExperimentConfig(ModelConfig(**MODEL), TrainingConfig(**{**AUDIT_TRAIN, "batch_size": 4}))
+    cfg = ExperimentConfig(ModelConfig(**MODEL), TrainingConfig(**{**AUDIT_TRAIN, **SAMPLERS[sampler], "batch_size": 4}))
     eng = TrainEngine(cfg, init_parameters(cfg.model, seed=3), device="cpu", ops=EmulOps(), use_cuda_graph=False,
                       process_group=dist.group.WORLD, bucket_cap_mb=0.05)
     x, y = _batch()
-    losses = [eng.train_step((x[:4], y[:4])).loss for _ in range(3)]
+    results = [eng.train_step((x[:4], y[:4])) for _ in range(3)]
     if rank == 0:
-        torch.save({"losses": losses, "params": {k: v.clone() for k, v in eng.params.items()}}, out_path)
+        torch.save({"losses": [r.loss for r in results], "counts": [r.metrics["audit_count"] for r in results],
+                    "params": {k: v.clone() for k, v in eng.params.items()}}, out_path)
     dist.barrier()
     dist.destroy_process_group()
 
 
-def test_two_ranks_with_the_same_shard_equal_one_process_with_audit(tmp_path):
-    """With an audited sample per rank (its gradients reach the buckets from the replay's side of the step, and the
+@pytest.mark.parametrize("sampler", list(SAMPLERS))
+def test_two_ranks_with_the_same_shard_equal_one_process_with_audit(tmp_path, sampler):
+    """With audited samples per rank (their gradients reach the buckets from the replay's side of the step, and the
     prelude's only after the last join), two ranks that hold the SAME shard must reproduce the single-process run:
-    every gradient is g/2 + g/2."""
+    every gradient is g/2 + g/2 -- for the fixed-count sampler, the Bernoulli sampler with a cap and the count
+    schedule alike (same shard, same seeds: the same subsets and the same counts on both ranks)."""
     with socket.socket() as s:
         s.bind(("127.0.0.1", 0))
         port = s.getsockname()[1]
     out = tmp_path / "rank0.pt"
-    mp.spawn(_replicated_worker, args=(2, port, str(out)), nprocs=2, join=True)
+    mp.spawn(_replicated_worker, args=(2, port, str(out), sampler), nprocs=2, join=True)
     got = torch.load(out)
-    cfg = ExperimentConfig(ModelConfig(**MODEL), TrainingConfig(**{**AUDIT_TRAIN, "batch_size": 4}))
+    cfg = ExperimentConfig(ModelConfig(**MODEL), TrainingConfig(**{**AUDIT_TRAIN, **SAMPLERS[sampler], "batch_size": 4}))
     single = TrainEngine(cfg, init_parameters(cfg.model, seed=3), device="cpu", ops=EmulOps(), use_cuda_graph=False)
     x, y = _batch()
-    losses = [single.train_step((x[:4], y[:4])).loss for _ in range(3)]
+    results = [single.train_step((x[:4], y[:4])) for _ in range(3)]
+    losses = [r.loss for r in results]
+    assert [r.metrics["audit_count"] for r in results] == got["counts"]
+    if sampler != "fixed_count":
+        assert len(set(got["counts"])) > 1 or sampler == "bernoulli"         # the schedule moved the count
     for a, b in zip(losses, got["losses"]):
         assert abs(a - b) <= 2e-3 * abs(a), (losses, got["losses"])
     for n, p in single.params.items():
