@@ -386,8 +386,7 @@ def unsupported(config: ExperimentConfig) -> list[str]:
         no("training", "fixed_recipe_schedule", "per-pass fixed recipes are implemented for the exact modes only")
     if t.mode == "recursive_deferred_grouped_exact" and (m.attn_banks != 1 or m.ffn_banks != 1):
         no("model", "attn_banks" if m.attn_banks != 1 else "ffn_banks", "the grouped block is implemented for one bank each")
-    if t.coda_warmup_steps:
-        no("training", "coda_warmup_steps", "coda warm-up is not implemented")
+    # (coda_warmup_steps only gates the phases of mode recursive_macro_lm_aligned, training.py:262-277: no influence here)
     if t.debug_force_full_output and t.mode == "recursive_macro_shortlist":
         no("training", "debug_force_full_output", "not implemented for the shortlist mode")
     if (t.mode == "recursive_macro_shortlist") != (config.output.mode == "shortlist") and t.mode in SUPPORTED_MODES:
