@@ -1,5 +1,5 @@
 """SVD-factor sparse SwiGLU FFN on the sm_100a kernels: the counterpart of the reference's ``SVDFactorSparseFFN``
-in mask mode (layers.py:342-643) and of ``triton_svd_sparse_ffn_forward`` (svd_sparse_ffn_triton.py:480-714).
+in mask and slots mode (layers.py:342-643) and of ``triton_svd_sparse_ffn_forward`` (svd_sparse_ffn_triton.py:480-714).
 
 The reference scores all F neurons with two low-rank products, takes three top-m lists, gathers the candidate
 weight rows per token (``w_up[candidate_ids]``: an [N, candidates, d] tensor), evaluates them exactly, re-ranks
@@ -27,7 +27,17 @@ class SVDFactorSparseFFN:
     factors up_a / gate_a [d_model, rank], up_b / gate_b [rank, d_ff]."""
 
     def __init__(self, w_up, w_gate, w_down, up_a, up_b, gate_a, gate_b, *, top_k: int, up_m: int,
-                 gate_m: int | None = None, product_m: int = 0, max_tokens: int, ops: CudaOps | None = None):
+                 gate_m: int | None = None, product_m: int = 0, max_tokens: int, ops: CudaOps | None = None,
+                 candidate_mode: str = "mask"):
+        # "mask" (layers.py:473-502) keeps the union of the three candidate lists as a mask, "slots" (layers.py:504-527)
+        # as their concatenation with first occurrences valid: the same SET of candidates as long as no token falls
+        # short of top_k of them -- which the limit below rules out (one list alone holds top_k distinct neurons) -- so
+        # both modes select the same neurons and give the same output (the reference's own two outputs are equal on
+        # the golden inputs, tests/golden/svd_ffn.npz); only the reported slot count differs
+        if candidate_mode not in ("mask", "slots"):
+            raise NotImplementedError(f"candidate_mode={candidate_mode!r}: 'mask' and 'slots' are implemented "
+                                      "(the Triton path of the reference is not translated)")
+        self.candidate_mode = candidate_mode
         if not (w_up.is_cuda and w_gate.is_cuda and w_down.is_cuda):
             raise RuntimeError("strict_cuda: SVDFactorSparseFFN needs CUDA tensors (no CPU or Triton path)")
         self.ops = ops if ops is not None else CudaOps(w_up.device)
@@ -104,6 +114,12 @@ class SVDFactorSparseFFN:
     @property
     def avg_candidate_size(self) -> float:
         return float(self.cand_count[: self._tokens].float().mean())
+
+    @property
+    def candidate_slots(self) -> int:
+        """`candidate_slots` of the reference's aux (layers.py:636-640): the width of its candidate id table."""
+        total = self.up_m + self.gate_m + self.product_m
+        return total if self.candidate_mode == "slots" else min(self.F, max(self.top_k, total))
 
 
 class _SvdFfnFn(torch.autograd.Function):

@@ -222,9 +222,16 @@ def svd_ffn_vectors() -> dict[str, np.ndarray]:
     out, aux = mod(x, return_aux=True)
     (out * t["probe"]).sum().backward()
     sel = torch.zeros(x.shape[0] * x.shape[1], c["f"], dtype=torch.bool).scatter_(-1, aux["selected_ids"], True)
+    # the same module in slots mode (layers.py:504-527: the three lists concatenated, first occurrences valid)
+    mod.candidate_mode = "slots"
+    with torch.no_grad():
+        out_slots, aux_slots = mod(t["x"], return_aux=True)
+    sel_slots = torch.zeros_like(sel).scatter_(-1, aux_slots["selected_ids"], True)
     return {"out": out.detach().numpy(), "selected": sel.numpy(), "avg_candidate_size": np.float64(aux["avg_candidate_size"]),
             "dx": x.grad.numpy(), "dw_up": mod.w_up.grad.numpy(), "dw_gate": mod.w_gate.grad.numpy(),
-            "dw_down": mod.w_down.grad.numpy()}
+            "dw_down": mod.w_down.grad.numpy(), "out_slots": out_slots.numpy(), "selected_slots": sel_slots.numpy(),
+            "avg_candidate_size_slots": np.float64(aux_slots["avg_candidate_size"]),
+            "candidate_slots_slots": np.float64(aux_slots["candidate_slots"])}
 
 
 def codebook_vectors() -> dict[str, np.ndarray]:

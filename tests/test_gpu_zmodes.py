@@ -67,3 +67,23 @@ def test_deferred_grouped_exact_mode():
     _grads_match(eng, case, params, batches[0])
     _, _, _, graphed, _, _ = _run("small_deferred")
     _curve_matches(graphed, batches, gold)
+
+
+def test_svd_ffn_slots_mode_equals_mask_mode_and_the_reference():
+    """`candidate_mode="slots"` (layers.py:504-527): the same selected neurons and output as mask mode, and the
+    reference's slots-mode output on the golden inputs."""
+    from speedup_thingy_b200.svd_ffn import SVDFactorSparseFFN
+    from tests.golden.cases import SVD_FFN, svd_ffn_inputs
+    c, t = SVD_FFN, svd_ffn_inputs()
+    gold = np.load(GOLDEN / "svd_ffn.npz")
+    outs = {}
+    for mode in ("mask", "slots"):
+        dev = lambda k: t[k].to("cuda:0")  # noqa: E731
+        m = SVDFactorSparseFFN(dev("w_up"), dev("w_gate"), dev("w_down"), t["up_a"], t["up_b"], t["gate_a"], t["gate_b"],
+                               top_k=c["top_k"], up_m=c["up_m"], gate_m=c["gate_m"], product_m=c["product_m"], max_tokens=64,
+                               candidate_mode=mode)
+        outs[mode] = (m.forward(t["x"].to("cuda:0")).cpu(), m.selected[:33].cpu().clone(), m.candidate_slots)
+    assert torch.equal(outs["mask"][0], outs["slots"][0]) and torch.equal(outs["mask"][1], outs["slots"][1])
+    assert outs["slots"][2] == int(gold["candidate_slots_slots"])
+    ref = torch.from_numpy(gold["out_slots"])
+    assert (outs["slots"][0].view_as(ref) - ref).abs().max() <= 2e-2 * ref.abs().max()

@@ -261,3 +261,28 @@ def test_fixed_count_schedule_decisions():
     default_min = O.TrainCfg(batch_size=512, audit_fixed_count_per_batch=8, audit_schedule_enabled=True)
     assert O.audit_schedule_next_count(default_min, 8, good, 512, {}) == 4    # minimum defaults to batch // 128
     assert O.audit_schedule_next_count(default_min, 4, good, 512, {}) == 4
+
+
+def test_svd_ffn_slots_mode_of_the_reference_equals_its_mask_mode():
+    """layers.py:473-527: with one candidate list at least top_k long no token falls short of top_k candidates, so the
+    concatenated lists (slots) and their union mask hold the same set: the reference selected the same neurons and
+    produced the same output in both modes on the golden inputs -- what lets one kernel serve both."""
+    from pathlib import Path
+
+    from tests.golden.cases import SVD_FFN
+    gold = np.load(Path(__file__).resolve().parent / "golden" / "svd_ffn.npz")
+    assert max(SVD_FFN["up_m"], SVD_FFN["gate_m"], SVD_FFN["product_m"]) >= SVD_FFN["top_k"]
+    assert np.array_equal(gold["selected"], gold["selected_slots"])
+    assert np.array_equal(gold["out"], gold["out_slots"])
+    assert float(gold["avg_candidate_size"]) == float(gold["avg_candidate_size_slots"])
+    assert int(gold["candidate_slots_slots"]) == SVD_FFN["up_m"] + SVD_FFN["gate_m"] + SVD_FFN["product_m"]
+
+
+def test_svd_ffn_module_accepts_both_candidate_modes_and_refuses_the_rest():
+    from speedup_thingy_b200.svd_ffn import SVDFactorSparseFFN
+    w = torch.zeros(64, 32)
+    a, b = torch.zeros(32, 8), torch.zeros(8, 64)
+    with pytest.raises(NotImplementedError, match="candidate_mode"):
+        SVDFactorSparseFFN(w, w, w, a, b, a, b, top_k=8, up_m=8, max_tokens=4, candidate_mode="triton")
+    with pytest.raises(RuntimeError, match="strict_cuda"):          # a known mode gets as far as the device check
+        SVDFactorSparseFFN(w, w, w, a, b, a, b, top_k=8, up_m=8, max_tokens=4, candidate_mode="slots")
